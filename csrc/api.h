@@ -1,0 +1,116 @@
+// Raw-pointer launch API of the native library.  Everything here is torch-free; the tensor
+// glue in bindings.cpp fills these structs from torch tensors.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rt {
+
+// ------------------------------------------------------------------ gemm/gemm_tcgen05.cu
+enum EpiMode : int {
+  EPI_NONE = 0,       // C = alpha*acc (+bias)
+  EPI_GELU_DUAL = 1,  // aux = alpha*acc+bias ; C = gelu(aux)
+  EPI_DGELU = 2,      // C = alpha*acc * gelu'(aux)
+  EPI_RESIDUAL = 3,   // C = alpha*acc + bias + aux
+};
+
+struct GemmArgs {
+  const void* a;  // K-major: [batch][M][K] ; MN-major: [batch][K][M]  (bf16)
+  bool a_mn;
+  long long lda, a_batch_stride;  // in elements
+  const void* b;  // K-major: [batch][N][K] ; MN-major: [batch][K][N]  (bf16)
+  bool b_mn;
+  long long ldb, b_batch_stride;
+  void* c;  // [batch][M][N] bf16 or fp32
+  long long ldc, c_batch_stride;
+  bool out_fp32;
+  const void* bias;  // bf16 [N] or null
+  void* aux;         // bf16, geometry of C, or null
+  long long ld_aux, aux_batch_stride;
+  int M, N, K, batch;
+  int epi_mode;
+  float alpha;
+  bool accumulate;  // fp32 C only: C += result with float atomics
+  int split_k;
+  int block_n;  // 0 = auto, 128 or 256
+};
+void gemm_bf16(const GemmArgs& g, cudaStream_t stream);
+
+// ------------------------------------------------------- attention/flash_{fwd,bwd}.cu
+// q: [B][Tq][H][D], k/v: [B][Tk][Hkv][D] as strided views (strides in elements, D contiguous).
+struct AttnArgs {
+  const void *q, *k, *v;
+  long long q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh;
+  void* o;  // bf16, [B][Tq][H][D] strided
+  long long o_sb, o_st, o_sh;
+  float* lse;  // [B][H][Tq] natural-log sum-exp of the scaled scores
+  int B, H, Hkv, Tq, Tk, D;
+  int causal;
+  float scale;
+  // backward only
+  const void* d_o;  // same strides as o
+  float* delta;     // [B][H][Tq] scratch: rowsum(o * do)
+  void *dq, *dk, *dv;  // bf16, strides below
+  long long dq_sb, dq_st, dq_sh, dk_sb, dk_st, dk_sh, dv_sb, dv_st, dv_sh;
+};
+void attn_fwd(const AttnArgs& a, cudaStream_t stream);
+void attn_bwd(const AttnArgs& a, cudaStream_t stream);
+
+// ----------------------------------------------------------------------- norm/norm.cu
+struct NormArgs {
+  const void* x;      // bf16 [rows][C]
+  const void* gamma;  // bf16 [C]
+  const void* beta;   // bf16 [C] or null (ignored for RMSNorm)
+  void* y;            // bf16 [rows][C]               (forward)
+  float* mean;        // fp32 [rows] (LayerNorm only; may be null for RMSNorm)
+  float* rstd;        // fp32 [rows]
+  long long rows;
+  int C;
+  float eps;
+  bool rms;
+  // backward
+  const void* dy;    // bf16 [rows][C]
+  const void* dres;  // bf16 [rows][C] or null: added to dx
+  void* dx;          // bf16 [rows][C]
+  float* dgamma;     // fp32 [C], accumulated into (may be null)
+  float* dbeta;      // fp32 [C], accumulated into (may be null)
+};
+void norm_fwd(const NormArgs& a, cudaStream_t stream);
+void norm_bwd(const NormArgs& a, cudaStream_t stream);
+
+// ------------------------------------------------------------------- nn/embedding.cu
+void embedding_fwd(const long long* idx, const void* wte, const void* wpe, void* out,
+                   long long rows, int T, int C, int vocab, cudaStream_t stream);
+void embedding_bwd(const long long* idx, const void* dout, float* dwte, float* dwpe,
+                   long long rows, int T, int C, int vocab, cudaStream_t stream);
+
+// ------------------------------------------------------------- loss/cross_entropy.cu
+// logits: bf16 [rows][ld] (ld >= vocab, ld % 8 == 0), overwritten with the gradient.
+void cross_entropy_fwd_bwd(void* logits, const long long* targets, float* loss, long long rows,
+                           int vocab, int ld, float grad_scale, long long ignore_index,
+                           cudaStream_t stream);
+
+// ------------------------------------------------------------------ reduce/reduce.cu
+void colsum_accum(const void* x_bf16, float* out, long long M, int N, long long ld,
+                  cudaStream_t stream);
+// dtype: 0 fp32, 1 bf16.  mode: 0 sum, 1 sum of squares, 2 max, 3 min.  *out pre-initialised.
+void reduce_all(const void* x, int dtype, int mode, float* out, long long n, cudaStream_t stream);
+
+// --------------------------------------------------------------- optim/fused_optim.cu
+enum OptimMode : int { OPT_ADAMW = 0, OPT_ADAM = 1, OPT_SGD = 2 };
+struct OptimArgs {
+  float* master;   // fp32 parameters [n]
+  float* grad;     // fp32 gradients  [n]
+  float* m;        // first moment / momentum buffer (null for plain SGD)
+  float* v;        // second moment (null for SGD)
+  void* param_lp;  // bf16 copy of the parameters to refresh, or null
+  long long n;
+  float lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, grad_scale;
+  int mode;
+  int zero_grad;
+  int nesterov;
+  int first_step;
+};
+void fused_optim_step(const OptimArgs& a, cudaStream_t stream);
+
+}  // namespace rt

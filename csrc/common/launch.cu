@@ -1,0 +1,125 @@
+#include "launch.h"
+
+#include <atomic>
+#include <mutex>
+
+namespace rt {
+
+namespace {
+std::atomic<long long> g_launches{0};
+std::mutex g_mu;
+int* g_status[64] = {nullptr};
+int g_sms[64] = {0};
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                              const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    RT_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    RT_CHECK(p != nullptr && q == cudaDriverEntryPointSuccess,
+             "cuTensorMapEncodeTiled not available from the driver");
+    fn = reinterpret_cast<EncodeFn>(p);
+  }
+  return fn;
+}
+}  // namespace
+
+void fail(const std::string& msg) { throw std::runtime_error(msg); }
+
+long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+int current_device() {
+  int d = 0;
+  RT_CUDA_CHECK(cudaGetDevice(&d));
+  return d;
+}
+
+int sm_count(int device) {
+  if (g_sms[device] == 0) {
+    int v = 0;
+    RT_CUDA_CHECK(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device));
+    g_sms[device] = v;
+  }
+  return g_sms[device];
+}
+
+int* status_word(int device) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_status[device]) {
+    int prev = current_device();
+    RT_CUDA_CHECK(cudaSetDevice(device));
+    int* p = nullptr;
+    RT_CUDA_CHECK(cudaMalloc(&p, sizeof(int) * 16));
+    RT_CUDA_CHECK(cudaMemset(p, 0, sizeof(int) * 16));
+    RT_CUDA_CHECK(cudaSetDevice(prev));
+    g_status[device] = p;
+  }
+  return g_status[device];
+}
+
+int read_status(int device) {
+  int* p = status_word(device);
+  int prev = current_device();
+  RT_CUDA_CHECK(cudaSetDevice(device));
+  int v = 0;
+  RT_CUDA_CHECK(cudaDeviceSynchronize());
+  RT_CUDA_CHECK(cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost));
+  if (v != 0) RT_CUDA_CHECK(cudaMemset(p, 0, sizeof(int)));
+  RT_CUDA_CHECK(cudaSetDevice(prev));
+  return v;
+}
+
+CUtensorMap make_tmap_2byte(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                            uint64_t stride1_elems, uint64_t stride2_elems, uint32_t b0,
+                            uint32_t b1) {
+  RT_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base must be 16-byte aligned");
+  RT_CHECK((stride1_elems * 2) % 16 == 0,
+           "TMA row stride must be a multiple of 16 bytes (got " + std::to_string(stride1_elems) +
+               " elements)");
+  RT_CHECK(d2 == 1 || (stride2_elems * 2) % 16 == 0,
+           "TMA batch stride must be a multiple of 16 bytes");
+  CUtensorMap m;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_elems * 2, (d2 == 1 ? stride1_elems * d1 : stride2_elems) * 2};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims,
+                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  RT_CHECK(r == CUDA_SUCCESS,
+           "cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)) + " dims=" +
+               std::to_string(d0) + "," + std::to_string(d1) + "," + std::to_string(d2) +
+               " strides=" + std::to_string(strides[0]) + "," + std::to_string(strides[1]) +
+               " box=" + std::to_string(b0) + "," + std::to_string(b1));
+  return m;
+}
+
+CUtensorMap make_tmap_2byte_4d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                               uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3, uint32_t b0,
+                               uint32_t b1) {
+  RT_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base must be 16-byte aligned");
+  RT_CHECK((s1 * 2) % 16 == 0 && (s2 * 2) % 16 == 0 && (s3 * 2) % 16 == 0,
+           "TMA strides must be multiples of 16 bytes");
+  CUtensorMap m;
+  cuuint64_t dims[4] = {d0, d1, d2, d3};
+  cuuint64_t strides[3] = {s1 * 2, s2 * 2, s3 * 2};
+  cuuint32_t box[4] = {b0, b1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims,
+                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  RT_CHECK(r == CUDA_SUCCESS,
+           "cuTensorMapEncodeTiled(4d) failed with code " + std::to_string(int(r)));
+  return m;
+}
+
+}  // namespace rt

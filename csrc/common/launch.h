@@ -1,0 +1,59 @@
+// Host-side helpers shared by every launcher.  Torch-free on purpose: kernel translation
+// units include only this and compile in seconds; the tensor-facing glue lives in
+// csrc/bindings.cpp.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <stdexcept>
+#include <string>
+
+namespace rt {
+
+// Number of kernels launched by this library since process start.
+long long launch_count();
+void count_launch(int n = 1);
+
+// One int32 status word per device, zero while healthy.  Kernels CAS an error code into
+// it when a bounded wait expires (see ptx.cuh); read_status() synchronises the device and
+// returns + clears it.
+int* status_word(int device);
+int read_status(int device);
+
+int current_device();
+int sm_count(int device);
+
+[[noreturn]] void fail(const std::string& msg);
+
+#define RT_CHECK(cond, msg)                                       \
+  do {                                                            \
+    if (!(cond)) ::rt::fail(std::string("rustorch_b200: ") + msg); \
+  } while (0)
+
+#define RT_CUDA_CHECK(expr)                                                               \
+  do {                                                                                    \
+    cudaError_t _e = (expr);                                                              \
+    if (_e != cudaSuccess)                                                                \
+      ::rt::fail(std::string(#expr) + " failed: " + cudaGetErrorString(_e));              \
+  } while (0)
+
+#define RT_LAUNCH_CHECK()                                                                 \
+  do {                                                                                    \
+    cudaError_t _e = cudaGetLastError();                                                  \
+    if (_e != cudaSuccess)                                                                \
+      ::rt::fail(std::string("kernel launch failed: ") + cudaGetErrorString(_e));         \
+    ::rt::count_launch();                                                                 \
+  } while (0)
+
+// Tiled 2-byte-element tensor map over a [d2][d1][d0] array (d0 contiguous) with a
+// 128-byte swizzle.  Strides in elements.  box = {b0, b1, 1}.
+CUtensorMap make_tmap_2byte(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                            uint64_t stride1_elems, uint64_t stride2_elems, uint32_t b0,
+                            uint32_t b1);
+// Rank-4 variant: [d3][d2][d1][d0], box = {b0, b1, 1, 1}.
+CUtensorMap make_tmap_2byte_4d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                               uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3, uint32_t b0,
+                               uint32_t b1);
+
+}  // namespace rt

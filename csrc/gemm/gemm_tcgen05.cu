@@ -1,0 +1,432 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a:
+//   TMA (plain per-CTA tiled loads, 128B swizzle) -> shared-memory ring
+//   -> tcgen05.mma (one issuing thread, fp32 accumulators in TMEM, double buffered)
+//   -> tcgen05.ld epilogue (bias / GELU / dGELU / residual / fp32 atomic accumulate).
+//
+//   C[b][m][n] = alpha * sum_k A[b][m][k] * B[b][n][k]   (+ epilogue)
+//
+// Each operand is either "K-major" (reduction dim contiguous: A stored [M][K], B stored
+// [N][K]) or "MN-major" (A stored [K][M], B stored [K][N]).  That covers the three GEMMs of
+// a Linear layer without any transposed copies:
+//   forward  y  = x W^T      : A K-major (x),  B K-major (W[out][in])
+//   dgrad    dx = dy W       : A K-major (dy), B MN-major (W as [K=out][N=in])
+//   wgrad    dW = dy^T x     : A MN-major (dy as [K=tokens][M=out]), B MN-major (x)
+// The reference's GPU matmul is a cuBLAS SGEMM wrapped in host<->device copies
+// (src/gpu/cuda_enhanced.rs:122-159) plus naive/tiled scalar kernels
+// (src/gpu/cuda_kernels.cu:59-75); this file replaces all of them.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (TMEM lane quarter = warp_id % 4).
+#include "../api.h"
+#include "../common/launch.h"
+#include "../common/ptx.cuh"
+
+namespace rt {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+
+struct GemmParams {
+  int M, N, K, batch;
+  void* C;
+  long long ldc, c_batch_stride;
+  const __nv_bfloat16* bias;  // [N] or null
+  __nv_bfloat16* aux;         // same geometry as C (bf16) or null
+  long long ld_aux, aux_batch_stride;
+  float alpha;
+  int epi_mode;
+  int out_fp32;    // C is fp32 instead of bf16
+  int accumulate;  // fp32 only: C += result using red.global.add.f32 (required when split_k > 1)
+  int split_k;
+  int m_blocks, n_blocks, k_blocks;
+  int* status;
+};
+
+template <int BLOCK_N>
+struct GemmSmem {
+  static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
+  static constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BLOCK_N == 256) ? 4 : 6;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem base, ctl
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
+};
+
+__device__ __forceinline__ void decode_tile(int t, const GemmParams& p, int& split, int& b,
+                                            int& mb, int& nb) {
+  const int tiles_per_mat = p.m_blocks * p.n_blocks;
+  const int per_batch = tiles_per_mat * p.split_k;
+  b = t / per_batch;
+  int r = t - b * per_batch;
+  split = r / tiles_per_mat;
+  r -= split * tiles_per_mat;
+  // grouped ordering: walk N fastest inside bands of 8 M-blocks so co-resident CTAs share
+  // A and B tiles through L2.
+  constexpr int GROUP = 8;
+  const int band = GROUP * p.n_blocks;
+  const int g = r / band;
+  const int first_m = g * GROUP;
+  const int rows = min(GROUP, p.m_blocks - first_m);
+  const int in_band = r - g * band;
+  mb = first_m + in_band % rows;
+  nb = in_band / rows;
+}
+
+template <int BLOCK_N, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  using S = GemmSmem<BLOCK_N>;
+  constexpr int STAGES = S::STAGES;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023) {  // swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, RT_ERR_BOUNDS);
+    return;
+  }
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  CtaCtl* ctl = reinterpret_cast<CtaCtl*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // 256 or 512, power of two
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);
+    }
+    ctl->abort = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  const int total_tiles = p.batch * p.m_blocks * p.n_blocks * p.split_k;
+  const int kb_per_split = (p.k_blocks + p.split_k - 1) / p.split_k;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int split, b, mb, nb;
+        decode_tile(t, p, split, b, mb, nb);
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(p.k_blocks, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * S::STAGE_BYTES;
+          uint8_t* sb = sa + S::A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[s], S::STAGE_BYTES);
+          if (!A_MN) {
+            tma_load_3d(sa, &tmap_a, &full_bar[s], kb * BLOCK_K, mb * BLOCK_M, b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BLOCK_M / 64; ++c)
+              tma_load_3d(sa + c * 8192, &tmap_a, &full_bar[s], mb * BLOCK_M + c * 64,
+                          kb * BLOCK_K, b);
+          }
+          if (!B_MN) {
+            tma_load_3d(sb, &tmap_b, &full_bar[s], kb * BLOCK_K, nb * BLOCK_N, b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BLOCK_N / 64; ++c)
+              tma_load_3d(sb + c * 8192, &tmap_b, &full_bar[s], nb * BLOCK_N + c * 64,
+                          kb * BLOCK_K, b);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(BLOCK_M, BLOCK_N, A_MN, B_MN, true);
+      uint32_t it = 0;
+      uint32_t tile_i = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
+        int split, b, mb, nb;
+        decode_tile(t, p, split, b, mb, nb);
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(p.k_blocks, kb0 + kb_per_split);
+        const uint32_t acc = tile_i & 1;
+        const uint32_t acc_ph = (tile_i >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, ctl, p.status, RT_ERR_TIMEOUT_MMA)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * S::STAGE_BYTES);
+          const uint32_t sb = sa + S::A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+            const uint64_t adesc = A_MN ? make_smem_desc_sw128(sa + kk * (UMMA_K * 128), 8192, 1024)
+                                        : make_smem_desc_sw128(sa + kk * (UMMA_K * 2), 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc_sw128(sb + kk * (UMMA_K * 128), 8192, 1024)
+                                        : make_smem_desc_sw128(sb + kk * (UMMA_K * 2), 16, 1024);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);  // frees the smem stage when these MMAs retire
+        }
+        if (ok) umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else {
+    // ----------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    uint32_t tile_i = 0;
+    bool ok = true;
+    const bool vec_ok = ((p.ldc & 7) == 0) && (p.aux == nullptr || (p.ld_aux & 7) == 0);
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
+      int split, b, mb, nb;
+      decode_tile(t, p, split, b, mb, nb);
+      const uint32_t acc = tile_i & 1;
+      const uint32_t acc_ph = (tile_i >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_ph, ctl, p.status, RT_ERR_TIMEOUT_EPILOGUE)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int m = mb * BLOCK_M + row_in_tile;
+      const bool row_ok = m < p.M;
+      const bool add_bias = (p.bias != nullptr) && (split == 0);
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        const int n0 = nb * BLOCK_N + c * 32;
+        if (n0 >= p.N) break;  // warp-uniform
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + acc * BLOCK_N + c * 32 + (uint32_t(quarter * 32) << 16);
+        __syncwarp();
+        tmem_ld_32x32b_x32(taddr, r);
+        tmem_ld_wait();
+        if (row_ok) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        const bool full_chunk = (n0 + 32 <= p.N) && vec_ok;
+        if (add_bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (n0 + j < p.N) v[j] += __bfloat162float(p.bias[n0 + j]);
+        }
+        __nv_bfloat16* aux_row =
+            p.aux ? p.aux + (long long)b * p.aux_batch_stride + (long long)m * p.ld_aux + n0
+                  : nullptr;
+        if (p.epi_mode == EPI_GELU_DUAL) {
+          if (full_chunk) {
+            uint4* dst = reinterpret_cast<uint4*>(aux_row);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 w;
+              w.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              w.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              w.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              w.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              dst[q] = w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) aux_row[j] = __float2bfloat16(v[j]);
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(__bfloat162float(__float2bfloat16(v[j])));
+        } else if (p.epi_mode == EPI_DGELU || p.epi_mode == EPI_RESIDUAL) {
+          float a[32];
+          if (full_chunk) {
+            const uint4* src = reinterpret_cast<const uint4*>(aux_row);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 w = src[q];
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float2 f = __bfloat1622float2(h[e]);
+                a[q * 8 + e * 2] = f.x;
+                a[q * 8 + e * 2 + 1] = f.y;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) a[j] = (n0 + j < p.N) ? __bfloat162float(aux_row[j]) : 0.f;
+          }
+          if (p.epi_mode == EPI_DGELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= gelu_tanh_grad(a[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += a[j];
+          }
+        }
+        if (p.out_fp32) {
+          float* crow = reinterpret_cast<float*>(p.C) + (long long)b * p.c_batch_stride +
+                        (long long)m * p.ldc + n0;
+          if (p.accumulate) {
+            if (full_chunk) {
+              float4* dst = reinterpret_cast<float4*>(crow);
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                atomicAdd(dst + q, make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + j < p.N) atomicAdd(crow + j, v[j]);
+            }
+          } else if (full_chunk) {
+            float4* dst = reinterpret_cast<float4*>(crow);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              dst[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) crow[j] = v[j];
+          }
+        } else {
+          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) +
+                                (long long)b * p.c_batch_stride + (long long)m * p.ldc + n0;
+          if (full_chunk) {
+            uint4* dst = reinterpret_cast<uint4*>(crow);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 w;
+              w.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              w.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              w.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              w.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              dst[q] = w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) crow[j] = __float2bfloat16(v[j]);
+          }
+        }
+        }  // row_ok
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+  // Common exit: on abort give in-flight bulk copies time to land, then release TMEM.
+  __syncwarp();
+  if (ctl->abort) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BLOCK_N, bool A_MN, bool B_MN>
+static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                        int device, cudaStream_t stream) {
+  using S = GemmSmem<BLOCK_N>;
+  auto kern = gemm_tcgen05_kernel<BLOCK_N, A_MN, B_MN>;
+  static bool configured[64] = {false};
+  if (!configured[device]) {
+    RT_CUDA_CHECK(
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    configured[device] = true;
+  }
+  const int total_tiles = p.batch * p.m_blocks * p.n_blocks * p.split_k;
+  const int grid = std::min(total_tiles, sm_count(device));
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, p);
+  RT_LAUNCH_CHECK();
+}
+
+void gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
+  if (g.M == 0 || g.N == 0 || g.batch == 0) return;
+  RT_CHECK(g.K > 0, "gemm_bf16: empty reduction dimension");
+  RT_CHECK(!g.accumulate || g.out_fp32, "gemm_bf16: accumulate needs an fp32 output");
+  RT_CHECK(g.split_k >= 1, "gemm_bf16: split_k >= 1");
+  RT_CHECK(g.split_k == 1 || g.accumulate, "gemm_bf16: split_k > 1 needs accumulate=true");
+  RT_CHECK(g.epi_mode == EPI_NONE || g.aux != nullptr, "gemm_bf16: this epilogue needs aux");
+  const int device = current_device();
+  int block_n = (g.block_n == 128 || g.block_n == 256) ? g.block_n : 0;
+  if (block_n == 0) block_n = (g.N <= 128) ? 128 : 256;
+
+  GemmParams p{};
+  p.M = g.M;
+  p.N = g.N;
+  p.K = g.K;
+  p.batch = g.batch;
+  p.C = g.c;
+  p.ldc = g.ldc;
+  p.c_batch_stride = g.c_batch_stride;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(g.bias);
+  p.aux = reinterpret_cast<__nv_bfloat16*>(g.aux);
+  p.ld_aux = g.ld_aux;
+  p.aux_batch_stride = g.aux_batch_stride;
+  p.alpha = g.alpha;
+  p.epi_mode = g.epi_mode;
+  p.out_fp32 = g.out_fp32;
+  p.accumulate = g.accumulate;
+  p.m_blocks = (g.M + BLOCK_M - 1) / BLOCK_M;
+  p.n_blocks = (g.N + block_n - 1) / block_n;
+  p.k_blocks = (g.K + BLOCK_K - 1) / BLOCK_K;
+  int sk = std::min(g.split_k, std::max(1, p.k_blocks));
+  // every split must own at least one k-block
+  while (sk > 1 && ((p.k_blocks + sk - 1) / sk) * (sk - 1) >= p.k_blocks) --sk;
+  p.split_k = sk;
+  p.status = status_word(device);
+
+  const uint64_t M = g.M, N = g.N, K = g.K, B = g.batch;
+  CUtensorMap ta = g.a_mn ? make_tmap_2byte(g.a, M, K, B, g.lda, g.a_batch_stride, 64, 64)
+                          : make_tmap_2byte(g.a, K, M, B, g.lda, g.a_batch_stride, 64, BLOCK_M);
+  CUtensorMap tb = g.b_mn ? make_tmap_2byte(g.b, N, K, B, g.ldb, g.b_batch_stride, 64, 64)
+                          : make_tmap_2byte(g.b, K, N, B, g.ldb, g.b_batch_stride, 64, block_n);
+#define RT_GEMM_DISPATCH(BN)                                                              \
+  if (!g.a_mn && !g.b_mn) launch_gemm<BN, false, false>(ta, tb, p, device, stream);       \
+  else if (!g.a_mn && g.b_mn) launch_gemm<BN, false, true>(ta, tb, p, device, stream);    \
+  else if (g.a_mn && g.b_mn) launch_gemm<BN, true, true>(ta, tb, p, device, stream);      \
+  else launch_gemm<BN, true, false>(ta, tb, p, device, stream);
+  if (block_n == 256) {
+    RT_GEMM_DISPATCH(256)
+  } else {
+    RT_GEMM_DISPATCH(128)
+  }
+#undef RT_GEMM_DISPATCH
+}
+
+}  // namespace rt

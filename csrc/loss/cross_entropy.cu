@@ -1,0 +1,130 @@
+// Fused softmax cross-entropy over bf16 logits: one pass computes the per-row loss and
+// overwrites the logits in place with d(loss)/d(logits) = (softmax - onehot) * grad_scale,
+// so the [tokens x vocab] probabilities never exist as a separate tensor.  The row is staged
+// in shared memory when it fits (one HBM read + one write per logit).
+// Columns >= vocab (padding added so rows are 16-byte aligned) are excluded and get zero
+// gradient.  The reference's CrossEntropyLoss recurses forever
+// (src/nn/loss.rs:58-69,98-106); semantics here are the standard mean-reduced NLL of softmax.
+#include "../api.h"
+#include "../common/launch.h"
+#include "../common/ptx.cuh"
+
+namespace rt {
+
+template <bool STAGED>
+__global__ void cross_entropy_kernel(__nv_bfloat16* __restrict__ logits,
+                                     const long long* __restrict__ targets,
+                                     float* __restrict__ loss, long long rows, int vocab, int ld,
+                                     float grad_scale, long long ignore_index, int* status) {
+  extern __shared__ __align__(16) uint8_t ce_smem[];
+  __shared__ float red[33];
+  const long long r = blockIdx.x;
+  if (r >= rows) return;
+  __nv_bfloat16* row = logits + r * (long long)ld;
+  __nv_bfloat16* srow = STAGED ? reinterpret_cast<__nv_bfloat16*>(ce_smem) : row;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
+  const int nvec = ld >> 3;
+  long long tgt = targets[r];
+  const bool ignored = (tgt == ignore_index);
+  if (!ignored && (tgt < 0 || tgt >= vocab)) {
+    if (tid == 0) atomicCAS(status, 0, RT_ERR_BOUNDS);
+    tgt = 0;
+  }
+  // pass 1: max (and stage)
+  float mx = -INFINITY;
+  for (int v = tid; v < nvec; v += nt) {
+    uint4 w = reinterpret_cast<const uint4*>(row)[v];
+    if (STAGED) reinterpret_cast<uint4*>(srow)[v] = w;
+    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&w);
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (v * 8 + e < vocab) mx = fmaxf(mx, __bfloat162float(h[e]));
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? red[lane] : -INFINITY;
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, s));
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  mx = red[32];
+  __syncthreads();
+  // pass 2: sum exp
+  float sum = 0.f;
+  for (int v = tid; v < nvec; v += nt) {
+    uint4 w = reinterpret_cast<const uint4*>(srow)[v];
+    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&w);
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (v * 8 + e < vocab) sum += __expf(__bfloat162float(h[e]) - mx);
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? red[lane] : 0.f;
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) t += __shfl_xor_sync(0xffffffffu, t, s);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  sum = red[32];
+  const float inv = 1.f / sum;
+  if (tid == 0) {
+    const float xt = __bfloat162float(srow[tgt]);
+    loss[r] = ignored ? 0.f : (logf(sum) + mx - xt);
+  }
+  __syncthreads();  // srow[tgt] read before it is overwritten (non-staged mode aliases the row)
+  const float gs = ignored ? 0.f : grad_scale;
+  // pass 3: gradient in place
+  for (int v = tid; v < nvec; v += nt) {
+    uint4 w = reinterpret_cast<const uint4*>(srow)[v];
+    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&w);
+    float g[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int c = v * 8 + e;
+      float pr = (c < vocab) ? __expf(__bfloat162float(h[e]) - mx) * inv : 0.f;
+      if (c == tgt) pr -= 1.f;
+      g[e] = pr * gs;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(g[0], g[1]);
+    o.y = pack_bf16x2(g[2], g[3]);
+    o.z = pack_bf16x2(g[4], g[5]);
+    o.w = pack_bf16x2(g[6], g[7]);
+    reinterpret_cast<uint4*>(row)[v] = o;
+  }
+}
+
+void cross_entropy_fwd_bwd(void* logits, const long long* targets, float* loss, long long rows,
+                           int vocab, int ld, float grad_scale, long long ignore_index,
+                           cudaStream_t stream) {
+  RT_CHECK(ld % 8 == 0 && ld >= vocab, "cross_entropy: row stride must be a multiple of 8 and >= vocab");
+  if (rows == 0) return;
+  const int device = current_device();
+  const size_t need = (size_t)ld * 2;
+  auto lg = reinterpret_cast<__nv_bfloat16*>(logits);
+  if (need <= 110 * 1024) {
+    static bool configured[64] = {false};
+    if (!configured[device]) {
+      RT_CUDA_CHECK(cudaFuncSetAttribute(cross_entropy_kernel<true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+      configured[device] = true;
+    }
+    cross_entropy_kernel<true><<<(unsigned)rows, 512, need, stream>>>(
+        lg, targets, loss, rows, vocab, ld, grad_scale, ignore_index, status_word(device));
+  } else {
+    cross_entropy_kernel<false><<<(unsigned)rows, 512, 0, stream>>>(
+        lg, targets, loss, rows, vocab, ld, grad_scale, ignore_index, status_word(device));
+  }
+  RT_LAUNCH_CHECK();
+}
+
+}  // namespace rt

@@ -1,0 +1,252 @@
+// LayerNorm / RMSNorm forward + backward, bf16 activations, fp32 statistics.
+// One warp per row, 16-byte vector loads, rows re-read through L1 instead of staged.
+// Backward fuses (a) the optional upstream residual gradient add into dx and (b) the
+// gamma/beta gradient reduction (shared-memory partials, one fp32 atomic per column per CTA),
+// accumulating straight into the fp32 gradient buffers the fused optimizer consumes.
+// Semantics follow the reference's layers (src/nn/normalization.rs:59-99 LayerNorm,
+// :587-608,652-701 RMSNorm), which have forward only and no backward.
+#include "../api.h"
+#include "../common/launch.h"
+#include "../common/ptx.cuh"
+
+namespace rt {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+  return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    float2 t = __bfloat1622float2(h[e]);
+    f[2 * e] = t.x;
+    f[2 * e + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 w;
+  w.x = pack_bf16x2(f[0], f[1]);
+  w.y = pack_bf16x2(f[2], f[3]);
+  w.z = pack_bf16x2(f[4], f[5]);
+  w.w = pack_bf16x2(f[6], f[7]);
+  return w;
+}
+
+// RMS = true: y = x * rstd * g (beta ignored, mean = 0).  C % 8 == 0.
+template <bool RMS>
+__global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                const __nv_bfloat16* __restrict__ gamma,
+                                const __nv_bfloat16* __restrict__ beta,
+                                __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out,
+                                float* __restrict__ rstd_out, long long rows, int C, float eps) {
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
+  const int nv = C >> 3;
+  float s = 0.f, ss = 0.f;
+  for (int v = lane; v < nv; v += 32) {
+    float f[8];
+    unpack8(xr[v], f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      s += f[e];
+      ss += f[e] * f[e];
+    }
+  }
+  s = warp_sum(s);
+  ss = warp_sum(ss);
+  float mean = RMS ? 0.f : s / C;
+  float var;
+  if (RMS) {
+    var = ss / C;
+  } else {
+    // second pass for a numerically safe variance
+    float sq = 0.f;
+    for (int v = lane; v < nv; v += 32) {
+      float f[8];
+      unpack8(xr[v], f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float d = f[e] - mean;
+        sq += d * d;
+      }
+    }
+    var = warp_sum(sq) / C;
+  }
+  const float rstd = rsqrtf(var + eps);
+  if (lane == 0) {
+    if (mean_out) mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
+  uint4* yr = reinterpret_cast<uint4*>(y + row * C);
+  const uint4* gr = reinterpret_cast<const uint4*>(gamma);
+  const uint4* br = reinterpret_cast<const uint4*>(beta);
+  for (int v = lane; v < nv; v += 32) {
+    float f[8], g[8], o[8];
+    unpack8(xr[v], f);
+    unpack8(gr[v], g);
+    if (!RMS && beta) {
+      float bb[8];
+      unpack8(br[v], bb);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = (f[e] - mean) * rstd * g[e] + bb[e];
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = (f[e] - mean) * rstd * g[e];
+    }
+    yr[v] = pack8(o);
+  }
+}
+
+// dx = rstd * (g*dy - c1 - xhat*c2) (+ dres);  LayerNorm: c1 = mean(g*dy), c2 = mean(g*dy*xhat)
+// RMSNorm: c1 = 0, c2 = mean(g*dy*xhat) with xhat = x*rstd.
+// MAXV > 0: per-lane register accumulators for dgamma/dbeta (C <= 256*MAXV); MAXV == 0: shared
+// atomics per element.
+template <bool RMS, int MAXV>
+__global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                const __nv_bfloat16* __restrict__ x,
+                                const __nv_bfloat16* __restrict__ gamma,
+                                const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                                const __nv_bfloat16* __restrict__ dres,
+                                __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma,
+                                float* __restrict__ dbeta, long long rows, int C) {
+  extern __shared__ float sacc[];  // [2][C]
+  float* sdg = sacc;
+  float* sdb = sacc + C;
+  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) sacc[i] = 0.f;
+  __syncthreads();
+  const int warps = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nv = C >> 3;
+  const uint4* gr = reinterpret_cast<const uint4*>(gamma);
+  float adg[MAXV > 0 ? MAXV * 8 : 1], adb[MAXV > 0 ? MAXV * 8 : 1];
+#pragma unroll
+  for (int i = 0; i < (MAXV > 0 ? MAXV * 8 : 1); ++i) adg[i] = adb[i] = 0.f;
+  for (long long row = (long long)blockIdx.x * warps + warp; row < rows;
+       row += (long long)gridDim.x * warps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * C);
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float c1 = 0.f, c2 = 0.f;
+    for (int v = lane; v < nv; v += 32) {
+      float f[8], d[8], g[8];
+      unpack8(xr[v], f);
+      unpack8(dyr[v], d);
+      unpack8(gr[v], g);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float xh = (f[e] - mean) * rstd;
+        const float gd = g[e] * d[e];
+        c1 += gd;
+        c2 += gd * xh;
+      }
+    }
+    c1 = RMS ? 0.f : warp_sum(c1) / C;
+    c2 = warp_sum(c2) / C;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + row * C);
+    const uint4* drr = dres ? reinterpret_cast<const uint4*>(dres + row * C) : nullptr;
+#pragma unroll
+    for (int vi = 0; vi < (MAXV > 0 ? MAXV : 64); ++vi) {
+      const int v = lane + vi * 32;
+      if (v >= nv) break;
+      float f[8], d[8], g[8], o[8];
+      unpack8(xr[v], f);
+      unpack8(dyr[v], d);
+      unpack8(gr[v], g);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float xh = (f[e] - mean) * rstd;
+        o[e] = rstd * (g[e] * d[e] - c1 - xh * c2);
+        if (MAXV > 0) {
+          adg[vi * 8 + e] += d[e] * xh;
+          if (!RMS) adb[vi * 8 + e] += d[e];
+        } else {
+          atomicAdd(&sdg[v * 8 + e], d[e] * xh);
+          if (!RMS) atomicAdd(&sdb[v * 8 + e], d[e]);
+        }
+      }
+      if (drr) {
+        float r[8];
+        unpack8(drr[v], r);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] += r[e];
+      }
+      dxr[v] = pack8(o);
+    }
+  }
+  if (MAXV > 0) {
+#pragma unroll
+    for (int vi = 0; vi < (MAXV > 0 ? MAXV : 1); ++vi) {
+      const int v = lane + vi * 32;
+      if (v < nv) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          atomicAdd(&sdg[v * 8 + e], adg[vi * 8 + e]);
+          if (!RMS) atomicAdd(&sdb[v * 8 + e], adb[vi * 8 + e]);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    if (dgamma) atomicAdd(&dgamma[i], sdg[i]);
+    if (!RMS && dbeta) atomicAdd(&dbeta[i], sdb[i]);
+  }
+}
+
+void norm_fwd(const NormArgs& a, cudaStream_t stream) {
+  RT_CHECK(a.C % 8 == 0, "norm: feature size must be a multiple of 8");
+  if (a.rows == 0) return;
+  const int wpb = 4;
+  const unsigned grid = (unsigned)((a.rows + wpb - 1) / wpb);
+  auto x = reinterpret_cast<const __nv_bfloat16*>(a.x);
+  auto g = reinterpret_cast<const __nv_bfloat16*>(a.gamma);
+  auto b = reinterpret_cast<const __nv_bfloat16*>(a.beta);
+  auto y = reinterpret_cast<__nv_bfloat16*>(a.y);
+  if (a.rms)
+    norm_fwd_kernel<true><<<grid, wpb * 32, 0, stream>>>(x, g, b, y, a.mean, a.rstd, a.rows, a.C, a.eps);
+  else
+    norm_fwd_kernel<false><<<grid, wpb * 32, 0, stream>>>(x, g, b, y, a.mean, a.rstd, a.rows, a.C, a.eps);
+  RT_LAUNCH_CHECK();
+}
+
+template <bool RMS, int MAXV>
+static void launch_norm_bwd(const NormArgs& a, unsigned grid, int threads, size_t smem,
+                            cudaStream_t stream) {
+  auto kern = norm_bwd_kernel<RMS, MAXV>;
+  if (smem > 48 * 1024)
+    RT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<grid, threads, smem, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(a.dy), reinterpret_cast<const __nv_bfloat16*>(a.x),
+      reinterpret_cast<const __nv_bfloat16*>(a.gamma), a.mean, a.rstd,
+      reinterpret_cast<const __nv_bfloat16*>(a.dres), reinterpret_cast<__nv_bfloat16*>(a.dx),
+      a.dgamma, a.dbeta, a.rows, a.C);
+  RT_LAUNCH_CHECK();
+}
+
+void norm_bwd(const NormArgs& a, cudaStream_t stream) {
+  RT_CHECK(a.C % 8 == 0, "norm: feature size must be a multiple of 8");
+  RT_CHECK(a.C <= 16384, "norm backward: feature size above 16384 not supported");
+  if (a.rows == 0) return;
+  const int threads = 256;
+  const int warps = threads / 32;
+  const long long want = (a.rows + warps - 1) / warps;
+  const unsigned grid = (unsigned)std::min<long long>(want, 2LL * sm_count(current_device()));
+  const size_t smem = sizeof(float) * 2 * a.C;
+  const bool small = a.C <= 1024;
+  if (a.rms) {
+    if (small) launch_norm_bwd<true, 4>(a, grid, threads, smem, stream);
+    else launch_norm_bwd<true, 0>(a, grid, threads, smem, stream);
+  } else {
+    if (small) launch_norm_bwd<false, 4>(a, grid, threads, smem, stream);
+    else launch_norm_bwd<false, 0>(a, grid, threads, smem, stream);
+  }
+}
+
+}  // namespace rt

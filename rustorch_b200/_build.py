@@ -1,0 +1,123 @@
+"""In-tree build of the native library (``rustorch_b200/_C*.so``) for sm_100a.
+
+Every ``csrc/**/*.cu`` is compiled by nvcc with ``-gencode arch=compute_100a,code=sm_100a``
+(kernel translation units are torch-free and compile in seconds), the tensor glue
+``csrc/*.cpp`` by g++ against the torch headers, and everything is linked into one Python
+extension module that sits next to this file.  Objects are cached under ``build/`` keyed by a
+content hash of the source and the headers it can see, so rebuilds only touch what changed.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import subprocess
+import sys
+import sysconfig
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+CSRC = ROOT / "csrc"
+BUILD = ROOT / "build" / "obj"
+EXT_SUFFIX = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+TARGET = Path(__file__).resolve().parent / f"_C{EXT_SUFFIX}"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "--threads", "2",
+]
+
+
+def _cuda_home() -> str:
+    return os.environ.get("CUDA_HOME") or os.environ.get("CUDA_PATH") or "/usr/local/cuda"
+
+
+def _headers_digest() -> str:
+    h = hashlib.sha256()
+    for p in sorted(CSRC.rglob("*")):
+        if p.suffix in (".h", ".cuh", ".hpp"):
+            h.update(p.read_bytes())
+    return h.hexdigest()
+
+
+def _obj_for(src: Path, hdr_digest: str, extra: str) -> Path:
+    h = hashlib.sha256(src.read_bytes())
+    h.update(hdr_digest.encode())
+    h.update(extra.encode())
+    rel = "_".join(src.relative_to(CSRC).with_suffix("").parts)
+    return BUILD / f"{rel}.{h.hexdigest()[:16]}.o"
+
+
+def _run(cmd: list[str]) -> None:
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("build step failed:\n  " + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+
+
+def sources() -> tuple[list[Path], list[Path]]:
+    cu = sorted(CSRC.rglob("*.cu"))
+    cpp = sorted(CSRC.glob("*.cpp"))
+    return cu, cpp
+
+
+def build(verbose: bool = False, force: bool = False) -> Path:
+    """Compile what changed and (re)link ``_C``.  Returns the path of the shared object."""
+    import torch  # noqa: F401  (headers + libs come from the installed torch)
+    from torch.utils import cpp_extension as ce
+
+    BUILD.mkdir(parents=True, exist_ok=True)
+    cu, cpp = sources()
+    hdr = _headers_digest()
+    nvcc = str(Path(_cuda_home()) / "bin" / "nvcc")
+    torch_inc = [f"-I{p}" for p in ce.include_paths()] + [f"-I{sysconfig.get_paths()['include']}"]
+    cxx_flags = [
+        "-O2", "-std=c++17", "-fPIC", "-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H",
+        f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+        f"-I{_cuda_home()}/include", "-Wno-deprecated-declarations",
+    ]
+    jobs: list[tuple[Path, list[str]]] = []
+    objs: list[Path] = []
+    for s in cu:
+        o = _obj_for(s, hdr, " ".join(NVCC_FLAGS))
+        objs.append(o)
+        if force or not o.exists():
+            jobs.append((o, [nvcc, *NVCC_FLAGS, f"-I{CSRC}", "-c", str(s), "-o", str(o)]))
+    for s in cpp:
+        o = _obj_for(s, hdr, " ".join(cxx_flags) + torch.__version__)
+        objs.append(o)
+        if force or not o.exists():
+            jobs.append((o, ["g++", *cxx_flags, *torch_inc, f"-I{CSRC}", "-c", str(s), "-o", str(o)]))
+
+    def _do(job):
+        o, cmd = job
+        if verbose:
+            print("[build]", " ".join(cmd[-4:]), flush=True)
+        _run(cmd)
+        return o
+
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
+            list(ex.map(_do, jobs))
+    # drop stale objects of sources that changed
+    keep = {o.name for o in objs}
+    for old in BUILD.glob("*.o"):
+        if old.name not in keep:
+            old.unlink()
+    stamp = BUILD / "link.stamp"
+    want = "\n".join(sorted(keep))
+    if force or jobs or not TARGET.exists() or not stamp.exists() or stamp.read_text() != want:
+        lib_dirs = ce.library_paths()
+        link = ["g++", "-shared", "-o", str(TARGET), *map(str, objs)]
+        for d in lib_dirs:
+            link += [f"-L{d}", f"-Wl,-rpath,{d}"]
+        link += [f"-L{_cuda_home()}/lib64", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda",
+                 "-ltorch", "-ltorch_python", "-lcudart"]
+        if verbose:
+            print("[build] link", TARGET.name, flush=True)
+        _run(link)
+        stamp.write_text(want)
+    return TARGET
+
+
+if __name__ == "__main__":
+    print(build(verbose=True, force="--force" in sys.argv))

@@ -1,0 +1,292 @@
+"""Fused transformer sub-blocks as autograd Functions over the native sm_100a kernels.
+
+Each Function covers one residual branch (pre-norm -> projections -> residual add) so that
+* the residual add rides in a GEMM epilogue on the way forward,
+* the upstream residual gradient is added inside the norm backward kernel,
+* GELU / dGELU ride in GEMM epilogues,
+* weight gradients are accumulated by the wgrad GEMM straight into the fp32 ``main_grad``
+  buffer of the parameter (when it has one), which the fused optimizer consumes and zeroes.
+
+Parameters without a ``main_grad`` attribute get an ordinary returned gradient instead, so the
+Functions also work with stock optimizers.
+
+The reference builds the same blocks from separate host loops without any backward for
+attention/norm/activation layers (src/nn/transformer_phase6.rs:922-976,
+src/models/transformer_models.rs:760-796).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from ..ops import kernels as K
+
+_NUM_SMS = 148
+
+
+def _split_k_for(tiles: int, k_blocks: int) -> int:
+    if tiles >= 4 * _NUM_SMS:
+        return 1
+    want = -(-4 * _NUM_SMS // max(tiles, 1))
+    return max(1, min(want, max(1, k_blocks // 8)))
+
+
+def wgrad_into(dy2d: torch.Tensor, x2d: torch.Tensor, param: torch.Tensor):
+    """dW[out,in] (+)= dy2d^T @ x2d.  Returns None if accumulated into ``param.main_grad``."""
+    n_out, n_in = dy2d.shape[1], x2d.shape[1]
+    tiles = -(-n_out // 128) * -(-n_in // 256)
+    sk = _split_k_for(tiles, -(-dy2d.shape[0] // 64))
+    mg = getattr(param, "main_grad", None)
+    if mg is not None:
+        K.gemm(dy2d, x2d, a_mn=True, b_mn=True, out=mg.view(n_out, n_in), accumulate=True, split_k=sk)
+        return None
+    g = K.gemm(dy2d, x2d, a_mn=True, b_mn=True, out_dtype=torch.float32, accumulate=True, split_k=sk)
+    return g.to(param.dtype)
+
+
+def bgrad_into(dy2d: torch.Tensor, param: Optional[torch.Tensor]):
+    if param is None:
+        return None
+    mg = getattr(param, "main_grad", None)
+    if mg is not None:
+        K.colsum_accum(dy2d, mg)
+        return None
+    g = torch.zeros(dy2d.shape[1], dtype=torch.float32, device=dy2d.device)
+    K.colsum_accum(dy2d, g)
+    return g.to(param.dtype)
+
+
+def _norm_grad_bufs(w, b):
+    """fp32 accumulation targets for dgamma/dbeta and whether they are the main_grad views."""
+    wg = getattr(w, "main_grad", None)
+    direct = wg is not None
+    if not direct:
+        wg = torch.zeros(w.numel(), dtype=torch.float32, device=w.device)
+    bg = None
+    if b is not None:
+        bg = getattr(b, "main_grad", None) if direct else torch.zeros(
+            b.numel(), dtype=torch.float32, device=b.device)
+    return wg, bg, direct
+
+
+class AttnBlockFn(torch.autograd.Function):
+    """y = x + proj(attention(qkv(norm(x))))  (pre-LayerNorm, fused QKV projection)."""
+
+    @staticmethod
+    def forward(ctx, x, ln_w, ln_b, w_qkv, b_qkv, w_proj, b_proj, n_head: int, eps: float,
+                causal: bool):
+        B, T, C = x.shape
+        D = C // n_head
+        x2 = x.reshape(B * T, C)
+        h, mean, rstd = K.layer_norm_fwd(x2, ln_w, ln_b, eps)
+        qkv = K.gemm(h, w_qkv, bias=b_qkv)                       # [B*T, 3C]
+        qkv5 = qkv.view(B, T, 3, n_head, D)
+        o, lse = K.attention_fwd(qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2], causal)
+        o2 = o.view(B * T, C)
+        y = K.gemm(o2, w_proj, bias=b_proj, aux=x2, epilogue=K.EPI_RESIDUAL)
+        ctx.save_for_backward(x2, ln_w, ln_b, w_qkv, b_qkv, w_proj, b_proj, mean, rstd, h, qkv, o, lse)
+        ctx.meta = (B, T, C, n_head, causal)
+        return y.view(B, T, C)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, ln_w, ln_b, w_qkv, b_qkv, w_proj, b_proj, mean, rstd, h, qkv, o, lse = ctx.saved_tensors
+        B, T, C, n_head, causal = ctx.meta
+        D = C // n_head
+        dy2 = dy.contiguous().view(B * T, C)
+        o2 = o.view(B * T, C)
+        g_wproj = wgrad_into(dy2, o2, w_proj)
+        g_bproj = bgrad_into(dy2, b_proj)
+        do = K.gemm(dy2, w_proj, b_mn=True)                      # [B*T, C]
+        qkv5 = qkv.view(B, T, 3, n_head, D)
+        dqkv = torch.empty_like(qkv)
+        dqkv5 = dqkv.view(B, T, 3, n_head, D)
+        K.attention_bwd(qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2], o, do.view(B, T, n_head, D), lse,
+                        causal, dq=dqkv5[:, :, 0], dk=dqkv5[:, :, 1], dv=dqkv5[:, :, 2])
+        g_wqkv = wgrad_into(dqkv, h, w_qkv)
+        g_bqkv = bgrad_into(dqkv, b_qkv)
+        dh = K.gemm(dqkv, w_qkv, b_mn=True)                      # [B*T, C]
+        wg, bg, direct = _norm_grad_bufs(ln_w, ln_b)
+        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dy2)
+        g_lnw = None if direct else wg.to(ln_w.dtype)
+        g_lnb = None if (direct or ln_b is None) else bg.to(ln_b.dtype)
+        return (dx.view(B, T, C), g_lnw, g_lnb, g_wqkv, g_bqkv, g_wproj, g_bproj, None, None, None)
+
+
+class MLPBlockFn(torch.autograd.Function):
+    """y = x + fc2(gelu(fc1(norm(x))))  (tanh GELU as in the reference, src/nn/activation.rs:206-217)."""
+
+    @staticmethod
+    def forward(ctx, x, ln_w, ln_b, w1, b1, w2, b2, eps: float):
+        B, T, C = x.shape
+        x2 = x.reshape(B * T, C)
+        h, mean, rstd = K.layer_norm_fwd(x2, ln_w, ln_b, eps)
+        pre = torch.empty((B * T, w1.shape[0]), dtype=torch.bfloat16, device=x.device)
+        act = K.gemm(h, w1, bias=b1, aux=pre, epilogue=K.EPI_GELU_DUAL)
+        y = K.gemm(act, w2, bias=b2, aux=x2, epilogue=K.EPI_RESIDUAL)
+        ctx.save_for_backward(x2, ln_w, ln_b, w1, b1, w2, b2, mean, rstd, h, pre, act)
+        ctx.meta = (B, T, C)
+        return y.view(B, T, C)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, ln_w, ln_b, w1, b1, w2, b2, mean, rstd, h, pre, act = ctx.saved_tensors
+        B, T, C = ctx.meta
+        dy2 = dy.contiguous().view(B * T, C)
+        g_w2 = wgrad_into(dy2, act, w2)
+        g_b2 = bgrad_into(dy2, b2)
+        dpre = K.gemm(dy2, w2, b_mn=True, aux=pre, epilogue=K.EPI_DGELU)   # [B*T, 4C]
+        g_w1 = wgrad_into(dpre, h, w1)
+        g_b1 = bgrad_into(dpre, b1)
+        dh = K.gemm(dpre, w1, b_mn=True)
+        wg, bg, direct = _norm_grad_bufs(ln_w, ln_b)
+        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dy2)
+        g_lnw = None if direct else wg.to(ln_w.dtype)
+        g_lnb = None if (direct or ln_b is None) else bg.to(ln_b.dtype)
+        return (dx.view(B, T, C), g_lnw, g_lnb, g_w1, g_b1, g_w2, g_b2, None)
+
+
+class EmbeddingFn(torch.autograd.Function):
+    """x[b,t] = wte[idx[b,t]] + wpe[t]."""
+
+    @staticmethod
+    def forward(ctx, idx, wte, wpe):
+        B, T = idx.shape
+        out = K.embedding_fwd(idx, wte, wpe, T)
+        ctx.save_for_backward(idx, wte, wpe)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        idx, wte, wpe = ctx.saved_tensors
+        T = idx.shape[1]
+        direct = getattr(wte, "main_grad", None) is not None
+        if direct:
+            dwte = wte.main_grad.view(wte.shape)
+            dwpe = wpe.main_grad.view(wpe.shape) if wpe is not None else None
+        else:
+            dwte = torch.zeros(wte.shape, dtype=torch.float32, device=wte.device)
+            dwpe = torch.zeros(wpe.shape, dtype=torch.float32, device=wte.device) if wpe is not None else None
+        K.embedding_bwd(idx, dout, dwte, dwpe, T, wte.shape[0])
+        if direct:
+            return None, None, None
+        return None, dwte.to(wte.dtype), (dwpe.to(wpe.dtype) if wpe is not None else None)
+
+
+class LMHeadLossFn(torch.autograd.Function):
+    """loss = mean CE(lm_head(norm(x)), targets); logits stay bf16 and become their own gradient.
+
+    ``w_head`` is ``[vocab_padded, C]`` (rows >= ``vocab`` are padding that receives zero
+    gradient); padding keeps logits rows 16-byte aligned for vector access.
+    """
+
+    assume_unit_grad = True
+
+    @staticmethod
+    def forward(ctx, x, ln_w, ln_b, w_head, targets, vocab: int, eps: float, ignore_index: int):
+        B, T, C = x.shape
+        x2 = x.reshape(B * T, C)
+        h, mean, rstd = K.layer_norm_fwd(x2, ln_w, ln_b, eps)
+        logits = K.gemm(h, w_head)                                # [B*T, Vp]
+        tgt = targets.reshape(-1)
+        # Mean over all rows; rows equal to ignore_index contribute zero loss and gradient.
+        n_valid = B * T
+        losses = K.cross_entropy_(logits, tgt, vocab, 1.0 / n_valid, ignore_index)
+        loss = K.reduce_all(losses, "sum")[0] / n_valid
+        ctx.save_for_backward(x2, ln_w, ln_b, w_head, mean, rstd, h, logits)
+        ctx.meta = (B, T, C)
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        x2, ln_w, ln_b, w_head, mean, rstd, h, dlogits = ctx.saved_tensors
+        B, T, C = ctx.meta
+        # dlogits already carries the 1/N of the mean.  Reading the upstream factor would cost a
+        # device sync, so plain loss.backward() (factor 1) is assumed unless the class flag is
+        # cleared, e.g. when a loss scaler multiplies the loss.
+        if not LMHeadLossFn.assume_unit_grad:
+            dlogits = dlogits * dloss.to(dlogits.dtype)
+        g_head = wgrad_into(dlogits, h, w_head)
+        dh = K.gemm(dlogits, w_head, b_mn=True)
+        wg, bg, direct = _norm_grad_bufs(ln_w, ln_b)
+        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg)
+        g_lnw = None if direct else wg.to(ln_w.dtype)
+        g_lnb = None if (direct or ln_b is None) else bg.to(ln_b.dtype)
+        return dx.view(B, T, C), g_lnw, g_lnb, g_head, None, None, None, None
+
+
+class LinearFn(torch.autograd.Function):
+    """y = x W^T + b on the tcgen05 GEMM (forward, dgrad and wgrad without transposed copies)."""
+
+    @staticmethod
+    def forward(ctx, x, w, b):
+        x2 = x.reshape(-1, x.shape[-1])
+        y = K.gemm(x2, w, bias=b)
+        ctx.save_for_backward(x2, w, b)
+        ctx.xshape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, b = ctx.saved_tensors
+        dy2 = dy.contiguous().view(-1, w.shape[0])
+        gw = wgrad_into(dy2, x2, w) if ctx.needs_input_grad[1] else None
+        gb = bgrad_into(dy2, b) if (b is not None and ctx.needs_input_grad[2]) else None
+        dx = K.gemm(dy2, w, b_mn=True).view(ctx.xshape) if ctx.needs_input_grad[0] else None
+        return dx, gw, gb
+
+
+class LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, eps):
+        x2 = x.reshape(-1, w.numel())
+        y, mean, rstd = K.layer_norm_fwd(x2, w, b, eps)
+        ctx.save_for_backward(x2, w, b, mean, rstd)
+        ctx.xshape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, b, mean, rstd = ctx.saved_tensors
+        wg, bg, direct = _norm_grad_bufs(w, b)
+        dx = K.layer_norm_bwd(dy.contiguous().view(x2.shape), x2, w, mean, rstd, wg, bg)
+        return (dx.view(ctx.xshape), None if direct else wg.to(w.dtype),
+                None if (direct or b is None) else bg.to(b.dtype), None)
+
+
+class RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        x2 = x.reshape(-1, w.numel())
+        y, rstd = K.rms_norm_fwd(x2, w, eps)
+        ctx.save_for_backward(x2, w, rstd)
+        ctx.xshape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, rstd = ctx.saved_tensors
+        wg, _, direct = _norm_grad_bufs(w, None)
+        dx = K.rms_norm_bwd(dy.contiguous().view(x2.shape), x2, w, rstd, wg)
+        return dx.view(ctx.xshape), None if direct else wg.to(w.dtype), None
+
+
+class FlashAttentionFn(torch.autograd.Function):
+    """softmax(q k^T * scale [+ causal mask]) v with q [B,T,H,D], k/v [B,T,Hkv,D]."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal: bool, scale: Optional[float]):
+        scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+        o, lse = K.attention_fwd(q, k, v, causal, scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.meta = (causal, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        causal, scale = ctx.meta
+        dq, dk, dv = K.attention_bwd(q, k, v, o, do.contiguous(), lse, causal, scale)
+        return dq, dk, dv, None, None

@@ -1,0 +1,88 @@
+"""tcgen05 GEMM vs an fp32 PyTorch matmul of the same bf16 inputs."""
+import pytest
+import torch
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(shape, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+
+
+def _ref(a, b, a_mn, b_mn):
+    A = a.float().transpose(-1, -2) if a_mn else a.float()
+    B = b.float() if b_mn else b.float().transpose(-1, -2)
+    return A @ B
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 768, 1024),
+                                   (200, 136, 72), (1000, 264, 520), (64, 8, 8)])
+def test_gemm_layouts(a_mn, b_mn, M, N, K):
+    from rustorch_b200.ops import kernels as K_
+    a = _mk((K, M) if a_mn else (M, K), 1)
+    b = _mk((K, N) if b_mn else (N, K), 2)
+    out = K_.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    ref = _ref(a, b, a_mn, b_mn)
+    assert rel_err(out, ref) < 1.5e-2
+
+
+@pytest.mark.parametrize("block_n", [128, 256])
+def test_gemm_block_n_and_fp32_out(block_n):
+    from rustorch_b200.ops import kernels as K_
+    a, b = _mk((512, 320), 3), _mk((640, 320), 4)
+    out = K_.gemm(a, b, out_dtype=torch.float32, block_n=block_n)
+    assert rel_err(out, _ref(a, b, False, False)) < 2e-3
+
+
+def test_gemm_batched_strided():
+    from rustorch_b200.ops import kernels as K_
+    big = _mk((4, 256, 3 * 128), 5)
+    a = big[:, :, 0:128]                 # strided view, row stride 384
+    b = _mk((4, 192, 128), 6)
+    out = K_.gemm(a, b)
+    assert rel_err(out, a.float() @ b.float().transpose(1, 2)) < 1.5e-2
+
+
+def test_gemm_bias_gelu_residual_epilogues():
+    from rustorch_b200.ops import kernels as K_
+    M, N, K = 512, 768, 256
+    a, b = _mk((M, K), 7), _mk((N, K), 8)
+    bias = _mk((N,), 9)
+    res = _mk((M, N), 10)
+    lin = a.float() @ b.float().t() + bias.float()
+    out = K_.gemm(a, b, bias=bias)
+    assert rel_err(out, lin) < 1.5e-2
+    out = K_.gemm(a, b, bias=bias, aux=res, epilogue=K_.EPI_RESIDUAL)
+    assert rel_err(out, lin + res.float()) < 1.5e-2
+    pre = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    act = K_.gemm(a, b, bias=bias, aux=pre, epilogue=K_.EPI_GELU_DUAL)
+    assert rel_err(pre, lin) < 1.5e-2
+    assert rel_err(act, torch.nn.functional.gelu(lin, approximate="tanh")) < 2e-2
+    # dGELU epilogue: out = (a @ b^T) * gelu'(pre)
+    x = pre.float().requires_grad_(True)
+    torch.nn.functional.gelu(x, approximate="tanh").sum().backward()
+    out = K_.gemm(a, b, aux=pre, epilogue=K_.EPI_DGELU)
+    assert rel_err(out, (a.float() @ b.float().t()) * x.grad) < 2e-2
+
+
+@pytest.mark.parametrize("split_k", [1, 4, 7])
+def test_gemm_wgrad_split_k_accumulate(split_k):
+    from rustorch_b200.ops import kernels as K_
+    tokens, n_out, n_in = 2048, 384, 256
+    dy, x = _mk((tokens, n_out), 11), _mk((tokens, n_in), 12)
+    acc = torch.ones(n_out, n_in, dtype=torch.float32, device="cuda")
+    K_.gemm(dy, x, a_mn=True, b_mn=True, out=acc, accumulate=True, split_k=split_k)
+    ref = 1.0 + dy.float().t() @ x.float()
+    assert rel_err(acc, ref) < 2e-3
+
+
+def test_gemm_large_persistent():
+    from rustorch_b200.ops import kernels as K_
+    a, b = _mk((4096, 1024), 13), _mk((4096, 1024), 14)
+    out = K_.gemm(a, b)
+    assert rel_err(out, a.float() @ b.float().t()) < 1.5e-2
