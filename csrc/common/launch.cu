@@ -16,7 +16,19 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// cuTensorMapEncodeTiled is a driver call and needs a current context on the calling thread.
+// Threads that have only ever queried the device (e.g. autograd's backward threads) may not
+// have the primary context bound yet; a no-op runtime call binds it.
+void bind_context_once() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    RT_CUDA_CHECK(cudaFree(nullptr));
+    bound = true;
+  }
+}
+
 EncodeFn encode_fn() {
+  bind_context_once();
   static EncodeFn fn = nullptr;
   if (!fn) {
     void* p = nullptr;
