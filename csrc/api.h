@@ -74,9 +74,13 @@ struct NormArgs {
   void* dx;          // bf16 [rows][C]
   float* dgamma;     // fp32 [C], accumulated into (may be null)
   float* dbeta;      // fp32 [C], accumulated into (may be null)
+  float* partial;    // backward scratch: fp32 [2][n_partial][C] per-CTA partial sums
+  int n_partial;     // = norm_bwd_num_partials(rows, sm_count)
 };
 void norm_fwd(const NormArgs& a, cudaStream_t stream);
 void norm_bwd(const NormArgs& a, cudaStream_t stream);
+// Number of CTAs (and therefore partial-sum rows) the backward kernel uses for `rows` rows.
+int norm_bwd_num_partials(long long rows, int sm_count);
 
 // ------------------------------------------------------------------- nn/embedding.cu
 void embedding_fwd(const long long* idx, const void* wte, const void* wpe, void* out,

@@ -31,28 +31,36 @@ struct AttnBwdParams {
 };
 
 // --------------------------------------------------------------------- delta pre-pass
-// delta[b][h][t] = sum_d o[b][t][h][d] * do[b][t][h][d]   (one warp per row)
+// delta[b][h][t] = sum_d o[b][t][h][d] * do[b][t][h][d].  D/8 lanes per row, one 16-byte load
+// per lane per tensor, so a warp covers 4 rows (D = 64) or 2 rows (D = 128).
+template <int D>
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
                                   const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
-                                  int B, int H, int T, int D, long long sb, long long st,
-                                  long long sh) {
-  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= (long long)B * H * T) return;
-  const int t = int(row % T);
-  const int h = int((row / T) % H);
-  const int b = int(row / ((long long)T * H));
-  const __nv_bfloat16* po = o + b * sb + t * st + h * sh;
-  const __nv_bfloat16* pd = d_o + b * sb + t * st + h * sh;
+                                  int B, int H, int T, long long sb, long long st, long long sh) {
+  constexpr int LPR = D / 8;  // lanes per row
+  const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gt / LPR;
+  const int sub = int(gt % LPR);
+  const long long rows = (long long)B * H * T;
   float acc = 0.f;
-  for (int d = lane * 2; d < D; d += 64) {
-    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(po + d));
-    float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pd + d));
-    acc += a.x * c.x + a.y * c.y;
+  if (row < rows) {
+    const int t = int(row % T);
+    const int h = int((row / T) % H);
+    const int b = int(row / ((long long)T * H));
+    const long long off = b * sb + t * st + h * sh + sub * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(o + off);
+    const uint4 c = *reinterpret_cast<const uint4*>(d_o + off);
+    const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* hc = reinterpret_cast<const __nv_bfloat162*>(&c);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 x = __bfloat1622float2(ha[e]), y = __bfloat1622float2(hc[e]);
+      acc += x.x * y.x + x.y * y.y;
+    }
   }
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (lane == 0) delta[row] = acc;
+  for (int s = LPR / 2; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (row < rows && sub == 0) delta[row] = acc;
 }
 
 // ------------------------------------------------------------------------ dK / dV
@@ -560,11 +568,10 @@ static void launch_bwd(const AttnArgs& a, cudaStream_t stream) {
     configured[device] = true;
   }
   {
-    const long long rows = (long long)a.B * a.H * a.Tq;
-    const int wpb = 8;
-    attn_delta_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, stream>>>(
+    const long long threads = (long long)a.B * a.H * a.Tq * (D / 8);
+    attn_delta_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(a.o), reinterpret_cast<const __nv_bfloat16*>(a.d_o),
-        a.delta, a.B, a.H, a.Tq, a.D, a.o_sb, a.o_st, a.o_sh);
+        a.delta, a.B, a.H, a.Tq, a.o_sb, a.o_st, a.o_sh);
     RT_LAUNCH_CHECK();
   }
   CUtensorMap tq = make_tmap_2byte_4d(a.q, D, a.Tq, a.H, a.B, a.q_st, a.q_sh, a.q_sb, 64, 128);

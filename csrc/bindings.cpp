@@ -211,6 +211,10 @@ void norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, const OptT
     a.dbeta = dbeta->data_ptr<float>();
   }
   a.rms = rms;
+  // scratch for the two-stage gamma/beta reduction
+  a.n_partial = rt::norm_bwd_num_partials(a.rows, rt::sm_count(x.device().index()));
+  at::Tensor partial = at::empty({2, a.n_partial, a.C}, x.options().dtype(at::kFloat));
+  a.partial = partial.data_ptr<float>();
   rt::norm_bwd(a, stream_of(x));
 }
 

@@ -15,8 +15,9 @@
 // (src/gpu/cuda_enhanced.rs:122-159) plus naive/tiled scalar kernels
 // (src/gpu/cuda_kernels.cu:59-75); this file replaces all of them.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2..5 = epilogue (TMEM lane quarter = warp_id % 4).
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..9 = epilogue (TMEM lane quarter = warp_id % 4; warps 2..5 take the left half of
+// the tile's columns, warps 6..9 the right half).
 #include "../api.h"
 #include "../common/launch.h"
 #include "../common/ptx.cuh"
@@ -26,7 +27,7 @@ namespace rt {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;  // 2 control warps + 8 epilogue warps
 
 struct GemmParams {
   int M, N, K, batch;
@@ -104,7 +105,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4);
+      mbar_init(&tmem_empty[a], 8);
     }
     ctl->abort = 0;
     fence_mbar_init();
@@ -208,6 +209,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else {
     // ----------------------------------------------------------------- epilogue
     const int quarter = warp & 3;
+    const int col_half = (warp - 2) >> 2;
     const int row_in_tile = quarter * 32 + lane;
     uint32_t tile_i = 0;
     bool ok = true;
@@ -226,7 +228,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool row_ok = m < p.M;
       const bool add_bias = (p.bias != nullptr) && (split == 0);
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
+      for (int c = col_half * (BLOCK_N / 64); c < (col_half + 1) * (BLOCK_N / 64); ++c) {
         const int n0 = nb * BLOCK_N + c * 32;
         if (n0 >= p.N) break;  // warp-uniform
         uint32_t r[32];

@@ -103,6 +103,113 @@ __global__ void cross_entropy_kernel(__nv_bfloat16* __restrict__ logits,
   }
 }
 
+// Register-resident variant: the whole row lives in the registers of one 1024-thread CTA as
+// packed bf16 (NV 16-byte vectors per thread), so each logit is read from HBM once, exponentiated
+// once (the exponentials overwrite the packed row in registers) and written once.
+template <int NV>
+__global__ void __launch_bounds__(1024, 1)
+cross_entropy_reg_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
+                         float* __restrict__ loss, long long rows, int vocab, int ld,
+                         float grad_scale, long long ignore_index, int* status) {
+  __shared__ float red[33];
+  __shared__ float s_xt;
+  const long long r = blockIdx.x;
+  if (r >= rows) return;
+  uint4* row = reinterpret_cast<uint4*>(logits + r * (long long)ld);
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int nvec = ld >> 3;
+  long long tgt = targets[r];
+  const bool ignored = (tgt == ignore_index);
+  if (!ignored && (tgt < 0 || tgt >= vocab)) {
+    if (tid == 0) atomicCAS(status, 0, RT_ERR_BOUNDS);
+    tgt = 0;
+  }
+  if (ignored) tgt = 0;
+  uint4 w[NV];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = tid + i * 1024;
+    if (v < nvec) {
+      w[i] = row[v];
+      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&w[i]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (v * 8 + e < vocab) mx = fmaxf(mx, __bfloat162float(h[e]));
+    }
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  if (warp == 0) {
+    float t = red[lane];
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, s));
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  mx = red[32];
+  __syncthreads();
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = tid + i * 1024;
+    if (v < nvec) {
+      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&w[i]);
+      float ev[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int c = v * 8 + e;
+        const float x = __bfloat162float(h[e]);
+        if (c == tgt) s_xt = x;
+        ev[e] = (c < vocab) ? __expf(x - mx) : 0.f;
+        sum += ev[e];
+      }
+      w[i].x = pack_bf16x2(ev[0], ev[1]);
+      w[i].y = pack_bf16x2(ev[2], ev[3]);
+      w[i].z = pack_bf16x2(ev[4], ev[5]);
+      w[i].w = pack_bf16x2(ev[6], ev[7]);
+    }
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  if (warp == 0) {
+    float t = red[lane];
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) t += __shfl_xor_sync(0xffffffffu, t, s);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  sum = red[32];
+  const float inv = 1.f / sum;
+  if (tid == 0) loss[r] = ignored ? 0.f : (logf(sum) + mx - s_xt);
+  const float gs = ignored ? 0.f : grad_scale;
+  const float gi = inv * gs;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = tid + i * 1024;
+    if (v < nvec) {
+      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&w[i]);
+      float g[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int c = v * 8 + e;
+        g[e] = __bfloat162float(h[e]) * gi - ((c == tgt) ? gs : 0.f);
+      }
+      uint4 o;
+      o.x = pack_bf16x2(g[0], g[1]);
+      o.y = pack_bf16x2(g[2], g[3]);
+      o.z = pack_bf16x2(g[4], g[5]);
+      o.w = pack_bf16x2(g[6], g[7]);
+      row[v] = o;
+    }
+  }
+}
+
 void cross_entropy_fwd_bwd(void* logits, const long long* targets, float* loss, long long rows,
                            int vocab, int ld, float grad_scale, long long ignore_index,
                            cudaStream_t stream) {
@@ -111,6 +218,8 @@ void cross_entropy_fwd_bwd(void* logits, const long long* targets, float* loss, 
   const int device = current_device();
   const size_t need = (size_t)ld * 2;
   auto lg = reinterpret_cast<__nv_bfloat16*>(logits);
+  const int nvec = ld >> 3;
+  const bool aligned = (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
   if (need <= 110 * 1024) {
     static bool configured[64] = {false};
     if (!configured[device]) {
@@ -119,6 +228,12 @@ void cross_entropy_fwd_bwd(void* logits, const long long* targets, float* loss, 
       configured[device] = true;
     }
     cross_entropy_kernel<true><<<(unsigned)rows, 512, need, stream>>>(
+        lg, targets, loss, rows, vocab, ld, grad_scale, ignore_index, status_word(device));
+  } else if (aligned && nvec <= 8 * 1024) {
+    cross_entropy_reg_kernel<8><<<(unsigned)rows, 1024, 0, stream>>>(
+        lg, targets, loss, rows, vocab, ld, grad_scale, ignore_index, status_word(device));
+  } else if (aligned && nvec <= 16 * 1024) {
+    cross_entropy_reg_kernel<16><<<(unsigned)rows, 1024, 0, stream>>>(
         lg, targets, loss, rows, vocab, ld, grad_scale, ignore_index, status_word(device));
   } else {
     cross_entropy_kernel<false><<<(unsigned)rows, 512, 0, stream>>>(

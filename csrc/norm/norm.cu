@@ -1,7 +1,8 @@
 // LayerNorm / RMSNorm forward + backward, bf16 activations, fp32 statistics.
 // One warp per row, 16-byte vector loads, rows re-read through L1 instead of staged.
 // Backward fuses (a) the optional upstream residual gradient add into dx and (b) the
-// gamma/beta gradient reduction (shared-memory partials, one fp32 atomic per column per CTA),
+// gamma/beta gradient reduction (per-CTA partial sums in a scratch buffer, then a small
+// column-parallel second stage; no global atomics),
 // accumulating straight into the fp32 gradient buffers the fused optimizer consumes.
 // Semantics follow the reference's layers (src/nn/normalization.rs:59-99 LayerNorm,
 // :587-608,652-701 RMSNorm), which have forward only and no backward.
@@ -36,7 +37,8 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 }
 
 // RMS = true: y = x * rstd * g (beta ignored, mean = 0).  C % 8 == 0.
-template <bool RMS>
+// MAXV > 0: the row is cached in registers (C <= 256*MAXV) and read from memory once.
+template <bool RMS, int MAXV>
 __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
                                 const __nv_bfloat16* __restrict__ gamma,
                                 const __nv_bfloat16* __restrict__ beta,
@@ -47,10 +49,16 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
   if (row >= rows) return;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
   const int nv = C >> 3;
+  uint4 cache[MAXV > 0 ? MAXV : 1];
   float s = 0.f, ss = 0.f;
-  for (int v = lane; v < nv; v += 32) {
+#pragma unroll
+  for (int vi = 0; vi < (MAXV > 0 ? MAXV : 64); ++vi) {
+    const int v = lane + vi * 32;
+    if (v >= nv) break;
+    const uint4 w = xr[v];
+    if (MAXV > 0) cache[vi] = w;
     float f[8];
-    unpack8(xr[v], f);
+    unpack8(w, f);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       s += f[e];
@@ -66,9 +74,12 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
   } else {
     // second pass for a numerically safe variance
     float sq = 0.f;
-    for (int v = lane; v < nv; v += 32) {
+#pragma unroll
+    for (int vi = 0; vi < (MAXV > 0 ? MAXV : 64); ++vi) {
+      const int v = lane + vi * 32;
+      if (v >= nv) break;
       float f[8];
-      unpack8(xr[v], f);
+      unpack8(MAXV > 0 ? cache[vi] : xr[v], f);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const float d = f[e] - mean;
@@ -85,9 +96,12 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
   uint4* yr = reinterpret_cast<uint4*>(y + row * C);
   const uint4* gr = reinterpret_cast<const uint4*>(gamma);
   const uint4* br = reinterpret_cast<const uint4*>(beta);
-  for (int v = lane; v < nv; v += 32) {
+#pragma unroll
+  for (int vi = 0; vi < (MAXV > 0 ? MAXV : 64); ++vi) {
+    const int v = lane + vi * 32;
+    if (v >= nv) break;
     float f[8], g[8], o[8];
-    unpack8(xr[v], f);
+    unpack8(MAXV > 0 ? cache[vi] : xr[v], f);
     unpack8(gr[v], g);
     if (!RMS && beta) {
       float bb[8];
@@ -112,14 +126,18 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
                                 const __nv_bfloat16* __restrict__ gamma,
                                 const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                                 const __nv_bfloat16* __restrict__ dres,
-                                __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma,
-                                float* __restrict__ dbeta, long long rows, int C) {
-  extern __shared__ float sacc[];  // [2][C]
+                                __nv_bfloat16* __restrict__ dx, float* __restrict__ partial,
+                                long long rows, int C) {
+  // MAXV > 0: one [2][C] slot per warp (plain stores); MAXV == 0: a single [2][C] slot (atomics)
+  extern __shared__ float sacc[];
+  const int warps = blockDim.x >> 5;
+  const int n_slots = MAXV > 0 ? warps : 1;
   float* sdg = sacc;
   float* sdb = sacc + C;
-  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) sacc[i] = 0.f;
-  __syncthreads();
-  const int warps = blockDim.x >> 5;
+  if (MAXV == 0) {
+    for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) sacc[i] = 0.f;
+    __syncthreads();
+  }
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nv = C >> 3;
@@ -181,22 +199,59 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
     }
   }
   if (MAXV > 0) {
+    float* wdg = sacc + (size_t)warp * 2 * C;
+    float* wdb = wdg + C;
 #pragma unroll
     for (int vi = 0; vi < (MAXV > 0 ? MAXV : 1); ++vi) {
       const int v = lane + vi * 32;
       if (v < nv) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          atomicAdd(&sdg[v * 8 + e], adg[vi * 8 + e]);
-          if (!RMS) atomicAdd(&sdb[v * 8 + e], adb[vi * 8 + e]);
+        float4* g4 = reinterpret_cast<float4*>(wdg + v * 8);
+        g4[0] = make_float4(adg[vi * 8 + 0], adg[vi * 8 + 1], adg[vi * 8 + 2], adg[vi * 8 + 3]);
+        g4[1] = make_float4(adg[vi * 8 + 4], adg[vi * 8 + 5], adg[vi * 8 + 6], adg[vi * 8 + 7]);
+        if (!RMS) {
+          float4* b4 = reinterpret_cast<float4*>(wdb + v * 8);
+          b4[0] = make_float4(adb[vi * 8 + 0], adb[vi * 8 + 1], adb[vi * 8 + 2], adb[vi * 8 + 3]);
+          b4[1] = make_float4(adb[vi * 8 + 4], adb[vi * 8 + 5], adb[vi * 8 + 6], adb[vi * 8 + 7]);
         }
       }
     }
   }
   __syncthreads();
+  // per-CTA partial sums: partial[0][cta][C] = dgamma part, partial[1][cta][C] = dbeta part
+  float* pg = partial + (long long)blockIdx.x * C;
+  float* pb = partial + ((long long)gridDim.x + blockIdx.x) * C;
   for (int i = threadIdx.x; i < C; i += blockDim.x) {
-    if (dgamma) atomicAdd(&dgamma[i], sdg[i]);
-    if (!RMS && dbeta) atomicAdd(&dbeta[i], sdb[i]);
+    float tg = 0.f, tb = 0.f;
+    for (int w = 0; w < n_slots; ++w) {
+      tg += sacc[(size_t)w * 2 * C + i];
+      if (!RMS) tb += sacc[(size_t)w * 2 * C + C + i];
+    }
+    pg[i] = tg;
+    if (!RMS) pb[i] = tb;
+  }
+}
+
+// Second stage: out[c] += sum over CTAs of partial[.][cta][c].  One CTA covers 32 columns with
+// 32 partial-row lanes (coalesced 128-byte reads), combined through shared memory.
+__global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dgamma,
+                                       float* __restrict__ dbeta, int n_part, int C) {
+  __shared__ float red[32][33];
+  const int cl = threadIdx.x & 31, pl = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cl;
+  const bool is_beta = blockIdx.y == 1;
+  float* out = is_beta ? dbeta : dgamma;
+  if (out == nullptr) return;
+  const float* src = partial + (is_beta ? (long long)n_part * C : 0);
+  float acc = 0.f;
+  if (c < C)
+    for (int g = pl; g < n_part; g += 32) acc += src[(long long)g * C + c];
+  red[pl][cl] = acc;
+  __syncthreads();
+  if (pl == 0 && c < C) {
+    float t = 0.f;
+#pragma unroll
+    for (int r = 0; r < 32; ++r) t += red[r][cl];
+    out[c] += t;
   }
 }
 
@@ -209,10 +264,14 @@ void norm_fwd(const NormArgs& a, cudaStream_t stream) {
   auto g = reinterpret_cast<const __nv_bfloat16*>(a.gamma);
   auto b = reinterpret_cast<const __nv_bfloat16*>(a.beta);
   auto y = reinterpret_cast<__nv_bfloat16*>(a.y);
-  if (a.rms)
-    norm_fwd_kernel<true><<<grid, wpb * 32, 0, stream>>>(x, g, b, y, a.mean, a.rstd, a.rows, a.C, a.eps);
-  else
-    norm_fwd_kernel<false><<<grid, wpb * 32, 0, stream>>>(x, g, b, y, a.mean, a.rstd, a.rows, a.C, a.eps);
+  const bool small = a.C <= 1024;
+  if (a.rms) {
+    if (small) norm_fwd_kernel<true, 4><<<grid, wpb * 32, 0, stream>>>(x, g, b, y, a.mean, a.rstd, a.rows, a.C, a.eps);
+    else norm_fwd_kernel<true, 0><<<grid, wpb * 32, 0, stream>>>(x, g, b, y, a.mean, a.rstd, a.rows, a.C, a.eps);
+  } else {
+    if (small) norm_fwd_kernel<false, 4><<<grid, wpb * 32, 0, stream>>>(x, g, b, y, a.mean, a.rstd, a.rows, a.C, a.eps);
+    else norm_fwd_kernel<false, 0><<<grid, wpb * 32, 0, stream>>>(x, g, b, y, a.mean, a.rstd, a.rows, a.C, a.eps);
+  }
   RT_LAUNCH_CHECK();
 }
 
@@ -226,26 +285,36 @@ static void launch_norm_bwd(const NormArgs& a, unsigned grid, int threads, size_
       reinterpret_cast<const __nv_bfloat16*>(a.dy), reinterpret_cast<const __nv_bfloat16*>(a.x),
       reinterpret_cast<const __nv_bfloat16*>(a.gamma), a.mean, a.rstd,
       reinterpret_cast<const __nv_bfloat16*>(a.dres), reinterpret_cast<__nv_bfloat16*>(a.dx),
-      a.dgamma, a.dbeta, a.rows, a.C);
+      a.partial, a.rows, a.C);
   RT_LAUNCH_CHECK();
+}
+
+int norm_bwd_num_partials(long long rows, int sm_count) {
+  const int warps = 8;
+  const long long want = (rows + warps - 1) / warps;
+  return (int)std::max<long long>(1, std::min<long long>(want, 2LL * sm_count));
 }
 
 void norm_bwd(const NormArgs& a, cudaStream_t stream) {
   RT_CHECK(a.C % 8 == 0, "norm: feature size must be a multiple of 8");
   RT_CHECK(a.C <= 16384, "norm backward: feature size above 16384 not supported");
   if (a.rows == 0) return;
+  RT_CHECK(a.partial != nullptr && a.n_partial >= 1, "norm backward: scratch for partial sums missing");
   const int threads = 256;
-  const int warps = threads / 32;
-  const long long want = (a.rows + warps - 1) / warps;
-  const unsigned grid = (unsigned)std::min<long long>(want, 2LL * sm_count(current_device()));
-  const size_t smem = sizeof(float) * 2 * a.C;
+  const unsigned grid = (unsigned)a.n_partial;
   const bool small = a.C <= 1024;
+  const size_t smem = sizeof(float) * 2 * a.C * (small ? threads / 32 : 1);
   if (a.rms) {
     if (small) launch_norm_bwd<true, 4>(a, grid, threads, smem, stream);
     else launch_norm_bwd<true, 0>(a, grid, threads, smem, stream);
   } else {
     if (small) launch_norm_bwd<false, 4>(a, grid, threads, smem, stream);
     else launch_norm_bwd<false, 0>(a, grid, threads, smem, stream);
+  }
+  if (a.dgamma != nullptr || (!a.rms && a.dbeta != nullptr)) {
+    dim3 g2((a.C + 31) / 32, a.rms ? 1 : 2);
+    norm_bwd_reduce_kernel<<<g2, 1024, 0, stream>>>(a.partial, a.dgamma, a.dbeta, a.n_partial, a.C);
+    RT_LAUNCH_CHECK();
   }
 }
 

@@ -7,39 +7,76 @@
 
 namespace rt {
 
-// out[n] += sum_m x[m][n]   x bf16 [M][ld], out fp32.  Thread owns 2 adjacent columns.
-__global__ void colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out,
-                              long long M, int N, long long ld, int rows_per_block) {
-  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+// out[n] += sum_m x[m][n]   x bf16 [M][ld], out fp32.
+// Block = 32 column groups (8 columns = one 16-byte load each) x 8 row lanes; a warp reads 512
+// contiguous bytes of one row.  Row lanes are combined through shared memory, then one fp32
+// atomic per column per block.
+__global__ void colsum_vec_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out,
+                                  long long M, int N, long long ld, int rows_per_block) {
+  __shared__ float part[8][32 * 8 + 8];
+  const int cg = threadIdx.x & 31;
+  const int rl = threadIdx.x >> 5;
+  const int c0 = (blockIdx.x * 32 + cg) * 8;
+  const long long m0 = (long long)blockIdx.y * rows_per_block;
+  const long long m1 = min(M, m0 + rows_per_block);
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  if (c0 < N) {
+#pragma unroll 4
+    for (long long m = m0 + rl; m < m1; m += 8) {
+      const uint4 w = *reinterpret_cast<const uint4*>(x + m * ld + c0);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) part[rl][cg * 8 + e] = acc[e];
+  __syncthreads();
+  const int c = threadIdx.x;  // 256 threads -> 256 columns of this block
+  const int col = blockIdx.x * 256 + c;
+  if (col < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) t += part[r][c];
+    atomicAdd(out + col, t);
+  }
+}
+
+// Scalar fallback for N % 8 != 0 or unaligned rows: thread owns one column.
+__global__ void colsum_scalar_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out,
+                                     long long M, int N, long long ld, int rows_per_block) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= N) return;
   const long long m0 = (long long)blockIdx.y * rows_per_block;
   const long long m1 = min(M, m0 + rows_per_block);
-  float a0 = 0.f, a1 = 0.f;
-  if (c + 1 < N) {
-    for (long long m = m0; m < m1; ++m) {
-      float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + m * ld + c));
-      a0 += v.x;
-      a1 += v.y;
-    }
-    atomicAdd(out + c, a0);
-    atomicAdd(out + c + 1, a1);
-  } else {
-    for (long long m = m0; m < m1; ++m) a0 += __bfloat162float(x[m * ld + c]);
-    atomicAdd(out + c, a0);
-  }
+  float a0 = 0.f;
+  for (long long m = m0; m < m1; ++m) a0 += __bfloat162float(x[m * ld + c]);
+  atomicAdd(out + c, a0);
 }
 
 void colsum_accum(const void* x, float* out, long long M, int N, long long ld,
                   cudaStream_t stream) {
-  RT_CHECK(ld % 2 == 0, "colsum: row stride must be even");
   if (M == 0 || N == 0) return;
-  const int threads = 128;
-  const int gx = ((N + 1) / 2 + threads - 1) / threads;
-  int rpb = 256;
-  long long gy = (M + rpb - 1) / rpb;
-  dim3 grid(gx, (unsigned)gy);
-  colsum_kernel<<<grid, threads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), out, M, N,
-                                              ld, rpb);
+  auto xp = reinterpret_cast<const __nv_bfloat16*>(x);
+  const bool vec = (N % 8 == 0) && (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+  if (vec) {
+    const int gx = (N + 255) / 256;
+    // enough blocks to cover the machine a few times over
+    int rpb = 512;
+    while (rpb > 64 && (long long)gx * ((M + rpb - 1) / rpb) < 4LL * sm_count(current_device())) rpb >>= 1;
+    dim3 grid(gx, (unsigned)((M + rpb - 1) / rpb));
+    colsum_vec_kernel<<<grid, 256, 0, stream>>>(xp, out, M, N, ld, rpb);
+  } else {
+    const int rpb = 256;
+    dim3 grid((N + 127) / 128, (unsigned)((M + rpb - 1) / rpb));
+    colsum_scalar_kernel<<<grid, 128, 0, stream>>>(xp, out, M, N, ld, rpb);
+  }
   RT_LAUNCH_CHECK();
 }
 
