@@ -1,7 +1,8 @@
 """The allocation-free C entry point ``rt_norm_bwd_noalloc`` against the normal norm backward.
 
-Some users of the library cannot allocate device memory when they need this kernel (inside
-stream capture, in allocator callbacks, in hosts without torch's caching allocator), so the
+Some users of the library cannot allocate device memory when they need this kernel (in
+allocator callbacks, in serving loops that forbid allocation after warm-up, in C hosts without
+torch's caching allocator), so the
 library exports one C symbol whose scratch lives in a fixed device array.  The test calls the
 symbol through ctypes with raw pointers, twice in a row (the second call sees the first
 call's leftovers in the shared array), and compares with the tensor path.  The file name makes
