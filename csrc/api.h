@@ -117,4 +117,27 @@ struct OptimArgs {
 };
 void fused_optim_step(const OptimArgs& a, cudaStream_t stream);
 
+// ------------------------------------------------------------ collective/ddp_fused.cu
+constexpr int RT_MAX_PEERS = 8;
+struct DdpBucketArgs {
+  float* grad[RT_MAX_PEERS];  // every rank's flat fp32 gradient buffer (peer pointers)
+  void* lp[RT_MAX_PEERS];     // every rank's flat bf16 parameter buffer (peer pointers)
+  int* flags[RT_MAX_PEERS];   // every rank's flag array (peer pointers)
+  float* master;              // local flat fp32 master weights / moments (indexed like grad)
+  float* m;
+  float* v;
+  unsigned* done_counter;     // local, zero-initialised
+  long long bucket_start;     // flat index of the bucket
+  long long chunk_len;        // elements owned by each rank inside the bucket (multiple of 4)
+  int world, rank;
+  int epoch;                  // strictly increasing per step
+  int start_slot, end_slot;   // offsets into the flag arrays (slot * world)
+  unsigned long long timeout_ns;
+  float lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, grad_scale;
+  int* status;
+};
+void ddp_bucket_adamw(const DdpBucketArgs& a, int n_ctas, cudaStream_t stream);
+void ddp_wait_end(const int* flags, int n_slots, int world, int rank, int epoch,
+                  unsigned long long timeout_ns, int* status, cudaStream_t stream);
+
 }  // namespace rt

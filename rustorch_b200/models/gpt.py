@@ -85,6 +85,7 @@ class GPT(nn.Module):
         self.lnf_b = nn.Parameter(torch.zeros(C, **kw))
         if cfg.tie_weights:
             self.lm_head = self.wte
+            self.wte._grad_contribs = 2  # embedding backward + lm_head backward
         else:
             self.lm_head = nn.Parameter(torch.empty(Vp, C, **kw))
         self.reset_parameters(seed)

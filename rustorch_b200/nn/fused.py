@@ -25,6 +25,16 @@ from ..ops import kernels as K
 
 _NUM_SMS = 148
 
+# Called at the end of every fused backward with the parameters whose gradients that backward has
+# finished accumulating AND whose values it no longer reads.  The data-parallel wrapper uses it to
+# launch a gradient bucket as soon as the bucket is complete (overlap with the rest of backward).
+grad_ready_hook = None
+
+
+def _notify(*params):
+    if grad_ready_hook is not None:
+        grad_ready_hook([p for p in params if p is not None])
+
 
 def _split_k_for(tiles: int, k_blocks: int) -> int:
     if tiles >= 4 * _NUM_SMS:
@@ -112,6 +122,7 @@ class AttnBlockFn(torch.autograd.Function):
         dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dy2)
         g_lnw = None if direct else wg.to(ln_w.dtype)
         g_lnb = None if (direct or ln_b is None) else bg.to(ln_b.dtype)
+        _notify(w_proj, b_proj, w_qkv, b_qkv, ln_w, ln_b)
         return (dx.view(B, T, C), g_lnw, g_lnb, g_wqkv, g_bqkv, g_wproj, g_bproj, None, None, None)
 
 
@@ -145,6 +156,7 @@ class MLPBlockFn(torch.autograd.Function):
         dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dy2)
         g_lnw = None if direct else wg.to(ln_w.dtype)
         g_lnb = None if (direct or ln_b is None) else bg.to(ln_b.dtype)
+        _notify(w2, b2, w1, b1, ln_w, ln_b)
         return (dx.view(B, T, C), g_lnw, g_lnb, g_w1, g_b1, g_w2, g_b2, None)
 
 
@@ -170,6 +182,7 @@ class EmbeddingFn(torch.autograd.Function):
             dwte = torch.zeros(wte.shape, dtype=torch.float32, device=wte.device)
             dwpe = torch.zeros(wpe.shape, dtype=torch.float32, device=wte.device) if wpe is not None else None
         K.embedding_bwd(idx, dout, dwte, dwpe, T, wte.shape[0])
+        _notify(wte, wpe)
         if direct:
             return None, None, None
         return None, dwte.to(wte.dtype), (dwpe.to(wpe.dtype) if wpe is not None else None)
@@ -214,6 +227,7 @@ class LMHeadLossFn(torch.autograd.Function):
         dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg)
         g_lnw = None if direct else wg.to(ln_w.dtype)
         g_lnb = None if (direct or ln_b is None) else bg.to(ln_b.dtype)
+        _notify(w_head, ln_w, ln_b)
         return dx.view(B, T, C), g_lnw, g_lnb, g_head, None, None, None, None
 
 
@@ -235,6 +249,7 @@ class LinearFn(torch.autograd.Function):
         gw = wgrad_into(dy2, x2, w) if ctx.needs_input_grad[1] else None
         gb = bgrad_into(dy2, b) if (b is not None and ctx.needs_input_grad[2]) else None
         dx = K.gemm(dy2, w, b_mn=True).view(ctx.xshape) if ctx.needs_input_grad[0] else None
+        _notify(w, b)
         return dx, gw, gb
 
 
@@ -252,6 +267,7 @@ class LayerNormFn(torch.autograd.Function):
         x2, w, b, mean, rstd = ctx.saved_tensors
         wg, bg, direct = _norm_grad_bufs(w, b)
         dx = K.layer_norm_bwd(dy.contiguous().view(x2.shape), x2, w, mean, rstd, wg, bg)
+        _notify(w, b)
         return (dx.view(ctx.xshape), None if direct else wg.to(w.dtype),
                 None if (direct or b is None) else bg.to(b.dtype), None)
 
@@ -270,6 +286,7 @@ class RMSNormFn(torch.autograd.Function):
         x2, w, rstd = ctx.saved_tensors
         wg, _, direct = _norm_grad_bufs(w, None)
         dx = K.rms_norm_bwd(dy.contiguous().view(x2.shape), x2, w, rstd, wg)
+        _notify(w)
         return dx.view(ctx.xshape), None if direct else wg.to(w.dtype), None
 
 

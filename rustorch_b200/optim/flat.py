@@ -32,7 +32,11 @@ def default_decay_filter(name: str, p: torch.Tensor) -> bool:
 
 class FlatParams:
     def __init__(self, module: torch.nn.Module, decay_filter: Callable = default_decay_filter,
-                 alloc: Optional[Callable] = None, alloc_f32: Optional[Callable] = None):
+                 alloc: Optional[Callable] = None, alloc_f32: Optional[Callable] = None,
+                 group_align: int = _ALIGN):
+        """``alloc(n)`` / ``alloc_f32(n)`` let a caller place the bf16 parameter buffer and the fp32
+        gradient buffer in special memory (e.g. symmetric memory visible to peer GPUs);
+        ``group_align`` pads the decay / no-decay groups to a multiple of that many elements."""
         named = [(n, p) for n, p in module.named_parameters() if p.requires_grad]
         seen, uniq = set(), []
         for n, p in named:
@@ -46,10 +50,12 @@ class FlatParams:
         for n, p in decay:
             self.entries.append((n, p, off, p.numel()))
             off += -(-p.numel() // _ALIGN) * _ALIGN
+        off = -(-off // group_align) * group_align
         self.n_decay = off
         for n, p in nodecay:
             self.entries.append((n, p, off, p.numel()))
             off += -(-p.numel() // _ALIGN) * _ALIGN
+        off = -(-off // group_align) * group_align
         self.numel = off
         dev = uniq[0][1].device if uniq else torch.device("cpu")
         self.device = dev

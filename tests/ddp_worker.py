@@ -1,0 +1,105 @@
+"""Worker for the multi-GPU data-parallel tests (launched by torch.distributed.run).
+
+Every rank trains the same tiny GPT on its own batches with the fused peer-memory bucket kernel
+and, in the same process, replays the job as one big-batch single-GPU run (gradients of all
+ranks' batches averaged) with the plain fused AdamW.  Prints one JSON line per rank.
+"""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    mode = sys.argv[1] if len(sys.argv) > 1 else "fused"
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from rustorch_b200 import _native
+    from rustorch_b200.models.gpt import GPT, GPTConfig
+    from rustorch_b200.optim.flat import FlatParams, FusedAdamW
+    from rustorch_b200.distributed.fused_allreduce import FusedDDPAdamW
+    from rustorch_b200.distributed.ddp_flat import FlatDDP
+
+    cfg = GPTConfig(vocab_size=512, n_positions=128, n_embd=256, n_layer=2, n_head=4, dropout=0.0)
+    steps, B, T = 6, 4, 128
+    gen = torch.Generator().manual_seed(7)
+    data = torch.randint(0, cfg.vocab_size, (steps, world, B, T + 1), generator=gen).to(dev)
+    hp = dict(lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+
+    # --- single-GPU big-batch replay (oracle)
+    ref = GPT(cfg, device=dev, dtype=torch.bfloat16, seed=3)
+    rflat = FlatParams(ref)
+    init = rflat.master.clone()
+    ropt = FusedAdamW(rflat, **hp)
+    ropt.grad_scale = 1.0 / world
+    ref_losses = []
+    for s in range(steps):
+        tot = 0.0
+        for r in range(world):
+            b = data[s, r]
+            loss = ref(b[:, :-1], b[:, 1:])
+            loss.backward()
+            tot += float(loss)
+        ropt.step()
+        ref_losses.append(tot / world)
+    ref_master = rflat.named_views(rflat.master)
+
+    # --- data-parallel run
+    model = GPT(cfg, device=dev, dtype=torch.bfloat16, seed=3)
+    losses = []
+    if mode == "fused":
+        ddp = FusedDDPAdamW(model, bucket_cap_mb=1.0, timeout_s=20.0, **hp)
+        for s in range(steps):
+            b = data[s, rank]
+            loss = model(b[:, :-1], b[:, 1:])
+            loss.backward()
+            ddp.step()
+            losses.append(float(loss))
+        _native.check_status()
+        full = ddp.gather_master()
+        got = ddp.flat.named_views(full)
+        n_buckets = ddp.n_buckets
+        ddp.close()
+    else:
+        flat = FlatParams(model)
+        opt = FusedAdamW(flat, **hp)
+        opt.grad_scale = 1.0 / world
+        nddp = FlatDDP(flat, bucket_cap_mb=1.0)
+        nddp.broadcast_parameters()
+        for s in range(steps):
+            b = data[s, rank]
+            loss = model(b[:, :-1], b[:, 1:])
+            loss.backward()
+            nddp.sync_gradients()
+            opt.step()
+            losses.append(float(loss))
+        got = flat.named_views(flat.master)
+        n_buckets = len(nddp.buckets)
+
+    # averaged loss across ranks must follow the big-batch run
+    lt = torch.tensor(losses, device=dev)
+    dist.all_reduce(lt)
+    lt /= world
+    init_v = rflat.named_views(init)
+    worst = 0.0
+    for name in ref_master:
+        upd = (ref_master[name] - init_v[name]).abs().mean().clamp_min(1e-12)
+        diff = (got[name].to(dev) - ref_master[name]).abs().mean()
+        worst = max(worst, float(diff / upd))
+    out = {"rank": rank, "world": world, "mode": mode, "n_buckets": n_buckets,
+           "loss_ddp": [round(float(x), 4) for x in lt], "loss_ref": [round(x, 4) for x in ref_losses],
+           "worst_rel_update_diff": round(worst, 4)}
+    print("RESULT " + json.dumps(out), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,40 @@
+"""Data-parallel step on >= 2 GPUs: fused peer-memory bucket kernel vs a single-GPU big-batch run."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(mode, nproc):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(ROOT, "tests", "ddp_worker.py"), mode]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    res = [json.loads(l.split("RESULT ", 1)[1]) for l in p.stdout.splitlines() if l.startswith("RESULT ")]
+    assert len(res) == nproc
+    return res
+
+
+@pytest.mark.parametrize("mode", ["fused", "nccl"])
+def test_ddp_matches_big_batch(mode):
+    nproc = min(torch.cuda.device_count(), 4)
+    for r in _run(mode, nproc):
+        for a, b in zip(r["loss_ddp"], r["loss_ref"]):
+            assert abs(a - b) < 3e-2, r
+        assert r["worst_rel_update_diff"] < 0.15, r
+        assert r["loss_ddp"][-1] < r["loss_ddp"][0]

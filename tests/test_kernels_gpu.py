@@ -136,3 +136,31 @@ def test_fused_sgd_momentum_matches_torch():
         ropt.step()
     views = flat.named_views(flat.master)
     assert rel_err(views["weight"], ref.weight) < 1e-5
+
+
+def test_ddp_bucket_kernel_single_rank_matches_fused_adamw():
+    """world = 1: the bucket kernel is a fused AdamW over buckets and must equal FusedAdamW."""
+    from rustorch_b200.distributed.fused_allreduce import FusedDDPAdamW
+    from rustorch_b200.optim.flat import FlatParams, FusedAdamW
+    from rustorch_b200.nn import fused
+    torch.manual_seed(0)
+    a = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.Linear(512, 128)).cuda().to(torch.bfloat16)
+    b = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.Linear(512, 128)).cuda().to(torch.bfloat16)
+    b.load_state_dict(a.state_dict())
+    hp = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    ddp = FusedDDPAdamW(a, bucket_cap_mb=0.25, overlap=False, **hp)
+    flat = FlatParams(b)
+    opt = FusedAdamW(flat, **hp)
+    assert ddp.n_buckets > 2
+    for _ in range(3):
+        g = torch.randn(flat.numel, device="cuda")
+        ddp.flat.grad.copy_(g)
+        flat.grad.copy_(g)
+        ddp.step()
+        opt.step()
+    torch.cuda.synchronize()
+    assert float((ddp.flat.master - flat.master).abs().max()) < 1e-6
+    assert float((ddp.flat.lp.float() - flat.lp.float()).abs().max()) == 0.0
+    assert float(ddp.flat.grad.abs().max()) == 0.0
+    ddp.close()
+    assert fused.grad_ready_hook is None
