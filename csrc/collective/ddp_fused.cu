@@ -14,8 +14,9 @@
 // and its 25 MB bucket plan (src/distributed/ddp.rs:235-271).
 //
 // Peer access is by plain loads/stores on peer pointers from symmetric allocations; there is no
-// TMA and no multicast in this file.  The kernel is deliberately small (few CTAs of 128 threads,
-// <= 48 registers) so it co-resides with the backward GEMMs it overlaps.
+// TMA and no multicast in this file.  The kernel uses a few dozen CTAs of 128 threads and keeps up
+// to 16 peer loads per thread in flight, so a 25 MB bucket takes tens of microseconds and the
+// backward kernels it overlaps lose little.
 // Every wait is bounded by a caller-supplied deadline; on expiry the kernel records
 // RT_ERR_TIMEOUT_PEER in the status word, skips its update and returns.
 #include "../api.h"
@@ -61,7 +62,7 @@ __device__ __forceinline__ bool wait_flags(const int* flags, int n, int skip, in
   return __syncthreads_and(ok ? 1 : 0) != 0;
 }
 
-__global__ void __launch_bounds__(128, 12) ddp_bucket_adamw_kernel(const DdpBucketArgs a) {
+__global__ void __launch_bounds__(128, 4) ddp_bucket_adamw_kernel(const DdpBucketArgs a) {
   const int W = a.world, R = a.rank;
   int* my_flags = a.flags[R];
   // ---- start barrier: tell every peer this rank's bucket gradients are final, wait for theirs
@@ -76,20 +77,35 @@ __global__ void __launch_bounds__(128, 12) ddp_bucket_adamw_kernel(const DdpBuck
   const long long base = a.bucket_start + (long long)R * a.chunk_len;  // flat index of my shard
   const long long n4 = a.chunk_len >> 2;
   const float inv_w = a.grad_scale;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long e = base + (i << 2);
-    float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
-    for (int p = 0; p < W; ++p) {
-      float* src = a.grad[p] + e;
-      const float4 v = ld_peer_f4(src);
-      g.x += v.x; g.y += v.y; g.z += v.z; g.w += v.w;
-      *reinterpret_cast<float4*>(src) = make_float4(0.f, 0.f, 0.f, 0.f);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  // Two 16-byte groups per thread per trip, and the loads from all ranks are issued before any
+  // is consumed, so up to 16 NVLink loads per thread are in flight.
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < n4; i0 += 2 * stride) {
+    const long long i1 = i0 + stride;
+    const bool has1 = i1 < n4;
+    const long long e0 = base + (i0 << 2);
+    const long long e1 = base + ((has1 ? i1 : i0) << 2);
+    float4 v0[RT_MAX_PEERS], v1[RT_MAX_PEERS];
+#pragma unroll
+    for (int p = 0; p < RT_MAX_PEERS; ++p) {
+      if (p < W) {
+        v0[p] = ld_peer_f4(a.grad[p] + e0);
+        if (has1) v1[p] = ld_peer_f4(a.grad[p] + e1);
+      }
     }
-    float4 pm = *reinterpret_cast<float4*>(a.master + e);
-    float4 m = *reinterpret_cast<float4*>(a.m + e);
-    float4 v = *reinterpret_cast<float4*>(a.v + e);
+    float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int p = 0; p < RT_MAX_PEERS; ++p) {
+      if (p < W) {
+        g0.x += v0[p].x; g0.y += v0[p].y; g0.z += v0[p].z; g0.w += v0[p].w;
+        *reinterpret_cast<float4*>(a.grad[p] + e0) = z;
+        if (has1) {
+          g1.x += v1[p].x; g1.y += v1[p].y; g1.z += v1[p].z; g1.w += v1[p].w;
+          *reinterpret_cast<float4*>(a.grad[p] + e1) = z;
+        }
+      }
+    }
 #define RT_ADAMW1(P, G, M, V)                                          \
     {                                                                  \
       const float gg = (G) * inv_w;                                    \
@@ -98,20 +114,29 @@ __global__ void __launch_bounds__(128, 12) ddp_bucket_adamw_kernel(const DdpBuck
       (P) *= (1.f - a.lr * a.weight_decay);                            \
       (P) -= a.lr * ((M) / a.bias_corr1) / (sqrtf((V) / a.bias_corr2) + a.eps); \
     }
-    RT_ADAMW1(pm.x, g.x, m.x, v.x)
-    RT_ADAMW1(pm.y, g.y, m.y, v.y)
-    RT_ADAMW1(pm.z, g.z, m.z, v.z)
-    RT_ADAMW1(pm.w, g.w, m.w, v.w)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      if (half == 1 && !has1) break;
+      const long long e = half == 0 ? e0 : e1;
+      const float4 g = half == 0 ? g0 : g1;
+      float4 pm = *reinterpret_cast<float4*>(a.master + e);
+      float4 m = *reinterpret_cast<float4*>(a.m + e);
+      float4 v = *reinterpret_cast<float4*>(a.v + e);
+      RT_ADAMW1(pm.x, g.x, m.x, v.x)
+      RT_ADAMW1(pm.y, g.y, m.y, v.y)
+      RT_ADAMW1(pm.z, g.z, m.z, v.z)
+      RT_ADAMW1(pm.w, g.w, m.w, v.w)
+      *reinterpret_cast<float4*>(a.master + e) = pm;
+      *reinterpret_cast<float4*>(a.m + e) = m;
+      *reinterpret_cast<float4*>(a.v + e) = v;
+      uint2 w;
+      w.x = pack_bf16x2(pm.x, pm.y);
+      w.y = pack_bf16x2(pm.z, pm.w);
+#pragma unroll
+      for (int p = 0; p < RT_MAX_PEERS; ++p)
+        if (p < W) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.lp[p]) + e) = w;
+    }
 #undef RT_ADAMW1
-    *reinterpret_cast<float4*>(a.master + e) = pm;
-    *reinterpret_cast<float4*>(a.m + e) = m;
-    *reinterpret_cast<float4*>(a.v + e) = v;
-    uint2 w;
-    w.x = pack_bf16x2(pm.x, pm.y);
-    w.y = pack_bf16x2(pm.z, pm.w);
-#pragma unroll 1
-    for (int p = 0; p < W; ++p)
-      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.lp[p]) + e) = w;
   }
 
   // ---- end signal: the last CTA to finish tells every peer that this rank is done writing

@@ -1,0 +1,790 @@
+"""``Tensor``: the RusTorch tensor surface over ``torch.Tensor``.
+
+Method names, argument order and defaults follow the reference's ``Tensor<T>``
+(src/tensor/core.rs:25-35,40-114,240-404; ops under src/tensor/ops/*) so code written against
+RusTorch's API reads the same here; the data lives in a ``torch.Tensor`` (``.data``), which on a
+CUDA device really is on the GPU (the reference's ``device`` is a tag only and its tensors never
+leave host memory, src/tensor/core.rs:136-138,168-179).
+
+Anything not spelled out below falls through to the wrapped ``torch.Tensor`` via
+``__getattr__`` with results re-wrapped, so the full PyTorch method set is available too.
+"""
+from __future__ import annotations
+
+import math
+from typing import Iterable, List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+
+from .dtype import DType, to_torch_dtype
+
+Number = Union[int, float]
+
+
+class Device:
+    """``Cpu / Cuda(idx) / Mps / Wasm`` device tag (src/tensor/device.rs:10-47); only cpu/cuda exist here."""
+
+    def __init__(self, kind: str = "cpu", index: int = 0):
+        kind = kind.lower()
+        if ":" in kind:
+            kind, idx = kind.split(":")
+            index = int(idx)
+        if kind in ("gpu",):
+            kind = "cuda"
+        if kind not in ("cpu", "cuda"):
+            raise ValueError(f"device '{kind}' does not exist in this build (cpu and cuda only)")
+        self.kind, self.index = kind, index
+
+    @staticmethod
+    def cpu() -> "Device":
+        return Device("cpu")
+
+    @staticmethod
+    def cuda(index: int = 0) -> "Device":
+        return Device("cuda", index)
+
+    def is_cuda(self) -> bool:
+        return self.kind == "cuda"
+
+    def to_torch(self) -> torch.device:
+        return torch.device(self.kind, self.index) if self.kind == "cuda" else torch.device("cpu")
+
+    def __str__(self) -> str:
+        return f"cuda:{self.index}" if self.kind == "cuda" else "cpu"
+
+    __repr__ = __str__
+
+    def __eq__(self, other) -> bool:
+        return isinstance(other, Device) and str(self) == str(other)
+
+
+def _dev(device) -> torch.device:
+    if device is None:
+        return torch.device("cpu")
+    if isinstance(device, Device):
+        return device.to_torch()
+    return torch.device(device)
+
+
+def _unwrap(x):
+    if isinstance(x, Tensor):
+        return x.data
+    if isinstance(x, (list, tuple)):
+        return type(x)(_unwrap(v) for v in x)
+    return x
+
+
+def _wrap(x):
+    if isinstance(x, torch.Tensor):
+        return Tensor(x)
+    if isinstance(x, (list, tuple)):
+        return type(x)(_wrap(v) for v in x)
+    return x
+
+
+class Tensor:
+    __slots__ = ("data",)
+    __array_priority__ = 100
+
+    # ------------------------------------------------------------ construction
+    def __init__(self, data=None, shape: Optional[Sequence[int]] = None, dtype=None, device=None,
+                 requires_grad: bool = False):
+        if isinstance(data, Tensor):
+            t = data.data
+        elif isinstance(data, torch.Tensor):
+            t = data
+        else:
+            t = torch.as_tensor(np.asarray(data, dtype=np.float32) if dtype is None and not isinstance(data, np.ndarray) else data)
+        if dtype is not None:
+            t = t.to(to_torch_dtype(dtype))
+        if shape is not None:
+            if int(np.prod(shape)) != t.numel():
+                raise ValueError(f"shape {tuple(shape)} does not match {t.numel()} elements")
+            t = t.reshape(tuple(shape))
+        if device is not None:
+            t = t.to(_dev(device))
+        if requires_grad:
+            t = t.detach().requires_grad_(True)
+        self.data = t
+
+    new = classmethod(lambda cls, data, shape=None, **kw: cls(data, shape, **kw))
+
+    @classmethod
+    def from_vec(cls, data: Sequence[Number], shape: Sequence[int], **kw) -> "Tensor":
+        return cls(list(data), shape, **kw)
+
+    try_from_vec = from_vec
+
+    @classmethod
+    def from_ndarray(cls, arr: np.ndarray, **kw) -> "Tensor":
+        return cls(torch.from_numpy(np.ascontiguousarray(arr)), **kw)
+
+    from_numpy = from_ndarray
+
+    @classmethod
+    def from_scalar(cls, v: Number, **kw) -> "Tensor":
+        return cls(torch.tensor(float(v)), **kw)
+
+    @classmethod
+    def zeros(cls, shape, dtype=None, device=None) -> "Tensor":
+        return cls(torch.zeros(tuple(shape), dtype=to_torch_dtype(dtype or "f32"), device=_dev(device)))
+
+    @classmethod
+    def ones(cls, shape, dtype=None, device=None) -> "Tensor":
+        return cls(torch.ones(tuple(shape), dtype=to_torch_dtype(dtype or "f32"), device=_dev(device)))
+
+    @classmethod
+    def full(cls, shape, value: Number, dtype=None, device=None) -> "Tensor":
+        return cls(torch.full(tuple(shape), value, dtype=to_torch_dtype(dtype or "f32"), device=_dev(device)))
+
+    zeros_on_device = classmethod(lambda cls, shape, device: cls.zeros(shape, device=device))
+    ones_on_device = classmethod(lambda cls, shape, device: cls.ones(shape, device=device))
+    zeros_auto = classmethod(lambda cls, shape: cls.zeros(shape, device="cuda" if torch.cuda.is_available() else "cpu"))
+    ones_auto = classmethod(lambda cls, shape: cls.ones(shape, device="cuda" if torch.cuda.is_available() else "cpu"))
+
+    # creation ops (src/tensor/ops/creation.rs:14-325)
+    @classmethod
+    def randn(cls, shape, dtype=None, device=None, generator=None) -> "Tensor":
+        return cls(torch.randn(tuple(shape), dtype=to_torch_dtype(dtype or "f32"), device=_dev(device), generator=generator))
+
+    @classmethod
+    def rand(cls, shape, dtype=None, device=None, generator=None) -> "Tensor":
+        return cls(torch.rand(tuple(shape), dtype=to_torch_dtype(dtype or "f32"), device=_dev(device), generator=generator))
+
+    @classmethod
+    def uniform(cls, shape, low: float = 0.0, high: float = 1.0, device=None) -> "Tensor":
+        return cls(torch.empty(tuple(shape), device=_dev(device)).uniform_(low, high))
+
+    @classmethod
+    def randint(cls, low: int, high: int, shape, device=None) -> "Tensor":
+        return cls(torch.randint(low, high, tuple(shape), device=_dev(device)).float())
+
+    @classmethod
+    def eye(cls, n: int, device=None) -> "Tensor":
+        return cls(torch.eye(n, device=_dev(device)))
+
+    @classmethod
+    def arange(cls, start: Number, end: Optional[Number] = None, step: Number = 1, device=None) -> "Tensor":
+        if end is None:
+            start, end = 0, start
+        return cls(torch.arange(start, end, step, dtype=torch.float32, device=_dev(device)))
+
+    @classmethod
+    def linspace(cls, start: Number, end: Number, steps: int, device=None) -> "Tensor":
+        return cls(torch.linspace(start, end, steps, device=_dev(device)))
+
+    @classmethod
+    def logspace(cls, start: Number, end: Number, steps: int, base: float = 10.0, device=None) -> "Tensor":
+        return cls(torch.logspace(start, end, steps, base=base, device=_dev(device)))
+
+    @classmethod
+    def diag(cls, values) -> "Tensor":
+        return cls(torch.diag(_unwrap(values) if isinstance(values, Tensor) else torch.as_tensor(values, dtype=torch.float32)))
+
+    @staticmethod
+    def meshgrid(*tensors: "Tensor", indexing: str = "ij") -> Tuple["Tensor", ...]:
+        return tuple(Tensor(t) for t in torch.meshgrid(*[_unwrap(t) for t in tensors], indexing=indexing))
+
+    # --------------------------------------------------------------- accessors
+    def shape(self) -> Tuple[int, ...]:
+        return tuple(self.data.shape)
+
+    def ndim(self) -> int:
+        return self.data.dim()
+
+    def size(self) -> Tuple[int, ...]:
+        return tuple(self.data.shape)
+
+    def numel(self) -> int:
+        return self.data.numel()
+
+    def len(self) -> int:
+        return self.data.numel()
+
+    def is_empty(self) -> bool:
+        return self.data.numel() == 0
+
+    def device(self) -> Device:
+        d = self.data.device
+        return Device(d.type, d.index or 0)
+
+    def dtype(self) -> DType:
+        return DType.from_torch(self.data.dtype)
+
+    def requires_grad(self) -> bool:
+        return self.data.requires_grad
+
+    def set_requires_grad(self, flag: bool = True) -> "Tensor":
+        self.data.requires_grad_(flag)
+        return self
+
+    def get(self, index: Sequence[int]) -> float:
+        return float(self.data[tuple(index)])
+
+    def set(self, index: Sequence[int], value: Number) -> None:
+        self.data[tuple(index)] = value
+
+    def item(self) -> float:
+        return float(self.data.item())
+
+    def as_slice(self) -> List[float]:
+        return self.data.detach().reshape(-1).tolist()
+
+    to_vec = as_slice
+    tolist = lambda self: self.data.detach().tolist()  # noqa: E731
+
+    def numpy(self) -> np.ndarray:
+        return self.data.detach().cpu().numpy()
+
+    as_array = numpy
+
+    def to_device(self, device) -> "Tensor":
+        return Tensor(self.data.to(_dev(device)))
+
+    to = to_device
+
+    def try_to_gpu(self, index: int = 0) -> "Tensor":
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device available")
+        return Tensor(self.data.to(torch.device("cuda", index)))
+
+    def cpu(self) -> "Tensor":
+        return Tensor(self.data.cpu())
+
+    def cuda(self, index: int = 0) -> "Tensor":
+        return self.try_to_gpu(index)
+
+    def is_cuda(self) -> bool:
+        return self.data.is_cuda
+
+    def clone(self) -> "Tensor":
+        return Tensor(self.data.clone())
+
+    def detach(self) -> "Tensor":
+        return Tensor(self.data.detach())
+
+    def astype(self, dtype) -> "Tensor":
+        return Tensor(self.data.to(to_torch_dtype(dtype)))
+
+    def copy_from(self, other: "Tensor") -> "Tensor":
+        with torch.no_grad():
+            self.data.copy_(_unwrap(other))
+        return self
+
+    # ------------------------------------------------------------------ shape
+    def reshape(self, shape: Sequence[int]) -> "Tensor":
+        return Tensor(self.data.reshape(tuple(shape)))
+
+    view_shape = reshape
+
+    def try_view(self, shape: Sequence[int]) -> "Tensor":
+        return Tensor(self.data.view(tuple(shape)))
+
+    view = try_view
+
+    def squeeze(self, dim: Optional[int] = None) -> "Tensor":
+        return Tensor(self.data.squeeze() if dim is None else self.data.squeeze(dim))
+
+    def unsqueeze(self, dim: int) -> "Tensor":
+        return Tensor(self.data.unsqueeze(dim))
+
+    def expand(self, shape: Sequence[int]) -> "Tensor":
+        return Tensor(self.data.expand(*shape))
+
+    def expand_as(self, other: "Tensor") -> "Tensor":
+        return Tensor(self.data.expand_as(_unwrap(other)))
+
+    def broadcast_with(self, other: "Tensor") -> Tuple["Tensor", "Tensor"]:
+        a, b = torch.broadcast_tensors(self.data, _unwrap(other))
+        return Tensor(a), Tensor(b)
+
+    def flatten(self, start_dim: int = 0, end_dim: int = -1) -> "Tensor":
+        return Tensor(self.data.flatten(start_dim, end_dim))
+
+    def unflatten(self, dim: int, sizes: Sequence[int]) -> "Tensor":
+        return Tensor(self.data.unflatten(dim, tuple(sizes)))
+
+    def repeat(self, repeats: Sequence[int]) -> "Tensor":
+        return Tensor(self.data.repeat(*repeats))
+
+    tile = repeat
+
+    def repeat_interleave(self, repeats: int, dim: Optional[int] = None) -> "Tensor":
+        return Tensor(self.data.repeat_interleave(repeats, dim=dim))
+
+    def roll(self, shifts, dims=None) -> "Tensor":
+        return Tensor(torch.roll(self.data, shifts, dims))
+
+    def rot90(self, k: int = 1, dims: Sequence[int] = (0, 1)) -> "Tensor":
+        return Tensor(torch.rot90(self.data, k, list(dims)))
+
+    def flip(self, dims: Sequence[int]) -> "Tensor":
+        return Tensor(torch.flip(self.data, list(dims)))
+
+    def fliplr(self) -> "Tensor":
+        return Tensor(torch.fliplr(self.data))
+
+    def flipud(self) -> "Tensor":
+        return Tensor(torch.flipud(self.data))
+
+    def permute(self, dims: Sequence[int]) -> "Tensor":
+        return Tensor(self.data.permute(*dims))
+
+    def movedim(self, src, dst) -> "Tensor":
+        return Tensor(self.data.movedim(src, dst))
+
+    def swapaxes(self, a: int, b: int) -> "Tensor":
+        return Tensor(self.data.transpose(a, b))
+
+    def transpose(self, dim0: Optional[int] = None, dim1: Optional[int] = None) -> "Tensor":
+        """2-D transpose with no arguments (src/tensor/ops/matrix.rs:199-216), else swap two dims."""
+        if dim0 is None:
+            if self.data.dim() < 2:
+                return Tensor(self.data.clone())
+            return Tensor(self.data.transpose(-1, -2))
+        return Tensor(self.data.transpose(dim0, dim1))
+
+    def transpose_last_two(self) -> "Tensor":
+        return Tensor(self.data.transpose(-1, -2))
+
+    t = transpose
+    T = property(lambda self: Tensor(self.data.transpose(-1, -2)))
+
+    def contiguous(self) -> "Tensor":
+        return Tensor(self.data.contiguous())
+
+    # -------------------------------------------------------------- arithmetic
+    def _bin(self, other, fn) -> "Tensor":
+        return Tensor(fn(self.data, _unwrap(other)))
+
+    def add(self, other) -> "Tensor":
+        return self._bin(other, torch.add)
+
+    def sub(self, other) -> "Tensor":
+        return self._bin(other, torch.sub)
+
+    def mul(self, other) -> "Tensor":
+        return self._bin(other, torch.mul)
+
+    def div(self, other) -> "Tensor":
+        return self._bin(other, torch.div)
+
+    add_scalar = add
+    sub_scalar = sub
+    mul_scalar = mul
+    div_scalar = div
+
+    def neg(self) -> "Tensor":
+        return Tensor(-self.data)
+
+    def maximum(self, other) -> "Tensor":
+        return self._bin(other, torch.maximum)
+
+    def minimum(self, other) -> "Tensor":
+        return self._bin(other, torch.minimum)
+
+    __add__ = add
+    __radd__ = add
+    __sub__ = sub
+    __mul__ = mul
+    __rmul__ = mul
+    __truediv__ = div
+    __neg__ = neg
+
+    def __rsub__(self, other):
+        return Tensor(_unwrap(other) - self.data)
+
+    def __rtruediv__(self, other):
+        return Tensor(_unwrap(other) / self.data)
+
+    def __pow__(self, e):
+        return Tensor(self.data ** _unwrap(e))
+
+    def __matmul__(self, other):
+        return self.matmul(other)
+
+    def __getitem__(self, idx):
+        return Tensor(self.data[_unwrap(idx)])
+
+    def __setitem__(self, idx, v):
+        self.data[_unwrap(idx)] = _unwrap(v)
+
+    def __len__(self):
+        return self.data.shape[0]
+
+    def __eq__(self, other):  # elementwise, like torch
+        return Tensor(self.data == _unwrap(other))
+
+    def __lt__(self, o):
+        return Tensor(self.data < _unwrap(o))
+
+    def __gt__(self, o):
+        return Tensor(self.data > _unwrap(o))
+
+    def __le__(self, o):
+        return Tensor(self.data <= _unwrap(o))
+
+    def __ge__(self, o):
+        return Tensor(self.data >= _unwrap(o))
+
+    __hash__ = object.__hash__
+
+    def __repr__(self) -> str:
+        return f"Tensor(shape={list(self.data.shape)}, device={self.device()}, data={self.data})"
+
+    def __float__(self):
+        return float(self.data)
+
+    # ------------------------------------------------------------------ matrix
+    def matmul(self, other) -> "Tensor":
+        """2D x 2D, 1D x 2D, 2D x 1D and batched products (src/tensor/ops/matrix.rs:42-157).
+
+        bf16 CUDA operands of rank 2/3 run on the hand-written tcgen05 GEMM; everything else on
+        torch.matmul.
+        """
+        a, b = self.data, _unwrap(other)
+        if (a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == b.dim()
+                and a.dim() in (2, 3) and a.shape[-1] % 8 == 0 and b.shape[-1] % 8 == 0
+                and a.stride(-1) == 1 and b.stride(-1) == 1 and not (a.requires_grad or b.requires_grad)):
+            from .ops import kernels as K
+            return Tensor(K.gemm(a, b, b_mn=True))
+        return Tensor(torch.matmul(a, b))
+
+    mm = matmul
+    bmm = matmul
+
+    def dot(self, other) -> "Tensor":
+        return Tensor(torch.dot(self.data.reshape(-1), _unwrap(other).reshape(-1)))
+
+    def det(self) -> float:
+        return float(torch.linalg.det(self.data))
+
+    def trace(self) -> float:
+        return float(torch.trace(self.data))
+
+    # -------------------------------------------------------------------- math
+    def pow(self, e: Number) -> "Tensor":
+        return Tensor(self.data.pow(e))
+
+    def pow_tensor(self, e: "Tensor") -> "Tensor":
+        return Tensor(self.data.pow(_unwrap(e)))
+
+    def log(self, base: Optional[float] = None) -> "Tensor":
+        return Tensor(self.data.log() if base is None else self.data.log() / math.log(base))
+
+    ln = lambda self: Tensor(self.data.log())  # noqa: E731
+
+    def square(self) -> "Tensor":
+        return Tensor(self.data * self.data)
+
+    def cbrt(self) -> "Tensor":
+        return Tensor(torch.sign(self.data) * self.data.abs().pow(1.0 / 3.0))
+
+    def clamp(self, lo: Optional[Number] = None, hi: Optional[Number] = None) -> "Tensor":
+        return Tensor(self.data.clamp(lo, hi))
+
+    def min_scalar(self, v: Number) -> "Tensor":
+        return Tensor(self.data.clamp(max=v))
+
+    def max_scalar(self, v: Number) -> "Tensor":
+        return Tensor(self.data.clamp(min=v))
+
+    def fract(self) -> "Tensor":
+        return Tensor(self.data - self.data.trunc())
+
+    def is_finite(self) -> bool:
+        return bool(torch.isfinite(self.data).all())
+
+    def has_nan(self) -> bool:
+        return bool(torch.isnan(self.data).any())
+
+    def has_inf(self) -> bool:
+        return bool(torch.isinf(self.data).any())
+
+    def nan_to_num(self, nan: float = 0.0, posinf: Optional[float] = None, neginf: Optional[float] = None) -> "Tensor":
+        return Tensor(torch.nan_to_num(self.data, nan, posinf, neginf))
+
+    def inf_to_num(self, value: float = 0.0) -> "Tensor":
+        return Tensor(torch.where(torch.isinf(self.data), torch.full_like(self.data, value), self.data))
+
+    def normalize_0_1(self) -> "Tensor":
+        lo, hi = self.data.min(), self.data.max()
+        return Tensor((self.data - lo) / (hi - lo).clamp_min(1e-12))
+
+    def standardize(self) -> "Tensor":
+        return Tensor((self.data - self.data.mean()) / self.data.std(unbiased=False).clamp_min(1e-12))
+
+    def atan2(self, other) -> "Tensor":
+        return self._bin(other, torch.atan2)
+
+    def lerp(self, end, weight: float) -> "Tensor":
+        return Tensor(torch.lerp(self.data, _unwrap(end), weight))
+
+    def gamma(self) -> "Tensor":
+        return Tensor(torch.exp(torch.lgamma(self.data)) * _gamma_sign(self.data))
+
+    def relu(self) -> "Tensor":
+        return Tensor(torch.relu(self.data))
+
+    def gelu(self) -> "Tensor":
+        return Tensor(torch.nn.functional.gelu(self.data, approximate="tanh"))
+
+    def softmax(self, dim: int = -1) -> "Tensor":
+        return Tensor(torch.softmax(self.data, dim))
+
+    # -------------------------------------------------------------- reductions
+    def sum(self, dim=None, keepdim: bool = False):
+        return Tensor(self.data.sum() if dim is None else self.data.sum(dim, keepdim))
+
+    def mean(self, dim=None, keepdim: bool = False):
+        return Tensor(self.data.mean() if dim is None else self.data.mean(dim, keepdim))
+
+    def sum_axis(self, axis: int) -> "Tensor":
+        return Tensor(self.data.sum(axis))
+
+    def mean_axis(self, axis: int) -> "Tensor":
+        return Tensor(self.data.mean(axis))
+
+    def max(self, dim=None):
+        return Tensor(self.data.max()) if dim is None else Tensor(self.data.max(dim).values)
+
+    def min(self, dim=None):
+        return Tensor(self.data.min()) if dim is None else Tensor(self.data.min(dim).values)
+
+    max_axis = lambda self, axis: Tensor(self.data.max(axis).values)  # noqa: E731
+    min_axis = lambda self, axis: Tensor(self.data.min(axis).values)  # noqa: E731
+
+    def var(self, unbiased: bool = False) -> "Tensor":
+        return Tensor(self.data.var(unbiased=unbiased))
+
+    def std(self, unbiased: bool = False) -> "Tensor":
+        return Tensor(self.data.std(unbiased=unbiased))
+
+    var_unbiased = lambda self: Tensor(self.data.var(unbiased=True))  # noqa: E731
+    var_axis = lambda self, axis, unbiased=False: Tensor(self.data.var(axis, unbiased=unbiased))  # noqa: E731
+    std_axis = lambda self, axis, unbiased=False: Tensor(self.data.std(axis, unbiased=unbiased))  # noqa: E731
+
+    def count_nonzero(self) -> int:
+        return int(torch.count_nonzero(self.data))
+
+    def argmax(self, dim=None):
+        r = self.data.argmax() if dim is None else self.data.argmax(dim)
+        return int(r) if r.dim() == 0 else Tensor(r)
+
+    def argmin(self, dim=None):
+        r = self.data.argmin() if dim is None else self.data.argmin(dim)
+        return int(r) if r.dim() == 0 else Tensor(r)
+
+    argmax_axis = lambda self, axis: Tensor(self.data.argmax(axis))  # noqa: E731
+    argmin_axis = lambda self, axis: Tensor(self.data.argmin(axis))  # noqa: E731
+
+    def median(self) -> float:
+        return float(self.data.reshape(-1).median())
+
+    def quantile(self, q: float) -> float:
+        return float(torch.quantile(self.data.reshape(-1).float(), q))
+
+    def percentile(self, p: float) -> float:
+        return self.quantile(p / 100.0)
+
+    def cumsum(self, dim: int = 0) -> "Tensor":
+        return Tensor(self.data.cumsum(dim))
+
+    def cumprod(self, dim: int = 0) -> "Tensor":
+        return Tensor(self.data.cumprod(dim))
+
+    def topk(self, k: int, dim: int = -1, largest: bool = True) -> Tuple["Tensor", "Tensor"]:
+        v, i = self.data.topk(k, dim, largest)
+        return Tensor(v), Tensor(i)
+
+    def bottomk(self, k: int, dim: int = -1) -> Tuple["Tensor", "Tensor"]:
+        return self.topk(k, dim, largest=False)
+
+    def kthvalue(self, k: int, dim: int = -1) -> Tuple["Tensor", "Tensor"]:
+        v, i = self.data.kthvalue(k, dim)
+        return Tensor(v), Tensor(i)
+
+    def cov(self) -> "Tensor":
+        return Tensor(torch.cov(self.data))
+
+    def corrcoef(self) -> "Tensor":
+        return Tensor(torch.corrcoef(self.data))
+
+    def unique(self) -> "Tensor":
+        return Tensor(torch.unique(self.data))
+
+    def histogram(self, bins: int = 10, range: Optional[Tuple[float, float]] = None) -> Tuple["Tensor", "Tensor"]:
+        x = self.data.detach().float().cpu().reshape(-1)
+        lo, hi = (float(x.min()), float(x.max())) if range is None else range
+        h = torch.histc(x, bins, lo, hi)
+        return Tensor(h), Tensor(torch.linspace(lo, hi, bins + 1))
+
+    # ------------------------------------------------------------------ linalg
+    def svd(self, full_matrices: bool = False):
+        u, s, vh = torch.linalg.svd(self.data, full_matrices=full_matrices)
+        return Tensor(u), Tensor(s), Tensor(vh.transpose(-1, -2))
+
+    def qr(self):
+        q, r = torch.linalg.qr(self.data)
+        return Tensor(q), Tensor(r)
+
+    def lu(self):
+        p, l, u = torch.linalg.lu(self.data)
+        return Tensor(l), Tensor(u), Tensor(p)
+
+    def eig(self):
+        w, v = torch.linalg.eig(self.data)
+        return Tensor(w), Tensor(v)
+
+    def symeig(self, upper: bool = False):
+        w, v = torch.linalg.eigh(self.data, UPLO="U" if upper else "L")
+        return Tensor(w), Tensor(v)
+
+    eigh = symeig
+
+    def cholesky(self, upper: bool = False) -> "Tensor":
+        return Tensor(torch.linalg.cholesky(self.data, upper=upper))
+
+    def inverse(self) -> "Tensor":
+        return Tensor(torch.linalg.inv(self.data))
+
+    def pinv(self) -> "Tensor":
+        return Tensor(torch.linalg.pinv(self.data))
+
+    def norm(self, p: Union[int, float, str] = 2) -> float:
+        return float(torch.linalg.vector_norm(self.data.reshape(-1).float(), p) if not isinstance(p, str)
+                     else torch.linalg.matrix_norm(self.data, p))
+
+    norm_p = norm
+    frobenius_norm = lambda self: float(torch.linalg.matrix_norm(self.data, "fro"))  # noqa: E731
+    nuclear_norm = lambda self: float(torch.linalg.matrix_norm(self.data, "nuc"))  # noqa: E731
+
+    # ------------------------------------------------------------------ signal
+    def fft(self) -> "Tensor":
+        return Tensor(torch.fft.fft(self.data))
+
+    def ifft(self) -> "Tensor":
+        return Tensor(torch.fft.ifft(self.data))
+
+    def rfft(self) -> "Tensor":
+        return Tensor(torch.fft.rfft(self.data))
+
+    def fftshift(self) -> "Tensor":
+        return Tensor(torch.fft.fftshift(self.data))
+
+    def ifftshift(self) -> "Tensor":
+        return Tensor(torch.fft.ifftshift(self.data))
+
+    def apply_window(self, window: str = "hann") -> "Tensor":
+        n = self.data.shape[-1]
+        w = {"hann": torch.hann_window, "hanning": torch.hann_window, "hamming": torch.hamming_window,
+             "blackman": torch.blackman_window, "bartlett": torch.bartlett_window,
+             "rectangular": lambda n, **k: torch.ones(n)}[window.lower()](n, periodic=False)
+        return Tensor(self.data * w.to(self.data.device, self.data.dtype))
+
+    # --------------------------------------------------------------- utilities
+    def where_(self, cond, other) -> "Tensor":
+        return Tensor(torch.where(_unwrap(cond).bool(), self.data, _unwrap(other) if isinstance(other, Tensor)
+                                  else torch.as_tensor(other, dtype=self.data.dtype, device=self.data.device)))
+
+    def masked_select(self, mask) -> "Tensor":
+        return Tensor(self.data.masked_select(_unwrap(mask).bool()))
+
+    def masked_fill(self, mask, value: Number) -> "Tensor":
+        return Tensor(self.data.masked_fill(_unwrap(mask).bool(), value))
+
+    def gather(self, dim: int, index) -> "Tensor":
+        return Tensor(self.data.gather(dim, _unwrap(index).long()))
+
+    def scatter(self, dim: int, index, src) -> "Tensor":
+        return Tensor(self.data.scatter(dim, _unwrap(index).long(), _unwrap(src)))
+
+    def index_select(self, dim: int, index) -> "Tensor":
+        return Tensor(self.data.index_select(dim, _unwrap(index).long()))
+
+    def select(self, dim: int, index: int) -> "Tensor":
+        return Tensor(self.data.select(dim, index))
+
+    def chunk(self, chunks: int, dim: int = 0) -> List["Tensor"]:
+        return [Tensor(t) for t in self.data.chunk(chunks, dim)]
+
+    def split(self, size, dim: int = 0) -> List["Tensor"]:
+        return [Tensor(t) for t in self.data.split(size, dim)]
+
+    def map(self, fn) -> "Tensor":
+        flat = [fn(v) for v in self.as_slice()]
+        return Tensor(flat, self.shape(), device=self.data.device)
+
+    def zip_with(self, other: "Tensor", fn) -> "Tensor":
+        flat = [fn(a, b) for a, b in zip(self.as_slice(), other.as_slice())]
+        return Tensor(flat, self.shape(), device=self.data.device)
+
+    @staticmethod
+    def stack(tensors: Sequence["Tensor"], dim: int = 0) -> "Tensor":
+        return Tensor(torch.stack([_unwrap(t) for t in tensors], dim))
+
+    @staticmethod
+    def concatenate(tensors: Sequence["Tensor"], dim: int = 0) -> "Tensor":
+        return Tensor(torch.cat([_unwrap(t) for t in tensors], dim))
+
+    concat = cat = concatenate
+
+    # ----------------------------------------------------------------- autograd
+    def backward(self, grad=None) -> None:
+        self.data.backward(_unwrap(grad))
+
+    @property
+    def grad(self) -> Optional["Tensor"]:
+        g = self.data.grad
+        return None if g is None else Tensor(g)
+
+    def zero_grad(self) -> None:
+        self.data.grad = None
+
+    # -------------------------------------------------------------------- save
+    def save(self, path: str) -> None:
+        """RUSTORCH container, object type ``tensor`` (src/tensor/core.rs:726-734)."""
+        from .formats import rustorch_bin
+        rustorch_bin.save_tensor(self.data, path)
+
+    @staticmethod
+    def load(path: str) -> "Tensor":
+        from .formats import rustorch_bin
+        return Tensor(rustorch_bin.load_tensor(path))
+
+    # ------------------------------------------------------ torch fall-through
+    def __getattr__(self, name):
+        if name.startswith("__"):
+            raise AttributeError(name)
+        attr = getattr(self.data, name)
+        if callable(attr):
+            def call(*a, **k):
+                return _wrap(attr(*_unwrap(a), **{kk: _unwrap(v) for kk, v in k.items()}))
+            return call
+        return _wrap(attr)
+
+
+def _gamma_sign(x: torch.Tensor) -> torch.Tensor:
+    # sign of Gamma(x) for negative non-integers: (-1)^ceil(-x)
+    neg = x < 0
+    s = torch.where((torch.ceil(-x) % 2) == 1, -torch.ones_like(x), torch.ones_like(x))
+    return torch.where(neg, s, torch.ones_like(x))
+
+
+def tensor(data, shape: Optional[Sequence[int]] = None, **kw) -> Tensor:
+    """``rustorch.tensor(data, shape)`` (python/src/lib.rs) and the ``tensor!`` literal macro."""
+    return Tensor(data, shape, **kw)
+
+
+def zeros(shape, **kw) -> Tensor:
+    return Tensor.zeros(shape, **kw)
+
+
+def ones(shape, **kw) -> Tensor:
+    return Tensor.ones(shape, **kw)
+
+
+def tensor_nd(nested) -> Tensor:
+    """Nested-list literal, the proc-macro ``tensor_nd!`` (rustorch-macros/src/lib.rs:43-68)."""
+    return Tensor(nested)

@@ -1,0 +1,134 @@
+"""Tensor façade, dtype and autograd surface (CPU)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from rustorch_b200.autograd import (ComputationGraph, AddFunction, MulFunction, MatMulFunction, SumFunction,
+                                    GradCheckConfig, GradientFlowAnalyzer, GradientFlowVisualizer, Variable,
+                                    grad, gradcheck, hessian, hvp, jacobian, no_grad)
+from rustorch_b200.dtype import DType, parse_dtype
+from rustorch_b200.tensor import Device, Tensor, tensor
+
+
+def test_constructors_and_accessors():
+    t = Tensor.from_vec([1, 2, 3, 4, 5, 6], [2, 3])
+    assert t.shape() == (2, 3) and t.ndim() == 2 and t.numel() == 6
+    assert t.get([1, 2]) == 6.0
+    t.set([0, 0], 9.0)
+    assert t.as_slice()[0] == 9.0
+    assert Tensor.zeros([2, 2]).sum().item() == 0 and Tensor.ones([2, 2]).sum().item() == 4
+    assert Tensor.full([3], 2.5).mean().item() == 2.5
+    assert Tensor.eye(3).trace() == 3.0
+    assert Tensor.arange(5).shape() == (5,) and Tensor.linspace(0, 1, 11).shape() == (11,)
+    with pytest.raises(ValueError):
+        Tensor.from_vec([1, 2, 3], [2, 2])
+    assert str(Device.cuda(1)) == "cuda:1" and str(t.device()) == "cpu"
+
+
+def test_arithmetic_matmul_broadcast():
+    a = tensor([[1.0, 2.0], [3.0, 4.0]])
+    b = tensor([[5.0, 6.0], [7.0, 8.0]])
+    assert (a + b).as_slice() == [6, 8, 10, 12]
+    assert (a * 2.0).as_slice() == [2, 4, 6, 8]
+    assert a.matmul(b).as_slice() == [19, 22, 43, 50]
+    assert (a @ tensor([1.0, 1.0])).as_slice() == [3, 7]
+    assert a.transpose().as_slice() == [1, 3, 2, 4]
+    assert abs(a.det() + 2.0) < 1e-5
+    assert (a + tensor([10.0, 20.0])).as_slice() == [11, 22, 13, 24]
+    assert a.maximum(tensor([[2.0, 2.0], [2.0, 2.0]])).as_slice() == [2, 2, 3, 4]
+
+
+def test_math_reductions_shape_ops():
+    x = tensor([[1.0, -2.0, 3.0], [4.0, 5.0, -6.0]])
+    assert x.abs().sum().item() == 21
+    assert x.argmax() == 4 and x.argmin() == 5
+    assert x.sum_axis(0).as_slice() == [5, 3, -3]
+    assert x.clamp(-1, 1).as_slice() == [1, -1, 1, 1, 1, -1]
+    assert x.flatten().shape() == (6,) and x.unsqueeze(0).shape() == (1, 2, 3)
+    assert x.flip([1]).as_slice()[:3] == [3, -2, 1]
+    assert Tensor.stack([x, x]).shape() == (2, 2, 3) and Tensor.concatenate([x, x], 1).shape() == (2, 6)
+    v, i = x.topk(2, dim=1)
+    assert v.as_slice() == [3, 1, 5, 4]
+    assert abs(tensor([1.0, 2.0, 3.0, 4.0]).var_unbiased().item() - 1.6666666) < 1e-5
+    assert tensor([0.5]).gamma().as_slice()[0] == pytest.approx(math.sqrt(math.pi), rel=1e-5)
+    assert tensor([1.0, float("nan")]).has_nan() and not tensor([1.0]).has_inf()
+    assert x.exp().shape() == (2, 3)  # falls through to torch
+    assert x.map(lambda v: v * 2).as_slice() == [2, -4, 6, 8, 10, -12]
+
+
+def test_linalg_and_fft():
+    a = tensor([[4.0, 1.0], [1.0, 3.0]])
+    u, s, v = a.svd()
+    rec = u.data @ torch.diag(s.data) @ v.data.t()
+    assert torch.allclose(rec, a.data, atol=1e-5)
+    q, r = a.qr()
+    assert torch.allclose(q.data @ r.data, a.data, atol=1e-5)
+    assert torch.allclose(a.inverse().data @ a.data, torch.eye(2), atol=1e-5)
+    L = a.cholesky()
+    assert torch.allclose(L.data @ L.data.t(), a.data, atol=1e-5)
+    sig = Tensor.arange(8)
+    assert torch.allclose(sig.fft().ifft().data.real, sig.data, atol=1e-5)
+    assert sig.apply_window("hamming").shape() == (8,)
+
+
+def test_dtype():
+    assert parse_dtype("float32") is DType.F32 and DType.BF16.size() == 2
+    assert DType.F16.promote(DType.F32) is DType.F32
+    assert DType.I32.is_int() and DType.C64.is_complex()
+    with pytest.raises(ValueError):
+        parse_dtype("q7")
+
+
+def test_variable_backward_and_hooks():
+    x = Variable(tensor([[1.0, 2.0], [3.0, 4.0]]), requires_grad=True)
+    w = Variable(tensor([[0.5], [0.25]]), requires_grad=True)
+    y = (x.matmul(w) * 2.0).sum()
+    y.backward()
+    assert x.grad().as_slice() == [1.0, 0.5, 1.0, 0.5]
+    assert w.grad().as_slice() == [8.0, 12.0]
+    x.zero_grad()
+    assert x.grad() is None
+    with no_grad():
+        z = x * 2.0
+    assert not z.requires_grad()
+    (gx,) = grad([(x * x).sum()], [x])
+    assert gx.as_slice() == [2, 4, 6, 8]
+    assert x.exp().shape() == (2, 2)
+
+
+def test_gradcheck_and_higher_order():
+    f = lambda v: (v * v * v).sum()
+    assert gradcheck(f, [tensor([1.0, 2.0])], GradCheckConfig(eps=1e-6, atol=1e-4, rtol=1e-3))
+    H = hessian(f, tensor([1.0, 2.0]))
+    assert torch.allclose(H.data, torch.tensor([[6.0, 0.0], [0.0, 12.0]]), atol=1e-2)
+    J = jacobian(lambda v: v * v, tensor([1.0, 3.0]))
+    assert torch.allclose(J.data, torch.tensor([[2.0, 0.0], [0.0, 6.0]]), atol=1e-3)
+    hv = hvp(f, tensor([1.0, 2.0]), tensor([1.0, 1.0]))
+    assert torch.allclose(hv.data, torch.tensor([6.0, 12.0]), atol=1e-2)
+
+
+def test_computation_graph_topological_backward():
+    g = ComputationGraph()
+    a = g.add_leaf(torch.tensor([[1.0, 2.0]]))
+    b = g.add_leaf(torch.tensor([[3.0], [4.0]]))
+    c = g.add_node(MatMulFunction(), [a, b])
+    d = g.add_node(MulFunction(), [c, c])       # shared sub-graph: c used twice
+    e = g.add_node(SumFunction(), [d])
+    g.backward(e)
+    assert g.value(e).item() == 121.0
+    assert g.grad(a).as_slice() == [66.0, 88.0]
+    assert g.topological_sort().index(c) < g.topological_sort().index(d)
+
+
+def test_gradient_flow_tools(tmp_path):
+    x = Variable(tensor([1.0, 2.0]), requires_grad=True)
+    y = (x * x).sum()
+    dot = GradientFlowVisualizer().to_dot(y)
+    assert "digraph" in dot and "MulBackward" in dot
+    lin = torch.nn.Linear(2, 1)
+    lin(torch.ones(1, 2)).sum().backward()
+    an = GradientFlowAnalyzer()
+    an.record(lin.named_parameters())
+    assert "weight" in an.history and an.issues() == {}
