@@ -1,1 +1,11 @@
-
+"""``rustorch.nn``: layers, activations, losses, transformer, recurrent nets (src/nn/mod.rs)."""
+from . import fused  # noqa: F401
+from .layers import *  # noqa: F401,F403
+from .layers import Module, Parameter, Sequential
+from .loss import *  # noqa: F401,F403
+from .rnn import GRU, GRUCell, LSTM, LSTMCell, RNN, RNNCell
+from .transformer import (CrossAttention, MultiheadAttention, SelfAttention, Transformer, TransformerDecoder,
+                          TransformerDecoderLayer, TransformerEncoder, TransformerEncoderLayer)
+from .pruning import Pruner, PruningMethod, PruningSchedule
+from .quantization import QuantizationType, QuantizedTensor, Quantizer
+from .safe_ops import SafeOps
