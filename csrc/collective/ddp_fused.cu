@@ -14,9 +14,9 @@
 // and its 25 MB bucket plan (src/distributed/ddp.rs:235-271).
 //
 // Peer access is by plain loads/stores on peer pointers from symmetric allocations; there is no
-// TMA and no multicast in this file.  The kernel uses a few dozen CTAs of 128 threads and keeps up
-// to 16 peer loads per thread in flight, so a 25 MB bucket takes tens of microseconds and the
-// backward kernels it overlaps lose little.
+// TMA and no multicast in this file.  Each thread keeps 8 sixteen-byte loads in flight, so a 25 MB
+// bucket streams at memory / link speed for a few tens of microseconds and the backward kernels
+// it overlaps lose little.
 // Every wait is bounded by a caller-supplied deadline; on expiry the kernel records
 // RT_ERR_TIMEOUT_PEER in the status word, skips its update and returns.
 #include "../api.h"
@@ -62,8 +62,33 @@ __device__ __forceinline__ bool wait_flags(const int* flags, int n, int skip, in
   return __syncthreads_and(ok ? 1 : 0) != 0;
 }
 
-__global__ void __launch_bounds__(128, 4) ddp_bucket_adamw_kernel(const DdpBucketArgs a) {
-  const int W = a.world, R = a.rank;
+__device__ __forceinline__ void adamw4(const DdpBucketArgs& a, float4& pm, const float4& g, float4& m,
+                                       float4& v) {
+  const float inv_w = a.grad_scale;
+#define RT_ADAMW1(P, G, M, V)                                          \
+  {                                                                    \
+    const float gg = (G) * inv_w;                                      \
+    (M) = a.beta1 * (M) + (1.f - a.beta1) * gg;                        \
+    (V) = a.beta2 * (V) + (1.f - a.beta2) * gg * gg;                   \
+    (P) *= (1.f - a.lr * a.weight_decay);                              \
+    (P) -= a.lr * ((M) / a.bias_corr1) / (sqrtf((V) / a.bias_corr2) + a.eps); \
+  }
+  RT_ADAMW1(pm.x, g.x, m.x, v.x)
+  RT_ADAMW1(pm.y, g.y, m.y, v.y)
+  RT_ADAMW1(pm.z, g.z, m.z, v.z)
+  RT_ADAMW1(pm.w, g.w, m.w, v.w)
+#undef RT_ADAMW1
+}
+
+// WT = compile-time world size (1, 2, 4, 8) or 0 for "read it from the arguments".  Each thread
+// handles G = 8 / WT groups of 4 elements per trip and issues the G x W peer loads before it
+// consumes any, i.e. 8 sixteen-byte loads in flight per thread whatever the world size.
+template <int WT>
+__global__ void __launch_bounds__(256, 2) ddp_bucket_adamw_kernel(const DdpBucketArgs a) {
+  const int W = WT > 0 ? WT : a.world;
+  const int R = a.rank;
+  constexpr int G = WT > 0 ? 8 / WT : 1;
+  constexpr int WMAX = WT > 0 ? WT : RT_MAX_PEERS;
   int* my_flags = a.flags[R];
   // ---- start barrier: tell every peer this rank's bucket gradients are final, wait for theirs
   if (W > 1) {
@@ -76,67 +101,46 @@ __global__ void __launch_bounds__(128, 4) ddp_bucket_adamw_kernel(const DdpBucke
 
   const long long base = a.bucket_start + (long long)R * a.chunk_len;  // flat index of my shard
   const long long n4 = a.chunk_len >> 2;
-  const float inv_w = a.grad_scale;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  // Two 16-byte groups per thread per trip, and the loads from all ranks are issued before any
-  // is consumed, so up to 16 NVLink loads per thread are in flight.
-  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < n4; i0 += 2 * stride) {
-    const long long i1 = i0 + stride;
-    const bool has1 = i1 < n4;
-    const long long e0 = base + (i0 << 2);
-    const long long e1 = base + ((has1 ? i1 : i0) << 2);
-    float4 v0[RT_MAX_PEERS], v1[RT_MAX_PEERS];
+  const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < n4; i0 += G * stride) {
+    float4 v[G][WMAX];
+    long long e[G];
+    bool on[G];
 #pragma unroll
-    for (int p = 0; p < RT_MAX_PEERS; ++p) {
-      if (p < W) {
-        v0[p] = ld_peer_f4(a.grad[p] + e0);
-        if (has1) v1[p] = ld_peer_f4(a.grad[p] + e1);
-      }
+    for (int g = 0; g < G; ++g) {
+      const long long i = i0 + g * stride;
+      on[g] = i < n4;
+      e[g] = base + ((on[g] ? i : i0) << 2);
+#pragma unroll
+      for (int p = 0; p < WMAX; ++p)
+        if (p < W && on[g]) v[g][p] = ld_peer_f4(a.grad[p] + e[g]);
     }
-    float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
-    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int p = 0; p < RT_MAX_PEERS; ++p) {
-      if (p < W) {
-        g0.x += v0[p].x; g0.y += v0[p].y; g0.z += v0[p].z; g0.w += v0[p].w;
-        *reinterpret_cast<float4*>(a.grad[p] + e0) = z;
-        if (has1) {
-          g1.x += v1[p].x; g1.y += v1[p].y; g1.z += v1[p].z; g1.w += v1[p].w;
-          *reinterpret_cast<float4*>(a.grad[p] + e1) = z;
+    for (int g = 0; g < G; ++g) {
+      if (!on[g]) continue;
+      float4 sum = z;
+#pragma unroll
+      for (int p = 0; p < WMAX; ++p) {
+        if (p < W) {
+          sum.x += v[g][p].x; sum.y += v[g][p].y; sum.z += v[g][p].z; sum.w += v[g][p].w;
+          *reinterpret_cast<float4*>(a.grad[p] + e[g]) = z;
         }
       }
-    }
-#define RT_ADAMW1(P, G, M, V)                                          \
-    {                                                                  \
-      const float gg = (G) * inv_w;                                    \
-      (M) = a.beta1 * (M) + (1.f - a.beta1) * gg;                      \
-      (V) = a.beta2 * (V) + (1.f - a.beta2) * gg * gg;                 \
-      (P) *= (1.f - a.lr * a.weight_decay);                            \
-      (P) -= a.lr * ((M) / a.bias_corr1) / (sqrtf((V) / a.bias_corr2) + a.eps); \
-    }
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      if (half == 1 && !has1) break;
-      const long long e = half == 0 ? e0 : e1;
-      const float4 g = half == 0 ? g0 : g1;
-      float4 pm = *reinterpret_cast<float4*>(a.master + e);
-      float4 m = *reinterpret_cast<float4*>(a.m + e);
-      float4 v = *reinterpret_cast<float4*>(a.v + e);
-      RT_ADAMW1(pm.x, g.x, m.x, v.x)
-      RT_ADAMW1(pm.y, g.y, m.y, v.y)
-      RT_ADAMW1(pm.z, g.z, m.z, v.z)
-      RT_ADAMW1(pm.w, g.w, m.w, v.w)
-      *reinterpret_cast<float4*>(a.master + e) = pm;
-      *reinterpret_cast<float4*>(a.m + e) = m;
-      *reinterpret_cast<float4*>(a.v + e) = v;
+      float4 pm = *reinterpret_cast<float4*>(a.master + e[g]);
+      float4 m = *reinterpret_cast<float4*>(a.m + e[g]);
+      float4 vv = *reinterpret_cast<float4*>(a.v + e[g]);
+      adamw4(a, pm, sum, m, vv);
+      *reinterpret_cast<float4*>(a.master + e[g]) = pm;
+      *reinterpret_cast<float4*>(a.m + e[g]) = m;
+      *reinterpret_cast<float4*>(a.v + e[g]) = vv;
       uint2 w;
       w.x = pack_bf16x2(pm.x, pm.y);
       w.y = pack_bf16x2(pm.z, pm.w);
 #pragma unroll
-      for (int p = 0; p < RT_MAX_PEERS; ++p)
-        if (p < W) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.lp[p]) + e) = w;
+      for (int p = 0; p < WMAX; ++p)
+        if (p < W) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.lp[p]) + e[g]) = w;
     }
-#undef RT_ADAMW1
   }
 
   // ---- end signal: the last CTA to finish tells every peer that this rank is done writing
@@ -170,7 +174,13 @@ void ddp_bucket_adamw(const DdpBucketArgs& a, int n_ctas, cudaStream_t stream) {
   RT_CHECK(a.world >= 1 && a.world <= RT_MAX_PEERS, "ddp: world size must be in [1, 8]");
   RT_CHECK(a.chunk_len % 4 == 0 && a.bucket_start % 4 == 0, "ddp: bucket geometry must be 4-aligned");
   if (a.chunk_len == 0) return;
-  ddp_bucket_adamw_kernel<<<n_ctas, 128, 0, stream>>>(a);
+  switch (a.world) {
+    case 1: ddp_bucket_adamw_kernel<1><<<n_ctas, 256, 0, stream>>>(a); break;
+    case 2: ddp_bucket_adamw_kernel<2><<<n_ctas, 256, 0, stream>>>(a); break;
+    case 4: ddp_bucket_adamw_kernel<4><<<n_ctas, 256, 0, stream>>>(a); break;
+    case 8: ddp_bucket_adamw_kernel<8><<<n_ctas, 256, 0, stream>>>(a); break;
+    default: ddp_bucket_adamw_kernel<0><<<n_ctas, 256, 0, stream>>>(a); break;
+  }
   RT_LAUNCH_CHECK();
 }
 

@@ -53,7 +53,7 @@ def _symm_empty(numel: int, dtype: torch.dtype, device: torch.device, group) -> 
 class FusedDDPAdamW:
     def __init__(self, module: torch.nn.Module, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.01, bucket_cap_mb: float = 25.0, process_group=None,
-                 decay_filter=default_decay_filter, n_ctas: int = 64, timeout_s: float = 60.0,
+                 decay_filter=default_decay_filter, n_ctas: int = 296, timeout_s: float = 60.0,
                  overlap: bool = True):
         self.module = module
         self.lr, self.betas, self.eps, self.weight_decay = float(lr), (float(betas[0]), float(betas[1])), float(eps), float(weight_decay)

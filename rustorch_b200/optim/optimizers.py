@@ -1,0 +1,235 @@
+"""Optimizers with the reference's constructors, defaults and accessor names (src/optim/*).
+
+All are ``torch.optim.Optimizer`` subclasses (so schedulers, ``state_dict`` with moment buffers and
+parameter groups work) plus the reference surface: ``learning_rate() / set_learning_rate(lr) /
+set_lr(lr)``, the alternate constructors (``Adam.default_params(lr)``, ``SGD.with_momentum`` ...)
+and a per-tensor ``step_tensor(param, grad)`` mirroring the trait's ``step(&param, &grad)``
+(src/optim/mod.rs:60-78).  Bias correction counts optimizer steps per parameter, not calls
+across parameters (the reference's quirk, src/optim/mod.rs:301).  The fused flat-buffer
+variants used by the bf16 training path live in :mod:`rustorch_b200.optim.flat`.
+"""
+from __future__ import annotations
+
+import math
+from typing import Iterable, Optional
+
+import torch
+from torch.optim import Optimizer as _TorchOptimizer
+
+
+class _RefAPI:
+    """Reference accessor names on top of torch's param_groups."""
+
+    def learning_rate(self) -> float:
+        return float(self.param_groups[0]["lr"])
+
+    def set_learning_rate(self, lr: float) -> None:
+        for g in self.param_groups:
+            g["lr"] = float(lr)
+
+    set_lr = set_learning_rate
+
+    @torch.no_grad()
+    def step_tensor(self, param: torch.Tensor, grad: torch.Tensor) -> None:
+        """Update one tensor in place from an explicit gradient."""
+        known = any(param is p for g in self.param_groups for p in g["params"])
+        if not known:
+            self.add_param_group({"params": [param]})
+        saved = [(p, p.grad) for g in self.param_groups for p in g["params"]]
+        for p, _ in saved:
+            p.grad = None
+        param.grad = grad
+        self.step()
+        for p, g in saved:
+            p.grad = g
+
+    def hyper_state(self) -> dict:
+        """Hyper-parameters only, like the reference's ``state_dict() -> HashMap<String, f32>``."""
+        g = self.param_groups[0]
+        return {k: v for k, v in g.items() if isinstance(v, (int, float, bool))}
+
+
+def _params(params) -> Iterable:
+    return params if params is not None else [torch.nn.Parameter(torch.zeros(0))]
+
+
+class SGD(torch.optim.SGD, _RefAPI):
+    """``SGD(params, lr, momentum=0, weight_decay=0, nesterov=False, dampening=0)`` (src/optim/mod.rs:93-137)."""
+
+    def __init__(self, params=None, lr: float = 0.01, momentum: float = 0.0, weight_decay: float = 0.0,
+                 nesterov: bool = False, dampening: float = 0.0):
+        super().__init__(_params(params), lr=lr, momentum=momentum, dampening=dampening,
+                         weight_decay=weight_decay, nesterov=nesterov)
+
+    with_momentum = classmethod(lambda cls, params, lr, momentum: cls(params, lr, momentum))
+    with_weight_decay = classmethod(lambda cls, params, lr, momentum, wd: cls(params, lr, momentum, wd))
+    with_nesterov = classmethod(lambda cls, params, lr, momentum, nesterov=True: cls(params, lr, momentum, 0.0, nesterov))
+
+    def set_dampening(self, d: float) -> None:
+        for g in self.param_groups:
+            g["dampening"] = d
+
+
+class Adam(torch.optim.Adam, _RefAPI):
+    """``Adam(params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0, amsgrad=False)``; L2 decay
+    folded into the gradient (src/optim/mod.rs:233-296)."""
+
+    def __init__(self, params=None, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.0, amsgrad: bool = False):
+        super().__init__(_params(params), lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay,
+                         amsgrad=amsgrad)
+
+    default_params = classmethod(lambda cls, params, lr=1e-3: cls(params, lr))
+    with_weight_decay = classmethod(lambda cls, params, lr, wd: cls(params, lr, weight_decay=wd))
+    with_amsgrad = classmethod(lambda cls, params, lr: cls(params, lr, amsgrad=True))
+
+
+class AdamW(torch.optim.AdamW, _RefAPI):
+    """``AdamW(params, lr, beta1, beta2, eps, weight_decay, amsgrad)``, defaults (0.9, 0.999, 1e-8, 0.01, False),
+    decoupled decay ``p *= 1 - lr*wd`` (src/optim/adamw.rs:39-78,159-163)."""
+
+    def __init__(self, params=None, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.01, amsgrad: bool = False):
+        super().__init__(_params(params), lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay,
+                         amsgrad=amsgrad)
+
+    default_params = classmethod(lambda cls, params, lr=1e-3: cls(params, lr))
+
+
+class RMSprop(torch.optim.RMSprop, _RefAPI):
+    """``default_params(lr)``: alpha 0.99, eps 1e-8; momentum / centered variants (src/optim/mod.rs:408-755)."""
+
+    def __init__(self, params=None, lr: float = 0.01, alpha: float = 0.99, eps: float = 1e-8,
+                 weight_decay: float = 0.0, momentum: float = 0.0, centered: bool = False):
+        super().__init__(_params(params), lr=lr, alpha=alpha, eps=eps, weight_decay=weight_decay,
+                         momentum=momentum, centered=centered)
+
+    default_params = classmethod(lambda cls, params, lr=0.01: cls(params, lr))
+
+
+class AdaGrad(torch.optim.Adagrad, _RefAPI):
+    """eps 1e-10, optional initial accumulator value (src/optim/mod.rs:646-648)."""
+
+    def __init__(self, params=None, lr: float = 0.01, lr_decay: float = 0.0, weight_decay: float = 0.0,
+                 initial_accumulator_value: float = 0.0, eps: float = 1e-10):
+        super().__init__(_params(params), lr=lr, lr_decay=lr_decay, weight_decay=weight_decay,
+                         initial_accumulator_value=initial_accumulator_value, eps=eps)
+
+    default_params = classmethod(lambda cls, params, lr=0.01: cls(params, lr))
+
+
+Adagrad = AdaGrad
+
+
+class NAdam(torch.optim.NAdam, _RefAPI):
+    """``(lr, beta1, beta2, eps, wd, momentum_decay=0.004, schedule_decay=0.004)`` (src/optim/nadam.rs:28-31,135-156)."""
+
+    def __init__(self, params=None, lr: float = 2e-3, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.0, momentum_decay: float = 0.004, schedule_decay: Optional[float] = None):
+        super().__init__(_params(params), lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay,
+                         momentum_decay=momentum_decay if schedule_decay is None else schedule_decay)
+
+
+class RAdam(torch.optim.RAdam, _RefAPI):
+    """Variance-rectified Adam; rectification applies once rho_t exceeds the threshold (reference 4.0,
+    torch 5.0 — torch's is used) (src/optim/radam.rs:25-31,187-205)."""
+
+    def __init__(self, params=None, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0):
+        super().__init__(_params(params), lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
+
+
+class Adamax(torch.optim.Adamax, _RefAPI):
+    """Infinity-norm Adam, eps default 1e-7 (src/optim/common.rs:107-117)."""
+
+    def __init__(self, params=None, lr: float = 2e-3, betas=(0.9, 0.999), eps: float = 1e-7, weight_decay: float = 0.0):
+        super().__init__(_params(params), lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
+
+
+class AdaBound(_TorchOptimizer, _RefAPI):
+    """Adam whose per-element step size is clipped into bounds that converge to ``final_lr``
+    (``new(lr)`` = final_lr 0.1, betas 0.9/0.999, eps 1e-8, wd 0, gamma 1e-3; src/optim/adabound.rs:35-64)."""
+
+    def __init__(self, params=None, lr: float = 1e-3, final_lr: float = 0.1, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.0, gamma: float = 1e-3):
+        super().__init__(_params(params), dict(lr=lr, final_lr=final_lr, betas=tuple(betas), eps=eps,
+                                               weight_decay=weight_decay, gamma=gamma, base_lr=lr))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                grad = p.grad.float()
+                if g["weight_decay"]:
+                    grad = grad.add(p.float(), alpha=g["weight_decay"])
+                st = self.state[p]
+                if not st:
+                    st["step"] = 0
+                    st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                    st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+                st["step"] += 1
+                t = st["step"]
+                st["exp_avg"].mul_(b1).add_(grad, alpha=1 - b1)
+                st["exp_avg_sq"].mul_(b2).addcmul_(grad, grad, value=1 - b2)
+                step_size = g["lr"] * math.sqrt(1 - b2 ** t) / (1 - b1 ** t)
+                final_lr = g["final_lr"] * g["lr"] / g["base_lr"]
+                lower = final_lr * (1 - 1 / (g["gamma"] * t + 1))
+                upper = final_lr * (1 + 1 / (g["gamma"] * t))
+                denom = st["exp_avg_sq"].sqrt().add_(g["eps"])
+                eta = torch.full_like(denom, step_size).div_(denom).clamp_(lower, upper)
+                p.add_((-eta * st["exp_avg"]).to(p.dtype))
+        return loss
+
+
+class LAMB(_TorchOptimizer, _RefAPI):
+    """Layer-wise adaptive moments with trust ratio (``new(lr)`` = betas 0.9/0.999, eps 1e-6, wd 0.01,
+    bias correction on; src/optim/lamb.rs:34-62)."""
+
+    def __init__(self, params=None, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-6,
+                 weight_decay: float = 0.01, bias_correction: bool = True):
+        super().__init__(_params(params), dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay,
+                                               bias_correction=bias_correction))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                grad = p.grad.float()
+                st = self.state[p]
+                if not st:
+                    st["step"] = 0
+                    st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                    st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+                st["step"] += 1
+                t = st["step"]
+                st["exp_avg"].mul_(b1).add_(grad, alpha=1 - b1)
+                st["exp_avg_sq"].mul_(b2).addcmul_(grad, grad, value=1 - b2)
+                m, v = st["exp_avg"], st["exp_avg_sq"]
+                if g["bias_correction"]:
+                    m, v = m / (1 - b1 ** t), v / (1 - b2 ** t)
+                upd = m / (v.sqrt() + g["eps"])
+                if g["weight_decay"]:
+                    upd = upd.add(p.float(), alpha=g["weight_decay"])
+                wn, un = float(p.float().norm()), float(upd.norm())
+                trust = wn / un if wn > 0 and un > 0 else 1.0
+                p.add_((-g["lr"] * trust * upd).to(p.dtype))
+        return loss
+
+
+class LBFGS(torch.optim.LBFGS, _RefAPI):
+    """``new(lr)``: max_iter 20, max_eval 20, tol_grad 1e-5, tol_change 1e-9, history 10, strong-Wolfe line
+    search (src/optim/lbfgs.rs:35-52,192-203)."""
+
+    def __init__(self, params=None, lr: float = 1.0, max_iter: int = 20, max_eval: Optional[int] = 20,
+                 tolerance_grad: float = 1e-5, tolerance_change: float = 1e-9, history_size: int = 10,
+                 line_search_fn: Optional[str] = "strong_wolfe"):
+        super().__init__(_params(params), lr=lr, max_iter=max_iter, max_eval=max_eval,
+                         tolerance_grad=tolerance_grad, tolerance_change=tolerance_change,
+                         history_size=history_size, line_search_fn=line_search_fn)
