@@ -2,7 +2,7 @@
 
 Every rank trains the same tiny GPT on its own batches with the fused peer-memory bucket kernel
 and, in the same process, replays the job as one big-batch single-GPU run (gradients of all
-ranks' batches averaged) with the plain fused AdamW.  Prints one JSON line per rank.
+ranks' batches averaged) with the plain fused AdamW.  Writes one JSON file per rank into $DDP_RESULT_DIR.
 """
 import json
 import os
@@ -96,7 +96,9 @@ def main():
     out = {"rank": rank, "world": world, "mode": mode, "n_buckets": n_buckets,
            "loss_ddp": [round(float(x), 4) for x in lt], "loss_ref": [round(x, 4) for x in ref_losses],
            "worst_rel_update_diff": round(worst, 4)}
-    print("RESULT " + json.dumps(out), flush=True)
+    # one file per rank: lines printed by several ranks to a shared pipe can interleave
+    with open(os.path.join(os.environ["DDP_RESULT_DIR"], f"rank{rank}.json"), "w") as f:
+        json.dump(out, f)
     dist.barrier()
     dist.destroy_process_group()
 

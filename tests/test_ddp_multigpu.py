@@ -4,6 +4,7 @@ import os
 import socket
 import subprocess
 import sys
+import tempfile
 
 import pytest
 import torch
@@ -19,14 +20,14 @@ def _free_port():
 
 
 def _run(mode, nproc):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out_dir = tempfile.mkdtemp(prefix="ddp_res_")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", DDP_RESULT_DIR=out_dir)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(ROOT, "tests", "ddp_worker.py"), mode]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
-    res = [json.loads(l.split("RESULT ", 1)[1]) for l in p.stdout.splitlines() if l.startswith("RESULT ")]
-    assert len(res) == nproc
+    res = [json.load(open(os.path.join(out_dir, f"rank{r}.json"))) for r in range(nproc)]
     return res
 
 
