@@ -314,6 +314,15 @@ def send(tensor, dst: int, group: Optional[ProcessGroup] = None, tag: int = 0) -
     dist.send(_t(tensor).contiguous(), dst, group=_h(group), tag=tag)
 
 
+def isend(tensor, dst: int, group: Optional[ProcessGroup] = None, tag: int = 0) -> DistributedRequest:
+    """Non-blocking send; keep the returned request (and the tensor) alive until ``wait()``."""
+    return DistributedRequest(dist.isend(_t(tensor).contiguous(), dst, group=_h(group), tag=tag))
+
+
+def irecv(tensor, src: int, group: Optional[ProcessGroup] = None, tag: int = 0) -> DistributedRequest:
+    return DistributedRequest(dist.irecv(_t(tensor), src, group=_h(group), tag=tag))
+
+
 def recv(tensor, src: int, group: Optional[ProcessGroup] = None, tag: int = 0) -> None:
     dist.recv(_t(tensor), src, group=_h(group), tag=tag)
 
