@@ -4,6 +4,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <cstring>
+
 #include "api.h"
 #include "common/launch.h"
 
@@ -68,9 +70,45 @@ void ddp_wait_end(int64_t flags_ptr, int64_t n_slots, int64_t world, int64_t ran
                    cur_stream(int(device)));
 }
 
+// CRC-64 (reflected polynomial 0xC96C5795D7870F42, init and final XOR all-ones): the checksum of the
+// RusTorch binary container (reference: src/serialization/core.rs:255-269), slicing-by-8.
+uint64_t crc64_bytes(const pybind11::bytes& data) {
+  static uint64_t table[8][256];
+  static bool ready = false;
+  if (!ready) {
+    for (int b = 0; b < 256; ++b) {
+      uint64_t c = uint64_t(b);
+      for (int k = 0; k < 8; ++k) c = (c & 1) ? (c >> 1) ^ 0xC96C5795D7870F42ull : (c >> 1);
+      table[0][b] = c;
+    }
+    for (int b = 0; b < 256; ++b)
+      for (int t = 1; t < 8; ++t) table[t][b] = table[0][table[t - 1][b] & 0xFF] ^ (table[t - 1][b] >> 8);
+    ready = true;
+  }
+  char* buf = nullptr;
+  Py_ssize_t n = 0;
+  if (PyBytes_AsStringAndSize(data.ptr(), &buf, &n) != 0) throw pybind11::error_already_set();
+  const unsigned char* p = reinterpret_cast<const unsigned char*>(buf);
+  uint64_t crc = ~0ull;
+  pybind11::gil_scoped_release release;
+  while (n >= 8) {
+    uint64_t w;
+    memcpy(&w, p, 8);
+    crc ^= w;
+    crc = table[7][crc & 0xFF] ^ table[6][(crc >> 8) & 0xFF] ^ table[5][(crc >> 16) & 0xFF] ^
+          table[4][(crc >> 24) & 0xFF] ^ table[3][(crc >> 32) & 0xFF] ^ table[2][(crc >> 40) & 0xFF] ^
+          table[1][(crc >> 48) & 0xFF] ^ table[0][crc >> 56];
+    p += 8;
+    n -= 8;
+  }
+  while (n-- > 0) crc = table[0][(crc ^ *p++) & 0xFF] ^ (crc >> 8);
+  return ~crc;
+}
+
 }  // namespace
 
 void register_extra_ops(pybind11::module_& m) {
+  m.def("crc64", &crc64_bytes, "CRC-64/XZ of a bytes object");
   m.def("ddp_bucket_adamw", &ddp_bucket_adamw,
         "fused reduce-scatter + scale + AdamW + all-gather of one gradient bucket over peer memory");
   m.def("ddp_wait_end", &ddp_wait_end);

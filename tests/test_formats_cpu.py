@@ -1,0 +1,165 @@
+"""File formats: RUSTORCH container (byte layout + CRC-64), safetensors, PYTORCH1, JSON, HF dir, GGUF + Q4_0/Q8_0."""
+import json
+import os
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from rustorch_b200.formats import gguf, rustorch_bin as rb
+from rustorch_b200 import formats as F
+from rustorch_b200.tensor import Tensor
+
+
+def test_crc64_known_vector_and_native_agree():
+    assert rb.crc64(b"123456789") == 0x995DC9BBDF1939FA        # CRC-64/XZ check value
+    d = os.urandom(4099)
+    assert rb.crc64(d) == rb.crc64_fast(d)
+
+
+def test_tensor_container_byte_layout(tmp_path):
+    p = str(tmp_path / "t.rustorch")
+    t = torch.arange(6, dtype=torch.float32).reshape(2, 3)
+    rb.save_tensor(t, p)
+    raw = open(p, "rb").read()
+    assert raw[:8] == b"RUSTORCH"
+    (hlen,) = struct.unpack_from("<Q", raw, 8)
+    header = raw[16:16 + hlen]
+    assert header[:8] == b"RUSTORCH"                                             # bincode [u8; 8]: raw bytes
+    assert struct.unpack_from("<Q", header, 8)[0] == 5 and header[16:21] == b"1.0.0"  # String: u64 len + bytes
+    assert struct.unpack_from("<Q", header, 21)[0] == 6 and header[29:35] == b"tensor"
+    payload = raw[16 + hlen:]
+    assert struct.unpack_from("<I", payload, 0)[0] == 2                          # ndim
+    assert struct.unpack_from("<QQ", payload, 4) == (2, 3)                       # dims
+    assert struct.unpack_from("<Q", payload, 20)[0] == 24                        # byte length
+    assert np.frombuffer(payload, "<f4", 6, 28).tolist() == [0, 1, 2, 3, 4, 5]
+    assert struct.unpack_from("<Q", header, hlen - 8)[0] == rb.crc64(payload)    # checksum is the last field
+    assert torch.equal(rb.load_tensor(p), t)
+    assert torch.equal(Tensor.load(p).data, t)
+
+
+def test_corruption_type_and_version_checks(tmp_path):
+    p = str(tmp_path / "t.bin")
+    rb.save_tensor(torch.ones(4), p)
+    raw = bytearray(open(p, "rb").read())
+    raw[-1] ^= 0xFF
+    open(p, "wb").write(raw)
+    with pytest.raises(IOError, match="Checksum"):
+        rb.load_tensor(p)
+    rb.save_tensor(torch.ones(4), p)
+    with pytest.raises(TypeError):
+        rb.load_state_dict(p)
+    open(p, "wb").write(b"NOTRUSTO" + b"\0" * 32)
+    with pytest.raises(ValueError):
+        rb.read_container(p)
+
+
+def test_state_dict_and_checkpoint_roundtrip(tmp_path):
+    m = torch.nn.Sequential(torch.nn.Linear(4, 3), torch.nn.BatchNorm1d(3))
+    p = str(tmp_path / "m.rustorch")
+    rb.save_module(m, p, config={"hidden": 3})
+    params, buffers, meta = rb.load_state_dict(p)
+    assert set(params) == {"0.weight", "0.bias", "1.weight", "1.bias"} and "1.running_mean" in buffers
+    assert meta["parameters"]["0.weight"]["shape"] == [3, 4] and meta["config"]["hidden"] == "3"
+    m2 = torch.nn.Sequential(torch.nn.Linear(4, 3), torch.nn.BatchNorm1d(3))
+    rb.load_module(m2, p)
+    assert torch.equal(m2[0].weight, m[0].weight)
+    c = str(tmp_path / "ck.rustorch")
+    mom = rb.encode_tensor(torch.full((3, 4), 0.5))
+    rb.save_checkpoint(c, 3, 1200, params, buffers, {"0.weight.exp_avg": mom, "hyper": json.dumps({"lr": 0.1}).encode()},
+                       {"last_epoch": b"3"}, {"loss": 0.25, "acc": 0.9}, timestamp=42)
+    ck = rb.load_checkpoint(c)
+    assert (ck["epoch"], ck["step"], ck["timestamp"]) == (3, 1200, 42) and ck["metrics"] == {"loss": 0.25, "acc": 0.9}
+    assert torch.equal(rb.decode_tensor(ck["optimizer_state"]["0.weight.exp_avg"])[0], torch.full((3, 4), 0.5))
+    assert torch.equal(ck["parameters"]["0.weight"], m[0].weight.detach())
+    v = torch.ones(3, requires_grad=True)
+    v.grad = torch.full((3,), 2.0)
+    rb.save_variable(v, str(tmp_path / "v.bin"))
+    v2 = rb.load_variable(str(tmp_path / "v.bin"))
+    assert v2.requires_grad and torch.equal(v2.grad, v.grad)
+    d = torch.ones(2, dtype=torch.float64)
+    rb.save_tensor(d, str(tmp_path / "d.bin"))
+    assert rb.load_tensor(str(tmp_path / "d.bin")).dtype == torch.float64
+
+
+def test_safetensors_spec_and_reference_style(tmp_path):
+    p = str(tmp_path / "m.safetensors")
+    ts = {"a": torch.randn(3, 4), "b": torch.randn(5).to(torch.bfloat16), "c": torch.arange(4)}
+    F.save_safetensors(ts, p, {"format": "pt"})
+    raw = open(p, "rb").read()
+    (n,) = struct.unpack_from("<Q", raw, 0)
+    assert n % 8 == 0 and json.loads(raw[8:8 + n])["a"]["dtype"] == "F32"
+    back = F.load_safetensors(p)
+    assert all(torch.equal(back[k], ts[k]) for k in ts) and back["b"].dtype == torch.bfloat16
+    # a file as the reference writes it: unpadded header, F64 entry, no metadata
+    hdr = json.dumps({"w": {"dtype": "F64", "shape": [2], "data_offsets": [0, 16]}}).encode()
+    q = str(tmp_path / "ref.safetensors")
+    open(q, "wb").write(struct.pack("<Q", len(hdr)) + hdr + np.array([1.5, -2.0], "<f8").tobytes())
+    assert F.load_safetensors(q)["w"].tolist() == [1.5, -2.0]
+    assert F.detect_format(p) == "safetensors"
+
+
+def test_pth_json_and_hf_dir(tmp_path):
+    ts = {"layer.weight": torch.randn(2, 3), "layer.bias": torch.zeros(2)}
+    p = str(tmp_path / "m.pth")
+    F.save_pth(ts, p)
+    assert open(p, "rb").read(8) == b"PYTORCH1" and torch.equal(F.load_pth(p)["layer.weight"], ts["layer.weight"])
+    tp = str(tmp_path / "real.pt")
+    F.save_torch_state_dict(ts, tp)
+    assert torch.equal(F.load_pth(tp)["layer.bias"], ts["layer.bias"]) and F.detect_format(tp) == "torch"
+    j = str(tmp_path / "m.json")
+    F.save_json_state_dict(ts, j, {"arch": "mlp"})
+    back, meta = F.load_json_state_dict(j)
+    assert torch.allclose(back["layer.weight"], ts["layer.weight"]) and meta["arch"] == "mlp"
+    d = str(tmp_path / "hf")
+    F.save_huggingface(ts, d, {"hidden_size": 3})
+    b2, cfg = F.load_huggingface(d)
+    assert cfg["hidden_size"] == 3 and torch.equal(b2["layer.bias"], ts["layer.bias"]) and F.detect_format(d) == "huggingface"
+
+
+def test_q4_0_q8_0_codecs():
+    rng = np.random.default_rng(0)
+    x = rng.normal(0, 0.02, (8, 64)).astype(np.float32)
+    q4 = gguf.quantize_q4_0(x)
+    assert q4.shape == (8, 2, 18) and q4.dtype == np.uint8
+    y = gguf.dequantize_q4_0(q4)
+    blk = x.reshape(8, 2, 32)
+    assert np.abs(y - x).max() <= np.abs(blk).max() / 8 * 0.51 + 1e-6          # half a quantisation step
+    # the element of largest magnitude maps to code 0 (value -8 * d) exactly up to f16 rounding of d
+    i = np.abs(blk[0, 0]).argmax()
+    assert abs(y.reshape(8, 2, 32)[0, 0, i] - blk[0, 0, i]) < abs(blk[0, 0, i]) * 2e-3
+    # manual decode of one block following the layout
+    b0 = q4[0, 0]
+    d = b0[:2].copy().view(np.float16).astype(np.float32)[0]
+    assert np.allclose(((b0[2:] & 0xF).astype(np.int32) - 8) * d, y[0, :16]) and np.allclose(((b0[2:] >> 4).astype(np.int32) - 8) * d, y[0, 16:32])
+    q8 = gguf.quantize_q8_0(x)
+    assert q8.shape == (8, 2, 34) and np.abs(gguf.dequantize_q8_0(q8) - x).max() <= np.abs(x).max() / 127 * 0.51 + 1e-6
+    assert np.all(gguf.dequantize_q4_0(gguf.quantize_q4_0(np.zeros((1, 32), np.float32))) == 0)
+
+
+def test_gguf_write_read_roundtrip(tmp_path):
+    p = str(tmp_path / "m.gguf")
+    w = torch.randn(16, 64) * 0.02
+    emb = torch.randn(10, 64)
+    md = {"general.architecture": "llama", "llama.block_count": 2, "llama.embedding_length": 64,
+          "llama.attention.head_count": 4, "llama.rope.freq_base": 10000.0, "tokenizer.ggml.tokens": ["a", "b", "c"],
+          "general.name": "tiny"}
+    gguf.write_gguf(p, md, {"blk.0.attn_q.weight": (w, gguf.GGMLType.Q4_0), "token_embd.weight": (emb, gguf.GGMLType.F16),
+                            "blk.0.ffn_up.weight": (w, gguf.GGMLType.Q8_0), "output_norm.weight": (torch.ones(64), gguf.GGMLType.F32)})
+    raw = open(p, "rb").read()
+    assert struct.unpack_from("<II", raw, 0) == (0x46554747, 3)
+    with gguf.GGUFFile(p) as g:
+        assert g.metadata["general.name"] == "tiny" and g.metadata["tokenizer.ggml.tokens"] == ["a", "b", "c"]
+        assert g.data_start % 32 == 0
+        info = g.tensors["blk.0.attn_q.weight"]
+        assert info.dims == (64, 16) and info.shape == (16, 64) and info.nbytes == 16 * 2 * 18
+        ref = torch.from_numpy(gguf.dequantize_q4_0(gguf.quantize_q4_0(w.numpy())))
+        assert torch.equal(g.load_tensor("blk.0.attn_q.weight"), ref)
+        assert torch.allclose(g.load_tensor("token_embd.weight"), emb, atol=2e-3)
+        assert torch.equal(g.load_tensor("output_norm.weight"), torch.ones(64))
+        blocks, _ = g.load_quantized("blk.0.ffn_up.weight")
+        assert blocks.shape == (16, 2, 34)
+        cfg = g.model_config()
+        assert cfg["n_layer"] == 2 and cfg["n_head_kv"] == 4 and cfg["vocab_size"] == 3
+    assert F.detect_format(p) == "gguf"
