@@ -140,4 +140,51 @@ void ddp_bucket_adamw(const DdpBucketArgs& a, int n_ctas, cudaStream_t stream);
 void ddp_wait_end(const int* flags, int n_slots, int world, int rank, int epoch,
                   unsigned long long timeout_ns, int* status, cudaStream_t stream);
 
+// ------------------------------------------------------------------ quant/q_gemv.cu
+struct QGemvArgs {
+  const void* qs;      // repacked quantised weights (layout in q_gemv.cu)
+  const void* scales;  // fp16 [N][K/32]
+  const void* x;       // fp16 [M][ldx]
+  long long ldx;
+  void* y;             // fp16 [M][ldy]
+  long long ldy;
+  const void* bias;      // fp16 [N] or null
+  const void* residual;  // fp16 [M][ldr] or null (added to the result)
+  long long ldr;
+  int M, N, K;
+  bool q8;  // false: Q4_0, true: Q8_0
+};
+void q_gemv(const QGemvArgs& a, cudaStream_t stream);
+void repack_q4_0(const void* blocks, void* qs, void* scales, long long n_blocks, cudaStream_t s);
+void repack_q8_0(const void* blocks, void* qs, void* scales, long long n_blocks, cudaStream_t s);
+
+// ------------------------------------------------------------- llm/decode_kernels.cu
+void rmsnorm_f16(const void* x, const void* w, void* y, long long rows, int C, float eps, cudaStream_t s);
+struct RopeKvArgs {
+  void *q, *k;          // fp16, rotated in place; [n_tok][H][D] / [n_tok][Hkv][D] with token strides
+  const void* v;
+  long long q_st, k_st, v_st;
+  void *cache_k, *cache_v;  // fp16 [B][Hkv][T_max][D]
+  const int* pos;           // [n_tok] position of each token in its sequence
+  const int* seq;           // [n_tok] sequence (batch) index of each token
+  int n_tok, H, Hkv, D, T_max;
+  float theta;
+  int interleaved;  // 1: pairs (2i, 2i+1) (GGUF llama), 0: pairs (i, i + D/2)
+};
+void rope_kv_f16(const RopeKvArgs& a, cudaStream_t s);
+struct AttnCacheArgs {
+  const void* q;  // fp16 [n_tok][H][D]
+  long long q_st;
+  const void *cache_k, *cache_v;
+  void* out;  // fp16 [n_tok][H][D]
+  long long o_st;
+  const int* kv_len;  // [n_tok] number of cached positions visible to the token
+  const int* seq;
+  int n_tok, H, Hkv, D, T_max, max_kv_len;
+  float scale;
+};
+void attn_cache_f16(const AttnCacheArgs& a, cudaStream_t s);
+void silu_mul_f16(const void* gate, const void* up, void* out, long long rows, int cols, long long g_ld,
+                  long long u_ld, long long o_ld, cudaStream_t s);
+
 }  // namespace rt

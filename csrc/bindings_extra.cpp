@@ -70,6 +70,119 @@ void ddp_wait_end(int64_t flags_ptr, int64_t n_slots, int64_t world, int64_t ran
                    cur_stream(int(device)));
 }
 
+void check_f16(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kHalf, name, ": fp16 CUDA tensor required");
+}
+
+// y[M, N] = dequant(W)[N, K] @ x[M, K]^T (+bias) (+residual); qs / scales are the repacked device layout.
+void q_gemv(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, const c10::optional<Tensor>& bias,
+            const c10::optional<Tensor>& residual, bool q8) {
+  check_f16(scales, "q_gemv scales");
+  check_f16(x, "q_gemv x");
+  check_f16(y, "q_gemv y");
+  TORCH_CHECK(qs.is_cuda() && qs.is_contiguous() && scales.is_contiguous(), "q_gemv: contiguous CUDA weights required");
+  TORCH_CHECK(x.dim() == 2 && y.dim() == 2 && x.stride(1) == 1 && y.stride(1) == 1, "q_gemv: x [M, K], y [M, N]");
+  c10::cuda::CUDAGuard guard(x.device());
+  rt::QGemvArgs a{};
+  a.N = int(scales.size(0));
+  a.K = int(scales.size(1)) * 32;
+  a.M = int(x.size(0));
+  TORCH_CHECK(x.size(1) == a.K && y.size(0) == a.M && y.size(1) == a.N, "q_gemv: shape mismatch");
+  TORCH_CHECK(qs.numel() * qs.element_size() == (int64_t)a.N * (a.K / 32) * (q8 ? 32 : 16), "q_gemv: qs size mismatch");
+  a.qs = qs.data_ptr();
+  a.scales = scales.data_ptr();
+  a.x = x.data_ptr();
+  a.ldx = x.stride(0);
+  a.y = y.data_ptr();
+  a.ldy = y.stride(0);
+  if (bias.has_value() && bias->defined()) {
+    check_f16(*bias, "q_gemv bias");
+    a.bias = bias->data_ptr();
+  }
+  if (residual.has_value() && residual->defined()) {
+    check_f16(*residual, "q_gemv residual");
+    TORCH_CHECK(residual->size(0) == a.M && residual->size(1) == a.N && residual->stride(1) == 1, "q_gemv: bad residual");
+    a.residual = residual->data_ptr();
+    a.ldr = residual->stride(0);
+  }
+  a.q8 = q8;
+  rt::q_gemv(a, cur_stream(x.device().index()));
+}
+
+// GGUF block stream (uint8 [n_blocks, 18 | 34]) -> (qs, scales) device layout.
+void repack_quant(const Tensor& blocks, Tensor& qs, Tensor& scales, bool q8) {
+  TORCH_CHECK(blocks.is_cuda() && blocks.scalar_type() == at::kByte && blocks.is_contiguous(), "repack: uint8 CUDA blocks");
+  check_f16(scales, "repack scales");
+  const int64_t bb = q8 ? 34 : 18;
+  const int64_t n_blocks = blocks.numel() / bb;
+  TORCH_CHECK(scales.numel() == n_blocks && qs.numel() * qs.element_size() == n_blocks * (q8 ? 32 : 16), "repack: size mismatch");
+  c10::cuda::CUDAGuard guard(blocks.device());
+  if (q8) rt::repack_q8_0(blocks.data_ptr(), qs.data_ptr(), scales.data_ptr(), n_blocks, cur_stream(blocks.device().index()));
+  else rt::repack_q4_0(blocks.data_ptr(), qs.data_ptr(), scales.data_ptr(), n_blocks, cur_stream(blocks.device().index()));
+}
+
+void rmsnorm_f16(const Tensor& x, const Tensor& w, Tensor& y, double eps) {
+  check_f16(x, "rmsnorm x");
+  check_f16(w, "rmsnorm w");
+  check_f16(y, "rmsnorm y");
+  TORCH_CHECK(x.is_contiguous() && y.is_contiguous(), "rmsnorm: contiguous");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int C = int(w.numel());
+  rt::rmsnorm_f16(x.data_ptr(), w.data_ptr(), y.data_ptr(), x.numel() / C, C, float(eps), cur_stream(x.device().index()));
+}
+
+void rope_kv(Tensor& q, Tensor& k, const Tensor& v, Tensor& cache_k, Tensor& cache_v, const Tensor& pos,
+             const Tensor& seq, double theta, bool interleaved) {
+  check_f16(q, "rope q");
+  check_f16(k, "rope k");
+  check_f16(v, "rope v");
+  check_f16(cache_k, "rope cache_k");
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3 && q.stride(2) == 1 && k.stride(2) == 1 && v.stride(2) == 1 &&
+                  q.stride(1) == q.size(2) && k.stride(1) == k.size(2) && v.stride(1) == v.size(2),
+              "rope: q/k/v must be [n_tok, heads, D] with packed heads");
+  TORCH_CHECK(cache_k.dim() == 4 && cache_k.is_contiguous() && cache_v.is_contiguous(), "rope: cache [B, Hkv, T, D]");
+  TORCH_CHECK(pos.scalar_type() == at::kInt && seq.scalar_type() == at::kInt && pos.is_cuda(), "rope: int32 CUDA pos/seq");
+  c10::cuda::CUDAGuard guard(q.device());
+  rt::RopeKvArgs a{};
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr();
+  a.q_st = q.stride(0); a.k_st = k.stride(0); a.v_st = v.stride(0);
+  a.cache_k = cache_k.data_ptr(); a.cache_v = cache_v.data_ptr();
+  a.pos = pos.data_ptr<int>(); a.seq = seq.data_ptr<int>();
+  a.n_tok = int(q.size(0)); a.H = int(q.size(1)); a.Hkv = int(k.size(1)); a.D = int(q.size(2));
+  a.T_max = int(cache_k.size(2));
+  a.theta = float(theta);
+  a.interleaved = interleaved ? 1 : 0;
+  rt::rope_kv_f16(a, cur_stream(q.device().index()));
+}
+
+void attn_cache(const Tensor& q, const Tensor& cache_k, const Tensor& cache_v, Tensor& out, const Tensor& kv_len,
+                const Tensor& seq, int64_t max_kv_len, double scale) {
+  check_f16(q, "attn_cache q");
+  check_f16(out, "attn_cache out");
+  TORCH_CHECK(q.dim() == 3 && out.dim() == 3 && q.stride(2) == 1 && out.stride(2) == 1 && q.stride(1) == q.size(2) &&
+                  out.stride(1) == out.size(2), "attn_cache: q/out [n_tok, H, D] with packed heads");
+  c10::cuda::CUDAGuard guard(q.device());
+  rt::AttnCacheArgs a{};
+  a.q = q.data_ptr(); a.q_st = q.stride(0);
+  a.cache_k = cache_k.data_ptr(); a.cache_v = cache_v.data_ptr();
+  a.out = out.data_ptr(); a.o_st = out.stride(0);
+  a.kv_len = kv_len.data_ptr<int>(); a.seq = seq.data_ptr<int>();
+  a.n_tok = int(q.size(0)); a.H = int(q.size(1)); a.Hkv = int(cache_k.size(1)); a.D = int(q.size(2));
+  a.T_max = int(cache_k.size(2)); a.max_kv_len = int(max_kv_len);
+  a.scale = float(scale);
+  rt::attn_cache_f16(a, cur_stream(q.device().index()));
+}
+
+void silu_mul(const Tensor& gate, const Tensor& up, Tensor& out) {
+  check_f16(gate, "silu_mul gate");
+  check_f16(up, "silu_mul up");
+  check_f16(out, "silu_mul out");
+  TORCH_CHECK(gate.dim() == 2 && gate.stride(1) == 1 && up.stride(1) == 1 && out.stride(1) == 1, "silu_mul: 2-D rows");
+  c10::cuda::CUDAGuard guard(gate.device());
+  rt::silu_mul_f16(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.size(0), int(gate.size(1)), gate.stride(0),
+                   up.stride(0), out.stride(0), cur_stream(gate.device().index()));
+}
+
 // CRC-64 (reflected polynomial 0xC96C5795D7870F42, init and final XOR all-ones): the checksum of the
 // RusTorch binary container (reference: src/serialization/core.rs:255-269), slicing-by-8.
 uint64_t crc64_bytes(const pybind11::bytes& data) {
@@ -109,6 +222,12 @@ uint64_t crc64_bytes(const pybind11::bytes& data) {
 
 void register_extra_ops(pybind11::module_& m) {
   m.def("crc64", &crc64_bytes, "CRC-64/XZ of a bytes object");
+  m.def("q_gemv", &q_gemv, "dequant-fused Q4_0 / Q8_0 matrix-vector product");
+  m.def("repack_quant", &repack_quant);
+  m.def("rmsnorm_f16", &rmsnorm_f16);
+  m.def("rope_kv", &rope_kv);
+  m.def("attn_cache", &attn_cache);
+  m.def("silu_mul", &silu_mul);
   m.def("ddp_bucket_adamw", &ddp_bucket_adamw,
         "fused reduce-scatter + scale + AdamW + all-gather of one gradient bucket over peer memory");
   m.def("ddp_wait_end", &ddp_wait_end);

@@ -236,7 +236,7 @@ class GGUFFile:
 
     def load_tensor(self, name: str, dtype: torch.dtype = torch.float32) -> torch.Tensor:
         info = self.tensors[name]
-        return torch.from_numpy(np.ascontiguousarray(dequantize(self.raw(name), info.ggml_type, info.shape))).to(dtype)
+        return torch.from_numpy(np.array(dequantize(self.raw(name), info.ggml_type, info.shape), copy=True)).to(dtype)
 
     def load_quantized(self, name: str) -> Tuple[torch.Tensor, GGUFTensorInfo]:
         """Block bytes ``[rows, K/32, block_bytes]`` (uint8) for Q4_0 / Q8_0 weights, kept quantised for the
@@ -263,7 +263,10 @@ class GGUFFile:
                                                           else (self.tensors["token_embd.weight"].dims[1] if "token_embd.weight" in self.tensors else None))}
 
     def close(self) -> None:
-        self._mm.close()
+        try:
+            self._mm.close()
+        except BufferError:      # a caller still holds a view from raw(); the mapping goes with it
+            pass
         self._f.close()
 
     def __enter__(self):

@@ -1,0 +1,327 @@
+"""Llama-family inference runtime: GGUF weights (Q4_0 / Q8_0 kept quantised), fp16 activations, KV cache,
+prefill + token-by-token decode, optional tensor parallelism.
+
+This is the working version of what the reference's CLI sketches: its ``load_gguf`` is a TODO that returns
+a dummy model (example-cli/src/model/loader.rs:55-59), its generation loop re-runs the whole sequence for
+every token without a KV cache (model/inference.rs:135-192) and its tensor loader never decodes quantised
+blocks (model/formats/tensor_loader.rs:103-122).
+
+Per token and layer: RMSNorm -> fused QKV dequant-GEMV -> RoPE + cache append -> cached attention ->
+output projection (+residual) -> RMSNorm -> gate/up dequant-GEMV -> SwiGLU -> down projection (+residual).
+Tensor parallel (``tp_world > 1``): Q/K/V/gate/up are split by output rows (heads), ``attn_output`` and
+``ffn_down`` by input columns; the two partial sums per layer are all-reduced.
+"""
+from __future__ import annotations
+
+import math
+import time
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from ..formats import gguf
+from .quant import QuantLinear
+
+
+@dataclass
+class LlamaConfig:
+    vocab_size: int = 32000
+    n_layer: int = 32
+    n_embd: int = 4096
+    n_head: int = 32
+    n_head_kv: int = 32
+    n_ff: int = 11008
+    rope_theta: float = 10000.0
+    rms_eps: float = 1e-5
+    context_length: int = 2048
+    rope_interleaved: bool = True
+
+    @property
+    def head_dim(self) -> int:
+        return self.n_embd // self.n_head
+
+    @staticmethod
+    def llama_7b() -> "LlamaConfig":
+        return LlamaConfig()
+
+    @staticmethod
+    def llama3_8b() -> "LlamaConfig":
+        return LlamaConfig(vocab_size=128256, n_head_kv=8, n_ff=14336, rope_theta=500000.0, context_length=8192)
+
+    def num_parameters(self) -> int:
+        d, hd = self.n_embd, self.head_dim
+        per = d * (self.n_head * hd) + 2 * d * (self.n_head_kv * hd) + (self.n_head * hd) * d + 3 * d * self.n_ff
+        return self.n_layer * per + 2 * self.vocab_size * d
+
+
+class KVCache:
+    """fp16 key/value cache ``[B, Hkv_local, T_max, D]`` per layer with per-sequence lengths."""
+
+    def __init__(self, n_layer: int, batch: int, n_head_kv: int, max_len: int, head_dim: int, device, dtype=torch.float16):
+        self.k = [torch.zeros(batch, n_head_kv, max_len, head_dim, dtype=dtype, device=device) for _ in range(n_layer)]
+        self.v = [torch.zeros(batch, n_head_kv, max_len, head_dim, dtype=dtype, device=device) for _ in range(n_layer)]
+        self.lengths = [0] * batch
+        self.max_len = max_len
+
+    def seq_len(self, b: int = 0) -> int:
+        return self.lengths[b]
+
+    def clear(self) -> None:
+        self.lengths = [0] * len(self.lengths)
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.k + self.v)
+
+
+class _Layer:
+    __slots__ = ("attn_norm", "wqkv", "wo", "ffn_norm", "w_gate_up", "w_down")
+
+
+class LlamaRuntime:
+    def __init__(self, cfg: LlamaConfig, device="cuda", tp_rank: int = 0, tp_world: int = 1, tp_group=None):
+        self.cfg, self.device = cfg, torch.device(device)
+        self.tp_rank, self.tp_world, self.tp_group = tp_rank, tp_world, tp_group
+        if cfg.n_head % tp_world or cfg.n_head_kv % tp_world or (cfg.n_ff // 32) % tp_world:
+            raise ValueError("heads and n_ff/32 must be divisible by the tensor-parallel size")
+        self.h_local, self.hkv_local = cfg.n_head // tp_world, cfg.n_head_kv // tp_world
+        self.ff_local = cfg.n_ff // tp_world
+        self.layers: List[_Layer] = []
+        self.tok_emb: Optional[torch.Tensor] = None        # fp16 [V, d]
+        self.out_norm: Optional[torch.Tensor] = None
+        self.lm_head: Optional[QuantLinear] = None
+        self.act_dtype = torch.float16 if self.device.type == "cuda" else torch.float32
+        self._graph = None
+
+    # ---------------------------------------------------------------- loading
+    def _shard_attn_rows(self, q: QuantLinear, heads: int) -> QuantLinear:
+        return q if self.tp_world == 1 else q.shard_rows(self.tp_rank, self.tp_world)
+
+    @staticmethod
+    def _cat_rows(parts: List[QuantLinear]) -> QuantLinear:
+        new = object.__new__(QuantLinear)
+        p0 = parts[0]
+        new.ggml_type, new.q8, new.device, new.in_features = p0.ggml_type, p0.q8, p0.device, p0.in_features
+        if p0.blocks is not None:
+            new.blocks = torch.cat([p.blocks for p in parts], 0)
+            new.qs = new.scales = None
+            new.out_features = new.blocks.shape[0]
+        else:
+            new.blocks = None
+            new.qs, new.scales = torch.cat([p.qs for p in parts], 0), torch.cat([p.scales for p in parts], 0)
+            new.out_features = new.scales.shape[0]
+        return new
+
+    def _assemble_layer(self, wq, wk, wv, wo, wg, wu, wd, attn_norm, ffn_norm) -> _Layer:
+        r, w = self.tp_rank, self.tp_world
+        L = _Layer()
+        if w > 1:
+            wq, wk, wv = wq.shard_rows(r, w), wk.shard_rows(r, w), wv.shard_rows(r, w)
+            wg, wu = wg.shard_rows(r, w), wu.shard_rows(r, w)
+            wo, wd = wo.shard_cols(r, w), wd.shard_cols(r, w)
+        L.wqkv = self._cat_rows([wq, wk, wv])
+        L.w_gate_up = self._cat_rows([wg, wu])
+        L.wo, L.w_down = wo, wd
+        L.attn_norm, L.ffn_norm = attn_norm.to(self.device, self.act_dtype), ffn_norm.to(self.device, self.act_dtype)
+        return L
+
+    @classmethod
+    def from_gguf(cls, path: str, device="cuda", tp_rank: int = 0, tp_world: int = 1, tp_group=None) -> "LlamaRuntime":
+        with gguf.GGUFFile(path) as g:
+            mc = g.model_config()
+            cfg = LlamaConfig(vocab_size=int(mc["vocab_size"]), n_layer=int(mc["n_layer"]), n_embd=int(mc["n_embd"]),
+                              n_head=int(mc["n_head"]), n_head_kv=int(mc["n_head_kv"]), n_ff=int(mc["n_ff"]),
+                              rope_theta=float(mc["rope_theta"]), rms_eps=float(mc["rms_eps"]),
+                              context_length=int(mc["context_length"]))
+            rt = cls(cfg, device, tp_rank, tp_world, tp_group)
+
+            def ql(name: str) -> QuantLinear:
+                info = g.tensors[name]
+                if info.ggml_type in (gguf.GGMLType.Q4_0, gguf.GGMLType.Q8_0):
+                    blocks, _ = g.load_quantized(name)
+                    return QuantLinear(blocks, info.ggml_type, rt.device)
+                return QuantLinear.from_float(g.load_tensor(name), gguf.GGMLType.Q8_0, rt.device)
+
+            for i in range(cfg.n_layer):
+                p = f"blk.{i}."
+                rt.layers.append(rt._assemble_layer(ql(p + "attn_q.weight"), ql(p + "attn_k.weight"), ql(p + "attn_v.weight"),
+                                                    ql(p + "attn_output.weight"), ql(p + "ffn_gate.weight"), ql(p + "ffn_up.weight"),
+                                                    ql(p + "ffn_down.weight"), g.load_tensor(p + "attn_norm.weight"),
+                                                    g.load_tensor(p + "ffn_norm.weight")))
+            rt.tok_emb = g.load_tensor("token_embd.weight").to(rt.device, rt.act_dtype)
+            rt.out_norm = g.load_tensor("output_norm.weight").to(rt.device, rt.act_dtype)
+            head_name = "output.weight" if "output.weight" in g.tensors else "token_embd.weight"
+            rt.lm_head = ql(head_name)
+        return rt
+
+    @classmethod
+    def random_init(cls, cfg: LlamaConfig, device="cuda", ggml_type=gguf.GGMLType.Q4_0, tp_rank: int = 0, tp_world: int = 1,
+                    tp_group=None, seed: int = 0, std: float = 0.02) -> "LlamaRuntime":
+        """Synthetic weights of the right shapes and statistics, built directly in quantised form."""
+        rt = cls(cfg, device, tp_rank, tp_world, tp_group)
+        d, hd = cfg.n_embd, cfg.head_dim
+        mk = lambda o, i, s: QuantLinear.random(o, i, ggml_type, std, rt.device, seed * 1000 + s)  # noqa: E731
+        for li in range(cfg.n_layer):
+            s = li * 10
+            rt.layers.append(rt._assemble_layer(mk(cfg.n_head * hd, d, s), mk(cfg.n_head_kv * hd, d, s + 1),
+                                                mk(cfg.n_head_kv * hd, d, s + 2), mk(d, cfg.n_head * hd, s + 3),
+                                                mk(cfg.n_ff, d, s + 4), mk(cfg.n_ff, d, s + 5), mk(d, cfg.n_ff, s + 6),
+                                                torch.ones(d), torch.ones(d)))
+        g = torch.Generator(device=rt.device).manual_seed(seed)
+        rt.tok_emb = (torch.randn(cfg.vocab_size, d, device=rt.device, generator=g) * std).to(rt.act_dtype)
+        rt.out_norm = torch.ones(d, device=rt.device, dtype=rt.act_dtype)
+        rt.lm_head = mk(cfg.vocab_size, d, 999999)
+        return rt
+
+    def weight_bytes(self) -> int:
+        n = self.lm_head.nbytes() + self.tok_emb.numel() * self.tok_emb.element_size()
+        for L in self.layers:
+            n += L.wqkv.nbytes() + L.wo.nbytes() + L.w_gate_up.nbytes() + L.w_down.nbytes()
+        return n
+
+    def new_cache(self, batch: int, max_len: Optional[int] = None) -> KVCache:
+        return KVCache(self.cfg.n_layer, batch, self.hkv_local, max_len or self.cfg.context_length, self.cfg.head_dim,
+                       self.device, self.act_dtype)
+
+    # ---------------------------------------------------------------- forward
+    def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp_world > 1:
+            dist.all_reduce(x, group=self.tp_group)
+        return x
+
+    def _rmsnorm(self, x, w):
+        if self.device.type == "cuda":
+            y = torch.empty_like(x)
+            _native.load(required=True).rmsnorm_f16(x, w, y, self.cfg.rms_eps)
+            return y
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.cfg.rms_eps) * w.float()).to(x.dtype)
+
+    def _rope_reference(self, t: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        D = t.shape[-1]
+        half = D // 2
+        inv = self.cfg.rope_theta ** (-torch.arange(half, device=t.device, dtype=torch.float32) * 2.0 / D)
+        ang = pos.float()[:, None, None] * inv
+        cs, sn = ang.cos(), ang.sin()
+        tf = t.float()
+        if self.cfg.rope_interleaved:
+            a, b = tf[..., 0::2], tf[..., 1::2]
+            out = torch.stack([a * cs - b * sn, a * sn + b * cs], -1).flatten(-2)
+        else:
+            a, b = tf[..., :half], tf[..., half:]
+            out = torch.cat([a * cs - b * sn, a * sn + b * cs], -1)
+        return out.to(t.dtype)
+
+    def forward_tokens(self, tokens: torch.Tensor, pos: torch.Tensor, seq: torch.Tensor, cache: KVCache,
+                       last_only: Optional[torch.Tensor] = None, max_kv: Optional[int] = None) -> torch.Tensor:
+        """``tokens / pos / seq``: ``[n_tok]`` (token id, position in its sequence, sequence index).  The new
+        keys/values are appended to ``cache`` and every token attends to positions ``0 .. pos`` of its own
+        sequence.  Returns fp32 logits ``[n_tok or len(last_only), vocab]``."""
+        cfg = self.cfg
+        C = _native.load(required=True) if self.device.type == "cuda" else None
+        n = tokens.shape[0]
+        H, Hkv, D = self.h_local, self.hkv_local, cfg.head_dim
+        x = self.tok_emb[tokens]                                       # [n, d]
+        pos32, seq32 = pos.to(torch.int32), seq.to(torch.int32)
+        kv_len = pos32 + 1
+        if max_kv is None:          # upper bound of kv_len known to the host (avoids a device sync)
+            max_kv = cache.max_len
+        scale = 1.0 / math.sqrt(D)
+        for li, L in enumerate(self.layers):
+            h = self._rmsnorm(x, L.attn_norm)
+            qkv = L.wqkv(h)                                            # [n, (H + 2 Hkv) D]
+            q = qkv[:, : H * D].view(n, H, D)
+            k = qkv[:, H * D: (H + Hkv) * D].view(n, Hkv, D)
+            v = qkv[:, (H + Hkv) * D:].view(n, Hkv, D)
+            if C is not None:
+                q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+                C.rope_kv(q, k, v, cache.k[li], cache.v[li], pos32, seq32, cfg.rope_theta, cfg.rope_interleaved)
+                att = torch.empty_like(q)
+                C.attn_cache(q, cache.k[li], cache.v[li], att, kv_len, seq32, max_kv, scale)
+            else:
+                q, k = self._rope_reference(q, pos), self._rope_reference(k, pos)
+                cache.k[li][seq, :, pos] = k
+                cache.v[li][seq, :, pos] = v
+                att = torch.empty_like(q)
+                for t in range(n):
+                    Lk = int(pos[t]) + 1
+                    kk = cache.k[li][int(seq[t]), :, :Lk].float().repeat_interleave(H // Hkv, 0)   # [H, Lk, D]
+                    vv = cache.v[li][int(seq[t]), :, :Lk].float().repeat_interleave(H // Hkv, 0)
+                    p = torch.softmax((kk @ q[t].float().unsqueeze(-1)).squeeze(-1) * scale, -1)   # [H, Lk]
+                    att[t] = (p.unsqueeze(1) @ vv).squeeze(1).to(att.dtype)
+            att2 = att.reshape(n, H * D)
+            if self.tp_world == 1:
+                x = L.wo(att2, residual=x)
+            else:
+                x = x + self._all_reduce(L.wo(att2))
+            h = self._rmsnorm(x, L.ffn_norm)
+            gu = L.w_gate_up(h)                                        # [n, 2 ff_local]
+            if C is not None:
+                act = torch.empty((n, self.ff_local), dtype=gu.dtype, device=gu.device)
+                C.silu_mul(gu[:, : self.ff_local], gu[:, self.ff_local:], act)
+            else:
+                act = torch.nn.functional.silu(gu[:, : self.ff_local].float()).to(gu.dtype) * gu[:, self.ff_local:]
+            if self.tp_world == 1:
+                x = L.w_down(act, residual=x)
+            else:
+                x = x + self._all_reduce(L.w_down(act))
+        if last_only is not None:
+            x = x[last_only]
+        x = self._rmsnorm(x, self.out_norm)
+        return self.lm_head(x).float()
+
+    # --------------------------------------------------------------- generate
+    @torch.no_grad()
+    def prefill(self, prompts: torch.Tensor, cache: KVCache) -> torch.Tensor:
+        """``prompts [B, T]`` (equal lengths) -> logits of the last position ``[B, vocab]``."""
+        B, T = prompts.shape
+        dev = self.device
+        tokens = prompts.reshape(-1).to(dev)
+        pos = torch.arange(T, device=dev).repeat(B)
+        seq = torch.arange(B, device=dev).repeat_interleave(T)
+        last = torch.arange(B, device=dev) * T + (T - 1)
+        logits = self.forward_tokens(tokens, pos, seq, cache, last_only=last, max_kv=T)
+        cache.lengths = [T] * B
+        return logits
+
+    @torch.no_grad()
+    def decode_step(self, tokens: torch.Tensor, cache: KVCache) -> torch.Tensor:
+        """One new token per sequence: ``tokens [B]`` -> logits ``[B, vocab]``."""
+        B = tokens.shape[0]
+        dev = self.device
+        pos = torch.tensor(cache.lengths, device=dev)
+        seq = torch.arange(B, device=dev)
+        logits = self.forward_tokens(tokens.to(dev), pos, seq, cache, max_kv=max(cache.lengths) + 1)
+        cache.lengths = [l + 1 for l in cache.lengths]
+        return logits
+
+    @torch.no_grad()
+    def generate(self, prompts: torch.Tensor, max_new_tokens: int, sampler=None, eos_token: Optional[int] = None,
+                 cache: Optional[KVCache] = None) -> Tuple[torch.Tensor, Dict[str, float]]:
+        """Greedy (or ``sampler(logits) -> tokens``) generation.  Returns tokens ``[B, T + new]`` and timing:
+        ``ttft_s`` (prefill + first token) and ``decode_tokens_per_s``."""
+        B, T = prompts.shape
+        cache = cache or self.new_cache(B, T + max_new_tokens)
+        sync = (lambda: torch.cuda.synchronize(self.device)) if self.device.type == "cuda" else (lambda: None)
+        sync()
+        t0 = time.perf_counter()
+        logits = self.prefill(prompts, cache)
+        nxt = sampler(logits) if sampler else logits.argmax(-1)
+        sync()
+        ttft = time.perf_counter() - t0
+        out = [prompts.to(self.device), nxt.view(B, 1)]
+        t1 = time.perf_counter()
+        steps = 0
+        for _ in range(max_new_tokens - 1):
+            logits = self.decode_step(nxt, cache)
+            nxt = sampler(logits) if sampler else logits.argmax(-1)
+            out.append(nxt.view(B, 1))
+            steps += 1
+            if eos_token is not None and bool((nxt == eos_token).all()):
+                break
+        sync()
+        dt = time.perf_counter() - t1
+        return torch.cat(out, 1), {"ttft_s": ttft, "decode_tokens_per_s": B * steps / dt if dt > 0 and steps else 0.0,
+                                   "decode_steps": steps, "batch": B}

@@ -1,0 +1,124 @@
+"""Quantised linear layers for the LLM runtime (GGUF Q4_0 / Q8_0 weights kept quantised on the device).
+
+``QuantLinear`` stores the repacked nibbles / int8 values and the fp16 block scales and multiplies fp16
+activations through the dequant-fused GEMV kernel (csrc/quant/q_gemv.cu).  On a machine without CUDA the
+same object dequantises to fp32 and uses a plain matmul, which is also the oracle in the tests.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+from .. import _native
+from ..formats import gguf
+
+
+class QuantLinear:
+    def __init__(self, blocks: torch.Tensor, ggml_type: gguf.GGMLType, device=None):
+        """``blocks``: uint8 ``[out_features, in_features / 32, 18 | 34]`` as stored in a GGUF file."""
+        self.ggml_type = gguf.GGMLType(ggml_type)
+        if self.ggml_type not in (gguf.GGMLType.Q4_0, gguf.GGMLType.Q8_0):
+            raise ValueError("QuantLinear supports Q4_0 and Q8_0")
+        self.q8 = self.ggml_type is gguf.GGMLType.Q8_0
+        self.out_features, nb, bb = blocks.shape
+        assert bb == (34 if self.q8 else 18), "block byte size does not match the type"
+        self.in_features = nb * 32
+        dev = torch.device(device) if device is not None else blocks.device
+        self.device = dev
+        if dev.type == "cuda":
+            C = _native.load(required=True)
+            b = blocks.to(dev).contiguous()
+            self.scales = torch.empty((self.out_features, nb), dtype=torch.float16, device=dev)
+            self.qs = torch.empty((self.out_features, nb, 32 if self.q8 else 16), dtype=torch.int8 if self.q8 else torch.uint8,
+                                  device=dev)
+            C.repack_quant(b, self.qs, self.scales, self.q8)
+            self.blocks = None
+        else:
+            self.blocks = blocks.contiguous()
+            self.qs = self.scales = None
+
+    # ------------------------------------------------------------ constructors
+    @classmethod
+    def from_float(cls, weight: torch.Tensor, ggml_type: gguf.GGMLType = gguf.GGMLType.Q4_0, device=None) -> "QuantLinear":
+        w = weight.detach().float().cpu().numpy()
+        q = gguf.quantize_q8_0(w) if gguf.GGMLType(ggml_type) is gguf.GGMLType.Q8_0 else gguf.quantize_q4_0(w)
+        return cls(torch.from_numpy(q), ggml_type, device or weight.device)
+
+    @classmethod
+    def random(cls, out_features: int, in_features: int, ggml_type: gguf.GGMLType = gguf.GGMLType.Q4_0, std: float = 0.02,
+               device="cpu", seed: int = 0) -> "QuantLinear":
+        """Synthetic quantised weights, statistically like quantising N(0, std) (random nibbles + the scale
+        that maps the extreme code to ~3.3 sigma), generated directly in block form on the target device."""
+        dev = torch.device(device)
+        g = torch.Generator(device=dev).manual_seed(seed)
+        nb = in_features // 32
+        q8 = gguf.GGMLType(ggml_type) is gguf.GGMLType.Q8_0
+        bb = 34 if q8 else 18
+        blocks = torch.randint(0, 256, (out_features, nb, bb), dtype=torch.uint8, device=dev, generator=g)
+        d = (torch.rand(out_features, nb, device=dev, generator=g) * 0.2 + 0.9) * (std * 3.3 / (127 if q8 else 8))
+        blocks[..., :2] = d.to(torch.float16).view(torch.uint8).reshape(out_features, nb, 2)
+        return cls(blocks, ggml_type, dev)
+
+    # ------------------------------------------------------------------ compute
+    def dequantize(self) -> torch.Tensor:
+        """fp32 ``[out, in]`` weights (decoded from the stored representation)."""
+        if self.blocks is not None:
+            arr = self.blocks.numpy()
+            w = gguf.dequantize_q8_0(arr) if self.q8 else gguf.dequantize_q4_0(arr)
+            return torch.from_numpy(w)
+        d = self.scales.float().unsqueeze(-1)
+        if self.q8:
+            return (self.qs.float() * d).reshape(self.out_features, self.in_features)
+        words = self.qs.view(torch.int32).to(torch.int64) & 0xFFFFFFFF            # [N, nb, 4]
+        out = torch.empty(self.out_features, self.in_features // 32, 32, dtype=torch.float32, device=self.device)
+        for e in range(8):
+            shift = 16 + 4 * (e >> 1) if e & 1 else 4 * (e >> 1)
+            out[..., e::8] = (((words >> shift) & 0xF).float() - 8.0)
+        # out[..., e::8] picks positions e, 8+e, 16+e, 24+e = word index 0..3 at element e  ->  weight 8*i + e
+        return (out * d).reshape(self.out_features, self.in_features)
+
+    def __call__(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``x [..., in]`` -> ``[..., out]`` (fp16 on CUDA)."""
+        shp = x.shape[:-1]
+        x2 = x.reshape(-1, self.in_features)
+        if self.device.type == "cuda":
+            C = _native.load(required=True)
+            x2 = x2.to(torch.float16).contiguous()
+            y = torch.empty((x2.shape[0], self.out_features), dtype=torch.float16, device=self.device)
+            r = residual.reshape(-1, self.out_features) if residual is not None else None
+            C.q_gemv(self.qs, self.scales, x2, y, None, r, self.q8)
+        else:
+            y = x2.float() @ self.dequantize().t()
+            if residual is not None:
+                y = y + residual.reshape(-1, self.out_features).float()
+            y = y.to(x.dtype)
+        return y.reshape(*shp, self.out_features)
+
+    def nbytes(self) -> int:
+        return self.out_features * (self.in_features // 32) * (34 if self.q8 else 18)
+
+    def shard_rows(self, rank: int, world: int) -> "QuantLinear":
+        """Column-parallel shard: a contiguous slice of output rows."""
+        n = self.out_features // world
+        return self._slice(slice(rank * n, (rank + 1) * n), slice(None))
+
+    def shard_cols(self, rank: int, world: int) -> "QuantLinear":
+        """Row-parallel shard: a contiguous slice of input blocks."""
+        nb = self.in_features // 32 // world
+        return self._slice(slice(None), slice(rank * nb, (rank + 1) * nb))
+
+    def _slice(self, rows, blks) -> "QuantLinear":
+        new = object.__new__(QuantLinear)
+        new.ggml_type, new.q8, new.device = self.ggml_type, self.q8, self.device
+        if self.blocks is not None:
+            new.blocks = self.blocks[rows, blks].contiguous()
+            new.qs = new.scales = None
+            new.out_features, nb = new.blocks.shape[0], new.blocks.shape[1]
+        else:
+            new.blocks = None
+            new.qs, new.scales = self.qs[rows, blks].contiguous(), self.scales[rows, blks].contiguous()
+            new.out_features, nb = new.scales.shape
+        new.in_features = nb * 32
+        return new

@@ -125,7 +125,7 @@ def test_q4_0_q8_0_codecs():
     assert q4.shape == (8, 2, 18) and q4.dtype == np.uint8
     y = gguf.dequantize_q4_0(q4)
     blk = x.reshape(8, 2, 32)
-    assert np.abs(y - x).max() <= np.abs(blk).max() / 8 * 0.51 + 1e-6          # half a quantisation step
+    assert np.abs(y - x).max() <= np.abs(blk).max() / 8 * 1.01 + 1e-6          # one step: the code range -8..7 clips the far side
     # the element of largest magnitude maps to code 0 (value -8 * d) exactly up to f16 rounding of d
     i = np.abs(blk[0, 0]).argmax()
     assert abs(y.reshape(8, 2, 32)[0, 0, i] - blk[0, 0, i]) < abs(blk[0, 0, i]) * 2e-3
