@@ -4,13 +4,17 @@
 // One CTA = one 128-row query tile of one (batch, head).  Warps 0..3 (128 threads) each own
 // one score row; warp 4 lane 0 issues every TMA load and every tcgen05.mma:
 //   S  = Q K_j^T          -> TMEM columns [0,128)
-//   row threads: online softmax on S (two TMEM passes, 32 columns at a time), P (bf16) into the
-//                swizzled staging tile in shared memory
-//   Ob = P V_j            -> TMEM columns [128,128+D)   (fresh each block)
-//   row threads: O = O * exp2(m_old - m_new) + Ob    (fp32 in registers)
-// K/V tiles stream through a 2-deep TMA ring.  The score matrix never reaches HBM, unlike
-// the reference, which materialises [B,H,T,T] scores (src/nn/transformer_phase6.rs:342-374)
-// and whose "fused_attention" kernel string is never compiled (src/gpu/custom_kernels.rs:439-536).
+//   row threads: pull their whole S row into registers (one wait), release S at once so the
+//                MMA of the NEXT key tile overlaps this tile's softmax, exponentiate against a
+//                running reference maximum and stage P (bf16) in shared memory
+//   O += P V_j            -> TMEM columns [128,128+D), accumulated by the tensor core
+// The reference maximum is only raised (and O / l rescaled through a TMEM load-scale-store)
+// when a row's block maximum exceeds it by more than 2^8; until then exponentials are taken
+// against the stale maximum, which the final division by l cancels exactly.  K and V tiles
+// stream through separate 2-deep TMA rings (K is released as soon as its S MMA retires).
+// The score matrix never reaches HBM, unlike the reference, which materialises [B,H,T,T]
+// scores (src/nn/transformer_phase6.rs:342-374) and whose "fused_attention" kernel string is
+// never compiled (src/gpu/custom_kernels.rs:439-536).
 #include "../api.h"
 #include "../common/launch.h"
 #include "attn_common.cuh"
@@ -35,9 +39,11 @@ struct AttnFwdSmem {
   static constexpr int OFF_V = 3 * TILE;
   static constexpr int OFF_P = 5 * TILE;
   static constexpr int OFF_BAR = OFF_P + 2 * ATT_HALF_BYTES;
-  // q_full, kv_full[2], kv_empty[2], s_full, p_full, o_full
-  static constexpr int TOTAL = OFF_BAR + 8 * 8 + 16;
+  // q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full, s_empty, p_full, pv_done
+  static constexpr int TOTAL = OFF_BAR + 13 * 8 + 16;
 };
+
+constexpr float ATT_RESCALE_THRESHOLD = 8.f;  // log2 units
 
 template <int D>
 __global__ void __launch_bounds__(160, (D == 64) ? 2 : 1)
@@ -54,12 +60,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   uint8_t* sP = smem + S::OFF_P;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;
-  uint64_t* kv_empty = bars + 3;
-  uint64_t* s_full = bars + 5;
-  uint64_t* p_full = bars + 6;
-  uint64_t* o_full = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = bars + 3;
+  uint64_t* v_full = bars + 5;
+  uint64_t* v_empty = bars + 7;
+  uint64_t* s_full = bars + 9;
+  uint64_t* s_empty = bars + 10;
+  uint64_t* p_full = bars + 11;
+  uint64_t* pv_done = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   CtaCtl* ctl = reinterpret_cast<CtaCtl*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -73,12 +82,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     mbar_init(s_full, 1);
+    mbar_init(s_empty, 128);
     mbar_init(p_full, 128);
-    mbar_init(o_full, 1);
+    mbar_init(pv_done, 1);
     ctl->abort = 0;
     fence_mbar_init();
   }
@@ -104,142 +116,182 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     if (lane == 0 && n_kv > 0) {
       constexpr uint32_t idesc_S = make_idesc_f16(128, 128, false, false, true);
       constexpr uint32_t idesc_PV = make_idesc_f16(128, D, false, true, true);
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+      auto kbuf = [&](int s) { return smem + S::OFF_K + s * S::TILE; };
+      auto vbuf = [&](int s) { return smem + S::OFF_V + s * S::TILE; };
+      auto issue_S = [&](int s) {
+        const uint32_t aK = smem_u32(kbuf(s));
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16_ss(tmem_S, tile_desc_kmajor<D>(aQ, kk), tile_desc_kmajor<D>(aK, kk), idesc_S, kk > 0 ? 1u : 0u);
+        umma_commit(s_full);
+        umma_commit(&k_empty[s]);
+      };
       bool ok = true;
       mbar_arrive_expect_tx(q_full, S::TILE);
       load_tile<D>(sQ, &tmap_q, q_full, q0, h, b);
-      mbar_arrive_expect_tx(&kv_full[0], 2 * S::TILE);
-      load_tile<D>(smem + S::OFF_K, &tmap_k, &kv_full[0], 0, hk, b);
-      load_tile<D>(smem + S::OFF_V, &tmap_v, &kv_full[0], 0, hk, b);
-      ok = mbar_wait(q_full, 0, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER);
+      for (int j = 0; j < min(2, n_kv); ++j) {
+        mbar_arrive_expect_tx(&k_full[j], S::TILE);
+        load_tile<D>(kbuf(j), &tmap_k, &k_full[j], j * ATT_BN, hk, b);
+        mbar_arrive_expect_tx(&v_full[j], S::TILE);
+        load_tile<D>(vbuf(j), &tmap_v, &v_full[j], j * ATT_BN, hk, b);
+      }
+      ok = mbar_wait(q_full, 0, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER) &&
+           mbar_wait(&k_full[0], 0, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER);
+      if (ok) {
+        tc_fence_after();
+        issue_S(0);
+      }
       for (int j = 0; j < n_kv && ok; ++j) {
         const int s = j & 1;
-        if (j + 1 < n_kv) {
-          const int s2 = (j + 1) & 1;
-          if (!mbar_wait(&kv_empty[s2], (((j + 1) >> 1) & 1) ^ 1, ctl, p.status,
-                         RT_ERR_TIMEOUT_PRODUCER)) {
-            ok = false;
-            break;
-          }
-          mbar_arrive_expect_tx(&kv_full[s2], 2 * S::TILE);
-          load_tile<D>(smem + S::OFF_K + s2 * S::TILE, &tmap_k, &kv_full[s2], (j + 1) * ATT_BN, hk,
-                       b);
-          load_tile<D>(smem + S::OFF_V + s2 * S::TILE, &tmap_v, &kv_full[s2], (j + 1) * ATT_BN, hk,
-                       b);
+        const uint32_t ph = (j >> 1) & 1;
+        if (j + 1 < n_kv) {  // S of the next key tile as soon as the row threads hold S(j) in registers
+          const int s1 = (j + 1) & 1;
+          ok = mbar_wait(&k_full[s1], ((j + 1) >> 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA) &&
+               mbar_wait(s_empty, j & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after();
+          issue_S(s1);
         }
-        if (!mbar_wait(&kv_full[s], (j >> 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA)) {
-          ok = false;
-          break;
+        if (j + 2 < n_kv) {  // refill this K stage once S(j) has retired
+          if (!mbar_wait(&k_empty[s], ph, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
+          mbar_arrive_expect_tx(&k_full[s], S::TILE);
+          load_tile<D>(kbuf(s), &tmap_k, &k_full[s], (j + 2) * ATT_BN, hk, b);
         }
+        ok = mbar_wait(&v_full[s], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA) &&
+             mbar_wait(p_full, j & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+        if (!ok) break;
         tc_fence_after();
-        const uint32_t aQ = smem_u32(sQ);
-        const uint32_t aK = smem_u32(smem + S::OFF_K + s * S::TILE);
-        const uint32_t aV = smem_u32(smem + S::OFF_V + s * S::TILE);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          umma_f16_ss(tmem_S, tile_desc_kmajor<D>(aQ, kk), tile_desc_kmajor<D>(aK, kk), idesc_S,
-                      kk > 0 ? 1u : 0u);
-        umma_commit(s_full);
-        if (!mbar_wait(p_full, j & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t aP = smem_u32(sP);
+        const uint32_t aV = smem_u32(vbuf(s));
 #pragma unroll
         for (int kk = 0; kk < ATT_BN / 16; ++kk)
           umma_f16_ss(tmem_O, stage_desc_kmajor(aP, kk), tile_desc_mnmajor<D>(aV, kk), idesc_PV,
-                      kk > 0 ? 1u : 0u);
-        umma_commit(o_full);
-        umma_commit(&kv_empty[s]);
+                      (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(pv_done);
+        umma_commit(&v_empty[s]);
+        if (j + 2 < n_kv) {  // refill this V stage once PV(j) has retired
+          if (!mbar_wait(&v_empty[s], ph, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
+          mbar_arrive_expect_tx(&v_full[s], S::TILE);
+          load_tile<D>(vbuf(s), &tmap_v, &v_full[s], (j + 2) * ATT_BN, hk, b);
+        }
       }
     }
   } else {
     const int row = warp * 32 + lane;
     const int qi = q0 + row;
     const uint32_t lane_sel = uint32_t(warp * 32) << 16;
-    float m = -INFINITY, l = 0.f;
-    float o_acc[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
+    const int limit = p.causal ? min(p.Tk - 1, qi + off) : (p.Tk - 1);  // last visible column
+    float m = 0.f, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
-      if (!mbar_wait(s_full, j & 1, ctl, p.status, RT_ERR_TIMEOUT_SOFTMAX)) {
-        ok = false;
-        break;
-      }
+      if (!mbar_wait(s_full, j & 1, ctl, p.status, RT_ERR_TIMEOUT_SOFTMAX)) { ok = false; break; }
       tc_fence_after();
-      const int col_base = j * ATT_BN;
-      const int limit = p.causal ? min(p.Tk - 1, qi + off) : (p.Tk - 1);  // last visible column
-      float mx = m;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32b_x32(tmem_S + lane_sel + c * 32, r);
-        tmem_ld_wait();
+      uint32_t r[128];
+      __syncwarp();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+      for (int c = 0; c < 4; ++c)
+        tmem_ld_32x32b_x32(tmem_S + lane_sel + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(s_empty);  // S is in registers: the next S MMA may overwrite TMEM now
+      const int col_base = j * ATT_BN;
+      // masking is only needed on the tile that crosses the causal diagonal or the end of the keys
+      const bool partial = (col_base + ATT_BN - 1 > q0 + off && p.causal) || (col_base + ATT_BN > p.Tk);
+      float mx = -INFINITY;
+      if (partial) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+          float s = __uint_as_float(r[i]) * p.scale_log2;
+          s = (col_base + i <= limit) ? s : -INFINITY;
+          r[i] = __float_as_uint(s);
+          mx = fmaxf(mx, s);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
           const float s = __uint_as_float(r[i]) * p.scale_log2;
-          if (col_base + c * 32 + i <= limit) mx = fmaxf(mx, s);
+          r[i] = __float_as_uint(s);
+          mx = fmaxf(mx, s);
         }
       }
-      const float m_new = mx;
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
+      float alpha = 1.f;
+      bool rescale = false;
+      if (j == 0) {
+        m = (mx == -INFINITY) ? 0.f : mx;
+      } else {
+        rescale = __any_sync(0xffffffffu, mx > m + ATT_RESCALE_THRESHOLD);
+        if (rescale) {
+          const float m_new = fmaxf(m, mx);
+          alpha = ex2_approx(m - m_new);
+          m = m_new;
+          l *= alpha;
+        }
+      }
       float rowsum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 128; ++i) {
+        const float e = ex2_approx(__uint_as_float(r[i]) - m);
+        r[i] = __float_as_uint(e);
+        rowsum += e;
+      }
+      l += rowsum;
+      // P(j-1) V(j-1) must have retired before the staging tile is overwritten or O is rescaled
+      if (j > 0 && !mbar_wait(pv_done, (j - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_SOFTMAX)) { ok = false; break; }
+      if (rescale) {
+        tc_fence_after();
 #pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          __syncwarp();
+          tmem_ld_32x32b_x32(tmem_O + lane_sel + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32b_x32(tmem_O + lane_sel + c * 32, o);
+        }
+        tmem_st_wait();
+      }
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32b_x32(tmem_S + lane_sel + c * 32, r);
-        tmem_ld_wait();
         float pv[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = __uint_as_float(r[i]) * p.scale_log2;
-          const float e = (col_base + c * 32 + i <= limit) ? exp2f(s - m_use) : 0.f;
-          pv[i] = e;
-          rowsum += e;
-        }
+        for (int i = 0; i < 32; ++i) pv[i] = __uint_as_float(r[c * 32 + i]);
         stage_row_chunk_bf16(sP, row, c * 32, pv);
       }
-      l = l * alpha + rowsum;
-      m = m_new;
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_full);
-      if (!mbar_wait(o_full, j & 1, ctl, p.status, RT_ERR_TIMEOUT_SOFTMAX)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
+    }
+    if (ok && n_kv > 0) ok = mbar_wait(pv_done, (n_kv - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_EPILOGUE);
+    tc_fence_after();
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    __nv_bfloat16* orow = p.o + (long long)b * p.o_sb + (long long)qi * p.o_st + (long long)h * p.o_sh;
+#pragma unroll 1
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t o[32];
+      if (ok && n_kv > 0) {
         __syncwarp();
-        tmem_ld_32x32b_x32(tmem_O + lane_sel + c * 32, r);
+        tmem_ld_32x32b_x32(tmem_O + lane_sel + c * 32, o);
         tmem_ld_wait();
+      } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha + __uint_as_float(r[i]);
+        for (int i = 0; i < 32; ++i) o[i] = 0u;
       }
-      tc_fence_before();
-    }
-    if (ok && qi < p.Tq) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = p.o + (long long)b * p.o_sb + (long long)qi * p.o_st + (long long)h * p.o_sh;
+      if (ok && qi < p.Tq) {
 #pragma unroll
-      for (int q = 0; q < D / 8; ++q) {
-        uint4 w;
-        w.x = pack_bf16x2(o_acc[q * 8 + 0] * inv, o_acc[q * 8 + 1] * inv);
-        w.y = pack_bf16x2(o_acc[q * 8 + 2] * inv, o_acc[q * 8 + 3] * inv);
-        w.z = pack_bf16x2(o_acc[q * 8 + 4] * inv, o_acc[q * 8 + 5] * inv);
-        w.w = pack_bf16x2(o_acc[q * 8 + 6] * inv, o_acc[q * 8 + 7] * inv);
-        reinterpret_cast<uint4*>(orow)[q] = w;
+        for (int q = 0; q < 4; ++q) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(o[q * 8 + 0]) * inv, __uint_as_float(o[q * 8 + 1]) * inv);
+          w.y = pack_bf16x2(__uint_as_float(o[q * 8 + 2]) * inv, __uint_as_float(o[q * 8 + 3]) * inv);
+          w.z = pack_bf16x2(__uint_as_float(o[q * 8 + 4]) * inv, __uint_as_float(o[q * 8 + 5]) * inv);
+          w.w = pack_bf16x2(__uint_as_float(o[q * 8 + 6]) * inv, __uint_as_float(o[q * 8 + 7]) * inv);
+          reinterpret_cast<uint4*>(orow + c * 32)[q] = w;
+        }
       }
-      p.lse[((long long)b * p.H + h) * p.Tq + qi] =
-          l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
     }
+    if (ok && qi < p.Tq)
+      p.lse[((long long)b * p.H + h) * p.Tq + qi] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+    tc_fence_before();
   }
 
   __syncwarp();
