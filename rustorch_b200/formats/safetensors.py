@@ -38,7 +38,7 @@ def save_safetensors(tensors: Dict[str, torch.Tensor], path: str, metadata: Opti
         t = tensors[name].detach().contiguous().cpu()
         if t.dtype not in _ST_NAMES:
             raise TypeError(f"dtype {t.dtype} of '{name}' cannot be stored in safetensors")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _ST_NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         blobs.append(raw)
         off += len(raw)

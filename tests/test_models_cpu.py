@@ -1,0 +1,88 @@
+"""Model zoo on CPU: shapes, the fixed ResNet semantics, Keras-style fit, save/load in every format."""
+import pytest
+import torch
+
+from rustorch_b200 import models as M
+from rustorch_b200 import nn
+
+
+def test_resnet18_structure_and_residual():
+    m = M.resnet18(10)
+    assert M.count_parameters(m) == 11181642          # torchvision's resnet18 with 10 classes
+    x = torch.randn(2, 3, 64, 64)
+    assert m(x).shape == (2, 10)
+    blk = M.BasicBlock(8, 8)
+    with torch.no_grad():
+        for p in blk.parameters():
+            p.zero_()
+    blk.eval()
+    y = blk(torch.ones(1, 8, 4, 4))
+    assert torch.allclose(y, torch.ones(1, 8, 4, 4))   # zero branch => output is the identity path (the add exists)
+    assert M.ResNetBuilder().depth(34).num_classes(5).build()(x).shape == (2, 5)
+    assert M.resnet50(7)(x).shape == (2, 7)
+    with pytest.raises(ValueError):
+        M.ResNetBuilder().depth(19)
+
+
+def test_cnn_rnn_seq2seq_bert_transformer_shapes():
+    c = M.CNNBuilder().input_shape(1, 28, 28).conv_channels([8, 16]).fc_sizes([32]).num_classes(10).batch_norm().build()
+    assert c(torch.randn(3, 1, 28, 28)).shape == (3, 10)
+    tok = torch.randint(0, 50, (4, 9))
+    assert M.RNNModel(50, 16, 32, 3)(tok).shape == (4, 3)
+    assert M.LSTMModel(50, 16, 32, 3, 2, True, 0.1)(tok).shape == (4, 3)
+    s2s = M.Seq2SeqModel(50, 60, 16, 32)
+    assert s2s(tok, torch.randint(0, 60, (4, 5))).shape == (4, 5, 60)
+    assert s2s.generate(tok, bos=1, max_len=6).shape == (4, 6)
+    cfg = M.BERTConfig(vocab_size=100, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
+                       max_position_embeddings=16)
+    bert = M.BERT(cfg, num_labels=3)
+    mask = torch.ones(4, 9)
+    mask[:, -2:] = 0
+    seq, pooled = bert(tok, attention_mask=mask)
+    assert seq.shape == (4, 9, 32) and pooled.shape == (4, 32) and bert.classify(tok).shape == (4, 3)
+    assert bert.masked_lm_logits(tok).shape == (4, 9, 100)
+    assert M.BERTConfig.bert_large_uncased().num_hidden_layers == 24
+    tm = M.TransformerModelBuilder().vocab_size(50).d_model(32).nhead(4).num_layers(2).dim_feedforward(64).causal(True).build()
+    assert tm(tok).shape == (4, 9, 50)
+    assert M.gpt2_medium is not None and M.GPTConfig.gpt2_medium().n_layer == 24
+
+
+def test_keras_style_fit_evaluate_predict():
+    torch.manual_seed(0)
+    X = torch.randn(200, 4)
+    y = (X.sum(1) > 0).long()
+    model = M.ModelBuilder().linear(4, 16).relu().linear(16, 2).build().compile("adam", "cross_entropy", ["accuracy"], lr=0.05)
+    hist = model.fit(X, y, epochs=15, batch_size=32, validation_split=0.2, seed=0)
+    assert hist.loss[-1] < hist.loss[0] and hist.metrics["accuracy"][-1] > 0.9 and len(hist.val_loss) == 15
+    assert model.evaluate(X, y)["accuracy"] > 0.9 and model.predict(X[:5]).shape == (5, 2)
+    assert "total parameters" in model.summary() and model.mode() is M.ModelMode.EVAL
+    eng = M.InferenceEngine(model)
+    eng.predict_batch([X[:3], X[3:7]])
+    assert eng.stats()["n"] == 2
+
+
+@pytest.mark.parametrize("fmt,ext", [(M.SerializationFormat.RUSTORCH, "rt"), (M.SerializationFormat.SAFETENSORS, "safetensors"),
+                                     (M.SerializationFormat.PYTORCH, "pt"), (M.SerializationFormat.JSON, "json")])
+def test_save_load_every_format(tmp_path, fmt, ext):
+    a = nn.Sequential(nn.Linear(4, 3), nn.BatchNorm1d(3))
+    b = nn.Sequential(nn.Linear(4, 3), nn.BatchNorm1d(3))
+    p = str(tmp_path / f"m.{ext}")
+    M.ModelSaver.save(a, p, fmt)
+    M.ModelLoader.load(b, p)
+    assert torch.allclose(a[0].weight, b[0].weight)
+    assert M.ModelInfo.of(a, p).size_bytes > 0
+
+
+def test_checkpoint_with_optimizer_moments(tmp_path):
+    m = nn.Linear(3, 2)
+    o = torch.optim.Adam(m.parameters(), 0.1)
+    m(torch.ones(1, 3)).sum().backward()
+    o.step()
+    p = str(tmp_path / "ck.rt")
+    M.ModelSaver.save_checkpoint(m, o, p, epoch=2, step=7, metrics={"loss": 0.5})
+    m2 = nn.Linear(3, 2)
+    o2 = torch.optim.Adam(m2.parameters(), 0.1)
+    ck = M.ModelLoader.load_checkpoint(m2, o2, p)
+    assert ck["epoch"] == 2 and ck["metrics"]["loss"] == 0.5 and torch.equal(m.weight, m2.weight)
+    st = list(o2.state_dict()["state"].values())
+    assert st and "exp_avg" in st[0]
