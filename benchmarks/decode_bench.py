@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--new", type=int, default=256)
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--eager", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     a = ap.parse_args()
     import torch.distributed as dist
     from rustorch_b200 import _native
@@ -50,6 +51,12 @@ def main():
     lg = rt.prefill(prompts[:, :64], cache)
     for _ in range(3):
         lg = rt.decode_step(lg.argmax(-1), cache)
+    launches_per_step = 0
+    graph = None
+    if not a.eager:
+        lc0 = _native.launch_count()
+        graph = rt.capture_decode_graph(cache, B)     # one decode step (all layers + lm_head + argmax) as a CUDA graph
+        launches_per_step = (_native.launch_count() - lc0) // 2      # warm-up pass + captured pass
     cache.clear()
     torch.cuda.synchronize()
     e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
@@ -58,8 +65,15 @@ def main():
     logits = rt.prefill(prompts, cache)
     nxt = logits.argmax(-1)
     e[1].record()
-    for _ in range(N - 1):
-        nxt = rt.decode_step(nxt, cache).argmax(-1)
+    if a.eager:
+        for _ in range(N - 1):
+            nxt = rt.decode_step(nxt, cache).argmax(-1)
+    else:
+        graph.tok.copy_(nxt)
+        graph.pos.fill_(T)
+        graph.step.zero_()
+        for _ in range(N - 1):
+            graph.graph.replay()
     e[2].record()
     torch.cuda.synchronize()
     t = torch.tensor([e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2])], device=dev)
@@ -75,7 +89,8 @@ def main():
            "batch": B, "prompt": T, "new_tokens": N, "ttft_ms": round(ttft_ms, 2), "ms_per_token": round(per_tok_s * 1e3, 4),
            "weight_bytes_per_rank": rt.weight_bytes(),
            "hbm_roofline_frac": round(rt.weight_bytes() / per_tok_s / hbm, 3),
-           "gpu_launches": _native.launch_count() - l0, "layers": a.layers,
+           "gpu_launches": _native.launch_count() - l0 + launches_per_step * (N - 1 if graph else 0), "layers": a.layers,
+           "decode_loop": "eager" if a.eager else "cuda_graph",
            "config": "llama-7b shape, Q4_0 random weights, fp16 KV cache, greedy", "parallelism": f"tp{world}"}
     if rank == 0:
         print(json.dumps(out), flush=True)

@@ -33,6 +33,7 @@ struct GemmArgs {
   bool accumulate;  // fp32 C only: C += result with float atomics
   int split_k;
   int block_n;  // 0 = auto, 128 or 256
+  bool ab_fp16 = false;  // A/B hold fp16 (C must be fp32, no fused epilogue)
 };
 void gemm_bf16(const GemmArgs& g, cudaStream_t stream);
 
@@ -81,6 +82,30 @@ void norm_fwd(const NormArgs& a, cudaStream_t stream);
 void norm_bwd(const NormArgs& a, cudaStream_t stream);
 // Number of CTAs (and therefore partial-sum rows) the backward kernel uses for `rows` rows.
 int norm_bwd_num_partials(long long rows, int sm_count);
+
+// ------------------------------------------------------------------ norm/batchnorm.cu
+// Channels-last matrix x[M][C]; gamma/beta/statistics fp32; scratch fp32 [2][C].
+struct BatchNormArgs {
+  int dtype;             // DType of x / y / residual / dy / dx
+  const void* x;
+  const void* residual;  // added before the ReLU, or null
+  void* y;
+  const float *gamma, *beta;                // may be null (affine = false)
+  float *running_mean, *running_var;        // updated in training when non-null; read in inference
+  float *save_mean, *save_rstd;             // [C], written in training, read by backward
+  float* scratch;
+  long long M;
+  int C;
+  float eps, momentum;
+  int relu, training;
+  // backward
+  const void* dy;
+  const void* y_relu;  // forward output when ReLU was fused (masks dy), else null
+  void* dx;
+  void* dres;          // gradient of the residual branch (= masked dy), or null
+};
+void batchnorm_fwd(const BatchNormArgs& a, cudaStream_t s);
+void batchnorm_bwd(const BatchNormArgs& a, cudaStream_t s);
 
 // ------------------------------------------------------------------- nn/embedding.cu
 void embedding_fwd(const long long* idx, const void* wte, const void* wpe, void* out,
@@ -140,6 +165,28 @@ void ddp_bucket_adamw(const DdpBucketArgs& a, int n_ctas, cudaStream_t stream);
 void ddp_wait_end(const int* flags, int n_slots, int world, int rank, int epoch,
                   unsigned long long timeout_ns, int* status, cudaStream_t stream);
 
+// ------------------------------------------------------- elementwise/elementwise.cu, softmax.cu
+enum DType : int { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2 };
+enum BinaryOp : int { EW_ADD = 0, EW_SUB, EW_MUL, EW_DIV, EW_MAX, EW_MIN, EW_POW };
+enum UnaryOp : int {
+  ACT_RELU = 0, ACT_SIGMOID, ACT_TANH, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU, ACT_ELU, ACT_LEAKY_RELU, ACT_SELU,
+  ACT_MISH, ACT_SOFTPLUS, ACT_HARDTANH, ACT_RELU6, ACT_HARDSIGMOID, ACT_HARDSWISH, ACT_EXP, ACT_LOG, ACT_SQRT,
+  ACT_RSQRT, ACT_NEG, ACT_ABS, ACT_SQUARE, ACT_SIN, ACT_COS, ACT_SCALE_SHIFT, ACT_RECIPROCAL
+};
+// mode 0: out = op(a, b) ; 1: out = op(a, scalar) ; 2: out = op(scalar, a).  ADD/SUB use a +- alpha * b.
+void elementwise_binary(int op, int dtype, const void* a, const void* b, void* out, long long n, float scalar,
+                        float alpha, int mode, cudaStream_t s);
+// forward: out = f(x; p0, p1) ; backward: out = dy * f'(x; p0, p1)
+void elementwise_unary(int op, int dtype, const void* x, const void* dy, void* out, long long n, float p0, float p1,
+                       bool backward, cudaStream_t s);
+// rows x C (contiguous rows, stride ld).  log_mode: 0 softmax, 1 log_softmax.
+void softmax_rows_fwd(int dtype, const void* x, void* y, long long rows, int C, long long ld, int log_mode, cudaStream_t s);
+// dx = y * (dy - sum(dy * y))  (softmax) ; dx = dy - exp(y) * sum(dy)  (log_softmax); y is the forward OUTPUT.
+void softmax_rows_bwd(int dtype, const void* y, const void* dy, void* dx, long long rows, int C, long long ld, int log_mode,
+                      cudaStream_t s);
+// Row reductions over the last dim: mode 0 sum, 1 mean, 2 max, 3 min, 4 variance (unbiased = p0 != 0), out fp32 [rows].
+void reduce_rows(int dtype, const void* x, float* out, long long rows, int C, long long ld, int mode, float p0, cudaStream_t s);
+
 // ------------------------------------------------------------------ quant/q_gemv.cu
 struct QGemvArgs {
   const void* qs;      // repacked quantised weights (layout in q_gemv.cu)
@@ -155,6 +202,7 @@ struct QGemvArgs {
   bool q8;  // false: Q4_0, true: Q8_0
 };
 void q_gemv(const QGemvArgs& a, cudaStream_t stream);
+void dequant_f16(const void* qs, const void* scales, void* out, long long n_blocks, bool q8, cudaStream_t s);
 void repack_q4_0(const void* blocks, void* qs, void* scales, long long n_blocks, cudaStream_t s);
 void repack_q8_0(const void* blocks, void* qs, void* scales, long long n_blocks, cudaStream_t s);
 
@@ -182,8 +230,15 @@ struct AttnCacheArgs {
   const int* seq;
   int n_tok, H, Hkv, D, T_max, max_kv_len;
   float scale;
+  // split-KV path only: fp32 scratch [n_tok][H][n_split][D + 2] (unused when n_split == 1)
+  float* partial = nullptr;
+  int n_split = 1;
 };
 void attn_cache_f16(const AttnCacheArgs& a, cudaStream_t s);
+// llm/attn_decode_split.cu: split-KV variant (D in {64,128,256}, H/Hkv in {1,2,4,8})
+bool attn_decode_split_supported(int D, int H, int Hkv);
+int attn_decode_num_splits(int n_tok, int Hkv, int max_kv_len, int sm_count);
+void attn_decode_split(const AttnCacheArgs& a, cudaStream_t s);
 void silu_mul_f16(const void* gate, const void* up, void* out, long long rows, int cols, long long g_ld,
                   long long u_ld, long long o_ld, cudaStream_t s);
 

@@ -28,8 +28,13 @@ void check_f32_cuda(const Tensor& t, const char* name) {
 void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, Tensor& c, const OptTensor& bias,
           const OptTensor& aux, int64_t epi_mode, double alpha, bool accumulate, int64_t split_k,
           int64_t block_n) {
-  check_bf16_cuda(a, "gemm a");
-  check_bf16_cuda(b, "gemm b");
+  const bool ab_fp16 = a.scalar_type() == at::kHalf;
+  if (ab_fp16) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && b.scalar_type() == at::kHalf, "gemm: fp16 A needs a CUDA fp16 B");
+  } else {
+    check_bf16_cuda(a, "gemm a");
+    check_bf16_cuda(b, "gemm b");
+  }
   TORCH_CHECK(c.is_cuda(), "gemm c: CUDA tensor required");
   TORCH_CHECK(a.dim() == b.dim() && a.dim() == c.dim() && (a.dim() == 2 || a.dim() == 3),
               "gemm: all operands rank 2 or all rank 3");
@@ -38,6 +43,7 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, Tensor& c, con
   c10::cuda::CUDAGuard guard(a.device());
   const bool batched = a.dim() == 3;
   rt::GemmArgs g{};
+  g.ab_fp16 = ab_fp16;
   g.batch = batched ? int(a.size(0)) : 1;
   g.M = int(a_mn ? a.size(-1) : a.size(-2));
   g.K = int(a_mn ? a.size(-2) : a.size(-1));

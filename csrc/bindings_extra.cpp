@@ -110,6 +110,17 @@ void q_gemv(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, 
 }
 
 // GGUF block stream (uint8 [n_blocks, 18 | 34]) -> (qs, scales) device layout.
+// out[N, K] fp16 = dequant(qs, scales): feeds the tensor-core GEMM on the prefill / large-batch path.
+void dequant_f16(const Tensor& qs, const Tensor& scales, Tensor& out, bool q8) {
+  check_f16(scales, "dequant scales");
+  check_f16(out, "dequant out");
+  TORCH_CHECK(qs.is_cuda() && qs.is_contiguous() && scales.is_contiguous() && out.is_contiguous(), "dequant: contiguous CUDA tensors");
+  const int64_t n_blocks = scales.numel();
+  TORCH_CHECK(out.numel() == n_blocks * 32 && qs.numel() * qs.element_size() == n_blocks * (q8 ? 32 : 16), "dequant: size mismatch");
+  c10::cuda::CUDAGuard guard(qs.device());
+  rt::dequant_f16(qs.data_ptr(), scales.data_ptr(), out.data_ptr(), n_blocks, q8, cur_stream(qs.device().index()));
+}
+
 void repack_quant(const Tensor& blocks, Tensor& qs, Tensor& scales, bool q8) {
   TORCH_CHECK(blocks.is_cuda() && blocks.scalar_type() == at::kByte && blocks.is_contiguous(), "repack: uint8 CUDA blocks");
   check_f16(scales, "repack scales");
@@ -170,6 +181,17 @@ void attn_cache(const Tensor& q, const Tensor& cache_k, const Tensor& cache_v, T
   a.n_tok = int(q.size(0)); a.H = int(q.size(1)); a.Hkv = int(cache_k.size(1)); a.D = int(q.size(2));
   a.T_max = int(cache_k.size(2)); a.max_kv_len = int(max_kv_len);
   a.scale = float(scale);
+  if (rt::attn_decode_split_supported(a.D, a.H, a.Hkv) && q.stride(0) % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(a.q) & 15) == 0) {
+    a.n_split = rt::attn_decode_num_splits(a.n_tok, a.Hkv, a.max_kv_len, rt::sm_count(q.device().index()));
+    Tensor part;
+    if (a.n_split > 1) {
+      part = at::empty({int64_t(a.n_tok) * a.H * a.n_split * (a.D + 2)}, q.options().dtype(at::kFloat));
+      a.partial = part.data_ptr<float>();
+    }
+    rt::attn_decode_split(a, cur_stream(q.device().index()));
+    return;
+  }
   rt::attn_cache_f16(a, cur_stream(q.device().index()));
 }
 
@@ -220,8 +242,155 @@ uint64_t crc64_bytes(const pybind11::bytes& data) {
 
 }  // namespace
 
+int dtype_code(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, ": CUDA tensor required");
+  switch (t.scalar_type()) {
+    case at::kFloat: return rt::DT_F32;
+    case at::kBFloat16: return rt::DT_BF16;
+    case at::kHalf: return rt::DT_F16;
+    default: TORCH_CHECK(false, name, ": dtype must be fp32, bf16 or fp16, got ", t.scalar_type());
+  }
+  return -1;
+}
+
+// mode 0: out = op(a, b) (same shape); 1: op(a, scalar); 2: op(scalar, a)
+void ew_binary(int64_t op, const Tensor& a, const c10::optional<Tensor>& b, Tensor& out, double scalar, double alpha,
+               int64_t mode) {
+  const int dt = dtype_code(a, "elementwise a");
+  TORCH_CHECK(a.is_contiguous() && out.is_contiguous() && out.numel() == a.numel() && out.scalar_type() == a.scalar_type(),
+              "elementwise: contiguous operands of one dtype and size");
+  const void* pb = nullptr;
+  if (mode == 0) {
+    TORCH_CHECK(b.has_value() && b->is_contiguous() && b->numel() == a.numel() && b->scalar_type() == a.scalar_type() &&
+                    b->is_cuda(), "elementwise: b must match a");
+    pb = b->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(a.device());
+  rt::elementwise_binary(int(op), dt, a.data_ptr(), pb, out.data_ptr(), a.numel(), float(scalar), float(alpha), int(mode),
+                         cur_stream(a.device().index()));
+}
+
+void ew_unary(int64_t op, const Tensor& x, const c10::optional<Tensor>& dy, Tensor& out, double p0, double p1) {
+  const int dt = dtype_code(x, "elementwise x");
+  TORCH_CHECK(x.is_contiguous() && out.is_contiguous() && out.numel() == x.numel() && out.scalar_type() == x.scalar_type(),
+              "elementwise: contiguous operands of one dtype and size");
+  const void* pg = nullptr;
+  if (dy.has_value() && dy->defined()) {
+    TORCH_CHECK(dy->is_contiguous() && dy->numel() == x.numel() && dy->scalar_type() == x.scalar_type() && dy->is_cuda(),
+                "elementwise: dy must match x");
+    pg = dy->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  rt::elementwise_unary(int(op), dt, x.data_ptr(), pg, out.data_ptr(), x.numel(), float(p0), float(p1), pg != nullptr,
+                        cur_stream(x.device().index()));
+}
+
+void softmax_rows(const Tensor& x, const c10::optional<Tensor>& dy, Tensor& out, bool log_mode) {
+  const int dt = dtype_code(x, "softmax x");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && out.dim() == 2 && out.stride(1) == 1 && out.stride(0) == x.stride(0) &&
+                  out.scalar_type() == x.scalar_type() && out.sizes() == x.sizes(), "softmax: 2-D rows, equal strides");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto st = cur_stream(x.device().index());
+  if (dy.has_value() && dy->defined()) {
+    TORCH_CHECK(dy->sizes() == x.sizes() && dy->stride(1) == 1 && dy->stride(0) == x.stride(0) &&
+                    dy->scalar_type() == x.scalar_type(), "softmax: dy must match y");
+    rt::softmax_rows_bwd(dt, x.data_ptr(), dy->data_ptr(), out.data_ptr(), x.size(0), int(x.size(1)), x.stride(0), log_mode, st);
+  } else {
+    rt::softmax_rows_fwd(dt, x.data_ptr(), out.data_ptr(), x.size(0), int(x.size(1)), x.stride(0), log_mode, st);
+  }
+}
+
+void reduce_rows(const Tensor& x, Tensor& out, int64_t mode, double p0) {
+  const int dt = dtype_code(x, "reduce_rows x");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && out.scalar_type() == at::kFloat && out.is_contiguous() &&
+                  out.numel() == x.size(0) && out.is_cuda(), "reduce_rows: x [rows, C], out fp32 [rows]");
+  c10::cuda::CUDAGuard guard(x.device());
+  rt::reduce_rows(dt, x.data_ptr(), out.data_ptr<float>(), x.size(0), int(x.size(1)), x.stride(0), int(mode), float(p0),
+                  cur_stream(x.device().index()));
+}
+
+const float* opt_f32(const c10::optional<Tensor>& t, int64_t n, const char* name) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == n, name,
+              ": fp32 CUDA tensor with one value per channel required");
+  return t->data_ptr<float>();
+}
+
+// x2 / y2: [M, C] contiguous (channels last).  scratch fp32 [2, C].
+void batchnorm_fwd(const Tensor& x2, const c10::optional<Tensor>& residual, Tensor& y2, const c10::optional<Tensor>& gamma,
+                   const c10::optional<Tensor>& beta, const c10::optional<Tensor>& running_mean,
+                   const c10::optional<Tensor>& running_var, const c10::optional<Tensor>& save_mean,
+                   const c10::optional<Tensor>& save_rstd, Tensor& scratch, double eps, double momentum, bool relu, bool training) {
+  rt::BatchNormArgs a{};
+  a.dtype = dtype_code(x2, "batchnorm x");
+  TORCH_CHECK(x2.dim() == 2 && x2.is_contiguous() && y2.is_contiguous() && y2.sizes() == x2.sizes() &&
+                  y2.scalar_type() == x2.scalar_type(), "batchnorm: x, y [M, C] contiguous");
+  a.M = x2.size(0);
+  a.C = int(x2.size(1));
+  a.x = x2.data_ptr();
+  a.y = y2.data_ptr();
+  if (residual.has_value() && residual->defined()) {
+    TORCH_CHECK(residual->is_contiguous() && residual->sizes() == x2.sizes() && residual->scalar_type() == x2.scalar_type(),
+                "batchnorm: residual must match x");
+    a.residual = residual->data_ptr();
+  }
+  a.gamma = opt_f32(gamma, a.C, "batchnorm gamma");
+  a.beta = opt_f32(beta, a.C, "batchnorm beta");
+  a.running_mean = const_cast<float*>(opt_f32(running_mean, a.C, "batchnorm running_mean"));
+  a.running_var = const_cast<float*>(opt_f32(running_var, a.C, "batchnorm running_var"));
+  a.save_mean = const_cast<float*>(opt_f32(save_mean, a.C, "batchnorm save_mean"));
+  a.save_rstd = const_cast<float*>(opt_f32(save_rstd, a.C, "batchnorm save_rstd"));
+  TORCH_CHECK(training || (a.running_mean && a.running_var), "batchnorm: inference needs running statistics");
+  a.scratch = const_cast<float*>(opt_f32(scratch, 2 * int64_t(a.C), "batchnorm scratch"));
+  a.eps = float(eps);
+  a.momentum = float(momentum);
+  a.relu = relu;
+  a.training = training;
+  c10::cuda::CUDAGuard guard(x2.device());
+  rt::batchnorm_fwd(a, cur_stream(x2.device().index()));
+}
+
+// scratch returns [dbeta, dgamma] (fp32 [2, C]).
+void batchnorm_bwd(const Tensor& x2, const Tensor& dy2, const c10::optional<Tensor>& y_relu, Tensor& dx2,
+                   const c10::optional<Tensor>& dres, const c10::optional<Tensor>& gamma, const Tensor& save_mean,
+                   const Tensor& save_rstd, Tensor& scratch) {
+  rt::BatchNormArgs a{};
+  a.dtype = dtype_code(x2, "batchnorm x");
+  TORCH_CHECK(x2.dim() == 2 && x2.is_contiguous() && dy2.is_contiguous() && dx2.is_contiguous() && dy2.sizes() == x2.sizes() &&
+                  dx2.sizes() == x2.sizes() && dy2.scalar_type() == x2.scalar_type() && dx2.scalar_type() == x2.scalar_type(),
+              "batchnorm_bwd: x, dy, dx [M, C] contiguous of one dtype");
+  a.M = x2.size(0);
+  a.C = int(x2.size(1));
+  a.x = x2.data_ptr();
+  a.dy = dy2.data_ptr();
+  a.dx = dx2.data_ptr();
+  if (y_relu.has_value() && y_relu->defined()) {
+    TORCH_CHECK(y_relu->is_contiguous() && y_relu->sizes() == x2.sizes() && y_relu->scalar_type() == x2.scalar_type(),
+                "batchnorm_bwd: y must match x");
+    a.y_relu = y_relu->data_ptr();
+  }
+  if (dres.has_value() && dres->defined()) {
+    TORCH_CHECK(dres->is_contiguous() && dres->sizes() == x2.sizes() && dres->scalar_type() == x2.scalar_type(),
+                "batchnorm_bwd: dres must match x");
+    a.dres = dres->data_ptr();
+  }
+  a.gamma = opt_f32(gamma, a.C, "batchnorm gamma");
+  a.save_mean = const_cast<float*>(opt_f32(save_mean, a.C, "batchnorm save_mean"));
+  a.save_rstd = const_cast<float*>(opt_f32(save_rstd, a.C, "batchnorm save_rstd"));
+  a.scratch = const_cast<float*>(opt_f32(scratch, 2 * int64_t(a.C), "batchnorm scratch"));
+  c10::cuda::CUDAGuard guard(x2.device());
+  rt::batchnorm_bwd(a, cur_stream(x2.device().index()));
+}
+
 void register_extra_ops(pybind11::module_& m) {
+  m.def("batchnorm_fwd", &batchnorm_fwd, "BatchNorm forward over a channels-last matrix (+residual, +ReLU)");
+  m.def("batchnorm_bwd", &batchnorm_bwd, "BatchNorm backward; scratch returns [dbeta, dgamma]");
+  m.def("ew_binary", &ew_binary, "elementwise binary op (add/sub/mul/div/max/min/pow)");
+  m.def("ew_unary", &ew_unary, "elementwise unary op / activation, forward or backward");
+  m.def("softmax_rows", &softmax_rows, "row softmax / log-softmax forward (dy absent) or backward");
+  m.def("reduce_rows", &reduce_rows, "row reduction over the last dim (sum/mean/max/min/var)");
   m.def("crc64", &crc64_bytes, "CRC-64/XZ of a bytes object");
+  m.def("dequant_f16", &dequant_f16, "expand repacked Q4_0 / Q8_0 weights to dense fp16");
   m.def("q_gemv", &q_gemv, "dequant-fused Q4_0 / Q8_0 matrix-vector product");
   m.def("repack_quant", &repack_quant);
   m.def("rmsnorm_f16", &rmsnorm_f16);

@@ -42,6 +42,7 @@ struct GemmParams {
   int accumulate;  // fp32 only: C += result using red.global.add.f32 (required when split_k > 1)
   int split_k;
   int m_blocks, n_blocks, k_blocks;
+  int ab_fp16;  // A and B are fp16 instead of bf16 (C must then be fp32)
   int* status;
 };
 
@@ -166,7 +167,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16(BLOCK_M, BLOCK_N, A_MN, B_MN, true);
+      const uint32_t idesc = make_idesc_f16(BLOCK_M, BLOCK_N, A_MN, B_MN, !p.ab_fp16);
       uint32_t it = 0;
       uint32_t tile_i = 0;
       bool ok = true;
@@ -404,6 +405,9 @@ void gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
   p.epi_mode = g.epi_mode;
   p.out_fp32 = g.out_fp32;
   p.accumulate = g.accumulate;
+  p.ab_fp16 = g.ab_fp16 ? 1 : 0;
+  RT_CHECK(!g.ab_fp16 || (g.out_fp32 && !g.bias && !g.aux && g.epi_mode == EPI_NONE),
+           "gemm: fp16 operands need an fp32 C and no fused epilogue");
   p.m_blocks = (g.M + BLOCK_M - 1) / BLOCK_M;
   p.n_blocks = (g.N + block_n - 1) / block_n;
   p.k_blocks = (g.K + BLOCK_K - 1) / BLOCK_K;

@@ -44,9 +44,17 @@ __device__ __forceinline__ void expand_q4(const uint4& q, __half2 (&w)[16]) {
   }
 }
 
-__device__ __forceinline__ void expand_q8(const int8_t* q, __half2 (&w)[16]) {
-  const uint4 a = *reinterpret_cast<const uint4*>(q);
-  const uint4 b = *reinterpret_cast<const uint4*>(q + 16);
+// Streaming 16-byte load: the weights are read once per token, so they bypass L1,
+// leaving it to the activations.
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void expand_q8(const uint4& a, const uint4& b, __half2 (&w)[16]) {
   const uint32_t words[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -58,61 +66,120 @@ __device__ __forceinline__ void expand_q8(const int8_t* q, __half2 (&w)[16]) {
 }
 
 // Q8 = false: Q4_0, true: Q8_0.  M rows of x handled together (dequant shared between them).
-template <bool Q8, int M>
-__global__ void __launch_bounds__(256) q_gemv_kernel(const void* __restrict__ qs,
-                                                     const __half* __restrict__ scales,
-                                                     const __half* __restrict__ x, long long ldx,
-                                                     __half* __restrict__ y, long long ldy,
-                                                     const __half* __restrict__ bias,
-                                                     const __half* __restrict__ residual, long long ldr,
-                                                     int N, int K) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (n >= N) return;
-  const int nb = K >> 5;  // blocks per row
-  const __half* drow = scales + (long long)n * nb;
-  float acc[M];
-#pragma unroll
-  for (int m = 0; m < M; ++m) acc[m] = 0.f;
+//
+// Work split: a warp owns R = 4 consecutive output rows and one of S = 4 slices of the K dimension; a CTA
+// of 8 warps therefore covers 8 rows.  The four rows share every activation load (without that, each row
+// re-reads x from L1 and the L1 bandwidth, not HBM, bounds the kernel), the K slices keep enough warps
+// in flight when N is small, and the loads of the next step are issued before the current step is
+// expanded and multiplied.  Slice sums meet in shared memory.
+constexpr int QG_R = 4, QG_S = 4, QG_WARPS = 8;
 
-  for (int b = lane; b < nb; b += 32) {
-    __half2 w[16];
-    if (Q8) {
-      expand_q8(reinterpret_cast<const int8_t*>(qs) + ((long long)n * nb + b) * 32, w);
-    } else {
-      expand_q4(reinterpret_cast<const uint4*>(qs)[(long long)n * nb + b], w);
+template <bool Q8>
+struct QRaw {
+  uint4 v[Q8 ? 2 : 1];
+};
+
+template <bool Q8, int M>
+__global__ void __launch_bounds__(QG_WARPS * 32) q_gemv_kernel(const void* __restrict__ qs,
+                                                               const __half* __restrict__ scales,
+                                                               const __half* __restrict__ x, long long ldx,
+                                                               __half* __restrict__ y, long long ldy,
+                                                               const __half* __restrict__ bias,
+                                                               const __half* __restrict__ residual, long long ldr,
+                                                               int N, int K) {
+  __shared__ float part[QG_WARPS / QG_S][QG_S][QG_R][M];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grp = warp / QG_S, sl = warp % QG_S;
+  const int n0 = (blockIdx.x * (QG_WARPS / QG_S) + grp) * QG_R;
+  const int nb = K >> 5;  // blocks per row
+  const int nbs = (nb + QG_S - 1) / QG_S;
+  const int b_begin = sl * nbs, b_end = min(nb, b_begin + nbs);
+
+  long long rowoff[QG_R];  // block offset of each row (rows past N are clamped; their sums are dropped)
+#pragma unroll
+  for (int r = 0; r < QG_R; ++r) rowoff[r] = (long long)min(n0 + r, N - 1) * nb;
+
+  float acc[QG_R][M];
+#pragma unroll
+  for (int r = 0; r < QG_R; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+
+  auto fetch = [&](int b, QRaw<Q8> (&raw)[QG_R], __half (&d)[QG_R]) {
+#pragma unroll
+    for (int r = 0; r < QG_R; ++r) {
+      const uint4* src = reinterpret_cast<const uint4*>(qs) + (rowoff[r] + b) * (Q8 ? 2 : 1);
+      raw[r].v[0] = ld_stream(src);
+      if (Q8) raw[r].v[Q8 ? 1 : 0] = ld_stream(src + 1);
+      d[r] = scales[rowoff[r] + b];
     }
-    const float d = __half2float(drow[b]);
+  };
+
+  QRaw<Q8> cur[QG_R], nxt[QG_R];
+  __half dcur[QG_R], dnxt[QG_R];
+  int b = b_begin + lane;
+  if (b < b_end) fetch(b, cur, dcur);
+  for (; b < b_end; b += 32) {
+    const bool more = b + 32 < b_end;
+    if (more) fetch(b + 32, nxt, dnxt);
+    __half2 w[QG_R][16];
+#pragma unroll
+    for (int r = 0; r < QG_R; ++r) {
+      if (Q8) expand_q8(cur[r].v[0], cur[r].v[Q8 ? 1 : 0], w[r]);
+      else expand_q4(cur[r].v[0], w[r]);
+    }
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       const uint4* xp = reinterpret_cast<const uint4*>(x + m * ldx + (b << 5));
-      __half2 s = __float2half2_rn(0.f);
+      __half2 xh[16];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint4 xv = __ldg(xp + i);
-        const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+      for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(&xh[4 * i]) = __ldg(xp + i);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) s = __hfma2(w[i * 4 + j], xh[j], s);
+      for (int r = 0; r < QG_R; ++r) {
+        __half2 s0 = __float2half2_rn(0.f), s1 = __float2half2_rn(0.f);
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+          s0 = __hfma2(w[r][j], xh[j], s0);
+          s1 = __hfma2(w[r][j + 1], xh[j + 1], s1);
+        }
+        const float2 f = __half22float2(__hadd2(s0, s1));
+        acc[r][m] = fmaf(__half2float(dcur[r]), f.x + f.y, acc[r][m]);
       }
-      const float2 f = __half22float2(s);
-      acc[m] = fmaf(d, f.x + f.y, acc[m]);
+    }
+    if (more) {
+#pragma unroll
+      for (int r = 0; r < QG_R; ++r) {
+        cur[r] = nxt[r];
+        dcur[r] = dnxt[r];
+      }
     }
   }
 #pragma unroll
-  for (int m = 0; m < M; ++m) {
-    float v = warp_sum_f(acc[m]);
-    if (lane == 0) {
-      if (bias) v += __half2float(bias[n]);
-      if (residual) v += __half2float(residual[m * ldr + n]);
-      y[m * ldy + n] = __float2half(v);
+  for (int r = 0; r < QG_R; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const float v = warp_sum_f(acc[r][m]);
+      if (lane == 0) part[grp][sl][r][m] = v;
     }
+  __syncthreads();
+  // 2 groups x R rows x M activations results per CTA
+  for (int i = threadIdx.x; i < (QG_WARPS / QG_S) * QG_R * M; i += blockDim.x) {
+    const int g = i / (QG_R * M), r = (i / M) % QG_R, m = i % M;
+    const int n = (blockIdx.x * (QG_WARPS / QG_S) + g) * QG_R + r;
+    if (n >= N) continue;
+    float v = 0.f;
+#pragma unroll
+    for (int s2 = 0; s2 < QG_S; ++s2) v += part[g][s2][r][m];
+    if (bias) v += __half2float(bias[n]);
+    if (residual) v += __half2float(residual[m * ldr + n]);
+    y[m * ldy + n] = __float2half(v);
   }
 }
 
 template <bool Q8>
 static void launch_rows(const QGemvArgs& a, int m0, int m, cudaStream_t s) {
-  const int warps = 8;
-  const dim3 grid((a.N + warps - 1) / warps), block(warps * 32);
+  const int rows_per_cta = (QG_WARPS / QG_S) * QG_R;
+  const dim3 grid((a.N + rows_per_cta - 1) / rows_per_cta), block(QG_WARPS * 32);
   const __half* x = reinterpret_cast<const __half*>(a.x) + (long long)m0 * a.ldx;
   __half* y = reinterpret_cast<__half*>(a.y) + (long long)m0 * a.ldy;
   const __half* r = a.residual ? reinterpret_cast<const __half*>(a.residual) + (long long)m0 * a.ldr : nullptr;
@@ -144,6 +211,41 @@ void q_gemv(const QGemvArgs& a, cudaStream_t stream) {
     if (a.q8) launch_rows<true>(a, m0, m, stream);
     else launch_rows<false>(a, m0, m, stream);
   }
+}
+
+// ---------------------------------------------------------------------------- dequantise to fp16
+// Expands repacked weights to a dense fp16 [N][K] matrix: the prefill / large-batch path, where the matrix
+// then feeds the tcgen05 GEMM (the expansion is one pass over 0.56 + 2 bytes per weight, small against a
+// GEMM over hundreds of rows).
+template <bool Q8>
+__global__ void __launch_bounds__(256) dequant_f16_kernel(const void* __restrict__ qs,
+                                                          const __half* __restrict__ scales,
+                                                          __half* __restrict__ out, long long n_blocks) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_blocks) return;
+  __half2 w[16];
+  const uint4* src = reinterpret_cast<const uint4*>(qs) + i * (Q8 ? 2 : 1);
+  if (Q8) expand_q8(ld_stream(src), ld_stream(src + (Q8 ? 1 : 0)), w);
+  else expand_q4(ld_stream(src), w);
+  const __half2 d = __half2half2(scales[i]);
+  uint4* dst = reinterpret_cast<uint4*>(out + i * 32);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    __half2 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __hmul2(w[q * 4 + j], d);
+    dst[q] = *reinterpret_cast<const uint4*>(v);
+  }
+}
+
+void dequant_f16(const void* qs, const void* scales, void* out, long long n_blocks, bool q8, cudaStream_t s) {
+  if (n_blocks == 0) return;
+  const unsigned grid = (unsigned)((n_blocks + 255) / 256);
+  if (q8) dequant_f16_kernel<true><<<grid, 256, 0, s>>>(qs, reinterpret_cast<const __half*>(scales),
+                                                      reinterpret_cast<__half*>(out), n_blocks);
+  else dequant_f16_kernel<false><<<grid, 256, 0, s>>>(qs, reinterpret_cast<const __half*>(scales),
+                                                      reinterpret_cast<__half*>(out), n_blocks);
+  RT_LAUNCH_CHECK();
 }
 
 // ---------------------------------------------------------------------------- repack

@@ -76,6 +76,11 @@ class KVCache:
         return sum(t.numel() * t.element_size() for t in self.k + self.v)
 
 
+class _DecodeGraph:
+    """Static device tensors and the captured graph of one decode step."""
+    tok = pos = seq = step = out = logits = graph = None
+
+
 class _Layer:
     __slots__ = ("attn_norm", "wqkv", "wo", "ffn_norm", "w_gate_up", "w_down")
 
@@ -236,9 +241,8 @@ class LlamaRuntime:
             k = qkv[:, H * D: (H + Hkv) * D].view(n, Hkv, D)
             v = qkv[:, (H + Hkv) * D:].view(n, Hkv, D)
             if C is not None:
-                q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
                 C.rope_kv(q, k, v, cache.k[li], cache.v[li], pos32, seq32, cfg.rope_theta, cfg.rope_interleaved)
-                att = torch.empty_like(q)
+                att = torch.empty((n, H, D), dtype=q.dtype, device=q.device)
                 C.attn_cache(q, cache.k[li], cache.v[li], att, kv_len, seq32, max_kv, scale)
             else:
                 q, k = self._rope_reference(q, pos), self._rope_reference(k, pos)
@@ -296,6 +300,70 @@ class LlamaRuntime:
         logits = self.forward_tokens(tokens.to(dev), pos, seq, cache, max_kv=max(cache.lengths) + 1)
         cache.lengths = [l + 1 for l in cache.lengths]
         return logits
+
+    # ----------------------------------------------------------- CUDA-graph decode
+    @torch.no_grad()
+    def capture_decode_graph(self, cache: KVCache, batch: int) -> "_DecodeGraph":
+        """Captures one greedy decode step (all layers, lm_head, argmax, position increment) into a CUDA
+        graph whose inputs live on the device: a step is then one graph launch, and the ~10 launches per
+        layer no longer pay host latency.  Positions and the current tokens are device tensors that the graph
+        itself advances, so replaying it N times generates N tokens without any host round trip."""
+        dev = self.device
+        g = _DecodeGraph()
+        g.tok = torch.zeros(batch, dtype=torch.long, device=dev)
+        g.pos = torch.zeros(batch, dtype=torch.int32, device=dev)
+        g.seq = torch.arange(batch, dtype=torch.int32, device=dev)
+        g.step = torch.zeros(1, dtype=torch.long, device=dev)
+        g.out = torch.zeros(batch, cache.max_len, dtype=torch.long, device=dev)
+
+        def body():
+            logits = self.forward_tokens(g.tok, g.pos, g.seq, cache, max_kv=cache.max_len)
+            nxt = logits.argmax(-1)
+            g.out.scatter_(1, g.step.view(1, 1).expand(batch, 1), nxt.view(batch, 1))
+            g.tok.copy_(nxt)
+            g.pos.add_(1)
+            g.step.add_(1)
+            return logits
+
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):                     # warm-up outside capture (lazy inits, scratch growth)
+            body()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        g.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g.graph):
+            g.logits = body()
+        return g
+
+    @torch.no_grad()
+    def generate_graph(self, prompts: torch.Tensor, max_new_tokens: int, cache: Optional[KVCache] = None
+                       ) -> Tuple[torch.Tensor, Dict[str, float]]:
+        """Greedy generation with the decode loop replayed from a CUDA graph (single process or TP ranks that
+        all call it together).  Same outputs as ``generate`` without a sampler."""
+        B, T = prompts.shape
+        cache = cache or self.new_cache(B, T + max_new_tokens)
+        dev = self.device
+        g = self.capture_decode_graph(cache, B)           # the warm-up/capture writes only at position 0.. (reset below)
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        logits = self.prefill(prompts, cache)
+        nxt = logits.argmax(-1)
+        g.tok.copy_(nxt)
+        g.pos.fill_(T)
+        g.step.zero_()
+        torch.cuda.synchronize(dev)
+        ttft = time.perf_counter() - t0
+        t1 = time.perf_counter()
+        steps = max_new_tokens - 1
+        for _ in range(steps):
+            g.graph.replay()
+        torch.cuda.synchronize(dev)
+        dt = time.perf_counter() - t1
+        cache.lengths = [T + steps] * B
+        toks = torch.cat([prompts.to(dev), nxt.view(B, 1), g.out[:, :steps]], 1)
+        return toks, {"ttft_s": ttft, "decode_tokens_per_s": B * steps / dt if dt > 0 and steps else 0.0,
+                      "decode_steps": steps, "batch": B}
 
     @torch.no_grad()
     def generate(self, prompts: torch.Tensor, max_new_tokens: int, sampler=None, eos_token: Optional[int] = None,

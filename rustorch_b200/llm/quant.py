@@ -62,6 +62,21 @@ class QuantLinear:
         return cls(blocks, ggml_type, dev)
 
     # ------------------------------------------------------------------ compute
+    # From this many activation rows on, expanding the weights (0.56 B read + 2 B written + 2 B re-read per
+    # weight) costs less than re-streaming the quantised matrix once per 8 rows through the GEMV kernel.
+    GEMM_MIN_ROWS = 64
+    _scratch_buf = {}
+
+    def _scratch(self, numel: int) -> torch.Tensor:
+        """One fp16 expansion buffer per device, grown to the largest matrix seen (kernels on one stream run in
+        order, so consecutive layers can share it)."""
+        key = (self.device.type, self.device.index)
+        buf = QuantLinear._scratch_buf.get(key)
+        if buf is None or buf.numel() < numel:
+            buf = torch.empty(numel, dtype=torch.float16, device=self.device)
+            QuantLinear._scratch_buf[key] = buf
+        return buf[:numel]
+
     def dequantize(self) -> torch.Tensor:
         """fp32 ``[out, in]`` weights (decoded from the stored representation)."""
         if self.blocks is not None:
@@ -86,9 +101,19 @@ class QuantLinear:
         if self.device.type == "cuda":
             C = _native.load(required=True)
             x2 = x2.to(torch.float16).contiguous()
-            y = torch.empty((x2.shape[0], self.out_features), dtype=torch.float16, device=self.device)
             r = residual.reshape(-1, self.out_features) if residual is not None else None
-            C.q_gemv(self.qs, self.scales, x2, y, None, r, self.q8)
+            if x2.shape[0] >= self.GEMM_MIN_ROWS:
+                # prefill / large batch: expand once to fp16 scratch, then the tcgen05 GEMM (fp32 accumulate + output)
+                w = self._scratch(self.out_features * self.in_features).view(self.out_features, self.in_features)
+                C.dequant_f16(self.qs, self.scales, w, self.q8)
+                acc = torch.empty((x2.shape[0], self.out_features), dtype=torch.float32, device=self.device)
+                C.gemm(x2, False, w, False, acc, None, None, 0, 1.0, False, 1, 0)
+                if r is not None:
+                    acc += r
+                y = acc.to(torch.float16)
+            else:
+                y = torch.empty((x2.shape[0], self.out_features), dtype=torch.float16, device=self.device)
+                C.q_gemv(self.qs, self.scales, x2, y, None, r, self.q8)
         else:
             y = x2.float() @ self.dequantize().t()
             if residual is not None:

@@ -170,6 +170,19 @@ class _BatchNorm(nn.modules.batchnorm._BatchNorm):
                  track_running_stats: bool = True, device=None, dtype=None):
         super().__init__(num_features, eps, momentum, affine, track_running_stats, device=device, dtype=dtype)
 
+    def forward(self, x, residual=None, relu: bool = False):
+        """``relu(bn(x) + residual)`` when the optional arguments are given (the ResNet block tail, fused)."""
+        self._check_input_dim(x)
+        from ..ops.batchnorm import batch_norm
+        momentum = 0.0 if self.momentum is None else self.momentum
+        if self.training and self.track_running_stats and self.num_batches_tracked is not None:
+            self.num_batches_tracked.add_(1)
+            if self.momentum is None:
+                momentum = 1.0 / float(self.num_batches_tracked)
+        rm = self.running_mean if (not self.training or self.track_running_stats) else None
+        rv = self.running_var if (not self.training or self.track_running_stats) else None
+        return batch_norm(x, rm, rv, self.weight, self.bias, self.training or rm is None, momentum, self.eps, residual, relu)
+
     def is_training(self) -> bool:
         return self.training
 
@@ -372,54 +385,75 @@ class AdaptiveMaxPool2d(nn.AdaptiveMaxPool2d):
 
 
 # -------------------------------------------------------------------- activations
+# On CUDA floating tensors these launch the native elementwise / softmax kernels (forward and backward);
+# elsewhere they are the PyTorch expression of the same function.
+from ..ops import elementwise as _ew  # noqa: E402
+
+
 def relu(x):
-    return F.relu(x)
+    return _ew.unary("relu", x)
 
 
 def sigmoid(x):
-    return torch.sigmoid(x)
+    return _ew.unary("sigmoid", x)
 
 
 def tanh(x):
-    return torch.tanh(x)
+    return _ew.unary("tanh", x)
 
 
 def leaky_relu(x, negative_slope: float = 0.01):
-    return F.leaky_relu(x, negative_slope)
+    return _ew.unary("leaky_relu", x, negative_slope)
 
 
 def softmax(x, dim: int = -1):
     """Row-wise softmax over ``dim`` (the reference's attention normalises over the whole
     tensor by mistake, src/nn/attention.rs:362-384)."""
-    return F.softmax(x, dim)
+    return _ew.softmax(x, dim)
+
+
+def log_softmax(x, dim: int = -1):
+    return _ew.log_softmax(x, dim)
 
 
 def gelu(x):
     """tanh approximation, as the reference (src/nn/activation.rs:206-217)."""
-    return F.gelu(x, approximate="tanh")
+    return _ew.unary("gelu_tanh", x)
 
 
 def swish(x):
-    return F.silu(x)
+    return _ew.unary("silu", x)
 
 
 silu = swish
 
 
 def elu(x, alpha: float = 1.0):
-    return F.elu(x, alpha)
+    return _ew.unary("elu", x, alpha)
 
 
 def selu(x):
-    return F.selu(x)
+    return _ew.unary("selu", x)
 
 
 def mish(x):
-    return F.mish(x)
+    return _ew.unary("mish", x)
 
 
 def hardswish(x):
-    return F.hardswish(x)
+    return _ew.unary("hardswish", x)
+
+
+def softplus(x, beta: float = 1.0, threshold: float = 20.0):
+    return _ew.unary("softplus", x, beta, threshold)
+
+
+def relu6(x):
+    return _ew.unary("relu6", x)
+
+
+def hardsigmoid(x):
+    return _ew.unary("hardsigmoid", x)
 
 
 def glu(x, dim: int = -1):
@@ -443,24 +477,39 @@ def reglu(x, dim: int = -1):
 
 
 class ReLU(nn.ReLU):
-    pass
+    def forward(self, x):
+        return relu(x)
 
 
 class Sigmoid(nn.Sigmoid):
-    pass
+    def forward(self, x):
+        return sigmoid(x)
 
 
 class Tanh(nn.Tanh):
-    pass
+    def forward(self, x):
+        return tanh(x)
 
 
 class LeakyReLU(nn.LeakyReLU):
-    pass
+    def forward(self, x):
+        return leaky_relu(x, self.negative_slope)
 
 
 class Softmax(nn.Softmax):
     def __init__(self, dim: int = -1):
         super().__init__(dim)
+
+    def forward(self, x):
+        return softmax(x, self.dim)
+
+
+class LogSoftmax(nn.LogSoftmax):
+    def __init__(self, dim: int = -1):
+        super().__init__(dim)
+
+    def forward(self, x):
+        return log_softmax(x, self.dim)
 
 
 class GELU(nn.Module):
@@ -469,7 +518,8 @@ class GELU(nn.Module):
 
 
 class Swish(nn.SiLU):
-    pass
+    def forward(self, x):
+        return swish(x)
 
 
 class GLU(nn.GLU):
@@ -477,16 +527,25 @@ class GLU(nn.GLU):
 
 
 class ELU(nn.ELU):
-    pass
+    def forward(self, x):
+        return elu(x, self.alpha)
 
 
 class SELU(nn.SELU):
-    pass
+    def forward(self, x):
+        return selu(x)
 
 
 class Mish(nn.Mish):
-    pass
+    def forward(self, x):
+        return mish(x)
 
 
 class Hardswish(nn.Hardswish):
-    pass
+    def forward(self, x):
+        return hardswish(x)
+
+
+class Softplus(nn.Softplus):
+    def forward(self, x):
+        return softplus(x, self.beta, self.threshold)

@@ -87,3 +87,55 @@ def test_runtime_gpu_matches_cpu_path(gqa):
     assert rel_err(cg.k[1][:, :, :10].float().cpu(), cc.k[1][:, :, :10]) < 2e-2
     out, stats = gpu.generate(prompt, 6)
     assert out.shape == (2, 15) and stats["decode_tokens_per_s"] > 0
+
+
+@pytest.mark.parametrize("D,H,Hkv", [(128, 8, 2), (64, 4, 4), (128, 16, 2), (256, 2, 1), (96, 4, 4)])
+def test_cached_attention_split_kv_vs_reference(D, H, Hkv):
+    """Split-KV decode attention (several key slices + merge) and the generic fallback (D = 96)."""
+    from rustorch_b200 import _native
+    C = _native.load(required=True)
+    torch.manual_seed(1)
+    B, T_max = 3, 1024
+    ck = torch.randn(B, Hkv, T_max, D, device="cuda").half()
+    cv = torch.randn(B, Hkv, T_max, D, device="cuda").half()
+    kv_len = torch.tensor([700, 1, 130, 64, 1024], dtype=torch.int32, device="cuda")
+    seq = torch.tensor([0, 1, 2, 1, 0], dtype=torch.int32, device="cuda")
+    n = kv_len.numel()
+    qkv = torch.randn(n, (H + 3) * D, device="cuda").half()          # q is a strided view, as in the runtime
+    q = qkv[:, : H * D].view(n, H, D)
+    out = torch.empty(n, H, D, device="cuda", dtype=torch.half)
+    scale = 1.0 / math.sqrt(D)
+    C.attn_cache(q, ck, cv, out, kv_len, seq, T_max, scale)
+    for t in range(n):
+        L, s = int(kv_len[t]), int(seq[t])
+        k = ck[s, :, :L].float().repeat_interleave(H // Hkv, 0)
+        v = cv[s, :, :L].float().repeat_interleave(H // Hkv, 0)
+        p = torch.softmax((k @ q[t].float().unsqueeze(-1)).squeeze(-1) * scale, -1)
+        ref = (p.unsqueeze(1) @ v).squeeze(1)
+        assert rel_err(out[t], ref) < 3e-3, (t, L)
+
+
+@pytest.mark.parametrize("q8", [False, True])
+def test_quant_linear_gemm_path_for_many_rows(q8):
+    """From 64 rows on the weights are expanded to fp16 and multiplied on the tcgen05 GEMM."""
+    from rustorch_b200.formats import gguf
+    from rustorch_b200.llm import QuantLinear
+    q = QuantLinear.random(1000, 1024, gguf.GGMLType.Q8_0 if q8 else gguf.GGMLType.Q4_0, 0.02, "cuda", seed=2)
+    x = (torch.randn(200, 1024, device="cuda") * 0.5).half()
+    res = torch.randn(200, 1000, device="cuda").half()
+    assert x.shape[0] >= QuantLinear.GEMM_MIN_ROWS
+    y = q(x, residual=res)
+    ref = x.float() @ q.dequantize().t() + res.float()
+    assert rel_err(y, ref) < 3e-3
+    from rustorch_b200 import _native
+    _native.check_status()
+
+
+def test_graph_decode_matches_eager_decode():
+    from rustorch_b200.llm import LlamaConfig, LlamaRuntime
+    cfg = LlamaConfig(vocab_size=256, n_layer=2, n_embd=256, n_head=4, n_head_kv=2, n_ff=512, context_length=128)
+    rt_ = LlamaRuntime.random_init(cfg, "cuda", seed=5, std=0.08)
+    prompt = torch.randint(0, 256, (2, 70), generator=torch.Generator().manual_seed(1))
+    a, _ = rt_.generate(prompt, 12)
+    b, stats = rt_.generate_graph(prompt, 12)
+    assert torch.equal(a, b) and stats["decode_steps"] == 11
