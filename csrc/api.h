@@ -200,8 +200,12 @@ struct QGemvArgs {
   long long ldr;
   int M, N, K;
   bool q8;  // false: Q4_0, true: Q8_0
+  bool force_register_path = false;  // skip the bulk-copy kernel (tests and comparisons)
 };
 void q_gemv(const QGemvArgs& a, cudaStream_t stream);
+// quant/q_gemv_bulk.cu: bulk-copy (TMA engine) fed variant; q_gemv() uses it when the shape allows (K % 256 == 0).
+bool q_gemv_bulk_supported(const QGemvArgs& a);
+void q_gemv_bulk(const QGemvArgs& a, cudaStream_t stream);
 void dequant_f16(const void* qs, const void* scales, void* out, long long n_blocks, bool q8, cudaStream_t s);
 void repack_q4_0(const void* blocks, void* qs, void* scales, long long n_blocks, cudaStream_t s);
 void repack_q8_0(const void* blocks, void* qs, void* scales, long long n_blocks, cudaStream_t s);

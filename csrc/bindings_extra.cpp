@@ -76,7 +76,7 @@ void check_f16(const Tensor& t, const char* name) {
 
 // y[M, N] = dequant(W)[N, K] @ x[M, K]^T (+bias) (+residual); qs / scales are the repacked device layout.
 void q_gemv(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, const c10::optional<Tensor>& bias,
-            const c10::optional<Tensor>& residual, bool q8) {
+            const c10::optional<Tensor>& residual, bool q8, bool register_path) {
   check_f16(scales, "q_gemv scales");
   check_f16(x, "q_gemv x");
   check_f16(y, "q_gemv y");
@@ -106,6 +106,7 @@ void q_gemv(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, 
     a.ldr = residual->stride(0);
   }
   a.q8 = q8;
+  a.force_register_path = register_path;
   rt::q_gemv(a, cur_stream(x.device().index()));
 }
 
@@ -391,7 +392,9 @@ void register_extra_ops(pybind11::module_& m) {
   m.def("reduce_rows", &reduce_rows, "row reduction over the last dim (sum/mean/max/min/var)");
   m.def("crc64", &crc64_bytes, "CRC-64/XZ of a bytes object");
   m.def("dequant_f16", &dequant_f16, "expand repacked Q4_0 / Q8_0 weights to dense fp16");
-  m.def("q_gemv", &q_gemv, "dequant-fused Q4_0 / Q8_0 matrix-vector product");
+  m.def("q_gemv", &q_gemv, "dequant-fused Q4_0 / Q8_0 matrix-vector product", pybind11::arg("qs"), pybind11::arg("scales"),
+        pybind11::arg("x"), pybind11::arg("y"), pybind11::arg("bias"), pybind11::arg("residual"), pybind11::arg("q8"),
+        pybind11::arg("register_path") = false);
   m.def("repack_quant", &repack_quant);
   m.def("rmsnorm_f16", &rmsnorm_f16);
   m.def("rope_kv", &rope_kv);

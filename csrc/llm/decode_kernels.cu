@@ -11,6 +11,9 @@
 // KVCache struct is unused (model/transformer.rs:221-270).
 #include <cuda_fp16.h>
 
+#include <algorithm>
+#include <cmath>
+
 #include "../api.h"
 #include "../common/launch.h"
 
@@ -57,37 +60,41 @@ __global__ void rmsnorm_f16_kernel(const __half* __restrict__ x, const __half* _
 
 // q: [n_tok][H][D], k/v: [n_tok][Hkv][D] (rows of the fused qkv output, strides in halves).
 // cache_k / cache_v: [B][Hkv][T_max][D].  Token t belongs to sequence seq[t] at position pos[t].
+// grid (n_tok, H + 2 Hkv): blockIdx.y selects a q head, a k head (rotated and appended to the cache) or a
+// v head (appended).  One thread per rotation pair; a token with one CTA per head keeps the step short
+// for decode, where n_tok is the batch size.
 __global__ void rope_kv_f16_kernel(__half* __restrict__ q, long long q_st, __half* __restrict__ k,
                                    long long k_st, const __half* __restrict__ v, long long v_st,
                                    __half* __restrict__ cache_k, __half* __restrict__ cache_v,
                                    const int* __restrict__ pos, const int* __restrict__ seq, int H, int Hkv,
-                                   int D, int T_max, float theta_base, int interleaved) {
-  const int t = blockIdx.x;
+                                   int D, int T_max, float log2_theta, int interleaved) {
+  const int t = blockIdx.x, hy = blockIdx.y;
   const int p = pos[t], s = seq[t];
   const int half_d = D >> 1;
-  const int pairs_q = H * half_d, pairs_k = Hkv * half_d;
-  for (int i = threadIdx.x; i < pairs_q + pairs_k; i += blockDim.x) {
-    const bool is_q = i < pairs_q;
-    const int j = is_q ? i : i - pairs_q;
-    const int h = j / half_d, d = j % half_d;
-    const float inv_freq = __powf(theta_base, -2.f * d / D);
+  if (hy >= H + Hkv) {  // v head: plain append
+    const int h = hy - H - Hkv;
+    const __half2* src = reinterpret_cast<const __half2*>(v + t * v_st + h * D);
+    __half2* dst = reinterpret_cast<__half2*>(cache_v + (((long long)s * Hkv + h) * T_max + p) * D);
+    for (int d = threadIdx.x; d < half_d; d += blockDim.x) dst[d] = src[d];
+    return;
+  }
+  const bool is_q = hy < H;
+  const int h = is_q ? hy : hy - H;
+  __half* base = is_q ? q + t * q_st + h * D : k + t * k_st + h * D;
+  __half* ck = is_q ? nullptr : cache_k + (((long long)s * Hkv + h) * T_max + p) * D;
+  for (int d = threadIdx.x; d < half_d; d += blockDim.x) {
+    const float inv_freq = exp2f(-2.f * (float)d / (float)D * log2_theta);
     float sn, cs;
-    __sincosf(p * inv_freq, &sn, &cs);
-    __half* base = is_q ? q + t * q_st + h * D : k + t * k_st + h * D;
+    sincosf((float)p * inv_freq, &sn, &cs);
     const int ia = interleaved ? 2 * d : d, ib = interleaved ? 2 * d + 1 : d + half_d;
     const float a = __half2float(base[ia]), b = __half2float(base[ib]);
-    const float ra = a * cs - b * sn, rb = a * sn + b * cs;
-    base[ia] = __float2half(ra);
-    base[ib] = __float2half(rb);
-    if (!is_q) {
-      __half* ck = cache_k + (((long long)s * Hkv + h) * T_max + p) * D;
-      ck[ia] = __float2half(ra);
-      ck[ib] = __float2half(rb);
+    const __half ra = __float2half(a * cs - b * sn), rb = __float2half(a * sn + b * cs);
+    base[ia] = ra;
+    base[ib] = rb;
+    if (ck) {
+      ck[ia] = ra;
+      ck[ib] = rb;
     }
-  }
-  for (int i = threadIdx.x; i < Hkv * D; i += blockDim.x) {
-    const int h = i / D, d = i % D;
-    cache_v[(((long long)s * Hkv + h) * T_max + p) * D + d] = v[t * v_st + h * D + d];
   }
 }
 
@@ -179,10 +186,11 @@ void rmsnorm_f16(const void* x, const void* w, void* y, long long rows, int C, f
 void rope_kv_f16(const RopeKvArgs& a, cudaStream_t s) {
   RT_CHECK(a.D % 2 == 0, "rope: head_dim must be even");
   if (a.n_tok == 0) return;
-  rope_kv_f16_kernel<<<a.n_tok, 256, 0, s>>>(reinterpret_cast<__half*>(a.q), a.q_st, reinterpret_cast<__half*>(a.k),
-                                             a.k_st, reinterpret_cast<const __half*>(a.v), a.v_st,
-                                             reinterpret_cast<__half*>(a.cache_k), reinterpret_cast<__half*>(a.cache_v),
-                                             a.pos, a.seq, a.H, a.Hkv, a.D, a.T_max, a.theta, a.interleaved);
+  const int threads = std::min(128, std::max(32, ((a.D / 2 + 31) / 32) * 32));
+  rope_kv_f16_kernel<<<dim3(a.n_tok, a.H + 2 * a.Hkv), threads, 0, s>>>(
+      reinterpret_cast<__half*>(a.q), a.q_st, reinterpret_cast<__half*>(a.k), a.k_st, reinterpret_cast<const __half*>(a.v),
+      a.v_st, reinterpret_cast<__half*>(a.cache_k), reinterpret_cast<__half*>(a.cache_v), a.pos, a.seq, a.H, a.Hkv, a.D,
+      a.T_max, log2f(a.theta), a.interleaved);
   RT_LAUNCH_CHECK();
 }
 

@@ -21,49 +21,9 @@
 
 #include "../api.h"
 #include "../common/launch.h"
+#include "q_expand.cuh"
 
 namespace rt {
-
-__device__ __forceinline__ float warp_sum_f(float v) {
-#pragma unroll
-  for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
-  return v;
-}
-
-// Expand one repacked Q4_0 block (4 words) into 16 half2 of (q - 8).
-__device__ __forceinline__ void expand_q4(const uint4& q, __half2 (&w)[16]) {
-  const uint32_t words[4] = {q.x, q.y, q.z, q.w};
-  const __half2 bias = __half2half2(__ushort_as_half(0x6408));  // 1032
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t bits = ((words[i] >> (4 * j)) & 0x000F000Fu) | 0x64006400u;
-      w[i * 4 + j] = __hsub2(*reinterpret_cast<const __half2*>(&bits), bias);
-    }
-  }
-}
-
-// Streaming 16-byte load: the weights are read once per token, so they bypass L1,
-// leaving it to the activations.
-__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-
-__device__ __forceinline__ void expand_q8(const uint4& a, const uint4& b, __half2 (&w)[16]) {
-  const uint32_t words[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int v0 = (int)(int8_t)(words[i] & 0xFF), v1 = (int)(int8_t)((words[i] >> 8) & 0xFF);
-    const int v2 = (int)(int8_t)((words[i] >> 16) & 0xFF), v3 = (int)(int8_t)(words[i] >> 24);
-    w[2 * i] = __halves2half2(__int2half_rn(v0), __int2half_rn(v1));
-    w[2 * i + 1] = __halves2half2(__int2half_rn(v2), __int2half_rn(v3));
-  }
-}
 
 // Q8 = false: Q4_0, true: Q8_0.  M rows of x handled together (dequant shared between them).
 //
@@ -206,6 +166,10 @@ void q_gemv(const QGemvArgs& a, cudaStream_t stream) {
   RT_CHECK((reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.qs) & 15) == 0,
            "q_gemv: x and qs must be 16-byte aligned");
   if (a.M == 0 || a.N == 0) return;
+  if (!a.force_register_path && q_gemv_bulk_supported(a)) {
+    q_gemv_bulk(a, stream);
+    return;
+  }
   for (int m0 = 0; m0 < a.M; m0 += 8) {
     const int m = std::min(8, a.M - m0);
     if (a.q8) launch_rows<true>(a, m0, m, stream);

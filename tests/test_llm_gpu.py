@@ -139,3 +139,21 @@ def test_graph_decode_matches_eager_decode():
     a, _ = rt_.generate(prompt, 12)
     b, stats = rt_.generate_graph(prompt, 12)
     assert torch.equal(a, b) and stats["decode_steps"] == 11
+
+
+@pytest.mark.parametrize("q8", [False, True])
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (2, 1001, 11008), (4, 70, 256), (7, 515, 2048)])
+def test_q_gemv_register_and_bulk_paths_agree(q8, M, N, K):
+    """The bulk-copy (shared-memory ring) kernel and the register-fed kernel compute the same product."""
+    from rustorch_b200 import _native
+    from rustorch_b200.formats import gguf
+    from rustorch_b200.llm import QuantLinear
+    C = _native.load(required=True)
+    q = QuantLinear.random(N, K, gguf.GGMLType.Q8_0 if q8 else gguf.GGMLType.Q4_0, 0.02, "cuda", seed=4)
+    x = (torch.randn(M, K, device="cuda") * 0.5).half()
+    ya, yb = torch.empty(M, N, device="cuda", dtype=torch.half), torch.empty(M, N, device="cuda", dtype=torch.half)
+    C.q_gemv(q.qs, q.scales, x, ya, None, None, q.q8, register_path=False)
+    C.q_gemv(q.qs, q.scales, x, yb, None, None, q.q8, register_path=True)
+    ref = x.float() @ q.dequantize().t()
+    assert rel_err(ya, ref) < 6e-3 and rel_err(yb, ref) < 6e-3
+    _native.check_status()
