@@ -164,6 +164,30 @@ def bench_ce(a):
     report(f"cross_entropy_{rows}x{V}", best, med, bytes_=4.0 * rows * ld)
 
 
+def bench_qgemv(a):
+    """Q4_0 dequant-fused GEMV at the llama-7B decode shapes, register-fed vs bulk-copy-fed kernel.  Each timed
+    region walks enough distinct weight matrices (> 300 MB) that none of them is served from L2."""
+    from rustorch_b200 import _native
+    from rustorch_b200.formats import gguf
+    from rustorch_b200.llm import QuantLinear
+    C = _native.load(required=True)
+    for (N, Kd) in [(12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008), (32000, 4096)]:
+        nbytes = N * Kd // 32 * 18
+        copies = max(2, -(-300_000_000 // nbytes))
+        mats = [QuantLinear.random(N, Kd, gguf.GGMLType.Q4_0, 0.02, "cuda", seed=i) for i in range(copies)]
+        for M in (1, 4):
+            x = (torch.randn(M, Kd, device="cuda") * 0.5).half()
+            y = torch.empty(M, N, device="cuda", dtype=torch.half)
+            for reg in (True, False):
+                def run():
+                    for q in mats:
+                        C.q_gemv(q.qs, q.scales, x, y, None, None, False, register_path=reg)
+                best, med = time_op(run, a.iters, flush=False)
+                report(f"q4_gemv_{'register' if reg else 'bulk'}_m{M}_{N}x{Kd}", best / copies, med / copies, bytes_=float(nbytes),
+                       extra=f"mean over {copies} distinct matrices per timed region")
+        del mats
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", default="all")
@@ -196,6 +220,8 @@ def main():
         bench_adamw(a)
     elif a.op == "ce":
         bench_ce(a)
+    elif a.op == "qgemv":
+        bench_qgemv(a)
     elif a.op == "all":
         a.compare = True
         for (m, n, k, lay, sk) in [(8192, 8192, 8192, "nt", 1), (16384, 2304, 768, "nt", 1),

@@ -134,4 +134,23 @@ CUtensorMap make_tmap_2byte_4d(const void* base, uint64_t d0, uint64_t d1, uint6
   return m;
 }
 
+CUtensorMap make_tmap_rows(const void* base, int elem_bytes, uint64_t row_elems, uint64_t rows,
+                           uint32_t box_elems, uint32_t box_rows) {
+  RT_CHECK(elem_bytes == 2 || elem_bytes == 4, "make_tmap_rows: 2- or 4-byte elements");
+  RT_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base must be 16-byte aligned");
+  RT_CHECK((row_elems * elem_bytes) % 16 == 0, "TMA row pitch must be a multiple of 16 bytes");
+  RT_CHECK(box_elems <= 256 && box_rows <= 256 && (box_elems * elem_bytes) % 16 == 0, "TMA box out of range");
+  CUtensorMap m;
+  cuuint64_t dims[2] = {row_elems, rows};
+  cuuint64_t strides[1] = {row_elems * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {box_elems, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode_fn()(&m, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2,
+                           const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  RT_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(rows) failed with code " + std::to_string(int(r)));
+  return m;
+}
+
 }  // namespace rt

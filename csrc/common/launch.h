@@ -55,5 +55,10 @@ CUtensorMap make_tmap_2byte(const void* base, uint64_t d0, uint64_t d1, uint64_t
 CUtensorMap make_tmap_2byte_4d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                                uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3, uint32_t b0,
                                uint32_t b1);
+// Plain (unswizzled) rank-2 map over rows of `row_bytes` bytes seen as 32-bit words (elem_bytes = 4) or
+// 16-bit values (elem_bytes = 2): dims {row_elems, rows}, box {box_elems, box_rows}; out-of-range parts of a
+// box read as zero.  row_bytes must be a multiple of 16.
+CUtensorMap make_tmap_rows(const void* base, int elem_bytes, uint64_t row_elems, uint64_t rows,
+                           uint32_t box_elems, uint32_t box_rows);
 
 }  // namespace rt

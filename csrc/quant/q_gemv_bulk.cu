@@ -2,8 +2,9 @@
 //
 // Same math and device layout as q_gemv.cu.  The difference is how the weights reach the SM: a producer
 // warp streams tiles of 32 output rows x 32 quant blocks (1024 weights per row) into a shared-memory ring
-// with `cp.async.bulk` (one contiguous copy per row for the nibbles, one for the scales) that completes
-// on an mbarrier, and eight consumer warps (four rows each) expand and multiply out of shared memory.
+// with two tiled TMA loads per stage (`cp.async.bulk.tensor.2d`: the nibbles as a 32-row box of 32-bit
+// words, the scales as a 32 x 32 box of halves; per-row 1-D bulk copies were tried first and were bound by
+// the copy engine's request rate) that complete on an mbarrier, and eight consumer warps (four rows each) expand and multiply out of shared memory.
 // With 6 stages of 18 KB in flight per CTA and two CTAs per SM, about 200 KB per SM is always on its way
 // from HBM regardless of what the consumer warps are doing, which is what a latency-bound register-fed
 // GEMV (one or two 16-byte loads per lane in flight) cannot reach.  CTAs are persistent over row tiles.
@@ -12,8 +13,9 @@
 // word, the producer stops issuing and waits for the copies it has in flight, and every role falls
 // through to the common exit.
 //
-// Requirements: K a multiple of 256 (so that a row slice of scales is a 16-byte multiple) and 16-byte
-// aligned x rows; other shapes take the register-fed kernel.
+// Requirements: K a multiple of 256 (so that a row of scales is a 16-byte multiple, which a tensor map
+// needs) and 16-byte aligned x rows; other shapes take the register-fed kernel.  Boxes that reach past
+// the last row or the last block read as zero and still count their full size on the mbarrier.
 #include <cuda_fp16.h>
 
 #include "../api.h"
@@ -25,38 +27,42 @@ namespace rt {
 
 namespace {
 
-constexpr int QB_ROWS = 32;    // output rows per tile
 constexpr int QB_KB = 32;      // quant blocks per tile and row (one per consumer lane)
-constexpr int QB_CONS = 8;     // consumer warps; each owns QB_ROWS / QB_CONS = 4 rows
-constexpr int QB_RPW = QB_ROWS / QB_CONS;
+constexpr int QB_CONS = 8;     // consumer warps; each owns RPW rows of a tile of QB_CONS * RPW rows
 constexpr int QB_THREADS = (QB_CONS + 1) * 32;
 
-template <bool Q8>
+// RPW = rows per consumer warp: 4 (32-row tiles) for large N; 2 or 1 when N alone would give too few tiles
+// to occupy the SMs (the activation loads are then shared by fewer rows, which only matters for M > 1).
+template <bool Q8, int RPW>
 struct QbCfg {
+  static constexpr int ROWS = QB_CONS * RPW;
   static constexpr int BQ = Q8 ? 32 : 16;                         // quant bytes per block
-  static constexpr int Q_BYTES = QB_ROWS * QB_KB * BQ;            // 16 KB / 32 KB
-  static constexpr int S_BYTES = QB_ROWS * QB_KB * 2;             // 2 KB
+  static constexpr int Q_BYTES = ROWS * QB_KB * BQ;               // 16 KB / 32 KB at 32 rows
+  static constexpr int S_BYTES = ROWS * QB_KB * 2;                // 2 KB at 32 rows
   static constexpr int STAGE_BYTES = Q_BYTES + S_BYTES;
-  static constexpr int STAGES = Q8 ? 4 : 6;
+  static constexpr int STAGES = (Q8 && RPW == 4) ? 4 : 6;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 2 * STAGES * 8 + 16;
 };
 
-__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(smem_dst)),
-               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
 }
 
-template <bool Q8, int M>
-__global__ void __launch_bounds__(QB_THREADS) q_gemv_bulk_kernel(const uint8_t* __restrict__ qs,
-                                                                 const __half* __restrict__ scales,
+template <bool Q8, int M, int RPW>
+__global__ void __launch_bounds__(QB_THREADS) q_gemv_bulk_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                                                                 const __grid_constant__ CUtensorMap tmap_s,
                                                                  const __half* __restrict__ x, long long ldx,
                                                                  __half* __restrict__ y, long long ldy,
                                                                  const __half* __restrict__ bias,
                                                                  const __half* __restrict__ residual, long long ldr,
                                                                  int N, int K, int* status) {
-  using Cfg = QbCfg<Q8>;
+  using Cfg = QbCfg<Q8, RPW>;
+  constexpr int QB_ROWS = Cfg::ROWS;
+  constexpr int QB_RPW = RPW;
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
   uint64_t* empty = full + Cfg::STAGES;
@@ -74,15 +80,16 @@ __global__ void __launch_bounds__(QB_THREADS) q_gemv_bulk_kernel(const uint8_t* 
     }
     ctl->abort = 0;
     fence_mbar_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_s);
   }
   __syncthreads();
 
   if (warp == QB_CONS) {
-    // ------------------------------------------------------------------ producer: lane l copies row l
+    // ------------------------------------------------------------------ producer (one elected lane issues)
     uint32_t it = 0;
     bool ok = true;
     for (int rt = blockIdx.x; rt < row_tiles && ok; rt += gridDim.x) {
-      const long long row = min(rt * QB_ROWS + lane, N - 1);  // rows past N repeat the last row (discarded)
       for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
         const int s = it % Cfg::STAGES;
         const uint32_t ph = (it / Cfg::STAGES) & 1;
@@ -90,13 +97,14 @@ __global__ void __launch_bounds__(QB_THREADS) q_gemv_bulk_kernel(const uint8_t* 
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const int kb0 = kt * QB_KB;
-        const int nblk = min(QB_KB, nb - kb0);
         uint8_t* sq = smem + s * Cfg::STAGE_BYTES;
         uint8_t* ss = sq + Cfg::Q_BYTES;
-        if (lane == 0) mbar_arrive_expect_tx(&full[s], (uint32_t)(QB_ROWS * nblk * (Cfg::BQ + 2)));
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&full[s], (uint32_t)Cfg::STAGE_BYTES);
+          tma_load_2d(sq, &tmap_q, &full[s], kb0 * (Cfg::BQ / 4), rt * QB_ROWS);
+          tma_load_2d(ss, &tmap_s, &full[s], kb0, rt * QB_ROWS);
+        }
         __syncwarp();
-        bulk_load_1d(sq + lane * (QB_KB * Cfg::BQ), qs + (row * nb + kb0) * Cfg::BQ, (uint32_t)(nblk * Cfg::BQ), &full[s]);
-        bulk_load_1d(ss + lane * (QB_KB * 2), scales + row * nb + kb0, (uint32_t)(nblk * 2), &full[s]);
       }
     }
     // Copies still in flight must land before the CTA may exit: wait for the last armed phase of every stage.
@@ -178,36 +186,47 @@ __global__ void __launch_bounds__(QB_THREADS) q_gemv_bulk_kernel(const uint8_t* 
   __syncthreads();
 }
 
-template <bool Q8, int M>
+template <bool Q8, int M, int RPW>
 void launch_bulk(const QGemvArgs& a, int m0, cudaStream_t s) {
-  using Cfg = QbCfg<Q8>;
+  using Cfg = QbCfg<Q8, RPW>;
+  constexpr int QB_ROWS = Cfg::ROWS;
   static bool attr_set[64] = {};  // per device
-  auto kern = q_gemv_bulk_kernel<Q8, M>;
+  auto kern = q_gemv_bulk_kernel<Q8, M, RPW>;
   const int dev = current_device();
   if (!attr_set[dev & 63]) {
     RT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     attr_set[dev & 63] = true;
   }
   const int row_tiles = (a.N + QB_ROWS - 1) / QB_ROWS;
-  const int ctas_per_sm = Q8 ? 1 : 2;
+  const int ctas_per_sm = std::max(1, std::min(4, (224 * 1024) / Cfg::SMEM));
   const int grid = std::min(row_tiles, sm_count(dev) * ctas_per_sm);
   const __half* x = reinterpret_cast<const __half*>(a.x) + (long long)m0 * a.ldx;
   __half* y = reinterpret_cast<__half*>(a.y) + (long long)m0 * a.ldy;
   const __half* r = a.residual ? reinterpret_cast<const __half*>(a.residual) + (long long)m0 * a.ldr : nullptr;
-  kern<<<grid, QB_THREADS, Cfg::SMEM, s>>>(reinterpret_cast<const uint8_t*>(a.qs), reinterpret_cast<const __half*>(a.scales), x,
-                                           a.ldx, y, a.ldy, reinterpret_cast<const __half*>(a.bias), r, a.ldr, a.N, a.K,
-                                           status_word(dev));
+  const uint64_t nb = a.K / 32;
+  const CUtensorMap tq = make_tmap_rows(a.qs, 4, nb * (Cfg::BQ / 4), a.N, QB_KB * (Cfg::BQ / 4), QB_ROWS);
+  const CUtensorMap ts = make_tmap_rows(a.scales, 2, nb, a.N, QB_KB, QB_ROWS);
+  kern<<<grid, QB_THREADS, Cfg::SMEM, s>>>(tq, ts, x, a.ldx, y, a.ldy, reinterpret_cast<const __half*>(a.bias), r, a.ldr, a.N,
+                                           a.K, status_word(dev));
   RT_LAUNCH_CHECK();
 }
 
-template <bool Q8>
+template <bool Q8, int RPW>
 void dispatch_m(const QGemvArgs& a, int m0, int m, cudaStream_t s) {
   switch (m) {
-    case 1: launch_bulk<Q8, 1>(a, m0, s); break;
-    case 2: launch_bulk<Q8, 2>(a, m0, s); break;
-    case 3: launch_bulk<Q8, 3>(a, m0, s); break;
-    default: launch_bulk<Q8, 4>(a, m0, s); break;
+    case 1: launch_bulk<Q8, 1, RPW>(a, m0, s); break;
+    case 2: launch_bulk<Q8, 2, RPW>(a, m0, s); break;
+    case 3: launch_bulk<Q8, 3, RPW>(a, m0, s); break;
+    default: launch_bulk<Q8, 4, RPW>(a, m0, s); break;
   }
+}
+
+template <bool Q8>
+void dispatch_rows(const QGemvArgs& a, int m0, int m, cudaStream_t s) {
+  const int sms = sm_count(current_device());
+  if (a.N >= 2 * sms * 32) dispatch_m<Q8, 4>(a, m0, m, s);
+  else if (a.N >= 2 * sms * 16) dispatch_m<Q8, 2>(a, m0, m, s);
+  else dispatch_m<Q8, 1>(a, m0, m, s);
 }
 
 }  // namespace
@@ -223,8 +242,8 @@ void q_gemv_bulk(const QGemvArgs& a, cudaStream_t stream) {
   if (a.M == 0) return;
   for (int m0 = 0; m0 < a.M; m0 += 4) {
     const int m = std::min(4, a.M - m0);
-    if (a.q8) dispatch_m<true>(a, m0, m, stream);
-    else dispatch_m<false>(a, m0, m, stream);
+    if (a.q8) dispatch_rows<true>(a, m0, m, stream);
+    else dispatch_rows<false>(a, m0, m, stream);
   }
 }
 
