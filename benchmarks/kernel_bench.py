@@ -181,7 +181,7 @@ def bench_qgemv(a):
             for reg in (True, False):
                 def run():
                     for q in mats:
-                        C.q_gemv(q.qs, q.scales, x, y, None, None, False, register_path=reg)
+                        C.q_gemv(q.qs, q.scales, x, y, None, None, False, path=1 if reg else 2)
                 best, med = time_op(run, a.iters, flush=False)
                 report(f"q4_gemv_{'register' if reg else 'bulk'}_m{M}_{N}x{Kd}", best / copies, med / copies, bytes_=float(nbytes),
                        extra=f"mean over {copies} distinct matrices per timed region")

@@ -200,11 +200,12 @@ struct QGemvArgs {
   long long ldr;
   int M, N, K;
   bool q8;  // false: Q4_0, true: Q8_0
-  bool force_register_path = false;  // skip the bulk-copy kernel (tests and comparisons)
+  int path = 0;  // 0: pick by shape, 1: register-fed kernel, 2: TMA-ring kernel (tests and comparisons)
 };
 void q_gemv(const QGemvArgs& a, cudaStream_t stream);
 // quant/q_gemv_bulk.cu: bulk-copy (TMA engine) fed variant; q_gemv() uses it when the shape allows (K % 256 == 0).
 bool q_gemv_bulk_supported(const QGemvArgs& a);
+bool q_gemv_bulk_preferred(const QGemvArgs& a);  // shape heuristic from measurements
 void q_gemv_bulk(const QGemvArgs& a, cudaStream_t stream);
 void dequant_f16(const void* qs, const void* scales, void* out, long long n_blocks, bool q8, cudaStream_t s);
 void repack_q4_0(const void* blocks, void* qs, void* scales, long long n_blocks, cudaStream_t s);

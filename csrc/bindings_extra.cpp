@@ -76,7 +76,7 @@ void check_f16(const Tensor& t, const char* name) {
 
 // y[M, N] = dequant(W)[N, K] @ x[M, K]^T (+bias) (+residual); qs / scales are the repacked device layout.
 void q_gemv(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, const c10::optional<Tensor>& bias,
-            const c10::optional<Tensor>& residual, bool q8, bool register_path) {
+            const c10::optional<Tensor>& residual, bool q8, int64_t path) {
   check_f16(scales, "q_gemv scales");
   check_f16(x, "q_gemv x");
   check_f16(y, "q_gemv y");
@@ -106,7 +106,7 @@ void q_gemv(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, 
     a.ldr = residual->stride(0);
   }
   a.q8 = q8;
-  a.force_register_path = register_path;
+  a.path = int(path);
   rt::q_gemv(a, cur_stream(x.device().index()));
 }
 
@@ -394,7 +394,7 @@ void register_extra_ops(pybind11::module_& m) {
   m.def("dequant_f16", &dequant_f16, "expand repacked Q4_0 / Q8_0 weights to dense fp16");
   m.def("q_gemv", &q_gemv, "dequant-fused Q4_0 / Q8_0 matrix-vector product", pybind11::arg("qs"), pybind11::arg("scales"),
         pybind11::arg("x"), pybind11::arg("y"), pybind11::arg("bias"), pybind11::arg("residual"), pybind11::arg("q8"),
-        pybind11::arg("register_path") = false);
+        pybind11::arg("path") = 0);
   m.def("repack_quant", &repack_quant);
   m.def("rmsnorm_f16", &rmsnorm_f16);
   m.def("rope_kv", &rope_kv);

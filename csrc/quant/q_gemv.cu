@@ -166,7 +166,7 @@ void q_gemv(const QGemvArgs& a, cudaStream_t stream) {
   RT_CHECK((reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.qs) & 15) == 0,
            "q_gemv: x and qs must be 16-byte aligned");
   if (a.M == 0 || a.N == 0) return;
-  if (!a.force_register_path && q_gemv_bulk_supported(a)) {
+  if (a.path != 1 && q_gemv_bulk_supported(a) && (a.path == 2 || q_gemv_bulk_preferred(a))) {
     q_gemv_bulk(a, stream);
     return;
   }

@@ -31,8 +31,7 @@ constexpr int QB_KB = 32;      // quant blocks per tile and row (one per consume
 constexpr int QB_CONS = 8;     // consumer warps; each owns RPW rows of a tile of QB_CONS * RPW rows
 constexpr int QB_THREADS = (QB_CONS + 1) * 32;
 
-// RPW = rows per consumer warp: 4 (32-row tiles) for large N; 2 or 1 when N alone would give too few tiles
-// to occupy the SMs (the activation loads are then shared by fewer rows, which only matters for M > 1).
+// RPW = rows per consumer warp (tiles of QB_CONS * RPW = 32 rows).
 template <bool Q8, int RPW>
 struct QbCfg {
   static constexpr int ROWS = QB_CONS * RPW;
@@ -223,13 +222,17 @@ void dispatch_m(const QGemvArgs& a, int m0, int m, cudaStream_t s) {
 
 template <bool Q8>
 void dispatch_rows(const QGemvArgs& a, int m0, int m, cudaStream_t s) {
-  const int sms = sm_count(current_device());
-  if (a.N >= 2 * sms * 32) dispatch_m<Q8, 4>(a, m0, m, s);
-  else if (a.N >= 2 * sms * 16) dispatch_m<Q8, 2>(a, m0, m, s);
-  else dispatch_m<Q8, 1>(a, m0, m, s);
+  dispatch_m<Q8, 4>(a, m0, m, s);
 }
 
 }  // namespace
+
+// Measured on B200 at the llama-7B shapes (benchmarks/kernel_bench.py --op qgemv): both kernels are bound by
+// the dequantisation arithmetic, not by memory, at about 2.9 TB/s for one activation row; the ring wins
+// (+10 to +20 %) for 3-4 rows when N gives at least two tiles per SM, the register kernel otherwise.
+bool q_gemv_bulk_preferred(const QGemvArgs& a) {
+  return a.M >= 3 && a.N >= 2 * 32 * sm_count(current_device());
+}
 
 bool q_gemv_bulk_supported(const QGemvArgs& a) {
   return a.K % 256 == 0 && a.ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 &&

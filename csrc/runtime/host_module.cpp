@@ -1,0 +1,95 @@
+// Python module `_host`: the torch-free, CUDA-free part of the native runtime (arena allocator, CRC-64,
+// plan scheduler).  It loads on machines without a GPU, so the host-side logic is tested there.
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cstdint>
+#include <string>
+
+#include "arena.h"
+#include "plan.h"
+
+namespace py = pybind11;
+
+namespace {
+
+// CRC-64/XZ (reflected polynomial 0xC96C5795D7870F42, init and final XOR all-ones), slicing-by-8: the
+// checksum of the RusTorch binary container (reference: src/serialization/core.rs:255-269).
+uint64_t crc64(py::bytes data, uint64_t crc) {
+  static uint64_t table[8][256];
+  static bool ready = false;
+  if (!ready) {
+    for (int i = 0; i < 256; ++i) {
+      uint64_t c = (uint64_t)i;
+      for (int k = 0; k < 8; ++k) c = (c & 1) ? (c >> 1) ^ 0xC96C5795D7870F42ull : c >> 1;
+      table[0][i] = c;
+    }
+    for (int i = 0; i < 256; ++i)
+      for (int t = 1; t < 8; ++t) table[t][i] = (table[t - 1][i] >> 8) ^ table[0][table[t - 1][i] & 0xFF];
+    ready = true;
+  }
+  char* buf;
+  py::ssize_t len;
+  if (PyBytes_AsStringAndSize(data.ptr(), &buf, &len)) throw py::error_already_set();
+  const unsigned char* p = reinterpret_cast<const unsigned char*>(buf);
+  uint64_t c = ~crc;
+  size_t n = (size_t)len;
+  while (n >= 8) {
+    uint64_t w;
+    memcpy(&w, p, 8);
+    c ^= w;
+    c = table[7][c & 0xFF] ^ table[6][(c >> 8) & 0xFF] ^ table[5][(c >> 16) & 0xFF] ^ table[4][(c >> 24) & 0xFF] ^
+        table[3][(c >> 32) & 0xFF] ^ table[2][(c >> 40) & 0xFF] ^ table[1][(c >> 48) & 0xFF] ^ table[0][c >> 56];
+    p += 8;
+    n -= 8;
+  }
+  while (n--) c = table[0][(c ^ *p++) & 0xFF] ^ (c >> 8);
+  return ~c;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(_host, m) {
+  m.doc() = "host-side native runtime (no CUDA, no torch)";
+  m.def("crc64", &crc64, py::arg("data"), py::arg("crc") = 0);
+
+  py::class_<rt::Arena>(m, "Arena")
+      .def(py::init<uint64_t, uint64_t>(), py::arg("capacity"), py::arg("alignment") = 256)
+      .def("allocate", &rt::Arena::allocate)
+      .def("release", &rt::Arena::release)
+      .def("reset", &rt::Arena::reset)
+      .def("size_of", &rt::Arena::size_of)
+      .def("stats", [](const rt::Arena& a) {
+        const rt::ArenaStats s = a.stats();
+        py::dict d;
+        d["capacity"] = s.capacity;
+        d["in_use"] = s.in_use;
+        d["peak"] = s.peak;
+        d["n_alloc"] = s.n_alloc;
+        d["n_free"] = s.n_free;
+        d["n_fail"] = s.n_fail;
+        d["live_blocks"] = s.live_blocks;
+        d["free_ranges"] = s.free_ranges;
+        d["largest_free"] = s.largest_free;
+        d["fragmentation"] = s.fragmentation;
+        return d;
+      });
+
+  py::class_<rt::PlanNode>(m, "PlanNode")
+      .def_readonly("id", &rt::PlanNode::id)
+      .def_readonly("op", &rt::PlanNode::op)
+      .def_readonly("inputs", &rt::PlanNode::inputs)
+      .def_readonly("out_bytes", &rt::PlanNode::out_bytes);
+
+  py::class_<rt::ExecutionPlan>(m, "ExecutionPlan")
+      .def(py::init<>())
+      .def("add_node", &rt::ExecutionPlan::add_node, py::arg("op"), py::arg("inputs"), py::arg("out_bytes") = 0)
+      .def("mark_output", &rt::ExecutionPlan::mark_output)
+      .def("num_nodes", &rt::ExecutionPlan::num_nodes)
+      .def("node", &rt::ExecutionPlan::node, py::return_value_policy::reference_internal)
+      .def("topo_order", &rt::ExecutionPlan::topo_order)
+      .def("levels", &rt::ExecutionPlan::levels)
+      .def("eliminate_dead", &rt::ExecutionPlan::eliminate_dead)
+      .def("memory_plan", &rt::ExecutionPlan::memory_plan, py::arg("alignment") = 256)
+      .def("fusible_chains", &rt::ExecutionPlan::fusible_chains);
+}

@@ -100,7 +100,10 @@ def build(verbose: bool = False, force: bool = False) -> Path:
             list(ex.map(_do, jobs))
     # drop stale objects of sources that changed
     keep = {o.name for o in objs}
+    hflags_probe = "runtime_"
     for old in BUILD.glob("*.o"):
+        if old.name.startswith(hflags_probe):
+            continue
         if old.name not in keep:
             old.unlink()
     stamp = BUILD / "link.stamp"
@@ -116,7 +119,34 @@ def build(verbose: bool = False, force: bool = False) -> Path:
             print("[build] link", TARGET.name, flush=True)
         _run(link)
         stamp.write_text(want)
+    build_host(verbose, force)
     return TARGET
+
+
+HOST_TARGET = Path(__file__).resolve().parent / f"_host{EXT_SUFFIX}"
+
+
+def build_host(verbose: bool = False, force: bool = False) -> Path:
+    """``csrc/runtime/*.cpp`` -> ``rustorch_b200/_host*.so``: the host-only native runtime (pybind11, no CUDA and
+    no torch), so it also loads where there is no GPU."""
+    import pybind11
+    BUILD.mkdir(parents=True, exist_ok=True)
+    srcs = sorted((CSRC / "runtime").glob("*.cpp"))
+    hdr = _headers_digest()
+    flags = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", f"-I{pybind11.get_include()}",
+             f"-I{sysconfig.get_paths()['include']}", f"-I{CSRC}"]
+    objs, rebuilt = [], False
+    for s in srcs:
+        o = _obj_for(s, hdr, "host " + " ".join(flags))
+        objs.append(o)
+        if force or not o.exists():
+            if verbose:
+                print("[build]", s.name, flush=True)
+            _run(["g++", *flags, "-c", str(s), "-o", str(o)])
+            rebuilt = True
+    if rebuilt or force or not HOST_TARGET.exists():
+        _run(["g++", "-shared", "-o", str(HOST_TARGET), *map(str, objs)])
+    return HOST_TARGET
 
 
 if __name__ == "__main__":

@@ -78,3 +78,22 @@ def check_status(device: int | None = None) -> None:
                  103: "epilogue wait timed out", 104: "peer wait timed out",
                  105: "softmax wait timed out", 201: "index or alignment check failed"}
         raise RuntimeError(f"rustorch_b200 kernel status {code}: {names.get(code, 'unknown')}")
+
+
+_HOST_SO = _HERE / f"_host{sysconfig.get_config_var('EXT_SUFFIX') or '.so'}"
+_host_mod = None
+
+
+def host():
+    """The host-only native runtime (arena allocator, CRC-64, execution planner): no CUDA, no torch, so it loads on
+    every machine once built."""
+    global _host_mod
+    if _host_mod is None:
+        if not _HOST_SO.exists():
+            from . import _build
+            _build.build_host()
+        spec = importlib.util.spec_from_file_location("rustorch_b200._host", str(_HOST_SO))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        _host_mod = mod
+    return _host_mod

@@ -152,8 +152,8 @@ def test_q_gemv_register_and_bulk_paths_agree(q8, M, N, K):
     q = QuantLinear.random(N, K, gguf.GGMLType.Q8_0 if q8 else gguf.GGMLType.Q4_0, 0.02, "cuda", seed=4)
     x = (torch.randn(M, K, device="cuda") * 0.5).half()
     ya, yb = torch.empty(M, N, device="cuda", dtype=torch.half), torch.empty(M, N, device="cuda", dtype=torch.half)
-    C.q_gemv(q.qs, q.scales, x, ya, None, None, q.q8, register_path=False)
-    C.q_gemv(q.qs, q.scales, x, yb, None, None, q.q8, register_path=True)
+    C.q_gemv(q.qs, q.scales, x, ya, None, None, q.q8, path=2)
+    C.q_gemv(q.qs, q.scales, x, yb, None, None, q.q8, path=1)
     ref = x.float() @ q.dequantize().t()
     assert rel_err(ya, ref) < 6e-3 and rel_err(yb, ref) < 6e-3
     _native.check_status()
