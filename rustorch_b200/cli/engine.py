@@ -1,0 +1,158 @@
+"""Model loading and text generation for the CLI (example-cli/src/model/loader.rs:6-156, model/inference.rs:58-331).
+
+``ModelLoader.from_file`` dispatches on the file type: GGUF files become a quantised ``LlamaRuntime`` with their
+embedded tokenizer; safetensors / RusTorch / torch checkpoints of the in-repo GPT architecture are loaded into
+``GPT``; ``dummy`` gives the reference's echo model.  ``InferenceEngine.generate`` streams tokens: prefill once,
+then one decode step per token against the KV cache (the reference re-runs the whole sequence per token).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Callable, Iterator, List, Optional
+
+import torch
+
+from ..formats import gguf as gguf_fmt
+from ..formats.safetensors import detect_format
+from ..llm import InferenceTimer, LlamaRuntime, Sampler, SamplingConfig
+from .session import GenerationConfig
+from .tokenizer import ByteTokenizer, Tokenizer, load_tokenizer
+
+
+@dataclass
+class ModelMetadata:
+    name: str
+    format: str
+    vocab_size: int = 0
+    hidden_size: int = 0
+    num_layers: int = 0
+    num_heads: int = 0
+    context_length: int = 0
+
+
+class _GPTAdapter:
+    """Gives the training-time ``GPT`` module the prefill / decode interface (no KV cache: re-runs the window)."""
+
+    def __init__(self, model, device):
+        self.model, self.device = model.to(device).eval(), torch.device(device)
+        self.tokens: Optional[torch.Tensor] = None
+
+    def new_cache(self, batch: int, max_len: int):
+        self.tokens = None
+        return self
+
+    @torch.no_grad()
+    def prefill(self, prompts: torch.Tensor, cache) -> torch.Tensor:
+        self.tokens = prompts.to(self.device)
+        return self._last_logits()
+
+    @torch.no_grad()
+    def decode_step(self, tokens: torch.Tensor, cache) -> torch.Tensor:
+        self.tokens = torch.cat([self.tokens, tokens.view(-1, 1).to(self.device)], 1)
+        return self._last_logits()
+
+    def _last_logits(self) -> torch.Tensor:
+        ctx = self.model.config.block_size
+        out = self.model.forward_reference(self.tokens[:, -ctx:]) if hasattr(self.model, "forward_reference") else self.model(self.tokens[:, -ctx:])
+        logits = out[0] if isinstance(out, tuple) else out
+        return logits[:, -1, : self.model.config.vocab_size].float()
+
+
+class ModelLoader:
+    @staticmethod
+    def from_file(path: str, device: str = "cpu", tokenizer_path: Optional[str] = None):
+        """-> ``(runtime, tokenizer, ModelMetadata)``."""
+        if path == "dummy":
+            return None, ByteTokenizer(), ModelMetadata("dummy", "dummy", 258)
+        if not os.path.exists(path):
+            raise FileNotFoundError(path)
+        fmt = detect_format(path)
+        name = os.path.basename(path)
+        if fmt == "gguf":
+            with gguf_fmt.GGUFFile(path) as g:
+                tok = load_tokenizer(tokenizer_path, g)
+                mc = g.model_config()
+            rt = LlamaRuntime.from_gguf(path, device)
+            meta = ModelMetadata(name, "gguf", rt.cfg.vocab_size, rt.cfg.n_embd, rt.cfg.n_layer, rt.cfg.n_head, rt.cfg.context_length)
+            if isinstance(tok, ByteTokenizer):
+                tok = ByteTokenizer(rt.cfg.vocab_size)
+            return rt, tok, meta
+        if fmt in ("safetensors", "rustorch", "torch", "pth", "huggingface", "json"):
+            from ..models.gpt import GPT, GPTConfig
+            from ..models.high_level import load_state_dict_file
+            sd = load_state_dict_file(path)
+            wte = next((v for k, v in sd.items() if k.endswith("wte.weight")), None)
+            if wte is None:
+                raise ValueError(f"{name}: no GPT token embedding found; only GPT checkpoints of this framework are supported here")
+            n_layer = 1 + max(int(k.split(".")[2]) for k in sd if k.startswith("transformer.h."))
+            wpe = next(v for k, v in sd.items() if k.endswith("wpe.weight"))
+            n_embd = wte.shape[1]
+            qkv = next(v for k, v in sd.items() if k.endswith("attn.c_attn.weight"))
+            cfg = GPTConfig(vocab_size=wte.shape[0], block_size=wpe.shape[0], n_embd=n_embd, n_layer=n_layer,
+                            n_head=max(1, n_embd // 64), dropout=0.0)
+            model = GPT(cfg)
+            model.load_state_dict(sd, strict=False)
+            meta = ModelMetadata(name, fmt, cfg.vocab_size, n_embd, n_layer, cfg.n_head, cfg.block_size)
+            return _GPTAdapter(model, device), load_tokenizer(tokenizer_path, vocab_size=cfg.vocab_size), meta
+        raise ValueError(f"{name}: unsupported model format '{fmt}'")
+
+
+class InferenceEngine:
+    def __init__(self, runtime=None, tokenizer: Optional[Tokenizer] = None, generation: Optional[GenerationConfig] = None,
+                 device: str = "cpu", seed: Optional[int] = None):
+        self.runtime, self.tokenizer = runtime, tokenizer or ByteTokenizer()
+        self.generation = generation or GenerationConfig()
+        self.device, self.seed = device, seed
+        self.timer = InferenceTimer()
+        self.last_token_count = 0
+
+    def is_loaded(self) -> bool:
+        return self.runtime is not None
+
+    def _sampler(self) -> Sampler:
+        g = self.generation
+        return Sampler(SamplingConfig(temperature=g.temperature, top_k=g.top_k, top_p=g.top_p, repetition_penalty=g.repetition_penalty,
+                                      seed=self.seed), device=self.device)
+
+    def stream(self, prompt: str) -> Iterator[str]:
+        """Yields decoded text pieces as tokens are produced."""
+        if self.runtime is None:                      # the reference's dummy model: echo
+            reply = f"[no model loaded] You said: {prompt.strip().splitlines()[-1] if prompt.strip() else ''}"
+            self.last_token_count = len(reply.split())
+            yield reply
+            return
+        ids = self.tokenizer.encode(prompt)
+        ctx = getattr(getattr(self.runtime, "cfg", None), "context_length", 0) or 0
+        budget = self.generation.max_tokens
+        if ctx and len(ids) + budget > ctx:
+            ids = ids[-max(1, ctx - budget):]
+        sampler = self._sampler()
+        self.timer.start()
+        cache = self.runtime.new_cache(1, len(ids) + budget + 1)
+        logits = self.runtime.prefill(torch.tensor([ids], dtype=torch.long), cache)
+        out: List[int] = []
+        emitted = ""
+        for _ in range(budget):
+            tok = int(sampler(logits.cpu() if logits.device.type != self.device else logits)[0])
+            self.timer.token()
+            if tok == self.tokenizer.eos_id:
+                break
+            out.append(tok)
+            text = self.tokenizer.decode(out)
+            if not text.endswith("�"):           # hold back incomplete UTF-8 sequences
+                yield text[len(emitted):]
+                emitted = text
+            logits = self.runtime.decode_step(torch.tensor([tok], dtype=torch.long), cache)
+        self.last_token_count = len(out)
+
+    def generate(self, prompt: str, on_token: Optional[Callable[[str], None]] = None) -> str:
+        parts = []
+        for piece in self.stream(prompt):
+            parts.append(piece)
+            if on_token:
+                on_token(piece)
+        return "".join(parts)
+
+    def stats(self) -> dict:
+        return {"tokens": self.last_token_count, "ttft_ms": self.timer.ttft_ms(), "tokens_per_s": self.timer.tokens_per_s()}

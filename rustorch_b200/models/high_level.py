@@ -281,6 +281,24 @@ class ModelSaver:
                                      type(model).__name__)
 
 
+def load_state_dict_file(path: str) -> Dict[str, torch.Tensor]:
+    """Read a state dict from any supported container (RusTorch binary, safetensors, torch / PYTORCH1, JSON, HF dir)."""
+    from ..formats import rustorch_bin, safetensors as st
+    kind = st.detect_format(path)
+    if kind == "rustorch":
+        params, buffers, _ = rustorch_bin.load_state_dict(path)
+        return {**params, **buffers}
+    if kind == "safetensors":
+        return st.load_safetensors(path)
+    if kind in ("torch", "pth"):
+        return st.load_pth(path)
+    if kind == "json":
+        return st.load_json_state_dict(path)[0]
+    if kind == "huggingface":
+        return st.load_huggingface(path)[0]
+    raise ValueError(f"unrecognised model file '{path}'")
+
+
 class ModelLoader:
     @staticmethod
     def load(model: nn.Module, path: str, strict: bool = True) -> nn.Module:

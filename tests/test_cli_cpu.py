@@ -1,0 +1,158 @@
+"""CPU tests of the CLI: arguments, configuration, commands, session, tokenizers, download logic, REPL end to end."""
+import json
+import os
+
+import pytest
+import torch
+
+from rustorch_b200 import cli
+from rustorch_b200.formats import gguf
+
+
+def test_args_defaults_overrides_and_validation(tmp_path):
+    a = cli.parse_args([])
+    assert (a.max_tokens, a.temperature, a.top_p, a.top_k, a.backend) == (512, 0.7, 0.9, 40, cli.Backend.CPU)
+    cfg = tmp_path / "c.toml"
+    cfg.write_text('[generation]\nmax_tokens = 64\ntemperature = 0.2\n[model]\ndefault = "m.gguf"\n[backend]\ndefault = "cuda"\n')
+    a = cli.parse_args(["--config", str(cfg), "--temperature", "1.5"])
+    assert a.max_tokens == 64 and a.temperature == 1.5 and a.model == "m.gguf" and a.backend is cli.Backend.CUDA
+    with pytest.raises(ValueError):
+        cli.parse_args(["--temperature", "3"])
+    with pytest.raises(ValueError):
+        cli.parse_args(["--top-k", "0"])
+    d = cli.parse_args(["download", "hf:org/repo", "--force"])
+    assert d.command == "download" and d.target == "hf:org/repo" and d.force
+    assert cli.Backend.METAL.available() is False and cli.Backend.METAL.device() in ("cpu", "cuda")
+
+
+def test_config_roundtrip_and_errors(tmp_path):
+    c = cli.Config()
+    c.generation.top_k = 7
+    c.model.default = 'a "quoted" path'
+    p = c.save(str(tmp_path / "cfg" / "config.toml"))
+    back = cli.Config.load(p)
+    assert back.generation.top_k == 7 and back.model.default == 'a "quoted" path' and back.session.max_history == 1000
+    assert cli.Config.load_or_default(str(tmp_path / "missing.toml")).generation.max_tokens == 512
+    (tmp_path / "bad.toml").write_text("[generation]\nbogus = 1\n")
+    with pytest.raises(ValueError):
+        cli.Config.load(str(tmp_path / "bad.toml"))
+
+
+def test_command_parsing():
+    K = cli.CommandKind
+    for text, kind in (("/exit", K.EXIT), ("/quit", K.EXIT), ("/q", K.EXIT), ("/help", K.HELP), ("/?", K.HELP), ("/cls", K.CLEAR),
+                       ("/stats", K.STATS), ("/config", K.CONFIG)):
+        assert cli.Command.parse(text).kind is kind
+    assert cli.Command.parse("/save x.json").arg == "x.json" and cli.Command.parse("/save").arg is None
+    assert cli.Command.parse("/system You are helpful").arg == "You are helpful"
+    assert cli.Command.parse("/nope").kind is K.UNKNOWN
+    for bad in ("/backend", "/system", "/load", "/model"):
+        with pytest.raises(ValueError):
+            cli.Command.parse(bad)
+    assert not cli.Command.is_command("hello")
+
+
+def test_session_history_save_load(tmp_path):
+    s = cli.SessionManager(cli.GenerationConfig(max_tokens=8), "cpu", "m", max_history=3)
+    s.set_system_prompt("Be brief.")
+    for i in range(3):
+        s.add_user_message(f"q{i}")
+        s.add_assistant_message(f"a{i}")
+    assert s.message_count() == 3 and s.get_messages()[0].content == "a1"       # capped
+    assert s.build_prompt().startswith("Be brief.\n") and s.build_prompt().endswith("Assistant:")
+    p = str(tmp_path / "h.json")
+    s.save_history(p)
+    t = cli.SessionManager()
+    t.load_history(p)
+    assert [m.content for m in t.get_messages()] == ["a1", "q2", "a2"] and t.system_prompt() == "Be brief."
+    assert json.load(open(p))["generation"]["max_tokens"] == 8 and s.total_tokens() == 3
+    with pytest.raises(ValueError):
+        cli.SessionManager(cli.GenerationConfig(temperature=9))
+
+
+def test_tokenizers():
+    bt = cli.ByteTokenizer()
+    ids = bt.encode("héllo")
+    assert ids[0] == bt.bos_id and bt.decode(ids) == "héllo"
+    toks = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)] + ["▁", "h", "e", "l", "o", "▁h", "he", "ll", "▁he", "llo", "▁hello", "w", "▁w"]
+    scores = [0.0] * 259 + [-1, -2, -2, -2, -2, -3, -3, -3, -4, -5, -6, -2, -3]
+    types = [2, 3, 3] + [6] * 256 + [1] * 13
+    gt = cli.GGUFTokenizer(toks, [-s if s > 0 else s for s in scores], types)
+    # higher score merges first; the full word exists so it becomes one token
+    ids = gt.encode("hello")
+    assert ids[0] == 1 and gt.decode(ids) == "hello"
+    assert gt.decode(gt.encode("hello wé")) == "hello wé"                      # byte fallback for é
+    assert any(259 <= i for i in gt.encode("hello", add_bos=False))
+
+
+def test_download_identifiers_and_offline_logic(tmp_path):
+    i = cli.ModelIdentifier.parse("hf:TheBloke/Llama-2-7B-GGUF:llama-2-7b.Q4_0.gguf")
+    assert i.source is cli.ModelSource.HUGGINGFACE and i.repo_id == "TheBloke/Llama-2-7B-GGUF" and i.filename.endswith("Q4_0.gguf")
+    o = cli.ModelIdentifier.parse("ollama:llama2:7b")
+    assert o.source is cli.ModelSource.OLLAMA and o.repo_id == "llama2" and o.revision == "7b"
+    for bad in ("llama", "s3:x/y", "hf:norepo", "hf:"):
+        with pytest.raises(ValueError):
+            cli.ModelIdentifier.parse(bad)
+    hf = cli.HuggingFaceClient(token="t")
+    assert hf.file_url("a/b", "f.gguf", "dev") == "https://huggingface.co/a/b/resolve/dev/f.gguf" and hf._headers()["Authorization"] == "Bearer t"
+    from rustorch_b200.cli.download import ModelFile
+    files = [ModelFile("README.md"), ModelFile("m.Q8_0.gguf"), ModelFile("m.Q4_0.gguf")]
+    assert hf.recommend_gguf(files, ["Q4_0", "Q8_0"]).filename == "m.Q4_0.gguf" and len(hf.find_gguf_files(files)) == 2
+    assert cli.OllamaClient().manifest_url("llama2", "7b") == "https://registry.ollama.ai/v2/library/llama2/manifests/7b"
+    assert cli.OllamaClient.model_layer({"layers": [{"mediaType": "application/vnd.ollama.image.model", "digest": "sha256:x"}]})["digest"] == "sha256:x"
+    mgr = cli.ModelDownloadManager(str(tmp_path))
+    d = mgr.target_dir(i)
+    os.makedirs(d)
+    open(os.path.join(d, "llama-2-7b.Q4_0.gguf"), "wb").close()
+    assert mgr.list_models() == ["hf:TheBloke/Llama-2-7B-GGUF:llama-2-7b.Q4_0.gguf"] and mgr.list_models(cli.ModelSource.OLLAMA) == []
+
+
+def _tiny_gguf(path):
+    torch.manual_seed(0)
+    V, d, ff, L, H = 300, 64, 128, 2, 2
+    toks = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)] + ["▁", "a", "b", "▁a", "ab"] + [f"t{i}" for i in range(V - 264)]
+    md = {"general.architecture": "llama", "llama.block_count": L, "llama.embedding_length": d, "llama.feed_forward_length": ff,
+          "llama.attention.head_count": H, "llama.attention.head_count_kv": H, "llama.context_length": 64,
+          "llama.attention.layer_norm_rms_epsilon": 1e-5, "llama.rope.freq_base": 10000.0,
+          "tokenizer.ggml.model": "llama", "tokenizer.ggml.tokens": toks, "tokenizer.ggml.scores": [0.0] * V,
+          "tokenizer.ggml.token_type": [2, 3, 3] + [6] * 256 + [1] * (V - 259),
+          "tokenizer.ggml.bos_token_id": 1, "tokenizer.ggml.eos_token_id": 2}
+    Q = gguf.GGMLType.Q8_0
+    t = {"token_embd.weight": (torch.randn(V, d) * 0.1, gguf.GGMLType.F32), "output_norm.weight": (torch.ones(d), gguf.GGMLType.F32),
+         "output.weight": (torch.randn(V, d) * 0.1, Q)}
+    for i in range(L):
+        p = f"blk.{i}."
+        for n, shp in (("attn_q", (d, d)), ("attn_k", (d, d)), ("attn_v", (d, d)), ("attn_output", (d, d)), ("ffn_gate", (ff, d)),
+                       ("ffn_up", (ff, d)), ("ffn_down", (d, ff))):
+            t[p + n + ".weight"] = (torch.randn(*shp) * 0.1, Q)
+        t[p + "attn_norm.weight"] = (torch.ones(d), gguf.GGMLType.F32)
+        t[p + "ffn_norm.weight"] = (torch.ones(d), gguf.GGMLType.F32)
+    gguf.write_gguf(path, md, t)
+
+
+def test_repl_end_to_end_with_gguf_model(tmp_path):
+    model = str(tmp_path / "tiny.gguf")
+    _tiny_gguf(model)
+    hist = str(tmp_path / "hist.json")
+    lines = iter(["/help", "/system Be terse.", "ab a", "/stats", "/config", f"/save {hist}", "/clear", "/bogus", "/backend metal", "/exit"])
+    buf = []
+    rc = cli.main(["--model", model, "--max-tokens", "6", "--temperature", "0"], read=lambda _: next(lines), out=buf.append)
+    text = "".join(buf)
+    assert rc == 0 and "Commands:" in text and "Assistant: " in text and "tokens generated: " in text and "Goodbye!" in text
+    assert "Unknown command '/bogus'" in text and "not available" in text and "model: tiny.gguf" in text
+    doc = json.load(open(hist))
+    assert [m["role"] for m in doc["messages"]] == ["user", "assistant"] and doc["system_prompt"] == "Be terse."
+    # deterministic at temperature 0: one-shot mode gives the same reply as the REPL turn
+    buf2 = []
+    assert cli.main(["--model", model, "--max-tokens", "6", "--temperature", "0", "--system-prompt", "Be terse.", "--prompt", "ab a"], out=buf2.append) == 0
+    assert doc["messages"][1]["content"] == "".join(buf2).split("Assistant: ", 1)[1].strip()
+
+
+def test_dummy_model_and_list_command(tmp_path):
+    buf = []
+    assert cli.main(["--prompt", "hi there"], out=buf.append) == 0 and "You said: " in "".join(buf)
+    buf = []
+    assert cli.main(["list", "hf"], out=buf.append) == 0
+    buf = []
+    assert cli.main(["--model", str(tmp_path / "nope.gguf"), "--prompt", "x"], out=buf.append) == 1 and "cannot load model" in "".join(buf)
+    assert cli.main(["download", "ftp:x"], out=buf.append) == 2
