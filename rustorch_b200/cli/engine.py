@@ -53,10 +53,10 @@ class _GPTAdapter:
         return self._last_logits()
 
     def _last_logits(self) -> torch.Tensor:
-        ctx = self.model.config.block_size
+        ctx = self.model.cfg.n_positions
         out = self.model.forward_reference(self.tokens[:, -ctx:]) if hasattr(self.model, "forward_reference") else self.model(self.tokens[:, -ctx:])
         logits = out[0] if isinstance(out, tuple) else out
-        return logits[:, -1, : self.model.config.vocab_size].float()
+        return logits[:, -1, : self.model.cfg.vocab_size].float()
 
 
 class ModelLoader:
@@ -82,18 +82,18 @@ class ModelLoader:
             from ..models.gpt import GPT, GPTConfig
             from ..models.high_level import load_state_dict_file
             sd = load_state_dict_file(path)
-            wte = next((v for k, v in sd.items() if k.endswith("wte.weight")), None)
-            if wte is None:
-                raise ValueError(f"{name}: no GPT token embedding found; only GPT checkpoints of this framework are supported here")
-            n_layer = 1 + max(int(k.split(".")[2]) for k in sd if k.startswith("transformer.h."))
-            wpe = next(v for k, v in sd.items() if k.endswith("wpe.weight"))
-            n_embd = wte.shape[1]
-            qkv = next(v for k, v in sd.items() if k.endswith("attn.c_attn.weight"))
-            cfg = GPTConfig(vocab_size=wte.shape[0], block_size=wpe.shape[0], n_embd=n_embd, n_layer=n_layer,
-                            n_head=max(1, n_embd // 64), dropout=0.0)
+            if "wte" not in sd or "wpe" not in sd or "blocks.0.w_qkv" not in sd:
+                raise ValueError(f"{name}: not a GPT checkpoint of this framework (wte / wpe / blocks.N.w_qkv expected)")
+            n_layer = 1 + max(int(k.split(".")[1]) for k in sd if k.startswith("blocks."))
+            n_embd = sd["wpe"].shape[1]
+            vocab = int(sd.get("vocab_size", torch.tensor(sd["wte"].shape[0])))
+            cfg = GPTConfig(vocab_size=vocab, n_positions=sd["wpe"].shape[0], n_embd=n_embd, n_layer=n_layer,
+                            n_head=max(1, n_embd // 64), dropout=0.0, tie_weights="lm_head" not in sd)
+            if cfg.padded_vocab != sd["wte"].shape[0]:
+                cfg.vocab_size = sd["wte"].shape[0]
             model = GPT(cfg)
             model.load_state_dict(sd, strict=False)
-            meta = ModelMetadata(name, fmt, cfg.vocab_size, n_embd, n_layer, cfg.n_head, cfg.block_size)
+            meta = ModelMetadata(name, fmt, cfg.vocab_size, n_embd, n_layer, cfg.n_head, cfg.n_positions)
             return _GPTAdapter(model, device), load_tokenizer(tokenizer_path, vocab_size=cfg.vocab_size), meta
         raise ValueError(f"{name}: unsupported model format '{fmt}'")
 
