@@ -187,6 +187,36 @@ void softmax_rows_bwd(int dtype, const void* y, const void* dy, void* dx, long l
 // Row reductions over the last dim: mode 0 sum, 1 mean, 2 max, 3 min, 4 variance (unbiased = p0 != 0), out fp32 [rows].
 void reduce_rows(int dtype, const void* x, float* out, long long rows, int C, long long ld, int mode, float p0, cudaStream_t s);
 
+// ------------------------------------------------------------ collective/tp_gemm.cu
+// mode 0: y[W*rows][N] = all_gather(x_shards)[.][K] . B^T (+bias)      (x_shards, flags: symmetric peer pointers)
+// mode 1: out[rows][N] = reduce_scatter(x[W*rows][K] . B^T) (+bias) (+residual)   (stage, flags: symmetric)
+struct TpGemmArgs {
+  int mode;
+  int world, rank, epoch;      // epoch: 1, 2, 3, ... per call on the same buffers
+  int rows_per_rank, N, K;     // rows_per_rank multiple of 128
+  const void* b;               // weights: [N][K] (b_mn = false) or [K][N] (b_mn = true), bf16
+  bool b_mn;
+  long long ldb;
+  void* out;
+  long long ld_out;
+  const void* bias;            // bf16 [N] or null
+  const void* residual;        // mode 1: bf16 [rows][ld_res] or null
+  long long ld_res;
+  unsigned long long timeout_ns;
+  int* flags[RT_MAX_PEERS];    // int32[2*world + (rows_per_rank/128)*world] per rank, zero-initialised once
+  // mode 0
+  const void* x_shards[RT_MAX_PEERS];  // every rank's [rows_per_rank][K] shard
+  void* gather;                        // local [W*rows_per_rank][K]
+  int* mb_ready;                       // local int32[W*rows_per_rank/128], zero-initialised once
+  unsigned* comm_done;                 // local, zero-initialised once
+  int n_comm;                          // copy CTAs (0 = default 8)
+  // mode 1
+  const void* x;                       // local [W*rows_per_rank][ld_x]
+  long long ld_x;
+  void* stage[RT_MAX_PEERS];           // every rank's staging: bf16 [2][W][rows_per_rank][N]
+};
+void tp_gemm(const TpGemmArgs& a, cudaStream_t stream);
+
 // ------------------------------------------------------------------ quant/q_gemv.cu
 struct QGemvArgs {
   const void* qs;      // repacked quantised weights (layout in q_gemv.cu)

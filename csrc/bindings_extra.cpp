@@ -243,6 +243,83 @@ uint64_t crc64_bytes(const pybind11::bytes& data) {
 
 }  // namespace
 
+void check_bf16(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16, name, ": bf16 CUDA tensor required");
+}
+
+// all-gather -> GEMM.  x_ptrs / flag_ptrs: peer pointers of the symmetric shard [rows, K] and flag buffers.
+void tp_ag_gemm(const std::vector<int64_t>& x_ptrs, const std::vector<int64_t>& flag_ptrs, Tensor& gather, Tensor& mb_ready,
+                Tensor& comm_done, const Tensor& weight, bool b_mn, Tensor& out, const c10::optional<Tensor>& bias, int64_t rank,
+                int64_t epoch, int64_t rows_per_rank, double timeout_s, int64_t n_comm) {
+  const int world = int(x_ptrs.size());
+  check_bf16(gather, "tp_ag_gemm gather");
+  check_bf16(weight, "tp_ag_gemm weight");
+  check_bf16(out, "tp_ag_gemm out");
+  TORCH_CHECK(int(flag_ptrs.size()) == world && weight.dim() == 2 && weight.stride(1) == 1 && out.dim() == 2 && out.stride(1) == 1 &&
+                  gather.is_contiguous() && gather.dim() == 2, "tp_ag_gemm: bad operands");
+  rt::TpGemmArgs a{};
+  a.mode = 0;
+  a.world = world; a.rank = int(rank); a.epoch = int(epoch); a.rows_per_rank = int(rows_per_rank);
+  a.K = int(gather.size(1));
+  a.N = int(b_mn ? weight.size(1) : weight.size(0));
+  TORCH_CHECK((b_mn ? weight.size(0) : weight.size(1)) == a.K, "tp_ag_gemm: weight K mismatch");
+  TORCH_CHECK(gather.size(0) == rows_per_rank * world && out.size(0) == gather.size(0) && out.size(1) == a.N, "tp_ag_gemm: shape mismatch");
+  TORCH_CHECK(mb_ready.scalar_type() == at::kInt && mb_ready.numel() >= gather.size(0) / 128 && comm_done.scalar_type() == at::kInt,
+              "tp_ag_gemm: int32 mb_ready / comm_done");
+  a.b = weight.data_ptr(); a.b_mn = b_mn; a.ldb = weight.stride(0);
+  a.out = out.data_ptr(); a.ld_out = out.stride(0);
+  if (bias.has_value() && bias->defined()) { check_bf16(*bias, "tp bias"); a.bias = bias->data_ptr(); }
+  a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
+  for (int r = 0; r < world; ++r) {
+    a.x_shards[r] = reinterpret_cast<const void*>(x_ptrs[r]);
+    a.flags[r] = reinterpret_cast<int*>(flag_ptrs[r]);
+  }
+  a.gather = gather.data_ptr();
+  a.mb_ready = mb_ready.data_ptr<int>();
+  a.comm_done = reinterpret_cast<unsigned*>(comm_done.data_ptr<int>());
+  a.n_comm = int(n_comm);
+  c10::cuda::CUDAGuard guard(gather.device());
+  rt::tp_gemm(a, cur_stream(gather.device().index()));
+}
+
+// GEMM -> reduce-scatter.  stage_ptrs / flag_ptrs: peer pointers of the symmetric staging and flag buffers.
+void tp_gemm_rs(const Tensor& x, const Tensor& weight, bool b_mn, const std::vector<int64_t>& stage_ptrs,
+                const std::vector<int64_t>& flag_ptrs, Tensor& out, const c10::optional<Tensor>& bias,
+                const c10::optional<Tensor>& residual, int64_t rank, int64_t epoch, double timeout_s) {
+  const int world = int(stage_ptrs.size());
+  check_bf16(x, "tp_gemm_rs x");
+  check_bf16(weight, "tp_gemm_rs weight");
+  check_bf16(out, "tp_gemm_rs out");
+  TORCH_CHECK(int(flag_ptrs.size()) == world && x.dim() == 2 && x.stride(1) == 1 && weight.dim() == 2 && weight.stride(1) == 1 &&
+                  out.dim() == 2 && out.stride(1) == 1, "tp_gemm_rs: bad operands");
+  rt::TpGemmArgs a{};
+  a.mode = 1;
+  a.world = world; a.rank = int(rank); a.epoch = int(epoch);
+  TORCH_CHECK(x.size(0) % world == 0, "tp_gemm_rs: rows must divide by the world size");
+  a.rows_per_rank = int(x.size(0) / world);
+  a.K = int(x.size(1));
+  a.N = int(b_mn ? weight.size(1) : weight.size(0));
+  TORCH_CHECK((b_mn ? weight.size(0) : weight.size(1)) == a.K, "tp_gemm_rs: weight K mismatch");
+  TORCH_CHECK(out.size(0) == a.rows_per_rank && out.size(1) == a.N, "tp_gemm_rs: out must be [rows / world, N]");
+  a.b = weight.data_ptr(); a.b_mn = b_mn; a.ldb = weight.stride(0);
+  a.x = x.data_ptr(); a.ld_x = x.stride(0);
+  a.out = out.data_ptr(); a.ld_out = out.stride(0);
+  if (bias.has_value() && bias->defined()) { check_bf16(*bias, "tp bias"); a.bias = bias->data_ptr(); }
+  if (residual.has_value() && residual->defined()) {
+    check_bf16(*residual, "tp residual");
+    TORCH_CHECK(residual->dim() == 2 && residual->stride(1) == 1 && residual->size(0) == a.rows_per_rank && residual->size(1) == a.N,
+                "tp_gemm_rs: residual must match out");
+    a.residual = residual->data_ptr(); a.ld_res = residual->stride(0);
+  }
+  a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
+  for (int r = 0; r < world; ++r) {
+    a.stage[r] = reinterpret_cast<void*>(stage_ptrs[r]);
+    a.flags[r] = reinterpret_cast<int*>(flag_ptrs[r]);
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  rt::tp_gemm(a, cur_stream(x.device().index()));
+}
+
 int dtype_code(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, ": CUDA tensor required");
   switch (t.scalar_type()) {
@@ -384,6 +461,8 @@ void batchnorm_bwd(const Tensor& x2, const Tensor& dy2, const c10::optional<Tens
 }
 
 void register_extra_ops(pybind11::module_& m) {
+  m.def("tp_ag_gemm", &tp_ag_gemm, "fused all-gather -> GEMM over symmetric peer memory");
+  m.def("tp_gemm_rs", &tp_gemm_rs, "fused GEMM -> reduce-scatter over symmetric peer memory");
   m.def("batchnorm_fwd", &batchnorm_fwd, "BatchNorm forward over a channels-last matrix (+residual, +ReLU)");
   m.def("batchnorm_bwd", &batchnorm_bwd, "BatchNorm backward; scratch returns [dbeta, dgamma]");
   m.def("ew_binary", &ew_binary, "elementwise binary op (add/sub/mul/div/max/min/pow)");

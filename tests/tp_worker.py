@@ -1,0 +1,104 @@
+"""torchrun worker: fused tensor-parallel linears on W GPUs vs the unsharded fp32 model.  Writes rank<r>.json."""
+import json
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def rel(a, b):
+    return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-6))
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from rustorch_b200 import _native
+    from rustorch_b200.distributed.tp_fused import AllGatherGemm, FusedColumnParallelLinear, FusedRowParallelLinear, GemmReduceScatter
+    res = {}
+    rows, d, ff = int(os.environ.get("TP_ROWS", "512")), int(os.environ.get("TP_D", "1024")), int(os.environ.get("TP_FF", "4096"))
+    g = torch.Generator().manual_seed(0)                              # identical full tensors on every rank
+    X = (torch.randn(world * rows, d, generator=g) * 0.5).bfloat16().to(dev)
+    Wc = (torch.randn(ff, d, generator=g) * 0.05).bfloat16().to(dev)
+    Wr = (torch.randn(d, ff, generator=g) * 0.05).bfloat16().to(dev)
+    bc = torch.randn(ff, generator=g).bfloat16().to(dev)
+    br = torch.randn(d, generator=g).bfloat16().to(dev)
+    G = torch.randn(world * rows, d, generator=g).bfloat16().to(dev)
+    ffl = ff // world
+    # ---- raw ops, several epochs
+    ag = AllGatherGemm(rows, d, dev)
+    rs = GemmReduceScatter(rows, d, dev)
+    worst_ag = worst_rs = 0.0
+    for it in range(3):
+        Xi = (X * (1 + it)).bfloat16()
+        y = ag(Wc[rank * ffl:(rank + 1) * ffl], bc[rank * ffl:(rank + 1) * ffl], x=Xi[rank * rows:(rank + 1) * rows])
+        ref = Xi.float() @ Wc[rank * ffl:(rank + 1) * ffl].float().t() + bc[rank * ffl:(rank + 1) * ffl].float()
+        worst_ag = max(worst_ag, rel(y, ref))
+        assert torch.equal(ag.gather, Xi)
+        H = torch.nn.functional.gelu(Xi.float() @ Wc.float().t() + bc.float(), approximate="tanh").bfloat16()
+        out = rs(H[:, rank * ffl:(rank + 1) * ffl].contiguous(), Wr[:, rank * ffl:(rank + 1) * ffl].contiguous(), br)
+        ref2 = (H.float() @ Wr.float().t() + br.float())[rank * rows:(rank + 1) * rows]
+        worst_rs = max(worst_rs, rel(out, ref2))
+    res["ag_rel"], res["rs_rel"] = worst_ag, worst_rs
+    # ---- layers with autograd
+    col = FusedColumnParallelLinear(d, ff, rows, device=dev)
+    row = FusedRowParallelLinear(ff, d, rows, device=dev)
+    with torch.no_grad():
+        col.weight.copy_(Wc[rank * ffl:(rank + 1) * ffl]); col.bias.copy_(bc[rank * ffl:(rank + 1) * ffl])
+        row.weight.copy_(Wr[:, rank * ffl:(rank + 1) * ffl]); row.bias.copy_(br)
+    xs = X[rank * rows:(rank + 1) * rows].clone().requires_grad_(True)
+    y = row(torch.nn.functional.gelu(col(xs), approximate="tanh"))
+    y.backward(G[rank * rows:(rank + 1) * rows])
+    Xr = X.float().requires_grad_(True)
+    wc, wr, bcf, brf = (t.float().requires_grad_(True) for t in (Wc, Wr, bc, br))
+    yr = torch.nn.functional.gelu(Xr @ wc.t() + bcf, approximate="tanh") @ wr.t() + brf
+    yr.backward(G.float())
+    res["y_rel"] = rel(y, yr[rank * rows:(rank + 1) * rows])
+    res["dx_rel"] = rel(xs.grad, Xr.grad[rank * rows:(rank + 1) * rows])
+    res["dwc_rel"] = rel(col.weight.grad, wc.grad[rank * ffl:(rank + 1) * ffl])
+    res["dwr_rel"] = rel(row.weight.grad, wr.grad[:, rank * ffl:(rank + 1) * ffl])
+    res["dbr_rel"] = rel(row.bias.grad, brf.grad)
+    # ---- timing against NCCL + library GEMM (device time, max over ranks)
+    def timed(fn, iters=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+    xsh, wcl = X[rank * rows:(rank + 1) * rows].contiguous(), Wc[rank * ffl:(rank + 1) * ffl].contiguous()
+    full = torch.empty(world * rows, d, dtype=torch.bfloat16, device=dev)
+    def nccl_ag():
+        dist.all_gather_into_tensor(full, xsh)
+        return full @ wcl.t()
+    hl, wrl = torch.randn(world * rows, ffl, device=dev).bfloat16(), Wr[:, rank * ffl:(rank + 1) * ffl].contiguous()
+    outb = torch.empty(rows, d, dtype=torch.bfloat16, device=dev)
+    def nccl_rs():
+        dist.reduce_scatter_tensor(outb, hl @ wrl.t())
+        return outb
+    res["ag_fused_ms"] = timed(lambda: ag(wcl, None, x=None))
+    res["ag_nccl_ms"] = timed(nccl_ag)
+    res["rs_fused_ms"] = timed(lambda: rs(hl, wrl))
+    res["rs_nccl_ms"] = timed(nccl_rs)
+    res["shape"] = {"rows_per_rank": rows, "d": d, "ff": ff, "world": world}
+    _native.check_status()
+    with open(os.path.join(os.environ["TP_RESULT_DIR"], f"rank{rank}.json"), "w") as f:
+        json.dump(res, f)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
