@@ -1,0 +1,203 @@
+"""Llama-family decoder for training: RMSNorm, rotary embeddings, grouped-query attention, SwiGLU MLP
+(the model family of the reference's CLI runtime, example-cli/src/model/transformer.rs:9-270, there
+forward-only and stubbed; here a trainable module).
+
+On CUDA with bf16 parameters the block runs on the native kernels: RMSNorm forward/backward, tcgen05 GEMMs
+for the projections, tcgen05 flash attention with GQA, elementwise SiLU-gate.  With ``tp_group`` set, the model
+is tensor- and sequence-parallel in the Megatron layout: tokens are sharded over ranks between blocks, ``wqkv``
+and ``w_gate_up`` are column-parallel (one fused all-gather -> GEMM kernel each), ``wo`` and ``w_down`` are
+row-parallel (one fused GEMM -> reduce-scatter kernel each); the fused layers live in
+``rustorch_b200.distributed.tp_fused``.  Elsewhere (CPU, fp32) the same math runs through PyTorch ops.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..nn import fused
+from ..ops import elementwise as ew
+
+
+@dataclass
+class LlamaTrainConfig:
+    vocab_size: int = 32000
+    n_layer: int = 32
+    n_embd: int = 4096
+    n_head: int = 32
+    n_head_kv: int = 32
+    n_ff: int = 11008
+    max_seq_len: int = 4096
+    rope_theta: float = 10000.0
+    rms_eps: float = 1e-5
+    init_std: float = 0.02
+
+    @property
+    def head_dim(self) -> int:
+        return self.n_embd // self.n_head
+
+    @staticmethod
+    def llama_7b() -> "LlamaTrainConfig":
+        return LlamaTrainConfig()
+
+    @staticmethod
+    def llama3_8b() -> "LlamaTrainConfig":
+        return LlamaTrainConfig(vocab_size=128256, n_head_kv=8, n_ff=14336, max_seq_len=8192, rope_theta=500000.0)
+
+    @staticmethod
+    def tiny(**kw) -> "LlamaTrainConfig":
+        base = dict(vocab_size=512, n_layer=2, n_embd=256, n_head=4, n_head_kv=2, n_ff=512, max_seq_len=256)
+        base.update(kw)
+        return LlamaTrainConfig(**base)
+
+
+def rope_tables(T: int, D: int, theta: float, device, dtype=torch.float32) -> Tuple[torch.Tensor, torch.Tensor]:
+    inv = theta ** (-torch.arange(0, D, 2, device=device, dtype=torch.float32) / D)
+    ang = torch.arange(T, device=device, dtype=torch.float32)[:, None] * inv[None, :]
+    return ang.cos().to(dtype), ang.sin().to(dtype)
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """``x [B, T, H, D]``, half-split pairs ``(i, i + D/2)`` (the HuggingFace Llama convention)."""
+    half = x.shape[-1] // 2
+    a, b = x[..., :half], x[..., half:]
+    c, s = cos[None, : x.shape[1], None, :], sin[None, : x.shape[1], None, :]
+    return torch.cat([a * c - b * s, a * s + b * c], -1).to(x.dtype)
+
+
+def _native_ok(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16
+
+
+def _rms(x, w, eps):
+    if _native_ok(x):
+        return fused.RMSNormFn.apply(x, w, eps)
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
+
+
+def _linear(x2, w):
+    return fused.LinearFn.apply(x2, w, None) if _native_ok(x2) else x2 @ w.t()
+
+
+def _attention(q, k, v):
+    if _native_ok(q) and q.shape[-1] in (64, 128):
+        return fused.FlashAttentionFn.apply(q, k, v, True, None)
+    g = q.shape[2] // k.shape[2]
+    kk, vv = k.repeat_interleave(g, 2), v.repeat_interleave(g, 2)
+    return F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), is_causal=True).transpose(1, 2)
+
+
+class LlamaBlock(nn.Module):
+    def __init__(self, cfg: LlamaTrainConfig, device=None, dtype=None, tp_group=None, rows_per_rank: int = 0):
+        super().__init__()
+        self.cfg = cfg
+        kw = dict(device=device, dtype=dtype)
+        D, H, Hkv = cfg.head_dim, cfg.n_head, cfg.n_head_kv
+        self.tp = tp_group is not None
+        self.attn_norm = nn.Parameter(torch.ones(cfg.n_embd, **kw))
+        self.ffn_norm = nn.Parameter(torch.ones(cfg.n_embd, **kw))
+        if self.tp:
+            import torch.distributed as dist
+            from ..distributed.tp_fused import FusedColumnParallelLinear, FusedRowParallelLinear
+            W = dist.get_world_size(tp_group)
+            if H % W or Hkv % W or cfg.n_ff % W:
+                raise ValueError("heads, kv heads and n_ff must divide by the tensor-parallel world size")
+            self.h_local, self.hkv_local, self.ff_local = H // W, Hkv // W, cfg.n_ff // W
+            self.wqkv = FusedColumnParallelLinear(cfg.n_embd, (H + 2 * Hkv) * D, rows_per_rank, False, tp_group, device, cfg.init_std)
+            self.wo = FusedRowParallelLinear(H * D, cfg.n_embd, rows_per_rank, False, tp_group, device, cfg.init_std / math.sqrt(2 * cfg.n_layer))
+            self.w_gate_up = FusedColumnParallelLinear(cfg.n_embd, 2 * cfg.n_ff, rows_per_rank, False, tp_group, device, cfg.init_std)
+            self.w_down = FusedRowParallelLinear(cfg.n_ff, cfg.n_embd, rows_per_rank, False, tp_group, device, cfg.init_std / math.sqrt(2 * cfg.n_layer))
+        else:
+            self.h_local, self.hkv_local, self.ff_local = H, Hkv, cfg.n_ff
+            self.wqkv = nn.Parameter(torch.randn((H + 2 * Hkv) * D, cfg.n_embd, **kw) * cfg.init_std)
+            self.wo = nn.Parameter(torch.randn(cfg.n_embd, H * D, **kw) * cfg.init_std / math.sqrt(2 * cfg.n_layer))
+            self.w_gate_up = nn.Parameter(torch.randn(2 * cfg.n_ff, cfg.n_embd, **kw) * cfg.init_std)
+            self.w_down = nn.Parameter(torch.randn(cfg.n_embd, cfg.n_ff, **kw) * cfg.init_std / math.sqrt(2 * cfg.n_layer))
+
+    def forward(self, x: torch.Tensor, cos, sin, B: int, T: int) -> torch.Tensor:
+        """``x``: ``[B*T, d]`` (or this rank's rows of it under tensor parallelism)."""
+        c = self.cfg
+        D, H, Hkv = c.head_dim, self.h_local, self.hkv_local
+        h = _rms(x, self.attn_norm, c.rms_eps)
+        qkv = self.wqkv(h) if self.tp else _linear(h, self.wqkv)                    # [B*T, (H + 2 Hkv) D] (all tokens)
+        qkv = qkv.view(B, T, H + 2 * Hkv, D)
+        q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        att = _attention(q, k, v.contiguous()).reshape(B * T, H * D)
+        x = x + (self.wo(att) if self.tp else _linear(att, self.wo))
+        h = _rms(x, self.ffn_norm, c.rms_eps)
+        gu = self.w_gate_up(h) if self.tp else _linear(h, self.w_gate_up)           # [B*T, 2 ff_local]: gate | up
+        act = ew.mul(ew.unary("silu", gu[:, : self.ff_local].contiguous()), gu[:, self.ff_local:].contiguous())
+        return x + (self.w_down(act) if self.tp else _linear(act, self.w_down))
+
+
+class LlamaModel(nn.Module):
+    """``forward(idx [B, T], targets) -> (logits or None, loss)``.  Under tensor parallelism every rank receives the
+    same ``idx``; the loss is the mean over this rank's token shard (average it over ranks for reporting)."""
+
+    def __init__(self, cfg: LlamaTrainConfig, device=None, dtype=None, tp_group=None, batch: int = 0, seq_len: int = 0):
+        super().__init__()
+        self.cfg, self.tp_group = cfg, tp_group
+        kw = dict(device=device, dtype=dtype)
+        self.world, self.rank, rows = 1, 0, 0
+        if tp_group is not None:
+            import torch.distributed as dist
+            self.world, self.rank = dist.get_world_size(tp_group), dist.get_rank(tp_group)
+            if batch * seq_len % (128 * self.world):
+                raise ValueError("batch * seq_len must be a multiple of 128 * world size for the fused TP kernels")
+            rows = batch * seq_len // self.world
+        self.tok_emb = nn.Parameter(torch.randn(cfg.vocab_size, cfg.n_embd, **kw) * cfg.init_std)
+        self.blocks = nn.ModuleList([LlamaBlock(cfg, device, dtype, tp_group, rows) for _ in range(cfg.n_layer)])
+        self.out_norm = nn.Parameter(torch.ones(cfg.n_embd, **kw))
+        self.lm_head = nn.Parameter(torch.randn(cfg.vocab_size, cfg.n_embd, **kw) * cfg.init_std)
+        self._rope = None
+
+    def num_parameters(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+    def forward(self, idx: torch.Tensor, targets: Optional[torch.Tensor] = None):
+        B, T = idx.shape
+        c = self.cfg
+        if self._rope is None or self._rope[0].shape[0] < T or self._rope[0].device != idx.device:
+            self._rope = rope_tables(max(T, c.max_seq_len), c.head_dim, c.rope_theta, idx.device)
+        cos, sin = self._rope
+        flat = idx.reshape(-1)
+        lo, hi = 0, B * T
+        if self.world > 1:
+            n = B * T // self.world
+            lo, hi = self.rank * n, (self.rank + 1) * n
+        x = self.tok_emb[flat[lo:hi]]
+        for blk in self.blocks:
+            x = blk(x, cos, sin, B, T)
+        x = _rms(x, self.out_norm, c.rms_eps)
+        logits = _linear(x, self.lm_head)
+        if targets is None:
+            return logits.view(-1, c.vocab_size), None
+        loss = F.cross_entropy(logits.float(), targets.reshape(-1)[lo:hi])
+        return logits, loss
+
+    @torch.no_grad()
+    def load_from_unsharded(self, full: "LlamaModel") -> None:
+        """Copy (and shard) the weights of a single-rank model with the same config: used by tests and for resharding."""
+        W, r = self.world, self.rank
+        self.tok_emb.copy_(full.tok_emb); self.out_norm.copy_(full.out_norm); self.lm_head.copy_(full.lm_head)
+        c = self.cfg
+        D, H, Hkv = c.head_dim, c.n_head, c.n_head_kv
+        for mine, ref in zip(self.blocks, full.blocks):
+            mine.attn_norm.copy_(ref.attn_norm); mine.ffn_norm.copy_(ref.ffn_norm)
+            if not mine.tp:
+                for n in ("wqkv", "wo", "w_gate_up", "w_down"):
+                    getattr(mine, n).copy_(getattr(ref, n))
+                continue
+            hl, kl, fl = H // W, Hkv // W, c.n_ff // W
+            q, k, v = ref.wqkv[: H * D], ref.wqkv[H * D:(H + Hkv) * D], ref.wqkv[(H + Hkv) * D:]
+            mine.wqkv.weight.copy_(torch.cat([q[r * hl * D:(r + 1) * hl * D], k[r * kl * D:(r + 1) * kl * D], v[r * kl * D:(r + 1) * kl * D]]))
+            mine.wo.weight.copy_(ref.wo[:, r * hl * D:(r + 1) * hl * D])
+            g, u = ref.w_gate_up[: c.n_ff], ref.w_gate_up[c.n_ff:]
+            mine.w_gate_up.weight.copy_(torch.cat([g[r * fl:(r + 1) * fl], u[r * fl:(r + 1) * fl]]))
+            mine.w_down.weight.copy_(ref.w_down[:, r * fl:(r + 1) * fl])

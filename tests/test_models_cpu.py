@@ -86,3 +86,34 @@ def test_checkpoint_with_optimizer_moments(tmp_path):
     assert ck["epoch"] == 2 and ck["metrics"]["loss"] == 0.5 and torch.equal(m.weight, m2.weight)
     st = list(o2.state_dict()["state"].values())
     assert st and "exp_avg" in st[0]
+
+
+def test_llama_training_model_cpu():
+    from rustorch_b200.models.llama import LlamaModel, LlamaTrainConfig, apply_rope, rope_tables
+    torch.manual_seed(0)
+    cfg = LlamaTrainConfig.tiny(n_layer=2, n_embd=64, n_head=4, n_head_kv=2, n_ff=128, vocab_size=97)
+    m = LlamaModel(cfg)
+    idx = torch.randint(0, 97, (2, 16))
+    logits, loss = m(idx, idx.roll(-1, 1))
+    assert logits.shape == (32, 97) and 3.5 < float(loss) < 6.0
+    loss.backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in m.parameters())
+    opt = torch.optim.AdamW(m.parameters(), lr=3e-3)
+    first = float(loss)
+    for _ in range(20):
+        opt.zero_grad()
+        _, l = m(idx, idx.roll(-1, 1))
+        l.backward()
+        opt.step()
+    assert float(l) < first * 0.7
+    # rotary embedding: norm preserving, position 0 is the identity, relative property q_m . k_n depends on m - n
+    cos, sin = rope_tables(8, 16, 10000.0, "cpu")
+    x = torch.randn(1, 8, 1, 16)
+    r = apply_rope(x, cos, sin)
+    assert torch.allclose(r.norm(dim=-1), x.norm(dim=-1), atol=1e-5) and torch.allclose(r[:, 0], x[:, 0])
+    q = torch.randn(16)
+    k = torch.randn(16)
+    qs = apply_rope(q.expand(1, 8, 1, 16), cos, sin)[0, :, 0]
+    ks = apply_rope(k.expand(1, 8, 1, 16), cos, sin)[0, :, 0]
+    assert torch.allclose(qs[5] @ ks[3], qs[4] @ ks[2], atol=1e-4)
+    assert LlamaTrainConfig.llama3_8b().n_head_kv == 8 and m.num_parameters() > 0

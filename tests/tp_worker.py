@@ -65,6 +65,29 @@ def main():
     res["dwc_rel"] = rel(col.weight.grad, wc.grad[rank * ffl:(rank + 1) * ffl])
     res["dwr_rel"] = rel(row.weight.grad, wr.grad[:, rank * ffl:(rank + 1) * ffl])
     res["dbr_rel"] = rel(row.bias.grad, brf.grad)
+    # ---- Llama block stack, tensor + sequence parallel, against the unsharded model
+    from rustorch_b200.models.llama import LlamaModel, LlamaTrainConfig
+    torch.manual_seed(7)
+    cfg = LlamaTrainConfig.tiny(n_layer=2, n_embd=256, n_head=4, n_head_kv=2, n_ff=512, vocab_size=512)
+    Bq, Tq = 2, 64 * world
+    full = LlamaModel(cfg, device=dev, dtype=torch.bfloat16)
+    for p_ in full.parameters():
+        dist.broadcast(p_.data, 0)
+    tpm = LlamaModel(cfg, device=dev, dtype=torch.bfloat16, tp_group=dist.group.WORLD, batch=Bq, seq_len=Tq)
+    tpm.load_from_unsharded(full)
+    gi = torch.Generator().manual_seed(3)
+    idx = torch.randint(0, 512, (Bq, Tq), generator=gi).to(dev)
+    tgt = idx.roll(-1, 1)
+    _, loss_tp = tpm(idx, tgt)
+    loss_tp.backward()
+    _, loss_full = full(idx, tgt)
+    loss_full.backward()
+    lt = loss_tp.detach().clone()
+    dist.all_reduce(lt)
+    res["llama_loss_tp"], res["llama_loss_full"] = float(lt) / world, float(loss_full)
+    ffl2 = cfg.n_ff // world
+    g_full = full.blocks[0].w_down.grad[:, rank * ffl2:(rank + 1) * ffl2] / world      # TP loss is a per-shard mean
+    res["llama_dw_rel"] = rel(tpm.blocks[0].w_down.weight.grad, g_full)
     # ---- timing against NCCL + library GEMM (device time, max over ranks)
     def timed(fn, iters=10):
         for _ in range(3):
