@@ -9,7 +9,9 @@
 //   with P = exp2(S*scale*log2e - lse*log2e), dS = P * (dP - delta), dP = dO V^T,
 //   delta = rowsum(O * dO) from a small pre-pass kernel.
 //
-// Thread/TMEM mapping as in the forward kernel: thread t of warps 0..3 owns score row t; P and
+// Thread/TMEM mapping: score row r is owned by lane r % 32 of the two warps with warp % 4 == r / 32; the one with
+// warp < 4 handles columns 0..63 of the tile, the other columns 64..127 (the softmax phase is latency bound, so
+// eight warps finish it in about half the time of four).  P and
 // dS go to the swizzled staging tiles, which serve as MN-major A operands (transposed use)
 // in dkdv and as a K-major A operand in dq.  The reference has no attention backward at all
 // (its head reshapes detach the graph, src/nn/attention.rs:255-289).
@@ -29,6 +31,10 @@ struct AttnBwdParams {
   long long dq_sb, dq_st, dq_sh, dk_sb, dk_st, dk_sh, dv_sb, dv_st, dv_sh;
   int* status;
 };
+
+// 8 softmax warps (two column halves x four TMEM lane quarters) + 1 control warp (TMA + MMA issue, TMEM owner).
+constexpr int ATT_BWD_THREADS = 288;
+constexpr int ATT_BWD_CTRL_WARP = 8;
 
 // --------------------------------------------------------------------- delta pre-pass
 // delta[b][h][t] = sum_d o[b][t][h][d] * do[b][t][h][d].  D/8 lanes per row, one 16-byte load
@@ -80,7 +86,7 @@ struct DkDvSmem {
 };
 
 template <int D>
-__global__ void __launch_bounds__(160, 1)
+__global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q,
                      const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v,
@@ -118,13 +124,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q,
       mbar_init(&qdo_empty[s], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 128);
+    mbar_init(pds_full, 256);
     mbar_init(pds_empty, 1);
     mbar_init(done, 1);
     ctl->abort = 0;
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == ATT_BWD_CTRL_WARP) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -144,7 +150,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q,
   const int per_head = max(0, n_q - i_start);
   const int n_it = per_head * group;
 
-  if (warp == 4) {
+  if (warp == ATT_BWD_CTRL_WARP) {
     if (lane == 0 && n_it > 0) {
       constexpr uint32_t idesc_S = make_idesc_f16(128, 128, false, false, true);
       constexpr uint32_t idesc_T = make_idesc_f16(128, D, true, true, true);  // P^T dO, dS^T Q
@@ -228,8 +234,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q,
       if (ok) umma_commit(done);
     }
   } else {
-    const int row = warp * 32 + lane;
-    const uint32_t lane_sel = uint32_t(warp * 32) << 16;
+    // warps 0..3 take score columns 0..63, warps 4..7 columns 64..127 of the same 128 rows
+    const int quarter = warp & 3, chalf = warp >> 2;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_sel = uint32_t(quarter * 32) << 16;
     uint8_t* sP = smem + S::OFF_P;
     uint8_t* sDS = smem + S::OFF_DS;
     bool ok = true;
@@ -250,20 +258,25 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q,
         break;
       }
       tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rp[32];
-        __syncwarp();
-        tmem_ld_32x32b_x32(tmem_S + lane_sel + c * 32, rs);
-        tmem_ld_32x32b_x32(tmem_dP + lane_sel + c * 32, rp);
-        tmem_ld_wait();
+      // all four TMEM loads of this thread's 64 columns are issued before the single wait
+      uint32_t rs[2][32], rp[2][32];
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        tmem_ld_32x32b_x32(tmem_S + lane_sel + (chalf * 2 + u) * 32, rs[u]);
+        tmem_ld_32x32b_x32(tmem_dP + lane_sel + (chalf * 2 + u) * 32, rp[u]);
+      }
+      tmem_ld_wait();
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int c = chalf * 2 + u;
         float pv[32], ds[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const bool vis = row_ok && (k0 + c * 32 + i <= limit);
-          const float e = vis ? exp2f(__uint_as_float(rs[i]) * p.scale_log2 - lse2) : 0.f;
+          const float e = vis ? ex2_approx(__uint_as_float(rs[u][i]) * p.scale_log2 - lse2) : 0.f;
           pv[i] = e;
-          ds[i] = e * (__uint_as_float(rp[i]) - dl);
+          ds[i] = e * (__uint_as_float(rp[u][i]) - dl);
         }
         stage_row_chunk_bf16(sP, row, c * 32, pv);
         stage_row_chunk_bf16(sDS, row, c * 32, ds);
@@ -277,7 +290,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tc_fence_after();
     const int kr = k0 + row;
 #pragma unroll 1
-    for (int which = 0; which < 2; ++which) {
+    for (int which = chalf; which < chalf + 1; ++which) {  // column half 0 writes dV, half 1 writes dK
       const uint32_t src = which == 0 ? tmem_dV : tmem_dK;
       const float mul = which == 0 ? 1.f : p.scale;
       __nv_bfloat16* dst =
@@ -317,7 +330,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q,
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == ATT_BWD_CTRL_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
@@ -339,7 +352,7 @@ struct DqSmem {
 };
 
 template <int D>
-__global__ void __launch_bounds__(160, 1)
+__global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v,
@@ -377,13 +390,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q,
       mbar_init(&kv_empty[s], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(ds_full, 128);
+    mbar_init(ds_full, 256);
     mbar_init(ds_empty, 1);
     mbar_init(done, 1);
     ctl->abort = 0;
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == ATT_BWD_CTRL_WARP) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -402,7 +415,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q,
     n_kv = last_col < 0 ? 0 : min(n_kv, last_col / ATT_BN + 1);
   }
 
-  if (warp == 4) {
+  if (warp == ATT_BWD_CTRL_WARP) {
     if (lane == 0 && n_kv > 0) {
       constexpr uint32_t idesc_S = make_idesc_f16(128, 128, false, false, true);
       constexpr uint32_t idesc_Q = make_idesc_f16(128, D, false, true, true);  // dS @ K
@@ -472,10 +485,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q,
       if (ok) umma_commit(done);
     }
   } else {
-    const int row = warp * 32 + lane;
+    const int quarter = warp & 3, chalf = warp >> 2;
+    const int row = quarter * 32 + lane;
     const int qi = q0 + row;
     const bool row_ok = qi < p.Tq;
-    const uint32_t lane_sel = uint32_t(warp * 32) << 16;
+    const uint32_t lane_sel = uint32_t(quarter * 32) << 16;
     uint8_t* sDS = smem + S::OFF_DS;
     const long long sidx = ((long long)b * p.H + h) * p.Tq + qi;
     const float lse2 = row_ok ? p.lse[sidx] * 1.4426950408889634f : 0.f;
@@ -492,19 +506,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q,
         break;
       }
       tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rp[32];
-        __syncwarp();
-        tmem_ld_32x32b_x32(tmem_S + lane_sel + c * 32, rs);
-        tmem_ld_32x32b_x32(tmem_dP + lane_sel + c * 32, rp);
-        tmem_ld_wait();
+      uint32_t rs[2][32], rp[2][32];
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        tmem_ld_32x32b_x32(tmem_S + lane_sel + (chalf * 2 + u) * 32, rs[u]);
+        tmem_ld_32x32b_x32(tmem_dP + lane_sel + (chalf * 2 + u) * 32, rp[u]);
+      }
+      tmem_ld_wait();
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int c = chalf * 2 + u;
         float ds[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const bool vis = row_ok && (j * ATT_BN + c * 32 + i <= limit);
-          const float e = vis ? exp2f(__uint_as_float(rs[i]) * p.scale_log2 - lse2) : 0.f;
-          ds[i] = e * (__uint_as_float(rp[i]) - dl);
+          const float e = vis ? ex2_approx(__uint_as_float(rs[u][i]) * p.scale_log2 - lse2) : 0.f;
+          ds[i] = e * (__uint_as_float(rp[u][i]) - dl);
         }
         stage_row_chunk_bf16(sDS, row, c * 32, ds);
       }
@@ -517,7 +535,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q,
     __nv_bfloat16* dst =
         p.dq + (long long)b * p.dq_sb + (long long)qi * p.dq_st + (long long)h * p.dq_sh;
 #pragma unroll 1
-    for (int c = 0; c < D / 32; ++c) {
+    for (int c = chalf * (D / 64); c < (chalf + 1) * (D / 64); ++c) {
       uint32_t r[32];
       if (n_kv > 0 && ok) {
         __syncwarp();
@@ -548,7 +566,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q,
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == ATT_BWD_CTRL_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
@@ -598,12 +616,12 @@ static void launch_bwd(const AttnArgs& a, cudaStream_t stream) {
   p.status = status_word(device);
   {
     dim3 grid((a.Tk + ATT_BN - 1) / ATT_BN, a.Hkv, a.B);
-    k1<<<grid, 160, DkDvSmem<D>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+    k1<<<grid, ATT_BWD_THREADS, DkDvSmem<D>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
     RT_LAUNCH_CHECK();
   }
   {
     dim3 grid((a.Tq + ATT_BM - 1) / ATT_BM, a.H, a.B);
-    k2<<<grid, 160, DqSmem<D>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+    k2<<<grid, ATT_BWD_THREADS, DqSmem<D>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
     RT_LAUNCH_CHECK();
   }
 }

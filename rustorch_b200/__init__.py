@@ -1,7 +1,14 @@
 """rustorch_b200: a Blackwell-native (sm_100a) deep-learning framework with the API surface of
 RusTorch.  PyTorch is the tensor/autograd substrate; hot paths are hand-written CUDA kernels
 (tcgen05 / TMEM / TMA) loaded from the in-tree ``_C`` extension.
+
+The top-level names are those of the reference's Python bindings (python/src/lib.rs:44-1484 and
+src/python/mod.rs:51-115): ``Tensor Variable Linear Conv2d ... SGD Adam tensor zeros ones no_grad grad``,
+plus ``Device functional DataLoader Trainer DistributedDataParallel init_distributed ...``.  They resolve lazily,
+so ``import rustorch_b200`` stays cheap.  ``import rustorch`` works through the alias package of the same tree.
 """
+import importlib
+
 from . import _native  # noqa: F401
 
 __version__ = "0.1.0"
@@ -10,3 +17,48 @@ __version__ = "0.1.0"
 def native_available() -> bool:
     """True when the compiled sm_100a kernel library is importable."""
     return _native.available()
+
+
+_LAZY = {
+    # tensors / autograd
+    "Tensor": "tensor", "tensor": "tensor", "zeros": "tensor", "ones": "tensor", "Variable": "autograd", "no_grad": "autograd",
+    "enable_grad": "autograd", "grad": "autograd", "gradcheck": "autograd", "jacobian": "autograd", "hessian": "autograd",
+    # layers and losses
+    **{n: "nn" for n in ("Module", "Parameter", "Sequential", "Linear", "Conv1d", "Conv2d", "Conv3d", "ConvTranspose2d", "MaxPool2d",
+                         "AvgPool2d", "BatchNorm1d", "BatchNorm2d", "LayerNorm", "RMSNorm", "GroupNorm", "Dropout", "Flatten", "Embedding",
+                         "ReLU", "Sigmoid", "Tanh", "GELU", "Softmax", "LeakyReLU", "MSELoss", "CrossEntropyLoss", "LSTM", "GRU", "RNN",
+                         "MultiheadAttention", "Transformer", "TransformerEncoder", "TransformerEncoderLayer")},
+    # optimizers / schedulers
+    **{n: "optim" for n in ("SGD", "Adam", "AdamW", "RMSprop", "AdaGrad", "NAdam", "RAdam", "Adamax", "LAMB", "AdaBound", "LBFGS", "StepLR",
+                            "ExponentialLR", "CosineAnnealingLR", "FusedAdamW", "FusedSGD")},
+    # data / training / models
+    **{n: "data" for n in ("Dataset", "TensorDataset", "DataLoader", "RandomSampler", "SequentialSampler", "BatchSampler")},
+    **{n: "training" for n in ("Trainer", "TrainerConfig", "TrainerBuilder", "EarlyStopping", "CheckpointManager")},
+    "TrainingHistory": "models.high_level", "Model": "models.high_level", "ModelBuilder": "models.high_level",
+    # utils of the binding
+    **{n: "python_api" for n in ("Device", "Config", "ModelSerializer", "ModelComparator", "Transform", "Transforms", "DistributedConfig",
+                                 "init_distributed", "cleanup_distributed", "set_seed", "cuda_is_available", "get_system_info")},
+    "Profiler": "profiler", "Plotter": "visualization", "ModelVisualizer": "visualization", "TensorStats": "visualization",
+    # distributed
+    **{n: "distributed" for n in ("DistributedDataParallel", "DistributedBackend", "DistributedSampler", "get_world_size", "get_rank",
+                                  "is_master", "DataParallel")},
+}
+_SUBMODULES = ("nn", "optim", "data", "training", "models", "distributed", "formats", "llm", "amp", "profiler", "debug", "validation",
+               "tensorboard", "visualization", "vision", "distributions", "special", "quantization", "sparse", "memory", "gpu", "execution",
+               "model_import", "convert", "model_hub", "jit", "cli", "autograd", "ops", "utils", "parallel")
+
+
+def __getattr__(name):
+    if name == "functional":
+        from .nn import layers
+        return layers
+    if name in _SUBMODULES:
+        return importlib.import_module(f"{__name__}.{name}")
+    mod = _LAZY.get(name)
+    if mod is None:
+        raise AttributeError(f"module '{__name__}' has no attribute '{name}'")
+    return getattr(importlib.import_module(f"{__name__}.{mod}"), name)
+
+
+def __dir__():
+    return sorted(list(globals()) + list(_LAZY) + list(_SUBMODULES) + ["functional"])

@@ -1,0 +1,203 @@
+"""The small helper classes of the reference's Python binding that have no other home
+(src/python/utils.rs, training.rs, distributed.rs:114-428, data.rs): ``Device``, ``Config``, ``ModelSerializer``,
+``ModelComparator``, ``Transform(s)``, ``DistributedConfig`` and the ``init_distributed`` family (real here: they
+drive ``torch.distributed``; the reference's print and return)."""
+from __future__ import annotations
+
+import os
+import platform
+import random
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+
+class Device:
+    """``Device("cpu")``, ``Device("cuda", 1)``, ``Device.cuda(0)``; ``metal`` is accepted as a name and reports
+    unavailable."""
+
+    def __init__(self, kind: str = "cpu", index: int = 0):
+        kind = kind.lower()
+        if ":" in kind:
+            kind, idx = kind.split(":")
+            index = int(idx)
+        if kind not in ("cpu", "cuda", "metal"):
+            raise ValueError(f"unknown device type '{kind}'")
+        self.type, self.index = kind, index
+
+    @classmethod
+    def cpu(cls) -> "Device":
+        return cls("cpu")
+
+    @classmethod
+    def cuda(cls, index: int = 0) -> "Device":
+        return cls("cuda", index)
+
+    @classmethod
+    def metal(cls, index: int = 0) -> "Device":
+        return cls("metal", index)
+
+    def is_available(self) -> bool:
+        return self.type == "cpu" or (self.type == "cuda" and torch.cuda.is_available() and self.index < torch.cuda.device_count())
+
+    def torch(self) -> torch.device:
+        if self.type == "metal":
+            raise RuntimeError("Metal devices do not exist on this platform")
+        return torch.device(self.type, self.index) if self.type == "cuda" else torch.device("cpu")
+
+    def __repr__(self) -> str:
+        return f"Device({self.type}:{self.index})" if self.type != "cpu" else "Device(cpu)"
+
+    def __eq__(self, other) -> bool:
+        return isinstance(other, Device) and (self.type, self.index) == (other.type, other.index)
+
+
+class Config:
+    """String-keyed settings with typed getters and environment override (``RUSTORCH_<KEY>``)."""
+
+    def __init__(self, **values):
+        self._v: Dict[str, object] = dict(values)
+
+    def set(self, key: str, value) -> None:
+        self._v[key] = value
+
+    def get(self, key: str, default=None):
+        env = os.environ.get("RUSTORCH_" + key.upper())
+        if env is not None:
+            return env
+        return self._v.get(key, default)
+
+    def get_int(self, key: str, default: int = 0) -> int:
+        return int(self.get(key, default))
+
+    def get_float(self, key: str, default: float = 0.0) -> float:
+        return float(self.get(key, default))
+
+    def get_bool(self, key: str, default: bool = False) -> bool:
+        v = self.get(key, default)
+        return v if isinstance(v, bool) else str(v).lower() in ("1", "true", "yes", "on")
+
+    def to_dict(self) -> Dict[str, object]:
+        return dict(self._v)
+
+
+def set_seed(seed: int) -> None:
+    random.seed(seed)
+    np.random.seed(seed % (1 << 32))
+    torch.manual_seed(seed)
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed_all(seed)
+
+
+def cuda_is_available() -> bool:
+    return torch.cuda.is_available()
+
+
+def get_system_info() -> Dict[str, object]:
+    info = {"platform": platform.platform(), "python": platform.python_version(), "torch": torch.__version__,
+            "cpu_count": os.cpu_count(), "cuda_available": torch.cuda.is_available(), "cuda_devices": []}
+    if torch.cuda.is_available():
+        for i in range(torch.cuda.device_count()):
+            p = torch.cuda.get_device_properties(i)
+            info["cuda_devices"].append({"index": i, "name": p.name, "memory_gb": round(p.total_memory / 2 ** 30, 1),
+                                         "sms": p.multi_processor_count, "capability": f"{p.major}.{p.minor}"})
+    from . import _native
+    info["native_kernels"] = _native.available()
+    return info
+
+
+class ModelSerializer:
+    @staticmethod
+    def save(model: torch.nn.Module, path: str, fmt: str = "rustorch") -> None:
+        from .models.high_level import ModelSaver, SerializationFormat
+        ModelSaver.save(model, path, SerializationFormat(fmt) if not isinstance(fmt, SerializationFormat) else fmt)
+
+    @staticmethod
+    def load(model: torch.nn.Module, path: str, strict: bool = True) -> torch.nn.Module:
+        from .models.high_level import ModelLoader
+        return ModelLoader.load(model, path, strict)
+
+
+class ModelComparator:
+    """Parameter-wise and output-wise comparison of two models."""
+
+    @staticmethod
+    def compare_parameters(a: torch.nn.Module, b: torch.nn.Module, atol: float = 0.0) -> Dict[str, object]:
+        sa, sb = a.state_dict(), b.state_dict()
+        missing = sorted(set(sa) ^ set(sb))
+        diffs = {k: float((sa[k].float() - sb[k].float()).abs().max()) for k in sa if k in sb and sa[k].shape == sb[k].shape}
+        shape_mismatch = [k for k in sa if k in sb and sa[k].shape != sb[k].shape]
+        return {"identical": not missing and not shape_mismatch and all(v <= atol for v in diffs.values()), "missing": missing,
+                "shape_mismatch": shape_mismatch, "max_abs_diff": max(diffs.values(), default=0.0), "per_parameter": diffs}
+
+    @staticmethod
+    def compare_outputs(a: torch.nn.Module, b: torch.nn.Module, x: torch.Tensor) -> Dict[str, float]:
+        with torch.no_grad():
+            ya, yb = a(x).float(), b(x).float()
+        d = (ya - yb).abs()
+        return {"max_abs_diff": float(d.max()), "mean_abs_diff": float(d.mean()),
+                "cosine": float(torch.nn.functional.cosine_similarity(ya.flatten(), yb.flatten(), dim=0))}
+
+
+class Transform:
+    def __init__(self, fn: Callable[[torch.Tensor], torch.Tensor], name: str = "transform"):
+        self.fn, self.name = fn, name
+
+    def __call__(self, x):
+        return self.fn(x)
+
+
+class Transforms:
+    """Factory with the binding's names: ``normalize resize random_crop random_horizontal_flip compose``."""
+
+    @staticmethod
+    def normalize(mean: Sequence[float], std: Sequence[float]) -> Transform:
+        from .vision import Normalize
+        return Transform(Normalize(mean, std), "normalize")
+
+    @staticmethod
+    def resize(size) -> Transform:
+        from .vision import Resize
+        return Transform(Resize(size), "resize")
+
+    @staticmethod
+    def random_crop(size, padding: int = 0) -> Transform:
+        from .vision import RandomCrop
+        return Transform(RandomCrop(size, padding), "random_crop")
+
+    @staticmethod
+    def random_horizontal_flip(p: float = 0.5) -> Transform:
+        from .vision import RandomHorizontalFlip
+        return Transform(RandomHorizontalFlip(p), "random_horizontal_flip")
+
+    @staticmethod
+    def compose(ts: Sequence[Callable]) -> Transform:
+        from .vision import Compose
+        return Transform(Compose(ts), "compose")
+
+
+@dataclass
+class DistributedConfig:
+    backend: str = "nccl"
+    init_method: str = "env://"
+    world_size: int = 1
+    rank: int = 0
+    timeout_s: float = 1800.0
+    master_addr: str = "127.0.0.1"
+    master_port: int = 29500
+
+
+def init_distributed(config: Optional[DistributedConfig] = None) -> None:
+    from .distributed import api
+    c = config or DistributedConfig(backend="nccl" if torch.cuda.is_available() else "gloo",
+                                    world_size=int(os.environ.get("WORLD_SIZE", "1")), rank=int(os.environ.get("RANK", "0")))
+    os.environ.setdefault("MASTER_ADDR", c.master_addr)
+    os.environ.setdefault("MASTER_PORT", str(c.master_port))
+    api.init_process_group(c.backend, c.init_method, c.world_size, c.rank, c.timeout_s)
+
+
+def cleanup_distributed() -> None:
+    from .distributed import api
+    api.destroy_process_group()

@@ -788,3 +788,17 @@ def ones(shape, **kw) -> Tensor:
 def tensor_nd(nested) -> Tensor:
     """Nested-list literal, the proc-macro ``tensor_nd!`` (rustorch-macros/src/lib.rs:43-68)."""
     return Tensor(nested)
+
+
+# ``rustorch.tensor`` is both this module and the constructor function of the binding: importing the submodule binds the
+# module object to that name on the package, so the module itself is made callable and forwards to ``tensor()``.
+import sys as _sys
+import types as _types
+
+
+class _CallableModule(_types.ModuleType):
+    def __call__(self, data, shape=None, **kw):
+        return tensor(data, shape, **kw)
+
+
+_sys.modules[__name__].__class__ = _CallableModule
