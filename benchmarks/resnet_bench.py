@@ -1,0 +1,137 @@
+"""ResNet-18 image classifier, data-parallel bf16 training (BASELINE config 2).
+
+  python benchmarks/resnet_bench.py --steps 10 --warmup 3 [--batch 256] [--impl ours|library]
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P benchmarks/resnet_bench.py ...
+
+Input 3x224x224 i.i.d. N(0,1), labels uniform in [0, 1000), per-GPU batch 256, SGD momentum 0.9 lr 0.1 wd 1e-4.
+``ours``: channels-last bf16 model with this framework's BatchNorm (+ residual + ReLU fused), activation and loss
+kernels, fused flat SGD and bucketed DDP; the convolutions themselves run through cuDNN (library call; the
+implicit-GEMM tcgen05 convolution is not written yet, which the JSON line states).  ``library``: torchvision-style
+stock modules + ``torch.optim.SGD`` + PyTorch DDP.  Prints one JSON line: images/s of the whole job, device time,
+max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def convert_bn(module: nn.Module) -> nn.Module:
+    """Swap ``nn.BatchNorm2d`` for the framework's BatchNorm2d (native kernels), keeping parameters."""
+    from rustorch_b200.nn import BatchNorm2d
+    for name, child in list(module.named_children()):
+        if isinstance(child, nn.BatchNorm2d) and not isinstance(child, BatchNorm2d):
+            new = BatchNorm2d(child.num_features, child.eps, child.momentum, child.affine, child.track_running_stats)
+            new.load_state_dict(child.state_dict())
+            setattr(module, name, new)
+        else:
+            convert_bn(child)
+    return module
+
+
+def fused_block_forward(self, x):
+    """BasicBlock forward with the tail ``relu(bn2(conv2(.)) + identity)`` as one BatchNorm kernel."""
+    identity = x if self.downsample is None else self.downsample(x)
+    out = self.bn1(self.conv1(x), relu=True)
+    return self.bn2(self.conv2(out), residual=identity, relu=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--impl", default="ours", choices=["ours", "library"])
+    a = ap.parse_args()
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from rustorch_b200 import _native
+    from rustorch_b200.models import cnn
+    from rustorch_b200.utils.clocks import ClockSampler
+    torch.manual_seed(0)
+    model = cnn.resnet18(1000).to(dev).to(memory_format=torch.channels_last)
+    x = torch.randn(a.batch, 3, 224, 224, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    y = torch.randint(0, 1000, (a.batch,), device=dev)
+    if a.impl == "ours":
+        convert_bn(model)
+        for m in model.modules():
+            if isinstance(m, cnn.BasicBlock):
+                m.forward = fused_block_forward.__get__(m)
+        model = model.to(torch.bfloat16)
+        from rustorch_b200.optim.flat import FlatParams, FusedSGD
+        flat = FlatParams(model, decay_filter=lambda n, p: p.dim() > 1)
+        opt = FusedSGD(flat, lr=0.1, momentum=0.9, weight_decay=1e-4)
+        ddp = None
+        if world > 1:
+            from rustorch_b200.distributed.ddp_flat import FlatDDP
+            ddp = FlatDDP(flat, bucket_cap_mb=25.0)
+
+        def step():
+            out = model(x)
+            loss = F.cross_entropy(out.float(), y)
+            loss.backward()
+            flat.collect_autograd_grads()
+            if ddp is not None:
+                ddp.sync_gradients()
+            opt.step()
+            return loss
+    else:
+        model = model.to(torch.bfloat16)
+        opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
+        net = nn.parallel.DistributedDataParallel(model, device_ids=[local], bucket_cap_mb=25) if world > 1 else model
+
+        def step():
+            opt.zero_grad(set_to_none=True)
+            loss = F.cross_entropy(net(x).float(), y)
+            loss.backward()
+            opt.step()
+            return loss
+
+    for _ in range(a.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    l0 = _native.launch_count()
+    sampler = ClockSampler(local, 0.05)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        loss = step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t) / a.steps
+    _native.check_status()
+    out = {"metric": "train_images_per_s", "value": round(a.batch * world / (ms / 1e3), 1), "unit": "images/s", "n_gpus": world,
+           "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "dtype": "bf16",
+           "impl": a.impl, "data": "synthetic N(0,1) images, random-init weights",
+           "config": {"model": "resnet18 (channels-last)", "per_gpu_batch": a.batch, "image": "3x224x224", "optimizer": "SGD m0.9 lr0.1 wd1e-4",
+                      "parallelism": f"dp{world}", "convolutions": "cuDNN (library)" , "batchnorm_activation_loss_optimizer": "native" if a.impl == "ours" else "library"},
+           "clocks": clocks, "gpu_launches": _native.launch_count() - l0, "final_loss": round(float(loss), 4)}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

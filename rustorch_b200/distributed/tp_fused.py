@@ -62,15 +62,18 @@ class AllGatherGemm:
         self.epoch, self.timeout_s, self.n_comm = 0, timeout_s, n_comm
 
     def __call__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, x: Optional[torch.Tensor] = None,
-                 b_mn: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 b_mn: bool = False, out: Optional[torch.Tensor] = None, gather: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``gather``: where the kernel leaves the gathered input (default: this op's own buffer).  Layers that need
+        it again in backward pass their own, so that one op (symmetric shard + flags) can serve many layers."""
         if x is not None:
             self.x_shard.copy_(x.reshape(self.rows, self.K))
         N = weight.shape[1] if b_mn else weight.shape[0]
         if out is None:
             out = torch.empty(self.world * self.rows, N, dtype=torch.bfloat16, device=self.device)
         self.epoch += 1
-        _native.load(required=True).tp_ag_gemm(self.x_ptrs, self.flag_ptrs, self.gather, self.mb_ready, self.comm_done, weight, b_mn,
-                                               out, bias, self.rank, self.epoch, self.rows, self.timeout_s, self.n_comm)
+        _native.load(required=True).tp_ag_gemm(self.x_ptrs, self.flag_ptrs, self.gather if gather is None else gather, self.mb_ready,
+                                               self.comm_done, weight, b_mn, out, bias, self.rank, self.epoch, self.rows,
+                                               self.timeout_s, self.n_comm)
         return out
 
 
@@ -97,10 +100,23 @@ class GemmReduceScatter:
         return out
 
 
+_OPS = {}
+
+
+def shared_op(kind: str, rows: int, dim: int, device, group):
+    """One op object (symmetric buffers, flags, epoch counter) per (kind, rows, dim, group): layers of equal shape use
+    it one after the other, which the kernels' double buffering and end-of-kernel flags make safe.  A 32-layer model then
+    holds 4 sets of communication buffers instead of 128."""
+    key = (kind, rows, dim, str(torch.device(device)), id(group) if group is not None else None)
+    if key not in _OPS:
+        _OPS[key] = AllGatherGemm(rows, dim, device, group) if kind == "ag" else GemmReduceScatter(rows, dim, device, group)
+    return _OPS[key]
+
+
 class _ColumnParallelFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_shard, weight, bias, layer):
-        y = layer.ag(weight, bias, x=x_shard)
+        y = layer.ag(weight, bias, x=x_shard, gather=layer.gather)
         ctx.layer = layer
         ctx.save_for_backward(weight)
         ctx.has_bias = bias is not None
@@ -112,7 +128,7 @@ class _ColumnParallelFn(torch.autograd.Function):
         L = ctx.layer
         dy = dy.contiguous()
         # dW[N_local, K] = dy^T @ x_gathered : both operands read "MN-major", fp32 accumulate
-        dw = K.gemm(dy, L.ag.gather, a_mn=True, b_mn=True, out_dtype=torch.float32, split_k=4, accumulate=True)
+        dw = K.gemm(dy, L.gather, a_mn=True, b_mn=True, out_dtype=torch.float32, split_k=4, accumulate=True)
         db = dy.float().sum(0).to(weight.dtype) if ctx.has_bias else None
         # dx_shard[rows, K] = reduce_scatter(dy[M, N_local] @ W[N_local, K]) : W read as [K_red = N_local][N_out = K]
         dx = L.rs_bwd(dy, weight, b_mn=True)
@@ -155,8 +171,10 @@ class FusedColumnParallelLinear(nn.Module):
         self.in_features, self.out_features, self.out_local = in_features, out_features, out_features // W
         self.weight = nn.Parameter(torch.randn(self.out_local, in_features, device=device, dtype=torch.bfloat16) * init_std)
         self.bias = nn.Parameter(torch.zeros(self.out_local, device=device, dtype=torch.bfloat16)) if bias else None
-        self.ag = AllGatherGemm(rows_per_rank, in_features, device, g)
-        self.rs_bwd = GemmReduceScatter(rows_per_rank, in_features, device, g)
+        self.ag = shared_op("ag", rows_per_rank, in_features, device, g)
+        self.rs_bwd = shared_op("rs", rows_per_rank, in_features, device, g)
+        # this layer's gathered input, kept for its weight gradient
+        self.gather = torch.empty(W * rows_per_rank, in_features, dtype=torch.bfloat16, device=device)
 
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
         return _ColumnParallelFn.apply(x_shard, self.weight, self.bias, self)
@@ -176,8 +194,8 @@ class FusedRowParallelLinear(nn.Module):
         self.in_features, self.out_features, self.in_local = in_features, out_features, in_features // W
         self.weight = nn.Parameter(torch.randn(out_features, self.in_local, device=device, dtype=torch.bfloat16) * init_std)
         self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=torch.bfloat16)) if bias else None
-        self.rs = GemmReduceScatter(rows_per_rank, out_features, device, g)
-        self.ag_bwd = AllGatherGemm(rows_per_rank, out_features, device, g)
+        self.rs = shared_op("rs", rows_per_rank, out_features, device, g)
+        self.ag_bwd = shared_op("ag", rows_per_rank, out_features, device, g)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return _RowParallelFn.apply(x, self.weight, self.bias, self)

@@ -138,7 +138,7 @@ class LlamaBlock(nn.Module):
 
 class LlamaModel(nn.Module):
     """``forward(idx [B, T], targets) -> (logits or None, loss)``.  Under tensor parallelism every rank receives the
-    same ``idx``; the loss is the mean over this rank's token shard (average it over ranks for reporting)."""
+    same ``idx``; the returned loss is this rank's share of the global mean (sum it over ranks for reporting)."""
 
     def __init__(self, cfg: LlamaTrainConfig, device=None, dtype=None, tp_group=None, batch: int = 0, seq_len: int = 0):
         super().__init__()
@@ -178,8 +178,37 @@ class LlamaModel(nn.Module):
         logits = _linear(x, self.lm_head)
         if targets is None:
             return logits.view(-1, c.vocab_size), None
-        loss = F.cross_entropy(logits.float(), targets.reshape(-1)[lo:hi])
+        # under tensor parallelism each rank owns 1/W of the tokens: its loss term is scaled so that the terms of all
+        # ranks add up to the global mean (gradients of sharded weights are then exact, see sync_replicated_grads)
+        loss = F.cross_entropy(logits.float(), targets.reshape(-1)[lo:hi]) / self.world
         return logits, loss
+
+    def replicated_parameters(self):
+        """Parameters every rank holds in full (embeddings, head, norm weights): their gradients are partial sums
+        over this rank's tokens."""
+        yield self.tok_emb
+        yield self.lm_head
+        yield self.out_norm
+        for b in self.blocks:
+            yield b.attn_norm
+            yield b.ffn_norm
+
+    def sync_replicated_grads(self) -> None:
+        """Sum the gradients of the replicated parameters over the tensor-parallel group (call after backward)."""
+        if self.world == 1:
+            return
+        import torch.distributed as dist
+        small = [p.grad for p in self.replicated_parameters() if p.grad is not None and p.grad.numel() < (1 << 20)]
+        if small:
+            flat = torch.cat([g.reshape(-1).float() for g in small])
+            dist.all_reduce(flat, group=self.tp_group)
+            o = 0
+            for g in small:
+                g.copy_(flat[o:o + g.numel()].view_as(g))
+                o += g.numel()
+        for p in self.replicated_parameters():
+            if p.grad is not None and p.grad.numel() >= (1 << 20):
+                dist.all_reduce(p.grad, group=self.tp_group)
 
     @torch.no_grad()
     def load_from_unsharded(self, full: "LlamaModel") -> None:

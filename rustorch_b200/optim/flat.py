@@ -77,6 +77,17 @@ class FlatParams:
                 p.main_grad = self.grad[o:o + k]
                 p.grad = None
 
+    def collect_autograd_grads(self) -> int:
+        """Fold ``p.grad`` tensors written by ordinary autograd (modules that do not accumulate into ``main_grad``
+        themselves) into the flat fp32 gradient buffer and drop them.  Returns how many were folded."""
+        n = 0
+        for _, p, o, k in self.entries:
+            if p.grad is not None:
+                self.grad[o:o + k].add_(p.grad.reshape(-1))
+                p.grad = None
+                n += 1
+        return n
+
     def groups(self) -> List[Tuple[int, int, bool]]:
         """[(start, stop, decays)] contiguous ranges."""
         out = []
@@ -137,6 +148,7 @@ class FusedAdamW(_FusedBase):
 
     def step(self, clip_grad_norm: Optional[float] = None) -> None:
         f = self.flat
+        f.collect_autograd_grads()
         self.step_count += 1
         b1, b2 = self.betas
         bc1 = 1.0 - b1 ** self.step_count
@@ -202,6 +214,7 @@ class FusedSGD(_FusedBase):
 
     def step(self) -> None:
         f = self.flat
+        f.collect_autograd_grads()
         self.step_count += 1
         first = self.step_count == 1
         for start, stop, decays in f.groups():

@@ -80,14 +80,16 @@ def main():
     tgt = idx.roll(-1, 1)
     _, loss_tp = tpm(idx, tgt)
     loss_tp.backward()
+    tpm.sync_replicated_grads()
     _, loss_full = full(idx, tgt)
     loss_full.backward()
     lt = loss_tp.detach().clone()
     dist.all_reduce(lt)
-    res["llama_loss_tp"], res["llama_loss_full"] = float(lt) / world, float(loss_full)
+    res["llama_loss_tp"], res["llama_loss_full"] = float(lt), float(loss_full)
     ffl2 = cfg.n_ff // world
-    g_full = full.blocks[0].w_down.grad[:, rank * ffl2:(rank + 1) * ffl2] / world      # TP loss is a per-shard mean
-    res["llama_dw_rel"] = rel(tpm.blocks[0].w_down.weight.grad, g_full)
+    res["llama_dw_rel"] = rel(tpm.blocks[0].w_down.weight.grad, full.blocks[0].w_down.grad[:, rank * ffl2:(rank + 1) * ffl2])
+    res["llama_dnorm_rel"] = rel(tpm.blocks[1].attn_norm.grad, full.blocks[1].attn_norm.grad)
+    res["llama_dhead_rel"] = rel(tpm.lm_head.grad, full.lm_head.grad)
     # ---- timing against NCCL + library GEMM (device time, max over ranks)
     def timed(fn, iters=10):
         for _ in range(3):
