@@ -4,10 +4,10 @@
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P benchmarks/resnet_bench.py ...
 
 Input 3x224x224 i.i.d. N(0,1), labels uniform in [0, 1000), per-GPU batch 256, SGD momentum 0.9 lr 0.1 wd 1e-4.
-``ours``: channels-last bf16 model with this framework's BatchNorm (+ residual + ReLU fused), activation and loss
-kernels, fused flat SGD and bucketed DDP; the convolutions themselves run through cuDNN (library call; the
-implicit-GEMM tcgen05 convolution is not written yet, which the JSON line states).  ``library``: torchvision-style
-stock modules + ``torch.optim.SGD`` + PyTorch DDP.  Prints one JSON line: images/s of the whole job, device time,
+``ours``: channels-last bf16 model on this framework's kernels: implicit-GEMM tcgen05 convolutions (forward, weight
+gradient, stride-1 input gradient; the 3-channel stem and the strided input gradients use the library), BatchNorm
+(+ residual + ReLU fused), fused flat SGD and bucketed DDP.  ``library``: the same topology from stock ``torch.nn``
+modules + ``torch.optim.SGD`` + PyTorch DDP.  Prints one JSON line: images/s of the whole job, device time,
 max over ranks.
 """
 from __future__ import annotations
@@ -26,24 +26,25 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 
-def convert_bn(module: nn.Module) -> nn.Module:
-    """Swap ``nn.BatchNorm2d`` for the framework's BatchNorm2d (native kernels), keeping parameters."""
-    from rustorch_b200.nn import BatchNorm2d
-    for name, child in list(module.named_children()):
-        if isinstance(child, nn.BatchNorm2d) and not isinstance(child, BatchNorm2d):
-            new = BatchNorm2d(child.num_features, child.eps, child.momentum, child.affine, child.track_running_stats)
-            new.load_state_dict(child.state_dict())
-            setattr(module, name, new)
-        else:
-            convert_bn(child)
-    return module
+class _StockBlock(nn.Module):
+    def __init__(self, i, o, stride):
+        super().__init__()
+        self.c1, self.b1 = nn.Conv2d(i, o, 3, stride, 1, bias=False), nn.BatchNorm2d(o)
+        self.c2, self.b2 = nn.Conv2d(o, o, 3, 1, 1, bias=False), nn.BatchNorm2d(o)
+        self.down = None if stride == 1 and i == o else nn.Sequential(nn.Conv2d(i, o, 1, stride, bias=False), nn.BatchNorm2d(o))
+
+    def forward(self, x):
+        idt = x if self.down is None else self.down(x)
+        return F.relu(self.b2(self.c2(F.relu(self.b1(self.c1(x))))) + idt)
 
 
-def fused_block_forward(self, x):
-    """BasicBlock forward with the tail ``relu(bn2(conv2(.)) + identity)`` as one BatchNorm kernel."""
-    identity = x if self.downsample is None else self.downsample(x)
-    out = self.bn1(self.conv1(x), relu=True)
-    return self.bn2(self.conv2(out), residual=identity, relu=True)
+def stock_resnet18(num_classes=1000) -> nn.Module:
+    """The same topology from stock ``torch.nn`` modules (cuDNN convolutions and BatchNorm): the library arm."""
+    layers, i = [nn.Conv2d(3, 64, 7, 2, 3, bias=False), nn.BatchNorm2d(64), nn.ReLU(), nn.MaxPool2d(3, 2, 1)], 64
+    for o, stride in ((64, 1), (64, 1), (128, 2), (128, 1), (256, 2), (256, 1), (512, 2), (512, 1)):
+        layers.append(_StockBlock(i, o, stride))
+        i = o
+    return nn.Sequential(*layers, nn.AdaptiveAvgPool2d(1), nn.Flatten(), nn.Linear(512, num_classes))
 
 
 def main():
@@ -62,14 +63,10 @@ def main():
     from rustorch_b200.models import cnn
     from rustorch_b200.utils.clocks import ClockSampler
     torch.manual_seed(0)
-    model = cnn.resnet18(1000).to(dev).to(memory_format=torch.channels_last)
+    model = (cnn.resnet18(1000) if a.impl == "ours" else stock_resnet18(1000)).to(dev).to(memory_format=torch.channels_last)
     x = torch.randn(a.batch, 3, 224, 224, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
     y = torch.randint(0, 1000, (a.batch,), device=dev)
     if a.impl == "ours":
-        convert_bn(model)
-        for m in model.modules():
-            if isinstance(m, cnn.BasicBlock):
-                m.forward = fused_block_forward.__get__(m)
         model = model.to(torch.bfloat16)
         from rustorch_b200.optim.flat import FlatParams, FusedSGD
         flat = FlatParams(model, decay_filter=lambda n, p: p.dim() > 1)
@@ -124,7 +121,7 @@ def main():
            "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "dtype": "bf16",
            "impl": a.impl, "data": "synthetic N(0,1) images, random-init weights",
            "config": {"model": "resnet18 (channels-last)", "per_gpu_batch": a.batch, "image": "3x224x224", "optimizer": "SGD m0.9 lr0.1 wd1e-4",
-                      "parallelism": f"dp{world}", "convolutions": "cuDNN (library)" , "batchnorm_activation_loss_optimizer": "native" if a.impl == "ours" else "library"},
+                      "parallelism": f"dp{world}", "convolutions": "implicit-GEMM tcgen05 (stem + strided dgrad: library)" if a.impl == "ours" else "cuDNN"},
            "clocks": clocks, "gpu_launches": _native.launch_count() - l0, "final_loss": round(float(loss), 4)}
     if rank == 0:
         print(json.dumps(out), flush=True)

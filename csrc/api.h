@@ -165,6 +165,21 @@ void ddp_bucket_adamw(const DdpBucketArgs& a, int n_ctas, cudaStream_t stream);
 void ddp_wait_end(const int* flags, int n_slots, int world, int rank, int epoch,
                   unsigned long long timeout_ns, int* status, cudaStream_t stream);
 
+// ------------------------------------------------------------------ conv/conv2d_igemm.cu
+// Channels-last bf16 tensors: x [N][H][W][Cin], w [Cout][KH][KW][Cin], out / dy [N][OH][OW][Cout]; dw fp32 like w.
+struct Conv2dArgs {
+  int N, H, W, Cin, Cout, KH, KW, stride, pad;
+  const void* x;
+  const void* w;
+  void* out;
+  const void* bias;  // bf16 [Cout] or null (forward)
+  const void* dy;    // wgrad
+  float* dw;         // wgrad: accumulated into (zero it first)
+};
+bool conv2d_igemm_supported(int Cin, int Cout, int KH, int KW, int stride);
+void conv2d_fwd(const Conv2dArgs& a, cudaStream_t stream);
+void conv2d_wgrad(const Conv2dArgs& a, cudaStream_t stream);
+
 // ------------------------------------------------------- elementwise/elementwise.cu, softmax.cu
 enum DType : int { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2 };
 enum BinaryOp : int { EW_ADD = 0, EW_SUB, EW_MUL, EW_DIV, EW_MAX, EW_MIN, EW_POW };

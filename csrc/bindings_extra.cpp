@@ -320,6 +320,44 @@ void tp_gemm_rs(const Tensor& x, const Tensor& weight, bool b_mn, const std::vec
   rt::tp_gemm(a, cur_stream(x.device().index()));
 }
 
+// x [N,H,W,Cin], w [Cout,KH,KW,Cin], out [N,OH,OW,Cout]: contiguous bf16 (channels-last views of NCHW tensors).
+void conv2d_fwd(const Tensor& x, const Tensor& w, Tensor& out, const c10::optional<Tensor>& bias, int64_t stride, int64_t pad) {
+  check_bf16(x, "conv2d x");
+  check_bf16(w, "conv2d w");
+  check_bf16(out, "conv2d out");
+  TORCH_CHECK(x.dim() == 4 && w.dim() == 4 && out.dim() == 4 && x.is_contiguous() && w.is_contiguous() && out.is_contiguous(),
+              "conv2d: contiguous NHWC / OHWI tensors required");
+  rt::Conv2dArgs a{};
+  a.N = int(x.size(0)); a.H = int(x.size(1)); a.W = int(x.size(2)); a.Cin = int(x.size(3));
+  a.Cout = int(w.size(0)); a.KH = int(w.size(1)); a.KW = int(w.size(2));
+  TORCH_CHECK(w.size(3) == a.Cin, "conv2d: weight / input channel mismatch");
+  a.stride = int(stride); a.pad = int(pad);
+  const int64_t OH = (a.H + 2 * a.pad - a.KH) / a.stride + 1, OW = (a.W + 2 * a.pad - a.KW) / a.stride + 1;
+  TORCH_CHECK(out.size(0) == a.N && out.size(1) == OH && out.size(2) == OW && out.size(3) == a.Cout, "conv2d: bad output shape");
+  a.x = x.data_ptr(); a.w = w.data_ptr(); a.out = out.data_ptr();
+  if (bias.has_value() && bias->defined()) { check_bf16(*bias, "conv2d bias"); a.bias = bias->data_ptr(); }
+  c10::cuda::CUDAGuard guard(x.device());
+  rt::conv2d_fwd(a, cur_stream(x.device().index()));
+}
+
+// dw [Cout,KH,KW,Cin] fp32 += dy^T (*) x
+void conv2d_wgrad(const Tensor& x, const Tensor& dy, Tensor& dw, int64_t stride, int64_t pad) {
+  check_bf16(x, "conv2d_wgrad x");
+  check_bf16(dy, "conv2d_wgrad dy");
+  TORCH_CHECK(dw.is_cuda() && dw.scalar_type() == at::kFloat && dw.is_contiguous() && dw.dim() == 4 && x.is_contiguous() &&
+                  dy.is_contiguous() && x.dim() == 4 && dy.dim() == 4, "conv2d_wgrad: contiguous NHWC tensors and fp32 dw");
+  rt::Conv2dArgs a{};
+  a.N = int(x.size(0)); a.H = int(x.size(1)); a.W = int(x.size(2)); a.Cin = int(x.size(3));
+  a.Cout = int(dw.size(0)); a.KH = int(dw.size(1)); a.KW = int(dw.size(2));
+  a.stride = int(stride); a.pad = int(pad);
+  const int64_t OH = (a.H + 2 * a.pad - a.KH) / a.stride + 1, OW = (a.W + 2 * a.pad - a.KW) / a.stride + 1;
+  TORCH_CHECK(dw.size(3) == a.Cin && dy.size(0) == a.N && dy.size(1) == OH && dy.size(2) == OW && dy.size(3) == a.Cout,
+              "conv2d_wgrad: shape mismatch");
+  a.x = x.data_ptr(); a.dy = dy.data_ptr(); a.dw = dw.data_ptr<float>();
+  c10::cuda::CUDAGuard guard(x.device());
+  rt::conv2d_wgrad(a, cur_stream(x.device().index()));
+}
+
 int dtype_code(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, ": CUDA tensor required");
   switch (t.scalar_type()) {
@@ -461,6 +499,9 @@ void batchnorm_bwd(const Tensor& x2, const Tensor& dy2, const c10::optional<Tens
 }
 
 void register_extra_ops(pybind11::module_& m) {
+  m.def("conv2d_fwd", &conv2d_fwd, "implicit-GEMM conv2d forward (channels-last bf16)");
+  m.def("conv2d_wgrad", &conv2d_wgrad, "implicit-GEMM conv2d weight gradient (fp32 accumulate)");
+  m.def("conv2d_igemm_supported", &rt::conv2d_igemm_supported);
   m.def("tp_ag_gemm", &tp_ag_gemm, "fused all-gather -> GEMM over symmetric peer memory");
   m.def("tp_gemm_rs", &tp_gemm_rs, "fused GEMM -> reduce-scatter over symmetric peer memory");
   m.def("batchnorm_fwd", &batchnorm_fwd, "BatchNorm forward over a channels-last matrix (+residual, +ReLU)");

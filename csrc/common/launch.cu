@@ -153,4 +153,25 @@ CUtensorMap make_tmap_rows(const void* base, int elem_bytes, uint64_t row_elems,
   return m;
 }
 
+CUtensorMap make_tmap_nhwc(const void* base, uint64_t C, uint64_t W, uint64_t H, uint64_t N, uint32_t box_w, uint32_t box_h,
+                           uint32_t box_n, uint32_t stride) {
+  RT_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base must be 16-byte aligned");
+  RT_CHECK(C % 8 == 0, "channels-last TMA needs a multiple of 8 channels");
+  RT_CHECK(box_w * stride <= 256 && box_h * stride <= 256 && box_n <= 256 && stride >= 1 && stride <= 8, "TMA box out of range");
+  CUtensorMap m;
+  cuuint64_t dims[4] = {C, W, H, N};
+  cuuint64_t strides[3] = {C * 2, W * C * 2, H * W * C * 2};
+  cuuint32_t box[4] = {64, box_w * stride, box_h * stride, box_n};  // extent in the tensor; every stride-th element is taken
+  cuuint32_t estr[4] = {1, stride, stride, 1};
+  if (stride > 1) {  // the extent only has to reach the last element taken
+    box[1] = (box_w - 1) * stride + 1;
+    box[2] = (box_h - 1) * stride + 1;
+  }
+  CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  RT_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(nhwc) failed with code " + std::to_string(int(r)));
+  return m;
+}
+
 }  // namespace rt

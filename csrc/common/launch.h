@@ -60,5 +60,9 @@ CUtensorMap make_tmap_2byte_4d(const void* base, uint64_t d0, uint64_t d1, uint6
 // box read as zero.  row_bytes must be a multiple of 16.
 CUtensorMap make_tmap_rows(const void* base, int elem_bytes, uint64_t row_elems, uint64_t rows,
                            uint32_t box_elems, uint32_t box_rows);
+// Rank-4 map over a channels-last activation tensor [N][H][W][C] (2-byte elements, C contiguous, 128-byte swizzle):
+// a box covers 64 channels x box_w x box_h x box_n positions taken every `stride` pixels along W and H.
+CUtensorMap make_tmap_nhwc(const void* base, uint64_t C, uint64_t W, uint64_t H, uint64_t N, uint32_t box_w, uint32_t box_h,
+                           uint32_t box_n, uint32_t stride);
 
 }  // namespace rt

@@ -4,7 +4,9 @@
 Same topology as the reference (7x7/2 stem + BN + ReLU + 3x3/2 max-pool, stages 64/128/256/512, 1x1
 down-sampling shortcuts, ``fc 512 -> classes``) with its two omissions fixed: the residual addition is
 really performed (commented out in cnn.rs:435-437) and the global average pool exists (empty in cnn.rs:551).
-Works in NCHW or channels-last memory format; bf16 runs on the tensor cores through cuDNN's kernels.
+Built from the framework's ``Conv2d`` / ``BatchNorm2d``: in bf16 on CUDA (channels-last) the body convolutions run on
+the implicit-GEMM tcgen05 kernels and every BatchNorm (+ residual add + ReLU) is one native kernel; the 3-channel
+stem convolution, pooling and anything on CPU / fp32 use the library.
 """
 from __future__ import annotations
 
@@ -15,25 +17,26 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..nn.layers import BatchNorm2d, Conv2d
+
 
 class BasicBlock(nn.Module):
     expansion = 1
 
     def __init__(self, in_ch: int, out_ch: int, stride: int = 1):
         super().__init__()
-        self.conv1 = nn.Conv2d(in_ch, out_ch, 3, stride, 1, bias=False)
-        self.bn1 = nn.BatchNorm2d(out_ch)
-        self.conv2 = nn.Conv2d(out_ch, out_ch, 3, 1, 1, bias=False)
-        self.bn2 = nn.BatchNorm2d(out_ch)
+        self.conv1 = Conv2d(in_ch, out_ch, 3, stride, 1, bias=False)
+        self.bn1 = BatchNorm2d(out_ch)
+        self.conv2 = Conv2d(out_ch, out_ch, 3, 1, 1, bias=False)
+        self.bn2 = BatchNorm2d(out_ch)
         self.downsample = None
         if stride != 1 or in_ch != out_ch:
-            self.downsample = nn.Sequential(nn.Conv2d(in_ch, out_ch, 1, stride, bias=False), nn.BatchNorm2d(out_ch))
+            self.downsample = nn.Sequential(Conv2d(in_ch, out_ch, 1, stride, 0, bias=False), BatchNorm2d(out_ch))
 
     def forward(self, x):
         identity = x if self.downsample is None else self.downsample(x)
-        out = F.relu(self.bn1(self.conv1(x)))
-        out = self.bn2(self.conv2(out))
-        return F.relu(out + identity)
+        out = self.bn1(self.conv1(x), relu=True)                       # BatchNorm + ReLU in one kernel
+        return self.bn2(self.conv2(out), residual=identity, relu=True)  # BatchNorm + residual add + ReLU in one kernel
 
 
 class Bottleneck(nn.Module):
@@ -42,30 +45,29 @@ class Bottleneck(nn.Module):
     def __init__(self, in_ch: int, mid: int, stride: int = 1):
         super().__init__()
         out_ch = mid * 4
-        self.conv1 = nn.Conv2d(in_ch, mid, 1, bias=False)
-        self.bn1 = nn.BatchNorm2d(mid)
-        self.conv2 = nn.Conv2d(mid, mid, 3, stride, 1, bias=False)
-        self.bn2 = nn.BatchNorm2d(mid)
-        self.conv3 = nn.Conv2d(mid, out_ch, 1, bias=False)
-        self.bn3 = nn.BatchNorm2d(out_ch)
+        self.conv1 = Conv2d(in_ch, mid, 1, 1, 0, bias=False)
+        self.bn1 = BatchNorm2d(mid)
+        self.conv2 = Conv2d(mid, mid, 3, stride, 1, bias=False)
+        self.bn2 = BatchNorm2d(mid)
+        self.conv3 = Conv2d(mid, out_ch, 1, 1, 0, bias=False)
+        self.bn3 = BatchNorm2d(out_ch)
         self.downsample = None
         if stride != 1 or in_ch != out_ch:
-            self.downsample = nn.Sequential(nn.Conv2d(in_ch, out_ch, 1, stride, bias=False), nn.BatchNorm2d(out_ch))
+            self.downsample = nn.Sequential(Conv2d(in_ch, out_ch, 1, stride, 0, bias=False), BatchNorm2d(out_ch))
 
     def forward(self, x):
         identity = x if self.downsample is None else self.downsample(x)
-        out = F.relu(self.bn1(self.conv1(x)))
-        out = F.relu(self.bn2(self.conv2(out)))
-        out = self.bn3(self.conv3(out))
-        return F.relu(out + identity)
+        out = self.bn1(self.conv1(x), relu=True)
+        out = self.bn2(self.conv2(out), relu=True)
+        return self.bn3(self.conv3(out), residual=identity, relu=True)
 
 
 class ResNet(nn.Module):
     def __init__(self, block, layers: Sequence[int], num_classes: int = 1000, in_channels: int = 3):
         super().__init__()
         self.in_ch = 64
-        self.conv1 = nn.Conv2d(in_channels, 64, 7, 2, 3, bias=False)
-        self.bn1 = nn.BatchNorm2d(64)
+        self.conv1 = Conv2d(in_channels, 64, 7, 2, 3, bias=False)
+        self.bn1 = BatchNorm2d(64)
         self.maxpool = nn.MaxPool2d(3, 2, 1)
         self.layer1 = self._make(block, 64, layers[0], 1)
         self.layer2 = self._make(block, 128, layers[1], 2)
@@ -74,7 +76,7 @@ class ResNet(nn.Module):
         self.avgpool = nn.AdaptiveAvgPool2d((1, 1))
         self.fc = nn.Linear(512 * block.expansion, num_classes)
         for m in self.modules():
-            if isinstance(m, nn.Conv2d):
+            if isinstance(m, Conv2d):
                 nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")
 
     def _make(self, block, ch: int, n: int, stride: int) -> nn.Sequential:
@@ -84,7 +86,7 @@ class ResNet(nn.Module):
         return nn.Sequential(*blocks)
 
     def forward(self, x):
-        x = self.maxpool(F.relu(self.bn1(self.conv1(x))))
+        x = self.maxpool(self.bn1(self.conv1(x), relu=True))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         return self.fc(torch.flatten(self.avgpool(x), 1))
 

@@ -112,6 +112,11 @@ class Conv2d(_ConvNd):
                  dilation=1, groups=1, device=None, dtype=None):
         super().__init__(in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias, device, dtype)
 
+    def forward(self, x):
+        """bf16 CUDA layers with Cin, Cout multiples of 64 run on the implicit-GEMM tcgen05 kernels; others on the library."""
+        from ..ops.conv import conv2d
+        return conv2d(x, self.weight, self.bias, self.stride, self.padding, self.dilation, self.groups)
+
 
 class Conv3d(_ConvNd):
     """``(in, out, kernel(d,h,w), stride, padding, dilation, groups, bias)`` (src/nn/conv3d.rs:74-90)."""

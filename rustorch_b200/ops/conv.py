@@ -1,0 +1,85 @@
+"""Conv2d on the implicit-GEMM tcgen05 kernels (csrc/conv/conv2d_igemm.cu), with autograd.
+
+Tensors are channels-last: an NCHW tensor in ``torch.channels_last`` memory format IS an NHWC array, and a weight
+``[Cout, Cin, KH, KW]`` in channels-last format IS ``[Cout, KH, KW, Cin]``, so the kernels read both without copies.
+Forward and the weight gradient always use the native kernels when the layer qualifies (Cin % 64 == 0, Cout % 8 == 0,
+groups 1, dilation 1, square stride / padding); the input gradient does for stride 1 (it is the forward kernel on ``dy``
+with the filter rotated and its channel axes swapped) and falls back to the library for strided layers.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from .. import _native
+
+
+def supported(x: torch.Tensor, weight: torch.Tensor, stride, padding, dilation=1, groups: int = 1) -> bool:
+    s = stride if isinstance(stride, int) else stride[0]
+    p = padding if isinstance(padding, int) else padding[0]
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 4 and _native.available()):
+        return False
+    if groups != 1 or (dilation if isinstance(dilation, int) else dilation[0]) != 1:
+        return False
+    if not isinstance(stride, int) and stride[0] != stride[1] or not isinstance(padding, int) and padding[0] != padding[1]:
+        return False
+    if isinstance(p, str):
+        return False
+    Cout, Cin, KH, KW = weight.shape
+    return Cin % 64 == 0 and Cout % 64 == 0 and KH <= 7 and KW <= 7 and 1 <= s <= 4
+
+
+def _nhwc(t: torch.Tensor) -> torch.Tensor:
+    """NCHW-shaped tensor -> contiguous [N, H, W, C] view (copy only if it was not channels-last)."""
+    return t.permute(0, 2, 3, 1).contiguous()
+
+
+class Conv2dFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, stride: int, pad: int):
+        C = _native.load(required=True)
+        xh, wh = _nhwc(x), _nhwc(weight)                       # [N,H,W,Cin], [Cout,KH,KW,Cin]
+        N, H, W, _ = xh.shape
+        Cout, KH, KW, _ = wh.shape
+        OH, OW = (H + 2 * pad - KH) // stride + 1, (W + 2 * pad - KW) // stride + 1
+        out = torch.empty(N, OH, OW, Cout, dtype=torch.bfloat16, device=x.device)
+        C.conv2d_fwd(xh, wh, out, bias, stride, pad)
+        ctx.save_for_backward(xh, wh)
+        ctx.geom = (stride, pad, bias is not None, tuple(x.shape))
+        return out.permute(0, 3, 1, 2)                          # NCHW shape, channels-last memory
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = _native.load(required=True)
+        xh, wh = ctx.saved_tensors
+        stride, pad, has_bias, xshape = ctx.geom
+        dyh = _nhwc(dy)
+        Cout, KH, KW, Cin = wh.shape
+        dx = dw = db = None
+        if ctx.needs_input_grad[1]:
+            dwf = torch.zeros(Cout, KH, KW, Cin, dtype=torch.float32, device=dyh.device)
+            C.conv2d_wgrad(xh, dyh, dwf, stride, pad)
+            dw = dwf.to(torch.bfloat16).permute(0, 3, 1, 2)    # back to [Cout, Cin, KH, KW] (channels-last memory)
+        if ctx.needs_input_grad[0]:
+            if stride == 1 and KH - 1 - pad >= 0:
+                # full correlation of dy with the rotated filter: w'[ci][kh][kw][co] = w[co][KH-1-kh][KW-1-kw][ci]
+                wr = wh.flip(1, 2).permute(3, 1, 2, 0).contiguous()
+                dxh = torch.empty(xh.shape, dtype=torch.bfloat16, device=dyh.device)
+                C.conv2d_fwd(dyh, wr, dxh, None, 1, KH - 1 - pad)
+                dx = dxh.permute(0, 3, 1, 2)
+            else:
+                dx = torch.nn.grad.conv2d_input(xshape, wh.permute(0, 3, 1, 2), dy, stride, pad)
+        if has_bias and ctx.needs_input_grad[2]:
+            db = dyh.float().sum((0, 1, 2)).to(torch.bfloat16)
+        return dx, dw, db, None, None
+
+
+def conv2d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, stride=1, padding=0, dilation=1,
+           groups: int = 1) -> torch.Tensor:
+    if supported(x, weight, stride, padding, dilation, groups):
+        s = stride if isinstance(stride, int) else stride[0]
+        p = padding if isinstance(padding, int) else padding[0]
+        return Conv2dFn.apply(x, weight, bias, s, p)
+    return F.conv2d(x, weight, bias, stride, padding, dilation, groups)
