@@ -188,6 +188,32 @@ def bench_qgemv(a):
         del mats
 
 
+def bench_conv(a):
+    """ResNet-18 body convolutions at batch 256 (channels-last bf16): implicit-GEMM kernels vs cuDNN."""
+    import torch.nn.functional as F
+    from rustorch_b200.ops.conv import Conv2dFn
+    for (N, Cin, H, W, Cout, k, s, p) in [(256, 64, 56, 56, 64, 3, 1, 1), (256, 128, 28, 28, 128, 3, 1, 1), (256, 256, 14, 14, 256, 3, 1, 1),
+                                          (256, 512, 7, 7, 512, 3, 1, 1), (256, 64, 56, 56, 128, 3, 2, 1)]:
+        x = torch.randn(N, Cin, H, W, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+        w = (torch.randn(Cout, Cin, k, k, device="cuda") * 0.05).bfloat16().contiguous(memory_format=torch.channels_last)
+        OH, OW = (H + 2 * p - k) // s + 1, (W + 2 * p - k) // s + 1
+        flops = 2.0 * N * OH * OW * Cout * Cin * k * k
+        tag = f"{N}x{Cin}x{H}x{W}_to{Cout}_k{k}s{s}"
+        best, med = time_op(lambda: Conv2dFn.apply(x, w, None, s, p), a.iters)
+        report(f"conv_fwd_{tag}", best, med, flops=flops)
+        best, med = time_op(lambda: F.conv2d(x, w, None, s, p), a.iters)
+        report(f"cudnn_fwd_{tag}", best, med, flops=flops, extra="library baseline")
+        xg, wg = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        y = Conv2dFn.apply(xg, wg, None, s, p)
+        g = torch.randn_like(y)
+        best, med = time_op(lambda: torch.autograd.grad(y, (xg, wg), g, retain_graph=True), a.iters)
+        report(f"conv_bwd_{tag}", best, med, flops=2 * flops, extra="dgrad + wgrad" + ("" if s == 1 else " (dgrad through the library)"))
+        xl, wl = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        yl = F.conv2d(xl, wl, None, s, p)
+        best, med = time_op(lambda: torch.autograd.grad(yl, (xl, wl), g, retain_graph=True), a.iters)
+        report(f"cudnn_bwd_{tag}", best, med, flops=2 * flops, extra="library baseline")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", default="all")
@@ -222,6 +248,8 @@ def main():
         bench_ce(a)
     elif a.op == "qgemv":
         bench_qgemv(a)
+    elif a.op == "conv":
+        bench_conv(a)
     elif a.op == "all":
         a.compare = True
         for (m, n, k, lay, sk) in [(8192, 8192, 8192, "nt", 1), (16384, 2304, 768, "nt", 1),

@@ -202,6 +202,22 @@ void softmax_rows_bwd(int dtype, const void* y, const void* dy, void* dx, long l
 // Row reductions over the last dim: mode 0 sum, 1 mean, 2 max, 3 min, 4 variance (unbiased = p0 != 0), out fp32 [rows].
 void reduce_rows(int dtype, const void* x, float* out, long long rows, int C, long long ld, int mode, float p0, cudaStream_t s);
 
+// ------------------------------------------------------ collective/p2p_collectives.cu
+enum P2PMode : int { P2P_ALL_REDUCE_ONE_SHOT = 0, P2P_ALL_REDUCE_TWO_SHOT = 1, P2P_ALL_GATHER = 2, P2P_REDUCE_SCATTER = 3, P2P_BROADCAST = 4 };
+struct P2PCollArgs {
+  int mode, dtype, world, rank, root;
+  long long numel;               // elements of one rank's input (all-gather: per-rank count; others: full length)
+  const void* in[RT_MAX_PEERS];  // every rank's input buffer (symmetric)
+  void* result[RT_MAX_PEERS];    // two-shot all-reduce: every rank's result buffer (symmetric), else unused
+  void* out;                     // local output
+  int* flags[RT_MAX_PEERS];      // symmetric int32[3 * world], zero-initialised once
+  int* epoch_dev;                // local int32, zero-initialised once; the kernel advances it
+  unsigned* grid_counter;        // local uint32[2], zero-initialised once
+  unsigned long long timeout_ns;
+  int* status;
+};
+void p2p_collective(const P2PCollArgs& a, cudaStream_t stream);
+
 // ------------------------------------------------------------ collective/tp_gemm.cu
 // mode 0: y[W*rows][N] = all_gather(x_shards)[.][K] . B^T (+bias)      (x_shards, flags: symmetric peer pointers)
 // mode 1: out[rows][N] = reduce_scatter(x[W*rows][K] . B^T) (+bias) (+residual)   (stage, flags: symmetric)

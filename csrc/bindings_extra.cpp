@@ -358,6 +358,33 @@ void conv2d_wgrad(const Tensor& x, const Tensor& dy, Tensor& dw, int64_t stride,
   rt::conv2d_wgrad(a, cur_stream(x.device().index()));
 }
 
+int dtype_code(const Tensor& t, const char* name);
+
+// in_ptrs / result_ptrs / flag_ptrs: peer pointers of symmetric buffers.  out: local tensor.
+void p2p_collective(int64_t mode, const std::vector<int64_t>& in_ptrs, const std::vector<int64_t>& result_ptrs,
+                    const std::vector<int64_t>& flag_ptrs, Tensor& out, int64_t numel, Tensor& epoch_dev, Tensor& barrier_state,
+                    int64_t rank, int64_t root, double timeout_s) {
+  const int world = int(in_ptrs.size());
+  rt::P2PCollArgs a{};
+  a.mode = int(mode);
+  a.dtype = dtype_code(out, "p2p_collective out");
+  a.world = world; a.rank = int(rank); a.root = int(root); a.numel = numel;
+  TORCH_CHECK(int(flag_ptrs.size()) == world && out.is_contiguous(), "p2p_collective: bad operands");
+  TORCH_CHECK(epoch_dev.scalar_type() == at::kInt && barrier_state.scalar_type() == at::kInt && barrier_state.numel() >= 2 &&
+                  epoch_dev.is_cuda() && barrier_state.is_cuda(), "p2p_collective: int32 CUDA epoch / barrier words");
+  for (int r = 0; r < world; ++r) {
+    a.in[r] = reinterpret_cast<const void*>(in_ptrs[r]);
+    a.result[r] = r < int(result_ptrs.size()) ? reinterpret_cast<void*>(result_ptrs[r]) : nullptr;
+    a.flags[r] = reinterpret_cast<int*>(flag_ptrs[r]);
+  }
+  a.out = out.data_ptr();
+  a.epoch_dev = epoch_dev.data_ptr<int>();
+  a.grid_counter = reinterpret_cast<unsigned*>(barrier_state.data_ptr<int>());
+  a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
+  c10::cuda::CUDAGuard guard(out.device());
+  rt::p2p_collective(a, cur_stream(out.device().index()));
+}
+
 int dtype_code(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, ": CUDA tensor required");
   switch (t.scalar_type()) {
@@ -499,6 +526,7 @@ void batchnorm_bwd(const Tensor& x2, const Tensor& dy2, const c10::optional<Tens
 }
 
 void register_extra_ops(pybind11::module_& m) {
+  m.def("p2p_collective", &p2p_collective, "all-reduce / all-gather / reduce-scatter / broadcast over symmetric peer memory");
   m.def("conv2d_fwd", &conv2d_fwd, "implicit-GEMM conv2d forward (channels-last bf16)");
   m.def("conv2d_wgrad", &conv2d_wgrad, "implicit-GEMM conv2d weight gradient (fp32 accumulate)");
   m.def("conv2d_igemm_supported", &rt::conv2d_igemm_supported);

@@ -455,7 +455,8 @@ void conv2d_fwd(const Conv2dArgs& a, cudaStream_t stream) {
   p.out = reinterpret_cast<__nv_bfloat16*>(a.out);
   p.bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
   p.status = status_word(device);
-  if (a.Cout <= 128) launch_fwd<128>(a, p, device, stream);
+  if (a.Cout <= 64) launch_fwd<64>(a, p, device, stream);
+  else if (a.Cout <= 128) launch_fwd<128>(a, p, device, stream);
   else launch_fwd<256>(a, p, device, stream);
 }
 

@@ -99,6 +99,7 @@ class LlamaRuntime:
         self.lm_head: Optional[QuantLinear] = None
         self.act_dtype = torch.float16 if self.device.type == "cuda" else torch.float32
         self._graph = None
+        self._p2p = None
 
     # ---------------------------------------------------------------- loading
     def _shard_attn_rows(self, q: QuantLinear, heads: int) -> QuantLinear:
@@ -192,8 +193,16 @@ class LlamaRuntime:
 
     # ---------------------------------------------------------------- forward
     def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
-        if self.tp_world > 1:
-            dist.all_reduce(x, group=self.tp_group)
+        """Sum of the row-parallel partial outputs over the TP ranks: the one-shot peer-memory kernel for decode-sized
+        activations (it is graph-capturable and has a fraction of NCCL's latency), NCCL for anything larger."""
+        if self.tp_world == 1:
+            return x
+        if x.is_cuda and x.numel() * x.element_size() <= (1 << 20):
+            if self._p2p is None:
+                from ..distributed.p2p_collectives import P2PCollectives
+                self._p2p = P2PCollectives(1 << 19, x.dtype, self.device, self.tp_group, one_shot_max_bytes=1 << 20)
+            return self._p2p.all_reduce(x)
+        dist.all_reduce(x, group=self.tp_group)
         return x
 
     def _rmsnorm(self, x, w):

@@ -66,3 +66,22 @@ def test_tp_linear_layers_forward_backward_single_rank():
     assert rel_err(x.grad, xr.grad) < 3e-2
     assert rel_err(col.weight.grad, wc.grad) < 3e-2 and rel_err(row.weight.grad, wr.grad) < 3e-2
     assert rel_err(col.bias.grad, bc.grad) < 3e-2 and rel_err(row.bias.grad, br.grad) < 3e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_p2p_collectives_single_rank(dtype):
+    """World of one: flags and barriers still run; results equal the input."""
+    from rustorch_b200 import _native
+    from rustorch_b200.distributed.p2p_collectives import P2PCollectives
+    pc = P2PCollectives(1 << 20, dtype, "cuda")
+    x = torch.randn(1000, 33, device="cuda").to(dtype)
+    for _ in range(3):
+        assert torch.equal(pc.all_reduce(x), x)
+    big = torch.randn(1 << 19, device="cuda").to(dtype)
+    pc.one_shot_max_bytes = 0
+    assert torch.equal(pc.all_reduce(big), big)
+    assert torch.equal(pc.all_gather(x)[0], x)
+    assert torch.equal(pc.reduce_scatter(big), big)
+    y = x.clone()
+    assert torch.equal(pc.broadcast(y), x) and int(pc.epoch_dev) == 7
+    _native.check_status()

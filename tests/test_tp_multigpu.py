@@ -31,6 +31,7 @@ def test_tp_fused_kernels_match_unsharded_model():
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     for r in range(nproc):
         res = json.load(open(os.path.join(out_dir, f"rank{r}.json")))
+        assert res["p2p_coll_rel"] < 1e-2, res
         assert res["ag_rel"] < 1e-2 and res["rs_rel"] < 2e-2, res
         assert abs(res["llama_loss_tp"] - res["llama_loss_full"]) < 3e-2 and res["llama_dw_rel"] < 6e-2, res
         assert res["llama_dnorm_rel"] < 6e-2 and res["llama_dhead_rel"] < 6e-2, res

@@ -65,6 +65,30 @@ def main():
     res["dwc_rel"] = rel(col.weight.grad, wc.grad[rank * ffl:(rank + 1) * ffl])
     res["dwr_rel"] = rel(row.weight.grad, wr.grad[:, rank * ffl:(rank + 1) * ffl])
     res["dbr_rel"] = rel(row.bias.grad, brf.grad)
+    # ---- peer-memory collectives against NCCL
+    from rustorch_b200.distributed.p2p_collectives import P2PCollectives
+    pc = P2PCollectives(1 << 22, torch.bfloat16, dev)
+    gq = torch.Generator().manual_seed(100 + rank)
+    worst = 0.0
+    for n_el in (4096, 1 << 20, 3 * (1 << 20) + 8 * world * 5):
+        v = torch.randn(n_el, generator=gq).bfloat16().to(dev)
+        ref = v.float().clone()
+        dist.all_reduce(ref)
+        worst = max(worst, rel(pc.all_reduce(v), ref))
+        gathered = pc.all_gather(v)
+        lst = [torch.empty_like(v) for _ in range(world)]
+        dist.all_gather(lst, v)
+        assert all(torch.equal(gathered[r], lst[r]) for r in range(world))
+        if n_el % (8 * world) == 0:
+            rs_ref = ref.view(world, -1)[rank]
+            worst = max(worst, rel(pc.reduce_scatter(v), rs_ref))
+        b = v.clone()
+        pc.broadcast(b, src=world - 1)
+        bref = v.clone()
+        dist.broadcast(bref, world - 1)
+        assert torch.equal(b, bref)
+    res["p2p_coll_rel"] = worst
+    small = torch.randn(4096, device=dev).bfloat16()
     # ---- Llama block stack, tensor + sequence parallel, against the unsharded model
     from rustorch_b200.models.llama import LlamaModel, LlamaTrainConfig
     torch.manual_seed(7)
@@ -113,6 +137,11 @@ def main():
     def nccl_rs():
         dist.reduce_scatter_tensor(outb, hl @ wrl.t())
         return outb
+    res["ar_8kb_p2p_us"] = timed(lambda: pc.all_reduce(small), 50) * 1e3
+    res["ar_8kb_nccl_us"] = timed(lambda: dist.all_reduce(small), 50) * 1e3
+    big_ar = torch.randn(1 << 22, device=dev).bfloat16()
+    res["ar_8mb_p2p_us"] = timed(lambda: pc.all_reduce(big_ar), 20) * 1e3
+    res["ar_8mb_nccl_us"] = timed(lambda: dist.all_reduce(big_ar), 20) * 1e3
     res["ag_fused_ms"] = timed(lambda: ag(wcl, None, x=None))
     res["ag_nccl_ms"] = timed(nccl_ag)
     res["rs_fused_ms"] = timed(lambda: rs(hl, wrl))
