@@ -7,6 +7,9 @@ from .api import (CommunicationStats, DistributedBackend, DistributedRequest, Pr
                   scatter, send)
 from .async_gradient import (AsyncConfig, AsyncGradientSynchronizer, CommunicationScheduler, GradientBucketManager,
                              GradientCompressor, Priority, QuantizationCompressor, TensorMemoryPool, TopKCompressor)
+from .backends import (BackendFactory, BackendOptimizations, DataParallelTrainer, DeviceInfo, DistributedOps, GlooBackend,
+                       GlooTransport, GpuMetrics, MultiGpuProfiler, MultiGpuValidator, NCCLBackend, NCCLBackendOptimized,
+                       NCCLCommunicator, NCCLUniqueId, P2PBackend, ScalingBenchmark, TCPBackend, ValidationReport)
 from .cluster import (ClusterConfig, ClusterManager, ClusterTopology, FaultToleranceConfig, HeartbeatMonitor,
                       NodeCapabilities, NodeInfo, NodeStatus, ResourceScheduler, SchedulingPolicy, StoreHeartbeat, retry)
 from .ddp import (DataParallel, DistributedDataLoader, DistributedDataParallel, DistributedSampler, GradientBucket,

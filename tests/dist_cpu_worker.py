@@ -34,6 +34,19 @@ def main():
         req.wait()
         out["async_done"] = req.is_completed()
         out["stats_calls"] = D.monitoring.get_communication_stats().calls.get("all_reduce", 0)
+    elif case == "backends":
+        be = D.BackendFactory.create_backend(D.DistributedBackend.GLOO, optimizations=D.BackendOptimizations(bucket_size_mb=1))
+        ts = [torch.full((n,), float(r + 1)) for n in (3, 300_000, 5)]
+        be.all_reduce_bucketed(ts)
+        out["bucketed"] = [float(t[0]) for t in ts]
+        out["name"] = be.name
+        rep = D.MultiGpuValidator().validate_distributed(torch.device("cpu"))
+        out["valid"], out["err"] = rep.collectives_ok, rep.max_error
+        x = torch.ones(1000)
+        sb = D.MultiGpuValidator().benchmark(lambda: x.mul(2.0), lambda: be.all_reduce(x.clone()), 10, iters=2)
+        out["bench_world"], out["overhead_ok"] = sb.world_size, 0.0 <= sb.comm_overhead <= 1.0
+        comm = D.NCCLCommunicator(0, r, W, num_streams=0)
+        out["comm_sum"] = float(comm.all_reduce(torch.tensor([1.0]))[0])
     elif case == "ddp":
         torch.manual_seed(0)
         model = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))

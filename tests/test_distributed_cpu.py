@@ -199,3 +199,44 @@ def test_async_sync_single_process_and_compression():
     m = D.GradientBucketManager(bucket_size_mb=0.001)
     assert m.add_gradient("a", torch.zeros(200)) is None and m.add_gradient("b", torch.zeros(200)) == 0
     assert len(m.flush()) == 2
+
+
+def test_backend_objects_validator_two_ranks():
+    res = _spawn("backends")
+    for o in res:
+        assert o["bucketed"] == [3.0, 3.0, 3.0] and o["name"] == "gloo"
+        assert o["valid"] and o["err"] == 0.0 and o["bench_world"] == 2 and o["overhead_ok"] and o["comm_sum"] == 2.0
+
+
+def test_backend_factory_profiler_and_dp_trainer():
+    assert isinstance(D.BackendFactory.create_backend(D.DistributedBackend.TCP), D.TCPBackend)
+    with pytest.raises(ValueError):
+        D.BackendFactory.create_backend(D.DistributedBackend.MPI)
+    o = D.BackendOptimizations()
+    assert (o.bucket_size_mb, o.memory_pool_mb, o.num_streams) == (25, 512, 4)
+    assert len(D.NCCLUniqueId().data) == 128
+    with pytest.raises(ValueError):
+        D.NCCLUniqueId(b"x")
+    prof = D.MultiGpuProfiler()
+    prof.record("compute", 0, 10.0)
+    prof.record("comm", 0, 9.0, nbytes=9_000_000)
+    prof.record("compute", 1, 20.0)
+    k = prof.start("idle", 1)
+    prof.stop(k)
+    rep = prof.report()
+    assert "communication" in rep and "rebalance" in rep and prof.comm_events[0]["gbps"] == pytest.approx(1.0)
+    assert D.MultiGpuValidator.scaling_efficiency(100.0, 350.0, 4) == pytest.approx(0.875)
+    torch.manual_seed(0)
+    m = torch.nn.Linear(4, 2)
+    ref = torch.nn.Linear(4, 2)
+    ref.load_state_dict(m.state_dict())
+    tr = D.DataParallelTrainer(m, device_ids=[0, 1]) if not torch.cuda.is_available() else D.DataParallelTrainer(m, device_ids=[0])
+    x, y = torch.randn(6, 4), torch.randn(6, 2)
+    opt, ropt = torch.optim.SGD(tr.replicas[0].parameters(), 0.1), torch.optim.SGD(ref.parameters(), 0.1)
+    loss = tr.train_step(x, y, torch.nn.functional.mse_loss, opt)
+    rl = torch.nn.functional.mse_loss(ref(x), y)
+    rl.backward()
+    ropt.step()
+    assert loss == pytest.approx(float(rl), rel=1e-5)
+    for rep_m in tr.replicas:
+        assert torch.allclose(rep_m.weight.cpu(), ref.weight, atol=1e-6)
