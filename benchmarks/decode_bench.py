@@ -48,7 +48,7 @@ def main():
     prompts = torch.randint(0, cfg.vocab_size, (B, T), generator=gen).to(dev)
     cache = rt.new_cache(B, T + N + 8)
     # warm-up
-    lg = rt.prefill(prompts[:, :64], cache)
+    lg = rt.prefill(prompts, cache)
     for _ in range(3):
         lg = rt.decode_step(lg.argmax(-1), cache)
     launches_per_step = 0

@@ -218,6 +218,24 @@ struct P2PCollArgs {
 };
 void p2p_collective(const P2PCollArgs& a, cudaStream_t stream);
 
+// ------------------------------------------------------ collective/ar_residual_norm.cu
+// x[rows][d] += sum over ranks of partial[rows][d]; h = rmsnorm(x) * w (h may be null).  fp16 / bf16.
+struct ArNormArgs {
+  int dtype, world, rank;
+  int rows, d;
+  float eps;
+  void* bufs[RT_MAX_PEERS];   // symmetric receive buffers [3][world][cap_numel], every 16-bit lane pre-set to 0x8000
+  long long cap_numel;        // elements per (slot, source) region
+  const void* partial;        // this rank's partial sums
+  void* x;                    // residual stream, updated in place
+  const void* w;              // norm weight [d] or null
+  void* h;                    // normalised output or null
+  int* state;                 // local int32[8], zero-initialised once
+  unsigned long long timeout_ns;
+  int* status;
+};
+void ar_residual_norm(const ArNormArgs& a, cudaStream_t stream);
+
 // ------------------------------------------------------------ collective/tp_gemm.cu
 // mode 0: y[W*rows][N] = all_gather(x_shards)[.][K] . B^T (+bias)      (x_shards, flags: symmetric peer pointers)
 // mode 1: out[rows][N] = reduce_scatter(x[W*rows][K] . B^T) (+bias) (+residual)   (stage, flags: symmetric)

@@ -385,6 +385,32 @@ void p2p_collective(int64_t mode, const std::vector<int64_t>& in_ptrs, const std
   rt::p2p_collective(a, cur_stream(out.device().index()));
 }
 
+// partial, x: [rows, d]; buf_ptrs: peer pointers of the receive buffers; state: int32[8].
+void ar_residual_norm(const std::vector<int64_t>& buf_ptrs, int64_t cap_numel, const Tensor& partial, Tensor& x,
+                      const c10::optional<Tensor>& w, const c10::optional<Tensor>& h, Tensor& state, int64_t rank, double eps,
+                      double timeout_s) {
+  rt::ArNormArgs a{};
+  a.dtype = dtype_code(x, "ar_residual_norm x");
+  a.world = int(buf_ptrs.size()); a.rank = int(rank);
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && partial.is_contiguous() && partial.sizes() == x.sizes() &&
+                  partial.scalar_type() == x.scalar_type() && partial.is_cuda(), "ar_residual_norm: partial and x must be matching [rows, d]");
+  TORCH_CHECK(state.scalar_type() == at::kInt && state.is_cuda() && state.numel() >= 8, "ar_residual_norm: int32[8] CUDA state");
+  a.rows = int(x.size(0)); a.d = int(x.size(1)); a.eps = float(eps);
+  for (int r = 0; r < a.world; ++r) a.bufs[r] = reinterpret_cast<void*>(buf_ptrs[r]);
+  a.cap_numel = cap_numel;
+  a.partial = partial.data_ptr(); a.x = x.data_ptr();
+  if (h.has_value()) {
+    TORCH_CHECK(w.has_value() && w->is_cuda() && w->is_contiguous() && w->numel() == x.size(1) && w->scalar_type() == x.scalar_type() &&
+                    h->is_contiguous() && h->sizes() == x.sizes() && h->scalar_type() == x.scalar_type() && h->is_cuda(),
+                "ar_residual_norm: norm weight [d] and output [rows, d] of the activation dtype");
+    a.w = w->data_ptr(); a.h = h->data_ptr();
+  }
+  a.state = state.data_ptr<int>();
+  a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
+  c10::cuda::CUDAGuard guard(x.device());
+  rt::ar_residual_norm(a, cur_stream(x.device().index()));
+}
+
 int dtype_code(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, ": CUDA tensor required");
   switch (t.scalar_type()) {
@@ -527,6 +553,7 @@ void batchnorm_bwd(const Tensor& x2, const Tensor& dy2, const c10::optional<Tens
 
 void register_extra_ops(pybind11::module_& m) {
   m.def("p2p_collective", &p2p_collective, "all-reduce / all-gather / reduce-scatter / broadcast over symmetric peer memory");
+  m.def("ar_residual_norm", &ar_residual_norm, "all-reduce over peer memory + residual add + RMSNorm in one kernel");
   m.def("conv2d_fwd", &conv2d_fwd, "implicit-GEMM conv2d forward (channels-last bf16)");
   m.def("conv2d_wgrad", &conv2d_wgrad, "implicit-GEMM conv2d weight gradient (fp32 accumulate)");
   m.def("conv2d_igemm_supported", &rt::conv2d_igemm_supported);

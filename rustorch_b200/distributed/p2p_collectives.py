@@ -102,3 +102,41 @@ class P2PCollectives:
         res = buf[:n].view(t.shape)
         t.copy_(res)
         return t
+
+
+class AllReduceResidualNorm:
+    """``x += all_reduce(partial)`` and ``h = rmsnorm(x) * w`` as one kernel (csrc/collective/ar_residual_norm.cu):
+    the epilogue of a row-parallel projection in tensor-parallel decoding.  The peers' partial sums arrive as
+    self-validating data in triple-buffered receive slots, so a call costs one NVLink store latency; the call counter
+    is device-resident, so the launch can be captured in a CUDA graph.  ``cap_numel`` bounds ``rows * d`` per call."""
+
+    def __init__(self, cap_numel: int, dtype: torch.dtype = torch.float16, device=None, group=None, timeout_s: float = 20.0):
+        if dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError("fp16 or bf16 activations")
+        if dist.is_available() and dist.is_initialized():
+            self.group = group or dist.group.WORLD
+            self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        else:
+            self.group, self.world, self.rank = None, 1, 0
+        self.device = torch.device(device if device is not None else ("cuda", torch.cuda.current_device()))
+        self.dtype, self.timeout_s = dtype, timeout_s
+        self.cap_numel = -(-cap_numel // 8) * 8
+        from .tp_fused import _symm
+        self.buf, self.buf_ptrs, self._h = _symm(3 * self.world * self.cap_numel, dtype, self.device, self.group, self.world)
+        self.buf.view(torch.int16).fill_(-32768)          # 0x8000 in every lane: "not arrived"
+        self.state = torch.zeros(8, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(self.group)                      # nobody pushes before every rank's slots are armed
+
+    def fits(self, rows: int, d: int) -> bool:
+        return rows * d <= self.cap_numel and d % 8 == 0 and d <= 16384
+
+    def __call__(self, partial: torch.Tensor, x: torch.Tensor, norm_weight: Optional[torch.Tensor] = None, eps: float = 1e-5,
+                 h: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """Updates ``x`` in place; returns the normalised activations when ``norm_weight`` is given."""
+        if norm_weight is not None and h is None:
+            h = torch.empty_like(x)
+        _native.load(required=True).ar_residual_norm(self.buf_ptrs, self.cap_numel, partial, x, norm_weight, h, self.state,
+                                                     self.rank, eps, self.timeout_s)
+        return h

@@ -100,6 +100,7 @@ class LlamaRuntime:
         self.act_dtype = torch.float16 if self.device.type == "cuda" else torch.float32
         self._graph = None
         self._p2p = None
+        self._ar_norm = None
 
     # ---------------------------------------------------------------- loading
     def _shard_attn_rows(self, q: QuantLinear, heads: int) -> QuantLinear:
@@ -205,6 +206,15 @@ class LlamaRuntime:
         dist.all_reduce(x, group=self.tp_group)
         return x
 
+    def _fused_epilogue(self, n: int, x: torch.Tensor):
+        """The all-reduce + residual + RMSNorm kernel, when this step's activations fit its receive buffers."""
+        if self.tp_world == 1 or not x.is_cuda or x.dtype not in (torch.float16, torch.bfloat16):
+            return None
+        if self._ar_norm is None:
+            from ..distributed.p2p_collectives import AllReduceResidualNorm
+            self._ar_norm = AllReduceResidualNorm(512 * self.cfg.n_embd, x.dtype, self.device, self.tp_group)
+        return self._ar_norm if self._ar_norm.fits(n, x.shape[1]) and x.is_contiguous() else None
+
     def _rmsnorm(self, x, w):
         if self.device.type == "cuda":
             y = torch.empty_like(x)
@@ -243,8 +253,11 @@ class LlamaRuntime:
         if max_kv is None:          # upper bound of kv_len known to the host (avoids a device sync)
             max_kv = cache.max_len
         scale = 1.0 / math.sqrt(D)
+        fused_ar = self._fused_epilogue(n, x)
+        h = None
         for li, L in enumerate(self.layers):
-            h = self._rmsnorm(x, L.attn_norm)
+            if h is None:
+                h = self._rmsnorm(x, L.attn_norm)
             qkv = L.wqkv(h)                                            # [n, (H + 2 Hkv) D]
             q = qkv[:, : H * D].view(n, H, D)
             k = qkv[:, H * D: (H + Hkv) * D].view(n, Hkv, D)
@@ -267,23 +280,34 @@ class LlamaRuntime:
             att2 = att.reshape(n, H * D)
             if self.tp_world == 1:
                 x = L.wo(att2, residual=x)
+                h = self._rmsnorm(x, L.ffn_norm)
+            elif fused_ar is not None:           # x += sum over ranks; h = norm(x): one kernel
+                h = fused_ar(L.wo(att2), x, L.ffn_norm, cfg.rms_eps)
             else:
                 x = x + self._all_reduce(L.wo(att2))
-            h = self._rmsnorm(x, L.ffn_norm)
+                h = self._rmsnorm(x, L.ffn_norm)
             gu = L.w_gate_up(h)                                        # [n, 2 ff_local]
             if C is not None:
                 act = torch.empty((n, self.ff_local), dtype=gu.dtype, device=gu.device)
                 C.silu_mul(gu[:, : self.ff_local], gu[:, self.ff_local:], act)
             else:
                 act = torch.nn.functional.silu(gu[:, : self.ff_local].float()).to(gu.dtype) * gu[:, self.ff_local:]
+            h = None
             if self.tp_world == 1:
                 x = L.w_down(act, residual=x)
+            elif fused_ar is not None:
+                last = li + 1 == len(self.layers)
+                if last and last_only is not None:
+                    fused_ar(L.w_down(act), x)
+                else:
+                    h = fused_ar(L.w_down(act), x, self.out_norm if last else self.layers[li + 1].attn_norm, cfg.rms_eps)
             else:
                 x = x + self._all_reduce(L.w_down(act))
         if last_only is not None:
             x = x[last_only]
-        x = self._rmsnorm(x, self.out_norm)
-        return self.lm_head(x).float()
+        if h is None:
+            h = self._rmsnorm(x, self.out_norm)
+        return self.lm_head(h).float()
 
     # --------------------------------------------------------------- generate
     @torch.no_grad()

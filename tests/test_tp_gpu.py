@@ -85,3 +85,24 @@ def test_p2p_collectives_single_rank(dtype):
     y = x.clone()
     assert torch.equal(pc.broadcast(y), x) and int(pc.epoch_dev) == 7
     _native.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_allreduce_residual_norm_single_rank(dtype):
+    """World of one: residual add + RMSNorm, call counter advances, receive slots untouched."""
+    from rustorch_b200 import _native
+    from rustorch_b200.distributed.p2p_collectives import AllReduceResidualNorm
+    arn = AllReduceResidualNorm(16 * 4096, dtype, "cuda")
+    w = (torch.rand(4096, device="cuda") + 0.5).to(dtype)
+    for call, rows in enumerate((1, 16, 5)):
+        part = torch.randn(rows, 4096, device="cuda").to(dtype)
+        x = torch.randn(rows, 4096, device="cuda").to(dtype)
+        x_ref = (x.float() + part.float()).to(dtype).float()
+        h_ref = x_ref * torch.rsqrt(x_ref.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+        h = arn(part, x, w, 1e-6)
+        assert torch.equal(x.float(), x_ref)
+        assert float((h.float() - h_ref).abs().max() / h_ref.abs().max()) < 8e-3
+        assert int(arn.state[0]) == call + 1
+    assert not arn.fits(17, 4096) and arn.fits(16, 4096)
+    _native.check_status()

@@ -32,6 +32,8 @@ def test_tp_fused_kernels_match_unsharded_model():
     for r in range(nproc):
         res = json.load(open(os.path.join(out_dir, f"rank{r}.json")))
         assert res["p2p_coll_rel"] < 1e-2, res
+        assert res["arn_x_rel"] < 4e-3 and res["arn_h_rel"] < 8e-3, res
+        assert res["dec_prefill_rel"] < 2e-2 and res["dec_tokens_equal"] > 0.9, res
         assert res["ag_rel"] < 1e-2 and res["rs_rel"] < 2e-2, res
         assert abs(res["llama_loss_tp"] - res["llama_loss_full"]) < 3e-2 and res["llama_dw_rel"] < 6e-2, res
         assert res["llama_dnorm_rel"] < 6e-2 and res["llama_dhead_rel"] < 6e-2, res

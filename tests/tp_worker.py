@@ -89,6 +89,63 @@ def main():
         assert torch.equal(b, bref)
     res["p2p_coll_rel"] = worst
     small = torch.randn(4096, device=dev).bfloat16()
+    # ---- all-reduce + residual + RMSNorm kernel: varying row counts, more calls than receive slots, then a CUDA graph
+    from rustorch_b200.distributed.p2p_collectives import AllReduceResidualNorm
+    worst_x = worst_h = 0.0
+    for dt_ in (torch.float16, torch.bfloat16):
+        arn = AllReduceResidualNorm(64 * 1024, dt_, dev)
+        wn = (torch.rand(1024, generator=gq) + 0.5).to(dt_).to(dev)
+        dist.broadcast(wn, 0)
+        for call, rows in enumerate((1, 32, 3, 64, 1, 1, 7)):
+            part = torch.randn(rows, 1024, generator=gq).to(dt_).to(dev)
+            if call == 2:
+                part[0, :16] = -0.0                      # the sentinel value itself must survive as a zero
+            x0 = torch.randn(rows, 1024, generator=torch.Generator().manual_seed(call)).to(dt_).to(dev)
+            tot = part.float().clone()
+            dist.all_reduce(tot)
+            x_ref = (x0.float() + tot).to(dt_).float()
+            h_ref = x_ref * torch.rsqrt(x_ref.pow(2).mean(-1, keepdim=True) + 1e-5) * wn.float()
+            x1 = x0.clone()
+            hh = arn(part, x1, wn, 1e-5) if call % 2 == 0 else (arn(part, x1), None)[1]
+            worst_x = max(worst_x, rel(x1, x_ref))
+            if hh is not None:
+                worst_h = max(worst_h, rel(hh, h_ref))
+            gat = [torch.empty_like(x1) for _ in range(world)]
+            dist.all_gather(gat, x1)
+            assert all(torch.equal(gat[0], g_) for g_ in gat), "ranks disagree on the residual stream"
+        # graph replay: the call counter is device state
+        part = torch.randn(4, 1024, generator=gq).to(dt_).to(dev)
+        xg = torch.zeros(4, 1024, dtype=dt_, device=dev)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            arn(part, xg)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            arn(part, xg)
+        for _ in range(5):
+            gr.replay()
+        torch.cuda.synchronize()
+        tot = part.float().clone()
+        dist.all_reduce(tot)
+        ref7 = torch.zeros(4, 1024, device=dev)
+        for _ in range(6):
+            ref7 = (ref7 + tot).to(dt_).float()
+        worst_x = max(worst_x, rel(xg, ref7))
+    res["arn_x_rel"], res["arn_h_rel"] = worst_x, worst_h
+    # ---- quantised Llama runtime: tensor-parallel prefill + CUDA-graph decode against the unsharded runtime
+    from rustorch_b200.llm import LlamaConfig, LlamaRuntime
+    qcfg = LlamaConfig(vocab_size=256, n_layer=2, n_embd=256, n_head=4, n_head_kv=4 if world > 2 else 2, n_ff=1024, context_length=128)
+    rt_full = LlamaRuntime.random_init(qcfg, dev, seed=5, std=0.08)
+    rt_tp = LlamaRuntime.random_init(qcfg, dev, tp_rank=rank, tp_world=world, tp_group=dist.group.WORLD, seed=5, std=0.08)
+    prompt = torch.randint(0, 256, (2, 70), generator=torch.Generator().manual_seed(1))
+    c1, c2 = rt_full.new_cache(2, 96), rt_tp.new_cache(2, 96)
+    res["dec_prefill_rel"] = rel(rt_tp.prefill(prompt, c2), rt_full.prefill(prompt, c1))
+    tok_full, _ = rt_full.generate_graph(prompt, 12)
+    tok_tp, _ = rt_tp.generate_graph(prompt, 12)
+    res["dec_tokens_equal"] = float((tok_full == tok_tp).float().mean())
     # ---- Llama block stack, tensor + sequence parallel, against the unsharded model
     from rustorch_b200.models.llama import LlamaModel, LlamaTrainConfig
     torch.manual_seed(7)
@@ -139,6 +196,13 @@ def main():
         return outb
     res["ar_8kb_p2p_us"] = timed(lambda: pc.all_reduce(small), 50) * 1e3
     res["ar_8kb_nccl_us"] = timed(lambda: dist.all_reduce(small), 50) * 1e3
+    arn = AllReduceResidualNorm(32 * 4096, torch.float16, dev)
+    for rows in (1, 32):
+        part = torch.randn(rows, 4096, device=dev).half()
+        xx = torch.zeros(rows, 4096, device=dev).half()
+        wn = torch.ones(4096, device=dev).half()
+        hb = torch.empty_like(xx)
+        res[f"arn_{rows}x4096_us"] = timed(lambda: arn(part, xx, wn, 1e-5, hb), 50) * 1e3
     big_ar = torch.randn(1 << 22, device=dev).bfloat16()
     res["ar_8mb_p2p_us"] = timed(lambda: pc.all_reduce(big_ar), 20) * 1e3
     res["ar_8mb_nccl_us"] = timed(lambda: dist.all_reduce(big_ar), 20) * 1e3
