@@ -188,6 +188,40 @@ def bench_qgemv(a):
         del mats
 
 
+def bench_qgemm(a):
+    """Q4_0 weights times 16 / 32 / 128 activation rows at the llama-7B shapes: dequant-fused tcgen05 GEMM against the
+    GEMV kernel (one pass over the weights per 8 rows) and the two-pass path (expand to fp16, then the dense GEMM).
+    Distinct matrices per timed region keep the weights out of L2."""
+    from rustorch_b200 import _native
+    from rustorch_b200.formats import gguf
+    from rustorch_b200.llm import QuantLinear
+    C = _native.load(required=True)
+    for (N, Kd) in [(12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008)]:
+        nbytes = N * Kd // 32 * 18
+        copies = max(2, -(-300_000_000 // nbytes))
+        mats = [QuantLinear.random(N, Kd, gguf.GGMLType.Q4_0, 0.02, "cuda", seed=i) for i in range(copies)]
+        for M in (16, 32, 128):
+            x = (torch.randn(M, Kd, device="cuda") * 0.5).half()
+            y = torch.empty(M, N, device="cuda", dtype=torch.half)
+            part, cnt = mats[0]._tc_buffers(M)
+
+            def run_tc():
+                for q in mats:
+                    C.q_gemm_tc(q.qs, q.scales, x, y, None, None, False, part, cnt)
+
+            def run_gemv():
+                for q in mats:
+                    for m0 in range(0, M, 8):
+                        C.q_gemv(q.qs, q.scales, x[m0:m0 + 8], y[m0:m0 + 8], None, None, False)
+            best, med = time_op(run_tc, a.iters, flush=False)
+            report(f"q4_gemm_tc_m{M}_{N}x{Kd}", best / copies, med / copies, bytes_=float(nbytes), flops=2.0 * M * N * Kd,
+                   extra=f"mean over {copies} distinct matrices per timed region")
+            if M <= 32:
+                best, med = time_op(run_gemv, a.iters, flush=False)
+                report(f"q4_gemv_x{M // 8}_m{M}_{N}x{Kd}", best / copies, med / copies, bytes_=float(nbytes), extra="GEMV kernel, 8 rows per pass")
+        del mats
+
+
 def bench_conv(a):
     """ResNet-18 body convolutions at batch 256 (channels-last bf16): implicit-GEMM kernels vs cuDNN."""
     import torch.nn.functional as F
@@ -250,6 +284,8 @@ def main():
         bench_qgemv(a)
     elif a.op == "conv":
         bench_conv(a)
+    elif a.op == "qgemm":
+        bench_qgemm(a)
     elif a.op == "all":
         a.compare = True
         for (m, n, k, lay, sk) in [(8192, 8192, 8192, "nt", 1), (16384, 2304, 768, "nt", 1),

@@ -286,6 +286,10 @@ void q_gemv(const QGemvArgs& a, cudaStream_t stream);
 bool q_gemv_bulk_supported(const QGemvArgs& a);
 bool q_gemv_bulk_preferred(const QGemvArgs& a);  // shape heuristic from measurements
 void q_gemv_bulk(const QGemvArgs& a, cudaStream_t stream);
+// quant/q_gemm_tc.cu: dequant-fused tcgen05 GEMM for 1 <= M <= 256 rows (weights read once whatever M is).
+bool q_gemm_tc_supported(int M, int N, int K);
+void q_gemm_tc_scratch(int M, int N, int K, bool q8, int sms, long long* partial_floats, int* counters, int* splits_out);
+void q_gemm_tc(const QGemvArgs& a, void* partial, int* counters, cudaStream_t stream);
 void dequant_f16(const void* qs, const void* scales, void* out, long long n_blocks, bool q8, cudaStream_t s);
 void repack_q4_0(const void* blocks, void* qs, void* scales, long long n_blocks, cudaStream_t s);
 void repack_q8_0(const void* blocks, void* qs, void* scales, long long n_blocks, cudaStream_t s);

@@ -75,14 +75,13 @@ void check_f16(const Tensor& t, const char* name) {
 }
 
 // y[M, N] = dequant(W)[N, K] @ x[M, K]^T (+bias) (+residual); qs / scales are the repacked device layout.
-void q_gemv(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, const c10::optional<Tensor>& bias,
-            const c10::optional<Tensor>& residual, bool q8, int64_t path) {
+static rt::QGemvArgs make_qargs(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, const c10::optional<Tensor>& bias,
+                                const c10::optional<Tensor>& residual, bool q8, int64_t path) {
   check_f16(scales, "q_gemv scales");
   check_f16(x, "q_gemv x");
   check_f16(y, "q_gemv y");
   TORCH_CHECK(qs.is_cuda() && qs.is_contiguous() && scales.is_contiguous(), "q_gemv: contiguous CUDA weights required");
   TORCH_CHECK(x.dim() == 2 && y.dim() == 2 && x.stride(1) == 1 && y.stride(1) == 1, "q_gemv: x [M, K], y [M, N]");
-  c10::cuda::CUDAGuard guard(x.device());
   rt::QGemvArgs a{};
   a.N = int(scales.size(0));
   a.K = int(scales.size(1)) * 32;
@@ -107,7 +106,40 @@ void q_gemv(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, 
   }
   a.q8 = q8;
   a.path = int(path);
+  return a;
+}
+
+void q_gemv(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, const c10::optional<Tensor>& bias,
+            const c10::optional<Tensor>& residual, bool q8, int64_t path) {
+  c10::cuda::CUDAGuard guard(x.device());
+  const rt::QGemvArgs a = make_qargs(qs, scales, x, y, bias, residual, q8, path);
   rt::q_gemv(a, cur_stream(x.device().index()));
+}
+
+// (fp32 words of split-K scratch, counters, splits) for a shape on the current device
+std::vector<int64_t> q_gemm_tc_scratch(int64_t M, int64_t N, int64_t K, bool q8) {
+  long long pf; int nc, sp;
+  rt::q_gemm_tc_scratch(int(M), int(N), int(K), q8, rt::sm_count(rt::current_device()), &pf, &nc, &sp);
+  return {pf, nc, sp};
+}
+
+// partial: fp32 scratch (>= q_gemm_tc_scratch()[0] words); counters: int32 zeros, one per 128 output columns.
+void q_gemm_tc(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, const c10::optional<Tensor>& bias,
+               const c10::optional<Tensor>& residual, bool q8, const c10::optional<Tensor>& partial, const c10::optional<Tensor>& counters) {
+  c10::cuda::CUDAGuard guard(x.device());
+  const rt::QGemvArgs a = make_qargs(qs, scales, x, y, bias, residual, q8, 0);
+  long long pf; int nc, sp;
+  rt::q_gemm_tc_scratch(a.M, a.N, a.K, q8, rt::sm_count(rt::current_device()), &pf, &nc, &sp);
+  void* pp = nullptr;
+  int* cc = nullptr;
+  if (sp > 1) {
+    TORCH_CHECK(partial.has_value() && partial->is_cuda() && partial->scalar_type() == at::kFloat && partial->numel() >= pf &&
+                    counters.has_value() && counters->is_cuda() && counters->scalar_type() == at::kInt && counters->numel() >= nc,
+                "q_gemm_tc: split-K scratch too small (need ", pf, " floats, ", nc, " counters)");
+    pp = partial->data_ptr();
+    cc = counters->data_ptr<int>();
+  }
+  rt::q_gemm_tc(a, pp, cc, cur_stream(x.device().index()));
 }
 
 // GGUF block stream (uint8 [n_blocks, 18 | 34]) -> (qs, scales) device layout.
@@ -570,6 +602,8 @@ void register_extra_ops(pybind11::module_& m) {
   m.def("q_gemv", &q_gemv, "dequant-fused Q4_0 / Q8_0 matrix-vector product", pybind11::arg("qs"), pybind11::arg("scales"),
         pybind11::arg("x"), pybind11::arg("y"), pybind11::arg("bias"), pybind11::arg("residual"), pybind11::arg("q8"),
         pybind11::arg("path") = 0);
+  m.def("q_gemm_tc", &q_gemm_tc, "dequant-fused Q4_0 / Q8_0 tcgen05 GEMM for up to 256 activation rows");
+  m.def("q_gemm_tc_scratch", &q_gemm_tc_scratch);
   m.def("repack_quant", &repack_quant);
   m.def("rmsnorm_f16", &rmsnorm_f16);
   m.def("rope_kv", &rope_kv);

@@ -153,6 +153,21 @@ CUtensorMap make_tmap_rows(const void* base, int elem_bytes, uint64_t row_elems,
   return m;
 }
 
+CUtensorMap make_tmap_words_sw128(const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows) {
+  RT_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0 && row_bytes % 16 == 0, "TMA rows must be 16-byte aligned");
+  RT_CHECK(box_rows >= 1 && box_rows <= 256, "TMA box out of range");
+  CUtensorMap m;
+  cuuint64_t dims[2] = {row_bytes / 4, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {32, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  RT_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(words, sw128) failed with code " + std::to_string(int(r)));
+  return m;
+}
+
 CUtensorMap make_tmap_nhwc(const void* base, uint64_t C, uint64_t W, uint64_t H, uint64_t N, uint32_t box_w, uint32_t box_h,
                            uint32_t box_n, uint32_t stride) {
   RT_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base must be 16-byte aligned");

@@ -60,6 +60,9 @@ CUtensorMap make_tmap_2byte_4d(const void* base, uint64_t d0, uint64_t d1, uint6
 // box read as zero.  row_bytes must be a multiple of 16.
 CUtensorMap make_tmap_rows(const void* base, int elem_bytes, uint64_t row_elems, uint64_t rows,
                            uint32_t box_elems, uint32_t box_rows);
+// Rank-2 map over byte rows seen as 32-bit words with the 128-byte swizzle: box = 128 bytes x box_rows rows; row r of
+// a box lands at r * 128 with its 16-byte chunk c stored at chunk position c ^ (r & 7).
+CUtensorMap make_tmap_words_sw128(const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows);
 // Rank-4 map over a channels-last activation tensor [N][H][W][C] (2-byte elements, C contiguous, 128-byte swizzle):
 // a box covers 64 channels x box_w x box_h x box_n positions taken every `stride` pixels along W and H.
 CUtensorMap make_tmap_nhwc(const void* base, uint64_t C, uint64_t W, uint64_t H, uint64_t N, uint32_t box_w, uint32_t box_h,

@@ -171,6 +171,7 @@ class FusedDDPAdamW:
     # ------------------------------------------------------------------- step
     def step(self) -> None:
         """Finish the data-parallel optimizer step for the gradients of the last backward."""
+        self.flat.collect_autograd_grads()      # gradients left in ``.grad`` by ordinary autograd modules
         for i in range(self.n_buckets):
             if not self._launched[i]:
                 self._launch_bucket(i)

@@ -65,7 +65,26 @@ class QuantLinear:
     # From this many activation rows on, expanding the weights (0.56 B read + 2 B written + 2 B re-read per
     # weight) costs less than re-streaming the quantised matrix once per 8 rows through the GEMV kernel.
     GEMM_MIN_ROWS = 64
+    # Between these row counts the dequant-fused tcgen05 GEMM reads the quantised weights once for all rows
+    # (the GEMV kernel re-reads them for every 8 rows; the two-pass path moves 4.5 B per weight).
+    TC_MIN_ROWS, TC_MAX_ROWS = 9, 256
     _scratch_buf = {}
+    _tc_scratch = {}
+
+    def _tc_buffers(self, rows: int):
+        """Split-K scratch of the fused GEMM: fp32 partial sums (grown on demand) and zeroed per-tile counters that
+        every call leaves zeroed; shared by all layers of a device (kernels on one stream run in order)."""
+        C = _native.load(required=True)
+        need, ncnt, splits = C.q_gemm_tc_scratch(rows, self.out_features, self.in_features, self.q8)
+        if splits == 1:
+            return None, None
+        key = (self.device.type, self.device.index)
+        part, cnt = QuantLinear._tc_scratch.get(key, (None, None))
+        if part is None or part.numel() < need or cnt.numel() < ncnt:
+            part = torch.empty(max(need, 1 << 22), dtype=torch.float32, device=self.device)
+            cnt = torch.zeros(max(ncnt, 4096), dtype=torch.int32, device=self.device)
+            QuantLinear._tc_scratch[key] = (part, cnt)
+        return part, cnt
 
     def _scratch(self, numel: int) -> torch.Tensor:
         """One fp16 expansion buffer per device, grown to the largest matrix seen (kernels on one stream run in
@@ -102,7 +121,11 @@ class QuantLinear:
             C = _native.load(required=True)
             x2 = x2.to(torch.float16).contiguous()
             r = residual.reshape(-1, self.out_features) if residual is not None else None
-            if x2.shape[0] >= self.GEMM_MIN_ROWS:
+            if self.TC_MIN_ROWS <= x2.shape[0] <= self.TC_MAX_ROWS:
+                y = torch.empty((x2.shape[0], self.out_features), dtype=torch.float16, device=self.device)
+                part, cnt = self._tc_buffers(x2.shape[0])
+                C.q_gemm_tc(self.qs, self.scales, x2, y, None, r, self.q8, part, cnt)
+            elif x2.shape[0] >= self.GEMM_MIN_ROWS:
                 # prefill / large batch: expand once to fp16 scratch, then the tcgen05 GEMM (fp32 accumulate + output)
                 w = self._scratch(self.out_features * self.in_features).view(self.out_features, self.in_features)
                 C.dequant_f16(self.qs, self.scales, w, self.q8)

@@ -157,3 +157,25 @@ def test_q_gemv_register_and_bulk_paths_agree(q8, M, N, K):
     ref = x.float() @ q.dequantize().t()
     assert rel_err(ya, ref) < 6e-3 and rel_err(yb, ref) < 6e-3
     _native.check_status()
+
+
+@pytest.mark.parametrize("q8", [False, True])
+@pytest.mark.parametrize("M,N,K", [(9, 1000, 1024), (16, 4096, 4096), (32, 515, 5504), (100, 384, 2752), (256, 1024, 4096),
+                                   (33, 128, 32), (64, 22016, 4096)])
+def test_q_gemm_tensor_core_matches_reference(q8, M, N, K):
+    """Dequant-fused tcgen05 GEMM (weights read once for all rows) against x @ dequant(W)^T + residual; covers ragged N,
+    K that is not a multiple of the raw tile, every padded row count and the split-K reduction."""
+    from rustorch_b200 import _native
+    from rustorch_b200.formats import gguf
+    from rustorch_b200.llm import QuantLinear
+    q = QuantLinear.random(N, K, gguf.GGMLType.Q8_0 if q8 else gguf.GGMLType.Q4_0, 0.05, "cuda", seed=M + N)
+    x = (torch.randn(M, K, device="cuda") * 0.5).half()
+    res = torch.randn(M, N, device="cuda").half()
+    assert QuantLinear.TC_MIN_ROWS <= M <= QuantLinear.TC_MAX_ROWS
+    ref = x.float() @ q.dequantize().t().to("cuda") + res.float()
+    for _ in range(2):                                # second call: the tile counters were left at zero
+        y = q(x, residual=res)
+        assert rel_err(y, ref) < 3e-3
+    y2 = q(x)
+    assert rel_err(y2, ref - res.float()) < 3e-3
+    _native.check_status()

@@ -96,11 +96,11 @@ def main():
         arn = AllReduceResidualNorm(64 * 1024, dt_, dev)
         wn = (torch.rand(1024, generator=gq) + 0.5).to(dt_).to(dev)
         dist.broadcast(wn, 0)
-        for call, rows in enumerate((1, 32, 3, 64, 1, 1, 7)):
-            part = torch.randn(rows, 1024, generator=gq).to(dt_).to(dev)
+        for call, nr in enumerate((1, 32, 3, 64, 1, 1, 7)):
+            part = torch.randn(nr, 1024, generator=gq).to(dt_).to(dev)
             if call == 2:
                 part[0, :16] = -0.0                      # the sentinel value itself must survive as a zero
-            x0 = torch.randn(rows, 1024, generator=torch.Generator().manual_seed(call)).to(dt_).to(dev)
+            x0 = torch.randn(nr, 1024, generator=torch.Generator().manual_seed(call)).to(dt_).to(dev)
             tot = part.float().clone()
             dist.all_reduce(tot)
             x_ref = (x0.float() + tot).to(dt_).float()
@@ -197,12 +197,12 @@ def main():
     res["ar_8kb_p2p_us"] = timed(lambda: pc.all_reduce(small), 50) * 1e3
     res["ar_8kb_nccl_us"] = timed(lambda: dist.all_reduce(small), 50) * 1e3
     arn = AllReduceResidualNorm(32 * 4096, torch.float16, dev)
-    for rows in (1, 32):
-        part = torch.randn(rows, 4096, device=dev).half()
-        xx = torch.zeros(rows, 4096, device=dev).half()
+    for nr in (1, 32):
+        part = torch.randn(nr, 4096, device=dev).half()
+        xx = torch.zeros(nr, 4096, device=dev).half()
         wn = torch.ones(4096, device=dev).half()
         hb = torch.empty_like(xx)
-        res[f"arn_{rows}x4096_us"] = timed(lambda: arn(part, xx, wn, 1e-5, hb), 50) * 1e3
+        res[f"arn_{nr}x4096_us"] = timed(lambda: arn(part, xx, wn, 1e-5, hb), 50) * 1e3
     big_ar = torch.randn(1 << 22, device=dev).bfloat16()
     res["ar_8mb_p2p_us"] = timed(lambda: pc.all_reduce(big_ar), 20) * 1e3
     res["ar_8mb_nccl_us"] = timed(lambda: dist.all_reduce(big_ar), 20) * 1e3
