@@ -167,7 +167,7 @@ def main():
     for i in range(args.warmup):
         step_device(i)
     _native.check_status()
-    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    sampler = ClockSampler(local_rank, 0.05).start() if rank == 0 else None
     ms, launches = timed(step_device, args.steps)
     clocks = sampler.stop() if sampler else None
     for i in range(min(2, args.warmup)):

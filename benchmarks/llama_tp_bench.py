@@ -1,11 +1,11 @@
 """Llama-style 8B decoder, tensor + sequence parallel bf16 training step (BASELINE config 4).
 
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-      benchmarks/llama_tp_bench.py --steps 5 --warmup 3 [--layers 32] [--seqs 8] [--seq-len 4096] [--impl ours|library]
+      benchmarks/llama_tp_bench.py --steps 5 --warmup 3 [--layers 32] [--seqs 8] [--seq-len 4096]
 
 Every rank gets the same global batch (``--seqs`` sequences of ``--seq-len`` uniform random token ids); the model
-is sharded over the N ranks with the fused all-gather->GEMM / GEMM->reduce-scatter kernels (``--impl ours``) or with
-NCCL collectives around library GEMMs (``--impl library``: ``distributed.model_parallel``).  AdamW through the fused
+is sharded over the N ranks with the fused all-gather->GEMM / GEMM->reduce-scatter kernels.
+AdamW through the fused
 flat optimizer.  Prints one JSON line (tokens/s of the whole job, device time, max over ranks).  ``--layers`` below 32
 is for bring-up and is marked ``"reduced": true`` in the output.
 """

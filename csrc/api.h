@@ -218,6 +218,36 @@ struct P2PCollArgs {
 };
 void p2p_collective(const P2PCollArgs& a, cudaStream_t stream);
 
+// ------------------------------------------------------------ nn/pool_dropout.cu
+// Channels-last pooling.  Forward: x [N][H][W][C] -> y [N][OH][OW][C] (+ idx for max).  Backward: y holds dy, x receives dx.
+struct Pool2dArgs {
+  int dtype;
+  bool max, backward;
+  void* x;              // forward: input (read); backward: dx (written)
+  void* y;              // forward: output (written); backward: dy (read)
+  unsigned char* idx;   // max pooling: window position of the maximum per output element
+  int N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw;
+};
+void pool2d(const Pool2dArgs& a, cudaStream_t stream);
+void dropout(int dtype, const void* x, void* y, long long n, float p, unsigned long long seed, unsigned long long offset,
+             cudaStream_t stream);
+// ------------------------------------------------------------ nn/llama_ops.cu (bf16)
+// forward: packed [rows][(H + 2 Hkv) D] -> q, k (rotated), v; backward: (dq, dk, dv) -> packed gradient (inverse rotation).
+void rope_split(void* packed, void* q, void* k, void* v, const float* cos_t, const float* sin_t, long long rows, int T, int H, int Hkv,
+                int D, bool backward, cudaStream_t s);
+// forward: out[rows][F] = silu(gu[:, :F]) * gu[:, F:]; backward: out[rows][2F] = d(gate) | d(up) from dact.
+void swiglu(const void* gu, const void* dact, void* out, long long rows, int F, bool backward, cudaStream_t s);
+// ------------------------------------------------------------ nn/rnn_amp_sparse.cu
+void lstm_gates_fwd(int dtype, void* gates, const void* c, void* h_out, void* c_out, int B, int H, cudaStream_t s);
+void lstm_gates_bwd(int dtype, const void* act, const void* c, const void* c_new, const void* dh, const void* dc_new, void* dgates,
+                    void* dc, int B, int H, cudaStream_t s);
+void gru_gates_fwd(int dtype, const void* gi, const void* gh, const void* h, void* h_out, void* save, int B, int H, cudaStream_t s);
+void gru_gates_bwd(int dtype, const void* save, const void* h, const void* dh_new, void* dgi, void* dgh, void* dh, int B, int H,
+                   cudaStream_t s);
+void amp_unscale(int dtype, void* grads, long long n, float inv_scale, float* found_inf, cudaStream_t s);
+void csr_spmm(const long long* row_ptr, const long long* col, const float* val, const float* x, float* y, long long rows, int n_dense,
+              cudaStream_t s);
+
 // ------------------------------------------------------ collective/ar_residual_norm.cu
 // x[rows][d] += sum over ranks of partial[rows][d]; h = rmsnorm(x) * w (h may be null).  fp16 / bf16.
 struct ArNormArgs {

@@ -583,8 +583,157 @@ void batchnorm_bwd(const Tensor& x2, const Tensor& dy2, const c10::optional<Tens
   rt::batchnorm_bwd(a, cur_stream(x2.device().index()));
 }
 
+
+// x: channels-last storage viewed as [N, H, W, C] (contiguous); y likewise [N, OH, OW, C].
+void pool2d(Tensor& x, Tensor& y, const c10::optional<Tensor>& idx, bool is_max, bool backward, int64_t kh, int64_t kw, int64_t sh,
+            int64_t sw, int64_t ph, int64_t pw) {
+  rt::Pool2dArgs a{};
+  a.dtype = dtype_code(x, "pool2d x");
+  TORCH_CHECK(x.dim() == 4 && y.dim() == 4 && x.is_contiguous() && y.is_contiguous() && y.scalar_type() == x.scalar_type() &&
+                  y.is_cuda() && y.size(0) == x.size(0) && y.size(3) == x.size(3), "pool2d: contiguous [N, H, W, C] tensors of one dtype");
+  a.max = is_max; a.backward = backward;
+  a.x = x.data_ptr(); a.y = y.data_ptr();
+  if (idx.has_value() && idx->defined()) {
+    TORCH_CHECK(idx->scalar_type() == at::kByte && idx->is_cuda() && idx->is_contiguous() && idx->numel() == y.numel(),
+                "pool2d: idx must be a uint8 tensor shaped like the output");
+    a.idx = idx->data_ptr<uint8_t>();
+  }
+  a.N = int(x.size(0)); a.H = int(x.size(1)); a.W = int(x.size(2)); a.C = int(x.size(3));
+  a.OH = int(y.size(1)); a.OW = int(y.size(2));
+  a.kh = int(kh); a.kw = int(kw); a.sh = int(sh); a.sw = int(sw); a.ph = int(ph); a.pw = int(pw);
+  c10::cuda::CUDAGuard guard(x.device());
+  rt::pool2d(a, cur_stream(x.device().index()));
+}
+
+void dropout(const Tensor& x, Tensor& y, double p, int64_t seed, int64_t offset) {
+  const int dt = dtype_code(x, "dropout x");
+  TORCH_CHECK(x.is_non_overlapping_and_dense() && y.strides() == x.strides() && y.is_cuda() && y.scalar_type() == x.scalar_type() &&
+                  y.numel() == x.numel(), "dropout: dense tensors of one dtype, size and memory layout");
+  c10::cuda::CUDAGuard guard(x.device());
+  rt::dropout(dt, x.data_ptr(), y.data_ptr(), x.numel(), float(p), (unsigned long long)seed, (unsigned long long)offset,
+              cur_stream(x.device().index()));
+}
+
+static void check_bh(const Tensor& t, int64_t B, int64_t cols, at::ScalarType st, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == st && t.dim() == 2 && t.size(0) == B && t.size(1) == cols, name,
+              ": expected a contiguous CUDA [", B, ", ", cols, "] tensor");
+}
+
+void lstm_gates_fwd(Tensor& gates, const Tensor& c, Tensor& h_out, Tensor& c_out) {
+  const int dt = dtype_code(gates, "lstm gates");
+  const int64_t B = c.size(0), H = c.size(1);
+  check_bh(gates, B, 4 * H, gates.scalar_type(), "lstm gates");
+  check_bh(c, B, H, gates.scalar_type(), "lstm c"); check_bh(h_out, B, H, gates.scalar_type(), "lstm h_out");
+  check_bh(c_out, B, H, gates.scalar_type(), "lstm c_out");
+  c10::cuda::CUDAGuard guard(gates.device());
+  rt::lstm_gates_fwd(dt, gates.data_ptr(), c.data_ptr(), h_out.data_ptr(), c_out.data_ptr(), int(B), int(H), cur_stream(gates.device().index()));
+}
+
+void lstm_gates_bwd(const Tensor& act, const Tensor& c, const Tensor& c_new, const c10::optional<Tensor>& dh,
+                    const c10::optional<Tensor>& dc_new, Tensor& dgates, Tensor& dc) {
+  const int dt = dtype_code(act, "lstm act");
+  const int64_t B = c.size(0), H = c.size(1);
+  const auto st = act.scalar_type();
+  check_bh(act, B, 4 * H, st, "lstm act"); check_bh(dgates, B, 4 * H, st, "lstm dgates");
+  check_bh(c, B, H, st, "lstm c"); check_bh(c_new, B, H, st, "lstm c_new"); check_bh(dc, B, H, st, "lstm dc");
+  const void *pdh = nullptr, *pdc = nullptr;
+  if (dh.has_value() && dh->defined()) { check_bh(*dh, B, H, st, "lstm dh"); pdh = dh->data_ptr(); }
+  if (dc_new.has_value() && dc_new->defined()) { check_bh(*dc_new, B, H, st, "lstm dc_new"); pdc = dc_new->data_ptr(); }
+  c10::cuda::CUDAGuard guard(act.device());
+  rt::lstm_gates_bwd(dt, act.data_ptr(), c.data_ptr(), c_new.data_ptr(), pdh, pdc, dgates.data_ptr(), dc.data_ptr(), int(B), int(H),
+                     cur_stream(act.device().index()));
+}
+
+void gru_gates_fwd(const Tensor& gi, const Tensor& gh, const Tensor& h, Tensor& h_out, Tensor& save) {
+  const int dt = dtype_code(gi, "gru gi");
+  const int64_t B = h.size(0), H = h.size(1);
+  const auto st = gi.scalar_type();
+  check_bh(gi, B, 3 * H, st, "gru gi"); check_bh(gh, B, 3 * H, st, "gru gh"); check_bh(h, B, H, st, "gru h");
+  check_bh(h_out, B, H, st, "gru h_out"); check_bh(save, B, 4 * H, st, "gru save");
+  c10::cuda::CUDAGuard guard(gi.device());
+  rt::gru_gates_fwd(dt, gi.data_ptr(), gh.data_ptr(), h.data_ptr(), h_out.data_ptr(), save.data_ptr(), int(B), int(H),
+                    cur_stream(gi.device().index()));
+}
+
+void gru_gates_bwd(const Tensor& save, const Tensor& h, const Tensor& dh_new, Tensor& dgi, Tensor& dgh, Tensor& dh) {
+  const int dt = dtype_code(save, "gru save");
+  const int64_t B = h.size(0), H = h.size(1);
+  const auto st = save.scalar_type();
+  check_bh(save, B, 4 * H, st, "gru save"); check_bh(h, B, H, st, "gru h"); check_bh(dh_new, B, H, st, "gru dh_new");
+  check_bh(dgi, B, 3 * H, st, "gru dgi"); check_bh(dgh, B, 3 * H, st, "gru dgh"); check_bh(dh, B, H, st, "gru dh");
+  c10::cuda::CUDAGuard guard(save.device());
+  rt::gru_gates_bwd(dt, save.data_ptr(), h.data_ptr(), dh_new.data_ptr(), dgi.data_ptr(), dgh.data_ptr(), dh.data_ptr(), int(B), int(H),
+                    cur_stream(save.device().index()));
+}
+
+void amp_unscale(Tensor& grads, double inv_scale, Tensor& found_inf) {
+  const int dt = dtype_code(grads, "amp_unscale grads");
+  TORCH_CHECK(grads.is_contiguous() && found_inf.is_cuda() && found_inf.scalar_type() == at::kFloat && found_inf.numel() >= 1,
+              "amp_unscale: contiguous gradients and a float CUDA flag");
+  c10::cuda::CUDAGuard guard(grads.device());
+  rt::amp_unscale(dt, grads.data_ptr(), grads.numel(), float(inv_scale), found_inf.data_ptr<float>(), cur_stream(grads.device().index()));
+}
+
+void csr_spmm(const Tensor& row_ptr, const Tensor& col, const Tensor& val, const Tensor& x, Tensor& y) {
+  TORCH_CHECK(row_ptr.is_cuda() && col.is_cuda() && val.is_cuda() && x.is_cuda() && y.is_cuda(), "csr_spmm: CUDA tensors");
+  TORCH_CHECK(row_ptr.scalar_type() == at::kLong && col.scalar_type() == at::kLong && val.scalar_type() == at::kFloat &&
+                  x.scalar_type() == at::kFloat && y.scalar_type() == at::kFloat, "csr_spmm: int64 indices, fp32 values");
+  TORCH_CHECK(row_ptr.is_contiguous() && col.is_contiguous() && val.is_contiguous() && x.is_contiguous() && y.is_contiguous() &&
+                  x.dim() == 2 && y.dim() == 2 && y.size(0) == row_ptr.numel() - 1 && y.size(1) == x.size(1) && col.numel() == val.numel(),
+              "csr_spmm: x [cols, n], y [rows, n]");
+  c10::cuda::CUDAGuard guard(x.device());
+  rt::csr_spmm(reinterpret_cast<const long long*>(row_ptr.data_ptr<int64_t>()), reinterpret_cast<const long long*>(col.data_ptr<int64_t>()), val.data_ptr<float>(), x.data_ptr<float>(), y.data_ptr<float>(),
+               y.size(0), int(x.size(1)), cur_stream(x.device().index()));
+}
+
+
+static void check_bf16c(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == at::kBFloat16, name, ": contiguous CUDA bf16 tensor required");
+}
+
+// packed [rows, (H + 2 Hkv) * D]; q [rows, H, D]; k, v [rows, Hkv, D]; cos / sin [T, D / 2] fp32; rows = B * T.
+void rope_split(Tensor& packed, Tensor& q, Tensor& k, Tensor& v, const Tensor& cos_t, const Tensor& sin_t, int64_t T, bool backward) {
+  check_bf16c(packed, "rope_split packed"); check_bf16c(q, "rope_split q"); check_bf16c(k, "rope_split k"); check_bf16c(v, "rope_split v");
+  const int64_t D = q.size(-1), H = q.size(-2), Hkv = k.size(-2);
+  const int64_t rows = q.numel() / (H * D);
+  TORCH_CHECK(k.numel() == rows * Hkv * D && v.numel() == k.numel() && packed.numel() == rows * (H + 2 * Hkv) * D && rows % T == 0,
+              "rope_split: shape mismatch");
+  TORCH_CHECK(cos_t.is_cuda() && sin_t.is_cuda() && cos_t.scalar_type() == at::kFloat && sin_t.scalar_type() == at::kFloat &&
+                  cos_t.is_contiguous() && sin_t.is_contiguous() && cos_t.size(-1) == D / 2 && sin_t.size(-1) == D / 2 &&
+                  cos_t.size(0) >= T && sin_t.size(0) >= T, "rope_split: cos / sin tables must be fp32 [>= T, D / 2]");
+  c10::cuda::CUDAGuard guard(packed.device());
+  rt::rope_split(packed.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), rows,
+                 int(T), int(H), int(Hkv), int(D), backward, cur_stream(packed.device().index()));
+}
+
+void swiglu(const Tensor& gu, const c10::optional<Tensor>& dact, Tensor& out, bool backward) {
+  check_bf16c(gu, "swiglu gu"); check_bf16c(out, "swiglu out");
+  TORCH_CHECK(gu.dim() == 2 && gu.size(1) % 2 == 0, "swiglu: gu must be [rows, 2 F]");
+  const int64_t rows = gu.size(0), F = gu.size(1) / 2;
+  const void* pd = nullptr;
+  if (backward) {
+    TORCH_CHECK(dact.has_value() && dact->numel() == rows * F && out.numel() == rows * 2 * F, "swiglu backward: shape mismatch");
+    check_bf16c(*dact, "swiglu dact");
+    pd = dact->data_ptr();
+  } else {
+    TORCH_CHECK(out.numel() == rows * F, "swiglu: out must be [rows, F]");
+  }
+  c10::cuda::CUDAGuard guard(gu.device());
+  rt::swiglu(gu.data_ptr(), pd, out.data_ptr(), rows, int(F), backward, cur_stream(gu.device().index()));
+}
+
 void register_extra_ops(pybind11::module_& m) {
   m.def("p2p_collective", &p2p_collective, "all-reduce / all-gather / reduce-scatter / broadcast over symmetric peer memory");
+  m.def("rope_split", &rope_split, "rotary embedding fused with the q / k / v split (bf16), forward or backward");
+  m.def("swiglu", &swiglu, "silu(gate) * up over a [rows, 2F] gate|up matrix (bf16), forward or backward");
+  m.def("pool2d", &pool2d, "channels-last max / average pooling, forward or backward");
+  m.def("dropout", &dropout, "Philox dropout (the backward pass is the same call on dy)");
+  m.def("lstm_gates_fwd", &lstm_gates_fwd);
+  m.def("lstm_gates_bwd", &lstm_gates_bwd);
+  m.def("gru_gates_fwd", &gru_gates_fwd);
+  m.def("gru_gates_bwd", &gru_gates_bwd);
+  m.def("amp_unscale", &amp_unscale, "grads *= inv_scale, found_inf = 1 on any non-finite value");
+  m.def("csr_spmm", &csr_spmm, "CSR sparse x dense product (fp32)");
   m.def("ar_residual_norm", &ar_residual_norm, "all-reduce over peer memory + residual add + RMSNorm in one kernel");
   m.def("conv2d_fwd", &conv2d_fwd, "implicit-GEMM conv2d forward (channels-last bf16)");
   m.def("conv2d_wgrad", &conv2d_wgrad, "implicit-GEMM conv2d weight gradient (fp32 accumulate)");

@@ -38,6 +38,7 @@ namespace {
 constexpr int QT_THREADS = 320;
 constexpr int QT_DQ_WARPS = 8;
 constexpr int QT_RAW_STAGES = 3;
+constexpr int QT_MAX_SLOTS = 6;
 constexpr int QT_RAW_BYTES = 128 * 128;   // 128 rows x 128 B
 constexpr int QT_A_BYTES = 128 * 128;     // 128 rows x 64 halves
 
@@ -86,9 +87,9 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q_gemm_tc_kernel(const __grid_c
   uint64_t* raw_full = bars;
   uint64_t* raw_empty = raw_full + QT_RAW_STAGES;
   uint64_t* x_full = raw_empty + QT_RAW_STAGES;
-  uint64_t* a_full = x_full + 4;
-  uint64_t* op_empty = a_full + 4;
-  uint64_t* acc_full = op_empty + 4;
+  uint64_t* a_full = x_full + QT_MAX_SLOTS;
+  uint64_t* op_empty = a_full + QT_MAX_SLOTS;
+  uint64_t* acc_full = op_empty + QT_MAX_SLOTS;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   CtaCtl* ctl = reinterpret_cast<CtaCtl*>(tmem_slot + 1);
   int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q_gemm_tc_kernel(const __grid_c
       mbar_init(&raw_full[i], 1);
       mbar_init(&raw_empty[i], QT_DQ_WARPS);
     }
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < QT_MAX_SLOTS; ++i) {
       mbar_init(&x_full[i], 1);
       mbar_init(&a_full[i], QT_DQ_WARPS);
       mbar_init(&op_empty[i], 1);
@@ -143,7 +144,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q_gemm_tc_kernel(const __grid_c
         bool progress = false;
         if (rc < c_end) {
           const int s = rci % QT_RAW_STAGES;
-          if (mbar_try_wait(&raw_empty[s], ((rci / QT_RAW_STAGES) & 1) ^ 1)) {
+          if (mbar_test_wait(&raw_empty[s], ((rci / QT_RAW_STAGES) & 1) ^ 1)) {
             mbar_arrive_expect_tx(&raw_full[s], QT_RAW_BYTES);
             tma_load_2d(raw + s * QT_RAW_BYTES, &tm_raw, &raw_full[s], rc * 32, n0);
             ++rc; ++rci;
@@ -152,7 +153,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q_gemm_tc_kernel(const __grid_c
         }
         if (xc < c_end) {
           const int j = xit % OS;
-          if (mbar_try_wait(&op_empty[j], ((xit / OS) & 1) ^ 1)) {
+          if (mbar_test_wait(&op_empty[j], ((xit / OS) & 1) ^ 1)) {
             mbar_arrive_expect_tx(&x_full[j], x_bytes);
             tma_load_3d(x_t + j * x_bytes, &tm_x, &x_full[j], xc * KRAW + xsub * 64, 0, 0);
             ++xit;
@@ -208,12 +209,26 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q_gemm_tc_kernel(const __grid_c
     const int n = n0 + r;
     const bool row_ok = n < p.N;
     const __half* srow = p.scales + (long long)min(n, p.N - 1) * nb;
-    constexpr int BPS = Q8 ? 2 : 2;              // blocks per 64-k step (both formats: 32-weight blocks)
+    // Scales of a row's chunk are SPC consecutive halves (16 B for Q4_0, 8 B for Q8_0): one vector load when the row
+    // pitch keeps them aligned and the chunk lies inside the row, else one 2-byte load per block.
+    constexpr int SPC = KRAW / 32;
+    const bool vec_scales = (nb % SPC) == 0;
     auto load_scales = [&](int c, __half (&d)[SUBS]) {
+      const bool live = row_ok && c < c_end;
+      if (vec_scales) {
+        __half tmp[SPC];
+        if (live) {
+          if (SPC == 8) *reinterpret_cast<uint4*>(tmp) = __ldg(reinterpret_cast<const uint4*>(srow + (long long)c * SPC));
+          else *reinterpret_cast<uint2*>(tmp) = __ldg(reinterpret_cast<const uint2*>(srow + (long long)c * SPC));
+        }
 #pragma unroll
-      for (int sub = 0; sub < SUBS; ++sub) {
-        const int b = (c * KRAW >> 5) + sub * BPS + hb;
-        d[sub] = (row_ok && b < nb && c < c_end) ? srow[b] : __ushort_as_half(0);
+        for (int sub = 0; sub < SUBS; ++sub) d[sub] = live ? (hb ? tmp[sub * 2 + 1] : tmp[sub * 2]) : __ushort_as_half(0);
+      } else {
+#pragma unroll
+        for (int sub = 0; sub < SUBS; ++sub) {
+          const int b = c * SPC + sub * 2 + hb;
+          d[sub] = (live && b < nb) ? srow[b] : __ushort_as_half(0);
+        }
       }
     };
     __half dcur[SUBS], dnxt[SUBS];
@@ -373,7 +388,7 @@ void q_gemm_tc(const QGemvArgs& a, void* partial, int* counters, cudaStream_t st
   p.ldy = a.ldy; p.ldr = a.ldr;
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.m_pad = pad_m(a.M);
-  p.op_slots = p.m_pad == 256 ? 3 : 4;
+  p.op_slots = p.m_pad == 256 ? 3 : p.m_pad == 128 ? 4 : QT_MAX_SLOTS;
   long long pf; int nc, splits;
   q_gemm_tc_scratch(a.M, a.N, a.K, a.q8, sm_count(device), &pf, &nc, &splits);
   p.total_chunks = (a.K + kraw - 1) / kraw;
@@ -385,7 +400,7 @@ void q_gemm_tc(const QGemvArgs& a, void* partial, int* counters, cudaStream_t st
   const uint64_t row_bytes = (uint64_t)(a.K / 32) * (a.q8 ? 32 : 16);
   const CUtensorMap tr = make_tmap_words_sw128(a.qs, row_bytes, a.N, 128);
   const CUtensorMap tx = make_tmap_2byte(a.x, a.K, a.M, 1, a.ldx, 0, 64, p.m_pad);
-  const int smem = 1024 + QT_RAW_STAGES * QT_RAW_BYTES + p.op_slots * (QT_A_BYTES + p.m_pad * 128) + 256;
+  const int smem = 1024 + QT_RAW_STAGES * QT_RAW_BYTES + p.op_slots * (QT_A_BYTES + p.m_pad * 128) + 512;
   const dim3 grid((a.N + 127) / 128, splits);
   if (a.q8) {
     static bool cfg[64] = {false};

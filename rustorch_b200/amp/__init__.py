@@ -16,6 +16,13 @@ from typing import Iterable, List, Optional
 
 import torch
 
+_NATIVE_DTYPES = (torch.float32, torch.bfloat16, torch.float16)
+
+
+def _native_ok() -> bool:
+    from .. import _native
+    return _native.available()
+
 
 class AutocastMode(enum.Enum):
     NONE = "none"
@@ -89,12 +96,32 @@ class GradScaler:
         """Divide gradients by the scale in place; returns whether an overflow was found."""
         if not self.enabled:
             return False
+        flat = getattr(optimizer_or_params, "flat", None)
+        if flat is not None and getattr(flat, "grad", None) is not None and flat.grad.is_cuda and not self._unscaled:
+            flat.collect_autograd_grads()
+            self._found_inf = self._native_unscale([flat.grad])      # one pass over the flat fp32 gradient buffer
+            self._unscaled = True
+            return self._found_inf
         ps = self._params(optimizer_or_params)
+        gs = [p.grad for p in ps]
+        if gs and not self._unscaled and all(g.is_cuda and g.is_contiguous() and g.dtype in _NATIVE_DTYPES for g in gs) and _native_ok():
+            self._found_inf = self._native_unscale(gs)
+            self._unscaled = True
+            return self._found_inf
         self._found_inf = self.check_overflow(ps)
         if not self._found_inf and not self._unscaled and ps:
-            torch._foreach_mul_([p.grad for p in ps], 1.0 / self._scale)
+            torch._foreach_mul_(gs, 1.0 / self._scale)
         self._unscaled = True
         return self._found_inf
+
+    def _native_unscale(self, grads) -> bool:
+        """``g *= 1 / scale`` and the inf / nan check in the same pass (csrc/nn/rnn_amp_sparse.cu); one host read."""
+        from .. import _native
+        C = _native.load(required=True)
+        flag = torch.zeros(1, dtype=torch.float32, device=grads[0].device)
+        for g in grads:
+            C.amp_unscale(g, 1.0 / self._scale, flag)
+        return bool(flag.item() != 0.0)
 
     unscale_ = unscale_grads
 

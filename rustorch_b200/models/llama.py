@@ -69,6 +69,57 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
     return torch.cat([a * c - b * s, a * s + b * c], -1).to(x.dtype)
 
 
+class _RopeSplit(torch.autograd.Function):
+    """qkv ``[B*T, (H + 2 Hkv) D]`` -> rotated q ``[B, T, H, D]``, rotated k and v ``[B, T, Hkv, D]`` in one kernel
+    (csrc/nn/llama_ops.cu); backward packs the three gradients back with the inverse rotation."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, B, T, H, Hkv, D):
+        from .. import _native
+        C = _native.load(required=True)
+        qkv = qkv.contiguous()
+        q = torch.empty((B, T, H, D), dtype=qkv.dtype, device=qkv.device)
+        k = torch.empty((B, T, Hkv, D), dtype=qkv.dtype, device=qkv.device)
+        v = torch.empty_like(k)
+        C.rope_split(qkv, q, k, v, cos, sin, T, False)
+        ctx.save_for_backward(cos, sin)
+        ctx.geom = (B, T, H, Hkv, D)
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        from .. import _native
+        C = _native.load(required=True)
+        cos, sin = ctx.saved_tensors
+        B, T, H, Hkv, D = ctx.geom
+        dqkv = torch.empty((B * T, (H + 2 * Hkv) * D), dtype=dq.dtype, device=dq.device)
+        C.rope_split(dqkv, dq.contiguous(), dk.contiguous(), dv.contiguous(), cos, sin, T, True)
+        return dqkv, None, None, None, None, None, None, None
+
+
+class _SwiGLU(torch.autograd.Function):
+    """``silu(gu[:, :F]) * gu[:, F:]`` forward and backward as one kernel each (csrc/nn/llama_ops.cu)."""
+
+    @staticmethod
+    def forward(ctx, gu):
+        from .. import _native
+        C = _native.load(required=True)
+        gu = gu.contiguous()
+        act = torch.empty((gu.shape[0], gu.shape[1] // 2), dtype=gu.dtype, device=gu.device)
+        C.swiglu(gu, None, act, False)
+        ctx.save_for_backward(gu)
+        return act
+
+    @staticmethod
+    def backward(ctx, dact):
+        from .. import _native
+        C = _native.load(required=True)
+        (gu,) = ctx.saved_tensors
+        dgu = torch.empty_like(gu)
+        C.swiglu(gu, dact.contiguous(), dgu, True)
+        return dgu
+
+
 def _native_ok(x: torch.Tensor) -> bool:
     return x.is_cuda and x.dtype == torch.bfloat16
 
@@ -125,14 +176,20 @@ class LlamaBlock(nn.Module):
         D, H, Hkv = c.head_dim, self.h_local, self.hkv_local
         h = _rms(x, self.attn_norm, c.rms_eps)
         qkv = self.wqkv(h) if self.tp else _linear(h, self.wqkv)                    # [B*T, (H + 2 Hkv) D] (all tokens)
-        qkv = qkv.view(B, T, H + 2 * Hkv, D)
-        q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
-        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-        att = _attention(q, k, v.contiguous()).reshape(B * T, H * D)
+        if _native_ok(qkv) and D % 16 == 0 and cos.dtype == torch.float32:
+            q, k, v = _RopeSplit.apply(qkv, cos, sin, B, T, H, Hkv, D)
+        else:
+            qkv = qkv.view(B, T, H + 2 * Hkv, D)
+            q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:].contiguous()
+            q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        att = _attention(q, k, v).reshape(B * T, H * D)
         x = x + (self.wo(att) if self.tp else _linear(att, self.wo))
         h = _rms(x, self.ffn_norm, c.rms_eps)
         gu = self.w_gate_up(h) if self.tp else _linear(h, self.w_gate_up)           # [B*T, 2 ff_local]: gate | up
-        act = ew.mul(ew.unary("silu", gu[:, : self.ff_local].contiguous()), gu[:, self.ff_local:].contiguous())
+        if _native_ok(gu) and self.ff_local % 8 == 0:
+            act = _SwiGLU.apply(gu)
+        else:
+            act = ew.mul(ew.unary("silu", gu[:, : self.ff_local].contiguous()), gu[:, self.ff_local:].contiguous())
         return x + (self.w_down(act) if self.tp else _linear(act, self.w_down))
 
 

@@ -268,6 +268,9 @@ class InstanceNorm3d(nn.InstanceNorm3d):
     pass
 
 
+from ..ops import pool as _pool  # noqa: E402
+
+
 class Dropout(nn.Module):
     """``(p, inplace)``: training zeroes with probability p and scales by 1/(1-p); eval is identity
     (src/nn/dropout.rs:63,105-176)."""
@@ -279,7 +282,7 @@ class Dropout(nn.Module):
         self.p, self.inplace = p, inplace
 
     def forward(self, x):
-        return F.dropout(x, self.p, self.training, self.inplace)
+        return _pool.dropout(x, self.p, self.training, self.inplace)      # Philox kernel on CUDA, no mask tensor
 
 
 class AlphaDropout(nn.AlphaDropout):
@@ -287,7 +290,7 @@ class AlphaDropout(nn.AlphaDropout):
 
 
 def dropout(x, p: float = 0.5, training: bool = True):
-    return F.dropout(x, p, training)
+    return _pool.dropout(x, p, training)
 
 
 class Flatten(nn.Flatten):
@@ -369,10 +372,16 @@ class MaxPool2d(nn.MaxPool2d):
     def __init__(self, kernel_size: IntOrPair, stride: Optional[IntOrPair] = None, padding: IntOrPair = 0):
         super().__init__(kernel_size, stride, padding)
 
+    def forward(self, x):
+        return _pool.max_pool2d(x, self.kernel_size, self.stride, self.padding)   # channels-last kernel on CUDA
+
 
 class AvgPool2d(nn.AvgPool2d):
     def __init__(self, kernel_size: IntOrPair, stride: Optional[IntOrPair] = None, padding: IntOrPair = 0):
         super().__init__(kernel_size, stride, padding)
+
+    def forward(self, x):
+        return _pool.avg_pool2d(x, self.kernel_size, self.stride, self.padding)
 
 
 class AdaptiveAvgPool2d(nn.AdaptiveAvgPool2d):
@@ -382,11 +391,17 @@ class AdaptiveAvgPool2d(nn.AdaptiveAvgPool2d):
     def global_pool(cls) -> "AdaptiveAvgPool2d":
         return cls((1, 1))
 
+    def forward(self, x):
+        return _pool.adaptive_avg_pool2d(x, self.output_size)
+
 
 class AdaptiveMaxPool2d(nn.AdaptiveMaxPool2d):
     @classmethod
     def global_pool(cls) -> "AdaptiveMaxPool2d":
         return cls((1, 1))
+
+    def forward(self, x):
+        return _pool.adaptive_max_pool2d(x, self.output_size)
 
 
 # -------------------------------------------------------------------- activations

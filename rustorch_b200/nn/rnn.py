@@ -13,6 +13,9 @@ from typing import Optional, Tuple
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import rnn as _rnn_ops
 
 
 class RNNCell(nn.RNNCell):
@@ -24,11 +27,23 @@ class LSTMCell(nn.LSTMCell):
     """``forward(x, (h, c) | None) -> (h, c)``; weights stacked ``[i, f, g, o]``."""
 
     def forward(self, x: torch.Tensor, state: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
-        return super().forward(x, state)
+        if x.dim() != 2:
+            return super().forward(x, state)
+        if state is None:
+            z = torch.zeros(x.shape[0], self.hidden_size, dtype=x.dtype, device=x.device)
+            state = (z, z)
+        h, c = state
+        gates = F.linear(x, self.weight_ih, self.bias_ih) + F.linear(h, self.weight_hh, self.bias_hh)
+        return _rnn_ops.lstm_gates(gates, c)          # one fused kernel on CUDA
 
 
 class GRUCell(nn.GRUCell):
-    pass
+    def forward(self, x: torch.Tensor, h: Optional[torch.Tensor] = None):
+        if x.dim() != 2:
+            return super().forward(x, h)
+        if h is None:
+            h = torch.zeros(x.shape[0], self.hidden_size, dtype=x.dtype, device=x.device)
+        return _rnn_ops.gru_gates(F.linear(x, self.weight_ih, self.bias_ih), F.linear(h, self.weight_hh, self.bias_hh), h)
 
 
 class _Recurrent:

@@ -116,11 +116,29 @@ class SparseTensor:
     def spmv(self, v: torch.Tensor) -> torch.Tensor:
         if len(self.shape) != 2 or v.dim() != 1 or v.shape[0] != self.shape[1]:
             raise ValueError("spmv: matrix [m, n] times vector [n]")
+        if self._native(v):
+            return self._native_spmm(v.unsqueeze(1)).squeeze(1)
         return (self.to_torch() @ v.unsqueeze(1)).squeeze(1)
+
+    def _native(self, dense: torch.Tensor) -> bool:
+        from .. import _native
+        return (dense.is_cuda and self.values.is_cuda and self.values.dtype == torch.float32 and dense.dtype == torch.float32
+                and not dense.requires_grad and _native.available())
+
+    def _native_spmm(self, dense: torch.Tensor) -> torch.Tensor:
+        """CSR x dense on the warp-per-row kernel (csrc/nn/rnn_amp_sparse.cu)."""
+        from .. import _native
+        c = self if self.format is SparseFormat.CSR else self.to_csr()
+        y = torch.empty((self.shape[0], dense.shape[1]), dtype=torch.float32, device=dense.device)
+        _native.load(required=True).csr_spmm(c.crow.to(torch.int64).contiguous(), c.col.to(torch.int64).contiguous(),
+                                             c.values.contiguous(), dense.contiguous(), y)
+        return y
 
     def spmm(self, dense: torch.Tensor) -> torch.Tensor:
         if len(self.shape) != 2 or dense.shape[0] != self.shape[1]:
             raise ValueError("spmm: matrix [m, n] times dense [n, k]")
+        if dense.dim() == 2 and self._native(dense):
+            return self._native_spmm(dense)
         return self.to_torch() @ dense
 
     def add(self, other: "SparseTensor") -> "SparseTensor":
