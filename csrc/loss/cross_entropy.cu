@@ -31,16 +31,27 @@ __global__ void cross_entropy_kernel(__nv_bfloat16* __restrict__ logits,
     if (tid == 0) atomicCAS(status, 0, RT_ERR_BOUNDS);
     tgt = 0;
   }
-  // pass 1: max (and stage)
+  // Vectors [0, nfull) lie entirely inside the vocabulary, vector nfull (if vocab % 8) is cut by it, the rest is
+  // padding.  Only the cut vector pays for per-element bounds tests.
+  const int nfull = vocab >> 3, ncut = (vocab + 7) >> 3;
+  const float LOG2E = 1.4426950408889634f;
+  // pass 1: max (and stage).  Packed bf16 maxima: 4 instructions per 8 logits.
+  __nv_bfloat162 m2 = __float2bfloat162_rn(-INFINITY);
   float mx = -INFINITY;
-  for (int v = tid; v < nvec; v += nt) {
+  for (int v = tid; v < ncut; v += nt) {
     uint4 w = reinterpret_cast<const uint4*>(row)[v];
     if (STAGED) reinterpret_cast<uint4*>(srow)[v] = w;
-    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&w);
+    if (v < nfull) {
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+      m2 = __hmax2(m2, __hmax2(__hmax2(h2[0], h2[1]), __hmax2(h2[2], h2[3])));
+    } else {
+      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&w);
 #pragma unroll
-    for (int e = 0; e < 8; ++e)
-      if (v * 8 + e < vocab) mx = fmaxf(mx, __bfloat162float(h[e]));
+      for (int e = 0; e < 8; ++e)
+        if (v * 8 + e < vocab) mx = fmaxf(mx, __bfloat162float(h[e]));
+    }
   }
+  mx = fmaxf(mx, fmaxf(__bfloat162float(m2.x), __bfloat162float(m2.y)));
 #pragma unroll
   for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
   if (lane == 0) red[warp] = mx;
@@ -54,14 +65,24 @@ __global__ void cross_entropy_kernel(__nv_bfloat16* __restrict__ logits,
   __syncthreads();
   mx = red[32];
   __syncthreads();
+  const float mxs = -mx * LOG2E;        // exp(x - mx) = ex2(x * log2e + mxs): one fma + one ex2 per logit
   // pass 2: sum exp
   float sum = 0.f;
-  for (int v = tid; v < nvec; v += nt) {
+  for (int v = tid; v < ncut; v += nt) {
     uint4 w = reinterpret_cast<const uint4*>(srow)[v];
-    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&w);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+    if (v < nfull) {
 #pragma unroll
-    for (int e = 0; e < 8; ++e)
-      if (v * 8 + e < vocab) sum += __expf(__bfloat162float(h[e]) - mx);
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        sum += ex2_approx(fmaf(f.x, LOG2E, mxs)) + ex2_approx(fmaf(f.y, LOG2E, mxs));
+      }
+    } else {
+      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&w);
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (v * 8 + e < vocab) sum += ex2_approx(fmaf(__bfloat162float(h[e]), LOG2E, mxs));
+    }
   }
 #pragma unroll
   for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
@@ -75,30 +96,39 @@ __global__ void cross_entropy_kernel(__nv_bfloat16* __restrict__ logits,
   }
   __syncthreads();
   sum = red[32];
-  const float inv = 1.f / sum;
-  if (tid == 0) {
-    const float xt = __bfloat162float(srow[tgt]);
-    loss[r] = ignored ? 0.f : (logf(sum) + mx - xt);
-  }
+  const float xt = __bfloat162float(srow[tgt]);
+  if (tid == 0) loss[r] = ignored ? 0.f : (logf(sum) + mx - xt);
   __syncthreads();  // srow[tgt] read before it is overwritten (non-staged mode aliases the row)
   const float gs = ignored ? 0.f : grad_scale;
-  // pass 3: gradient in place
+  const float gi = gs / sum;
+  // pass 3: gradient in place; the "- onehot" term is patched in afterwards by one thread
   for (int v = tid; v < nvec; v += nt) {
-    uint4 w = reinterpret_cast<const uint4*>(srow)[v];
-    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&w);
-    float g[8];
+    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+    if (v < ncut) {
+      uint4 w = reinterpret_cast<const uint4*>(srow)[v];
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+      float g[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int c = v * 8 + e;
-      float pr = (c < vocab) ? __expf(__bfloat162float(h[e]) - mx) * inv : 0.f;
-      if (c == tgt) pr -= 1.f;
-      g[e] = pr * gs;
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        g[2 * e] = ex2_approx(fmaf(f.x, LOG2E, mxs)) * gi;
+        g[2 * e + 1] = ex2_approx(fmaf(f.y, LOG2E, mxs)) * gi;
+      }
+      if (v >= nfull) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (v * 8 + e >= vocab) g[e] = 0.f;
+      }
+      if (v == (int)(tgt >> 3)) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (e == (int)(tgt & 7)) g[e] -= gs;
+      }
+      o.x = pack_bf16x2(g[0], g[1]);
+      o.y = pack_bf16x2(g[2], g[3]);
+      o.z = pack_bf16x2(g[4], g[5]);
+      o.w = pack_bf16x2(g[6], g[7]);
     }
-    uint4 o;
-    o.x = pack_bf16x2(g[0], g[1]);
-    o.y = pack_bf16x2(g[2], g[3]);
-    o.z = pack_bf16x2(g[4], g[5]);
-    o.w = pack_bf16x2(g[6], g[7]);
     reinterpret_cast<uint4*>(row)[v] = o;
   }
 }

@@ -5,8 +5,9 @@
 // The weights stay quantised in HBM and are read exactly once per call, whatever M is: a CTA owns 128 weight rows
 // (the M side of the MMA) and a slice of K; the activations are the N side (M padded to 16 / 32 / 64 / 128 / 256).
 //
-//   warp 0       producer: TMA tiles of raw nibbles / bytes (128 rows x 128 B, 128-byte swizzle so that the row-per-
-//                thread reads below are bank-conflict free) and SW128 K-major tiles of x (64 k x M_pad rows)
+//   warp 0       producer of raw nibbles / bytes: TMA tiles of 128 rows x 128 B, 128-byte swizzle so that the row-per-
+//                thread reads below are bank-conflict free
+//   warp 10      producer of the SW128 K-major tiles of x (64 k x M_pad rows)
 //   warp 1       tcgen05.mma issuer, accumulator D[128 weight rows][M_pad] fp32 in TMEM
 //   warps 2..9   dequantise: thread (row r, half hb) expands one 32-weight block per 64-k step to fp16 * scale and
 //                stores it as four 16-byte chunks of row r of the A tile in the canonical SW128 K-major layout
@@ -35,12 +36,14 @@ namespace rt {
 
 namespace {
 
-constexpr int QT_THREADS = 320;
+constexpr int QT_THREADS = 352;   // warp 0 raw producer, 1 MMA, 2..9 dequantise + epilogue, 10 activation producer
+constexpr int QT_X_WARP = 10;
 constexpr int QT_DQ_WARPS = 8;
-constexpr int QT_RAW_STAGES = 3;
+constexpr int QT_RAW_STAGES = 3;   // most; small activation tiles use 2 so that two CTAs share an SM
 constexpr int QT_MAX_SLOTS = 6;
 constexpr int QT_RAW_BYTES = 128 * 128;   // 128 rows x 128 B
-constexpr int QT_A_BYTES = 128 * 128;     // 128 rows x 64 halves
+constexpr int QT_ATOM_BYTES = 128 * 128;  // one SW128 atom: 128 rows x 64 halves
+constexpr int QT_A_BYTES = 2 * QT_ATOM_BYTES;   // an operand slot holds two atoms (128 k): one handshake per 128 k
 
 struct QtParams {
   const __half* scales;
@@ -50,7 +53,7 @@ struct QtParams {
   float* partial;        // [tiles][splits][m_pad][128]
   int* counters;         // [tiles], zero between calls
   long long ldy, ldr;
-  int M, N, K, m_pad, op_slots, chunks_per_split, total_chunks;
+  int M, N, K, m_pad, op_slots, raw_stages, chunks_per_split, total_chunks;
   int* status;
 };
 
@@ -62,6 +65,19 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
       : "memory");
 }
 
+// Position in a ring of n slots and the parity of the current pass over it.
+struct Ring {
+  int i, n;
+  uint32_t ph;
+  __device__ __forceinline__ Ring(int n_) : i(0), n(n_), ph(0) {}
+  __device__ __forceinline__ void next() {
+    if (++i == n) {
+      i = 0;
+      ph ^= 1;
+    }
+  }
+};
+
 __device__ __forceinline__ uint4 pack8(const __half2 (&w)[16], int i) {
   uint4 v;
   v.x = *reinterpret_cast<const uint32_t*>(&w[i]);
@@ -72,16 +88,25 @@ __device__ __forceinline__ uint4 pack8(const __half2 (&w)[16], int i) {
 }
 
 template <bool Q8>
-__global__ void __launch_bounds__(QT_THREADS, 1) q_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_raw,
+__global__ void __launch_bounds__(QT_THREADS, 2) q_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_raw,
                                                                   const __grid_constant__ CUtensorMap tm_x, const QtParams p) {
   constexpr int KRAW = Q8 ? 128 : 256;   // k covered by one raw stage (128 B per row)
-  constexpr int SUBS = KRAW / 64;        // 64-k MMA steps per raw stage
-  extern __shared__ uint8_t qt_smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(qt_smem_raw) + 1023) & ~uintptr_t(1023));
-  const int OS = p.op_slots, MP = p.m_pad;
-  const int x_bytes = MP * 128;
+  constexpr int SUBS = KRAW / 64;        // 64-k atoms per raw stage
+  constexpr int STEPS = KRAW / 128;      // 128-k operand slots per raw stage
+  // The swizzled tiles need a 1024-byte aligned base.  Dynamic shared memory starts right after the 1 KB the driver
+  // keeps per block, so it is aligned; the launch reserves no slack (two CTAs must fit one SM), and a base that is
+  // not aligned ends the kernel with an error code before anything is touched.
+  extern __shared__ __align__(1024) uint8_t qt_smem_raw[];
+  uint8_t* smem = qt_smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, RT_ERR_BOUNDS);
+    return;
+  }
+  const int OS = p.op_slots, MP = p.m_pad, RS = p.raw_stages;
+  const int x_atom = MP * 128;            // one 64-k activation box
+  const int x_bytes = 2 * x_atom;
   uint8_t* raw = smem;
-  uint8_t* a_t = raw + QT_RAW_STAGES * QT_RAW_BYTES;
+  uint8_t* a_t = raw + RS * QT_RAW_BYTES;
   uint8_t* x_t = a_t + OS * QT_A_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(x_t + OS * x_bytes);
   uint64_t* raw_full = bars;
@@ -127,51 +152,38 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q_gemm_tc_kernel(const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  auto subs_of = [&](int c) { return min(SUBS, (p.K - c * KRAW + 63) >> 6); };
+  auto steps_of = [&](int c) { return min(STEPS, (p.K - c * KRAW + 127) >> 7); };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
-    // Two independent cursors served by one thread without blocking on either: raw weight tiles run up to
-    // QT_RAW_STAGES chunks ahead of the dequantisers, activation tiles up to op_slots steps ahead of the MMAs.
+    // Raw weight tiles: up to raw_stages chunks ahead of the dequantisers (blocking waits: the thread sleeps in hardware).
     if (lane == 0) {
-      int rc = c_begin;                 // next raw chunk to load
-      uint32_t rci = 0;
-      int xc = c_begin, xsub = 0;       // next activation step to load
-      uint32_t xit = 0;
-      uint32_t idle = 0;
-      unsigned long long t0 = 0;
-      while (rc < c_end || xc < c_end) {
-        bool progress = false;
-        if (rc < c_end) {
-          const int s = rci % QT_RAW_STAGES;
-          if (mbar_test_wait(&raw_empty[s], ((rci / QT_RAW_STAGES) & 1) ^ 1)) {
-            mbar_arrive_expect_tx(&raw_full[s], QT_RAW_BYTES);
-            tma_load_2d(raw + s * QT_RAW_BYTES, &tm_raw, &raw_full[s], rc * 32, n0);
-            ++rc; ++rci;
-            progress = true;
-          }
-        }
-        if (xc < c_end) {
-          const int j = xit % OS;
-          if (mbar_test_wait(&op_empty[j], ((xit / OS) & 1) ^ 1)) {
-            mbar_arrive_expect_tx(&x_full[j], x_bytes);
-            tma_load_3d(x_t + j * x_bytes, &tm_x, &x_full[j], xc * KRAW + xsub * 64, 0, 0);
-            ++xit;
-            if (++xsub == subs_of(xc)) { xsub = 0; ++xc; }
-            progress = true;
-          }
-        }
-        if (progress) {
-          idle = 0;
-          t0 = 0;
-        } else if ((++idle & 0xff) == 0) {
-          if (ctl->abort) break;
-          if (t0 == 0) t0 = globaltimer_ns();
-          if (globaltimer_ns() - t0 > RT_WAIT_TIMEOUT_NS) {
-            ctl->abort = 1;
-            atomicCAS(p.status, 0, RT_ERR_TIMEOUT_PRODUCER);
+      Ring rr(RS);
+      for (int c = c_begin; c < c_end; ++c) {
+        if (!mbar_wait(&raw_empty[rr.i], rr.ph ^ 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) break;
+        mbar_arrive_expect_tx(&raw_full[rr.i], QT_RAW_BYTES);
+        tma_load_2d(raw + rr.i * QT_RAW_BYTES, &tm_raw, &raw_full[rr.i], c * 32, n0);
+        rr.next();
+      }
+    }
+  } else if (warp == QT_X_WARP) {
+    // Activation tiles: up to op_slots steps ahead of the MMAs.  A warp of its own, so that neither producer holds
+    // up the other and neither has to poll.
+    if (lane == 0) {
+      Ring xr(OS);
+      bool ok = true;
+      for (int c = c_begin; c < c_end && ok; ++c) {
+        const int ns = steps_of(c);
+        for (int st = 0; st < ns; ++st) {
+          if (!mbar_wait(&op_empty[xr.i], xr.ph ^ 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) {
+            ok = false;
             break;
           }
+          mbar_arrive_expect_tx(&x_full[xr.i], x_bytes);
+          const int k0 = c * KRAW + st * 128;      // the second box may lie past K: it reads as zeros
+          tma_load_3d(x_t + xr.i * x_bytes, &tm_x, &x_full[xr.i], k0, 0, 0);
+          tma_load_3d(x_t + xr.i * x_bytes + x_atom, &tm_x, &x_full[xr.i], k0 + 64, 0, 0);
+          xr.next();
         }
       }
     }
@@ -179,25 +191,28 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q_gemm_tc_kernel(const __grid_c
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc = make_idesc_f16(128, MP, false, false, false);
-      uint32_t it = 0;
-      bool ok = true;
+      Ring r(OS);
+      bool first = true, ok = true;
       for (int c = c_begin; c < c_end && ok; ++c) {
-        const int ns = subs_of(c);
-        for (int sub = 0; sub < ns; ++sub, ++it) {
-          const int j = it % OS;
-          const uint32_t ph = (it / OS) & 1;
-          if (!mbar_wait(&x_full[j], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA) ||
-              !mbar_wait(&a_full[j], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA)) {
+        const int ns = steps_of(c);
+        for (int st = 0; st < ns; ++st) {
+          const int j = r.i;
+          if (!mbar_wait(&x_full[j], r.ph, ctl, p.status, RT_ERR_TIMEOUT_MMA) ||
+              !mbar_wait(&a_full[j], r.ph, ctl, p.status, RT_ERR_TIMEOUT_MMA)) {
             ok = false;
             break;
           }
           tc_fence_after();
           const uint32_t sa = smem_u32(a_t + j * QT_A_BYTES), sb = smem_u32(x_t + j * x_bytes);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_f16_ss(tmem_base, make_smem_desc_sw128(sa + kk * 32, 16, 1024), make_smem_desc_sw128(sb + kk * 32, 16, 1024),
-                        idesc, (it > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t oa = (kk >> 2) * QT_ATOM_BYTES + (kk & 3) * 32, ob = (kk >> 2) * x_atom + (kk & 3) * 32;
+            umma_f16_ss(tmem_base, make_smem_desc_sw128(sa + oa, 16, 1024), make_smem_desc_sw128(sb + ob, 16, 1024), idesc,
+                        (!first || kk > 0) ? 1u : 0u);
+          }
+          first = false;
           umma_commit(&op_empty[j]);
+          r.next();
         }
       }
       if (ok) umma_commit(acc_full);
@@ -233,47 +248,53 @@ __global__ void __launch_bounds__(QT_THREADS, 1) q_gemm_tc_kernel(const __grid_c
     };
     __half dcur[SUBS], dnxt[SUBS];
     load_scales(c_begin, dcur);
-    uint32_t it = 0, ci = 0;
+    Ring rr(RS), orr(OS);
     bool ok = true;
-    for (int c = c_begin; c < c_end && ok; ++c, ++ci) {
-      const int s = ci % QT_RAW_STAGES;
+    for (int c = c_begin; c < c_end && ok; ++c) {
+      const int s = rr.i;
       load_scales(c + 1, dnxt);
-      if (!mbar_wait(&raw_full[s], (ci / QT_RAW_STAGES) & 1, ctl, p.status, RT_ERR_TIMEOUT_EPILOGUE)) break;
+      if (!mbar_wait(&raw_full[s], rr.ph, ctl, p.status, RT_ERR_TIMEOUT_EPILOGUE)) break;
       const uint8_t* rrow = raw + s * QT_RAW_BYTES + r * 128;
-      const int ns = subs_of(c);
+      const int ns = steps_of(c);
 #pragma unroll
-      for (int sub = 0; sub < SUBS; ++sub) {
-        if (sub >= ns) break;
-        const int j = it % OS;
-        __half2 w[16];
-        if (Q8) {
-          const int cj = (sub * 2 + hb) * 2;
-          const uint4 q0 = *reinterpret_cast<const uint4*>(rrow + ((cj ^ (r & 7)) << 4));
-          const uint4 q1 = *reinterpret_cast<const uint4*>(rrow + (((cj + 1) ^ (r & 7)) << 4));
-          expand_q8(q0, q1, w);
-        } else {
-          const int cj = sub * 2 + hb;
-          const uint4 q = *reinterpret_cast<const uint4*>(rrow + ((cj ^ (r & 7)) << 4));
-          expand_q4(q, w);
-        }
-        const __half2 d2 = __half2half2(dcur[sub]);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) w[i] = __hmul2(w[i], d2);
-        if (!mbar_wait(&op_empty[j], ((it / OS) & 1) ^ 1, ctl, p.status, RT_ERR_TIMEOUT_EPILOGUE)) {
-          ok = false;
-          break;
-        }
+      for (int st = 0; st < STEPS; ++st) {
+        if (st >= ns) break;
+        const int j = orr.i;
         uint8_t* arow = a_t + j * QT_A_BYTES + r * 128;
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-          *reinterpret_cast<uint4*>(arow + (((hb * 4 + e) ^ (r & 7)) << 4)) = pack8(w, e * 4);
+        for (int half_step = 0; half_step < 2; ++half_step) {
+          const int sub = st * 2 + half_step;
+          __half2 w[16];
+          if (Q8) {
+            const int cj = (sub * 2 + hb) * 2;
+            const uint4 q0 = *reinterpret_cast<const uint4*>(rrow + ((cj ^ (r & 7)) << 4));
+            const uint4 q1 = *reinterpret_cast<const uint4*>(rrow + (((cj + 1) ^ (r & 7)) << 4));
+            expand_q8(q0, q1, w);
+          } else {
+            const int cj = sub * 2 + hb;
+            const uint4 q = *reinterpret_cast<const uint4*>(rrow + ((cj ^ (r & 7)) << 4));
+            expand_q4(q, w);
+          }
+          const __half2 d2 = __half2half2(dcur[sub]);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) w[i] = __hmul2(w[i], d2);
+          if (half_step == 0 && !mbar_wait(&op_empty[j], orr.ph ^ 1, ctl, p.status, RT_ERR_TIMEOUT_EPILOGUE)) {
+            ok = false;
+            break;
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            *reinterpret_cast<uint4*>(arow + half_step * QT_ATOM_BYTES + (((hb * 4 + e) ^ (r & 7)) << 4)) = pack8(w, e * 4);
+        }
+        if (!ok) break;
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&a_full[j]);
-        ++it;
+        orr.next();
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&raw_empty[s]);
+      rr.next();
 #pragma unroll
       for (int sub = 0; sub < SUBS; ++sub) dcur[sub] = dnxt[sub];
     }
@@ -363,8 +384,9 @@ void q_gemm_tc_scratch(int M, int N, int K, bool q8, int sms, long long* partial
   // CTAs run one per SM: cost = waves x (chunks per CTA + fixed part); pick the cheapest split count.
   int splits = 1;
   double best = 1e30;
+  const int slots = sms * (pad_m(M) <= 32 ? 2 : 1);      // up to 32 rows two CTAs share an SM
   for (int s = 1; s <= std::min(16, std::max(1, total / 2)); ++s) {
-    const int per_s = (total + s - 1) / s, waves = (tiles * s + sms - 1) / sms;
+    const int per_s = (total + s - 1) / s, waves = (tiles * s + slots - 1) / slots;
     const double cost = waves * (per_s + 1.5);
     if (cost < best - 1e-9) best = cost, splits = s;
   }
@@ -388,7 +410,9 @@ void q_gemm_tc(const QGemvArgs& a, void* partial, int* counters, cudaStream_t st
   p.ldy = a.ldy; p.ldr = a.ldr;
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.m_pad = pad_m(a.M);
-  p.op_slots = p.m_pad == 256 ? 3 : p.m_pad == 128 ? 4 : QT_MAX_SLOTS;
+  p.op_slots = 2;                                       // 128 k each
+  // <= 32 rows: two CTAs per SM (113 KB each); 256 rows: the activation slots take 128 KB
+  p.raw_stages = (p.m_pad <= 32 || p.m_pad == 256) ? 2 : QT_RAW_STAGES;
   long long pf; int nc, splits;
   q_gemm_tc_scratch(a.M, a.N, a.K, a.q8, sm_count(device), &pf, &nc, &splits);
   p.total_chunks = (a.K + kraw - 1) / kraw;
@@ -400,7 +424,8 @@ void q_gemm_tc(const QGemvArgs& a, void* partial, int* counters, cudaStream_t st
   const uint64_t row_bytes = (uint64_t)(a.K / 32) * (a.q8 ? 32 : 16);
   const CUtensorMap tr = make_tmap_words_sw128(a.qs, row_bytes, a.N, 128);
   const CUtensorMap tx = make_tmap_2byte(a.x, a.K, a.M, 1, a.ldx, 0, 64, p.m_pad);
-  const int smem = 1024 + QT_RAW_STAGES * QT_RAW_BYTES + p.op_slots * (QT_A_BYTES + p.m_pad * 128) + 512;
+  const int smem = p.raw_stages * QT_RAW_BYTES + p.op_slots * (QT_A_BYTES + 2 * p.m_pad * 128) + 512;
+  RT_CHECK(smem <= 227 * 1024, "q_gemm_tc: shared-memory budget exceeded");
   const dim3 grid((a.N + 127) / 128, splits);
   if (a.q8) {
     static bool cfg[64] = {false};

@@ -66,8 +66,9 @@ class QuantLinear:
     # weight) costs less than re-streaming the quantised matrix once per 8 rows through the GEMV kernel.
     GEMM_MIN_ROWS = 64
     # Between these row counts the dequant-fused tcgen05 GEMM reads the quantised weights once for all rows
-    # (the GEMV kernel re-reads them for every 8 rows; the two-pass path moves 4.5 B per weight).
-    TC_MIN_ROWS, TC_MAX_ROWS = 9, 256
+    # (the GEMV kernel's per-row arithmetic makes it slower from 5 rows on, and it re-reads the weights for every
+    # 8 rows; the two-pass path moves 4.5 B per weight).
+    TC_MIN_ROWS, TC_MAX_ROWS = 5, 256
     _scratch_buf = {}
     _tc_scratch = {}
 

@@ -17,7 +17,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..nn.layers import BatchNorm2d, Conv2d
+from ..nn.layers import AdaptiveAvgPool2d, BatchNorm2d, Conv2d, Dropout, MaxPool2d
 
 
 class BasicBlock(nn.Module):
@@ -68,12 +68,12 @@ class ResNet(nn.Module):
         self.in_ch = 64
         self.conv1 = Conv2d(in_channels, 64, 7, 2, 3, bias=False)
         self.bn1 = BatchNorm2d(64)
-        self.maxpool = nn.MaxPool2d(3, 2, 1)
+        self.maxpool = MaxPool2d(3, 2, 1)
         self.layer1 = self._make(block, 64, layers[0], 1)
         self.layer2 = self._make(block, 128, layers[1], 2)
         self.layer3 = self._make(block, 256, layers[2], 2)
         self.layer4 = self._make(block, 512, layers[3], 2)
-        self.avgpool = nn.AdaptiveAvgPool2d((1, 1))
+        self.avgpool = AdaptiveAvgPool2d((1, 1))
         self.fc = nn.Linear(512 * block.expansion, num_classes)
         for m in self.modules():
             if isinstance(m, Conv2d):
@@ -119,7 +119,7 @@ class CNN(nn.Module):
             layers.append(nn.Conv2d(c, oc, kernel_size, padding=kernel_size // 2))
             if batch_norm:
                 layers.append(nn.BatchNorm2d(oc))
-            layers += [nn.ReLU(), nn.MaxPool2d(2)]
+            layers += [nn.ReLU(), MaxPool2d(2)]
             c, h, w = oc, h // 2, w // 2
         self.features = nn.Sequential(*layers)
         fcs: List[nn.Module] = []
@@ -127,7 +127,7 @@ class CNN(nn.Module):
         for s in fc_sizes:
             fcs += [nn.Linear(d, s), nn.ReLU()]
             if dropout:
-                fcs.append(nn.Dropout(dropout))
+                fcs.append(Dropout(dropout))
             d = s
         fcs.append(nn.Linear(d, num_classes))
         self.classifier = nn.Sequential(*fcs)

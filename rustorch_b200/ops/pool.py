@@ -117,11 +117,22 @@ def _next_offset(device: torch.device, numel: int) -> Tuple[int, int]:
     return seed, off
 
 
+def _dense(x: torch.Tensor) -> bool:
+    """Memory is one gap-free block (any dimension order that PyTorch names a memory format)."""
+    if x.is_contiguous():
+        return True
+    if x.dim() == 4:
+        return x.is_contiguous(memory_format=torch.channels_last)
+    if x.dim() == 5:
+        return x.is_contiguous(memory_format=torch.channels_last_3d)
+    return False
+
+
 class _Dropout(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, p, seed, offset):
         C = _native.load(required=True)
-        xc = x if x.is_non_overlapping_and_dense() else x.contiguous()   # the mask is indexed by memory offset
+        xc = x if _dense(x) else x.contiguous()   # the mask is indexed by memory offset
         y = torch.empty_like(xc)
         C.dropout(xc, y, p, seed, offset)
         ctx.args = (p, seed, offset, y.stride())

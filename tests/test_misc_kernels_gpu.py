@@ -15,13 +15,14 @@ def test_max_and_avg_pool_forward_backward(dtype, k, s, p):
     from rustorch_b200.ops import pool
     x = torch.randn(3, 16, 13, 14, device="cuda").to(dtype).contiguous(memory_format=torch.channels_last)
     for ours, ref in ((pool.max_pool2d, F.max_pool2d), (pool.avg_pool2d, F.avg_pool2d)):
-        xa, xb = x.clone().requires_grad_(True), x.float().clone().requires_grad_(True)
+        # fp32 reference on the CPU, on a plain NCHW tensor
+        xa, xb = x.clone().requires_grad_(True), x.float().cpu().contiguous().clone().requires_grad_(True)
         ya, yb = ours(xa, k, s, p), ref(xb, k, s, p)
-        assert ya.shape == yb.shape and rel_err(ya, yb) < (1e-6 if dtype == torch.float32 else 8e-3)
+        assert ya.shape == yb.shape and rel_err(ya.cpu(), yb) < (1e-6 if dtype == torch.float32 else 8e-3)
         g = torch.randn_like(yb)
-        ya.backward(g.to(dtype))
+        ya.backward(g.to(dtype).cuda())
         yb.backward(g)
-        assert rel_err(xa.grad, xb.grad) < (1e-6 if dtype == torch.float32 else 1e-2)
+        assert rel_err(xa.grad.cpu(), xb.grad) < (1e-6 if dtype == torch.float32 else 1e-2)
     _native.check_status()
 
 
