@@ -207,7 +207,11 @@ def bench_qgemm(a):
 
             def run_tc():
                 for q in mats:
-                    C.q_gemm_tc(q.qs, q.scales, x, y, None, None, False, part, cnt)
+                    C.q_gemm_tc(q.qs, q.scales, x, y, None, None, False, part, cnt, 0)
+
+            def run_tc_smem():
+                for q in mats:
+                    C.q_gemm_tc(q.qs, q.scales, x, y, None, None, False, part, cnt, 1)
 
             def run_gemv():
                 for q in mats:
@@ -216,7 +220,10 @@ def bench_qgemm(a):
             best, med = time_op(run_tc, a.iters, flush=False)
             report(f"q4_gemm_tc_m{M}_{N}x{Kd}", best / copies, med / copies, bytes_=float(nbytes), flops=2.0 * M * N * Kd,
                    extra=f"mean over {copies} distinct matrices per timed region")
-            if M <= 32:
+            best, med = time_op(run_tc_smem, a.iters, flush=False)
+            report(f"q4_gemm_tc_smemA_m{M}_{N}x{Kd}", best / copies, med / copies, bytes_=float(nbytes), flops=2.0 * M * N * Kd,
+                   extra="operand A staged in shared memory")
+            if M <= 16:
                 best, med = time_op(run_gemv, a.iters, flush=False)
                 report(f"q4_gemv_x{M // 8}_m{M}_{N}x{Kd}", best / copies, med / copies, bytes_=float(nbytes), extra="GEMV kernel, 8 rows per pass")
         del mats

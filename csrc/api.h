@@ -48,6 +48,7 @@ struct AttnArgs {
   int B, H, Hkv, Tq, Tk, D;
   int causal;
   float scale;
+  int io_fp16 = 0;  // forward only: q / k / v / o are fp16 instead of bf16
   // backward only
   const void* d_o;  // same strides as o
   float* delta;     // [B][H][Tq] scratch: rowsum(o * do)
@@ -320,6 +321,8 @@ void q_gemv_bulk(const QGemvArgs& a, cudaStream_t stream);
 bool q_gemm_tc_supported(int M, int N, int K);
 void q_gemm_tc_scratch(int M, int N, int K, bool q8, int sms, long long* partial_floats, int* counters, int* splits_out);
 void q_gemm_tc(const QGemvArgs& a, void* partial, int* counters, cudaStream_t stream);
+// quant/q_gemm_ts.cu: same product with the expanded weights held in tensor memory (tcgen05.st + A-from-TMEM MMA).
+void q_gemm_ts(const QGemvArgs& a, void* partial, int* counters, cudaStream_t stream);
 void dequant_f16(const void* qs, const void* scales, void* out, long long n_blocks, bool q8, cudaStream_t s);
 void repack_q4_0(const void* blocks, void* qs, void* scales, long long n_blocks, cudaStream_t s);
 void repack_q8_0(const void* blocks, void* qs, void* scales, long long n_blocks, cudaStream_t s);

@@ -18,8 +18,9 @@ constexpr int ATT_BM = 128;  // query rows per tile
 constexpr int ATT_BN = 128;  // key rows per tile
 constexpr int ATT_HALF_BYTES = 128 * 128;  // one 64-column half: 128 rows x 128 B
 
-// Store 32 consecutive columns [col0, col0+32) of row `row` (fp32 -> bf16) into the swizzled
-// [128][128] bf16 staging tile at `tile`.
+// Store 32 consecutive columns [col0, col0+32) of row `row` (fp32 -> bf16, or fp16 with F16) into the swizzled
+// [128][128] 16-bit staging tile at `tile`.
+template <bool F16 = false>
 __device__ __forceinline__ void stage_row_chunk_bf16(uint8_t* tile, int row, int col0,
                                                      const float (&v)[32]) {
   const int half = col0 >> 6;
@@ -28,10 +29,10 @@ __device__ __forceinline__ void stage_row_chunk_bf16(uint8_t* tile, int row, int
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
     uint4 w;
-    w.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-    w.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-    w.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-    w.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+    w.x = pack_2x16<F16>(v[q * 8 + 0], v[q * 8 + 1]);
+    w.y = pack_2x16<F16>(v[q * 8 + 2], v[q * 8 + 3]);
+    w.z = pack_2x16<F16>(v[q * 8 + 4], v[q * 8 + 5]);
+    w.w = pack_2x16<F16>(v[q * 8 + 6], v[q * 8 + 7]);
     const int c16 = (c16_0 + q) ^ (row & 7);
     *reinterpret_cast<uint4*>(rowp + c16 * 16) = w;
   }

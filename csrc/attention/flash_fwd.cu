@@ -25,7 +25,7 @@ struct AttnFwdParams {
   int B, H, Hkv, Tq, Tk;
   int causal;
   float scale_log2;  // softmax scale * log2(e)
-  __nv_bfloat16* o;
+  uint16_t* o;   // bf16, or fp16 in the F16 instantiation
   long long o_sb, o_st, o_sh;
   float* lse;  // [B][H][Tq]
   int* status;
@@ -45,7 +45,8 @@ struct AttnFwdSmem {
 
 constexpr float ATT_RESCALE_THRESHOLD = 8.f;  // log2 units
 
-template <int D>
+// F16: q / k / v / o are fp16 (the quantised LLM runtime's activations); P is then staged as fp16 too.
+template <int D, bool F16>
 __global__ void __launch_bounds__(160, (D == 64) ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_k,
@@ -114,8 +115,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
   if (warp == 4) {
     if (lane == 0 && n_kv > 0) {
-      constexpr uint32_t idesc_S = make_idesc_f16(128, 128, false, false, true);
-      constexpr uint32_t idesc_PV = make_idesc_f16(128, D, false, true, true);
+      constexpr uint32_t idesc_S = make_idesc_f16(128, 128, false, false, !F16);
+      constexpr uint32_t idesc_PV = make_idesc_f16(128, D, false, true, !F16);
       const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
       auto kbuf = [&](int s) { return smem + S::OFF_K + s * S::TILE; };
       auto vbuf = [&](int s) { return smem + S::OFF_V + s * S::TILE; };
@@ -256,7 +257,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         float pv[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) pv[i] = __uint_as_float(r[c * 32 + i]);
-        stage_row_chunk_bf16(sP, row, c * 32, pv);
+        stage_row_chunk_bf16<F16>(sP, row, c * 32, pv);
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -265,7 +266,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     if (ok && n_kv > 0) ok = mbar_wait(pv_done, (n_kv - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_EPILOGUE);
     tc_fence_after();
     const float inv = l > 0.f ? 1.f / l : 0.f;
-    __nv_bfloat16* orow = p.o + (long long)b * p.o_sb + (long long)qi * p.o_st + (long long)h * p.o_sh;
+    uint16_t* orow = p.o + (long long)b * p.o_sb + (long long)qi * p.o_st + (long long)h * p.o_sh;
 #pragma unroll 1
     for (int c = 0; c < D / 32; ++c) {
       uint32_t o[32];
@@ -281,10 +282,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint4 w;
-          w.x = pack_bf16x2(__uint_as_float(o[q * 8 + 0]) * inv, __uint_as_float(o[q * 8 + 1]) * inv);
-          w.y = pack_bf16x2(__uint_as_float(o[q * 8 + 2]) * inv, __uint_as_float(o[q * 8 + 3]) * inv);
-          w.z = pack_bf16x2(__uint_as_float(o[q * 8 + 4]) * inv, __uint_as_float(o[q * 8 + 5]) * inv);
-          w.w = pack_bf16x2(__uint_as_float(o[q * 8 + 6]) * inv, __uint_as_float(o[q * 8 + 7]) * inv);
+          w.x = pack_2x16<F16>(__uint_as_float(o[q * 8 + 0]) * inv, __uint_as_float(o[q * 8 + 1]) * inv);
+          w.y = pack_2x16<F16>(__uint_as_float(o[q * 8 + 2]) * inv, __uint_as_float(o[q * 8 + 3]) * inv);
+          w.z = pack_2x16<F16>(__uint_as_float(o[q * 8 + 4]) * inv, __uint_as_float(o[q * 8 + 5]) * inv);
+          w.w = pack_2x16<F16>(__uint_as_float(o[q * 8 + 6]) * inv, __uint_as_float(o[q * 8 + 7]) * inv);
           reinterpret_cast<uint4*>(orow + c * 32)[q] = w;
         }
       }
@@ -306,11 +307,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   }
 }
 
-template <int D>
+template <int D, bool F16>
 static void launch_fwd(const AttnArgs& a, cudaStream_t stream) {
   using S = AttnFwdSmem<D>;
   const int device = current_device();
-  auto kern = attn_fwd_kernel<D>;
+  auto kern = attn_fwd_kernel<D, F16>;
   static bool configured[64] = {false};
   if (!configured[device]) {
     RT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
@@ -327,7 +328,7 @@ static void launch_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.Tk = a.Tk;
   p.causal = a.causal;
   p.scale_log2 = a.scale * 1.4426950408889634f;
-  p.o = reinterpret_cast<__nv_bfloat16*>(a.o);
+  p.o = reinterpret_cast<uint16_t*>(a.o);
   p.o_sb = a.o_sb;
   p.o_st = a.o_st;
   p.o_sh = a.o_sh;
@@ -344,8 +345,14 @@ void attn_fwd(const AttnArgs& a, cudaStream_t stream) {
   RT_CHECK((a.o_st % 8) == 0 && (a.o_sh % 8) == 0 && (a.o_sb % 8) == 0,
            "attention: output strides must be multiples of 8 elements");
   if (a.B == 0 || a.Tq == 0) return;
-  if (a.D == 64) launch_fwd<64>(a, stream);
-  else launch_fwd<128>(a, stream);
+  if (a.io_fp16) {
+    if (a.D == 64) launch_fwd<64, true>(a, stream);
+    else launch_fwd<128, true>(a, stream);
+  } else if (a.D == 64) {
+    launch_fwd<64, false>(a, stream);
+  } else {
+    launch_fwd<128, false>(a, stream);
+  }
 }
 
 }  // namespace rt

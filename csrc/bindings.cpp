@@ -89,11 +89,17 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, Tensor& c, con
 }
 
 rt::AttnArgs make_attn_args(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
-                            const Tensor& lse, bool causal, double scale) {
-  check_bf16_cuda(q, "attention q");
-  check_bf16_cuda(k, "attention k");
-  check_bf16_cuda(v, "attention v");
-  check_bf16_cuda(o, "attention o");
+                            const Tensor& lse, bool causal, double scale, bool allow_f16 = false) {
+  const bool f16 = allow_f16 && q.scalar_type() == at::kHalf;
+  if (f16) {
+    TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda() && o.is_cuda() && k.scalar_type() == at::kHalf &&
+                    v.scalar_type() == at::kHalf && o.scalar_type() == at::kHalf, "attention: q, k, v, o must all be fp16 CUDA tensors");
+  } else {
+    check_bf16_cuda(q, "attention q");
+    check_bf16_cuda(k, "attention k");
+    check_bf16_cuda(v, "attention v");
+    check_bf16_cuda(o, "attention o");
+  }
   check_f32_cuda(lse, "attention lse");
   TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4 && o.dim() == 4,
               "attention: tensors must be [B, T, H, D]");
@@ -123,13 +129,14 @@ rt::AttnArgs make_attn_args(const Tensor& q, const Tensor& k, const Tensor& v, c
   a.lse = lse.data_ptr<float>();
   a.causal = causal ? 1 : 0;
   a.scale = float(scale);
+  a.io_fp16 = f16 ? 1 : 0;
   return a;
 }
 
 void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tensor& lse,
               bool causal, double scale) {
   c10::cuda::CUDAGuard guard(q.device());
-  rt::AttnArgs a = make_attn_args(q, k, v, o, lse, causal, scale);
+  rt::AttnArgs a = make_attn_args(q, k, v, o, lse, causal, scale, /*allow_f16=*/true);
   rt::attn_fwd(a, stream_of(q));
 }
 

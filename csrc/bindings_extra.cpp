@@ -125,7 +125,8 @@ std::vector<int64_t> q_gemm_tc_scratch(int64_t M, int64_t N, int64_t K, bool q8)
 
 // partial: fp32 scratch (>= q_gemm_tc_scratch()[0] words); counters: int32 zeros, one per 128 output columns.
 void q_gemm_tc(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, const c10::optional<Tensor>& bias,
-               const c10::optional<Tensor>& residual, bool q8, const c10::optional<Tensor>& partial, const c10::optional<Tensor>& counters) {
+               const c10::optional<Tensor>& residual, bool q8, const c10::optional<Tensor>& partial, const c10::optional<Tensor>& counters,
+               int64_t path) {
   c10::cuda::CUDAGuard guard(x.device());
   const rt::QGemvArgs a = make_qargs(qs, scales, x, y, bias, residual, q8, 0);
   long long pf; int nc, sp;
@@ -139,7 +140,9 @@ void q_gemm_tc(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& 
     pp = partial->data_ptr();
     cc = counters->data_ptr<int>();
   }
-  rt::q_gemm_tc(a, pp, cc, cur_stream(x.device().index()));
+  // path 0 / 2: operand A in tensor memory; 1: operand A staged in shared memory
+  if (path == 1) rt::q_gemm_tc(a, pp, cc, cur_stream(x.device().index()));
+  else rt::q_gemm_ts(a, pp, cc, cur_stream(x.device().index()));
 }
 
 // GGUF block stream (uint8 [n_blocks, 18 | 34]) -> (qs, scales) device layout.
@@ -751,7 +754,9 @@ void register_extra_ops(pybind11::module_& m) {
   m.def("q_gemv", &q_gemv, "dequant-fused Q4_0 / Q8_0 matrix-vector product", pybind11::arg("qs"), pybind11::arg("scales"),
         pybind11::arg("x"), pybind11::arg("y"), pybind11::arg("bias"), pybind11::arg("residual"), pybind11::arg("q8"),
         pybind11::arg("path") = 0);
-  m.def("q_gemm_tc", &q_gemm_tc, "dequant-fused Q4_0 / Q8_0 tcgen05 GEMM for up to 256 activation rows");
+  m.def("q_gemm_tc", &q_gemm_tc, "dequant-fused Q4_0 / Q8_0 tcgen05 GEMM for up to 256 activation rows", pybind11::arg("qs"),
+        pybind11::arg("scales"), pybind11::arg("x"), pybind11::arg("y"), pybind11::arg("bias"), pybind11::arg("residual"),
+        pybind11::arg("q8"), pybind11::arg("partial"), pybind11::arg("counters"), pybind11::arg("path") = 0);
   m.def("q_gemm_tc_scratch", &q_gemm_tc_scratch);
   m.def("repack_quant", &repack_quant);
   m.def("rmsnorm_f16", &rmsnorm_f16);

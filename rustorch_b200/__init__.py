@@ -39,13 +39,28 @@ _LAZY = {
     **{n: "python_api" for n in ("Device", "Config", "ModelSerializer", "ModelComparator", "Transform", "Transforms", "DistributedConfig",
                                  "init_distributed", "cleanup_distributed", "set_seed", "cuda_is_available", "get_system_info")},
     "Profiler": "profiler", "Plotter": "visualization", "ModelVisualizer": "visualization", "TensorStats": "visualization",
+    # errors, hybrid f32 universe, parallel traits, hardware hints, misc named pieces
+    **{n: "error" for n in ("RusTorchError", "RusTorchResult", "ShapeMismatch", "TensorOp", "GpuError", "DistributedError")},
+    **{n: "hybrid_f32" for n in ("F32Tensor", "F32Variable", "F32Trainer", "F32TrainerConfig", "F32Linear", "F32Conv2d", "F32LSTM")},
+    **{n: "parallel" for n in ("ParallelTensor", "ParallelConfig", "ParallelContext", "ParallelOp", "BatchParallelOp", "MatrixParallelOp",
+                               "ReductionParallelOp", "SimdParallelOp", "batch_matmul_parallel", "kaiming_init")},
+    **{n: "optimization" for n in ("HardwareOptimizer", "PlatformOptimizer", "SimdOptimizer")},
+    **{n: "compat" for n in ("AdamConfig", "AdamState", "AdamUtils", "LBFGSMemory", "LineSearchMethod", "AllocationStrategy", "ZeroCopyOps",
+                             "TensorIterOps", "ShapeBuilder", "LazyExpandedTensor", "SafeTensor", "SafeNumeric", "TypedTensor", "WindowType",
+                             "Int4", "ProfilerCore", "RecurrentOps", "LinearBackward", "DistributedState", "GPTModel", "OnnxModel")},
+    **{n: "formats.loaders" for n in ("GGUFLoader", "SafetensorsLoader", "SafetensorsSaver", "Saver", "TensorLoader")},
+    **{n: "gpu.devices" for n in ("GpuDevice", "GpuStream", "CpuDevice", "CudaDevice", "GpuKernel", "ModernGpuKernel", "AddKernel", "MatMulKernel",
+                                  "ConvKernel", "KernelExecutor", "CudaKernelExecutor", "CudaMatrixExecutor", "CudaBuffer", "ComputeBackend",
+                                  "CpuBackend", "GpuBackend", "BackendManager", "SelectionStrategy", "StreamOperation",
+                                  "MetalKernelExecutor", "OpenClKernelExecutor", "OpenClMatrixExecutor", "CoreMLHybrid", "MacHybrid")},
     # distributed
     **{n: "distributed" for n in ("DistributedDataParallel", "DistributedBackend", "DistributedSampler", "get_world_size", "get_rank",
                                   "is_master", "DataParallel")},
 }
 _SUBMODULES = ("nn", "optim", "data", "training", "models", "distributed", "formats", "llm", "amp", "profiler", "debug", "validation",
                "tensorboard", "visualization", "vision", "distributions", "special", "quantization", "sparse", "memory", "gpu", "execution",
-               "model_import", "convert", "model_hub", "jit", "cli", "autograd", "ops", "utils", "parallel")
+               "model_import", "convert", "model_hub", "jit", "cli", "autograd", "ops", "utils", "parallel", "error", "hybrid_f32",
+               "optimization", "compat")
 
 
 def __getattr__(name):

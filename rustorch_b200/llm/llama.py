@@ -239,7 +239,8 @@ class LlamaRuntime:
         return out.to(t.dtype)
 
     def forward_tokens(self, tokens: torch.Tensor, pos: torch.Tensor, seq: torch.Tensor, cache: KVCache,
-                       last_only: Optional[torch.Tensor] = None, max_kv: Optional[int] = None) -> torch.Tensor:
+                       last_only: Optional[torch.Tensor] = None, max_kv: Optional[int] = None,
+                       prefill_bt: Optional[Tuple[int, int]] = None) -> torch.Tensor:
         """``tokens / pos / seq``: ``[n_tok]`` (token id, position in its sequence, sequence index).  The new
         keys/values are appended to ``cache`` and every token attends to positions ``0 .. pos`` of its own
         sequence.  Returns fp32 logits ``[n_tok or len(last_only), vocab]``."""
@@ -255,6 +256,11 @@ class LlamaRuntime:
         scale = 1.0 / math.sqrt(D)
         fused_ar = self._fused_epilogue(n, x)
         h = None
+        flash_bt, flash_lse = None, None
+        if (prefill_bt is not None and C is not None and D in (64, 128) and self.act_dtype == torch.float16 and prefill_bt[1] >= 16
+                and prefill_bt[0] * prefill_bt[1] == n):
+            flash_bt = prefill_bt
+            flash_lse = torch.empty((prefill_bt[0], H, prefill_bt[1]), dtype=torch.float32, device=self.device)
         for li, L in enumerate(self.layers):
             if h is None:
                 h = self._rmsnorm(x, L.attn_norm)
@@ -265,7 +271,14 @@ class LlamaRuntime:
             if C is not None:
                 C.rope_kv(q, k, v, cache.k[li], cache.v[li], pos32, seq32, cfg.rope_theta, cfg.rope_interleaved)
                 att = torch.empty((n, H, D), dtype=q.dtype, device=q.device)
-                C.attn_cache(q, cache.k[li], cache.v[li], att, kv_len, seq32, max_kv, scale)
+                if flash_bt is not None:
+                    # prompt processing: causal attention among the new tokens on the tcgen05 flash kernel (fp16 I/O),
+                    # reading the rotated q / k and v straight from the fused projection output
+                    Bp, Tp = flash_bt
+                    C.attn_fwd(q.unflatten(0, (Bp, Tp)), k.unflatten(0, (Bp, Tp)), v.unflatten(0, (Bp, Tp)),
+                               att.view(Bp, Tp, H, D), flash_lse, True, scale)
+                else:
+                    C.attn_cache(q, cache.k[li], cache.v[li], att, kv_len, seq32, max_kv, scale)
             else:
                 q, k = self._rope_reference(q, pos), self._rope_reference(k, pos)
                 cache.k[li][seq, :, pos] = k
@@ -319,7 +332,7 @@ class LlamaRuntime:
         pos = torch.arange(T, device=dev).repeat(B)
         seq = torch.arange(B, device=dev).repeat_interleave(T)
         last = torch.arange(B, device=dev) * T + (T - 1)
-        logits = self.forward_tokens(tokens, pos, seq, cache, last_only=last, max_kv=T)
+        logits = self.forward_tokens(tokens, pos, seq, cache, last_only=last, max_kv=T, prefill_bt=(B, T))
         cache.lengths = [T] * B
         return logits
 

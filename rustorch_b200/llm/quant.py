@@ -69,6 +69,7 @@ class QuantLinear:
     # (the GEMV kernel's per-row arithmetic makes it slower from 5 rows on, and it re-reads the weights for every
     # 8 rows; the two-pass path moves 4.5 B per weight).
     TC_MIN_ROWS, TC_MAX_ROWS = 5, 256
+    TC_PATH = 0          # 0: expanded weights in tensor memory (default); 1: staged in shared memory
     _scratch_buf = {}
     _tc_scratch = {}
 
@@ -125,7 +126,7 @@ class QuantLinear:
             if self.TC_MIN_ROWS <= x2.shape[0] <= self.TC_MAX_ROWS:
                 y = torch.empty((x2.shape[0], self.out_features), dtype=torch.float16, device=self.device)
                 part, cnt = self._tc_buffers(x2.shape[0])
-                C.q_gemm_tc(self.qs, self.scales, x2, y, None, r, self.q8, part, cnt)
+                C.q_gemm_tc(self.qs, self.scales, x2, y, None, r, self.q8, part, cnt, self.TC_PATH)
             elif x2.shape[0] >= self.GEMM_MIN_ROWS:
                 # prefill / large batch: expand once to fp16 scratch, then the tcgen05 GEMM (fp32 accumulate + output)
                 w = self._scratch(self.out_features * self.in_features).view(self.out_features, self.in_features)

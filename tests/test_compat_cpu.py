@@ -1,0 +1,149 @@
+"""Named pieces of the reference surface: errors, parallel traits, hardware hints, hybrid f32, loaders, devices."""
+import os
+
+import pytest
+import torch
+
+import rustorch_b200 as rt
+
+
+def test_error_hierarchy_and_helpers():
+    from rustorch_b200 import error as E
+    with pytest.raises(E.TensorOp) as ei:
+        raise E.RusTorchError.shape_mismatch([2, 3], [3, 2])
+    assert ei.value.kind == "ShapeMismatch" and "expected [2, 3]" in str(ei.value)
+    assert issubclass(E.KernelTimeout, E.GpuError) and issubclass(E.GpuError, rt.RusTorchError)
+    assert E.check_status_to_error(0) is None and isinstance(E.check_status_to_error(104), E.KernelTimeout)
+    assert isinstance(E.check_status_to_error(201), E.IndexOutOfBounds)
+
+
+def test_parallel_traits_and_context():
+    from rustorch_b200 import parallel as P
+    a, b = torch.randn(6, 4, 5), torch.randn(6, 5, 3)
+    assert torch.allclose(P.batch_matmul_parallel(a, b), torch.bmm(a, b))
+    n = P.batch_normalize_parallel(torch.randn(4, 10))
+    assert n.mean(1).abs().max() < 1e-5 and (n.var(1, unbiased=False) - 1).abs().max() < 1e-3
+    with P.ParallelContext(P.ParallelConfig(strategy=P.ParallelStrategy.FORCE_PARALLEL, chunk_size=2)) as ctx:
+        assert torch.equal(ctx.map_chunks(lambda t: t * 3, torch.ones(7, 2)), torch.full((7, 2), 3.0))
+    pt = rt.ParallelTensor(a)
+    assert pt.matmul(b).data.shape == (6, 4, 3) and abs(float(pt.sum()) - float(a.sum())) < 1e-3
+    assert not P.ParallelConfig(strategy=P.ParallelStrategy.SEQUENTIAL).should_parallelize(10 ** 9)
+    assert P.kaiming_init((64, 32)).std() < 1.0 and P.DistributedSampler is not None
+
+
+def test_hardware_optimizer_and_backends():
+    h = rt.HardwareOptimizer()
+    assert h.gemm_tile(4096, 4096, 4096) == (128, 256, 64) and h.gemm_tile(64, 100, 64)[1] == 128
+    assert h.persistent_grid(10) <= 10 and h.preferred_layout("conv2d") == "channels_last"
+    assert rt.SimdOptimizer().vector_width(torch.bfloat16) == 8
+    from rustorch_b200.gpu import devices as D
+    cpu = D.CpuBackend()
+    assert torch.equal(cpu.add(torch.ones(2), torch.ones(2)), torch.full((2,), 2.0)) and "threads" in cpu.capabilities()
+    assert isinstance(D.BackendManager(D.SelectionStrategy.CPU_ONLY).select(), D.CpuBackend)
+    ex = D.KernelExecutor(D.CpuDevice())
+    assert torch.allclose(ex.execute("matmul", torch.eye(3), torch.ones(3, 2)), torch.ones(3, 2))
+    from rustorch_b200.gpu import DeviceNotAvailable
+    for cls in (D.MetalKernelExecutor, D.OpenClKernelExecutor, D.CoreMLHybrid):
+        with pytest.raises(DeviceNotAvailable):
+            cls()
+
+
+def test_adam_utils_and_lbfgs_memory_match_torch():
+    from rustorch_b200.compat import AdamConfig, AdamState, AdamUtils, LBFGSMemory, LineSearchMethod
+    p = torch.nn.Parameter(torch.tensor([1.0, -2.0, 3.0]))
+    ref = p.detach().clone()
+    opt = torch.optim.Adam([p], lr=0.1)
+    st, cfg = AdamState(), AdamConfig(lr=0.1)
+    for _ in range(3):
+        g = torch.tensor([0.5, -1.0, 2.0])
+        p.grad = g.clone()
+        opt.step()
+        AdamUtils.step(ref, g, st, cfg)
+    assert torch.allclose(ref, p.detach(), atol=1e-6)
+    mem = LBFGSMemory(4)
+    A = torch.diag(torch.tensor([1.0, 4.0, 9.0]))          # quadratic: after n updates the direction is Newton's
+    x = torch.zeros(3)
+    for _ in range(6):
+        g = A @ x - torch.ones(3)
+        d = mem.direction(g)
+        x_new = x + d * (0.1 if len(mem) == 0 else 1.0)
+        mem.update(x_new - x, A @ x_new - torch.ones(3) - g)
+        x = x_new
+    assert torch.allclose(x, torch.tensor([1.0, 0.25, 1 / 9]), atol=1e-3)
+    assert LineSearchMethod.STRONG_WOLFE.torch_name() == "strong_wolfe"
+
+
+def test_shape_builder_lazy_expand_safe_numeric_window_int4():
+    from rustorch_b200 import compat as C
+    assert C.ShapeBuilder(torch.zeros(2, 3)).unsqueeze(0).expand(4, -1, -1).flatten(1).shape() == (4, 6)
+    lz = C.LazyExpandedTensor(torch.arange(3.0).view(1, 3), (5, 3))
+    assert lz.memory_saved() == 12 * 4 and lz.materialize().is_contiguous() and float(lz[4, 2]) == 2.0
+    with pytest.raises(rt.RusTorchError):
+        C.SafeTensor(torch.tensor([1e38])) * 1e10
+    with pytest.raises(rt.RusTorchError):
+        C.SafeNumeric.safe_cast(torch.tensor([70000.0]), torch.float16)
+    with pytest.raises(rt.RusTorchError):
+        C.TypedTensor(torch.zeros(3), 2)
+    assert torch.allclose(C.WindowType.HAMMING.apply(torch.ones(8)), torch.hamming_window(8, periodic=False))
+    v = torch.tensor([-8, 7, 0, -1, 5])
+    assert torch.equal(C.Int4.unpack(C.Int4.pack(v), 5), v.to(torch.int8))
+    assert C.ZeroCopyOps.shares_storage(torch.zeros(4, 4), torch.zeros(1)) is False
+    t = torch.arange(12.0).view(3, 4)
+    assert C.ZeroCopyOps.shares_storage(t, C.ZeroCopyOps.slice_view(t, 1, 1, 3))
+    assert C.TensorIterOps.fold(t, 0.0, lambda a, c: a + float(c.sum()), chunk=5) == 66.0
+    pc = C.ProfilerCore()
+    pc.start_session("s"); pc.start_timer("a"); pc.stop_timer("a")
+    assert pc.end_session()["timers"]["a"] and pc.summary()["a"]["count"] == 1
+
+
+def test_hybrid_f32_tensor_variable_trainer(tmp_path):
+    from rustorch_b200 import hybrid_f32 as H
+    a = H.F32Tensor.from_vec([1, 2, 3, 4], [2, 2])
+    assert (a @ a).to_vec() == [7.0, 10.0, 15.0, 22.0] and a.transpose().to_vec() == [1.0, 3.0, 2.0, 4.0]
+    v = H.F32Variable(a, True)
+    (v * v).sum().backward()
+    assert v.grad().to_vec() == [2.0, 4.0, 6.0, 8.0]
+    torch.manual_seed(0)
+    m = torch.nn.Sequential(H.F32Linear(4, 8), torch.nn.ReLU(), H.F32Linear(8, 1))
+    X = torch.randn(64, 4)
+    Y = X.sum(1, keepdim=True)
+    data = [(X[i:i + 16], Y[i:i + 16]) for i in range(0, 64, 16)]
+    cfg = H.F32TrainerConfig(epochs=40, learning_rate=0.05, early_stopping_patience=8, scheduler="cosine", checkpoint_dir=str(tmp_path))
+    tr = H.F32Trainer(m, torch.nn.functional.mse_loss, cfg, device="cpu")
+    hist = tr.fit(data, data)
+    assert hist["train_loss"][-1] < 0.2 * hist["train_loss"][0] and os.path.exists(tmp_path / "best.pt")
+    assert tr.load_checkpoint(str(tmp_path / "best.pt")) >= 0
+
+
+def test_loader_objects_round_trip(tmp_path):
+    from rustorch_b200.formats import gguf
+    from rustorch_b200.formats.loaders import GGUFLoader, SafetensorsLoader, SafetensorsSaver, TensorLoader
+    p = str(tmp_path / "m.safetensors")
+    w = {"a.weight": torch.randn(3, 4), "b": torch.arange(5.0)}
+    sv = SafetensorsSaver({"format": "pt"})
+    for k, t in w.items():
+        sv.add_tensor(k, t)
+    sv.save_to_file(p)
+    ld = SafetensorsLoader.from_file(p)
+    assert sorted(ld.tensor_names()) == sorted(w) and ld.metadata()["format"] == "pt" and torch.equal(ld.tensor("b"), w["b"])
+    assert torch.equal(TensorLoader(p).load_tensor("a.weight"), w["a.weight"])
+    g = str(tmp_path / "m.gguf")
+    gguf.write_gguf(g, {"general.architecture": "llama", "llama.block_count": 2}, {"t": (torch.randn(4, 64), gguf.GGMLType.Q8_0)})
+    with GGUFLoader(g) as gl:
+        assert gl.architecture() == "llama" and gl.tensor_names() == ["t"] and gl.load_tensor("t").shape == (4, 64)
+    assert TensorLoader(g).tensor_names() == ["t"]
+
+
+def test_misc_named_pieces():
+    from rustorch_b200 import compat as C
+    g = C.GPTModel(50, 32, 1, 2, 16)
+    out = g(torch.randint(0, 50, (2, 8)))
+    assert out.shape == (2, 8, 50) and torch.equal(out, C.GPTModel(50, 32, 1, 2, 16)(torch.randint(0, 50, (2, 8), generator=None)) * 0 + out)
+    x, w = torch.randn(4, 3, requires_grad=True), torch.randn(2, 3, requires_grad=True)
+    C.LinearBackward.apply(x, w, None).sum().backward()
+    assert torch.allclose(w.grad, x.detach().sum(0).expand(2, 3))
+    assert C.DistributedState.get()["world_size"] == 1 and not C.DistributedState.is_initialized()
+    cell = torch.nn.GRUCell(3, 4)
+    ys, h = C.RecurrentOps.run_cell(lambda xt, s: cell(xt, s), torch.randn(5, 2, 3))
+    assert ys.shape == (5, 2, 4) and torch.equal(ys[-1], h)
+    assert C.AllocationStrategy.PINNED.allocate((4,)).shape == (4,)

@@ -173,9 +173,53 @@ def test_q_gemm_tensor_core_matches_reference(q8, M, N, K):
     res = torch.randn(M, N, device="cuda").half()
     assert QuantLinear.TC_MIN_ROWS <= M <= QuantLinear.TC_MAX_ROWS
     ref = x.float() @ q.dequantize().t().to("cuda") + res.float()
-    for _ in range(2):                                # second call: the tile counters were left at zero
-        y = q(x, residual=res)
-        assert rel_err(y, ref) < 3e-3
-    y2 = q(x)
-    assert rel_err(y2, ref - res.float()) < 3e-3
+    try:
+        for path in (0, 1):                           # operand A in tensor memory / staged in shared memory
+            QuantLinear.TC_PATH = path
+            for _ in range(2):                        # second call: the tile counters were left at zero
+                y = q(x, residual=res)
+                assert rel_err(y, ref) < 3e-3, path
+            y2 = q(x)
+            assert rel_err(y2, ref - res.float()) < 3e-3, path
+    finally:
+        QuantLinear.TC_PATH = 0
     _native.check_status()
+
+
+@pytest.mark.parametrize("D,H,Hkv", [(64, 4, 2), (128, 8, 2)])
+def test_flash_attention_fp16_io_on_packed_qkv(D, H, Hkv):
+    """The prefill path: fp16 q / k / v read as strided views of one packed projection output."""
+    from rustorch_b200 import _native
+    C = _native.load(required=True)
+    B, T = 2, 200
+    qkv = (torch.randn(B * T, (H + 2 * Hkv) * D, device="cuda") * 0.7).half()
+    q = qkv[:, : H * D].view(B * T, H, D).unflatten(0, (B, T))
+    k = qkv[:, H * D: (H + Hkv) * D].view(B * T, Hkv, D).unflatten(0, (B, T))
+    v = qkv[:, (H + Hkv) * D:].view(B * T, Hkv, D).unflatten(0, (B, T))
+    out = torch.empty((B, T, H, D), dtype=torch.half, device="cuda")
+    lse = torch.empty((B, H, T), dtype=torch.float32, device="cuda")
+    scale = D ** -0.5
+    C.attn_fwd(q, k, v, out, lse, True, scale)
+    g = H // Hkv
+    qf, kf, vf = q.float().transpose(1, 2), k.float().repeat_interleave(g, 2).transpose(1, 2), v.float().repeat_interleave(g, 2).transpose(1, 2)
+    s = (qf @ kf.transpose(-1, -2)) * scale
+    s = s.masked_fill(torch.ones(T, T, device="cuda", dtype=torch.bool).triu(1), float("-inf"))
+    ref = (torch.softmax(s, -1) @ vf).transpose(1, 2)
+    assert rel_err(out, ref) < 4e-3
+    assert rel_err(lse, torch.logsumexp(s, -1)) < 1e-3
+    _native.check_status()
+
+
+def test_prefill_flash_path_matches_cached_attention_path():
+    from rustorch_b200.llm import LlamaConfig, LlamaRuntime
+    cfg = LlamaConfig(vocab_size=256, n_layer=2, n_embd=256, n_head=4, n_head_kv=2, n_ff=512, context_length=128)
+    rt_ = LlamaRuntime.random_init(cfg, "cuda", seed=5, std=0.08)
+    prompt = torch.randint(0, 256, (2, 70), generator=torch.Generator().manual_seed(1)).cuda()
+    c1, c2 = rt_.new_cache(2, 96), rt_.new_cache(2, 96)
+    a = rt_.prefill(prompt, c1)                                               # flash kernel
+    pos = torch.arange(70, device="cuda").repeat(2)
+    seq = torch.arange(2, device="cuda").repeat_interleave(70)
+    last = torch.arange(2, device="cuda") * 70 + 69
+    b = rt_.forward_tokens(prompt.reshape(-1), pos, seq, c2, last_only=last, max_kv=70)   # per-token cached attention
+    assert rel_err(a, b) < 5e-3
+    assert all(rel_err(x, y) < 1e-6 for x, y in zip(c1.k, c2.k))
