@@ -137,9 +137,14 @@ class AllocationStrategy(Enum):
         if self is AllocationStrategy.PINNED:
             return torch.empty(*shape, dtype=dtype, pin_memory=torch.cuda.is_available())
         if self is AllocationStrategy.POOLED:
-            from .memory import MemoryPool
-            pool = _POOLS.setdefault(str(device), MemoryPool())
-            return pool.allocate(tuple(shape), dtype, device) if hasattr(pool, "allocate") else torch.empty(*shape, dtype=dtype, device=device)
+            from .memory import MemoryPool, PoolExhausted
+            key = str(device)
+            if key not in _POOLS:
+                _POOLS[key] = MemoryPool(64 << 20, device)          # 64 MiB arena per device, best-fit with coalescing
+            try:
+                return _POOLS[key].allocate(tuple(shape), dtype)
+            except PoolExhausted:
+                return torch.empty(*shape, dtype=dtype, device=device)
         return torch.empty(*shape, dtype=dtype, device=device)
 
 

@@ -192,7 +192,24 @@ class SimdParallelOp(ParallelOp):
         return (a.reshape(-1).float() * b.reshape(-1).float()).sum()
 
 
-class ParallelTensor(BatchParallelOp, MatrixParallelOp, ReductionParallelOp, SimdParallelOp):
+class GpuParallelOp(ParallelOp):
+    """Reductions and batched products that pick the device by size (src/tensor/gpu_parallel.rs:139-333)."""
+
+    @staticmethod
+    def _place(x: torch.Tensor) -> torch.Tensor:
+        from ..tensor import select_optimal_device
+        return x.to(select_optimal_device(x.numel())) if not x.is_cuda else x
+
+    def gpu_sum(self, x): return self._place(x).sum()
+    def gpu_mean(self, x): return self._place(x).mean()
+    def gpu_max(self, x): return self._place(x).max()
+    def gpu_min(self, x): return self._place(x).min()
+    def gpu_std(self, x, unbiased: bool = False): return self._place(x).std(unbiased=unbiased)
+    def gpu_var(self, x, unbiased: bool = False): return self._place(x).var(unbiased=unbiased)
+    def gpu_batch_matmul(self, a, b): return torch.matmul(self._place(a), self._place(b).to(self._place(a).device))
+
+
+class ParallelTensor(BatchParallelOp, MatrixParallelOp, ReductionParallelOp, SimdParallelOp, GpuParallelOp):
     """A tensor with the parallel traits attached (src/parallel.rs:7-28)."""
 
     def __init__(self, data: torch.Tensor, config: Optional[ParallelConfig] = None):

@@ -754,6 +754,51 @@ class Tensor:
         return Tensor(rustorch_bin.load_tensor(path))
 
     # ------------------------------------------------------ torch fall-through
+    # ------------------------------------------------ GpuLinearAlgebra / GpuReduction / GpuParallelOp traits
+    # (src/gpu/matrix_ops.rs:274-632, src/tensor/gpu_parallel.rs:139-333): the operands move to the GPU when there is
+    # one; bf16 matrices go through the tcgen05 GEMM, everything else through the library kernels.
+    def _gpu(self) -> torch.Tensor:
+        return self.data.cuda() if torch.cuda.is_available() and not self.data.is_cuda else self.data
+
+    def gpu_matmul(self, other) -> "Tensor":
+        from .gpu.devices import MatMulKernel
+        return Tensor(MatMulKernel()(self._gpu(), Tensor(_unwrap(other))._gpu()))
+
+    def gpu_batch_matmul(self, other) -> "Tensor":
+        return Tensor(torch.matmul(self._gpu(), Tensor(_unwrap(other))._gpu()))
+
+    def gpu_matvec(self, vec) -> "Tensor":
+        return Tensor(self._gpu() @ Tensor(_unwrap(vec))._gpu())
+
+    def gpu_conv2d(self, weight, bias=None, stride=1, padding=0) -> "Tensor":
+        from .ops import conv
+        b = None if bias is None else Tensor(_unwrap(bias))._gpu()
+        return Tensor(conv.conv2d(self._gpu(), Tensor(_unwrap(weight))._gpu(), b, stride, padding))
+
+    def gpu_sum(self) -> float:
+        return float(self._gpu().sum())
+
+    def gpu_mean(self) -> float:
+        return float(self._gpu().mean())
+
+    def gpu_max(self) -> float:
+        return float(self._gpu().max())
+
+    def gpu_min(self) -> float:
+        return float(self._gpu().min())
+
+    def gpu_std(self, unbiased: bool = False) -> float:
+        return float(self._gpu().std(unbiased=unbiased))
+
+    def gpu_var(self, unbiased: bool = False) -> float:
+        return float(self._gpu().var(unbiased=unbiased))
+
+    def topk_util(self, k: int, dim: int = -1, largest: bool = True):
+        return self.topk(k, dim, largest)
+
+    def quantile_util(self, q: float) -> float:
+        return self.quantile(q)
+
     def __getattr__(self, name):
         if name.startswith("__"):
             raise AttributeError(name)
@@ -783,6 +828,34 @@ def zeros(shape, **kw) -> Tensor:
 
 def ones(shape, **kw) -> Tensor:
     return Tensor.ones(shape, **kw)
+
+
+def select_optimal_device(numel: int, threshold: int = 1 << 14) -> str:
+    """``"cuda"`` for tensors worth a kernel launch when a GPU is present, else ``"cpu"`` (src/tensor/gpu_parallel.rs:473)."""
+    return "cuda" if torch.cuda.is_available() and numel >= threshold else "cpu"
+
+
+def optimized_matmul(a, b) -> Tensor:
+    """BLAS-backed matrix product (src/linalg/optimized_blas.rs:11-193): MKL / OpenBLAS on the host, the GEMM kernels on the GPU."""
+    return Tensor(_unwrap(a) @ _unwrap(b))
+
+
+def multithreaded_matmul(a, b, num_threads: Optional[int] = None) -> Tensor:
+    if num_threads:
+        prev = torch.get_num_threads()
+        torch.set_num_threads(num_threads)
+        try:
+            return optimized_matmul(a, b)
+        finally:
+            torch.set_num_threads(prev)
+    return optimized_matmul(a, b)
+
+
+def memory_optimized(shape, dtype=torch.float32, device="cpu", pinned: bool = False) -> Tensor:
+    """A tensor from the pooled / pinned allocators (src/tensor/memory/memory_optimized.rs:155-402)."""
+    from .compat import AllocationStrategy
+    strat = AllocationStrategy.PINNED if pinned else AllocationStrategy.POOLED
+    return Tensor(strat.allocate(tuple(shape), dtype, device).zero_())
 
 
 def tensor_nd(nested) -> Tensor:

@@ -147,3 +147,15 @@ def test_misc_named_pieces():
     ys, h = C.RecurrentOps.run_cell(lambda xt, s: cell(xt, s), torch.randn(5, 2, 3))
     assert ys.shape == (5, 2, 4) and torch.equal(ys[-1], h)
     assert C.AllocationStrategy.PINNED.allocate((4,)).shape == (4,)
+
+
+def test_gpu_trait_methods_and_linalg_helpers_on_cpu():
+    from rustorch_b200 import tensor as T
+    from rustorch_b200.parallel import GpuParallelOp
+    a = rt.tensor([[1.0, 2.0], [3.0, 4.0]])
+    assert a.gpu_matmul(a).data.cpu().tolist() == [[7.0, 10.0], [15.0, 22.0]] and a.gpu_sum() == 10.0 and a.gpu_max() == 4.0
+    assert a.gpu_matvec(rt.tensor([1.0, 1.0])).data.cpu().tolist() == [3.0, 7.0]
+    assert a.topk_util(1)[0].data.cpu().flatten().tolist() == [2.0, 4.0] and abs(a.quantile_util(0.5) - 2.5) < 1e-6
+    assert T.select_optimal_device(4) == "cpu" and T.multithreaded_matmul(a, a, 2).data.shape == (2, 2)
+    assert T.memory_optimized((3, 3)).data.sum() == 0
+    assert float(GpuParallelOp().gpu_var(torch.tensor([1.0, 3.0]))) == 1.0
