@@ -6,6 +6,8 @@ same object dequantises to fp32 and uses a plain matmul, which is also the oracl
 """
 from __future__ import annotations
 
+import os
+
 from typing import Optional, Tuple
 
 import numpy as np
@@ -69,7 +71,8 @@ class QuantLinear:
     # (the GEMV kernel's per-row arithmetic makes it slower from 5 rows on, and it re-reads the weights for every
     # 8 rows; the two-pass path moves 4.5 B per weight).
     TC_MIN_ROWS, TC_MAX_ROWS = 5, 256
-    TC_PATH = 0          # 0: expanded weights in tensor memory (default); 1: staged in shared memory
+    # 0: expanded weights in tensor memory (default); 1: staged in shared memory (RUSTORCH_QGEMM_PATH overrides)
+    TC_PATH = int(os.environ.get("RUSTORCH_QGEMM_PATH", "0"))
     _scratch_buf = {}
     _tc_scratch = {}
 
