@@ -82,6 +82,8 @@ __device__ __forceinline__ void ar_accumulate(float (&acc)[8], const uint4& v) {
 template <typename T>
 __global__ void __launch_bounds__(1024, 1) ar_residual_norm_kernel(const ArNormArgs a) {
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int W = a.world, R = a.rank;
   const int row = blockIdx.x;
   const int vpr = a.d / 8;                         // vectors per row
@@ -217,8 +219,8 @@ void ar_residual_norm(const ArNormArgs& a, cudaStream_t stream) {
   const int threads = std::min(1024, std::max(32, ((vpr + 31) / 32) * 32));
   ArNormArgs b = a;
   b.status = status_word(current_device());
-  if (a.dtype == DT_F16) ar_residual_norm_kernel<__half><<<a.rows, threads, 0, stream>>>(b);
-  else ar_residual_norm_kernel<__nv_bfloat16><<<a.rows, threads, 0, stream>>>(b);
+  if (a.dtype == DT_F16) launch_pdl(ar_residual_norm_kernel<__half>, dim3(a.rows), dim3(threads), 0, stream, b);
+  else launch_pdl(ar_residual_norm_kernel<__nv_bfloat16>, dim3(a.rows), dim3(threads), 0, stream, b);
   RT_LAUNCH_CHECK();
 }
 

@@ -1,5 +1,7 @@
 #include "launch.h"
 
+#include <cstdlib>
+
 #include <atomic>
 #include <mutex>
 
@@ -187,6 +189,14 @@ CUtensorMap make_tmap_nhwc(const void* base, uint64_t C, uint64_t W, uint64_t H,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   RT_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(nhwc) failed with code " + std::to_string(int(r)));
   return m;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("RUSTORCH_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 }  // namespace rt

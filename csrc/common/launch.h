@@ -2,6 +2,7 @@
 // units include only this and compile in seconds; the tensor-facing glue lives in
 // csrc/bindings.cpp.
 #pragma once
+#include <utility>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -67,5 +68,27 @@ CUtensorMap make_tmap_words_sw128(const void* base, uint64_t row_bytes, uint64_t
 // a box covers 64 channels x box_w x box_h x box_n positions taken every `stride` pixels along W and H.
 CUtensorMap make_tmap_nhwc(const void* base, uint64_t C, uint64_t W, uint64_t H, uint64_t N, uint32_t box_w, uint32_t box_h,
                            uint32_t box_n, uint32_t stride);
+
+// True unless RUSTORCH_PDL=0: kernels of the decode path are then launched with programmatic stream serialization
+// (the next kernel's prologue and weight prefetch overlap the tail of the previous one; see pdl_wait in ptx.cuh).
+bool pdl_enabled();
+
+#ifdef __CUDACC__
+// kern<<<grid, block, smem, stream>>>(args...) with the programmatic-dependent-launch attribute.
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  RT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, KArgs(std::forward<Args>(args))...));
+}
+#endif
 
 }  // namespace rt

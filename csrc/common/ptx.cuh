@@ -102,6 +102,15 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may start while its
+// predecessor in the stream is still running.  pdl_launch_dependents() lets the NEXT kernel start (once every CTA of
+// this grid has executed it or exited); pdl_wait() blocks until the PREVIOUS grid has completed and its writes are
+// visible.  Rule used throughout: a thread calls pdl_wait() before its first read of anything an earlier kernel
+// produced and before any global write; loads of weights (constant during a run) may come first.  Both are no-ops
+// for kernels launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Shared per-CTA control block used by the bounded waits.
 struct CtaCtl {
   volatile int abort;  // set by the first role that times out

@@ -19,6 +19,7 @@
 
 #include "../api.h"
 #include "../common/launch.h"
+#include "../common/ptx.cuh"
 
 namespace rt {
 
@@ -60,6 +61,8 @@ attn_decode_split_kernel(const __half* __restrict__ q, long long q_st, const __h
   constexpr int KPW = 32 / LPK; // keys per warp step
   __shared__ float sm_acc[ADS_WARPS][G][D];
   __shared__ float sm_ml[ADS_WARPS][G][2];
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int t = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z;
   const int L = kv_len[t], s = seq[t];
@@ -172,6 +175,8 @@ attn_decode_split_kernel(const __half* __restrict__ q, long long q_st, const __h
 
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part, __half* __restrict__ out, long long o_st,
                                            int H, int D, int n_split) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const float* src = part + ((long long)t * H + h) * n_split * (D + 2);
   float mm = -CUDART_INF_F;
@@ -192,14 +197,13 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part, __hal
 template <int D, int G>
 void launch_split(const AttnCacheArgs& a, cudaStream_t s) {
   dim3 grid(a.n_tok, a.Hkv, a.n_split);
-  attn_decode_split_kernel<D, G><<<grid, ADS_WARPS * 32, 0, s>>>(
-      reinterpret_cast<const __half*>(a.q), a.q_st, reinterpret_cast<const __half*>(a.cache_k),
-      reinterpret_cast<const __half*>(a.cache_v), reinterpret_cast<__half*>(a.out), a.o_st, a.kv_len, a.seq, a.H,
-      a.Hkv, a.T_max, a.scale * 1.4426950408889634f, a.n_split, a.partial);
+  launch_pdl(attn_decode_split_kernel<D, G>, grid, dim3(ADS_WARPS * 32), 0, s, reinterpret_cast<const __half*>(a.q), a.q_st,
+             reinterpret_cast<const __half*>(a.cache_k), reinterpret_cast<const __half*>(a.cache_v), reinterpret_cast<__half*>(a.out),
+             a.o_st, a.kv_len, a.seq, a.H, a.Hkv, a.T_max, a.scale * 1.4426950408889634f, a.n_split, a.partial);
   RT_LAUNCH_CHECK();
   if (a.n_split > 1) {
-    attn_decode_combine_kernel<<<dim3(a.n_tok, a.H), D <= 128 ? D : 128, 0, s>>>(
-        a.partial, reinterpret_cast<__half*>(a.out), a.o_st, a.H, D, a.n_split);
+    launch_pdl(attn_decode_combine_kernel, dim3(a.n_tok, a.H), dim3(D <= 128 ? D : 128), 0, s,
+               static_cast<const float*>(a.partial), reinterpret_cast<__half*>(a.out), a.o_st, a.H, D, a.n_split);
     RT_LAUNCH_CHECK();
   }
 }

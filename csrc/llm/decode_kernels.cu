@@ -16,6 +16,7 @@
 
 #include "../api.h"
 #include "../common/launch.h"
+#include "../common/ptx.cuh"
 
 namespace rt {
 
@@ -32,6 +33,8 @@ __device__ __forceinline__ float wmax(float v) {
 
 __global__ void rmsnorm_f16_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
                                    __half* __restrict__ y, int C, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long row = blockIdx.x;
   const __half2* xr = reinterpret_cast<const __half2*>(x + row * C);
   __shared__ float red[32];
@@ -68,6 +71,8 @@ __global__ void rope_kv_f16_kernel(__half* __restrict__ q, long long q_st, __hal
                                    __half* __restrict__ cache_k, __half* __restrict__ cache_v,
                                    const int* __restrict__ pos, const int* __restrict__ seq, int H, int Hkv,
                                    int D, int T_max, float log2_theta, int interleaved) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x, hy = blockIdx.y;
   const int p = pos[t], s = seq[t];
   const int half_d = D >> 1;
@@ -165,6 +170,8 @@ __global__ void attn_cache_f16_kernel(const __half* __restrict__ q, long long q_
 __global__ void silu_mul_f16_kernel(const __half* __restrict__ gate, const __half* __restrict__ up,
                                     __half* __restrict__ out, long long n2, long long g_ld, long long u_ld,
                                     long long o_ld, int cols2) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n2) return;
   const long long r = i / cols2, c = i % cols2;
@@ -177,9 +184,8 @@ __global__ void silu_mul_f16_kernel(const __half* __restrict__ gate, const __hal
 void rmsnorm_f16(const void* x, const void* w, void* y, long long rows, int C, float eps, cudaStream_t s) {
   RT_CHECK(C % 2 == 0, "rmsnorm_f16: feature size must be even");
   if (rows == 0) return;
-  rmsnorm_f16_kernel<<<(unsigned)rows, 256, 0, s>>>(reinterpret_cast<const __half*>(x),
-                                                    reinterpret_cast<const __half*>(w),
-                                                    reinterpret_cast<__half*>(y), C, eps);
+  launch_pdl(rmsnorm_f16_kernel, dim3((unsigned)rows), dim3(256), 0, s, reinterpret_cast<const __half*>(x),
+             reinterpret_cast<const __half*>(w), reinterpret_cast<__half*>(y), C, eps);
   RT_LAUNCH_CHECK();
 }
 
@@ -187,10 +193,10 @@ void rope_kv_f16(const RopeKvArgs& a, cudaStream_t s) {
   RT_CHECK(a.D % 2 == 0, "rope: head_dim must be even");
   if (a.n_tok == 0) return;
   const int threads = std::min(128, std::max(32, ((a.D / 2 + 31) / 32) * 32));
-  rope_kv_f16_kernel<<<dim3(a.n_tok, a.H + 2 * a.Hkv), threads, 0, s>>>(
-      reinterpret_cast<__half*>(a.q), a.q_st, reinterpret_cast<__half*>(a.k), a.k_st, reinterpret_cast<const __half*>(a.v),
-      a.v_st, reinterpret_cast<__half*>(a.cache_k), reinterpret_cast<__half*>(a.cache_v), a.pos, a.seq, a.H, a.Hkv, a.D,
-      a.T_max, log2f(a.theta), a.interleaved);
+  launch_pdl(rope_kv_f16_kernel, dim3(a.n_tok, a.H + 2 * a.Hkv), dim3(threads), 0, s, reinterpret_cast<__half*>(a.q), a.q_st,
+             reinterpret_cast<__half*>(a.k), a.k_st, reinterpret_cast<const __half*>(a.v), a.v_st,
+             reinterpret_cast<__half*>(a.cache_k), reinterpret_cast<__half*>(a.cache_v), a.pos, a.seq, a.H, a.Hkv, a.D, a.T_max,
+             log2f(a.theta), a.interleaved);
   RT_LAUNCH_CHECK();
 }
 
@@ -216,9 +222,8 @@ void silu_mul_f16(const void* gate, const void* up, void* out, long long rows, i
   RT_CHECK(cols % 2 == 0 && g_ld % 2 == 0 && u_ld % 2 == 0 && o_ld % 2 == 0, "silu_mul: even sizes required");
   const long long n2 = rows * (cols / 2);
   if (n2 == 0) return;
-  silu_mul_f16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, s>>>(
-      reinterpret_cast<const __half*>(gate), reinterpret_cast<const __half*>(up), reinterpret_cast<__half*>(out), n2,
-      g_ld, u_ld, o_ld, cols / 2);
+  launch_pdl(silu_mul_f16_kernel, dim3((unsigned)((n2 + 255) / 256)), dim3(256), 0, s, reinterpret_cast<const __half*>(gate),
+             reinterpret_cast<const __half*>(up), reinterpret_cast<__half*>(out), n2, g_ld, u_ld, o_ld, cols / 2);
   RT_LAUNCH_CHECK();
 }
 

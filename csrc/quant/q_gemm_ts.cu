@@ -134,6 +134,7 @@ __global__ void __launch_bounds__(QT_THREADS, 3) q_gemm_ts_kernel(const __grid_c
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_launch_dependents();
   const uint32_t tmem_base = *tmem_slot;
   auto subs_of = [&](int c) { return min(SUBS, (p.K - c * KRAW + 63) >> 6); };
 
@@ -155,6 +156,7 @@ __global__ void __launch_bounds__(QT_THREADS, 3) q_gemm_ts_kernel(const __grid_c
     if (lane == 0) {
       Ring xr(OS);
       bool ok = true;
+      pdl_wait();                       // the activations come from the previous kernel; the weights above do not
       for (int c = c_begin; c < c_end && ok; ++c) {
         const int ns = subs_of(c);
         for (int sub = 0; sub < ns; ++sub) {
@@ -276,6 +278,7 @@ __global__ void __launch_bounds__(QT_THREADS, 3) q_gemm_ts_kernel(const __grid_c
 #pragma unroll
       for (int sub = 0; sub < SUBS; ++sub) dcur[sub] = dnxt[sub];
     }
+    pdl_wait();                          // residual / y / split-K scratch: only after the previous kernel has finished
     // ---- epilogue: D[lane = weight row][col = activation row]
     const int quarter = warp & 3, col_half = (warp - 2) >> 2;
     const int nl = quarter * 32 + lane;            // row of the tile this thread reads from TMEM
@@ -396,14 +399,14 @@ void q_gemm_ts(const QGemvArgs& a, void* partial, int* counters, cudaStream_t st
       RT_CUDA_CHECK(cudaFuncSetAttribute(q_gemm_ts_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
       cfg[device] = true;
     }
-    q_gemm_ts_kernel<true><<<grid, QT_THREADS, smem, stream>>>(tr, tx, p);
+    launch_pdl(q_gemm_ts_kernel<true>, grid, dim3(QT_THREADS), (size_t)smem, stream, tr, tx, p);
   } else {
     static bool cfg[64] = {false};
     if (!cfg[device]) {
       RT_CUDA_CHECK(cudaFuncSetAttribute(q_gemm_ts_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
       cfg[device] = true;
     }
-    q_gemm_ts_kernel<false><<<grid, QT_THREADS, smem, stream>>>(tr, tx, p);
+    launch_pdl(q_gemm_ts_kernel<false>, grid, dim3(QT_THREADS), (size_t)smem, stream, tr, tx, p);
   }
   RT_LAUNCH_CHECK();
 }

@@ -21,6 +21,7 @@
 
 #include "../api.h"
 #include "../common/launch.h"
+#include "../common/ptx.cuh"
 #include "q_expand.cuh"
 
 namespace rt {
@@ -78,7 +79,9 @@ __global__ void __launch_bounds__(QG_WARPS * 32) q_gemv_kernel(const void* __res
   QRaw<Q8> cur[QG_R], nxt[QG_R];
   __half dcur[QG_R], dnxt[QG_R];
   int b = b_begin + lane;
-  if (b < b_end) fetch(b, cur, dcur);
+  pdl_launch_dependents();
+  if (b < b_end) fetch(b, cur, dcur);   // weights do not depend on the previous kernel: in flight before the wait
+  pdl_wait();
   for (; b < b_end; b += 32) {
     const bool more = b + 32 < b_end;
     if (more) fetch(b + 32, nxt, dnxt);
@@ -145,7 +148,7 @@ static void launch_rows(const QGemvArgs& a, int m0, int m, cudaStream_t s) {
   const __half* r = a.residual ? reinterpret_cast<const __half*>(a.residual) + (long long)m0 * a.ldr : nullptr;
   auto sc = reinterpret_cast<const __half*>(a.scales);
   auto bi = reinterpret_cast<const __half*>(a.bias);
-#define RT_QG(MM) q_gemv_kernel<Q8, MM><<<grid, block, 0, s>>>(a.qs, sc, x, a.ldx, y, a.ldy, bi, r, a.ldr, a.N, a.K)
+#define RT_QG(MM) launch_pdl(q_gemv_kernel<Q8, MM>, grid, block, 0, s, a.qs, sc, x, a.ldx, y, a.ldy, bi, r, a.ldr, a.N, a.K)
   switch (m) {
     case 1: RT_QG(1); break;
     case 2: RT_QG(2); break;

@@ -222,4 +222,5 @@ def test_prefill_flash_path_matches_cached_attention_path():
     last = torch.arange(2, device="cuda") * 70 + 69
     b = rt_.forward_tokens(prompt.reshape(-1), pos, seq, c2, last_only=last, max_kv=70)   # per-token cached attention
     assert rel_err(a, b) < 5e-3
-    assert all(rel_err(x, y) < 1e-6 for x, y in zip(c1.k, c2.k))
+    assert rel_err(c1.k[0], c2.k[0]) < 1e-6                      # layer 0: same inputs, same rotation
+    assert all(rel_err(x, y) < 5e-3 for x, y in zip(c1.k, c2.k))   # later layers see the other kernel's rounding
