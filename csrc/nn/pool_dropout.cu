@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const T* __restrict__ x, 
     pix /= a.OW;
     const int oh = (int)(pix % a.OH), n = (int)(pix / a.OH);
     float acc[V];
-    unsigned char best[V];
+    __align__(8) unsigned char best[V];
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = MAX ? -INFINITY : 0.f, best[i] = 0;
     const int h0 = oh * a.sh - a.ph, w0 = ow * a.sw - a.pw;
@@ -95,8 +95,8 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const T* __restrict__ x, 
     const long long o = (((long long)n * a.OH + oh) * a.OW + ow) * a.C + c;
     pstore(y + o, acc);
     if (MAX && idx != nullptr) {
-#pragma unroll
-      for (int i = 0; i < V; ++i) idx[o + i] = best[i];
+      if (V == 8) *reinterpret_cast<uint2*>(idx + o) = *reinterpret_cast<const uint2*>(best);
+      else *reinterpret_cast<unsigned*>(idx + o) = *reinterpret_cast<const unsigned*>(best);
     }
   }
 }
@@ -131,9 +131,12 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const T* __restrict__ dy,
         pload(dy + o, g);
         if (MAX) {
           const unsigned char me = (unsigned char)(kh * a.kw + kw);
+          __align__(8) unsigned char rec[V];         // V consecutive bytes: one 4- or 8-byte load
+          if (V == 8) *reinterpret_cast<uint2*>(rec) = *reinterpret_cast<const uint2*>(idx + o);
+          else *reinterpret_cast<unsigned*>(rec) = *reinterpret_cast<const unsigned*>(idx + o);
 #pragma unroll
           for (int i = 0; i < V; ++i)
-            if (idx[o + i] == me) acc[i] += g[i];
+            if (rec[i] == me) acc[i] += g[i];
         } else {
 #pragma unroll
           for (int i = 0; i < V; ++i) acc[i] += g[i] * inv;

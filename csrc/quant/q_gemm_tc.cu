@@ -387,7 +387,8 @@ void q_gemm_tc_scratch(int M, int N, int K, bool q8, int sms, long long* partial
   // CTAs run one per SM: cost = waves x (chunks per CTA + fixed part); pick the cheapest split count.
   int splits = 1;
   double best = 1e30;
-  const int slots = sms * (pad_m(M) <= 32 ? 2 : 1);      // up to 32 rows two CTAs share an SM
+  // CTAs that share an SM hide each other's latencies but also share its issue slots: count waves per SM
+  const int slots = sms;
   for (int s = 1; s <= std::min(16, std::max(1, total / 2)); ++s) {
     const int per_s = (total + s - 1) / s, waves = (tiles * s + slots - 1) / slots;
     const double cost = waves * (per_s + 1.5);

@@ -21,6 +21,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "../api.h"
 #include "../common/launch.h"
@@ -34,7 +35,7 @@ namespace {
 constexpr int QT_THREADS = 352;   // warp 0 raw producer, 1 MMA, 2..9 dequantise + epilogue, 10 activation producer
 constexpr int QT_X_WARP = 10;
 constexpr int QT_DQ_WARPS = 8;
-constexpr int QT_RAW_STAGES = 3;   // most; small activation tiles use 2 so that two CTAs share an SM
+constexpr int QT_RAW_STAGES = 4;   // most
 constexpr int QT_MAX_SLOTS = 6;
 constexpr int QT_RAW_BYTES = 128 * 128;   // 128 rows x 128 B
 constexpr int QT_A_COLS = 32;              // TMEM columns of one 64-k operand slot (128 lanes x 64 halves)
@@ -372,7 +373,8 @@ void q_gemm_ts(const QGemvArgs& a, void* partial, int* counters, cudaStream_t st
   p.m_pad = pad_m(a.M);
   // TMEM: accumulator (max(32, m_pad) columns) + operand slots of 32 columns, rounded up to a power of two.
   p.op_slots = p.m_pad <= 32 ? 3 : p.m_pad == 64 ? 2 : 4;
-  p.raw_stages = p.m_pad <= 64 ? 2 : QT_RAW_STAGES;
+  p.raw_stages = p.m_pad <= 64 ? 2 : 3;
+  if (const char* e = std::getenv("RUSTORCH_QGEMM_RAW_STAGES")) p.raw_stages = std::min(QT_RAW_STAGES, std::max(1, atoi(e)));
   {
     const int need = std::max(32, p.m_pad) + p.op_slots * QT_A_COLS;
     int cols = 32;

@@ -184,6 +184,10 @@ class _BatchNorm(nn.modules.batchnorm._BatchNorm):
             self.num_batches_tracked.add_(1)
             if self.momentum is None:
                 momentum = 1.0 / float(self.num_batches_tracked)
+        if self.running_mean is not None and self.running_mean.dtype != torch.float32 and x.is_cuda:
+            # ``model.to(bf16)`` also casts the buffers; the statistics are kept (and updated by the kernel) in fp32
+            self.running_mean = self.running_mean.float()
+            self.running_var = self.running_var.float()
         rm = self.running_mean if (not self.training or self.track_running_stats) else None
         rv = self.running_var if (not self.training or self.track_running_stats) else None
         return batch_norm(x, rm, rv, self.weight, self.bias, self.training or rm is None, momentum, self.eps, residual, relu)
