@@ -219,6 +219,9 @@ struct P2PCollArgs {
 };
 void p2p_collective(const P2PCollArgs& a, cudaStream_t stream);
 
+// conv/im2col.cu: patch matrix [N*OH*OW][k_pad] of a channels-last bf16 image (rows zero-padded to k_pad)
+void im2col_nhwc(const void* x, void* col, int N, int H, int W, int C, int OH, int OW, int KH, int KW, int stride, int pad, int k_pad,
+                 cudaStream_t s);
 // ------------------------------------------------------------ nn/pool_dropout.cu
 // Channels-last pooling.  Forward: x [N][H][W][C] -> y [N][OH][OW][C] (+ idx for max).  Backward: y holds dy, x receives dx.
 struct Pool2dArgs {

@@ -725,7 +725,20 @@ void swiglu(const Tensor& gu, const c10::optional<Tensor>& dact, Tensor& out, bo
   rt::swiglu(gu.data_ptr(), pd, out.data_ptr(), rows, int(F), backward, cur_stream(gu.device().index()));
 }
 
+// x: [N, H, W, C] contiguous bf16; col: [N * OH * OW, k_pad] bf16.
+void im2col_nhwc(const Tensor& x, Tensor& col, int64_t KH, int64_t KW, int64_t stride, int64_t pad) {
+  check_bf16c(x, "im2col x"); check_bf16c(col, "im2col col");
+  TORCH_CHECK(x.dim() == 4 && col.dim() == 2, "im2col: x [N, H, W, C], col [N * OH * OW, k_pad]");
+  const int64_t N = x.size(0), H = x.size(1), W = x.size(2), C = x.size(3);
+  const int64_t OH = (H + 2 * pad - KH) / stride + 1, OW = (W + 2 * pad - KW) / stride + 1;
+  TORCH_CHECK(col.size(0) == N * OH * OW, "im2col: col has ", col.size(0), " rows, expected ", N * OH * OW);
+  c10::cuda::CUDAGuard guard(x.device());
+  rt::im2col_nhwc(x.data_ptr(), col.data_ptr(), int(N), int(H), int(W), int(C), int(OH), int(OW), int(KH), int(KW), int(stride), int(pad),
+                  int(col.size(1)), cur_stream(x.device().index()));
+}
+
 void register_extra_ops(pybind11::module_& m) {
+  m.def("im2col_nhwc", &im2col_nhwc, "patch matrix of a channels-last bf16 image (few input channels)");
   m.def("p2p_collective", &p2p_collective, "all-reduce / all-gather / reduce-scatter / broadcast over symmetric peer memory");
   m.def("rope_split", &rope_split, "rotary embedding fused with the q / k / v split (bf16), forward or backward");
   m.def("swiglu", &swiglu, "silu(gate) * up over a [rows, 2F] gate|up matrix (bf16), forward or backward");

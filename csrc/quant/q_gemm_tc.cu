@@ -387,11 +387,14 @@ void q_gemm_tc_scratch(int M, int N, int K, bool q8, int sms, long long* partial
   // CTAs run one per SM: cost = waves x (chunks per CTA + fixed part); pick the cheapest split count.
   int splits = 1;
   double best = 1e30;
-  // CTAs that share an SM hide each other's latencies but also share its issue slots: count waves per SM
-  const int slots = sms;
+  // Cost of a split count: the busiest SM gets n = ceil(CTAs / SMs) CTAs of (chunks + fixed part) each.  Up to 32 rows
+  // two CTAs share an SM; measured, a co-resident pair finishes in ~1.43x the time of one CTA (they hide each
+  // other's latencies but share the issue slots), so n CTAs cost (n / 2) * 1.43 + (n % 2).
+  const bool pairs = pad_m(M) <= 32;
   for (int s = 1; s <= std::min(16, std::max(1, total / 2)); ++s) {
-    const int per_s = (total + s - 1) / s, waves = (tiles * s + slots - 1) / slots;
-    const double cost = waves * (per_s + 1.5);
+    const int per_s = (total + s - 1) / s, n = (tiles * s + sms - 1) / sms;
+    const double rounds = pairs ? (n / 2) * 1.43 + (n % 2) : (double)n;
+    const double cost = rounds * (per_s + 1.5);
     if (cost < best - 1e-9) best = cost, splits = s;
   }
   const int per = (total + splits - 1) / splits;

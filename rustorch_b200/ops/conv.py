@@ -76,8 +76,65 @@ class Conv2dFn(torch.autograd.Function):
         return dx, dw, db, None, None
 
 
+def im2col_supported(x: torch.Tensor, weight: torch.Tensor, stride, padding, dilation=1, groups: int = 1) -> bool:
+    """Few input channels (a network's stem): patch matrix + tcgen05 GEMM.  The input must not need a gradient."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 4 and _native.available()):
+        return False
+    if x.requires_grad or groups != 1 or (dilation if isinstance(dilation, int) else dilation[0]) != 1:
+        return False
+    if not isinstance(stride, int) and stride[0] != stride[1] or not isinstance(padding, int) and padding[0] != padding[1]:
+        return False
+    if isinstance(padding if isinstance(padding, int) else padding[0], str):
+        return False
+    Cout, Cin, KH, KW = weight.shape
+    return Cin % 64 != 0 and Cin * KH * KW <= 512 and Cout % 8 == 0
+
+
+class Im2colConv2dFn(torch.autograd.Function):
+    """``y = col(x) @ W^T`` with ``col`` written once by csrc/conv/im2col.cu and kept for the weight gradient
+    ``dW = dy^T @ col`` (both products on the tcgen05 GEMM; the second in its weight-gradient layout with split-K)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, stride: int, pad: int):
+        from . import kernels as K
+        C = _native.load(required=True)
+        xh, wh = _nhwc(x), _nhwc(weight)                       # [N,H,W,Cin], [Cout,KH,KW,Cin]
+        N, H, W, Cin = xh.shape
+        Cout, KH, KW, _ = wh.shape
+        OH, OW = (H + 2 * pad - KH) // stride + 1, (W + 2 * pad - KW) // stride + 1
+        k_real = KH * KW * Cin
+        k_pad = -(-k_real // 64) * 64
+        col = torch.empty(N * OH * OW, k_pad, dtype=torch.bfloat16, device=x.device)
+        C.im2col_nhwc(xh, col, KH, KW, stride, pad)
+        w2 = torch.zeros(Cout, k_pad, dtype=torch.bfloat16, device=x.device)
+        w2[:, :k_real] = wh.reshape(Cout, k_real)
+        out = K.gemm(col, w2, bias=bias)                       # [N*OH*OW, Cout] = NHWC output
+        ctx.save_for_backward(col)
+        ctx.geom = (Cout, KH, KW, Cin, k_real, bias is not None)
+        return out.view(N, OH, OW, Cout).permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import kernels as K
+        (col,) = ctx.saved_tensors
+        Cout, KH, KW, Cin, k_real, has_bias = ctx.geom
+        dy2 = _nhwc(dy).reshape(-1, Cout)
+        dw = db = None
+        if ctx.needs_input_grad[1]:
+            dwf = torch.zeros(Cout, col.shape[1], dtype=torch.float32, device=dy.device)
+            K.gemm(dy2, col, a_mn=True, b_mn=True, out=dwf, accumulate=True, split_k=148)
+            dw = dwf[:, :k_real].reshape(Cout, KH, KW, Cin).to(torch.bfloat16).permute(0, 3, 1, 2)
+        if has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(torch.bfloat16)
+        return None, dw, db, None, None
+
+
 def conv2d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, stride=1, padding=0, dilation=1,
            groups: int = 1) -> torch.Tensor:
+    if im2col_supported(x, weight, stride, padding, dilation, groups):
+        s = stride if isinstance(stride, int) else stride[0]
+        p = padding if isinstance(padding, int) else padding[0]
+        return Im2colConv2dFn.apply(x, weight, bias, s, p)
     if supported(x, weight, stride, padding, dilation, groups):
         s = stride if isinstance(stride, int) else stride[0]
         p = padding if isinstance(padding, int) else padding[0]

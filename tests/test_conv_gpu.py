@@ -57,5 +57,30 @@ def test_conv_module_and_resnet_block_use_native_kernels():
     assert _native.launch_count() - before >= 3 and x.grad is not None and conv.weight.grad is not None
     ref = F.conv2d(x.detach().float(), conv.weight.detach().float(), None, 1, 1)
     assert rel_err(y, ref) < 1e-2
-    stem = rnn.Conv2d(3, 64, 7, stride=2, padding=3).cuda().bfloat16()          # 3 input channels: library path
+    stem = rnn.Conv2d(3, 64, 7, stride=2, padding=3).cuda().bfloat16()          # 3 input channels: patch matrix + GEMM
     assert stem(torch.randn(2, 3, 32, 32, device="cuda").bfloat16()).shape == (2, 64, 16, 16)
+
+
+@pytest.mark.parametrize("N,Cin,H,W,Cout,k,s,p", [(4, 3, 64, 64, 64, 7, 2, 3), (2, 3, 33, 41, 32, 3, 1, 1), (3, 12, 20, 20, 64, 4, 1, 0)])
+def test_small_cin_conv_im2col_gemm(N, Cin, H, W, Cout, k, s, p):
+    """Stem convolutions: patch matrix + tcgen05 GEMM forward, weight and bias gradients against fp32."""
+    from rustorch_b200 import _native
+    from rustorch_b200.ops.conv import conv2d, im2col_supported
+    torch.manual_seed(1)
+    x = torch.randn(N, Cin, H, W, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    w0 = (torch.randn(Cout, Cin, k, k, device="cuda") * (2.0 / (Cin * k * k)) ** 0.5).bfloat16()
+    b0 = torch.randn(Cout, device="cuda").bfloat16()
+    assert im2col_supported(x, w0, s, p)
+    w, b = w0.clone().requires_grad_(True), b0.clone().requires_grad_(True)
+    before = _native.launch_count()
+    y = conv2d(x, w, b, s, p)
+    wr, br = w0.float().requires_grad_(True), b0.float().requires_grad_(True)
+    yr = F.conv2d(x.float(), wr, br, s, p)
+    assert y.shape == yr.shape and rel_err(y, yr) < 1e-2
+    g = torch.randn_like(yr)
+    y.backward(g.bfloat16())
+    yr.backward(g.bfloat16().float())
+    assert _native.launch_count() - before >= 3          # im2col, forward GEMM, weight-gradient GEMM
+    assert rel_err(w.grad, wr.grad) < 2e-2 and rel_err(b.grad, br.grad) < 2e-2
+    assert not im2col_supported(x.clone().requires_grad_(True), w0, s, p)       # an input gradient is not provided
+    _native.check_status()
