@@ -19,32 +19,36 @@ namespace rt {
 
 namespace {
 
+// A kernel row (fixed kh) of a patch is KW * C consecutive input values: x[n][ih][iw0 .. iw0 + KW - 1][0 .. C - 1] is
+// contiguous in a channels-last image, so a patch is KH shifted copies of KW * C elements each; (kh, j) below walk
+// them without a division per element.
 __global__ void __launch_bounds__(256) im2col_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ col, int N, int H,
                                                      int W, int C, int OH, int OW, int KH, int KW, int stride, int pad, int k_pad) {
   const int kv = k_pad / 8;
-  const int k_real = KH * KW * C;
+  const int row_len = KW * C, k_real = KH * row_len, wc = W * C;
   const long long total = (long long)N * OH * OW * kv;
+  const __nv_bfloat16 zero = __float2bfloat16(0.f);
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
-    const int k0 = (int)(t % kv) * 8;
-    long long p = t / kv;
-    const int ow = (int)(p % OW);
-    p /= OW;
-    const int oh = (int)(p % OH), n = (int)(p / OH);
-    const int h0 = oh * stride - pad, w0 = ow * stride - pad;
+    const long long pix = t / kv;
+    const int k0 = (int)(t - pix * kv) * 8;
+    const int ow = (int)(pix % OW);
+    const long long r = pix / OW;
+    const int oh = (int)(r % OH), n = (int)(r / OH);
+    const int h0 = oh * stride - pad, col0 = (ow * stride - pad) * C;       // first input row / first element of a kernel row
+    int kh = k0 / row_len, j = k0 - kh * row_len;
+    const __nv_bfloat16* img = x + (long long)n * H * wc;
     __align__(16) __nv_bfloat16 v[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      const int k = k0 + e;
-      float val = 0.f;
-      if (k < k_real) {
-        const int c = k % C, tap = k / C;
-        const int kw = tap % KW, kh = tap / KW;
-        const int ih = h0 + kh, iw = w0 + kw;
-        if (ih >= 0 && ih < H && iw >= 0 && iw < W) val = __bfloat162float(x[(((long long)n * H + ih) * W + iw) * C + c]);
+      const int ih = h0 + kh, src = col0 + j;
+      const bool ok = (k0 + e < k_real) && ih >= 0 && ih < H && src >= 0 && src < wc;
+      v[e] = ok ? img[(long long)ih * wc + src] : zero;
+      if (++j == row_len) {
+        j = 0;
+        ++kh;
       }
-      v[e] = __float2bfloat16(val);
     }
-    *reinterpret_cast<uint4*>(col + (t / kv) * k_pad + k0) = *reinterpret_cast<const uint4*>(v);
+    *reinterpret_cast<uint4*>(col + pix * k_pad + k0) = *reinterpret_cast<const uint4*>(v);
   }
 }
 
