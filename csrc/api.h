@@ -176,6 +176,10 @@ struct Conv2dArgs {
   const void* bias;  // bf16 [Cout] or null (forward)
   const void* dy;    // wgrad
   float* dw;         // wgrad: accumulated into (zero it first)
+  // forward only: explicit output extent and element strides of the output view (0 = derive / contiguous NHWC).
+  // Used by the strided input gradient, which writes every stride-th pixel of dx from a stride-1 convolution of dy.
+  int out_h = 0, out_w = 0;
+  long long out_sn = 0, out_sh = 0, out_sw = 0;
 };
 bool conv2d_igemm_supported(int Cin, int Cout, int KH, int KW, int stride);
 void conv2d_fwd(const Conv2dArgs& a, cudaStream_t stream);

@@ -375,6 +375,33 @@ void conv2d_fwd(const Tensor& x, const Tensor& w, Tensor& out, const c10::option
   rt::conv2d_fwd(a, cur_stream(x.device().index()));
 }
 
+// Stride-1 convolution of x [N,H,W,Cin] (zero outside the image, first tap at input offset -pad) whose out_h x out_w
+// results go to every step-th pixel of the contiguous NHWC tensor `out`, starting at pixel (off_h, off_w): one parity
+// class of a strided input gradient.
+void conv2d_fwd_scatter(const Tensor& x, const Tensor& w, Tensor& out, int64_t pad, int64_t out_h, int64_t out_w, int64_t step,
+                        int64_t off_h, int64_t off_w) {
+  check_bf16(x, "conv2d x");
+  check_bf16(w, "conv2d w");
+  check_bf16(out, "conv2d out");
+  TORCH_CHECK(x.dim() == 4 && w.dim() == 4 && out.dim() == 4 && x.is_contiguous() && w.is_contiguous() && out.is_contiguous(),
+              "conv2d: contiguous NHWC / OHWI tensors required");
+  rt::Conv2dArgs a{};
+  a.N = int(x.size(0)); a.H = int(x.size(1)); a.W = int(x.size(2)); a.Cin = int(x.size(3));
+  a.Cout = int(w.size(0)); a.KH = int(w.size(1)); a.KW = int(w.size(2));
+  TORCH_CHECK(w.size(3) == a.Cin && out.size(0) == a.N && out.size(3) == a.Cout, "conv2d_fwd_scatter: channel / batch mismatch");
+  TORCH_CHECK(pad >= 0 && step >= 1 && out_h >= 1 && out_w >= 1 && off_h >= 0 && off_w >= 0 &&
+                  off_h + (out_h - 1) * step < out.size(1) && off_w + (out_w - 1) * step < out.size(2),
+              "conv2d_fwd_scatter: the scattered results must lie inside the output tensor");
+  a.stride = 1; a.pad = int(pad);
+  a.out_h = int(out_h); a.out_w = int(out_w);
+  const int64_t H = out.size(1), W = out.size(2), C = out.size(3);
+  a.out_sn = H * W * C; a.out_sh = step * W * C; a.out_sw = step * C;
+  a.x = x.data_ptr(); a.w = w.data_ptr();
+  a.out = static_cast<at::BFloat16*>(out.data_ptr()) + (off_h * W + off_w) * C;
+  c10::cuda::CUDAGuard guard(x.device());
+  rt::conv2d_fwd(a, cur_stream(x.device().index()));
+}
+
 // dw [Cout,KH,KW,Cin] fp32 += dy^T (*) x
 void conv2d_wgrad(const Tensor& x, const Tensor& dy, Tensor& dw, int64_t stride, int64_t pad) {
   check_bf16(x, "conv2d_wgrad x");
@@ -751,6 +778,7 @@ void register_extra_ops(pybind11::module_& m) {
   m.def("amp_unscale", &amp_unscale, "grads *= inv_scale, found_inf = 1 on any non-finite value");
   m.def("csr_spmm", &csr_spmm, "CSR sparse x dense product (fp32)");
   m.def("ar_residual_norm", &ar_residual_norm, "all-reduce over peer memory + residual add + RMSNorm in one kernel");
+  m.def("conv2d_fwd_scatter", &conv2d_fwd_scatter, "stride-1 convolution written to every step-th output pixel");
   m.def("conv2d_fwd", &conv2d_fwd, "implicit-GEMM conv2d forward (channels-last bf16)");
   m.def("conv2d_wgrad", &conv2d_wgrad, "implicit-GEMM conv2d weight gradient (fp32 accumulate)");
   m.def("conv2d_igemm_supported", &rt::conv2d_igemm_supported);

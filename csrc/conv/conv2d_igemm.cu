@@ -17,6 +17,8 @@
 // The reference's convolution is nested host loops (src/nn/conv2d.rs:150-260) and an im2col CUDA-C string kernel
 // followed by SGEMM (K9-K12, src/gpu/conv_ops.rs:27-765).  Requirements here: Cin % 64 == 0 (forward / wgrad B
 // boxes are 64 channels wide), Cout % 8 == 0; other layers (the 3-channel stem) stay on the library path.
+#include <cstdlib>
+
 #include "../api.h"
 #include "../common/launch.h"
 #include "../common/ptx.cuh"
@@ -34,6 +36,7 @@ struct ConvParams {
   int m_tiles, n_blocks, k_chunks;            // k_chunks = Cin / 64
   __nv_bfloat16* out;
   const __nv_bfloat16* bias;
+  long long out_sn, out_sh, out_sw;  // element strides of the output view
   // wgrad
   float* dw;       // [Cout][KH*KW][Cin] fp32, accumulated into
   int split;       // CTAs per output tile along the pixel dimension
@@ -189,7 +192,7 @@ conv_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
       tc_fence_after();
       const int n = n0 + tn, oh = oh0 + th, ow = ow0 + tw;
       const bool row_ok = n < p.N && oh < p.OH && ow < p.OW;
-      __nv_bfloat16* orow = p.out + (((long long)n * p.OH + oh) * p.OW + ow) * p.Cout;
+      __nv_bfloat16* orow = p.out + n * p.out_sn + oh * p.out_sh + ow * p.out_sw;
 #pragma unroll 1
       for (int c = col_half * (BLOCK_N / 64); c < (col_half + 1) * (BLOCK_N / 64); ++c) {
         const int c0 = nb * BLOCK_N + c * 32;
@@ -375,6 +378,139 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_cons
   }
 }
 
+// Three-tap variant for KW == 3: one CTA owns 128 out-channels x 64 in-channels x the three taps of one kernel ROW.
+// The three input boxes (shifted by one pixel in W) sit side by side as three 64-column chunks of one MN-major B tile,
+// so one MMA of N = 192 serves them and the dy tile is fetched once per three taps instead of once per tap
+// (the kernel is bound by L2 -> shared-memory traffic, not by the tensor pipe).
+__global__ void __launch_bounds__(CV_THREADS, 1)
+conv_wgrad3_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_x, const ConvParams p) {
+  constexpr int BLOCK_N = 192;   // 3 taps x 64 in-channels
+  using S = ConvSmem<256>;       // A: [64 pixels][128 co] (16 KB); B: three [64 pixels][64 ci] chunks (24 of 32 KB)
+  constexpr int STAGES = S::STAGES;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, RT_ERR_BOUNDS);
+    return;
+  }
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_full + 4);
+  CtaCtl* ctl = reinterpret_cast<CtaCtl*>(tmem_base_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 256;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    ctl->abort = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_dy);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  // blockIdx.x = output tile (co block, kernel row, 64-channel ci block), blockIdx.y = pixel slice
+  const int ci_blocks = p.Cin / 64;
+  const int taps = p.KH * p.KW;
+  const int cib = blockIdx.x % ci_blocks;
+  const int kh = (blockIdx.x / ci_blocks) % p.KH;
+  const int cob = blockIdx.x / (ci_blocks * p.KH);
+  const int per = (p.m_tiles + p.split - 1) / p.split;
+  const int mt0 = blockIdx.y * per, mt1 = min(p.m_tiles, mt0 + per);
+  const int n_kb = max(0, mt1 - mt0);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int i = 0; i < n_kb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) {
+          ok = false;
+          break;
+        }
+        int n0, oh0, ow0;
+        cv_tile_origin(mt0 + i, p, n0, oh0, ow0);
+        uint8_t* sa = smem + s * S::STAGE_BYTES;
+        uint8_t* sb = sa + S::A_BYTES;
+        mbar_arrive_expect_tx(&full_bar[s], S::A_BYTES + BLOCK_N * 64 * 2);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) tma_load_4d(sa + c * 8192, &tmap_dy, &full_bar[s], cob * 128 + c * 64, ow0, oh0, n0);
+#pragma unroll
+        for (int kw = 0; kw < 3; ++kw)      // chunk kw of the B tile = the box of tap (kh, kw)
+          tma_load_4d(sb + kw * 8192, &tmap_x, &full_bar[s], cib * 64, ow0 * p.stride + kw - p.pad, oh0 * p.stride + kh - p.pad, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_kb > 0) {
+      constexpr uint32_t idesc = make_idesc_f16(128, BLOCK_N, true, true, true);
+      bool ok = true;
+      for (int i = 0; i < n_kb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait(&full_bar[s], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + s * S::STAGE_BYTES);
+        const uint32_t sb = sa + S::A_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < CV_BK / 16; ++kk)
+          umma_f16_ss(tmem_base, make_smem_desc_sw128(sa + kk * 2048, 8192, 1024), make_smem_desc_sw128(sb + kk * 2048, 8192, 1024),
+                      idesc, (i > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+      }
+      if (ok) umma_commit(tmem_full);
+    }
+  } else if (n_kb > 0) {
+    const int quarter = warp & 3, col_half = (warp - 2) >> 2;
+    const int co = cob * 128 + quarter * 32 + lane;
+    if (mbar_wait(tmem_full, 0, ctl, p.status, RT_ERR_TIMEOUT_EPILOGUE)) {
+      tc_fence_after();
+      constexpr int CHUNKS = BLOCK_N / 32;  // 6: two 32-column chunks per tap
+#pragma unroll 1
+      for (int c = col_half * (CHUNKS / 2); c < (col_half + 1) * (CHUNKS / 2); ++c) {
+        const int tap = kh * p.KW + (c >> 1);
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(tmem_base + c * 32 + (uint32_t(quarter * 32) << 16), v);
+        tmem_ld_wait();
+        const int ci0 = cib * 64 + (c & 1) * 32;
+        if (co < p.Cout && ci0 < p.Cin) {
+          float4* dst = reinterpret_cast<float4*>(p.dw + ((long long)co * taps + tap) * p.Cin + ci0);
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            atomicAdd(dst + q, make_float4(__uint_as_float(v[q * 4]), __uint_as_float(v[q * 4 + 1]), __uint_as_float(v[q * 4 + 2]),
+                                           __uint_as_float(v[q * 4 + 3])));
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncwarp();
+  if (ctl->abort) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 void pick_tile(int OH, int OW, int Nimg, int pixels, int& TW, int& TH, int& TN) {
   // widths of 8 or 16 output columns, whichever wastes fewer columns; then rows, then images
   const int w8 = (OW + 7) / 8 * 8, w16 = (OW + 15) / 16 * 16;
@@ -389,8 +525,11 @@ void pick_tile(int OH, int OW, int Nimg, int pixels, int& TW, int& TH, int& TN) 
 
 void fill_common(const Conv2dArgs& a, ConvParams& p, int pixels) {
   p.N = a.N; p.H = a.H; p.W = a.W; p.Cin = a.Cin; p.Cout = a.Cout; p.KH = a.KH; p.KW = a.KW; p.stride = a.stride; p.pad = a.pad;
-  p.OH = (a.H + 2 * a.pad - a.KH) / a.stride + 1;
-  p.OW = (a.W + 2 * a.pad - a.KW) / a.stride + 1;
+  p.OH = a.out_h > 0 ? a.out_h : (a.H + 2 * a.pad - a.KH) / a.stride + 1;
+  p.OW = a.out_w > 0 ? a.out_w : (a.W + 2 * a.pad - a.KW) / a.stride + 1;
+  p.out_sw = a.out_sw > 0 ? a.out_sw : a.Cout;
+  p.out_sh = a.out_sh > 0 ? a.out_sh : (long long)p.OW * a.Cout;
+  p.out_sn = a.out_sn > 0 ? a.out_sn : (long long)p.OH * p.OW * a.Cout;
   pick_tile(p.OH, p.OW, a.N, pixels, p.TW, p.TH, p.TN);
   p.tiles_w = (p.OW + p.TW - 1) / p.TW;
   p.tiles_h = (p.OH + p.TH - 1) / p.TH;
@@ -403,7 +542,8 @@ void check_conv(const Conv2dArgs& a) {
   RT_CHECK(a.Cin % 64 == 0, "conv2d_igemm: input channels must be a multiple of 64");
   RT_CHECK(a.Cout % 8 == 0, "conv2d_igemm: output channels must be a multiple of 8");
   RT_CHECK(a.stride >= 1 && a.stride <= 4 && a.pad >= 0 && a.KH >= 1 && a.KW >= 1 && a.KH <= 7 && a.KW <= 7, "conv2d_igemm: unsupported geometry");
-  RT_CHECK(a.N > 0 && a.H + 2 * a.pad >= a.KH && a.W + 2 * a.pad >= a.KW, "conv2d_igemm: empty output");
+  RT_CHECK(a.N > 0 && (a.out_h > 0 || (a.H + 2 * a.pad >= a.KH && a.W + 2 * a.pad >= a.KW)), "conv2d_igemm: empty output");
+  RT_CHECK(a.out_sw % 8 == 0 && a.out_sh % 8 == 0 && a.out_sn % 8 == 0, "conv2d_igemm: output strides must keep 16-byte alignment");
 }
 
 template <int BLOCK_N>
@@ -441,6 +581,22 @@ void launch_wgrad(const Conv2dArgs& a, ConvParams& p, int device, cudaStream_t s
   RT_LAUNCH_CHECK();
 }
 
+void launch_wgrad3(const Conv2dArgs& a, ConvParams& p, int device, cudaStream_t stream) {
+  using S = ConvSmem<256>;
+  static bool configured[64] = {false};
+  if (!configured[device & 63]) {
+    RT_CUDA_CHECK(cudaFuncSetAttribute(conv_wgrad3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    configured[device & 63] = true;
+  }
+  const int out_tiles = ((a.Cout + 127) / 128) * a.KH * (a.Cin / 64);
+  const int sms = sm_count(device);
+  p.split = std::max(1, std::min(p.m_tiles, (2 * sms + out_tiles - 1) / out_tiles));
+  const CUtensorMap tdy = make_tmap_nhwc(a.dy, a.Cout, p.OW, p.OH, a.N, p.TW, p.TH, p.TN, 1);
+  const CUtensorMap tx = make_tmap_nhwc(a.x, a.Cin, a.W, a.H, a.N, p.TW, p.TH, p.TN, a.stride);
+  conv_wgrad3_kernel<<<dim3(out_tiles, p.split), CV_THREADS, S::TOTAL, stream>>>(tdy, tx, p);
+  RT_LAUNCH_CHECK();
+}
+
 }  // namespace
 
 bool conv2d_igemm_supported(int Cin, int Cout, int KH, int KW, int stride) {
@@ -468,7 +624,12 @@ void conv2d_wgrad(const Conv2dArgs& a, cudaStream_t stream) {
   fill_common(a, p, 64);
   p.dw = a.dw;
   p.status = status_word(device);
-  if (a.Cin % 128 == 0) launch_wgrad<128>(a, p, device, stream);
+  static const bool three_tap = [] {
+    const char* e = std::getenv("RUSTORCH_CONV_WGRAD3");
+    return !(e && e[0] == '0');
+  }();
+  if (a.KW == 3 && three_tap) launch_wgrad3(a, p, device, stream);      // one dy fetch per kernel row
+  else if (a.Cin % 128 == 0) launch_wgrad<128>(a, p, device, stream);
   else launch_wgrad<64>(a, p, device, stream);
 }
 

@@ -110,7 +110,8 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     want = "\n".join(sorted(keep))
     if force or jobs or not TARGET.exists() or not stamp.exists() or stamp.read_text() != want:
         lib_dirs = ce.library_paths()
-        link = ["g++", "-shared", "-o", str(TARGET), *map(str, objs)]
+        tmp = TARGET.with_suffix(".so.tmp")       # link beside the target, then rename: readers never see a partial file
+        link = ["g++", "-shared", "-o", str(tmp), *map(str, objs)]
         for d in lib_dirs:
             link += [f"-L{d}", f"-Wl,-rpath,{d}"]
         link += [f"-L{_cuda_home()}/lib64", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda",
@@ -118,6 +119,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         if verbose:
             print("[build] link", TARGET.name, flush=True)
         _run(link)
+        os.replace(tmp, TARGET)
         stamp.write_text(want)
     build_host(verbose, force)
     return TARGET

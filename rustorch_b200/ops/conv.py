@@ -36,6 +36,46 @@ def _nhwc(t: torch.Tensor) -> torch.Tensor:
     return t.permute(0, 2, 3, 1).contiguous()
 
 
+def _strided_dgrad(C, dyh: torch.Tensor, wh: torch.Tensor, xshape, stride: int, pad: int) -> Optional[torch.Tensor]:
+    """Input gradient of a strided convolution as ``stride^2`` stride-1 convolutions of ``dy``, one per parity class
+    of the input pixels: class ``(ph, pw)`` only receives the taps with ``kh = ph + pad (mod stride)`` (same for kw),
+    and its pixels form a dense grid, so the forward kernel computes it with a sub-filter and scatters the results to
+    every ``stride``-th pixel of ``dx``.  Classes without taps (1x1 kernels) stay zero.  ``None``: geometry not covered."""
+    N, H, W, Cin = xshape
+    Cout, KH, KW, _ = wh.shape
+
+    def taps(ph: int, K: int):
+        ks = [k for k in range(K) if (ph + pad - k) % stride == 0]
+        offs = [(ph + pad - k) // stride for k in ks]            # dy index = y + off, descending k -> ascending off
+        return ks[::-1], offs[::-1]
+
+    plans = []
+    for ph in range(stride):
+        khs, offh = taps(ph, KH)
+        for pw in range(stride):
+            kws, offw = taps(pw, KW)
+            rows, cols = -(-(H - ph) // stride), -(-(W - pw) // stride)
+            if rows <= 0 or cols <= 0 or not khs or not kws:
+                plans.append(None)
+                continue
+            # a stride-1 correlation needs consecutive offsets starting at -pad' with pad' >= 0, the same for h and w
+            if offh != list(range(offh[0], offh[0] + len(offh))) or offw != list(range(offw[0], offw[0] + len(offw))):
+                return None
+            if offh[0] > 0 or offw[0] > 0 or offh[0] != offw[0]:
+                return None
+            plans.append((ph, pw, khs, kws, -offh[0], rows, cols))
+    full = all(pl is not None for pl in plans)
+    dx = (torch.empty if full else torch.zeros)((N, H, W, Cin), dtype=torch.bfloat16, device=dyh.device)
+    for pl in plans:
+        if pl is None:
+            continue
+        ph, pw, khs, kws, p2, rows, cols = pl
+        # sub-filter [Cin][n_h][n_w][Cout]: the contraction runs over the layer's output channels
+        sub = wh[:, khs][:, :, kws].permute(3, 1, 2, 0).contiguous()
+        C.conv2d_fwd_scatter(dyh, sub, dx, p2, rows, cols, stride, ph, pw)
+    return dx
+
+
 class Conv2dFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, stride: int, pad: int):
@@ -70,7 +110,9 @@ class Conv2dFn(torch.autograd.Function):
                 C.conv2d_fwd(dyh, wr, dxh, None, 1, KH - 1 - pad)
                 dx = dxh.permute(0, 3, 1, 2)
             else:
-                dx = torch.nn.grad.conv2d_input(xshape, wh.permute(0, 3, 1, 2), dy, stride, pad)
+                dxh = _strided_dgrad(C, dyh, wh, xh.shape, stride, pad)
+                dx = dxh.permute(0, 3, 1, 2) if dxh is not None else \
+                    torch.nn.grad.conv2d_input(xshape, wh.permute(0, 3, 1, 2), dy, stride, pad)
         if has_bias and ctx.needs_input_grad[2]:
             db = dyh.float().sum((0, 1, 2)).to(torch.bfloat16)
         return dx, dw, db, None, None
