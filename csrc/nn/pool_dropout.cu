@@ -109,11 +109,21 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const T* __restrict__ dy,
   const long long total = (long long)a.N * a.H * a.W * cv;
   const float inv = 1.f / (float)(a.kh * a.kw);
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
-    const int c = (int)(t % cv) * V;
-    long long pix = t / cv;
-    const int iw = (int)(pix % a.W);
-    pix /= a.W;
-    const int ih = (int)(pix % a.H), n = (int)(pix / a.H);
+    int c, iw, ih, n;
+    if (total < 0x7fffffffLL) {                      // 32-bit divisions (an order of magnitude cheaper than 64-bit ones)
+      const unsigned tt = (unsigned)t, pix = tt / (unsigned)cv, row = pix / (unsigned)a.W;
+      c = (int)(tt - pix * cv) * V;
+      iw = (int)(pix - row * a.W);
+      n = (int)(row / (unsigned)a.H);
+      ih = (int)(row - (unsigned)n * a.H);
+    } else {
+      c = (int)(t % cv) * V;
+      long long pix = t / cv;
+      iw = (int)(pix % a.W);
+      pix /= a.W;
+      ih = (int)(pix % a.H);
+      n = (int)(pix / a.H);
+    }
     float acc[V];
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = 0.f;
