@@ -7,6 +7,7 @@
 #include <string>
 
 #include "arena.h"
+#include "cpu_optim.h"
 #include "plan.h"
 
 namespace py = pybind11;
@@ -52,6 +53,20 @@ uint64_t crc64(py::bytes data, uint64_t crc) {
 PYBIND11_MODULE(_host, m) {
   m.doc() = "host-side native runtime (no CUDA, no torch)";
   m.def("crc64", &crc64, py::arg("data"), py::arg("crc") = 0);
+  // optimizer updates on host buffers given by address (torch tensors' data_ptr(); the module itself is torch-free)
+  m.def("cpu_adam_family_step",
+        [](int kind, uintptr_t p, uintptr_t g, uintptr_t mm, uintptr_t v, int64_t n, double lr, double b1, double b2, double eps,
+           double wd, int64_t step, double momentum_decay, double mu_product) {
+          rt::cpu_adam_family_step(kind, reinterpret_cast<float*>(p), reinterpret_cast<const float*>(g), reinterpret_cast<float*>(mm),
+                                   reinterpret_cast<float*>(v), n, lr, b1, b2, eps, wd, step, momentum_decay, &mu_product);
+          return mu_product;
+        });
+  m.def("cpu_lbfgs_step", [](uintptr_t p, uintptr_t g, uintptr_t pp, uintptr_t pg, uintptr_t S, uintptr_t Y, uintptr_t rho,
+                             uintptr_t scratch, int64_t n, int64_t hist, int64_t count, int64_t head, int64_t has_prev, double lr) {
+    return rt::cpu_lbfgs_step(reinterpret_cast<float*>(p), reinterpret_cast<const float*>(g), reinterpret_cast<float*>(pp),
+                              reinterpret_cast<float*>(pg), reinterpret_cast<float*>(S), reinterpret_cast<float*>(Y),
+                              reinterpret_cast<float*>(rho), reinterpret_cast<float*>(scratch), n, hist, count, head, has_prev, lr);
+  });
 
   py::class_<rt::Arena>(m, "Arena")
       .def(py::init<uint64_t, uint64_t>(), py::arg("capacity"), py::arg("alignment") = 256)

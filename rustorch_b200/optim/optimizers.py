@@ -29,9 +29,41 @@ class _RefAPI:
 
     set_lr = set_learning_rate
 
+    _NATIVE_KIND: Optional[int] = None      # Adam 0, AdamW 1, Adamax 2, NAdam 3, RAdam 4 (csrc/runtime/cpu_optim.cpp)
+
+    def _native_step(self, param: torch.Tensor, grad: torch.Tensor) -> bool:
+        """Host fast path of ``step_tensor``: fp32 CPU tensors are updated by the native runtime from their addresses.
+        On a 1000-element parameter the interpreter, not the arithmetic, bounds the step rate; this path keeps its own
+        per-tensor state (moments, step count) and uses the same formulas as the torch path."""
+        k = self._NATIVE_KIND
+        if (k is None or param.device.type != "cpu" or param.dtype != torch.float32 or grad.dtype != torch.float32
+                or not param.is_contiguous() or not grad.is_contiguous() or grad.device.type != "cpu"):
+            return False
+        g = self.param_groups[0]
+        flags = ("amsgrad", "maximize", "capturable", "differentiable") + (() if k == 1 else ("decoupled_weight_decay",))
+        if any(g.get(f) for f in flags):
+            return False
+        fs = self.__dict__.setdefault("_fast_state", {})
+        st = fs.get(id(param))
+        if st is None:
+            if any(param is q for q in self.state):     # already stepped through torch's own state: stay on that path
+                return False
+            from .. import _native
+            st = {"m": torch.zeros_like(param), "v": torch.zeros_like(param), "step": 0, "mu": 1.0, "host": _native.host(), "ref": param}
+            st["ptrs"] = (param.data_ptr(), st["m"].data_ptr(), st["v"].data_ptr())
+            fs[id(param)] = st
+        st["step"] += 1
+        b1, b2 = g["betas"]
+        pp, pm, pv = st["ptrs"]
+        st["mu"] = st["host"].cpu_adam_family_step(k, pp, grad.data_ptr(), pm, pv, param.numel(), g["lr"], b1, b2, g["eps"],
+                                                   g["weight_decay"], st["step"], g.get("momentum_decay", 0.0), st["mu"])
+        return True
+
     @torch.no_grad()
     def step_tensor(self, param: torch.Tensor, grad: torch.Tensor) -> None:
-        """Update one tensor in place from an explicit gradient."""
+        """Update one tensor in place from an explicit gradient (the reference's ``step(&param, &grad)``)."""
+        if self._native_step(param, grad):
+            return
         known = any(param is p for g in self.param_groups for p in g["params"])
         if not known:
             self.add_param_group({"params": [param]})
@@ -42,6 +74,19 @@ class _RefAPI:
         self.step()
         for p, g in saved:
             p.grad = g
+
+    def _publish_fast_state(self) -> None:
+        """Copy the host fast path's per-tensor state into ``self.state`` under torch's key names."""
+        for st in self.__dict__.get("_fast_state", {}).values():
+            if "m" not in st:
+                continue
+            p = st["ref"]
+            if not any(p is q for g in self.param_groups for q in g["params"]):
+                self.add_param_group({"params": [p]})
+            second = "exp_inf" if self._NATIVE_KIND == 2 else "exp_avg_sq"
+            self.state[p] = {"step": torch.tensor(float(st["step"])), "exp_avg": st["m"], second: st["v"]}
+            if self._NATIVE_KIND == 3:
+                self.state[p]["mu_product"] = torch.tensor(st["mu"])
 
     def hyper_state(self) -> dict:
         """Hyper-parameters only, like the reference's ``state_dict() -> HashMap<String, f32>``."""
@@ -233,3 +278,40 @@ class LBFGS(torch.optim.LBFGS, _RefAPI):
         super().__init__(_params(params), lr=lr, max_iter=max_iter, max_eval=max_eval,
                          tolerance_grad=tolerance_grad, tolerance_change=tolerance_change,
                          history_size=history_size, line_search_fn=line_search_fn)
+
+    @torch.no_grad()
+    def step_tensor(self, param: torch.Tensor, grad: torch.Tensor) -> None:
+        """One L-BFGS iteration from an explicit gradient, as the reference's ``step(&param, &grad)`` does: two-loop
+        direction over the stored (s, y) pairs, ``param += lr * d``.  fp32 CPU tensors run in the native runtime."""
+        if (param.device.type != "cpu" or param.dtype != torch.float32 or not param.is_contiguous() or grad.dtype != torch.float32
+                or not grad.is_contiguous()):
+            from ..compat import LBFGSMemory
+            st = self.__dict__.setdefault("_mem", {}).setdefault(id(param), {"mem": LBFGSMemory(self.param_groups[0]["history_size"])})
+            if "p" in st:
+                st["mem"].update(param - st["p"], grad - st["g"])
+            st["p"], st["g"] = param.clone(), grad.clone()
+            param.add_(st["mem"].direction(grad), alpha=self.param_groups[0]["lr"])
+            return
+        fs = self.__dict__.setdefault("_fast_state", {})
+        st = fs.get(id(param))
+        n, hist = param.numel(), int(self.param_groups[0]["history_size"])
+        if st is None:
+            from .. import _native
+            z = lambda *shape: torch.zeros(*shape, dtype=torch.float32)  # noqa: E731
+            st = {"pp": z(n), "pg": z(n), "S": z(hist, n), "Y": z(hist, n), "rho": z(hist), "scratch": z(n + hist), "count": 0, "head": 0,
+                  "has_prev": 0, "host": _native.host(), "ref": param}
+            fs[id(param)] = st
+        packed = st["host"].cpu_lbfgs_step(param.data_ptr(), grad.data_ptr(), st["pp"].data_ptr(), st["pg"].data_ptr(), st["S"].data_ptr(),
+                                           st["Y"].data_ptr(), st["rho"].data_ptr(), st["scratch"].data_ptr(), n, hist, st["count"],
+                                           st["head"], st["has_prev"], float(self.param_groups[0]["lr"]))
+        st["count"], st["head"], st["has_prev"] = packed >> 16, packed & 0xFFFF, 1
+
+
+def _state_dict_with_fast(self):
+    self._publish_fast_state()
+    return torch.optim.Optimizer.state_dict(self)
+
+
+for _k, _cls in enumerate((Adam, AdamW, Adamax, NAdam, RAdam)):
+    _cls._NATIVE_KIND = _k
+    _cls.state_dict = _state_dict_with_fast
