@@ -164,6 +164,25 @@ def bench_ce(a):
     report(f"cross_entropy_{rows}x{V}", best, med, bytes_=4.0 * rows * ld)
 
 
+def bench_bn(a):
+    """BatchNorm2d (+ ReLU) training forward and backward at the ResNet-18 activation shapes, batch 256, channels-last
+    bf16.  Bytes: forward reads x twice and writes y; backward reads x, dy and y twice and writes dx."""
+    from rustorch_b200.ops.batchnorm import batch_norm
+    for (C, H) in [(64, 112), (64, 56), (128, 28), (256, 14), (512, 7)]:
+        x = bf(256, C, H, H).contiguous(memory_format=torch.channels_last).requires_grad_(True)
+        w = torch.ones(C, device="cuda", requires_grad=True)
+        b = torch.zeros(C, device="cuda", requires_grad=True)
+        rm, rv = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda")
+        dy = torch.randn_like(x)
+        nbytes = 2.0 * x.numel()
+        best, med = time_op(lambda: batch_norm(x, rm, rv, w, b, True, 0.1, 1e-5, None, True), a.iters)
+        report(f"bn_relu_fwd_256x{C}x{H}x{H}", best, med, bytes_=3.0 * nbytes)
+        y = batch_norm(x, rm, rv, w, b, True, 0.1, 1e-5, None, True)
+        best, med = time_op(lambda: torch.autograd.grad(y, (x, w, b), dy, retain_graph=True), a.iters)
+        report(f"bn_relu_bwd_256x{C}x{H}x{H}", best, med, bytes_=7.0 * nbytes)
+        del x, y, dy
+
+
 def bench_qgemv(a):
     """Q4_0 dequant-fused GEMV at the llama-7B decode shapes, register-fed vs bulk-copy-fed kernel.  Each timed
     region walks enough distinct weight matrices (> 300 MB) that none of them is served from L2."""
@@ -285,6 +304,8 @@ def main():
         bench_norm(a)
     elif a.op == "adamw":
         bench_adamw(a)
+    elif a.op == "bn":
+        bench_bn(a)
     elif a.op == "ce":
         bench_ce(a)
     elif a.op == "qgemv":

@@ -50,7 +50,9 @@ __device__ __forceinline__ void stv(T* p, const float (&f)[VecN<T>::N]) {
   *reinterpret_cast<uint4*>(p) = raw;
 }
 
-// CTA shape: blockDim.x = channel groups handled side by side (cg), blockDim.y = row lanes.
+// CTA shape for every kernel here: blockDim.x = channel groups handled side by side (a power of two <= 32),
+// blockDim.y = row lanes.  A thread keeps one channel group for its whole life, so the per-channel constants sit
+// in registers, and it walks rows r = first + k * row_step with U independent 16-byte loads in flight.
 // Two accumulators per channel (A, B): forward (x, x^2); backward (dy, dy * xhat).
 template <typename T, bool BWD>
 __global__ void __launch_bounds__(512) bn_reduce_kernel(const T* __restrict__ x, const T* __restrict__ dy,
@@ -58,11 +60,13 @@ __global__ void __launch_bounds__(512) bn_reduce_kernel(const T* __restrict__ x,
                                                         const float* __restrict__ rstd, float* __restrict__ out,
                                                         long long M, int C, long long rows_per_cta) {
   constexpr int V = VecN<T>::N;
+  constexpr int U = BWD ? 2 : 4;
   extern __shared__ float sm[];  // [2][blockDim.y][blockDim.x * V]
   const int cgroups = C / V;
   const int cg = blockIdx.x * blockDim.x + threadIdx.x;
   const long long r0 = (long long)blockIdx.y * rows_per_cta;
   const long long r1 = min(M, r0 + rows_per_cta);
+  const long long step = blockDim.y;
   float a[V], b[V];
 #pragma unroll
   for (int i = 0; i < V; ++i) a[i] = b[i] = 0.f;
@@ -75,9 +79,7 @@ __global__ void __launch_bounds__(512) bn_reduce_kernel(const T* __restrict__ x,
         rs[i] = rstd[cg * V + i];
       }
     }
-    for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
-      float xv[V];
-      ldv(x + r * C + cg * V, xv);
+    auto accumulate = [&](const float (&xv)[V], float (&g)[V], const float (&yv)[V], bool masked) {
       if (!BWD) {
 #pragma unroll
         for (int i = 0; i < V; ++i) {
@@ -85,20 +87,39 @@ __global__ void __launch_bounds__(512) bn_reduce_kernel(const T* __restrict__ x,
           b[i] = fmaf(xv[i], xv[i], b[i]);
         }
       } else {
-        float g[V];
-        ldv(dy + r * C + cg * V, g);
-        if (y_relu) {
-          float yv[V];
-          ldv(y_relu + r * C + cg * V, yv);
-#pragma unroll
-          for (int i = 0; i < V; ++i) g[i] = yv[i] > 0.f ? g[i] : 0.f;
-        }
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-          a[i] += g[i];
-          b[i] = fmaf(g[i], (xv[i] - mu[i]) * rs[i], b[i]);
+          const float gi = (masked && !(yv[i] > 0.f)) ? 0.f : g[i];
+          a[i] += gi;
+          b[i] = fmaf(gi, (xv[i] - mu[i]) * rs[i], b[i]);
         }
       }
+    };
+    const size_t col = (size_t)cg * V;
+    long long r = r0 + threadIdx.y;
+    for (; r + (U - 1) * step < r1; r += U * step) {
+      float xv[U][V], g[U][V], yv[U][V];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t off = (size_t)(r + u * step) * C + col;
+        ldv(x + off, xv[u]);
+        if (BWD) {
+          ldv(dy + off, g[u]);
+          if (y_relu) ldv(y_relu + off, yv[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) accumulate(xv[u], g[u], yv[u], y_relu != nullptr);
+    }
+    for (; r < r1; r += step) {
+      float xv[V], g[V], yv[V];
+      const size_t off = (size_t)r * C + col;
+      ldv(x + off, xv);
+      if (BWD) {
+        ldv(dy + off, g);
+        if (y_relu) ldv(y_relu + off, yv);
+      }
+      accumulate(xv, g, yv, y_relu != nullptr);
     }
   }
   const int W = blockDim.x * V;
@@ -123,6 +144,7 @@ __global__ void __launch_bounds__(512) bn_reduce_kernel(const T* __restrict__ x,
 }
 
 // Forward apply.  stats = [2][C] sums from bn_reduce (training) or null (inference: uses running stats).
+// y = x * scale + shift per channel (+ residual, ReLU); the CTAs of grid row 0 write the saved and running statistics.
 template <typename T>
 __global__ void __launch_bounds__(256) bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ residual, T* __restrict__ y,
                                                        const float* __restrict__ stats, const float* __restrict__ gamma,
@@ -131,48 +153,29 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(const T* __restrict__ x, 
                                                        float* __restrict__ save_rstd, long long M, int C, float eps,
                                                        float momentum, int relu, int training) {
   constexpr int V = VecN<T>::N;
-  const int cgroups = C / V;
+  constexpr int U = 4;
+  const int cg = blockIdx.x * blockDim.x + threadIdx.x;
+  if (cg >= C / V) return;
   const float invM = 1.f / (float)M;
-  const long long total = M * cgroups;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int cg = (int)(i % cgroups);
-    float xv[V], o[V];
-    ldv(x + i * V, xv);
+  float scale[V], shift[V];
+  const bool writer = training && blockIdx.y == 0 && threadIdx.y == 0;
 #pragma unroll
-    for (int e = 0; e < V; ++e) {
-      const int c = cg * V + e;
-      float mu, var;
-      if (training) {
-        mu = stats[c] * invM;
-        var = fmaxf(stats[C + c] * invM - mu * mu, 0.f);
-      } else {
-        mu = running_mean[c];
-        var = running_var[c];
-      }
-      const float rs = rsqrtf(var + eps);
-      const float g = gamma ? gamma[c] : 1.f, bb = beta ? beta[c] : 0.f;
-      o[e] = (xv[e] - mu) * rs * g + bb;
+  for (int e = 0; e < V; ++e) {
+    const int c = cg * V + e;
+    float mu, var;
+    if (training) {
+      mu = stats[c] * invM;
+      var = fmaxf(stats[C + c] * invM - mu * mu, 0.f);
+    } else {
+      mu = running_mean[c];
+      var = running_var[c];
     }
-    if (residual) {
-      float rv[V];
-      ldv(residual + i * V, rv);
-#pragma unroll
-      for (int e = 0; e < V; ++e) o[e] += rv[e];
-    }
-    if (relu) {
-#pragma unroll
-      for (int e = 0; e < V; ++e) o[e] = fmaxf(o[e], 0.f);
-    }
-    stv(y + i * V, o);
-  }
-  // per-channel outputs: saved statistics for backward and the running averages
-  if (training && blockIdx.x == 0) {
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-      const float mu = stats[c] * invM;
-      const float var = fmaxf(stats[C + c] * invM - mu * mu, 0.f);
+    const float rs = rsqrtf(var + eps);
+    scale[e] = rs * (gamma ? gamma[c] : 1.f);
+    shift[e] = (beta ? beta[c] : 0.f) - mu * scale[e];
+    if (writer) {
       if (save_mean) save_mean[c] = mu;
-      if (save_rstd) save_rstd[c] = rsqrtf(var + eps);
+      if (save_rstd) save_rstd[c] = rs;
       if (running_mean) running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * mu;
       if (running_var) {
         const float unbiased = M > 1 ? var * (float)M / (float)(M - 1) : var;
@@ -180,9 +183,43 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(const T* __restrict__ x, 
       }
     }
   }
+  const size_t col = (size_t)cg * V;
+  const long long step = (long long)gridDim.y * blockDim.y;
+  auto finish = [&](float (&o)[V], const float (&rv)[V]) {
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      o[e] = fmaf(o[e], scale[e], shift[e]);
+      if (residual) o[e] += rv[e];
+      if (relu) o[e] = fmaxf(o[e], 0.f);
+    }
+  };
+  long long r = (long long)blockIdx.y * blockDim.y + threadIdx.y;
+  for (; r + (U - 1) * step < M; r += U * step) {
+    float o[U][V], rv[U][V];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t off = (size_t)(r + u * step) * C + col;
+      ldv(x + off, o[u]);
+      if (residual) ldv(residual + off, rv[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      finish(o[u], rv[u]);
+      stv(y + (size_t)(r + u * step) * C + col, o[u]);
+    }
+  }
+  for (; r < M; r += step) {
+    float o[V], rv[V];
+    const size_t off = (size_t)r * C + col;
+    ldv(x + off, o);
+    if (residual) ldv(residual + off, rv);
+    finish(o, rv);
+    stv(y + off, o);
+  }
 }
 
-// dx (and the residual branch gradient = masked dy) from the per-channel sums in `sums` = [2][C].
+// dx (and the residual branch gradient = masked dy) from the per-channel sums in `sums` = [2][C]:
+// dx = ka * dy + kb * x + kc with ka = gamma * rstd, kb = -ka * rstd * sum(dy xhat) / M, kc = -ka * sum(dy) / M - kb * mean.
 template <typename T>
 __global__ void __launch_bounds__(256) bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ dy,
                                                            const T* __restrict__ y_relu, T* __restrict__ dx,
@@ -190,60 +227,86 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_kernel(const T* __restrict__
                                                            const float* __restrict__ mean, const float* __restrict__ rstd,
                                                            const float* __restrict__ gamma, long long M, int C) {
   constexpr int V = VecN<T>::N;
-  const int cgroups = C / V;
+  constexpr int U = 2;
+  const int cg = blockIdx.x * blockDim.x + threadIdx.x;
+  if (cg >= C / V) return;
   const float invM = 1.f / (float)M;
-  const long long total = M * cgroups;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int cg = (int)(i % cgroups);
-    float xv[V], g[V], o[V];
-    ldv(x + i * V, xv);
-    ldv(dy + i * V, g);
-    if (y_relu) {
-      float yv[V];
-      ldv(y_relu + i * V, yv);
+  float ka[V], kb[V], kc[V];
 #pragma unroll
-      for (int e = 0; e < V; ++e) g[e] = yv[e] > 0.f ? g[e] : 0.f;
-    }
+  for (int e = 0; e < V; ++e) {
+    const int c = cg * V + e;
+    ka[e] = (gamma ? gamma[c] : 1.f) * rstd[c];
+    kb[e] = -ka[e] * rstd[c] * sums[C + c] * invM;
+    kc[e] = -ka[e] * sums[c] * invM - kb[e] * mean[c];
+  }
+  const size_t col = (size_t)cg * V;
+  const long long step = (long long)gridDim.y * blockDim.y;
+  auto finish = [&](const float (&xv)[V], float (&g)[V], const float (&yv)[V], float (&o)[V]) {
 #pragma unroll
     for (int e = 0; e < V; ++e) {
-      const int c = cg * V + e;
-      const float xhat = (xv[e] - mean[c]) * rstd[c];
-      const float gm = gamma ? gamma[c] : 1.f;
-      o[e] = gm * rstd[c] * (g[e] - sums[c] * invM - xhat * sums[C + c] * invM);
+      if (y_relu && !(yv[e] > 0.f)) g[e] = 0.f;
+      o[e] = fmaf(ka[e], g[e], fmaf(kb[e], xv[e], kc[e]));
     }
-    stv(dx + i * V, o);
-    if (dres) stv(dres + i * V, g);
+  };
+  long long r = (long long)blockIdx.y * blockDim.y + threadIdx.y;
+  for (; r + (U - 1) * step < M; r += U * step) {
+    float xv[U][V], g[U][V], yv[U][V], o[U][V];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t off = (size_t)(r + u * step) * C + col;
+      ldv(x + off, xv[u]);
+      ldv(dy + off, g[u]);
+      if (y_relu) ldv(y_relu + off, yv[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t off = (size_t)(r + u * step) * C + col;
+      finish(xv[u], g[u], yv[u], o[u]);
+      stv(dx + off, o[u]);
+      if (dres) stv(dres + off, g[u]);
+    }
   }
+  for (; r < M; r += step) {
+    float xv[V], g[V], yv[V], o[V];
+    const size_t off = (size_t)r * C + col;
+    ldv(x + off, xv);
+    ldv(dy + off, g);
+    if (y_relu) ldv(y_relu + off, yv);
+    finish(xv, g, yv, o);
+    stv(dx + off, o);
+    if (dres) stv(dres + off, g);
+  }
+}
+
+// Channel groups side by side (a power of two <= 32) and the CTA grid for `threads` threads per CTA.
+struct BnShape {
+  dim3 grid, block;
+};
+BnShape bn_shape(long long M, int cgroups, int threads, int unroll, int ctas_per_sm) {
+  int bx = 1;
+  while (bx < cgroups && bx < 32) bx <<= 1;
+  const int by = threads / bx;
+  const int gx = (cgroups + bx - 1) / bx;
+  const long long want = ((long long)sm_count(current_device()) * ctas_per_sm + gx - 1) / gx;
+  const long long gy = std::max<long long>(1, std::min<long long>((M + (long long)by * unroll - 1) / ((long long)by * unroll), want));
+  return {dim3(gx, (unsigned)gy), dim3(bx, by)};
 }
 
 template <typename T>
 void launch_reduce(const BatchNormArgs& a, bool bwd, float* out, cudaStream_t s) {
   constexpr int V = VecN<T>::N;
-  const int cgroups = a.C / V;
-  int bx = 1;
-  while (bx < cgroups && bx < 32) bx <<= 1;  // channel groups side by side (<= 32)
-  const int by = 512 / bx;                   // row lanes
-  const int gx = (cgroups + bx - 1) / bx;
-  const int sms = sm_count(current_device());
-  long long gy = std::max<long long>(1, std::min<long long>((a.M + by * 4 - 1) / (by * 4), (4LL * sms + gx - 1) / gx));
-  const long long rows_per_cta = (a.M + gy - 1) / gy;
-  gy = (a.M + rows_per_cta - 1) / rows_per_cta;
-  const size_t smem = sizeof(float) * 2 * by * bx * V;
-  const dim3 grid(gx, (unsigned)gy), block(bx, by);
+  BnShape sh = bn_shape(a.M, a.C / V, 512, 4, 4);
+  const long long rows_per_cta = (a.M + sh.grid.y - 1) / sh.grid.y;
+  sh.grid.y = (unsigned)((a.M + rows_per_cta - 1) / rows_per_cta);
+  const size_t smem = sizeof(float) * 2 * sh.block.y * sh.block.x * V;
   auto px = reinterpret_cast<const T*>(a.x);
   if (bwd)
-    bn_reduce_kernel<T, true><<<grid, block, smem, s>>>(px, reinterpret_cast<const T*>(a.dy),
-                                                        reinterpret_cast<const T*>(a.y_relu), a.save_mean, a.save_rstd, out,
-                                                        a.M, a.C, rows_per_cta);
+    bn_reduce_kernel<T, true><<<sh.grid, sh.block, smem, s>>>(px, reinterpret_cast<const T*>(a.dy),
+                                                              reinterpret_cast<const T*>(a.y_relu), a.save_mean, a.save_rstd, out,
+                                                              a.M, a.C, rows_per_cta);
   else
-    bn_reduce_kernel<T, false><<<grid, block, smem, s>>>(px, nullptr, nullptr, nullptr, nullptr, out, a.M, a.C, rows_per_cta);
+    bn_reduce_kernel<T, false><<<sh.grid, sh.block, smem, s>>>(px, nullptr, nullptr, nullptr, nullptr, out, a.M, a.C, rows_per_cta);
   RT_LAUNCH_CHECK();
-}
-
-unsigned apply_grid(long long total) {
-  const long long cap = (long long)sm_count(current_device()) * 8;
-  return (unsigned)std::max<long long>(1, std::min((total + 255) / 256, cap));
 }
 
 template <typename T>
@@ -253,7 +316,8 @@ void fwd_t(const BatchNormArgs& a, cudaStream_t s) {
     RT_CUDA_CHECK(cudaMemsetAsync(a.scratch, 0, sizeof(float) * 2 * a.C, s));
     launch_reduce<T>(a, false, a.scratch, s);
   }
-  bn_apply_kernel<T><<<apply_grid(a.M * (a.C / V)), 256, 0, s>>>(
+  const BnShape sh = bn_shape(a.M, a.C / V, 256, 4, 8);
+  bn_apply_kernel<T><<<sh.grid, sh.block, 0, s>>>(
       reinterpret_cast<const T*>(a.x), reinterpret_cast<const T*>(a.residual), reinterpret_cast<T*>(a.y), a.scratch, a.gamma,
       a.beta, a.running_mean, a.running_var, a.save_mean, a.save_rstd, a.M, a.C, a.eps, a.momentum, a.relu, a.training);
   RT_LAUNCH_CHECK();
@@ -264,7 +328,8 @@ void bwd_t(const BatchNormArgs& a, cudaStream_t s) {
   constexpr int V = VecN<T>::N;
   RT_CUDA_CHECK(cudaMemsetAsync(a.scratch, 0, sizeof(float) * 2 * a.C, s));
   launch_reduce<T>(a, true, a.scratch, s);
-  bn_bwd_apply_kernel<T><<<apply_grid(a.M * (a.C / V)), 256, 0, s>>>(
+  const BnShape sh = bn_shape(a.M, a.C / V, 256, 2, 8);
+  bn_bwd_apply_kernel<T><<<sh.grid, sh.block, 0, s>>>(
       reinterpret_cast<const T*>(a.x), reinterpret_cast<const T*>(a.dy), reinterpret_cast<const T*>(a.y_relu),
       reinterpret_cast<T*>(a.dx), reinterpret_cast<T*>(a.dres), a.scratch, a.save_mean, a.save_rstd, a.gamma, a.M, a.C);
   RT_LAUNCH_CHECK();
