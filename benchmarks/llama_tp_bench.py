@@ -80,12 +80,13 @@ def main():
     ms = float(t) / a.steps
     _native.check_status()
     tokens = a.seqs * a.seq_len
-    n_params = sum(p.numel() for p in model.parameters()) * (world if world > 1 else 1)
+    d, dkv, ff = 4096, 1024, 14336
+    n_params = a.layers * (2 * d * d + 2 * d * dkv + 3 * d * ff + 2 * d) + 2 * a.vocab * d + d
     out = {"metric": "train_tokens_per_s", "value": round(tokens / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
            "warmup": a.warmup, "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "strong", "dtype": "bf16",
            "data": "synthetic uniform random tokens, random-init weights", "reduced": a.layers != 32,
            "config": {"model": f"llama-8B style ({a.layers}L, d4096, 32q/8kv heads, SwiGLU 14336, vocab {a.vocab})", "global_batch": a.seqs,
-                      "seq_len": a.seq_len, "parallelism": f"tp{world}+sp", "approx_params": n_params},
+                      "seq_len": a.seq_len, "parallelism": f"tp{world}+sp", "params": n_params},
            "clocks": clocks, "gpu_launches": _native.launch_count() - l0, "final_loss": round(float(loss), 4)}
     if rank == 0:
         print(json.dumps(out), flush=True)

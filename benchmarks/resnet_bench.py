@@ -121,7 +121,7 @@ def main():
            "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "dtype": "bf16",
            "impl": a.impl, "data": "synthetic N(0,1) images, random-init weights",
            "config": {"model": "resnet18 (channels-last)", "per_gpu_batch": a.batch, "image": "3x224x224", "optimizer": "SGD m0.9 lr0.1 wd1e-4",
-                      "parallelism": f"dp{world}", "convolutions": "implicit-GEMM tcgen05 (stem + strided dgrad: library)" if a.impl == "ours" else "cuDNN"},
+                      "parallelism": f"dp{world}", "convolutions": "implicit-GEMM tcgen05; stem as im2col + tcgen05 GEMM" if a.impl == "ours" else "cuDNN"},
            "clocks": clocks, "gpu_launches": _native.launch_count() - l0, "final_loss": round(float(loss), 4)}
     if rank == 0:
         print(json.dumps(out), flush=True)

@@ -108,6 +108,26 @@ struct BatchNormArgs {
 void batchnorm_fwd(const BatchNormArgs& a, cudaStream_t s);
 void batchnorm_bwd(const BatchNormArgs& a, cudaStream_t s);
 
+// ------------------------------------------------------------------ norm/groupnorm.cu
+// Contiguous x[N][C][HW]; G groups (G == C: InstanceNorm); gamma/beta/statistics fp32; mean/rstd [N*G].
+struct GroupNormArgs {
+  int dtype;
+  const void* x;
+  void* y;
+  const float *gamma, *beta;  // may be null
+  float *mean, *rstd;         // written by forward, read by backward
+  long long N;
+  int C, G;
+  long long HW;
+  float eps;
+  // backward
+  const void* dy;
+  void* dx;
+  float *dgamma, *dbeta;      // fp32 [C], accumulated into (caller zeroes), may be null
+};
+void groupnorm_fwd(const GroupNormArgs& a, cudaStream_t s);
+void groupnorm_bwd(const GroupNormArgs& a, cudaStream_t s);
+
 // ------------------------------------------------------------------- nn/embedding.cu
 void embedding_fwd(const long long* idx, const void* wte, const void* wpe, void* out,
                    long long rows, int T, int C, int vocab, cudaStream_t stream);
@@ -169,7 +189,8 @@ void ddp_wait_end(const int* flags, int n_slots, int world, int rank, int epoch,
 // ------------------------------------------------------------------ conv/conv2d_igemm.cu
 // Channels-last bf16 tensors: x [N][H][W][Cin], w [Cout][KH][KW][Cin], out / dy [N][OH][OW][Cout]; dw fp32 like w.
 struct Conv2dArgs {
-  int N, H, W, Cin, Cout, KH, KW, stride, pad;
+  int N, H, W, Cin, Cout, KH, KW, stride, pad;  // pad: both directions unless pad_h >= 0 (then pad is along W only)
+  int pad_h = -1;
   const void* x;
   const void* w;
   void* out;

@@ -356,7 +356,8 @@ void tp_gemm_rs(const Tensor& x, const Tensor& weight, bool b_mn, const std::vec
 }
 
 // x [N,H,W,Cin], w [Cout,KH,KW,Cin], out [N,OH,OW,Cout]: contiguous bf16 (channels-last views of NCHW tensors).
-void conv2d_fwd(const Tensor& x, const Tensor& w, Tensor& out, const c10::optional<Tensor>& bias, int64_t stride, int64_t pad) {
+void conv2d_fwd(const Tensor& x, const Tensor& w, Tensor& out, const c10::optional<Tensor>& bias, int64_t stride, int64_t pad,
+                int64_t pad_h) {
   check_bf16(x, "conv2d x");
   check_bf16(w, "conv2d w");
   check_bf16(out, "conv2d out");
@@ -366,8 +367,9 @@ void conv2d_fwd(const Tensor& x, const Tensor& w, Tensor& out, const c10::option
   a.N = int(x.size(0)); a.H = int(x.size(1)); a.W = int(x.size(2)); a.Cin = int(x.size(3));
   a.Cout = int(w.size(0)); a.KH = int(w.size(1)); a.KW = int(w.size(2));
   TORCH_CHECK(w.size(3) == a.Cin, "conv2d: weight / input channel mismatch");
-  a.stride = int(stride); a.pad = int(pad);
-  const int64_t OH = (a.H + 2 * a.pad - a.KH) / a.stride + 1, OW = (a.W + 2 * a.pad - a.KW) / a.stride + 1;
+  a.stride = int(stride); a.pad = int(pad); a.pad_h = int(pad_h);
+  const int64_t ph = pad_h >= 0 ? pad_h : pad;
+  const int64_t OH = (a.H + 2 * ph - a.KH) / a.stride + 1, OW = (a.W + 2 * a.pad - a.KW) / a.stride + 1;
   TORCH_CHECK(out.size(0) == a.N && out.size(1) == OH && out.size(2) == OW && out.size(3) == a.Cout, "conv2d: bad output shape");
   a.x = x.data_ptr(); a.w = w.data_ptr(); a.out = out.data_ptr();
   if (bias.has_value() && bias->defined()) { check_bf16(*bias, "conv2d bias"); a.bias = bias->data_ptr(); }
@@ -379,7 +381,7 @@ void conv2d_fwd(const Tensor& x, const Tensor& w, Tensor& out, const c10::option
 // results go to every step-th pixel of the contiguous NHWC tensor `out`, starting at pixel (off_h, off_w): one parity
 // class of a strided input gradient.
 void conv2d_fwd_scatter(const Tensor& x, const Tensor& w, Tensor& out, int64_t pad, int64_t out_h, int64_t out_w, int64_t step,
-                        int64_t off_h, int64_t off_w) {
+                        int64_t off_h, int64_t off_w, int64_t pad_h) {
   check_bf16(x, "conv2d x");
   check_bf16(w, "conv2d w");
   check_bf16(out, "conv2d out");
@@ -392,7 +394,7 @@ void conv2d_fwd_scatter(const Tensor& x, const Tensor& w, Tensor& out, int64_t p
   TORCH_CHECK(pad >= 0 && step >= 1 && out_h >= 1 && out_w >= 1 && off_h >= 0 && off_w >= 0 &&
                   off_h + (out_h - 1) * step < out.size(1) && off_w + (out_w - 1) * step < out.size(2),
               "conv2d_fwd_scatter: the scattered results must lie inside the output tensor");
-  a.stride = 1; a.pad = int(pad);
+  a.stride = 1; a.pad = int(pad); a.pad_h = int(pad_h);
   a.out_h = int(out_h); a.out_w = int(out_w);
   const int64_t H = out.size(1), W = out.size(2), C = out.size(3);
   a.out_sn = H * W * C; a.out_sh = step * W * C; a.out_sw = step * C;
@@ -403,7 +405,7 @@ void conv2d_fwd_scatter(const Tensor& x, const Tensor& w, Tensor& out, int64_t p
 }
 
 // dw [Cout,KH,KW,Cin] fp32 += dy^T (*) x
-void conv2d_wgrad(const Tensor& x, const Tensor& dy, Tensor& dw, int64_t stride, int64_t pad) {
+void conv2d_wgrad(const Tensor& x, const Tensor& dy, Tensor& dw, int64_t stride, int64_t pad, int64_t pad_h) {
   check_bf16(x, "conv2d_wgrad x");
   check_bf16(dy, "conv2d_wgrad dy");
   TORCH_CHECK(dw.is_cuda() && dw.scalar_type() == at::kFloat && dw.is_contiguous() && dw.dim() == 4 && x.is_contiguous() &&
@@ -411,8 +413,9 @@ void conv2d_wgrad(const Tensor& x, const Tensor& dy, Tensor& dw, int64_t stride,
   rt::Conv2dArgs a{};
   a.N = int(x.size(0)); a.H = int(x.size(1)); a.W = int(x.size(2)); a.Cin = int(x.size(3));
   a.Cout = int(dw.size(0)); a.KH = int(dw.size(1)); a.KW = int(dw.size(2));
-  a.stride = int(stride); a.pad = int(pad);
-  const int64_t OH = (a.H + 2 * a.pad - a.KH) / a.stride + 1, OW = (a.W + 2 * a.pad - a.KW) / a.stride + 1;
+  a.stride = int(stride); a.pad = int(pad); a.pad_h = int(pad_h);
+  const int64_t ph = pad_h >= 0 ? pad_h : pad;
+  const int64_t OH = (a.H + 2 * ph - a.KH) / a.stride + 1, OW = (a.W + 2 * a.pad - a.KW) / a.stride + 1;
   TORCH_CHECK(dw.size(3) == a.Cin && dy.size(0) == a.N && dy.size(1) == OH && dy.size(2) == OW && dy.size(3) == a.Cout,
               "conv2d_wgrad: shape mismatch");
   a.x = x.data_ptr(); a.dy = dy.data_ptr(); a.dw = dw.data_ptr<float>();
@@ -614,6 +617,39 @@ void batchnorm_bwd(const Tensor& x2, const Tensor& dy2, const c10::optional<Tens
 }
 
 
+// x, y (and dy, dx): contiguous [N, C, *]; mean / rstd fp32 [N * groups]; gamma / beta / dgamma / dbeta fp32 [C] or none.
+void groupnorm(const Tensor& x, Tensor& out, const c10::optional<Tensor>& dy, const c10::optional<Tensor>& gamma,
+               const c10::optional<Tensor>& beta, Tensor& mean, Tensor& rstd, const c10::optional<Tensor>& dgamma,
+               const c10::optional<Tensor>& dbeta, int64_t groups, double eps) {
+  rt::GroupNormArgs a{};
+  a.dtype = dtype_code(x, "groupnorm x");
+  TORCH_CHECK(x.dim() >= 2 && x.is_contiguous() && out.is_contiguous() && out.sizes() == x.sizes() &&
+                  out.scalar_type() == x.scalar_type(), "groupnorm: x and out must be contiguous [N, C, ...] of one dtype");
+  a.N = x.size(0);
+  a.C = int(x.size(1));
+  a.G = int(groups);
+  TORCH_CHECK(a.N > 0 && a.C > 0 && a.G > 0 && a.C % a.G == 0 && x.numel() > 0, "groupnorm: bad shape");
+  a.HW = x.numel() / (a.N * a.C);
+  a.eps = float(eps);
+  a.x = x.data_ptr();
+  a.gamma = opt_f32(gamma, a.C, "groupnorm gamma");
+  a.beta = opt_f32(beta, a.C, "groupnorm beta");
+  a.mean = const_cast<float*>(opt_f32(mean, a.N * a.G, "groupnorm mean"));
+  a.rstd = const_cast<float*>(opt_f32(rstd, a.N * a.G, "groupnorm rstd"));
+  c10::cuda::CUDAGuard guard(x.device());
+  if (dy.has_value() && dy->defined()) {
+    TORCH_CHECK(dy->is_contiguous() && dy->sizes() == x.sizes() && dy->scalar_type() == x.scalar_type(), "groupnorm: dy must match x");
+    a.dy = dy->data_ptr();
+    a.dx = out.data_ptr();
+    a.dgamma = const_cast<float*>(opt_f32(dgamma, a.C, "groupnorm dgamma"));
+    a.dbeta = const_cast<float*>(opt_f32(dbeta, a.C, "groupnorm dbeta"));
+    rt::groupnorm_bwd(a, cur_stream(x.device().index()));
+  } else {
+    a.y = out.data_ptr();
+    rt::groupnorm_fwd(a, cur_stream(x.device().index()));
+  }
+}
+
 // x: channels-last storage viewed as [N, H, W, C] (contiguous); y likewise [N, OH, OW, C].
 void pool2d(Tensor& x, Tensor& y, const c10::optional<Tensor>& idx, bool is_max, bool backward, int64_t kh, int64_t kw, int64_t sh,
             int64_t sw, int64_t ph, int64_t pw) {
@@ -778,12 +814,17 @@ void register_extra_ops(pybind11::module_& m) {
   m.def("amp_unscale", &amp_unscale, "grads *= inv_scale, found_inf = 1 on any non-finite value");
   m.def("csr_spmm", &csr_spmm, "CSR sparse x dense product (fp32)");
   m.def("ar_residual_norm", &ar_residual_norm, "all-reduce over peer memory + residual add + RMSNorm in one kernel");
-  m.def("conv2d_fwd_scatter", &conv2d_fwd_scatter, "stride-1 convolution written to every step-th output pixel");
-  m.def("conv2d_fwd", &conv2d_fwd, "implicit-GEMM conv2d forward (channels-last bf16)");
-  m.def("conv2d_wgrad", &conv2d_wgrad, "implicit-GEMM conv2d weight gradient (fp32 accumulate)");
+  m.def("conv2d_fwd_scatter", &conv2d_fwd_scatter, "stride-1 convolution written to every step-th output pixel", py::arg("x"),
+        py::arg("w"), py::arg("out"), py::arg("pad"), py::arg("out_h"), py::arg("out_w"), py::arg("step"), py::arg("off_h"),
+        py::arg("off_w"), py::arg("pad_h") = -1);
+  m.def("conv2d_fwd", &conv2d_fwd, "implicit-GEMM conv2d forward (channels-last bf16); pad_h >= 0: pad is along W only", py::arg("x"),
+        py::arg("w"), py::arg("out"), py::arg("bias"), py::arg("stride"), py::arg("pad"), py::arg("pad_h") = -1);
+  m.def("conv2d_wgrad", &conv2d_wgrad, "implicit-GEMM conv2d weight gradient (fp32 accumulate)", py::arg("x"), py::arg("dy"),
+        py::arg("dw"), py::arg("stride"), py::arg("pad"), py::arg("pad_h") = -1);
   m.def("conv2d_igemm_supported", &rt::conv2d_igemm_supported);
   m.def("tp_ag_gemm", &tp_ag_gemm, "fused all-gather -> GEMM over symmetric peer memory");
   m.def("tp_gemm_rs", &tp_gemm_rs, "fused GEMM -> reduce-scatter over symmetric peer memory");
+  m.def("groupnorm", &groupnorm, "GroupNorm / InstanceNorm forward (dy absent) or backward (out = dx) over contiguous [N, C, ...]");
   m.def("batchnorm_fwd", &batchnorm_fwd, "BatchNorm forward over a channels-last matrix (+residual, +ReLU)");
   m.def("batchnorm_bwd", &batchnorm_bwd, "BatchNorm backward; scratch returns [dbeta, dgamma]");
   m.def("ew_binary", &ew_binary, "elementwise binary op (add/sub/mul/div/max/min/pow)");

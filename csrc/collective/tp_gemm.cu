@@ -13,13 +13,15 @@
 //
 //   MODE_RS (GEMM -> reduce-scatter, row-parallel forward / column-parallel dgrad)
 //     out_r[M/W][N] = sum_src (x_src . B_src^T)[rows of r]
-//     The epilogue stores each bf16 tile straight into the OWNER rank's staging buffer over NVLink and
-//     bumps a per-(block, source) counter there; tiles for remote owners are computed first so their
-//     transfer overlaps the remaining math.  When a CTA runs out of tiles it joins the reduce phase: for
-//     its share of the owned rows it waits for the W sources' counters, sums the W partials in fp32
-//     (+ bias, + residual) and writes the bf16 result.  Staging is double-buffered by call parity, which
-//     makes reuse safe without a second barrier (a rank can never be two calls ahead of a peer, because
-//     each call's reduce phase needs that peer's partials of the same call).
+//     Tiles for remote owners are computed first: the epilogue turns each warp's 32 x 64 piece of the tile
+//     into row-major bf16 in shared memory and stores it to the OWNER rank's staging buffer over NVLink as
+//     128-byte row segments, then bumps a per-(block, source) counter there, so the transfer overlaps the
+//     remaining math.  The rank's own rows come last and never leave the chip as partials: their epilogue
+//     waits for the W-1 sources' counters of the block, adds the staged partials (+ bias, + residual) to the
+//     fp32 accumulator straight out of TMEM and writes the bf16 result.  No separate reduce phase.  Staging
+//     is double-buffered by call parity, which makes reuse safe without a second barrier (a rank can never
+//     be two calls ahead of a peer, because each call's own-row tiles need that peer's partials of the same
+//     call).
 //
 // Synchronisation is by flags in symmetric memory (st.release.sys / red.release.sys / ld.acquire.sys),
 // every wait is bounded by a globaltimer deadline and reports through the status word; on a timeout the
@@ -71,8 +73,11 @@ struct TpSmem {
   static constexpr int B_BYTES = BLOCK_N * TP_BLOCK_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BLOCK_N == 256) ? 4 : 6;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;  // 8 epilogue warps x (32 rows x 128 B), 16-byte pieces XOR-swizzled
+  static constexpr int EPI_BYTES = 8 * 4096;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EPI_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
+  static_assert(TOTAL <= 232448, "tp_gemm: shared memory over the per-CTA limit");
 };
 
 __device__ __forceinline__ void tp_st_release_sys(int* p, int v) {
@@ -377,59 +382,146 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,   // AG: local shard 
       }
       tc_fence_after();
       __nv_bfloat16* row_ptr;
-      long long ld;
       int dst = R, mbl = 0;
+      const __nv_bfloat16* part = nullptr;  // RS, own rows: the sources' staged partials of this row
       if (P.mode == 0) {
         row_ptr = P.C + ((long long)gmb * TP_BLOCK_M + row_in_tile) * P.ldc;
-        ld = P.ldc;
       } else {
         dst = gmb / P.mbs;
         mbl = gmb - dst * P.mbs;
-        // staging of the owner: [parity][src = R][Ms][N]
-        row_ptr = P.stage_peer[dst] + (long long)(P.epoch & 1) * P.stage_parity_stride +
-                  ((long long)R * Ms + (long long)mbl * TP_BLOCK_M + row_in_tile) * P.N;
-        ld = P.N;
+        const long long parity_off = (long long)(P.epoch & 1) * P.stage_parity_stride;
+        if (dst == R) {
+          // own rows: every other source has sent all its tiles of this 128-row block?
+          const int want = P.epoch * 8 * P.n_blocks;  // 8 epilogue warps signal once per tile
+          bool arrived = true;
+          if (lane < W && lane != R) arrived = tp_wait_ge<true>(my_flags + 2 * W + mbl * W + lane, want, P, ctl);
+          if (!__all_sync(0xffffffffu, arrived)) {
+            ok = false;
+            break;
+          }
+          row_ptr = P.C + ((long long)mbl * TP_BLOCK_M + row_in_tile) * P.ldc;
+          part = P.stage_peer[R] + parity_off + ((long long)mbl * TP_BLOCK_M + row_in_tile) * P.N;
+        } else {
+          // staging of the owner: [parity][src = R][Ms][N]; row_ptr = first row of this warp's 32
+          row_ptr = P.stage_peer[dst] + parity_off + ((long long)R * Ms + (long long)mbl * TP_BLOCK_M + quarter * 32) * P.N;
+        }
       }
-      (void)ld;
+      const bool remote = P.mode == 1 && dst != R;
+      uint8_t* wstage = smem + S::EPI_OFFSET + (warp - 2) * 4096;
 #pragma unroll 1
-      for (int c = col_half * (BLOCK_N / 64); c < (col_half + 1) * (BLOCK_N / 64); ++c) {
+      for (int c = col_half * (BLOCK_N / 64); c < (col_half + 1) * (BLOCK_N / 64); c += 2) {
         const int n0 = nb * BLOCK_N + c * 32;
         if (n0 >= P.N) break;
-        uint32_t r[32];
+        const bool full = n0 + 64 <= P.N;
+        uint32_t r[2][32];
         const uint32_t taddr = tmem_base + acc * BLOCK_N + c * 32 + (uint32_t(quarter * 32) << 16);
         __syncwarp();
-        tmem_ld_32x32b_x32(taddr, r);
+        tmem_ld_32x32b_x32(taddr, r[0]);
+        tmem_ld_32x32b_x32(taddr + 32, r[1]);
         tmem_ld_wait();
-        float v[32];
+        if (remote && full) {
+          // row-major through shared memory: lane = row writes its eight 16-byte pieces, then eight lanes
+          // cover one row's 128 bytes, so every store instruction sends four full 128-byte segments
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (P.mode == 0 && P.bias) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (n0 + j < P.N) v[j] += __bfloat162float(P.bias[n0 + j]);
-        }
-        __nv_bfloat16* crow = row_ptr + n0;
-        if (n0 + 32 <= P.N) {
-          uint4* d4 = reinterpret_cast<uint4*>(crow);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
+          for (int q = 0; q < 8; ++q) {
+            const int hq = q >> 2, o = (q & 3) * 8;
             uint4 w;
-            w.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-            w.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-            w.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-            w.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-            d4[q] = w;
+            w.x = pack_bf16x2(__uint_as_float(r[hq][o + 0]), __uint_as_float(r[hq][o + 1]));
+            w.y = pack_bf16x2(__uint_as_float(r[hq][o + 2]), __uint_as_float(r[hq][o + 3]));
+            w.z = pack_bf16x2(__uint_as_float(r[hq][o + 4]), __uint_as_float(r[hq][o + 5]));
+            w.w = pack_bf16x2(__uint_as_float(r[hq][o + 6]), __uint_as_float(r[hq][o + 7]));
+            *reinterpret_cast<uint4*>(wstage + lane * 128 + ((q ^ (lane & 7)) << 4)) = w;
           }
-        } else {
+          __syncwarp();
+          const int piece = lane & 7;
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (n0 + j < P.N) crow[j] = __float2bfloat16(v[j]);
+          for (int itr = 0; itr < 8; ++itr) {
+            const int row = itr * 4 + (lane >> 3);
+            const uint4 w = *reinterpret_cast<const uint4*>(wstage + row * 128 + ((piece ^ (row & 7)) << 4));
+            *reinterpret_cast<uint4*>(row_ptr + (long long)row * P.N + n0 + piece * 8) = w;
+          }
+          continue;
+        }
+        // direct path: this lane's row, 32 columns at a time
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int nh = n0 + h * 32;
+          if (nh >= P.N) break;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[h][j]);
+          const bool whole = nh + 32 <= P.N;
+          if (part) {
+            for (int src = 0; src < W; ++src) {
+              if (src == R) continue;
+              const __nv_bfloat16* prow = part + (long long)src * Ms * P.N + nh;
+              if (whole) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const uint4 raw = tp_ld_cg(prow + q * 8);
+                  const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(hh[e]);
+                    v[q * 8 + 2 * e] += f.x;
+                    v[q * 8 + 2 * e + 1] += f.y;
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (nh + j < P.N) v[j] += __bfloat162float(prow[j]);
+              }
+            }
+          }
+          if (P.bias && (P.mode == 0 || part)) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nh + j < P.N) v[j] += __bfloat162float(P.bias[nh + j]);
+          }
+          if (part && P.residual) {
+            const __nv_bfloat16* rrow = P.residual + ((long long)mbl * TP_BLOCK_M + row_in_tile) * P.ld_res + nh;
+            if (whole) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(rrow + q * 8);
+                const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f = __bfloat1622float2(hh[e]);
+                  v[q * 8 + 2 * e] += f.x;
+                  v[q * 8 + 2 * e + 1] += f.y;
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nh + j < P.N) v[j] += __bfloat162float(rrow[j]);
+            }
+          }
+          __nv_bfloat16* crow = (remote ? row_ptr + (long long)lane * P.N : row_ptr) + nh;
+          if (whole) {
+            uint4* d4 = reinterpret_cast<uint4*>(crow);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 w;
+              w.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              w.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              w.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              w.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              d4[q] = w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nh + j < P.N) crow[j] = __float2bfloat16(v[j]);
+          }
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-      if (P.mode == 1) {
+      if (remote) {
         // this warp's part of the tile is on its way to the owner: make it visible, then count it
         __threadfence_system();
         __syncwarp();
@@ -450,60 +542,6 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,   // AG: local shard 
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
 
-  // =========================================================================== reduce phase (RS)
-  if (P.mode == 1 && !ctl->abort) {
-    const long long Ms = (long long)P.mbs * TP_BLOCK_M;
-    const int want = P.epoch * 8 * P.n_blocks;  // 8 epilogue warps signal once per tile
-    const int warps = TP_THREADS / 32;
-    const __nv_bfloat16* stage = P.stage_peer[R] + (long long)(P.epoch & 1) * P.stage_parity_stride;
-    int ready_mbl = -1;
-    bool ok = true;
-    const int nvec = P.N / 8;
-    for (long long row = (long long)blockIdx.x * warps + warp; row < Ms && ok; row += (long long)gridDim.x * warps) {
-      const int mbl = (int)(row / TP_BLOCK_M);
-      if (mbl != ready_mbl) {
-        if (lane < W) ok = tp_wait_ge<true>(my_flags + 2 * W + mbl * W + lane, want, P, nullptr);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        ready_mbl = mbl;
-      }
-      for (int vct = lane; vct < nvec; vct += 32) {
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-        for (int src = 0; src < W; ++src) {
-          const uint4 raw = tp_ld_cg(stage + ((long long)src * Ms + row) * P.N + vct * 8);
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(h[e]);
-            acc[2 * e] += f.x;
-            acc[2 * e + 1] += f.y;
-          }
-        }
-        if (P.bias) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] += __bfloat162float(P.bias[vct * 8 + e]);
-        }
-        if (P.residual) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(P.residual + row * P.ld_res + vct * 8);
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(h[e]);
-            acc[2 * e] += f.x;
-            acc[2 * e + 1] += f.y;
-          }
-        }
-        uint4 w;
-        w.x = pack_bf16x2(acc[0], acc[1]);
-        w.y = pack_bf16x2(acc[2], acc[3]);
-        w.z = pack_bf16x2(acc[4], acc[5]);
-        w.w = pack_bf16x2(acc[6], acc[7]);
-        *reinterpret_cast<uint4*>(P.C + row * P.ldc + vct * 8) = w;
-      }
-    }
-  }
 }
 
 template <int BLOCK_N, bool B_MN>

@@ -31,7 +31,7 @@ constexpr int CV_THREADS = 320;
 constexpr int CV_BK = 64;
 
 struct ConvParams {
-  int N, H, W, Cin, OH, OW, Cout, KH, KW, stride, pad;
+  int N, H, W, Cin, OH, OW, Cout, KH, KW, stride, pad, pad_h;  // pad: along W; pad_h: along H
   int TW, TH, TN, tiles_w, tiles_h, tiles_n;  // output-pixel tile and tile counts
   int m_tiles, n_blocks, k_chunks;            // k_chunks = Cin / 64
   __nv_bfloat16* out;
@@ -137,7 +137,7 @@ conv_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
           uint8_t* sa = smem + s * S::STAGE_BYTES;
           uint8_t* sb = sa + S::A_BYTES;
           mbar_arrive_expect_tx(&full_bar[s], S::STAGE_BYTES);
-          tma_load_4d(sa, &tmap_x, &full_bar[s], cc * CV_BK, ow0 * p.stride + kw - p.pad, oh0 * p.stride + kh - p.pad, n0);
+          tma_load_4d(sa, &tmap_x, &full_bar[s], cc * CV_BK, ow0 * p.stride + kw - p.pad, oh0 * p.stride + kh - p.pad_h, n0);
           tma_load_3d(sb, &tmap_w, &full_bar[s], tap * p.Cin + cc * CV_BK, nb * BLOCK_N, 0);
         }
       }
@@ -317,7 +317,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_cons
 #pragma unroll
         for (int c = 0; c < BLOCK_N / 64; ++c)
           tma_load_4d(sb + c * 8192, &tmap_x, &full_bar[s], cib * BLOCK_N + c * 64, ow0 * p.stride + kw - p.pad,
-                      oh0 * p.stride + kh - p.pad, n0);
+                      oh0 * p.stride + kh - p.pad_h, n0);
       }
     }
   } else if (warp == 1) {
@@ -449,7 +449,7 @@ conv_wgrad3_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_con
         for (int c = 0; c < 2; ++c) tma_load_4d(sa + c * 8192, &tmap_dy, &full_bar[s], cob * 128 + c * 64, ow0, oh0, n0);
 #pragma unroll
         for (int kw = 0; kw < 3; ++kw)      // chunk kw of the B tile = the box of tap (kh, kw)
-          tma_load_4d(sb + kw * 8192, &tmap_x, &full_bar[s], cib * 64, ow0 * p.stride + kw - p.pad, oh0 * p.stride + kh - p.pad, n0);
+          tma_load_4d(sb + kw * 8192, &tmap_x, &full_bar[s], cib * 64, ow0 * p.stride + kw - p.pad, oh0 * p.stride + kh - p.pad_h, n0);
       }
     }
   } else if (warp == 1) {
@@ -525,7 +525,8 @@ void pick_tile(int OH, int OW, int Nimg, int pixels, int& TW, int& TH, int& TN) 
 
 void fill_common(const Conv2dArgs& a, ConvParams& p, int pixels) {
   p.N = a.N; p.H = a.H; p.W = a.W; p.Cin = a.Cin; p.Cout = a.Cout; p.KH = a.KH; p.KW = a.KW; p.stride = a.stride; p.pad = a.pad;
-  p.OH = a.out_h > 0 ? a.out_h : (a.H + 2 * a.pad - a.KH) / a.stride + 1;
+  p.pad_h = a.pad_h >= 0 ? a.pad_h : a.pad;
+  p.OH = a.out_h > 0 ? a.out_h : (a.H + 2 * p.pad_h - a.KH) / a.stride + 1;
   p.OW = a.out_w > 0 ? a.out_w : (a.W + 2 * a.pad - a.KW) / a.stride + 1;
   p.out_sw = a.out_sw > 0 ? a.out_sw : a.Cout;
   p.out_sh = a.out_sh > 0 ? a.out_sh : (long long)p.OW * a.Cout;
@@ -542,7 +543,7 @@ void check_conv(const Conv2dArgs& a) {
   RT_CHECK(a.Cin % 64 == 0, "conv2d_igemm: input channels must be a multiple of 64");
   RT_CHECK(a.Cout % 8 == 0, "conv2d_igemm: output channels must be a multiple of 8");
   RT_CHECK(a.stride >= 1 && a.stride <= 4 && a.pad >= 0 && a.KH >= 1 && a.KW >= 1 && a.KH <= 7 && a.KW <= 7, "conv2d_igemm: unsupported geometry");
-  RT_CHECK(a.N > 0 && (a.out_h > 0 || (a.H + 2 * a.pad >= a.KH && a.W + 2 * a.pad >= a.KW)), "conv2d_igemm: empty output");
+  RT_CHECK(a.N > 0 && (a.out_h > 0 || (a.H + 2 * (a.pad_h >= 0 ? a.pad_h : a.pad) >= a.KH && a.W + 2 * a.pad >= a.KW)), "conv2d_igemm: empty output");
   RT_CHECK(a.out_sw % 8 == 0 && a.out_sh % 8 == 0 && a.out_sn % 8 == 0, "conv2d_igemm: output strides must keep 16-byte alignment");
 }
 

@@ -103,6 +103,11 @@ class Conv1d(_ConvNd):
     """``(in, out, kernel, stride=1, padding=0, dilation=1, groups=1, bias=True)`` (src/nn/conv1d.rs:121-135)."""
     _fn, _nd = staticmethod(F.conv1d), 1
 
+    def forward(self, x):
+        """bf16 CUDA layers with Cin, Cout multiples of 64 run as one-row images on the implicit-GEMM kernels."""
+        from ..ops.conv import conv1d
+        return conv1d(x, self.weight, self.bias, self.stride, self.padding, self.dilation, self.groups)
+
 
 class Conv2d(_ConvNd):
     """``(in, out, kernel(h,w), stride=(1,1), padding=(0,0), bias=True)`` weight ``[oc, ic, kh, kw]`` (src/nn/conv2d.rs:77-88)."""
@@ -153,6 +158,11 @@ class ConvTranspose1d(_ConvTransposeNd):
 class ConvTranspose2d(_ConvTransposeNd):
     """``(in, out, kernel, stride, padding, output_padding, dilation, groups, bias)`` (src/nn/conv_transpose.rs:81-96)."""
     _fn, _nd = staticmethod(F.conv_transpose2d), 2
+
+    def forward(self, x):
+        """bf16 CUDA layers with Cin, Cout multiples of 64 run as the input-gradient form of the implicit-GEMM kernels."""
+        from ..ops.conv import conv_transpose2d
+        return conv_transpose2d(x, self.weight, self.bias, self.stride, self.padding, self.output_padding, self.groups, self.dilation)
 
     @classmethod
     def upsample_2x(cls, channels: int, **kw) -> "ConvTranspose2d":
@@ -257,19 +267,36 @@ class RMSNorm(nn.Module):
 
 
 class GroupNorm(nn.GroupNorm):
-    """``(num_groups, num_channels, eps=1e-5, affine=True)`` (src/nn/normalization.rs:343-350)."""
+    """``(num_groups, num_channels, eps=1e-5, affine=True)`` (src/nn/normalization.rs:343-350); one CTA per
+    (sample, group) slab on CUDA."""
+
+    def forward(self, x):
+        from ..ops.groupnorm import group_norm
+        return group_norm(x, self.num_groups, self.weight, self.bias, self.eps)
 
 
-class InstanceNorm1d(nn.InstanceNorm1d):
+class _InstanceNormNative:
+    """Batch statistics on the slab kernel; layers that track running statistics (or evaluate with them) keep
+    PyTorch's path."""
+
+    def forward(self, x):
+        if self.track_running_stats or x.dim() != self._rank:
+            return super().forward(x)
+        from ..ops.groupnorm import instance_norm
+        return instance_norm(x, self.weight, self.bias, self.eps)
+
+
+class InstanceNorm1d(_InstanceNormNative, nn.InstanceNorm1d):
     """``(num_features, eps=1e-5, momentum=0.1, affine, track_running_stats)`` (src/nn/instance_norm.rs:148-156)."""
+    _rank = 3
 
 
-class InstanceNorm2d(nn.InstanceNorm2d):
-    pass
+class InstanceNorm2d(_InstanceNormNative, nn.InstanceNorm2d):
+    _rank = 4
 
 
-class InstanceNorm3d(nn.InstanceNorm3d):
-    pass
+class InstanceNorm3d(_InstanceNormNative, nn.InstanceNorm3d):
+    _rank = 5
 
 
 from ..ops import pool as _pool  # noqa: E402

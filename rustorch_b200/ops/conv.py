@@ -23,9 +23,9 @@ def supported(x: torch.Tensor, weight: torch.Tensor, stride, padding, dilation=1
         return False
     if groups != 1 or (dilation if isinstance(dilation, int) else dilation[0]) != 1:
         return False
-    if not isinstance(stride, int) and stride[0] != stride[1] or not isinstance(padding, int) and padding[0] != padding[1]:
+    if not isinstance(stride, int) and stride[0] != stride[1]:
         return False
-    if isinstance(p, str):
+    if isinstance(padding, str) or isinstance(p, str):
         return False
     Cout, Cin, KH, KW = weight.shape
     return Cin % 64 == 0 and Cout % 64 == 0 and KH <= 7 and KW <= 7 and 1 <= s <= 4
@@ -36,24 +36,30 @@ def _nhwc(t: torch.Tensor) -> torch.Tensor:
     return t.permute(0, 2, 3, 1).contiguous()
 
 
-def _strided_dgrad(C, dyh: torch.Tensor, wh: torch.Tensor, xshape, stride: int, pad: int) -> Optional[torch.Tensor]:
+def _pads(padding) -> tuple:
+    return (padding, padding) if isinstance(padding, int) else (int(padding[0]), int(padding[-1]))
+
+
+def _strided_dgrad(C, dyh: torch.Tensor, wh: torch.Tensor, xshape, stride: int, pad_h: int, pad_w: Optional[int] = None
+                   ) -> Optional[torch.Tensor]:
     """Input gradient of a strided convolution as ``stride^2`` stride-1 convolutions of ``dy``, one per parity class
     of the input pixels: class ``(ph, pw)`` only receives the taps with ``kh = ph + pad (mod stride)`` (same for kw),
     and its pixels form a dense grid, so the forward kernel computes it with a sub-filter and scatters the results to
     every ``stride``-th pixel of ``dx``.  Classes without taps (1x1 kernels) stay zero.  ``None``: geometry not covered."""
     N, H, W, Cin = xshape
     Cout, KH, KW, _ = wh.shape
+    pad_w = pad_h if pad_w is None else pad_w
 
-    def taps(ph: int, K: int):
+    def taps(ph: int, K: int, pad: int):
         ks = [k for k in range(K) if (ph + pad - k) % stride == 0]
         offs = [(ph + pad - k) // stride for k in ks]            # dy index = y + off, descending k -> ascending off
         return ks[::-1], offs[::-1]
 
     plans = []
     for ph in range(stride):
-        khs, offh = taps(ph, KH)
+        khs, offh = taps(ph, KH, pad_h)
         for pw in range(stride):
-            kws, offw = taps(pw, KW)
+            kws, offw = taps(pw, KW, pad_w)
             rows, cols = -(-(H - ph) // stride), -(-(W - pw) // stride)
             if rows <= 0 or cols <= 0 or not khs or not kws:
                 plans.append(None)
@@ -61,31 +67,32 @@ def _strided_dgrad(C, dyh: torch.Tensor, wh: torch.Tensor, xshape, stride: int, 
             # a stride-1 correlation needs consecutive offsets starting at -pad' with pad' >= 0, the same for h and w
             if offh != list(range(offh[0], offh[0] + len(offh))) or offw != list(range(offw[0], offw[0] + len(offw))):
                 return None
-            if offh[0] > 0 or offw[0] > 0 or offh[0] != offw[0]:
+            if offh[0] > 0 or offw[0] > 0:
                 return None
-            plans.append((ph, pw, khs, kws, -offh[0], rows, cols))
+            plans.append((ph, pw, khs, kws, -offh[0], -offw[0], rows, cols))
     full = all(pl is not None for pl in plans)
     dx = (torch.empty if full else torch.zeros)((N, H, W, Cin), dtype=torch.bfloat16, device=dyh.device)
     for pl in plans:
         if pl is None:
             continue
-        ph, pw, khs, kws, p2, rows, cols = pl
+        ph, pw, khs, kws, p2h, p2w, rows, cols = pl
         # sub-filter [Cin][n_h][n_w][Cout]: the contraction runs over the layer's output channels
         sub = wh[:, khs][:, :, kws].permute(3, 1, 2, 0).contiguous()
-        C.conv2d_fwd_scatter(dyh, sub, dx, p2, rows, cols, stride, ph, pw)
+        C.conv2d_fwd_scatter(dyh, sub, dx, p2w, rows, cols, stride, ph, pw, pad_h=p2h)
     return dx
 
 
 class Conv2dFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, stride: int, pad: int):
+    def forward(ctx, x, weight, bias, stride: int, pad):
         C = _native.load(required=True)
         xh, wh = _nhwc(x), _nhwc(weight)                       # [N,H,W,Cin], [Cout,KH,KW,Cin]
         N, H, W, _ = xh.shape
         Cout, KH, KW, _ = wh.shape
-        OH, OW = (H + 2 * pad - KH) // stride + 1, (W + 2 * pad - KW) // stride + 1
+        pad_h, pad_w = _pads(pad)
+        OH, OW = (H + 2 * pad_h - KH) // stride + 1, (W + 2 * pad_w - KW) // stride + 1
         out = torch.empty(N, OH, OW, Cout, dtype=torch.bfloat16, device=x.device)
-        C.conv2d_fwd(xh, wh, out, bias, stride, pad)
+        C.conv2d_fwd(xh, wh, out, bias, stride, pad_w, pad_h=pad_h)
         ctx.save_for_backward(xh, wh)
         ctx.geom = (stride, pad, bias is not None, tuple(x.shape))
         return out.permute(0, 3, 1, 2)                          # NCHW shape, channels-last memory
@@ -95,24 +102,25 @@ class Conv2dFn(torch.autograd.Function):
         C = _native.load(required=True)
         xh, wh = ctx.saved_tensors
         stride, pad, has_bias, xshape = ctx.geom
+        pad_h, pad_w = _pads(pad)
         dyh = _nhwc(dy)
         Cout, KH, KW, Cin = wh.shape
         dx = dw = db = None
         if ctx.needs_input_grad[1]:
             dwf = torch.zeros(Cout, KH, KW, Cin, dtype=torch.float32, device=dyh.device)
-            C.conv2d_wgrad(xh, dyh, dwf, stride, pad)
+            C.conv2d_wgrad(xh, dyh, dwf, stride, pad_w, pad_h=pad_h)
             dw = dwf.to(torch.bfloat16).permute(0, 3, 1, 2)    # back to [Cout, Cin, KH, KW] (channels-last memory)
         if ctx.needs_input_grad[0]:
-            if stride == 1 and KH - 1 - pad >= 0:
+            if stride == 1 and KH - 1 - pad_h >= 0 and KW - 1 - pad_w >= 0:
                 # full correlation of dy with the rotated filter: w'[ci][kh][kw][co] = w[co][KH-1-kh][KW-1-kw][ci]
                 wr = wh.flip(1, 2).permute(3, 1, 2, 0).contiguous()
                 dxh = torch.empty(xh.shape, dtype=torch.bfloat16, device=dyh.device)
-                C.conv2d_fwd(dyh, wr, dxh, None, 1, KH - 1 - pad)
+                C.conv2d_fwd(dyh, wr, dxh, None, 1, KW - 1 - pad_w, pad_h=KH - 1 - pad_h)
                 dx = dxh.permute(0, 3, 1, 2)
             else:
-                dxh = _strided_dgrad(C, dyh, wh, xh.shape, stride, pad)
+                dxh = _strided_dgrad(C, dyh, wh, xh.shape, stride, pad_h, pad_w)
                 dx = dxh.permute(0, 3, 1, 2) if dxh is not None else \
-                    torch.nn.grad.conv2d_input(xshape, wh.permute(0, 3, 1, 2), dy, stride, pad)
+                    torch.nn.grad.conv2d_input(xshape, wh.permute(0, 3, 1, 2), dy, stride, (pad_h, pad_w))
         if has_bias and ctx.needs_input_grad[2]:
             db = dyh.float().sum((0, 1, 2)).to(torch.bfloat16)
         return dx, dw, db, None, None
@@ -179,6 +187,85 @@ def conv2d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         return Im2colConv2dFn.apply(x, weight, bias, s, p)
     if supported(x, weight, stride, padding, dilation, groups):
         s = stride if isinstance(stride, int) else stride[0]
-        p = padding if isinstance(padding, int) else padding[0]
-        return Conv2dFn.apply(x, weight, bias, s, p)
+        return Conv2dFn.apply(x, weight, bias, s, _pads(padding))
     return F.conv2d(x, weight, bias, stride, padding, dilation, groups)
+
+
+def _one(v) -> int:
+    return v if isinstance(v, int) else int(v[0])
+
+
+def conv1d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, stride=1, padding=0, dilation=1,
+           groups: int = 1) -> torch.Tensor:
+    """``[N, C, L]`` convolution as a one-row image on the 2-D kernels (padding along the length only)."""
+    if (x.dim() == 3 and not isinstance(padding, str) and _one(dilation) == 1 and groups == 1 and _one(stride) <= 4
+            and supported(x.unsqueeze(2), weight.unsqueeze(2), _one(stride), (0, _one(padding)))):
+        y = Conv2dFn.apply(x.unsqueeze(2), weight.unsqueeze(2), bias, _one(stride), (0, _one(padding)))
+        return y.squeeze(2)
+    return F.conv1d(x, weight, bias, stride, padding, dilation, groups)
+
+
+class ConvTranspose2dFn(torch.autograd.Function):
+    """Transposed convolution = the input gradient of the convolution with the same weight: forward runs the (strided)
+    dgrad path, the gradient with respect to the input is a plain forward convolution of ``dy``, the weight gradient is
+    the convolution's weight gradient with the roles of input and output swapped."""
+
+    @staticmethod
+    def forward(ctx, x, weight, stride: int, pad: int, out_pad: int):
+        C = _native.load(required=True)
+        xh = _nhwc(x)                                           # [N,H,W,Cin]: the "dy" of the underlying convolution
+        wh = _nhwc(weight)                                      # weight [Cin, Cout, KH, KW] -> [Cin, KH, KW, Cout]
+        N, H, W, Cin = xh.shape
+        _, KH, KW, Cout = wh.shape
+        OH, OW = (H - 1) * stride - 2 * pad + KH + out_pad, (W - 1) * stride - 2 * pad + KW + out_pad
+        if stride == 1:
+            wr = wh.flip(1, 2).permute(3, 1, 2, 0).contiguous()
+            out = torch.empty(N, OH, OW, Cout, dtype=torch.bfloat16, device=x.device)
+            C.conv2d_fwd(xh, wr, out, None, 1, KW - 1 - pad, pad_h=KH - 1 - pad)
+        else:
+            out = _strided_dgrad(C, xh, wh, (N, OH, OW, Cout), stride, pad)
+            if out is None:
+                raise RuntimeError("conv_transpose2d: geometry not covered by the native path")
+        ctx.save_for_backward(xh, wh)
+        ctx.geom = (stride, pad)
+        return out.permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = _native.load(required=True)
+        xh, wh = ctx.saved_tensors
+        stride, pad = ctx.geom
+        dyh = _nhwc(dy)                                         # [N,OH,OW,Cout]: the input of the underlying convolution
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dxh = torch.empty(xh.shape, dtype=torch.bfloat16, device=dyh.device)
+            C.conv2d_fwd(dyh, wh, dxh, None, stride, pad)
+            dx = dxh.permute(0, 3, 1, 2)
+        if ctx.needs_input_grad[1]:
+            dwf = torch.zeros(wh.shape, dtype=torch.float32, device=dyh.device)
+            C.conv2d_wgrad(dyh, xh, dwf, stride, pad)
+            dw = dwf.to(torch.bfloat16).permute(0, 3, 1, 2)
+        return dx, dw, None, None, None
+
+
+def conv_transpose2d_supported(x, weight, stride, padding, output_padding, dilation, groups) -> bool:
+    if not (x.is_cuda and x.dim() == 4 and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and _native.available()):
+        return False
+    s, p, op = _pads(stride), _pads(padding), _pads(output_padding)
+    if s[0] != s[1] or p[0] != p[1] or op[0] != op[1] or _one(dilation) != 1 or groups != 1 or not 1 <= s[0] <= 4:
+        return False
+    Cin, Cout, KH, KW = weight.shape
+    if Cin % 64 or Cout % 64 or KH > 7 or KW > 7 or KH - 1 - p[0] < 0 or KW - 1 - p[0] < 0 or op[0] >= s[0]:
+        return False
+    return KH >= s[0] and KW >= s[0]                 # every parity class of the output sees at least one tap
+
+
+def conv_transpose2d(x, weight, bias=None, stride=1, padding=0, output_padding=0, groups: int = 1, dilation=1) -> torch.Tensor:
+    if conv_transpose2d_supported(x, weight, stride, padding, output_padding, dilation, groups):
+        try:
+            y = ConvTranspose2dFn.apply(x, weight, _one(stride), _one(padding), _one(output_padding))
+            return y if bias is None else y + bias.view(1, -1, 1, 1)
+        except RuntimeError as e:
+            if "not covered" not in str(e):
+                raise
+    return F.conv_transpose2d(x, weight, bias, stride, padding, output_padding, groups, dilation)

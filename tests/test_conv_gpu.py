@@ -84,3 +84,42 @@ def test_small_cin_conv_im2col_gemm(N, Cin, H, W, Cout, k, s, p):
     assert rel_err(w.grad, wr.grad) < 2e-2 and rel_err(b.grad, br.grad) < 2e-2
     assert not im2col_supported(x.clone().requires_grad_(True), w0, s, p)       # an input gradient is not provided
     _native.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("L,K,s,p", [(100, 3, 1, 1), (257, 5, 2, 2), (64, 1, 1, 0), (90, 7, 1, 3)])
+def test_conv1d_native(L, K, s, p):
+    from rustorch_b200.ops.conv import conv1d
+    torch.manual_seed(0)
+    x = torch.randn(3, 64, L, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(128, 64, K, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    b = torch.randn(128, device="cuda").bfloat16().requires_grad_(True)
+    y = conv1d(x, w, b, s, p)
+    dy = torch.randn_like(y)
+    gx, gw, gb = torch.autograd.grad(y, (x, w, b), dy)
+    xr, wr, br = (t.detach().float().cpu().requires_grad_(True) for t in (x, w, b))
+    yr = F.conv1d(xr, wr, br, s, p)
+    rx, rw, rb = torch.autograd.grad(yr, (xr, wr, br), dy.float().cpu())
+    for got, ref in ((y, yr), (gx, rx), (gw, rw), (gb, rb)):
+        assert got.shape == ref.shape
+        assert rel_err(got.float().cpu(), ref) < 2e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("K,s,p,op", [(3, 1, 1, 0), (4, 2, 1, 0), (3, 2, 1, 1), (6, 3, 2, 1), (2, 2, 0, 0)])
+def test_conv_transpose2d_native(K, s, p, op):
+    from rustorch_b200.ops.conv import conv_transpose2d, conv_transpose2d_supported
+    torch.manual_seed(0)
+    x = torch.randn(2, 64, 9, 11, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(64, 128, K, K, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    b = torch.randn(128, device="cuda").bfloat16()
+    assert conv_transpose2d_supported(x, w, s, p, op, 1, 1)
+    y = conv_transpose2d(x, w, b, s, p, op)
+    dy = torch.randn_like(y)
+    gx, gw = torch.autograd.grad(y, (x, w), dy)
+    xr, wr = (t.detach().float().cpu().requires_grad_(True) for t in (x, w))
+    yr = F.conv_transpose2d(xr, wr, b.float().cpu(), s, p, op)
+    rx, rw = torch.autograd.grad(yr, (xr, wr), dy.float().cpu())
+    for got, ref in ((y, yr), (gx, rx), (gw, rw)):
+        assert got.shape == ref.shape
+        assert rel_err(got.float().cpu(), ref) < 2e-2

@@ -148,3 +148,42 @@ def test_llama_model_native_path_matches_fp32_reference():
         ga = pa.grad if pa.grad is not None else getattr(pa, "main_grad", None)
         if ga is not None and pb.grad is not None:
             assert rel_err(ga, pb.grad) < 8e-2, n
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape,groups", [((4, 32, 14, 14), 8), ((3, 12, 7, 5), 4), ((2, 16, 33), 16), ((5, 6, 3, 4, 4), 3)])
+def test_group_norm_native(dtype, shape, groups):
+    from rustorch_b200.ops.groupnorm import group_norm
+    torch.manual_seed(0)
+    x = (torch.randn(*shape, device="cuda") * 2 + 0.5).to(dtype).requires_grad_(True)
+    w = (torch.rand(shape[1], device="cuda") + 0.5).to(dtype).requires_grad_(True)
+    b = torch.randn(shape[1], device="cuda").to(dtype).requires_grad_(True)
+    dy = torch.randn(*shape, device="cuda").to(dtype)
+    y = group_norm(x, groups, w, b, 1e-5)
+    gx, gw, gb = torch.autograd.grad(y, (x, w, b), dy)
+    xr, wr, br = (t.detach().cpu().float().requires_grad_(True) for t in (x, w, b))
+    yr = torch.nn.functional.group_norm(xr, groups, wr, br, 1e-5)
+    rx, rw, rb = torch.autograd.grad(yr, (xr, wr, br), dy.cpu().float())
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    for got, ref in ((y, yr), (gx, rx), (gw, rw), (gb, rb)):
+        err = (got.detach().cpu().float() - ref.detach()).abs().max() / ref.detach().abs().max().clamp_min(1e-6)
+        assert float(err) < tol, float(err)
+
+
+@pytest.mark.gpu
+def test_instance_norm_layers_native():
+    from rustorch_b200 import nn as rnn
+    torch.manual_seed(1)
+    for layer, shape in ((rnn.InstanceNorm1d(8, affine=True), (3, 8, 50)), (rnn.InstanceNorm2d(6), (2, 6, 9, 11)),
+                         (rnn.InstanceNorm3d(4, affine=True), (2, 4, 3, 5, 6))):
+        layer = layer.cuda()
+        x = torch.randn(*shape, device="cuda", requires_grad=True)
+        y = layer(x)
+        y.square().sum().backward()
+        xr = x.detach().cpu().requires_grad_(True)
+        yr = torch.nn.functional.instance_norm(xr, None, None, None if layer.weight is None else layer.weight.detach().cpu(),
+                                               None if layer.bias is None else layer.bias.detach().cpu(), True, 0.0, layer.eps)
+        yr.square().sum().backward()
+        assert torch.allclose(y.detach().cpu(), yr.detach(), atol=1e-4, rtol=1e-4)
+        assert torch.allclose(x.grad.cpu(), xr.grad, atol=2e-3, rtol=1e-3)

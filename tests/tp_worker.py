@@ -43,8 +43,11 @@ def main():
         worst_ag = max(worst_ag, rel(y, ref))
         assert torch.equal(ag.gather, Xi)
         H = torch.nn.functional.gelu(Xi.float() @ Wc.float().t() + bc.float(), approximate="tanh").bfloat16()
-        out = rs(H[:, rank * ffl:(rank + 1) * ffl].contiguous(), Wr[:, rank * ffl:(rank + 1) * ffl].contiguous(), br)
+        resid = Xi[rank * rows:(rank + 1) * rows].contiguous() if it == 1 else None      # fused residual on one of the epochs
+        out = rs(H[:, rank * ffl:(rank + 1) * ffl].contiguous(), Wr[:, rank * ffl:(rank + 1) * ffl].contiguous(), br, residual=resid)
         ref2 = (H.float() @ Wr.float().t() + br.float())[rank * rows:(rank + 1) * rows]
+        if resid is not None:
+            ref2 = ref2 + resid.float()
         worst_rs = max(worst_rs, rel(out, ref2))
     res["ag_rel"], res["rs_rel"] = worst_ag, worst_rs
     # ---- layers with autograd
@@ -137,7 +140,8 @@ def main():
     res["arn_x_rel"], res["arn_h_rel"] = worst_x, worst_h
     # ---- quantised Llama runtime: tensor-parallel prefill + CUDA-graph decode against the unsharded runtime
     from rustorch_b200.llm import LlamaConfig, LlamaRuntime
-    qcfg = LlamaConfig(vocab_size=256, n_layer=2, n_embd=256, n_head=4, n_head_kv=4 if world > 2 else 2, n_ff=1024, context_length=128)
+    qh = max(4, world)                                   # heads (and KV heads beyond two ranks) must split over the ranks
+    qcfg = LlamaConfig(vocab_size=256, n_layer=2, n_embd=64 * qh, n_head=qh, n_head_kv=qh if world > 2 else 2, n_ff=256 * qh, context_length=128)
     rt_full = LlamaRuntime.random_init(qcfg, dev, seed=5, std=0.08)
     rt_tp = LlamaRuntime.random_init(qcfg, dev, tp_rank=rank, tp_world=world, tp_group=dist.group.WORLD, seed=5, std=0.08)
     prompt = torch.randint(0, 256, (2, 70), generator=torch.Generator().manual_seed(1))
@@ -149,7 +153,8 @@ def main():
     # ---- Llama block stack, tensor + sequence parallel, against the unsharded model
     from rustorch_b200.models.llama import LlamaModel, LlamaTrainConfig
     torch.manual_seed(7)
-    cfg = LlamaTrainConfig.tiny(n_layer=2, n_embd=256, n_head=4, n_head_kv=2, n_ff=512, vocab_size=512)
+    th = max(4, world)
+    cfg = LlamaTrainConfig.tiny(n_layer=2, n_embd=64 * th, n_head=th, n_head_kv=max(2, world), n_ff=128 * th, vocab_size=512)
     Bq, Tq = 2, 64 * world
     full = LlamaModel(cfg, device=dev, dtype=torch.bfloat16)
     for p_ in full.parameters():
