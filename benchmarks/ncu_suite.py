@@ -100,6 +100,44 @@ def case_conv():
     w = (bf(128, 128, 3, 3) * 0.1).contiguous(memory_format=torch.channels_last).requires_grad_(True)
     y = Conv2dFn.apply(x, w, None, 1, 1)
     y.backward(torch.ones_like(y))                                # input gradient (forward kernel) + weight gradient
+    del x, w, y
+    # 64-channel 3 x 3 layer: resident-halo forward / input gradient, three-tap weight gradient
+    x = bf(256, 64, 56, 56).contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    w = (bf(64, 64, 3, 3) * 0.1).contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    y = Conv2dFn.apply(x, w, None, 1, (1, 1))
+    y.backward(torch.ones_like(y))
+    del x, w, y
+    # strided layer: input gradient as parity-class convolutions scattered into dx
+    x = bf(256, 64, 56, 56).contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    w = (bf(128, 64, 3, 3) * 0.1).contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    y = Conv2dFn.apply(x, w, None, 2, (1, 1))
+    y.backward(torch.ones_like(y))
+    del x, w, y
+    # stem: patch matrix + tcgen05 GEMM
+    from rustorch_b200.ops.conv import conv2d
+    x = bf(256, 3, 224, 224).contiguous(memory_format=torch.channels_last)
+    w = (bf(64, 3, 7, 7) * 0.1).contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    y = conv2d(x, w, None, 2, 3)
+    y.backward(torch.ones_like(y))
+
+
+def case_pool_groupnorm_rnn():
+    from rustorch_b200.ops import pool
+    from rustorch_b200.ops.groupnorm import group_norm
+    from rustorch_b200.ops.rnn import lstm_gates
+    x = bf(256, 64, 112, 112).contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    y = pool.max_pool2d(x, 3, 2, 1)
+    y.backward(torch.ones_like(y))
+    z = pool.adaptive_avg_pool2d(bf(256, 512, 7, 7).contiguous(memory_format=torch.channels_last), 1)
+    pool.dropout(bf(1 << 27), 0.1, True)
+    del x, y, z
+    g = bf(64, 256, 56, 56).requires_grad_(True)
+    wg, bg = torch.ones(256, device="cuda", requires_grad=True), torch.zeros(256, device="cuda", requires_grad=True)
+    o = group_norm(g, 32, wg, bg)
+    o.backward(torch.ones_like(o))
+    gates, c0 = bf(65536, 4 * 1024).requires_grad_(True), bf(65536, 1024)
+    h, c = lstm_gates(gates, c0)
+    (h.sum() + c.sum()).backward()
 
 
 def case_quant_decode():
@@ -114,7 +152,11 @@ def case_quant_decode():
             C.q_gemv(q.qs, q.scales, x, yv, None, None, qt == gguf.GGMLType.Q8_0, path=1)
             if M == 4:
                 C.q_gemv(q.qs, q.scales, x, yv, None, None, qt == gguf.GGMLType.Q8_0, path=2)
-        q((torch.randn(32, 4096, device="cuda") * 0.5).half())     # dequant-fused tcgen05 GEMM (batched decode)
+        q((torch.randn(32, 4096, device="cuda") * 0.5).half())     # dequant-fused tcgen05 GEMM (batched decode), A from TMEM
+        if qt == gguf.GGMLType.Q4_0:
+            part, cnt = q._tc_buffers(32)                          # the shared-memory-A variant of the same GEMM
+            x32 = (torch.randn(32, 4096, device="cuda") * 0.5).half()
+            C.q_gemm_tc(q.qs, q.scales, x32, torch.empty(32, 22016, device="cuda", dtype=torch.half), None, None, False, part, cnt, path=1)
         q((torch.randn(512, 4096, device="cuda") * 0.5).half())    # dequantise + tcgen05 GEMM (prefill path)
     cfg = LlamaConfig(n_layer=1)
     rt = LlamaRuntime.random_init(cfg, "cuda", seed=0)
@@ -145,7 +187,8 @@ def case_collectives_single_rank():
 
 
 CASES = {"gemm": case_gemm, "attn": case_attn, "norm": case_norm, "optim": case_optim, "loss": case_loss_embedding,
-         "elementwise": case_elementwise, "batchnorm": case_batchnorm, "conv": case_conv, "quant": case_quant_decode,
+         "elementwise": case_elementwise, "batchnorm": case_batchnorm, "conv": case_conv, "pool_gn_rnn": case_pool_groupnorm_rnn,
+         "quant": case_quant_decode,
          "collectives": case_collectives_single_rank}
 
 

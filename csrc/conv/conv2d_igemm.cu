@@ -245,6 +245,186 @@ conv_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
   }
 }
 
+// ------------------------------------------------------------------------------- forward, resident halo
+// 3 x 3, stride 1, padding 1, 64 input channels: the general kernel above fetches the input tile once per filter
+// tap (nine boxes per output tile), which makes the 64-channel layers L2 -> shared-memory bound.  Here the image
+// is read as rows that are two pixels wider than the image (the TMA box starts at column -1 and zero-fills the
+// border), so in the flattened, padded pixel order q = row * (W + 2) + col the tap (kh, kw) of output q is
+// input q + kh (W + 2) + kw: every tap's A operand is the SAME shared-memory halo tile, shifted by whole
+// 128-byte pixel rows.  One box per tile (all rows the 128 outputs touch), nine descriptor offsets, and the
+// 9 x BLOCK_N x 64 filter stays resident in shared memory for the CTA's lifetime.  Outputs that fall on the
+// two padding columns are computed and dropped (2 / (W + 2) of the tile).
+struct HaloParams {
+  int N, H, W, Cout, PW, R;          // PW = W + 2, R = rows per halo box
+  int tiles_per_img, n_blocks;
+  int halo_bytes, stages;            // bytes of one halo stage (multiple of 1024)
+  int base_offset_mode;              // 1: descriptors carry (address >> 7) & 7 as the matrix base offset
+  __nv_bfloat16* out;
+  const __nv_bfloat16* bias;
+  long long out_sn, out_sh, out_sw;
+  int* status;
+};
+
+__device__ __forceinline__ uint64_t make_smem_desc_sw128_rows(uint32_t smem_addr, int base_offset_mode) {
+  uint64_t d = make_smem_desc_sw128(smem_addr, 16, 1024);
+  if (base_offset_mode) d |= static_cast<uint64_t>((smem_addr >> 7) & 7) << 49;
+  return d;
+}
+
+template <int BLOCK_N>
+__global__ void __launch_bounds__(CV_THREADS, 1)
+conv_fwd_halo_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, const HaloParams p) {
+  constexpr int W_BYTES = 9 * BLOCK_N * 128;
+  constexpr int MAX_STAGES = 4;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, RT_ERR_BOUNDS);
+    return;
+  }
+  uint8_t* halo = smem + W_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(halo + (size_t)p.stages * p.halo_bytes);
+  uint64_t* empty_bar = full_bar + MAX_STAGES;
+  uint64_t* tmem_full = empty_bar + MAX_STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint64_t* w_bar = tmem_empty + 2;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(w_bar + 1);
+  CtaCtl* ctl = reinterpret_cast<CtaCtl*>(tmem_base_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;
+  const int STAGES = p.stages;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < MAX_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 8);
+    }
+    mbar_init(w_bar, 1);
+    ctl->abort = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_x);
+    tma_prefetch_desc(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  // a CTA keeps one block of output channels (its filter stays resident) and walks the pixel tiles
+  const int nb = (int)blockIdx.x % p.n_blocks;
+  const int first = (int)blockIdx.x / p.n_blocks, step = (int)gridDim.x / p.n_blocks;
+  const int m_tiles = p.N * p.tiles_per_img;
+
+  if (warp == 0) {
+    if (lane == 0 && first < m_tiles) {
+      mbar_arrive_expect_tx(w_bar, W_BYTES);
+      for (int tap = 0; tap < 9; ++tap) tma_load_3d(smem + tap * BLOCK_N * 128, &tmap_w, w_bar, tap * 64, nb * BLOCK_N, 0);
+      uint32_t it = 0;
+      for (int mt = first; mt < m_tiles; mt += step, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) break;
+        const int n = mt / p.tiles_per_img, p0 = (mt - n * p.tiles_per_img) * 128;
+        mbar_arrive_expect_tx(&full_bar[s], (uint32_t)p.R * p.PW * 128);
+        tma_load_4d(halo + (size_t)s * p.halo_bytes, &tmap_x, &full_bar[s], 0, -1, p0 / p.PW - 1, n);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && first < m_tiles) {
+      constexpr uint32_t idesc = make_idesc_f16(128, BLOCK_N, false, false, true);
+      bool ok = mbar_wait(w_bar, 0, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+      uint32_t it = 0;
+      for (int mt = first; mt < m_tiles && ok; mt += step, ++it) {
+        const uint32_t acc = it & 1, acc_ph = (it >> 1) & 1;
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, ctl, p.status, RT_ERR_TIMEOUT_MMA) ||
+            !mbar_wait(&full_bar[s], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const int p0 = (mt % p.tiles_per_img) * 128;
+        const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+        const uint32_t sh = smem_u32(halo + (size_t)s * p.halo_bytes) + (uint32_t)(p0 % p.PW) * 128;
+        const uint32_t sw = smem_u32(smem);
+#pragma unroll 1
+        for (int tap = 0; tap < 9; ++tap) {
+          const int kh = tap / 3, kw = tap - kh * 3;
+          const uint32_t sa = sh + (uint32_t)(kh * p.PW + kw) * 128;
+          const uint32_t sb = sw + tap * BLOCK_N * 128;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16_ss(d_tmem, make_smem_desc_sw128_rows(sa + kk * 32, p.base_offset_mode), make_smem_desc_sw128(sb + kk * 32, 16, 1024),
+                        idesc, (tap > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);
+        umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3, col_half = (warp - 2) >> 2;
+    const int r = quarter * 32 + lane;
+    uint32_t it = 0;
+    for (int mt = first; mt < m_tiles; mt += step, ++it) {
+      const uint32_t acc = it & 1, acc_ph = (it >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_ph, ctl, p.status, RT_ERR_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      const int n = mt / p.tiles_per_img, q = (mt - n * p.tiles_per_img) * 128 + r;
+      const int oh = q / p.PW, ow = q - oh * p.PW;
+      const bool row_ok = oh < p.H && ow < p.W;
+      __nv_bfloat16* orow = p.out + n * p.out_sn + oh * p.out_sh + ow * p.out_sw;
+#pragma unroll 1
+      for (int c = col_half * (BLOCK_N / 64); c < (col_half + 1) * (BLOCK_N / 64); ++c) {
+        const int c0 = nb * BLOCK_N + c * 32;
+        if (c0 >= p.Cout) break;
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(tmem_base + acc * BLOCK_N + c * 32 + (uint32_t(quarter * 32) << 16), v);
+        tmem_ld_wait();
+        if (row_ok) {
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] += __bfloat162float(p.bias[c0 + j]);
+          }
+          uint4* d4 = reinterpret_cast<uint4*>(orow + c0);
+#pragma unroll
+          for (int qd = 0; qd < 4; ++qd) {
+            uint4 w;
+            w.x = pack_bf16x2(f[qd * 8 + 0], f[qd * 8 + 1]);
+            w.y = pack_bf16x2(f[qd * 8 + 2], f[qd * 8 + 3]);
+            w.z = pack_bf16x2(f[qd * 8 + 4], f[qd * 8 + 5]);
+            w.w = pack_bf16x2(f[qd * 8 + 6], f[qd * 8 + 7]);
+            d4[qd] = w;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+  __syncwarp();
+  if (ctl->abort) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------------------------------ wgrad
 // One CTA = one output tile (128 out-channels x BLOCK_N in-channels of one tap) x one slice of the pixel tiles.
 // k-block = 64 output pixels (TW*TH*TN = 64).
@@ -598,6 +778,44 @@ void launch_wgrad3(const Conv2dArgs& a, ConvParams& p, int device, cudaStream_t 
   RT_LAUNCH_CHECK();
 }
 
+// 3 x 3 / stride 1 / pad 1 / 64 input channels / Cout a multiple of 64: the resident-halo kernel.  Returns false when
+// the layer does not qualify or the tiles do not fit in shared memory (the general kernel takes it then).
+// RUSTORCH_CONV_HALO: 0 = off, 1 = descriptors without base offset, 2 (default) = with the matrix base offset.
+template <int BLOCK_N>
+bool launch_fwd_halo(const Conv2dArgs& a, const ConvParams& cp, int mode, int device, cudaStream_t stream) {
+  HaloParams p{};
+  p.N = a.N; p.H = a.H; p.W = a.W; p.Cout = a.Cout;
+  p.PW = a.W + 2;
+  p.R = (127 + 2 * p.PW + 2) / p.PW + 2;
+  if (p.PW > 256 || p.R > 256) return false;
+  p.tiles_per_img = (a.H * p.PW + 127) / 128;
+  p.n_blocks = a.Cout / BLOCK_N;
+  p.halo_bytes = ((p.R * p.PW * 128) + 1023) / 1024 * 1024;
+  constexpr int W_BYTES = 9 * BLOCK_N * 128;
+  const int bar_bytes = (2 * 4 + 5) * 8 + 16;
+  const int room = 232448 - W_BYTES - bar_bytes;
+  p.stages = std::min(4, room / p.halo_bytes);
+  if (p.stages < 2) return false;
+  p.base_offset_mode = mode == 2;
+  p.out = cp.out; p.bias = cp.bias; p.status = cp.status;
+  p.out_sn = cp.out_sn; p.out_sh = cp.out_sh; p.out_sw = cp.out_sw;
+  const int smem_total = W_BYTES + p.stages * p.halo_bytes + bar_bytes;
+  auto kern = conv_fwd_halo_kernel<BLOCK_N>;
+  static bool configured[64] = {false};
+  if (!configured[device & 63]) {
+    RT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+    configured[device & 63] = true;
+  }
+  const CUtensorMap tx = make_tmap_nhwc(a.x, a.Cin, a.W, a.H, a.N, p.PW, p.R, 1, 1);
+  const CUtensorMap tw = make_tmap_2byte(a.w, (uint64_t)9 * a.Cin, a.Cout, 1, (uint64_t)9 * a.Cin, 0, 64, BLOCK_N);
+  const int m_tiles = p.N * p.tiles_per_img;
+  int grid = std::min(m_tiles * p.n_blocks, sm_count(device));
+  grid = std::max(p.n_blocks, grid / p.n_blocks * p.n_blocks);
+  kern<<<grid, CV_THREADS, smem_total, stream>>>(tx, tw, p);
+  RT_LAUNCH_CHECK();
+  return true;
+}
+
 }  // namespace
 
 bool conv2d_igemm_supported(int Cin, int Cout, int KH, int KW, int stride) {
@@ -612,6 +830,16 @@ void conv2d_fwd(const Conv2dArgs& a, cudaStream_t stream) {
   p.out = reinterpret_cast<__nv_bfloat16*>(a.out);
   p.bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
   p.status = status_word(device);
+  static const int halo_mode = [] {
+    const char* e = std::getenv("RUSTORCH_CONV_HALO");
+    return e ? std::atoi(e) : 2;
+  }();
+  const int pad_h = a.pad_h >= 0 ? a.pad_h : a.pad;
+  if (halo_mode > 0 && a.Cin == 64 && a.KH == 3 && a.KW == 3 && a.stride == 1 && a.pad == 1 && pad_h == 1 && a.out_h == 0 &&
+      a.out_w == 0 && a.Cout % 64 == 0) {
+    if (a.Cout % 128 == 0 ? launch_fwd_halo<128>(a, p, halo_mode, device, stream) : launch_fwd_halo<64>(a, p, halo_mode, device, stream))
+      return;
+  }
   if (a.Cout <= 64) launch_fwd<64>(a, p, device, stream);
   else if (a.Cout <= 128) launch_fwd<128>(a, p, device, stream);
   else launch_fwd<256>(a, p, device, stream);

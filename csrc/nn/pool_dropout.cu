@@ -52,43 +52,84 @@ __device__ __forceinline__ void pstore(T* p, const float (&f)[PVec<T>::N]) {
 }
 
 // ------------------------------------------------------------------------------------------------ pooling
-template <typename T, bool MAX>
+// K, S: square window and stride known at compile time (0 = read them from the arguments).  With constants the tap
+// loops unroll, so all window loads of a thread are in flight together and the index arithmetic has no divisions
+// by runtime strides.
+template <typename T, bool MAX, int K, int S>
 __global__ void __launch_bounds__(256) pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, unsigned char* __restrict__ idx,
                                                        const Pool2dArgs a) {
   constexpr int V = PVec<T>::N;
   const int cv = a.C / V;
+  const int KH = K ? K : a.kh, KW = K ? K : a.kw, SH = S ? S : a.sh, SW = S ? S : a.sw;
   const long long total = (long long)a.N * a.OH * a.OW * cv;
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
-    const int c = (int)(t % cv) * V;
-    long long pix = t / cv;
-    const int ow = (int)(pix % a.OW);
-    pix /= a.OW;
-    const int oh = (int)(pix % a.OH), n = (int)(pix / a.OH);
+    int c, ow, oh, n;
+    if (total < 0x7fffffffLL) {
+      const unsigned tt = (unsigned)t, pix = tt / (unsigned)cv, row = pix / (unsigned)a.OW;
+      c = (int)(tt - pix * cv) * V;
+      ow = (int)(pix - row * a.OW);
+      n = (int)(row / (unsigned)a.OH);
+      oh = (int)(row - (unsigned)n * a.OH);
+    } else {
+      c = (int)(t % cv) * V;
+      long long pix = t / cv;
+      ow = (int)(pix % a.OW);
+      pix /= a.OW;
+      oh = (int)(pix % a.OH);
+      n = (int)(pix / a.OH);
+    }
     float acc[V];
     __align__(8) unsigned char best[V];
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = MAX ? -INFINITY : 0.f, best[i] = 0;
-    const int h0 = oh * a.sh - a.ph, w0 = ow * a.sw - a.pw;
-    for (int kh = 0; kh < a.kh; ++kh) {
-      const int ih = h0 + kh;
-      if (ih < 0 || ih >= a.H) continue;
-      for (int kw = 0; kw < a.kw; ++kw) {
-        const int iw = w0 + kw;
-        if (iw < 0 || iw >= a.W) continue;
-        float v[V];
-        pload(x + (((long long)n * a.H + ih) * a.W + iw) * a.C + c, v);
+    const int h0 = oh * SH - a.ph, w0 = ow * SW - a.pw;
+    const T* xn = x + (long long)n * a.H * a.W * a.C + c;
+    if (K) {
+      // all taps loaded first (out-of-image taps are skipped by predicate), then reduced in tap order
+      float v[(K ? K * K : 1)][V];
+      bool in[(K ? K * K : 1)];
+#pragma unroll
+      for (int kh = 0; kh < K; ++kh)
+#pragma unroll
+        for (int kw = 0; kw < K; ++kw) {
+          const int ih = h0 + kh, iw = w0 + kw;
+          in[kh * K + kw] = ih >= 0 && ih < a.H && iw >= 0 && iw < a.W;
+          if (in[kh * K + kw]) pload(xn + ((long long)ih * a.W + iw) * a.C, v[kh * K + kw]);
+        }
+#pragma unroll
+      for (int tap = 0; tap < K * K; ++tap) {
+        if (!in[tap]) continue;
 #pragma unroll
         for (int i = 0; i < V; ++i) {
           if (MAX) {
-            if (v[i] > acc[i] || v[i] != v[i]) acc[i] = v[i], best[i] = (unsigned char)(kh * a.kw + kw);
+            if (v[tap][i] > acc[i] || v[tap][i] != v[tap][i]) acc[i] = v[tap][i], best[i] = (unsigned char)tap;
           } else {
-            acc[i] += v[i];
+            acc[i] += v[tap][i];
+          }
+        }
+      }
+    } else {
+      for (int kh = 0; kh < KH; ++kh) {
+        const int ih = h0 + kh;
+        if (ih < 0 || ih >= a.H) continue;
+        for (int kw = 0; kw < KW; ++kw) {
+          const int iw = w0 + kw;
+          if (iw < 0 || iw >= a.W) continue;
+          float v[V];
+          pload(xn + ((long long)ih * a.W + iw) * a.C, v);
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            if (MAX) {
+              if (v[i] > acc[i] || v[i] != v[i]) acc[i] = v[i], best[i] = (unsigned char)(kh * KW + kw);
+            } else {
+              acc[i] += v[i];
+            }
           }
         }
       }
     }
     if (!MAX) {
-      const float inv = 1.f / (float)(a.kh * a.kw);
+      const float inv = 1.f / (float)(KH * KW);
 #pragma unroll
       for (int i = 0; i < V; ++i) acc[i] *= inv;
     }
@@ -101,13 +142,14 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const T* __restrict__ x, 
   }
 }
 
-template <typename T, bool MAX>
+template <typename T, bool MAX, int K, int S>
 __global__ void __launch_bounds__(256) pool_bwd_kernel(const T* __restrict__ dy, const unsigned char* __restrict__ idx,
                                                        T* __restrict__ dx, const Pool2dArgs a) {
   constexpr int V = PVec<T>::N;
   const int cv = a.C / V;
+  const int KH = K ? K : a.kh, KW = K ? K : a.kw, SH = S ? S : a.sh, SW = S ? S : a.sw;
   const long long total = (long long)a.N * a.H * a.W * cv;
-  const float inv = 1.f / (float)(a.kh * a.kw);
+  const float inv = 1.f / (float)(KH * KW);
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
     int c, iw, ih, n;
     if (total < 0x7fffffffLL) {                      // 32-bit divisions (an order of magnitude cheaper than 64-bit ones)
@@ -128,28 +170,69 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const T* __restrict__ dy,
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = 0.f;
     // outputs whose window contains (ih, iw): oh in [ceil((ih + ph - kh + 1) / sh), floor((ih + ph) / sh)]
-    const int oh_hi = min(a.OH - 1, (ih + a.ph) / a.sh), ow_hi = min(a.OW - 1, (iw + a.pw) / a.sw);
-    const int oh_lo = max(0, (ih + a.ph - a.kh + a.sh) / a.sh), ow_lo = max(0, (iw + a.pw - a.kw + a.sw) / a.sw);
-    for (int oh = oh_lo; oh <= oh_hi; ++oh) {
-      const int kh = ih + a.ph - oh * a.sh;
-      if (kh < 0 || kh >= a.kh) continue;
-      for (int ow = ow_lo; ow <= ow_hi; ++ow) {
-        const int kw = iw + a.pw - ow * a.sw;
-        if (kw < 0 || kw >= a.kw) continue;
-        const long long o = (((long long)n * a.OH + oh) * a.OW + ow) * a.C + c;
-        float g[V];
-        pload(dy + o, g);
-        if (MAX) {
-          const unsigned char me = (unsigned char)(kh * a.kw + kw);
-          __align__(8) unsigned char rec[V];         // V consecutive bytes: one 4- or 8-byte load
-          if (V == 8) *reinterpret_cast<uint2*>(rec) = *reinterpret_cast<const uint2*>(idx + o);
-          else *reinterpret_cast<unsigned*>(rec) = *reinterpret_cast<const unsigned*>(idx + o);
+    const int oh_top = (ih + a.ph) / SH, ow_top = (iw + a.pw) / SW;
+    const T* gn = dy + (long long)n * a.OH * a.OW * a.C + c;
+    const unsigned char* in_ = idx ? idx + (long long)n * a.OH * a.OW * a.C + c : nullptr;
+    if (K) {
+      constexpr int NC = K ? (K + (S ? S : 1) - 1) / (S ? S : 1) : 1;   // candidate outputs per direction
+      float g[NC * NC][V];
+      __align__(8) unsigned char rec[NC * NC][8];
+      bool in[NC * NC];
+      unsigned char me[NC * NC];
 #pragma unroll
-          for (int i = 0; i < V; ++i)
-            if (rec[i] == me) acc[i] += g[i];
-        } else {
+      for (int jh = 0; jh < NC; ++jh)
 #pragma unroll
-          for (int i = 0; i < V; ++i) acc[i] += g[i] * inv;
+        for (int jw = 0; jw < NC; ++jw) {
+          const int q = jh * NC + jw;
+          const int oh = oh_top - jh, ow = ow_top - jw;
+          const int kh = ih + a.ph - oh * SH, kw = iw + a.pw - ow * SW;     // >= 0 by construction
+          in[q] = oh >= 0 && oh < a.OH && ow >= 0 && ow < a.OW && kh < K && kw < K;
+          me[q] = (unsigned char)(kh * K + kw);
+          if (in[q]) {
+            const long long o = ((long long)oh * a.OW + ow) * a.C;
+            pload(gn + o, g[q]);
+            if (MAX) {
+              if (V == 8) *reinterpret_cast<uint2*>(rec[q]) = *reinterpret_cast<const uint2*>(in_ + o);
+              else *reinterpret_cast<unsigned*>(rec[q]) = *reinterpret_cast<const unsigned*>(in_ + o);
+            }
+          }
+        }
+#pragma unroll
+      for (int q = NC * NC - 1; q >= 0; --q) {     // ascending (oh, ow), the order of the runtime path
+        if (!in[q]) continue;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          if (MAX) {
+            if (rec[q][i] == me[q]) acc[i] += g[q][i];
+          } else {
+            acc[i] += g[q][i] * inv;
+          }
+        }
+      }
+    } else {
+      const int oh_hi = min(a.OH - 1, oh_top), ow_hi = min(a.OW - 1, ow_top);
+      const int oh_lo = max(0, (ih + a.ph - KH + SH) / SH), ow_lo = max(0, (iw + a.pw - KW + SW) / SW);
+      for (int oh = oh_lo; oh <= oh_hi; ++oh) {
+        const int kh = ih + a.ph - oh * SH;
+        if (kh < 0 || kh >= KH) continue;
+        for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+          const int kw = iw + a.pw - ow * SW;
+          if (kw < 0 || kw >= KW) continue;
+          const long long o = ((long long)oh * a.OW + ow) * a.C;
+          float g[V];
+          pload(gn + o, g);
+          if (MAX) {
+            const unsigned char me = (unsigned char)(kh * KW + kw);
+            __align__(8) unsigned char rec[V];         // V consecutive bytes: one 4- or 8-byte load
+            if (V == 8) *reinterpret_cast<uint2*>(rec) = *reinterpret_cast<const uint2*>(in_ + o);
+            else *reinterpret_cast<unsigned*>(rec) = *reinterpret_cast<const unsigned*>(in_ + o);
+#pragma unroll
+            for (int i = 0; i < V; ++i)
+              if (rec[i] == me) acc[i] += g[i];
+          } else {
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] += g[i] * inv;
+          }
         }
       }
     }
@@ -209,19 +292,27 @@ void pool2d(const Pool2dArgs& a, cudaStream_t stream) {
   const long long work = (long long)a.N * (a.backward ? (long long)a.H * a.W : (long long)a.OH * a.OW) * (a.C / V);
   if (work == 0) return;
   const int grid = grid_for(work, device);
-#define RT_POOL(T)                                                                                                              \
+#define RT_POOL(T, K, S)                                                                                                              \
   do {                                                                                                                          \
     if (!a.backward) {                                                                                                          \
-      if (a.max) pool_fwd_kernel<T, true><<<grid, 256, 0, stream>>>((const T*)a.x, (T*)a.y, a.idx, a);                          \
-      else pool_fwd_kernel<T, false><<<grid, 256, 0, stream>>>((const T*)a.x, (T*)a.y, nullptr, a);                             \
+      if (a.max) pool_fwd_kernel<T, true, K, S><<<grid, 256, 0, stream>>>((const T*)a.x, (T*)a.y, a.idx, a);                    \
+      else pool_fwd_kernel<T, false, K, S><<<grid, 256, 0, stream>>>((const T*)a.x, (T*)a.y, nullptr, a);                       \
     } else {                                                                                                                    \
-      if (a.max) pool_bwd_kernel<T, true><<<grid, 256, 0, stream>>>((const T*)a.y, a.idx, (T*)a.x, a);                          \
-      else pool_bwd_kernel<T, false><<<grid, 256, 0, stream>>>((const T*)a.y, nullptr, (T*)a.x, a);                             \
+      if (a.max) pool_bwd_kernel<T, true, K, S><<<grid, 256, 0, stream>>>((const T*)a.y, a.idx, (T*)a.x, a);                    \
+      else pool_bwd_kernel<T, false, K, S><<<grid, 256, 0, stream>>>((const T*)a.y, nullptr, (T*)a.x, a);                       \
     }                                                                                                                           \
   } while (0)
-  if (a.dtype == DT_F32) RT_POOL(float);
-  else if (a.dtype == DT_BF16) RT_POOL(__nv_bfloat16);
-  else RT_POOL(__half);
+#define RT_POOL_T(K, S)                                                                                                         \
+  do {                                                                                                                          \
+    if (a.dtype == DT_F32) RT_POOL(float, K, S);                                                                                \
+    else if (a.dtype == DT_BF16) RT_POOL(__nv_bfloat16, K, S);                                                                  \
+    else RT_POOL(__half, K, S);                                                                                                 \
+  } while (0)
+  const bool square = a.kh == a.kw && a.sh == a.sw;
+  if (square && a.kh == 3 && a.sh == 2) RT_POOL_T(3, 2);
+  else if (square && a.kh == 2 && a.sh == 2) RT_POOL_T(2, 2);
+  else RT_POOL_T(0, 0);
+#undef RT_POOL_T
 #undef RT_POOL
   RT_LAUNCH_CHECK();
 }

@@ -19,6 +19,8 @@ CASES = [
     (2, 64, 19, 23, 192, 3, 1, 1),      # odd spatial sizes, Cout not a multiple of 128
     (1, 128, 9, 9, 64, 5, 1, 2),
     (2, 64, 12, 12, 64, 1, 1, 0),
+    (2, 64, 112, 112, 64, 3, 1, 1),     # resident-halo kernel, two halo stages
+    (3, 64, 7, 9, 128, 3, 1, 1),        # resident-halo kernel, 128 output channels per CTA, images smaller than a tile
 ]
 
 
