@@ -95,6 +95,8 @@ class Conv2dFn(torch.autograd.Function):
         C.conv2d_fwd(xh, wh, out, bias, stride, pad_w, pad_h=pad_h)
         ctx.save_for_backward(xh, wh)
         ctx.geom = (stride, pad, bias is not None, tuple(x.shape))
+        # flat-parameter training keeps conv filters in [Cout, KH, KW, Cin] order: dW accumulates straight into the fp32 buffer
+        ctx.main_grad = weight.main_grad if getattr(weight, "_flat_ohwi", False) and hasattr(weight, "main_grad") else None
         return out.permute(0, 3, 1, 2)                          # NCHW shape, channels-last memory
 
     @staticmethod
@@ -106,7 +108,9 @@ class Conv2dFn(torch.autograd.Function):
         dyh = _nhwc(dy)
         Cout, KH, KW, Cin = wh.shape
         dx = dw = db = None
-        if ctx.needs_input_grad[1]:
+        if ctx.needs_input_grad[1] and ctx.main_grad is not None:
+            C.conv2d_wgrad(xh, dyh, ctx.main_grad.view(Cout, KH, KW, Cin), stride, pad_w, pad_h=pad_h)
+        elif ctx.needs_input_grad[1]:
             dwf = torch.zeros(Cout, KH, KW, Cin, dtype=torch.float32, device=dyh.device)
             C.conv2d_wgrad(xh, dyh, dwf, stride, pad_w, pad_h=pad_h)
             dw = dwf.to(torch.bfloat16).permute(0, 3, 1, 2)    # back to [Cout, Cin, KH, KW] (channels-last memory)

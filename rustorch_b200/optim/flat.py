@@ -30,6 +30,10 @@ def default_decay_filter(name: str, p: torch.Tensor) -> bool:
     return p.dim() >= 2
 
 
+def _is_channels_last(t: torch.Tensor) -> bool:
+    return t.dim() == 4 and t.is_contiguous(memory_format=torch.channels_last) and not t.is_contiguous()
+
+
 class FlatParams:
     def __init__(self, module: torch.nn.Module, decay_filter: Callable = default_decay_filter,
                  alloc: Optional[Callable] = None, alloc_f32: Optional[Callable] = None,
@@ -69,11 +73,20 @@ class FlatParams:
         with torch.no_grad():
             for n, p, o, k in self.entries:
                 src = getattr(p, "_fp32_init", None)
-                self.master[o:o + k].copy_((src if src is not None else p.data).reshape(-1).float())
+                base = src if src is not None else p.data
+                # channels-last 4-D parameters (conv filters) keep their physical [Cout, KH, KW, Cin] order in the flat
+                # buffers, so the conv kernels read them without a copy and accumulate dW straight into ``main_grad``
+                cl = _is_channels_last(p.data)
+                self.master[o:o + k].copy_((base.permute(0, 2, 3, 1) if cl else base).reshape(-1).float())
                 if src is not None:
                     del p._fp32_init
                 self.lp[o:o + k].copy_(self.master[o:o + k])
-                p.data = self.lp[o:o + k].view(p.shape)
+                if cl:
+                    co, ci, kh, kw = p.shape
+                    p.data = self.lp[o:o + k].view(co, kh, kw, ci).permute(0, 3, 1, 2)
+                else:
+                    p.data = self.lp[o:o + k].view(p.shape)
+                p._flat_ohwi = cl
                 p.main_grad = self.grad[o:o + k]
                 p.grad = None
 
@@ -83,7 +96,8 @@ class FlatParams:
         n = 0
         for _, p, o, k in self.entries:
             if p.grad is not None:
-                self.grad[o:o + k].add_(p.grad.reshape(-1))
+                g = p.grad.permute(0, 2, 3, 1) if getattr(p, "_flat_ohwi", False) else p.grad
+                self.grad[o:o + k].add_(g.reshape(-1))
                 p.grad = None
                 n += 1
         return n
@@ -106,7 +120,12 @@ class FlatParams:
         return self.grad.norm().reshape(1)
 
     def named_views(self, buf: torch.Tensor) -> Dict[str, torch.Tensor]:
-        return {n: buf[o:o + k].view(p.shape) for n, p, o, k in self.entries}
+        def view(p, t):
+            if getattr(p, "_flat_ohwi", False):
+                co, ci, kh, kw = p.shape
+                return t.view(co, kh, kw, ci).permute(0, 3, 1, 2)
+            return t.view(p.shape)
+        return {n: view(p, buf[o:o + k]) for n, p, o, k in self.entries}
 
 
 class _FusedBase:

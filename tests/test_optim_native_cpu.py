@@ -61,3 +61,22 @@ def test_lbfgs_native_matches_python_two_loop():
         o1.step_tensor(x1, a * (x1 - 1))
         o2.step_tensor(x2, a.double() * (x2 - 1))
     torch.testing.assert_close(x1, x2.float(), rtol=1e-3, atol=1e-4)
+
+
+def test_flat_params_keep_channels_last_filters_in_physical_order():
+    from rustorch_b200.optim.flat import FlatParams
+    torch.manual_seed(0)
+    m = torch.nn.Sequential(torch.nn.Conv2d(4, 8, 3), torch.nn.Conv2d(8, 8, 1), torch.nn.Linear(8, 2)).to(memory_format=torch.channels_last)
+    w0 = m[0].weight.detach().clone()
+    flat = FlatParams(m)
+    assert m[0].weight._flat_ohwi and not m[2].weight._flat_ohwi
+    assert torch.equal(m[0].weight.data, w0) and m[0].weight.data.is_contiguous(memory_format=torch.channels_last)
+    # the flat slice IS the [Cout, KH, KW, Cin] array
+    _, p, o, k = next(e for e in flat.entries if e[0] == "0.weight")
+    assert torch.equal(flat.lp[o:o + k].view(8, 3, 3, 4), w0.permute(0, 2, 3, 1))
+    x = torch.randn(2, 4, 6, 6).contiguous(memory_format=torch.channels_last)
+    m[2](m[1](m[0](x)).mean((2, 3))).sum().backward()
+    g0 = m[0].weight.grad.clone()
+    assert flat.collect_autograd_grads() == 6
+    assert torch.allclose(flat.named_views(flat.grad)["0.weight"], g0)
+    assert torch.allclose(m[0].weight.main_grad.view(8, 3, 3, 4), g0.permute(0, 2, 3, 1))
