@@ -780,7 +780,9 @@ void launch_wgrad3(const Conv2dArgs& a, ConvParams& p, int device, cudaStream_t 
 
 // 3 x 3 / stride 1 / pad 1 / 64 input channels / Cout a multiple of 64: the resident-halo kernel.  Returns false when
 // the layer does not qualify or the tiles do not fit in shared memory (the general kernel takes it then).
-// RUSTORCH_CONV_HALO: 0 (default) = off, 1 = descriptors without base offset, 2 = with the matrix base offset.
+// RUSTORCH_CONV_HALO: 0 = off, 1 (default) = on.  The shifted descriptors carry no matrix base offset: the tensor core
+// applies the 128-byte swizzle to absolute shared-memory address bits, exactly as TMA wrote the tile (setting the
+// base-offset field to (address >> 7) & 7 as well gives wrong results; mode 2 keeps that variant for reference).
 template <int BLOCK_N>
 bool launch_fwd_halo(const Conv2dArgs& a, const ConvParams& cp, int mode, int device, cudaStream_t stream) {
   HaloParams p{};
@@ -832,7 +834,7 @@ void conv2d_fwd(const Conv2dArgs& a, cudaStream_t stream) {
   p.status = status_word(device);
   static const int halo_mode = [] {
     const char* e = std::getenv("RUSTORCH_CONV_HALO");
-    return e ? std::atoi(e) : 0;
+    return e ? std::atoi(e) : 1;
   }();
   const int pad_h = a.pad_h >= 0 ? a.pad_h : a.pad;
   if (halo_mode > 0 && a.Cin == 64 && a.KH == 3 && a.KW == 3 && a.stride == 1 && a.pad == 1 && pad_h == 1 && a.out_h == 0 &&
