@@ -52,9 +52,13 @@ struct GemmSmem {
   static constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BLOCK_N == 256) ? 4 : 6;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  // epilogue staging: 8 warps x (32 rows x 128 B), 16-byte pieces XOR-swizzled by the row
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int EPI_BYTES = 8 * 4096;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EPI_BYTES;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem base, ctl
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
+  static_assert(TOTAL <= 232448, "gemm: shared memory over the per-CTA limit");
 };
 
 __device__ __forceinline__ void decode_tile(int t, const GemmParams& p, int& split, int& b,
@@ -228,27 +232,119 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int m = mb * BLOCK_M + row_in_tile;
       const bool row_ok = m < p.M;
       const bool add_bias = (p.bias != nullptr) && (split == 0);
+      // bf16 outputs leave through shared memory when the 64-column pair is complete: a lane's 64 bytes of ITS row
+      // become 128-byte row segments written by 8 lanes, so a store instruction touches 4 full lines instead of 32
+      // half sectors (the per-lane path remains for fp32 / atomic outputs, ragged edges and unaligned rows)
+      const bool staged_ok = !p.out_fp32 && vec_ok;
+      uint8_t* wstage = smem + S::EPI_OFFSET + (warp - 2) * 4096;
+      const int m_warp = mb * BLOCK_M + quarter * 32;  // first row of this warp
+      auto stage_put = [&](int piece, uint4 w) {
+        *reinterpret_cast<uint4*>(wstage + lane * 128 + ((piece ^ (lane & 7)) << 4)) = w;
+      };
+      auto stage_store = [&](__nv_bfloat16* base, long long ld) {  // base: row m_warp, column n0
+        const int piece = lane & 7;
+#pragma unroll
+        for (int itr = 0; itr < 8; ++itr) {
+          const int row = itr * 4 + (lane >> 3);
+          if (m_warp + row < p.M) {
+            const uint4 w = *reinterpret_cast<const uint4*>(wstage + row * 128 + ((piece ^ (row & 7)) << 4));
+            *reinterpret_cast<uint4*>(base + (long long)row * ld + piece * 8) = w;
+          }
+        }
+      };
 #pragma unroll 1
-      for (int c = col_half * (BLOCK_N / 64); c < (col_half + 1) * (BLOCK_N / 64); ++c) {
+      for (int c = col_half * (BLOCK_N / 64); c < (col_half + 1) * (BLOCK_N / 64); c += 2) {
         const int n0 = nb * BLOCK_N + c * 32;
         if (n0 >= p.N) break;  // warp-uniform
-        uint32_t r[32];
+        uint32_t r2[2][32];
         const uint32_t taddr = tmem_base + acc * BLOCK_N + c * 32 + (uint32_t(quarter * 32) << 16);
         __syncwarp();
-        tmem_ld_32x32b_x32(taddr, r);
+        tmem_ld_32x32b_x32(taddr, r2[0]);
+        tmem_ld_32x32b_x32(taddr + 32, r2[1]);
         tmem_ld_wait();
+        if (staged_ok && n0 + 64 <= p.N) {
+          uint4 keep[2][4];  // GELU_DUAL: the bf16 pre-activations, reused for the second output
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int nh = n0 + h * 32;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r2[h][j]) * p.alpha;
+            if (add_bias) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += __bfloat162float(p.bias[nh + j]);
+            }
+            if ((p.epi_mode == EPI_DGELU || p.epi_mode == EPI_RESIDUAL) && row_ok) {
+              const uint4* src = reinterpret_cast<const uint4*>(p.aux + (long long)b * p.aux_batch_stride + (long long)m * p.ld_aux + nh);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 w = src[q];
+                const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f = __bfloat1622float2(hh[e]);
+                  if (p.epi_mode == EPI_DGELU) {
+                    v[q * 8 + e * 2] *= gelu_tanh_grad(f.x);
+                    v[q * 8 + e * 2 + 1] *= gelu_tanh_grad(f.y);
+                  } else {
+                    v[q * 8 + e * 2] += f.x;
+                    v[q * 8 + e * 2 + 1] += f.y;
+                  }
+                }
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 w;
+              w.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              w.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              w.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              w.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              keep[h][q] = w;
+              stage_put(h * 4 + q, w);
+            }
+          }
+          __syncwarp();
+          __nv_bfloat16* c_base = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)b * p.c_batch_stride + (long long)m_warp * p.ldc + n0;
+          if (p.epi_mode == EPI_GELU_DUAL) {
+            stage_store(p.aux + (long long)b * p.aux_batch_stride + (long long)m_warp * p.ld_aux + n0, p.ld_aux);
+            __syncwarp();
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&keep[h][q]);
+                float2 f0 = __bfloat1622float2(hh[0]), f1 = __bfloat1622float2(hh[1]);
+                float2 f2 = __bfloat1622float2(hh[2]), f3 = __bfloat1622float2(hh[3]);
+                uint4 w;
+                w.x = pack_bf16x2(gelu_tanh(f0.x), gelu_tanh(f0.y));
+                w.y = pack_bf16x2(gelu_tanh(f1.x), gelu_tanh(f1.y));
+                w.z = pack_bf16x2(gelu_tanh(f2.x), gelu_tanh(f2.y));
+                w.w = pack_bf16x2(gelu_tanh(f3.x), gelu_tanh(f3.y));
+                stage_put(h * 4 + q, w);
+              }
+            __syncwarp();
+          }
+          stage_store(c_base, p.ldc);
+          continue;
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+        const int nq = n0 + h * 32;
+        if (nq >= p.N) break;  // warp-uniform
+        uint32_t(&r)[32] = r2[h];
         if (row_ok) {
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-        const bool full_chunk = (n0 + 32 <= p.N) && vec_ok;
+        const bool full_chunk = (nq + 32 <= p.N) && vec_ok;
         if (add_bias) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (n0 + j < p.N) v[j] += __bfloat162float(p.bias[n0 + j]);
+            if (nq + j < p.N) v[j] += __bfloat162float(p.bias[nq + j]);
         }
         __nv_bfloat16* aux_row =
-            p.aux ? p.aux + (long long)b * p.aux_batch_stride + (long long)m * p.ld_aux + n0
+            p.aux ? p.aux + (long long)b * p.aux_batch_stride + (long long)m * p.ld_aux + nq
                   : nullptr;
         if (p.epi_mode == EPI_GELU_DUAL) {
           if (full_chunk) {
@@ -265,7 +361,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N) aux_row[j] = __float2bfloat16(v[j]);
+              if (nq + j < p.N) aux_row[j] = __float2bfloat16(v[j]);
           }
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(__bfloat162float(__float2bfloat16(v[j])));
@@ -286,7 +382,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) a[j] = (n0 + j < p.N) ? __bfloat162float(aux_row[j]) : 0.f;
+            for (int j = 0; j < 32; ++j) a[j] = (nq + j < p.N) ? __bfloat162float(aux_row[j]) : 0.f;
           }
           if (p.epi_mode == EPI_DGELU) {
 #pragma unroll
@@ -298,7 +394,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         if (p.out_fp32) {
           float* crow = reinterpret_cast<float*>(p.C) + (long long)b * p.c_batch_stride +
-                        (long long)m * p.ldc + n0;
+                        (long long)m * p.ldc + nq;
           if (p.accumulate) {
             if (full_chunk) {
               float4* dst = reinterpret_cast<float4*>(crow);
@@ -308,7 +404,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (n0 + j < p.N) atomicAdd(crow + j, v[j]);
+                if (nq + j < p.N) atomicAdd(crow + j, v[j]);
             }
           } else if (full_chunk) {
             float4* dst = reinterpret_cast<float4*>(crow);
@@ -318,11 +414,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N) crow[j] = v[j];
+              if (nq + j < p.N) crow[j] = v[j];
           }
         } else {
           __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) +
-                                (long long)b * p.c_batch_stride + (long long)m * p.ldc + n0;
+                                (long long)b * p.c_batch_stride + (long long)m * p.ldc + nq;
           if (full_chunk) {
             uint4* dst = reinterpret_cast<uint4*>(crow);
 #pragma unroll
@@ -337,10 +433,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N) crow[j] = __float2bfloat16(v[j]);
+              if (nq + j < p.N) crow[j] = __float2bfloat16(v[j]);
           }
         }
         }  // row_ok
+        }  // halves
       }
       tc_fence_before();
       __syncwarp();

@@ -116,6 +116,12 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
   }
 }
 
+__device__ __forceinline__ uint4 ld_nc16(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
 // dx = rstd * (g*dy - c1 - xhat*c2) (+ dres);  LayerNorm: c1 = mean(g*dy), c2 = mean(g*dy*xhat)
 // RMSNorm: c1 = 0, c2 = mean(g*dy*xhat) with xhat = x*rstd.
 // MAXV > 0: per-lane register accumulators for dgamma/dbeta (C <= 256*MAXV); MAXV == 0: shared
@@ -145,24 +151,63 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
   float adg[MAXV > 0 ? MAXV * 8 : 1], adb[MAXV > 0 ? MAXV * 8 : 1];
 #pragma unroll
   for (int i = 0; i < (MAXV > 0 ? MAXV * 8 : 1); ++i) adg[i] = adb[i] = 0.f;
-  for (long long row = (long long)blockIdx.x * warps + warp; row < rows;
-       row += (long long)gridDim.x * warps) {
+  // MAXV > 0: the row lives in registers (one 16-byte load of x and dy per vector, no second read), and the next row's
+  // loads are issued before this row's reductions, so the memory pipe stays busy through the arithmetic.
+  constexpr int NV = MAXV > 0 ? MAXV : 1;
+  const long long row_step = (long long)gridDim.x * warps;
+  long long row = (long long)blockIdx.x * warps + warp;
+  uint4 cx[NV], cd[NV], nx[NV], nd[NV];
+  auto fetch = [&](long long r, uint4 (&fx)[NV], uint4 (&fd)[NV]) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + r * C);
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + r * C);
+#pragma unroll
+    for (int vi = 0; vi < NV; ++vi) {
+      const int v = lane + vi * 32;
+      if (v < nv) {
+        fx[vi] = ld_nc16(xr + v);
+        fd[vi] = ld_nc16(dyr + v);
+      }
+    }
+  };
+  if (MAXV > 0 && row < rows) fetch(row, cx, cd);
+  for (; row < rows; row += row_step) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
     const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * C);
+    if (MAXV > 0 && row + row_step < rows) fetch(row + row_step, nx, nd);
     const float mean = RMS ? 0.f : mean_in[row];
     const float rstd = rstd_in[row];
     float c1 = 0.f, c2 = 0.f;
-    for (int v = lane; v < nv; v += 32) {
-      float f[8], d[8], g[8];
-      unpack8(xr[v], f);
-      unpack8(dyr[v], d);
-      unpack8(gr[v], g);
+    if (MAXV > 0) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float xh = (f[e] - mean) * rstd;
-        const float gd = g[e] * d[e];
-        c1 += gd;
-        c2 += gd * xh;
+      for (int vi = 0; vi < NV; ++vi) {
+        const int v = lane + vi * 32;
+        if (v < nv) {
+          float f[8], d[8], g[8];
+          unpack8(cx[vi], f);
+          unpack8(cd[vi], d);
+          unpack8(gr[v], g);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float xh = (f[e] - mean) * rstd;
+            const float gd = g[e] * d[e];
+            c1 += gd;
+            c2 += gd * xh;
+          }
+        }
+      }
+    } else {
+      for (int v = lane; v < nv; v += 32) {
+        float f[8], d[8], g[8];
+        unpack8(xr[v], f);
+        unpack8(dyr[v], d);
+        unpack8(gr[v], g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xh = (f[e] - mean) * rstd;
+          const float gd = g[e] * d[e];
+          c1 += gd;
+          c2 += gd * xh;
+        }
       }
     }
     c1 = RMS ? 0.f : warp_sum(c1) / C;
@@ -174,8 +219,8 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
       const int v = lane + vi * 32;
       if (v >= nv) break;
       float f[8], d[8], g[8], o[8];
-      unpack8(xr[v], f);
-      unpack8(dyr[v], d);
+      unpack8(MAXV > 0 ? cx[MAXV > 0 ? vi : 0] : xr[v], f);
+      unpack8(MAXV > 0 ? cd[MAXV > 0 ? vi : 0] : dyr[v], d);
       unpack8(gr[v], g);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -196,6 +241,13 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
         for (int e = 0; e < 8; ++e) o[e] += r[e];
       }
       dxr[v] = pack8(o);
+    }
+    if (MAXV > 0) {
+#pragma unroll
+      for (int vi = 0; vi < NV; ++vi) {
+        cx[vi] = nx[vi];
+        cd[vi] = nd[vi];
+      }
     }
   }
   if (MAXV > 0) {
@@ -304,13 +356,18 @@ void norm_bwd(const NormArgs& a, cudaStream_t stream) {
   const unsigned grid = (unsigned)a.n_partial;
   const bool small = a.C <= 1024;
   const size_t smem = sizeof(float) * 2 * a.C * (small ? threads / 32 : 1);
-  if (a.rms) {
-    if (small) launch_norm_bwd<true, 4>(a, grid, threads, smem, stream);
-    else launch_norm_bwd<true, 0>(a, grid, threads, smem, stream);
-  } else {
-    if (small) launch_norm_bwd<false, 4>(a, grid, threads, smem, stream);
-    else launch_norm_bwd<false, 0>(a, grid, threads, smem, stream);
-  }
+  const int maxv = small ? (a.C + 255) / 256 : 0;  // 16-byte vectors per lane
+#define RT_NORM_BWD(R)                                                        \
+  do {                                                                        \
+    if (maxv == 1) launch_norm_bwd<R, 1>(a, grid, threads, smem, stream);     \
+    else if (maxv == 2) launch_norm_bwd<R, 2>(a, grid, threads, smem, stream); \
+    else if (maxv == 3) launch_norm_bwd<R, 3>(a, grid, threads, smem, stream); \
+    else if (maxv == 4) launch_norm_bwd<R, 4>(a, grid, threads, smem, stream); \
+    else launch_norm_bwd<R, 0>(a, grid, threads, smem, stream);               \
+  } while (0)
+  if (a.rms) RT_NORM_BWD(true);
+  else RT_NORM_BWD(false);
+#undef RT_NORM_BWD
   if (a.dgamma != nullptr || (!a.rms && a.dbeta != nullptr)) {
     dim3 g2((a.C + 31) / 32, a.rms ? 1 : 2);
     norm_bwd_reduce_kernel<<<g2, 1024, 0, stream>>>(a.partial, a.dgamma, a.dbeta, a.n_partial, a.C);
