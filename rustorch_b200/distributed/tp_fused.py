@@ -103,6 +103,12 @@ class GemmReduceScatter:
 _OPS = {}
 
 
+def _wgrad_splits(n_out: int, n_in: int, rows: int) -> int:
+    """Split count of a weight-gradient GEMM [n_out, n_in] over ``rows`` contraction rows: one wave of work units."""
+    from ..nn.fused import _split_k_for
+    return _split_k_for(-(-n_out // 128) * -(-n_in // 256), -(-rows // 64))
+
+
 def shared_op(kind: str, rows: int, dim: int, device, group):
     """One op object (symmetric buffers, flags, epoch counter) per (kind, rows, dim, group): layers of equal shape use
     it one after the other, which the kernels' double buffering and end-of-kernel flags make safe.  A 32-layer model then
@@ -128,7 +134,7 @@ class _ColumnParallelFn(torch.autograd.Function):
         L = ctx.layer
         dy = dy.contiguous()
         # dW[N_local, K] = dy^T @ x_gathered : both operands read "MN-major", fp32 accumulate
-        dw = K.gemm(dy, L.gather, a_mn=True, b_mn=True, out_dtype=torch.float32, split_k=4, accumulate=True)
+        dw = K.gemm(dy, L.gather, a_mn=True, b_mn=True, out_dtype=torch.float32, split_k=_wgrad_splits(dy.shape[1], L.gather.shape[1], dy.shape[0]), accumulate=True)
         db = dy.float().sum(0).to(weight.dtype) if ctx.has_bias else None
         # dx_shard[rows, K] = reduce_scatter(dy[M, N_local] @ W[N_local, K]) : W read as [K_red = N_local][N_out = K]
         dx = L.rs_bwd(dy, weight, b_mn=True)
@@ -150,7 +156,7 @@ class _RowParallelFn(torch.autograd.Function):
         L = ctx.layer
         # dx[M, K_local] = all_gather(dy)[M, N] @ W[N, K_local]  (W read as [K_red = N][N_out = K_local])
         dx = L.ag_bwd(weight, None, x=dy_shard.contiguous(), b_mn=True)
-        dw = K.gemm(L.ag_bwd.gather, x, a_mn=True, b_mn=True, out_dtype=torch.float32, split_k=4, accumulate=True)
+        dw = K.gemm(L.ag_bwd.gather, x, a_mn=True, b_mn=True, out_dtype=torch.float32, split_k=_wgrad_splits(L.ag_bwd.gather.shape[1], x.shape[1], x.shape[0]), accumulate=True)
         db = None
         if ctx.has_bias:
             db = L.ag_bwd.gather.float().sum(0).to(weight.dtype)

@@ -37,10 +37,12 @@ def _notify(*params):
 
 
 def _split_k_for(tiles: int, k_blocks: int) -> int:
-    if tiles >= 4 * _NUM_SMS:
+    """Split the contraction so that tiles x splits fill ONE wave of the persistent GEMM (measured on the GPT-2 weight
+    gradient shapes: 3072 x 768 x 16384 takes 67.6 us with 2 splits = 144 work units, 77.8 us with 8, 84 us with 9; every
+    extra split adds a pass of fp32 atomics over the output)."""
+    if tiles >= _NUM_SMS:
         return 1
-    want = -(-4 * _NUM_SMS // max(tiles, 1))
-    return max(1, min(want, max(1, k_blocks // 8)))
+    return max(1, min(_NUM_SMS // max(tiles, 1), max(1, k_blocks // 8)))
 
 
 def wgrad_into(dy2d: torch.Tensor, x2d: torch.Tensor, param: torch.Tensor):
