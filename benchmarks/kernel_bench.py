@@ -321,8 +321,8 @@ def main():
                                    (16384, 768, 768, "nt", 1), (16384, 50304, 768, "nt", 1),
                                    (16384, 768, 3072, "nn", 1), (16384, 3072, 768, "nn", 1),
                                    (16384, 768, 50304, "nn", 1),
-                                   (3072, 768, 16384, "tn", 8), (768, 3072, 16384, "tn", 8),
-                                   (2304, 768, 16384, "tn", 8), (50304, 768, 16384, "tn", 1)]:
+                                   (3072, 768, 16384, "tn", 2), (768, 3072, 16384, "tn", 2),
+                                   (2304, 768, 16384, "tn", 2), (50304, 768, 16384, "tn", 1)]:
             a.m, a.n, a.k, a.layout, a.split_k = m, n, k, lay, sk
             a.accumulate = lay == "tn"
             bench_gemm(a)

@@ -153,11 +153,15 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
   for (int i = 0; i < (MAXV > 0 ? MAXV * 8 : 1); ++i) adg[i] = adb[i] = 0.f;
   // MAXV > 0: the row lives in registers (one 16-byte load of x and dy per vector, no second read), and the next row's
   // loads are issued before this row's reductions, so the memory pipe stays busy through the arithmetic.
+  // The prefetch costs 8 * MAXV registers: RMSNorm has them (no beta accumulators), LayerNorm at MAXV = 4 would
+  // drop to one CTA per SM (168 registers), so LayerNorm loads the row at the top of its own iteration.
   constexpr int NV = MAXV > 0 ? MAXV : 1;
+  constexpr bool PREFETCH = MAXV > 0 && RMS;
+  constexpr bool CACHE = MAXV > 0 && (RMS || MAXV <= 3);  // LayerNorm at MAXV = 4 re-reads the row (L1) instead
   const long long row_step = (long long)gridDim.x * warps;
   long long row = (long long)blockIdx.x * warps + warp;
-  uint4 cx[NV], cd[NV], nx[NV], nd[NV];
-  auto fetch = [&](long long r, uint4 (&fx)[NV], uint4 (&fd)[NV]) {
+  uint4 cx[CACHE ? NV : 1], cd[CACHE ? NV : 1], nx[PREFETCH ? NV : 1], nd[PREFETCH ? NV : 1];
+  auto fetch = [&](long long r, auto& fx, auto& fd) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + r * C);
     const uint4* dyr = reinterpret_cast<const uint4*>(dy + r * C);
 #pragma unroll
@@ -169,15 +173,19 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
       }
     }
   };
-  if (MAXV > 0 && row < rows) fetch(row, cx, cd);
+  if (PREFETCH && row < rows) fetch(row, cx, cd);
   for (; row < rows; row += row_step) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
     const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * C);
-    if (MAXV > 0 && row + row_step < rows) fetch(row + row_step, nx, nd);
+    if constexpr (PREFETCH) {
+      if (row + row_step < rows) fetch(row + row_step, nx, nd);
+    } else if constexpr (CACHE) {
+      fetch(row, cx, cd);
+    }
     const float mean = RMS ? 0.f : mean_in[row];
     const float rstd = rstd_in[row];
     float c1 = 0.f, c2 = 0.f;
-    if (MAXV > 0) {
+    if constexpr (CACHE) {
 #pragma unroll
       for (int vi = 0; vi < NV; ++vi) {
         const int v = lane + vi * 32;
@@ -219,8 +227,8 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
       const int v = lane + vi * 32;
       if (v >= nv) break;
       float f[8], d[8], g[8], o[8];
-      unpack8(MAXV > 0 ? cx[MAXV > 0 ? vi : 0] : xr[v], f);
-      unpack8(MAXV > 0 ? cd[MAXV > 0 ? vi : 0] : dyr[v], d);
+      unpack8(CACHE ? cx[CACHE ? vi : 0] : xr[v], f);
+      unpack8(CACHE ? cd[CACHE ? vi : 0] : dyr[v], d);
       unpack8(gr[v], g);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -242,7 +250,7 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
       }
       dxr[v] = pack8(o);
     }
-    if (MAXV > 0) {
+    if constexpr (PREFETCH) {
 #pragma unroll
       for (int vi = 0; vi < NV; ++vi) {
         cx[vi] = nx[vi];
