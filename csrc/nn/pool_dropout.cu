@@ -43,6 +43,12 @@ __device__ __forceinline__ void pload(const T* p, float (&f)[PVec<T>::N]) {
   for (int i = 0; i < PVec<T>::N; ++i) f[i] = pf(e[i]);
 }
 template <typename T>
+__device__ __forceinline__ void punpack(const uint4& raw, float (&f)[PVec<T>::N]) {
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < PVec<T>::N; ++i) f[i] = pf(e[i]);
+}
+template <typename T>
 __device__ __forceinline__ void pstore(T* p, const float (&f)[PVec<T>::N]) {
   uint4 raw;
   T* e = reinterpret_cast<T*>(&raw);
@@ -56,7 +62,7 @@ __device__ __forceinline__ void pstore(T* p, const float (&f)[PVec<T>::N]) {
 // loops unroll, so all window loads of a thread are in flight together and the index arithmetic has no divisions
 // by runtime strides.
 template <typename T, bool MAX, int K, int S>
-__global__ void __launch_bounds__(256) pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, unsigned char* __restrict__ idx,
+__global__ void __launch_bounds__(256, 3) pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, unsigned char* __restrict__ idx,
                                                        const Pool2dArgs a) {
   constexpr int V = PVec<T>::N;
   const int cv = a.C / V;
@@ -86,7 +92,7 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const T* __restrict__ x, 
     const T* xn = x + (long long)n * a.H * a.W * a.C + c;
     if (K) {
       // all taps loaded first (out-of-image taps are skipped by predicate), then reduced in tap order
-      float v[(K ? K * K : 1)][V];
+      uint4 v[(K ? K * K : 1)];      // raw vectors: 4 registers per tap while the loads are in flight
       bool in[(K ? K * K : 1)];
 #pragma unroll
       for (int kh = 0; kh < K; ++kh)
@@ -94,17 +100,19 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const T* __restrict__ x, 
         for (int kw = 0; kw < K; ++kw) {
           const int ih = h0 + kh, iw = w0 + kw;
           in[kh * K + kw] = ih >= 0 && ih < a.H && iw >= 0 && iw < a.W;
-          if (in[kh * K + kw]) pload(xn + ((long long)ih * a.W + iw) * a.C, v[kh * K + kw]);
+          if (in[kh * K + kw]) v[kh * K + kw] = *reinterpret_cast<const uint4*>(xn + ((long long)ih * a.W + iw) * a.C);
         }
 #pragma unroll
       for (int tap = 0; tap < K * K; ++tap) {
         if (!in[tap]) continue;
+        float f[V];
+        punpack<T>(v[tap], f);
 #pragma unroll
         for (int i = 0; i < V; ++i) {
           if (MAX) {
-            if (v[tap][i] > acc[i] || v[tap][i] != v[tap][i]) acc[i] = v[tap][i], best[i] = (unsigned char)tap;
+            if (f[i] > acc[i] || f[i] != f[i]) acc[i] = f[i], best[i] = (unsigned char)tap;
           } else {
-            acc[i] += v[tap][i];
+            acc[i] += f[i];
           }
         }
       }
@@ -175,7 +183,7 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const T* __restrict__ dy,
     const unsigned char* in_ = idx ? idx + (long long)n * a.OH * a.OW * a.C + c : nullptr;
     if (K) {
       constexpr int NC = K ? (K + (S ? S : 1) - 1) / (S ? S : 1) : 1;   // candidate outputs per direction
-      float g[NC * NC][V];
+      uint4 g[NC * NC];
       __align__(8) unsigned char rec[NC * NC][8];
       bool in[NC * NC];
       unsigned char me[NC * NC];
@@ -190,7 +198,7 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const T* __restrict__ dy,
           me[q] = (unsigned char)(kh * K + kw);
           if (in[q]) {
             const long long o = ((long long)oh * a.OW + ow) * a.C;
-            pload(gn + o, g[q]);
+            g[q] = *reinterpret_cast<const uint4*>(gn + o);
             if (MAX) {
               if (V == 8) *reinterpret_cast<uint2*>(rec[q]) = *reinterpret_cast<const uint2*>(in_ + o);
               else *reinterpret_cast<unsigned*>(rec[q]) = *reinterpret_cast<const unsigned*>(in_ + o);
@@ -200,12 +208,14 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const T* __restrict__ dy,
 #pragma unroll
       for (int q = NC * NC - 1; q >= 0; --q) {     // ascending (oh, ow), the order of the runtime path
         if (!in[q]) continue;
+        float f[V];
+        punpack<T>(g[q], f);
 #pragma unroll
         for (int i = 0; i < V; ++i) {
           if (MAX) {
-            if (rec[q][i] == me[q]) acc[i] += g[q][i];
+            if (rec[q][i] == me[q]) acc[i] += f[i];
           } else {
-            acc[i] += g[q][i] * inv;
+            acc[i] += f[i] * inv;
           }
         }
       }
