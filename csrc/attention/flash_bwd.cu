@@ -15,6 +15,8 @@
 // dS go to the swizzled staging tiles, which serve as MN-major A operands (transposed use)
 // in dkdv and as a K-major A operand in dq.  The reference has no attention backward at all
 // (its head reshapes detach the graph, src/nn/attention.rs:255-289).
+#include <cstdlib>
+
 #include "../api.h"
 #include "../common/launch.h"
 #include "attn_common.cuh"
@@ -572,6 +574,283 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q,
   }
 }
 
+// ------------------------------------------------------------------------ dK / dV, pipelined (D = 64)
+// The kernel above runs MMA(S, dP) -> softmax -> MMA(dV, dK) as a serial chain per (kv block, q block) pair.  With
+// 64-wide heads tensor memory has room for a second S accumulator (2 x 128 + 128 + 64 + 64 = 512 columns), so here
+// the control thread issues S of pair i+1 before it waits for the softmax warps of pair i, and dP of pair i+1
+// directly after that wait, ahead of dV / dK of pair i: the exponentials of pair i+1 then run under the dV / dK
+// MMAs of pair i.  Q / dO tiles sit in a three-stage ring so that the loads of pair i+2 never wait on those MMAs.
+struct DkDvPipeSmem {
+  static constexpr int TILE = 128 * 64 * 2;
+  static constexpr int QSTAGES = 3;
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = TILE;
+  static constexpr int OFF_Q = 2 * TILE;
+  static constexpr int OFF_DO = OFF_Q + QSTAGES * TILE;
+  static constexpr int OFF_P = OFF_DO + QSTAGES * TILE;
+  static constexpr int OFF_DS = OFF_P + 2 * ATT_HALF_BYTES;
+  static constexpr int OFF_BAR = OFF_DS + 2 * ATT_HALF_BYTES;
+  // kv_full, qdo_full[3], qdo_empty[3], s_full[2], dp_full, pds_full, pds_empty, done
+  static constexpr int TOTAL = OFF_BAR + 13 * 8 + 16;
+};
+
+__global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
+attn_bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                          const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                          const AttnBwdParams p) {
+  constexpr int D = 64;
+  using S = DkDvPipeSmem;
+  constexpr int QS = S::QSTAGES;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, RT_ERR_BOUNDS);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = bars + 4;
+  uint64_t* s_full = bars + 7;
+  uint64_t* dp_full = bars + 9;
+  uint64_t* pds_full = bars + 10;
+  uint64_t* pds_empty = bars + 11;
+  uint64_t* done = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  CtaCtl* ctl = reinterpret_cast<CtaCtl*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int k0 = blockIdx.x * ATT_BN;
+  const int hk = blockIdx.y;
+  const int b = blockIdx.z;
+  const int group = p.H / p.Hkv;
+  constexpr uint32_t TMEM_COLS = 512;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < QS; ++s) {
+      mbar_init(&qdo_full[s], 1);
+      mbar_init(&qdo_empty[s], 1);
+    }
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
+    mbar_init(dp_full, 1);
+    mbar_init(pds_full, 256);
+    mbar_init(pds_empty, 1);
+    mbar_init(done, 1);
+    ctl->abort = 0;
+    fence_mbar_init();
+  }
+  if (warp == ATT_BWD_CTRL_WARP) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S0 = tmem_base;  // S of pair i lives at tmem_S0 + (i & 1) * 128
+  const uint32_t tmem_dP = tmem_base + 256;
+  const uint32_t tmem_dV = tmem_base + 384;
+  const uint32_t tmem_dK = tmem_base + 448;
+
+  const int off = p.Tk - p.Tq;
+  const int n_q = (p.Tq + ATT_BM - 1) / ATT_BM;
+  int i_start = 0;
+  if (p.causal) i_start = max(0, (k0 - off)) / ATT_BM;
+  const int per_head = max(0, n_q - i_start);
+  const int n_it = per_head * group;
+
+  if (warp == ATT_BWD_CTRL_WARP) {
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idesc_S = make_idesc_f16(128, 128, false, false, true);
+      constexpr uint32_t idesc_T = make_idesc_f16(128, D, true, true, true);  // P^T dO, dS^T Q
+      bool ok = true;
+      const uint32_t aK = smem_u32(smem + S::OFF_K);
+      const uint32_t aV = smem_u32(smem + S::OFF_V);
+      const uint32_t aP = smem_u32(smem + S::OFF_P);
+      const uint32_t aDS = smem_u32(smem + S::OFF_DS);
+      auto load_q = [&](int n) {  // Q / dO tiles of pair n into ring stage n % QS (after the MMAs of pair n - QS retired)
+        const int st = n % QS;
+        if (!mbar_wait(&qdo_empty[st], ((n / QS) & 1) ^ 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) return false;
+        const int h = hk * group + n / per_head;
+        const int qi0 = (i_start + n % per_head) * ATT_BM;
+        mbar_arrive_expect_tx(&qdo_full[st], 2 * S::TILE);
+        load_tile<D>(smem + S::OFF_Q + st * S::TILE, &tmap_q, &qdo_full[st], qi0, h, b);
+        load_tile<D>(smem + S::OFF_DO + st * S::TILE, &tmap_do, &qdo_full[st], qi0, h, b);
+        return true;
+      };
+      auto issue_S = [&](int n) {
+        const uint32_t aQ = smem_u32(smem + S::OFF_Q + (n % QS) * S::TILE);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16_ss(tmem_S0 + (n & 1) * 128, tile_desc_kmajor<D>(aQ, kk), tile_desc_kmajor<D>(aK, kk), idesc_S, kk > 0 ? 1u : 0u);
+        umma_commit(&s_full[n & 1]);
+      };
+      auto issue_dP = [&](int n) {
+        const uint32_t aDO = smem_u32(smem + S::OFF_DO + (n % QS) * S::TILE);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16_ss(tmem_dP, tile_desc_kmajor<D>(aDO, kk), tile_desc_kmajor<D>(aV, kk), idesc_S, kk > 0 ? 1u : 0u);
+        umma_commit(dp_full);
+      };
+      mbar_arrive_expect_tx(kv_full, 2 * S::TILE);
+      load_tile<D>(smem + S::OFF_K, &tmap_k, kv_full, k0, hk, b);
+      load_tile<D>(smem + S::OFF_V, &tmap_v, kv_full, k0, hk, b);
+      ok = load_q(0);
+      if (ok && n_it > 1) ok = load_q(1);
+      ok = ok && mbar_wait(kv_full, 0, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER);
+      ok = ok && mbar_wait(&qdo_full[0], 0, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+      if (ok) {
+        tc_fence_after();
+        issue_S(0);
+        issue_dP(0);
+      }
+      for (int it = 0; it < n_it && ok; ++it) {
+        if (it + 1 < n_it) {
+          const int n = it + 1;
+          if (!mbar_wait(&qdo_full[n % QS], (n / QS) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_S(n);  // its buffer was last read by the softmax warps of pair n - 2, which finished before pds_full(n - 2)
+        }
+        if (it + 2 < n_it && !load_q(it + 2)) {
+          ok = false;
+          break;
+        }
+        if (!mbar_wait(pds_full, it & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (it + 1 < n_it) issue_dP(it + 1);  // ahead of dV / dK: the softmax warps of pair it + 1 need it first
+        const int s = it % QS;
+        const uint32_t aQ = smem_u32(smem + S::OFF_Q + s * S::TILE);
+        const uint32_t aDO = smem_u32(smem + S::OFF_DO + s * S::TILE);
+#pragma unroll
+        for (int kk = 0; kk < ATT_BM / 16; ++kk)
+          umma_f16_ss(tmem_dV, stage_desc_mnmajor(aP, kk), tile_desc_mnmajor<D>(aDO, kk), idesc_T, (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < ATT_BM / 16; ++kk)
+          umma_f16_ss(tmem_dK, stage_desc_mnmajor(aDS, kk), tile_desc_mnmajor<D>(aQ, kk), idesc_T, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&qdo_empty[s]);
+        umma_commit(pds_empty);
+      }
+      if (ok) umma_commit(done);
+    }
+  } else {
+    // warps 0..3 take score columns 0..63, warps 4..7 columns 64..127 of the same 128 rows
+    const int quarter = warp & 3, chalf = warp >> 2;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_sel = uint32_t(quarter * 32) << 16;
+    uint8_t* sP = smem + S::OFF_P;
+    uint8_t* sDS = smem + S::OFF_DS;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int h = hk * group + it / per_head;
+      const int qi = (i_start + it % per_head) * ATT_BM + row;
+      const bool row_ok = qi < p.Tq;
+      const long long sidx = ((long long)b * p.H + h) * p.Tq + qi;
+      const float lse2 = row_ok ? p.lse[sidx] * 1.4426950408889634f : 0.f;
+      const float dl = row_ok ? p.delta[sidx] : 0.f;
+      const int limit = p.causal ? min(p.Tk - 1, qi + off) : (p.Tk - 1);
+      if (!mbar_wait(&s_full[it & 1], (it >> 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_SOFTMAX)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t rs[2][32], rp[2][32];
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 2; ++u) tmem_ld_32x32b_x32(tmem_S0 + (it & 1) * 128 + lane_sel + (chalf * 2 + u) * 32, rs[u]);
+      tmem_ld_wait();
+      // probabilities first (they only need S); rs is reused for them
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int c = chalf * 2 + u;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const bool vis = row_ok && (k0 + c * 32 + i <= limit);
+          rs[u][i] = __float_as_uint(vis ? ex2_approx(__uint_as_float(rs[u][i]) * p.scale_log2 - lse2) : 0.f);
+        }
+      }
+      if (!mbar_wait(dp_full, it & 1, ctl, p.status, RT_ERR_TIMEOUT_SOFTMAX)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 2; ++u) tmem_ld_32x32b_x32(tmem_dP + lane_sel + (chalf * 2 + u) * 32, rp[u]);
+      tmem_ld_wait();
+      if (it > 0 && !mbar_wait(pds_empty, (it - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_SOFTMAX)) {
+        ok = false;
+        break;
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int c = chalf * 2 + u;
+        float pv[32], ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          pv[i] = __uint_as_float(rs[u][i]);
+          ds[i] = pv[i] * (__uint_as_float(rp[u][i]) - dl);
+        }
+        stage_row_chunk_bf16(sP, row, c * 32, pv);
+        stage_row_chunk_bf16(sDS, row, c * 32, ds);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+    }
+    // final: thread t owns key row k0 + t of dK / dV
+    if (n_it > 0 && ok) ok = mbar_wait(done, 0, ctl, p.status, RT_ERR_TIMEOUT_EPILOGUE);
+    tc_fence_after();
+    const int kr = k0 + row;
+    const uint32_t src = chalf == 0 ? tmem_dV : tmem_dK;  // column half 0 writes dV, half 1 writes dK
+    const float mul = chalf == 0 ? 1.f : p.scale;
+    __nv_bfloat16* dst = chalf == 0 ? p.dv + (long long)b * p.dv_sb + (long long)kr * p.dv_st + (long long)hk * p.dv_sh
+                                    : p.dk + (long long)b * p.dk_sb + (long long)kr * p.dk_st + (long long)hk * p.dk_sh;
+#pragma unroll 1
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t r[32];
+      if (n_it > 0 && ok) {
+        __syncwarp();
+        tmem_ld_32x32b_x32(src + lane_sel + c * 32, r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = 0u;
+      }
+      if (kr < p.Tk) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(r[q * 8 + 0]) * mul, __uint_as_float(r[q * 8 + 1]) * mul);
+          w.y = pack_bf16x2(__uint_as_float(r[q * 8 + 2]) * mul, __uint_as_float(r[q * 8 + 3]) * mul);
+          w.z = pack_bf16x2(__uint_as_float(r[q * 8 + 4]) * mul, __uint_as_float(r[q * 8 + 5]) * mul);
+          w.w = pack_bf16x2(__uint_as_float(r[q * 8 + 6]) * mul, __uint_as_float(r[q * 8 + 7]) * mul);
+          reinterpret_cast<uint4*>(dst + c * 32)[q] = w;
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  __syncwarp();
+  if (ctl->abort) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == ATT_BWD_CTRL_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 template <int D>
 static void launch_bwd(const AttnArgs& a, cudaStream_t stream) {
   const int device = current_device();
@@ -616,7 +895,20 @@ static void launch_bwd(const AttnArgs& a, cudaStream_t stream) {
   p.status = status_word(device);
   {
     dim3 grid((a.Tk + ATT_BN - 1) / ATT_BN, a.Hkv, a.B);
-    k1<<<grid, ATT_BWD_THREADS, DkDvSmem<D>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+    static const bool pipe = [] {  // RUSTORCH_ATTN_BWD_PIPE=0 falls back to the serial dK / dV kernel for 64-wide heads
+      const char* e = std::getenv("RUSTORCH_ATTN_BWD_PIPE");
+      return !(e && e[0] == '0');
+    }();
+    if (D == 64 && pipe) {
+      static bool configured_pipe[64] = {false};
+      if (!configured_pipe[device]) {
+        RT_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkdv_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DkDvPipeSmem::TOTAL));
+        configured_pipe[device] = true;
+      }
+      attn_bwd_dkdv_pipe_kernel<<<grid, ATT_BWD_THREADS, DkDvPipeSmem::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+    } else {
+      k1<<<grid, ATT_BWD_THREADS, DkDvSmem<D>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+    }
     RT_LAUNCH_CHECK();
   }
   {
