@@ -851,6 +851,259 @@ attn_bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   }
 }
 
+// ------------------------------------------------------------------------ dQ, pipelined (D = 64)
+// Same scheme as the pipelined dK / dV kernel: S of kv block j+1 goes to the second S accumulator before the control
+// thread waits for the softmax warps of block j, dP of block j+1 is issued ahead of dQ += dS K of block j, and the
+// K / V tiles sit in a three-stage ring.  Tensor memory: 2 x 128 (S) + 128 (dP) + 64 (dQ) = 448 columns.
+struct DqPipeSmem {
+  static constexpr int TILE = 128 * 64 * 2;
+  static constexpr int KSTAGES = 3;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_DO = TILE;
+  static constexpr int OFF_K = 2 * TILE;
+  static constexpr int OFF_V = OFF_K + KSTAGES * TILE;
+  static constexpr int OFF_DS = OFF_V + KSTAGES * TILE;
+  static constexpr int OFF_BAR = OFF_DS + 2 * ATT_HALF_BYTES;
+  // qdo_full, kv_full[3], kv_empty[3], s_full[2], dp_full, ds_full, ds_empty, done
+  static constexpr int TOTAL = OFF_BAR + 13 * 8 + 16;
+};
+
+__global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
+attn_bwd_dq_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                        const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                        const AttnBwdParams p) {
+  constexpr int D = 64;
+  using S = DqPipeSmem;
+  constexpr int KS = S::KSTAGES;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, RT_ERR_BOUNDS);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
+  uint64_t* qdo_full = bars;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_empty = bars + 4;
+  uint64_t* s_full = bars + 7;
+  uint64_t* dp_full = bars + 9;
+  uint64_t* ds_full = bars + 10;
+  uint64_t* ds_empty = bars + 11;
+  uint64_t* done = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  CtaCtl* ctl = reinterpret_cast<CtaCtl*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * ATT_BM;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  constexpr uint32_t TMEM_COLS = 512;
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    for (int s = 0; s < KS; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
+    mbar_init(dp_full, 1);
+    mbar_init(ds_full, 256);
+    mbar_init(ds_empty, 1);
+    mbar_init(done, 1);
+    ctl->abort = 0;
+    fence_mbar_init();
+  }
+  if (warp == ATT_BWD_CTRL_WARP) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S0 = tmem_base;  // S of block j at tmem_S0 + (j & 1) * 128
+  const uint32_t tmem_dP = tmem_base + 256;
+  const uint32_t tmem_dQ = tmem_base + 384;
+
+  const int off = p.Tk - p.Tq;
+  int n_kv = (p.Tk + ATT_BN - 1) / ATT_BN;
+  if (p.causal) {
+    const int last_col = min(p.Tk - 1, q0 + ATT_BM - 1 + off);
+    n_kv = last_col < 0 ? 0 : min(n_kv, last_col / ATT_BN + 1);
+  }
+
+  if (warp == ATT_BWD_CTRL_WARP) {
+    if (lane == 0 && n_kv > 0) {
+      constexpr uint32_t idesc_S = make_idesc_f16(128, 128, false, false, true);
+      constexpr uint32_t idesc_Q = make_idesc_f16(128, D, false, true, true);  // dS @ K
+      bool ok = true;
+      const uint32_t aQ = smem_u32(smem + S::OFF_Q);
+      const uint32_t aDO = smem_u32(smem + S::OFF_DO);
+      const uint32_t aDS = smem_u32(smem + S::OFF_DS);
+      auto load_kv = [&](int n) {
+        const int st = n % KS;
+        if (!mbar_wait(&kv_empty[st], ((n / KS) & 1) ^ 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) return false;
+        mbar_arrive_expect_tx(&kv_full[st], 2 * S::TILE);
+        load_tile<D>(smem + S::OFF_K + st * S::TILE, &tmap_k, &kv_full[st], n * ATT_BN, hk, b);
+        load_tile<D>(smem + S::OFF_V + st * S::TILE, &tmap_v, &kv_full[st], n * ATT_BN, hk, b);
+        return true;
+      };
+      auto issue_S = [&](int n) {
+        const uint32_t aK = smem_u32(smem + S::OFF_K + (n % KS) * S::TILE);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16_ss(tmem_S0 + (n & 1) * 128, tile_desc_kmajor<D>(aQ, kk), tile_desc_kmajor<D>(aK, kk), idesc_S, kk > 0 ? 1u : 0u);
+        umma_commit(&s_full[n & 1]);
+      };
+      auto issue_dP = [&](int n) {
+        const uint32_t aV = smem_u32(smem + S::OFF_V + (n % KS) * S::TILE);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16_ss(tmem_dP, tile_desc_kmajor<D>(aDO, kk), tile_desc_kmajor<D>(aV, kk), idesc_S, kk > 0 ? 1u : 0u);
+        umma_commit(dp_full);
+      };
+      mbar_arrive_expect_tx(qdo_full, 2 * S::TILE);
+      load_tile<D>(smem + S::OFF_Q, &tmap_q, qdo_full, q0, h, b);
+      load_tile<D>(smem + S::OFF_DO, &tmap_do, qdo_full, q0, h, b);
+      ok = load_kv(0);
+      if (ok && n_kv > 1) ok = load_kv(1);
+      ok = ok && mbar_wait(qdo_full, 0, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER);
+      ok = ok && mbar_wait(&kv_full[0], 0, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+      if (ok) {
+        tc_fence_after();
+        issue_S(0);
+        issue_dP(0);
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) {
+          const int n = j + 1;
+          if (!mbar_wait(&kv_full[n % KS], (n / KS) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_S(n);
+        }
+        if (j + 2 < n_kv && !load_kv(j + 2)) {
+          ok = false;
+          break;
+        }
+        if (!mbar_wait(ds_full, j & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (j + 1 < n_kv) issue_dP(j + 1);
+        const int s = j % KS;
+        const uint32_t aK = smem_u32(smem + S::OFF_K + s * S::TILE);
+#pragma unroll
+        for (int kk = 0; kk < ATT_BN / 16; ++kk)
+          umma_f16_ss(tmem_dQ, stage_desc_kmajor(aDS, kk), tile_desc_mnmajor<D>(aK, kk), idesc_Q, (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&kv_empty[s]);
+        umma_commit(ds_empty);
+      }
+      if (ok) umma_commit(done);
+    }
+  } else {
+    const int quarter = warp & 3, chalf = warp >> 2;
+    const int row = quarter * 32 + lane;
+    const int qi = q0 + row;
+    const bool row_ok = qi < p.Tq;
+    const uint32_t lane_sel = uint32_t(quarter * 32) << 16;
+    uint8_t* sDS = smem + S::OFF_DS;
+    const long long sidx = ((long long)b * p.H + h) * p.Tq + qi;
+    const float lse2 = row_ok ? p.lse[sidx] * 1.4426950408889634f : 0.f;
+    const float dl = row_ok ? p.delta[sidx] : 0.f;
+    const int limit = p.causal ? min(p.Tk - 1, qi + off) : (p.Tk - 1);
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_SOFTMAX)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t rs[2][32], rp[2][32];
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 2; ++u) tmem_ld_32x32b_x32(tmem_S0 + (j & 1) * 128 + lane_sel + (chalf * 2 + u) * 32, rs[u]);
+      tmem_ld_wait();
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int c = chalf * 2 + u;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const bool vis = row_ok && (j * ATT_BN + c * 32 + i <= limit);
+          rs[u][i] = __float_as_uint(vis ? ex2_approx(__uint_as_float(rs[u][i]) * p.scale_log2 - lse2) : 0.f);
+        }
+      }
+      if (!mbar_wait(dp_full, j & 1, ctl, p.status, RT_ERR_TIMEOUT_SOFTMAX)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 2; ++u) tmem_ld_32x32b_x32(tmem_dP + lane_sel + (chalf * 2 + u) * 32, rp[u]);
+      tmem_ld_wait();
+      if (j > 0 && !mbar_wait(ds_empty, (j - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_SOFTMAX)) {
+        ok = false;
+        break;
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int c = chalf * 2 + u;
+        float ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) ds[i] = __uint_as_float(rs[u][i]) * (__uint_as_float(rp[u][i]) - dl);
+        stage_row_chunk_bf16(sDS, row, c * 32, ds);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(ds_full);
+    }
+    if (n_kv > 0 && ok) ok = mbar_wait(done, 0, ctl, p.status, RT_ERR_TIMEOUT_EPILOGUE);
+    tc_fence_after();
+    __nv_bfloat16* dst = p.dq + (long long)b * p.dq_sb + (long long)qi * p.dq_st + (long long)h * p.dq_sh;
+    {
+      const int c = chalf;  // 32 of the 64 columns per column half
+      uint32_t r[32];
+      if (n_kv > 0 && ok) {
+        __syncwarp();
+        tmem_ld_32x32b_x32(tmem_dQ + lane_sel + c * 32, r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = 0u;
+      }
+      if (row_ok) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(r[q * 8 + 0]) * p.scale, __uint_as_float(r[q * 8 + 1]) * p.scale);
+          w.y = pack_bf16x2(__uint_as_float(r[q * 8 + 2]) * p.scale, __uint_as_float(r[q * 8 + 3]) * p.scale);
+          w.z = pack_bf16x2(__uint_as_float(r[q * 8 + 4]) * p.scale, __uint_as_float(r[q * 8 + 5]) * p.scale);
+          w.w = pack_bf16x2(__uint_as_float(r[q * 8 + 6]) * p.scale, __uint_as_float(r[q * 8 + 7]) * p.scale);
+          reinterpret_cast<uint4*>(dst + c * 32)[q] = w;
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  __syncwarp();
+  if (ctl->abort) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == ATT_BWD_CTRL_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 template <int D>
 static void launch_bwd(const AttnArgs& a, cudaStream_t stream) {
   const int device = current_device();
@@ -913,7 +1166,20 @@ static void launch_bwd(const AttnArgs& a, cudaStream_t stream) {
   }
   {
     dim3 grid((a.Tq + ATT_BM - 1) / ATT_BM, a.H, a.B);
-    k2<<<grid, ATT_BWD_THREADS, DqSmem<D>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+    static const bool pipe_dq = [] {  // RUSTORCH_ATTN_BWD_PIPE_DQ=0 falls back to the serial dQ kernel for 64-wide heads
+      const char* e = std::getenv("RUSTORCH_ATTN_BWD_PIPE_DQ");
+      return !(e && e[0] == '0');
+    }();
+    if (D == 64 && pipe_dq) {
+      static bool configured_dq[64] = {false};
+      if (!configured_dq[device]) {
+        RT_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DqPipeSmem::TOTAL));
+        configured_dq[device] = true;
+      }
+      attn_bwd_dq_pipe_kernel<<<grid, ATT_BWD_THREADS, DqPipeSmem::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+    } else {
+      k2<<<grid, ATT_BWD_THREADS, DqSmem<D>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+    }
     RT_LAUNCH_CHECK();
   }
 }
