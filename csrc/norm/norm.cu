@@ -335,6 +335,127 @@ void norm_fwd(const NormArgs& a, cudaStream_t stream) {
   RT_LAUNCH_CHECK();
 }
 
+// Wide rows (2048-column multiples up to 8192, e.g. the 4096-wide RMSNorm of an 8B Llama): one CTA per row, every
+// thread owns VPT 16-byte vectors of the row for the whole kernel, so gamma and the dgamma / dbeta accumulators sit in
+// registers and the CTA's partial sums are written without any cross-thread reduction; only the two row scalars go
+// through shared memory (one barrier per row, buffers alternate by row parity).  The next row is prefetched.
+template <bool RMS, int VPT>
+__global__ void __launch_bounds__(256) norm_bwd_wide_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                            const __nv_bfloat16* __restrict__ gamma,
+                                                            const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                                                            const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                                                            float* __restrict__ partial, long long rows, int C) {
+  __shared__ float red[2][2][8];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint4 gv[VPT];
+  float adg[VPT * 8], adb[RMS ? 1 : VPT * 8];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) gv[i] = reinterpret_cast<const uint4*>(gamma)[tid + i * 256];
+#pragma unroll
+  for (int i = 0; i < VPT * 8; ++i) adg[i] = 0.f;
+#pragma unroll
+  for (int i = 0; i < (RMS ? 1 : VPT * 8); ++i) adb[i] = 0.f;
+  uint4 cx[VPT], cd[VPT], nx[VPT], nd[VPT];
+  auto fetch = [&](long long r, uint4 (&fx)[VPT], uint4 (&fd)[VPT]) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + r * C);
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + r * C);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      fx[i] = ld_nc16(xr + tid + i * 256);
+      fd[i] = ld_nc16(dyr + tid + i * 256);
+    }
+  };
+  long long row = blockIdx.x;
+  if (row < rows) fetch(row, cx, cd);
+  int par = 0;
+  for (; row < rows; row += gridDim.x, par ^= 1) {
+    if (row + gridDim.x < rows) fetch(row + gridDim.x, nx, nd);
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      float f[8], d[8], g[8];
+      unpack8(cx[i], f);
+      unpack8(cd[i], d);
+      unpack8(gv[i], g);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float xh = (f[e] - mean) * rstd;
+        const float gd = g[e] * d[e];
+        c1 += gd;
+        c2 += gd * xh;
+      }
+    }
+    c1 = warp_sum(c1);
+    c2 = warp_sum(c2);
+    if (lane == 0) {
+      red[par][0][warp] = c1;
+      red[par][1][warp] = c2;
+    }
+    __syncthreads();
+    c1 = c2 = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      c1 += red[par][0][w];
+      c2 += red[par][1][w];
+    }
+    c1 = RMS ? 0.f : c1 / C;
+    c2 = c2 / C;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + row * C);
+    const uint4* drr = dres ? reinterpret_cast<const uint4*>(dres + row * C) : nullptr;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      float f[8], d[8], g[8], o[8];
+      unpack8(cx[i], f);
+      unpack8(cd[i], d);
+      unpack8(gv[i], g);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float xh = (f[e] - mean) * rstd;
+        o[e] = rstd * (g[e] * d[e] - c1 - xh * c2);
+        adg[i * 8 + e] += d[e] * xh;
+        if (!RMS) adb[i * 8 + e] += d[e];
+      }
+      if (drr) {
+        float r[8];
+        unpack8(drr[tid + i * 256], r);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] += r[e];
+      }
+      dxr[tid + i * 256] = pack8(o);
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      cx[i] = nx[i];
+      cd[i] = nd[i];
+    }
+  }
+  float* pg = partial + (long long)blockIdx.x * C;
+  float* pb = partial + ((long long)gridDim.x + blockIdx.x) * C;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c0 = (tid + i * 256) * 8;
+    float4* g4 = reinterpret_cast<float4*>(pg + c0);
+    g4[0] = make_float4(adg[i * 8 + 0], adg[i * 8 + 1], adg[i * 8 + 2], adg[i * 8 + 3]);
+    g4[1] = make_float4(adg[i * 8 + 4], adg[i * 8 + 5], adg[i * 8 + 6], adg[i * 8 + 7]);
+    if (!RMS) {
+      float4* b4 = reinterpret_cast<float4*>(pb + c0);
+      b4[0] = make_float4(adb[i * 8 + 0], adb[i * 8 + 1], adb[i * 8 + 2], adb[i * 8 + 3]);
+      b4[1] = make_float4(adb[i * 8 + 4], adb[i * 8 + 5], adb[i * 8 + 6], adb[i * 8 + 7]);
+    }
+  }
+}
+
+template <bool RMS, int VPT>
+static void launch_norm_bwd_wide(const NormArgs& a, unsigned grid, cudaStream_t stream) {
+  norm_bwd_wide_kernel<RMS, VPT><<<grid, 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(a.dy), reinterpret_cast<const __nv_bfloat16*>(a.x),
+      reinterpret_cast<const __nv_bfloat16*>(a.gamma), a.mean, a.rstd, reinterpret_cast<const __nv_bfloat16*>(a.dres),
+      reinterpret_cast<__nv_bfloat16*>(a.dx), a.partial, a.rows, a.C);
+  RT_LAUNCH_CHECK();
+}
+
 template <bool RMS, int MAXV>
 static void launch_norm_bwd(const NormArgs& a, unsigned grid, int threads, size_t smem,
                             cudaStream_t stream) {
@@ -364,6 +485,7 @@ void norm_bwd(const NormArgs& a, cudaStream_t stream) {
   const unsigned grid = (unsigned)a.n_partial;
   const bool small = a.C <= 1024;
   const size_t smem = sizeof(float) * 2 * a.C * (small ? threads / 32 : 1);
+  const int vpt = (!small && a.C % 2048 == 0 && a.C <= 8192) ? a.C / 2048 : 0;  // wide rows: one CTA per row
   const int maxv = small ? (a.C + 255) / 256 : 0;  // 16-byte vectors per lane
 #define RT_NORM_BWD(R)                                                        \
   do {                                                                        \
@@ -373,7 +495,17 @@ void norm_bwd(const NormArgs& a, cudaStream_t stream) {
     else if (maxv == 4) launch_norm_bwd<R, 4>(a, grid, threads, smem, stream); \
     else launch_norm_bwd<R, 0>(a, grid, threads, smem, stream);               \
   } while (0)
-  if (a.rms) RT_NORM_BWD(true);
+  if (vpt == 1 || vpt == 2 || vpt == 4) {
+    if (a.rms) {
+      if (vpt == 1) launch_norm_bwd_wide<true, 1>(a, grid, stream);
+      else if (vpt == 2) launch_norm_bwd_wide<true, 2>(a, grid, stream);
+      else launch_norm_bwd_wide<true, 4>(a, grid, stream);
+    } else {
+      if (vpt == 1) launch_norm_bwd_wide<false, 1>(a, grid, stream);
+      else if (vpt == 2) launch_norm_bwd_wide<false, 2>(a, grid, stream);
+      else launch_norm_bwd_wide<false, 4>(a, grid, stream);
+    }
+  } else if (a.rms) RT_NORM_BWD(true);
   else RT_NORM_BWD(false);
 #undef RT_NORM_BWD
   if (a.dgamma != nullptr || (!a.rms && a.dbeta != nullptr)) {

@@ -13,7 +13,7 @@ def _bf(shape, seed, scale=1.0):
     return (torch.randn(shape, device="cuda", generator=g) * scale).to(torch.bfloat16)
 
 
-@pytest.mark.parametrize("rows,C", [(64, 768), (1000, 256), (33, 4096)])
+@pytest.mark.parametrize("rows,C", [(64, 768), (1000, 256), (33, 4096), (700, 2048), (50, 8192), (40, 3072)])
 def test_layer_norm_fwd_bwd(rows, C):
     from rustorch_b200.ops import kernels as K_
     x, w, b, dy, dres = _bf((rows, C), 1), _bf((C,), 2), _bf((C,), 3), _bf((rows, C), 4), _bf((rows, C), 5)
@@ -31,7 +31,7 @@ def test_layer_norm_fwd_bwd(rows, C):
     assert rel_err(db, br.grad) < 1e-2
 
 
-@pytest.mark.parametrize("rows,C", [(128, 512), (77, 4096)])
+@pytest.mark.parametrize("rows,C", [(128, 512), (77, 4096), (1300, 4096), (19, 8192), (64, 5120)])
 def test_rms_norm_fwd_bwd(rows, C):
     from rustorch_b200.ops import kernels as K_
     x, w, dy = _bf((rows, C), 1), _bf((C,), 2), _bf((rows, C), 4)
