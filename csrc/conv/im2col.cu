@@ -29,11 +29,23 @@ __global__ void __launch_bounds__(256) im2col_kernel(const __nv_bfloat16* __rest
   const long long total = (long long)N * OH * OW * kv;
   const __nv_bfloat16 zero = __float2bfloat16(0.f);
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
-    const long long pix = t / kv;
-    const int k0 = (int)(t - pix * kv) * 8;
-    const int ow = (int)(pix % OW);
-    const long long r = pix / OW;
-    const int oh = (int)(r % OH), n = (int)(r / OH);
+    long long pix;
+    int k0, ow, oh, n;
+    if (total < 0x7fffffffLL) {  // 32-bit divisions: an order of magnitude cheaper than the 64-bit ones
+      const unsigned tt = (unsigned)t, p32 = tt / (unsigned)kv, r32 = p32 / (unsigned)OW;
+      pix = p32;
+      k0 = (int)(tt - p32 * (unsigned)kv) * 8;
+      ow = (int)(p32 - r32 * (unsigned)OW);
+      n = (int)(r32 / (unsigned)OH);
+      oh = (int)(r32 - (unsigned)n * (unsigned)OH);
+    } else {
+      pix = t / kv;
+      k0 = (int)(t - pix * kv) * 8;
+      ow = (int)(pix % OW);
+      const long long r = pix / OW;
+      oh = (int)(r % OH);
+      n = (int)(r / OH);
+    }
     const int h0 = oh * stride - pad, col0 = (ow * stride - pad) * C;       // first input row / first element of a kernel row
     int kh = k0 / row_len, j = k0 - kh * row_len;
     const __nv_bfloat16* img = x + (long long)n * H * wc;
