@@ -17,6 +17,7 @@ ColumnParallel / RowParallel layers slice weights on the host and call a blockin
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -47,7 +48,7 @@ class AllGatherGemm:
     """``out[W*rows, N] = all_gather(shards)[W*rows, K] @ weight^T (+ bias)`` as one kernel.  Write this rank's rows into
     ``self.x_shard`` (or pass ``x``), then call."""
 
-    def __init__(self, rows_per_rank: int, K_: int, device, group=None, timeout_s: float = 20.0, n_comm: int = 8):
+    def __init__(self, rows_per_rank: int, K_: int, device, group=None, timeout_s: float = 20.0, n_comm: Optional[int] = None):
         if rows_per_rank % 128:
             raise ValueError("rows per rank must be a multiple of 128")
         self.group, self.world, self.rank = _group_info(group)
@@ -59,6 +60,10 @@ class AllGatherGemm:
         self.gather = torch.empty(W * rows_per_rank, K_, dtype=torch.bfloat16, device=self.device)
         self.mb_ready = torch.zeros(W * rows_per_rank // 128, dtype=torch.int32, device=self.device)
         self.comm_done = torch.zeros(1, dtype=torch.int32, device=self.device)
+        if n_comm is None:
+            # copy CTAs: the bytes they keep in flight (a few hundred KB each) over the NVLink latency set the pull rate.
+            # Eight of them moved 235 MB at ~250 GB/s on 8 ranks (transfer-bound), while 2 ranks need no more than 8.
+            n_comm = int(os.environ.get("RUSTORCH_TP_NCOMM", "0")) or (8 if W <= 2 else 16 if W <= 4 else 24)
         self.epoch, self.timeout_s, self.n_comm = 0, timeout_s, n_comm
 
     def __call__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, x: Optional[torch.Tensor] = None,
