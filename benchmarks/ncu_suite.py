@@ -45,6 +45,10 @@ def case_norm():
     K.layer_norm_bwd(dy, x, w, mean, rstd, dg, db, dres=dy)
     y, rstd = K.rms_norm_fwd(x, w, 1e-5)
     K.rms_norm_bwd(dy, x, w, rstd, dg)
+    del x, dy, y
+    xw, ww, dyw = bf(16384, 4096), bf(4096), bf(16384, 4096)       # wide rows (Llama-8B width): CTA-per-row backward
+    yw, rstdw = K.rms_norm_fwd(xw, ww, 1e-5)
+    K.rms_norm_bwd(dyw, xw, ww, rstdw, torch.zeros(4096, device="cuda"))
 
 
 def case_optim():
