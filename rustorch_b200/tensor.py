@@ -127,11 +127,22 @@ class Tensor:
         return cls(torch.tensor(float(v)), **kw)
 
     @classmethod
+    def _wrap(cls, t: torch.Tensor) -> "Tensor":
+        """Wrap an existing torch tensor without the conversions of ``__init__`` (creation fast path)."""
+        obj = cls.__new__(cls)
+        obj.data = t
+        return obj
+
+    @classmethod
     def zeros(cls, shape, dtype=None, device=None) -> "Tensor":
+        if dtype is None and device is None:
+            return cls._wrap(torch.zeros(shape, dtype=torch.float32))
         return cls(torch.zeros(tuple(shape), dtype=to_torch_dtype(dtype or "f32"), device=_dev(device)))
 
     @classmethod
     def ones(cls, shape, dtype=None, device=None) -> "Tensor":
+        if dtype is None and device is None:
+            return cls._wrap(torch.ones(shape, dtype=torch.float32))
         return cls(torch.ones(tuple(shape), dtype=to_torch_dtype(dtype or "f32"), device=_dev(device)))
 
     @classmethod
