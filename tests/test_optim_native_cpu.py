@@ -80,3 +80,18 @@ def test_flat_params_keep_channels_last_filters_in_physical_order():
     assert flat.collect_autograd_grads() == 6
     assert torch.allclose(flat.named_views(flat.grad)["0.weight"], g0)
     assert torch.allclose(m[0].weight.main_grad.view(8, 3, 3, 4), g0.permute(0, 2, 3, 1))
+
+
+def test_split_k_rule_fills_one_wave():
+    """Weight-gradient GEMMs split the contraction so that tiles x splits stay within one wave of 148 CTAs."""
+    from rustorch_b200.nn import fused
+    from rustorch_b200.distributed.tp_fused import _wgrad_splits
+    sms = fused._NUM_SMS
+    for tiles, kb in ((72, 256), (54, 256), (18, 256), (1, 4096), (147, 256), (148, 256), (1179, 256), (6, 16)):
+        sk = fused._split_k_for(tiles, kb)
+        assert sk >= 1 and (tiles >= sms or tiles * sk <= sms) and sk <= max(1, kb // 8)
+        if tiles < sms and kb >= 8 * (sms // tiles):
+            assert tiles * (sk + 1) > sms                # as many splits as fit
+    assert fused._split_k_for(72, 256) == sms // 72
+    assert _wgrad_splits(3072, 768, 16384) == fused._split_k_for(24 * 3, 256)
+    assert _wgrad_splits(50304, 768, 16384) == 1
