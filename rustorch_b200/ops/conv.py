@@ -16,12 +16,16 @@ import torch.nn.functional as F
 from .. import _native
 
 
+def _all_one(v) -> bool:
+    return v == 1 if isinstance(v, int) else all(int(e) == 1 for e in v)
+
+
 def supported(x: torch.Tensor, weight: torch.Tensor, stride, padding, dilation=1, groups: int = 1) -> bool:
     s = stride if isinstance(stride, int) else stride[0]
     p = padding if isinstance(padding, int) else padding[0]
     if not (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 4 and _native.available()):
         return False
-    if groups != 1 or (dilation if isinstance(dilation, int) else dilation[0]) != 1:
+    if groups != 1 or not _all_one(dilation):
         return False
     if not isinstance(stride, int) and stride[0] != stride[1]:
         return False
@@ -134,7 +138,7 @@ def im2col_supported(x: torch.Tensor, weight: torch.Tensor, stride, padding, dil
     """Few input channels (a network's stem): patch matrix + tcgen05 GEMM.  The input must not need a gradient."""
     if not (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 4 and _native.available()):
         return False
-    if x.requires_grad or groups != 1 or (dilation if isinstance(dilation, int) else dilation[0]) != 1:
+    if x.requires_grad or groups != 1 or not _all_one(dilation):
         return False
     if not isinstance(stride, int) and stride[0] != stride[1] or not isinstance(padding, int) and padding[0] != padding[1]:
         return False
@@ -202,7 +206,7 @@ def _one(v) -> int:
 def conv1d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, stride=1, padding=0, dilation=1,
            groups: int = 1) -> torch.Tensor:
     """``[N, C, L]`` convolution as a one-row image on the 2-D kernels (padding along the length only)."""
-    if (x.dim() == 3 and not isinstance(padding, str) and _one(dilation) == 1 and groups == 1 and _one(stride) <= 4
+    if (x.dim() == 3 and not isinstance(padding, str) and _all_one(dilation) and groups == 1 and _one(stride) <= 4
             and supported(x.unsqueeze(2), weight.unsqueeze(2), _one(stride), (0, _one(padding)))):
         y = Conv2dFn.apply(x.unsqueeze(2), weight.unsqueeze(2), bias, _one(stride), (0, _one(padding)))
         return y.squeeze(2)
@@ -256,7 +260,7 @@ def conv_transpose2d_supported(x, weight, stride, padding, output_padding, dilat
     if not (x.is_cuda and x.dim() == 4 and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and _native.available()):
         return False
     s, p, op = _pads(stride), _pads(padding), _pads(output_padding)
-    if s[0] != s[1] or p[0] != p[1] or op[0] != op[1] or _one(dilation) != 1 or groups != 1 or not 1 <= s[0] <= 4:
+    if s[0] != s[1] or p[0] != p[1] or op[0] != op[1] or not _all_one(dilation) or groups != 1 or not 1 <= s[0] <= 4:
         return False
     Cin, Cout, KH, KW = weight.shape
     if Cin % 64 or Cout % 64 or KH > 7 or KW > 7 or KH - 1 - p[0] < 0 or KW - 1 - p[0] < 0 or op[0] >= s[0]:
