@@ -144,6 +144,17 @@ def _attention(q, k, v):
 
 
 class LlamaBlock(nn.Module):
+    def shard_spec(self) -> dict:
+        """How the fused projections are cut over tensor-parallel ranks (``training.sharded``): q | k | v and gate | up
+        are sharded part by part, so a rank holds the concatenation of its slice of every part."""
+        from ..training.sharded import ShardSpec
+        c = self.cfg
+        D = c.head_dim
+        dot = ".weight" if self.tp else ""
+        return {"wqkv" + dot: ShardSpec(0, [c.n_head * D, c.n_head_kv * D, c.n_head_kv * D]),
+                "w_gate_up" + dot: ShardSpec(0, [c.n_ff, c.n_ff]),
+                "wo" + dot: ShardSpec(1), "w_down" + dot: ShardSpec(1)}
+
     def __init__(self, cfg: LlamaTrainConfig, device=None, dtype=None, tp_group=None, rows_per_rank: int = 0):
         super().__init__()
         self.cfg = cfg

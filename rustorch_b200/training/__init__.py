@@ -523,3 +523,11 @@ class TrainerBuilder:
 
     def build(self) -> Trainer:
         return Trainer(self._cfg, self._cbs, self._metrics)
+
+
+def __getattr__(name: str):
+    """``training.sharded`` members (sharded checkpoints, ``AsyncCheckpointer``) load on first use."""
+    if name in ("ShardSpec", "save_sharded", "merge_sharded", "load_sharded", "infer_spec", "shard_tensor", "merge_tensors", "AsyncCheckpointer"):
+        from . import sharded
+        return getattr(sharded, name)
+    raise AttributeError(name)
