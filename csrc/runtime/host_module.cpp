@@ -9,6 +9,7 @@
 #include "arena.h"
 #include "cpu_optim.h"
 #include "plan.h"
+#include "protocol_sim.h"
 
 namespace py = pybind11;
 
@@ -67,6 +68,37 @@ PYBIND11_MODULE(_host, m) {
                               reinterpret_cast<float*>(pg), reinterpret_cast<float*>(S), reinterpret_cast<float*>(Y),
                               reinterpret_cast<float*>(rho), reinterpret_cast<float*>(scratch), n, hist, count, head, has_prev, lr);
   });
+
+  // host emulation of the peer-memory kernels' synchronisation protocols, one thread per rank (GIL released)
+  auto sim_dict = [](const rt_host::SimResult& r) {
+    py::dict d;
+    d["mismatches"] = r.mismatches;
+    d["timeouts"] = r.timeouts;
+    d["checked"] = r.checked;
+    return d;
+  };
+  m.def("sim_lamport_allreduce",
+        [sim_dict](int world, long long calls, int words, int slots, int slow_rank, int slow_us, unsigned seed) {
+          rt_host::SimResult r;
+          {
+            py::gil_scoped_release nogil;
+            r = rt_host::sim_lamport_allreduce(world, calls, words, slots, slow_rank, slow_us, seed);
+          }
+          return sim_dict(r);
+        },
+        py::arg("world"), py::arg("calls"), py::arg("words") = 64, py::arg("slots") = 3, py::arg("slow_rank") = -1,
+        py::arg("slow_us") = 0, py::arg("seed") = 1);
+  m.def("sim_epoch_counters",
+        [sim_dict](int world, long long calls, int blocks, int tiles, int parities, int slow_rank, int slow_us, unsigned seed) {
+          rt_host::SimResult r;
+          {
+            py::gil_scoped_release nogil;
+            r = rt_host::sim_epoch_counters(world, calls, blocks, tiles, parities, slow_rank, slow_us, seed);
+          }
+          return sim_dict(r);
+        },
+        py::arg("world"), py::arg("calls"), py::arg("blocks") = 4, py::arg("tiles") = 8, py::arg("parities") = 2,
+        py::arg("slow_rank") = -1, py::arg("slow_us") = 0, py::arg("seed") = 1);
 
   py::class_<rt::Arena>(m, "Arena")
       .def(py::init<uint64_t, uint64_t>(), py::arg("capacity"), py::arg("alignment") = 256)

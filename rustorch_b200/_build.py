@@ -135,7 +135,7 @@ def build_host(verbose: bool = False, force: bool = False) -> Path:
     BUILD.mkdir(parents=True, exist_ok=True)
     srcs = sorted((CSRC / "runtime").glob("*.cpp"))
     hdr = _headers_digest()
-    flags = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", f"-I{pybind11.get_include()}",
+    flags = ["-O2", "-std=c++17", "-fPIC", "-pthread", "-fvisibility=hidden", f"-I{pybind11.get_include()}",
              f"-I{sysconfig.get_paths()['include']}", f"-I{CSRC}"]
     objs, rebuilt = [], False
     for s in srcs:
@@ -147,7 +147,7 @@ def build_host(verbose: bool = False, force: bool = False) -> Path:
             _run(["g++", *flags, "-c", str(s), "-o", str(o)])
             rebuilt = True
     if rebuilt or force or not HOST_TARGET.exists():
-        _run(["g++", "-shared", "-o", str(HOST_TARGET), *map(str, objs)])
+        _run(["g++", "-shared", "-pthread", "-o", str(HOST_TARGET), *map(str, objs)])
     return HOST_TARGET
 
 
