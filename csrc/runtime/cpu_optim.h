@@ -1,6 +1,7 @@
 // Single-tensor optimizer updates on host memory (fp32), for the small-tensor regime where interpreter overhead, not
 // arithmetic, sets the step rate (the reference publishes 15-34 K steps/s on a 1000-element parameter,
-// docs/guides/performance.md:15-18).  Same update formulas as torch.optim, so the two paths are interchangeable.
+// docs/guides/performance.md:15-18; its updates are src/optim/adamax.rs, nadam.rs:135-156, radam.rs:187-205,
+// lbfgs.rs:192-203).  Same update formulas as torch.optim, so the two paths are interchangeable.
 #pragma once
 #include <cstdint>
 
