@@ -159,3 +159,22 @@ def test_gpu_trait_methods_and_linalg_helpers_on_cpu():
     assert T.select_optimal_device(4) == "cpu" and T.multithreaded_matmul(a, a, 2).data.shape == (2, 2)
     assert T.memory_optimized((3, 3)).data.sum() == 0
     assert float(GpuParallelOp().gpu_var(torch.tensor([1.0, 3.0]))) == 1.0
+
+
+def test_guarded_tensor_detects_overrun():
+    import pytest
+    import torch
+    from rustorch_b200.debug.guards import GuardedTensor, guard_scope
+    from rustorch_b200.error import RusTorchError
+    g = GuardedTensor((5, 7), torch.bfloat16)
+    assert g.tensor.shape == (5, 7) and g.tensor.is_contiguous() and g.tensor.data_ptr() % 16 == 0
+    with guard_scope(g):
+        g.tensor.fill_(3.0)                               # in bounds: nothing to report
+    past_end = torch.as_strided(g.tensor, (36,), (1,))    # one element more than the 35 the tensor has
+    past_end[35] = 1.0
+    assert g.violations() and g.violations()[0] == 70
+    with pytest.raises(RusTorchError):
+        g.check("workspace")
+    h = GuardedTensor((16,), torch.float32)
+    torch.as_strided(h.tensor, (1,), (1,), storage_offset=h.tensor.storage_offset() - 1)[0] = 2.0
+    assert h.violations()[0] == -4
