@@ -63,7 +63,18 @@ _SUBMODULES = ("nn", "optim", "data", "training", "models", "distributed", "form
                "optimization", "compat")
 
 
+# functional activations and image transforms of the reference's Python module (src/python/nn.rs, src/python/data.rs)
+_FUNCTIONAL = ("relu", "sigmoid", "tanh", "softmax", "gelu", "leaky_relu", "swish", "elu", "selu", "mish")
+_TRANSFORMS = ("normalize", "resize", "random_crop", "random_horizontal_flip")
+
+
 def __getattr__(name):
+    if name in _FUNCTIONAL:
+        from .nn import layers
+        return getattr(layers, name)
+    if name in _TRANSFORMS:
+        from .python_api import Transforms
+        return getattr(Transforms, name)
     if name == "functional":
         from .nn import layers
         return layers
@@ -76,4 +87,4 @@ def __getattr__(name):
 
 
 def __dir__():
-    return sorted(list(globals()) + list(_LAZY) + list(_SUBMODULES) + ["functional"])
+    return sorted(list(globals()) + list(_LAZY) + list(_SUBMODULES) + ["functional"] + list(_FUNCTIONAL) + list(_TRANSFORMS))

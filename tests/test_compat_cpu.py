@@ -178,3 +178,20 @@ def test_guarded_tensor_detects_overrun():
     h = GuardedTensor((16,), torch.float32)
     torch.as_strided(h.tensor, (1,), (1,), storage_offset=h.tensor.storage_offset() - 1)[0] = 2.0
     assert h.violations()[0] == -4
+
+
+def test_python_module_surface_of_the_reference():
+    """Names of the reference's Python module (src/python/mod.rs:51-115) resolve on ``import rustorch``."""
+    import rustorch as rt
+    names = ("Tensor Variable Linear Conv2d MaxPool2d BatchNorm1d BatchNorm2d Dropout Flatten ReLU Sigmoid Tanh MSELoss "
+             "CrossEntropyLoss SGD Adam tensor zeros ones no_grad enable_grad grad Device relu sigmoid tanh softmax gelu leaky_relu "
+             "swish elu selu mish StepLR ExponentialLR TensorDataset DataLoader Transform Transforms normalize resize random_crop "
+             "random_horizontal_flip Trainer TrainerConfig TrainingHistory Model ModelBuilder ModelSerializer ModelComparator Config "
+             "Profiler get_system_info set_seed cuda_is_available DistributedDataParallel DistributedConfig DistributedBackend "
+             "DistributedSampler init_distributed get_world_size get_rank is_master cleanup_distributed Plotter ModelVisualizer "
+             "TensorStats Sequential Module Parameter").split()
+    missing = [n for n in names if not hasattr(rt, n)]
+    assert not missing, missing
+    import torch
+    x = torch.tensor([-1.0, 0.5])
+    assert torch.equal(rt.relu(x), torch.tensor([0.0, 0.5])) and abs(float(rt.softmax(x).sum()) - 1.0) < 1e-6
