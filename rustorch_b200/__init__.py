@@ -48,6 +48,10 @@ _LAZY = {
     **{n: "compat" for n in ("AdamConfig", "AdamState", "AdamUtils", "LBFGSMemory", "LineSearchMethod", "AllocationStrategy", "ZeroCopyOps",
                              "TensorIterOps", "ShapeBuilder", "LazyExpandedTensor", "SafeTensor", "SafeNumeric", "TypedTensor", "WindowType",
                              "Int4", "ProfilerCore", "RecurrentOps", "LinearBackward", "DistributedState", "GPTModel", "OnnxModel")},
+    **{n: "compat_extra" for n in ("GradFn", "AddBackward", "SubBackward", "MulBackward", "MatMulBackward", "SumBackward", "MeanBackward",
+                                   "TensorMetadata", "StateDict", "ModelStateDict", "AdamVariant", "CommonOps", "GenericAdamOptimizer",
+                                   "GradientCompression", "GpuBuffer", "CudaBlas", "CudaSparseOps", "GpuActivation", "GpuConvolution",
+                                   "GpuBatchMatrixExecutor", "CommunicationOp", "CommunicationManager")},
     **{n: "formats.loaders" for n in ("GGUFLoader", "SafetensorsLoader", "SafetensorsSaver", "Saver", "TensorLoader")},
     **{n: "gpu.devices" for n in ("GpuDevice", "GpuStream", "CpuDevice", "CudaDevice", "GpuKernel", "ModernGpuKernel", "AddKernel", "MatMulKernel",
                                   "ConvKernel", "KernelExecutor", "CudaKernelExecutor", "CudaMatrixExecutor", "CudaBuffer", "ComputeBackend",
@@ -60,7 +64,7 @@ _LAZY = {
 _SUBMODULES = ("nn", "optim", "data", "training", "models", "distributed", "formats", "llm", "amp", "profiler", "debug", "validation",
                "tensorboard", "visualization", "vision", "distributions", "special", "quantization", "sparse", "memory", "gpu", "execution",
                "model_import", "convert", "model_hub", "jit", "cli", "autograd", "ops", "utils", "parallel", "error", "hybrid_f32",
-               "optimization", "compat")
+               "optimization", "compat", "compat_extra")
 
 
 # functional activations and image transforms of the reference's Python module (src/python/nn.rs, src/python/data.rs)

@@ -195,3 +195,54 @@ def test_python_module_surface_of_the_reference():
     import torch
     x = torch.tensor([-1.0, 0.5])
     assert torch.equal(rt.relu(x), torch.tensor([0.0, 0.5])) and abs(float(rt.softmax(x).sum()) - 1.0) < 1e-6
+
+
+def test_compat_extra_objects(tmp_path):
+    import torch
+    import rustorch_b200 as rt
+    a, b = torch.randn(3, 4, requires_grad=True), torch.randn(4, 5, requires_grad=True)
+    g = torch.randn(3, 5)
+    (a @ b).backward(g)
+    ga, gb = rt.MatMulBackward(a.detach(), b.detach()).apply(g)
+    assert torch.allclose(ga, a.grad) and torch.allclose(gb, b.grad)
+    x, y = torch.randn(3, 4), torch.randn(1, 4)
+    gx, gy = rt.MulBackward(x, y).apply(torch.ones(3, 4))
+    assert gx.shape == x.shape and gy.shape == y.shape and torch.allclose(gy, x.sum(0, keepdim=True))
+    assert torch.allclose(rt.MeanBackward(x).apply(torch.tensor(1.0))[0], torch.full_like(x, 1 / 12))
+    # state dicts
+    m = torch.nn.Sequential(torch.nn.Linear(4, 3), torch.nn.BatchNorm1d(3))
+    sd = rt.StateDict.from_module(m)
+    assert "1.running_mean" in sd.buffers and sd.tensor_metadata()["0.weight"].shape == [3, 4]
+    path = str(tmp_path / "sd.rustorch")
+    sd.save(path)
+    back = rt.StateDict.load(path)
+    assert torch.equal(back.parameters["0.weight"], sd.parameters["0.weight"]) and torch.equal(back.buffers["1.running_var"], sd.buffers["1.running_var"])
+    msd = rt.ModelStateDict.from_module(m)
+    assert torch.allclose(msd.to_tensors()["0.bias"], m[0].bias.detach())
+    # generic Adam family
+    p = torch.nn.Parameter(torch.ones(4))
+    opt = rt.GenericAdamOptimizer([p], rt.AdamVariant.RADAM, lr=0.1)
+    p.grad = torch.ones(4)
+    opt.step()
+    assert type(opt).__name__ == "RAdam" and float(p.detach().sum()) < 4.0
+    assert abs(rt.CommonOps.bias_correction(0.9, 2) - 0.19) < 1e-12
+    # gradient compression
+    grad = torch.randn(1000)
+    topk = rt.GradientCompression.TOP_K.compressor(ratio=0.1).compress_decompress(grad)
+    assert int((topk != 0).sum()) == 100 and torch.equal(topk[topk != 0], grad[topk != 0])
+    q = rt.GradientCompression.QUANTIZATION.compressor(bits=8).compress_decompress(grad)
+    assert float((q - grad).abs().max()) < float(grad.abs().max()) / 100
+    assert int((rt.GradientCompression.RANDOM.compressor(ratio=0.05).compress_decompress(grad) != 0).sum()) == 50
+    # device helpers on CPU
+    buf = rt.GpuBuffer.from_host([1.0, 2.0, 3.0], device="cpu")
+    assert len(buf) == 3 and not buf.is_cuda() and buf.to_host().tolist() == [1.0, 2.0, 3.0]
+    assert torch.allclose(rt.CudaBlas.gemm(x, y.t().contiguous()), x @ y.t())
+    dense = torch.tensor([[1.0, 0.0, 2.0], [0.0, 3.0, 0.0]])
+    csr = dense.to_sparse_csr()
+    v = torch.tensor([1.0, 1.0, 1.0])
+    assert torch.allclose(rt.CudaSparseOps.spmv(csr.crow_indices(), csr.col_indices(), csr.values(), v, 2), dense @ v)
+    assert torch.equal(rt.GpuActivation.relu(torch.tensor([-1.0, 2.0])), torch.tensor([0.0, 2.0]))
+    assert rt.GpuBatchMatrixExecutor("cpu").batch_matmul(torch.randn(2, 3, 4), torch.randn(2, 4, 5)).shape == (2, 3, 5)
+    mgr = rt.CommunicationManager()
+    mgr.schedule(rt.CommunicationOp.ALL_REDUCE, torch.ones(2))
+    assert mgr.execute_all()[0].tolist() == [1.0, 1.0] and mgr.completed == 1
