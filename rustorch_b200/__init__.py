@@ -51,7 +51,8 @@ _LAZY = {
     **{n: "compat_extra" for n in ("GradFn", "AddBackward", "SubBackward", "MulBackward", "MatMulBackward", "SumBackward", "MeanBackward",
                                    "TensorMetadata", "StateDict", "ModelStateDict", "AdamVariant", "CommonOps", "GenericAdamOptimizer",
                                    "GradientCompression", "GpuBuffer", "CudaBlas", "CudaSparseOps", "GpuActivation", "GpuConvolution",
-                                   "GpuBatchMatrixExecutor", "CommunicationOp", "CommunicationManager")},
+                                   "GpuBatchMatrixExecutor", "CommunicationOp", "CommunicationManager", "get_compute_capability",
+                                   "execute_attention")},
     **{n: "formats.loaders" for n in ("GGUFLoader", "SafetensorsLoader", "SafetensorsSaver", "Saver", "TensorLoader")},
     **{n: "gpu.devices" for n in ("GpuDevice", "GpuStream", "CpuDevice", "CudaDevice", "GpuKernel", "ModernGpuKernel", "AddKernel", "MatMulKernel",
                                   "ConvKernel", "KernelExecutor", "CudaKernelExecutor", "CudaMatrixExecutor", "CudaBuffer", "ComputeBackend",

@@ -342,6 +342,24 @@ class GpuBatchMatrixExecutor:
     def batch_matmul(self, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         return torch.bmm(a.to(self.device), b.to(self.device))
 
+    cuda_batch_matmul = batch_matmul
+
+
+def get_compute_capability(device: int = 0) -> Tuple[int, int]:
+    """``(major, minor)`` of a CUDA device, ``(0, 0)`` without one (src/gpu/cuda_enhanced.rs:160-190)."""
+    return tuple(torch.cuda.get_device_capability(device)) if torch.cuda.is_available() else (0, 0)
+
+
+def execute_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False) -> torch.Tensor:
+    """``softmax(q k^T / sqrt(d)) v`` over ``[B, H, T, D]`` (the reference's custom-kernel entry, src/gpu/custom_kernels.rs:
+    439-536, computes it on the host): bf16 CUDA inputs with D = 64 / 128 run on the tcgen05 flash-attention kernel."""
+    from . import _native
+    if q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and _native.available():
+        from .nn.fused import FlashAttentionFn                     # expects [B, T, H, D]
+        o = FlashAttentionFn.apply(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), causal, None)
+        return o.transpose(1, 2)
+    return torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=causal)
+
 
 # ------------------------------------------------------------------------------------------------ model-parallel communication
 class CommunicationOp(enum.Enum):

@@ -431,6 +431,54 @@ class NCCLOps:
                                  num_streams=8 if num_gpus > 4 else 4)
 
 
+    @staticmethod
+    def init_multi_gpu(device_ids: Optional[List[int]] = None) -> "MultiGpuContext":
+        """A context over the given (default: all visible) devices (nccl_integration.rs:402-440)."""
+        ids = list(device_ids) if device_ids is not None else list(range(max(1, torch.cuda.device_count())))
+        return MultiGpuContext(ids)
+
+    @staticmethod
+    def all_reduce_multi_gpu(tensors: List[torch.Tensor], average: bool = True) -> List[torch.Tensor]:
+        """In-place all-reduce over one tensor per device (nccl_integration.rs:441-470)."""
+        return p2p_all_reduce(tensors, average)
+
+
+def p2p_all_reduce(tensors: List[torch.Tensor], average: bool = False) -> List[torch.Tensor]:
+    """Ring all-reduce (reduce-scatter + all-gather, chunk = numel / devices) over one tensor per device, in place
+    (src/gpu/multi_gpu.rs:583-700)."""
+    if len(tensors) > 1 and tensors[0].numel() >= len(tensors):
+        MultiGpuContext._ring_all_reduce(tensors)
+    elif len(tensors) > 1:
+        host_staged_all_reduce(tensors, average=False)
+    if average:
+        for t in tensors:
+            t.div_(len(tensors))
+    return tensors
+
+
+def host_staged_all_reduce(tensors: List[torch.Tensor], average: bool = True) -> List[torch.Tensor]:
+    """Sum on the host, copy the result back to every device (src/gpu/multi_gpu.rs:704-751)."""
+    total = torch.zeros_like(tensors[0], device="cpu", dtype=torch.float32)
+    for t in tensors:
+        total += t.detach().to("cpu", torch.float32)
+    if average:
+        total /= len(tensors)
+    for t in tensors:
+        t.copy_(total.to(t.device, t.dtype))
+    return tensors
+
+
+def nccl_all_reduce(tensor: torch.Tensor, average: bool = False, group=None) -> torch.Tensor:
+    """All-reduce across the process group when one is initialised (NCCL on GPUs, gloo on CPU), else identity
+    (``CommunicationManager::nccl_all_reduce``, src/gpu/multi_gpu.rs:560-582)."""
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(tensor, group=group)
+        if average:
+            tensor.div_(dist.get_world_size(group))
+    return tensor
+
+
 class NCCLProfiler:
     """Times collectives and reports bandwidth (``TimingGuard`` is the context manager)."""
 

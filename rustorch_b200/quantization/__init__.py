@@ -547,3 +547,17 @@ def prepare_qat(model: nn.Module, config: Optional[QATConfig] = None) -> nn.Modu
         else:
             prepare_qat(child, config)
     return model
+
+
+def qmatmul_cuda(a: "QuantizedTensor", b: "QuantizedTensor", out_scale=None, out_zp=None) -> "QuantizedTensor":
+    """int8 matmul with the operands moved to the GPU when one is present (src/quantization/hardware.rs qmatmul_cuda runs
+    CPU loops behind the name)."""
+    if torch.cuda.is_available():
+        a, b = a.to("cuda") if hasattr(a, "to") else a, b.to("cuda") if hasattr(b, "to") else b
+    return QuantizedOps.qmatmul(a, b, out_scale, out_zp)
+
+
+def qconv2d_cuda(x: "QuantizedTensor", w: "QuantizedTensor", bias=None, stride=1, padding=0) -> torch.Tensor:
+    if torch.cuda.is_available():
+        x, w = x.to("cuda") if hasattr(x, "to") else x, w.to("cuda") if hasattr(w, "to") else w
+    return QuantizedOps.qconv2d(x, w, bias, stride, padding)

@@ -496,3 +496,31 @@ class ImageFolder:
             t = t.unsqueeze(0)
         t = self.transform(t) if self.transform else (t.float() / 255.0 if t.dtype == torch.uint8 else t.float())
         return t, label
+
+
+def make_grid(images, nrow: int = 8, padding: int = 2, pad_value: float = 0.0) -> torch.Tensor:
+    """``[N, C, H, W]`` (or a list of ``[C, H, W]``) tiled into one ``[C, rows * (H + p) + p, cols * (W + p) + p]`` image
+    (src/vision/utils.rs make_grid)."""
+    x = torch.stack([_t(i) for i in images]) if not isinstance(images, torch.Tensor) else images
+    if x.dim() == 3:
+        x = x.unsqueeze(0)
+    n, c, h, w = x.shape
+    cols = min(nrow, n)
+    rows = -(-n // cols)
+    grid = torch.full((c, rows * (h + padding) + padding, cols * (w + padding) + padding), pad_value, dtype=x.dtype)
+    for i in range(n):
+        r, q = divmod(i, cols)
+        top, left = padding + r * (h + padding), padding + q * (w + padding)
+        grid[:, top:top + h, left:left + w] = x[i]
+    return grid
+
+
+def save_image(image, path: str, nrow: int = 8, padding: int = 2) -> None:
+    """Writes a ``[C, H, W]`` image (or a batch, tiled with ``make_grid``) with values in [0, 1] as PNG."""
+    from ..tensorboard import encode_png
+    x = image if isinstance(image, torch.Tensor) else torch.stack([_t(i) for i in image])
+    if x.dim() == 4:
+        x = make_grid(x, nrow, padding)
+    arr = (x.detach().float().clamp(0, 1) * 255).round().to(torch.uint8).permute(1, 2, 0).cpu().numpy()
+    with open(path, "wb") as f:
+        f.write(encode_png(arr))

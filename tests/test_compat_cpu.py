@@ -246,3 +246,27 @@ def test_compat_extra_objects(tmp_path):
     mgr = rt.CommunicationManager()
     mgr.schedule(rt.CommunicationOp.ALL_REDUCE, torch.ones(2))
     assert mgr.execute_all()[0].tolist() == [1.0, 1.0] and mgr.completed == 1
+
+
+def test_named_call_sites_of_the_reference(tmp_path):
+    import torch
+    import rustorch_b200 as rt
+    from rustorch_b200 import quantization, vision
+    from rustorch_b200.distributed import multi_gpu as mg
+    ts = [torch.full((8,), float(i + 1)) for i in range(4)]
+    assert all(torch.allclose(t, torch.full((8,), 10.0)) for t in mg.p2p_all_reduce([t.clone() for t in ts]))
+    assert all(torch.allclose(t, torch.full((8,), 2.5)) for t in mg.host_staged_all_reduce([t.clone() for t in ts]))
+    assert all(torch.allclose(t, torch.full((8,), 2.5)) for t in mg.NCCLOps.all_reduce_multi_gpu([t.clone() for t in ts]))
+    assert torch.equal(mg.nccl_all_reduce(torch.ones(3)), torch.ones(3))                  # no process group: identity
+    assert len(mg.NCCLOps.init_multi_gpu([0]).device_ids) == 1
+    grid = vision.make_grid(torch.rand(5, 3, 4, 4), nrow=3, padding=1)
+    assert grid.shape == (3, 2 * 5 + 1, 3 * 5 + 1)
+    png = str(tmp_path / "g.png")
+    vision.save_image(torch.rand(5, 3, 4, 4), png, nrow=3, padding=1)
+    assert open(png, "rb").read(4)[1:] == b"PNG"
+    assert rt.get_compute_capability() == (0, 0) or rt.get_compute_capability()[0] >= 7
+    q, k, v = (torch.randn(1, 2, 5, 8) for _ in range(3))
+    ref = torch.softmax(q @ k.transpose(-1, -2) / 8 ** 0.5, -1) @ v
+    assert torch.allclose(rt.execute_attention(q, k, v), ref, atol=1e-5)
+    assert hasattr(quantization, "qmatmul_cuda") and hasattr(quantization, "qconv2d_cuda")
+    assert rt.GpuBatchMatrixExecutor("cpu").cuda_batch_matmul(torch.randn(2, 3, 4), torch.randn(2, 4, 5)).shape == (2, 3, 5)
