@@ -34,6 +34,7 @@ struct GemmArgs {
   int split_k;
   int block_n;  // 0 = auto, 128 or 256
   bool ab_fp16 = false;  // A/B hold fp16 (C must be fp32, no fused epilogue)
+  const float* alpha_dev = nullptr;  // optional fp32 device scalar: the result is scaled by alpha * (*alpha_dev)
 };
 void gemm_bf16(const GemmArgs& g, cudaStream_t stream);
 
@@ -169,9 +170,11 @@ struct DdpBucketArgs {
   float* grad[RT_MAX_PEERS];  // every rank's flat fp32 gradient buffer (peer pointers)
   void* lp[RT_MAX_PEERS];     // every rank's flat bf16 parameter buffer (peer pointers)
   int* flags[RT_MAX_PEERS];   // every rank's flag array (peer pointers)
+  float* mc_grad = nullptr;   // multicast (NVLS) mapping of the gradient buffers, or null: plain peer loads / stores
+  void* mc_lp = nullptr;      // multicast mapping of the bf16 parameter buffers (needed together with mc_grad)
   float* master;              // local flat fp32 master weights / moments (indexed like grad)
-  float* m;
-  float* v;
+  float* m;                   // first moment / momentum buffer (null for SGD without momentum)
+  float* v;                   // second moment (null for SGD)
   unsigned* done_counter;     // local, zero-initialised
   long long bucket_start;     // flat index of the bucket
   long long chunk_len;        // elements owned by each rank inside the bucket (multiple of 4)
@@ -179,10 +182,12 @@ struct DdpBucketArgs {
   int epoch;                  // strictly increasing per step
   int start_slot, end_slot;   // offsets into the flag arrays (slot * world)
   unsigned long long timeout_ns;
+  int opt_mode = 0;           // OptimMode: OPT_ADAMW, OPT_ADAM or OPT_SGD (beta1 = momentum, beta2 = dampening)
+  int nesterov = 0, first_step = 0;
   float lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, grad_scale;
   int* status;
 };
-void ddp_bucket_adamw(const DdpBucketArgs& a, int n_ctas, cudaStream_t stream);
+void ddp_bucket_step(const DdpBucketArgs& a, int n_ctas, cudaStream_t stream);  // n_ctas <= 0: two per SM
 void ddp_wait_end(const int* flags, int n_slots, int world, int rank, int epoch,
                   unsigned long long timeout_ns, int* status, cudaStream_t stream);
 

@@ -27,7 +27,7 @@ void check_f32_cuda(const Tensor& t, const char* name) {
 
 void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, Tensor& c, const OptTensor& bias,
           const OptTensor& aux, int64_t epi_mode, double alpha, bool accumulate, int64_t split_k,
-          int64_t block_n) {
+          int64_t block_n, const OptTensor& alpha_dev) {
   const bool ab_fp16 = a.scalar_type() == at::kHalf;
   if (ab_fp16) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && b.scalar_type() == at::kHalf, "gemm: fp16 A needs a CUDA fp16 B");
@@ -85,6 +85,11 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, Tensor& c, con
   g.accumulate = accumulate;
   g.split_k = int(split_k);
   g.block_n = int(block_n);
+  if (alpha_dev.has_value() && alpha_dev->defined()) {
+    check_f32_cuda(*alpha_dev, "gemm alpha_dev");
+    TORCH_CHECK(alpha_dev->numel() == 1, "gemm: alpha_dev must hold one fp32 value");
+    g.alpha_dev = alpha_dev->data_ptr<float>();
+  }
   rt::gemm_bf16(g, stream_of(a));
 }
 
@@ -359,7 +364,10 @@ void register_extra_ops(pybind11::module_& m);  // bindings_extra.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "rustorch_b200 native sm_100a kernels";
-  m.def("gemm", &gemm, "bf16 tcgen05 GEMM with fused epilogues");
+  m.def("gemm", &gemm, "bf16 tcgen05 GEMM with fused epilogues", pybind11::arg("a"), pybind11::arg("a_mn"), pybind11::arg("b"),
+        pybind11::arg("b_mn"), pybind11::arg("c"), pybind11::arg("bias"), pybind11::arg("aux"), pybind11::arg("epi_mode"),
+        pybind11::arg("alpha"), pybind11::arg("accumulate"), pybind11::arg("split_k"), pybind11::arg("block_n"),
+        pybind11::arg("alpha_dev") = pybind11::none());
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
   m.def("norm_fwd", &norm_fwd);

@@ -16,19 +16,24 @@ using at::Tensor;
 cudaStream_t cur_stream(int device) { return at::cuda::getCurrentCUDAStream(device).stream(); }
 
 // Peer pointers arrive as Python ints (they come from symmetric-memory rendezvous).
-void ddp_bucket_adamw(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& lp_ptrs,
-                      const std::vector<int64_t>& flag_ptrs, Tensor& master, Tensor& m, Tensor& v,
-                      Tensor& done_counter, int64_t bucket_start, int64_t chunk_len, int64_t rank,
-                      int64_t epoch, int64_t start_slot, int64_t end_slot, double timeout_s, double lr,
-                      double beta1, double beta2, double eps, double weight_decay, double bias_corr1,
-                      double bias_corr2, double grad_scale, int64_t n_ctas) {
+void ddp_bucket_step(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& lp_ptrs,
+                     const std::vector<int64_t>& flag_ptrs, Tensor& master, const c10::optional<Tensor>& m_opt,
+                     const c10::optional<Tensor>& v_opt, Tensor& done_counter, int64_t bucket_start, int64_t chunk_len,
+                     int64_t rank, int64_t epoch, int64_t start_slot, int64_t end_slot, double timeout_s, double lr,
+                     double beta1, double beta2, double eps, double weight_decay, double bias_corr1,
+                     double bias_corr2, double grad_scale, int64_t n_ctas, int64_t opt_mode, bool nesterov,
+                     bool first_step, int64_t mc_grad_ptr, int64_t mc_lp_ptr) {
   const int world = int(grad_ptrs.size());
   TORCH_CHECK(world >= 1 && world <= rt::RT_MAX_PEERS, "ddp: world size must be in [1, 8]");
   TORCH_CHECK(int(lp_ptrs.size()) == world && int(flag_ptrs.size()) == world, "ddp: pointer lists differ");
-  TORCH_CHECK(master.is_cuda() && master.scalar_type() == at::kFloat && master.is_contiguous() &&
-                  m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat &&
-                  m.numel() == master.numel() && v.numel() == master.numel(),
-              "ddp: master/m/v must be flat fp32 CUDA buffers of equal length");
+  TORCH_CHECK(master.is_cuda() && master.scalar_type() == at::kFloat && master.is_contiguous(),
+              "ddp: master must be a flat fp32 CUDA buffer");
+  auto state_ptr = [&](const c10::optional<Tensor>& t) -> float* {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == master.numel(),
+                "ddp: optimizer state must be a flat fp32 CUDA buffer as long as master");
+    return t->data_ptr<float>();
+  };
   TORCH_CHECK(bucket_start >= 0 && bucket_start + chunk_len * world <= master.numel(),
               "ddp: bucket outside the flat buffer");
   c10::cuda::CUDAGuard guard(master.device());
@@ -39,8 +44,13 @@ void ddp_bucket_adamw(const std::vector<int64_t>& grad_ptrs, const std::vector<i
     a.flags[p] = reinterpret_cast<int*>(flag_ptrs[p]);
   }
   a.master = master.data_ptr<float>();
-  a.m = m.data_ptr<float>();
-  a.v = v.data_ptr<float>();
+  a.m = state_ptr(m_opt);
+  a.v = state_ptr(v_opt);
+  a.mc_grad = reinterpret_cast<float*>(mc_grad_ptr);
+  a.mc_lp = reinterpret_cast<void*>(mc_lp_ptr);
+  a.opt_mode = int(opt_mode);
+  a.nesterov = nesterov ? 1 : 0;
+  a.first_step = first_step ? 1 : 0;
   a.done_counter = reinterpret_cast<unsigned*>(done_counter.data_ptr<int32_t>());
   a.bucket_start = bucket_start;
   a.chunk_len = chunk_len;
@@ -59,7 +69,7 @@ void ddp_bucket_adamw(const std::vector<int64_t>& grad_ptrs, const std::vector<i
   a.bias_corr2 = float(bias_corr2);
   a.grad_scale = float(grad_scale);
   a.status = rt::status_word(master.device().index());
-  rt::ddp_bucket_adamw(a, int(n_ctas), cur_stream(master.device().index()));
+  rt::ddp_bucket_step(a, int(n_ctas), cur_stream(master.device().index()));
 }
 
 void ddp_wait_end(int64_t flags_ptr, int64_t n_slots, int64_t world, int64_t rank, int64_t epoch,
@@ -845,7 +855,8 @@ void register_extra_ops(pybind11::module_& m) {
   m.def("rope_kv", &rope_kv);
   m.def("attn_cache", &attn_cache);
   m.def("silu_mul", &silu_mul);
-  m.def("ddp_bucket_adamw", &ddp_bucket_adamw,
-        "fused reduce-scatter + scale + AdamW + all-gather of one gradient bucket over peer memory");
+  m.def("ddp_bucket_step", &ddp_bucket_step,
+        "fused reduce-scatter + scale + AdamW / Adam / SGD + all-gather of one gradient bucket over peer memory "
+        "(plain peer loads / stores, or NVLS multimem when the multicast pointers are non-zero)");
   m.def("ddp_wait_end", &ddp_wait_end);
 }

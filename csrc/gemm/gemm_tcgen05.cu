@@ -37,6 +37,7 @@ struct GemmParams {
   __nv_bfloat16* aux;         // same geometry as C (bf16) or null
   long long ld_aux, aux_batch_stride;
   float alpha;
+  const float* alpha_dev;  // optional device scalar multiplied into alpha (read by the epilogue warps)
   int epi_mode;
   int out_fp32;    // C is fp32 instead of bf16
   int accumulate;  // fp32 only: C += result using red.global.add.f32 (required when split_k > 1)
@@ -219,6 +220,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t tile_i = 0;
     bool ok = true;
     const bool vec_ok = ((p.ldc & 7) == 0) && (p.aux == nullptr || (p.ld_aux & 7) == 0);
+    const float alpha = p.alpha_dev ? p.alpha * __ldg(p.alpha_dev) : p.alpha;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
       int split, b, mb, nb;
       decode_tile(t, p, split, b, mb, nb);
@@ -269,7 +271,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int nh = n0 + h * 32;
             float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r2[h][j]) * p.alpha;
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r2[h][j]) * alpha;
             if (add_bias) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] += __bfloat162float(p.bias[nh + j]);
@@ -336,7 +338,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (row_ok) {
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
         const bool full_chunk = (nq + 32 <= p.N) && vec_ok;
         if (add_bias) {
 #pragma unroll
@@ -499,6 +501,7 @@ void gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
   p.ld_aux = g.ld_aux;
   p.aux_batch_stride = g.aux_batch_stride;
   p.alpha = g.alpha;
+  p.alpha_dev = g.alpha_dev;
   p.epi_mode = g.epi_mode;
   p.out_fp32 = g.out_fp32;
   p.accumulate = g.accumulate;

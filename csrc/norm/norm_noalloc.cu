@@ -2,6 +2,7 @@
 // device array instead of caller- or allocator-provided memory.
 #include "norm_noalloc.h"
 
+#include <atomic>
 #include <string>
 
 #include "../api.h"
@@ -14,8 +15,12 @@ static __device__ __align__(256) float g_norm_scratch[RT_NORM_NOALLOC_SCRATCH_FL
 
 // Device address of g_norm_scratch per device.  In host code the name g_norm_scratch is only a
 // handle for the runtime, not a device pointer, so it must be translated once per device.
-float* g_scratch_addr[64] = {nullptr};
-int g_sm_count[64] = {0};
+// Two host threads may make the first call on one device at the same time: both resolve the same
+// values, the SM count is stored first and the address last with release order, and readers load
+// the address with acquire order, so whoever sees a non-null address also sees the SM count.
+constexpr int kMaxDevices = 64;
+std::atomic<float*> g_scratch_addr[kMaxDevices];
+std::atomic<int> g_sm_count[kMaxDevices];
 thread_local std::string g_last_error;
 
 int fail_with(int code, const std::string& msg) {
@@ -43,9 +48,13 @@ extern "C" int rt_norm_bwd_noalloc(const void* dy, const void* x, const void* ga
 
   int device = 0;
   cudaError_t e = cudaGetDevice(&device);
-  if (e != cudaSuccess || device < 0 || device >= 64)
+  if (e != cudaSuccess)
     return fail_with(RT_NOALLOC_ERR_CUDA, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
-  if (g_scratch_addr[device] == nullptr) {
+  if (device < 0 || device >= kMaxDevices)
+    return fail_with(RT_NOALLOC_ERR_ARG, "rt_norm_bwd_noalloc: device index " + std::to_string(device) +
+                                             " is outside the supported range [0, " + std::to_string(kMaxDevices) + ")");
+  float* scratch = g_scratch_addr[device].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
     // One-time set-up for this device (current right now): translate the symbol to its address.
     float* ptr = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_norm_scratch);
@@ -57,8 +66,9 @@ extern "C" int rt_norm_bwd_noalloc(const void* dy, const void* x, const void* ga
     if (e != cudaSuccess || sms <= 0)
       return fail_with(RT_NOALLOC_ERR_CUDA,
                        std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e));
-    g_sm_count[device] = sms;
-    g_scratch_addr[device] = ptr;
+    g_sm_count[device].store(sms, std::memory_order_relaxed);
+    g_scratch_addr[device].store(ptr, std::memory_order_release);
+    scratch = ptr;
   }
 
   rt::NormArgs a{};
@@ -76,8 +86,8 @@ extern "C" int rt_norm_bwd_noalloc(const void* dy, const void* x, const void* ga
   a.rms = rms != 0;
   // as many partial-sum rows as the normal path would use, capped by the fixed array
   const int fit = RT_NORM_NOALLOC_SCRATCH_FLOATS / (2 * C);
-  a.n_partial = std::min(rt::norm_bwd_num_partials(rows, g_sm_count[device]), fit);
-  a.partial = g_scratch_addr[device];
+  a.n_partial = std::min(rt::norm_bwd_num_partials(rows, g_sm_count[device].load(std::memory_order_relaxed)), fit);
+  a.partial = scratch;
   try {
     rt::norm_bwd(a, static_cast<cudaStream_t>(stream));
   } catch (const std::exception& ex) {

@@ -20,7 +20,9 @@
 //    library keeps it until the process exits.
 //  * the first call on a device looks up the device address of the array (one
 //    cudaGetSymbolAddress, no allocation).  Make that first call before starting any stream
-//    capture on that device.
+//    capture on that device.  The per-device cache of that address is published with
+//    release / acquire atomics, so host threads may make their first calls concurrently.
+//  * devices with an index of 64 or more are rejected with RT_NOALLOC_ERR_ARG.
 //  * all calls on a device share the one array.  It keeps whatever the previous call left in
 //    it; nothing in it needs to start at zero because the first kernel overwrites every
 //    partial-sum row the second kernel reads.  Two calls whose kernels overlap on the GPU
@@ -37,7 +39,7 @@ extern "C" {
 
 #define RT_NOALLOC_OK 0
 #define RT_NOALLOC_ERR_SIZE (-1)    /* C above the maximum, not a multiple of 8, or rows < 0 */
-#define RT_NOALLOC_ERR_ARG (-2)     /* a required pointer is null */
+#define RT_NOALLOC_ERR_ARG (-2)     /* a required pointer is null, or the device index is 64 or more */
 #define RT_NOALLOC_ERR_CUDA (-3)    /* a CUDA call failed; see rt_noalloc_last_error() */
 
 // dy, x, dres (optional), dx: bf16 [rows][C]; gamma: bf16 [C]; mean (LayerNorm only), rstd:

@@ -67,7 +67,8 @@ def launch_count() -> int:
 
 
 def check_status(device: int | None = None) -> None:
-    """Synchronise and raise if any kernel reported a bounded-wait timeout or a bounds error."""
+    """Synchronise and raise if any kernel reported a bounded-wait timeout (:class:`rustorch_b200.error.KernelTimeout`)
+    or a bounds error.  Reading the status clears it, so the device stays usable afterwards."""
     m = load(required=False)
     if m is None or not torch.cuda.is_available():
         return
@@ -77,7 +78,8 @@ def check_status(device: int | None = None) -> None:
         names = {101: "TMA producer wait timed out", 102: "MMA issuer wait timed out",
                  103: "epilogue wait timed out", 104: "peer wait timed out",
                  105: "softmax wait timed out", 201: "index or alignment check failed"}
-        raise RuntimeError(f"rustorch_b200 kernel status {code}: {names.get(code, 'unknown')}")
+        from .error import check_status_to_error
+        raise check_status_to_error(code, f"rustorch_b200 kernel status {code}: {names.get(code, 'unknown')}")
 
 
 _HOST_SO = _HERE / f"_host{sysconfig.get_config_var('EXT_SUFFIX') or '.so'}"

@@ -61,7 +61,7 @@ class CliArgs:
 
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="rustorch-cli", description="Interactive CLI for local LLM inference")
-    p.add_argument("-m", "--model", help="path to a model file (GGUF, safetensors, .pt)")
+    p.add_argument("-m", "--model", help="path to a model file (GGUF, safetensors, MLX, .pt)")
     p.add_argument("-b", "--backend", default="cpu", choices=[b.value for b in Backend])
     p.add_argument("-c", "--config", help="TOML configuration file")
     p.add_argument("--log-level", default="info", choices=["trace", "debug", "info", "warn", "error"])

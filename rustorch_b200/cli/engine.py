@@ -78,7 +78,7 @@ class ModelLoader:
             if isinstance(tok, ByteTokenizer):
                 tok = ByteTokenizer(rt.cfg.vocab_size)
             return rt, tok, meta
-        if fmt in ("safetensors", "rustorch", "torch", "pth", "huggingface", "json"):
+        if fmt in ("safetensors", "mlx", "rustorch", "torch", "pth", "huggingface", "json"):
             from ..models.gpt import GPT, GPTConfig
             from ..models.high_level import load_state_dict_file
             sd = load_state_dict_file(path)

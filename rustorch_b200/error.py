@@ -93,7 +93,7 @@ DeviceError = _variant("DeviceError")
 DeviceNotAvailable = _variant("DeviceNotAvailable", DeviceError)
 GpuError = _variant("GpuError", DeviceError)
 CudaError = _variant("CudaError", GpuError)
-KernelError = _variant("KernelError", GpuError)
+KernelError = type("KernelError", (GpuError, RuntimeError), {"kind": "KernelError"})   # also a RuntimeError: raised by status checks
 KernelTimeout = _variant("KernelTimeout", KernelError)
 OutOfMemory = _variant("OutOfMemory", DeviceError)
 MemoryError_ = _variant("MemoryError")

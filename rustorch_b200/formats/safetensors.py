@@ -182,7 +182,7 @@ def load_huggingface(directory: str, device: str = "cpu") -> Tuple[Dict[str, tor
 
 
 def detect_format(path: str) -> str:
-    """``rustorch | gguf | safetensors | pth | torch | json | onnx | unknown`` from magic bytes / extension."""
+    """``rustorch | gguf | safetensors | mlx | pth | torch | json | onnx | unknown`` from magic bytes / extension."""
     if os.path.isdir(path):
         return "huggingface" if os.path.exists(os.path.join(path, "config.json")) else "unknown"
     with open(path, "rb") as f:
@@ -196,6 +196,8 @@ def detect_format(path: str) -> str:
     if head[:2] == b"PK" or head[:1] == b"\x80":
         return "torch"
     ext = os.path.splitext(path)[1].lower()
+    if ext == ".mlx":
+        return "mlx"
     if ext == ".safetensors":
         return "safetensors"
     if ext == ".json":

@@ -290,6 +290,9 @@ def load_state_dict_file(path: str) -> Dict[str, torch.Tensor]:
         return {**params, **buffers}
     if kind == "safetensors":
         return st.load_safetensors(path)
+    if kind == "mlx":
+        from ..formats.mlx import MLXLoader
+        return MLXLoader.load(path)[0]
     if kind in ("torch", "pth"):
         return st.load_pth(path)
     if kind == "json":

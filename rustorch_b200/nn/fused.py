@@ -23,7 +23,18 @@ import torch
 
 from ..ops import kernels as K
 
-_NUM_SMS = 148
+_sm_count_cache = {}
+
+
+def _num_sms(device=None) -> int:
+    """SM count of ``device`` (the current CUDA device by default), read once per device; 148 where there is no GPU."""
+    if not torch.cuda.is_available():
+        return 148
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    n = _sm_count_cache.get(idx)
+    if n is None:
+        n = _sm_count_cache[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+    return n
 
 # Called at the end of every fused backward with the parameters whose gradients that backward has
 # finished accumulating AND whose values it no longer reads.  The data-parallel wrapper uses it to
@@ -36,25 +47,29 @@ def _notify(*params):
         grad_ready_hook([p for p in params if p is not None])
 
 
-def _split_k_for(tiles: int, k_blocks: int) -> int:
+def _split_k_for(tiles: int, k_blocks: int, device=None) -> int:
     """Split the contraction so that tiles x splits fill ONE wave of the persistent GEMM (measured on the GPT-2 weight
     gradient shapes: 3072 x 768 x 16384 takes 67.6 us with 2 splits = 144 work units, 77.8 us with 8, 84 us with 9; every
     extra split adds a pass of fp32 atomics over the output)."""
-    if tiles >= _NUM_SMS:
+    sms = _num_sms(device)
+    if tiles >= sms:
         return 1
-    return max(1, min(_NUM_SMS // max(tiles, 1), max(1, k_blocks // 8)))
+    return max(1, min(sms // max(tiles, 1), max(1, k_blocks // 8)))
 
 
-def wgrad_into(dy2d: torch.Tensor, x2d: torch.Tensor, param: torch.Tensor):
-    """dW[out,in] (+)= dy2d^T @ x2d.  Returns None if accumulated into ``param.main_grad``."""
+def wgrad_into(dy2d: torch.Tensor, x2d: torch.Tensor, param: torch.Tensor, alpha_dev: Optional[torch.Tensor] = None):
+    """dW[out,in] (+)= dy2d^T @ x2d (times the device scalar ``alpha_dev`` when given).  Returns None if
+    accumulated into ``param.main_grad``."""
     n_out, n_in = dy2d.shape[1], x2d.shape[1]
     tiles = -(-n_out // 128) * -(-n_in // 256)
-    sk = _split_k_for(tiles, -(-dy2d.shape[0] // 64))
+    sk = _split_k_for(tiles, -(-dy2d.shape[0] // 64), dy2d.device)
     mg = getattr(param, "main_grad", None)
     if mg is not None:
-        K.gemm(dy2d, x2d, a_mn=True, b_mn=True, out=mg.view(n_out, n_in), accumulate=True, split_k=sk)
+        K.gemm(dy2d, x2d, a_mn=True, b_mn=True, out=mg.view(n_out, n_in), accumulate=True, split_k=sk,
+               alpha_dev=alpha_dev)
         return None
-    g = K.gemm(dy2d, x2d, a_mn=True, b_mn=True, out_dtype=torch.float32, accumulate=True, split_k=sk)
+    g = K.gemm(dy2d, x2d, a_mn=True, b_mn=True, out_dtype=torch.float32, accumulate=True, split_k=sk,
+               alpha_dev=alpha_dev)
     return g.to(param.dtype)
 
 
@@ -191,13 +206,16 @@ class EmbeddingFn(torch.autograd.Function):
 
 
 class LMHeadLossFn(torch.autograd.Function):
-    """loss = mean CE(lm_head(norm(x)), targets); logits stay bf16 and become their own gradient.
+    """loss = mean over the non-ignored rows of CE(lm_head(norm(x)), targets); logits stay bf16 and become their
+    own (unscaled) gradient ``softmax - onehot`` in the forward pass.
 
     ``w_head`` is ``[vocab_padded, C]`` (rows >= ``vocab`` are padding that receives zero
-    gradient); padding keeps logits rows 16-byte aligned for vector access.
+    gradient); padding keeps logits rows 16-byte aligned for vector access.  The factor
+    ``dloss / n_valid`` (upstream gradient over the number of rows that are not ``ignore_index``, the
+    normalisation of ``F.cross_entropy``) never visits the host: it is a one-element device tensor that
+    the weight- and input-gradient GEMMs multiply into their epilogues, so ``(2 * loss).backward()``
+    and a loss scaler give exact gradients.
     """
-
-    assume_unit_grad = True
 
     @staticmethod
     def forward(ctx, x, ln_w, ln_b, w_head, targets, vocab: int, eps: float, ignore_index: int):
@@ -206,25 +224,20 @@ class LMHeadLossFn(torch.autograd.Function):
         h, mean, rstd = K.layer_norm_fwd(x2, ln_w, ln_b, eps)
         logits = K.gemm(h, w_head)                                # [B*T, Vp]
         tgt = targets.reshape(-1)
-        # Mean over all rows; rows equal to ignore_index contribute zero loss and gradient.
-        n_valid = B * T
-        losses = K.cross_entropy_(logits, tgt, vocab, 1.0 / n_valid, ignore_index)
-        loss = K.reduce_all(losses, "sum")[0] / n_valid
-        ctx.save_for_backward(x2, ln_w, ln_b, w_head, mean, rstd, h, logits)
+        losses = K.cross_entropy_(logits, tgt, vocab, 1.0, ignore_index)   # rows == ignore_index: zero loss, zero gradient
+        inv_valid = (tgt != ignore_index).sum().clamp_(min=1).to(torch.float32).reciprocal_().view(1)
+        loss = K.reduce_all(losses, "sum")[0] * inv_valid[0]
+        ctx.save_for_backward(x2, ln_w, ln_b, w_head, mean, rstd, h, logits, inv_valid)
         ctx.meta = (B, T, C)
         return loss
 
     @staticmethod
     def backward(ctx, dloss):
-        x2, ln_w, ln_b, w_head, mean, rstd, h, dlogits = ctx.saved_tensors
+        x2, ln_w, ln_b, w_head, mean, rstd, h, dlogits, inv_valid = ctx.saved_tensors
         B, T, C = ctx.meta
-        # dlogits already carries the 1/N of the mean.  Reading the upstream factor would cost a
-        # device sync, so plain loss.backward() (factor 1) is assumed unless the class flag is
-        # cleared, e.g. when a loss scaler multiplies the loss.
-        if not LMHeadLossFn.assume_unit_grad:
-            dlogits = dlogits * dloss.to(dlogits.dtype)
-        g_head = wgrad_into(dlogits, h, w_head)
-        dh = K.gemm(dlogits, w_head, b_mn=True)
+        factor = (inv_valid * dloss.to(torch.float32)).view(1)    # device scalar, folded into both GEMM epilogues
+        g_head = wgrad_into(dlogits, h, w_head, alpha_dev=factor)
+        dh = K.gemm(dlogits, w_head, b_mn=True, alpha_dev=factor)
         wg, bg, direct = _norm_grad_bufs(ln_w, ln_b)
         dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg)
         g_lnw = None if direct else wg.to(ln_w.dtype)

@@ -180,7 +180,8 @@ class Im2colConv2dFn(torch.autograd.Function):
         dw = db = None
         if ctx.needs_input_grad[1]:
             dwf = torch.zeros(Cout, col.shape[1], dtype=torch.float32, device=dy.device)
-            K.gemm(dy2, col, a_mn=True, b_mn=True, out=dwf, accumulate=True, split_k=148)
+            K.gemm(dy2, col, a_mn=True, b_mn=True, out=dwf, accumulate=True,
+                   split_k=torch.cuda.get_device_properties(dy2.device).multi_processor_count)
             dw = dwf[:, :k_real].reshape(Cout, KH, KW, Cin).to(torch.bfloat16).permute(0, 3, 1, 2)
         if has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(torch.bfloat16)

@@ -25,18 +25,19 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
          bias: Optional[torch.Tensor] = None, aux: Optional[torch.Tensor] = None,
          epilogue: int = EPI_NONE, alpha: float = 1.0, accumulate: bool = False,
-         split_k: int = 1, block_n: int = 0) -> torch.Tensor:
+         split_k: int = 1, block_n: int = 0, alpha_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out[b,m,n] = alpha * sum_k A[b,m,k] B[b,n,k]`` (+ epilogue) on tcgen05.
 
     ``a`` is ``[.., M, K]`` (``a_mn=False``) or ``[.., K, M]`` (``a_mn=True``); ``b`` is
-    ``[.., N, K]`` or ``[.., K, N]`` likewise.  Rank 2 or 3; last dim contiguous.
+    ``[.., N, K]`` or ``[.., K, N]`` likewise.  Rank 2 or 3; last dim contiguous.  ``alpha_dev`` is an optional
+    one-element fp32 CUDA tensor multiplied into ``alpha`` on the device (no host read).
     """
     M = a.shape[-1] if a_mn else a.shape[-2]
     N = b.shape[-1] if b_mn else b.shape[-2]
     if out is None:
         shape = (*a.shape[:-2], M, N)
         out = (torch.zeros if accumulate else torch.empty)(shape, dtype=out_dtype, device=a.device)
-    _C().gemm(a, a_mn, b, b_mn, out, bias, aux, epilogue, float(alpha), accumulate, split_k, block_n)
+    _C().gemm(a, a_mn, b, b_mn, out, bias, aux, epilogue, float(alpha), accumulate, split_k, block_n, alpha_dev)
     return out
 
 

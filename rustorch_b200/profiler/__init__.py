@@ -31,6 +31,58 @@ class ProfilerConfig:
     sampling_rate_hz: float = 10.0
     export_chrome_trace: bool = False
     export_json: bool = False
+    enable_nvtx: bool = True          # every profiled scope is also an NVTX range (visible in Nsight timelines)
+
+
+class _Nvtx:
+    """NVTX range push / pop through ``torch.cuda.nvtx`` (a few nanoseconds when no profiler is attached).  ``depth``
+    counts the ranges this process has open; where the NVTX library cannot be reached the calls only keep the count."""
+
+    def __init__(self):
+        self.depth = 0
+        self.pushed = 0
+        try:
+            from torch.cuda import nvtx as _n
+            self._n = _n
+        except Exception:  # noqa: BLE001
+            self._n = None
+
+    def push(self, name: str) -> None:
+        self.depth += 1
+        self.pushed += 1
+        if self._n is not None:
+            try:
+                self._n.range_push(name)
+            except Exception:  # noqa: BLE001  (no NVTX library on this machine)
+                self._n = None
+
+    def pop(self) -> None:
+        self.depth = max(0, self.depth - 1)
+        if self._n is not None:
+            try:
+                self._n.range_pop()
+            except Exception:  # noqa: BLE001
+                self._n = None
+
+    def mark(self, name: str) -> None:
+        if self._n is not None:
+            try:
+                self._n.mark(name)
+            except Exception:  # noqa: BLE001
+                self._n = None
+
+
+nvtx = _Nvtx()
+
+
+@contextlib.contextmanager
+def nvtx_range(name: str):
+    """``with nvtx_range("attn_fwd"): ...`` marks the enclosed host span (and the kernels launched in it) for Nsight."""
+    nvtx.push(name)
+    try:
+        yield
+    finally:
+        nvtx.pop()
 
 
 @dataclass
@@ -267,6 +319,9 @@ class Profiler:
             return
         depth = getattr(self._depth, "v", 0)
         self._depth.v = depth + 1
+        use_nvtx = self.config.enable_nvtx
+        if use_nvtx:
+            nvtx.push(f"{category}:{name}")
         use_gpu = self.config.enable_gpu and torch.cuda.is_available()
         if use_gpu:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -281,6 +336,8 @@ class Profiler:
                 e1.record()
                 e1.synchronize()
                 dev = e0.elapsed_time(e1)
+            if use_nvtx:
+                nvtx.pop()
             self._depth.v = depth
             self.timeline.add(ProfileEvent(name, category, (t0 - self._t0) * 1e6, dt * 1e6, depth, threading.get_ident() % 100000, dev, args))
 

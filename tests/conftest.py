@@ -35,3 +35,21 @@ def _kernel_status_guard(request):
 def rel_err(out: torch.Tensor, ref: torch.Tensor) -> float:
     out, ref = out.float(), ref.float()
     return float((out - ref).abs().max() / ref.abs().max().clamp_min(1e-6))
+
+
+def assert_close(out: torch.Tensor, ref: torch.Tensor, rtol: float = 2e-2, atol_frac: float = 4e-3, what: str = "") -> None:
+    """Per-element check ``|out - ref| <= atol + rtol * |ref|`` with ``atol = atol_frac * max|ref|``.
+
+    Unlike a max-error-over-max-value ratio this fails on a wrong tile of small-magnitude outputs or a wrong ragged
+    tail: the absolute allowance is a few bf16 ulps of the largest value, everything above it must agree relatively.
+    """
+    out, ref = out.float(), ref.float()
+    assert out.shape == ref.shape, f"{what}: shape {tuple(out.shape)} vs {tuple(ref.shape)}"
+    atol = atol_frac * float(ref.abs().max().clamp_min(1e-12))
+    bad = (out - ref).abs() > (atol + rtol * ref.abs())
+    n_bad = int(bad.sum())
+    if n_bad:
+        idx = bad.nonzero()[0].tolist()
+        raise AssertionError(
+            f"{what}: {n_bad} of {out.numel()} elements differ; first at {idx}: got {float(out[tuple(idx)])}, "
+            f"want {float(ref[tuple(idx)])} (atol {atol:.3e}, rtol {rtol})")

@@ -23,21 +23,22 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     from rustorch_b200 import _native
     from rustorch_b200.models.gpt import GPT, GPTConfig
-    from rustorch_b200.optim.flat import FlatParams, FusedAdamW
-    from rustorch_b200.distributed.fused_allreduce import FusedDDPAdamW
+    from rustorch_b200.optim.flat import FlatParams, FusedAdamW, FusedSGD
+    from rustorch_b200.distributed.fused_allreduce import FusedDDPAdamW, FusedDDPSGD
     from rustorch_b200.distributed.ddp_flat import FlatDDP
 
     cfg = GPTConfig(vocab_size=512, n_positions=128, n_embd=256, n_layer=2, n_head=4, dropout=0.0)
     steps, B, T = 6, 4, 128
     gen = torch.Generator().manual_seed(7)
     data = torch.randint(0, cfg.vocab_size, (steps, world, B, T + 1), generator=gen).to(dev)
-    hp = dict(lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    sgd = mode.endswith("_sgd")
+    hp = dict(lr=0.05, momentum=0.9, weight_decay=1e-4) if sgd else dict(lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
 
     # --- single-GPU big-batch replay (oracle)
     ref = GPT(cfg, device=dev, dtype=torch.bfloat16, seed=3)
     rflat = FlatParams(ref)
     init = rflat.master.clone()
-    ropt = FusedAdamW(rflat, **hp)
+    ropt = FusedSGD(rflat, **hp) if sgd else FusedAdamW(rflat, **hp)
     ropt.grad_scale = 1.0 / world
     ref_losses = []
     for s in range(steps):
@@ -54,8 +55,12 @@ def main():
     # --- data-parallel run
     model = GPT(cfg, device=dev, dtype=torch.bfloat16, seed=3)
     losses = []
-    if mode == "fused":
-        ddp = FusedDDPAdamW(model, bucket_cap_mb=1.0, timeout_s=20.0, **hp)
+    nvls_used = False
+    if mode.startswith("fused"):
+        # "fused" / "fused_sgd": plain peer loads and stores; "fused_nvls" / "fused_nvls_sgd": multimem through the switch
+        kw = dict(bucket_cap_mb=1.0, timeout_s=10.0, use_nvls="nvls" in mode, **hp)
+        ddp = FusedDDPSGD(model, **kw) if sgd else FusedDDPAdamW(model, **kw)
+        nvls_used = ddp.nvls
         for s in range(steps):
             b = data[s, rank]
             loss = model(b[:, :-1], b[:, 1:])
@@ -95,7 +100,7 @@ def main():
         worst = max(worst, float(diff / upd))
     out = {"rank": rank, "world": world, "mode": mode, "n_buckets": n_buckets,
            "loss_ddp": [round(float(x), 4) for x in lt], "loss_ref": [round(x, 4) for x in ref_losses],
-           "worst_rel_update_diff": round(worst, 4)}
+           "worst_rel_update_diff": round(worst, 4), "nvls": nvls_used}
     # one file per rank: lines printed by several ranks to a shared pipe can interleave
     with open(os.path.join(os.environ["DDP_RESULT_DIR"], f"rank{rank}.json"), "w") as f:
         json.dump(out, f)

@@ -253,3 +253,27 @@ def test_discrete_distributions_and_validation():
     loc = torch.tensor(0.0, requires_grad=True)
     D.Normal(loc, 1.0).rsample((8,)).sum().backward()
     assert loc.grad.item() == 8
+
+
+def test_profiler_scopes_are_nvtx_ranges():
+    """Every profiled scope pushes / pops one NVTX range (balanced, also when the body raises); ``nvtx_range`` is the
+    stand-alone form."""
+    from rustorch_b200 import profiler as P
+    prof = P.Profiler(P.ProfilerConfig(enable_gpu=False))
+    prof.enable()
+    before = P.nvtx.pushed
+    with prof.profile("outer"):
+        assert P.nvtx.depth == 1
+        with prof.profile("inner", category="kernel"):
+            assert P.nvtx.depth == 2
+    assert P.nvtx.depth == 0 and P.nvtx.pushed == before + 2
+    with pytest.raises(ValueError):
+        with P.nvtx_range("boom"):
+            raise ValueError("x")
+    assert P.nvtx.depth == 0
+    quiet = P.Profiler(P.ProfilerConfig(enable_gpu=False, enable_nvtx=False))
+    quiet.enable()
+    n = P.nvtx.pushed
+    with quiet.profile("silent"):
+        pass
+    assert P.nvtx.pushed == n

@@ -21,7 +21,9 @@ def _free_port():
 
 def _run(mode, nproc):
     out_dir = tempfile.mkdtemp(prefix="ddp_res_")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", DDP_RESULT_DIR=out_dir)
+    env = dict(os.environ, DDP_RESULT_DIR=out_dir)
+    if "nvls" not in mode:
+        env["NCCL_NVLS_ENABLE"] = "0"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(ROOT, "tests", "ddp_worker.py"), mode]
@@ -31,11 +33,16 @@ def _run(mode, nproc):
     return res
 
 
-@pytest.mark.parametrize("mode", ["fused", "nccl"])
+@pytest.mark.parametrize("mode", ["fused", "fused_nvls", "fused_sgd", "fused_nvls_sgd", "nccl"])
 def test_ddp_matches_big_batch(mode):
+    """Every variant of the fused bucket step (peer loads or switch-side multimem reduction; AdamW or SGD with
+    momentum) follows the single-GPU big-batch run.  SGD is linear in the gradient, so its parameters must agree to
+    fp32 summation order; Adam's early steps divide by tiny second moments, which amplifies that order."""
     nproc = min(torch.cuda.device_count(), 4)
     for r in _run(mode, nproc):
         for a, b in zip(r["loss_ddp"], r["loss_ref"]):
-            assert abs(a - b) < 3e-2, r
-        assert r["worst_rel_update_diff"] < 0.15, r
+            assert abs(a - b) < 2e-2, r
+        assert r["worst_rel_update_diff"] < (0.02 if mode.endswith("_sgd") else 0.1), r
         assert r["loss_ddp"][-1] < r["loss_ddp"][0]
+        if "nvls" in mode:
+            assert r["nvls"], "the symmetric allocation has no multicast mapping on this machine"

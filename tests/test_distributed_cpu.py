@@ -46,6 +46,16 @@ def test_ddp_matches_single_process_big_batch():
         assert r["max_diff"] < 1e-5 and r["n_buckets"] > 1
 
 
+@pytest.mark.parametrize("kind", ["adamw", "sgd"])
+def test_fused_ddp_state_dict_resumes_next_step(kind):
+    """The gathered state dict of the fused data-parallel optimizer (host emulation over gloo) restores master
+    weights, moments and step count so that the next step is reproduced exactly."""
+    for r in _spawn("fused_ddp_resume", extra=(kind,)):
+        assert r["n_buckets"] > 1 and r["step"] == 4
+        assert r["local_m_is_partial"]
+        assert r["lp_restored"] == 0.0 and r["resume_diff"] < 1e-7, r
+
+
 def test_tensor_parallel_layers_match_unsharded():
     for r in _spawn("tp"):
         assert r["fwd"] < 1e-5 and r["bwd"] < 1e-5 and r["gathered"] == [3, 16]

@@ -163,3 +163,49 @@ def test_gguf_write_read_roundtrip(tmp_path):
         cfg = g.model_config()
         assert cfg["n_layer"] == 2 and cfg["n_head_kv"] == 4 and cfg["vocab_size"] == 3
     assert F.detect_format(p) == "gguf"
+
+
+def test_mlx_loader_roundtrip_metadata_and_errors(tmp_path):
+    """MLX weight files (example-cli/src/model/formats/mlx.rs:12-144): 8-byte header length, JSON header, raw data."""
+    import json
+    import struct
+    from rustorch_b200.error import ModelFormatError
+    from rustorch_b200.formats import detect_format
+    from rustorch_b200.formats.mlx import MLXLoader, extract_metadata, parse_tensor, save_mlx
+    # the reference's own unit vectors: [1.0, 2.0, 3.0] as little-endian f32, and Llama-7B defaults for empty metadata
+    t = parse_tensor(bytes([0, 0, 128, 63, 0, 0, 0, 64, 0, 0, 64, 64]), [3], "F32")
+    assert t.tolist() == [1.0, 2.0, 3.0]
+    md = extract_metadata({})
+    assert (md.vocab_size, md.hidden_size, md.num_layers, md.num_heads, md.context_length) == (32000, 4096, 32, 32, 2048)
+    tensors = {"a.weight": torch.randn(3, 5), "b": torch.arange(6, dtype=torch.int64).reshape(2, 3),
+               "h": torch.randn(4).half(), "i": torch.tensor([1, -2], dtype=torch.int32), "bf": torch.randn(2, 2).bfloat16()}
+    path = str(tmp_path / "model.mlx")
+    save_mlx(path, tensors, {"vocab_size": 1234, "hidden_size": "64", "num_hidden_layers": 2})
+    assert detect_format(path) == "mlx"
+    got, md = MLXLoader.load(path)
+    assert set(got) == set(tensors)
+    for k, v in tensors.items():
+        assert got[k].dtype == v.dtype and torch.equal(got[k], v), k
+    assert (md.vocab_size, md.hidden_size, md.num_layers, md.num_heads, md.format) == (1234, 64, 2, 32, "mlx")
+    # hand-built file with the long dtype spelling the reference accepts
+    hdr = json.dumps({"w": {"dtype": "float32", "shape": [2], "data_offsets": [0, 8]}}).encode()
+    p2 = str(tmp_path / "hand.mlx")
+    with open(p2, "wb") as f:
+        f.write(struct.pack("<Q", len(hdr)) + hdr + struct.pack("<2f", 0.5, -1.5))
+    assert MLXLoader.load(p2)[0]["w"].tolist() == [0.5, -1.5]
+    # corrupt: header longer than the file; unknown dtype; offsets outside the data
+    p3 = str(tmp_path / "bad.mlx")
+    with open(p3, "wb") as f:
+        f.write(struct.pack("<Q", 1 << 20) + b"{}")
+    with pytest.raises(ModelFormatError):
+        MLXLoader.load(p3)
+    with pytest.raises(ModelFormatError):
+        parse_tensor(b"\0" * 4, [1], "C64")
+    hdr = json.dumps({"w": {"dtype": "F32", "shape": [4], "data_offsets": [0, 16]}}).encode()
+    with open(p3, "wb") as f:
+        f.write(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 8)
+    with pytest.raises(ModelFormatError):
+        MLXLoader.load(p3)
+    # the generic state-dict reader goes through the same loader
+    from rustorch_b200.models.high_level import load_state_dict_file
+    assert torch.equal(load_state_dict_file(path)["a.weight"], tensors["a.weight"])

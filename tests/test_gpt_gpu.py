@@ -59,3 +59,47 @@ def test_gpt_inference_logits():
         r = ref(idx)
     assert out.shape == r.shape
     assert rel_err(out, r) < 5e-2
+
+
+def _grads_of(m, flat, idx, tgt, loss_fn):
+    flat.grad.zero_()
+    loss = m(idx, tgt)
+    loss_fn(loss).backward()
+    return float(loss), {k: v.clone() for k, v in flat.named_views(flat.grad).items()}
+
+
+def test_lm_head_loss_applies_upstream_gradient():
+    """(2 * loss).backward() doubles every gradient: the fused loss reads the upstream factor on the device."""
+    from rustorch_b200.optim.flat import FlatParams
+    cfg, m, ref = _models()
+    flat = FlatParams(m)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    idx = torch.randint(0, cfg.vocab_size, (2, 256), device="cuda", generator=g)
+    tgt = torch.randint(0, cfg.vocab_size, (2, 256), device="cuda", generator=g)
+    (ref(idx, tgt) * 2.0).backward()
+    refg = dict(ref.named_parameters())
+    _, g2 = _grads_of(m, flat, idx, tgt, lambda l: l * 2.0)
+    for name in ["lm_head", "lnf_w", "blocks.1.w_fc2", "blocks.0.w_qkv", "wte"]:
+        assert rel_err(g2[name], refg[name].grad) < 6e-2, name
+    # a loss scaler: scale by 65536, unscale the gradients, compare with the unscaled oracle
+    _, gs = _grads_of(m, flat, idx, tgt, lambda l: l * 65536.0)
+    for name in ["lm_head", "blocks.0.w_qkv"]:
+        assert rel_err(gs[name] / 65536.0, refg[name].grad / 2.0) < 6e-2, name
+
+
+def test_lm_head_loss_ignore_index_matches_reference_mean():
+    """Rows equal to ignore_index are left out of the mean, as in F.cross_entropy."""
+    from rustorch_b200.optim.flat import FlatParams
+    cfg, m, ref = _models()
+    flat = FlatParams(m)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    idx = torch.randint(0, cfg.vocab_size, (2, 256), device="cuda", generator=g)
+    tgt = torch.randint(0, cfg.vocab_size, (2, 256), device="cuda", generator=g)
+    tgt[:, 100:] = -100                       # 61 % of the rows are padding
+    rloss = ref(idx, tgt)
+    rloss.backward()
+    refg = dict(ref.named_parameters())
+    loss, grads = _grads_of(m, flat, idx, tgt, lambda l: l)
+    assert abs(loss - float(rloss)) / float(rloss) < 1e-2
+    for name in ["lm_head", "lnf_w", "blocks.0.w_qkv"]:
+        assert rel_err(grads[name], refg[name].grad) < 6e-2, name

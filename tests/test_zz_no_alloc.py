@@ -70,6 +70,19 @@ def test_noalloc_matches_tensor_path_twice(rms):
         assert rel_err(dg, dg_ref) < 1e-3
         if not rms:
             assert rel_err(db, db_ref) < 1e-3
+        # independent oracle: the same backward in fp32 torch math on the same bf16 inputs
+        xf = x.float().requires_grad_(True)
+        wf = w.float().requires_grad_(True)
+        bf = b.float().requires_grad_(True)
+        if rms:
+            yf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+        else:
+            yf = torch.nn.functional.layer_norm(xf, (C,), wf, bf, 1e-5)
+        yf.backward(dy.float())
+        assert rel_err(dx, xf.grad + dres.float()) < 2e-2
+        assert rel_err(dg, wf.grad) < 2e-2
+        if not rms:
+            assert rel_err(db, bf.grad) < 2e-2
 
 
 def test_noalloc_rejects_oversize():
