@@ -164,6 +164,30 @@ struct OptimArgs {
 };
 void fused_optim_step(const OptimArgs& a, cudaStream_t stream);
 
+// ------------------------------------------------------- optim/multi_tensor_optim.cu
+enum MultiTensorMode : int {
+  MT_ADAM = 0, MT_ADAMW, MT_SGD, MT_NADAM, MT_RADAM, MT_ADAMAX, MT_RMSPROP, MT_ADAGRAD, MT_ADABOUND, MT_LAMB_STAGE1, MT_LAMB_STAGE2
+};
+constexpr int MT_MAX_TENSORS = 32;
+struct MultiTensorArgs {
+  void* param[MT_MAX_TENSORS];        // fp32 or bf16 (param_bf16)
+  const void* grad[MT_MAX_TENSORS];   // fp32 or bf16 (grad_bf16)
+  float* state0[MT_MAX_TENSORS];      // first moment / momentum buffer, or null
+  float* state1[MT_MAX_TENSORS];      // second moment / infinity norm / square average / sum of squares, or null
+  float* state2[MT_MAX_TENSORS];      // centered RMSprop: gradient average, else null
+  long long numel[MT_MAX_TENSORS];
+  int chunk_start[MT_MAX_TENSORS + 1];  // filled by the launcher
+  int n_tensors;
+  int mode;                           // MultiTensorMode
+  int param_bf16, grad_bf16;
+  int decoupled, maximize;
+  float lr, beta1, beta2, eps, weight_decay, grad_scale;
+  float c0, c1, c2;                   // per-step scalars of the rule (see multi_tensor_optim.cu)
+  float* norms;                       // LAMB: fp32 [2 * total tensors] (|w|^2, |update|^2), zeroed before stage 1
+  int tensor_base;                    // index of param[0] in the norm table
+};
+void multi_tensor_optim_step(MultiTensorArgs& a, cudaStream_t stream);
+
 // ------------------------------------------------------------ collective/ddp_fused.cu
 constexpr int RT_MAX_PEERS = 8;
 struct DdpBucketArgs {

@@ -19,7 +19,12 @@
 #include "../common/launch.h"
 #include "attn_common.cuh"
 
+#include <cstdlib>
+#include <string>
+
 namespace rt {
+
+void attn_fwd_pp(const AttnArgs& a, cudaStream_t stream);  // flash_fwd_pp.cu
 
 struct AttnFwdParams {
   int B, H, Hkv, Tq, Tk;
@@ -345,6 +350,16 @@ void attn_fwd(const AttnArgs& a, cudaStream_t stream) {
   RT_CHECK((a.o_st % 8) == 0 && (a.o_sh % 8) == 0 && (a.o_sb % 8) == 0,
            "attention: output strides must be multiples of 8 elements");
   if (a.B == 0 || a.Tq == 0) return;
+  // Default: the persistent ping-pong kernel (flash_fwd_pp.cu).  RUSTORCH_ATTN_FWD=tile selects the one-CTA-per-query-tile
+  // kernel of this file, which is also used for a non-positive softmax scale.
+  static const bool use_tile_kernel = [] {
+    const char* e = std::getenv("RUSTORCH_ATTN_FWD");
+    return e != nullptr && std::string(e) == "tile";
+  }();
+  if (!use_tile_kernel && a.scale > 0.f) {
+    attn_fwd_pp(a, stream);
+    return;
+  }
   if (a.io_fp16) {
     if (a.D == 64) launch_fwd<64, true>(a, stream);
     else launch_fwd<128, true>(a, stream);

@@ -72,6 +72,62 @@ void ddp_bucket_step(const std::vector<int64_t>& grad_ptrs, const std::vector<in
   rt::ddp_bucket_step(a, int(n_ctas), cur_stream(master.device().index()));
 }
 
+// One rule applied to a list of tensors; lists longer than 32 are cut into several launches.
+void multi_tensor_optim(int64_t mode, const std::vector<Tensor>& params, const std::vector<Tensor>& grads,
+                        const std::vector<c10::optional<Tensor>>& s0, const std::vector<c10::optional<Tensor>>& s1,
+                        const std::vector<c10::optional<Tensor>>& s2, double lr, double beta1, double beta2, double eps,
+                        double weight_decay, double c0, double c1, double c2, double grad_scale, bool decoupled,
+                        bool maximize, const c10::optional<Tensor>& norms, int64_t tensor_base) {
+  const size_t n = params.size();
+  TORCH_CHECK(grads.size() == n && s0.size() == n && s1.size() == n && s2.size() == n, "multi_tensor_optim: list lengths differ");
+  if (n == 0) return;
+  const auto pd = params[0].scalar_type(), gd = grads[0].scalar_type();
+  TORCH_CHECK(pd == at::kFloat || pd == at::kBFloat16, "multi_tensor_optim: parameters must be fp32 or bf16");
+  TORCH_CHECK(gd == at::kFloat || gd == at::kBFloat16, "multi_tensor_optim: gradients must be fp32 or bf16");
+  c10::cuda::CUDAGuard guard(params[0].device());
+  auto state_ptr = [&](const c10::optional<Tensor>& t, const Tensor& p) -> float* {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == p.numel(),
+                "multi_tensor_optim: state tensors must be contiguous fp32 CUDA tensors shaped like their parameter");
+    return t->data_ptr<float>();
+  };
+  float* norm_ptr = nullptr;
+  if (norms.has_value() && norms->defined()) {
+    TORCH_CHECK(norms->is_cuda() && norms->scalar_type() == at::kFloat && norms->is_contiguous() &&
+                    norms->numel() >= 2 * (tensor_base + int64_t(n)), "multi_tensor_optim: norm table too small");
+    norm_ptr = norms->data_ptr<float>();
+  }
+  for (size_t base = 0; base < n; base += rt::MT_MAX_TENSORS) {
+    rt::MultiTensorArgs a{};
+    const size_t cnt = std::min<size_t>(rt::MT_MAX_TENSORS, n - base);
+    for (size_t k = 0; k < cnt; ++k) {
+      const Tensor& p = params[base + k];
+      const Tensor& g = grads[base + k];
+      TORCH_CHECK(p.is_cuda() && g.is_cuda() && p.is_contiguous() && g.is_contiguous() && p.numel() == g.numel() &&
+                      p.scalar_type() == pd && g.scalar_type() == gd && p.device() == params[0].device(),
+                  "multi_tensor_optim: parameters / gradients must be contiguous CUDA tensors of one dtype on one device");
+      a.param[k] = p.data_ptr();
+      a.grad[k] = g.data_ptr();
+      a.state0[k] = state_ptr(s0[base + k], p);
+      a.state1[k] = state_ptr(s1[base + k], p);
+      a.state2[k] = state_ptr(s2[base + k], p);
+      a.numel[k] = p.numel();
+    }
+    a.n_tensors = int(cnt);
+    a.mode = int(mode);
+    a.param_bf16 = pd == at::kBFloat16;
+    a.grad_bf16 = gd == at::kBFloat16;
+    a.decoupled = decoupled ? 1 : 0;
+    a.maximize = maximize ? 1 : 0;
+    a.lr = float(lr); a.beta1 = float(beta1); a.beta2 = float(beta2); a.eps = float(eps);
+    a.weight_decay = float(weight_decay); a.grad_scale = float(grad_scale);
+    a.c0 = float(c0); a.c1 = float(c1); a.c2 = float(c2);
+    a.norms = norm_ptr;
+    a.tensor_base = int(tensor_base + int64_t(base));
+    rt::multi_tensor_optim_step(a, cur_stream(params[0].device().index()));
+  }
+}
+
 void ddp_wait_end(int64_t flags_ptr, int64_t n_slots, int64_t world, int64_t rank, int64_t epoch,
                   double timeout_s, int64_t device) {
   c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
@@ -859,4 +915,6 @@ void register_extra_ops(pybind11::module_& m) {
         "fused reduce-scatter + scale + AdamW / Adam / SGD + all-gather of one gradient bucket over peer memory "
         "(plain peer loads / stores, or NVLS multimem when the multicast pointers are non-zero)");
   m.def("ddp_wait_end", &ddp_wait_end);
+  m.def("multi_tensor_optim", &multi_tensor_optim,
+        "one launch per 32 tensors: Adam / AdamW / SGD / NAdam / RAdam / Adamax / RMSprop / AdaGrad / AdaBound / LAMB update");
 }

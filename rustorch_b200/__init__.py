@@ -23,6 +23,7 @@ _LAZY = {
     # tensors / autograd
     "Tensor": "tensor", "tensor": "tensor", "zeros": "tensor", "ones": "tensor", "Variable": "autograd", "no_grad": "autograd",
     "enable_grad": "autograd", "grad": "autograd", "gradcheck": "autograd", "jacobian": "autograd", "hessian": "autograd",
+    "Complex": "complex",
     # layers and losses
     **{n: "nn" for n in ("Module", "Parameter", "Sequential", "Linear", "Conv1d", "Conv2d", "Conv3d", "ConvTranspose2d", "MaxPool2d",
                          "AvgPool2d", "BatchNorm1d", "BatchNorm2d", "LayerNorm", "RMSNorm", "GroupNorm", "Dropout", "Flatten", "Embedding",
@@ -65,7 +66,7 @@ _LAZY = {
 _SUBMODULES = ("nn", "optim", "data", "training", "models", "distributed", "formats", "llm", "amp", "profiler", "debug", "validation",
                "tensorboard", "visualization", "vision", "distributions", "special", "quantization", "sparse", "memory", "gpu", "execution",
                "model_import", "convert", "model_hub", "jit", "cli", "autograd", "ops", "utils", "parallel", "error", "hybrid_f32",
-               "optimization", "compat", "compat_extra")
+               "optimization", "compat", "compat_extra", "complex")
 
 
 # functional activations and image transforms of the reference's Python module (src/python/nn.rs, src/python/data.rs)

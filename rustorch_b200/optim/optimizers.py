@@ -18,7 +18,31 @@ from torch.optim import Optimizer as _TorchOptimizer
 
 
 class _RefAPI:
-    """Reference accessor names on top of torch's param_groups."""
+    """Reference accessor names on top of torch's param_groups, and the native multi-tensor ``step``."""
+
+    _MT_KIND: Optional[int] = None          # update rule of csrc/optim/multi_tensor_optim.cu, None: no native step
+
+    def step(self, closure=None):           # noqa: D401
+        """One optimizer step.  CUDA parameters are updated by the multi-tensor kernel (one launch per 32 tensors,
+        see :mod:`rustorch_b200.optim.multi_tensor`); anything it does not cover takes the per-tensor path."""
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        if self._MT_KIND is not None:
+            from . import multi_tensor
+            with torch.no_grad():
+                if multi_tensor.try_step(self, self._MT_KIND):
+                    return loss
+        self._fallback_step()
+        return loss
+
+    def _fallback_step(self) -> None:
+        for base in type(self).__mro__:
+            if base.__module__.startswith("torch.optim") and "step" in base.__dict__:
+                base.step(self)
+                return
+        raise NotImplementedError
 
     def learning_rate(self) -> float:
         return float(self.param_groups[0]["lr"])
@@ -98,7 +122,7 @@ def _params(params) -> Iterable:
     return params if params is not None else [torch.nn.Parameter(torch.zeros(0))]
 
 
-class SGD(torch.optim.SGD, _RefAPI):
+class SGD(_RefAPI, torch.optim.SGD):
     """``SGD(params, lr, momentum=0, weight_decay=0, nesterov=False, dampening=0)`` (src/optim/mod.rs:93-137)."""
 
     def __init__(self, params=None, lr: float = 0.01, momentum: float = 0.0, weight_decay: float = 0.0,
@@ -115,7 +139,7 @@ class SGD(torch.optim.SGD, _RefAPI):
             g["dampening"] = d
 
 
-class Adam(torch.optim.Adam, _RefAPI):
+class Adam(_RefAPI, torch.optim.Adam):
     """``Adam(params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0, amsgrad=False)``; L2 decay
     folded into the gradient (src/optim/mod.rs:233-296)."""
 
@@ -129,7 +153,7 @@ class Adam(torch.optim.Adam, _RefAPI):
     with_amsgrad = classmethod(lambda cls, params, lr: cls(params, lr, amsgrad=True))
 
 
-class AdamW(torch.optim.AdamW, _RefAPI):
+class AdamW(_RefAPI, torch.optim.AdamW):
     """``AdamW(params, lr, beta1, beta2, eps, weight_decay, amsgrad)``, defaults (0.9, 0.999, 1e-8, 0.01, False),
     decoupled decay ``p *= 1 - lr*wd`` (src/optim/adamw.rs:39-78,159-163)."""
 
@@ -141,7 +165,7 @@ class AdamW(torch.optim.AdamW, _RefAPI):
     default_params = classmethod(lambda cls, params, lr=1e-3: cls(params, lr))
 
 
-class RMSprop(torch.optim.RMSprop, _RefAPI):
+class RMSprop(_RefAPI, torch.optim.RMSprop):
     """``default_params(lr)``: alpha 0.99, eps 1e-8; momentum / centered variants (src/optim/mod.rs:408-755)."""
 
     def __init__(self, params=None, lr: float = 0.01, alpha: float = 0.99, eps: float = 1e-8,
@@ -152,7 +176,7 @@ class RMSprop(torch.optim.RMSprop, _RefAPI):
     default_params = classmethod(lambda cls, params, lr=0.01: cls(params, lr))
 
 
-class AdaGrad(torch.optim.Adagrad, _RefAPI):
+class AdaGrad(_RefAPI, torch.optim.Adagrad):
     """eps 1e-10, optional initial accumulator value (src/optim/mod.rs:646-648)."""
 
     def __init__(self, params=None, lr: float = 0.01, lr_decay: float = 0.0, weight_decay: float = 0.0,
@@ -166,7 +190,7 @@ class AdaGrad(torch.optim.Adagrad, _RefAPI):
 Adagrad = AdaGrad
 
 
-class NAdam(torch.optim.NAdam, _RefAPI):
+class NAdam(_RefAPI, torch.optim.NAdam):
     """``(lr, beta1, beta2, eps, wd, momentum_decay=0.004, schedule_decay=0.004)`` (src/optim/nadam.rs:28-31,135-156)."""
 
     def __init__(self, params=None, lr: float = 2e-3, betas=(0.9, 0.999), eps: float = 1e-8,
@@ -175,7 +199,7 @@ class NAdam(torch.optim.NAdam, _RefAPI):
                          momentum_decay=momentum_decay if schedule_decay is None else schedule_decay)
 
 
-class RAdam(torch.optim.RAdam, _RefAPI):
+class RAdam(_RefAPI, torch.optim.RAdam):
     """Variance-rectified Adam; rectification applies once rho_t exceeds the threshold (reference 4.0,
     torch 5.0 — torch's is used) (src/optim/radam.rs:25-31,187-205)."""
 
@@ -183,14 +207,14 @@ class RAdam(torch.optim.RAdam, _RefAPI):
         super().__init__(_params(params), lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
 
 
-class Adamax(torch.optim.Adamax, _RefAPI):
+class Adamax(_RefAPI, torch.optim.Adamax):
     """Infinity-norm Adam, eps default 1e-7 (src/optim/common.rs:107-117)."""
 
     def __init__(self, params=None, lr: float = 2e-3, betas=(0.9, 0.999), eps: float = 1e-7, weight_decay: float = 0.0):
         super().__init__(_params(params), lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
 
 
-class AdaBound(_TorchOptimizer, _RefAPI):
+class AdaBound(_RefAPI, _TorchOptimizer):
     """Adam whose per-element step size is clipped into bounds that converge to ``final_lr``
     (``new(lr)`` = final_lr 0.1, betas 0.9/0.999, eps 1e-8, wd 0, gamma 1e-3; src/optim/adabound.rs:35-64)."""
 
@@ -200,8 +224,7 @@ class AdaBound(_TorchOptimizer, _RefAPI):
                                                weight_decay=weight_decay, gamma=gamma, base_lr=lr))
 
     @torch.no_grad()
-    def step(self, closure=None):
-        loss = closure() if closure is not None else None
+    def _fallback_step(self) -> None:
         for g in self.param_groups:
             b1, b2 = g["betas"]
             for p in g["params"]:
@@ -226,10 +249,9 @@ class AdaBound(_TorchOptimizer, _RefAPI):
                 denom = st["exp_avg_sq"].sqrt().add_(g["eps"])
                 eta = torch.full_like(denom, step_size).div_(denom).clamp_(lower, upper)
                 p.add_((-eta * st["exp_avg"]).to(p.dtype))
-        return loss
 
 
-class LAMB(_TorchOptimizer, _RefAPI):
+class LAMB(_RefAPI, _TorchOptimizer):
     """Layer-wise adaptive moments with trust ratio (``new(lr)`` = betas 0.9/0.999, eps 1e-6, wd 0.01,
     bias correction on; src/optim/lamb.rs:34-62)."""
 
@@ -239,8 +261,7 @@ class LAMB(_TorchOptimizer, _RefAPI):
                                                bias_correction=bias_correction))
 
     @torch.no_grad()
-    def step(self, closure=None):
-        loss = closure() if closure is not None else None
+    def _fallback_step(self) -> None:
         for g in self.param_groups:
             b1, b2 = g["betas"]
             for p in g["params"]:
@@ -265,10 +286,9 @@ class LAMB(_TorchOptimizer, _RefAPI):
                 wn, un = float(p.float().norm()), float(upd.norm())
                 trust = wn / un if wn > 0 and un > 0 else 1.0
                 p.add_((-g["lr"] * trust * upd).to(p.dtype))
-        return loss
 
 
-class LBFGS(torch.optim.LBFGS, _RefAPI):
+class LBFGS(_RefAPI, torch.optim.LBFGS):
     """``new(lr)``: max_iter 20, max_eval 20, tol_grad 1e-5, tol_change 1e-9, history 10, strong-Wolfe line
     search (src/optim/lbfgs.rs:35-52,192-203)."""
 
@@ -278,6 +298,8 @@ class LBFGS(torch.optim.LBFGS, _RefAPI):
         super().__init__(_params(params), lr=lr, max_iter=max_iter, max_eval=max_eval,
                          tolerance_grad=tolerance_grad, tolerance_change=tolerance_change,
                          history_size=history_size, line_search_fn=line_search_fn)
+
+    step = torch.optim.LBFGS.step          # host loop with closure re-evaluation; no multi-tensor form
 
     @torch.no_grad()
     def step_tensor(self, param: torch.Tensor, grad: torch.Tensor) -> None:
@@ -315,3 +337,8 @@ def _state_dict_with_fast(self):
 for _k, _cls in enumerate((Adam, AdamW, Adamax, NAdam, RAdam)):
     _cls._NATIVE_KIND = _k
     _cls.state_dict = _state_dict_with_fast
+
+# update rules of the CUDA multi-tensor kernel (rustorch_b200/optim/multi_tensor.py)
+for _cls, _kind in ((Adam, 0), (AdamW, 1), (SGD, 2), (NAdam, 3), (RAdam, 4), (Adamax, 5), (RMSprop, 6), (AdaGrad, 7), (AdaBound, 8),
+                    (LAMB, 9)):
+    _cls._MT_KIND = _kind

@@ -672,11 +672,31 @@ class Tensor:
     nuclear_norm = lambda self: float(torch.linalg.matrix_norm(self.data, "nuc"))  # noqa: E731
 
     # ------------------------------------------------------------------ signal
-    def fft(self) -> "Tensor":
-        return Tensor(torch.fft.fft(self.data))
+    def fft(self, n: Optional[int] = None, dim: Optional[int] = None, norm: Optional[str] = None) -> "Tensor":
+        """``fft(n, dim, norm)`` on real or complex data (src/tensor/complex_impl/matrix.rs:154-191)."""
+        return Tensor(torch.fft.fft(self.data, n=n, dim=-1 if dim is None else dim, norm=norm or "backward"))
 
-    def ifft(self) -> "Tensor":
-        return Tensor(torch.fft.ifft(self.data))
+    def ifft(self, n: Optional[int] = None, dim: Optional[int] = None, norm: Optional[str] = None) -> "Tensor":
+        return Tensor(torch.fft.ifft(self.data, n=n, dim=-1 if dim is None else dim, norm=norm or "backward"))
+
+    # complex tensors (src/tensor/complex_impl/tensor_ops.rs:28-64, matrix.rs:61-152)
+    def is_complex(self) -> bool:
+        return self.data.is_complex()
+
+    def real_part(self) -> "Tensor":
+        return Tensor(self.data.real.clone() if self.data.is_complex() else self.data.clone())
+
+    def imag_part(self) -> "Tensor":
+        return Tensor(self.data.imag.clone() if self.data.is_complex() else torch.zeros_like(self.data))
+
+    def arg(self) -> "Tensor":
+        return Tensor(self.data.angle())
+
+    def conj(self) -> "Tensor":
+        return Tensor(self.data.conj().resolve_conj())
+
+    def conj_transpose(self) -> "Tensor":
+        return Tensor(self.data.transpose(-1, -2).conj().resolve_conj().contiguous())
 
     def rfft(self) -> "Tensor":
         return Tensor(torch.fft.rfft(self.data))

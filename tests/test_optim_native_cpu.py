@@ -86,7 +86,7 @@ def test_split_k_rule_fills_one_wave():
     """Weight-gradient GEMMs split the contraction so that tiles x splits stay within one wave of 148 CTAs."""
     from rustorch_b200.nn import fused
     from rustorch_b200.distributed.tp_fused import _wgrad_splits
-    sms = fused._NUM_SMS
+    sms = fused._num_sms()
     for tiles, kb in ((72, 256), (54, 256), (18, 256), (1, 4096), (147, 256), (148, 256), (1179, 256), (6, 16)):
         sk = fused._split_k_for(tiles, kb)
         assert sk >= 1 and (tiles >= sms or tiles * sk <= sms) and sk <= max(1, kb // 8)
