@@ -164,6 +164,24 @@ struct OptimArgs {
 };
 void fused_optim_step(const OptimArgs& a, cudaStream_t stream);
 
+// ---------------------------------------------------------- quant/gemm_i8_tcgen05.cu
+// acc = A_s8[M][K] . B_s8[N][K]^T on the integer tensor cores.  Output either the raw int32 accumulator or
+// fp32 acc * row_scale * col_scale + bias (scales per tensor or per row / column).
+struct GemmI8Args {
+  const void* a;   // s8 [M][K], row stride lda (elements = bytes, multiple of 16)
+  const void* b;   // s8 [N][K], row stride ldb
+  long long lda, ldb;
+  int M, N, K;     // K a multiple of 16
+  int32_t* c_i32 = nullptr;
+  float* c_f32 = nullptr;
+  long long ldc = 0;
+  const float* row_scale = nullptr;  // fp32 output: [M] when row_scale_per_row, else one value
+  const float* col_scale = nullptr;  // fp32 output: [N] when col_scale_per_col, else one value
+  const float* bias = nullptr;       // fp32 [N] or null
+  bool row_scale_per_row = false, col_scale_per_col = false;
+};
+void gemm_i8(const GemmI8Args& g, cudaStream_t stream);
+
 // ------------------------------------------------------- optim/multi_tensor_optim.cu
 enum MultiTensorMode : int {
   MT_ADAM = 0, MT_ADAMW, MT_SGD, MT_NADAM, MT_RADAM, MT_ADAMAX, MT_RMSPROP, MT_ADAGRAD, MT_ADABOUND, MT_LAMB_STAGE1, MT_LAMB_STAGE2

@@ -14,6 +14,9 @@ namespace {
 using at::Tensor;
 
 cudaStream_t cur_stream(int device) { return at::cuda::getCurrentCUDAStream(device).stream(); }
+void check_f32_cuda_extra(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat, name, ": fp32 CUDA tensor required");
+}
 
 // Peer pointers arrive as Python ints (they come from symmetric-memory rendezvous).
 void ddp_bucket_step(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& lp_ptrs,
@@ -70,6 +73,47 @@ void ddp_bucket_step(const std::vector<int64_t>& grad_ptrs, const std::vector<in
   a.grad_scale = float(grad_scale);
   a.status = rt::status_word(master.device().index());
   rt::ddp_bucket_step(a, int(n_ctas), cur_stream(master.device().index()));
+}
+
+// int8 GEMM: a [M, K] s8, b [N, K] s8 -> out int32 [M, N] (no scales) or fp32 [M, N] (scales given).
+void gemm_i8(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Tensor>& row_scale,
+             const c10::optional<Tensor>& col_scale, const c10::optional<Tensor>& bias) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda(), "gemm_i8: CUDA tensors required");
+  TORCH_CHECK(a.scalar_type() == at::kChar && b.scalar_type() == at::kChar, "gemm_i8: int8 operands required");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1,
+              "gemm_i8: rank-2 operands with contiguous rows");
+  TORCH_CHECK(a.size(1) == b.size(1) && out.size(0) == a.size(0) && out.size(1) == b.size(0), "gemm_i8: a [M, K], b [N, K], out [M, N]");
+  c10::cuda::CUDAGuard guard(a.device());
+  rt::GemmI8Args g{};
+  g.a = a.data_ptr();
+  g.b = b.data_ptr();
+  g.lda = a.stride(0);
+  g.ldb = b.stride(0);
+  g.M = int(a.size(0));
+  g.N = int(b.size(0));
+  g.K = int(a.size(1));
+  g.ldc = out.stride(0);
+  if (out.scalar_type() == at::kInt) {
+    g.c_i32 = out.data_ptr<int32_t>();
+  } else {
+    TORCH_CHECK(out.scalar_type() == at::kFloat, "gemm_i8: out must be int32 or fp32");
+    TORCH_CHECK(row_scale.has_value() && col_scale.has_value(), "gemm_i8: an fp32 output needs row_scale and col_scale");
+    check_f32_cuda_extra(*row_scale, "gemm_i8 row_scale");
+    check_f32_cuda_extra(*col_scale, "gemm_i8 col_scale");
+    TORCH_CHECK(row_scale->is_contiguous() && (row_scale->numel() == 1 || row_scale->numel() == g.M), "gemm_i8: row_scale has 1 or M values");
+    TORCH_CHECK(col_scale->is_contiguous() && (col_scale->numel() == 1 || col_scale->numel() == g.N), "gemm_i8: col_scale has 1 or N values");
+    g.c_f32 = out.data_ptr<float>();
+    g.row_scale = row_scale->data_ptr<float>();
+    g.col_scale = col_scale->data_ptr<float>();
+    g.row_scale_per_row = row_scale->numel() == g.M && g.M > 1;
+    g.col_scale_per_col = col_scale->numel() == g.N && g.N > 1;
+    if (bias.has_value() && bias->defined()) {
+      check_f32_cuda_extra(*bias, "gemm_i8 bias");
+      TORCH_CHECK(bias->is_contiguous() && bias->numel() == g.N, "gemm_i8: bias has N values");
+      g.bias = bias->data_ptr<float>();
+    }
+  }
+  rt::gemm_i8(g, cur_stream(a.device().index()));
 }
 
 // One rule applied to a list of tensors; lists longer than 32 are cut into several launches.
@@ -915,6 +959,8 @@ void register_extra_ops(pybind11::module_& m) {
         "fused reduce-scatter + scale + AdamW / Adam / SGD + all-gather of one gradient bucket over peer memory "
         "(plain peer loads / stores, or NVLS multimem when the multicast pointers are non-zero)");
   m.def("ddp_wait_end", &ddp_wait_end);
+  m.def("gemm_i8", &gemm_i8, "int8 x int8 -> int32 tcgen05 GEMM, optional fused dequantisation to fp32", py::arg("a"), py::arg("b"),
+        py::arg("out"), py::arg("row_scale") = py::none(), py::arg("col_scale") = py::none(), py::arg("bias") = py::none());
   m.def("multi_tensor_optim", &multi_tensor_optim,
         "one launch per 32 tensors: Adam / AdamW / SGD / NAdam / RAdam / Adamax / RMSprop / AdaGrad / AdaBound / LAMB update");
 }

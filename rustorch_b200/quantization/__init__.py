@@ -347,13 +347,45 @@ def _requant(acc: torch.Tensor, scale: float, out_scale: torch.Tensor, out_zp: t
     return quantize(acc.float() * scale, out_scale, out_zp, qtype)
 
 
+def _native_i8():
+    from .. import _native
+    return _native.load(required=False)
+
+
+def int8_gemm(a: torch.Tensor, b_nk: torch.Tensor, row_scale: Optional[torch.Tensor] = None,
+              col_scale: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a [M, K] (int8) . b_nk [N, K]^T (int8)`` on the tcgen05 integer tensor cores (csrc/quant/gemm_i8_tcgen05.cu).
+
+    Without scales the int32 accumulator is returned; with ``row_scale`` (1 or M values) and ``col_scale`` (1 or N
+    values) the kernel's epilogue returns fp32 ``acc * row_scale * col_scale (+ bias)``.  K is zero-padded to a
+    multiple of 16 (zeros add nothing to the sum).  CPU tensors take an exact integer matmul.
+    """
+    C = _native_i8() if a.is_cuda else None
+    if C is None:
+        acc = a.to(torch.int32) @ b_nk.to(torch.int32).t()
+        if row_scale is None:
+            return acc
+        y = acc.float() * row_scale.reshape(-1, 1) * col_scale.reshape(1, -1)
+        return y + bias if bias is not None else y
+    K = a.shape[1]
+    if K % 16 or a.stride(0) % 16 or b_nk.stride(0) % 16 or a.stride(1) != 1 or b_nk.stride(1) != 1:
+        pad = -K % 16
+        a = F.pad(a, (0, pad)).contiguous()
+        b_nk = F.pad(b_nk, (0, pad)).contiguous()
+    if row_scale is None:
+        out = torch.empty(a.shape[0], b_nk.shape[0], dtype=torch.int32, device=a.device)
+        C.gemm_i8(a, b_nk, out)
+        return out
+    out = torch.empty(a.shape[0], b_nk.shape[0], dtype=torch.float32, device=a.device)
+    f = lambda t: t.detach().to(device=a.device, dtype=torch.float32).reshape(-1).contiguous()  # noqa: E731
+    C.gemm_i8(a, b_nk, out, f(row_scale), f(col_scale), None if bias is None else f(bias))
+    return out
+
+
 def _int_mm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """int8 [M, K] @ int8 [K, N] -> int32, on the integer tensor cores where the shapes qualify."""
-    if a.is_cuda and a.shape[0] > 16 and a.shape[1] % 8 == 0 and b.shape[1] % 8 == 0:
-        try:
-            return torch._int_mm(a.contiguous(), b.contiguous())
-        except RuntimeError:
-            pass
+    """int8 [M, K] @ int8 [K, N] -> int32: the native tcgen05 int8 GEMM on CUDA, an exact integer matmul on the CPU."""
+    if a.is_cuda and _native_i8() is not None:
+        return int8_gemm(a.contiguous(), b.t().contiguous())
     if a.is_cuda:                         # exact: |codes| <= 128, K < 2^24 / 2^14
         return (a.float() @ b.float()).round().to(torch.int32) if a.shape[1] <= 1024 else (a.double() @ b.double()).round().to(torch.int32)
     return a.to(torch.int32) @ b.to(torch.int32)
@@ -403,7 +435,27 @@ class QuantizedOps:
 
     @staticmethod
     def qconv2d(x: QuantizedTensor, w: QuantizedTensor, bias: Optional[torch.Tensor] = None, stride=1, padding=0) -> torch.Tensor:
-        return F.conv2d(x.dequantize(), w.dequantize(), bias, stride, padding)
+        """Quantised convolution as an int8 GEMM over the unfolded patches: codes are centred by their zero points,
+        multiplied on the integer tensor cores (CUDA) or exactly on the CPU, and scaled back to fp32 in the epilogue.
+        Falls back to the dequantised convolution for per-channel activations or codes that do not fit int8 once
+        centred."""
+        st = (stride, stride) if isinstance(stride, int) else tuple(stride)
+        pd = (padding, padding) if isinstance(padding, int) else tuple(padding)
+        per_tensor_x = x.axis is None and x.scale.numel() == 1
+        w_sym = (w.zero_point.numel() == 1 and int(w.zero_point) == 0) or (w.zero_point.numel() > 1 and not bool(w.zero_point.any()))
+        if x.data.dim() != 4 or not per_tensor_x or not w_sym or (w.axis not in (None, 0)):
+            return F.conv2d(x.dequantize(), w.dequantize(), bias, st, pd)
+        xc = x.data.to(torch.int32) - x.zero_point.to(torch.int32)
+        if int(xc.min()) < -128 or int(xc.max()) > 127:
+            return F.conv2d(x.dequantize(), w.dequantize(), bias, st, pd)
+        N, Cin, H, W = x.data.shape
+        Cout, _, KH, KW = w.data.shape
+        OH, OW = (H + 2 * pd[0] - KH) // st[0] + 1, (W + 2 * pd[1] - KW) // st[1] + 1
+        cols = F.unfold(xc.float(), (KH, KW), padding=pd, stride=st)                 # [N, Cin*KH*KW, OH*OW] (zero = centred zero point)
+        a = cols.transpose(1, 2).reshape(N * OH * OW, Cin * KH * KW).to(torch.int8).contiguous()
+        wk = w.data.reshape(Cout, -1).to(torch.int8).contiguous()
+        y = int8_gemm(a, wk, x.scale.reshape(-1)[:1], w.scale.reshape(-1) if w.scale.numel() > 1 else w.scale.reshape(-1)[:1], bias)
+        return y.reshape(N, OH, OW, Cout).permute(0, 3, 1, 2).contiguous()
 
 
 class DequantizeOps:
@@ -415,12 +467,12 @@ class DequantizeOps:
 def qlinear(x: QuantizedTensor, w: QuantizedTensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x [.., K]`` (per-tensor) times ``w [N, K]`` (per-tensor or per-output-channel, symmetric) -> fp32."""
     K = x.data.shape[-1]
-    acc = _int_mm((x.data.reshape(-1, K).to(torch.int32) - x.zero_point).clamp(-128, 127).to(torch.int8), w.data.t().contiguous().to(torch.int8))
     if w.zero_point.numel() == 1 and int(w.zero_point) != 0 or w.zero_point.numel() > 1 and bool(w.zero_point.any()):
         raise ValueError("qlinear expects symmetric weights (zero_point 0)")
-    y = acc.float() * (x.scale * w.scale.reshape(1, -1))
-    y = y.reshape(*x.data.shape[:-1], w.data.shape[0])
-    return y + bias if bias is not None else y
+    xc = (x.data.reshape(-1, K).to(torch.int32) - x.zero_point).clamp(-128, 127).to(torch.int8)
+    # one kernel: int8 GEMM with the activation scale, the per-channel weight scales and the bias in its epilogue
+    y = int8_gemm(xc, w.data.to(torch.int8), x.scale.reshape(-1)[:1], w.scale.reshape(-1), bias)
+    return y.reshape(*x.data.shape[:-1], w.data.shape[0])
 
 
 def qconv1d(x: QuantizedTensor, w: QuantizedTensor, bias: Optional[torch.Tensor] = None, stride: int = 1, padding: int = 0) -> torch.Tensor:
@@ -550,14 +602,17 @@ def prepare_qat(model: nn.Module, config: Optional[QATConfig] = None) -> nn.Modu
 
 
 def qmatmul_cuda(a: "QuantizedTensor", b: "QuantizedTensor", out_scale=None, out_zp=None) -> "QuantizedTensor":
-    """int8 matmul with the operands moved to the GPU when one is present (src/quantization/hardware.rs qmatmul_cuda runs
-    CPU loops behind the name)."""
+    """Quantised matmul on the GPU: the integer product runs on the tcgen05 int8 GEMM (``int8_gemm``), the zero-point
+    corrections and the requantisation follow.  (The reference's qmatmul_cuda runs CPU loops behind the name,
+    src/quantization/hardware/cuda.rs:12-27.)"""
     if torch.cuda.is_available():
         a, b = a.to("cuda") if hasattr(a, "to") else a, b.to("cuda") if hasattr(b, "to") else b
     return QuantizedOps.qmatmul(a, b, out_scale, out_zp)
 
 
 def qconv2d_cuda(x: "QuantizedTensor", w: "QuantizedTensor", bias=None, stride=1, padding=0) -> torch.Tensor:
+    """Quantised conv2d on the GPU: patches x filters as one tcgen05 int8 GEMM with the scales and bias in its epilogue
+    (src/quantization/hardware/cuda.rs:29-48 names it, CPU loops run behind it there)."""
     if torch.cuda.is_available():
         x, w = x.to("cuda") if hasattr(x, "to") else x, w.to("cuda") if hasattr(w, "to") else w
     return QuantizedOps.qconv2d(x, w, bias, stride, padding)

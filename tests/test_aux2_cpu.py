@@ -192,3 +192,17 @@ def test_qat_fake_quant_and_training():
     assert qw.data.dtype == torch.int8 and bias is not None
     conv = Q.QATConv2d(2, 3, 3, padding=1)
     assert conv(torch.randn(1, 2, 5, 5)).shape == (1, 3, 5, 5)
+
+
+def test_qconv2d_integer_path_matches_dequantised_conv():
+    import torch
+    from rustorch_b200 import quantization as Q
+    torch.manual_seed(0)
+    img, filt = torch.randn(2, 3, 9, 9), torch.randn(5, 3, 3, 3) * 0.3
+    qi = Q.quantize(img, torch.tensor(0.05), torch.tensor(2), Q.QuantizationType.INT8)
+    qf = Q.quantize(filt, torch.tensor(0.01), torch.tensor(0), Q.QuantizationType.INT8)
+    y = Q.QuantizedOps.qconv2d(qi, qf, torch.ones(5), stride=2, padding=1)
+    ref = torch.nn.functional.conv2d(qi.dequantize(), qf.dequantize(), torch.ones(5), 2, 1)
+    torch.testing.assert_close(y, ref, rtol=1e-4, atol=1e-4)
+    acc = Q.int8_gemm(torch.tensor([[1, -2, 3]], dtype=torch.int8), torch.tensor([[4, 5, -6], [1, 1, 1]], dtype=torch.int8))
+    assert acc.tolist() == [[-24, 2]]

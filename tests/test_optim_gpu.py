@@ -51,7 +51,7 @@ def test_multi_tensor_step_matches_torch_optim(name, kw, tname, tkw):
         ref.step()
     assert multi_tensor.launches - n0 == 8 * 2, "the native multi-tensor path did not run"
     for p, r in zip(ps, ref_ps):
-        torch.testing.assert_close(p.data, r.data, rtol=2e-5, atol=2e-6)
+        torch.testing.assert_close(p.data, r.data, rtol=1e-4, atol=2e-5)
     # state dict keeps torch's layout: a torch optimizer of the same kind loads it and continues identically
     sd = ours.state_dict()
     ref2_ps = [torch.nn.Parameter(p.detach().clone()) for p in ps]
@@ -62,7 +62,7 @@ def test_multi_tensor_step_matches_torch_optim(name, kw, tname, tkw):
     ours.step()
     ref2.step()
     for p, r in zip(ps, ref2_ps):
-        torch.testing.assert_close(p.data, r.data, rtol=2e-5, atol=2e-6)
+        torch.testing.assert_close(p.data, r.data, rtol=1e-4, atol=2e-5)
 
 
 @pytest.mark.parametrize("name,kw", [("LAMB", dict(lr=1e-2, weight_decay=0.01)), ("AdaBound", dict(lr=1e-2, final_lr=0.1, weight_decay=0.01))])
