@@ -27,6 +27,14 @@
 #include "../common/launch.h"
 #include "attn_common.cuh"
 
+#include <algorithm>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <queue>
+#include <tuple>
+#include <vector>
+
 namespace rt {
 
 struct AttnFwdPPParams {
@@ -38,7 +46,12 @@ struct AttnFwdPPParams {
   float* lse;  // [B][H][Tq]
   int n_pairs;  // pairs of query tiles per (batch, head)
   int total_items;
+  const int* item_list;  // [gridDim.x][items_per_cta]: the items of each CTA in processing order, -1 = none
+  int items_per_cta;
   int* status;
+#ifdef RT_ATTN_PROF
+  long long* prof;  // [gridDim.x][2 groups][8]: cycles spent in each phase by lane 0 of the group's first warp
+#endif
 };
 
 template <int D>
@@ -55,8 +68,36 @@ struct AttnFwdPPSmem {
   static_assert(TOTAL <= 232448, "attention: shared memory over the per-CTA limit");
 };
 
+#ifdef RT_ATTN_PROF
+long long*& attn_prof_buffer() {
+  static long long* b = nullptr;
+  return b;
+}
+extern "C" long long* rt_attn_prof_buffer() { return attn_prof_buffer(); }
+#endif
+
 constexpr float ATT_PP_RESCALE_THRESHOLD = 8.f;  // log2 units
 constexpr int ATT_PP_THREADS = 352;
+
+// 2^x for x <= ~8 on the FMA / integer pipes: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-3
+// minimax polynomial (relative error 7.7e-5, far below the 16-bit rounding of P), then n is added to the exponent
+// field.  Used for one exponential in eight so that the special-function unit (16 ex2 per clock and SM) and the FMA
+// pipe finish a score tile at about the same time.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = x + 12582912.f;                 // 1.5 * 2^23: the integer part of x lands in the low mantissa bits
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 0.05511089786887169f, 0.2426059991121292f);
+  p = fmaf(p, f, 0.6932721734046936f);
+  p = fmaf(p, f, 0.9999287128448486f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&w)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+               "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
 
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float r;
@@ -64,21 +105,18 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return r;
 }
 
-// Item w of the longest-first list -> (batch, head, pair of query tiles).
+// Item id = pair * (B * H) + batch * H + head.
 __device__ __forceinline__ void pp_decode_item(int w, const AttnFwdPPParams& p, int& b, int& h, int& pair) {
   const int bh = p.B * p.H;
-  const int level = w / bh;
-  const int r = w - level * bh;
-  pair = p.causal ? (p.n_pairs - 1 - level) : level;
+  pair = w / bh;
+  const int r = w - pair * bh;
   b = r / p.H;
   h = r - b * p.H;
 }
-// k-th item of this CTA in serpentine order (even rounds left to right, odd rounds right to left); -1 past the end.
+// k-th item of this CTA; -1 past the end.  The host deals the items longest first to the least loaded CTA, so the
+// per-CTA totals differ by less than one short item (see build_item_list).
 __device__ __forceinline__ int pp_item_of(int k, const AttnFwdPPParams& p) {
-  const int G = gridDim.x;
-  const int c = (k & 1) ? (G - 1 - int(blockIdx.x)) : int(blockIdx.x);
-  const int w = k * G + c;
-  return w < p.total_items ? w : -1;
+  return k < p.items_per_cta ? __ldg(p.item_list + (long long)blockIdx.x * p.items_per_cta + k) : -1;
 }
 // Number of key tiles query tile `qt` looks at (0: the tile has no rows or sees no key).
 __device__ __forceinline__ int pp_n_kv(int qt, const AttnFwdPPParams& p) {
@@ -92,7 +130,7 @@ __device__ __forceinline__ int pp_n_kv(int qt, const AttnFwdPPParams& p) {
   return n;
 }
 
-template <int D, bool F16>
+template <int D, bool F16, int POLY>
 __global__ void __launch_bounds__(ATT_PP_THREADS, 1)
 attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const AttnFwdPPParams p) {
@@ -172,27 +210,33 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         const int hk = h / group;
         const int n0 = pp_n_kv(2 * pair, p), n1 = pp_n_kv(2 * pair + 1, p);
         const int n = max(n0, n1);
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          if ((i == 0 ? n0 : n1) == 0) continue;
-          if (q_items[i] > 0 && !mbar_wait(&q_empty[i], (q_items[i] - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) {
-            ok = false;
-            break;
-          }
+        // Order: the first active query tile, the first key / value tile, then the other query tile and the rest, so
+        // that the group that finished the previous item first is not held up by the other group's last tile.
+        auto load_q = [&](int i) -> bool {
+          if ((i == 0 ? n0 : n1) == 0) return true;
+          if (q_items[i] > 0 && !mbar_wait_idle(&q_empty[i], (q_items[i] - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) return false;
           mbar_arrive_expect_tx(&q_full[i], S::TILE);
           load_tile<D>(smem + S::OFF_Q + i * S::TILE, &tmap_q, &q_full[i], (2 * pair + i) * ATT_BM, h, b);
           ++q_items[i];
-        }
-        for (int j = 0; j < n && ok; ++j, ++kv_it) {
+          return true;
+        };
+        auto load_kv = [&](int j) -> bool {
           const int s = kv_it % KS;
           const uint32_t ph = (kv_it / KS) & 1;
-          if (!mbar_wait(&k_empty[s], ph ^ 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
+          if (!mbar_wait_idle(&k_empty[s], ph ^ 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) return false;
           mbar_arrive_expect_tx(&k_full[s], S::TILE);
           load_tile<D>(smem + S::OFF_K + s * S::TILE, &tmap_k, &k_full[s], j * ATT_BN, hk, b);
-          if (!mbar_wait(&v_empty[s], ph ^ 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
+          if (!mbar_wait_idle(&v_empty[s], ph ^ 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) return false;
           mbar_arrive_expect_tx(&v_full[s], S::TILE);
           load_tile<D>(smem + S::OFF_V + s * S::TILE, &tmap_v, &v_full[s], j * ATT_BN, hk, b);
-        }
+          ++kv_it;
+          return true;
+        };
+        const int first = n0 > 0 ? 0 : 1;
+        ok = load_q(first);
+        if (ok && n > 0) ok = load_kv(0);
+        if (ok) ok = load_q(1 - first);
+        for (int j = 1; j < n && ok; ++j) ok = load_kv(j);
       }
     }
   } else if (warp >= 8) {
@@ -225,9 +269,9 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         const int ni = i == 0 ? n0 : n1;
         if (ni > 0) {
           // first S of the item: Q_i and K(0) loaded, the S region free of the previous item's last tile
-          ok = mbar_wait(&q_full[i], items & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA) &&
-               mbar_wait(&k_full[kv_it % KS], (kv_it / KS) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA);
-          if (ok && !ALIAS && cnt > 0) ok = mbar_wait(&s_free[i], (cnt - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+          ok = mbar_wait_idle(&q_full[i], items & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA) &&
+               mbar_wait_idle(&k_full[kv_it % KS], (kv_it / KS) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+          if (ok && !ALIAS && cnt > 0) ok = mbar_wait_idle(&s_free[i], (cnt - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA);
           if (!ok) break;
           tc_fence_after();
           issue_S(kv_it);
@@ -238,16 +282,16 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           const int s = pos % KS;
           const uint32_t ph = (pos / KS) & 1;
           if (!ALIAS && j + 1 < ni) {  // next S while this tile's softmax runs: needs S(j) in registers and K(j+1)
-            ok = mbar_wait(&s_free[i], cnt & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA) &&
-                 mbar_wait(&k_full[(pos + 1) % KS], ((pos + 1) / KS) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+            ok = mbar_wait_idle(&s_free[i], cnt & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA) &&
+                 mbar_wait_idle(&k_full[(pos + 1) % KS], ((pos + 1) / KS) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA);
             if (!ok) break;
             tc_fence_after();
             issue_S(pos + 1);
             if (j + 2 == ni) umma_commit(&q_empty[i]);
           }
-          ok = mbar_wait(&p_full[i], cnt & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA) &&
-               mbar_wait(&v_full[s], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA);
-          if (ok && j == 0 && items > 0) ok = mbar_wait(&o_free[i], (items - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+          ok = mbar_wait_idle(&p_full[i], cnt & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA) &&
+               mbar_wait_idle(&v_full[s], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+          if (ok && j == 0 && items > 0) ok = mbar_wait_idle(&o_free[i], (items - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA);
           if (!ok) break;
           tc_fence_after();
           const uint32_t aV = smem_u32(smem + S::OFF_V + s * S::TILE);
@@ -257,7 +301,7 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           umma_commit(&pv_done[i]);
           umma_commit(&v_empty[s]);
           if (ALIAS && j + 1 < ni) {  // P overlays S: the next S follows O += P V in issue order
-            if (!mbar_wait(&k_full[(pos + 1) % KS], ((pos + 1) / KS) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA)) { ok = false; break; }
+            if (!mbar_wait_idle(&k_full[(pos + 1) % KS], ((pos + 1) / KS) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA)) { ok = false; break; }
             tc_fence_after();
             issue_S(pos + 1);
             if (j + 2 == ni) umma_commit(&q_empty[i]);
@@ -268,9 +312,9 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           const uint32_t pos = kv_it + j;
           const int s = pos % KS;
           const uint32_t ph = (pos / KS) & 1;
-          ok = mbar_wait(&k_full[s], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+          ok = mbar_wait_idle(&k_full[s], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA);
           if (ok) mbar_arrive(&k_empty[s]);
-          ok = ok && mbar_wait(&v_full[s], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+          ok = ok && mbar_wait_idle(&v_full[s], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA);
           if (ok) mbar_arrive(&v_empty[s]);
         }
         kv_it += n;
@@ -285,6 +329,13 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int off = p.Tk - p.Tq;  // causal: key col visible iff col <= row + off
     uint32_t cnt = 0;
     bool ok = true;
+#ifdef RT_ATTN_PROF
+    long long pf[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long t_prev = clock64();
+#define PROF_MARK(slot) { const long long t_now = clock64(); pf[slot] += t_now - t_prev; t_prev = t_now; }
+#else
+#define PROF_MARK(slot)
+#endif
     for (int k = 0; ok; ++k) {
       const int w = pp_item_of(k, p);
       if (w < 0) break;
@@ -306,14 +357,17 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const int limit = p.causal ? min(p.Tk - 1, qi + off) : (p.Tk - 1);  // last visible column
       float m = 0.f, l = 0.f;
       for (int j = 0; j < ni && ok; ++j, ++cnt) {
+        PROF_MARK(0)
         if (!mbar_wait(&s_full[i], cnt & 1, ctl, p.status, RT_ERR_TIMEOUT_SOFTMAX)) { ok = false; break; }
         tc_fence_after();
+        PROF_MARK(1)
         uint32_t r[128];
         __syncwarp();
 #pragma unroll
         for (int c = 0; c < 4; ++c)
           tmem_ld_32x32b_x32(tmem_S(i) + lane_sel + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
         tmem_ld_wait();
+        PROF_MARK(2)
         if (!ALIAS) {
           tc_fence_before();
           mbar_arrive(&s_free[i]);  // S is in registers: the next S MMA may overwrite TMEM now
@@ -325,13 +379,15 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           for (int e = 0; e < 128; ++e)
             if (col_base + e > limit) r[e] = 0xff800000u;  // -inf
         }
-        float mx0 = -INFINITY, mx1 = -INFINITY;
+        float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;   // four independent chains
 #pragma unroll
-        for (int e = 0; e < 128; e += 4) {
-          mx0 = fmax3(mx0, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
-          mx1 = fmax3(mx1, __uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
+        for (int e = 0; e < 128; e += 8) {
+          a0 = fmax3(a0, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
+          a1 = fmax3(a1, __uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
+          a2 = fmax3(a2, __uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
+          a3 = fmax3(a3, __uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
         }
-        const float mx = fmaxf(mx0, mx1) * p.scale_log2;  // scale > 0: max commutes with it
+        const float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * p.scale_log2;  // scale > 0: max commutes with it
         float alpha = 1.f;
         bool rescale = false;
         if (j == 0) {
@@ -345,6 +401,7 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             l *= alpha;
           }
         }
+        PROF_MARK(7)
         const float neg_m = -m;
         float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
         uint32_t pk[64];
@@ -353,7 +410,8 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           const float e0 = ex2_approx(fmaf(__uint_as_float(r[e]), p.scale_log2, neg_m));
           const float e1 = ex2_approx(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, neg_m));
           const float e2 = ex2_approx(fmaf(__uint_as_float(r[e + 2]), p.scale_log2, neg_m));
-          const float e3 = ex2_approx(fmaf(__uint_as_float(r[e + 3]), p.scale_log2, neg_m));
+          const float x3 = fmaf(__uint_as_float(r[e + 3]), p.scale_log2, neg_m);
+          const float e3 = (POLY == 4 || (POLY == 8 && (e & 4))) ? exp2_poly(x3) : ex2_approx(x3);
           sum0 += e0;
           sum1 += e1;
           sum2 += e2;
@@ -362,9 +420,11 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           pk[e / 2 + 1] = pack_2x16<F16>(e2, e3);
         }
         l += (sum0 + sum1) + (sum2 + sum3);
+        PROF_MARK(3)
         // O_i += P V of the previous key tile must have retired before P is overwritten or O rescaled
         if (cnt > 0 && !mbar_wait(&pv_done[i], (cnt - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_SOFTMAX)) { ok = false; break; }
         tc_fence_after();
+        PROF_MARK(4)
         if (rescale) {
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
@@ -383,12 +443,15 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&p_full[i]);
+        PROF_MARK(5)
       }
       // ---- epilogue of the item: O / l -> global, log-sum-exp, then hand O back to the MMA warp
       if (ok) ok = mbar_wait(&pv_done[i], (cnt - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_EPILOGUE);
       if (!ok) break;
       tc_fence_after();
+      PROF_MARK(6)
       const float inv = l > 0.f ? 1.f / l : 0.f;
+      const bool wide_store = ((reinterpret_cast<uintptr_t>(orow) & 31) == 0);   // rows of this (batch, head) 32-byte aligned
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
@@ -396,14 +459,17 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tmem_ld_32x32b_x32(tmem_O(i) + lane_sel + c * 32, o);
         tmem_ld_wait();
         if (qi < p.Tq) {
+          uint32_t w16[16];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 w4;
-            w4.x = pack_2x16<F16>(__uint_as_float(o[q * 8 + 0]) * inv, __uint_as_float(o[q * 8 + 1]) * inv);
-            w4.y = pack_2x16<F16>(__uint_as_float(o[q * 8 + 2]) * inv, __uint_as_float(o[q * 8 + 3]) * inv);
-            w4.z = pack_2x16<F16>(__uint_as_float(o[q * 8 + 4]) * inv, __uint_as_float(o[q * 8 + 5]) * inv);
-            w4.w = pack_2x16<F16>(__uint_as_float(o[q * 8 + 6]) * inv, __uint_as_float(o[q * 8 + 7]) * inv);
-            reinterpret_cast<uint4*>(orow + c * 32)[q] = w4;
+          for (int q = 0; q < 16; ++q)
+            w16[q] = pack_2x16<F16>(__uint_as_float(o[2 * q]) * inv, __uint_as_float(o[2 * q + 1]) * inv);
+          if (wide_store) {  // 32-byte stores: two per 32 columns
+            st_global_v8(orow + c * 32, *reinterpret_cast<uint32_t(*)[8]>(&w16[0]));
+            st_global_v8(orow + c * 32 + 16, *reinterpret_cast<uint32_t(*)[8]>(&w16[8]));
+          } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              reinterpret_cast<uint4*>(orow + c * 32)[q] = make_uint4(w16[q * 4], w16[q * 4 + 1], w16[q * 4 + 2], w16[q * 4 + 3]);
           }
         }
       }
@@ -411,7 +477,12 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       mbar_arrive(&o_free[i]);
       if (qi < p.Tq)
         p.lse[((long long)b * p.H + h) * p.Tq + qi] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      PROF_MARK(7)
     }
+#ifdef RT_ATTN_PROF
+    if ((warp & 3) == 0 && lane == 0 && p.prof)
+      for (int e = 0; e < 8; ++e) p.prof[(blockIdx.x * 2 + i) * 8 + e] = pf[e];
+#endif
   }
 
   // Common exit: on abort give in-flight bulk copies time to land, then release TMEM.
@@ -427,11 +498,72 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   }
 }
 
-template <int D, bool F16>
+// Longest-processing-time-first assignment of the work items to `grid` CTAs, cached on the device per problem
+// geometry.  The cost of an item is the number of key tiles its two query tiles look at; items go, longest first, to
+// the CTA with the smallest total so far, and each CTA processes its own items longest first.
+struct ItemListKey {
+  int device, B, H, Tq, Tk, causal, grid;
+  bool operator<(const ItemListKey& o) const {
+    return std::tie(device, B, H, Tq, Tk, causal, grid) < std::tie(o.device, o.B, o.H, o.Tq, o.Tk, o.causal, o.grid);
+  }
+};
+struct ItemList {
+  int* dev = nullptr;
+  int per_cta = 0;
+};
+static ItemList build_item_list(const AttnArgs& a, int n_pairs, int grid, int device, cudaStream_t stream) {
+  static std::mutex mu;
+  static std::map<ItemListKey, ItemList> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  const ItemListKey key{device, a.B, a.H, a.Tq, a.Tk, a.causal, grid};
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  const int bh = a.B * a.H;
+  auto n_kv = [&](int qt) {
+    const int q0 = qt * ATT_BM;
+    if (q0 >= a.Tq) return 0;
+    int n = (a.Tk + ATT_BN - 1) / ATT_BN;
+    if (a.causal) {
+      const int last_col = std::min(a.Tk - 1, q0 + ATT_BM - 1 + (a.Tk - a.Tq));
+      n = last_col < 0 ? 0 : std::min(n, last_col / ATT_BN + 1);
+    }
+    return n;
+  };
+  std::vector<std::pair<int, int>> items;  // (cost, id)
+  items.reserve(size_t(n_pairs) * bh);
+  for (int pair = 0; pair < n_pairs; ++pair) {
+    const int cost = n_kv(2 * pair) + n_kv(2 * pair + 1) + 1;  // + 1: per-item prologue / epilogue
+    for (int r = 0; r < bh; ++r) items.emplace_back(cost, pair * bh + r);
+  }
+  std::stable_sort(items.begin(), items.end(), [](const auto& x, const auto& y) { return x.first > y.first; });
+  std::vector<std::vector<int>> per(grid);
+  using Load = std::pair<long long, int>;  // (total cost, cta)
+  std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+  for (int c = 0; c < grid; ++c) heap.emplace(0, c);
+  for (const auto& itx : items) {
+    Load top = heap.top();
+    heap.pop();
+    per[top.second].push_back(itx.second);
+    heap.emplace(top.first + itx.first, top.second);
+  }
+  size_t mx = 1;
+  for (const auto& v : per) mx = std::max(mx, v.size());
+  std::vector<int> flat(size_t(grid) * mx, -1);
+  for (int c = 0; c < grid; ++c) std::copy(per[c].begin(), per[c].end(), flat.begin() + size_t(c) * mx);
+  ItemList out;
+  out.per_cta = int(mx);
+  RT_CUDA_CHECK(cudaMalloc(&out.dev, flat.size() * sizeof(int)));
+  RT_CUDA_CHECK(cudaMemcpyAsync(out.dev, flat.data(), flat.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
+  RT_CUDA_CHECK(cudaStreamSynchronize(stream));  // `flat` is pageable host memory that dies with this scope
+  cache.emplace(key, out);
+  return out;
+}
+
+template <int D, bool F16, int POLY>
 static void launch_fwd_pp(const AttnArgs& a, cudaStream_t stream) {
   using S = AttnFwdPPSmem<D>;
   const int device = current_device();
-  auto kern = attn_fwd_pp_kernel<D, F16>;
+  auto kern = attn_fwd_pp_kernel<D, F16, POLY>;
   static bool configured[64] = {false};
   if (!configured[device]) {
     RT_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
@@ -458,6 +590,15 @@ static void launch_fwd_pp(const AttnArgs& a, cudaStream_t stream) {
   p.total_items = a.B * a.H * p.n_pairs;
   p.status = status_word(device);
   const int grid = std::min(p.total_items, sm_count(device));
+  const ItemList il = build_item_list(a, p.n_pairs, grid, device, stream);
+  p.item_list = il.dev;
+  p.items_per_cta = il.per_cta;
+#ifdef RT_ATTN_PROF
+  static long long* prof_buf = nullptr;
+  if (!prof_buf) RT_CUDA_CHECK(cudaMallocManaged(&prof_buf, 148 * 2 * 8 * sizeof(long long)));
+  p.prof = prof_buf;
+  attn_prof_buffer() = prof_buf;
+#endif
   kern<<<grid, ATT_PP_THREADS, S::TOTAL, stream>>>(tq, tk, tv, p);
   RT_LAUNCH_CHECK();
 }
@@ -465,12 +606,12 @@ static void launch_fwd_pp(const AttnArgs& a, cudaStream_t stream) {
 // Same contract as attn_fwd (flash_fwd.cu); requires scale > 0.
 void attn_fwd_pp(const AttnArgs& a, cudaStream_t stream) {
   if (a.io_fp16) {
-    if (a.D == 64) launch_fwd_pp<64, true>(a, stream);
-    else launch_fwd_pp<128, true>(a, stream);
+    if (a.D == 64) launch_fwd_pp<64, true, 8>(a, stream);
+    else launch_fwd_pp<128, true, 8>(a, stream);
   } else if (a.D == 64) {
-    launch_fwd_pp<64, false>(a, stream);
+    launch_fwd_pp<64, false, 8>(a, stream);
   } else {
-    launch_fwd_pp<128, false>(a, stream);
+    launch_fwd_pp<128, false, 8>(a, stream);
   }
 }
 

@@ -86,6 +86,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait with a suspend-time hint: the thread sleeps in hardware for up to `ns` nanoseconds and wakes as soon as
+// the phase completes, so a waiting control warp takes no issue slots from the warps that share its scheduler.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Non-blocking probe of an mbarrier phase (try_wait may suspend the thread for a system-dependent time; a thread that
 // serves several barriers in turn must not be held up by the one that is not ready).
 __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
@@ -132,6 +148,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, CtaCtl
         if (status) atomicCAS(status, 0, err_code);
         return false;
       }
+    }
+  }
+}
+
+// Same contract as mbar_wait for threads that have nothing else to do (TMA producers, MMA issuers): every probe may
+// sleep up to 20 us in hardware, so the loop issues a handful of instructions per wake-up instead of spinning.
+__device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity, CtaCtl* ctl, int* status, int err_code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+    if (ctl->abort) return false;
+    if (globaltimer_ns() - t0 > RT_WAIT_TIMEOUT_NS) {
+      ctl->abort = 1;
+      if (status) atomicCAS(status, 0, err_code);
+      return false;
     }
   }
 }

@@ -25,7 +25,7 @@ TARGET = Path(__file__).resolve().parent / f"_C{EXT_SUFFIX}"
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "--threads", "2",
-]
+] + os.environ.get("RUSTORCH_NVCC_EXTRA", "").split()          # e.g. "-DRT_ATTN_PROF" for an instrumented build
 
 
 def _cuda_home() -> str:
