@@ -77,7 +77,10 @@ extern "C" long long* rt_attn_prof_buffer() { return attn_prof_buffer(); }
 #endif
 
 constexpr float ATT_PP_RESCALE_THRESHOLD = 8.f;  // log2 units
-constexpr int ATT_PP_THREADS = 352;
+// The CTA owns 384 x 168 = 64512 registers at launch; the two budgets must fit into that or setmaxnreg.inc never returns.
+constexpr int ATT_PP_REGS_CONTROL = 64, ATT_PP_REGS_SOFTMAX = 216;  // 128 x 64 + 256 x 216 = 63488
+static_assert(128 * ATT_PP_REGS_CONTROL + 256 * ATT_PP_REGS_SOFTMAX <= 384 * 168, "register budgets exceed the CTA allocation");
+constexpr int ATT_PP_THREADS = 384;  // 12 warps; warp 11 idles (register re-division works on groups of four warps)
 
 // 2^x for x <= ~8 on the FMA / integer pipes: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-3
 // minimax polynomial (relative error 7.7e-5, far below the 16-bit rounding of P), then n is added to the exponent
@@ -196,6 +199,9 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   auto tmem_P = [&](int i) { return ALIAS ? tmem_S(i) : (tmem_base + 384u + uint32_t(i) * 64u); };
   const int group = p.H / p.Hkv;
 
+  if (warp >= 8) {
+  // Control warps give registers up, the softmax groups take them (setmaxnreg acts on aligned groups of four warps).
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ATT_PP_REGS_CONTROL));
   if (warp == 10) {
     // ================================================================== TMA producer
     if (lane == 0) {
@@ -239,7 +245,7 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         for (int j = 1; j < n && ok; ++j) ok = load_kv(j);
       }
     }
-  } else if (warp >= 8) {
+  } else if (warp < 10) {
     // ================================================================== MMA issuer of query tile i
     const int i = warp - 8;
     if (lane == 0) {
@@ -321,7 +327,9 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         if (ni > 0) ++items;
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(ATT_PP_REGS_SOFTMAX));
     // ================================================================== softmax group of query tile i
     const int i = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
