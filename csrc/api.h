@@ -53,6 +53,7 @@ struct AttnArgs {
   // backward only
   const void* d_o;  // same strides as o
   float* delta;     // [B][H][Tq] scratch: rowsum(o * do)
+  float* dq_acc = nullptr;  // optional fp32 scratch [B][Tq][H][D]: enables the single-kernel backward for D == 64
   void *dq, *dk, *dv;  // bf16, strides below
   long long dq_sb, dq_st, dq_sh, dk_sb, dk_st, dk_sh, dv_sb, dv_st, dv_sh;
 };

@@ -23,6 +23,8 @@
 
 namespace rt {
 
+void attn_bwd_fused_d64(const AttnArgs& a, cudaStream_t stream);  // flash_bwd_fused.cu
+
 struct AttnBwdParams {
   int B, H, Hkv, Tq, Tk;
   int causal;
@@ -1123,6 +1125,16 @@ static void launch_bwd(const AttnArgs& a, cudaStream_t stream) {
         reinterpret_cast<const __nv_bfloat16*>(a.o), reinterpret_cast<const __nv_bfloat16*>(a.d_o),
         a.delta, a.B, a.H, a.Tq, a.o_sb, a.o_st, a.o_sh);
     RT_LAUNCH_CHECK();
+  }
+  // 64-wide heads with an accumulation buffer: one kernel computes dK, dV and dQ from a single S / dP per tile pair
+  // (flash_bwd_fused.cu).  RUSTORCH_ATTN_BWD_FUSED=0 keeps the two-kernel path below.
+  static const bool fused = [] {
+    const char* e = std::getenv("RUSTORCH_ATTN_BWD_FUSED");
+    return !(e && e[0] == '0');
+  }();
+  if (D == 64 && a.dq_acc != nullptr && fused) {
+    attn_bwd_fused_d64(a, stream);
+    return;
   }
   CUtensorMap tq = make_tmap_2byte_4d(a.q, D, a.Tq, a.H, a.B, a.q_st, a.q_sh, a.q_sb, 64, 128);
   CUtensorMap tk = make_tmap_2byte_4d(a.k, D, a.Tk, a.Hkv, a.B, a.k_st, a.k_sh, a.k_sb, 64, 128);

@@ -63,7 +63,7 @@ struct AttnFwdPPSmem {
   static constexpr int OFF_V = OFF_K + KV_STAGES * TILE;
   static constexpr int OFF_BAR = OFF_V + KV_STAGES * TILE;
   // q_full[2] q_empty[2] s_full[2] s_free[2] p_full[2] pv_done[2] o_free[2] k_full[KS] k_empty[KS] v_full[KS] v_empty[KS]
-  static constexpr int N_BARS = 14 + 4 * KV_STAGES;
+  static constexpr int N_BARS = 16 + 4 * KV_STAGES;   // ... + tok[2]
   static constexpr int TOTAL = OFF_BAR + N_BARS * 8 + 16;
   static_assert(TOTAL <= 232448, "attention: shared memory over the per-CTA limit");
 };
@@ -157,6 +157,7 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   uint64_t* k_empty = k_full + KS;
   uint64_t* v_full = k_empty + KS;
   uint64_t* v_empty = v_full + KS;
+  uint64_t* tok = v_empty + KS;  // D = 128 only: the two MMA issuers take turns, tile 0 first
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + S::N_BARS);
   CtaCtl* ctl = reinterpret_cast<CtaCtl*>(tmem_slot + 1);
 
@@ -173,6 +174,7 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       mbar_init(&p_full[i], 128);
       mbar_init(&pv_done[i], 1);
       mbar_init(&o_free[i], 128);
+      mbar_init(&tok[i], 1);
     }
     for (int s = 0; s < KS; ++s) {
       mbar_init(&k_full[s], 1);
@@ -255,7 +257,20 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       uint32_t kv_it = 0;   // ring position at the start of the current item
       uint32_t cnt = 0;     // key tiles this query tile has processed over all items (phase of the per-tile barriers)
       uint32_t items = 0;   // items in which this tile was active
+      uint32_t slot = 0;    // key-tile slots walked so far (both issuers walk the same number per item)
       bool ok = true;
+      // D = 128 (P overlays S): the two issuers alternate strictly, tile 0 then tile 1, per key tile.  Tile 1's
+      // "O += P V, next S" batch then always follows tile 0's, which keeps the two softmax groups half a period apart:
+      // one exponentiates while the tensor core works for the other, instead of both waiting for it at once.
+      auto turn_acquire = [&]() -> bool {
+        if (!ALIAS) return true;
+        if (i == 0) return slot == 0 || mbar_wait_idle(&tok[0], (slot - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+        return mbar_wait_idle(&tok[1], slot & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+      };
+      auto turn_release = [&]() {
+        if (ALIAS) mbar_arrive(&tok[1 - i]);
+        ++slot;
+      };
       auto issue_S = [&](uint32_t ring_pos) {
         const int s = ring_pos % KS;
         const uint32_t aK = smem_u32(smem + S::OFF_K + s * S::TILE);
@@ -295,7 +310,7 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             issue_S(pos + 1);
             if (j + 2 == ni) umma_commit(&q_empty[i]);
           }
-          ok = mbar_wait_idle(&p_full[i], cnt & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA) &&
+          ok = turn_acquire() && mbar_wait_idle(&p_full[i], cnt & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA) &&
                mbar_wait_idle(&v_full[s], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA);
           if (ok && j == 0 && items > 0) ok = mbar_wait_idle(&o_free[i], (items - 1) & 1, ctl, p.status, RT_ERR_TIMEOUT_MMA);
           if (!ok) break;
@@ -312,16 +327,18 @@ attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             issue_S(pos + 1);
             if (j + 2 == ni) umma_commit(&q_empty[i]);
           }
+          turn_release();
         }
         // key tiles only the other query tile looks at: hand the ring slots back once they are loaded
         for (int j = ni; j < n && ok; ++j) {
           const uint32_t pos = kv_it + j;
           const int s = pos % KS;
           const uint32_t ph = (pos / KS) & 1;
-          ok = mbar_wait_idle(&k_full[s], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA);
+          ok = turn_acquire() && mbar_wait_idle(&k_full[s], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA);
           if (ok) mbar_arrive(&k_empty[s]);
           ok = ok && mbar_wait_idle(&v_full[s], ph, ctl, p.status, RT_ERR_TIMEOUT_MMA);
           if (ok) mbar_arrive(&v_empty[s]);
+          if (ok) turn_release();
         }
         kv_it += n;
         if (ni > 0) ++items;

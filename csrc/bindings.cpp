@@ -147,7 +147,7 @@ void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tens
 
 void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o,
               const Tensor& lse, Tensor& delta, Tensor& dq, Tensor& dk, Tensor& dv, bool causal,
-              double scale) {
+              double scale, const OptTensor& dq_acc) {
   c10::cuda::CUDAGuard guard(q.device());
   rt::AttnArgs a = make_attn_args(q, k, v, o, lse, causal, scale);
   check_bf16_cuda(d_o, "attention do");
@@ -172,6 +172,11 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   a.dv_sb = dv.stride(0); a.dv_st = dv.stride(1); a.dv_sh = dv.stride(2);
   for (int64_t s : {a.dq_sb, a.dq_st, a.dq_sh, a.dk_sb, a.dk_st, a.dk_sh, a.dv_sb, a.dv_st, a.dv_sh})
     TORCH_CHECK(s % 8 == 0, "attention: gradient strides must be multiples of 8 elements");
+  if (dq_acc.has_value() && dq_acc->defined()) {
+    check_f32_cuda(*dq_acc, "attention dq_acc");
+    TORCH_CHECK(dq_acc->is_contiguous() && dq_acc->numel() == q.numel(), "attention: dq_acc must be a contiguous fp32 tensor shaped like q");
+    a.dq_acc = dq_acc->data_ptr<float>();
+  }
   rt::attn_bwd(a, stream_of(q));
 }
 
@@ -369,7 +374,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("alpha"), pybind11::arg("accumulate"), pybind11::arg("split_k"), pybind11::arg("block_n"),
         pybind11::arg("alpha_dev") = pybind11::none());
   m.def("attn_fwd", &attn_fwd);
-  m.def("attn_bwd", &attn_bwd);
+  m.def("attn_bwd", &attn_bwd, pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("o"), pybind11::arg("d_o"),
+        pybind11::arg("lse"), pybind11::arg("delta"), pybind11::arg("dq"), pybind11::arg("dk"), pybind11::arg("dv"), pybind11::arg("causal"),
+        pybind11::arg("scale"), pybind11::arg("dq_acc") = pybind11::none());
   m.def("norm_fwd", &norm_fwd);
   m.def("norm_bwd", &norm_bwd);
   m.def("embedding_fwd", &embedding_fwd);

@@ -64,7 +64,9 @@ def attention_bwd(q, k, v, o, d_o, lse, causal: bool, scale: Optional[float] = N
     delta = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device)
     if d_o.stride() != o.stride():
         d_o = d_o.contiguous() if o.is_contiguous() else d_o.clone(memory_format=torch.preserve_format)
-    _C().attn_bwd(q, k, v, o, d_o, lse, delta, dq, dk, dv, causal, float(scale))
+    # 64-wide heads: fp32 accumulation buffer for dQ, which turns the backward into one kernel over the tile pairs
+    dq_acc = torch.empty((B, Tq, H, D), dtype=torch.float32, device=q.device) if D == 64 else None
+    _C().attn_bwd(q, k, v, o, d_o, lse, delta, dq, dk, dv, causal, float(scale), dq_acc)
     return dq, dk, dv
 
 
