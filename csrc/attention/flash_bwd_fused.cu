@@ -3,7 +3,7 @@
 //     S  = Q K^T                 dP = dO V^T                                  (tcgen05, fp32 in tensor memory)
 //     P  = exp2(S scale log2e - lse log2e)      dS = P (dP - delta)           (256 softmax threads, 64 columns each)
 //     dV += P^T dO               dK += dS^T Q                                 (accumulated in tensor memory per key tile)
-//     dQ_partial = dS K          -> fp32 atomics into a dQ accumulation buffer (scale folded in)
+//     dQ_partial = dS K          -> TMA reduce-add of fp32 tiles into a dQ accumulation buffer (scale folded in)
 // instead of one kernel that recomputes S / dP for dK, dV and a second one that recomputes them again for dQ.
 //
 // A CTA (one per SM) walks a list of work items; an item is one key tile of one (batch, kv head) and all the query
@@ -55,15 +55,14 @@ struct FusedBwdSmem {
   static constexpr int OFF_DO = OFF_Q + QSTAGES * TILE;
   static constexpr int OFF_P = OFF_DO + QSTAGES * TILE;
   static constexpr int OFF_DS = OFF_P + 2 * ATT_HALF_BYTES;
-  static constexpr int OFF_BAR = OFF_DS + 2 * ATT_HALF_BYTES;
+  static constexpr int OFF_DQ = OFF_DS + 2 * ATT_HALF_BYTES;   // 8 warps x (32 rows x 128 B) fp32 staging for the dQ reduce
+  static constexpr int OFF_BAR = OFF_DQ + 8 * 4096;
   // kv_full, qdo_full[3], qdo_empty[3], s_full[2], dp_full, pds_full, pds_empty, dq_full, dq_drained, done, acc_free
   static constexpr int N_BARS = 16;
   static constexpr int TOTAL = OFF_BAR + N_BARS * 8 + 16;
+  static_assert(TOTAL <= 232448, "attention backward: shared memory over the per-CTA limit");
 };
 
-__device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
 
 // Geometry of one item.
 struct FbItem {
@@ -88,7 +87,7 @@ __device__ __forceinline__ bool fb_item(int k, const AttnBwdFusedParams& p, FbIt
 __global__ void __launch_bounds__(FB_THREADS, 1)
 attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                      const AttnBwdFusedParams p) {
+                      const __grid_constant__ CUtensorMap tmap_dq, const AttnBwdFusedParams p) {
   constexpr int D = FB_D;
   using S = FusedBwdSmem;
   constexpr int QS = S::QSTAGES;
@@ -138,6 +137,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
     tma_prefetch_desc(&tmap_do);
+    tma_prefetch_desc(&tmap_dq);
   }
   if (warp == FB_CTRL_WARP) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -266,8 +266,11 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     uint8_t* sDS = smem + S::OFF_DS;
     bool ok = true;
     uint32_t g_base = 0, items = 0;
-    // dQ_partial of pair g (rows of query tile qi0, head h): this thread owns 32 of the 64 columns of its row
-    auto drain_dq = [&](uint32_t g, int bq, int h, int qi) -> bool {
+    // dQ_partial of pair g (query tile starting at row q0 of head h): each warp owns a 32-row x 32-column block.  It
+    // goes TMEM -> registers -> the warp's own swizzled fp32 staging block -> ONE TMA reduce-add into the accumulation
+    // buffer (full 128-byte lines through the copy engine instead of 32 scattered 16-byte atomics per instruction).
+    uint8_t* dq_stage = smem + S::OFF_DQ + warp * 4096;
+    auto drain_dq = [&](uint32_t g, int bq, int h, int q0) -> bool {
       if (!mbar_wait(dq_full, g & 1, ctl, p.status, RT_ERR_TIMEOUT_SOFTMAX)) return false;
       tc_fence_after();
       uint32_t r[32];
@@ -276,12 +279,19 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(dq_drained);
-      if (qi < p.Tq) {
-        float* dst = p.dq_acc + (((long long)bq * p.Tq + qi) * p.H + h) * D + chalf * 32;
+      if (lane == 0) bulk_wait_group_read<0>();   // the previous reduce of this warp has read the staging block
+      __syncwarp();
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
-          red_add_f32x4(dst + q * 4, __uint_as_float(r[q * 4]) * p.scale, __uint_as_float(r[q * 4 + 1]) * p.scale,
-                        __uint_as_float(r[q * 4 + 2]) * p.scale, __uint_as_float(r[q * 4 + 3]) * p.scale);
+      for (int c = 0; c < 8; ++c) {
+        float4 v4 = make_float4(__uint_as_float(r[c * 4]) * p.scale, __uint_as_float(r[c * 4 + 1]) * p.scale,
+                                __uint_as_float(r[c * 4 + 2]) * p.scale, __uint_as_float(r[c * 4 + 3]) * p.scale);
+        *reinterpret_cast<float4*>(dq_stage + lane * 128 + ((c ^ (lane & 7)) << 4)) = v4;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_reduce_add_4d(&tmap_dq, dq_stage, chalf * 32, q0 + quarter * 32, h, bq);   // rows past Tq are clipped
+        bulk_commit_group();
       }
       return true;
     };
@@ -333,7 +343,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         // dQ_partial of the previous pair (issued first after that pair's staging) is complete by now
         if (it > 0 && !drain_dq(g - 1, itm.b, prev_h, prev_qi)) { ok = false; break; }
         prev_h = h;
-        prev_qi = qi;
+        prev_qi = qi - row;
         if (!mbar_wait(dp_full, g & 1, ctl, p.status, RT_ERR_TIMEOUT_SOFTMAX)) { ok = false; break; }
         tc_fence_after();
         __syncwarp();
@@ -389,6 +399,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   }
 
   __syncwarp();
+  if (warp != FB_CTRL_WARP && lane == 0) bulk_wait_group<0>();   // this warp's dQ reduces have landed
   if (ctl->abort) {
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
   }
@@ -488,6 +499,8 @@ void attn_bwd_fused_d64(const AttnArgs& a, cudaStream_t stream) {
   CUtensorMap tk = make_tmap_2byte_4d(a.k, D, a.Tk, a.Hkv, a.B, a.k_st, a.k_sh, a.k_sb, 64, 128);
   CUtensorMap tv = make_tmap_2byte_4d(a.v, D, a.Tk, a.Hkv, a.B, a.v_st, a.v_sh, a.v_sb, 64, 128);
   CUtensorMap tdo = make_tmap_2byte_4d(a.d_o, D, a.Tq, a.H, a.B, a.o_st, a.o_sh, a.o_sb, 64, 128);
+  // fp32 accumulation buffer [B][Tq][H][64] seen as (d, t, h, b); one reduce covers 32 columns x 32 rows
+  CUtensorMap tdq = make_tmap_f32_4d(a.dq_acc, D, a.Tq, a.H, a.B, uint64_t(a.H) * D, D, uint64_t(a.Tq) * a.H * D, 32, 32);
   AttnBwdFusedParams p{};
   p.B = a.B;
   p.H = a.H;
@@ -513,7 +526,7 @@ void attn_bwd_fused_d64(const AttnArgs& a, cudaStream_t stream) {
   const FbList il = fb_item_list(a, grid, device, stream);
   p.item_list = il.dev;
   p.items_per_cta = il.per_cta;
-  attn_bwd_fused_kernel<<<grid, FB_THREADS, S::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+  attn_bwd_fused_kernel<<<grid, FB_THREADS, S::TOTAL, stream>>>(tq, tk, tv, tdo, tdq, p);
   RT_LAUNCH_CHECK();
   const long long n8 = n_acc / 8;
   attn_dq_convert_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>(a.dq_acc, reinterpret_cast<__nv_bfloat16*>(a.dq), n8, a.H, a.Tq,

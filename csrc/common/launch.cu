@@ -170,6 +170,23 @@ CUtensorMap make_tmap_words_sw128(const void* base, uint64_t row_bytes, uint64_t
   return m;
 }
 
+CUtensorMap make_tmap_f32_4d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t s1, uint64_t s2,
+                             uint64_t s3, uint32_t b0, uint32_t b1) {
+  RT_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base must be 16-byte aligned");
+  RT_CHECK((s1 * 4) % 16 == 0 && (s2 * 4) % 16 == 0 && (s3 * 4) % 16 == 0, "TMA strides must be multiples of 16 bytes");
+  RT_CHECK(b0 * 4 == 128 && b1 >= 1 && b1 <= 256, "fp32 swizzled TMA box: 32 elements (128 bytes) wide, at most 256 rows");
+  CUtensorMap m;
+  cuuint64_t dims[4] = {d0, d1, d2, d3};
+  cuuint64_t strides[3] = {s1 * 4, s2 * 4, s3 * 4};
+  cuuint32_t box[4] = {b0, b1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  RT_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(f32 4d) failed with code " + std::to_string(int(r)));
+  return m;
+}
+
 CUtensorMap make_tmap_nhwc(const void* base, uint64_t C, uint64_t W, uint64_t H, uint64_t N, uint32_t box_w, uint32_t box_h,
                            uint32_t box_n, uint32_t stride) {
   RT_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base must be 16-byte aligned");

@@ -56,6 +56,10 @@ CUtensorMap make_tmap_2byte(const void* base, uint64_t d0, uint64_t d1, uint64_t
 CUtensorMap make_tmap_2byte_4d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                                uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3, uint32_t b0,
                                uint32_t b1);
+// Rank-4 fp32 map [d3][d2][d1][d0] (strides in elements) with the 128-byte swizzle: box = 32 floats x b1 rows.  Used for
+// TMA reduce-add (cp.reduce.async.bulk.tensor ... .add) of fp32 tiles staged in shared memory.
+CUtensorMap make_tmap_f32_4d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t s1, uint64_t s2,
+                             uint64_t s3, uint32_t b0, uint32_t b1);
 // Plain (unswizzled) rank-2 map over rows of `row_bytes` bytes seen as 32-bit words (elem_bytes = 4) or
 // 16-bit values (elem_bytes = 2): dims {row_elems, rows}, box {box_elems, box_rows}; out-of-range parts of a
 // box read as zero.  row_bytes must be a multiple of 16.
