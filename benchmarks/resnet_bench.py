@@ -6,7 +6,8 @@
 Input 3x224x224 i.i.d. N(0,1), labels uniform in [0, 1000), per-GPU batch 256, SGD momentum 0.9 lr 0.1 wd 1e-4.
 ``ours``: channels-last bf16 model on this framework's kernels: implicit-GEMM tcgen05 convolutions (forward, weight
 gradient, stride-1 input gradient; the 3-channel stem and the strided input gradients use the library), BatchNorm
-(+ residual + ReLU fused), fused flat SGD and bucketed DDP.  ``library``: the same topology from stock ``torch.nn``
+(+ residual + ReLU fused), fused flat SGD; on more than one GPU the fused data-parallel bucket kernel (reduce + SGD
+momentum + parameter broadcast over peer memory, overlapped with backward).  ``library``: the same topology from stock ``torch.nn``
 modules + ``torch.optim.SGD`` + PyTorch DDP.  Prints one JSON line: images/s of the whole job, device time,
 max over ranks.
 """
@@ -69,22 +70,30 @@ def main():
     if a.impl == "ours":
         model = model.to(torch.bfloat16)
         from rustorch_b200.optim.flat import FlatParams, FusedSGD
-        flat = FlatParams(model, decay_filter=lambda n, p: p.dim() > 1)
-        opt = FusedSGD(flat, lr=0.1, momentum=0.9, weight_decay=1e-4)
-        ddp = None
         if world > 1:
-            from rustorch_b200.distributed.ddp_flat import FlatDDP
-            ddp = FlatDDP(flat, bucket_cap_mb=25.0)
+            # one fused kernel per 25 MB bucket: reduce over NVLink (NVLS where available) + SGD momentum + parameter
+            # broadcast, launched from gradient hooks while backward is still running
+            from rustorch_b200.distributed.fused_allreduce import FusedDDPSGD
+            ddp = FusedDDPSGD(model, lr=0.1, momentum=0.9, weight_decay=1e-4, bucket_cap_mb=25.0,
+                              decay_filter=lambda n, p: p.dim() > 1)
 
-        def step():
-            out = model(x)
-            loss = F.cross_entropy(out.float(), y)
-            loss.backward()
-            flat.collect_autograd_grads()
-            if ddp is not None:
-                ddp.sync_gradients()
-            opt.step()
-            return loss
+            def step():
+                out = model(x)
+                loss = F.cross_entropy(out.float(), y)
+                loss.backward()
+                ddp.step()
+                return loss
+        else:
+            flat = FlatParams(model, decay_filter=lambda n, p: p.dim() > 1)
+            opt = FusedSGD(flat, lr=0.1, momentum=0.9, weight_decay=1e-4)
+
+            def step():
+                out = model(x)
+                loss = F.cross_entropy(out.float(), y)
+                loss.backward()
+                flat.collect_autograd_grads()
+                opt.step()
+                return loss
     else:
         model = model.to(torch.bfloat16)
         opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)

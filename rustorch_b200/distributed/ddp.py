@@ -12,8 +12,11 @@ hooks (ddp.rs:139-172).  This one is real:
 * ``sync_gradients()`` waits for the outstanding reductions (and reduces anything whose hook did not
   fire, e.g. unused parameters when ``find_unused_parameters``).
 
-The flat-buffer bf16 path with the fused peer-memory kernel is
-:class:`rustorch_b200.distributed.fused_allreduce.FusedDDPAdamW`.
+``DistributedDataParallel(module, fused_optimizer={...})`` takes the flat-buffer bf16 path instead: gradient
+reduction, scaling, the optimizer rule (AdamW / Adam / SGD with momentum) and the parameter broadcast run as one
+peer-memory kernel per bucket, overlapped with backward
+(:class:`rustorch_b200.distributed.fused_allreduce.FusedDDP`); ``step()`` then replaces the separate
+``sync_gradients()`` + ``optimizer.step()``.
 """
 from __future__ import annotations
 
@@ -58,11 +61,26 @@ class DistributedDataParallel(nn.Module):
     def __init__(self, module: nn.Module, device_ids: Optional[Sequence[int]] = None, output_device: Optional[int] = None,
                  dim: int = 0, broadcast_buffers: bool = True, process_group: Optional[api.ProcessGroup] = None,
                  bucket_cap_mb: float = 25.0, find_unused_parameters: bool = False, check_reduction: bool = False,
-                 gradient_as_bucket_view: bool = False, static_graph: bool = False):
+                 gradient_as_bucket_view: bool = False, static_graph: bool = False, fused_optimizer: Optional[dict] = None):
         super().__init__()
         if not dist.is_initialized():
             raise RuntimeError("DistributedDataParallel needs init_process_group() first")
         self.module = module
+        self.fused = None
+        if fused_optimizer is not None:
+            # bf16 parameters on a GPU (or, for tests of the bookkeeping, on the CPU over gloo): one fused kernel per
+            # gradient bucket does the all-reduce, the optimizer step and the parameter broadcast
+            from .fused_allreduce import FusedDDP
+            self.device_ids, self.output_device, self.dim = device_ids, output_device, dim
+            self.broadcast_buffers, self.bucket_cap_mb = broadcast_buffers, bucket_cap_mb
+            self._group = None if process_group is None else process_group.handle
+            self.world_size = dist.get_world_size(self._group)
+            for b in module.buffers():
+                dist.broadcast(b.data, 0, group=self._group)
+            self.fused = FusedDDP(module, bucket_cap_mb=bucket_cap_mb, process_group=self._group, **fused_optimizer)
+            self.buckets, self._hooks = [], []
+            self.require_backward_grad_sync = True
+            return
         self.device_ids, self.output_device, self.dim = device_ids, output_device, dim
         self.broadcast_buffers, self.bucket_cap_mb = broadcast_buffers, bucket_cap_mb
         self.find_unused_parameters, self.static_graph = find_unused_parameters, static_graph
@@ -104,8 +122,17 @@ class DistributedDataParallel(nn.Module):
         if b.pending == 0 and b.work is None:
             self._launch(b)
 
+    def step(self) -> None:
+        """Fused mode only: finish the data-parallel optimizer step for the gradients of the last backward."""
+        if self.fused is None:
+            raise RuntimeError("step() belongs to the fused mode; pass fused_optimizer={...} or use an optimizer with sync_gradients()")
+        self.fused.step()
+
     def sync_gradients(self) -> None:
-        """Block until every bucket is averaged and written back into ``.grad``."""
+        """Block until every bucket is averaged and written back into ``.grad`` (a no-op in fused mode, where the
+        reduction is part of ``step()``)."""
+        if self.fused is not None:
+            return
         for b in self.buckets:
             if b.work is None:
                 if not self.find_unused_parameters and any(p.grad is None for p in b.params) \

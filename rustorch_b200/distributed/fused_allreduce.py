@@ -177,6 +177,11 @@ class FusedDDP:
         self._comm = None if self.host else torch.cuda.Stream(device=dev, priority=-1)
         self._in_step = False
         fused.grad_ready_hook = self._on_grads_ready
+        # Parameters of ordinary autograd modules (convolutions, BatchNorm, ...) get their gradient in ``.grad``: a
+        # post-accumulate hook folds it into the flat fp32 buffer at once and reports the parameter as ready, so their
+        # buckets overlap with the rest of backward too.  Parameters of the fused Functions never see the hook fire.
+        self._ag_hooks = [p.register_post_accumulate_grad_hook(self._on_autograd_grad) for _, p, _, _ in f.entries]
+        self._entry_of = {id(p): (o, n) for _, p, o, n in f.entries}
         if W > 1:
             dist.barrier(group=self.group)
         if not self.host:
@@ -248,6 +253,15 @@ class FusedDDP:
             f.lp[s:e].copy_(torch.cat(parts))
         else:
             f.lp[s:e].copy_(mine)
+
+    def _on_autograd_grad(self, p) -> None:
+        if p.grad is None:
+            return
+        o, n = self._entry_of[id(p)]
+        g = p.grad.permute(0, 2, 3, 1) if getattr(p, "_flat_ohwi", False) else p.grad
+        self.flat.grad[o:o + n].add_(g.reshape(-1))
+        p.grad = None
+        self._on_grads_ready([p])
 
     def _on_grads_ready(self, params) -> None:
         if not self.overlap:
@@ -342,6 +356,9 @@ class FusedDDP:
     def close(self) -> None:
         if fused.grad_ready_hook == self._on_grads_ready:
             fused.grad_ready_hook = None
+        for h in getattr(self, "_ag_hooks", []):
+            h.remove()
+        self._ag_hooks = []
 
 
 class FusedDDPAdamW(FusedDDP):

@@ -56,7 +56,22 @@ def main():
     model = GPT(cfg, device=dev, dtype=torch.bfloat16, seed=3)
     losses = []
     nvls_used = False
-    if mode.startswith("fused"):
+    if mode == "public":
+        # the public wrapper in fused mode: forward through the wrapper, step() instead of sync_gradients + optimizer
+        from rustorch_b200.distributed.ddp import DistributedDataParallel
+        wrap = DistributedDataParallel(model, bucket_cap_mb=1.0, fused_optimizer=dict(optimizer="adamw", timeout_s=10.0, **hp))
+        for s in range(steps):
+            b = data[s, rank]
+            loss = wrap(b[:, :-1], b[:, 1:])
+            loss.backward()
+            wrap.step()
+            losses.append(float(loss))
+        _native.check_status()
+        got = wrap.fused.flat.named_views(wrap.fused.gather_master())
+        n_buckets = wrap.fused.n_buckets
+        nvls_used = wrap.fused.nvls
+        wrap.fused.close()
+    elif mode.startswith("fused"):
         # "fused" / "fused_sgd": plain peer loads and stores; "fused_nvls" / "fused_nvls_sgd": multimem through the switch
         kw = dict(bucket_cap_mb=1.0, timeout_s=10.0, use_nvls="nvls" in mode, **hp)
         ddp = FusedDDPSGD(model, **kw) if sgd else FusedDDPAdamW(model, **kw)

@@ -22,7 +22,7 @@ def _free_port():
 def _run(mode, nproc):
     out_dir = tempfile.mkdtemp(prefix="ddp_res_")
     env = dict(os.environ, DDP_RESULT_DIR=out_dir)
-    if "nvls" not in mode:
+    if "nvls" not in mode and mode != "public":
         env["NCCL_NVLS_ENABLE"] = "0"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
@@ -33,7 +33,7 @@ def _run(mode, nproc):
     return res
 
 
-@pytest.mark.parametrize("mode", ["fused", "fused_nvls", "fused_sgd", "fused_nvls_sgd", "nccl"])
+@pytest.mark.parametrize("mode", ["fused", "fused_nvls", "fused_sgd", "fused_nvls_sgd", "public", "nccl"])
 def test_ddp_matches_big_batch(mode):
     """Every variant of the fused bucket step (peer loads or switch-side multimem reduction; AdamW or SGD with
     momentum) follows the single-GPU big-batch run.  SGD is linear in the gradient, so its parameters must agree to
