@@ -11,8 +11,15 @@ wd 0.1, init N(0, 0.02), synthetic uniform random tokens, random-init weights.
 Prints one JSON line on rank 0.  ``value`` is device-timed (CUDA events, max over ranks) with
 the step's tokens already resident on the GPU; ``e2e`` repeats the measurement through the
 public API with, every step, a host->device copy of that step's tokens from pinned memory
-and a device->host read of the loss.  ``--impl reference`` reports that the reference (a Rust
-workspace; no cargo/rustc/maturin on this machine) cannot be installed.
+and a device->host read of the loss.  After its own timed region the ``ours`` arm also times the
+library arm (the same model through stock PyTorch: cuBLAS, SDPA, ``torch.optim.AdamW(fused=True)``,
+NCCL DDP) in the same process on the same batches; ``vs_baseline`` is ours / library, the bar the
+baseline document names because the reference publishes no number for this metric.
+``--impl reference`` looks for an installed reference (``baseline/_ref``) or a Rust toolchain to
+build it and reports ``unavailable`` with what it found.
+
+``--config resnet_ddp | llama_tp | gguf_decode`` runs the other headline configurations from
+``benchmarks/`` through the same entry point (same launch line, one JSON line each).
 """
 from __future__ import annotations
 
@@ -28,22 +35,79 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "library"])
     ap.add_argument("--batch", type=int, default=16, help="per-GPU batch (sequences)")
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=12)
     ap.add_argument("--ddp-mode", default=os.environ.get("RUSTORCH_DDP_MODE", "auto"))
-    return ap.parse_args()
+    ap.add_argument("--config", default="gpt2_ddp", choices=["gpt2_ddp", "resnet_ddp", "llama_tp", "gguf_decode"])
+    ap.add_argument("--no-library-arm", action="store_true", help="skip the in-process library timing (vs_baseline stays null)")
+    ap.add_argument("--library-steps", type=int, default=0, help="timed steps of the library arm (0: as many as --steps, at most 20)")
+    return ap.parse_known_args()
+
+
+def probe_reference() -> dict:
+    """What could run the reference here: an installed copy under baseline/_ref, or a Rust toolchain to build one."""
+    import importlib.util
+    import shutil
+    root = os.path.dirname(os.path.abspath(__file__))
+    ref_dir = os.path.join(root, "baseline", "_ref")
+    found = {"baseline/_ref": os.path.isdir(ref_dir) and bool(os.listdir(ref_dir)) if os.path.isdir(ref_dir) else False,
+             "cargo": shutil.which("cargo"), "rustc": shutil.which("rustc"), "maturin": shutil.which("maturin"),
+             "maturin_module": importlib.util.find_spec("maturin") is not None}
+    importable = False
+    if found["baseline/_ref"]:
+        sys.path.insert(0, ref_dir)
+        try:
+            spec = importlib.util.find_spec("rustorch")
+            importable = spec is not None and spec.origin is not None and ref_dir in os.path.abspath(spec.origin)
+        except Exception:  # noqa: BLE001
+            importable = False
+        finally:
+            sys.path.remove(ref_dir)
+    found["rustorch_importable_from_ref"] = importable
+    return found
+
+
+def run_other_config(args, rest) -> int:
+    """resnet_ddp / llama_tp / gguf_decode: hand over to the benchmark module with the driver's steps and warm-up."""
+    import runpy
+    root = os.path.dirname(os.path.abspath(__file__))
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "config": args.config, "unavailable": reference_unavailable_reason()}))
+        return 0
+    script = {"resnet_ddp": "resnet_bench.py", "llama_tp": "llama_tp_bench.py", "gguf_decode": "decode_bench.py"}[args.config]
+    argv = [os.path.join(root, "benchmarks", script)]
+    if args.config == "gguf_decode":
+        argv += ["--tp", str(args.gpus)]
+    else:
+        argv += ["--steps", str(args.steps), "--warmup", str(args.warmup)]
+        if args.config == "resnet_ddp":
+            argv += ["--impl", "library" if args.impl == "library" else "ours"]
+    sys.argv = argv + list(rest)
+    runpy.run_path(argv[0], run_name="__main__")
+    return 0
+
+
+def reference_unavailable_reason() -> str:
+    f = probe_reference()
+    if f["rustorch_importable_from_ref"]:
+        return ("baseline/_ref holds an importable rustorch, but its Python surface has no GPT training step to time "
+                "(tensors live in host memory; no transformer backward)")
+    have = [k for k in ("cargo", "rustc", "maturin") if f[k]] + (["maturin (module)"] if f["maturin_module"] else [])
+    return ("reference is a Rust/PyO3 workspace (no setup.py / pyproject at its root; python/ builds with maturin): "
+            f"baseline/_ref {'present but not importable' if f['baseline/_ref'] else 'absent'}, "
+            f"toolchain found: {', '.join(have) if have else 'none of cargo / rustc / maturin'}")
 
 
 def main():
-    args = parse()
+    args, rest = parse()
+    if args.config != "gpt2_ddp":
+        return run_other_config(args, rest)
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference",
-                          "unavailable": "reference is a Rust/PyO3 workspace: pip install needs maturin + "
-                                         "cargo/rustc, none present offline (no setup.py/pyproject at its root)"}))
+        print(json.dumps({"impl": "reference", "unavailable": reference_unavailable_reason()}))
         return 0
 
     import torch
@@ -69,26 +133,27 @@ def main():
     B, T = args.batch, args.seq
     library = args.impl == "library"
 
-    if library:
-        # Library baseline arm: the same model through stock PyTorch kernels (cuBLAS / SDPA /
-        # torch.optim fused AdamW / NCCL DDP).  Not the product; kept for comparison.
-        model = GPT(cfg, device=dev, dtype=torch.bfloat16, seed=1234)
-        opt = torch.optim.AdamW(model.parameters(), lr=6e-4, betas=(0.9, 0.95), weight_decay=0.1,
-                                fused=True)
-        fwd = model.forward_reference
+    def make_library_step():
+        """Library baseline arm: the same model through stock PyTorch kernels (cuBLAS / SDPA / torch.optim fused
+        AdamW / NCCL DDP).  Not the product; the bar it is compared with."""
+        lib_model = GPT(cfg, device=dev, dtype=torch.bfloat16, seed=1234)
+        lib_opt = torch.optim.AdamW(lib_model.parameters(), lr=6e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+        fwd = lib_model.forward_reference
         if world > 1:
-            ddp = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank],
-                                                            bucket_cap_mb=25)
-            _orig = model.forward
-            model.forward = model.forward_reference
-            fwd = ddp
+            lib_ddp = torch.nn.parallel.DistributedDataParallel(lib_model, device_ids=[local_rank], bucket_cap_mb=25)
+            lib_model.forward = lib_model.forward_reference
+            fwd = lib_ddp
 
-        def train_step(idx, tgt):
+        def lib_step(idx, tgt):
             loss = fwd(idx, tgt)
             loss.backward()
-            opt.step()
-            opt.zero_grad(set_to_none=True)
+            lib_opt.step()
+            lib_opt.zero_grad(set_to_none=True)
             return loss
+        return lib_step
+
+    if library:
+        train_step = make_library_step()
     else:
         model = GPT(cfg, device=dev, dtype=torch.bfloat16, seed=1234)
         from rustorch_b200.distributed.ddp_flat import FlatDDP
@@ -175,6 +240,25 @@ def main():
     ms_e2e, _ = timed(step_e2e, args.steps)
     _native.check_status()
 
+    baseline = None
+    if not library and not args.no_library_arm:
+        # the library arm on the same batches, in this process, after our own timed regions
+        if ddp is not None and hasattr(ddp, "close"):
+            ddp.close()
+        lib_step = make_library_step()
+        lib_steps = args.library_steps or min(args.steps, 20)
+
+        def step_library(i):
+            b = dev_batches[i % n_host]
+            lib_step(b[:, :-1], b[:, 1:])
+        for i in range(max(3, min(args.warmup, 5))):
+            step_library(i)
+        ms_lib, _ = timed(step_library, lib_steps)
+        baseline = {"kind": "library arm: stock PyTorch (cuBLAS, SDPA, torch.optim.AdamW(fused=True), NCCL DDP), eager, "
+                            "same model / batches / process", "steps": lib_steps,
+                    "ms_per_step": round(ms_lib / lib_steps, 3),
+                    "value": round(B * T * world * lib_steps / (ms_lib / 1e3), 1)}
+
     tokens = B * T * world * args.steps
     value = tokens / (ms / 1e3)
     e2e_value = tokens / (ms_e2e / 1e3)
@@ -182,7 +266,7 @@ def main():
         "metric": "train_tokens_per_s", "value": round(value, 1), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform random tokens, random-init weights",
+        "vs_baseline": (round(value / baseline["value"], 4) if baseline else None), "baseline": baseline, "dtype": "bf16", "data": "synthetic uniform random tokens, random-init weights",
         "impl": args.impl,
         "config": {"model": "gpt2-small (12L, d768, 12h, mlp3072, learned pos-emb, untied lm_head, dropout 0)",
                    "layers": args.layers, "global_batch": B * world, "per_gpu_batch": B, "seq_len": T,
