@@ -295,6 +295,21 @@ void p2p_collective(const P2PCollArgs& a, cudaStream_t stream);
 // conv/im2col.cu: patch matrix [N*OH*OW][k_pad] of a channels-last bf16 image (rows zero-padded to k_pad)
 void im2col_nhwc(const void* x, void* col, int N, int H, int W, int C, int OH, int OW, int KH, int KW, int stride, int pad, int k_pad,
                  cudaStream_t s);
+// conv/unfold_nd.cu: patch gather / scatter for 1-3 D convolutions with stride, padding, dilation and groups on
+// channels-last bf16 tensors; col is [groups][N*OD*OH*OW][k_pad] with k_pad >= KD*KH*KW*(C/groups), a multiple of 8.
+struct UnfoldArgs {
+  const void* x_in = nullptr;  // unused alias kept zero; x below is read by unfold_nd and written by fold_nd
+  void* x;
+  void* col;
+  int N, D, H, W, C;
+  int OD, OH, OW;
+  int KD, KH, KW;
+  int stride[3], pad[3], dilation[3];
+  int groups;
+  int k_pad;
+};
+void unfold_nd(const UnfoldArgs& a, cudaStream_t s);
+void fold_nd(const UnfoldArgs& a, cudaStream_t s);
 // ------------------------------------------------------------ nn/pool_dropout.cu
 // Channels-last pooling.  Forward: x [N][H][W][C] -> y [N][OH][OW][C] (+ idx for max).  Backward: y holds dy, x receives dx.
 struct Pool2dArgs {

@@ -75,6 +75,30 @@ void ddp_bucket_step(const std::vector<int64_t>& grad_ptrs, const std::vector<in
   rt::ddp_bucket_step(a, int(n_ctas), cur_stream(master.device().index()));
 }
 
+// x: channels-last bf16 [N, D, H, W, C] (contiguous), col: bf16 [groups, N*OD*OH*OW, k_pad].  fold = false gathers patches
+// from x into col; fold = true sums col back into x.
+void unfold_nd(Tensor& x, Tensor& col, std::vector<int64_t> out_size, std::vector<int64_t> kernel, std::vector<int64_t> stride,
+               std::vector<int64_t> pad, std::vector<int64_t> dilation, int64_t groups, bool fold) {
+  TORCH_CHECK(x.is_cuda() && col.is_cuda() && x.scalar_type() == at::kBFloat16 && col.scalar_type() == at::kBFloat16,
+              "unfold_nd: bf16 CUDA tensors required");
+  TORCH_CHECK(x.dim() == 5 && x.is_contiguous() && col.dim() == 3 && col.is_contiguous(), "unfold_nd: x [N, D, H, W, C], col [G, M, k_pad]");
+  TORCH_CHECK(out_size.size() == 3 && kernel.size() == 3 && stride.size() == 3 && pad.size() == 3 && dilation.size() == 3,
+              "unfold_nd: three values per geometry list");
+  rt::UnfoldArgs a{};
+  a.x = x.data_ptr();
+  a.col = col.data_ptr();
+  a.N = int(x.size(0)); a.D = int(x.size(1)); a.H = int(x.size(2)); a.W = int(x.size(3)); a.C = int(x.size(4));
+  a.OD = int(out_size[0]); a.OH = int(out_size[1]); a.OW = int(out_size[2]);
+  a.KD = int(kernel[0]); a.KH = int(kernel[1]); a.KW = int(kernel[2]);
+  for (int i = 0; i < 3; ++i) { a.stride[i] = int(stride[i]); a.pad[i] = int(pad[i]); a.dilation[i] = int(dilation[i]); }
+  a.groups = int(groups);
+  a.k_pad = int(col.size(2));
+  TORCH_CHECK(col.size(0) == groups && col.size(1) == int64_t(a.N) * a.OD * a.OH * a.OW, "unfold_nd: col must be [groups, N*OD*OH*OW, k_pad]");
+  c10::cuda::CUDAGuard guard(x.device());
+  if (fold) rt::fold_nd(a, cur_stream(x.device().index()));
+  else rt::unfold_nd(a, cur_stream(x.device().index()));
+}
+
 // int8 GEMM: a [M, K] s8, b [N, K] s8 -> out int32 [M, N] (no scales) or fp32 [M, N] (scales given).
 void gemm_i8(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Tensor>& row_scale,
              const c10::optional<Tensor>& col_scale, const c10::optional<Tensor>& bias) {
@@ -959,6 +983,7 @@ void register_extra_ops(pybind11::module_& m) {
         "fused reduce-scatter + scale + AdamW / Adam / SGD + all-gather of one gradient bucket over peer memory "
         "(plain peer loads / stores, or NVLS multimem when the multicast pointers are non-zero)");
   m.def("ddp_wait_end", &ddp_wait_end);
+  m.def("unfold_nd", &unfold_nd, "patch gather (fold = false) / scatter-sum (fold = true) for 1-3 D convolutions with groups and dilation");
   m.def("gemm_i8", &gemm_i8, "int8 x int8 -> int32 tcgen05 GEMM, optional fused dequantisation to fp32", py::arg("a"), py::arg("b"),
         py::arg("out"), py::arg("row_scale") = py::none(), py::arg("col_scale") = py::none(), py::arg("bias") = py::none());
   m.def("multi_tensor_optim", &multi_tensor_optim,

@@ -3,7 +3,7 @@
 //   start barrier (flags in peer memory)                         "bucket gradients are final on every rank"
 //   for the 1/N shard of the bucket this rank owns:
 //     g  = (1/N) * sum over ranks of grad_rank[i]                 P2P loads, or ONE multimem.ld_reduce (NVLS)
-//     peers' and own grad[i] = 0                                 P2P stores, or one multimem.st
+//     own grad[i] = 0                                            local (each rank zeroes the rest of its buffer itself after the step)
 //     AdamW / Adam / SGD-momentum(master, m, v, g)               fp32, local
 //     every rank's bf16 parameter copy[i] = bf16(master[i])      P2P stores, or one multimem.st
 //   end signal (flags in peer memory)                            "my writes into your buffers are done"
@@ -73,11 +73,6 @@ __device__ __forceinline__ float4 mc_ld_reduce_f4(const float* mc) {
                : "l"(mc)
                : "memory");
   return v;
-}
-__device__ __forceinline__ void mc_st_f4(float* mc, const float4& v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z),
-               "f"(v.w)
-               : "memory");
 }
 __device__ __forceinline__ void mc_st_b32x2(void* mc, uint32_t lo, uint32_t hi) {
   asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(mc), "f"(__uint_as_float(lo)),
@@ -161,19 +156,20 @@ __global__ void __launch_bounds__(256, 2) ddp_bucket_step_kernel(const DdpBucket
     for (int g = 0; g < G; ++g) {
       if (!on[g]) continue;
       float4 sum;
+      // Gradients are zeroed for the next backward pass: this rank's copy here, the peers' copies by their owners
+      // after the end-of-step wait (a local memset instead of N - 1 remote stores per element).
       if (NVLS) {
         sum = v[g][0];
-        mc_st_f4(a.mc_grad + e[g], z);
       } else {
         sum = z;
 #pragma unroll
         for (int p = 0; p < WMAX; ++p) {
           if (p < W) {
             sum.x += v[g][p].x; sum.y += v[g][p].y; sum.z += v[g][p].z; sum.w += v[g][p].w;
-            *reinterpret_cast<float4*>(a.grad[p] + e[g]) = z;
           }
         }
       }
+      *reinterpret_cast<float4*>(a.grad[R] + e[g]) = z;
       float4 pm = *reinterpret_cast<float4*>(a.master + e[g]);
       float4 m = has_m ? *reinterpret_cast<float4*>(a.m + e[g]) : z;
       float4 vv = has_v ? *reinterpret_cast<float4*>(a.v + e[g]) : z;

@@ -294,6 +294,9 @@ class FusedDDP:
             with torch.cuda.stream(self._comm):
                 C.ddp_wait_end(self.flags.data_ptr() + 4 * self.n_buckets * W, self.n_buckets, W, self.rank,
                                self.step_count + 1, self.timeout_s, self.device.index or 0)
+                # every peer has read its slices of this rank's gradients: clear them for the next backward pass
+                # (the kernels only zero the slice their own rank owns)
+                self.flat.grad.zero_()
         torch.cuda.current_stream(self.device).wait_stream(self._comm)
         self.step_count += 1
         self._pending = list(self._bucket_need)

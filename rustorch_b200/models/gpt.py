@@ -137,17 +137,31 @@ class GPT(nn.Module):
         if not self._native_ok(idx):
             return self.forward_reference(idx, targets)
         c = self.cfg
-        if self.training and c.dropout > 0:
-            raise NotImplementedError(
-                "the fused GPT path runs without dropout; build the model with dropout=0.0")
         B, T = idx.shape
         assert T <= c.n_positions, "sequence longer than n_positions"
         x = fused.EmbeddingFn.apply(idx, self.wte, self.wpe)
-        for b in self.blocks:
-            x = fused.AttnBlockFn.apply(x, b.ln1_w, b.ln1_b, b.w_qkv, b.b_qkv, b.w_proj, b.b_proj,
-                                        c.n_head, c.layer_norm_eps, True)
-            x = fused.MLPBlockFn.apply(x, b.ln2_w, b.ln2_b, b.w_fc, b.b_fc, b.w_fc2, b.b_fc2,
-                                       c.layer_norm_eps)
+        p_drop = c.dropout if self.training else 0.0
+        if p_drop > 0.0:
+            # Dropout (reference default 0.1, src/models/transformer_models.rs:727-738) on the embeddings and on both
+            # residual branches: the blocks return their branch alone, the Philox dropout kernel (mask regenerated in
+            # backward) and the elementwise add kernel finish ``x + dropout(branch)``.  The flash kernel has no dropout
+            # on the attention probabilities.
+            from ..ops import elementwise as E
+            from ..ops.pool import dropout as native_dropout
+            x = native_dropout(x, p_drop, True)
+            for b in self.blocks:
+                br = fused.AttnBlockFn.apply(x, b.ln1_w, b.ln1_b, b.w_qkv, b.b_qkv, b.w_proj, b.b_proj,
+                                             c.n_head, c.layer_norm_eps, True, False)
+                x = E.add(x, native_dropout(br, p_drop, True))
+                br = fused.MLPBlockFn.apply(x, b.ln2_w, b.ln2_b, b.w_fc, b.b_fc, b.w_fc2, b.b_fc2,
+                                            c.layer_norm_eps, False)
+                x = E.add(x, native_dropout(br, p_drop, True))
+        else:
+            for b in self.blocks:
+                x = fused.AttnBlockFn.apply(x, b.ln1_w, b.ln1_b, b.w_qkv, b.b_qkv, b.w_proj, b.b_proj,
+                                            c.n_head, c.layer_norm_eps, True)
+                x = fused.MLPBlockFn.apply(x, b.ln2_w, b.ln2_b, b.w_fc, b.b_fc, b.w_fc2, b.b_fc2,
+                                           c.layer_norm_eps)
         if targets is not None:
             return fused.LMHeadLossFn.apply(x, self.lnf_w, self.lnf_b, self.lm_head, targets,
                                             c.vocab_size, c.layer_norm_eps, -100)

@@ -103,7 +103,7 @@ class AttnBlockFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, ln_w, ln_b, w_qkv, b_qkv, w_proj, b_proj, n_head: int, eps: float,
-                causal: bool):
+                causal: bool, residual: bool = True):
         B, T, C = x.shape
         D = C // n_head
         x2 = x.reshape(B * T, C)
@@ -112,15 +112,16 @@ class AttnBlockFn(torch.autograd.Function):
         qkv5 = qkv.view(B, T, 3, n_head, D)
         o, lse = K.attention_fwd(qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2], causal)
         o2 = o.view(B * T, C)
-        y = K.gemm(o2, w_proj, bias=b_proj, aux=x2, epilogue=K.EPI_RESIDUAL)
+        # residual=False returns the branch alone (the caller applies dropout to it before the residual add)
+        y = K.gemm(o2, w_proj, bias=b_proj, aux=x2, epilogue=K.EPI_RESIDUAL) if residual else K.gemm(o2, w_proj, bias=b_proj)
         ctx.save_for_backward(x2, ln_w, ln_b, w_qkv, b_qkv, w_proj, b_proj, mean, rstd, h, qkv, o, lse)
-        ctx.meta = (B, T, C, n_head, causal)
+        ctx.meta = (B, T, C, n_head, causal, residual)
         return y.view(B, T, C)
 
     @staticmethod
     def backward(ctx, dy):
         x2, ln_w, ln_b, w_qkv, b_qkv, w_proj, b_proj, mean, rstd, h, qkv, o, lse = ctx.saved_tensors
-        B, T, C, n_head, causal = ctx.meta
+        B, T, C, n_head, causal, residual = ctx.meta
         D = C // n_head
         dy2 = dy.contiguous().view(B * T, C)
         o2 = o.view(B * T, C)
@@ -136,32 +137,32 @@ class AttnBlockFn(torch.autograd.Function):
         g_bqkv = bgrad_into(dqkv, b_qkv)
         dh = K.gemm(dqkv, w_qkv, b_mn=True)                      # [B*T, C]
         wg, bg, direct = _norm_grad_bufs(ln_w, ln_b)
-        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dy2)
+        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dy2 if residual else None)
         g_lnw = None if direct else wg.to(ln_w.dtype)
         g_lnb = None if (direct or ln_b is None) else bg.to(ln_b.dtype)
         _notify(w_proj, b_proj, w_qkv, b_qkv, ln_w, ln_b)
-        return (dx.view(B, T, C), g_lnw, g_lnb, g_wqkv, g_bqkv, g_wproj, g_bproj, None, None, None)
+        return (dx.view(B, T, C), g_lnw, g_lnb, g_wqkv, g_bqkv, g_wproj, g_bproj, None, None, None, None)
 
 
 class MLPBlockFn(torch.autograd.Function):
     """y = x + fc2(gelu(fc1(norm(x))))  (tanh GELU as in the reference, src/nn/activation.rs:206-217)."""
 
     @staticmethod
-    def forward(ctx, x, ln_w, ln_b, w1, b1, w2, b2, eps: float):
+    def forward(ctx, x, ln_w, ln_b, w1, b1, w2, b2, eps: float, residual: bool = True):
         B, T, C = x.shape
         x2 = x.reshape(B * T, C)
         h, mean, rstd = K.layer_norm_fwd(x2, ln_w, ln_b, eps)
         pre = torch.empty((B * T, w1.shape[0]), dtype=torch.bfloat16, device=x.device)
         act = K.gemm(h, w1, bias=b1, aux=pre, epilogue=K.EPI_GELU_DUAL)
-        y = K.gemm(act, w2, bias=b2, aux=x2, epilogue=K.EPI_RESIDUAL)
+        y = K.gemm(act, w2, bias=b2, aux=x2, epilogue=K.EPI_RESIDUAL) if residual else K.gemm(act, w2, bias=b2)
         ctx.save_for_backward(x2, ln_w, ln_b, w1, b1, w2, b2, mean, rstd, h, pre, act)
-        ctx.meta = (B, T, C)
+        ctx.meta = (B, T, C, residual)
         return y.view(B, T, C)
 
     @staticmethod
     def backward(ctx, dy):
         x2, ln_w, ln_b, w1, b1, w2, b2, mean, rstd, h, pre, act = ctx.saved_tensors
-        B, T, C = ctx.meta
+        B, T, C, residual = ctx.meta
         dy2 = dy.contiguous().view(B * T, C)
         g_w2 = wgrad_into(dy2, act, w2)
         g_b2 = bgrad_into(dy2, b2)
@@ -170,11 +171,11 @@ class MLPBlockFn(torch.autograd.Function):
         g_b1 = bgrad_into(dpre, b1)
         dh = K.gemm(dpre, w1, b_mn=True)
         wg, bg, direct = _norm_grad_bufs(ln_w, ln_b)
-        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dy2)
+        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dy2 if residual else None)
         g_lnw = None if direct else wg.to(ln_w.dtype)
         g_lnb = None if (direct or ln_b is None) else bg.to(ln_b.dtype)
         _notify(w2, b2, w1, b1, ln_w, ln_b)
-        return (dx.view(B, T, C), g_lnw, g_lnb, g_w1, g_b1, g_w2, g_b2, None)
+        return (dx.view(B, T, C), g_lnw, g_lnb, g_w1, g_b1, g_w2, g_b2, None, None)
 
 
 class EmbeddingFn(torch.autograd.Function):
@@ -322,3 +323,63 @@ class FlashAttentionFn(torch.autograd.Function):
         causal, scale = ctx.meta
         dq, dk, dv = K.attention_bwd(q, k, v, o, do.contiguous(), lse, causal, scale)
         return dq, dk, dv, None, None
+
+
+class BmmNTFn(torch.autograd.Function):
+    """``c[b] = alpha * a[b] @ bt[b]^T`` with a [b, M, K], bt [b, N, K] on the batched tcgen05 GEMM."""
+
+    @staticmethod
+    def forward(ctx, a, bt, alpha: float):
+        a, bt = a.contiguous(), bt.contiguous()
+        ctx.save_for_backward(a, bt)
+        ctx.alpha = alpha
+        return K.gemm(a, bt, alpha=alpha)
+
+    @staticmethod
+    def backward(ctx, dc):
+        a, bt = ctx.saved_tensors
+        dc = dc.contiguous()
+        da = K.gemm(dc, bt, b_mn=True, alpha=ctx.alpha) if ctx.needs_input_grad[0] else None            # dc [M,N] @ bt [N,K]
+        dbt = K.gemm(dc, a, a_mn=True, b_mn=True, alpha=ctx.alpha) if ctx.needs_input_grad[1] else None  # dc^T [N,M] @ a [M,K]
+        return da, dbt, None
+
+
+class BmmNNFn(torch.autograd.Function):
+    """``c[b] = a[b] @ b[b]`` with a [b, M, K], b [b, K, N] on the batched tcgen05 GEMM (no transposed copies)."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        a, b = a.contiguous(), b.contiguous()
+        ctx.save_for_backward(a, b)
+        return K.gemm(a, b, b_mn=True)
+
+    @staticmethod
+    def backward(ctx, dc):
+        a, b = ctx.saved_tensors
+        dc = dc.contiguous()
+        da = K.gemm(dc, b) if ctx.needs_input_grad[0] else None                                 # dc [M,N] . b [K,N]^T
+        db = K.gemm(a, dc, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None           # a^T [K,M] @ dc [M,N]
+        return da, db
+
+
+def materialized_attention(q, k, v, bias: Optional[torch.Tensor], p_drop: float, scale: Optional[float] = None):
+    """Attention with an explicit probability matrix, for the cases the flash kernels do not take (additive masks,
+    key-padding masks, dropout on the probabilities, returning the weights): batched tcgen05 GEMM for ``q k^T``, the
+    native row-softmax and Philox dropout kernels, and a second batched GEMM for ``p v``.  q [B, Tq, H, D], k / v
+    [B, Tk, H, D] bf16, ``bias`` broadcastable to [B, H, Tq, Tk] (0 = keep, large negative = masked).
+    Returns ``(o [B, Tq, H, D], probabilities [B, H, Tq, Tk])``.  Tq, Tk and D must be multiples of 8."""
+    from ..ops import elementwise as E
+    from ..ops.pool import dropout as native_dropout
+    B, Tq, H, D = q.shape
+    Tk = k.shape[1]
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    qb = q.transpose(1, 2).reshape(B * H, Tq, D)
+    kb = k.transpose(1, 2).reshape(B * H, Tk, D)
+    vb = v.transpose(1, 2).reshape(B * H, Tk, D)
+    s = BmmNTFn.apply(qb, kb, scale)                                         # [BH, Tq, Tk]
+    if bias is not None:
+        s = E.add(s, bias.to(s.dtype).expand(B, H, Tq, Tk).reshape(B * H, Tq, Tk).contiguous())
+    w = E.softmax(s, -1)
+    wd = native_dropout(w, p_drop, True) if p_drop > 0.0 else w
+    o = BmmNNFn.apply(wd, vb)                                                # [BH, Tq, D]
+    return o.view(B, H, Tq, D).transpose(1, 2), w.view(B, H, Tq, Tk)

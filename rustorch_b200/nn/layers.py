@@ -127,6 +127,11 @@ class Conv3d(_ConvNd):
     """``(in, out, kernel(d,h,w), stride, padding, dilation, groups, bias)`` (src/nn/conv3d.rs:74-90)."""
     _fn, _nd = staticmethod(F.conv3d), 3
 
+    def forward(self, x):
+        """bf16 CUDA tensors: patch gather + tcgen05 GEMM per group (+ patch scatter backward), csrc/conv/unfold_nd.cu."""
+        from ..ops.conv_nd import conv_nd
+        return conv_nd(x, self.weight, self.bias, self.stride, self.padding, self.dilation, self.groups)
+
 
 class _ConvTransposeNd(nn.Module):
     _fn = None
@@ -147,8 +152,9 @@ class _ConvTransposeNd(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_channels, **kw)) if bias else None
 
     def forward(self, x):
-        return type(self)._fn(x, self.weight, self.bias, self.stride, self.padding, self.output_padding,
-                              self.groups, self.dilation)
+        """bf16 CUDA tensors: GEMM + patch scatter (the input-gradient form of a convolution), csrc/conv/unfold_nd.cu."""
+        from ..ops.conv_nd import conv_transpose_nd
+        return conv_transpose_nd(x, self.weight, self.bias, self.stride, self.padding, self.output_padding, self.groups, self.dilation)
 
 
 class ConvTranspose1d(_ConvTransposeNd):

@@ -10,8 +10,11 @@ masked out (the reference adds -1e9 there, :469-481).
 
 The reference's batch matmul returns a constant 0.1 tensor (:378-418) and its older module
 softmaxes over the whole tensor (src/nn/attention.rs:362-384); this implementation computes
-real attention.  With bf16 CUDA inputs, no explicit masks (or a causal mask) and
-``need_weights=False`` it runs the hand-written tcgen05 flash-attention kernels.
+real attention.  With bf16 CUDA inputs, no explicit masks (or a causal mask), no dropout and
+``need_weights=False`` it runs the hand-written tcgen05 flash-attention kernels; with masks, a key-padding mask,
+dropout on the probabilities or ``need_weights=True`` it runs the same math with an explicit probability matrix on
+the batched tcgen05 GEMM and the native softmax / dropout kernels (``fused.materialized_attention``).  Only CPU
+tensors and other dtypes take the PyTorch expression.
 """
 from __future__ import annotations
 
@@ -60,6 +63,24 @@ class MultiheadAttention(nn.Module):
             return (F.linear(query, w[:E], bs[0]), F.linear(key, w[E:2 * E], bs[1]), F.linear(value, w[2 * E:], bs[2]))
         return self.w_q(query), self.w_k(key), self.w_v(value)
 
+    @staticmethod
+    def _mask_bias(attn_mask, key_padding_mask, is_causal: bool, B: int, Tq: int, Tk: int, like: torch.Tensor):
+        """Additive bias [*, *, Tq, Tk] from the masks (reference convention: 0 / False = masked out, -1e9 added there)."""
+        bias = None
+        if attn_mask is not None:
+            bias = torch.zeros(attn_mask.shape, dtype=like.dtype, device=like.device).masked_fill(attn_mask == 0, -1e9)
+            while bias.dim() < 4:
+                bias = bias.unsqueeze(0)
+        if key_padding_mask is not None:
+            kp = torch.zeros(B, 1, 1, Tk, dtype=like.dtype, device=like.device).masked_fill(
+                (key_padding_mask == 0).view(B, 1, 1, Tk), -1e9)
+            bias = kp if bias is None else bias + kp
+        if is_causal:
+            causal = torch.ones(Tq, Tk, dtype=torch.bool, device=like.device).tril(Tk - Tq)
+            cb = torch.zeros(Tq, Tk, dtype=like.dtype, device=like.device).masked_fill(~causal, -1e9)
+            bias = cb if bias is None else bias + cb
+        return bias
+
     def forward(self, query, key=None, value=None, key_padding_mask: Optional[torch.Tensor] = None,
                 need_weights: bool = True, attn_mask: Optional[torch.Tensor] = None,
                 average_attn_weights: bool = True, is_causal: bool = False):
@@ -76,8 +97,15 @@ class MultiheadAttention(nn.Module):
         native = (q.is_cuda and q.dtype == torch.bfloat16 and not need_weights and key_padding_mask is None
                   and attn_mask is None and p_drop == 0.0 and D in (64, 128))
         weights = None
+        own = (q.is_cuda and q.dtype == torch.bfloat16 and D % 8 == 0 and Tq % 8 == 0 and Tk % 8 == 0
+               and fused.K._native.available())
         if native:
             o = fused.FlashAttentionFn.apply(q.contiguous(), k.contiguous(), v.contiguous(), is_causal, None)
+        elif own:
+            bias = self._mask_bias(attn_mask, key_padding_mask, is_causal, B, Tq, Tk, q)
+            o, w = fused.materialized_attention(q, k, v, bias, p_drop)
+            if need_weights:
+                weights = w.mean(1) if average_attn_weights else w
         else:
             qh, kh, vh = (t.transpose(1, 2) for t in (q, k, v))            # [B,H,T,D]
             bias = None

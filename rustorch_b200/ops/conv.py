@@ -5,6 +5,8 @@ Tensors are channels-last: an NCHW tensor in ``torch.channels_last`` memory form
 Forward and the weight gradient always use the native kernels when the layer qualifies (Cin % 64 == 0, Cout % 8 == 0,
 groups 1, dilation 1, square stride / padding); the input gradient does for stride 1 (it is the forward kernel on ``dy``
 with the filter rotated and its channel axes swapped) and falls back to the library for strided layers.
+Layers these kernels do not cover (groups, dilation, other channel counts) go to :mod:`rustorch_b200.ops.conv_nd`
+(patch gather + tcgen05 GEMM + patch scatter).
 """
 from __future__ import annotations
 
@@ -197,7 +199,8 @@ def conv2d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if supported(x, weight, stride, padding, dilation, groups):
         s = stride if isinstance(stride, int) else stride[0]
         return Conv2dFn.apply(x, weight, bias, s, _pads(padding))
-    return F.conv2d(x, weight, bias, stride, padding, dilation, groups)
+    from .conv_nd import conv_nd      # groups, dilation, other channel counts: unfold + tcgen05 GEMM (library on the CPU)
+    return conv_nd(x, weight, bias, stride, padding, dilation, groups)
 
 
 def _one(v) -> int:
@@ -211,7 +214,8 @@ def conv1d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
             and supported(x.unsqueeze(2), weight.unsqueeze(2), _one(stride), (0, _one(padding)))):
         y = Conv2dFn.apply(x.unsqueeze(2), weight.unsqueeze(2), bias, _one(stride), (0, _one(padding)))
         return y.squeeze(2)
-    return F.conv1d(x, weight, bias, stride, padding, dilation, groups)
+    from .conv_nd import conv_nd
+    return conv_nd(x, weight, bias, stride, padding, dilation, groups)
 
 
 class ConvTranspose2dFn(torch.autograd.Function):
@@ -277,4 +281,5 @@ def conv_transpose2d(x, weight, bias=None, stride=1, padding=0, output_padding=0
         except RuntimeError as e:
             if "not covered" not in str(e):
                 raise
-    return F.conv_transpose2d(x, weight, bias, stride, padding, output_padding, groups, dilation)
+    from .conv_nd import conv_transpose_nd
+    return conv_transpose_nd(x, weight, bias, stride, padding, output_padding, groups, dilation)

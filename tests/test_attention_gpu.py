@@ -67,3 +67,44 @@ def test_attention_strided_qkv_views():
     o, _ = K_.attention_fwd(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], True)
     ref = _ref_attn(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], True)
     assert rel_err(o, ref) < 2e-2
+
+
+def test_multihead_attention_masks_weights_dropout_on_native_kernels():
+    """Masks, key-padding masks, need_weights and dropout take the batched tcgen05 GEMM + native softmax / dropout
+    kernels (not SDPA / eager): values and gradients against the fp32 PyTorch expression of the same module."""
+    from rustorch_b200 import _native
+    from rustorch_b200 import nn as rnn
+    torch.manual_seed(0)
+    B, T, E, H = 3, 64, 128, 4
+    mha = rnn.MultiheadAttention(E, H).cuda().bfloat16()
+    ref = rnn.MultiheadAttention(E, H).cuda().float()
+    ref.load_state_dict({k: v.float() for k, v in mha.state_dict().items()})
+    x = torch.randn(B, T, E, device="cuda").bfloat16()
+    attn_mask = (torch.rand(T, T, device="cuda") > 0.3).float()
+    attn_mask.fill_diagonal_(1.0)
+    kpm = torch.ones(B, T, device="cuda")
+    kpm[:, 50:] = 0
+    x1, x2 = x.clone().requires_grad_(True), x.float().requires_grad_(True)
+    n0 = _native.launch_count()
+    o1, w1 = mha(x1, x1, x1, key_padding_mask=kpm, need_weights=True, attn_mask=attn_mask)
+    assert _native.launch_count() - n0 >= 5, "native kernels not used"
+    o2, w2 = ref(x2, x2, x2, key_padding_mask=kpm, need_weights=True, attn_mask=attn_mask)
+    assert rel_err(o1, o2) < 3e-2 and rel_err(w1, w2) < 3e-2
+    assert float(w1[:, :, 50:].abs().max()) < 1e-6                         # padded keys get no weight
+    g = torch.randn_like(o2)
+    (o1.float() * g).sum().backward()
+    (o2 * g).sum().backward()
+    assert rel_err(x1.grad, x2.grad) < 5e-2
+    for (k1, p1), (_, p2) in zip(sorted(mha.named_parameters()), sorted(ref.named_parameters())):
+        assert rel_err(p1.grad, p2.grad) < 5e-2, k1
+    # dropout on the probabilities: native Philox kernel, expectation preserved, eval mode deterministic
+    drop = rnn.MultiheadAttention(E, H, dropout=0.5).cuda().bfloat16()
+    drop.train()
+    n0 = _native.launch_count()
+    a, _ = drop(x, need_weights=False)
+    b, _ = drop(x, need_weights=False)
+    assert _native.launch_count() > n0 and not torch.equal(a, b)
+    drop.eval()
+    c, _ = drop(x, need_weights=False)
+    d, _ = drop(x, need_weights=False)
+    assert torch.equal(c, d)

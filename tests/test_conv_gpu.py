@@ -4,6 +4,7 @@ import torch
 import torch.nn.functional as F
 
 from conftest import rel_err
+from rustorch_b200 import _native
 
 pytestmark = pytest.mark.gpu
 
@@ -125,3 +126,82 @@ def test_conv_transpose2d_native(K, s, p, op):
     for got, ref in ((y, yr), (gx, rx), (gw, rw)):
         assert got.shape == ref.shape
         assert rel_err(got.float().cpu(), ref) < 2e-2
+
+
+# ---------------------------------------------------------------- generic N-d path: unfold + tcgen05 GEMM + fold
+def _conv_nd_case(nd, cin, cout, k, stride, pad, dil, groups, size, seed=0):
+    from rustorch_b200.ops import conv_nd as CN
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn((2, cin) + (size,) * nd, device="cuda", generator=g).bfloat16()
+    w = (torch.randn((cout, cin // groups) + (k,) * nd, device="cuda", generator=g) * 0.2).bfloat16()
+    b = torch.randn(cout, device="cuda", generator=g).bfloat16()
+    xs = [x.clone().requires_grad_(True), x.float().requires_grad_(True)]
+    ws = [w.clone().requires_grad_(True), w.float().requires_grad_(True)]
+    bs = [b.clone().requires_grad_(True), b.float().requires_grad_(True)]
+    n0 = _native.launch_count()
+    y = CN.conv_nd(xs[0], ws[0], bs[0], stride, pad, dil, groups)
+    assert _native.launch_count() > n0, "native path not taken"
+    ref = (F.conv1d, F.conv2d, F.conv3d)[nd - 1](xs[1], ws[1], bs[1], stride, pad, dil, groups)
+    assert y.shape == ref.shape
+    assert rel_err(y, ref) < 2e-2
+    dy = torch.randn(ref.shape, device="cuda", generator=g)
+    y.backward(dy.bfloat16())
+    ref.backward(dy.bfloat16().float())
+    assert rel_err(xs[0].grad, xs[1].grad) < 3e-2
+    assert rel_err(ws[0].grad, ws[1].grad) < 3e-2
+    assert rel_err(bs[0].grad, bs[1].grad) < 3e-2
+
+
+@pytest.mark.parametrize("nd,cin,cout,k,stride,pad,dil,groups,size", [
+    (3, 16, 32, 3, 1, 1, 1, 1, 9),          # Conv3d
+    (3, 16, 24, 3, 2, 1, 2, 4, 11),         # Conv3d with stride, dilation and groups (the reference kernel's feature set)
+    (2, 24, 48, 3, 1, 2, 2, 3, 14),         # dilated grouped Conv2d
+    (2, 12, 12, 3, 1, 1, 1, 12, 10),        # depthwise Conv2d (one channel per group)
+    (1, 8, 20, 5, 2, 3, 1, 2, 33),          # grouped Conv1d, channel counts that are not multiples of 8
+    (2, 3, 10, 2, 1, 0, 1, 1, 7),           # tiny channel counts, even kernel
+])
+def test_conv_nd_unfold_gemm_path(nd, cin, cout, k, stride, pad, dil, groups, size):
+    _conv_nd_case(nd, cin, cout, k, stride, pad, dil, groups, size)
+
+
+@pytest.mark.parametrize("nd,cin,cout,k,stride,pad,opad,dil,groups,size", [
+    (1, 16, 24, 4, 2, 1, 0, 1, 1, 17),      # ConvTranspose1d
+    (3, 8, 16, 3, 2, 1, 1, 1, 2, 5),        # ConvTranspose3d with groups and output padding
+    (2, 12, 8, 3, 1, 0, 0, 2, 4, 9),        # dilated grouped ConvTranspose2d
+])
+def test_conv_transpose_nd_path(nd, cin, cout, k, stride, pad, opad, dil, groups, size):
+    from rustorch_b200.ops import conv_nd as CN
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn((2, cin) + (size,) * nd, device="cuda", generator=g).bfloat16()
+    w = (torch.randn((cin, cout // groups) + (k,) * nd, device="cuda", generator=g) * 0.2).bfloat16()
+    b = torch.randn(cout, device="cuda", generator=g).bfloat16()
+    xs = [x.clone().requires_grad_(True), x.float().requires_grad_(True)]
+    ws = [w.clone().requires_grad_(True), w.float().requires_grad_(True)]
+    bs = [b.clone().requires_grad_(True), b.float().requires_grad_(True)]
+    n0 = _native.launch_count()
+    y = CN.conv_transpose_nd(xs[0], ws[0], bs[0], stride, pad, opad, groups, dil)
+    assert _native.launch_count() > n0
+    ref = (F.conv_transpose1d, F.conv_transpose2d, F.conv_transpose3d)[nd - 1](xs[1], ws[1], bs[1], stride, pad, opad, groups, dil)
+    assert y.shape == ref.shape and rel_err(y, ref) < 2e-2
+    dy = torch.randn(ref.shape, device="cuda", generator=g)
+    y.backward(dy.bfloat16())
+    ref.backward(dy.bfloat16().float())
+    assert rel_err(xs[0].grad, xs[1].grad) < 3e-2 and rel_err(ws[0].grad, ws[1].grad) < 3e-2 and rel_err(bs[0].grad, bs[1].grad) < 3e-2
+
+
+def test_conv3d_and_transpose_layers_use_the_native_path():
+    from rustorch_b200 import nn as rnn
+    torch.manual_seed(0)
+    layer = rnn.Conv3d(8, 16, (3, 3, 3), stride=1, padding=1, dilation=1, groups=2).cuda().bfloat16()
+    x = torch.randn(2, 8, 6, 6, 6, device="cuda").bfloat16()
+    n0 = _native.launch_count()
+    y = layer(x)
+    assert _native.launch_count() > n0
+    ref = F.conv3d(x.float(), layer.weight.float(), layer.bias.float(), 1, 1, 1, 2)
+    assert rel_err(y, ref) < 2e-2
+    up = rnn.ConvTranspose1d(8, 8, 4, stride=2, padding=1).cuda().bfloat16()
+    z = torch.randn(2, 8, 10, device="cuda").bfloat16()
+    n0 = _native.launch_count()
+    out = up(z)
+    assert _native.launch_count() > n0 and out.shape == (2, 8, 20)
+    assert rel_err(out, F.conv_transpose1d(z.float(), up.weight.float(), up.bias.float(), 2, 1)) < 2e-2
