@@ -383,3 +383,28 @@ def materialized_attention(q, k, v, bias: Optional[torch.Tensor], p_drop: float,
     wd = native_dropout(w, p_drop, True) if p_drop > 0.0 else w
     o = BmmNNFn.apply(wd, vb)                                                # [BH, Tq, D]
     return o.view(B, H, Tq, D).transpose(1, 2), w.view(B, H, Tq, Tk)
+
+
+class LinearF16Fn(torch.autograd.Function):
+    """``y = x W^T + b`` for fp16 tensors on the tcgen05 GEMM: fp16 operands, fp32 accumulation and output, cast back
+    to fp16 (forward, input gradient and weight gradient read the same row-major tensors; no transposed copies)."""
+
+    @staticmethod
+    def forward(ctx, x, w, b):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        y = K.gemm(x2, w, out_dtype=torch.float32)
+        if b is not None:
+            y = y + b.float()
+        ctx.save_for_backward(x2, w)
+        ctx.meta = (x.shape, b is not None)
+        return y.to(torch.float16).view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        xshape, has_b = ctx.meta
+        dy2 = dy.reshape(-1, w.shape[0]).contiguous()
+        dx = K.gemm(dy2, w, b_mn=True, out_dtype=torch.float32).to(torch.float16).view(xshape) if ctx.needs_input_grad[0] else None
+        gw = K.gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32).to(torch.float16) if ctx.needs_input_grad[1] else None
+        gb = dy2.float().sum(0).to(torch.float16) if (has_b and ctx.needs_input_grad[2]) else None
+        return dx, gw, gb

@@ -64,8 +64,11 @@ class Linear(nn.Module):
         return cls(input_size, output_size, bias=False, **kw)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if _native(x, self.weight, self.bias) and self.input_size % 8 == 0 and self.output_size % 8 == 0:
-            return fused.LinearFn.apply(x, self.weight, self.bias)
+        if self.input_size % 8 == 0 and self.output_size % 8 == 0 and x.is_cuda:
+            if _native(x, self.weight, self.bias):
+                return fused.LinearFn.apply(x, self.weight, self.bias)
+            if x.dtype == torch.float16 and self.weight.dtype == torch.float16 and fused.K._native.available():
+                return fused.LinearF16Fn.apply(x, self.weight, self.bias)      # fp16 operands, fp32 accumulation
         return F.linear(x, self.weight, self.bias)
 
 

@@ -86,3 +86,56 @@ def test_gemm_large_persistent():
     a, b = _mk((4096, 1024), 13), _mk((4096, 1024), 14)
     out = K_.gemm(a, b)
     assert rel_err(out, a.float() @ b.float().t()) < 1.5e-2
+
+
+def test_fp16_linear_layer_runs_on_the_native_gemm():
+    from rustorch_b200 import _native
+    from rustorch_b200 import nn as rnn
+    torch.manual_seed(0)
+    lin = rnn.Linear(136, 72).cuda().half()
+    x = torch.randn(5, 33, 136, device="cuda").half()
+    x1, x2 = x.clone().requires_grad_(True), x.float().requires_grad_(True)
+    n0 = _native.launch_count()
+    y = lin(x1)
+    assert _native.launch_count() > n0 and y.dtype == torch.float16
+    ref = torch.nn.functional.linear(x2, lin.weight.detach().float(), lin.bias.detach().float())
+    assert rel_err(y, ref) < 5e-3
+    g = torch.randn_like(ref)
+    y.backward(g.half())
+    ref.backward(g.half().float())
+    assert rel_err(x1.grad, x2.grad) < 5e-3
+    w32 = lin.weight.float().detach().requires_grad_(True)
+    torch.nn.functional.linear(x.float(), w32, lin.bias.detach().float()).backward(g.half().float())
+    assert rel_err(lin.weight.grad, w32.grad) < 5e-3
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,Kd", [(256, 256, 64), (1000, 520, 200), (392, 2304, 768)])
+def test_cta_pair_gemm_matches_fp32_reference(monkeypatch, M, N, Kd, a_mn, b_mn):
+    """256 x 256 tiles over two CTAs (cta_group::2), forced on for every layout, ragged M / N / K tails included."""
+    monkeypatch.setenv("RUSTORCH_GEMM_PAIR", "1")
+    from rustorch_b200 import _native
+    from rustorch_b200.ops import kernels as K
+    torch.manual_seed(1)
+    a = torch.randn((Kd, M) if a_mn else (M, Kd), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((Kd, N) if b_mn else (N, Kd), device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    out = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias)
+    _native.check_status()
+    af = a.float().t() if a_mn else a.float()
+    bf = b.float() if b_mn else b.float().t()
+    assert rel_err(out, af @ bf + bias.float()) < 1.5e-2
+
+
+def test_cta_pair_gemm_split_k_and_batch(monkeypatch):
+    monkeypatch.setenv("RUSTORCH_GEMM_PAIR", "1")
+    from rustorch_b200.ops import kernels as K
+    torch.manual_seed(2)
+    a = torch.randn(8192, 512, device="cuda", dtype=torch.bfloat16)   # [K][M]
+    b = torch.randn(8192, 768, device="cuda", dtype=torch.bfloat16)   # [K][N]
+    acc = torch.zeros(512, 768, device="cuda")
+    K.gemm(a, b, a_mn=True, b_mn=True, out=acc, accumulate=True, split_k=4)
+    assert rel_err(acc, a.float().t() @ b.float()) < 2e-3
+    x = torch.randn(3, 300, 256, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(3, 512, 256, device="cuda", dtype=torch.bfloat16)
+    assert rel_err(K.gemm(x, w), x.float() @ w.float().transpose(1, 2)) < 1.5e-2
