@@ -190,11 +190,15 @@ def bench_qgemv(a):
     from rustorch_b200.formats import gguf
     from rustorch_b200.llm import QuantLinear
     C = _native.load(required=True)
-    for (N, Kd) in [(12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008), (32000, 4096)]:
+    shapes = [(12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008), (32000, 4096)]
+    rows = (1, 4)
+    if getattr(a, "qshape", ""):
+        shapes, rows = [tuple(int(v) for v in a.qshape.split(","))], (1,)
+    for (N, Kd) in shapes:
         nbytes = N * Kd // 32 * 18
         copies = max(2, -(-300_000_000 // nbytes))
         mats = [QuantLinear.random(N, Kd, gguf.GGMLType.Q4_0, 0.02, "cuda", seed=i) for i in range(copies)]
-        for M in (1, 4):
+        for M in rows:
             x = (torch.randn(M, Kd, device="cuda") * 0.5).half()
             y = torch.empty(M, N, device="cuda", dtype=torch.half)
             for reg in (True, False):
@@ -204,6 +208,17 @@ def bench_qgemv(a):
                 best, med = time_op(run, a.iters, flush=False)
                 report(f"q4_gemv_{'register' if reg else 'bulk'}_m{M}_{N}x{Kd}", best / copies, med / copies, bytes_=float(nbytes),
                        extra=f"mean over {copies} distinct matrices per timed region")
+            # the decode kernel: RMSNorm prologue + int8-activation dp4a GEMV (+ SwiGLU epilogue on the gate/up shape)
+            nw = torch.ones(Kd, device="cuda", dtype=torch.half)
+            sw = N == 22016
+            yf = torch.empty(M, N // 2 if sw else N, device="cuda", dtype=torch.half)
+
+            def run_fused():
+                for q in mats:
+                    C.q_gemv_fused(q.qs, q.scales, x, yf, nw, 1e-5, None, False, sw)
+            best, med = time_op(run_fused, a.iters, flush=False)
+            report(f"q4_gemv_fused_norm{'_swiglu' if sw else ''}_m{M}_{N}x{Kd}", best / copies, med / copies, bytes_=float(nbytes),
+                   extra=f"mean over {copies} distinct matrices per timed region")
         del mats
 
 
@@ -292,6 +307,7 @@ def main():
     ap.add_argument("--non-causal", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--compare", action="store_true", help="also time the stock PyTorch op")
+    ap.add_argument("--qshape", default="", help="qgemv: only this N,K (e.g. 12288,4096), one activation row: a small case for a profiler capture")
     a = ap.parse_args()
     torch.cuda.set_device(0)
     if a.op == "gemm":

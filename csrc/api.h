@@ -408,6 +408,29 @@ void q_gemv(const QGemvArgs& a, cudaStream_t stream);
 bool q_gemv_bulk_supported(const QGemvArgs& a);
 bool q_gemv_bulk_preferred(const QGemvArgs& a);  // shape heuristic from measurements
 void q_gemv_bulk(const QGemvArgs& a, cudaStream_t stream);
+// quant/q_gemv_fused.cu: decode projection in one kernel: optional RMSNorm of x, GEMV, residual or SwiGLU epilogue.
+struct QGemvFusedArgs {
+  const void* qs;
+  const void* scales;
+  const void* x;       // fp16 [M][ldx]
+  long long ldx;
+  const void* norm_w;  // fp16 [K] RMSNorm weight applied to x first, or null
+  float eps;
+  void* y;             // fp16 [M][ldy]; swiglu: N / 2 columns
+  long long ldy;
+  const void* residual;  // fp16 [M][ldr] or null
+  long long ldr;
+  int M, N, K;         // N weight rows (swiglu: gate rows then up rows)
+  bool q8;
+  bool swiglu;
+  // two byte ranges (the next projection's nibbles and scales) to pull towards L2 meanwhile, or null
+  const void* prefetch0 = nullptr;
+  long long prefetch0_bytes = 0;
+  const void* prefetch1 = nullptr;
+  long long prefetch1_bytes = 0;
+};
+bool q_gemv_fused_supported(int M, int N, int K, bool swiglu);
+void q_gemv_fused(const QGemvFusedArgs& a, cudaStream_t stream);
 // quant/q_gemm_tc.cu: dequant-fused tcgen05 GEMM for 1 <= M <= 256 rows (weights read once whatever M is).
 bool q_gemm_tc_supported(int M, int N, int K);
 void q_gemm_tc_scratch(int M, int N, int K, bool q8, int sms, long long* partial_floats, int* counters, int* splits_out);
@@ -444,6 +467,7 @@ struct AttnCacheArgs {
   float scale;
   // split-KV path only: fp32 scratch [n_tok][H][n_split][D + 2] (unused when n_split == 1)
   float* partial = nullptr;
+  int* counters = nullptr;  // [n_tok * Hkv] zeros (n_split > 1); every call leaves them zero
   int n_split = 1;
 };
 void attn_cache_f16(const AttnCacheArgs& a, cudaStream_t s);

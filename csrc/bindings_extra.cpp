@@ -4,6 +4,9 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <map>
+#include <mutex>
+
 #include <cstring>
 
 #include "api.h"
@@ -250,6 +253,55 @@ void q_gemv(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, 
   rt::q_gemv(a, cur_stream(x.device().index()));
 }
 
+// y = epilogue(dequant(W) @ rmsnorm(x)); norm_w / residual optional; swiglu: W = [gate; up], y has N / 2 columns.
+void q_gemv_fused(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, const c10::optional<Tensor>& norm_w, double eps,
+                  const c10::optional<Tensor>& residual, bool q8, bool swiglu, const c10::optional<Tensor>& prefetch_qs,
+                  const c10::optional<Tensor>& prefetch_scales) {
+  check_f16(scales, "q_gemv_fused scales");
+  check_f16(x, "q_gemv_fused x");
+  check_f16(y, "q_gemv_fused y");
+  TORCH_CHECK(qs.is_cuda() && qs.is_contiguous() && scales.is_contiguous() && scales.dim() == 2, "q_gemv_fused: contiguous CUDA weights required");
+  TORCH_CHECK(x.dim() == 2 && y.dim() == 2 && x.stride(1) == 1 && y.stride(1) == 1, "q_gemv_fused: x [M, K], y [M, N]");
+  rt::QGemvFusedArgs a{};
+  a.M = int(x.size(0));
+  a.K = int(x.size(1));
+  a.N = int(scales.size(0));
+  a.q8 = q8;
+  a.swiglu = swiglu;
+  TORCH_CHECK(scales.size(1) * 32 == a.K, "q_gemv_fused: scales do not match K");
+  TORCH_CHECK(y.size(0) == a.M && y.size(1) == (swiglu ? a.N / 2 : a.N), "q_gemv_fused: bad output shape");
+  TORCH_CHECK(qs.numel() * qs.element_size() == (int64_t)a.N * (a.K / 32) * (q8 ? 32 : 16), "q_gemv_fused: qs size mismatch");
+  TORCH_CHECK(rt::q_gemv_fused_supported(a.M, a.N, a.K, swiglu), "q_gemv_fused: unsupported shape");
+  a.qs = qs.data_ptr();
+  a.scales = scales.data_ptr();
+  a.x = x.data_ptr();
+  a.ldx = x.stride(0);
+  a.y = y.data_ptr();
+  a.ldy = y.stride(0);
+  a.eps = float(eps);
+  if (norm_w.has_value()) {
+    check_f16(*norm_w, "q_gemv_fused norm weight");
+    TORCH_CHECK(norm_w->is_contiguous() && norm_w->numel() == a.K, "q_gemv_fused: norm weight must be [K]");
+    a.norm_w = norm_w->data_ptr();
+  }
+  if (residual.has_value()) {
+    check_f16(*residual, "q_gemv_fused residual");
+    TORCH_CHECK(residual->dim() == 2 && residual->size(0) == a.M && residual->size(1) == a.N && residual->stride(1) == 1, "q_gemv_fused: bad residual");
+    a.residual = residual->data_ptr();
+    a.ldr = residual->stride(0);
+  }
+  if (prefetch_qs.has_value() && prefetch_qs->is_cuda() && prefetch_qs->is_contiguous()) {
+    a.prefetch0 = prefetch_qs->data_ptr();
+    a.prefetch0_bytes = prefetch_qs->numel() * prefetch_qs->element_size();
+  }
+  if (prefetch_scales.has_value() && prefetch_scales->is_cuda() && prefetch_scales->is_contiguous()) {
+    a.prefetch1 = prefetch_scales->data_ptr();
+    a.prefetch1_bytes = prefetch_scales->numel() * prefetch_scales->element_size();
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  rt::q_gemv_fused(a, cur_stream(x.device().index()));
+}
+
 // (fp32 words of split-K scratch, counters, splits) for a shape on the current device
 std::vector<int64_t> q_gemm_tc_scratch(int64_t M, int64_t N, int64_t K, bool q8) {
   long long pf; int nc, sp;
@@ -358,6 +410,15 @@ void attn_cache(const Tensor& q, const Tensor& cache_k, const Tensor& cache_v, T
     if (a.n_split > 1) {
       part = at::empty({int64_t(a.n_tok) * a.H * a.n_split * (a.D + 2)}, q.options().dtype(at::kFloat));
       a.partial = part.data_ptr<float>();
+      // arrival counters of the in-kernel merge: one zeroed buffer per device, re-armed by the kernel itself
+      static std::mutex mu;
+      // (outgrown buffers stay alive: a captured CUDA graph may still point at them)
+      static std::map<int, std::vector<Tensor>> counters;
+      std::lock_guard<std::mutex> lock(mu);
+      std::vector<Tensor>& cs = counters[q.device().index()];
+      const int64_t need = int64_t(a.n_tok) * a.Hkv;
+      if (cs.empty() || cs.back().numel() < need) cs.push_back(at::zeros({std::max<int64_t>(need, 4096)}, q.options().dtype(at::kInt)));
+      a.counters = cs.back().data_ptr<int>();
     }
     rt::attn_decode_split(a, cur_stream(q.device().index()));
     return;
@@ -970,6 +1031,10 @@ void register_extra_ops(pybind11::module_& m) {
   m.def("q_gemv", &q_gemv, "dequant-fused Q4_0 / Q8_0 matrix-vector product", pybind11::arg("qs"), pybind11::arg("scales"),
         pybind11::arg("x"), pybind11::arg("y"), pybind11::arg("bias"), pybind11::arg("residual"), pybind11::arg("q8"),
         pybind11::arg("path") = 0);
+  m.def("q_gemv_fused", &q_gemv_fused, "decode projection: RMSNorm prologue + dequant-fused GEMV + residual / SwiGLU epilogue",
+        pybind11::arg("qs"), pybind11::arg("scales"), pybind11::arg("x"), pybind11::arg("y"), pybind11::arg("norm_w"), pybind11::arg("eps"),
+        pybind11::arg("residual"), pybind11::arg("q8"), pybind11::arg("swiglu") = false, pybind11::arg("prefetch_qs") = pybind11::none(),
+        pybind11::arg("prefetch_scales") = pybind11::none());
   m.def("q_gemm_tc", &q_gemm_tc, "dequant-fused Q4_0 / Q8_0 tcgen05 GEMM for up to 256 activation rows", pybind11::arg("qs"),
         pybind11::arg("scales"), pybind11::arg("x"), pybind11::arg("y"), pybind11::arg("bias"), pybind11::arg("residual"),
         pybind11::arg("q8"), pybind11::arg("partial"), pybind11::arg("counters"), pybind11::arg("path") = 0);

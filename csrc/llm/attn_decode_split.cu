@@ -4,8 +4,9 @@
 //
 // A decode step has only batch x heads independent rows, far fewer than 148 SMs can hide HBM latency
 // with, so the key range of every (token, kv head) is cut into `n_split` slices handled by separate CTAs
-// (grid = tokens x kv heads x slices) and a second small kernel merges the slices' (max, sum, acc)
-// triples.  Inside a CTA a key row of D halves is read by D/8 lanes with one 16-byte load each, so a warp
+// (grid = tokens x kv heads x slices); the slices' (max, sum, acc) triples meet in a global scratch and the CTA
+// that arrives last at a per-(token, kv head) counter merges them and re-arms the counter, so the step is one
+// launch.  Inside a CTA a key row of D halves is read by D/8 lanes with one 16-byte load each, so a warp
 // covers 32/(D/8) keys per step and keeps UN steps of K and V loads in flight; all G = H/Hkv query heads
 // that share the kv head are served from the same K/V registers (grouped-query attention reads the cache
 // once).  Each (warp, key slot) keeps its own running softmax state, merged once at the end: no
@@ -26,7 +27,7 @@ namespace rt {
 namespace {
 
 constexpr int ADS_WARPS = 4;
-constexpr int ADS_UN = 4;
+constexpr int ADS_UN = 8;
 
 __device__ __forceinline__ uint4 ld16(const __half* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 
@@ -56,11 +57,12 @@ __global__ void __launch_bounds__(ADS_WARPS * 32)
 attn_decode_split_kernel(const __half* __restrict__ q, long long q_st, const __half* __restrict__ cache_k,
                          const __half* __restrict__ cache_v, __half* __restrict__ out, long long o_st,
                          const int* __restrict__ kv_len, const int* __restrict__ seq, int H, int Hkv, int T_max,
-                         float scale_log2, int n_split, float* __restrict__ part) {
+                         float scale_log2, int n_split, float* __restrict__ part, int* __restrict__ counters) {
   constexpr int LPK = D / 8;    // lanes per key row
   constexpr int KPW = 32 / LPK; // keys per warp step
   __shared__ float sm_acc[ADS_WARPS][G][D];
   __shared__ float sm_ml[ADS_WARPS][G][2];
+  __shared__ int sm_last;
   pdl_launch_dependents();
   pdl_wait();
 
@@ -171,27 +173,34 @@ attn_decode_split_kernel(const __half* __restrict__ q, long long q_st, const __h
       }
     }
   }
-}
-
-__global__ void attn_decode_combine_kernel(const float* __restrict__ part, __half* __restrict__ out, long long o_st,
-                                           int H, int D, int n_split) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int t = blockIdx.x, h = blockIdx.y;
-  const float* src = part + ((long long)t * H + h) * n_split * (D + 2);
-  float mm = -CUDART_INF_F;
-  for (int sp = 0; sp < n_split; ++sp) mm = fmaxf(mm, src[sp * (D + 2) + D]);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  if (n_split == 1) return;
+  // last slice to arrive merges all slices of this (token, kv head)
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(&counters[t * Hkv + hk], 1);
+    sm_last = (prev == n_split - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!sm_last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+    const int g = i / D, d = i % D;
+    const int h = hk * G + g;
+    const float* src = part + ((long long)t * H + h) * n_split * (D + 2);
+    float mm = -CUDART_INF_F;
+    for (int k = 0; k < n_split; ++k) mm = fmaxf(mm, __ldcg(src + k * (D + 2) + D));
     float a = 0.f, ll = 0.f;
     if (mm != -CUDART_INF_F) {
-      for (int sp = 0; sp < n_split; ++sp) {
-        const float c = exp2f(src[sp * (D + 2) + D] - mm);
-        a += src[sp * (D + 2) + d] * c;
-        ll += src[sp * (D + 2) + D + 1] * c;
+      for (int k = 0; k < n_split; ++k) {
+        const float c = exp2f(__ldcg(src + k * (D + 2) + D) - mm);
+        a += __ldcg(src + k * (D + 2) + d) * c;
+        ll += __ldcg(src + k * (D + 2) + D + 1) * c;
       }
     }
     out[t * o_st + (long long)h * D + d] = __float2half(ll > 0.f ? a / ll : 0.f);
   }
+  if (threadIdx.x == 0) counters[t * Hkv + hk] = 0;  // re-armed for the next call on this stream
 }
 
 template <int D, int G>
@@ -199,13 +208,8 @@ void launch_split(const AttnCacheArgs& a, cudaStream_t s) {
   dim3 grid(a.n_tok, a.Hkv, a.n_split);
   launch_pdl(attn_decode_split_kernel<D, G>, grid, dim3(ADS_WARPS * 32), 0, s, reinterpret_cast<const __half*>(a.q), a.q_st,
              reinterpret_cast<const __half*>(a.cache_k), reinterpret_cast<const __half*>(a.cache_v), reinterpret_cast<__half*>(a.out),
-             a.o_st, a.kv_len, a.seq, a.H, a.Hkv, a.T_max, a.scale * 1.4426950408889634f, a.n_split, a.partial);
+             a.o_st, a.kv_len, a.seq, a.H, a.Hkv, a.T_max, a.scale * 1.4426950408889634f, a.n_split, a.partial, a.counters);
   RT_LAUNCH_CHECK();
-  if (a.n_split > 1) {
-    launch_pdl(attn_decode_combine_kernel, dim3(a.n_tok, a.H), dim3(D <= 128 ? D : 128), 0, s,
-               static_cast<const float*>(a.partial), reinterpret_cast<__half*>(a.out), a.o_st, a.H, D, a.n_split);
-    RT_LAUNCH_CHECK();
-  }
 }
 
 template <int D>
@@ -226,11 +230,12 @@ bool attn_decode_split_supported(int D, int H, int Hkv) {
   return (D == 64 || D == 128 || D == 256) && (g == 1 || g == 2 || g == 4 || g == 8);
 }
 
-// Number of key slices: enough CTAs for two waves over the SMs, but at least 64 keys per slice.
+// Number of key slices: enough CTAs for four per SM (a slice is then a handful of loads deep: the kernel is bound
+// by dependent-load latency, not bandwidth), but at least 32 keys per slice.
 int attn_decode_num_splits(int n_tok, int Hkv, int max_kv_len, int sm_count) {
   const long long rows = (long long)n_tok * Hkv;
-  long long want = (2LL * sm_count + rows - 1) / rows;
-  const long long cap = (max_kv_len + 63) / 64;
+  long long want = (4LL * sm_count + rows - 1) / rows;
+  const long long cap = (max_kv_len + 31) / 32;
   if (want > cap) want = cap;
   if (want > 64) want = 64;
   return want < 1 ? 1 : (int)want;
@@ -238,7 +243,8 @@ int attn_decode_num_splits(int n_tok, int Hkv, int max_kv_len, int sm_count) {
 
 void attn_decode_split(const AttnCacheArgs& a, cudaStream_t s) {
   RT_CHECK(attn_decode_split_supported(a.D, a.H, a.Hkv), "attn_decode_split: unsupported head_dim / group size");
-  RT_CHECK(a.n_split >= 1 && (a.n_split == 1 || a.partial != nullptr), "attn_decode_split: partial buffer required");
+  RT_CHECK(a.n_split >= 1 && (a.n_split == 1 || (a.partial != nullptr && a.counters != nullptr)),
+           "attn_decode_split: partial buffer and zeroed counters required");
   RT_CHECK(a.q_st % 8 == 0 && (reinterpret_cast<uintptr_t>(a.q) & 15) == 0, "attn_decode_split: q must be 16-byte aligned");
   if (a.n_tok == 0) return;
   bool ok = false;

@@ -261,10 +261,16 @@ class LlamaRuntime:
                 and prefill_bt[0] * prefill_bt[1] == n):
             flash_bt = prefill_bt
             flash_lse = torch.empty((prefill_bt[0], H, prefill_bt[1]), dtype=torch.float32, device=self.device)
+        # decode-sized steps on one GPU: each projection is one kernel with the RMSNorm as its prologue and the
+        # residual add / SwiGLU as its epilogue (QuantLinear.fused)
+        fuse = C is not None and self.tp_world == 1 and 1 <= n <= QuantLinear.FUSED_MAX_ROWS and x.dtype == torch.float16
         for li, L in enumerate(self.layers):
-            if h is None:
-                h = self._rmsnorm(x, L.attn_norm)
-            qkv = L.wqkv(h)                                            # [n, (H + 2 Hkv) D]
+            if fuse:
+                qkv = L.wqkv.fused(x, norm_w=L.attn_norm, eps=cfg.rms_eps)
+            else:
+                if h is None:
+                    h = self._rmsnorm(x, L.attn_norm)
+                qkv = L.wqkv(h)                                            # [n, (H + 2 Hkv) D]
             q = qkv[:, : H * D].view(n, H, D)
             k = qkv[:, H * D: (H + Hkv) * D].view(n, Hkv, D)
             v = qkv[:, (H + Hkv) * D:].view(n, Hkv, D)
@@ -291,6 +297,12 @@ class LlamaRuntime:
                     p = torch.softmax((kk @ q[t].float().unsqueeze(-1)).squeeze(-1) * scale, -1)   # [H, Lk]
                     att[t] = (p.unsqueeze(1) @ vv).squeeze(1).to(att.dtype)
             att2 = att.reshape(n, H * D)
+            if fuse:
+                # wo / down (no prologue, short rows of work per SM) are faster on the K-sliced GEMV kernel
+                x = L.wo(att2, residual=x)
+                act = L.w_gate_up.fused(x, norm_w=L.ffn_norm, eps=cfg.rms_eps, swiglu=True)
+                x = L.w_down(act, residual=x)
+                continue
             if self.tp_world == 1:
                 x = L.wo(att2, residual=x)
                 h = self._rmsnorm(x, L.ffn_norm)
@@ -299,12 +311,15 @@ class LlamaRuntime:
             else:
                 x = x + self._all_reduce(L.wo(att2))
                 h = self._rmsnorm(x, L.ffn_norm)
-            gu = L.w_gate_up(h)                                        # [n, 2 ff_local]
-            if C is not None:
-                act = torch.empty((n, self.ff_local), dtype=gu.dtype, device=gu.device)
-                C.silu_mul(gu[:, : self.ff_local], gu[:, self.ff_local:], act)
+            if C is not None and n <= QuantLinear.FUSED_MAX_ROWS and h.dtype == torch.float16:
+                act = L.w_gate_up.fused(h, swiglu=True)                # gate/up GEMV + SwiGLU in one kernel
             else:
-                act = torch.nn.functional.silu(gu[:, : self.ff_local].float()).to(gu.dtype) * gu[:, self.ff_local:]
+                gu = L.w_gate_up(h)                                    # [n, 2 ff_local]
+                if C is not None:
+                    act = torch.empty((n, self.ff_local), dtype=gu.dtype, device=gu.device)
+                    C.silu_mul(gu[:, : self.ff_local], gu[:, self.ff_local:], act)
+                else:
+                    act = torch.nn.functional.silu(gu[:, : self.ff_local].float()).to(gu.dtype) * gu[:, self.ff_local:]
             h = None
             if self.tp_world == 1:
                 x = L.w_down(act, residual=x)
@@ -318,6 +333,8 @@ class LlamaRuntime:
                 x = x + self._all_reduce(L.w_down(act))
         if last_only is not None:
             x = x[last_only]
+        if fuse and last_only is None:
+            return self.lm_head.fused(x, norm_w=self.out_norm, eps=cfg.rms_eps).float()
         if h is None:
             h = self._rmsnorm(x, self.out_norm)
         return self.lm_head(h).float()

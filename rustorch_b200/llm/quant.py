@@ -149,6 +149,47 @@ class QuantLinear:
             y = y.to(x.dtype)
         return y.reshape(*shp, self.out_features)
 
+    FUSED_MAX_ROWS = 4 if os.environ.get("RUSTORCH_DECODE_FUSED", "1") != "0" else 0
+
+    PREFETCH_NEXT = os.environ.get("RUSTORCH_DECODE_PREFETCH", "1") != "0"
+
+    def fused(self, x: torch.Tensor, norm_w: Optional[torch.Tensor] = None, eps: float = 1e-5,
+              residual: Optional[torch.Tensor] = None, swiglu: bool = False,
+              prefetch: Optional["QuantLinear"] = None) -> torch.Tensor:
+        """``epilogue(W @ rmsnorm(x))`` for ``x [n, in]``: ``norm_w`` applies RMSNorm to ``x`` first, ``residual`` is
+        added to the result, ``swiglu`` treats the rows of ``W`` as ``[gate; up]`` and returns ``silu(gate) * up``
+        (``out_features / 2`` columns).  Up to ``FUSED_MAX_ROWS`` rows on CUDA this is ONE kernel (decode steps);
+        otherwise the same arithmetic through the separate kernels.  ``prefetch``: the projection that runs next; the
+        kernel asks the L2 for its weights while it works, so HBM keeps streaming across the kernel boundary."""
+        n = x.shape[0]
+        if (self.device.type == "cuda" and 1 <= n <= self.FUSED_MAX_ROWS and x.dtype == torch.float16
+                and self.in_features % 64 == 0):
+            C = _native.load(required=True)
+            x2 = x if x.stride(-1) == 1 else x.contiguous()
+            y = torch.empty((n, self.out_features // 2 if swiglu else self.out_features), dtype=torch.float16, device=self.device)
+            pq = ps = None
+            if prefetch is not None and self.PREFETCH_NEXT and prefetch.qs is not None:
+                pq, ps = prefetch.qs, prefetch.scales        # the kernel pulls the next projection's weights towards L2
+            C.q_gemv_fused(self.qs, self.scales, x2, y, norm_w, float(eps), residual, self.q8, swiglu, pq, ps)
+            return y
+        h = x
+        if norm_w is not None:
+            if self.device.type == "cuda":
+                h = torch.empty_like(x)
+                _native.load(required=True).rmsnorm_f16(x, norm_w, h, float(eps))
+            else:
+                xf = x.float()
+                h = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()).to(x.dtype)
+        y = self(h, residual=residual)
+        if swiglu:
+            ff = self.out_features // 2
+            if self.device.type == "cuda":
+                act = torch.empty((n, ff), dtype=y.dtype, device=y.device)
+                _native.load(required=True).silu_mul(y[:, :ff], y[:, ff:], act)
+                return act
+            return torch.nn.functional.silu(y[:, :ff].float()).to(y.dtype) * y[:, ff:]
+        return y
+
     def nbytes(self) -> int:
         return self.out_features * (self.in_features // 32) * (34 if self.q8 else 18)
 

@@ -224,3 +224,49 @@ def test_prefill_flash_path_matches_cached_attention_path():
     assert rel_err(a, b) < 5e-3
     assert rel_err(c1.k[0], c2.k[0]) < 1e-6                      # layer 0: same inputs, same rotation
     assert all(rel_err(x, y) < 5e-3 for x, y in zip(c1.k, c2.k))   # later layers see the other kernel's rounding
+
+
+@pytest.mark.parametrize("q8", [False, True])
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (2, 1002, 11008), (4, 250, 832), (3, 64, 64), (1, 38, 128)])
+def test_fused_decode_projection_matches_fp32_reference(q8, M, N, K):
+    """RMSNorm prologue + dequant-fused GEMV + residual / SwiGLU epilogue in one kernel vs fp32 math on the
+    dequantised weights (ragged N, K that is not a multiple of the lanes' stride, 1..4 rows).  The kernel
+    quantises the activations to int8 per 32-element block (max |h| / 127), which bounds its error at ~0.4 % of a
+    typical output; the tolerances are set for that."""
+    from rustorch_b200 import _native
+    from rustorch_b200.formats import gguf
+    from rustorch_b200.llm import QuantLinear
+    ty = gguf.GGMLType.Q8_0 if q8 else gguf.GGMLType.Q4_0
+    q = QuantLinear.random(N, K, ty, 0.02, "cuda", seed=2)
+    W = q.dequantize()
+    x = (torch.randn(M, K, device="cuda") * 0.7).half()
+    nw = (1.0 + 0.1 * torch.randn(K, device="cuda")).half()
+    res = torch.randn(M, N, device="cuda").half()
+    eps = 1e-5
+    xf = x.float()
+    h = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * nw.float()).half().float()
+    n0 = _native.launch_count()
+    y = q.fused(x, norm_w=nw, eps=eps, residual=res)
+    assert _native.launch_count() == n0 + 1                      # one kernel
+    assert rel_err(y, h @ W.t() + res.float()) < 8e-3
+    y2 = q.fused(x)                                              # no prologue, no epilogue
+    assert rel_err(y2, xf @ W.t()) < 8e-3
+    ff = N // 2
+    act = q.fused(x, norm_w=nw, eps=eps, swiglu=True)
+    t = h @ W.t()
+    ref = torch.nn.functional.silu(t[:, :ff].half().float()) * t[:, ff:].half().float()
+    assert act.shape == (M, ff) and rel_err(act, ref) < 1e-2
+    _native.check_status()
+
+
+def test_fused_decode_projection_falls_back_beyond_four_rows():
+    from rustorch_b200.formats import gguf
+    from rustorch_b200.llm import QuantLinear
+    q = QuantLinear.random(512, 256, gguf.GGMLType.Q4_0, 0.02, "cuda", seed=3)
+    x = (torch.randn(6, 256, device="cuda") * 0.7).half()
+    nw = torch.ones(256, device="cuda").half()
+    xf = x.float()
+    h = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)).half().float()
+    t = h @ q.dequantize().t()
+    ref = torch.nn.functional.silu(t[:, :256].half().float()) * t[:, 256:].half().float()
+    assert rel_err(q.fused(x, norm_w=nw, eps=1e-5, swiglu=True), ref) < 8e-3
