@@ -22,3 +22,4 @@ from .multi_gpu import (AllReduceAlgorithm, CommBackend, DistributedTrainer, Gpu
                         LoadBalancer, MultiGpuBarrier, MultiGpuContext, NCCLOps, NCCLOptimizations, NCCLProfiler,
                         ParallelismStrategy, ParameterServer, StreamManager, StreamPriority, TransferStatistics)
 from .optimizer import DistributedOptimizer, SyncStrategy
+from .context_parallel import RingAttention, gather_sequence, ring_attention, shard_sequence

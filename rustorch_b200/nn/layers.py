@@ -9,6 +9,7 @@ tensors Linear / LayerNorm / RMSNorm / attention run on the hand-written sm_100a
 from __future__ import annotations
 
 import math
+import os
 from typing import List, Optional, Sequence, Tuple, Union
 
 import torch
@@ -16,6 +17,9 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from . import fused
+
+# fp32 CUDA Linear layers run on the tcgen05 GEMM as three bf16 products (RUSTORCH_FP32_LINEAR=library: cuBLAS SGEMM)
+_FP32_NATIVE = os.environ.get("RUSTORCH_FP32_LINEAR", "native") != "library"
 
 Module = nn.Module
 Parameter = nn.Parameter
@@ -69,6 +73,9 @@ class Linear(nn.Module):
                 return fused.LinearFn.apply(x, self.weight, self.bias)
             if x.dtype == torch.float16 and self.weight.dtype == torch.float16 and fused.K._native.available():
                 return fused.LinearF16Fn.apply(x, self.weight, self.bias)      # fp16 operands, fp32 accumulation
+            if (x.dtype == torch.float32 and self.weight.dtype == torch.float32 and _FP32_NATIVE
+                    and fused.K._native.available()):
+                return fused.LinearF32Fn.apply(x, self.weight, self.bias)      # three bf16 GEMMs, fp32 accumulation
         return F.linear(x, self.weight, self.bias)
 
 

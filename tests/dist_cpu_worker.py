@@ -34,6 +34,30 @@ def main():
         req.wait()
         out["async_done"] = req.is_completed()
         out["stats_calls"] = D.monitoring.get_communication_stats().calls.get("all_reduce", 0)
+    elif case == "ring_attention":
+        from rustorch_b200.distributed.context_parallel import gather_sequence, ring_attention, shard_sequence
+        g = torch.Generator().manual_seed(5)
+        B, T, H, Hkv, Dh = 2, 8 * W, 4, 2, 16
+        q = torch.randn(B, T, H, Dh, generator=g, dtype=torch.float64)
+        k = torch.randn(B, T, Hkv, Dh, generator=g, dtype=torch.float64)
+        v = torch.randn(B, T, Hkv, Dh, generator=g, dtype=torch.float64)
+        go = torch.randn(B, T, H, Dh, generator=g, dtype=torch.float64)
+        for causal in (False, True):
+            # oracle: full attention on every rank
+            qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
+            s = (qf.transpose(1, 2) @ kf.repeat_interleave(H // Hkv, 2).transpose(1, 2).transpose(-1, -2)) / Dh ** 0.5
+            if causal:
+                s = s.masked_fill(torch.ones(T, T, dtype=torch.bool).triu(1), float("-inf"))
+            ref = (torch.softmax(s, -1) @ vf.repeat_interleave(H // Hkv, 2).transpose(1, 2)).transpose(1, 2)
+            ref.backward(go)
+            ql, kl, vl = (shard_sequence(t).requires_grad_(True) for t in (q, k, v))
+            att = ring_attention(ql, kl, vl, causal=causal)
+            att.backward(shard_sequence(go))
+            tag = "causal" if causal else "full"
+            out[f"{tag}_fwd"] = float((gather_sequence(att.detach()) - ref.detach()).abs().max())
+            out[f"{tag}_dq"] = float((gather_sequence(ql.grad) - qf.grad).abs().max())
+            out[f"{tag}_dk"] = float((gather_sequence(kl.grad) - kf.grad).abs().max())
+            out[f"{tag}_dv"] = float((gather_sequence(vl.grad) - vf.grad).abs().max())
     elif case == "backends":
         be = D.BackendFactory.create_backend(D.DistributedBackend.GLOO, optimizations=D.BackendOptimizations(bucket_size_mb=1))
         ts = [torch.full((n,), float(r + 1)) for n in (3, 300_000, 5)]

@@ -56,6 +56,15 @@ def test_fused_ddp_state_dict_resumes_next_step(kind):
         assert r["lp_restored"] == 0.0 and r["resume_diff"] < 1e-7, r
 
 
+@pytest.mark.parametrize("world", [2, 3])
+def test_ring_attention_matches_full_attention(world):
+    """Sequence-sharded ring attention (forward and backward, causal and not, grouped kv heads) against attention
+    over the whole sequence, fp64 on gloo ranks."""
+    for res in _spawn("ring_attention", world=world):
+        for key, err in res.items():
+            assert err < 1e-9, (key, err)
+
+
 def test_tensor_parallel_layers_match_unsharded():
     for r in _spawn("tp"):
         assert r["fwd"] < 1e-5 and r["bwd"] < 1e-5 and r["gathered"] == [3, 16]

@@ -139,3 +139,26 @@ def test_cta_pair_gemm_split_k_and_batch(monkeypatch):
     x = torch.randn(3, 300, 256, device="cuda", dtype=torch.bfloat16)
     w = torch.randn(3, 512, 256, device="cuda", dtype=torch.bfloat16)
     assert rel_err(K.gemm(x, w), x.float() @ w.float().transpose(1, 2)) < 1.5e-2
+
+
+def test_fp32_linear_layer_runs_three_bf16_gemms_with_fp32_accuracy():
+    from rustorch_b200 import _native
+    from rustorch_b200 import nn as rnn
+    torch.manual_seed(0)
+    lin = rnn.Linear(264, 136).cuda()
+    x = torch.randn(7, 19, 264, device="cuda")
+    x1 = x.clone().requires_grad_(True)
+    x2 = x.double().requires_grad_(True)
+    n0 = _native.launch_count()
+    y = lin(x1)
+    assert _native.launch_count() >= n0 + 3 and y.dtype == torch.float32
+    w64, b64 = lin.weight.detach().double().requires_grad_(True), lin.bias.detach().double()
+    ref = torch.nn.functional.linear(x2, w64, b64)
+    # split-bf16 keeps 16 mantissa bits per operand: far tighter than a tf32 product (~5e-4)
+    torch.testing.assert_close(y.double(), ref, rtol=1e-4, atol=2e-4)
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref.backward(g.double())
+    torch.testing.assert_close(x1.grad.double(), x2.grad, rtol=1e-4, atol=2e-4)
+    torch.testing.assert_close(lin.weight.grad.double(), w64.grad, rtol=1e-4, atol=5e-4)
+    torch.testing.assert_close(lin.bias.grad.double(), g.double().sum((0, 1)), rtol=1e-5, atol=1e-4)
