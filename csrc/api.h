@@ -451,6 +451,7 @@ struct RopeKvArgs {
   const int* pos;           // [n_tok] position of each token in its sequence
   const int* seq;           // [n_tok] sequence (batch) index of each token
   int n_tok, H, Hkv, D, T_max;
+  int n_seq;  // sequences in the cache (B): seq[t] is checked against it on the device
   float theta;
   int interleaved;  // 1: pairs (2i, 2i+1) (GGUF llama), 0: pairs (i, i + D/2)
 };
@@ -464,6 +465,7 @@ struct AttnCacheArgs {
   const int* kv_len;  // [n_tok] number of cached positions visible to the token
   const int* seq;
   int n_tok, H, Hkv, D, T_max, max_kv_len;
+  int n_seq = 0;  // sequences in the cache (B)
   float scale;
   // split-KV path only: fp32 scratch [n_tok][H][n_split][D + 2] (unused when n_split == 1)
   float* partial = nullptr;

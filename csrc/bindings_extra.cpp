@@ -383,6 +383,7 @@ void rope_kv(Tensor& q, Tensor& k, const Tensor& v, Tensor& cache_k, Tensor& cac
   a.pos = pos.data_ptr<int>(); a.seq = seq.data_ptr<int>();
   a.n_tok = int(q.size(0)); a.H = int(q.size(1)); a.Hkv = int(k.size(1)); a.D = int(q.size(2));
   a.T_max = int(cache_k.size(2));
+  a.n_seq = int(cache_k.size(0));
   a.theta = float(theta);
   a.interleaved = interleaved ? 1 : 0;
   rt::rope_kv_f16(a, cur_stream(q.device().index()));
@@ -402,6 +403,7 @@ void attn_cache(const Tensor& q, const Tensor& cache_k, const Tensor& cache_v, T
   a.kv_len = kv_len.data_ptr<int>(); a.seq = seq.data_ptr<int>();
   a.n_tok = int(q.size(0)); a.H = int(q.size(1)); a.Hkv = int(cache_k.size(1)); a.D = int(q.size(2));
   a.T_max = int(cache_k.size(2)); a.max_kv_len = int(max_kv_len);
+  a.n_seq = int(cache_k.size(0));
   a.scale = float(scale);
   if (rt::attn_decode_split_supported(a.D, a.H, a.Hkv) && q.stride(0) % 8 == 0 &&
       (reinterpret_cast<uintptr_t>(a.q) & 15) == 0) {
@@ -1039,6 +1041,7 @@ void register_extra_ops(pybind11::module_& m) {
         pybind11::arg("scales"), pybind11::arg("x"), pybind11::arg("y"), pybind11::arg("bias"), pybind11::arg("residual"),
         pybind11::arg("q8"), pybind11::arg("partial"), pybind11::arg("counters"), pybind11::arg("path") = 0);
   m.def("q_gemm_tc_scratch", &q_gemm_tc_scratch);
+  m.def("bounds_check_build", []() { return rt::bounds_check_build(); }, "true when the extension was compiled with -DRT_BOUNDS_CHECK");
   m.def("repack_quant", &repack_quant);
   m.def("rmsnorm_f16", &rmsnorm_f16);
   m.def("rope_kv", &rope_kv);

@@ -169,7 +169,12 @@ __global__ void __launch_bounds__(256, 2) ddp_bucket_step_kernel(const DdpBucket
           }
         }
       }
-      *reinterpret_cast<float4*>(a.grad[R] + e[g]) = z;
+      // This rank's copy of its own slice is zeroed here on the peer-load path (same address as the load above, so
+      // the hardware orders the two).  On the multimem path the switch reads this copy through ANOTHER virtual
+      // address; a zero stored from the same kernel, even one computed from the loaded value, was measured to make
+      // this rank's own gradient read as zero in the reduction.  There the whole buffer is cleared by its owner
+      // after the end-of-step wait instead.
+      if (!NVLS) *reinterpret_cast<float4*>(a.grad[R] + e[g]) = z;
       float4 pm = *reinterpret_cast<float4*>(a.master + e[g]);
       float4 m = has_m ? *reinterpret_cast<float4*>(a.m + e[g]) : z;
       float4 vv = has_v ? *reinterpret_cast<float4*>(a.v + e[g]) : z;

@@ -47,6 +47,14 @@ EncodeFn encode_fn() {
 void fail(const std::string& msg) { throw std::runtime_error(msg); }
 
 long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+bool bounds_check_build() {
+#ifdef RT_BOUNDS_CHECK
+  return true;
+#else
+  return false;
+#endif
+}
+
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 int current_device() {

@@ -15,6 +15,7 @@ namespace rt {
 // Number of kernels launched by this library since process start.
 long long launch_count();
 void count_launch(int n = 1);
+bool bounds_check_build();  // compiled with -DRT_BOUNDS_CHECK
 
 // One int32 status word per device, zero while healthy.  Kernels CAS an error code into
 // it when a bounded wait expires (see ptx.cuh); read_status() synchronises the device and

@@ -27,6 +27,24 @@ enum : int {
   RT_ERR_BOUNDS = 201,
 };
 
+// Bounds-checked build (-DRT_BOUNDS_CHECK; RUSTORCH_BOUNDS_CHECK=1 python -m rustorch_b200._build): RT_GUARD(index,
+// extent, status) is true for 0 <= index < extent; otherwise it records RT_ERR_BOUNDS in the status word and the
+// caller skips the access, so an indexing bug shows up as a Python exception instead of a memory fault.  In the
+// normal build the macro is the constant true and costs nothing.  Checks of indices that come from DATA (token ids,
+// cache positions, sequence numbers, class labels) are not behind this macro: they are always on.
+#ifdef RT_BOUNDS_CHECK
+__device__ __forceinline__ bool rt_guard_index(long long idx, long long extent, int* status) {
+  if (idx >= 0 && idx < extent) return true;
+  if (status) atomicCAS(status, 0, RT_ERR_BOUNDS);
+  return false;
+}
+#define RT_GUARD(idx, extent, status) ::rt::rt_guard_index((long long)(idx), (long long)(extent), (status))
+#define RT_BOUNDS_CHECK_BUILD 1
+#else
+#define RT_GUARD(idx, extent, status) true
+#define RT_BOUNDS_CHECK_BUILD 0
+#endif
+
 #ifndef RT_WAIT_TIMEOUT_NS
 #define RT_WAIT_TIMEOUT_NS 2000000000ull  // 2 s
 #endif

@@ -30,7 +30,8 @@ struct UnfoldGeom {
 
 template <int VEC>  // channels per thread: 8 (16-byte accesses) or 1
 __global__ void __launch_bounds__(256) unfold_nd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ col,
-                                                        const UnfoldGeom g, long long M) {
+                                                        const UnfoldGeom g, long long M, long long x_elems, long long col_elems,
+                                                        int* status) {
   const int taps = g.KD * g.KH * g.KW;
   const int cv = g.Cg / VEC;                       // vectors per tap
   const long long per_row = (long long)taps * cv;
@@ -52,6 +53,8 @@ __global__ void __launch_bounds__(256) unfold_nd_kernel(const __nv_bfloat16* __r
     const bool in = id >= 0 && id < g.D && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W;
     __nv_bfloat16* dst = col + ((long long)grp * M + m) * g.k_pad + (long long)tap * g.Cg + v * VEC;
     const __nv_bfloat16* src = x + ((((long long)n * g.D + id) * g.H + ih) * g.W + iw) * g.C + grp * g.Cg + v * VEC;
+    // checked builds: both addresses against the tensors' element counts
+    if (!RT_GUARD((dst - col) + VEC - 1, col_elems, status) || (in && !RT_GUARD((src - x) + VEC - 1, x_elems, status))) continue;
     if (VEC == 8) {
       *reinterpret_cast<uint4*>(dst) = in ? *reinterpret_cast<const uint4*>(src) : make_uint4(0u, 0u, 0u, 0u);
     } else {
@@ -62,13 +65,15 @@ __global__ void __launch_bounds__(256) unfold_nd_kernel(const __nv_bfloat16* __r
   const int pad = g.k_pad - taps * g.Cg;
   if (pad > 0) {
     const long long rows = (long long)g.groups * M;
-    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < rows * pad; t += (long long)gridDim.x * blockDim.x)
-      col[(t / pad) * g.k_pad + taps * g.Cg + (t % pad)] = __float2bfloat16(0.f);
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < rows * pad; t += (long long)gridDim.x * blockDim.x) {
+      const long long at = (t / pad) * g.k_pad + taps * g.Cg + (t % pad);
+      if (RT_GUARD(at, col_elems, status)) col[at] = __float2bfloat16(0.f);
+    }
   }
 }
 
 __global__ void __launch_bounds__(256) fold_nd_kernel(const __nv_bfloat16* __restrict__ col, __nv_bfloat16* __restrict__ x,
-                                                      const UnfoldGeom g, long long M) {
+                                                      const UnfoldGeom g, long long M, long long col_elems, int* status) {
   const long long total = (long long)g.N * g.D * g.H * g.W * g.C;
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
     const int c = int(t % g.C);
@@ -96,7 +101,8 @@ __global__ void __launch_bounds__(256) fold_nd_kernel(const __nv_bfloat16* __res
           if (ow >= g.OW) continue;
           const long long m = (((long long)n * g.OD + od) * g.OH + oh) * g.OW + ow;
           const int tap = (kd * g.KH + kh) * g.KW + kw;
-          acc += __bfloat162float(col[((long long)grp * M + m) * g.k_pad + (long long)tap * g.Cg + cc]);
+          const long long at = ((long long)grp * M + m) * g.k_pad + (long long)tap * g.Cg + cc;
+          if (RT_GUARD(at, col_elems, status)) acc += __bfloat162float(col[at]);
         }
       }
     }
@@ -137,8 +143,10 @@ void unfold_nd(const UnfoldArgs& a, cudaStream_t s) {
   const int grid = (int)std::min<long long>((work + 255) / 256, 32LL * sm_count(current_device()));
   auto* x = reinterpret_cast<const __nv_bfloat16*>(a.x);
   auto* col = reinterpret_cast<__nv_bfloat16*>(a.col);
-  if (vec) unfold_nd_kernel<8><<<std::max(grid, 1), 256, 0, s>>>(x, col, g, M);
-  else unfold_nd_kernel<1><<<std::max(grid, 1), 256, 0, s>>>(x, col, g, M);
+  const long long x_elems = (long long)a.N * a.D * a.H * a.W * a.C, col_elems = (long long)a.groups * M * a.k_pad;
+  int* status = status_word(current_device());
+  if (vec) unfold_nd_kernel<8><<<std::max(grid, 1), 256, 0, s>>>(x, col, g, M, x_elems, col_elems, status);
+  else unfold_nd_kernel<1><<<std::max(grid, 1), 256, 0, s>>>(x, col, g, M, x_elems, col_elems, status);
   RT_LAUNCH_CHECK();
 }
 
@@ -149,7 +157,8 @@ void fold_nd(const UnfoldArgs& a, cudaStream_t s) {
   const long long total = (long long)a.N * a.D * a.H * a.W * a.C;
   if (total == 0) return;
   const int grid = (int)std::min<long long>((total + 255) / 256, 32LL * sm_count(current_device()));
-  fold_nd_kernel<<<std::max(grid, 1), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(a.col), reinterpret_cast<__nv_bfloat16*>(a.x), g, M);
+  fold_nd_kernel<<<std::max(grid, 1), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(a.col), reinterpret_cast<__nv_bfloat16*>(a.x), g, M,
+                                                   (long long)a.groups * M * a.k_pad, status_word(current_device()));
   RT_LAUNCH_CHECK();
 }
 

@@ -346,6 +346,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       auto stage_put = [&](int piece, uint4 w) {
         *reinterpret_cast<uint4*>(wstage + lane * 128 + ((piece ^ (lane & 7)) << 4)) = w;
       };
+      int n_store = 0;  // first column of the 64-column group being stored (read by the checked build only)
       auto stage_store = [&](__nv_bfloat16* base, long long ld) {  // base: row m_warp, column n0
         const int piece = lane & 7;
 #pragma unroll
@@ -353,7 +354,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const int row = itr * 4 + (lane >> 3);
           if (m_warp + row < p.M) {
             const uint4 w = *reinterpret_cast<const uint4*>(wstage + row * 128 + ((piece ^ (row & 7)) << 4));
-            *reinterpret_cast<uint4*>(base + (long long)row * ld + piece * 8) = w;
+            // checked builds: the 8 columns this lane writes lie inside the row's N columns
+            if (RT_GUARD(n_store + piece * 8 + 7, p.N, p.status))
+              *reinterpret_cast<uint4*>(base + (long long)row * ld + piece * 8) = w;
           }
         }
       };
@@ -368,6 +371,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tmem_ld_32x32b_x32(taddr + 32, r2[1]);
         tmem_ld_wait();
         if (staged_ok && n0 + 64 <= p.N) {
+          n_store = n0;
           uint4 keep[2][4];  // GELU_DUAL: the bf16 pre-activations, reused for the second output
 #pragma unroll
           for (int h = 0; h < 2; ++h) {

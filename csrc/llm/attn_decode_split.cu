@@ -57,7 +57,8 @@ __global__ void __launch_bounds__(ADS_WARPS * 32)
 attn_decode_split_kernel(const __half* __restrict__ q, long long q_st, const __half* __restrict__ cache_k,
                          const __half* __restrict__ cache_v, __half* __restrict__ out, long long o_st,
                          const int* __restrict__ kv_len, const int* __restrict__ seq, int H, int Hkv, int T_max,
-                         float scale_log2, int n_split, float* __restrict__ part, int* __restrict__ counters) {
+                         float scale_log2, int n_split, float* __restrict__ part, int* __restrict__ counters, int n_seq,
+                         int* __restrict__ status) {
   constexpr int LPK = D / 8;    // lanes per key row
   constexpr int KPW = 32 / LPK; // keys per warp step
   __shared__ float sm_acc[ADS_WARPS][G][D];
@@ -67,13 +68,20 @@ attn_decode_split_kernel(const __half* __restrict__ q, long long q_st, const __h
   pdl_wait();
 
   const int t = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z;
-  const int L = kv_len[t], s = seq[t];
+  int L = kv_len[t];
+  const int s = seq[t];
+  // both come from device data: a length past the cache or a foreign sequence number is reported and made harmless
+  if (L > T_max || L < 0 || s < 0 || s >= n_seq) {
+    if (threadIdx.x == 0) atomicCAS(status, 0, RT_ERR_BOUNDS);
+    L = (s < 0 || s >= n_seq) ? 0 : min(max(L, 0), T_max);
+  }
+  const int s_safe = (s < 0 || s >= n_seq) ? 0 : s;
   const int per = (L + n_split - 1) / n_split;
   const int j0 = sp * per, j1 = min(L, j0 + per);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / LPK, dl = lane % LPK;
-  const __half* K = cache_k + ((long long)s * Hkv + hk) * T_max * D + dl * 8;
-  const __half* V = cache_v + ((long long)s * Hkv + hk) * T_max * D + dl * 8;
+  const __half* K = cache_k + ((long long)s_safe * Hkv + hk) * T_max * D + dl * 8;
+  const __half* V = cache_v + ((long long)s_safe * Hkv + hk) * T_max * D + dl * 8;
 
   float qr[G][8], acc[G][8], m[G], l[G];
 #pragma unroll
@@ -208,7 +216,8 @@ void launch_split(const AttnCacheArgs& a, cudaStream_t s) {
   dim3 grid(a.n_tok, a.Hkv, a.n_split);
   launch_pdl(attn_decode_split_kernel<D, G>, grid, dim3(ADS_WARPS * 32), 0, s, reinterpret_cast<const __half*>(a.q), a.q_st,
              reinterpret_cast<const __half*>(a.cache_k), reinterpret_cast<const __half*>(a.cache_v), reinterpret_cast<__half*>(a.out),
-             a.o_st, a.kv_len, a.seq, a.H, a.Hkv, a.T_max, a.scale * 1.4426950408889634f, a.n_split, a.partial, a.counters);
+             a.o_st, a.kv_len, a.seq, a.H, a.Hkv, a.T_max, a.scale * 1.4426950408889634f, a.n_split, a.partial, a.counters, a.n_seq,
+             status_word(current_device()));
   RT_LAUNCH_CHECK();
 }
 

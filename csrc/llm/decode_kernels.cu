@@ -70,11 +70,17 @@ __global__ void rope_kv_f16_kernel(__half* __restrict__ q, long long q_st, __hal
                                    long long k_st, const __half* __restrict__ v, long long v_st,
                                    __half* __restrict__ cache_k, __half* __restrict__ cache_v,
                                    const int* __restrict__ pos, const int* __restrict__ seq, int H, int Hkv,
-                                   int D, int T_max, float log2_theta, int interleaved) {
+                                   int D, int T_max, float log2_theta, int interleaved, int n_seq, int* status) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, hy = blockIdx.y;
   const int p = pos[t], s = seq[t];
+  // position and sequence number come from device data (a replayed decode graph advances them itself): a step past
+  // the end of the cache is reported, not written
+  if (p < 0 || p >= T_max || s < 0 || s >= n_seq) {
+    if (threadIdx.x == 0) atomicCAS(status, 0, RT_ERR_BOUNDS);
+    return;
+  }
   const int half_d = D >> 1;
   if (hy >= H + Hkv) {  // v head: plain append
     const int h = hy - H - Hkv;
@@ -191,12 +197,13 @@ void rmsnorm_f16(const void* x, const void* w, void* y, long long rows, int C, f
 
 void rope_kv_f16(const RopeKvArgs& a, cudaStream_t s) {
   RT_CHECK(a.D % 2 == 0, "rope: head_dim must be even");
+  RT_CHECK(a.n_seq >= 1, "rope: the cache holds no sequence");
   if (a.n_tok == 0) return;
   const int threads = std::min(128, std::max(32, ((a.D / 2 + 31) / 32) * 32));
   launch_pdl(rope_kv_f16_kernel, dim3(a.n_tok, a.H + 2 * a.Hkv), dim3(threads), 0, s, reinterpret_cast<__half*>(a.q), a.q_st,
              reinterpret_cast<__half*>(a.k), a.k_st, reinterpret_cast<const __half*>(a.v), a.v_st,
              reinterpret_cast<__half*>(a.cache_k), reinterpret_cast<__half*>(a.cache_v), a.pos, a.seq, a.H, a.Hkv, a.D, a.T_max,
-             log2f(a.theta), a.interleaved);
+             log2f(a.theta), a.interleaved, a.n_seq, status_word(current_device()));
   RT_LAUNCH_CHECK();
 }
 

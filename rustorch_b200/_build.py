@@ -26,6 +26,11 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "--threads", "2",
 ] + os.environ.get("RUSTORCH_NVCC_EXTRA", "").split()          # e.g. "-DRT_ATTN_PROF" for an instrumented build
+# RUSTORCH_BOUNDS_CHECK=1: the checked build.  Guarded global accesses compare their index with the extent passed by
+# the host and record an error code instead of touching memory outside (csrc/common/ptx.cuh, RT_GUARD);
+# ``_C.bounds_check_build()`` tells which build is loaded.
+if os.environ.get("RUSTORCH_BOUNDS_CHECK", "0") == "1":
+    NVCC_FLAGS.append("-DRT_BOUNDS_CHECK")
 
 
 def _cuda_home() -> str:

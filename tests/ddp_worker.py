@@ -108,14 +108,16 @@ def main():
     dist.all_reduce(lt)
     lt /= world
     init_v = rflat.named_views(init)
-    worst = 0.0
+    worst, per_name = 0.0, []
     for name in ref_master:
         upd = (ref_master[name] - init_v[name]).abs().mean().clamp_min(1e-12)
         diff = (got[name].to(dev) - ref_master[name]).abs().mean()
         worst = max(worst, float(diff / upd))
+        per_name.append((round(float(diff / upd), 4), name))
+    per_name.sort(reverse=True)
     out = {"rank": rank, "world": world, "mode": mode, "n_buckets": n_buckets,
            "loss_ddp": [round(float(x), 4) for x in lt], "loss_ref": [round(x, 4) for x in ref_losses],
-           "worst_rel_update_diff": round(worst, 4), "nvls": nvls_used}
+           "worst_rel_update_diff": round(worst, 4), "nvls": nvls_used, "worst_params": per_name[:6]}
     # one file per rank: lines printed by several ranks to a shared pipe can interleave
     with open(os.path.join(os.environ["DDP_RESULT_DIR"], f"rank{rank}.json"), "w") as f:
         json.dump(out, f)

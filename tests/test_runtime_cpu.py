@@ -193,3 +193,22 @@ def test_dynamic_graph_and_runtime_engine():
     assert eng.profile_report()["f"]["calls"] == 3
     with pytest.raises(ValueError):
         ctx.add_op(E.DynamicOp.CUSTOM, [x])
+
+
+def test_bounds_checked_build_mode_compiles(tmp_path):
+    """The checked build (-DRT_BOUNDS_CHECK) turns RT_GUARD into real index checks; it must keep compiling for sm_100a.
+    One translation unit that uses the macro is enough to catch a broken guard expression."""
+    import shutil
+    import subprocess
+    from pathlib import Path
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(nvcc).exists():
+        import pytest
+        pytest.skip("no nvcc")
+    root = Path(__file__).resolve().parents[1]
+    src = root / "csrc" / "conv" / "unfold_nd.cu"
+    assert "RT_GUARD" in src.read_text()
+    for flags in ([], ["-DRT_BOUNDS_CHECK"]):
+        r = subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "--expt-relaxed-constexpr", *flags,
+                            f"-I{root / 'csrc'}", "-c", str(src), "-o", str(tmp_path / "u.o")], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr[-2000:]
