@@ -272,3 +272,38 @@ def test_fused_decode_projection_falls_back_beyond_four_rows():
     t = h @ q.dequantize().t()
     ref = torch.nn.functional.silu(t[:, :256].half().float()) * t[:, 256:].half().float()
     assert rel_err(q.fused(x, norm_w=nw, eps=1e-5, swiglu=True), ref) < 8e-3
+
+
+def test_cache_position_past_the_end_is_reported_not_written():
+    """Positions and sequence numbers come from device data (a replayed decode graph advances them itself): a token
+    past the end of the cache must turn into an IndexOutOfBounds error with the cache untouched, never a write
+    outside it, and the device stays usable."""
+    from rustorch_b200 import _native
+    from rustorch_b200.error import IndexOutOfBounds
+    C = _native.load(required=True)
+    H, Hkv, D, T_max = 4, 2, 64, 16
+    q = torch.randn(1, H, D, device="cuda").half()
+    k = torch.randn(1, Hkv, D, device="cuda").half()
+    v = torch.randn(1, Hkv, D, device="cuda").half()
+    ck = torch.zeros(2, Hkv, T_max, D, device="cuda", dtype=torch.half)
+    cv = torch.zeros_like(ck)
+    seq = torch.zeros(1, device="cuda", dtype=torch.int32)
+    for bad_pos, bad_seq in ((T_max, 0), (-1, 0), (3, 2)):
+        pos = torch.full((1,), bad_pos, device="cuda", dtype=torch.int32)
+        seq.fill_(bad_seq)
+        C.rope_kv(q.clone(), k.clone(), v, ck, cv, pos, seq, 10000.0, True)
+        with pytest.raises(IndexOutOfBounds):
+            _native.check_status()
+        assert float(ck.abs().max()) == 0.0 and float(cv.abs().max()) == 0.0
+    # attention over a claimed length beyond the cache: reported, result finite
+    out = torch.empty(1, H, D, device="cuda", dtype=torch.half)
+    seq.fill_(0)
+    C.attn_cache(q, ck, cv, out, torch.full((1,), T_max + 5, device="cuda", dtype=torch.int32), seq, T_max, 0.125)
+    with pytest.raises(IndexOutOfBounds):
+        _native.check_status()
+    assert torch.isfinite(out.float()).all()
+    # a valid step still works afterwards
+    pos = torch.full((1,), 3, device="cuda", dtype=torch.int32)
+    C.rope_kv(q.clone(), k.clone(), v, ck, cv, pos, seq, 10000.0, True)
+    _native.check_status()
+    assert float(ck[0, :, 3].abs().max()) > 0.0
