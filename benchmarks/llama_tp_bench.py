@@ -31,6 +31,9 @@ def main():
     ap.add_argument("--seqs", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--vocab", type=int, default=128256)
+    ap.add_argument("--impl", default="ours", choices=["ours", "library"],
+                    help="library: the same model and sharding on NCCL collectives + cuBLAS + SDPA + torch.optim.AdamW(fused=True)")
+    ap.add_argument("--checkpoint", action="store_true", help="recompute each block in backward (activation checkpointing)")
     a = ap.parse_args()
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -38,7 +41,10 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     from rustorch_b200 import _native
+    from rustorch_b200.models import llama as llama_mod
     from rustorch_b200.models.llama import LlamaModel, LlamaTrainConfig
+    llama_mod.LIBRARY_MODE = a.impl == "library"
+    llama_mod.CHECKPOINT_BLOCKS = a.checkpoint
     from rustorch_b200.optim.flat import FlatParams, FusedAdamW
     from rustorch_b200.utils.clocks import ClockSampler
     cfg = LlamaTrainConfig.llama3_8b()
@@ -46,8 +52,11 @@ def main():
     torch.manual_seed(0)
     model = LlamaModel(cfg, device=dev, dtype=torch.bfloat16, tp_group=dist.group.WORLD if world > 1 else None, batch=a.seqs,
                        seq_len=a.seq_len)
-    flat = FlatParams(model)
-    opt = FusedAdamW(flat, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    if a.impl == "library":
+        opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+    else:
+        flat = FlatParams(model)
+        opt = FusedAdamW(flat, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
     g = torch.Generator().manual_seed(1)
     idx = torch.randint(0, a.vocab, (a.seqs, a.seq_len), generator=g).to(dev)
     tgt = idx.roll(-1, 1)
@@ -57,6 +66,8 @@ def main():
         loss.backward()
         model.sync_replicated_grads()
         opt.step()
+        if a.impl == "library":
+            opt.zero_grad(set_to_none=True)
         return loss
 
     for _ in range(a.warmup):
@@ -83,11 +94,11 @@ def main():
     d, dkv, ff = 4096, 1024, 14336
     n_params = a.layers * (2 * d * d + 2 * d * dkv + 3 * d * ff + 2 * d) + 2 * a.vocab * d + d
     out = {"metric": "train_tokens_per_s", "value": round(tokens / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
-           "warmup": a.warmup, "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "strong", "dtype": "bf16",
+           "warmup": a.warmup, "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "impl": a.impl, "activation_checkpointing": bool(a.checkpoint),
            "data": "synthetic uniform random tokens, random-init weights", "reduced": a.layers != 32,
            "config": {"model": f"llama-8B style ({a.layers}L, d4096, 32q/8kv heads, SwiGLU 14336, vocab {a.vocab})", "global_batch": a.seqs,
                       "seq_len": a.seq_len, "parallelism": f"tp{world}+sp", "params": n_params},
-           "clocks": clocks, "gpu_launches": _native.launch_count() - l0, "final_loss": round(float(loss), 4)}
+           "clocks": clocks, "gpu_launches": _native.launch_count() - l0, "final_loss": round(float(loss.detach()), 4)}
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:

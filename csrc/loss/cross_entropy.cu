@@ -66,17 +66,25 @@ __global__ void cross_entropy_kernel(__nv_bfloat16* __restrict__ logits,
   mx = red[32];
   __syncthreads();
   const float mxs = -mx * LOG2E;        // exp(x - mx) = ex2(x * log2e + mxs): one fma + one ex2 per logit
-  // pass 2: sum exp
+  const float xt = __bfloat162float(srow[tgt]);  // before the staged row is overwritten with its exponentials
+  if (STAGED) __syncthreads();
+  // pass 2: sum exp.  The staged row keeps the exponentials (bf16, the precision of the gradient that leaves anyway),
+  // so the special-function unit runs once per logit instead of twice.
   float sum = 0.f;
   for (int v = tid; v < ncut; v += nt) {
     uint4 w = reinterpret_cast<const uint4*>(srow)[v];
     const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w);
     if (v < nfull) {
+      uint4 ex;
+      uint32_t* exw = reinterpret_cast<uint32_t*>(&ex);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 f = __bfloat1622float2(h2[e]);
-        sum += ex2_approx(fmaf(f.x, LOG2E, mxs)) + ex2_approx(fmaf(f.y, LOG2E, mxs));
+        const float a = ex2_approx(fmaf(f.x, LOG2E, mxs)), b = ex2_approx(fmaf(f.y, LOG2E, mxs));
+        sum += a + b;
+        exw[e] = pack_bf16x2(a, b);
       }
+      if (STAGED) reinterpret_cast<uint4*>(srow)[v] = ex;
     } else {
       const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&w);
 #pragma unroll
@@ -96,7 +104,6 @@ __global__ void cross_entropy_kernel(__nv_bfloat16* __restrict__ logits,
   }
   __syncthreads();
   sum = red[32];
-  const float xt = __bfloat162float(srow[tgt]);
   if (tid == 0) loss[r] = ignored ? 0.f : (logf(sum) + mx - xt);
   __syncthreads();  // srow[tgt] read before it is overwritten (non-staged mode aliases the row)
   const float gs = ignored ? 0.f : grad_scale;
@@ -111,8 +118,13 @@ __global__ void cross_entropy_kernel(__nv_bfloat16* __restrict__ logits,
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 f = __bfloat1622float2(h2[e]);
-        g[2 * e] = ex2_approx(fmaf(f.x, LOG2E, mxs)) * gi;
-        g[2 * e + 1] = ex2_approx(fmaf(f.y, LOG2E, mxs)) * gi;
+        if (STAGED && v < nfull) {      // the staged vector already holds exp(x - max)
+          g[2 * e] = f.x * gi;
+          g[2 * e + 1] = f.y * gi;
+        } else {
+          g[2 * e] = ex2_approx(fmaf(f.x, LOG2E, mxs)) * gi;
+          g[2 * e + 1] = ex2_approx(fmaf(f.y, LOG2E, mxs)) * gi;
+        }
       }
       if (v >= nfull) {
 #pragma unroll

@@ -120,8 +120,15 @@ class _SwiGLU(torch.autograd.Function):
         return dgu
 
 
+# True: every op of the model runs on stock PyTorch kernels (cuBLAS, SDPA, ATen elementwise, NCCL collectives): the
+# baseline arm of benchmarks/llama_tp_bench.py.  The default is the native path.
+LIBRARY_MODE = False
+# True: every block is recomputed in backward (activation checkpointing), for models whose activations do not fit.
+CHECKPOINT_BLOCKS = False
+
+
 def _native_ok(x: torch.Tensor) -> bool:
-    return x.is_cuda and x.dtype == torch.bfloat16
+    return x.is_cuda and x.dtype == torch.bfloat16 and not LIBRARY_MODE
 
 
 def _rms(x, w, eps):
@@ -138,6 +145,9 @@ def _linear(x2, w):
 def _attention(q, k, v):
     if _native_ok(q) and q.shape[-1] in (64, 128):
         return fused.FlashAttentionFn.apply(q, k, v, True, None)
+    if q.is_cuda and q.shape[2] != k.shape[2]:
+        return F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
+                                              enable_gqa=True).transpose(1, 2)
     g = q.shape[2] // k.shape[2]
     kk, vv = k.repeat_interleave(g, 2), v.repeat_interleave(g, 2)
     return F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), is_causal=True).transpose(1, 2)
@@ -165,7 +175,11 @@ class LlamaBlock(nn.Module):
         self.ffn_norm = nn.Parameter(torch.ones(cfg.n_embd, **kw))
         if self.tp:
             import torch.distributed as dist
-            from ..distributed.tp_fused import FusedColumnParallelLinear, FusedRowParallelLinear
+            if LIBRARY_MODE:
+                from ..distributed.tp_library import LibraryColumnParallelLinear as FusedColumnParallelLinear
+                from ..distributed.tp_library import LibraryRowParallelLinear as FusedRowParallelLinear
+            else:
+                from ..distributed.tp_fused import FusedColumnParallelLinear, FusedRowParallelLinear
             W = dist.get_world_size(tp_group)
             if H % W or Hkv % W or cfg.n_ff % W:
                 raise ValueError("heads, kv heads and n_ff must divide by the tensor-parallel world size")
@@ -199,6 +213,8 @@ class LlamaBlock(nn.Module):
         gu = self.w_gate_up(h) if self.tp else _linear(h, self.w_gate_up)           # [B*T, 2 ff_local]: gate | up
         if _native_ok(gu) and self.ff_local % 8 == 0:
             act = _SwiGLU.apply(gu)
+        elif LIBRARY_MODE:
+            act = F.silu(gu[:, : self.ff_local]) * gu[:, self.ff_local:]
         else:
             act = ew.mul(ew.unary("silu", gu[:, : self.ff_local].contiguous()), gu[:, self.ff_local:].contiguous())
         return x + (self.w_down(act) if self.tp else _linear(act, self.w_down))
@@ -241,7 +257,11 @@ class LlamaModel(nn.Module):
             lo, hi = self.rank * n, (self.rank + 1) * n
         x = self.tok_emb[flat[lo:hi]]
         for blk in self.blocks:
-            x = blk(x, cos, sin, B, T)
+            if CHECKPOINT_BLOCKS and torch.is_grad_enabled():
+                from torch.utils.checkpoint import checkpoint
+                x = checkpoint(blk, x, cos, sin, B, T, use_reentrant=False)   # keep only the block inputs
+            else:
+                x = blk(x, cos, sin, B, T)
         x = _rms(x, self.out_norm, c.rms_eps)
         logits = _linear(x, self.lm_head)
         if targets is None:

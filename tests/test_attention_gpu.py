@@ -4,7 +4,7 @@ import math
 import pytest
 import torch
 
-from conftest import rel_err
+from conftest import assert_close, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -40,10 +40,12 @@ def test_attention_forward(causal, B, T, H, Hkv, D):
     o, lse = K_.attention_fwd(q, k, v, causal)
     ref = _ref_attn(q, k, v, causal)
     assert rel_err(o, ref) < 2e-2
+    assert_close(o, ref, atol_frac=8e-3, rtol=3e-2)
 
 
 @pytest.mark.parametrize("causal", [True, False])
-@pytest.mark.parametrize("B,T,H,Hkv,D", [(2, 256, 4, 4, 64), (1, 384, 8, 2, 128), (1, 200, 2, 2, 64)])
+@pytest.mark.parametrize("B,T,H,Hkv,D", [(2, 256, 4, 4, 64), (1, 384, 8, 2, 128), (1, 200, 2, 2, 64), (1, 328, 4, 2, 128),
+                                         (2, 72, 4, 4, 128), (1, 1160, 3, 3, 64)])
 def test_attention_backward(causal, B, T, H, Hkv, D):
     from rustorch_b200.nn.fused import FlashAttentionFn
     q, k, v = _inputs(B, T, H, Hkv, D, seed=1)
@@ -55,8 +57,11 @@ def test_attention_backward(causal, B, T, H, Hkv, D):
     qr, kr, vr = (t.float().requires_grad_(True) for t in (q, k, v))
     _ref_attn(qr, kr, vr, causal).backward(do.float())
     assert rel_err(qa.grad, qr.grad) < 3e-2
+    assert_close(qa.grad, qr.grad, atol_frac=8e-3, rtol=3e-2)
     assert rel_err(ka.grad, kr.grad) < 3e-2
+    assert_close(ka.grad, kr.grad, atol_frac=8e-3, rtol=3e-2)
     assert rel_err(va.grad, vr.grad) < 3e-2
+    assert_close(va.grad, vr.grad, atol_frac=8e-3, rtol=3e-2)
 
 
 def test_attention_strided_qkv_views():
@@ -67,6 +72,7 @@ def test_attention_strided_qkv_views():
     o, _ = K_.attention_fwd(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], True)
     ref = _ref_attn(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], True)
     assert rel_err(o, ref) < 2e-2
+    assert_close(o, ref, atol_frac=8e-3, rtol=3e-2)
 
 
 def test_multihead_attention_masks_weights_dropout_on_native_kernels():
@@ -95,6 +101,7 @@ def test_multihead_attention_masks_weights_dropout_on_native_kernels():
     (o1.float() * g).sum().backward()
     (o2 * g).sum().backward()
     assert rel_err(x1.grad, x2.grad) < 5e-2
+    assert_close(x1.grad, x2.grad, atol_frac=8e-3, rtol=3e-2)
     for (k1, p1), (_, p2) in zip(sorted(mha.named_parameters()), sorted(ref.named_parameters())):
         assert rel_err(p1.grad, p2.grad) < 5e-2, k1
     # dropout on the probabilities: native Philox kernel, expectation preserved, eval mode deterministic

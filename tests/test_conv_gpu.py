@@ -3,7 +3,7 @@ import pytest
 import torch
 import torch.nn.functional as F
 
-from conftest import rel_err
+from conftest import assert_close, rel_err
 from rustorch_b200 import _native
 
 pytestmark = pytest.mark.gpu
@@ -47,6 +47,7 @@ def test_conv2d_forward_backward(N, Cin, H, W, Cout, k, s, p):
     assert rel_err(w.grad, wr.grad) < 2e-2, "wgrad"
     assert rel_err(x.grad, xr.grad) < 2e-2, "dgrad"
     assert rel_err(b.grad, br.grad) < 2e-2
+    assert_close(b.grad, br.grad, atol_frac=8e-3, rtol=3e-2)
     _native.check_status()
 
 
@@ -60,6 +61,7 @@ def test_conv_module_and_resnet_block_use_native_kernels():
     assert _native.launch_count() - before >= 3 and x.grad is not None and conv.weight.grad is not None
     ref = F.conv2d(x.detach().float(), conv.weight.detach().float(), None, 1, 1)
     assert rel_err(y, ref) < 1e-2
+    assert_close(y, ref, atol_frac=8e-3, rtol=3e-2)
     stem = rnn.Conv2d(3, 64, 7, stride=2, padding=3).cuda().bfloat16()          # 3 input channels: patch matrix + GEMM
     assert stem(torch.randn(2, 3, 32, 32, device="cuda").bfloat16()).shape == (2, 64, 16, 16)
 
@@ -144,12 +146,16 @@ def _conv_nd_case(nd, cin, cout, k, stride, pad, dil, groups, size, seed=0):
     ref = (F.conv1d, F.conv2d, F.conv3d)[nd - 1](xs[1], ws[1], bs[1], stride, pad, dil, groups)
     assert y.shape == ref.shape
     assert rel_err(y, ref) < 2e-2
+    assert_close(y, ref, atol_frac=8e-3, rtol=3e-2)
     dy = torch.randn(ref.shape, device="cuda", generator=g)
     y.backward(dy.bfloat16())
     ref.backward(dy.bfloat16().float())
     assert rel_err(xs[0].grad, xs[1].grad) < 3e-2
+    assert_close(xs[0].grad, xs[1].grad, atol_frac=8e-3, rtol=3e-2)
     assert rel_err(ws[0].grad, ws[1].grad) < 3e-2
+    assert_close(ws[0].grad, ws[1].grad, atol_frac=8e-3, rtol=3e-2)
     assert rel_err(bs[0].grad, bs[1].grad) < 3e-2
+    assert_close(bs[0].grad, bs[1].grad, atol_frac=8e-3, rtol=3e-2)
 
 
 @pytest.mark.parametrize("nd,cin,cout,k,stride,pad,dil,groups,size", [
@@ -199,6 +205,7 @@ def test_conv3d_and_transpose_layers_use_the_native_path():
     assert _native.launch_count() > n0
     ref = F.conv3d(x.float(), layer.weight.float(), layer.bias.float(), 1, 1, 1, 2)
     assert rel_err(y, ref) < 2e-2
+    assert_close(y, ref, atol_frac=8e-3, rtol=3e-2)
     up = rnn.ConvTranspose1d(8, 8, 4, stride=2, padding=1).cuda().bfloat16()
     z = torch.randn(2, 8, 10, device="cuda").bfloat16()
     n0 = _native.launch_count()

@@ -37,4 +37,5 @@ def test_tp_fused_kernels_match_unsharded_model():
         assert res["ag_rel"] < 1e-2 and res["rs_rel"] < 2e-2, res
         assert abs(res["llama_loss_tp"] - res["llama_loss_full"]) < 3e-2 and res["llama_dw_rel"] < 6e-2, res
         assert res["llama_dnorm_rel"] < 6e-2 and res["llama_dhead_rel"] < 6e-2, res
+        assert res["lib_y_rel"] < 3e-2 and res["lib_dx_rel"] < 4e-2 and res["lib_dw_rel"] < 4e-2, res
         assert res["y_rel"] < 3e-2 and res["dx_rel"] < 4e-2 and res["dwc_rel"] < 4e-2 and res["dwr_rel"] < 4e-2 and res["dbr_rel"] < 4e-2, res

@@ -68,6 +68,22 @@ def main():
     res["dwc_rel"] = rel(col.weight.grad, wc.grad[rank * ffl:(rank + 1) * ffl])
     res["dwr_rel"] = rel(row.weight.grad, wr.grad[:, rank * ffl:(rank + 1) * ffl])
     res["dbr_rel"] = rel(row.bias.grad, brf.grad)
+    # ---- the library arm (NCCL + cuBLAS) of the same two layers: the benchmark baseline must compute the same thing
+    from rustorch_b200.distributed.tp_library import LibraryColumnParallelLinear, LibraryRowParallelLinear
+    lcol = LibraryColumnParallelLinear(d, ff, rows, device=dev)
+    lrow = LibraryRowParallelLinear(ff, d, rows, device=dev)
+    with torch.no_grad():
+        lcol.weight.copy_(Wc[rank * ffl:(rank + 1) * ffl]); lrow.weight.copy_(Wr[:, rank * ffl:(rank + 1) * ffl])
+    xl = X[rank * rows:(rank + 1) * rows].clone().requires_grad_(True)
+    yl = lrow(torch.nn.functional.gelu(lcol(xl), approximate="tanh"))
+    yl.backward(G[rank * rows:(rank + 1) * rows])
+    Xq = X.float().requires_grad_(True)
+    wq, wq2 = Wc.float().requires_grad_(True), Wr.float().requires_grad_(True)
+    yq = torch.nn.functional.gelu(Xq @ wq.t(), approximate="tanh") @ wq2.t()
+    yq.backward(G.float())
+    res["lib_y_rel"] = rel(yl, yq[rank * rows:(rank + 1) * rows])
+    res["lib_dx_rel"] = rel(xl.grad, Xq.grad[rank * rows:(rank + 1) * rows])
+    res["lib_dw_rel"] = max(rel(lcol.weight.grad, wq.grad[rank * ffl:(rank + 1) * ffl]), rel(lrow.weight.grad, wq2.grad[:, rank * ffl:(rank + 1) * ffl]))
     # ---- peer-memory collectives against NCCL
     from rustorch_b200.distributed.p2p_collectives import P2PCollectives
     pc = P2PCollectives(1 << 22, torch.bfloat16, dev)
