@@ -127,9 +127,15 @@ def bench_attn(a, bwd):
         o, lse = K.attention_fwd(q, k, v, causal)
         do = bf(B, T, H, D)
         best, med = time_op(lambda: K.attention_bwd(q, k, v, o, do, lse, causal), a.iters)
-        # 7 GEMM-tiles of work in this two-kernel formulation; the algorithmic minimum is 5 (2.5x fwd)
         report(f"attn_bwd_b{B}h{H}t{T}d{D}", best, med, flops=2.5 * fl,
-               extra="flops counted as 2.5x forward (algorithmic), kernel recomputes S and dP twice")
+               extra="flops counted as 2.5x forward (algorithmic); includes the delta and dQ-conversion kernels")
+        if a.compare:
+            qt, kt, vt = (x.transpose(1, 2).detach().requires_grad_(True) for x in (q, k, v))
+            ot = torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, is_causal=causal, enable_gqa=Hkv != H)
+            dot = do.transpose(1, 2)
+            f = lambda: torch.autograd.grad(ot, (qt, kt, vt), dot, retain_graph=True)
+            best, med = time_op(f, a.iters)
+            report(f"sdpa_bwd_b{B}h{H}t{T}d{D}", best, med, flops=2.5 * fl, extra="library baseline (backward only)")
 
 
 def bench_norm(a):
@@ -344,6 +350,11 @@ def main():
             bench_gemm(a)
         bench_attn(a, False)
         bench_attn(a, True)
+        sv = (a.batch, a.heads, a.kv_heads, a.seq, a.dim)
+        a.batch, a.heads, a.kv_heads, a.seq, a.dim = 2, 32, 8, 4096, 128      # the Llama-8B attention shape (GQA 32 / 8)
+        bench_attn(a, False)
+        bench_attn(a, True)
+        a.batch, a.heads, a.kv_heads, a.seq, a.dim = sv
         a.m, a.n = 16384, 768
         bench_norm(a)
         a.m, a.n = 16384, 50257

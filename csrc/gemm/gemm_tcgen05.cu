@@ -639,15 +639,12 @@ void gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
   const int device = current_device();
   int block_n = (g.block_n == 128 || g.block_n == 256) ? g.block_n : 0;
   if (block_n == 0) block_n = (g.N <= 128) ? 128 : 256;
-  // CTA pairs (one 256 x 256 tile per two SMs, a third less operand traffic from L2): measured 3-6 % ahead for
-  // weight-gradient shapes (both operands MN-major, long K) and level or slightly behind elsewhere, so that is the
-  // automatic choice; RUSTORCH_GEMM_PAIR=1 uses pairs wherever they are legal, =0 nowhere.
+  // CTA pairs (one 256 x 256 tile per two SMs, a third less operand traffic from L2) measured level with single-CTA
+  // tiles on the benchmarked shapes (+-5 % either way, run to run), and the training step does not move, so they are
+  // opt-in: RUSTORCH_GEMM_PAIR=1 uses pairs wherever they are legal.
   const bool pair_legal = block_n == 256 && g.M > BLOCK_M;
-  bool pair = pair_legal && g.a_mn && g.b_mn && g.K >= 2048;
-  if (const char* e = std::getenv("RUSTORCH_GEMM_PAIR")) {
-    if (e[0] == '0') pair = false;
-    else if (e[0] == '1') pair = pair_legal;
-  }
+  bool pair = false;
+  if (const char* e = std::getenv("RUSTORCH_GEMM_PAIR")) pair = pair_legal && e[0] == '1';
 
   GemmParams p{};
   p.M = g.M;
