@@ -84,8 +84,8 @@ def run_other_config(args, rest) -> int:
         argv += ["--tp", str(args.gpus)]
     else:
         argv += ["--steps", str(args.steps), "--warmup", str(args.warmup)]
-        if args.config == "resnet_ddp":
-            argv += ["--impl", "library" if args.impl == "library" else "ours"]
+    # every benchmark module has the same two arms
+    argv += ["--impl", "library" if args.impl == "library" else "ours"]
     sys.argv = argv + list(rest)
     runpy.run_path(argv[0], run_name="__main__")
     return 0
