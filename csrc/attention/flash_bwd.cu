@@ -47,6 +47,7 @@ template <int D>
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
                                   const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
                                   int B, int H, int T, long long sb, long long st, long long sh) {
+  pdl_launch_dependents();  // a dependent-launch kernel that follows may set up while this one runs
   constexpr int LPR = D / 8;  // lanes per row
   const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long row = gt / LPR;

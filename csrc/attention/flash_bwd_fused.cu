@@ -88,6 +88,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1)
 attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                       const __grid_constant__ CUtensorMap tmap_dq, const AttnBwdFusedParams p) {
+  pdl_launch_dependents();  // a dependent-launch kernel that follows may set up while this one runs
   constexpr int D = FB_D;
   using S = FusedBwdSmem;
   constexpr int QS = S::QSTAGES;
@@ -414,6 +415,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 // dq[b][t][h][:] (bf16, strided) = dq_acc[b][t][h][:] (fp32, contiguous); 8 elements per thread.
 __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long n8, int H, int Tq,
                                        long long sb, long long st, long long sh) {
+  pdl_launch_dependents();  // a dependent-launch kernel that follows may set up while this one runs
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n8) return;
   const long long e = i * 8;

@@ -137,6 +137,7 @@ template <int D, bool F16, int POLY>
 __global__ void __launch_bounds__(ATT_PP_THREADS, 1)
 attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const AttnFwdPPParams p) {
+  pdl_launch_dependents();  // a dependent-launch kernel that follows may set up while this one runs
   using S = AttnFwdPPSmem<D>;
   constexpr int KS = S::KV_STAGES;
   constexpr bool ALIAS = (D == 128);  // P_i overlays S_i

@@ -162,6 +162,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (PAIR) cluster_sync_all();  // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
+  // Programmatic dependent launch: the next kernel of the stream may start its prologue now (it becomes resident as
+  // this grid's CTAs retire); this kernel's own first read of global memory and its first write wait for the
+  // previous grid to complete (pdl_wait in the producer and epilogue roles; the MMA role touches no global memory).
+  pdl_launch_dependents();
 
   const int total_tiles = p.batch * p.m_blocks * p.n_blocks * p.split_k;
   const int kb_per_split = (p.k_blocks + p.split_k - 1) / p.split_k;
@@ -174,6 +178,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #ifdef RT_GEMM_PROF
       long long acc_prof[1] = {0};
 #endif
+      pdl_wait();
       for (int t = worker; t < total_tiles && ok; t += n_workers) {
         int split, b, mb, nb;
         decode_tile(t, p, split, b, mb, nb);
@@ -322,6 +327,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t tile_i = 0;
     bool ok = true;
     const bool vec_ok = ((p.ldc & 7) == 0) && (p.aux == nullptr || (p.ld_aux & 7) == 0);
+    pdl_wait();
     const float alpha = p.alpha_dev ? p.alpha * __ldg(p.alpha_dev) : p.alpha;
     for (int t = worker; t < total_tiles && ok; t += n_workers, ++tile_i) {
       int split, b, mb, nb;
@@ -614,17 +620,19 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
     cfg.blockDim = dim3(GEMM_THREADS);
     cfg.dynamicSmemBytes = S::TOTAL;
     cfg.stream = stream;
-    cudaLaunchAttribute at{};
-    at.id = cudaLaunchAttributeClusterDimension;
-    at.val.clusterDim.x = 2;
-    at.val.clusterDim.y = 1;
-    at.val.clusterDim.z = 1;
-    cfg.attrs = &at;
-    cfg.numAttrs = 1;
+    cudaLaunchAttribute at[2]{};
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = at;
+    cfg.numAttrs = 2;
     RT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
     count_launch();
   } else {
-    kern<<<n_workers, GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, p);
+    launch_pdl(kern, dim3(n_workers), dim3(GEMM_THREADS), S::TOTAL, stream, ta, tb, p);
     RT_LAUNCH_CHECK();
   }
 }

@@ -44,6 +44,7 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
                                 const __nv_bfloat16* __restrict__ beta,
                                 __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out,
                                 float* __restrict__ rstd_out, long long rows, int C, float eps) {
+  pdl_launch_dependents();  // a dependent-launch kernel that follows may set up while this one runs
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -134,6 +135,7 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
                                 const __nv_bfloat16* __restrict__ dres,
                                 __nv_bfloat16* __restrict__ dx, float* __restrict__ partial,
                                 long long rows, int C) {
+  pdl_launch_dependents();  // a dependent-launch kernel that follows may set up while this one runs
   // MAXV > 0: one [2][C] slot per warp (plain stores); MAXV == 0: a single [2][C] slot (atomics)
   extern __shared__ float sacc[];
   const int warps = blockDim.x >> 5;
@@ -295,6 +297,7 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
 // 32 partial-row lanes (coalesced 128-byte reads), combined through shared memory.
 __global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dgamma,
                                        float* __restrict__ dbeta, int n_part, int C) {
+  pdl_launch_dependents();  // a dependent-launch kernel that follows may set up while this one runs
   __shared__ float red[32][33];
   const int cl = threadIdx.x & 31, pl = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cl;
@@ -345,6 +348,7 @@ __global__ void __launch_bounds__(256) norm_bwd_wide_kernel(const __nv_bfloat16*
                                                             const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                                                             const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                                                             float* __restrict__ partial, long long rows, int C) {
+  pdl_launch_dependents();  // a dependent-launch kernel that follows may set up while this one runs
   __shared__ float red[2][2][8];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint4 gv[VPT];

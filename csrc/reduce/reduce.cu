@@ -13,6 +13,7 @@ namespace rt {
 // atomic per column per block.
 __global__ void colsum_vec_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out,
                                   long long M, int N, long long ld, int rows_per_block) {
+  pdl_launch_dependents();  // a dependent-launch kernel that follows may set up while this one runs
   __shared__ float part[8][32 * 8 + 8];
   const int cg = threadIdx.x & 31;
   const int rl = threadIdx.x >> 5;
@@ -51,6 +52,7 @@ __global__ void colsum_vec_kernel(const __nv_bfloat16* __restrict__ x, float* __
 // Scalar fallback for N % 8 != 0 or unaligned rows: thread owns one column.
 __global__ void colsum_scalar_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out,
                                      long long M, int N, long long ld, int rows_per_block) {
+  pdl_launch_dependents();  // a dependent-launch kernel that follows may set up while this one runs
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= N) return;
   const long long m0 = (long long)blockIdx.y * rows_per_block;
