@@ -17,6 +17,7 @@ src/models/transformer_models.rs:760-796).
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -42,7 +43,40 @@ def _num_sms(device=None) -> int:
 grad_ready_hook = None
 
 
+# Weight- and bias-gradient kernels that accumulate straight into ``main_grad`` have no consumer inside backward, so
+# they run on a side stream: the input-gradient GEMM of the same layer (and whatever follows it) proceeds on the main
+# stream meanwhile and the CTAs of one persistent GEMM fill the SMs the other leaves idle in its last wave.  Every
+# backward joins the side stream before it reports its parameters ready (RUSTORCH_WGRAD_STREAM=0: one stream).
+_SIDE_ON = os.environ.get("RUSTORCH_WGRAD_STREAM", "1") != "0"
+_side_streams = {}
+_side_used = {}
+
+
+def _side_run(device: torch.device, fn, *inputs) -> None:
+    if not _SIDE_ON or device.type != "cuda":
+        fn()
+        return
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    side = _side_streams.get(idx)
+    if side is None:
+        side = _side_streams[idx] = torch.cuda.Stream(device=idx)
+    side.wait_stream(torch.cuda.current_stream(idx))      # the inputs were produced on the main stream
+    with torch.cuda.stream(side):
+        fn()
+    for t in inputs:                                       # their memory must outlive the side stream's reads
+        t.record_stream(side)
+    _side_used[idx] = True
+
+
+def _side_join() -> None:
+    for idx, used in _side_used.items():
+        if used:
+            torch.cuda.current_stream(idx).wait_stream(_side_streams[idx])
+            _side_used[idx] = False
+
+
 def _notify(*params):
+    _side_join()
     if grad_ready_hook is not None:
         grad_ready_hook([p for p in params if p is not None])
 
@@ -65,8 +99,9 @@ def wgrad_into(dy2d: torch.Tensor, x2d: torch.Tensor, param: torch.Tensor, alpha
     sk = _split_k_for(tiles, -(-dy2d.shape[0] // 64), dy2d.device)
     mg = getattr(param, "main_grad", None)
     if mg is not None:
-        K.gemm(dy2d, x2d, a_mn=True, b_mn=True, out=mg.view(n_out, n_in), accumulate=True, split_k=sk,
-               alpha_dev=alpha_dev)
+        extra = (alpha_dev,) if alpha_dev is not None else ()
+        _side_run(dy2d.device, lambda: K.gemm(dy2d, x2d, a_mn=True, b_mn=True, out=mg.view(n_out, n_in), accumulate=True,
+                                               split_k=sk, alpha_dev=alpha_dev), dy2d, x2d, *extra)
         return None
     g = K.gemm(dy2d, x2d, a_mn=True, b_mn=True, out_dtype=torch.float32, accumulate=True, split_k=sk,
                alpha_dev=alpha_dev)
@@ -78,7 +113,7 @@ def bgrad_into(dy2d: torch.Tensor, param: Optional[torch.Tensor]):
         return None
     mg = getattr(param, "main_grad", None)
     if mg is not None:
-        K.colsum_accum(dy2d, mg)
+        _side_run(dy2d.device, lambda: K.colsum_accum(dy2d, mg), dy2d)
         return None
     g = torch.zeros(dy2d.shape[1], dtype=torch.float32, device=dy2d.device)
     K.colsum_accum(dy2d, g)
