@@ -83,6 +83,10 @@ struct NormArgs {
 };
 void norm_fwd(const NormArgs& a, cudaStream_t stream);
 void norm_bwd(const NormArgs& a, cudaStream_t stream);
+// The two stages separately: stage 1 writes dx and the partial sums (and runs stage 2 itself when `reduce_stream` is
+// null); norm_bwd_reduce folds the partial sums into dgamma / dbeta.
+void norm_bwd_stage1(const NormArgs& a, cudaStream_t stream, const cudaStream_t* reduce_stream);
+void norm_bwd_reduce(const NormArgs& a, cudaStream_t stream);
 // Number of CTAs (and therefore partial-sum rows) the backward kernel uses for `rows` rows.
 int norm_bwd_num_partials(long long rows, int sm_count);
 

@@ -1,7 +1,9 @@
 // Tensor-facing glue: validates torch tensors, fills the raw launch structs of api.h and
 // launches on torch's current CUDA stream.  All math lives in the .cu files.
 #include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
 
 #include "api.h"
@@ -205,7 +207,7 @@ void norm_fwd(const Tensor& x, const Tensor& gamma, const OptTensor& beta, Tenso
 
 void norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, const OptTensor& mean,
               const Tensor& rstd, const OptTensor& dres, Tensor& dx, const OptTensor& dgamma,
-              const OptTensor& dbeta, bool rms) {
+              const OptTensor& dbeta, bool rms, int64_t reduce_stream) {
   check_bf16_cuda(dy, "norm dy");
   check_bf16_cuda(x, "norm x");
   check_bf16_cuda(dx, "norm dx");
@@ -238,7 +240,22 @@ void norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, const OptT
   a.n_partial = rt::norm_bwd_num_partials(a.rows, rt::sm_count(x.device().index()));
   at::Tensor partial = at::empty({2, a.n_partial, a.C}, x.options().dtype(at::kFloat));
   a.partial = partial.data_ptr<float>();
-  rt::norm_bwd(a, stream_of(x));
+  if (reduce_stream == 0) {
+    rt::norm_bwd(a, stream_of(x));
+    return;
+  }
+  // dgamma / dbeta have no consumer before the optimizer: their reduction goes to the caller's side stream, ordered
+  // after stage 1 by an event, and the partial sums are kept alive for it
+  cudaStream_t main_s = stream_of(x), side = reinterpret_cast<cudaStream_t>(reduce_stream);
+  rt::norm_bwd_stage1(a, main_s, &side);
+  static thread_local cudaEvent_t ev[64] = {nullptr};
+  const int dev = x.device().index();
+  if (ev[dev] == nullptr) C10_CUDA_CHECK(cudaEventCreateWithFlags(&ev[dev], cudaEventDisableTiming));
+  C10_CUDA_CHECK(cudaEventRecord(ev[dev], main_s));
+  C10_CUDA_CHECK(cudaStreamWaitEvent(side, ev[dev], 0));
+  rt::norm_bwd_reduce(a, side);
+  c10::cuda::CUDACachingAllocator::recordStream(partial.storage().data_ptr(),
+                                                c10::cuda::getStreamFromExternal(side, x.device().index()));
 }
 
 void embedding_fwd(const Tensor& idx, const Tensor& wte, const OptTensor& wpe, Tensor& out,
@@ -378,7 +395,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("lse"), pybind11::arg("delta"), pybind11::arg("dq"), pybind11::arg("dk"), pybind11::arg("dv"), pybind11::arg("causal"),
         pybind11::arg("scale"), pybind11::arg("dq_acc") = pybind11::none());
   m.def("norm_fwd", &norm_fwd);
-  m.def("norm_bwd", &norm_bwd);
+  m.def("norm_bwd", &norm_bwd, pybind11::arg("dy"), pybind11::arg("x"), pybind11::arg("gamma"), pybind11::arg("mean"), pybind11::arg("rstd"), pybind11::arg("dres"), pybind11::arg("dx"),
+        pybind11::arg("dgamma"), pybind11::arg("dbeta"), pybind11::arg("rms"), pybind11::arg("reduce_stream") = 0);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("cross_entropy", &cross_entropy);

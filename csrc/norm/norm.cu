@@ -480,7 +480,9 @@ int norm_bwd_num_partials(long long rows, int sm_count) {
   return (int)std::max<long long>(1, std::min<long long>(want, 2LL * sm_count));
 }
 
-void norm_bwd(const NormArgs& a, cudaStream_t stream) {
+// Stage 1 (dx and the per-CTA partial sums); with a null `reduce_stream` the second stage follows on `stream`, otherwise
+// the caller runs norm_bwd_reduce itself (on another stream, after an event) so that dx is not held up by it.
+void norm_bwd_stage1(const NormArgs& a, cudaStream_t stream, const cudaStream_t* reduce_stream) {
   RT_CHECK(a.C % 8 == 0, "norm: feature size must be a multiple of 8");
   RT_CHECK(a.C <= 16384, "norm backward: feature size above 16384 not supported");
   if (a.rows == 0) return;
@@ -512,11 +514,18 @@ void norm_bwd(const NormArgs& a, cudaStream_t stream) {
   } else if (a.rms) RT_NORM_BWD(true);
   else RT_NORM_BWD(false);
 #undef RT_NORM_BWD
+  if (reduce_stream == nullptr) norm_bwd_reduce(a, stream);
+}
+
+void norm_bwd_reduce(const NormArgs& a, cudaStream_t stream) {
+  if (a.rows == 0) return;
   if (a.dgamma != nullptr || (!a.rms && a.dbeta != nullptr)) {
     dim3 g2((a.C + 31) / 32, a.rms ? 1 : 2);
     norm_bwd_reduce_kernel<<<g2, 1024, 0, stream>>>(a.partial, a.dgamma, a.dbeta, a.n_partial, a.C);
     RT_LAUNCH_CHECK();
   }
 }
+
+void norm_bwd(const NormArgs& a, cudaStream_t stream) { norm_bwd_stage1(a, stream, nullptr); }
 
 }  // namespace rt

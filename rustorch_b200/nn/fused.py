@@ -68,6 +68,19 @@ def _side_run(device: torch.device, fn, *inputs) -> None:
     _side_used[idx] = True
 
 
+def _side_handle(device: torch.device, direct: bool) -> int:
+    """Raw handle of the side stream for kernels that order themselves after the main stream with an event (the second
+    stage of the norm backward); 0 when the gradients are returned to autograd instead of accumulated in place."""
+    if not (_SIDE_ON and direct and device.type == "cuda"):
+        return 0
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    side = _side_streams.get(idx)
+    if side is None:
+        side = _side_streams[idx] = torch.cuda.Stream(device=idx)
+    _side_used[idx] = True
+    return side.cuda_stream
+
+
 def _side_join() -> None:
     for idx, used in _side_used.items():
         if used:
@@ -172,7 +185,8 @@ class AttnBlockFn(torch.autograd.Function):
         g_bqkv = bgrad_into(dqkv, b_qkv)
         dh = K.gemm(dqkv, w_qkv, b_mn=True)                      # [B*T, C]
         wg, bg, direct = _norm_grad_bufs(ln_w, ln_b)
-        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dy2 if residual else None)
+        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dy2 if residual else None,
+                              reduce_stream=_side_handle(dh.device, direct))
         g_lnw = None if direct else wg.to(ln_w.dtype)
         g_lnb = None if (direct or ln_b is None) else bg.to(ln_b.dtype)
         _notify(w_proj, b_proj, w_qkv, b_qkv, ln_w, ln_b)
@@ -206,7 +220,8 @@ class MLPBlockFn(torch.autograd.Function):
         g_b1 = bgrad_into(dpre, b1)
         dh = K.gemm(dpre, w1, b_mn=True)
         wg, bg, direct = _norm_grad_bufs(ln_w, ln_b)
-        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dy2 if residual else None)
+        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dy2 if residual else None,
+                              reduce_stream=_side_handle(dh.device, direct))
         g_lnw = None if direct else wg.to(ln_w.dtype)
         g_lnb = None if (direct or ln_b is None) else bg.to(ln_b.dtype)
         _notify(w2, b2, w1, b1, ln_w, ln_b)
@@ -275,7 +290,7 @@ class LMHeadLossFn(torch.autograd.Function):
         g_head = wgrad_into(dlogits, h, w_head, alpha_dev=factor)
         dh = K.gemm(dlogits, w_head, b_mn=True, alpha_dev=factor)
         wg, bg, direct = _norm_grad_bufs(ln_w, ln_b)
-        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg)
+        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, reduce_stream=_side_handle(dh.device, direct))
         g_lnw = None if direct else wg.to(ln_w.dtype)
         g_lnb = None if (direct or ln_b is None) else bg.to(ln_b.dtype)
         _notify(w_head, ln_w, ln_b)

@@ -79,9 +79,11 @@ def layer_norm_fwd(x, gamma, beta, eps: float):
     return y, mean, rstd
 
 
-def layer_norm_bwd(dy, x, gamma, mean, rstd, dgamma, dbeta, dres=None):
+def layer_norm_bwd(dy, x, gamma, mean, rstd, dgamma, dbeta, dres=None, reduce_stream: int = 0):
+    """``reduce_stream``: raw handle of a CUDA stream that takes the second stage (partial sums -> dgamma / dbeta),
+    ordered after the first by an event; 0 keeps both stages on the current stream."""
     dx = torch.empty_like(x)
-    _C().norm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, False)
+    _C().norm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, False, int(reduce_stream))
     return dx
 
 
@@ -93,9 +95,9 @@ def rms_norm_fwd(x, gamma, eps: float):
     return y, rstd
 
 
-def rms_norm_bwd(dy, x, gamma, rstd, dgamma, dres=None):
+def rms_norm_bwd(dy, x, gamma, rstd, dgamma, dres=None, reduce_stream: int = 0):
     dx = torch.empty_like(x)
-    _C().norm_bwd(dy, x, gamma, None, rstd, dres, dx, dgamma, None, True)
+    _C().norm_bwd(dy, x, gamma, None, rstd, dres, dx, dgamma, None, True, int(reduce_stream))
     return dx
 
 
