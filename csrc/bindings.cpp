@@ -205,7 +205,7 @@ void norm_fwd(const Tensor& x, const Tensor& gamma, const OptTensor& beta, Tenso
   rt::norm_fwd(a, stream_of(x));
 }
 
-void norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, const OptTensor& mean,
+OptTensor norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, const OptTensor& mean,
               const Tensor& rstd, const OptTensor& dres, Tensor& dx, const OptTensor& dgamma,
               const OptTensor& dbeta, bool rms, int64_t reduce_stream) {
   check_bf16_cuda(dy, "norm dy");
@@ -242,10 +242,10 @@ void norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, const OptT
   a.partial = partial.data_ptr<float>();
   if (reduce_stream == 0) {
     rt::norm_bwd(a, stream_of(x));
-    return;
+    return c10::nullopt;
   }
   // dgamma / dbeta have no consumer before the optimizer: their reduction goes to the caller's side stream, ordered
-  // after stage 1 by an event, and the partial sums are kept alive for it
+  // after stage 1 by an event; the partial sums go back to the caller, who keeps them alive for it
   cudaStream_t main_s = stream_of(x), side = reinterpret_cast<cudaStream_t>(reduce_stream);
   rt::norm_bwd_stage1(a, main_s, &side);
   static thread_local cudaEvent_t ev[64] = {nullptr};
@@ -254,8 +254,7 @@ void norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, const OptT
   C10_CUDA_CHECK(cudaEventRecord(ev[dev], main_s));
   C10_CUDA_CHECK(cudaStreamWaitEvent(side, ev[dev], 0));
   rt::norm_bwd_reduce(a, side);
-  c10::cuda::CUDACachingAllocator::recordStream(partial.storage().data_ptr(),
-                                                c10::cuda::getStreamFromExternal(side, x.device().index()));
+  return partial;  // the caller holds it until its main stream has waited for the side stream
 }
 
 void embedding_fwd(const Tensor& idx, const Tensor& wte, const OptTensor& wpe, Tensor& out,

@@ -50,6 +50,8 @@ grad_ready_hook = None
 _SIDE_ON = os.environ.get("RUSTORCH_WGRAD_STREAM", "1") != "0"
 _side_streams = {}
 _side_used = {}
+_side_keep = {}   # tensors the side stream still reads: released after the join, never through record_stream (a host
+                  # that runs many steps ahead would otherwise leave the allocator with blocks it cannot reuse yet)
 
 
 def _side_run(device: torch.device, fn, *inputs) -> None:
@@ -63,9 +65,13 @@ def _side_run(device: torch.device, fn, *inputs) -> None:
     side.wait_stream(torch.cuda.current_stream(idx))      # the inputs were produced on the main stream
     with torch.cuda.stream(side):
         fn()
-    for t in inputs:                                       # their memory must outlive the side stream's reads
-        t.record_stream(side)
+    _side_keep.setdefault(idx, []).extend(inputs)          # their memory must outlive the side stream's reads
     _side_used[idx] = True
+
+
+def _side_hold(device: torch.device, *tensors) -> None:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    _side_keep.setdefault(idx, []).extend(t for t in tensors if t is not None)
 
 
 def _side_handle(device: torch.device, direct: bool) -> int:
@@ -81,11 +87,23 @@ def _side_handle(device: torch.device, direct: bool) -> int:
     return side.cuda_stream
 
 
+def _ln_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres, direct: bool):
+    """LayerNorm backward; when the parameter gradients are accumulated in place their reduction runs on the side
+    stream (nothing in backward reads them)."""
+    h = _side_handle(dh.device, direct)
+    if not h:
+        return K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dres)
+    dx, partial = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dres, reduce_stream=h)
+    _side_hold(dh.device, partial)
+    return dx
+
+
 def _side_join() -> None:
     for idx, used in _side_used.items():
         if used:
             torch.cuda.current_stream(idx).wait_stream(_side_streams[idx])
             _side_used[idx] = False
+            _side_keep.get(idx, []).clear()                # freed on the main stream, after its wait on the side stream
 
 
 def _notify(*params):
@@ -185,8 +203,7 @@ class AttnBlockFn(torch.autograd.Function):
         g_bqkv = bgrad_into(dqkv, b_qkv)
         dh = K.gemm(dqkv, w_qkv, b_mn=True)                      # [B*T, C]
         wg, bg, direct = _norm_grad_bufs(ln_w, ln_b)
-        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dy2 if residual else None,
-                              reduce_stream=_side_handle(dh.device, direct))
+        dx = _ln_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dy2 if residual else None, direct)
         g_lnw = None if direct else wg.to(ln_w.dtype)
         g_lnb = None if (direct or ln_b is None) else bg.to(ln_b.dtype)
         _notify(w_proj, b_proj, w_qkv, b_qkv, ln_w, ln_b)
@@ -220,8 +237,7 @@ class MLPBlockFn(torch.autograd.Function):
         g_b1 = bgrad_into(dpre, b1)
         dh = K.gemm(dpre, w1, b_mn=True)
         wg, bg, direct = _norm_grad_bufs(ln_w, ln_b)
-        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dres=dy2 if residual else None,
-                              reduce_stream=_side_handle(dh.device, direct))
+        dx = _ln_bwd(dh, x2, ln_w, mean, rstd, wg, bg, dy2 if residual else None, direct)
         g_lnw = None if direct else wg.to(ln_w.dtype)
         g_lnb = None if (direct or ln_b is None) else bg.to(ln_b.dtype)
         _notify(w2, b2, w1, b1, ln_w, ln_b)
@@ -290,7 +306,7 @@ class LMHeadLossFn(torch.autograd.Function):
         g_head = wgrad_into(dlogits, h, w_head, alpha_dev=factor)
         dh = K.gemm(dlogits, w_head, b_mn=True, alpha_dev=factor)
         wg, bg, direct = _norm_grad_bufs(ln_w, ln_b)
-        dx = K.layer_norm_bwd(dh, x2, ln_w, mean, rstd, wg, bg, reduce_stream=_side_handle(dh.device, direct))
+        dx = _ln_bwd(dh, x2, ln_w, mean, rstd, wg, bg, None, direct)
         g_lnw = None if direct else wg.to(ln_w.dtype)
         g_lnb = None if (direct or ln_b is None) else bg.to(ln_b.dtype)
         _notify(w_head, ln_w, ln_b)

@@ -83,7 +83,9 @@ def layer_norm_bwd(dy, x, gamma, mean, rstd, dgamma, dbeta, dres=None, reduce_st
     """``reduce_stream``: raw handle of a CUDA stream that takes the second stage (partial sums -> dgamma / dbeta),
     ordered after the first by an event; 0 keeps both stages on the current stream."""
     dx = torch.empty_like(x)
-    _C().norm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, False, int(reduce_stream))
+    partial = _C().norm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, False, int(reduce_stream))
+    if reduce_stream:
+        return dx, partial          # the caller keeps the partial sums alive until it has joined the side stream
     return dx
 
 
@@ -97,7 +99,9 @@ def rms_norm_fwd(x, gamma, eps: float):
 
 def rms_norm_bwd(dy, x, gamma, rstd, dgamma, dres=None, reduce_stream: int = 0):
     dx = torch.empty_like(x)
-    _C().norm_bwd(dy, x, gamma, None, rstd, dres, dx, dgamma, None, True, int(reduce_stream))
+    partial = _C().norm_bwd(dy, x, gamma, None, rstd, dres, dx, dgamma, None, True, int(reduce_stream))
+    if reduce_stream:
+        return dx, partial
     return dx
 
 
