@@ -51,6 +51,7 @@ struct GemmParams {
   int accumulate;  // fp32 only: C += result using red.global.add.f32 (required when split_k > 1)
   int split_k;
   int m_blocks, n_blocks, k_blocks;
+  int group;    // M-blocks per band of the tile order
   int ab_fp16;  // A and B are fp16 instead of bf16 (C must then be fp32)
   int* status;
 #ifdef RT_GEMM_PROF
@@ -94,9 +95,9 @@ __device__ __forceinline__ void decode_tile(int t, const GemmParams& p, int& spl
   int r = t - b * per_batch;
   split = r / tiles_per_mat;
   r -= split * tiles_per_mat;
-  // grouped ordering: walk N fastest inside bands of 8 M-blocks so co-resident CTAs share
-  // A and B tiles through L2.
-  constexpr int GROUP = 8;
+  // grouped ordering: M fastest inside bands of p.group M-blocks, so co-resident CTAs share A and B tiles through L2
+  // and B is swept from DRAM once per band (the host picks the band height, see gemm_bf16)
+  const int GROUP = p.group;
   const int band = GROUP * p.n_blocks;
   const int g = r / band;
   const int first_m = g * GROUP;
@@ -677,6 +678,16 @@ void gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
   p.m_blocks = pair ? (g.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M) : (g.M + BLOCK_M - 1) / BLOCK_M;
   p.n_blocks = (g.N + block_n - 1) / block_n;
   p.k_blocks = (g.K + BLOCK_K - 1) / BLOCK_K;
+  // Tile order: bands of `group` M-blocks, swept over all N-blocks.  B comes from DRAM once per band unless it stays in
+  // L2 between bands, which a B larger than a fraction of L2 next to a streaming output does not (measured on
+  // 16384 x 50304 x 768: 1.25 GB of DRAM reads for 102 MB of operands with bands of 8).  Then the band grows until
+  // its rows of A are ~12 MB: fewer sweeps of B, and the band's A still lives in L2 through its sweep.
+  {
+    const double b_bytes = 2.0 * g.N * g.K, a_block_bytes = 2.0 * (pair ? 2 * BLOCK_M : BLOCK_M) * g.K;
+    int group = 8;
+    if (b_bytes > 24.0 * 1024 * 1024) group = std::max(8, std::min(64, int(12.0 * 1024 * 1024 / a_block_bytes)));
+    p.group = std::min(group, std::max(1, p.m_blocks));
+  }
   int sk = std::min(g.split_k, std::max(1, p.k_blocks));
   // every split must own at least one k-block
   while (sk > 1 && ((p.k_blocks + sk - 1) / sk) * (sk - 1) >= p.k_blocks) --sk;
