@@ -212,6 +212,14 @@ __device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* tmap, const
                "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z), "r"(w)
                : "memory");
 }
+// TMA store of a shared-memory tile (laid out as the tensor map's box, 128-byte swizzle) to global memory; parts of
+// the box beyond the tensor's extents are not written.  Tracked by the bulk async-group of the issuing thread.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* tmap, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // All but the newest N bulk groups of this thread have finished READING their shared-memory source.
 template <int N>

@@ -52,6 +52,7 @@ struct GemmParams {
   int split_k;
   int m_blocks, n_blocks, k_blocks;
   int group;    // M-blocks per band of the tile order
+  int c_tma, aux_tma;  // bf16 C / aux tiles leave through TMA stores (tensor maps tmap_c / tmap_aux are valid)
   int ab_fp16;  // A and B are fp16 instead of bf16 (C must then be fp32)
   int* status;
 #ifdef RT_GEMM_PROF
@@ -109,8 +110,9 @@ __device__ __forceinline__ void decode_tile(int t, const GemmParams& p, int& spl
 
 template <int BLOCK_N, bool A_MN, bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                    const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_aux,
+                    const GemmParams p) {
   using S = GemmSmem<BLOCK_N, PAIR>;
   constexpr int STAGES = S::STAGES;
   // PAIR: launched as clusters of two CTAs.  p.m_blocks counts 256-row blocks; CTA `cta_rank` of the pair owns rows
@@ -353,6 +355,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       auto stage_put = [&](int piece, uint4 w) {
         *reinterpret_cast<uint4*>(wstage + lane * 128 + ((piece ^ (lane & 7)) << 4)) = w;
       };
+      // With a tensor map for the output the staged 32 x 64 tile leaves as ONE TMA store issued by lane 0 (the copy
+      // engine writes whole lines and clips rows / columns beyond the matrix); the warp only waits, before it refills
+      // the staging buffer, until the engine has read it.
+      auto stage_flush = [&](const CUtensorMap* tm, int n_first, int bz) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && m_warp < p.M) {
+          tma_store_3d(tm, wstage, n_first, m_warp, bz);
+          bulk_commit_group();
+        }
+      };
+      auto stage_free = [&]() {
+        if (lane == 0) bulk_wait_group_read<0>();
+        __syncwarp();
+      };
       int n_store = 0;  // first column of the 64-column group being stored (read by the checked build only)
       auto stage_store = [&](__nv_bfloat16* base, long long ld) {  // base: row m_warp, column n0
         const int piece = lane & 7;
@@ -379,6 +396,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tmem_ld_wait();
         if (staged_ok && n0 + 64 <= p.N) {
           n_store = n0;
+          if (p.c_tma) stage_free();
           uint4 keep[2][4];  // GELU_DUAL: the bf16 pre-activations, reused for the second output
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
@@ -423,8 +441,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           __syncwarp();
           __nv_bfloat16* c_base = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)b * p.c_batch_stride + (long long)m_warp * p.ldc + n0;
           if (p.epi_mode == EPI_GELU_DUAL) {
-            stage_store(p.aux + (long long)b * p.aux_batch_stride + (long long)m_warp * p.ld_aux + n0, p.ld_aux);
-            __syncwarp();
+            if (p.aux_tma) {
+              stage_flush(&tmap_aux, n0, b);
+              stage_free();
+            } else {
+              stage_store(p.aux + (long long)b * p.aux_batch_stride + (long long)m_warp * p.ld_aux + n0, p.ld_aux);
+              __syncwarp();
+            }
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -441,7 +464,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
             __syncwarp();
           }
-          stage_store(c_base, p.ldc);
+          if (p.c_tma) stage_flush(&tmap_c, n0, b);
+          else stage_store(c_base, p.ldc);
           continue;
         }
 #pragma unroll
@@ -562,6 +586,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         else mbar_arrive(&tmem_empty[acc]);
       }
     }
+    if (lane == 0) bulk_wait_group<0>();  // every TMA store of this warp has been performed
   }
 
   // Common exit: on abort give in-flight bulk copies time to land, then release TMEM.
@@ -580,8 +605,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 template <int BLOCK_N, bool A_MN, bool B_MN, bool PAIR>
-static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
-                        int device, cudaStream_t stream) {
+static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx,
+                        const GemmParams& p, int device, cudaStream_t stream) {
   using S = GemmSmem<BLOCK_N, PAIR>;
   auto kern = gemm_tcgen05_kernel<BLOCK_N, A_MN, B_MN, PAIR>;
   static int workers[64] = {0};  // persistent CTAs (or CTA pairs) that are resident at once on this device
@@ -630,10 +655,10 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
     at[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
     cfg.attrs = at;
     cfg.numAttrs = 2;
-    RT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
+    RT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tx, p));
     count_launch();
   } else {
-    launch_pdl(kern, dim3(n_workers), dim3(GEMM_THREADS), S::TOTAL, stream, ta, tb, p);
+    launch_pdl(kern, dim3(n_workers), dim3(GEMM_THREADS), S::TOTAL, stream, ta, tb, tc, tx, p);
     RT_LAUNCH_CHECK();
   }
 }
@@ -699,11 +724,30 @@ void gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
                           : make_tmap_2byte(g.a, K, M, B, g.lda, g.a_batch_stride, 64, BLOCK_M);
   CUtensorMap tb = g.b_mn ? make_tmap_2byte(g.b, N, K, B, g.ldb, g.b_batch_stride, 64, 64)
                           : make_tmap_2byte(g.b, K, N, B, g.ldb, g.b_batch_stride, 64, pair ? block_n / 2 : block_n);
+  // Output tiles through TMA stores: bf16 C (and aux for the dual-output GELU epilogue) with 16-byte aligned base and
+  // rows.  RUSTORCH_GEMM_TMA_STORE=0 keeps the per-lane stores.
+  static const bool tma_store_on = [] {
+    const char* e = std::getenv("RUSTORCH_GEMM_TMA_STORE");
+    return !(e && e[0] == '0');
+  }();
+  auto storable = [&](const void* base, long long ld, long long bstride) {
+    return tma_store_on && base != nullptr && (reinterpret_cast<uintptr_t>(base) & 15) == 0 && ld % 8 == 0 &&
+           (g.batch == 1 || bstride % 8 == 0);
+  };
+  CUtensorMap tc = ta, tx = ta;
+  if (!g.out_fp32 && storable(g.c, g.ldc, g.c_batch_stride)) {
+    tc = make_tmap_2byte(g.c, N, M, B, g.ldc, g.c_batch_stride, 64, 32);
+    p.c_tma = 1;
+  }
+  if (p.c_tma && g.epi_mode == EPI_GELU_DUAL && storable(g.aux, g.ld_aux, g.aux_batch_stride)) {
+    tx = make_tmap_2byte(g.aux, N, M, B, g.ld_aux, g.aux_batch_stride, 64, 32);
+    p.aux_tma = 1;
+  }
 #define RT_GEMM_DISPATCH(BN, PR)                                                              \
-  if (!g.a_mn && !g.b_mn) launch_gemm<BN, false, false, PR>(ta, tb, p, device, stream);       \
-  else if (!g.a_mn && g.b_mn) launch_gemm<BN, false, true, PR>(ta, tb, p, device, stream);    \
-  else if (g.a_mn && g.b_mn) launch_gemm<BN, true, true, PR>(ta, tb, p, device, stream);      \
-  else launch_gemm<BN, true, false, PR>(ta, tb, p, device, stream);
+  if (!g.a_mn && !g.b_mn) launch_gemm<BN, false, false, PR>(ta, tb, tc, tx, p, device, stream);       \
+  else if (!g.a_mn && g.b_mn) launch_gemm<BN, false, true, PR>(ta, tb, tc, tx, p, device, stream);    \
+  else if (g.a_mn && g.b_mn) launch_gemm<BN, true, true, PR>(ta, tb, tc, tx, p, device, stream);      \
+  else launch_gemm<BN, true, false, PR>(ta, tb, tc, tx, p, device, stream);
   if (pair) {
     RT_GEMM_DISPATCH(256, true)
   } else if (block_n == 256) {
