@@ -193,7 +193,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           const long long tp0 = GPROF_T();
-          if (!mbar_wait_idle(&empty_bar[s], ph ^ 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, ctl, p.status, RT_ERR_TIMEOUT_PRODUCER)) {
             ok = false;
             break;
           }
@@ -338,7 +338,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (PAIR) mb = mb * 2 + int(cta_rank);
       const uint32_t acc = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
-      if (!mbar_wait_idle(&tmem_full[acc], acc_ph, ctl, p.status, RT_ERR_TIMEOUT_EPILOGUE)) {
+      if (!mbar_wait(&tmem_full[acc], acc_ph, ctl, p.status, RT_ERR_TIMEOUT_EPILOGUE)) {
         ok = false;
         break;
       }
