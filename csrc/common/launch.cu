@@ -4,6 +4,7 @@
 
 #include <atomic>
 #include <mutex>
+#include <unordered_map>
 
 namespace rt {
 
@@ -98,9 +99,46 @@ int read_status(int device) {
   return v;
 }
 
+namespace {
+// A tensor map is a pure function of (base, extents, strides, box): the maps of one training or decode step recur every
+// step because the caching allocator hands the same addresses out again, so they are kept per host thread instead of
+// being encoded by the driver on every launch.
+struct TmapKey {
+  const void* base;
+  uint64_t d0, d1, d2, s1, s2;
+  uint32_t b0, b1;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && s1 == o.s1 && s2 == o.s2 && b0 == o.b0 && b1 == o.b1;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    for (uint64_t v : {k.d0, k.d1, k.d2, k.s1, k.s2, (uint64_t(k.b0) << 32) | k.b1}) h = (h ^ v) * 0x100000001B3ull + (h >> 29);
+    return size_t(h);
+  }
+};
+CUtensorMap encode_tmap_2byte(const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_elems,
+                              uint64_t stride2_elems, uint32_t b0, uint32_t b1);
+}  // namespace
+
 CUtensorMap make_tmap_2byte(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                             uint64_t stride1_elems, uint64_t stride2_elems, uint32_t b0,
                             uint32_t b1) {
+  thread_local std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  const TmapKey key{base, d0, d1, d2, stride1_elems, stride2_elems, b0, b1};
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  if (cache.size() >= 8192) cache.clear();
+  const CUtensorMap m = encode_tmap_2byte(base, d0, d1, d2, stride1_elems, stride2_elems, b0, b1);
+  cache.emplace(key, m);
+  return m;
+}
+
+namespace {
+CUtensorMap encode_tmap_2byte(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                              uint64_t stride1_elems, uint64_t stride2_elems, uint32_t b0,
+                              uint32_t b1) {
   RT_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base must be 16-byte aligned");
   RT_CHECK((stride1_elems * 2) % 16 == 0,
            "TMA row stride must be a multiple of 16 bytes (got " + std::to_string(stride1_elems) +
@@ -123,6 +161,7 @@ CUtensorMap make_tmap_2byte(const void* base, uint64_t d0, uint64_t d1, uint64_t
                " box=" + std::to_string(b0) + "," + std::to_string(b1));
   return m;
 }
+}  // namespace
 
 CUtensorMap make_tmap_2byte_4d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                                uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3, uint32_t b0,
