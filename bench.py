@@ -19,7 +19,7 @@ because the reference publishes no number for this metric.
 ``--impl reference`` looks for an installed reference (``baseline/_ref``) or a Rust toolchain to
 build it and reports ``unavailable`` with what it found.
 
-``--config resnet_ddp | llama_tp | gguf_decode`` runs the other headline configurations from
+``--config resnet_ddp | llama_tp | gguf_decode | mlp_cpu`` runs the other benchmark configurations from
 ``benchmarks/`` through the same entry point (same launch line, one JSON line each).
 """
 from __future__ import annotations
@@ -43,7 +43,7 @@ def parse():
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=12)
     ap.add_argument("--ddp-mode", default=os.environ.get("RUSTORCH_DDP_MODE", "auto"))
-    ap.add_argument("--config", default="gpt2_ddp", choices=["gpt2_ddp", "resnet_ddp", "llama_tp", "gguf_decode"])
+    ap.add_argument("--config", default="gpt2_ddp", choices=["gpt2_ddp", "resnet_ddp", "llama_tp", "gguf_decode", "mlp_cpu"])
     ap.add_argument("--no-library-arm", action="store_true", help="skip the in-process library timing (vs_baseline stays null)")
     ap.add_argument("--library-steps", type=int, default=0, help="timed steps of the library arm (0: as many as --steps, at most 20)")
     ap.add_argument("--no-library-compile", dest="library_compile", action="store_false",
@@ -75,13 +75,14 @@ def probe_reference() -> dict:
 
 
 def run_other_config(args, rest) -> int:
-    """resnet_ddp / llama_tp / gguf_decode: hand over to the benchmark module with the driver's steps and warm-up."""
+    """resnet_ddp / llama_tp / gguf_decode / mlp_cpu: hand over to the benchmark module with the driver's steps and warm-up."""
     import runpy
     root = os.path.dirname(os.path.abspath(__file__))
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "config": args.config, "unavailable": reference_unavailable_reason()}))
         return 0
-    script = {"resnet_ddp": "resnet_bench.py", "llama_tp": "llama_tp_bench.py", "gguf_decode": "decode_bench.py"}[args.config]
+    script = {"resnet_ddp": "resnet_bench.py", "llama_tp": "llama_tp_bench.py", "gguf_decode": "decode_bench.py",
+              "mlp_cpu": "mlp_cpu_bench.py"}[args.config]
     argv = [os.path.join(root, "benchmarks", script)]
     if args.config == "gguf_decode":
         argv += ["--tp", str(args.gpus)]
