@@ -86,3 +86,24 @@ def test_gguf_runtime_cache_equals_full_recompute(tmp_path):
     # tensor-parallel shards sum to the unsharded result
     r0 = llm.LlamaRuntime.from_gguf(p, device="cpu", tp_rank=0, tp_world=2)
     assert r0.h_local == 2 and r0.hkv_local == 1 and r0.layers[0].wo.in_features == 32
+
+
+def test_quant_linear_fused_projection_fallback_on_cpu():
+    """``QuantLinear.fused`` (RMSNorm prologue, residual or SwiGLU epilogue) away from the one-kernel CUDA path is the
+    same arithmetic through separate ops: checked against plain fp32 math on the dequantised weights."""
+    from rustorch_b200.formats import gguf
+    from rustorch_b200.llm import QuantLinear
+    torch.manual_seed(0)
+    q = QuantLinear.random(64, 128, gguf.GGMLType.Q4_0, 0.05, "cpu", seed=4)
+    W = q.dequantize()
+    x = torch.randn(3, 128)
+    nw = 1.0 + 0.1 * torch.randn(128)
+    res = torch.randn(3, 64)
+    h = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * nw
+    y = q.fused(x, norm_w=nw, eps=1e-5, residual=res)
+    assert torch.allclose(y, h @ W.t() + res, atol=1e-4, rtol=1e-4)
+    act = q.fused(x, norm_w=nw, eps=1e-5, swiglu=True)
+    t = h @ W.t()
+    assert act.shape == (3, 32)
+    assert torch.allclose(act, torch.nn.functional.silu(t[:, :32]) * t[:, 32:], atol=1e-4, rtol=1e-4)
+    assert torch.allclose(q.fused(x), x @ W.t(), atol=1e-4, rtol=1e-4)
