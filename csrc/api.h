@@ -432,6 +432,13 @@ struct QGemvFusedArgs {
   long long prefetch0_bytes = 0;
   const void* prefetch1 = nullptr;
   long long prefetch1_bytes = 0;
+  // rotary + KV-cache epilogue over [q; k; v] rows (interleaved pairs), when rope_pos is set
+  const int* rope_pos = nullptr;  // [M] positions
+  const int* rope_seq = nullptr;  // [M] sequence numbers
+  void* cache_k = nullptr;        // fp16 [n_seq][Hkv][T_max][D]
+  void* cache_v = nullptr;
+  int rope_H = 0, rope_Hkv = 0, rope_D = 0, rope_T_max = 0, rope_n_seq = 0;
+  float rope_theta = 10000.f;
 };
 bool q_gemv_fused_supported(int M, int N, int K, bool swiglu);
 void q_gemv_fused(const QGemvFusedArgs& a, cudaStream_t stream);

@@ -256,7 +256,9 @@ void q_gemv(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, 
 // y = epilogue(dequant(W) @ rmsnorm(x)); norm_w / residual optional; swiglu: W = [gate; up], y has N / 2 columns.
 void q_gemv_fused(const Tensor& qs, const Tensor& scales, const Tensor& x, Tensor& y, const c10::optional<Tensor>& norm_w, double eps,
                   const c10::optional<Tensor>& residual, bool q8, bool swiglu, const c10::optional<Tensor>& prefetch_qs,
-                  const c10::optional<Tensor>& prefetch_scales) {
+                  const c10::optional<Tensor>& prefetch_scales, const c10::optional<Tensor>& rope_pos,
+                  const c10::optional<Tensor>& rope_seq, const c10::optional<Tensor>& cache_k, const c10::optional<Tensor>& cache_v,
+                  int64_t n_head, double rope_theta) {
   check_f16(scales, "q_gemv_fused scales");
   check_f16(x, "q_gemv_fused x");
   check_f16(y, "q_gemv_fused y");
@@ -297,6 +299,25 @@ void q_gemv_fused(const Tensor& qs, const Tensor& scales, const Tensor& x, Tenso
   if (prefetch_scales.has_value() && prefetch_scales->is_cuda() && prefetch_scales->is_contiguous()) {
     a.prefetch1 = prefetch_scales->data_ptr();
     a.prefetch1_bytes = prefetch_scales->numel() * prefetch_scales->element_size();
+  }
+  if (rope_pos.has_value()) {
+    TORCH_CHECK(rope_seq.has_value() && cache_k.has_value() && cache_v.has_value(), "q_gemv_fused: rotary epilogue needs seq and both caches");
+    TORCH_CHECK(rope_pos->scalar_type() == at::kInt && rope_seq->scalar_type() == at::kInt && rope_pos->is_cuda() && rope_seq->is_cuda() &&
+                    rope_pos->numel() == a.M && rope_seq->numel() == a.M, "q_gemv_fused: int32 CUDA pos / seq, one per row");
+    check_f16(*cache_k, "q_gemv_fused cache_k");
+    check_f16(*cache_v, "q_gemv_fused cache_v");
+    TORCH_CHECK(cache_k->dim() == 4 && cache_k->is_contiguous() && cache_v->is_contiguous() && cache_v->sizes() == cache_k->sizes(),
+                "q_gemv_fused: caches [n_seq, Hkv, T_max, D], contiguous");
+    a.rope_pos = rope_pos->data_ptr<int>();
+    a.rope_seq = rope_seq->data_ptr<int>();
+    a.cache_k = cache_k->data_ptr();
+    a.cache_v = cache_v->data_ptr();
+    a.rope_H = int(n_head);
+    a.rope_Hkv = int(cache_k->size(1));
+    a.rope_T_max = int(cache_k->size(2));
+    a.rope_D = int(cache_k->size(3));
+    a.rope_n_seq = int(cache_k->size(0));
+    a.rope_theta = float(rope_theta);
   }
   c10::cuda::CUDAGuard guard(x.device());
   rt::q_gemv_fused(a, cur_stream(x.device().index()));
@@ -1036,7 +1057,9 @@ void register_extra_ops(pybind11::module_& m) {
   m.def("q_gemv_fused", &q_gemv_fused, "decode projection: RMSNorm prologue + dequant-fused GEMV + residual / SwiGLU epilogue",
         pybind11::arg("qs"), pybind11::arg("scales"), pybind11::arg("x"), pybind11::arg("y"), pybind11::arg("norm_w"), pybind11::arg("eps"),
         pybind11::arg("residual"), pybind11::arg("q8"), pybind11::arg("swiglu") = false, pybind11::arg("prefetch_qs") = pybind11::none(),
-        pybind11::arg("prefetch_scales") = pybind11::none());
+        pybind11::arg("prefetch_scales") = pybind11::none(), pybind11::arg("rope_pos") = pybind11::none(),
+        pybind11::arg("rope_seq") = pybind11::none(), pybind11::arg("cache_k") = pybind11::none(), pybind11::arg("cache_v") = pybind11::none(),
+        pybind11::arg("n_head") = 0, pybind11::arg("rope_theta") = 10000.0);
   m.def("q_gemm_tc", &q_gemm_tc, "dequant-fused Q4_0 / Q8_0 tcgen05 GEMM for up to 256 activation rows", pybind11::arg("qs"),
         pybind11::arg("scales"), pybind11::arg("x"), pybind11::arg("y"), pybind11::arg("bias"), pybind11::arg("residual"),
         pybind11::arg("q8"), pybind11::arg("partial"), pybind11::arg("counters"), pybind11::arg("path") = 0);

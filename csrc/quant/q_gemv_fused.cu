@@ -3,7 +3,8 @@
 //   h[m][k]  = x[m][k] * rsqrt(mean_k x[m][k]^2 + eps) * norm_w[k]     (optional prologue)
 //   t[m][n]  = sum_k dequant(W)[n][k] * h[m][k]
 //   y[m][n]  = t[m][n] (+ residual[m][n])                               (plain epilogue), or
-//   y[m][i]  = silu(t[m][i]) * t[m][ff + i]                             (SwiGLU epilogue over a [gate; up] matrix)
+//   y[m][i]  = silu(t[m][i]) * t[m][ff + i]                             (SwiGLU epilogue over a [gate; up] matrix), or
+//   y[m]     = [rope(q); rope(k); v] with k and v also appended to the KV cache   (rotary epilogue over [q; k; v])
 //
 // for M <= 4 activation rows.  A decode step of a Llama layer is then four of these (qkv, wo, gate/up, down) plus
 // the rotary / cache / attention kernels, instead of four GEMVs, two RMSNorm and one SwiGLU launch.
@@ -58,7 +59,20 @@ struct QfRaw {
   uint4 v[Q8 ? 2 : 1];
 };
 
-template <bool Q8, int M, bool SWIGLU>
+// Rotary epilogue of the fused q | k | v projection (pairs (2i, 2i + 1) of a head, as GGUF Llama weights expect): q and
+// k rows are rotated by the token's position, k and v rows are also appended to the KV cache.
+struct QfRope {
+  const int* pos;   // [M] position of each token in its sequence
+  const int* seq;   // [M] sequence (cache batch) index of each token
+  __half* cache_k;  // [n_seq][Hkv][T_max][D]
+  __half* cache_v;
+  int H, Hkv, D, T_max, n_seq;
+  float log2_theta;
+  int* status;
+};
+
+// EPI: 0 = plain / residual, 1 = SwiGLU over [gate; up] rows, 2 = rotary + KV-cache append over [q; k; v] rows
+template <bool Q8, int M, int EPI>
 __global__ void __launch_bounds__(QF_WARPS * 32, 2) q_gemv_fused_kernel(const void* __restrict__ qs, const __half* __restrict__ scales,
                                                                      const __half* __restrict__ x, long long ldx,
                                                                      const __half* __restrict__ norm_w, float eps,
@@ -66,7 +80,8 @@ __global__ void __launch_bounds__(QF_WARPS * 32, 2) q_gemv_fused_kernel(const vo
                                                                      const __half* __restrict__ residual, long long ldr,
                                                                      int N, int K, const uint8_t* __restrict__ pf0,
                                                                      long long pf0_bytes, const uint8_t* __restrict__ pf1,
-                                                                     long long pf1_bytes) {
+                                                                     long long pf1_bytes, const QfRope rope) {
+  constexpr bool SWIGLU = EPI == 1, ROPE = EPI == 2;
   extern __shared__ __align__(16) uint8_t qf_smem[];
   __shared__ float red[M][QF_WARPS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -80,8 +95,9 @@ __global__ void __launch_bounds__(QF_WARPS * 32, 2) q_gemv_fused_kernel(const vo
   constexpr int PER_ITEM = SWIGLU ? QF_R / 2 : QF_R;
   const long long all_warps = (long long)gridDim.x * QF_WARPS;
   const long long gw = (long long)blockIdx.x * QF_WARPS + warp;
-  const int u_begin = int(out_n * gw / all_warps);
-  const int u_end = int(out_n * (gw + 1) / all_warps);
+  // ROPE: ranges in whole items of four rows, so that a rotation pair never straddles two warps (N % 4 == 0)
+  const int u_begin = ROPE ? 4 * int((out_n >> 2) * gw / all_warps) : int(out_n * gw / all_warps);
+  const int u_end = ROPE ? 4 * int((out_n >> 2) * (gw + 1) / all_warps) : int(out_n * (gw + 1) / all_warps);
   const int spi = (nb + 31) >> 5;  // block-steps per item: lane l takes block l + 32 k in step k
 
   // The weight stream of a warp is one sequence of block-steps over all its items; the loads run QF_DEPTH steps
@@ -301,6 +317,38 @@ __global__ void __launch_bounds__(QF_WARPS * 32, 2) q_gemv_fused_kernel(const vo
                   y[m * ldy + n] = __float2half(g / (1.f + __expf(-g)) * up);
                 }
               }
+            } else if (ROPE) {
+#pragma unroll
+              for (int j2 = 0; j2 < 2; ++j2) {
+                const int n = cu + 2 * j2;                 // rows n, n + 1: one rotation pair (items are whole here)
+                const int qk_end = (rope.H + rope.Hkv) * rope.D, q_end = rope.H * rope.D;
+                const int d0 = n % rope.D;                 // even index inside the head
+                const float inv_freq = exp2f(-(float)d0 / (float)rope.D * rope.log2_theta);
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                  const int p = rope.pos[m], sq = rope.seq[m];
+                  const bool ok = p >= 0 && p < rope.T_max && sq >= 0 && sq < rope.n_seq;
+                  if (!ok) atomicCAS(rope.status, 0, RT_ERR_BOUNDS);   // reported; the cache is not touched
+                  // rounded to fp16 first, as the separate rotary kernel reads the projection's fp16 output
+                  const float a = __half2float(__float2half(acc[2 * j2][m])), b = __half2float(__float2half(acc[2 * j2 + 1][m]));
+                  __half ra = __float2half(a), rb = __float2half(b);
+                  if (n < qk_end) {
+                    float sn, cs;
+                    sincosf((float)p * inv_freq, &sn, &cs);
+                    ra = __float2half(a * cs - b * sn);
+                    rb = __float2half(a * sn + b * cs);
+                  }
+                  y[m * ldy + n] = ra;
+                  y[m * ldy + n + 1] = rb;
+                  if (n >= q_end && ok) {
+                    const bool is_k = n < qk_end;
+                    const int hk = (n - (is_k ? q_end : qk_end)) / rope.D;
+                    __half* dst = (is_k ? rope.cache_k : rope.cache_v) + (((long long)sq * rope.Hkv + hk) * rope.T_max + p) * rope.D + d0;
+                    dst[0] = ra;
+                    dst[1] = rb;
+                  }
+                }
+              }
             } else {
 #pragma unroll
               for (int r = 0; r < QF_R; ++r) {
@@ -327,9 +375,24 @@ __global__ void __launch_bounds__(QF_WARPS * 32, 2) q_gemv_fused_kernel(const vo
   }
 }
 
-template <bool Q8, int M, bool SWIGLU>
+template <bool Q8, int M, int EPI>
 static void launch_fused(const QGemvFusedArgs& a, cudaStream_t s) {
-  auto kern = q_gemv_fused_kernel<Q8, M, SWIGLU>;
+  constexpr bool SWIGLU = EPI == 1;
+  auto kern = q_gemv_fused_kernel<Q8, M, EPI>;
+  QfRope rope{};
+  if (EPI == 2) {
+    rope.pos = a.rope_pos;
+    rope.seq = a.rope_seq;
+    rope.cache_k = reinterpret_cast<__half*>(a.cache_k);
+    rope.cache_v = reinterpret_cast<__half*>(a.cache_v);
+    rope.H = a.rope_H;
+    rope.Hkv = a.rope_Hkv;
+    rope.D = a.rope_D;
+    rope.T_max = a.rope_T_max;
+    rope.n_seq = a.rope_n_seq;
+    rope.log2_theta = log2f(a.rope_theta);
+    rope.status = status_word(current_device());
+  }
   constexpr int RAW_B = Q8 ? 32 : 16;
   // int8 activations + per-block scale and sum, then the warps' cp.async rings
   const size_t smem = ((size_t(M) * (a.K + (a.K / 32) * 8) + 15) & ~size_t(15)) +
@@ -355,7 +418,7 @@ static void launch_fused(const QGemvFusedArgs& a, cudaStream_t s) {
   launch_pdl(kern, grid, block, smem, s, a.qs, reinterpret_cast<const __half*>(a.scales), reinterpret_cast<const __half*>(a.x),
              a.ldx, reinterpret_cast<const __half*>(a.norm_w), a.eps, reinterpret_cast<__half*>(a.y), a.ldy,
              reinterpret_cast<const __half*>(a.residual), a.ldr, a.N, a.K, reinterpret_cast<const uint8_t*>(a.prefetch0),
-             a.prefetch0_bytes, reinterpret_cast<const uint8_t*>(a.prefetch1), a.prefetch1_bytes);
+             a.prefetch0_bytes, reinterpret_cast<const uint8_t*>(a.prefetch1), a.prefetch1_bytes, rope);
   RT_LAUNCH_CHECK();
 }
 
@@ -372,10 +435,18 @@ void q_gemv_fused(const QGemvFusedArgs& a, cudaStream_t stream) {
   RT_CHECK((long long)a.N * (a.K / 32) < (1LL << 31), "q_gemv_fused: weight matrix too large for 32-bit block offsets");
   RT_CHECK((reinterpret_cast<uintptr_t>(a.prefetch0) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.prefetch1) & 15) == 0,
            "q_gemv_fused: prefetch ranges must be 16-byte aligned");
+  if (a.rope_pos != nullptr) {
+    RT_CHECK(!a.swiglu && a.residual == nullptr, "q_gemv_fused: the rotary epilogue excludes SwiGLU and the residual");
+    RT_CHECK(a.rope_D % 2 == 0 && a.rope_D > 0 && a.N == (a.rope_H + 2 * a.rope_Hkv) * a.rope_D && a.N % 4 == 0,
+             "q_gemv_fused: rotary epilogue needs N = (H + 2 Hkv) D rows, D even");
+    RT_CHECK(a.rope_seq != nullptr && a.cache_k != nullptr && a.cache_v != nullptr && a.rope_T_max > 0 && a.rope_n_seq > 0,
+             "q_gemv_fused: rotary epilogue needs positions, sequence numbers and both caches");
+  }
   if (a.N == 0) return;
 #define RT_QF(Q8, MM)                                           \
-  if (a.swiglu) launch_fused<Q8, MM, true>(a, stream);          \
-  else launch_fused<Q8, MM, false>(a, stream);
+  if (a.swiglu) launch_fused<Q8, MM, 1>(a, stream);             \
+  else if (a.rope_pos != nullptr) launch_fused<Q8, MM, 2>(a, stream); \
+  else launch_fused<Q8, MM, 0>(a, stream);
 #define RT_QF_M(Q8)                   \
   switch (a.M) {                      \
     case 1: RT_QF(Q8, 1) break;       \

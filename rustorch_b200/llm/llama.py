@@ -265,8 +265,16 @@ class LlamaRuntime:
         # residual add / SwiGLU as its epilogue (QuantLinear.fused)
         fuse = C is not None and self.tp_world == 1 and 1 <= n <= QuantLinear.FUSED_MAX_ROWS and x.dtype == torch.float16
         for li, L in enumerate(self.layers):
+            rope_done = False
             if fuse:
-                qkv = L.wqkv.fused(x, norm_w=L.attn_norm, eps=cfg.rms_eps)
+                if cfg.rope_interleaved and QuantLinear.ROPE_FUSED and L.wqkv.in_features % 64 == 0 and (H + 2 * Hkv) * D % 4 == 0:
+                    # rotary embedding and the cache append ride in the projection's epilogue
+                    qkv = L.wqkv.fused(x, norm_w=L.attn_norm, eps=cfg.rms_eps,
+                                       rope=dict(pos=pos32, seq=seq32, cache_k=cache.k[li], cache_v=cache.v[li], n_head=H,
+                                                 theta=cfg.rope_theta))
+                    rope_done = True
+                else:
+                    qkv = L.wqkv.fused(x, norm_w=L.attn_norm, eps=cfg.rms_eps)
             else:
                 if h is None:
                     h = self._rmsnorm(x, L.attn_norm)
@@ -275,7 +283,8 @@ class LlamaRuntime:
             k = qkv[:, H * D: (H + Hkv) * D].view(n, Hkv, D)
             v = qkv[:, (H + Hkv) * D:].view(n, Hkv, D)
             if C is not None:
-                C.rope_kv(q, k, v, cache.k[li], cache.v[li], pos32, seq32, cfg.rope_theta, cfg.rope_interleaved)
+                if not rope_done:
+                    C.rope_kv(q, k, v, cache.k[li], cache.v[li], pos32, seq32, cfg.rope_theta, cfg.rope_interleaved)
                 att = torch.empty((n, H, D), dtype=q.dtype, device=q.device)
                 if flash_bt is not None:
                     # prompt processing: causal attention among the new tokens on the tcgen05 flash kernel (fp16 I/O),

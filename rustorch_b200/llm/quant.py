@@ -152,15 +152,20 @@ class QuantLinear:
     FUSED_MAX_ROWS = 4 if os.environ.get("RUSTORCH_DECODE_FUSED", "1") != "0" else 0
 
     PREFETCH_NEXT = os.environ.get("RUSTORCH_DECODE_PREFETCH", "1") != "0"
+    # rotary embedding + cache append in the q | k | v projection's epilogue: one launch per layer less, but measured
+    # slower (571.7 against 587.8 tokens/s at batch 1: the rotation runs on one lane per warp at the kernel's tail), so
+    # it is opt-in
+    ROPE_FUSED = os.environ.get("RUSTORCH_DECODE_ROPE_FUSED", "0") == "1"
 
     def fused(self, x: torch.Tensor, norm_w: Optional[torch.Tensor] = None, eps: float = 1e-5,
               residual: Optional[torch.Tensor] = None, swiglu: bool = False,
-              prefetch: Optional["QuantLinear"] = None) -> torch.Tensor:
+              prefetch: Optional["QuantLinear"] = None, rope: Optional[dict] = None) -> torch.Tensor:
         """``epilogue(W @ rmsnorm(x))`` for ``x [n, in]``: ``norm_w`` applies RMSNorm to ``x`` first, ``residual`` is
         added to the result, ``swiglu`` treats the rows of ``W`` as ``[gate; up]`` and returns ``silu(gate) * up``
         (``out_features / 2`` columns).  Up to ``FUSED_MAX_ROWS`` rows on CUDA this is ONE kernel (decode steps);
         otherwise the same arithmetic through the separate kernels.  ``prefetch``: the projection that runs next; the
-        kernel asks the L2 for its weights while it works, so HBM keeps streaming across the kernel boundary."""
+        kernel asks the L2 for its weights while it works, so HBM keeps streaming across the kernel boundary.  ``rope``
+        (one-kernel path only): ``dict(pos, seq, cache_k, cache_v, n_head, theta)`` for a fused q | k | v projection."""
         n = x.shape[0]
         if (self.device.type == "cuda" and 1 <= n <= self.FUSED_MAX_ROWS and x.dtype == torch.float16
                 and self.in_features % 64 == 0):
@@ -170,7 +175,13 @@ class QuantLinear:
             pq = ps = None
             if prefetch is not None and self.PREFETCH_NEXT and prefetch.qs is not None:
                 pq, ps = prefetch.qs, prefetch.scales        # the kernel pulls the next projection's weights towards L2
-            C.q_gemv_fused(self.qs, self.scales, x2, y, norm_w, float(eps), residual, self.q8, swiglu, pq, ps)
+            if rope is not None:
+                # [q; k; v] projection: rotate q and k by the tokens' positions and append k, v to the cache in the
+                # kernel's epilogue (interleaved pairs only; the caller checks that)
+                C.q_gemv_fused(self.qs, self.scales, x2, y, norm_w, float(eps), None, self.q8, False, pq, ps,
+                               rope["pos"], rope["seq"], rope["cache_k"], rope["cache_v"], int(rope["n_head"]), float(rope["theta"]))
+            else:
+                C.q_gemv_fused(self.qs, self.scales, x2, y, norm_w, float(eps), residual, self.q8, swiglu, pq, ps)
             return y
         h = x
         if norm_w is not None:

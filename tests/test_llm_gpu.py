@@ -307,3 +307,38 @@ def test_cache_position_past_the_end_is_reported_not_written():
     C.rope_kv(q.clone(), k.clone(), v, ck, cv, pos, seq, 10000.0, True)
     _native.check_status()
     assert float(ck[0, :, 3].abs().max()) > 0.0
+
+
+@pytest.mark.parametrize("q8", [False, True])
+@pytest.mark.parametrize("M,H,Hkv,D", [(1, 4, 4, 64), (3, 8, 2, 128), (4, 2, 1, 32)])
+def test_fused_qkv_projection_with_rotary_epilogue_matches_separate_kernels(q8, M, H, Hkv, D):
+    """q | k | v projection with the rotary embedding and the cache append in its epilogue against the projection
+    kernel followed by the stand-alone rotary / append kernel: same outputs, same cache contents."""
+    from rustorch_b200 import _native
+    from rustorch_b200.formats import gguf
+    from rustorch_b200.llm import QuantLinear
+    C = _native.load(required=True)
+    K, T_max, B = 256, 24, 5
+    ty = gguf.GGMLType.Q8_0 if q8 else gguf.GGMLType.Q4_0
+    lin = QuantLinear.random((H + 2 * Hkv) * D, K, ty, 0.05, "cuda", seed=6)
+    x = (torch.randn(M, K, device="cuda") * 0.7).half()
+    nw = (1.0 + 0.1 * torch.randn(K, device="cuda")).half()
+    pos = torch.tensor([5, 0, 23, 11][:M], device="cuda", dtype=torch.int32)
+    seq = torch.tensor([4, 1, 0, 2][:M], device="cuda", dtype=torch.int32)
+    # separate kernels
+    y_ref = lin.fused(x, norm_w=nw, eps=1e-5)
+    ck_ref = torch.zeros(B, Hkv, T_max, D, device="cuda", dtype=torch.half)
+    cv_ref = torch.zeros_like(ck_ref)
+    q = y_ref[:, : H * D].view(M, H, D)
+    k = y_ref[:, H * D: (H + Hkv) * D].view(M, Hkv, D)
+    v = y_ref[:, (H + Hkv) * D:].view(M, Hkv, D)
+    C.rope_kv(q, k, v, ck_ref, cv_ref, pos, seq, 10000.0, True)
+    # one kernel
+    ck, cv = torch.zeros_like(ck_ref), torch.zeros_like(cv_ref)
+    n0 = _native.launch_count()
+    y = lin.fused(x, norm_w=nw, eps=1e-5, rope=dict(pos=pos, seq=seq, cache_k=ck, cache_v=cv, n_head=H, theta=10000.0))
+    assert _native.launch_count() == n0 + 1
+    _native.check_status()
+    assert torch.equal(y, y_ref)
+    assert torch.equal(ck, ck_ref) and torch.equal(cv, cv_ref)
+    assert float(ck.abs().max()) > 0 and float(cv.abs().max()) > 0
