@@ -156,6 +156,8 @@ def case_quant_decode():
             C.q_gemv(q.qs, q.scales, x, yv, None, None, qt == gguf.GGMLType.Q8_0, path=1)
             if M == 4:
                 C.q_gemv(q.qs, q.scales, x, yv, None, None, qt == gguf.GGMLType.Q8_0, path=2)
+            # decode projection in one kernel: RMSNorm prologue + dp4a GEMV + SwiGLU epilogue (rows as [gate; up])
+            q.fused(x, norm_w=torch.ones(4096, device="cuda", dtype=torch.half), eps=1e-5, swiglu=True)
         q((torch.randn(32, 4096, device="cuda") * 0.5).half())     # dequant-fused tcgen05 GEMM (batched decode), A from TMEM
         if qt == gguf.GGMLType.Q4_0:
             part, cnt = q._tc_buffers(32)                          # the shared-memory-A variant of the same GEMM
