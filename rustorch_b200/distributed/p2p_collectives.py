@@ -39,6 +39,21 @@ class P2PCollectives:
         self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.barrier = torch.zeros(2, dtype=torch.int32, device=self.device)
 
+    def reset(self) -> None:
+        """Re-arms the object after a call reported a timeout (a peer that never arrived).  A kernel that gave up
+        can leave its grid-barrier count, the call epoch and the peers' flag words out of step with the other
+        ranks, so every rank of the group calls this together: it clears the three, then meets at a host barrier
+        so that nobody launches against flags that a slower rank is still clearing."""
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(self.group)                      # no rank clears while a peer's kernel still writes flags
+        self.barrier.zero_()
+        self.epoch_dev.zero_()
+        self.flags.zero_()
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(self.group)
+
     def _pad(self, n: int, unit: int) -> int:
         return -(-n // unit) * unit
 
