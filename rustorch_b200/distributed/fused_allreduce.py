@@ -302,6 +302,38 @@ class FusedDDP:
         self._pending = list(self._bucket_need)
         self._launched = [False] * self.n_buckets
 
+    def _rearm(self) -> None:
+        """Clears the cross-rank flag words, the CTA counter and the bucket bookkeeping (all ranks together, between
+        two host barriers, so that nobody clears while a peer's kernel still signals and nobody launches against
+        flags that a slower rank has yet to clear).  The flag words hold step numbers and the kernels wait for
+        ``flag >= step``; they must therefore go back to zero whenever the step count can move backwards."""
+        if self.host:
+            self._pending = list(self._bucket_need)
+            self._launched = [False] * self.n_buckets
+            return
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self.flags.zero_()
+        self.done_counter.zero_()
+        self._pending = list(self._bucket_need)
+        self._launched = [False] * self.n_buckets
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+
+    def reset_after_timeout(self) -> None:
+        """Re-arms the object after a step reported a peer timeout.  CTAs that gave up leave the kernel before they
+        count themselves in ``done_counter``, so the next launch would see its "last CTA" early; the gradient
+        buffer may also hold slices that nobody cleared.  All ranks call this together, then restore a checkpoint
+        with ``load_state_dict`` (the step that timed out is lost) before they train on."""
+        self._rearm()
+        if not self.host:
+            self.flat.grad.zero_()
+            torch.cuda.synchronize(self.device)
+            if self.world > 1:
+                dist.barrier(group=self.group)
+
     def zero_grad(self, set_to_none: bool = False) -> None:
         """Gradients are zeroed by the bucket kernel itself; kept for API parity."""
 
@@ -357,6 +389,7 @@ class FusedDDP:
                 self.m.copy_(sd["exp_avg"].to(self.device))
             if self.v is not None and sd.get("exp_avg_sq") is not None:
                 self.v.copy_(sd["exp_avg_sq"].to(self.device))
+        self._rearm()                           # the step count may have moved backwards: flags back to zero
         if self.world > 1:
             dist.barrier(group=self.group)      # nobody launches a bucket into a peer that is still loading
 
