@@ -406,40 +406,7 @@ class ProfilerCore:
 
 
 # ------------------------------------------------------------------------------------------------ nn / autograd
-class RecurrentOps:
-    """What the RNN / LSTM / GRU layers share: state initialisation, direction handling, per-step cell math."""
-
-    @staticmethod
-    def init_state(num_layers: int, batch: int, hidden: int, bidirectional: bool = False, device=None, dtype=None) -> torch.Tensor:
-        return torch.zeros(num_layers * (2 if bidirectional else 1), batch, hidden, device=device, dtype=dtype)
-
-    @staticmethod
-    def to_time_major(x: torch.Tensor, batch_first: bool) -> torch.Tensor:
-        return x.transpose(0, 1) if batch_first else x
-
-    @staticmethod
-    def reverse_sequence(x: torch.Tensor) -> torch.Tensor:
-        return x.flip(0)
-
-    @staticmethod
-    def lstm_step(gates: torch.Tensor, c: torch.Tensor):
-        from .ops import rnn
-        return rnn.lstm_gates(gates, c)
-
-    @staticmethod
-    def gru_step(gi: torch.Tensor, gh: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
-        from .ops import rnn
-        return rnn.gru_gates(gi, gh, h)
-
-    @staticmethod
-    def run_cell(cell, x: torch.Tensor, state=None, reverse: bool = False):
-        """Unrolls a cell over a time-major sequence; returns (outputs [T, B, H], last state)."""
-        steps = range(x.shape[0] - 1, -1, -1) if reverse else range(x.shape[0])
-        outs = [None] * x.shape[0]
-        for t in steps:
-            state = cell(x[t], state)
-            outs[t] = state[0] if isinstance(state, tuple) else state
-        return torch.stack(outs, 0), state
+from .nn.recurrent_common import RecurrentOps  # noqa: E402,F401  (kept importable from here)
 
 
 class LinearBackward(torch.autograd.Function):

@@ -17,6 +17,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from . import fused
+from .conv_base import Validator
 
 # fp32 CUDA Linear layers run on the tcgen05 GEMM as three bf16 products (RUSTORCH_FP32_LINEAR=library: cuBLAS SGEMM)
 _FP32_NATIVE = os.environ.get("RUSTORCH_FP32_LINEAR", "native") != "library"
@@ -91,8 +92,7 @@ class _ConvNd(nn.Module):
         self.in_channels, self.out_channels = in_channels, out_channels
         self.kernel_size, self.stride, self.padding, self.dilation = tup(kernel_size), tup(stride), tup(padding), tup(dilation)
         self.groups = groups
-        if in_channels % groups or out_channels % groups:
-            raise ValueError("channels must be divisible by groups")
+        Validator.validate_conv_params(in_channels, out_channels, self.kernel_size, self.stride, self.padding, self.dilation, groups)
         fan_in = in_channels // groups * math.prod(self.kernel_size)
         kw = dict(device=device, dtype=dtype)
         # Kaiming normal, std = sqrt(2 / fan_in) (src/nn/conv2d.rs:77-130)
@@ -155,6 +155,9 @@ class _ConvTransposeNd(nn.Module):
         self.in_channels, self.out_channels, self.groups = in_channels, out_channels, groups
         self.kernel_size, self.stride, self.padding = tup(kernel_size), tup(stride), tup(padding)
         self.output_padding, self.dilation = tup(output_padding), tup(dilation)
+        Validator.validate_conv_params(in_channels, out_channels, self.kernel_size, self.stride, self.padding, self.dilation, groups)
+        if any(op >= max(st, d) for op, st, d in zip(self.output_padding, self.stride, self.dilation)):
+            raise ValueError("Output padding must be smaller than either stride or dilation")
         fan_in = in_channels * math.prod(self.kernel_size)
         kw = dict(device=device, dtype=dtype)
         self.weight = nn.Parameter(torch.empty(in_channels, out_channels // groups, *self.kernel_size, **kw)
@@ -417,6 +420,7 @@ class MaxPool2d(nn.MaxPool2d):
     """``(kernel, stride=kernel, padding=(0,0))`` (src/nn/pool2d.rs:34-40)."""
 
     def __init__(self, kernel_size: IntOrPair, stride: Optional[IntOrPair] = None, padding: IntOrPair = 0):
+        Validator.validate_pool_params(kernel_size, stride, padding)
         super().__init__(kernel_size, stride, padding)
 
     def forward(self, x):
@@ -425,6 +429,7 @@ class MaxPool2d(nn.MaxPool2d):
 
 class AvgPool2d(nn.AvgPool2d):
     def __init__(self, kernel_size: IntOrPair, stride: Optional[IntOrPair] = None, padding: IntOrPair = 0):
+        Validator.validate_pool_params(kernel_size, stride, padding)
         super().__init__(kernel_size, stride, padding)
 
     def forward(self, x):

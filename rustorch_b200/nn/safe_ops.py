@@ -1,9 +1,37 @@
 """Validated tensor / variable helpers (src/nn/safe_ops.rs:13-263)."""
 from __future__ import annotations
 
-from typing import Dict, Sequence
+import math
+from dataclasses import dataclass
+from typing import Sequence
 
 import torch
+
+
+@dataclass
+class TensorStats:
+    """Summary of a tensor's values (src/nn/safe_ops.rs:236-270); also indexable by field name."""
+    min: float
+    max: float
+    mean: float
+    variance: float
+    count: int
+    nan_count: int = 0
+    inf_count: int = 0
+
+    def std_dev(self) -> float:
+        return math.sqrt(self.variance) if self.variance >= 0 else float("nan")
+
+    def is_reasonable(self) -> bool:
+        return not (math.isinf(self.min) or math.isinf(self.max) or math.isnan(self.mean) or math.isnan(self.variance)) \
+            and self.variance >= 0
+
+    def __getitem__(self, key: str):
+        if key == "std":
+            return self.std_dev()
+        if key == "numel":
+            return self.count
+        return getattr(self, key)
 
 
 class SafeOps:
@@ -30,11 +58,12 @@ class SafeOps:
         return bool(torch.isfinite(t).all())
 
     @staticmethod
-    def get_stats(t: torch.Tensor) -> Dict[str, float]:
+    def get_stats(t: torch.Tensor) -> TensorStats:
+        if t.numel() == 0:
+            raise ValueError("Empty tensor")
         f = t.detach().float()
-        return {"mean": float(f.mean()), "std": float(f.std(unbiased=False)), "min": float(f.min()),
-                "max": float(f.max()), "numel": f.numel(),
-                "nan_count": int(torch.isnan(f).sum()), "inf_count": int(torch.isinf(f).sum())}
+        return TensorStats(float(f.min()), float(f.max()), float(f.mean()), float(f.var(unbiased=False)), f.numel(),
+                           int(torch.isnan(f).sum()), int(torch.isinf(f).sum()))
 
     @staticmethod
     def reshape(t: torch.Tensor, shape: Sequence[int]) -> torch.Tensor:
