@@ -56,6 +56,7 @@ def main():
     model = GPT(cfg, device=dev, dtype=torch.bfloat16, seed=3)
     losses = []
     nvls_used = False
+    rollback = None
     if mode == "public":
         # the public wrapper in fused mode: forward through the wrapper, step() instead of sync_gradients + optimizer
         from rustorch_b200.distributed.ddp import DistributedDataParallel
@@ -86,6 +87,24 @@ def main():
         full = ddp.gather_master()
         got = ddp.flat.named_views(full)
         n_buckets = ddp.n_buckets
+        if mode in ("fused", "fused_sgd"):
+            # roll back in place: two more steps, restore the state from before them (the step count, which the
+            # cross-rank flag words carry, goes back by two), repeat the same two steps
+            sd = ddp.state_dict()
+
+            def two_steps():
+                for s in (0, 1):
+                    b = data[s, rank]
+                    model(b[:, :-1], b[:, 1:]).backward()
+                    ddp.step()
+                _native.check_status()
+                return ddp.gather_master().clone()
+
+            first = two_steps()
+            ddp.load_state_dict(sd)
+            second = two_steps()
+            moved = (first - full).abs().mean().clamp_min(1e-12)
+            rollback = float((second - first).abs().mean() / moved)
         ddp.close()
     else:
         flat = FlatParams(model)
@@ -117,7 +136,8 @@ def main():
     per_name.sort(reverse=True)
     out = {"rank": rank, "world": world, "mode": mode, "n_buckets": n_buckets,
            "loss_ddp": [round(float(x), 4) for x in lt], "loss_ref": [round(x, 4) for x in ref_losses],
-           "worst_rel_update_diff": round(worst, 4), "nvls": nvls_used, "worst_params": per_name[:6]}
+           "worst_rel_update_diff": round(worst, 4), "nvls": nvls_used, "worst_params": per_name[:6],
+           "rollback_rel_diff": rollback}
     # one file per rank: lines printed by several ranks to a shared pipe can interleave
     with open(os.path.join(os.environ["DDP_RESULT_DIR"], f"rank{rank}.json"), "w") as f:
         json.dump(out, f)
