@@ -38,6 +38,7 @@ _LAZY = {
     "TrainingHistory": "models.high_level", "Model": "models.high_level", "ModelBuilder": "models.high_level",
     # utils of the binding
     **{n: "python_api" for n in ("Device", "Config", "ModelSerializer", "ModelComparator", "Transform", "Transforms", "DistributedConfig",
+                                 "DistributedBackend",
                                  "init_distributed", "cleanup_distributed", "set_seed", "cuda_is_available", "get_system_info")},
     "Profiler": "profiler", "Plotter": "visualization", "ModelVisualizer": "visualization", "TensorStats": "visualization",
     # errors, hybrid f32 universe, parallel traits, hardware hints, misc named pieces
@@ -60,7 +61,7 @@ _LAZY = {
                                   "CpuBackend", "GpuBackend", "BackendManager", "SelectionStrategy", "StreamOperation",
                                   "MetalKernelExecutor", "OpenClKernelExecutor", "OpenClMatrixExecutor", "CoreMLHybrid", "MacHybrid")},
     # distributed
-    **{n: "distributed" for n in ("DistributedDataParallel", "DistributedBackend", "DistributedSampler", "get_world_size", "get_rank",
+    **{n: "distributed" for n in ("DistributedDataParallel", "DistributedSampler", "get_world_size", "get_rank",
                                   "is_master", "DataParallel")},
 }
 _SUBMODULES = ("nn", "optim", "data", "training", "models", "distributed", "formats", "llm", "amp", "profiler", "debug", "validation",

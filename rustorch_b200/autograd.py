@@ -18,6 +18,7 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
+from ._interop import FlagValue, IntValue, ShapeValue
 from .tensor import Tensor, _unwrap
 
 _ids = itertools.count(1)
@@ -25,6 +26,13 @@ _ids = itertools.count(1)
 
 class Variable:
     """A tensor that records operations for reverse-mode differentiation."""
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        """Layers and ``torch`` functions accept a ``Variable`` and return ``Variable``s (python/src/lib.rs:377-452:
+        the reference's layers map Variable to Variable)."""
+        from ._interop import torch_function
+        return torch_function(cls, func, types, args, kwargs)
 
     def __init__(self, data, requires_grad: bool = False):
         t = _unwrap(data) if isinstance(data, (Tensor, torch.Tensor)) else torch.as_tensor(data, dtype=torch.float32)
@@ -42,15 +50,64 @@ class Variable:
     def from_tensor(cls, t, requires_grad: bool = False) -> "Variable":
         return cls(t, requires_grad)
 
+    # constructors of the Python binding (src/python/autograd.rs: from_data / zeros / ones / randn)
+    @classmethod
+    def from_data(cls, data, shape, requires_grad: bool = False) -> "Variable":
+        return cls(Tensor(list(data), shape), requires_grad)
+
+    @classmethod
+    def zeros(cls, shape, requires_grad: bool = False) -> "Variable":
+        return cls(torch.zeros(tuple(shape)), requires_grad)
+
+    @classmethod
+    def ones(cls, shape, requires_grad: bool = False) -> "Variable":
+        return cls(torch.ones(tuple(shape)), requires_grad)
+
+    @classmethod
+    def randn(cls, shape, requires_grad: bool = False) -> "Variable":
+        return cls(torch.randn(tuple(shape)), requires_grad)
+
+    def requires_grad_(self, requires_grad: bool = True) -> "Variable":
+        if self.tensor.is_leaf:
+            self.tensor.requires_grad_(requires_grad)
+        elif not requires_grad:
+            self.tensor = self.tensor.detach()
+        return self
+
+    @property
+    def numel(self) -> int:
+        return IntValue(self.tensor.numel())
+
+    def transpose(self, dim0: Optional[int] = None, dim1: Optional[int] = None) -> "Variable":
+        """Without arguments: the last two dimensions swapped (the binding's matrix transpose)."""
+        if dim0 is None and dim1 is None:
+            dim0, dim1 = -2, -1
+        return self._w(self.tensor.transpose(dim0, dim1))
+
+    def dot(self, other) -> "Variable":
+        return self._w((self.tensor.flatten() * _v(other).flatten()).sum())
+
+    def __copy__(self) -> "Variable":
+        return type(self)(self.tensor, self.tensor.requires_grad)            # same storage
+
+    def __deepcopy__(self, memo) -> "Variable":
+        return type(self)(self.tensor.detach().clone(), self.tensor.requires_grad)
+
+    # ``data`` / ``grad`` / ``requires_grad`` / ``shape`` are attributes as in the Python wheel
+    # (python/src/lib.rs:248-270); their values can also be called, which is the Rust spelling (``v.data()``).
+    # ``v.grad`` is None until a backward pass reached ``v``.
+    @property
     def data(self) -> Tensor:
         return Tensor(self.tensor.detach())
 
+    @property
     def grad(self) -> Optional[Tensor]:
         g = self.tensor.grad
         return None if g is None else Tensor(g)
 
+    @property
     def requires_grad(self) -> bool:
-        return self.tensor.requires_grad
+        return FlagValue(self.tensor.requires_grad)
 
     def zero_grad(self) -> None:
         self.tensor.grad = None
@@ -63,7 +120,7 @@ class Variable:
     backward_with_grad = backward
 
     def detach(self) -> "Variable":
-        return Variable(self.tensor.detach(), False)
+        return type(self)(self.tensor.detach(), False)
 
     def retain_grad(self) -> "Variable":
         if not self.tensor.is_leaf:
@@ -74,17 +131,18 @@ class Variable:
         return self.tensor.register_hook(lambda g: _unwrap(fn(Tensor(g))) if fn(Tensor(g)) is not None else None)
 
     def clone(self) -> "Variable":
-        return Variable(self.tensor.clone())
+        return type(self)(self.tensor.clone())
 
+    @property
     def shape(self) -> Tuple[int, ...]:
-        return tuple(self.tensor.shape)
+        return ShapeValue(self.tensor.shape)
 
     def item(self) -> float:
         return float(self.tensor.item())
 
     # differentiable ops
     def _w(self, t: torch.Tensor) -> "Variable":
-        return Variable(t)
+        return type(self)(t)
 
     def __add__(self, o):
         return self._w(self.tensor + _v(o))
@@ -141,7 +199,7 @@ class Variable:
         if callable(attr):
             def call(*a, **k):
                 r = attr(*[_v(x) for x in a], **{kk: _v(x) for kk, x in k.items()})
-                return Variable(r) if isinstance(r, torch.Tensor) else r
+                return self._w(r) if isinstance(r, torch.Tensor) else r
             return call
         return attr
 

@@ -8,11 +8,12 @@ reference, plus Python iteration.  ``with_options`` adds ``num_workers`` (thread
 """
 from __future__ import annotations
 
-import queue
 import threading
 from typing import Callable, Iterator, List, Optional, Sequence, Tuple
 
 import torch
+
+from .._interop import IntValue
 
 
 # ------------------------------------------------------------------- datasets
@@ -56,11 +57,33 @@ class TensorDataset(Dataset):
     def from_features_targets(cls, features, targets) -> "TensorDataset":
         return cls(features, targets)
 
+    @classmethod
+    def from_tensors(cls, tensors) -> "TensorDataset":
+        return cls(*tensors)
+
     def __len__(self):
         return self.tensors[0].shape[0]
 
     def __getitem__(self, i):
+        if not -len(self) <= i < len(self):
+            raise IndexError(f"index {i} outside a dataset of {len(self)}")
         return tuple(t[i] for t in self.tensors)
+
+    def get_batch(self, indices: Sequence[int]):
+        """One entry per tensor of the dataset, each the rows ``indices`` stacked (src/python/data.rs get_batch)."""
+        idx = torch.as_tensor(list(indices), dtype=torch.long)
+        return tuple(t[idx.to(t.device)] for t in self.tensors)
+
+    # first / last tensor under the names of the Python binding; attribute or call (src/python/data.rs)
+    @property
+    def data(self):
+        from ..tensor import Tensor
+        return Tensor(self.tensors[0])
+
+    @property
+    def targets(self):
+        from ..tensor import Tensor
+        return Tensor(self.tensors[-1])
 
 
 class ConcatDataset(Dataset):
@@ -250,9 +273,21 @@ class DataLoader:
                  collate_fn: Callable = default_collate, shuffle: bool = False, prefetch: int = 2):
         self.dataset = dataset
         self.sampler = sampler or (RandomSampler(len(dataset)) if shuffle else SequentialSampler(len(dataset)))
-        self.batch_size, self.drop_last = batch_size, drop_last
+        if int(batch_size) <= 0:
+            raise ValueError("batch_size must be positive")
+        self._batch_size, self.drop_last = int(batch_size), drop_last
         self.num_workers, self.pin_memory, self.collate_fn, self.prefetch = num_workers, pin_memory, collate_fn, prefetch
         self._it: Optional[Iterator] = None
+        self._served = 0
+
+    @property
+    def batch_size(self) -> int:
+        """Attribute, or ``loader.batch_size()`` as in the Python binding."""
+        return IntValue(self._batch_size)
+
+    @batch_size.setter
+    def batch_size(self, n: int) -> None:
+        self._batch_size = int(n)
 
     @classmethod
     def with_options(cls, dataset, sampler, batch_size, drop_last=False, num_workers=0, pin_memory=False,
@@ -272,22 +307,30 @@ class DataLoader:
             for idx in self._batches():
                 yield self._load(idx)
             return
-        # threaded prefetch that preserves batch order
-        q: "queue.Queue" = queue.Queue(maxsize=max(1, self.prefetch) * self.num_workers)
+        # threaded prefetch that preserves batch order; the workers stay at most ``prefetch * num_workers`` batches
+        # ahead of the consumer, and stop when the consumer abandons the iterator
+        window = max(1, self.prefetch) * self.num_workers
         index_list = list(self._batches())
         results = {}
-        lock = threading.Lock()
-        cond = threading.Condition(lock)
-        next_job = [0]
+        cond = threading.Condition()
+        state = {"next": 0, "consumed": 0, "stop": False, "error": None}
 
         def worker():
             while True:
-                with lock:
-                    j = next_job[0]
-                    if j >= len(index_list):
+                with cond:
+                    while not state["stop"] and state["next"] < len(index_list) and state["next"] - state["consumed"] >= window:
+                        cond.wait()
+                    if state["stop"] or state["next"] >= len(index_list):
                         return
-                    next_job[0] += 1
-                b = self._load(index_list[j])
+                    j = state["next"]
+                    state["next"] += 1
+                try:
+                    b = self._load(index_list[j])
+                except BaseException as e:  # noqa: BLE001  (handed to the consumer, which re-raises it)
+                    with cond:
+                        state["error"], state["stop"] = e, True
+                        cond.notify_all()
+                    return
                 with cond:
                     results[j] = b
                     cond.notify_all()
@@ -295,13 +338,21 @@ class DataLoader:
         threads = [threading.Thread(target=worker, daemon=True) for _ in range(self.num_workers)]
         for t in threads:
             t.start()
-        for j in range(len(index_list)):
+        try:
+            for j in range(len(index_list)):
+                with cond:
+                    while j not in results and state["error"] is None:
+                        cond.wait()
+                    if state["error"] is not None:
+                        raise state["error"]
+                    b = results.pop(j)
+                    state["consumed"] = j + 1
+                    cond.notify_all()
+                yield b
+        finally:
             with cond:
-                while j not in results:
-                    cond.wait()
-                b = results.pop(j)
-            yield b
-        del q
+                state["stop"] = True
+                cond.notify_all()
 
     def __len__(self):
         return len(BatchSampler(self.sampler, self.batch_size, self.drop_last))
@@ -310,14 +361,28 @@ class DataLoader:
     def next_batch(self):
         if self._it is None:
             self._it = iter(self)
+            self._served = 0
         try:
-            return next(self._it)
+            b = next(self._it)
+            self._served += 1
+            return b
         except StopIteration:
             self._it = None
             return None
 
     def reset(self) -> None:
         self._it = None
+        self._served = 0
+
+    def num_batches(self) -> int:
+        return len(self)
+
+    def current_batch_index(self) -> int:
+        """Batches handed out by ``next_batch`` since the last ``reset``."""
+        return self._served
+
+    def has_next(self) -> bool:
+        return self._served < len(self)
 
     def is_empty(self) -> bool:
         return len(self.dataset) == 0

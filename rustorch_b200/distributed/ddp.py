@@ -296,6 +296,8 @@ class DistributedSampler:
         s = self.rank * self.num_samples
         return idx[s:s + self.num_samples]
 
+    get_indices = sample_indices            # name in the Python binding (src/python/distributed.rs)
+
     def __iter__(self) -> Iterator[int]:
         return iter(self.sample_indices())
 

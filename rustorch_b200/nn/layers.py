@@ -621,3 +621,8 @@ class Hardswish(nn.Hardswish):
 class Softplus(nn.Softplus):
     def forward(self, x):
         return softplus(x, self.beta, self.threshold)
+
+
+from .._interop import accept_wrappers as _accept_wrappers  # noqa: E402
+
+_accept_wrappers(globals())       # forward() of the layers above also takes this package's Tensor / Variable

@@ -219,3 +219,8 @@ class CosineEmbeddingLoss(_Loss):
 
     def forward(self, x1, x2, target):
         return cosine_embedding_loss(x1, x2, target, self.margin, self.reduction)
+
+
+from .._interop import accept_wrappers as _accept_wrappers  # noqa: E402
+
+_accept_wrappers(globals())       # forward() of the layers above also takes this package's Tensor / Variable

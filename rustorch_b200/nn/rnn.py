@@ -220,3 +220,8 @@ class GRU(_RecurrentBase):
     def _run(self, x, state, params, reverse):
         w_ih, w_hh, b_ih, b_hh = params
         return _seq.gru_layer(x, state[0], w_ih, w_hh, b_ih, b_hh, reverse)
+
+
+from .._interop import accept_wrappers as _accept_wrappers  # noqa: E402
+
+_accept_wrappers(globals())       # forward() of the layers above also takes this package's Tensor / Variable

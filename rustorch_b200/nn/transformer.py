@@ -291,3 +291,8 @@ class Transformer(nn.Module):
     def generate_square_subsequent_mask(size: int, device=None) -> torch.Tensor:
         """Lower-triangular 1/0 mask (1 = may attend)."""
         return torch.ones(size, size, device=device).tril()
+
+
+from .._interop import accept_wrappers as _accept_wrappers  # noqa: E402
+
+_accept_wrappers(globals())       # forward() of the layers above also takes this package's Tensor / Variable

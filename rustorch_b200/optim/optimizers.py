@@ -16,6 +16,8 @@ from typing import Iterable, Optional
 import torch
 from torch.optim import Optimizer as _TorchOptimizer
 
+from .._interop import FlagValue, FloatValue, IntValue
+
 
 class _RefAPI:
     """Reference accessor names on top of torch's param_groups, and the native multi-tensor ``step``."""
@@ -44,8 +46,57 @@ class _RefAPI:
                 return
         raise NotImplementedError
 
+    # attributes in the Python wheel (python/src/lib.rs:502-505, 731-770), calls in Rust: the values answer both
+    @property
     def learning_rate(self) -> float:
-        return float(self.param_groups[0]["lr"])
+        return FloatValue(self.param_groups[0]["lr"])
+
+    def _hyper(self, key: str):
+        try:
+            return self.param_groups[0][key]
+        except KeyError:
+            raise AttributeError(f"{type(self).__name__} has no hyper-parameter {key!r}") from None
+
+    @property
+    def beta1(self) -> float:
+        return FloatValue(self._hyper("betas")[0])
+
+    @property
+    def beta2(self) -> float:
+        return FloatValue(self._hyper("betas")[1])
+
+    @property
+    def eps(self) -> float:
+        return FloatValue(self._hyper("eps"))
+
+    @property
+    def weight_decay(self) -> float:
+        return FloatValue(self._hyper("weight_decay"))
+
+    @property
+    def momentum(self) -> float:
+        return FloatValue(self._hyper("momentum"))
+
+    @property
+    def nesterov(self) -> bool:
+        return FlagValue(bool(self._hyper("nesterov")))
+
+    @property
+    def amsgrad(self) -> bool:
+        return FlagValue(bool(self._hyper("amsgrad")))
+
+    def param_count(self) -> int:
+        """Number of parameter tensors the optimizer steps (src/python/optim.rs param_count)."""
+        return sum(len(g["params"]) for g in self.param_groups)
+
+    @property
+    def step_count(self) -> int:
+        """Steps taken so far (the largest per-parameter step in the optimizer state)."""
+        n = 0
+        for st in self.state.values():
+            v = st.get("step", 0) if isinstance(st, dict) else 0
+            n = max(n, int(v.item()) if isinstance(v, torch.Tensor) else int(v))
+        return IntValue(n)
 
     def set_learning_rate(self, lr: float) -> None:
         for g in self.param_groups:

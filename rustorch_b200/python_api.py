@@ -198,6 +198,63 @@ def init_distributed(config: Optional[DistributedConfig] = None) -> None:
     api.init_process_group(c.backend, c.init_method, c.world_size, c.rank, c.timeout_s)
 
 
+class DistributedBackend:
+    """The binding's back-end object (src/python/distributed.rs:169-297): holds the back-end name and drives the
+    process group and the basic collectives.  ``DistributedBackend("nccl")``; the enumeration of back-end kinds is
+    ``rustorch_b200.distributed.DistributedBackend``.  Collectives accept ``torch.Tensor``, ``Tensor`` or
+    ``Variable`` and work in place on the wrapped tensor, returning their argument."""
+
+    def __init__(self, backend_type: Optional[str] = None):
+        from .distributed.api import DistributedBackend as Kind
+        self.backend_type = Kind.parse(backend_type or ("nccl" if torch.cuda.is_available() else "gloo")).value
+
+    @property
+    def value(self) -> str:
+        return self.backend_type
+
+    def init_process_group(self, config: Optional[DistributedConfig] = None) -> None:
+        c = config or DistributedConfig(backend=self.backend_type, world_size=int(os.environ.get("WORLD_SIZE", "1")),
+                                        rank=int(os.environ.get("RANK", "0")))
+        if c.backend != self.backend_type:
+            c = DistributedConfig(**{**c.__dict__, "backend": self.backend_type})
+        init_distributed(c)
+
+    def destroy_process_group(self) -> None:
+        cleanup_distributed()
+
+    def is_initialized(self) -> bool:
+        from .distributed import api
+        return api.is_initialized()
+
+    def barrier(self) -> None:
+        from .distributed import api
+        api.barrier()
+
+    @staticmethod
+    def _raw(t) -> torch.Tensor:
+        if isinstance(t, torch.Tensor):
+            return t
+        from .autograd import Variable
+        return t.tensor if isinstance(t, Variable) else t.data
+
+    def all_reduce(self, tensor, op: str = "sum"):
+        from .distributed import api
+        api.all_reduce(self._raw(tensor), api.ReduceOp(op))
+        return tensor
+
+    def all_gather(self, tensor) -> list:
+        from .distributed import api
+        return api.all_gather(self._raw(tensor))
+
+    def broadcast(self, tensor, src: int = 0):
+        from .distributed import api
+        api.broadcast(self._raw(tensor), src)
+        return tensor
+
+    def __repr__(self) -> str:
+        return f"DistributedBackend(backend='{self.backend_type}', initialized={self.is_initialized()})"
+
+
 def cleanup_distributed() -> None:
     from .distributed import api
     api.destroy_process_group()

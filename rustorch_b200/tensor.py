@@ -17,6 +17,7 @@ from typing import Iterable, List, Optional, Sequence, Tuple, Union
 import numpy as np
 import torch
 
+from ._interop import FlagValue, IntValue, ShapeValue
 from .dtype import DType, to_torch_dtype
 
 Number = Union[int, float]
@@ -86,6 +87,13 @@ def _wrap(x):
 class Tensor:
     __slots__ = ("data",)
     __array_priority__ = 100
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        """``torch.*`` / ``torch.nn.functional.*`` calls and ``torch.nn`` layers accept a ``Tensor``: the call runs on
+        the wrapped tensors and tensor results come back wrapped."""
+        from ._interop import torch_function
+        return torch_function(cls, func, types, args, kwargs)
 
     # ------------------------------------------------------------ construction
     def __init__(self, data=None, shape: Optional[Sequence[int]] = None, dtype=None, device=None,
@@ -198,17 +206,25 @@ class Tensor:
         return tuple(Tensor(t) for t in torch.meshgrid(*[_unwrap(t) for t in tensors], indexing=indexing))
 
     # --------------------------------------------------------------- accessors
+    # ``shape`` / ``ndim`` / ``numel`` / ``requires_grad`` read as attributes (the Python wheel) or as calls (Rust)
+    @property
     def shape(self) -> Tuple[int, ...]:
-        return tuple(self.data.shape)
+        return ShapeValue(self.data.shape)
 
+    @property
     def ndim(self) -> int:
-        return self.data.dim()
+        return IntValue(self.data.dim())
+
+    def __call__(self) -> "Tensor":
+        """``v.data()`` and ``v.grad()`` (Rust spelling) on the attribute values ``v.data`` / ``v.grad`` (wheel spelling)."""
+        return self
 
     def size(self) -> Tuple[int, ...]:
         return tuple(self.data.shape)
 
+    @property
     def numel(self) -> int:
-        return self.data.numel()
+        return IntValue(self.data.numel())
 
     def len(self) -> int:
         return self.data.numel()
@@ -223,8 +239,9 @@ class Tensor:
     def dtype(self) -> DType:
         return DType.from_torch(self.data.dtype)
 
+    @property
     def requires_grad(self) -> bool:
-        return self.data.requires_grad
+        return FlagValue(self.data.requires_grad)
 
     def set_requires_grad(self, flag: bool = True) -> "Tensor":
         self.data.requires_grad_(flag)
@@ -446,6 +463,19 @@ class Tensor:
 
     def __float__(self):
         return float(self.data)
+
+    def __int__(self):
+        return int(self.data)
+
+    def __bool__(self):
+        return bool(self.data)
+
+    def __format__(self, spec: str) -> str:
+        """One-element tensors format like the number they hold (``f"{loss:.3f}"``: the binding's sum / mean / losses
+        are plain floats, python/src/lib.rs:150-165)."""
+        if spec and self.data.numel() == 1:
+            return format(self.data.item(), spec)
+        return str(self) if not spec else format(str(self), spec)
 
     # ------------------------------------------------------------------ matrix
     def matmul(self, other) -> "Tensor":

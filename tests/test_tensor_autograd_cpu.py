@@ -89,7 +89,7 @@ def test_variable_backward_and_hooks():
     assert x.grad().as_slice() == [1.0, 0.5, 1.0, 0.5]
     assert w.grad().as_slice() == [8.0, 12.0]
     x.zero_grad()
-    assert x.grad() is None
+    assert x.grad is None
     with no_grad():
         z = x * 2.0
     assert not z.requires_grad()
