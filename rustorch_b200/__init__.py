@@ -35,7 +35,7 @@ _LAZY = {
     # data / training / models
     **{n: "data" for n in ("Dataset", "TensorDataset", "DataLoader", "RandomSampler", "SequentialSampler", "BatchSampler")},
     **{n: "training" for n in ("Trainer", "TrainerConfig", "TrainerBuilder", "EarlyStopping", "CheckpointManager")},
-    "TrainingHistory": "models.high_level", "Model": "models.high_level", "ModelBuilder": "models.high_level",
+    "TrainingHistory": "models.high_level", "Model": ("models.high_level", "BindingModel"), "ModelBuilder": "models.high_level",
     # utils of the binding
     **{n: "python_api" for n in ("Device", "Config", "ModelSerializer", "ModelComparator", "Transform", "Transforms", "DistributedConfig",
                                  "DistributedBackend",
@@ -90,7 +90,8 @@ def __getattr__(name):
     mod = _LAZY.get(name)
     if mod is None:
         raise AttributeError(f"module '{__name__}' has no attribute '{name}'")
-    return getattr(importlib.import_module(f"{__name__}.{mod}"), name)
+    mod, attr = mod if isinstance(mod, tuple) else (mod, name)      # (module, name there) when the two differ
+    return getattr(importlib.import_module(f"{__name__}.{mod}"), attr)
 
 
 def __dir__():

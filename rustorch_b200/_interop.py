@@ -49,6 +49,21 @@ class FloatValue(float):
         return float(self)
 
 
+class StrValue(str):
+    def __call__(self):
+        return str(self)
+
+
+class ListValue(list):
+    def __call__(self):
+        return list(self)
+
+
+class DictValue(dict):
+    def __call__(self):
+        return dict(self)
+
+
 class FlagValue(int):
     """A boolean (``bool`` cannot be subclassed)."""
 

@@ -17,6 +17,7 @@ from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple, Un
 import torch
 import torch.nn as nn
 
+from .._interop import DictValue, FloatValue, ListValue
 from ..data import DataLoader, RandomSampler, SequentialSampler, TensorDataset
 
 
@@ -60,17 +61,67 @@ class FitConfig:
 
 @dataclass
 class TrainingHistory:
-    loss: List[float] = field(default_factory=list)
-    val_loss: List[float] = field(default_factory=list)
-    metrics: Dict[str, List[float]] = field(default_factory=dict)
-    epoch_time_s: List[float] = field(default_factory=list)
+    """Per-epoch record of a ``fit``.  The binding's accessors (src/python/training.rs:66-117: ``train_loss()``,
+    ``val_loss()``, ``metrics()``, ``training_time()``, ``best_val_loss()``, ``best_epoch()``, ``summary()``,
+    ``plot_data()``) read the same lists; list / dict / float members can be read as attributes or called."""
+    loss: List[float] = field(default_factory=ListValue)
+    val_loss: List[float] = field(default_factory=ListValue)
+    metrics: Dict[str, List[float]] = field(default_factory=DictValue)
+    epoch_time_s: List[float] = field(default_factory=ListValue)
+    total_time_s: Optional[float] = None
+
+    def __post_init__(self):
+        self.loss, self.val_loss = ListValue(self.loss), ListValue(self.val_loss)
+        self.metrics, self.epoch_time_s = DictValue(self.metrics), ListValue(self.epoch_time_s)
+
+    def add_epoch(self, train_loss: float, val_loss: Optional[float] = None, metrics: Optional[Dict[str, float]] = None,
+                  seconds: Optional[float] = None) -> None:
+        self.loss.append(float(train_loss))
+        if val_loss is not None:
+            self.val_loss.append(float(val_loss))
+        for k, v in (metrics or {}).items():
+            self.metrics.setdefault(k, []).append(float(v))
+        if seconds is not None:
+            self.epoch_time_s.append(float(seconds))
+
+    @property
+    def train_loss(self) -> List[float]:
+        return self.loss
+
+    @property
+    def training_time(self) -> float:
+        return FloatValue(self.total_time_s if self.total_time_s is not None else sum(self.epoch_time_s))
+
+    @training_time.setter
+    def training_time(self, seconds: float) -> None:
+        self.total_time_s = float(seconds)
+
+    def best_val_loss(self) -> Optional[float]:
+        return min(self.val_loss) if self.val_loss else None
 
     def best_epoch(self) -> int:
+        """Index of the epoch with the lowest validation loss (training loss without validation); -1 when empty."""
         src = self.val_loss or self.loss
         return min(range(len(src)), key=src.__getitem__) if src else -1
 
+    def summary(self) -> str:
+        if not self.loss:
+            return "TrainingHistory: no epochs"
+        rows = [f"TrainingHistory: {len(self.loss)} epochs in {float(self.training_time):.2f} s",
+                f"  final train loss {self.loss[-1]:.6f}"]
+        if self.val_loss:
+            rows.append(f"  final val loss   {self.val_loss[-1]:.6f}  (best {self.best_val_loss():.6f} at epoch {self.best_epoch() + 1})")
+        for k, v in self.metrics.items():
+            if v:
+                rows.append(f"  {k}: {v[-1]:.4f}")
+        return "\n".join(rows)
+
+    def plot_data(self) -> Tuple[List[float], List[float], List[float]]:
+        """``(epochs 1.., train losses, validation losses)`` for a loss curve."""
+        return [float(i + 1) for i in range(len(self.loss))], list(self.loss), list(self.val_loss)
+
     def to_json(self) -> str:
-        return json.dumps({"loss": self.loss, "val_loss": self.val_loss, "metrics": self.metrics})
+        return json.dumps({"loss": list(self.loss), "val_loss": list(self.val_loss), "metrics": dict(self.metrics)})
 
 
 _LOSSES = {"mse": nn.MSELoss, "cross_entropy": nn.CrossEntropyLoss, "categorical_crossentropy": nn.CrossEntropyLoss,
@@ -85,6 +136,126 @@ def _metric(name: str) -> Callable:
     raise ValueError(f"unknown metric '{name}'")
 
 
+def _raw(t):
+    """The ``torch.Tensor`` inside a ``Tensor`` / ``Variable`` wrapper (or the argument itself)."""
+    if t is None or isinstance(t, torch.Tensor):
+        return t
+    from ..autograd import Variable
+    if isinstance(t, Variable):
+        return t.tensor
+    return getattr(t, "data", t)
+
+
+_ACTIVATIONS = {"linear": None, "none": None, "relu": nn.ReLU, "sigmoid": nn.Sigmoid, "tanh": nn.Tanh, "gelu": nn.GELU,
+                "softmax": lambda: nn.Softmax(dim=-1), "leaky_relu": nn.LeakyReLU, "elu": nn.ELU, "selu": nn.SELU,
+                "swish": nn.SiLU, "silu": nn.SiLU}
+
+
+def _activation(name: Optional[str]) -> Optional[nn.Module]:
+    key = (name or "linear").strip().lower()
+    if key not in _ACTIVATIONS:
+        raise ValueError(f"unknown activation '{name}'")
+    f = _ACTIVATIONS[key]
+    return None if f is None else f()
+
+
+class _Deferred(nn.Module):
+    """A layer described without its input width; ``inner`` is built from the first input."""
+
+    def __init__(self, activation: Optional[str]):
+        super().__init__()
+        self.inner: Optional[nn.Module] = None
+        self.act = _activation(activation)
+        self.activation = (activation or "linear").lower()
+        self.last_output_shape = None
+
+    def _build(self, x: torch.Tensor) -> nn.Module:
+        raise NotImplementedError
+
+    def _prepare(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
+    def forward(self, x):
+        x = self._prepare(x)
+        if self.inner is None:
+            self.inner = self._build(x).to(device=x.device, dtype=x.dtype if x.is_floating_point() else None)
+        y = self.inner(x)
+        y = y if self.act is None else self.act(y)
+        self.last_output_shape = (None, *y.shape[1:])
+        return y
+
+
+class Dense(_Deferred):
+    """``Dense(units, activation)``: this package's ``Linear`` (tcgen05 GEMM on CUDA) + activation; inputs with more
+    than two dimensions are flattened per sample first."""
+
+    def __init__(self, units: int, activation: Optional[str] = None):
+        super().__init__(activation)
+        if int(units) <= 0:
+            raise ValueError("units must be positive")
+        self.units = int(units)
+
+    def _prepare(self, x):
+        return x.flatten(1) if x.dim() > 2 else x
+
+    def _build(self, x):
+        from ..nn import Linear
+        return Linear(x.shape[-1], self.units)
+
+    def extra_repr(self) -> str:
+        return f"{self.units}, activation={self.activation}"
+
+
+class Conv2D(_Deferred):
+    """``Conv2D(filters, kernel_size, activation)`` over ``[N, C, H, W]`` inputs."""
+
+    def __init__(self, filters: int, kernel_size: int, activation: Optional[str] = "relu"):
+        super().__init__(activation)
+        if int(filters) <= 0 or int(kernel_size) <= 0:
+            raise ValueError("filters and kernel_size must be positive")
+        self.filters, self.kernel_size = int(filters), int(kernel_size)
+
+    def _build(self, x):
+        from ..nn import Conv2d
+        if x.dim() != 4:
+            raise ValueError(f"Conv2D needs [N, C, H, W] inputs, got {tuple(x.shape)}")
+        return Conv2d(x.shape[1], self.filters, (self.kernel_size, self.kernel_size))
+
+    def extra_repr(self) -> str:
+        return f"{self.filters}, {self.kernel_size}, activation={self.activation}"
+
+
+def _layer_kind(l: nn.Module) -> str:
+    return {"Dense": "Dense", "Conv2D": "Conv2D"}.get(type(l).__name__, type(l).__name__)
+
+
+def layer_from_spec(spec: str) -> nn.Module:
+    """Parses ``Name(arg, ..., key=value)`` as written by :class:`ModelBuilder` of the binding."""
+    import re
+    m = re.fullmatch(r"\s*([A-Za-z_][A-Za-z0-9_]*)\s*(?:\((.*)\))?\s*", spec)
+    if not m:
+        raise ValueError(f"cannot parse layer description '{spec}'")
+    name, body = m.group(1).lower(), (m.group(2) or "").strip()
+    pos, kw = [], {}
+    for part in [p.strip() for p in body.split(",") if p.strip()]:
+        if "=" in part:
+            k, v = part.split("=", 1)
+            kw[k.strip().lower()] = v.strip().strip("'\"")
+        else:
+            pos.append(part.strip("'\""))
+    if name == "dense":
+        return Dense(int(pos[0]), kw.get("activation", pos[1] if len(pos) > 1 else None))
+    if name in ("conv2d",):
+        return Conv2D(int(pos[0]), int(pos[1]), kw.get("activation", pos[2] if len(pos) > 2 else "relu"))
+    if name == "dropout":
+        return nn.Dropout(float(pos[0]) if pos else float(kw.get("rate", kw.get("p", 0.5))))
+    if name == "flatten":
+        return nn.Flatten()
+    if name in _ACTIVATIONS and _ACTIVATIONS[name] is not None:
+        return _ACTIVATIONS[name]()
+    raise ValueError(f"unknown layer '{spec}'")
+
+
 class Sequential(Model):
     """``Sequential().add(layer)...compile(optimizer, loss, metrics).fit(x, y, ...)``."""
 
@@ -93,10 +264,15 @@ class Sequential(Model):
         self.layers = nn.ModuleList(layers or [])
         self.name = name
         self._optimizer = self._loss = None
+        self._optimizer_spec = ("sgd", 1e-3)
+        self.compiled = False
         self._metrics: Dict[str, Callable] = {}
 
-    def add(self, layer: nn.Module) -> "Sequential":
-        self.layers.append(layer)
+    def add(self, layer: Union[nn.Module, str]) -> "Sequential":
+        """A module, or a layer description as the binding's builder writes them (src/python/training.rs:326-347):
+        ``"Dense(64, activation=relu)"``, ``"Conv2D(32, 3, activation=relu)"``, ``"Dropout(0.5)"``, ``"Flatten"``, or an
+        activation name.  Described layers take their input width from the first batch they see."""
+        self.layers.append(layer_from_spec(layer) if isinstance(layer, str) else layer)
         return self
 
     def forward(self, x):
@@ -104,22 +280,52 @@ class Sequential(Model):
             x = l(x)
         return x
 
-    def compile(self, optimizer: Union[str, torch.optim.Optimizer] = "adam", loss: Union[str, nn.Module] = "mse",
-                metrics: Sequence[str] = (), lr: float = 1e-3) -> "Sequential":
-        from ..optim import OptimizerFactory
-        self._optimizer = OptimizerFactory.create(optimizer, self.parameters(), lr=lr) if isinstance(optimizer, str) else optimizer
-        self._loss = _LOSSES[loss]() if isinstance(loss, str) else loss
-        self._metrics = {m: _metric(m) for m in metrics}
+    def compile(self, optimizer: Union[str, torch.optim.Optimizer, None] = "adam", loss: Union[str, nn.Module, None] = "mse",
+                metrics: Optional[Sequence[str]] = (), lr: float = 1e-3) -> "Sequential":
+        self._optimizer_spec = (optimizer or "sgd", lr)      # the binding's defaults: sgd / mse (training.rs:228-238)
+        self._optimizer = None
+        self._loss = _LOSSES[loss or "mse"]() if isinstance(loss or "mse", str) else loss
+        self._metrics = {m: _metric(m) for m in (metrics or ())}
+        self.compiled = True
+        if not any(isinstance(m, _Deferred) and m.inner is None for m in self.modules()):
+            self._make_optimizer()
         return self
+
+    def _make_optimizer(self) -> None:
+        from ..optim import OptimizerFactory
+        opt, lr = self._optimizer_spec
+        self._optimizer = OptimizerFactory.create(opt, self.parameters(), lr=lr) if isinstance(opt, str) else opt
+
+    def _ready(self, sample: torch.Tensor) -> None:
+        """Described layers are built by a forward pass of the first batch; the optimizer is made after that."""
+        if self._optimizer is None:
+            if not getattr(self, "compiled", False):
+                raise RuntimeError("Model must be compiled before training")
+            with torch.no_grad():
+                self(sample)
+            self._make_optimizer()
 
     def _loader(self, x, y, batch_size, shuffle, seed=None):
         ds = TensorDataset(x, y)
         sampler = RandomSampler(len(ds), seed=seed) if shuffle else SequentialSampler(len(ds))
         return DataLoader(ds, sampler, batch_size)
 
-    def fit(self, x: torch.Tensor, y: torch.Tensor, config: Optional[FitConfig] = None, **kw) -> TrainingHistory:
-        if self._optimizer is None:
-            raise RuntimeError("call compile() before fit()")
+    def fit(self, x, y=None, config: Optional[FitConfig] = None, validation_data=None, epochs: Optional[int] = None,
+            verbose: Optional[bool] = None, **kw) -> TrainingHistory:
+        """``fit(x, y, config | epochs=, batch_size=, ...)`` on tensors, or the binding's
+        ``fit(train_loader, validation_loader=None, epochs=10, verbose=True)`` on data loaders
+        (src/python/training.rs:239-275; the reference returns made-up losses there, this trains)."""
+        if not getattr(self, "compiled", False):
+            raise RuntimeError("Model must be compiled before training")
+        if hasattr(x, "next_batch"):
+            val = validation_data if validation_data is not None else (y if hasattr(y, "next_batch") else None)
+            return self._fit_loaders(x, val, 10 if epochs is None else epochs, True if verbose is None else verbose)
+        x, y = _raw(x), _raw(y)
+        self._ready(x[:2])
+        if epochs is not None:
+            kw["epochs"] = epochs
+        if verbose is not None:
+            kw["verbose"] = verbose
         cfg = config or FitConfig(**kw)
         n_val = int(len(x) * cfg.validation_split)
         xt, yt = (x[:-n_val], y[:-n_val]) if n_val else (x, y)
@@ -150,12 +356,46 @@ class Sequential(Model):
                 print(f"epoch {epoch + 1}/{cfg.epochs} loss {hist.loss[-1]:.4f}")
         return hist
 
+    def _fit_loaders(self, train, val, epochs: int, verbose: bool) -> TrainingHistory:
+        hist = TrainingHistory(metrics={m: [] for m in self._metrics})
+        t_all = time.time()
+        for epoch in range(epochs):
+            t0 = time.time()
+            self.train()
+            tot, n = 0.0, 0
+            train.reset()
+            for batch in train:
+                xb, yb = _raw(batch[0]), _raw(batch[1])
+                self._ready(xb)
+                self._optimizer.zero_grad()
+                loss = self._loss(self(xb), yb)
+                loss.backward()
+                self._optimizer.step()
+                tot += float(loss.detach()) * len(xb)
+                n += len(xb)
+            ev = self.evaluate(val) if val is not None else (self.evaluate(train) if self._metrics else {})
+            hist.add_epoch(tot / max(1, n), ev.get("loss") if val is not None else None,
+                           {m: ev[m] for m in self._metrics if m in ev}, time.time() - t0)
+            if verbose:
+                tail = f" val_loss={hist.val_loss[-1]:.4f}" if val is not None else ""
+                print(f"Epoch {epoch + 1}/{epochs}: loss={hist.loss[-1]:.4f}{tail}")
+        hist.training_time = time.time() - t_all
+        return hist
+
     @torch.no_grad()
-    def evaluate(self, x, y, batch_size: int = 32) -> Dict[str, float]:
+    def evaluate(self, x, y=None, batch_size: int = 32) -> Dict[str, float]:
+        """``evaluate(x, y)`` on tensors or ``evaluate(loader)``: mean loss and the compiled metrics."""
+        if not getattr(self, "compiled", False):
+            raise RuntimeError("Model must be compiled before evaluation")
         self.eval()
         tot: Dict[str, float] = {"loss": 0.0, **{m: 0.0 for m in self._metrics}}
         n = 0
-        for xb, yb in self._loader(x, y, batch_size, False):
+        if hasattr(x, "next_batch"):
+            x.reset()
+            batches = ((_raw(b[0]), _raw(b[1])) for b in x)
+        else:
+            batches = self._loader(_raw(x), _raw(y), batch_size, False)
+        for xb, yb in batches:
             out = self(xb)
             tot["loss"] += float(self._loss(out, yb)) * len(xb)
             for m, fn in self._metrics.items():
@@ -164,13 +404,39 @@ class Sequential(Model):
         return {k: v / max(1, n) for k, v in tot.items()}
 
     @torch.no_grad()
-    def predict(self, x, batch_size: int = 32) -> torch.Tensor:
+    def predict(self, x, batch_size: int = 32):
+        """Outputs for ``x`` in evaluation mode; a ``Tensor`` / ``Variable`` argument gives a result of its own kind."""
         self.eval()
-        return torch.cat([self(x[i:i + batch_size]) for i in range(0, len(x), batch_size)])
+        from .._interop import call_unwrapped
+        return call_unwrapped(lambda t: torch.cat([self(t[i:i + batch_size]) for i in range(0, len(t), batch_size)]), (x,), {})
+
+    def summary(self) -> str:
+        line = "_" * 65
+        rows = [f"Model: {self.name}", line, f"{'Layer (type)':<29}{'Output Shape':<26}Param #", "=" * 65]
+        total = 0
+        for i, l in enumerate(self.layers):
+            n = sum(p.numel() for p in l.parameters())
+            total += n
+            shape = getattr(l, "last_output_shape", None)
+            rows.append(f"{f'{type(l).__name__.lower().lstrip(chr(95))}_{i} ({_layer_kind(l)})':<29}"
+                        f"{str(shape) if shape is not None else '?':<26}{n:,}")
+        rows += ["=" * 65, f"Total params: {total:,}", f"Compiled: {bool(getattr(self, 'compiled', False))}"]
+        return "\n".join(rows)
 
 
 BasicSequential = Sequential
 HighLevelModel = Sequential
+
+
+class BindingModel(Sequential):
+    """``Model(name)`` of the Python binding (src/python/training.rs:208-313): ``add`` (layer descriptions or modules),
+    ``compile``, ``fit`` / ``evaluate`` on data loaders, ``predict``, ``summary``."""
+
+    def __init__(self, name: Optional[str] = None, layers: Optional[Sequence[nn.Module]] = None):
+        super().__init__(layers, name or "Model")
+
+    def __repr__(self) -> str:
+        return f"Model(name='{self.name}', layers={len(self.layers)}, compiled={self.compiled})"
 
 
 class ModelBuilder:
@@ -194,12 +460,33 @@ class ModelBuilder:
         self._layers.append(GELU())
         return self
 
+    def dense(self, units: int, activation: Optional[str] = None):
+        """Binding form (src/python/training.rs:326-331): the input width comes from the data."""
+        self._layers.append(Dense(units, activation))
+        return self
+
     def dropout(self, p: float):
+        if not 0.0 <= float(p) < 1.0:
+            raise ValueError("dropout rate must be in [0, 1)")
         self._layers.append(nn.Dropout(p))
         return self
 
-    def conv2d(self, i, o, k, stride=1, padding=0):
-        self._layers.append(nn.Conv2d(i, o, k, stride, padding))
+    def conv2d(self, *args, activation: Optional[str] = None, stride=1, padding=0):
+        """``conv2d(in_channels, out_channels, kernel, stride, padding)``, or the binding's
+        ``conv2d(filters, kernel_size, activation="relu")`` whose input channels come from the data."""
+        if len(args) == 2 or (len(args) == 3 and (args[2] is None or isinstance(args[2], str))):
+            act = args[2] if len(args) == 3 else activation
+            self._layers.append(Conv2D(args[0], args[1], "relu" if act is None else act))
+            return self
+        i, o, k = args[:3]
+        stride = args[3] if len(args) > 3 else stride
+        padding = args[4] if len(args) > 4 else padding
+        from ..nn import Conv2d
+        self._layers.append(Conv2d(i, o, k if isinstance(k, (tuple, list)) else (k, k),
+                                   stride if isinstance(stride, (tuple, list)) else (stride, stride),
+                                   padding if isinstance(padding, (tuple, list)) else (padding, padding)))
+        if activation:
+            self._layers.append(_activation(activation))
         return self
 
     def flatten(self):
@@ -210,8 +497,13 @@ class ModelBuilder:
         self._layers.append(m)
         return self
 
-    def build(self) -> Sequential:
-        return Sequential(self._layers, self._name)
+    def build(self, name: Optional[str] = None) -> Sequential:
+        """A new model with its own copies of the layers, so one builder can make several independent models."""
+        import copy
+        return BindingModel(name or self._name, [copy.deepcopy(l) for l in self._layers])
+
+    def __repr__(self) -> str:
+        return f"ModelBuilder(layers={len(self._layers)})"
 
 
 class InferenceEngine:

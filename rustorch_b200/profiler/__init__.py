@@ -311,6 +311,20 @@ class Profiler:
 
     def clear(self) -> None:
         self.timeline = Timeline()
+        self._recorded: Dict[str, List[float]] = {}
+
+    # the Python binding's manual form (src/python/utils.rs:249-272): durations handed in by the caller
+    def record(self, name: str, duration: float) -> None:
+        if self.enabled:
+            self.__dict__.setdefault("_recorded", {}).setdefault(name, []).append(float(duration))
+
+    def get_stats(self) -> Dict[str, Dict[str, float]]:
+        """count / total / mean / min / max per name over ``record``ed durations and profiled scopes (seconds)."""
+        series: Dict[str, List[float]] = {k: list(v) for k, v in self.__dict__.get("_recorded", {}).items()}
+        for e in self.timeline.events:
+            series.setdefault(e.name, []).append(e.host_us / 1e6)
+        return {k: {"count": float(len(v)), "total": sum(v), "mean": sum(v) / len(v), "min": min(v), "max": max(v)}
+                for k, v in series.items() if v}
 
     @contextlib.contextmanager
     def profile(self, name: str, category: str = "op", **args):

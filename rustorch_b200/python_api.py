@@ -57,8 +57,11 @@ class Device:
 class Config:
     """String-keyed settings with typed getters and environment override (``RUSTORCH_<KEY>``)."""
 
+    # the binding's defaults (src/python/utils.rs:166-174)
+    DEFAULTS = {"device": "cpu", "dtype": "float32", "backend": "native", "num_threads": "4", "memory_limit": "1024"}
+
     def __init__(self, **values):
-        self._v: Dict[str, object] = dict(values)
+        self._v: Dict[str, object] = {**self.DEFAULTS, **values}
 
     def set(self, key: str, value) -> None:
         self._v[key] = value
@@ -81,6 +84,33 @@ class Config:
 
     def to_dict(self) -> Dict[str, object]:
         return dict(self._v)
+
+    def all(self) -> Dict[str, object]:
+        return dict(self._v)
+
+    def load_from_file(self, path: str) -> None:
+        """``key=value`` lines; blank lines and ``#`` comments are skipped (src/python/utils.rs:185-206)."""
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"Configuration file not found: {path}")
+        with open(path) as f:
+            for line in f:
+                line = line.strip()
+                if not line or line.startswith("#") or "=" not in line:
+                    continue
+                k, v = line.split("=", 1)
+                self._v[k.strip()] = v.strip()
+
+    def save_to_file(self, path: str) -> None:
+        with open(path, "w") as f:
+            f.write("# RusTorch Configuration\n# Auto-generated configuration file\n\n")
+            for k in sorted(self._v):
+                f.write(f"{k}={self._v[k]}\n")
+
+    def reset(self) -> None:
+        self._v = dict(self.DEFAULTS)
+
+    def __repr__(self) -> str:
+        return f"Config(settings={len(self._v)})"
 
 
 def set_seed(seed: int) -> None:
@@ -115,13 +145,71 @@ class ModelSerializer:
         ModelSaver.save(model, path, SerializationFormat(fmt) if not isinstance(fmt, SerializationFormat) else fmt)
 
     @staticmethod
-    def load(model: torch.nn.Module, path: str, strict: bool = True) -> torch.nn.Module:
-        from .models.high_level import ModelLoader
+    def load(model, path: Optional[str] = None, strict: bool = True):
+        """``load(model, path)`` fills ``model``; the binding's ``load(path)`` (src/python/utils.rs:38-48) returns the
+        tensors of the file as a dictionary, since a path alone does not say which architecture to build."""
+        from .models.high_level import ModelLoader, load_state_dict_file
+        if path is None and isinstance(model, (str, os.PathLike)):
+            return load_state_dict_file(str(model))
         return ModelLoader.load(model, path, strict)
+
+    @staticmethod
+    def get_model_info(path: str) -> Dict[str, object]:
+        """``exists`` / ``path`` / ``size`` (bytes) and, for a readable checkpoint, its format, tensor count and
+        parameter count (src/python/utils.rs:50-69)."""
+        if not os.path.exists(path):
+            return {"exists": False}
+        info: Dict[str, object] = {"exists": True, "path": path, "size": os.path.getsize(path)}
+        try:
+            from .formats import detect_format
+            from .models.high_level import load_state_dict_file
+            info["format"] = str(getattr(detect_format(path), "value", detect_format(path)))
+            sd = load_state_dict_file(path)
+            info["tensors"] = len(sd)
+            info["parameters"] = int(sum(v.numel() for v in sd.values() if isinstance(v, torch.Tensor)))
+        except Exception as e:  # noqa: BLE001  (an unreadable file still has a size)
+            info["error"] = f"{type(e).__name__}: {e}"
+        return info
+
+    @staticmethod
+    def export(model: torch.nn.Module, path: str, format: Optional[str] = None) -> None:
+        """``format``: ``rustorch`` (default), ``safetensors``, ``pytorch`` / ``pth``, ``json`` (src/python/utils.rs:71-100)."""
+        from .models.high_level import ModelSaver, SerializationFormat
+        name = {"pth": "pytorch", "pt": "pytorch", "torch": "pytorch", None: "rustorch"}.get(format, format)
+        try:
+            fmt = SerializationFormat(name)
+        except ValueError:
+            raise ValueError(f"Unsupported export format: {format}") from None
+        ModelSaver.save(model, path, fmt)
 
 
 class ModelComparator:
     """Parameter-wise and output-wise comparison of two models."""
+
+    @staticmethod
+    def get_stats(model: torch.nn.Module) -> Dict[str, object]:
+        """Name, layer count, layer-kind histogram and parameter count (src/python/utils.rs:131-157)."""
+        layers = list(getattr(model, "layers", None) or [m for m in model.children()])
+        kinds: Dict[str, int] = {}
+        for l in layers:
+            n = type(l).__name__
+            kind = ("dense" if n in ("Dense", "Linear") else "convolutional" if "Conv" in n else "dropout" if "Dropout" in n else "other")
+            kinds[f"{kind}_layers"] = kinds.get(f"{kind}_layers", 0) + 1
+        return {"name": getattr(model, "name", type(model).__name__), "num_layers": len(layers),
+                "compiled": bool(getattr(model, "compiled", False)),
+                "parameters": sum(p.numel() for p in model.parameters()), **kinds}
+
+    @staticmethod
+    def compare(model1: torch.nn.Module, model2: torch.nn.Module) -> Dict[str, object]:
+        """Structure of two models side by side (src/python/utils.rs:113-129) plus whether their parameters agree."""
+        a, b = ModelComparator.get_stats(model1), ModelComparator.get_stats(model2)
+        sig = lambda m: [(type(l).__name__, tuple(tuple(p.shape) for p in l.parameters()))   # noqa: E731
+                         for l in (getattr(m, "layers", None) or m.children())]
+        same_layers = sig(model1) == sig(model2)
+        return {"model1_name": a["name"], "model2_name": b["name"], "model1_layers": a["num_layers"], "model2_layers": b["num_layers"],
+                "model1_compiled": a["compiled"], "model2_compiled": b["compiled"], "layers_identical": same_layers,
+                "compilation_identical": a["compiled"] == b["compiled"],
+                "parameters_identical": same_layers and ModelComparator.compare_parameters(model1, model2)["identical"]}
 
     @staticmethod
     def compare_parameters(a: torch.nn.Module, b: torch.nn.Module, atol: float = 0.0) -> Dict[str, object]:

@@ -20,6 +20,8 @@ from typing import Any, Callable, Dict, Iterable, List, Optional, Tuple
 
 import torch
 
+from .._interop import FlagValue, FloatValue, IntValue, StrValue
+
 
 # ----------------------------------------------------------------------- state
 @dataclass
@@ -354,15 +356,59 @@ class ModelCheckpoint(Callback):
 
 
 # --------------------------------------------------------------------- trainer
-@dataclass
 class TrainerConfig:
-    epochs: int = 10
-    log_frequency: int = 100
-    validation_frequency: int = 1
-    gradient_clip_value: Optional[float] = None
-    device: str = "cpu"
-    use_mixed_precision: bool = False
-    accumulation_steps: int = 1
+    """``epochs=10, log_frequency=100, validation_frequency=1, gradient_clip_value=None, device="cpu",
+    use_mixed_precision=False, accumulation_steps=1`` (src/training/trainer.rs:19-48).  The Python binding's constructor
+    also takes ``learning_rate`` and ``batch_size`` and reads ``epochs() / device() / use_mixed_precision()`` as calls
+    with ``set_*`` mutators (src/python/training.rs:11-64); the members answer both spellings."""
+
+    _FIELDS = ("epochs", "learning_rate", "batch_size", "log_frequency", "validation_frequency", "gradient_clip_value", "device",
+               "use_mixed_precision", "accumulation_steps")
+
+    def __init__(self, epochs: int = 10, log_frequency: int = 100, validation_frequency: int = 1,
+                 gradient_clip_value: Optional[float] = None, device: str = "cpu", use_mixed_precision: bool = False,
+                 accumulation_steps: int = 1, learning_rate: Optional[float] = None, batch_size: Optional[int] = None):
+        if int(epochs) < 0 or int(accumulation_steps) < 1:
+            raise ValueError("epochs must be >= 0 and accumulation_steps >= 1")
+        self._v = dict(epochs=int(epochs), log_frequency=int(log_frequency), validation_frequency=int(validation_frequency),
+                       gradient_clip_value=gradient_clip_value, device=str(device), use_mixed_precision=bool(use_mixed_precision),
+                       accumulation_steps=int(accumulation_steps), learning_rate=learning_rate, batch_size=batch_size)
+
+    def __getattr__(self, name):
+        v = self.__dict__.get("_v", {})
+        if name in v:
+            x = v[name]
+            if isinstance(x, bool):
+                return FlagValue(x)
+            if isinstance(x, int):
+                return IntValue(x)
+            if isinstance(x, float):
+                return FloatValue(x)
+            if isinstance(x, str):
+                return StrValue(x)
+            return x
+        raise AttributeError(name)
+
+    def __setattr__(self, name, value):
+        if name in self._FIELDS:
+            self._v[name] = value
+        else:
+            object.__setattr__(self, name, value)
+
+    def set_epochs(self, epochs: int) -> None:
+        self._v["epochs"] = int(epochs)
+
+    def set_device(self, device: str) -> None:
+        self._v["device"] = str(device)
+
+    def set_mixed_precision(self, use_mixed_precision: bool) -> None:
+        self._v["use_mixed_precision"] = bool(use_mixed_precision)
+
+    def __eq__(self, other) -> bool:
+        return isinstance(other, TrainerConfig) and self._v == other._v
+
+    def __repr__(self) -> str:
+        return f"TrainerConfig(epochs={self._v['epochs']}, device='{self._v['device']}', mixed_precision={self._v['use_mixed_precision']})"
 
 
 class Trainer:
@@ -387,7 +433,7 @@ class Trainer:
 
     def _autocast(self):
         dev = torch.device(self.config.device)
-        return torch.autocast(dev.type, dtype=torch.bfloat16, enabled=self.config.use_mixed_precision)
+        return torch.autocast(dev.type, dtype=torch.bfloat16, enabled=bool(self.config.use_mixed_precision))
 
     def clip_gradients(self, model: torch.nn.Module) -> Optional[float]:
         c = self.config.gradient_clip_value
@@ -443,7 +489,19 @@ class Trainer:
             self.metrics.update(float(loss), outputs, targets, bs)
         return self.metrics.finalize_epoch("val_")
 
-    def train(self, model, train_loader, loss_fn, optimizer, val_loader=None) -> Dict[str, Any]:
+    def _binding_form(self, model, third) -> bool:
+        """``train(model, train_loader, val_loader=None)`` / ``evaluate(model, loader)`` of the Python binding
+        (src/python/training.rs:131-200): the model was ``compile``d and carries its own loss and optimizer."""
+        return hasattr(model, "_fit_loaders") and (third is None or hasattr(third, "next_batch"))
+
+    def train(self, model, train_loader, loss_fn=None, optimizer=None, val_loader=None):
+        """``train(model, train_loader, loss_fn, optimizer, val_loader=None)`` -> metrics dictionary
+        (src/training/trainer.rs), or the binding's ``train(compiled_model, train_loader, val_loader=None)`` ->
+        ``TrainingHistory`` (real training; the reference's binding reports placeholder losses)."""
+        if optimizer is None and self._binding_form(model, loss_fn):
+            model.to(torch.device(self.config.device))
+            return model.fit(train_loader, loss_fn if loss_fn is not None else val_loader, epochs=int(self.config.epochs),
+                             verbose=False)
         cfg, st = self.config, self.state
         model.to(torch.device(cfg.device))
         for cb in self.callbacks:
@@ -475,8 +533,13 @@ class Trainer:
             cb.on_train_end(st)
         return self.metrics.finalize(st)
 
-    def evaluate(self, model, loader, loss_fn) -> Dict[str, float]:
+    def evaluate(self, model, loader, loss_fn=None) -> Dict[str, float]:
+        if loss_fn is None and self._binding_form(model, None):
+            return model.evaluate(loader)
         return self.validate_epoch(model, loader, loss_fn)
+
+    def __repr__(self) -> str:
+        return f"Trainer(epochs={int(self.config.epochs)}, device='{self.config.device}')"
 
 
 class TrainerBuilder:

@@ -226,7 +226,49 @@ class TensorVisualizer:
                 "sparsity": float((f == 0).float().mean()), "numel": f.numel()}
 
 
-TensorStats = TensorVisualizer
+class TensorStats(TensorVisualizer):
+    """``TensorStats(tensor)`` of the Python binding (src/python/visualization.rs:300-372): ``compute_stats()`` then
+    ``get_stats()`` -> count / mean / std / min / max / median / q25 / q75, ``plot_stats(save_path)``.  Without a tensor
+    it is the plain :class:`TensorVisualizer`."""
+
+    def __init__(self, tensor=None):
+        self.tensor = None if tensor is None else _raw_tensor(tensor)
+        self._stats: Optional[Dict[str, float]] = None
+
+    def compute_stats(self) -> None:
+        if self.tensor is None or self.tensor.numel() == 0:
+            raise ValueError("Cannot compute statistics for empty tensor")
+        f = self.tensor.detach().double().flatten()
+        srt = f.sort().values
+        n = f.numel()
+        self._stats = {"count": float(n), "mean": float(f.mean()), "std": float(f.var(unbiased=False).sqrt()), "min": float(srt[0]),
+                       "max": float(srt[-1]), "median": float(srt[n // 2]), "q25": float(srt[n // 4]), "q75": float(srt[3 * n // 4])}
+
+    def get_stats(self) -> Dict[str, float]:
+        if self._stats is None:
+            raise RuntimeError("Statistics not computed. Call compute_stats() first.")
+        return dict(self._stats)
+
+    def plot_stats(self, save_path: Optional[str] = None) -> str:
+        """Histogram of the values with the computed mean / median in the title; written to ``save_path`` when given."""
+        st = self.get_stats()
+        svg = self.histogram(self.tensor, title=f"mean {st['mean']:.4g}  median {st['median']:.4g}  std {st['std']:.4g}")
+        if save_path:
+            save_plot(svg, save_path)
+        return svg
+
+    def __repr__(self) -> str:
+        return f"TensorStats(computed={self._stats is not None})"
+
+
+def _raw_tensor(t) -> torch.Tensor:
+    if isinstance(t, torch.Tensor):
+        return t
+    inner = getattr(t, "tensor", None)
+    if isinstance(inner, torch.Tensor):
+        return inner
+    inner = getattr(t, "data", None)
+    return inner if isinstance(inner, torch.Tensor) else torch.as_tensor(t, dtype=torch.float32)
 
 
 class GraphVisualizer:
@@ -275,11 +317,174 @@ class GraphVisualizer:
         return "\n".join(out + ["</svg>"])
 
 
-ModelVisualizer = GraphVisualizer
+class ModelVisualizer(GraphVisualizer):
+    """``ModelVisualizer(layout_engine, show_shapes, show_layer_names)`` of the Python binding
+    (src/python/visualization.rs:222-298) on top of :class:`GraphVisualizer`."""
+
+    def __init__(self, layout_engine: Optional[str] = None, show_shapes: Optional[bool] = None,
+                 show_layer_names: Optional[bool] = None):
+        self.layout_engine = layout_engine or "dot"
+        self.show_shapes = True if show_shapes is None else bool(show_shapes)
+        self.show_layer_names = True if show_layer_names is None else bool(show_layer_names)
+
+    def visualize_model(self, model_summary, save_path: Optional[str] = None, format: Optional[str] = None) -> str:
+        """``model_summary``: the text of ``model.summary()`` (one box per layer row, chained top to bottom) or a
+        module (its tree).  Returns Graphviz source; ``format="svg"`` returns a drawing of the chain instead."""
+        if isinstance(model_summary, torch.nn.Module):
+            out = self.module_svg(model_summary) if (format or "dot").lower() == "svg" else self.module_dot(model_summary)
+            if save_path:
+                save_plot(out, save_path)
+            return out
+        if True:
+            rows = [ln.strip() for ln in str(model_summary).splitlines()
+                    if "(" in ln and not ln.startswith(("Model:", "Layer (type)", "Total", "Compiled"))]
+            lines = [f"digraph model {{", f"  layout={self.layout_engine};", "  rankdir=TB;", '  node [shape=box, fontname="sans-serif"];']
+            for i, r in enumerate(rows):
+                parts = r.split()
+                label = (parts[0] + " " + parts[1] if self.show_layer_names and len(parts) > 1 else parts[1] if len(parts) > 1 else parts[0])
+                if self.show_shapes and "(None" in r:
+                    label += "\\n" + r[r.index("(None"):r.index(")", r.index("(None")) + 1]
+                lines.append(f'  l{i} [label="{label}"];')
+            lines += [f"  l{i} -> l{i + 1};" for i in range(len(rows) - 1)] + ["}"]
+            dot = "\n".join(lines)
+        out = dot
+        if (format or "dot").lower() == "svg":
+            h = 40 * max(1, len(rows)) + 20
+            body = [f'<svg xmlns="http://www.w3.org/2000/svg" width="420" height="{h}">', f'<rect width="420" height="{h}" fill="white"/>']
+            for i, r in enumerate(rows):
+                body.append(f'<rect x="10" y="{10 + 40 * i}" width="400" height="28" fill="#deebf7" stroke="#2171b5"/>')
+                body.append(f'<text x="18" y="{29 + 40 * i}" font-size="12" font-family="monospace">{html.escape(r[:56])}</text>')
+                if i:
+                    body.append(f'<line x1="210" y1="{40 * i - 2}" x2="210" y2="{10 + 40 * i}" stroke="black"/>')
+            out = "\n".join(body + ["</svg>"])
+        if save_path:
+            save_plot(out, save_path)
+        return out
+
+    def plot_attention_heatmap(self, attention_weights, tokens: Optional[Sequence[str]] = None, title: Optional[str] = None,
+                               save_path: Optional[str] = None) -> str:
+        """``[T, S]`` attention weights (or ``[..., T, S]``: leading dimensions averaged) as a heat-map with token labels."""
+        w = _raw_tensor(attention_weights).detach().float()
+        while w.dim() > 2:
+            w = w.mean(0)
+        if w.dim() != 2:
+            raise ValueError("attention weights must have at least two dimensions")
+        T, S = w.shape
+        if tokens is not None and len(tokens) not in (T, S):
+            raise ValueError(f"{len(tokens)} tokens for a {T} x {S} attention map")
+        cell, left, top = 22, 90, 60
+        scale = float(w.max()) or 1.0
+        vals = (w / scale).cpu().tolist()
+        out = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{left + S * cell + 10}" height="{top + T * cell + 10}">',
+               f'<rect width="100%" height="100%" fill="white"/>',
+               f'<text x="{left}" y="18" font-size="14" font-family="sans-serif">{html.escape(title or "Attention")}</text>']
+        for i in range(T):
+            for j in range(S):
+                out.append(f'<rect x="{left + j * cell}" y="{top + i * cell}" width="{cell}" height="{cell}" fill="{ColorPalette.get_sequential_color(vals[i][j])}"/>')
+        if tokens is not None:
+            for i in range(T):
+                out.append(f'<text x="{left - 4}" y="{top + i * cell + 15}" text-anchor="end" font-size="11" font-family="sans-serif">{html.escape(str(tokens[i % len(tokens)]))}</text>')
+            for j in range(S):
+                x = left + j * cell + 14
+                out.append(f'<text x="{x}" y="{top - 4}" font-size="11" font-family="sans-serif" transform="rotate(-60 {x} {top - 4})">{html.escape(str(tokens[j % len(tokens)]))}</text>')
+        svg = "\n".join(out + ["</svg>"])
+        if save_path:
+            save_plot(svg, save_path)
+        return svg
+
+    def __repr__(self) -> str:
+        return f"ModelVisualizer(layout_engine='{self.layout_engine}', show_shapes={self.show_shapes})"
 
 
 class Plotter(TrainingPlotter):
-    """Name used by the Python binding surface."""
+    """``Plotter(backend, style, figure_size, dpi)`` of the Python binding (src/python/visualization.rs:11-220).  Every
+    method returns the SVG text and writes it to ``save_path`` when one is given (the reference prints a description of
+    the plot instead of drawing it)."""
+
+    def __init__(self, backend=None, style: Optional[str] = None, figure_size: Optional[Tuple[int, int]] = None,
+                 dpi: Optional[int] = None, config: Optional[PlotConfig] = None, metadata: Optional[PlotMetadata] = None):
+        if isinstance(backend, PlotConfig):                           # TrainingPlotter(config, metadata) order
+            config, backend = backend, None
+        if isinstance(style, PlotMetadata):
+            metadata, style = style, None
+        self.backend, self.style_name, self.dpi = backend or "svg", style or "default", int(dpi or 100)
+        self.figure_size = tuple(figure_size or (10, 6))
+        cfg = config or PlotConfig(width=int(self.figure_size[0] * 80), height=int(self.figure_size[1] * 80))
+        super().__init__(cfg, metadata)
+
+    def _cfg(self, **kw) -> PlotConfig:
+        return PlotConfig(**{**self.config.__dict__, **{k: v for k, v in kw.items() if v is not None}})
+
+    def _done(self, svg: str, save_path: Optional[str]) -> str:
+        if save_path:
+            save_plot(svg, save_path)
+        return svg
+
+    def plot_training_history(self, history, save_path: Optional[str] = None, show_validation: Optional[bool] = None) -> str:
+        show_val = True if show_validation is None else bool(show_validation)
+        tr = [float(v) for v in (history.train_loss() if callable(getattr(history, "train_loss", None)) else history["train_loss"])]
+        va = [float(v) for v in (history.val_loss() if callable(getattr(history, "val_loss", None)) else history.get("val_loss", []))]
+        series = [PlotData(list(range(1, len(tr) + 1)), tr, "train")]
+        if show_val and va:
+            series.append(PlotData(list(range(1, len(va) + 1)), va, "validation"))
+        return self._done(line_chart(series, self._cfg(title=self.config.title or "Training history", ylabel="loss")), save_path)
+
+    def plot_tensor_as_image(self, tensor, title: Optional[str] = None, colormap: Optional[str] = None,
+                             save_path: Optional[str] = None) -> str:
+        return self._done(TensorVisualizer().heatmap(_raw_tensor(tensor), title or "Tensor"), save_path)
+
+    def plot_multiple_tensors(self, tensors, titles: Optional[Sequence[str]] = None, layout: Optional[Tuple[int, int]] = None,
+                              save_path: Optional[str] = None) -> str:
+        n = len(tensors)
+        if titles is not None and len(titles) != n:
+            raise ValueError(f"{len(titles)} titles for {n} tensors")
+        rows, cols = layout or (1, n)
+        if rows * cols < n:
+            raise ValueError(f"layout {rows} x {cols} holds fewer than {n} tensors")
+        plots = [((titles[i] if titles else f"tensor {i}"), TensorVisualizer().heatmap(_raw_tensor(t))) for i, t in enumerate(tensors)]
+        cells = []
+        for r in range(rows):
+            row = "".join(f"<td style='padding:6px;vertical-align:top'><div style='font-family:sans-serif'>{html.escape(t)}</div>{s}</td>"
+                          for t, s in plots[r * cols:(r + 1) * cols])
+            cells.append(f"<tr>{row}</tr>")
+        return self._done(wrap_in_html("<table>" + "".join(cells) + "</table>", "tensors"), save_path)
+
+    def line_plot(self, x_data, y_data, title: Optional[str] = None, xlabel: Optional[str] = None, ylabel: Optional[str] = None,
+                  save_path: Optional[str] = None) -> str:
+        if len(x_data) != len(y_data):
+            raise ValueError("x_data and y_data must have the same length")
+        cfg = self._cfg(title=title or "Line Plot", xlabel=xlabel or "x", ylabel=ylabel or "y", style=PlotStyle.LINE, legend=False)
+        return self._done(line_chart([PlotData([float(v) for v in x_data], [float(v) for v in y_data])], cfg), save_path)
+
+    def scatter_plot(self, x_data, y_data, colors=None, sizes=None, title: Optional[str] = None, save_path: Optional[str] = None) -> str:
+        if len(x_data) != len(y_data):
+            raise ValueError("x_data and y_data must have the same length")
+        for name, extra in (("colors", colors), ("sizes", sizes)):
+            if extra is not None and len(extra) != len(x_data):
+                raise ValueError(f"{name} must have one entry per point")
+        cfg = self._cfg(title=title or "Scatter Plot", xlabel="x", ylabel="y", legend=False)
+        xs, ys = [float(v) for v in x_data], [float(v) for v in y_data]
+        out, sx, sy = _axes(cfg, min(xs, default=0.0), max(xs, default=1.0), min(ys, default=0.0), max(ys, default=1.0))
+        lo, hi = (min(colors), max(colors)) if colors else (0.0, 1.0)
+        for i, (a, b) in enumerate(zip(xs, ys)):
+            col = ColorPalette.get_sequential_color(0.3 + 0.7 * ((colors[i] - lo) / (hi - lo) if hi > lo else 1.0)) if colors else ColorPalette.get_categorical_color(0)
+            out.append(f'<circle cx="{sx(a):.1f}" cy="{sy(b):.1f}" r="{float(sizes[i]) if sizes else 3.0:.1f}" fill="{col}"/>')
+        return self._done("\n".join(out + ["</svg>"]), save_path)
+
+    def histogram(self, data, bins: Optional[int] = None, title: Optional[str] = None, xlabel: Optional[str] = None,
+                  ylabel: Optional[str] = None, save_path: Optional[str] = None) -> str:
+        t = _raw_tensor(data).float().flatten()
+        if t.numel() == 0:
+            raise ValueError("histogram of no data")
+        nb = int(bins or 30)
+        lo, hi = float(t.min()), float(t.max())
+        counts = torch.histc(t, bins=nb, min=lo, max=hi if hi > lo else lo + 1).tolist()
+        xs = [lo + (max(hi - lo, 1.0 if hi == lo else hi - lo)) * (i + 0.5) / nb for i in range(nb)]
+        cfg = self._cfg(title=title or "Histogram", xlabel=xlabel or "Value", ylabel=ylabel or "Frequency", style=PlotStyle.BAR, legend=False)
+        return self._done(line_chart([PlotData(xs, counts, "count")], cfg), save_path)
+
+    def __repr__(self) -> str:
+        return f"Plotter(backend='{self.backend}', style='{self.style_name}', figure_size={self.figure_size}, dpi={self.dpi})"
 
 
 def wrap_in_html(svg: str, title: str = "plot") -> str:

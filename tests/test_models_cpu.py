@@ -55,7 +55,7 @@ def test_keras_style_fit_evaluate_predict():
     hist = model.fit(X, y, epochs=15, batch_size=32, validation_split=0.2, seed=0)
     assert hist.loss[-1] < hist.loss[0] and hist.metrics["accuracy"][-1] > 0.9 and len(hist.val_loss) == 15
     assert model.evaluate(X, y)["accuracy"] > 0.9 and model.predict(X[:5]).shape == (5, 2)
-    assert "total parameters" in model.summary() and model.mode() is M.ModelMode.EVAL
+    assert "Total params: 114" in model.summary() and model.mode() is M.ModelMode.EVAL
     eng = M.InferenceEngine(model)
     eng.predict_batch([X[:3], X[3:7]])
     assert eng.stats()["n"] == 2

@@ -199,3 +199,181 @@ def test_binding_dataset_loader_sampler_backend():
     be.barrier()
     with pytest.raises(ValueError):
         rt.DistributedBackend("carrier-pigeon")
+
+
+def test_binding_model_builder_trainer_history():
+    """src/python/training.rs: ModelBuilder.dense / conv2d / dropout / build, Model.add / compile / fit / evaluate /
+    predict / summary on data loaders, Trainer(config).train / evaluate, TrainingHistory and TrainerConfig accessors.
+    The reference's binding reports placeholder numbers there; these train."""
+    import rustorch as rt
+    rt.set_seed(0)
+    X = torch.randn(256, 6)
+    y = (X[:, :3].sum(1) > X[:, 3:].sum(1)).long()
+    train = rt.DataLoader(rt.TensorDataset(X[:192], y[:192]), batch_size=32)
+    val = rt.DataLoader(rt.TensorDataset(X[192:], y[192:]), batch_size=32)
+    b = rt.ModelBuilder()
+    b.dense(32, "relu")
+    b.dropout(0.0)
+    b.dense(2)
+    assert repr(b) == "ModelBuilder(layers=3)"
+    model = b.build("clf")
+    assert isinstance(model, rt.Model) and "compiled=False" in repr(model)
+    with pytest.raises(RuntimeError, match="compiled"):
+        model.fit(train)
+    with pytest.raises(RuntimeError, match="compiled"):
+        model.evaluate(val)
+    model.compile("adam", "cross_entropy", ["accuracy"], lr=0.02)
+    hist = model.fit(train, val, epochs=12, verbose=False)
+    assert isinstance(hist, rt.TrainingHistory) and len(hist.train_loss()) == 12 and len(hist.val_loss) == 12
+    assert hist.train_loss[-1] < hist.train_loss[0] and hist.metrics()["accuracy"][-1] > 0.85
+    assert hist.best_val_loss() == min(hist.val_loss()) and hist.val_loss[hist.best_epoch()] == hist.best_val_loss()
+    assert hist.training_time > 0 and hist.training_time() >= sum(hist.epoch_time_s) * 0.5
+    ep, tr, va = hist.plot_data()
+    assert ep == [float(i) for i in range(1, 13)] and tr == hist.train_loss() and va == hist.val_loss()
+    assert "12 epochs" in hist.summary() and "accuracy" in hist.summary()
+    ev = model.evaluate(val)
+    assert ev["accuracy"] > 0.85 and ev["loss"] == pytest.approx(hist.val_loss[-1], rel=1e-5)
+    out = model.predict(rt.Variable(X[:5]))
+    assert isinstance(out, rt.Variable) and out.shape == (5, 2)
+    text = model.summary()
+    assert "Model: clf" in text and "(Dense)" in text and "(None, 32)" in text and "Total params: 290" in text and "Compiled: True" in text
+    # descriptions as strings, convolution with its input channels from the data, Dense flattening the feature map
+    cnn = rt.Model("cnn")
+    for spec in ("Conv2D(4, 3, activation=relu)", "Dropout(0.1)", "Dense(8, activation=tanh)", "Dense(3)"):
+        cnn.add(spec)
+    cnn.compile(None, None, None)                                     # binding defaults: sgd, mse, no extra metrics
+    img = rt.DataLoader(rt.TensorDataset(torch.randn(16, 2, 6, 6), torch.randn(16, 3)), batch_size=8)
+    h2 = cnn.fit(img, epochs=2, verbose=False)
+    assert len(h2.train_loss) == 2 and h2.best_val_loss() is None and cnn.layers[0].inner.weight.shape == (4, 2, 3, 3)
+    assert cnn.layers[2].inner.weight.shape == (8, 4 * 4 * 4) and cnn.predict(torch.randn(3, 2, 6, 6)).shape == (3, 3)
+    with pytest.raises(ValueError):
+        cnn.add("Banana(3)")
+    with pytest.raises(ValueError):
+        rt.ModelBuilder().dense(4, "nope")
+    b2 = rt.ModelBuilder()
+    b2.conv2d(4, 3, "relu")                                           # binding form
+    b2.conv2d(4, 8, 3, 1, 1)                                          # explicit channels
+    assert b2.build()(torch.randn(1, 2, 8, 8)).shape == (1, 8, 6, 6)
+    # Trainer(config).train(model, loaders) -> history; evaluate -> metrics
+    cfg = rt.TrainerConfig(epochs=3, learning_rate=0.01, batch_size=32, device="cpu")
+    assert cfg.epochs == 3 and cfg.epochs() == 3 and cfg.device == "cpu" and cfg.device() == "cpu" and not cfg.use_mixed_precision()
+    cfg.set_epochs(4)
+    cfg.set_mixed_precision(False)
+    cfg.set_device("cpu")
+    cfg.log_frequency = 7
+    assert cfg.epochs == 4 and cfg.log_frequency == 7 and "epochs=4" in repr(cfg) and cfg.learning_rate == pytest.approx(0.01)
+    tr_ = rt.Trainer(cfg)
+    h3 = tr_.train(model, train, val)
+    assert isinstance(h3, rt.TrainingHistory) and len(h3.train_loss) == 4 and len(h3.val_loss) == 4
+    m = tr_.evaluate(model, val)
+    assert set(m) == {"loss", "accuracy"} and m["accuracy"] > 0.85 and "epochs=4" in repr(tr_)
+    hh = rt.TrainingHistory()
+    hh.add_epoch(0.5, 0.6, {"accuracy": 0.8})
+    hh.add_epoch(0.4, 0.7)
+    assert hh.train_loss() == [0.5, 0.4] and hh.val_loss() == [0.6, 0.7] and hh.best_epoch() == 0 and hh.metrics()["accuracy"] == [0.8]
+
+
+def test_binding_utils_config_serializer_comparator_profiler(tmp_path):
+    """src/python/utils.rs method sets."""
+    import rustorch as rt
+    c = rt.Config()
+    assert c.get("device") == "cpu" and c.all()["num_threads"] == "4" and repr(c) == "Config(settings=5)"
+    c.set("device", "cuda")
+    c.set("lr", "0.01")
+    path = str(tmp_path / "cfg.txt")
+    c.save_to_file(path)
+    c2 = rt.Config()
+    c2.load_from_file(path)
+    assert c2.get("device") == "cuda" and c2.get_float("lr") == 0.01 and c2.all() == c.all()
+    c2.reset()
+    assert c2.get("device") == "cpu" and c2.get("lr") is None
+    with pytest.raises(FileNotFoundError):
+        c2.load_from_file(str(tmp_path / "missing.txt"))
+    b = rt.ModelBuilder()
+    b.dense(4, "relu")
+    b.dropout(0.1)
+    b.dense(2)
+    m1, m2 = b.build("a"), b.build("b")
+    for m in (m1, m2):
+        m.compile("sgd", "mse")
+        m(torch.randn(1, 3))                                          # builds the described layers
+    st = rt.ModelComparator.get_stats(m1)
+    assert st["name"] == "a" and st["num_layers"] == 3 and st["dense_layers"] == 2 and st["dropout_layers"] == 1 and st["compiled"]
+    assert st["parameters"] == 3 * 4 + 4 + 4 * 2 + 2
+    cmp_ = rt.ModelComparator.compare(m1, m2)
+    assert cmp_["layers_identical"] and cmp_["compilation_identical"] and cmp_["model2_name"] == "b"
+    assert not cmp_["parameters_identical"]
+    file = str(tmp_path / "m.safetensors")
+    rt.ModelSerializer.export(m1, file, "safetensors")
+    info = rt.ModelSerializer.get_model_info(file)
+    assert info["exists"] and info["size"] > 0 and info["tensors"] == 4 and info["parameters"] == st["parameters"]
+    assert rt.ModelSerializer.get_model_info(str(tmp_path / "none"))["exists"] is False
+    assert len(rt.ModelSerializer.load(file)) == 4                    # path only: the tensors
+    rt.ModelSerializer.load(m2, file)
+    assert rt.ModelComparator.compare(m1, m2)["parameters_identical"]
+    with pytest.raises(ValueError, match="Unsupported export format"):
+        rt.ModelSerializer.export(m1, file, "docx")
+    p = rt.Profiler()
+    p.record("matmul", 1.0)                                           # disabled: ignored
+    p.enable()
+    for d in (0.5, 1.5, 1.0):
+        p.record("matmul", d)
+    with p.profile("scope"):
+        pass
+    s = p.get_stats()
+    assert s["matmul"] == {"count": 3.0, "total": 3.0, "mean": 1.0, "min": 0.5, "max": 1.5} and s["scope"]["count"] == 1.0
+    p.clear()
+    assert p.get_stats() == {}
+
+
+def test_binding_visualization(tmp_path):
+    """src/python/visualization.rs: Plotter, ModelVisualizer, TensorStats draw (SVG / Graphviz text) instead of printing."""
+    import rustorch as rt
+    pl = rt.Plotter("svg", "default", (8, 4), 100)
+    assert "figure_size=(8, 4)" in repr(pl) and pl.config.width == 640
+    h = rt.TrainingHistory()
+    for i in range(5):
+        h.add_epoch(1.0 / (i + 1), 1.2 / (i + 1))
+    out = str(tmp_path / "hist.svg")
+    svg = pl.plot_training_history(h, out, True)
+    assert svg.startswith("<svg") and svg.count("<polyline") == 2 and open(out).read() == svg
+    assert pl.plot_training_history(h, None, False).count("<polyline") == 1
+    assert pl.plot_tensor_as_image(rt.tensor(torch.randn(4, 6)), "w").count("<rect") == 24
+    grid = pl.plot_multiple_tensors([torch.randn(2, 2), torch.randn(3, 3), torch.randn(2, 2)], ["a", "b", "c"], (2, 2))
+    assert grid.count("<svg") == 3 and grid.count("<tr>") == 2
+    with pytest.raises(ValueError):
+        pl.plot_multiple_tensors([torch.randn(2, 2)] * 3, None, (1, 2))
+    assert "<polyline" in pl.line_plot([0, 1, 2], [1.0, 4.0, 9.0], "squares", "n", "n^2") and "squares" in pl.line_plot([0, 1], [0, 1], "squares")
+    with pytest.raises(ValueError):
+        pl.line_plot([0, 1], [1.0])
+    sc = pl.scatter_plot([0, 1, 2], [2, 1, 0], colors=[0.0, 0.5, 1.0], sizes=[2, 4, 6])
+    assert sc.count("<circle") == 3 and 'r="6.0"' in sc
+    with pytest.raises(ValueError):
+        pl.scatter_plot([0, 1], [1, 2], sizes=[1])
+    hs = pl.histogram(torch.randn(500).tolist(), 20, "h")
+    assert hs.count('<rect x=') >= 15
+    mv = rt.ModelVisualizer("dot", True, True)
+    b = rt.ModelBuilder()
+    b.dense(8, "relu")
+    b.dense(2)
+    model = b.build("viz")
+    model.compile("sgd", "mse")
+    model(torch.randn(1, 4))
+    dot = mv.visualize_model(model.summary(), str(tmp_path / "m.dot"))
+    assert dot.startswith("digraph model") and "l0 -> l1" in dot and "(None, 8)" in dot and open(tmp_path / "m.dot").read() == dot
+    assert mv.visualize_model(model.summary(), None, "svg").count("<rect x=") == 2
+    assert mv.visualize_model(model).startswith("digraph")
+    att = torch.softmax(torch.randn(2, 3, 3), -1)                     # heads averaged
+    hm = mv.plot_attention_heatmap(att, ["a", "b", "c"], "attn")
+    assert hm.count("<rect x=") == 9 and hm.count(">a<") == 2
+    with pytest.raises(ValueError):
+        mv.plot_attention_heatmap(att, ["a", "b"])
+    ts = rt.TensorStats(rt.tensor([4.0, 1.0, 3.0, 2.0]))
+    with pytest.raises(RuntimeError):
+        ts.get_stats()
+    ts.compute_stats()
+    st = ts.get_stats()
+    assert st["count"] == 4 and st["mean"] == 2.5 and st["min"] == 1.0 and st["max"] == 4.0 and st["median"] == 3.0 and st["q25"] == 2.0
+    assert st["q75"] == 4.0 and st["std"] == pytest.approx(1.118034, rel=1e-5) and ts.plot_stats(str(tmp_path / "s.svg")).startswith("<svg")
+    with pytest.raises(ValueError):
+        rt.TensorStats(torch.empty(0)).compute_stats()
