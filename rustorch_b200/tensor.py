@@ -860,6 +860,201 @@ class Tensor:
     def quantile_util(self, q: float) -> float:
         return self.quantile(q)
 
+    # ------------------------------------------------ device / metadata helpers (src/tensor/core.rs:436-445,640-790)
+    def resolve_dim(self, dim: int) -> int:
+        """Non-negative index of ``dim`` (negative values count from the end)."""
+        n = self.data.dim()
+        if not -n <= dim < n:
+            raise IndexError(f"Dimension {dim} out of range for tensor with {n} dimensions")
+        return dim % n if n else 0
+
+    def to_cpu(self) -> "Tensor":
+        return Tensor(self.data.cpu())
+
+    def is_on_gpu(self) -> bool:
+        return self.data.is_cuda
+
+    def device_type(self) -> str:
+        return self.data.device.type
+
+    def with_device(self, device) -> "Tensor":
+        return self.to_device(device)
+
+    def clone_to_device(self, device) -> "Tensor":
+        return Tensor(self.data.detach().clone().to(_dev(device)))
+
+    def clone_with_grad(self) -> "Tensor":
+        """A copy that keeps ``requires_grad`` and, when there is one, a copy of the gradient."""
+        t = self.data.detach().clone().requires_grad_(self.data.requires_grad)
+        if self.data.grad is not None:
+            t.grad = self.data.grad.detach().clone()
+        return Tensor(t)
+
+    def auto_device(self) -> "Tensor":
+        """On the GPU when one is there, else unchanged."""
+        return self.to_device("cuda") if torch.cuda.is_available() and not self.data.is_cuda else self
+
+    def as_ptr(self) -> int:
+        return self.data.data_ptr()
+
+    def get_metadata(self) -> dict:
+        """String-valued description used by the serializers (shape, dtype, device, element count, gradient flag)."""
+        return {"shape": str(list(self.data.shape)), "dtype": str(self.data.dtype).replace("torch.", ""),
+                "device": str(self.data.device), "numel": str(self.data.numel()), "requires_grad": str(self.data.requires_grad).lower()}
+
+    def batch_size(self) -> int:
+        return self.data.shape[0] if self.data.dim() else 1
+
+    # ------------------------------------------------ shape variants (src/tensor/ops/shape_operations.rs, advanced_shape.rs)
+    def can_broadcast_with(self, other) -> bool:
+        a, b = tuple(self.data.shape), tuple(_unwrap(other).shape)
+        return all(x == y or x == 1 or y == 1 for x, y in zip(reversed(a), reversed(b)))
+
+    def squeeze_dim(self, dim: int) -> "Tensor":
+        d = self.resolve_dim(dim)
+        if self.data.shape[d] != 1:
+            raise ValueError(f"Cannot squeeze dimension {dim} with size {self.data.shape[d]}")
+        return Tensor(self.data.squeeze(d))
+
+    def squeeze_all(self) -> "Tensor":
+        return Tensor(self.data.squeeze())
+
+    squeeze_view = squeeze_all
+
+    def squeeze_inplace(self) -> "Tensor":
+        self.data = self.data.squeeze()
+        return self
+
+    def unsqueeze_view(self, dim: int) -> "Tensor":
+        return Tensor(self.data.unsqueeze(dim))
+
+    expand_dims = unsqueeze_view
+
+    def unsqueeze_inplace(self, dim: int) -> "Tensor":
+        self.data = self.data.unsqueeze(dim)
+        return self
+
+    def unsqueeze_multiple(self, axes: Sequence[int]) -> "Tensor":
+        """Singleton dimensions at the positions ``axes`` of the RESULT (ascending insertion)."""
+        t = self.data
+        for a in sorted(int(x) for x in axes):
+            if not 0 <= a <= t.dim():
+                raise IndexError(f"axis {a} outside a result of {t.dim() + 1} dimensions")
+            t = t.unsqueeze(a)
+        return Tensor(t)
+
+    def flatten_from(self, start_dim: int) -> "Tensor":
+        return self.flatten_range(start_dim, None)
+
+    def flatten_range(self, start_dim: int = 0, end_dim: Optional[int] = None) -> "Tensor":
+        n = self.data.dim()
+        end = n - 1 if end_dim is None else end_dim
+        if not (0 <= start_dim <= end < max(n, 1)):
+            raise IndexError(f"flatten range [{start_dim}, {end}] outside {n} dimensions")
+        return Tensor(self.data.flatten(start_dim, end))
+
+    def flatten_view(self) -> "Tensor":
+        """Flattened without a copy; fails if the memory layout needs one."""
+        return Tensor(self.data.view(-1))
+
+    def flatten_owned(self) -> "Tensor":
+        return Tensor(self.data.reshape(-1).clone())
+
+    def flatten_inplace(self) -> "Tensor":
+        self.data = self.data.reshape(-1)
+        return self
+
+    def expand_shared(self, shape: Sequence[int]) -> "Tensor":
+        """Broadcast view (stride-0 dimensions, no copy)."""
+        return Tensor(self.data.expand(*shape))
+
+    expand_lazy = expand_shared
+
+    def expand_owned(self, shape: Sequence[int]) -> "Tensor":
+        return Tensor(self.data.expand(*shape).contiguous())
+
+    def materialize(self) -> "Tensor":
+        return Tensor(self.data.contiguous())
+
+    def repeat_advanced(self, repeats: Sequence[int]) -> "Tensor":
+        """``repeats`` may be longer than the rank (leading dimensions are added) but not shorter."""
+        if len(repeats) < self.data.dim():
+            raise ValueError(f"{len(repeats)} repeat counts for a tensor of {self.data.dim()} dimensions")
+        if any(int(r) <= 0 for r in repeats):
+            raise ValueError("repeat counts must be positive")
+        return Tensor(self.data.repeat(*[int(r) for r in repeats]))
+
+    def repeat_interleave_scalar(self, repeats: int, dim: Optional[int] = None) -> "Tensor":
+        return Tensor(self.data.repeat_interleave(int(repeats), dim=dim))
+
+    def roll_1d(self, shifts: int, dim: Optional[int] = None) -> "Tensor":
+        """Without ``dim`` the flattened tensor is rolled and reshaped back."""
+        return Tensor(self.data.roll(int(shifts)) if dim is None else self.data.roll(int(shifts), self.resolve_dim(dim)))
+
+    # ------------------------------------------------ statistics / linear algebra variants
+    def std_unbiased(self) -> float:
+        return float(self.data.float().std(unbiased=True)) if self.data.numel() > 1 else 0.0
+
+    def quantile_advanced(self, q: float) -> float:
+        if not 0.0 <= q <= 1.0:
+            raise ValueError("Quantile must be between 0 and 1")
+        if self.data.numel() == 0:
+            raise ValueError("quantile of an empty tensor")
+        return float(torch.quantile(self.data.detach().double().flatten(), q))
+
+    def count_nonzero_axis(self, axis: int) -> "Tensor":
+        return Tensor(torch.count_nonzero(self.data, dim=self.resolve_dim(axis)).float())
+
+    def qr_basic(self):
+        return self.qr()
+
+    def eig_basic(self):
+        return self.eig()
+
+    def symeig_basic(self, upper: bool = False):
+        return self.symeig(upper)
+
+    def matmul_hybrid(self, other) -> "Tensor":
+        """The reference picks a device per call (src/tensor/ops/matrix.rs); here the product runs where the data is."""
+        return self.matmul(other)
+
+    # ------------------------------------------------ predicate helpers (src/tensor/ops/utils.rs:28-140)
+    def _mask(self, condition) -> torch.Tensor:
+        """``condition`` maps the whole tensor to a boolean mask, or one element to a bool."""
+        try:
+            m = condition(self.data)
+            if isinstance(m, torch.Tensor) and m.dtype == torch.bool and m.shape == self.data.shape:
+                return m
+        except Exception:  # noqa: BLE001  (an element-wise predicate may not accept a tensor)
+            pass
+        flat = [bool(condition(v)) for v in self.data.detach().flatten().tolist()]
+        return torch.tensor(flat, dtype=torch.bool, device=self.data.device).view(self.data.shape)
+
+    def count_where(self, condition) -> int:
+        return int(self._mask(condition).sum())
+
+    def find_first(self, condition) -> Optional[int]:
+        idx = self._mask(condition).flatten().nonzero()
+        return int(idx[0]) if idx.numel() else None
+
+    def find_all(self, condition) -> List[int]:
+        return self._mask(condition).flatten().nonzero().flatten().tolist()
+
+    def replace_where(self, condition, replacement: Number) -> "Tensor":
+        return Tensor(torch.where(self._mask(condition), torch.as_tensor(replacement, dtype=self.data.dtype, device=self.data.device), self.data))
+
+    def map_with_index(self, fn) -> "Tensor":
+        """``fn(flat_index, value) -> value`` over the elements in row-major order."""
+        vals = [fn(i, v) for i, v in enumerate(self.data.detach().flatten().tolist())]
+        return Tensor(torch.tensor(vals, dtype=self.data.dtype, device=self.data.device).view(self.data.shape))
+
+    def map_inplace(self, fn) -> "Tensor":
+        self.data = self.map(fn).data
+        return self
+
+    def clone_tensor(self) -> "Tensor":
+        return self.clone()
+
     def __getattr__(self, name):
         if name.startswith("__"):
             raise AttributeError(name)

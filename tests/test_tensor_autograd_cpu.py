@@ -132,3 +132,67 @@ def test_gradient_flow_tools(tmp_path):
     an = GradientFlowAnalyzer()
     an.record(lin.named_parameters())
     assert "weight" in an.history and an.issues() == {}
+
+
+def test_tensor_shape_device_and_predicate_helpers():
+    """src/tensor/core.rs:436-445, ops/shape_operations.rs, ops/advanced_shape.rs, ops/utils.rs:28-140."""
+    from rustorch_b200.tensor import Tensor
+    t = Tensor(torch.arange(24.0).view(2, 3, 4))
+    assert t.resolve_dim(-1) == 2 and t.resolve_dim(0) == 0
+    with pytest.raises(IndexError):
+        t.resolve_dim(3)
+    assert t.to_cpu().device_type() == "cpu" and not t.is_on_gpu() and t.batch_size() == 2 and t.as_ptr() == t.data.data_ptr()
+    assert t.with_device("cpu").shape == (2, 3, 4) and t.clone_to_device("cpu").as_ptr() != t.as_ptr()
+    md = t.get_metadata()
+    assert md == {"shape": "[2, 3, 4]", "dtype": "float32", "device": "cpu", "numel": "24", "requires_grad": "false"}
+    g = Tensor(torch.ones(3), requires_grad=True)
+    (g.data * 2).sum().backward()
+    c = g.clone_with_grad()
+    assert c.requires_grad and torch.equal(c.data.grad, g.data.grad) and c.data.grad is not g.data.grad
+    assert t.can_broadcast_with(Tensor(torch.ones(3, 1))) and t.can_broadcast_with(Tensor(torch.ones(4)))
+    assert not t.can_broadcast_with(Tensor(torch.ones(3)))
+    u = Tensor(torch.zeros(1, 3, 1))
+    assert u.squeeze_dim(0).shape == (3, 1) and u.squeeze_dim(-1).shape == (1, 3) and u.squeeze_all().shape == (3,)
+    with pytest.raises(ValueError):
+        u.squeeze_dim(1)
+    assert Tensor(torch.zeros(3)).unsqueeze_multiple([0, 2]).shape == (1, 3, 1) and Tensor(torch.zeros(3)).expand_dims(1).shape == (3, 1)
+    with pytest.raises(IndexError):
+        Tensor(torch.zeros(3)).unsqueeze_multiple([3])
+    assert t.flatten_from(1).shape == (2, 12) and t.flatten_range(0, 1).shape == (6, 4) and t.flatten_view().shape == (24,)
+    with pytest.raises(IndexError):
+        t.flatten_range(2, 1)
+    o = t.flatten_owned()
+    assert o.as_ptr() != t.as_ptr() and t.flatten_view().as_ptr() == t.as_ptr()
+    v = Tensor(torch.zeros(2, 1))
+    sh = v.expand_shared([2, 5])
+    assert sh.data.stride() == (1, 0) and v.expand_owned([2, 5]).data.is_contiguous() and sh.materialize().data.is_contiguous()
+    assert Tensor(torch.zeros(2, 3)).repeat_advanced([2, 1, 2]).shape == (2, 2, 6)
+    with pytest.raises(ValueError):
+        Tensor(torch.zeros(2, 3)).repeat_advanced([2])
+    r = Tensor([1.0, 2.0, 3.0, 4.0])
+    assert r.roll_1d(1, 0).as_slice() == [4.0, 1.0, 2.0, 3.0] and r.repeat_interleave_scalar(2, 0).shape == (8,)
+    assert Tensor(torch.arange(6.0).view(2, 3)).roll_1d(1).as_slice() == [5.0, 0.0, 1.0, 2.0, 3.0, 4.0]
+    m = Tensor(torch.arange(6.0).view(2, 3))
+    m.unsqueeze_inplace(0)
+    assert m.shape == (1, 2, 3)
+    m.squeeze_inplace()
+    m.flatten_inplace()
+    assert m.shape == (6,)
+    assert r.std_unbiased() == pytest.approx(1.2909944, rel=1e-6) and r.quantile_advanced(0.5) == 2.5
+    with pytest.raises(ValueError):
+        r.quantile_advanced(1.5)
+    z = Tensor(torch.tensor([[0.0, 1.0, 2.0], [0.0, 0.0, 3.0]]))
+    assert z.count_nonzero_axis(0).as_slice() == [0.0, 1.0, 2.0] and z.count_nonzero_axis(-1).as_slice() == [2.0, 1.0]
+    q, rr = Tensor(torch.randn(4, 3)).qr_basic()
+    assert q.shape == (4, 3) and rr.shape == (3, 3)
+    w, _ = Tensor(torch.eye(3) * 2).symeig_basic()
+    assert w.as_slice() == [2.0, 2.0, 2.0]
+    assert Tensor(torch.eye(2)).matmul_hybrid(Tensor([[1.0, 2.0], [3.0, 4.0]])).as_slice() == [1.0, 2.0, 3.0, 4.0]
+    # predicates: a whole-tensor mask function or an element-wise Python predicate
+    assert r.count_where(lambda x: x > 2) == 2 and r.count_where(lambda x: 1.5 < x < 3.5) == 2
+    assert r.find_first(lambda x: x > 2) == 2 and r.find_first(lambda x: x > 9) is None and r.find_all(lambda x: x % 2 == 0) == [1, 3]
+    assert r.replace_where(lambda x: x > 2, 0.0).as_slice() == [1.0, 2.0, 0.0, 0.0]
+    assert r.map_with_index(lambda i, x: x * i).as_slice() == [0.0, 2.0, 6.0, 12.0]
+    k = r.clone_tensor()
+    k.map_inplace(lambda x: x + 1)
+    assert k.as_slice() == [2.0, 3.0, 4.0, 5.0] and r.as_slice() == [1.0, 2.0, 3.0, 4.0]
