@@ -393,3 +393,104 @@ for _k, _cls in enumerate((Adam, AdamW, Adamax, NAdam, RAdam)):
 for _cls, _kind in ((Adam, 0), (AdamW, 1), (SGD, 2), (NAdam, 3), (RAdam, 4), (Adamax, 5), (RMSprop, 6), (AdaGrad, 7), (AdaBound, 8),
                     (LAMB, 9)):
     _cls._MT_KIND = _kind
+
+
+# ---- named constructors of the Rust API (``Type::new / default_params / with_*``); the parameters come first here
+def _ctor(cls, name: str, fn) -> None:
+    setattr(cls, name, classmethod(fn))
+
+
+for _cls in (SGD, Adam, AdamW, RMSprop, AdaGrad, NAdam, RAdam, Adamax, AdaBound, LAMB, LBFGS):
+    _ctor(_cls, "new", lambda cls, params=None, *a, **k: cls(params, *a, **k))
+
+# src/optim/adamw.rs:66-80
+_ctor(AdamW, "with_weight_decay", lambda cls, params, lr, weight_decay: cls(params, lr, weight_decay=weight_decay))
+_ctor(AdamW, "with_amsgrad", lambda cls, params, lr, weight_decay=0.01: cls(params, lr, weight_decay=weight_decay, amsgrad=True))
+# src/optim/mod.rs:447-500, 646-660
+_ctor(RMSprop, "with_momentum", lambda cls, params, lr, alpha=0.99, eps=1e-8, momentum=0.0: cls(params, lr, alpha, eps, momentum=momentum))
+_ctor(RMSprop, "with_weight_decay", lambda cls, params, lr, alpha=0.99, eps=1e-8, weight_decay=0.0: cls(params, lr, alpha, eps, weight_decay))
+_ctor(AdaGrad, "with_weight_decay", lambda cls, params, lr, eps=1e-10, weight_decay=0.0: cls(params, lr, weight_decay=weight_decay, eps=eps))
+# src/optim/nadam.rs:156-175, radam.rs:206-225, adamax.rs:152-171
+_ctor(NAdam, "default_params", lambda cls, params, lr=2e-3: cls(params, lr))
+_ctor(NAdam, "with_weight_decay", lambda cls, params, lr, weight_decay: cls(params, lr, weight_decay=weight_decay))
+_ctor(NAdam, "with_momentum_decay", lambda cls, params, lr, momentum_decay: cls(params, lr, momentum_decay=momentum_decay))
+_ctor(RAdam, "default_params", lambda cls, params, lr=1e-3: cls(params, lr))
+_ctor(RAdam, "with_weight_decay", lambda cls, params, lr, weight_decay: cls(params, lr, weight_decay=weight_decay))
+_ctor(Adamax, "default_params", lambda cls, params, lr=2e-3: cls(params, lr))
+_ctor(Adamax, "with_weight_decay", lambda cls, params, lr, weight_decay: cls(params, lr, weight_decay=weight_decay))
+_ctor(Adamax, "with_infinity_eps", lambda cls, params, lr, infinity_eps: cls(params, lr, eps=infinity_eps))
+# src/optim/lamb.rs:40-75, adabound.rs:41-64, lbfgs.rs:206-250
+_ctor(LAMB, "with_params", lambda cls, params, lr, beta1=0.9, beta2=0.999, eps=1e-6, weight_decay=0.01:
+      cls(params, lr, (beta1, beta2), eps, weight_decay))
+_ctor(LAMB, "without_bias_correction", lambda cls, params, lr, beta1=0.9, beta2=0.999, eps=1e-6, weight_decay=0.01:
+      cls(params, lr, (beta1, beta2), eps, weight_decay, bias_correction=False))
+_ctor(AdaBound, "with_params", lambda cls, params, lr, final_lr=0.1, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, gamma=1e-3:
+      cls(params, lr, final_lr, (beta1, beta2), eps, weight_decay, gamma))
+
+
+def _lbfgs_with_params(cls, params, lr, max_iter=20, max_eval=20, tolerance_grad=1e-5, tolerance_change=1e-9, history_size=10,
+                       line_search_fn="strong_wolfe"):
+    if lr <= 0:
+        raise ValueError("Learning rate must be positive")
+    if tolerance_grad < 0 or tolerance_change < 0:
+        raise ValueError("Tolerances must be non-negative")
+    if history_size <= 0:
+        raise ValueError("History size must be positive")
+    ls = getattr(line_search_fn, "value", line_search_fn)
+    ls = None if ls in (None, "none", "None") else "strong_wolfe" if "wolfe" in str(ls).lower() else ls
+    return cls(params, lr, max_iter, max_eval, tolerance_grad, tolerance_change, history_size, ls)
+
+
+_ctor(LBFGS, "with_params", _lbfgs_with_params)
+
+
+def _set_final_lr(self, final_lr: float) -> None:
+    for g in self.param_groups:
+        g["final_lr"] = float(final_lr)
+
+
+AdaBound.set_final_lr = _set_final_lr
+
+
+def _radam_with_threshold(cls, params, lr, threshold: float):
+    """The rectification threshold is part of the fused update rules (``rho_t > 5``, as in PyTorch); the reference's
+    default is 4 (src/optim/radam.rs:25-40).  Another value takes a per-tensor update written out here."""
+    opt = cls(params, lr)
+    if float(threshold) != 5.0:
+        opt.threshold = float(threshold)
+        opt._MT_KIND = opt._NATIVE_KIND = None
+        opt._fallback_step = lambda: _radam_step(opt)
+    return opt
+
+
+@torch.no_grad()
+def _radam_step(self) -> None:
+    for g in self.param_groups:
+        b1, b2 = g["betas"]
+        rho_inf = 2.0 / (1.0 - b2) - 1.0
+        for p in g["params"]:
+            if p.grad is None:
+                continue
+            grad = p.grad.float()
+            if g["weight_decay"]:
+                grad = grad.add(p.float(), alpha=g["weight_decay"])
+            st = self.state[p]
+            if not st:
+                st["step"] = 0
+                st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+            st["step"] += 1
+            t = int(st["step"])
+            st["exp_avg"].mul_(b1).add_(grad, alpha=1 - b1)
+            st["exp_avg_sq"].mul_(b2).addcmul_(grad, grad, value=1 - b2)
+            m_hat = st["exp_avg"] / (1 - b1 ** t)
+            rho_t = rho_inf - 2.0 * t * b2 ** t / (1 - b2 ** t)
+            if rho_t > self.threshold:
+                rect = math.sqrt((rho_t - 4) * (rho_t - 2) * rho_inf / ((rho_inf - 4) * (rho_inf - 2) * rho_t))
+                v_hat = (st["exp_avg_sq"] / (1 - b2 ** t)).sqrt().add_(g["eps"])
+                p.add_((-g["lr"] * rect * m_hat / v_hat).to(p.dtype))
+            else:
+                p.add_((-g["lr"] * m_hat).to(p.dtype))
+
+
+_ctor(RAdam, "with_threshold", _radam_with_threshold)

@@ -124,3 +124,48 @@ def test_utils():
     assert isinstance(optim.OptimizerFactory.create("radam", [p], lr=0.1), optim.RAdam)
     r = optim.OptimizerBenchmark(2, 100, 20).run("adamax")
     assert r["steps_per_s"] > 0
+
+
+def test_named_constructors_of_the_rust_api():
+    """``Type::new / default_params / with_*`` (src/optim/mod.rs:93-137,233-296,424-500; adamw.rs:39-80; nadam.rs:135-175;
+    radam.rs:187-225; adamax.rs:133-171; lamb.rs:34-75; adabound.rs:35-70; lbfgs.rs:192-250), parameters first."""
+    import rustorch_b200.optim as O
+    p = lambda: [torch.nn.Parameter(torch.ones(3))]   # noqa: E731
+    assert O.SGD.new(p(), 0.1).learning_rate == pytest.approx(0.1) and O.Adam.new(p(), 0.01, (0.8, 0.9), 1e-6).beta1 == pytest.approx(0.8)
+    assert O.AdamW.with_weight_decay(p(), 1e-3, 0.1).weight_decay == pytest.approx(0.1) and O.AdamW.with_amsgrad(p(), 1e-3).amsgrad
+    r = O.RMSprop.with_momentum(p(), 0.01, 0.9, 1e-7, 0.5)
+    assert (r.param_groups[0]["alpha"], r.eps, r.momentum) == (0.9, pytest.approx(1e-7), pytest.approx(0.5))
+    assert O.RMSprop.with_weight_decay(p(), 0.01, 0.99, 1e-8, 0.1).weight_decay == pytest.approx(0.1)
+    assert O.AdaGrad.with_weight_decay(p(), 0.01, 1e-9, 0.2).eps == pytest.approx(1e-9)
+    n = O.NAdam.with_momentum_decay(p(), 2e-3, 0.01)
+    assert n.param_groups[0]["momentum_decay"] == 0.01 and O.NAdam.default_params(p()).learning_rate == pytest.approx(2e-3)
+    assert O.NAdam.with_weight_decay(p(), 2e-3, 0.1).weight_decay == pytest.approx(0.1)
+    assert O.Adamax.with_infinity_eps(p(), 2e-3, 1e-5).eps == pytest.approx(1e-5) and O.Adamax.default_params(p()).eps == pytest.approx(1e-7)
+    assert O.Adamax.with_weight_decay(p(), 2e-3, 0.1).weight_decay == pytest.approx(0.1)
+    la = O.LAMB.with_params(p(), 1e-3, 0.8, 0.9, 1e-5, 0.0)
+    assert (la.beta1, la.beta2, la.eps, la.weight_decay) == tuple(pytest.approx(v) for v in (0.8, 0.9, 1e-5, 0.0))
+    assert la.param_groups[0]["bias_correction"] and not O.LAMB.without_bias_correction(p(), 1e-3).param_groups[0]["bias_correction"]
+    ab = O.AdaBound.with_params(p(), 1e-3, 0.05, gamma=1e-2)
+    ab.set_final_lr(0.2)
+    assert ab.param_groups[0]["final_lr"] == 0.2 and ab.param_groups[0]["gamma"] == 1e-2
+    lb = O.LBFGS.with_params(p(), 0.5, 10, 15, 1e-6, 1e-10, 5, "StrongWolfe")
+    g = lb.param_groups[0]
+    assert (g["lr"], g["max_iter"], g["max_eval"], g["history_size"], g["line_search_fn"]) == (0.5, 10, 15, 5, "strong_wolfe")
+    for bad in (dict(lr=0.0), dict(lr=1.0, tolerance_grad=-1.0), dict(lr=1.0, history_size=0)):
+        with pytest.raises(ValueError):
+            O.LBFGS.with_params(p(), **bad)
+    # RAdam: threshold 5 is the fused rule; another value changes when rectification starts
+    torch.manual_seed(0)
+    w5, w4, wt = (torch.nn.Parameter(torch.tensor([1.0, -2.0, 3.0])) for _ in range(3))
+    o5, o4, ot = O.RAdam.with_threshold([w5], 0.01, 5.0), O.RAdam.with_threshold([w4], 0.01, 4.0), torch.optim.RAdam([wt], 0.01)
+    first_diff = None
+    for step in range(1, 9):
+        gr = torch.randn(3)
+        for w, o in ((w5, o5), (w4, o4), (wt, ot)):
+            w.grad = gr.clone()
+            o.step()
+        assert torch.allclose(w5, wt, atol=1e-6)                      # threshold 5 == torch
+        if first_diff is None and not torch.allclose(w4, w5, atol=1e-7):
+            first_diff = step
+    # with beta2 = 0.999, rho_t passes 4 at step 5 and 5 at step 6: the two runs part at step 5
+    assert first_diff == 5 and O.RAdam.with_weight_decay(p(), 1e-3, 0.1).weight_decay == pytest.approx(0.1)
