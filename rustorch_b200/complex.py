@@ -69,6 +69,8 @@ class Complex:
     def abs(self) -> float:
         return math.hypot(self.re, self.im)
 
+    __abs__ = abs
+
     def abs_sq(self) -> float:
         return self.re * self.re + self.im * self.im
 

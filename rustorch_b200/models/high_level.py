@@ -276,8 +276,11 @@ class Sequential(Model):
         return self
 
     def forward(self, x):
-        for l in self.layers:
+        shapes = self.__dict__.setdefault("_out_shapes", {})
+        for i, l in enumerate(self.layers):
             x = l(x)
+            if isinstance(x, torch.Tensor):
+                shapes[i] = (None, *x.shape[1:])
         return x
 
     def compile(self, optimizer: Union[str, torch.optim.Optimizer, None] = "adam", loss: Union[str, nn.Module, None] = "mse",
@@ -417,7 +420,7 @@ class Sequential(Model):
         for i, l in enumerate(self.layers):
             n = sum(p.numel() for p in l.parameters())
             total += n
-            shape = getattr(l, "last_output_shape", None)
+            shape = self.__dict__.get("_out_shapes", {}).get(i, getattr(l, "last_output_shape", None))
             rows.append(f"{f'{type(l).__name__.lower().lstrip(chr(95))}_{i} ({_layer_kind(l)})':<29}"
                         f"{str(shape) if shape is not None else '?':<26}{n:,}")
         rows += ["=" * 65, f"Total params: {total:,}", f"Compiled: {bool(getattr(self, 'compiled', False))}"]

@@ -331,12 +331,18 @@ class Dropout(nn.Module):
             raise ValueError("dropout probability must be in [0, 1]")
         self.p, self.inplace = p, inplace
 
+    def is_training(self) -> bool:
+        return self.training
+
     def forward(self, x):
         return _pool.dropout(x, self.p, self.training, self.inplace)      # Philox kernel on CUDA, no mask tensor
 
 
 class AlphaDropout(nn.AlphaDropout):
     pass
+
+
+Identity = nn.Identity
 
 
 def dropout(x, p: float = 0.5, training: bool = True):

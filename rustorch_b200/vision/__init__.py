@@ -185,14 +185,38 @@ class ToTensor(Transform):
 
 
 class ColorJitter(Transform):
-    def __init__(self, brightness: float = 0.0, contrast: float = 0.0, generator: Optional[torch.Generator] = None):
-        self.brightness, self.contrast, self.generator = brightness, contrast, generator
+    """Random brightness, contrast, saturation and hue changes of ``[..., C, H, W]`` images in ``[0, 1]``; each factor is
+    drawn uniformly from ``1 +- amount`` (hue: a rotation of the chroma plane by up to ``hue`` turns)."""
+
+    def __init__(self, brightness: float = 0.0, contrast: float = 0.0, saturation: float = 0.0, hue: float = 0.0,
+                 generator: Optional[torch.Generator] = None):
+        if isinstance(saturation, torch.Generator):                   # (brightness, contrast, generator)
+            saturation, generator = 0.0, saturation
+        if min(brightness, contrast, saturation) < 0 or not 0.0 <= hue <= 0.5:
+            raise ValueError("jitter amounts must be non-negative and hue at most 0.5")
+        self.brightness, self.contrast, self.saturation, self.hue, self.generator = brightness, contrast, saturation, hue, generator
+
+    def _draw(self, amount: float) -> float:
+        return 1 + (float(torch.rand(1, generator=self.generator)) * 2 - 1) * amount
 
     def apply(self, x):
-        b = 1 + (float(torch.rand(1, generator=self.generator)) * 2 - 1) * self.brightness
-        c = 1 + (float(torch.rand(1, generator=self.generator)) * 2 - 1) * self.contrast
-        mean = x.float().mean(dim=(-3, -2, -1), keepdim=True)
-        return ((x.float() * b - mean) * c + mean).clamp(0, 1)
+        x = x.float()
+        b, c = self._draw(self.brightness), self._draw(self.contrast)
+        mean = x.mean(dim=(-3, -2, -1), keepdim=True)
+        x = ((x * b - mean) * c + mean).clamp(0, 1)
+        if x.shape[-3] == 3 and (self.saturation or self.hue):
+            wts = torch.tensor([0.299, 0.587, 0.114], device=x.device).view(3, 1, 1)
+            grey = (x * wts).sum(-3, keepdim=True)
+            if self.saturation:
+                x = (grey + (x - grey) * self._draw(self.saturation)).clamp(0, 1)
+            if self.hue:
+                # rotate the chroma (I, Q) plane of YIQ by the drawn angle
+                ang = (float(torch.rand(1, generator=self.generator)) * 2 - 1) * self.hue * 2 * math.pi
+                to_yiq = torch.tensor([[0.299, 0.587, 0.114], [0.596, -0.274, -0.322], [0.211, -0.523, 0.312]], device=x.device)
+                rot = torch.tensor([[1.0, 0.0, 0.0], [0.0, math.cos(ang), -math.sin(ang)], [0.0, math.sin(ang), math.cos(ang)]], device=x.device)
+                m = torch.linalg.inv(to_yiq) @ rot @ to_yiq
+                x = torch.einsum("ij,...jhw->...ihw", m, x).clamp(0, 1)
+        return x
 
 
 class Compose(Transform):

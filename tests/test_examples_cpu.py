@@ -1,9 +1,13 @@
 """The programs under examples/ run to completion on CPU."""
+import contextlib
+import io
 import os
+import runpy
 import subprocess
 import sys
 
 import pytest
+import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -17,3 +21,24 @@ def test_example_runs(name):
     r = subprocess.run([sys.executable, os.path.join(ROOT, "examples", name + ".py")], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0, r.stderr[-2000:]
     assert r.stdout.strip()
+
+
+@pytest.mark.parametrize("name", ["mlp_training", "cnn_demo", "readme_basic_usage_demo", "tensor_nd_demo", "broadcasting_demo",
+                                  "activation_demo", "special_functions_demo", "complex_tensor_demo", "fft_demo",
+                                  "matrix_decomposition_demo", "linear_regression", "boston_housing_regression", "embedding_demo",
+                                  "batchnorm_demo", "adamw_scheduler_demo", "gradient_flow_demo", "neural_network_demo",
+                                  "complete_training_demo", "rnn_sequence_demo", "data_loading_demo", "vision_pipeline_demo",
+                                  "visualization_demo", "distributions_demo", "quantization_sparsity_demo", "model_hub_demo",
+                                  "validation_debug_demo", "llm_decode_demo", "gpu_kernel_demo"])
+def test_example_runs_in_process(name, monkeypatch):
+    """The single-process examples, run inside this interpreter (no second import of torch per program)."""
+    if torch.cuda.is_available():
+        pytest.skip("the in-process form is the CPU check; on a GPU box run the programs themselves")
+    monkeypatch.syspath_prepend(os.path.join(ROOT, "examples"))
+    out = io.StringIO()
+    with contextlib.redirect_stdout(out):
+        try:
+            runpy.run_path(os.path.join(ROOT, "examples", name + ".py"), run_name="__main__")
+        except SystemExit as e:
+            assert not e.code
+    assert out.getvalue().strip()
