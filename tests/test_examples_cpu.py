@@ -42,3 +42,24 @@ def test_example_runs_in_process(name, monkeypatch):
         except SystemExit as e:
             assert not e.code
     assert out.getvalue().strip()
+
+
+def test_quickstart_notebook_cells_run(monkeypatch):
+    import json
+    nb = json.load(open(os.path.join(ROOT, "notebooks", "quickstart.ipynb")))
+    assert nb["nbformat"] == 4
+    monkeypatch.chdir(os.path.join(ROOT, "notebooks"))
+    ns: dict = {}
+    out = io.StringIO()
+    with contextlib.redirect_stdout(out):
+        for cell in nb["cells"]:
+            if cell["cell_type"] == "code":
+                src = "".join(cell["source"])
+                if "IPython" in src and "IPython" not in sys.modules:
+                    try:
+                        import IPython  # noqa: F401
+                    except ImportError:
+                        continue
+                exec(compile(src, "<notebook cell>", "exec"), ns)
+    text = out.getvalue()
+    assert "dy/dx = [7.0, 9.0]" in text and "Total params" in text and "epochs" in text
