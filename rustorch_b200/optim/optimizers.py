@@ -24,9 +24,16 @@ class _RefAPI:
 
     _MT_KIND: Optional[int] = None          # update rule of csrc/optim/multi_tensor_optim.cu, None: no native step
 
-    def step(self, closure=None):           # noqa: D401
+    def step(self, closure=None, grad=None):           # noqa: D401
         """One optimizer step.  CUDA parameters are updated by the multi-tensor kernel (one launch per 32 tensors,
-        see :mod:`rustorch_b200.optim.multi_tensor`); anything it does not cover takes the per-tensor path."""
+        see :mod:`rustorch_b200.optim.multi_tensor`); anything it does not cover takes the per-tensor path.
+        ``step(param, grad)`` with two tensors is the reference's per-tensor call (``Optimizer::step(&param, &grad)``,
+        src/optim/mod.rs:45-60) and goes to :meth:`step_tensor`."""
+        if grad is not None:
+            from ..tensor import _unwrap
+            raw = lambda t: t.tensor if hasattr(t, "tensor") and isinstance(t.tensor, torch.Tensor) else _unwrap(t)   # noqa: E731
+            self.step_tensor(raw(closure), raw(grad))
+            return None
         loss = None
         if closure is not None:
             with torch.enable_grad():
@@ -397,11 +404,21 @@ for _cls, _kind in ((Adam, 0), (AdamW, 1), (SGD, 2), (NAdam, 3), (RAdam, 4), (Ad
 
 # ---- named constructors of the Rust API (``Type::new / default_params / with_*``); the parameters come first here
 def _ctor(cls, name: str, fn) -> None:
-    setattr(cls, name, classmethod(fn))
+    """Registers ``fn(cls, params, ...)`` as a classmethod.  A leading number instead of parameters is the Rust call
+    (``SGD::new(0.01)``): an optimizer without registered parameters, stepped with ``step(param, grad)``."""
+    def make(c, *a, **k):
+        if a and isinstance(a[0], (int, float)) and not isinstance(a[0], bool):
+            a = (None,) + a
+        return fn(c, *a, **k)
+    make.__name__ = name
+    setattr(cls, name, classmethod(make))
 
 
 for _cls in (SGD, Adam, AdamW, RMSprop, AdaGrad, NAdam, RAdam, Adamax, AdaBound, LAMB, LBFGS):
     _ctor(_cls, "new", lambda cls, params=None, *a, **k: cls(params, *a, **k))
+    for _name in ("default_params", "with_momentum", "with_weight_decay", "with_nesterov", "with_amsgrad"):
+        if _name in _cls.__dict__:                      # the ones written in the class bodies take the same two call forms
+            _ctor(_cls, _name, _cls.__dict__[_name].__func__)
 
 # src/optim/adamw.rs:66-80
 _ctor(AdamW, "with_weight_decay", lambda cls, params, lr, weight_decay: cls(params, lr, weight_decay=weight_decay))

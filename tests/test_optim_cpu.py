@@ -169,3 +169,29 @@ def test_named_constructors_of_the_rust_api():
             first_diff = step
     # with beta2 = 0.999, rho_t passes 4 at step 5 and 5 at step 6: the two runs part at step 5
     assert first_diff == 5 and O.RAdam.with_weight_decay(p(), 1e-3, 0.1).weight_decay == pytest.approx(0.1)
+
+
+def test_rust_call_forms_without_parameters():
+    """``SGD::new(0.01)`` then ``optimizer.step(&param, &grad)`` (README of the reference; src/optim/mod.rs:45-60,93-137)."""
+    import rustorch as rt
+    import rustorch_b200.optim as O
+    o = O.SGD.new(0.1)
+    p, g = rt.tensor([1.0, 2.0]), rt.tensor([1.0, 1.0])
+    o.step(p, g)                                                     # wrapper tensors, updated in place
+    assert p.as_slice() == pytest.approx([0.9, 1.9]) and o.learning_rate == pytest.approx(0.1)
+    m = O.SGD.with_momentum(0.1, 0.9)
+    t = torch.ones(3)
+    m.step(t, torch.ones(3))
+    m.step(t, torch.ones(3))
+    assert t.tolist() == pytest.approx([0.71] * 3)                    # 1 - 0.1 - 0.1 * 1.9
+    a = O.Adam.default_params(0.01)
+    a.step(t, torch.ones(3))
+    assert t.tolist() == pytest.approx([0.70] * 3, abs=1e-6) and a.beta1 == pytest.approx(0.9)
+    assert O.AdamW.default_params(1e-3).weight_decay == pytest.approx(0.01) and O.RMSprop.default_params(0.01).eps == pytest.approx(1e-8)
+    assert O.NAdam.with_weight_decay(2e-3, 0.1).weight_decay == pytest.approx(0.1) and O.LBFGS.new(1.0).learning_rate == 1.0
+    lin = torch.nn.Linear(2, 1)
+    assert O.SGD.with_momentum(lin.parameters(), 0.1, 0.9).momentum == pytest.approx(0.9)      # parameters first still works
+    sched = O.WarmupScheduler(O.SGD.new(0.01), 0.1, 5)
+    for _ in range(5):
+        sched.step()
+    assert sched.optimizer.learning_rate == pytest.approx(0.1)
