@@ -55,6 +55,8 @@ class Linear(nn.Module):
 
     def __init__(self, input_size: int, output_size: int, bias: Optional[bool] = True, device=None, dtype=None):
         super().__init__()
+        if int(input_size) <= 0 or int(output_size) <= 0:
+            raise ValueError("Linear: input_size and output_size must be positive")
         self.input_size, self.output_size = input_size, output_size
         std = math.sqrt(2.0 / input_size)
         kw = dict(device=device, dtype=dtype)

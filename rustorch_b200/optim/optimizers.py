@@ -176,8 +176,29 @@ class _RefAPI:
         return {k: v for k, v in g.items() if isinstance(v, (int, float, bool))}
 
 
+def _raw_param(p):
+    """The leaf ``torch.Tensor`` behind a ``Variable`` / ``Tensor`` wrapper: the binding's optimizers take lists of
+    Variables (python/src/lib.rs:454-470), and stepping must update the wrapped tensor in place."""
+    if isinstance(p, torch.Tensor):
+        return p
+    inner = getattr(p, "tensor", None)                   # Variable
+    if not isinstance(inner, torch.Tensor):
+        inner = getattr(p, "data", None)                 # Tensor
+    if not isinstance(inner, torch.Tensor):
+        raise TypeError(f"optimizer can only optimize tensors, got {type(p).__name__}")
+    return inner
+
+
 def _params(params) -> Iterable:
-    return params if params is not None else [torch.nn.Parameter(torch.zeros(0))]
+    if params is None:
+        return [torch.nn.Parameter(torch.zeros(0))]
+    out = []
+    for p in params:
+        if isinstance(p, dict):
+            out.append({**p, "params": [_raw_param(q) for q in (p["params"] if isinstance(p["params"], (list, tuple)) else [p["params"]])]})
+        else:
+            out.append(_raw_param(p))
+    return out
 
 
 class SGD(_RefAPI, torch.optim.SGD):

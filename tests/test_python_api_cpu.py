@@ -377,3 +377,75 @@ def test_binding_visualization(tmp_path):
     assert st["q75"] == 4.0 and st["std"] == pytest.approx(1.118034, rel=1e-5) and ts.plot_stats(str(tmp_path / "s.svg")).startswith("<svg")
     with pytest.raises(ValueError):
         rt.TensorStats(torch.empty(0)).compute_stats()
+
+
+def test_flows_of_the_reference_wheel_tests():
+    """Call sequences of the reference's own Python tests (python/tests/test_phase3.py, test_phase4_*.py,
+    test_phase5_autograd.py), re-expressed: optimizers over lists of Variables and of layer parameters, positional layer
+    constructors, train / eval switches, ``rustorch.grad``."""
+    import rustorch
+    rustorch.set_seed(0)
+    v = rustorch.Variable(rustorch.tensor([1.0, 2.0]), requires_grad=True)
+    opt = rustorch.SGD([v], lr=0.1, momentum=0.0)
+    (v * v).sum().backward()
+    opt.step()
+    assert v.data.as_slice() == pytest.approx([0.8, 1.6])            # the wrapped tensor was updated in place
+    opt.zero_grad()
+    assert v.grad is None
+    adam = rustorch.Adam([v], lr=0.001, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, amsgrad=False)
+    (v * 3.0).sum().backward()
+    adam.step()
+    assert v.data.as_slice() == pytest.approx([0.799, 1.599], abs=1e-5)
+    X = rustorch.Variable(rustorch.tensor([1.0, 2.0]), requires_grad=False)
+    y = rustorch.Variable(rustorch.tensor([1.0]), requires_grad=False)
+    l1, l2 = rustorch.Linear(2, 4, True), rustorch.Linear(4, 1, True)
+    relu, sig, crit = rustorch.ReLU(), rustorch.Sigmoid(), rustorch.MSELoss()
+    sgd = rustorch.SGD([l1.weight, l1.bias, l2.weight, l2.bias], lr=0.5, momentum=0.0)
+    losses = []
+    for _ in range(20):
+        sgd.zero_grad()
+        loss = crit(sig(l2(relu(l1(X)))), y)
+        loss.backward()
+        sgd.step()
+        losses.append(float(loss.item()))
+    assert isinstance(loss, rustorch.Variable) and losses[-1] < losses[0]
+    with pytest.raises(ValueError):
+        rustorch.Linear(0, 5, True)
+    assert rustorch.Linear(3, 2, bias=False).bias is None
+    # CNN stack with positional constructor arguments, in training and evaluation mode
+    layers = [rustorch.Conv2d(1, 4, (3, 3), (1, 1), (1, 1), True), rustorch.BatchNorm2d(4, 1e-5, 0.1, True), rustorch.ReLU(),
+              rustorch.MaxPool2d((2, 2), (2, 2), (0, 0)), rustorch.Flatten(1, -1), rustorch.Linear(4 * 4 * 4, 8, True),
+              rustorch.BatchNorm1d(8, 1e-5, 0.1, True, True), rustorch.Dropout(0.5, False), rustorch.Linear(8, 3, True)]
+    params = [p for l in layers for p in (getattr(l, "weight", None), getattr(l, "bias", None)) if p is not None]
+    opt2 = rustorch.Adam(params, lr=0.01, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, amsgrad=False)
+    img = rustorch.Variable(rustorch.tensor(torch.randn(6, 1, 8, 8)), requires_grad=False)
+    tgt = rustorch.Variable(rustorch.tensor(torch.tensor([0.0, 1.0, 2.0, 0.0, 1.0, 2.0])), requires_grad=False)
+    ce = rustorch.CrossEntropyLoss()
+
+    def run(x):
+        for l in layers:
+            x = l(x)
+        return x
+
+    first = None
+    for _ in range(15):
+        for l in layers:
+            l.train()
+        opt2.zero_grad()
+        loss = ce(run(img), tgt)
+        loss.backward()
+        opt2.step()
+        first = first if first is not None else float(loss.item())
+    for l in layers:
+        l.eval()
+    out = run(img)
+    assert isinstance(out, rustorch.Variable) and out.shape == (6, 3) and float(loss.item()) < first
+    assert torch.equal(run(img).tensor, out.tensor)                   # evaluation mode: dropout off, running statistics
+    a = rustorch.Variable(rustorch.tensor([2.0, 3.0]), requires_grad=True)
+    yv = (a * a).sum()
+    g = rustorch.grad([yv], [a], retain_graph=False, create_graph=False)
+    assert g[0].as_slice() == [4.0, 6.0]
+    with rustorch.no_grad():
+        assert not (a * 2.0).requires_grad
+    with rustorch.enable_grad():
+        assert (a * 2.0).requires_grad
