@@ -83,8 +83,11 @@ def __getattr__(name):
         from .python_api import Transforms
         return getattr(Transforms, name)
     if name == "functional":
-        from .nn import layers
-        return layers
+        from .nn import functional
+        return functional
+    if name == "is_tensor":
+        from .tensor import Tensor
+        return lambda obj: isinstance(obj, Tensor)
     if name in _SUBMODULES:
         return importlib.import_module(f"{__name__}.{name}")
     mod = _LAZY.get(name)
@@ -95,4 +98,4 @@ def __getattr__(name):
 
 
 def __dir__():
-    return sorted(list(globals()) + list(_LAZY) + list(_SUBMODULES) + ["functional"] + list(_FUNCTIONAL) + list(_TRANSFORMS))
+    return sorted(list(globals()) + list(_LAZY) + list(_SUBMODULES) + ["functional", "is_tensor"] + list(_FUNCTIONAL) + list(_TRANSFORMS))

@@ -13,3 +13,4 @@ from .safe_ops import SafeOps, TensorStats
 from .conv_base import ConvOps, Validator, collect_conv_parameters
 from .recurrent_common import (MultiLayerUtils, RecurrentConfig, RecurrentOps, TrainingMode,
                                collect_recurrent_parameters)
+from . import functional  # noqa: E402,F401

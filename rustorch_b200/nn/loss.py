@@ -38,7 +38,16 @@ def mse_loss(input, target, reduction="mean"):
     return F.mse_loss(input, target, reduction=_red(reduction))
 
 
+def _class_targets(input, target):
+    """Class indices held in a floating tensor (the binding has one tensor type, so its targets are floats) become
+    ``long``; a floating target of the logits' own shape is a distribution over classes and stays as it is."""
+    if isinstance(target, torch.Tensor) and target.is_floating_point() and target.dim() == input.dim() - 1:
+        return target.long()
+    return target
+
+
 def cross_entropy(input, target, weight=None, ignore_index: int = -100, reduction="mean", label_smoothing: float = 0.0):
+    target = _class_targets(input, target)
     return F.cross_entropy(input, target, weight, ignore_index=ignore_index, reduction=_red(reduction),
                            label_smoothing=label_smoothing)
 
@@ -47,7 +56,7 @@ cross_entropy_loss = cross_entropy
 
 
 def nll_loss(input, target, weight=None, ignore_index: int = -100, reduction="mean"):
-    return F.nll_loss(input, target, weight, ignore_index=ignore_index, reduction=_red(reduction))
+    return F.nll_loss(input, _class_targets(input, target), weight, ignore_index=ignore_index, reduction=_red(reduction))
 
 
 def binary_cross_entropy(input, target, weight=None, reduction="mean"):
@@ -131,7 +140,7 @@ class CrossEntropyLoss(_Loss):
         self.ignore_index, self.label_smoothing = ignore_index, label_smoothing
 
     def forward(self, input, target):
-        return cross_entropy(input, target.long(), self.weight, self.ignore_index, self.reduction, self.label_smoothing)
+        return cross_entropy(input, target, self.weight, self.ignore_index, self.reduction, self.label_smoothing)
 
 
 class NLLLoss(_Loss):

@@ -449,3 +449,32 @@ def test_flows_of_the_reference_wheel_tests():
         assert not (a * 2.0).requires_grad
     with rustorch.enable_grad():
         assert (a * 2.0).requires_grad
+
+
+def test_alias_package_shares_modules_and_functional_namespace():
+    """``import rustorch.nn`` must give the same module object as ``rustorch_b200.nn`` (one copy of every class), and
+    ``rustorch.nn.functional`` has the stateless forms (python/python/rustorch/nn.py:444-464)."""
+    import rustorch
+    import rustorch.nn as N
+    import rustorch.optim
+    import rustorch_b200
+    from rustorch.models.high_level import ModelBuilder
+    from rustorch.nn import functional as F
+    assert N is rustorch_b200.nn and F is rustorch_b200.nn.functional and rustorch.optim is rustorch_b200.optim
+    assert ModelBuilder is rustorch_b200.models.high_level.ModelBuilder and rustorch.functional is F
+    with pytest.raises(ImportError):
+        import rustorch.does_not_exist  # noqa: F401
+    assert rustorch.is_tensor(rustorch.tensor([1.0])) and not rustorch.is_tensor(torch.ones(1))
+    v = rustorch.Variable(rustorch.tensor([[-1.0, 2.0]]), requires_grad=True)
+    assert isinstance(N.Linear(2, 3)(v), rustorch.Variable)
+    r = F.relu(v)
+    assert isinstance(r, rustorch.Variable) and r.data.as_slice() == [0.0, 2.0]
+    assert float(F.mse_loss(v, rustorch.Variable(rustorch.zeros([1, 2]))).item()) == 2.5
+    ce = F.cross_entropy(v, rustorch.tensor([1.0]))                  # class index held in a float tensor
+    assert isinstance(ce, rustorch.Variable) and float(ce.item()) == pytest.approx(0.048587, rel=1e-4)
+    soft = F.cross_entropy(torch.tensor([[-1.0, 2.0]]), torch.tensor([[0.25, 0.75]]))      # a distribution stays one
+    assert float(soft) == pytest.approx(0.25 * 3.048587 + 0.75 * 0.048587, rel=1e-4)
+    assert float(N.CrossEntropyLoss()(torch.tensor([[-1.0, 2.0]]), torch.tensor([[0.25, 0.75]]))) == pytest.approx(float(soft))
+    assert F.softmax(torch.zeros(2)).tolist() == [0.5, 0.5] and F.max_pool2d(torch.randn(1, 1, 4, 4), 2).shape == (1, 1, 2, 2)
+    assert F.linear(v, torch.ones(3, 2)).shape == (1, 3) and F.one_hot(rustorch.tensor([1.0, 0.0]), 3).shape == (2, 3)
+    assert F.layer_norm(torch.randn(2, 4), 4).shape == (2, 4) and F.silu(torch.zeros(1)).item() == 0.0
