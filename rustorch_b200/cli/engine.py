@@ -123,6 +123,10 @@ class InferenceEngine:
             yield reply
             return
         ids = self.tokenizer.encode(prompt)
+        vocab = getattr(getattr(self.runtime, "cfg", None), "vocab_size", 0) or 0
+        if vocab and ids and max(ids) >= vocab:
+            raise ValueError(f"the tokenizer produced id {max(ids)} but the model's vocabulary has {vocab} entries: "
+                             "pass --tokenizer <file> with the tokenizer that belongs to this model")
         ctx = getattr(getattr(self.runtime, "cfg", None), "context_length", 0) or 0
         budget = self.generation.max_tokens
         if ctx and len(ids) + budget > ctx:

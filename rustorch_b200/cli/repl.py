@@ -20,6 +20,7 @@ class Repl:
         self.out = out or (lambda s: (sys.stdout.write(s), sys.stdout.flush()))
         self.stream, self.show_metrics = stream, show_metrics
         self.running = True
+        self.errors = 0                              # generations that failed in this session
         self.tokenizer_path: Optional[str] = None
 
     # -- one line of input -> True while the loop should go on
@@ -35,7 +36,15 @@ class Repl:
             return self.running
         self.session.add_user_message(line)
         self.out("Assistant: ")
-        reply = self.engine.generate(self.session.build_prompt(), on_token=self.out if self.stream else None)
+        try:
+            reply = self.engine.generate(self.session.build_prompt(), on_token=self.out if self.stream else None)
+        except KeyboardInterrupt:
+            raise
+        except Exception as e:  # noqa: BLE001  (a failed generation must not end the session; the turn is dropped)
+            self.session.drop_last_message()
+            self.errors += 1
+            self.out(f"\nerror: {type(e).__name__}: {e}\n")
+            return True
         if not self.stream:
             self.out(reply)
         self.out("\n")
@@ -160,7 +169,7 @@ def main(argv: Optional[List[str]] = None, read: Callable[[str], str] = input, o
         repl.handle_line(a.prompt)
         if a.save_history:
             session.save_history(a.save_history)
-        return 0
+        return 1 if repl.errors else 0
     repl.run(read)
     if a.save_history:
         session.save_history(a.save_history)

@@ -74,6 +74,10 @@ class SessionHistory:
     def add_system_message(self, c: str) -> None:
         self._add(Message.new_system(c))
 
+    def pop_last(self) -> None:
+        if self._messages:
+            self._messages.pop()
+
     def clear(self) -> None:
         self._messages.clear()
 
@@ -113,6 +117,10 @@ class SessionManager:
 
     def add_assistant_message(self, c: str) -> None:
         self.history.add_assistant_message(c)
+
+    def drop_last_message(self) -> None:
+        """Forget the newest message (a user turn whose reply could not be generated)."""
+        self.history.pop_last()
 
     def clear_history(self) -> None:
         self.history.clear()

@@ -156,3 +156,22 @@ def test_dummy_model_and_list_command(tmp_path):
     buf = []
     assert cli.main(["--model", str(tmp_path / "nope.gguf"), "--prompt", "x"], out=buf.append) == 1 and "cannot load model" in "".join(buf)
     assert cli.main(["download", "ftp:x"], out=buf.append) == 2
+
+
+def test_repl_survives_a_failed_generation(tmp_path):
+    """A model without an embedded tokenizer and a prompt whose byte-level ids exceed its vocabulary: the turn is
+    reported and dropped, the session goes on (the reference's REPL prints the error and continues,
+    example-cli/src/cli/repl.rs)."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from test_llm_cpu import _tiny_gguf as plain_gguf                # no tokenizer metadata, vocabulary of 64
+    model = str(tmp_path / "plain.gguf")
+    plain_gguf(model)
+    lines = iter(["hello there", "/stats", "/exit"])
+    buf = []
+    rc = cli.main(["--model", model, "--backend", "cpu", "--max-tokens", "4"], read=lambda _: next(lines), out=buf.append)
+    text = "".join(buf)
+    assert rc == 0 and "error: ValueError: the tokenizer produced id" in text and "--tokenizer" in text
+    assert "messages: 0" in text and "Goodbye!" in text             # the failed turn left no half conversation behind
+    one = []
+    assert cli.main(["--model", model, "--backend", "cpu", "--prompt", "hello"], out=one.append) == 1 and "error:" in "".join(one)
