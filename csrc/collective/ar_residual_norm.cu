@@ -17,7 +17,7 @@
 // One CTA per row; a thread owns up to AR_VPT 16-byte vectors of the row in registers (row length <= 8*AR_VPT*1024).
 //
 // The reference has no tensor-parallel decode; its all-reduce is a host loop (src/gpu/multi_gpu.rs:583-700) and its
-// RMSNorm a CPU loop (src/hybrid_f32/models/llama.rs rms_norm).
+// RMSNorm a CPU loop (src/nn/normalization.rs:652, rms_normalize).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 

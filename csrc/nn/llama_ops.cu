@@ -8,7 +8,8 @@
 //
 // Angles come from cos / sin tables [T][D/2] (fp32).  A thread handles 8 consecutive elements of the first half of a
 // head and their partners in the second half (two 16-byte loads, two stores).
-// Reference: src/hybrid_f32/models/llama.rs (apply_rope, SwiGLU in the MLP), src/nn/activation.rs:378-419.
+// Reference: SwiGLU is src/nn/activation.rs:378-419; the reference has no rotary embedding (its attention,
+// example-cli/src/model/architectures/attention.rs, applies none), the rotation here is the Llama convention.
 #include <cuda_bf16.h>
 
 #include <algorithm>

@@ -10,7 +10,7 @@
 //   amp_unscale  g *= inv_scale over a flat fp32 / bf16 / fp16 buffer and found_inf = 1 if any value is not finite
 //                (src/amp/grad_scaler.rs unscale + check loops).
 //   csr_spmm     y[rows][n] = A_csr x[cols][n], fp32: one warp per sparse row, lanes across dense columns
-//                (n = 1 is SpMV with lanes across the row's non-zeros).  src/sparse/ops.rs.
+//                (n = 1 is SpMV with lanes across the row's non-zeros).  src/sparse/gpu_ops.rs:26-120.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 

@@ -25,6 +25,8 @@ def _native_ok() -> bool:
 
 
 class AutocastMode(enum.Enum):
+    """Which dtype ``autocast`` computes in (src/amp/autocast.rs)."""
+
     NONE = "none"
     FP16 = "fp16"
     BF16 = "bf16"

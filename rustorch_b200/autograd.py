@@ -241,6 +241,8 @@ class NoGradGuard:
 
 
 class EnableGradGuard(NoGradGuard):
+    """Context manager that turns gradient recording on inside a ``no_grad`` region (src/autograd/context.rs:10-155)."""
+
     def __enter__(self):
         self._prev = torch.is_grad_enabled()
         torch.set_grad_enabled(True)

@@ -7,6 +7,8 @@ from typing import Optional
 
 
 class CommandKind(Enum):
+    """The REPL's slash commands (example-cli/src/cli/commands.rs)."""
+
     EXIT = "exit"
     HELP = "help"
     CLEAR = "clear"

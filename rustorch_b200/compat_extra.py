@@ -157,6 +157,8 @@ class ModelStateDict:
 
 # ------------------------------------------------------------------------------------------------ generic Adam family
 class AdamVariant(enum.Enum):
+    """Which member of the Adam family a generic Adam optimizer runs (src/optim/common.rs)."""
+
     ADAM = "adam"
     ADAMW = "adamw"
     ADAMAX = "adamax"
@@ -363,6 +365,8 @@ def execute_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal:
 
 # ------------------------------------------------------------------------------------------------ model-parallel communication
 class CommunicationOp(enum.Enum):
+    """Kinds of collective operations a communication manager schedules (src/gpu/multi_gpu.rs)."""
+
     SEND = "send"
     RECV = "recv"
     ALL_REDUCE = "all_reduce"

@@ -15,7 +15,7 @@ import torch.nn as nn
 
 
 class SimpleConversionError(ValueError):
-    pass
+    """Raised when a PyTorch layer has no counterpart in the simplified converter (src/convert/pytorch_to_rustorch_simplified.rs)."""
 
 
 @dataclass

@@ -35,6 +35,8 @@ class Dataset:
 
 
 class IterableDataset:
+    """A dataset that is only iterated, not indexed (src/data/dataset.rs)."""
+
     def __iter__(self):
         raise NotImplementedError
 
@@ -87,6 +89,8 @@ class TensorDataset(Dataset):
 
 
 class ConcatDataset(Dataset):
+    """Several datasets end to end (src/data/dataset.rs)."""
+
     def __init__(self, datasets: Sequence[Dataset]):
         self.datasets = list(datasets)
         self.offsets = []
@@ -157,6 +161,8 @@ class _ListSampler(Sampler):
 
 
 class SequentialSampler(_ListSampler):
+    """Indices ``0 .. len - 1`` in order (src/data/sampler.rs:33-60)."""
+
     def __init__(self, data_len: int):
         super().__init__()
         self.data_len = data_len
@@ -190,6 +196,8 @@ class RandomSampler(_ListSampler):
 
 
 class SubsetRandomSampler(_ListSampler):
+    """A random permutation of the given indices (src/data/sampler.rs)."""
+
     def __init__(self, indices: Sequence[int], seed: Optional[int] = None):
         super().__init__()
         self.indices = list(indices)
@@ -205,6 +213,8 @@ class SubsetRandomSampler(_ListSampler):
 
 
 class WeightedRandomSampler(_ListSampler):
+    """``num_samples`` indices drawn in proportion to ``weights``, with or without replacement (src/data/sampler.rs)."""
+
     def __init__(self, weights: Sequence[float], num_samples: int, replacement: bool = True, seed: Optional[int] = None):
         super().__init__()
         self.weights = torch.as_tensor(weights, dtype=torch.double)

@@ -78,6 +78,8 @@ class Logger:
 
 
 class ProfileScope:
+    """Times the enclosed block into a ``DebugProfiler`` (src/debug/profiler.rs)."""
+
     def __init__(self, profiler: "DebugProfiler", name: str):
         self.p, self.name = profiler, name
 

@@ -33,6 +33,8 @@ class DistributedBackend(enum.Enum):
 
 
 class ReduceOp(enum.Enum):
+    """Reduction of a collective; ``AVERAGE`` is a sum followed by a division by the group size (src/distributed/mod.rs)."""
+
     SUM = "sum"
     PRODUCT = "product"
     MIN = "min"

@@ -22,6 +22,8 @@ from . import api
 
 
 class Priority(enum.IntEnum):
+    """Scheduling priority of a gradient synchronisation request (src/distributed/async_gradient.rs)."""
+
     LOW = 0
     NORMAL = 1
     HIGH = 2

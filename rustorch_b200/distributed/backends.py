@@ -34,6 +34,8 @@ class BackendOptimizations:
 
 
 class GlooTransport(Enum):
+    """Transports gloo can run over; TCP is the one available here."""
+
     TCP = "tcp"
     INFINIBAND = "ib"
     SHARED_MEMORY = "shm"
@@ -95,10 +97,14 @@ class DistributedOps:
 
 
 class NCCLBackend(DistributedOps):
+    """Back-end object for NCCL over NVLink / NVSwitch (src/distributed/nccl_integration.rs)."""
+
     name = "nccl"
 
 
 class GlooBackend(DistributedOps):
+    """Back-end object for the gloo transport (CPU tensors) (src/distributed/backends.rs)."""
+
     name = "gloo"
 
     def __init__(self, group=None, optimizations=None, transport: GlooTransport = GlooTransport.TCP):
@@ -107,6 +113,8 @@ class GlooBackend(DistributedOps):
 
 
 class TCPBackend(GlooBackend):
+    """Plain TCP back-end, served by gloo's TCP transport (src/distributed/backends.rs)."""
+
     name = "tcp"
 
 

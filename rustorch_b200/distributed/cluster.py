@@ -18,6 +18,8 @@ from typing import Callable, Dict, List, Optional
 
 
 class NodeStatus(enum.Enum):
+    """Life-cycle state of a cluster node as seen by the heartbeat monitor."""
+
     ACTIVE = "active"
     IDLE = "idle"
     BUSY = "busy"
@@ -26,6 +28,8 @@ class NodeStatus(enum.Enum):
 
 
 class ClusterTopology(enum.Enum):
+    """How the nodes of a cluster are connected (src/distributed/cluster.rs)."""
+
     FLAT = "flat"
     TREE = "tree"
     RING = "ring"
@@ -33,6 +37,8 @@ class ClusterTopology(enum.Enum):
 
 
 class SchedulingPolicy(enum.Enum):
+    """How the cluster manager picks nodes for a job."""
+
     FIRST_FIT = "first_fit"
     BEST_FIT = "best_fit"
     LOAD_BALANCING = "load_balancing"

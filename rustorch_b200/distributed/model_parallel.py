@@ -27,6 +27,8 @@ from . import api
 
 
 class PartitionStrategy(enum.Enum):
+    """How a model is cut for model parallelism: by layer, by tensor, by expert."""
+
     LAYER_WISE = "layer_wise"
     TENSOR_WISE = "tensor_wise"
     COLUMN_WISE = "column_wise"
@@ -133,6 +135,8 @@ class RowParallelLinear(nn.Module):
 
 # ---------------------------------------------------------------- pipeline parallel
 class PipelineSchedule(enum.Enum):
+    """Order of micro-batch forward / backward passes in a pipeline (fill-drain or one-forward-one-backward)."""
+
     GPIPE = "gpipe"
     PIPEDREAM = "pipedream"
     ONE_F_ONE_B = "1f1b"
@@ -140,6 +144,8 @@ class PipelineSchedule(enum.Enum):
 
 
 class CommunicationType(enum.Enum):
+    """Collective that connects two partitions of a model-parallel layer (src/distributed/model_parallel.rs)."""
+
     P2P = "p2p"
     ALL_TO_ALL = "all_to_all"
     ALL_REDUCE = "all_reduce"

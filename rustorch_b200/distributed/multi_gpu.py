@@ -21,6 +21,8 @@ import torch
 
 
 class ParallelismStrategy(enum.Enum):
+    """Data, model, pipeline or hybrid parallelism of a multi-GPU context."""
+
     DATA_PARALLEL = "data_parallel"
     MODEL_PARALLEL = "model_parallel"
     PIPELINE_PARALLEL = "pipeline_parallel"
@@ -29,12 +31,16 @@ class ParallelismStrategy(enum.Enum):
 
 
 class CommBackend(enum.Enum):
+    """Communication library a multi-GPU context uses."""
+
     NCCL = "nccl"
     P2P = "p2p"
     HOST_STAGED = "host_staged"
 
 
 class AllReduceAlgorithm(enum.Enum):
+    """Algorithm choices of the multi-GPU all-reduce (src/gpu/multi_gpu.rs:583-701)."""
+
     RING = "ring"
     TREE = "tree"
     BUTTERFLY = "butterfly"
@@ -96,6 +102,8 @@ class MultiGpuBarrier:
 
 
 class StreamPriority(enum.IntEnum):
+    """Priority class of a CUDA stream."""
+
     LOW = 0
     NORMAL = 1
     HIGH = 2
@@ -274,6 +282,8 @@ class LoadBalancer:
 
 # ------------------------------------------------------- distributed trainer (host)
 class LearningRateSchedule(enum.Enum):
+    """Learning-rate policy of the distributed trainer (src/gpu/distributed_training.rs)."""
+
     CONSTANT = "constant"
     LINEAR_DECAY = "linear_decay"
     EXPONENTIAL_DECAY = "exponential_decay"

@@ -68,7 +68,8 @@ class RusTorchError(Exception):
 
 
 def _variant(name: str, base=RusTorchError):
-    return type(name, (base,), {"kind": name})
+    parent = "" if base is RusTorchError else f"; also caught as ``{base.__name__}``"
+    return type(name, (base,), {"kind": name, "__doc__": f"Error kind ``{name}``{parent} (kinds are named after the variants of the reference's ``RusTorchError``, src/error.rs:11-535)."})
 
 
 TensorOp = _variant("TensorOp")
@@ -93,7 +94,8 @@ DeviceError = _variant("DeviceError")
 DeviceNotAvailable = _variant("DeviceNotAvailable", DeviceError)
 GpuError = _variant("GpuError", DeviceError)
 CudaError = _variant("CudaError", GpuError)
-KernelError = type("KernelError", (GpuError, RuntimeError), {"kind": "KernelError"})   # also a RuntimeError: raised by status checks
+KernelError = type("KernelError", (GpuError, RuntimeError), {
+    "kind": "KernelError", "__doc__": "A native kernel reported a non-zero status word; also a ``RuntimeError`` and a ``GpuError``."})
 KernelTimeout = _variant("KernelTimeout", KernelError)
 OutOfMemory = _variant("OutOfMemory", DeviceError)
 MemoryError_ = _variant("MemoryError")

@@ -20,6 +20,8 @@ from .. import _native
 
 
 class DynamicOp(Enum):
+    """Operation kinds of the dynamic execution graph (src/execution/dynamic.rs)."""
+
     INPUT = "input"
     MATMUL = "matmul"
     ADD = "add"

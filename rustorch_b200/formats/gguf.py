@@ -31,6 +31,8 @@ DEFAULT_ALIGNMENT = 32
 
 
 class GGMLType(enum.IntEnum):
+    """Tensor storage types of GGUF files with their block sizes (F32, F16, Q4_0, Q8_0, ...)."""
+
     F32 = 0
     F16 = 1
     Q4_0 = 2
@@ -58,6 +60,8 @@ _BLOCK = {GGMLType.F32: (1, 4), GGMLType.F16: (1, 2), GGMLType.BF16: (1, 2), GGM
 
 
 class GGUFValueType(enum.IntEnum):
+    """Type tags of GGUF metadata values."""
+
     UINT8 = 0
     INT8 = 1
     UINT16 = 2

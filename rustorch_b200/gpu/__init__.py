@@ -232,6 +232,8 @@ class DataTransfer:
 
 # ------------------------------------------------------------------------------ availability cache
 class DeviceStatus(Enum):
+    """Availability state of a device in the device manager (src/gpu/device.rs)."""
+
     AVAILABLE = "available"
     UNAVAILABLE = "unavailable"
     ERROR = "error"
@@ -295,6 +297,8 @@ class DeviceCache:
 
 # ------------------------------------------------------------------------------ selection / optimisation
 class OperationType(Enum):
+    """Operation classes the device selectors and the performance optimizer distinguish (src/gpu/smart_device_selector.rs)."""
+
     MATMUL = "matmul"
     CONV = "conv"
     ELEMENTWISE = "elementwise"
@@ -481,6 +485,8 @@ class GpuValidator:
 
 # ------------------------------------------------------------------------------ kernel executor façade
 class KernelOp(Enum):
+    """Operation a kernel executor is asked to run (src/gpu/kernels.rs)."""
+
     ADD = "add"
     SUB = "sub"
     MUL = "mul"

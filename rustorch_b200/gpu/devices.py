@@ -349,6 +349,8 @@ MacHybrid = _unavailable("MacHybrid", "The Metal / CoreML hybrid executor")
 
 # ------------------------------------------------------------------------------------------------ compute back-ends
 class SelectionStrategy(Enum):
+    """How the back-end manager picks a compute back-end (src/backends/mod.rs)."""
+
     PERFORMANCE = "performance"
     MEMORY = "memory"
     FIRST_AVAILABLE = "first_available"

@@ -21,6 +21,8 @@ from .nn import rnn as R
 
 
 class F32Device:
+    """Device names of the fp32 universe; only ``cpu`` / ``cuda`` / ``auto`` route anywhere here (src/hybrid_f32/mod.rs)."""
+
     CPU, GPU, AUTO = "cpu", "cuda", "auto"
 
 

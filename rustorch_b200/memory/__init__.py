@@ -20,7 +20,7 @@ from .. import _native
 
 
 class PoolExhausted(MemoryError):
-    pass
+    """Raised when a bounded memory pool cannot serve an allocation."""
 
 
 class MemoryPool:

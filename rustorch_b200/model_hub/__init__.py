@@ -87,7 +87,7 @@ class DownloadProgress:
 
 
 class DownloadError(RuntimeError):
-    pass
+    """A download failed after all retries, or its checksum did not match (src/model_hub/downloader.rs)."""
 
 
 class ModelDownloader:

@@ -63,6 +63,8 @@ class ModelFormat(Enum):
 
 
 class FormatFeature(Enum):
+    """Capabilities a model file format may have (metadata, quantisation, streaming ...)."""
+
     WEIGHTS = "weights"
     GRAPH = "graph"
     OPTIMIZER_STATE = "optimizer_state"
@@ -73,12 +75,16 @@ class FormatFeature(Enum):
 
 
 class CompressionType(Enum):
+    """Compression of an exported model file (src/model_import/formats.rs)."""
+
     NONE = "none"
     GZIP = "gzip"
     ZSTD = "zstd"
 
 
 class DeploymentTarget(Enum):
+    """Where an exported model is meant to run."""
+
     SERVER = "server"
     MOBILE = "mobile"
     EDGE = "edge"

@@ -54,6 +54,8 @@ class GPTConfig:
 
 
 class GPTBlock(nn.Module):
+    """Parameters of one transformer block of the fused GPT model (the block's arithmetic lives in ``nn.fused``)."""
+
     def __init__(self, cfg: GPTConfig, device=None, dtype=None):
         super().__init__()
         C = cfg.n_embd

@@ -22,6 +22,8 @@ from ..data import DataLoader, RandomSampler, SequentialSampler, TensorDataset
 
 
 class ModelMode(enum.Enum):
+    """Training or evaluation mode of a model (src/models/mod.rs:48-60)."""
+
     TRAIN = "train"
     EVAL = "eval"
 
@@ -542,6 +544,8 @@ class InferenceEngine:
 
 # ------------------------------------------------------------------ save / load
 class SerializationFormat(enum.Enum):
+    """File formats ``ModelSaver`` / ``ModelLoader`` handle (src/models/serialization.rs:18-60)."""
+
     RUSTORCH = "rustorch"
     SAFETENSORS = "safetensors"
     PYTORCH = "pytorch"

@@ -33,6 +33,8 @@ class RNNModel(nn.Module):
 
 
 class LSTMModel(RNNModel):
+    """Embedding + LSTM stack + classifier head (src/models/rnn.rs)."""
+
     def __init__(self, vocab_size, embedding_dim, hidden_size, num_classes, num_layers=1, bidirectional=False, dropout=0.0):
         super().__init__(vocab_size, embedding_dim, hidden_size, num_classes, num_layers, bidirectional, dropout, "lstm")
 
@@ -87,14 +89,20 @@ class _Builder:
 
 
 class RNNModelBuilder(_Builder):
+    """Fluent builder of :class:`RNNModel`."""
+
     _cls = RNNModel
 
 
 class LSTMModelBuilder(_Builder):
+    """Fluent builder of :class:`LSTMModel`."""
+
     _cls = LSTMModel
 
 
 class Seq2SeqModelBuilder(_Builder):
+    """Fluent builder of :class:`Seq2SeqModel`."""
+
     _cls = Seq2SeqModel
 
 
@@ -198,4 +206,6 @@ class TransformerModel(nn.Module):
 
 
 class TransformerModelBuilder(_Builder):
+    """Fluent builder of :class:`TransformerModel`."""
+
     _cls = TransformerModel

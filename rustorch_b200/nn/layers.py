@@ -173,6 +173,8 @@ class _ConvTransposeNd(nn.Module):
 
 
 class ConvTranspose1d(_ConvTransposeNd):
+    """Transposed 1-D convolution: GEMM + patch scatter (src/nn/conv_transpose.rs)."""
+
     _fn, _nd = staticmethod(F.conv_transpose1d), 1
 
 
@@ -195,6 +197,8 @@ class ConvTranspose2d(_ConvTransposeNd):
 
 
 class ConvTranspose3d(_ConvTransposeNd):
+    """Transposed 3-D convolution: GEMM + patch scatter (src/nn/conv_transpose_3d.rs)."""
+
     _fn, _nd = staticmethod(F.conv_transpose3d), 3
 
 
@@ -234,12 +238,16 @@ class _BatchNorm(nn.modules.batchnorm._BatchNorm):
 
 
 class BatchNorm1d(_BatchNorm):
+    """Batch normalisation over ``[N, C]`` or ``[N, C, L]`` (src/nn/batchnorm.rs:77-92)."""
+
     def _check_input_dim(self, x):
         if x.dim() not in (2, 3):
             raise ValueError(f"expected 2D or 3D input (got {x.dim()}D)")
 
 
 class BatchNorm2d(_BatchNorm):
+    """Batch normalisation over ``[N, C, H, W]``; channels-last CUDA kernels for statistics, apply and backward (src/nn/batchnorm.rs)."""
+
     def _check_input_dim(self, x):
         if x.dim() != 4:
             raise ValueError(f"expected 4D input (got {x.dim()}D)")
@@ -313,10 +321,14 @@ class InstanceNorm1d(_InstanceNormNative, nn.InstanceNorm1d):
 
 
 class InstanceNorm2d(_InstanceNormNative, nn.InstanceNorm2d):
+    """Instance normalisation over ``[N, C, H, W]`` (src/nn/instance_norm.rs:148-156)."""
+
     _rank = 4
 
 
 class InstanceNorm3d(_InstanceNormNative, nn.InstanceNorm3d):
+    """Instance normalisation over ``[N, C, D, H, W]`` (src/nn/instance_norm.rs)."""
+
     _rank = 5
 
 
@@ -341,7 +353,7 @@ class Dropout(nn.Module):
 
 
 class AlphaDropout(nn.AlphaDropout):
-    pass
+    """Dropout that keeps the self-normalising property of SELU networks (src/nn/dropout.rs:290-420)."""
 
 
 Identity = nn.Identity
@@ -603,7 +615,7 @@ class Swish(nn.SiLU):
 
 
 class GLU(nn.GLU):
-    pass
+    """Gated linear unit: first half of ``dim`` times the sigmoid of the second half (src/nn/activation.rs)."""
 
 
 class ELU(nn.ELU):

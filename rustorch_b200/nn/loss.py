@@ -15,6 +15,8 @@ import torch.nn.functional as F
 
 
 class Reduction(enum.Enum):
+    """``mean`` / ``sum`` / ``none`` reduction of a loss (src/nn/loss.rs:26-69)."""
+
     NONE = "none"
     MEAN = "mean"
     SUM = "sum"

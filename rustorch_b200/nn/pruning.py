@@ -18,6 +18,8 @@ import torch.nn as nn
 
 
 class PruningMethod(enum.Enum):
+    """Importance criterion of the pruner (src/nn/pruning.rs:30-47); ``MAGNITUDE`` is ``L1_NORM``."""
+
     L1_NORM = "l1"               # |w|
     L2_NORM = "l2"               # w^2
     RANDOM = "random"

@@ -1,4 +1,4 @@
-"""Shared pieces of the recurrent layers (src/nn/recurrent_common.rs:13-460): the per-cell configuration, weight
+"""Shared pieces of the recurrent layers (src/nn/recurrent_common.rs:13-450): the per-cell configuration, weight
 initialisation, gate slicing and the time-step / stacking helpers of the multi-layer loops.  The whole-sequence
 layers in ``rnn.py`` do their input projections as one GEMM over all steps and only keep the recurrent product and
 the fused gate kernel inside the time loop; these helpers are the reference-shaped view of the same arithmetic."""

@@ -33,6 +33,8 @@ def _linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor]) -> torc
 
 
 class RNNCell(nn.RNNCell):
+    """Elman cell ``h' = act(W_ih x + b_ih + W_hh h + b_hh)`` (src/nn/rnn.rs)."""
+
     def __init__(self, input_size: int, hidden_size: int, bias: bool = True, nonlinearity: str = "tanh", **kw):
         super().__init__(input_size, hidden_size, bias, nonlinearity, **kw)
 

@@ -109,6 +109,8 @@ class WarmupScheduler(LRScheduler):
 
 
 class AnnealStrategy(enum.Enum):
+    """Cosine or linear annealing of ``OneCycleLR`` (src/optim/lr_scheduler.rs:428-436)."""
+
     COS = "cos"
     LINEAR = "linear"
 
@@ -154,11 +156,15 @@ class PolynomialLR(LRScheduler):
 
 
 class PlateauMode(enum.Enum):
+    """Whether ``ReduceLROnPlateau`` watches a metric that should fall or rise."""
+
     MIN = "min"
     MAX = "max"
 
 
 class ThresholdMode(enum.Enum):
+    """Relative or absolute improvement threshold of ``ReduceLROnPlateau``."""
+
     REL = "rel"
     ABS = "abs"
 

@@ -19,6 +19,8 @@ import torch.nn.functional as F
 
 
 class ParallelStrategy(Enum):
+    """How a batch operation is split across workers (src/tensor/parallel_traits.rs)."""
+
     AUTO = "auto"
     SEQUENTIAL = "sequential"
     FORCE_PARALLEL = "force_parallel"

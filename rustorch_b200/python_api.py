@@ -230,6 +230,8 @@ class ModelComparator:
 
 
 class Transform:
+    """A named image transform of the Python binding (src/python/data.rs)."""
+
     def __init__(self, fn: Callable[[torch.Tensor], torch.Tensor], name: str = "transform"):
         self.fn, self.name = fn, name
 

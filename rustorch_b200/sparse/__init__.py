@@ -19,6 +19,8 @@ import torch.nn.functional as F
 
 
 class SparseFormat(Enum):
+    """COO or CSR storage of a sparse tensor (src/sparse/mod.rs)."""
+
     COO = "coo"
     CSR = "csr"
 
@@ -161,6 +163,8 @@ SparseOps = SparseTensor
 
 # ------------------------------------------------------------------------------ pruning
 class PruningStrategy(Enum):
+    """Criterion of the sparse module's pruners (src/sparse/pruning.rs)."""
+
     MAGNITUDE = "magnitude"
     RANDOM = "random"
     STRUCTURED = "structured"
@@ -169,6 +173,8 @@ class PruningStrategy(Enum):
 
 
 class StructuredGranularity(Enum):
+    """Rows, columns or blocks as the unit of structured pruning."""
+
     ROW = "row"           # output neurons
     COLUMN = "column"     # input features
     CHANNEL = "channel"   # conv filters

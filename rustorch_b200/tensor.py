@@ -1108,7 +1108,7 @@ def multithreaded_matmul(a, b, num_threads: Optional[int] = None) -> Tensor:
 
 
 def memory_optimized(shape, dtype=torch.float32, device="cpu", pinned: bool = False) -> Tensor:
-    """A tensor from the pooled / pinned allocators (src/tensor/memory/memory_optimized.rs:155-402)."""
+    """A tensor from the pooled / pinned allocators (src/tensor/memory_optimized.rs:155-402)."""
     from .compat import AllocationStrategy
     strat = AllocationStrategy.PINNED if pinned else AllocationStrategy.POOLED
     return Tensor(strat.allocate(tuple(shape), dtype, device).zero_())

@@ -56,6 +56,8 @@ class TrainingState:
 
 
 class CallbackSignal(enum.Enum):
+    """What a callback asks the trainer to do after an epoch: go on or stop (src/training/callbacks.rs:12-30)."""
+
     CONTINUE = "continue"
     STOP = "stop"
 

@@ -28,6 +28,8 @@ class ValidationResult:
 
 
 class ValidationRule:
+    """A named check ``tensor -> error message or None`` with a severity (src/validation/core.rs)."""
+
     def __init__(self, name: str, check: Callable[[torch.Tensor], Optional[str]], severity: str = "error"):
         self.name, self.check, self.severity = name, check, severity
 

@@ -23,6 +23,8 @@ import torch.nn.functional as F
 
 
 class ImageFormat(Enum):
+    """Channel layout of an image tensor: CHW or HWC (src/vision/mod.rs)."""
+
     CHW = "chw"
     HWC = "hwc"
 
@@ -69,6 +71,8 @@ class Transform:
 
 
 class InterpolationMode(Enum):
+    """Resampling filter of ``Resize``."""
+
     NEAREST = "nearest"
     BILINEAR = "bilinear"
     BICUBIC = "bicubic"
@@ -220,6 +224,8 @@ class ColorJitter(Transform):
 
 
 class Compose(Transform):
+    """Applies transforms one after another (src/vision/transforms.rs)."""
+
     def __init__(self, transforms: Sequence[Callable]):
         self.transforms = list(transforms)
 
@@ -231,6 +237,8 @@ class Compose(Transform):
 
 # ------------------------------------------------------------------------------ pipeline
 class ExecutionMode(Enum):
+    """Sequential, batched or parallel execution of a pipeline (src/vision/pipeline.rs)."""
+
     SEQUENTIAL = "sequential"
     BATCH = "batch"
 
@@ -248,6 +256,8 @@ class PipelineStats:
 
 
 class ConditionalTransform(Transform):
+    """Applies a transform only where a predicate on the image holds (src/vision/pipeline.rs)."""
+
     def __init__(self, transform: Callable, predicate: Callable[[torch.Tensor], bool]):
         self.transform, self.predicate = transform, predicate
 
@@ -421,6 +431,8 @@ class _ArrayDataset:
 
 
 class MNIST(_ArrayDataset):
+    """MNIST from the IDX files, gzip or plain (src/vision/datasets.rs)."""
+
     classes = [str(i) for i in range(10)]
 
     def __init__(self, root: str, train: bool = True, transform: Optional[Callable] = None):
@@ -437,6 +449,8 @@ class MNIST(_ArrayDataset):
 
 
 class CIFAR10(_ArrayDataset):
+    """CIFAR-10 from the binary batch files (src/vision/datasets.rs)."""
+
     classes = ["airplane", "automobile", "bird", "cat", "deer", "dog", "frog", "horse", "ship", "truck"]
     _label_bytes, _label_index = 1, 0
 

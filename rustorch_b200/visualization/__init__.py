@@ -30,12 +30,16 @@ class PlotFormat(Enum):
 
 
 class PlotStyle(Enum):
+    """Line, scatter or bar rendering of a series."""
+
     LINE = "line"
     SCATTER = "scatter"
     BAR = "bar"
 
 
 class ChartType(Enum):
+    """Chart kinds the plotters draw (src/visualization/plotting.rs)."""
+
     LOSS = "loss"
     ACCURACY = "accuracy"
     LEARNING_RATE = "learning_rate"

@@ -279,7 +279,7 @@ def test_quantizer_calibration_cache_and_qat():
 
 
 def test_conv_validator_recurrent_helpers_and_stats():
-    """src/nn/conv_base.rs:103-310, src/nn/recurrent_common.rs:13-460, src/nn/safe_ops.rs:236-270."""
+    """src/nn/conv_base.rs:103-310, src/nn/recurrent_common.rs:13-450, src/nn/safe_ops.rs:236-270."""
     for bad in (dict(in_channels=0, out_channels=4, kernel_size=3), dict(in_channels=6, out_channels=4, kernel_size=3, groups=4),
                 dict(in_channels=4, out_channels=4, kernel_size=0), dict(in_channels=4, out_channels=4, kernel_size=3, stride=0),
                 dict(in_channels=4, out_channels=4, kernel_size=3, dilation=0), dict(in_channels=4, out_channels=4, kernel_size=3, groups=0)):
