@@ -138,6 +138,16 @@ def _metric(name: str) -> Callable:
     raise ValueError(f"unknown metric '{name}'")
 
 
+def _is_loader(x) -> bool:
+    """This package's ``DataLoader`` (stepping API) or a ``torch.utils.data.DataLoader``."""
+    return hasattr(x, "next_batch") or isinstance(x, torch.utils.data.DataLoader)
+
+
+def _rewind(loader) -> None:
+    if hasattr(loader, "reset"):
+        loader.reset()
+
+
 def _raw(t):
     """The ``torch.Tensor`` inside a ``Tensor`` / ``Variable`` wrapper (or the argument itself)."""
     if t is None or isinstance(t, torch.Tensor):
@@ -322,8 +332,8 @@ class Sequential(Model):
         (src/python/training.rs:239-275; the reference returns made-up losses there, this trains)."""
         if not getattr(self, "compiled", False):
             raise RuntimeError("Model must be compiled before training")
-        if hasattr(x, "next_batch"):
-            val = validation_data if validation_data is not None else (y if hasattr(y, "next_batch") else None)
+        if _is_loader(x):
+            val = validation_data if validation_data is not None else (y if _is_loader(y) else None)
             return self._fit_loaders(x, val, 10 if epochs is None else epochs, True if verbose is None else verbose)
         x, y = _raw(x), _raw(y)
         self._ready(x[:2])
@@ -368,7 +378,7 @@ class Sequential(Model):
             t0 = time.time()
             self.train()
             tot, n = 0.0, 0
-            train.reset()
+            _rewind(train)
             for batch in train:
                 xb, yb = _raw(batch[0]), _raw(batch[1])
                 self._ready(xb)
@@ -395,8 +405,8 @@ class Sequential(Model):
         self.eval()
         tot: Dict[str, float] = {"loss": 0.0, **{m: 0.0 for m in self._metrics}}
         n = 0
-        if hasattr(x, "next_batch"):
-            x.reset()
+        if _is_loader(x):
+            _rewind(x)
             batches = ((_raw(b[0]), _raw(b[1])) for b in x)
         else:
             batches = self._loader(_raw(x), _raw(y), batch_size, False)

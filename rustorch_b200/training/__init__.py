@@ -494,7 +494,8 @@ class Trainer:
     def _binding_form(self, model, third) -> bool:
         """``train(model, train_loader, val_loader=None)`` / ``evaluate(model, loader)`` of the Python binding
         (src/python/training.rs:131-200): the model was ``compile``d and carries its own loss and optimizer."""
-        return hasattr(model, "_fit_loaders") and (third is None or hasattr(third, "next_batch"))
+        return hasattr(model, "_fit_loaders") and (third is None or hasattr(third, "next_batch")
+                                                   or isinstance(third, torch.utils.data.DataLoader))
 
     def train(self, model, train_loader, loss_fn=None, optimizer=None, val_loader=None):
         """``train(model, train_loader, loss_fn, optimizer, val_loader=None)`` -> metrics dictionary

@@ -267,6 +267,10 @@ def test_binding_model_builder_trainer_history():
     assert isinstance(h3, rt.TrainingHistory) and len(h3.train_loss) == 4 and len(h3.val_loss) == 4
     m = tr_.evaluate(model, val)
     assert set(m) == {"loss", "accuracy"} and m["accuracy"] > 0.85 and "epochs=4" in repr(tr_)
+    # stock torch loaders are accepted wherever this package's loaders are
+    tl = torch.utils.data.DataLoader(torch.utils.data.TensorDataset(X[:64], y[:64]), batch_size=16)
+    assert len(model.fit(tl, tl, epochs=2, verbose=False).val_loss) == 2 and "accuracy" in model.evaluate(tl)
+    assert len(rt.Trainer(rt.TrainerConfig(epochs=1)).train(model, tl, tl).train_loss) == 1
     hh = rt.TrainingHistory()
     hh.add_epoch(0.5, 0.6, {"accuracy": 0.8})
     hh.add_epoch(0.4, 0.7)
