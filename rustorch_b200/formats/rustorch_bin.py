@@ -260,7 +260,9 @@ def load_module(module: torch.nn.Module, path: str, strict: bool = True) -> dict
     p, b, meta = load_state_dict(path)
     sd = {**p, **b}
     own = module.state_dict()
-    cast = {k: v.to(own[k].dtype).reshape(own[k].shape) for k, v in sd.items() if k in own}
+    # tensors the module has yet to create (layers built from their first input) pass through as stored; with
+    # ``strict`` a name the module does not know is an error, not something to drop silently
+    cast = {k: (v.to(own[k].dtype).reshape(own[k].shape) if k in own else v) for k, v in sd.items() if k in own or strict}
     module.load_state_dict(cast, strict=strict)
     return meta
 

@@ -187,6 +187,16 @@ class _Deferred(nn.Module):
     def _prepare(self, x: torch.Tensor) -> torch.Tensor:
         return x
 
+    def _build_from_weight(self, weight: torch.Tensor) -> nn.Module:
+        raise NotImplementedError
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        """A checkpoint can be loaded into a layer that has not seen data yet: the stored weight tells the input width."""
+        w = state_dict.get(prefix + "inner.weight")
+        if self.inner is None and w is not None:
+            self.inner = self._build_from_weight(w).to(w.dtype)
+        return super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+
     def forward(self, x):
         x = self._prepare(x)
         if self.inner is None:
@@ -214,6 +224,12 @@ class Dense(_Deferred):
         from ..nn import Linear
         return Linear(x.shape[-1], self.units)
 
+    def _build_from_weight(self, weight):
+        from ..nn import Linear
+        if weight.shape[0] != self.units:
+            raise ValueError(f"checkpoint has {weight.shape[0]} units, the layer {self.units}")
+        return Linear(weight.shape[1], self.units)
+
     def extra_repr(self) -> str:
         return f"{self.units}, activation={self.activation}"
 
@@ -232,6 +248,12 @@ class Conv2D(_Deferred):
         if x.dim() != 4:
             raise ValueError(f"Conv2D needs [N, C, H, W] inputs, got {tuple(x.shape)}")
         return Conv2d(x.shape[1], self.filters, (self.kernel_size, self.kernel_size))
+
+    def _build_from_weight(self, weight):
+        from ..nn import Conv2d
+        if weight.shape[0] != self.filters or tuple(weight.shape[2:]) != (self.kernel_size, self.kernel_size):
+            raise ValueError(f"checkpoint holds a {tuple(weight.shape)} filter bank, the layer wants {self.filters} filters of size {self.kernel_size}")
+        return Conv2d(weight.shape[1], self.filters, (self.kernel_size, self.kernel_size))
 
     def extra_repr(self) -> str:
         return f"{self.filters}, {self.kernel_size}, activation={self.activation}"
@@ -628,7 +650,9 @@ class ModelLoader:
         else:
             raise ValueError(f"unrecognised model file '{path}'")
         own = model.state_dict()
-        model.load_state_dict({k: v.to(own[k].dtype) for k, v in sd.items() if k in own}, strict=strict)
+        # names the model does not have (yet) go through untouched: layers built from their first input create
+        # them while loading, and with ``strict`` a genuinely unknown name must fail rather than vanish
+        model.load_state_dict({k: (v.to(own[k].dtype) if k in own else v) for k, v in sd.items() if k in own or strict}, strict=strict)
         return model
 
     @staticmethod

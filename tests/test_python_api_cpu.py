@@ -482,3 +482,38 @@ def test_alias_package_shares_modules_and_functional_namespace():
     assert F.softmax(torch.zeros(2)).tolist() == [0.5, 0.5] and F.max_pool2d(torch.randn(1, 1, 4, 4), 2).shape == (1, 1, 2, 2)
     assert F.linear(v, torch.ones(3, 2)).shape == (1, 3) and F.one_hot(rustorch.tensor([1.0, 0.0]), 3).shape == (2, 3)
     assert F.layer_norm(torch.randn(2, 4), 4).shape == (2, 4) and F.silu(torch.zeros(1)).item() == 0.0
+
+
+def test_described_layers_load_checkpoints_before_seeing_data(tmp_path):
+    """A freshly built Keras-like model (layers not materialised yet) loads a saved one in every file format, and a
+    strict load does not drop names it does not know."""
+    import rustorch as rt
+    b = rt.ModelBuilder()
+    b.conv2d(4, 3, "relu")
+    b.dense(8, "relu")
+    b.dense(2)
+    src = b.build("src")
+    x = torch.randn(2, 3, 6, 6)
+    want = src(x)
+    for fmt, name in (("safetensors", "m.safetensors"), ("rustorch", "m.rustorch"), ("pytorch", "m.pt")):
+        path = str(tmp_path / name)
+        rt.ModelSerializer.export(src, path, fmt)
+        fresh = b.build("fresh")
+        assert fresh.layers[0].inner is None
+        rt.ModelSerializer.load(fresh, path)
+        assert torch.equal(fresh(x), want), fmt
+    third = b.build("third")
+    third.load_state_dict(src.state_dict())
+    assert torch.equal(third(x), want)
+    other = rt.ModelBuilder()
+    other.dense(9)
+    with pytest.raises(ValueError, match="8 units"):
+        other.build().load_state_dict({"layers.0.inner.weight": torch.zeros(8, 4), "layers.0.inner.bias": torch.zeros(8)})
+    plain = torch.nn.Linear(4, 2)
+    extra = str(tmp_path / "extra.safetensors")
+    from rustorch_b200.formats import save_safetensors
+    save_safetensors({"weight": torch.zeros(2, 4), "bias": torch.zeros(2), "ghost": torch.zeros(1)}, extra)
+    with pytest.raises(RuntimeError, match="ghost"):
+        rt.ModelSerializer.load(plain, extra)                        # strict: the unknown name is reported
+    rt.ModelSerializer.load(plain, extra, strict=False)
+    assert float(plain.weight.abs().sum()) == 0.0
