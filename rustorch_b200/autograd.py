@@ -87,6 +87,16 @@ class Variable:
     def dot(self, other) -> "Variable":
         return self._w((self.tensor.flatten() * _v(other).flatten()).sum())
 
+    def __array__(self, dtype=None, copy=None):
+        a = self.tensor.detach().cpu().numpy()
+        return a.astype(dtype) if dtype is not None else a
+
+    def __len__(self) -> int:
+        return len(self.tensor)
+
+    def __getitem__(self, idx) -> "Variable":
+        return self._w(self.tensor[_v(idx)])
+
     def __copy__(self) -> "Variable":
         return type(self)(self.tensor, self.tensor.requires_grad)            # same storage
 

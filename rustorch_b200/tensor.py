@@ -444,6 +444,20 @@ class Tensor:
     def __eq__(self, other):  # elementwise, like torch
         return Tensor(self.data == _unwrap(other))
 
+    def __ne__(self, other):
+        return Tensor(self.data != _unwrap(other))
+
+    def __iter__(self):
+        """Slices along the first dimension, as ``torch.Tensor`` iterates."""
+        if self.data.dim() == 0:
+            raise TypeError("iteration over a 0-d tensor")
+        return (Tensor(t) for t in self.data)
+
+    def __array__(self, dtype=None, copy=None):
+        """NumPy conversion (``np.asarray(t)``); CUDA data is copied to the host."""
+        a = self.data.detach().cpu().numpy()
+        return a.astype(dtype) if dtype is not None else a
+
     def __lt__(self, o):
         return Tensor(self.data < _unwrap(o))
 

@@ -196,3 +196,20 @@ def test_tensor_shape_device_and_predicate_helpers():
     k = r.clone_tensor()
     k.map_inplace(lambda x: x + 1)
     assert k.as_slice() == [2.0, 3.0, 4.0, 5.0] and r.as_slice() == [1.0, 2.0, 3.0, 4.0]
+
+
+def test_wrapper_protocols_numpy_iteration_comparison():
+    import numpy as np
+    import rustorch as rt
+    a = rt.tensor([[1.0, 2.0], [3.0, 4.0]])
+    assert np.asarray(a).dtype == np.float32 and np.asarray(a).shape == (2, 2) and np.asarray(a, dtype=np.float64).dtype == np.float64
+    assert np.asarray(rt.Variable(a)).tolist() == [[1.0, 2.0], [3.0, 4.0]]
+    assert (a != rt.tensor([[1.0, 0.0], [3.0, 0.0]])).data.tolist() == [[False, True], [False, True]]
+    assert [r.as_slice() for r in a] == [[1.0, 2.0], [3.0, 4.0]] and len({a: 1}) == 1
+    with pytest.raises(TypeError):
+        iter(rt.tensor(3.0).reshape([]))
+    v = rt.Variable(a, requires_grad=True)
+    assert len(v) == 2 and isinstance(v[0], rt.Variable)
+    v[1].sum().backward()
+    assert v.grad.as_slice() == [0.0, 0.0, 1.0, 1.0]
+    assert isinstance(torch.ones(2, 2) + a, rt.Tensor) and isinstance(torch.ones(2, 2) * v, rt.Variable)
