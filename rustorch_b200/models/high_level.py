@@ -656,11 +656,15 @@ class ModelLoader:
         return model
 
     @staticmethod
-    def load_checkpoint(model: nn.Module, optimizer, path: str) -> dict:
+    def load_checkpoint(model: nn.Module, optimizer, path: str, strict: bool = True) -> dict:
+        """Restores ``model`` (and ``optimizer``) from a checkpoint file; returns the checkpoint (epoch, step, metrics).
+        With ``strict`` a checkpoint that does not cover the model's tensors exactly is an error: resuming from the
+        wrong file must not pass for a resume."""
         from ..formats import rustorch_bin
         ck = rustorch_bin.load_checkpoint(path)
         own = model.state_dict()
-        model.load_state_dict({k: v.to(own[k].dtype) for k, v in {**ck["parameters"], **ck["buffers"]}.items() if k in own}, strict=False)
+        tensors = {**ck["parameters"], **ck["buffers"]}
+        model.load_state_dict({k: (v.to(own[k].dtype) if k in own else v) for k, v in tensors.items() if k in own or strict}, strict=strict)
         blob = ck["optimizer_state"].get("torch_state_dict")
         if optimizer is not None and blob:
             import io

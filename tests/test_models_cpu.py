@@ -117,3 +117,18 @@ def test_llama_training_model_cpu():
     ks = apply_rope(k.expand(1, 8, 1, 16), cos, sin)[0, :, 0]
     assert torch.allclose(qs[5] @ ks[3], qs[4] @ ks[2], atol=1e-4)
     assert LlamaTrainConfig.llama3_8b().n_head_kv == 8 and m.num_parameters() > 0
+
+
+def test_load_checkpoint_rejects_a_checkpoint_of_another_model(tmp_path):
+    a, b = torch.nn.Linear(4, 2), torch.nn.Sequential(torch.nn.Linear(4, 2))
+    oa = torch.optim.SGD(a.parameters(), 0.1)
+    p = str(tmp_path / "a.ckpt")
+    M.ModelSaver.save_checkpoint(a, oa, p, epoch=1, step=2, metrics={"loss": 1.0})
+    with pytest.raises(RuntimeError):
+        M.ModelLoader.load_checkpoint(b, None, p)                    # names differ: nothing would have been restored
+    before = b[0].weight.detach().clone()
+    M.ModelLoader.load_checkpoint(b, None, p, strict=False)
+    assert torch.equal(b[0].weight, before)
+    a2 = torch.nn.Linear(4, 2)
+    ck = M.ModelLoader.load_checkpoint(a2, None, p)
+    assert torch.equal(a2.weight, a.weight) and ck["epoch"] == 1
