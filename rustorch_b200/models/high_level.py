@@ -47,6 +47,38 @@ class Model(nn.Module):
         return "\n".join(rows)
 
 
+@dataclass
+class Metrics:
+    """Classification summary ``accuracy / precision / recall / f1_score / loss`` (src/models/mod.rs:118-152).
+    ``from_predictions`` fills it from logits (or class ids) and targets with macro-averaged precision / recall."""
+    accuracy: float = 0.0
+    precision: float = 0.0
+    recall: float = 0.0
+    f1_score: float = 0.0
+    loss: float = 0.0
+
+    @classmethod
+    def new(cls) -> "Metrics":
+        return cls()
+
+    @classmethod
+    def with_values(cls, accuracy: float, precision: float, recall: float, f1_score: float, loss: float) -> "Metrics":
+        return cls(float(accuracy), float(precision), float(recall), float(f1_score), float(loss))
+
+    @classmethod
+    def from_predictions(cls, outputs: torch.Tensor, targets: torch.Tensor, loss: float = 0.0, num_classes: Optional[int] = None) -> "Metrics":
+        pred = outputs.argmax(-1) if outputs.is_floating_point() and outputs.dim() > targets.dim() else outputs
+        pred, tgt = pred.flatten().long(), targets.flatten().long()
+        k = int(num_classes or max(int(pred.max()), int(tgt.max())) + 1)
+        cm = torch.bincount(tgt * k + pred, minlength=k * k).view(k, k).double()      # rows: truth, columns: prediction
+        tp = cm.diag()
+        seen = (cm.sum(1) + cm.sum(0)) > 0
+        prec = torch.where(cm.sum(0) > 0, tp / cm.sum(0).clamp_min(1), torch.zeros_like(tp))[seen].mean()
+        rec = torch.where(cm.sum(1) > 0, tp / cm.sum(1).clamp_min(1), torch.zeros_like(tp))[seen].mean()
+        f1 = 0.0 if float(prec + rec) == 0 else float(2 * prec * rec / (prec + rec))
+        return cls(float(tp.sum() / cm.sum().clamp_min(1)), float(prec), float(rec), f1, float(loss))
+
+
 def count_parameters(module: nn.Module, trainable_only: bool = False) -> int:
     return sum(p.numel() for p in module.parameters() if p.requires_grad or not trainable_only)
 

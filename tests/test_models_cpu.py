@@ -132,3 +132,12 @@ def test_load_checkpoint_rejects_a_checkpoint_of_another_model(tmp_path):
     a2 = torch.nn.Linear(4, 2)
     ck = M.ModelLoader.load_checkpoint(a2, None, p)
     assert torch.equal(a2.weight, a.weight) and ck["epoch"] == 1
+
+
+def test_metrics_summary():
+    """src/models/mod.rs:118-152 plus a real computation from predictions (macro averages)."""
+    m = M.Metrics.from_predictions(torch.tensor([[2., 1.], [0., 3.], [1., 0.], [0., 1.]]), torch.tensor([0, 1, 1, 1]), 0.3)
+    assert m.accuracy == 0.75 and m.precision == 0.75 and m.recall == pytest.approx(5 / 6) and m.f1_score == pytest.approx(2 * 0.75 * (5 / 6) / (0.75 + 5 / 6))
+    assert m.loss == 0.3 and M.Metrics.new().accuracy == 0.0 and M.Metrics.with_values(1, 0.9, 0.8, 0.85, 0.1).recall == 0.8
+    ids = M.Metrics.from_predictions(torch.tensor([0, 2, 2]), torch.tensor([0, 1, 2]), num_classes=3)
+    assert ids.accuracy == pytest.approx(2 / 3) and ids.precision == pytest.approx((1 + 0 + 0.5) / 3) and ids.recall == pytest.approx((1 + 0 + 1) / 3)
