@@ -56,7 +56,10 @@ class GGMLType(enum.IntEnum):
 # (block elements, block bytes)
 _BLOCK = {GGMLType.F32: (1, 4), GGMLType.F16: (1, 2), GGMLType.BF16: (1, 2), GGMLType.Q4_0: (32, 18),
           GGMLType.Q4_1: (32, 20), GGMLType.Q5_0: (32, 22), GGMLType.Q5_1: (32, 24), GGMLType.Q8_0: (32, 34),
-          GGMLType.Q8_1: (32, 36), GGMLType.I8: (1, 1), GGMLType.I16: (1, 2), GGMLType.I32: (1, 4)}
+          GGMLType.Q8_1: (32, 36), GGMLType.I8: (1, 1), GGMLType.I16: (1, 2), GGMLType.I32: (1, 4),
+          # K-quants: super-blocks of 256 weights
+          GGMLType.Q2_K: (256, 84), GGMLType.Q3_K: (256, 110), GGMLType.Q4_K: (256, 144), GGMLType.Q5_K: (256, 176),
+          GGMLType.Q6_K: (256, 210), GGMLType.Q8_K: (256, 292)}
 
 
 class GGUFValueType(enum.IntEnum):
@@ -155,6 +158,132 @@ def dequantize_q8_0(blocks: np.ndarray) -> np.ndarray:
     return (q * d).reshape(*blocks.shape[:-2], -1)
 
 
+# Decoders of the other GGML block types.  They only ever run at load time (a tensor in one of these types is expanded
+# and, for the runtime's linears, re-encoded as Q8_0, which holds 4- to 6-bit sources without visible loss), so they are
+# NumPy: every function takes ``uint8 [nb, block_bytes]`` and returns ``fp32 [nb, block_elements]``.
+def _f16(col: np.ndarray) -> np.ndarray:
+    """Two byte columns -> fp32 ``[nb, 1]``."""
+    return np.ascontiguousarray(col).view(np.float16).astype(np.float32).reshape(-1, 1)
+
+
+def _nibbles(qs: np.ndarray) -> np.ndarray:
+    """``[nb, n]`` bytes -> ``[nb, 2n]``: all low nibbles, then all high nibbles (the 32-weight block layout)."""
+    return np.concatenate([qs & 0x0F, qs >> 4], -1)
+
+
+def _high_bits(qh: np.ndarray) -> np.ndarray:
+    """Four bytes (little-endian u32) -> ``[nb, 32]`` bits, bit ``i`` for weight ``i``."""
+    word = np.ascontiguousarray(qh).view("<u4").reshape(-1, 1)
+    return ((word >> np.arange(32, dtype=np.uint32)) & 1).astype(np.uint8)
+
+
+def dequantize_q4_1(b: np.ndarray) -> np.ndarray:
+    return _nibbles(b[:, 4:20]).astype(np.float32) * _f16(b[:, 0:2]) + _f16(b[:, 2:4])
+
+
+def dequantize_q5_0(b: np.ndarray) -> np.ndarray:
+    q = (_nibbles(b[:, 6:22]) | (_high_bits(b[:, 2:6]) << 4)).astype(np.int16) - 16
+    return q.astype(np.float32) * _f16(b[:, 0:2])
+
+
+def dequantize_q5_1(b: np.ndarray) -> np.ndarray:
+    q = _nibbles(b[:, 8:24]) | (_high_bits(b[:, 4:8]) << 4)
+    return q.astype(np.float32) * _f16(b[:, 0:2]) + _f16(b[:, 2:4])
+
+
+def dequantize_q8_1(b: np.ndarray) -> np.ndarray:
+    return np.ascontiguousarray(b[:, 4:36]).view(np.int8).astype(np.float32) * _f16(b[:, 0:2])
+
+
+def _per16(v: np.ndarray) -> np.ndarray:
+    """``[nb, 16]`` values, one per run of 16 weights -> ``[nb, 256]``."""
+    return np.repeat(v, 16, axis=-1)
+
+
+def _two_bit_planes(qs: np.ndarray) -> np.ndarray:
+    """``[nb, 64]`` bytes of 2-bit codes -> ``[nb, 256]``: per 32-byte half, shifts 0, 2, 4, 6 in turn over its 32 bytes."""
+    q = qs.reshape(-1, 2, 1, 32)
+    sh = np.array([0, 2, 4, 6], dtype=np.uint8).reshape(1, 1, 4, 1)
+    return ((q >> sh) & 3).reshape(-1, 256)
+
+
+def dequantize_q2_k(b: np.ndarray) -> np.ndarray:
+    sc = b[:, 0:16]
+    d, dmin = _f16(b[:, 80:82]), _f16(b[:, 82:84])
+    return d * _per16((sc & 0x0F).astype(np.float32)) * _two_bit_planes(b[:, 16:80]).astype(np.float32) - dmin * _per16((sc >> 4).astype(np.float32))
+
+
+def _q3k_scales(raw: np.ndarray) -> np.ndarray:
+    """12 bytes -> sixteen 6-bit scales (still biased by 32): low 4 bits from the first 8 bytes, high 2 bits from the last 4."""
+    a = np.ascontiguousarray(raw).view("<u4").reshape(-1, 3).astype(np.uint32)
+    k1, k2 = np.uint32(0x03030303), np.uint32(0x0F0F0F0F)
+    a0, a1, t = a[:, 0], a[:, 1], a[:, 2]
+    out = np.stack([(a0 & k2) | ((t & k1) << 4), (a1 & k2) | (((t >> 2) & k1) << 4),
+                    ((a0 >> 4) & k2) | (((t >> 4) & k1) << 4), ((a1 >> 4) & k2) | (((t >> 6) & k1) << 4)], -1).astype("<u4")
+    return np.ascontiguousarray(out).view(np.uint8).reshape(-1, 16)
+
+
+def dequantize_q3_k(b: np.ndarray) -> np.ndarray:
+    hm, d = b[:, 0:32], _f16(b[:, 108:110])
+    low = _two_bit_planes(b[:, 32:96]).astype(np.int16)                      # order: half, shift, byte
+    bit = np.arange(8, dtype=np.uint8).reshape(1, 8, 1)                         # plane (half * 4 + shift) tests bit of that index
+    high = ((hm.reshape(-1, 1, 32) >> bit) & 1).reshape(-1, 256).astype(np.int16)
+    q = low - 4 * (1 - high)
+    sc = _q3k_scales(b[:, 96:108]).astype(np.int16) - 32
+    return d * _per16(sc.astype(np.float32)) * q.astype(np.float32)
+
+
+def _k4_scales(raw: np.ndarray):
+    """12 bytes -> eight 6-bit scales and eight 6-bit minima of a Q4_K / Q5_K super-block."""
+    q = raw.astype(np.uint8)
+    sc = np.concatenate([q[:, 0:4] & 63, (q[:, 8:12] & 0x0F) | ((q[:, 0:4] >> 6) << 4)], -1)
+    mn = np.concatenate([q[:, 4:8] & 63, (q[:, 8:12] >> 4) | ((q[:, 4:8] >> 6) << 4)], -1)
+    return sc.astype(np.float32), mn.astype(np.float32)
+
+
+def _per32(v: np.ndarray) -> np.ndarray:
+    return np.repeat(v, 32, axis=-1)
+
+
+def _k4_codes(qs: np.ndarray) -> np.ndarray:
+    """``[nb, 128]`` bytes -> ``[nb, 256]``: per 32-byte chunk its low nibbles, then its high nibbles."""
+    q = qs.reshape(-1, 4, 1, 32)
+    return np.concatenate([q & 0x0F, q >> 4], 2).reshape(-1, 256)
+
+
+def dequantize_q4_k(b: np.ndarray) -> np.ndarray:
+    sc, mn = _k4_scales(b[:, 4:16])
+    return _f16(b[:, 0:2]) * _per32(sc) * _k4_codes(b[:, 16:144]).astype(np.float32) - _f16(b[:, 2:4]) * _per32(mn)
+
+
+def dequantize_q5_k(b: np.ndarray) -> np.ndarray:
+    sc, mn = _k4_scales(b[:, 4:16])
+    bit = np.arange(8, dtype=np.uint8).reshape(1, 8, 1)                         # run r of 32 weights takes bit r of qh
+    high = ((b[:, 16:48].reshape(-1, 1, 32) >> bit) & 1).reshape(-1, 256)
+    q = _k4_codes(b[:, 48:176]) | (high.astype(np.uint8) << 4)
+    return _f16(b[:, 0:2]) * _per32(sc) * q.astype(np.float32) - _f16(b[:, 2:4]) * _per32(mn)
+
+
+def dequantize_q6_k(b: np.ndarray) -> np.ndarray:
+    ql = b[:, 0:128].reshape(-1, 2, 2, 32)                                      # half, which 32-byte row, byte
+    qh = b[:, 128:192].reshape(-1, 2, 1, 32)
+    low = np.concatenate([ql & 0x0F, ql >> 4], 2)                               # [nb, 2, 4, 32]: rows lo(0..31), lo(32..63), hi(0..31), hi(32..63)
+    sh = np.array([0, 2, 4, 6], dtype=np.uint8).reshape(1, 1, 4, 1)
+    q = (low | (((qh >> sh) & 3) << 4)).astype(np.int16) - 32
+    sc = np.ascontiguousarray(b[:, 192:208]).view(np.int8).astype(np.float32)  # one per 16 weights, in output order
+    return _f16(b[:, 208:210]) * _per16(sc) * q.reshape(-1, 256).astype(np.float32)
+
+
+def dequantize_q8_k(b: np.ndarray) -> np.ndarray:
+    d = np.ascontiguousarray(b[:, 0:4]).view("<f4").reshape(-1, 1)
+    return np.ascontiguousarray(b[:, 4:260]).view(np.int8).astype(np.float32) * d
+
+
+_DECODERS = {GGMLType.Q4_1: dequantize_q4_1, GGMLType.Q5_0: dequantize_q5_0, GGMLType.Q5_1: dequantize_q5_1, GGMLType.Q8_1: dequantize_q8_1,
+             GGMLType.Q2_K: dequantize_q2_k, GGMLType.Q3_K: dequantize_q3_k, GGMLType.Q4_K: dequantize_q4_k, GGMLType.Q5_K: dequantize_q5_k,
+             GGMLType.Q6_K: dequantize_q6_k, GGMLType.Q8_K: dequantize_q8_k}
+
+
 def dequantize(raw: np.ndarray, ggml_type: GGMLType, shape: Tuple[int, ...]) -> np.ndarray:
     t = GGMLType(ggml_type)
     if t is GGMLType.F32:
@@ -169,6 +298,8 @@ def dequantize(raw: np.ndarray, ggml_type: GGMLType, shape: Tuple[int, ...]) -> 
         return dequantize_q8_0(raw.reshape(-1, 34)).reshape(shape)
     if t in (GGMLType.I8, GGMLType.I16, GGMLType.I32):
         return raw.view({GGMLType.I8: np.int8, GGMLType.I16: np.int16, GGMLType.I32: np.int32}[t]).reshape(shape)
+    if t in _DECODERS:
+        return _DECODERS[t](np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1, _BLOCK[t][1])).reshape(shape)
     raise NotImplementedError(f"dequantisation of {t.name} is not implemented")
 
 
@@ -305,9 +436,26 @@ def _wval(v) -> bytes:
     raise TypeError(f"cannot store {type(v)} in GGUF metadata")
 
 
-def encode_tensor(t: torch.Tensor, ggml_type: GGMLType) -> bytes:
-    x = t.detach().float().cpu().numpy()
+@dataclass
+class RawTensor:
+    """Blocks that are encoded already (any GGML type): ``shape`` in torch layout ``[out, in]`` and the block bytes in
+    row-major order.  ``write_gguf`` stores them as they are."""
+    shape: Tuple[int, ...]
+    data: bytes
+
+    def check(self, ggml_type: GGMLType) -> None:
+        be, bb = _BLOCK[GGMLType(ggml_type)]
+        n = int(np.prod(self.shape))
+        if self.shape[-1] % be or len(self.data) != n // be * bb:
+            raise ValueError(f"{len(self.data)} bytes do not hold a {tuple(self.shape)} tensor of {GGMLType(ggml_type).name} blocks")
+
+
+def encode_tensor(t, ggml_type: GGMLType) -> bytes:
     ty = GGMLType(ggml_type)
+    if isinstance(t, RawTensor):
+        t.check(ty)
+        return bytes(t.data)
+    x = t.detach().float().cpu().numpy()
     if ty is GGMLType.F32:
         return x.astype("<f4").tobytes()
     if ty is GGMLType.F16:
@@ -316,12 +464,12 @@ def encode_tensor(t: torch.Tensor, ggml_type: GGMLType) -> bytes:
         return quantize_q4_0(x).tobytes()
     if ty is GGMLType.Q8_0:
         return quantize_q8_0(x).tobytes()
-    raise NotImplementedError(f"writing {ty.name} is not implemented")
+    raise NotImplementedError(f"encoding {ty.name} is not implemented: pass blocks that are encoded already as a RawTensor")
 
 
 def write_gguf(path: str, metadata: Dict[str, Any], tensors: Dict[str, Tuple[torch.Tensor, GGMLType]],
                alignment: int = DEFAULT_ALIGNMENT) -> None:
-    """``tensors[name] = (tensor in torch layout [out, in], ggml type)``."""
+    """``tensors[name] = (tensor in torch layout [out, in], ggml type)``; the tensor may be a :class:`RawTensor`."""
     md = dict(metadata)
     md.setdefault("general.alignment", alignment)
     head = struct.pack("<IIQQ", GGUF_MAGIC, GGUF_VERSION, len(tensors), len(md))

@@ -209,3 +209,116 @@ def test_mlx_loader_roundtrip_metadata_and_errors(tmp_path):
     # the generic state-dict reader goes through the same loader
     from rustorch_b200.models.high_level import load_state_dict_file
     assert torch.equal(load_state_dict_file(path)["a.weight"], tensors["a.weight"])
+
+
+# ------------------------------------------------------------------ the other GGML block types
+def _rand_blocks(rng, nb, nbytes, f16_cols=(), f32_cols=()):
+    b = rng.integers(0, 256, (nb, nbytes), dtype=np.uint8)
+    for c in f16_cols:
+        b[:, c:c + 2] = (rng.standard_normal(nb) * 0.1).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    for c in f32_cols:
+        b[:, c:c + 4] = (rng.standard_normal(nb) * 0.1).astype(np.float32).view(np.uint8).reshape(nb, 4)
+    return b
+
+
+_BLOCK_CASES = {"Q4_1": (20, (0, 2)), "Q5_0": (22, (0,)), "Q5_1": (24, (0, 2)), "Q2_K": (84, (80, 82)), "Q3_K": (110, (108,)),
+                "Q4_K": (144, (0, 2)), "Q5_K": (176, (0, 2)), "Q6_K": (210, (208,))}
+
+
+@pytest.mark.parametrize("name", sorted(_BLOCK_CASES))
+def test_block_decoders_match_the_gguf_package(name):
+    """Random block bytes (finite scales) decode to the same floats as the ``gguf`` package's reference decoders."""
+    ref_pkg = pytest.importorskip("gguf")
+    from gguf import quants
+    from rustorch_b200.formats import gguf as ours
+    nbytes, cols = _BLOCK_CASES[name]
+    b = _rand_blocks(np.random.default_rng(1), 96, nbytes, cols)
+    want = quants.dequantize(b, getattr(ref_pkg.GGMLQuantizationType, name))
+    got = ours.dequantize(b.reshape(-1), getattr(ours.GGMLType, name), want.shape)
+    assert got.dtype == np.float32 and np.array_equal(got, want)
+
+
+def test_block_decoders_against_scalar_loops():
+    """Q4_K, Q6_K, Q8_1 and Q8_K written out weight by weight from the format's definition (no package needed)."""
+    from rustorch_b200.formats import gguf as ours
+    rng = np.random.default_rng(2)
+    h = lambda two: float(np.frombuffer(bytes(two), dtype=np.float16)[0])      # noqa: E731
+    # Q4_K: d, dmin, 12 scale bytes, 128 code bytes; chunk c of 64 weights = low nibbles then high nibbles of 32 bytes
+    b = _rand_blocks(rng, 3, 144, (0, 2))
+    want = np.zeros((3, 256), dtype=np.float32)
+    for n in range(3):
+        d, dmin, sc, qs = h(b[n, 0:2]), h(b[n, 2:4]), b[n, 4:16].astype(int), b[n, 16:144].astype(int)
+
+        def scale_min(j):
+            if j < 4:
+                return sc[j] & 63, sc[j + 4] & 63
+            return (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4), (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4)
+        for c in range(4):
+            (s1, m1), (s2, m2) = scale_min(2 * c), scale_min(2 * c + 1)
+            for l in range(32):
+                want[n, c * 64 + l] = np.float32(d) * np.float32(s1) * np.float32(qs[c * 32 + l] & 0xF) - np.float32(dmin) * np.float32(m1)
+                want[n, c * 64 + 32 + l] = np.float32(d) * np.float32(s2) * np.float32(qs[c * 32 + l] >> 4) - np.float32(dmin) * np.float32(m2)
+    assert np.allclose(ours.dequantize(b.reshape(-1), ours.GGMLType.Q4_K, (3, 256)), want, rtol=1e-6, atol=1e-6)
+    # Q6_K: 128 low-nibble bytes, 64 bytes of 2-bit highs, 16 int8 scales, d
+    b = _rand_blocks(rng, 2, 210, (208,))
+    want = np.zeros((2, 256), dtype=np.float32)
+    for n in range(2):
+        ql, qh, sc, d = b[n, 0:128].astype(int), b[n, 128:192].astype(int), b[n, 192:208].view(np.int8).astype(int), h(b[n, 208:210])
+        for half in range(2):
+            for l in range(32):
+                i = l // 16
+                qv = [(ql[half * 64 + l] & 0xF) | (((qh[half * 32 + l] >> 0) & 3) << 4), (ql[half * 64 + l + 32] & 0xF) | (((qh[half * 32 + l] >> 2) & 3) << 4),
+                      (ql[half * 64 + l] >> 4) | (((qh[half * 32 + l] >> 4) & 3) << 4), (ql[half * 64 + l + 32] >> 4) | (((qh[half * 32 + l] >> 6) & 3) << 4)]
+                for k in range(4):
+                    want[n, half * 128 + k * 32 + l] = np.float32(d) * np.float32(sc[half * 8 + i + 2 * k]) * np.float32(qv[k] - 32)
+    assert np.allclose(ours.dequantize(b.reshape(-1), ours.GGMLType.Q6_K, (2, 256)), want, rtol=1e-6, atol=1e-6)
+    b = _rand_blocks(rng, 4, 36, (0, 2))
+    want = b[:, 4:36].copy().view(np.int8).astype(np.float32) * b[:, 0:2].copy().view(np.float16).astype(np.float32)
+    assert np.array_equal(ours.dequantize(b.reshape(-1), ours.GGMLType.Q8_1, (4, 32)), want)
+    b = _rand_blocks(rng, 2, 292, (), (0,))
+    want = b[:, 4:260].copy().view(np.int8).astype(np.float32) * b[:, 0:4].copy().view(np.float32)
+    assert np.array_equal(ours.dequantize(b.reshape(-1), ours.GGMLType.Q8_K, (2, 256)), want)
+    with pytest.raises(ValueError):
+        ours.RawTensor((2, 256), b"x" * 10).check(ours.GGMLType.Q4_K)
+
+
+def test_runtime_loads_a_k_quant_file(tmp_path):
+    """A Llama GGUF whose linears are Q4_K / Q6_K / Q5_0 blocks: tensor sizes and offsets follow the 256-weight block
+    sizes, the runtime expands and re-encodes the linears, and its logits equal those of a runtime built from the same
+    weights stored as F32."""
+    from rustorch_b200 import llm
+    from rustorch_b200.formats import gguf as ours
+    rng = np.random.default_rng(3)
+    d_model, n_ff, vocab, hd = 256, 512, 64, 64
+
+    def blocks(ty, out_f, in_f):
+        nbytes, cols = _BLOCK_CASES[ty]
+        b = _rand_blocks(rng, out_f * in_f // ours._BLOCK[getattr(ours.GGMLType, ty)][0], nbytes, cols)
+        for c in cols:                                                # small block scales: weights of order 0.01 - 0.1
+            b[:, c:c + 2] = (rng.standard_normal(len(b)) * (0.002 if ty == "Q5_0" else 4e-5)).astype(np.float16).view(np.uint8).reshape(len(b), 2)
+        return ours.RawTensor((out_f, in_f), b.tobytes())
+    quant = {"token_embd.weight": (torch.randn(vocab, d_model) * 0.05, ours.GGMLType.F16), "output_norm.weight": (torch.ones(d_model), ours.GGMLType.F32),
+             "output.weight": (blocks("Q6_K", vocab, d_model), ours.GGMLType.Q6_K)}
+    p = "blk.0."
+    quant.update({p + "attn_q.weight": (blocks("Q4_K", 4 * hd, d_model), ours.GGMLType.Q4_K), p + "attn_k.weight": (blocks("Q4_K", 2 * hd, d_model), ours.GGMLType.Q4_K),
+                  p + "attn_v.weight": (blocks("Q6_K", 2 * hd, d_model), ours.GGMLType.Q6_K), p + "attn_output.weight": (blocks("Q5_0", d_model, 4 * hd), ours.GGMLType.Q5_0),
+                  p + "ffn_gate.weight": (blocks("Q4_K", n_ff, d_model), ours.GGMLType.Q4_K), p + "ffn_up.weight": (blocks("Q4_K", n_ff, d_model), ours.GGMLType.Q4_K),
+                  p + "ffn_down.weight": (blocks("Q6_K", d_model, n_ff), ours.GGMLType.Q6_K), p + "attn_norm.weight": (torch.ones(d_model), ours.GGMLType.F32),
+                  p + "ffn_norm.weight": (torch.ones(d_model), ours.GGMLType.F32)})
+    md = {"general.architecture": "llama", "llama.block_count": 1, "llama.embedding_length": d_model, "llama.feed_forward_length": n_ff,
+          "llama.attention.head_count": 4, "llama.attention.head_count_kv": 2, "llama.rope.freq_base": 10000.0,
+          "llama.attention.layer_norm_rms_epsilon": 1e-5, "llama.context_length": 64, "llama.vocab_size": vocab}
+    qpath, fpath = str(tmp_path / "k.gguf"), str(tmp_path / "f32.gguf")
+    ours.write_gguf(qpath, md, quant)
+    with ours.GGUFFile(qpath) as g:
+        assert g.tensors[p + "attn_q.weight"].ggml_type == ours.GGMLType.Q4_K and g.tensors[p + "attn_q.weight"].nbytes == 4 * hd * d_model // 256 * 144
+        dense = {k: (g.load_tensor(k), ours.GGMLType.F32 if k.endswith("weight") and "norm" not in k and "token_embd" not in k else quant[k][1])
+                 for k in quant}
+        w = dense[p + "ffn_down.weight"][0]
+        assert w.shape == (d_model, n_ff) and torch.isfinite(w).all() and 0.001 < float(w.std()) < 1.0, float(w.std())
+    dense["token_embd.weight"] = quant["token_embd.weight"]
+    ours.write_gguf(fpath, md, dense)
+    rq, rf = llm.LlamaRuntime.from_gguf(qpath, device="cpu"), llm.LlamaRuntime.from_gguf(fpath, device="cpu")
+    prompt = torch.randint(0, vocab, (1, 6), generator=torch.Generator().manual_seed(0))
+    lq, lf = rq.prefill(prompt, rq.new_cache(1, 16)), rf.prefill(prompt, rf.new_cache(1, 16))
+    assert torch.isfinite(lq).all() and torch.allclose(lq, lf, atol=1e-5)
