@@ -142,6 +142,15 @@ class LlamaRuntime:
                               n_head=int(mc["n_head"]), n_head_kv=int(mc["n_head_kv"]), n_ff=int(mc["n_ff"]),
                               rope_theta=float(mc["rope_theta"]), rms_eps=float(mc["rms_eps"]),
                               context_length=int(mc["context_length"]))
+            need = ["token_embd.weight", "output_norm.weight"] + [f"blk.{i}.{t}.weight" for i in range(cfg.n_layer) for t in (
+                "attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down", "attn_norm", "ffn_norm")]
+            absent = [n for n in need if n not in g.tensors]
+            extra = sorted({n.split(".", 2)[-1] for n in g.tensors if n.startswith("blk.") and n.endswith(".bias")}
+                           | {n.split(".", 2)[-1] for n in g.tensors if "_exps." in n or "ffn_gate_inp" in n})
+            if absent or extra:
+                what = (f"missing {absent[:4]}{'...' if len(absent) > 4 else ''}" if absent else "") + \
+                       (("; " if absent else "") + f"tensors this runtime does not execute: {extra[:6]}" if extra else "")
+                raise ValueError(f"{path}: architecture '{mc['architecture']}' is not a bias-free Llama-style decoder ({what})")
             rt = cls(cfg, device, tp_rank, tp_world, tp_group)
 
             def ql(name: str) -> QuantLinear:

@@ -107,3 +107,24 @@ def test_quant_linear_fused_projection_fallback_on_cpu():
     assert act.shape == (3, 32)
     assert torch.allclose(act, torch.nn.functional.silu(t[:, :32]) * t[:, 32:], atol=1e-4, rtol=1e-4)
     assert torch.allclose(q.fused(x), x @ W.t(), atol=1e-4, rtol=1e-4)
+
+
+def test_from_gguf_names_what_it_cannot_run(tmp_path):
+    """Files of other decoder families fail with a message that says which tensors are the problem, not with a KeyError
+    or, worse, by ignoring biases."""
+    p = str(tmp_path / "t.gguf")
+    _tiny_gguf(p)
+    with gguf.GGUFFile(p) as g:
+        md = dict(g.metadata)
+        tensors = {n: (g.load_tensor(n), gguf.GGMLType.F32) for n in g.tensors}
+    biased = dict(tensors)
+    biased["blk.0.attn_q.bias"] = (torch.zeros(64), gguf.GGMLType.F32)
+    pb = str(tmp_path / "biased.gguf")
+    gguf.write_gguf(pb, md, biased)
+    with pytest.raises(ValueError, match="attn_q.bias"):
+        llm.LlamaRuntime.from_gguf(pb, device="cpu")
+    lacking = {k: v for k, v in tensors.items() if "ffn_gate" not in k}
+    pl = str(tmp_path / "lacking.gguf")
+    gguf.write_gguf(pl, md, lacking)
+    with pytest.raises(ValueError, match="missing"):
+        llm.LlamaRuntime.from_gguf(pl, device="cpu")
