@@ -259,6 +259,60 @@ class EnableGradGuard(NoGradGuard):
         return self
 
 
+class AnomalyDetectionGuard:
+    """Guard that turns autograd anomaly detection on (NaN checks in backward, forward stack traces in the errors) and
+    puts the previous setting back on exit (src/autograd/context.rs:107-127)."""
+
+    def __init__(self, check_nan: bool = True):
+        self.check_nan = check_nan
+
+    def __enter__(self):
+        self._prev = torch.is_anomaly_enabled()
+        self._prev_nan = torch.is_anomaly_check_nan_enabled()
+        torch.autograd.set_detect_anomaly(True, check_nan=self.check_nan)
+        return self
+
+    def __exit__(self, *exc):
+        torch.autograd.set_detect_anomaly(self._prev, check_nan=self._prev_nan)
+        return False
+
+
+def is_anomaly_detection_enabled() -> bool:
+    return torch.is_anomaly_enabled()
+
+
+def set_anomaly_detection(enabled: bool) -> None:
+    torch.autograd.set_detect_anomaly(bool(enabled))
+
+
+class GradientContext:
+    """The current thread's gradient mode as one object: ``grad_enabled`` and ``anomaly_detection`` flags that read
+    and write torch's thread-local state (src/autograd/context.rs:10-60 keeps the same two flags in a thread-local)."""
+
+    @property
+    def grad_enabled(self) -> bool:
+        return torch.is_grad_enabled()
+
+    @grad_enabled.setter
+    def grad_enabled(self, on: bool) -> None:
+        torch.set_grad_enabled(bool(on))
+
+    @property
+    def anomaly_detection(self) -> bool:
+        return torch.is_anomaly_enabled()
+
+    @anomaly_detection.setter
+    def anomaly_detection(self, on: bool) -> None:
+        torch.autograd.set_detect_anomaly(bool(on))
+
+    @classmethod
+    def current(cls) -> "GradientContext":
+        return cls()
+
+    def __repr__(self) -> str:
+        return f"GradientContext(grad_enabled={self.grad_enabled}, anomaly_detection={self.anomaly_detection})"
+
+
 # ------------------------------------------------------------------ functional API
 def grad(outputs: Sequence[Variable], inputs: Sequence[Variable], grad_outputs=None, retain_graph: bool = False,
          create_graph: bool = False, allow_unused: bool = False) -> List[Optional[Tensor]]:

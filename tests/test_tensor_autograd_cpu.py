@@ -213,3 +213,30 @@ def test_wrapper_protocols_numpy_iteration_comparison():
     v[1].sum().backward()
     assert v.grad.as_slice() == [0.0, 0.0, 1.0, 1.0]
     assert isinstance(torch.ones(2, 2) + a, rt.Tensor) and isinstance(torch.ones(2, 2) * v, rt.Variable)
+
+
+def test_gradient_context_and_anomaly_guard():
+    """src/autograd/context.rs:10-155: the two thread-local flags, their guards, and what anomaly detection does."""
+    from rustorch_b200 import autograd as A
+    ctx = A.GradientContext.current()
+    assert ctx.grad_enabled and not ctx.anomaly_detection and "grad_enabled=True" in repr(ctx)
+    with A.NoGradGuard():
+        assert not ctx.grad_enabled
+        with A.EnableGradGuard():
+            assert A.is_grad_enabled()
+        assert not A.is_grad_enabled()
+    ctx.grad_enabled = False
+    assert not torch.is_grad_enabled()
+    ctx.grad_enabled = True
+    x = torch.tensor([0.0], requires_grad=True)
+    torch.sqrt(x).sum().backward()                                    # silently produces inf without the guard
+    assert torch.isinf(x.grad).all()
+    with A.AnomalyDetectionGuard():
+        assert A.is_anomaly_detection_enabled() and ctx.anomaly_detection
+        y = torch.tensor([0.0], requires_grad=True)
+        with pytest.raises(RuntimeError, match="nan"):
+            (torch.sqrt(y) * 0.0).sum().backward()                    # 0 * inf = nan in the backward pass
+    assert not A.is_anomaly_detection_enabled()
+    A.set_anomaly_detection(True)
+    assert ctx.anomaly_detection
+    A.set_anomaly_detection(False)
