@@ -78,6 +78,17 @@ class ModelLoader:
             if isinstance(tok, ByteTokenizer):
                 tok = ByteTokenizer(rt.cfg.vocab_size)
             return rt, tok, meta
+        if fmt == "huggingface":
+            import json as _json
+            cfg_path = os.path.join(path, "config.json")
+            hf = _json.load(open(cfg_path)) if os.path.exists(cfg_path) else {}
+            if str(hf.get("model_type", "")).lower() in ("llama", "mistral") or any("Llama" in a or "Mistral" in a for a in hf.get("architectures", [])):
+                rt = LlamaRuntime.from_hf(path, device)
+                spm = tokenizer_path or (os.path.join(path, "tokenizer.model") if os.path.exists(os.path.join(path, "tokenizer.model")) else None)
+                tok = load_tokenizer(spm, vocab_size=rt.cfg.vocab_size)
+                meta = ModelMetadata(os.path.basename(os.path.normpath(path)), "huggingface", rt.cfg.vocab_size, rt.cfg.n_embd, rt.cfg.n_layer,
+                                     rt.cfg.n_head, rt.cfg.context_length)
+                return rt, tok, meta
         if fmt in ("safetensors", "mlx", "rustorch", "torch", "pth", "huggingface", "json"):
             from ..models.gpt import GPT, GPTConfig
             from ..models.high_level import load_state_dict_file

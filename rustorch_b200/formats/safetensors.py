@@ -80,6 +80,97 @@ def load_safetensors(path: str, device: str = "cpu", use_mmap: bool = True) -> D
     return out
 
 
+class SafetensorsFile:
+    """One safetensors file read tensor by tensor from a memory map: ``keys()``, ``shape(name)``, ``get(name)`` (a copy,
+    so the file can be closed).  For checkpoints that are too large to materialise whole."""
+
+    def __init__(self, path: str):
+        self.path = path
+        self.header, self._base = read_safetensors_header(path)
+        self._f = open(path, "rb")
+        self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ) if os.path.getsize(path) > 0 else b""
+
+    def keys(self):
+        return [k for k in self.header if k != "__metadata__"]
+
+    def __contains__(self, name: str) -> bool:
+        return name in self.header and name != "__metadata__"
+
+    def shape(self, name: str) -> Tuple[int, ...]:
+        return tuple(self.header[name]["shape"])
+
+    def get(self, name: str) -> torch.Tensor:
+        info = self.header[name]
+        b, e = info["data_offsets"]
+        dt = _ST_DTYPES[info["dtype"]]
+        if e == b:
+            return torch.empty(info["shape"], dtype=dt)
+        arr = np.frombuffer(self._mm, dtype=np.uint8, count=e - b, offset=self._base + b).copy()
+        return torch.from_numpy(arr).view(dt).reshape(info["shape"])
+
+    def close(self) -> None:
+        if not isinstance(self._mm, bytes):
+            self._mm.close()
+        self._f.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+        return False
+
+
+class HuggingFaceCheckpoint:
+    """A Hugging Face model directory: ``config.json`` plus ``model.safetensors`` or the shards named by
+    ``model.safetensors.index.json``; tensors are fetched one at a time from whichever shard holds them."""
+
+    def __init__(self, directory: str):
+        self.directory = directory
+        cp = os.path.join(directory, "config.json")
+        self.config: dict = json.load(open(cp)) if os.path.exists(cp) else {}
+        idx = os.path.join(directory, "model.safetensors.index.json")
+        if os.path.exists(idx):
+            self.weight_map: Dict[str, str] = dict(json.load(open(idx))["weight_map"])
+        else:
+            single = os.path.join(directory, "model.safetensors")
+            if not os.path.exists(single):
+                raise FileNotFoundError(f"{directory}: neither model.safetensors nor model.safetensors.index.json")
+            with SafetensorsFile(single) as f:
+                self.weight_map = {k: "model.safetensors" for k in f.keys()}
+        self._open: Dict[str, SafetensorsFile] = {}
+
+    def keys(self):
+        return list(self.weight_map)
+
+    def __contains__(self, name: str) -> bool:
+        return name in self.weight_map
+
+    def _file(self, name: str) -> SafetensorsFile:
+        shard = self.weight_map[name]
+        if shard not in self._open:
+            self._open[shard] = SafetensorsFile(os.path.join(self.directory, shard))
+        return self._open[shard]
+
+    def shape(self, name: str) -> Tuple[int, ...]:
+        return self._file(name).shape(name)
+
+    def get(self, name: str) -> torch.Tensor:
+        return self._file(name).get(name)
+
+    def close(self) -> None:
+        for f in self._open.values():
+            f.close()
+        self._open.clear()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+        return False
+
+
 def safetensors_metadata(path: str) -> Dict[str, str]:
     return read_safetensors_header(path)[0].get("__metadata__", {})
 

@@ -173,6 +173,51 @@ class LlamaRuntime:
         return rt
 
     @classmethod
+    def from_hf(cls, directory: str, device="cuda", ggml_type=gguf.GGMLType.Q8_0, tp_rank: int = 0, tp_world: int = 1,
+                tp_group=None) -> "LlamaRuntime":
+        """A Hugging Face Llama-style checkpoint directory (``config.json`` + safetensors, sharded or not).  Every linear
+        is quantised to ``ggml_type`` (Q8_0 or Q4_0) as it is read, one tensor at a time, so a bf16 checkpoint never
+        sits in memory whole.  These checkpoints rotate the two halves of a head (``rotate_half``), not adjacent pairs
+        as GGUF files do, hence ``rope_interleaved=False``."""
+        from ..formats.safetensors import HuggingFaceCheckpoint
+        with HuggingFaceCheckpoint(directory) as ck:
+            c = ck.config
+            arch = (c.get("architectures") or [c.get("model_type", "?")])[0]
+            try:
+                n_head = int(c["num_attention_heads"])
+                cfg = LlamaConfig(vocab_size=int(c["vocab_size"]), n_layer=int(c["num_hidden_layers"]), n_embd=int(c["hidden_size"]),
+                                  n_head=n_head, n_head_kv=int(c.get("num_key_value_heads") or n_head), n_ff=int(c["intermediate_size"]),
+                                  rope_theta=float(c.get("rope_theta", 10000.0)), rms_eps=float(c.get("rms_norm_eps", 1e-5)),
+                                  context_length=int(c.get("max_position_embeddings", 2048)))
+            except KeyError as e:
+                raise ValueError(f"{directory}: config.json lacks {e.args[0]!r}") from None
+            if c.get("head_dim") not in (None, cfg.n_embd // cfg.n_head):
+                raise ValueError(f"{directory}: head_dim {c['head_dim']} differs from hidden_size / num_attention_heads")
+            if c.get("rope_scaling"):
+                raise ValueError(f"{directory}: rope_scaling {c['rope_scaling']} is not implemented by this runtime")
+            cfg.rope_interleaved = False
+            lay = lambda i, t: f"model.layers.{i}.{t}.weight"      # noqa: E731
+            parts = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj", "mlp.gate_proj", "mlp.up_proj",
+                     "mlp.down_proj", "input_layernorm", "post_attention_layernorm")
+            need = ["model.embed_tokens.weight", "model.norm.weight"] + [lay(i, t) for i in range(cfg.n_layer) for t in parts]
+            absent = [n for n in need if n not in ck]
+            extra = sorted({n.split(".", 3)[-1] for n in ck.keys() if n.startswith("model.layers.") and n.endswith(".bias")}
+                           | {n.split(".", 3)[-1] for n in ck.keys() if ".experts." in n or "block_sparse_moe" in n})
+            if absent or extra:
+                what = (f"missing {absent[:4]}{'...' if len(absent) > 4 else ''}" if absent else "") + \
+                       (("; " if absent else "") + f"tensors this runtime does not execute: {extra[:6]}" if extra else "")
+                raise ValueError(f"{directory}: '{arch}' is not a bias-free Llama-style decoder ({what})")
+            rt = cls(cfg, device, tp_rank, tp_world, tp_group)
+            ql = lambda name: QuantLinear.from_float(ck.get(name).float(), ggml_type, rt.device)      # noqa: E731
+            for i in range(cfg.n_layer):
+                rt.layers.append(rt._assemble_layer(*(ql(lay(i, t)) for t in parts[:7]), ck.get(lay(i, parts[7])).float(),
+                                                    ck.get(lay(i, parts[8])).float()))
+            rt.tok_emb = ck.get("model.embed_tokens.weight").to(rt.device, rt.act_dtype)
+            rt.out_norm = ck.get("model.norm.weight").to(rt.device, rt.act_dtype)
+            rt.lm_head = ql("lm_head.weight" if "lm_head.weight" in ck else "model.embed_tokens.weight")
+        return rt
+
+    @classmethod
     def random_init(cls, cfg: LlamaConfig, device="cuda", ggml_type=gguf.GGMLType.Q4_0, tp_rank: int = 0, tp_world: int = 1,
                     tp_group=None, seed: int = 0, std: float = 0.02) -> "LlamaRuntime":
         """Synthetic weights of the right shapes and statistics, built directly in quantised form."""

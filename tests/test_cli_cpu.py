@@ -175,3 +175,19 @@ def test_repl_survives_a_failed_generation(tmp_path):
     assert "messages: 0" in text and "Goodbye!" in text             # the failed turn left no half conversation behind
     one = []
     assert cli.main(["--model", model, "--backend", "cpu", "--prompt", "hello"], out=one.append) == 1 and "error:" in "".join(one)
+
+
+def test_cli_runs_a_hugging_face_llama_directory(tmp_path):
+    tf = pytest.importorskip("transformers")
+    torch.manual_seed(0)
+    hc = tf.LlamaConfig(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4,
+                        num_key_value_heads=2, max_position_embeddings=128, tie_word_embeddings=True)
+    d = str(tmp_path / "hf-llama")
+    tf.LlamaForCausalLM(hc).save_pretrained(d, safe_serialization=True)
+    buf = []
+    assert cli.main(["--model", d, "--backend", "cpu", "--max-tokens", "4", "--temperature", "0", "--prompt", "hi"], out=buf.append) == 0
+    assert "Assistant: " in "".join(buf) and "error" not in "".join(buf)
+    lines = iter(["/config", "/exit"])
+    buf2 = []
+    cli.main(["--model", d, "--backend", "cpu"], read=lambda _: next(lines), out=buf2.append)
+    assert "model: hf-llama" in "".join(buf2)

@@ -1,4 +1,6 @@
 """LLM runtime on CPU: quantised linear, sampling, metrics, GGUF -> runtime -> generation."""
+import os
+
 import pytest
 import torch
 
@@ -128,3 +130,58 @@ def test_from_gguf_names_what_it_cannot_run(tmp_path):
     gguf.write_gguf(pl, md, lacking)
     with pytest.raises(ValueError, match="missing"):
         llm.LlamaRuntime.from_gguf(pl, device="cpu")
+
+
+def test_from_hf_matches_transformers_llama(tmp_path):
+    """A Hugging Face Llama checkpoint directory runs on the quantised runtime and agrees with ``transformers``' own
+    forward pass (grouped-query attention, rotate-half RoPE, RMSNorm epsilon, untied head) up to Q8_0 rounding."""
+    tf = pytest.importorskip("transformers")
+    torch.manual_seed(0)
+    hc = tf.LlamaConfig(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, max_position_embeddings=64, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False)
+    ref = tf.LlamaForCausalLM(hc).eval()
+    d = str(tmp_path / "hf")
+    ref.save_pretrained(d, safe_serialization=True)
+    rt = llm.LlamaRuntime.from_hf(d, device="cpu")
+    assert not rt.cfg.rope_interleaved and rt.cfg.n_head_kv == 2 and len(rt.layers) == 2
+    prompt = torch.randint(0, 96, (2, 9), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = ref(prompt).logits[:, -1]
+    cache = rt.new_cache(2, 16)
+    got = rt.prefill(prompt, cache)
+    assert float((want - got).abs().max()) < 0.03 * float(want.abs().max()) and torch.equal(want.argmax(-1), got.argmax(-1))
+    nxt = want.argmax(-1)
+    with torch.no_grad():
+        want2 = ref(torch.cat([prompt, nxt[:, None]], 1)).logits[:, -1]
+    assert float((want2 - rt.decode_step(nxt, cache)).abs().max()) < 0.03 * float(want2.abs().max())
+    # 4-bit on load, tied head, and the sharded layout (index file naming two shards)
+    from rustorch_b200.formats.safetensors import HuggingFaceCheckpoint, load_safetensors, save_safetensors
+    import json
+    q4 = llm.LlamaRuntime.from_hf(d, device="cpu", ggml_type=gguf.GGMLType.Q4_0)
+    assert q4.layers[0].wqkv.ggml_type is gguf.GGMLType.Q4_0 and torch.isfinite(q4.prefill(prompt, q4.new_cache(2, 16))).all()
+    sd = load_safetensors(os.path.join(d, "model.safetensors"))
+    sd.pop("lm_head.weight")
+    names = sorted(sd)
+    sh = str(tmp_path / "sharded")
+    os.makedirs(sh)
+    save_safetensors({k: sd[k] for k in names[::2]}, os.path.join(sh, "model-00001-of-00002.safetensors"))
+    save_safetensors({k: sd[k] for k in names[1::2]}, os.path.join(sh, "model-00002-of-00002.safetensors"))
+    json.dump({"weight_map": {k: f"model-0000{1 + i % 2}-of-00002.safetensors" for i, k in enumerate(names)}}, open(os.path.join(sh, "model.safetensors.index.json"), "w"))
+    json.dump({**json.load(open(os.path.join(d, "config.json"))), "tie_word_embeddings": True}, open(os.path.join(sh, "config.json"), "w"))
+    with HuggingFaceCheckpoint(sh) as ck:
+        assert len(ck.keys()) == len(names) and ck.shape("model.embed_tokens.weight") == (96, 64)
+    tied = llm.LlamaRuntime.from_hf(sh, device="cpu")
+    assert tied.lm_head.out_features == 96 and torch.isfinite(tied.prefill(prompt, tied.new_cache(2, 16))).all()
+    # other families are refused by name
+    cfg = json.load(open(os.path.join(d, "config.json")))
+    bad = str(tmp_path / "bad")
+    os.makedirs(bad)
+    json.dump(cfg, open(os.path.join(bad, "config.json"), "w"))
+    full = load_safetensors(os.path.join(d, "model.safetensors"))
+    full["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(64)
+    save_safetensors(full, os.path.join(bad, "model.safetensors"))
+    with pytest.raises(ValueError, match="q_proj.bias"):
+        llm.LlamaRuntime.from_hf(bad, device="cpu")
+    json.dump({**cfg, "rope_scaling": {"type": "linear", "factor": 2.0}}, open(os.path.join(d, "config.json"), "w"))
+    with pytest.raises(ValueError, match="rope_scaling"):
+        llm.LlamaRuntime.from_hf(d, device="cpu")
