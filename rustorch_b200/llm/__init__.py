@@ -1,4 +1,5 @@
 """LLM runtime: GGUF Llama inference with KV cache, quantised linears, sampling, metrics, CLI."""
+from .convert import hf_to_gguf, interleave_rope_rows
 from .llama import KVCache, LlamaConfig, LlamaRuntime
 from .metrics import InferenceMetrics, InferenceTimer, MetricsCollector, MetricsReporter, PerformanceTargets
 from .quant import QuantLinear

@@ -1,0 +1,66 @@
+"""Hugging Face Llama checkpoint directory -> GGUF file.
+
+The two layouts differ in one thing besides the names: a GGUF Llama file rotates adjacent pairs of a head's dimensions
+(RoPE on ``(x[2i], x[2i+1])``), a Hugging Face checkpoint the two halves (``rotate_half``), so the rows of the query and
+key projections are re-ordered head by head (half-split order -> interleaved order).  With that permutation both
+layouts give the same logits, which the tests check against ``transformers``' own forward pass.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..formats import gguf
+from ..formats.safetensors import HuggingFaceCheckpoint
+
+_LAYER = {"self_attn.q_proj": "attn_q", "self_attn.k_proj": "attn_k", "self_attn.v_proj": "attn_v", "self_attn.o_proj": "attn_output",
+          "mlp.gate_proj": "ffn_gate", "mlp.up_proj": "ffn_up", "mlp.down_proj": "ffn_down", "input_layernorm": "attn_norm",
+          "post_attention_layernorm": "ffn_norm"}
+
+
+def interleave_rope_rows(w: torch.Tensor, n_head: int) -> torch.Tensor:
+    """Rows of a q / k projection from half-split order (dimension ``i`` pairs with ``i + D/2``) to interleaved order
+    (``2i`` pairs with ``2i + 1``), head by head."""
+    d = w.shape[0] // n_head
+    return w.reshape(n_head, 2, d // 2, *w.shape[1:]).transpose(1, 2).reshape(w.shape)
+
+
+def hf_to_gguf(directory: str, path: str, ggml_type: gguf.GGMLType = gguf.GGMLType.Q8_0, name: Optional[str] = None) -> Dict[str, int]:
+    """Writes ``path`` from the checkpoint in ``directory``: matrices as ``ggml_type`` (F32, F16, Q8_0 or Q4_0), norms and,
+    for quantised types, the embedding table as F32 / F16.  Returns ``{"tensors": n, "bytes": size}``."""
+    ty = gguf.GGMLType(ggml_type)
+    with HuggingFaceCheckpoint(directory) as ck:
+        c = ck.config
+        try:
+            n_layer, n_head = int(c["num_hidden_layers"]), int(c["num_attention_heads"])
+            n_kv = int(c.get("num_key_value_heads") or n_head)
+            md = {"general.architecture": "llama", "general.name": name or os.path.basename(os.path.normpath(directory)),
+                  "llama.block_count": n_layer, "llama.embedding_length": int(c["hidden_size"]),
+                  "llama.feed_forward_length": int(c["intermediate_size"]), "llama.attention.head_count": n_head,
+                  "llama.attention.head_count_kv": n_kv, "llama.rope.freq_base": float(c.get("rope_theta", 10000.0)),
+                  "llama.attention.layer_norm_rms_epsilon": float(c.get("rms_norm_eps", 1e-5)),
+                  "llama.context_length": int(c.get("max_position_embeddings", 2048)), "llama.vocab_size": int(c["vocab_size"])}
+        except KeyError as e:
+            raise ValueError(f"{directory}: config.json lacks {e.args[0]!r}") from None
+        if c.get("rope_scaling"):
+            raise ValueError(f"{directory}: rope_scaling {c['rope_scaling']} has no counterpart in the written file")
+        if any(k.endswith(".bias") for k in ck.keys()):
+            raise ValueError(f"{directory}: projections with biases are not a Llama-style decoder")
+        emb_ty = gguf.GGMLType.F16 if ty in (gguf.GGMLType.Q8_0, gguf.GGMLType.Q4_0, gguf.GGMLType.F16) else gguf.GGMLType.F32
+        tensors: Dict[str, Tuple[torch.Tensor, gguf.GGMLType]] = {
+            "token_embd.weight": (ck.get("model.embed_tokens.weight").float(), emb_ty),
+            "output_norm.weight": (ck.get("model.norm.weight").float(), gguf.GGMLType.F32)}
+        if "lm_head.weight" in ck:
+            tensors["output.weight"] = (ck.get("lm_head.weight").float(), ty)
+        for i in range(n_layer):
+            for src, dst in _LAYER.items():
+                w = ck.get(f"model.layers.{i}.{src}.weight").float()
+                if dst == "attn_q":
+                    w = interleave_rope_rows(w, n_head)
+                elif dst == "attn_k":
+                    w = interleave_rope_rows(w, n_kv)
+                tensors[f"blk.{i}.{dst}.weight"] = (w, gguf.GGMLType.F32 if dst.endswith("norm") else ty)
+    gguf.write_gguf(path, md, tensors)
+    return {"tensors": len(tensors), "bytes": os.path.getsize(path)}

@@ -185,3 +185,28 @@ def test_from_hf_matches_transformers_llama(tmp_path):
     json.dump({**cfg, "rope_scaling": {"type": "linear", "factor": 2.0}}, open(os.path.join(d, "config.json"), "w"))
     with pytest.raises(ValueError, match="rope_scaling"):
         llm.LlamaRuntime.from_hf(d, device="cpu")
+
+
+def test_hf_to_gguf_keeps_the_logits(tmp_path):
+    """The converter's row permutation of q / k turns rotate-half checkpoints into interleaved-RoPE GGUF files: the
+    runtime on the written file agrees with ``transformers`` on the original checkpoint."""
+    tf = pytest.importorskip("transformers")
+    torch.manual_seed(0)
+    hc = tf.LlamaConfig(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, max_position_embeddings=64, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False)
+    ref = tf.LlamaForCausalLM(hc).eval()
+    d = str(tmp_path / "hf")
+    ref.save_pretrained(d, safe_serialization=True)
+    prompt = torch.randint(0, 96, (2, 9), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = ref(prompt).logits[:, -1]
+    for ty, tol in ((gguf.GGMLType.F32, 0.03), (gguf.GGMLType.Q8_0, 0.03), (gguf.GGMLType.Q4_0, 0.4)):      # the runtime holds F32 matrices as Q8_0
+        out = str(tmp_path / f"{ty.name}.gguf")
+        info = llm.hf_to_gguf(d, out, ty)
+        assert info["tensors"] == 3 + 9 * 2 and info["bytes"] == os.path.getsize(out)
+        rt = llm.LlamaRuntime.from_gguf(out, device="cpu")
+        assert rt.cfg.rope_interleaved
+        got = rt.prefill(prompt, rt.new_cache(2, 16))
+        assert float((want - got).abs().max()) < tol * float(want.abs().max()), ty
+    w = torch.arange(16.0).view(8, 2)                                # two heads of four rows: halves (0, 1 | 2, 3) -> pairs (0, 2, 1, 3)
+    assert llm.interleave_rope_rows(w, 2)[:, 0].tolist() == [0.0, 4.0, 2.0, 6.0, 8.0, 12.0, 10.0, 14.0]
