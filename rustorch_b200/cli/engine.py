@@ -84,11 +84,17 @@ class ModelLoader:
             hf = _json.load(open(cfg_path)) if os.path.exists(cfg_path) else {}
             if str(hf.get("model_type", "")).lower() in ("llama", "mistral") or any("Llama" in a or "Mistral" in a for a in hf.get("architectures", [])):
                 rt = LlamaRuntime.from_hf(path, device)
-                spm = tokenizer_path or (os.path.join(path, "tokenizer.model") if os.path.exists(os.path.join(path, "tokenizer.model")) else None)
-                tok = load_tokenizer(spm, vocab_size=rt.cfg.vocab_size)
+                tok = load_tokenizer(tokenizer_path or path, vocab_size=rt.cfg.vocab_size)
                 meta = ModelMetadata(os.path.basename(os.path.normpath(path)), "huggingface", rt.cfg.vocab_size, rt.cfg.n_embd, rt.cfg.n_layer,
                                      rt.cfg.n_head, rt.cfg.context_length)
                 return rt, tok, meta
+            if str(hf.get("model_type", "")).lower() == "gpt2" or any("GPT2" in a for a in hf.get("architectures", [])):
+                from ..models.gpt import GPT
+                model = GPT.from_hf(path)
+                tok = load_tokenizer(tokenizer_path or path, vocab_size=model.cfg.vocab_size)
+                meta = ModelMetadata(os.path.basename(os.path.normpath(path)), "huggingface", model.cfg.vocab_size, model.cfg.n_embd,
+                                     model.cfg.n_layer, model.cfg.n_head, model.cfg.n_positions)
+                return _GPTAdapter(model, device), tok, meta
         if fmt in ("safetensors", "mlx", "rustorch", "torch", "pth", "huggingface", "json"):
             from ..models.gpt import GPT, GPTConfig
             from ..models.high_level import load_state_dict_file

@@ -5,6 +5,9 @@
   merged best-score-first while the merged piece exists in the vocabulary, unknown characters fall back to
   ``<0xXX>`` byte tokens.
 * ``SentencePieceTokenizer``: a ``.model`` file through the ``sentencepiece`` package.
+* ``BPETokenizer``: byte-level BPE from ``vocab.json`` + ``merges.txt`` (the GPT-2 family's files in a Hugging Face
+  directory): text is cut by the GPT-2 pre-tokenisation pattern, every piece's UTF-8 bytes are mapped to printable
+  characters and merged in the order of the merge table.
 * ``ByteTokenizer``: 256 byte tokens + BOS/EOS, for models without a vocabulary (and for tests).
 """
 from __future__ import annotations
@@ -129,6 +132,89 @@ class GGUFTokenizer(Tokenizer):
         return s[1:] if self.add_space_prefix and s.startswith(" ") else s
 
 
+def _byte_alphabet() -> Dict[int, str]:
+    """The byte -> printable character table of byte-level BPE: printable Latin-1 bytes stand for themselves, the rest
+    are moved to code points from 256 upwards."""
+    keep = list(range(ord("!"), ord("~") + 1)) + list(range(0xA1, 0xAD)) + list(range(0xAE, 0x100))
+    table, extra = {}, 0
+    for b in range(256):
+        if b in keep:
+            table[b] = chr(b)
+        else:
+            table[b] = chr(256 + extra)
+            extra += 1
+    return table
+
+
+class BPETokenizer(Tokenizer):
+    _PATTERN = r"""'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"""
+
+    def __init__(self, vocab: Dict[str, int], merges: Sequence[Sequence[str]], eos_token: str = "<|endoftext|>"):
+        import regex
+        self.vocab = dict(vocab)
+        self.inverse = {i: t for t, i in self.vocab.items()}
+        self.rank = {tuple(m): r for r, m in enumerate(merges)}
+        self.to_char = _byte_alphabet()
+        self.to_byte = {c: b for b, c in self.to_char.items()}
+        self._split = regex.compile(self._PATTERN)
+        self._cache: Dict[str, List[str]] = {}
+        self.eos_id = self.vocab.get(eos_token)
+        self.bos_id = None                                   # the GPT-2 family starts a text without a marker
+
+    @classmethod
+    def from_files(cls, vocab_path: str, merges_path: str) -> "BPETokenizer":
+        import json
+        with open(vocab_path, encoding="utf-8") as f:
+            vocab = json.load(f)
+        with open(merges_path, encoding="utf-8") as f:
+            merges = [tuple(line.split()) for line in f.read().split("\n") if line and not line.startswith("#version") and len(line.split()) == 2]
+        return cls(vocab, merges)
+
+    @property
+    def vocab_size(self):
+        return len(self.vocab)
+
+    def _merge(self, word: str) -> List[str]:
+        hit = self._cache.get(word)
+        if hit is not None:
+            return hit
+        parts = list(word)
+        while len(parts) > 1:
+            best, at = None, -1
+            for i in range(len(parts) - 1):
+                r = self.rank.get((parts[i], parts[i + 1]))
+                if r is not None and (best is None or r < best):
+                    best, at = r, i
+            if best is None:
+                break
+            a, b = parts[at], parts[at + 1]
+            out, i = [], 0
+            while i < len(parts):                            # merge every occurrence of the best pair, left to right
+                if i < len(parts) - 1 and parts[i] == a and parts[i + 1] == b:
+                    out.append(a + b)
+                    i += 2
+                else:
+                    out.append(parts[i])
+                    i += 1
+            parts = out
+        self._cache[word] = parts
+        return parts
+
+    def encode(self, text, add_bos=True):
+        ids: List[int] = []
+        for piece in self._split.findall(text):
+            word = "".join(self.to_char[b] for b in piece.encode("utf-8"))
+            for tok in self._merge(word):
+                if tok not in self.vocab:
+                    raise ValueError(f"token {tok!r} is not in the vocabulary: vocab.json and merges.txt do not belong together")
+                ids.append(self.vocab[tok])
+        return ids
+
+    def decode(self, ids):
+        chars = "".join(self.inverse.get(int(i), "") for i in ids)
+        return bytes(self.to_byte[c] for c in chars if c in self.to_byte).decode("utf-8", errors="replace")
+
+
 class SentencePieceTokenizer(Tokenizer):
     def __init__(self, path: str):
         import sentencepiece as spm
@@ -148,6 +234,18 @@ class SentencePieceTokenizer(Tokenizer):
 
 
 def load_tokenizer(path: Optional[str] = None, gguf_file=None, vocab_size: int = 258) -> Tokenizer:
+    """``path``: a SentencePiece ``.model`` file, a ``vocab.json`` (its ``merges.txt`` beside it) or a directory that
+    holds one of the two."""
+    import os
+    if path and os.path.isdir(path):
+        for cand in ("tokenizer.model", "vocab.json"):
+            if os.path.exists(os.path.join(path, cand)):
+                path = os.path.join(path, cand)
+                break
+        else:
+            path = None
+    if path and path.endswith("vocab.json"):
+        return BPETokenizer.from_files(path, os.path.join(os.path.dirname(path), "merges.txt"))
     if path and path.endswith(".model"):
         return SentencePieceTokenizer(path)
     if gguf_file is not None and "tokenizer.ggml.tokens" in gguf_file.metadata:

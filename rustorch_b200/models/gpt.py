@@ -117,6 +117,39 @@ class GPT(nn.Module):
             for w in (b.w_qkv, b.w_proj, b.w_fc, b.w_fc2):
                 normal_(w)
 
+    @classmethod
+    def from_hf(cls, directory: str, device=None, dtype=torch.float32) -> "GPT":
+        """A model with the weights of a Hugging Face GPT-2 checkpoint directory (``config.json`` + safetensors).  GPT-2
+        stores its projections as ``Conv1D`` weights ``[in, out]``; they are transposed into the ``[out, in]`` layout of
+        this model.  The embedding is padded with zero rows to the model's vocabulary multiple and tied to the head, as
+        GPT-2's is."""
+        from ..formats.safetensors import HuggingFaceCheckpoint
+        with HuggingFaceCheckpoint(directory) as ck:
+            c = ck.config
+            if c.get("activation_function", "gelu_new") not in ("gelu_new", "gelu_pytorch_tanh"):
+                raise ValueError(f"{directory}: activation {c['activation_function']!r}; this model computes the tanh form of GELU")
+            pre = "transformer." if any(k.startswith("transformer.") for k in ck.keys()) else ""
+            cfg = GPTConfig(vocab_size=int(c["vocab_size"]), n_positions=int(c.get("n_positions", 1024)), n_embd=int(c["n_embd"]),
+                            n_layer=int(c["n_layer"]), n_head=int(c["n_head"]), dropout=float(c.get("resid_pdrop", 0.1)),
+                            layer_norm_eps=float(c.get("layer_norm_epsilon", 1e-5)), tie_weights=True)
+            model = cls(cfg, device=device, dtype=dtype)
+            get = lambda n: ck.get(pre + n).to(device=device, dtype=dtype)      # noqa: E731
+            with torch.no_grad():
+                model.wte.zero_()
+                model.wte[: cfg.vocab_size].copy_(get("wte.weight"))
+                model.wpe.copy_(get("wpe.weight"))
+                model.lnf_w.copy_(get("ln_f.weight"))
+                model.lnf_b.copy_(get("ln_f.bias"))
+                for i, b in enumerate(model.blocks):
+                    h = f"h.{i}."
+                    for ours, theirs in (("ln1", "ln_1"), ("ln2", "ln_2")):
+                        getattr(b, ours + "_w").copy_(get(h + theirs + ".weight"))
+                        getattr(b, ours + "_b").copy_(get(h + theirs + ".bias"))
+                    for ours, theirs in (("qkv", "attn.c_attn"), ("proj", "attn.c_proj"), ("fc", "mlp.c_fc"), ("fc2", "mlp.c_proj")):
+                        getattr(b, "w_" + ours).copy_(get(h + theirs + ".weight").t())
+                        getattr(b, "b_" + ours).copy_(get(h + theirs + ".bias"))
+        return model
+
     def num_parameters(self, count_padding: bool = False) -> int:
         n = sum(p.numel() for p in self.parameters())
         if not count_padding:

@@ -244,6 +244,37 @@ class LlamaModel(nn.Module):
     def num_parameters(self) -> int:
         return sum(p.numel() for p in self.parameters())
 
+    @classmethod
+    def from_hf(cls, directory: str, device=None, dtype=None) -> "LlamaModel":
+        """A single-rank model with the weights of a Hugging Face Llama checkpoint directory (``config.json`` +
+        safetensors, sharded or not), e.g. to fine-tune it.  Same head layout (rotate-half RoPE) as those checkpoints, so
+        the tensors are copied as they are: q | k | v stacked into ``wqkv``, gate | up into ``w_gate_up``."""
+        from ..formats.safetensors import HuggingFaceCheckpoint
+        with HuggingFaceCheckpoint(directory) as ck:
+            c = ck.config
+            if c.get("rope_scaling") or any(k.endswith(".bias") for k in ck.keys()):
+                raise ValueError(f"{directory}: rope scaling and projection biases are outside this model")
+            n_head = int(c["num_attention_heads"])
+            cfg = LlamaTrainConfig(vocab_size=int(c["vocab_size"]), n_layer=int(c["num_hidden_layers"]), n_embd=int(c["hidden_size"]),
+                                   n_head=n_head, n_head_kv=int(c.get("num_key_value_heads") or n_head), n_ff=int(c["intermediate_size"]),
+                                   max_seq_len=int(c.get("max_position_embeddings", 4096)), rope_theta=float(c.get("rope_theta", 10000.0)),
+                                   rms_eps=float(c.get("rms_norm_eps", 1e-5)))
+            model = cls(cfg, device=device, dtype=dtype)
+            get = lambda n: ck.get(n).to(device=device, dtype=dtype or torch.float32)      # noqa: E731
+            with torch.no_grad():
+                model.tok_emb.copy_(get("model.embed_tokens.weight"))
+                model.out_norm.copy_(get("model.norm.weight"))
+                model.lm_head.copy_(get("lm_head.weight" if "lm_head.weight" in ck else "model.embed_tokens.weight"))
+                for i, b in enumerate(model.blocks):
+                    p = f"model.layers.{i}."
+                    b.wqkv.copy_(torch.cat([get(p + f"self_attn.{n}_proj.weight") for n in ("q", "k", "v")], 0))
+                    b.wo.copy_(get(p + "self_attn.o_proj.weight"))
+                    b.w_gate_up.copy_(torch.cat([get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")], 0))
+                    b.w_down.copy_(get(p + "mlp.down_proj.weight"))
+                    b.attn_norm.copy_(get(p + "input_layernorm.weight"))
+                    b.ffn_norm.copy_(get(p + "post_attention_layernorm.weight"))
+        return model
+
     def forward(self, idx: torch.Tensor, targets: Optional[torch.Tensor] = None):
         B, T = idx.shape
         c = self.cfg

@@ -191,3 +191,84 @@ def test_cli_runs_a_hugging_face_llama_directory(tmp_path):
     buf2 = []
     cli.main(["--model", d, "--backend", "cpu"], read=lambda _: next(lines), out=buf2.append)
     assert "model: hf-llama" in "".join(buf2)
+
+
+def _tiny_bpe_files(directory):
+    """vocab.json + merges.txt of a byte-level BPE trained on a few sentences (60 merges)."""
+    import collections
+    import regex
+    from rustorch_b200.cli.tokenizer import BPETokenizer, _byte_alphabet
+    text = "Hello world! The quick brown fox jumps over the lazy dog. It's 2024, isn't it?  Naïve café — 東京 \n\n tabs\tand   spaces. " * 3
+    tab = _byte_alphabet()
+    words = collections.Counter("".join(tab[b] for b in w.encode()) for w in regex.compile(BPETokenizer._PATTERN).findall(text))
+    vocab = {tab[b]: b for b in range(256)}
+    vocab = {c: i for i, c in enumerate(tab[b] for b in range(256))}
+    merges, seqs = [], {w: list(w) for w in words}
+    for _ in range(60):
+        pairs = collections.Counter()
+        for w, s in seqs.items():
+            for a, b in zip(s, s[1:]):
+                pairs[(a, b)] += words[w]
+        (a, b), _n = pairs.most_common(1)[0]
+        merges.append((a, b))
+        vocab[a + b] = len(vocab)
+        for w, s in seqs.items():
+            out, i = [], 0
+            while i < len(s):
+                if i < len(s) - 1 and s[i] == a and s[i + 1] == b:
+                    out.append(a + b)
+                    i += 2
+                else:
+                    out.append(s[i])
+                    i += 1
+            seqs[w] = out
+    vocab["<|endoftext|>"] = len(vocab)
+    os.makedirs(directory, exist_ok=True)
+    json.dump(vocab, open(os.path.join(directory, "vocab.json"), "w", encoding="utf-8"), ensure_ascii=False)
+    open(os.path.join(directory, "merges.txt"), "w", encoding="utf-8").write("#version: 0.2\n" + "\n".join(" ".join(m) for m in merges) + "\n")
+    return text, len(vocab)
+
+
+def test_bpe_tokenizer_matches_transformers(tmp_path):
+    tf = pytest.importorskip("transformers")
+    from rustorch_b200.cli.tokenizer import BPETokenizer, load_tokenizer
+    d = str(tmp_path / "tok")
+    text, n = _tiny_bpe_files(d)
+    ours = load_tokenizer(d)
+    assert isinstance(ours, BPETokenizer) and ours.vocab_size == n and ours.eos_id == n - 1 and ours.bos_id is None
+    hf = tf.GPT2Tokenizer(os.path.join(d, "vocab.json"), os.path.join(d, "merges.txt"))
+    for t in (text, "isn't it lazy?", "  leading and trailing  ", "unseen ZZZ qqq 東 ☃", ""):
+        ids = ours.encode(t)
+        assert ids == hf.encode(t) and ours.decode(ids) == t
+    assert len(ours.encode("the lazy dog")) < len("the lazy dog")        # merges really apply
+    bad = dict(ours.vocab)
+    del bad[next(k for k in bad if len(k) > 1 and k.startswith("Ġ"))]
+    with pytest.raises(ValueError, match="not in the vocabulary"):
+        BPETokenizer(bad, list(ours.rank)).encode(text)
+
+
+def test_cli_runs_a_hugging_face_gpt2_directory(tmp_path):
+    """``config.json`` + safetensors + vocab.json / merges.txt of a GPT-2 checkpoint: weights load into the GPT model
+    (logits equal ``transformers``'), the BPE tokenizer is picked up, one prompt is answered."""
+    tf = pytest.importorskip("transformers")
+    from rustorch_b200.models.gpt import GPT
+    d = str(tmp_path / "gpt2-tiny")
+    _, n = _tiny_bpe_files(d)
+    torch.manual_seed(0)
+    hc = tf.GPT2Config(vocab_size=n, n_positions=64, n_embd=64, n_layer=2, n_head=4, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    ref = tf.GPT2LMHeadModel(hc).eval()
+    with torch.no_grad():
+        for p in ref.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)                     # non-trivial biases and norm parameters
+    ref.save_pretrained(d, safe_serialization=True)
+    m = GPT.from_hf(d).eval()
+    idx = torch.randint(0, n, (2, 16))
+    with torch.no_grad():
+        want = ref(idx).logits
+    got = m.forward_reference(idx)
+    assert m.cfg.tie_weights and got.shape == want.shape and torch.allclose(got, want, atol=1e-5)
+    assert float(m.wte[n:].abs().sum()) == 0.0                         # padding rows of the vocabulary stay zero
+    buf = []
+    assert cli.main(["--model", d, "--backend", "cpu", "--max-tokens", "5", "--temperature", "0", "--prompt", "The quick brown"], out=buf.append) == 0
+    assert "Assistant: " in "".join(buf) and "error" not in "".join(buf)

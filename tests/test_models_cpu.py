@@ -141,3 +141,31 @@ def test_metrics_summary():
     assert m.loss == 0.3 and M.Metrics.new().accuracy == 0.0 and M.Metrics.with_values(1, 0.9, 0.8, 0.85, 0.1).recall == 0.8
     ids = M.Metrics.from_predictions(torch.tensor([0, 2, 2]), torch.tensor([0, 1, 2]), num_classes=3)
     assert ids.accuracy == pytest.approx(2 / 3) and ids.precision == pytest.approx((1 + 0 + 0.5) / 3) and ids.recall == pytest.approx((1 + 0 + 1) / 3)
+
+
+def test_llama_training_model_matches_transformers(tmp_path):
+    """``LlamaModel.from_hf`` copies a Hugging Face checkpoint; logits, loss and gradients equal ``transformers``' Llama
+    (grouped-query attention, rotate-half RoPE, SwiGLU, RMSNorm) in fp32 on CPU."""
+    tf = pytest.importorskip("transformers")
+    from rustorch_b200.models.llama import LlamaModel
+    torch.manual_seed(0)
+    hc = tf.LlamaConfig(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, max_position_embeddings=64, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False)
+    ref = tf.LlamaForCausalLM(hc)
+    d = str(tmp_path / "hf")
+    ref.save_pretrained(d, safe_serialization=True)
+    m = LlamaModel.from_hf(d)
+    assert m.cfg.n_head_kv == 2 and m.num_parameters() == sum(p.numel() for p in ref.parameters())
+    idx, tgt = torch.randint(0, 96, (2, 12)), torch.randint(0, 96, (2, 12))
+    logits, loss = m(idx, tgt)
+    want = ref(idx).logits.view(-1, 96)
+    want_loss = torch.nn.functional.cross_entropy(want, tgt.view(-1))
+    assert torch.allclose(logits, want, atol=1e-5) and float(loss.detach()) == pytest.approx(float(want_loss.detach()), rel=1e-6)
+    loss.backward()
+    want_loss.backward()
+    l0 = ref.model.layers[0]
+    qkv = torch.cat([l0.self_attn.q_proj.weight.grad, l0.self_attn.k_proj.weight.grad, l0.self_attn.v_proj.weight.grad], 0)
+    gu = torch.cat([l0.mlp.gate_proj.weight.grad, l0.mlp.up_proj.weight.grad], 0)
+    assert torch.allclose(m.blocks[0].wqkv.grad, qkv, atol=1e-6) and torch.allclose(m.blocks[0].w_gate_up.grad, gu, atol=1e-6)
+    assert torch.allclose(m.tok_emb.grad, ref.model.embed_tokens.weight.grad, atol=1e-6)
+    assert torch.allclose(m.blocks[1].attn_norm.grad, ref.model.layers[1].input_layernorm.weight.grad, atol=1e-6)
