@@ -163,6 +163,48 @@ class BERT(nn.Module):
         h = self.encoder(self.embeddings(input_ids, token_type_ids), src_key_padding_mask=attention_mask)
         return h, torch.tanh(self.pooler(h[:, 0]))
 
+    @classmethod
+    def from_hf(cls, directory: str, num_labels: int = 2) -> "BERT":
+        """The encoder, embeddings and pooler of a Hugging Face BERT checkpoint directory (``config.json`` +
+        safetensors).  Query / key / value projections are stacked into the attention's input projection; the
+        masked-LM and classification heads keep their fresh initialisation unless the checkpoint has a decoder bias
+        and tied decoder (``cls.predictions``), which only the full pre-training head has."""
+        from ..formats.safetensors import HuggingFaceCheckpoint
+        with HuggingFaceCheckpoint(directory) as ck:
+            c = ck.config
+            if c.get("hidden_act", "gelu") != "gelu" or c.get("position_embedding_type", "absolute") != "absolute":
+                raise ValueError(f"{directory}: only absolute positions and the erf form of GELU are implemented")
+            cfg = BERTConfig(vocab_size=int(c["vocab_size"]), hidden_size=int(c["hidden_size"]), num_hidden_layers=int(c["num_hidden_layers"]),
+                             num_attention_heads=int(c["num_attention_heads"]), intermediate_size=int(c["intermediate_size"]),
+                             max_position_embeddings=int(c.get("max_position_embeddings", 512)), type_vocab_size=int(c.get("type_vocab_size", 2)),
+                             hidden_dropout_prob=float(c.get("hidden_dropout_prob", 0.1)), layer_norm_eps=float(c.get("layer_norm_eps", 1e-12)))
+            model = cls(cfg, num_labels)
+            pre = "bert." if any(k.startswith("bert.") for k in ck.keys()) else ""
+            get = lambda n: ck.get(pre + n).float()      # noqa: E731
+
+            def lin(dst, src):
+                dst.weight.copy_(get(src + ".weight"))
+                dst.bias.copy_(get(src + ".bias"))
+            with torch.no_grad():
+                e = model.embeddings
+                e.word.weight.copy_(get("embeddings.word_embeddings.weight"))
+                e.position.weight.copy_(get("embeddings.position_embeddings.weight"))
+                e.token_type.weight.copy_(get("embeddings.token_type_embeddings.weight"))
+                lin(e.norm, "embeddings.LayerNorm")
+                for i, layer in enumerate(model.encoder.layers):
+                    p = f"encoder.layer.{i}."
+                    att = layer.self_attn
+                    att.in_proj.weight.copy_(torch.cat([get(p + f"attention.self.{n}.weight") for n in ("query", "key", "value")], 0))
+                    att.in_proj.bias.copy_(torch.cat([get(p + f"attention.self.{n}.bias") for n in ("query", "key", "value")], 0))
+                    lin(att.out_proj, p + "attention.output.dense")
+                    lin(layer.norm1, p + "attention.output.LayerNorm")
+                    lin(layer.linear1, p + "intermediate.dense")
+                    lin(layer.linear2, p + "output.dense")
+                    lin(layer.norm2, p + "output.LayerNorm")
+                if pre + "pooler.dense.weight" in ck:
+                    lin(model.pooler, "pooler.dense")
+        return model
+
     def masked_lm_logits(self, input_ids, **kw) -> torch.Tensor:
         return self.mlm_head(self.forward(input_ids, **kw)[0])
 

@@ -169,3 +169,32 @@ def test_llama_training_model_matches_transformers(tmp_path):
     assert torch.allclose(m.blocks[0].wqkv.grad, qkv, atol=1e-6) and torch.allclose(m.blocks[0].w_gate_up.grad, gu, atol=1e-6)
     assert torch.allclose(m.tok_emb.grad, ref.model.embed_tokens.weight.grad, atol=1e-6)
     assert torch.allclose(m.blocks[1].attn_norm.grad, ref.model.layers[1].input_layernorm.weight.grad, atol=1e-6)
+
+
+def test_bert_matches_transformers(tmp_path):
+    """``BERT.from_hf``: embeddings, post-norm encoder (erf GELU), pooler and the padding mask agree with ``transformers``'
+    BertModel."""
+    tf = pytest.importorskip("transformers")
+    torch.manual_seed(0)
+    hc = tf.BertConfig(vocab_size=120, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
+                       max_position_embeddings=40, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    ref = tf.BertModel(hc).eval()
+    with torch.no_grad():
+        for p in ref.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = str(tmp_path / "bert")
+    ref.save_pretrained(d, safe_serialization=True)
+    m = M.BERT.from_hf(d).eval()
+    ids, tt = torch.randint(0, 120, (2, 10)), torch.randint(0, 2, (2, 10))
+    mask = torch.ones(2, 10, dtype=torch.long)
+    mask[1, 7:] = 0
+    with torch.no_grad():
+        want = ref(ids, token_type_ids=tt)
+        seq, pooled = m(ids, tt)
+        assert torch.allclose(seq, want.last_hidden_state, atol=2e-5) and torch.allclose(pooled, want.pooler_output, atol=2e-5)
+        wm = ref(ids, token_type_ids=tt, attention_mask=mask)
+        sm, pm = m(ids, tt, attention_mask=mask)
+        assert torch.allclose(sm[0], wm.last_hidden_state[0], atol=2e-5) and torch.allclose(sm[1, :7], wm.last_hidden_state[1, :7], atol=2e-5)
+        assert torch.allclose(pm, wm.pooler_output, atol=2e-5) and not torch.allclose(sm[1, :7], seq[1, :7], atol=1e-4)
+    assert m.masked_lm_logits(ids).shape == (2, 10, 120) and m.classify(ids).shape == (2, 2)
