@@ -27,6 +27,24 @@ def interleave_rope_rows(w: torch.Tensor, n_head: int) -> torch.Tensor:
     return w.reshape(n_head, 2, d // 2, *w.shape[1:]).transpose(1, 2).reshape(w.shape)
 
 
+def sentencepiece_metadata(model_path: str) -> Dict[str, object]:
+    """``tokenizer.ggml.*`` entries (pieces, scores, piece types, special ids) of a SentencePiece ``.model`` file, so that the
+    written GGUF file carries its own tokenizer."""
+    import sentencepiece as spm
+    sp = spm.SentencePieceProcessor(model_file=model_path)
+    n = sp.get_piece_size()
+
+    def kind(i: int) -> int:                               # GGUF token types: 1 normal, 2 unknown, 3 control, 5 unused, 6 byte
+        return 2 if sp.is_unknown(i) else 3 if sp.is_control(i) else 5 if sp.is_unused(i) else 6 if sp.is_byte(i) else 1
+    md: Dict[str, object] = {"tokenizer.ggml.model": "llama", "tokenizer.ggml.tokens": [sp.id_to_piece(i) for i in range(n)],
+                             "tokenizer.ggml.scores": [float(sp.get_score(i)) for i in range(n)],
+                             "tokenizer.ggml.token_type": [kind(i) for i in range(n)]}
+    for key, val in (("bos_token_id", sp.bos_id()), ("eos_token_id", sp.eos_id()), ("unknown_token_id", sp.unk_id()), ("padding_token_id", sp.pad_id())):
+        if val is not None and val >= 0:
+            md[f"tokenizer.ggml.{key}"] = int(val)
+    return md
+
+
 def hf_to_gguf(directory: str, path: str, ggml_type: gguf.GGMLType = gguf.GGMLType.Q8_0, name: Optional[str] = None) -> Dict[str, int]:
     """Writes ``path`` from the checkpoint in ``directory``: matrices as ``ggml_type`` (F32, F16, Q8_0 or Q4_0), norms and,
     for quantised types, the embedding table as F32 / F16.  Returns ``{"tensors": n, "bytes": size}``."""
@@ -62,5 +80,8 @@ def hf_to_gguf(directory: str, path: str, ggml_type: gguf.GGMLType = gguf.GGMLTy
                 elif dst == "attn_k":
                     w = interleave_rope_rows(w, n_kv)
                 tensors[f"blk.{i}.{dst}.weight"] = (w, gguf.GGMLType.F32 if dst.endswith("norm") else ty)
+    spm_path = os.path.join(directory, "tokenizer.model")
+    if os.path.exists(spm_path):
+        md.update(sentencepiece_metadata(spm_path))
     gguf.write_gguf(path, md, tensors)
-    return {"tensors": len(tensors), "bytes": os.path.getsize(path)}
+    return {"tensors": len(tensors), "bytes": os.path.getsize(path), "tokenizer": os.path.exists(spm_path)}

@@ -210,3 +210,36 @@ def test_hf_to_gguf_keeps_the_logits(tmp_path):
         assert float((want - got).abs().max()) < tol * float(want.abs().max()), ty
     w = torch.arange(16.0).view(8, 2)                                # two heads of four rows: halves (0, 1 | 2, 3) -> pairs (0, 2, 1, 3)
     assert llm.interleave_rope_rows(w, 2)[:, 0].tolist() == [0.0, 4.0, 2.0, 6.0, 8.0, 12.0, 10.0, 14.0]
+
+
+def test_hf_to_gguf_embeds_the_sentencepiece_tokenizer(tmp_path):
+    """With a ``tokenizer.model`` beside the weights the written GGUF file carries the vocabulary, and the CLI's GGUF
+    tokenizer then splits text like SentencePiece does."""
+    tf = pytest.importorskip("transformers")
+    spm = pytest.importorskip("sentencepiece")
+    from rustorch_b200.cli.tokenizer import GGUFTokenizer
+    d = str(tmp_path / "hf")
+    os.makedirs(d)
+    corpus = str(tmp_path / "corpus.txt")
+    words = "the quick brown fox jumps over the lazy dog and runs far away from here with great speed every single day".split()
+    g = torch.Generator().manual_seed(0)
+    with open(corpus, "w") as f:
+        for _ in range(400):
+            f.write(" ".join(words[int(i)] for i in torch.randint(0, len(words), (8,), generator=g)) + "\n")
+    spm.SentencePieceTrainer.train(input=corpus, model_prefix=os.path.join(d, "tokenizer"), vocab_size=340, model_type="bpe", byte_fallback=True,
+                                   character_coverage=1.0, bos_id=1, eos_id=2, unk_id=0, minloglevel=2)
+    sp = spm.SentencePieceProcessor(model_file=os.path.join(d, "tokenizer.model"))
+    n = sp.get_piece_size()
+    torch.manual_seed(0)
+    hc = tf.LlamaConfig(vocab_size=n, hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2,
+                        max_position_embeddings=64)
+    tf.LlamaForCausalLM(hc).save_pretrained(d, safe_serialization=True)
+    out = str(tmp_path / "m.gguf")
+    info = llm.hf_to_gguf(d, out, gguf.GGMLType.Q8_0)
+    assert info["tokenizer"]
+    with gguf.GGUFFile(out) as f:
+        assert len(f.metadata["tokenizer.ggml.tokens"]) == n and f.metadata["tokenizer.ggml.bos_token_id"] == 1
+        tok = GGUFTokenizer.from_gguf(f)
+    for text in ("the quick brown fox", "lazy dog runs far away", "zebra!"):
+        ids = tok.encode(text, add_bos=False)
+        assert ids == sp.encode(text) and tok.decode(ids).strip() == text
