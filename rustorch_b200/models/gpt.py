@@ -150,6 +150,33 @@ class GPT(nn.Module):
                         getattr(b, "b_" + ours).copy_(get(h + theirs + ".bias"))
         return model
 
+    def save_hf(self, directory: str) -> None:
+        """Writes a Hugging Face GPT-2 checkpoint directory (``config.json`` + ``model.safetensors``): projections go back to
+        the ``Conv1D`` layout ``[in, out]``, the vocabulary padding is dropped.  An untied head has no place in that
+        format, so the model must tie ``lm_head`` to ``wte``."""
+        import json
+        import os
+        from ..formats.safetensors import save_safetensors
+        if not self.cfg.tie_weights:
+            raise ValueError("the GPT-2 checkpoint format ties the head to the embedding; this model does not")
+        c = self.cfg
+        cast = lambda t: t.detach().float().cpu().contiguous()      # noqa: E731
+        sd = {"transformer.wte.weight": cast(self.wte[: c.vocab_size]), "transformer.wpe.weight": cast(self.wpe),
+              "transformer.ln_f.weight": cast(self.lnf_w), "transformer.ln_f.bias": cast(self.lnf_b)}
+        for i, b in enumerate(self.blocks):
+            h = f"transformer.h.{i}."
+            for ours, theirs in (("ln1", "ln_1"), ("ln2", "ln_2")):
+                sd[h + theirs + ".weight"], sd[h + theirs + ".bias"] = cast(getattr(b, ours + "_w")), cast(getattr(b, ours + "_b"))
+            for ours, theirs in (("qkv", "attn.c_attn"), ("proj", "attn.c_proj"), ("fc", "mlp.c_fc"), ("fc2", "mlp.c_proj")):
+                sd[h + theirs + ".weight"], sd[h + theirs + ".bias"] = cast(getattr(b, "w_" + ours).t()), cast(getattr(b, "b_" + ours))
+        os.makedirs(directory, exist_ok=True)
+        save_safetensors(sd, os.path.join(directory, "model.safetensors"), {"format": "pt"})
+        with open(os.path.join(directory, "config.json"), "w") as f:
+            json.dump({"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2", "vocab_size": c.vocab_size, "n_positions": c.n_positions,
+                       "n_embd": c.n_embd, "n_layer": c.n_layer, "n_head": c.n_head, "activation_function": "gelu_new",
+                       "resid_pdrop": c.dropout, "embd_pdrop": c.dropout, "attn_pdrop": c.dropout, "layer_norm_epsilon": c.layer_norm_eps,
+                       "tie_word_embeddings": True}, f, indent=2)
+
     def num_parameters(self, count_padding: bool = False) -> int:
         n = sum(p.numel() for p in self.parameters())
         if not count_padding:

@@ -302,6 +302,35 @@ class LlamaModel(nn.Module):
         loss = F.cross_entropy(logits.float(), targets.reshape(-1)[lo:hi]) / self.world
         return logits, loss
 
+    def save_hf(self, directory: str, dtype: torch.dtype = torch.float32) -> None:
+        """Writes a Hugging Face Llama checkpoint directory (``config.json`` + ``model.safetensors``) from a single-rank
+        model: the inverse of :meth:`from_hf`, readable by ``transformers`` and by ``llm.hf_to_gguf``."""
+        import json
+        import os
+        from ..formats.safetensors import save_safetensors
+        if self.world > 1:
+            raise ValueError("gather a tensor-parallel model to one rank before saving it")
+        c = self.cfg
+        H, Hkv, D = c.n_head, c.n_head_kv, c.head_dim
+        cast = lambda t: t.detach().to("cpu", dtype).contiguous()      # noqa: E731
+        sd = {"model.embed_tokens.weight": cast(self.tok_emb), "model.norm.weight": cast(self.out_norm), "lm_head.weight": cast(self.lm_head)}
+        for i, b in enumerate(self.blocks):
+            p = f"model.layers.{i}."
+            q, k, v = b.wqkv.split([H * D, Hkv * D, Hkv * D], 0)
+            gate, up = b.w_gate_up.split([c.n_ff, c.n_ff], 0)
+            sd.update({p + "self_attn.q_proj.weight": cast(q), p + "self_attn.k_proj.weight": cast(k), p + "self_attn.v_proj.weight": cast(v),
+                       p + "self_attn.o_proj.weight": cast(b.wo), p + "mlp.gate_proj.weight": cast(gate), p + "mlp.up_proj.weight": cast(up),
+                       p + "mlp.down_proj.weight": cast(b.w_down), p + "input_layernorm.weight": cast(b.attn_norm),
+                       p + "post_attention_layernorm.weight": cast(b.ffn_norm)})
+        os.makedirs(directory, exist_ok=True)
+        save_safetensors(sd, os.path.join(directory, "model.safetensors"), {"format": "pt"})
+        name = {torch.float32: "float32", torch.bfloat16: "bfloat16", torch.float16: "float16"}[dtype]
+        with open(os.path.join(directory, "config.json"), "w") as f:
+            json.dump({"architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": c.vocab_size, "hidden_size": c.n_embd,
+                       "intermediate_size": c.n_ff, "num_hidden_layers": c.n_layer, "num_attention_heads": H, "num_key_value_heads": Hkv,
+                       "hidden_act": "silu", "max_position_embeddings": c.max_seq_len, "rms_norm_eps": c.rms_eps, "rope_theta": c.rope_theta,
+                       "tie_word_embeddings": False, "attention_bias": False, "mlp_bias": False, "torch_dtype": name}, f, indent=2)
+
     def replicated_parameters(self):
         """Parameters every rank holds in full (embeddings, head, norm weights): their gradients are partial sums
         over this rank's tokens."""

@@ -198,3 +198,38 @@ def test_bert_matches_transformers(tmp_path):
         assert torch.allclose(sm[0], wm.last_hidden_state[0], atol=2e-5) and torch.allclose(sm[1, :7], wm.last_hidden_state[1, :7], atol=2e-5)
         assert torch.allclose(pm, wm.pooler_output, atol=2e-5) and not torch.allclose(sm[1, :7], seq[1, :7], atol=1e-4)
     assert m.masked_lm_logits(ids).shape == (2, 10, 120) and m.classify(ids).shape == (2, 2)
+
+
+def test_save_hf_is_read_back_by_transformers(tmp_path):
+    """Fine-tuning loop closed: a model of this package written with ``save_hf`` loads in ``transformers`` and gives the
+    same logits; ``from_hf`` of the written directory reproduces the parameters."""
+    tf = pytest.importorskip("transformers")
+    from rustorch_b200.models.gpt import GPT, GPTConfig
+    from rustorch_b200.models.llama import LlamaModel, LlamaTrainConfig
+    torch.manual_seed(0)
+    lm = LlamaModel(LlamaTrainConfig.tiny(vocab_size=96, n_embd=64, n_ff=128, max_seq_len=64))
+    with torch.no_grad():
+        for b in lm.blocks:
+            b.attn_norm.add_(torch.randn_like(b.attn_norm) * 0.1)
+    d = str(tmp_path / "llama")
+    lm.save_hf(d)
+    ref = tf.LlamaForCausalLM.from_pretrained(d).eval()
+    idx = torch.randint(0, 96, (2, 10))
+    with torch.no_grad():
+        assert torch.allclose(lm(idx)[0], ref(idx).logits.view(-1, 96), atol=1e-5)
+    back = LlamaModel.from_hf(d)
+    assert all(torch.equal(a, b) for a, b in zip(lm.parameters(), back.parameters()))
+    g = GPT(GPTConfig(vocab_size=100, n_positions=32, n_embd=64, n_layer=2, n_head=4, dropout=0.0, tie_weights=True), seed=0).eval()
+    with torch.no_grad():
+        for b in g.blocks:
+            b.b_qkv.normal_(0, 0.1)
+            b.ln2_b.normal_(0, 0.1)
+    d2 = str(tmp_path / "gpt2")
+    g.save_hf(d2)
+    ref2 = tf.GPT2LMHeadModel.from_pretrained(d2).eval()
+    ids = torch.randint(0, 100, (2, 12))
+    with torch.no_grad():
+        assert torch.allclose(g.forward_reference(ids), ref2(ids).logits, atol=1e-5)
+    assert all(torch.equal(a, b) for a, b in zip(g.parameters(), GPT.from_hf(d2).parameters()))
+    with pytest.raises(ValueError, match="ties the head"):
+        GPT(GPTConfig(vocab_size=100, n_positions=32, n_embd=64, n_layer=1, n_head=4), seed=0).save_hf(str(tmp_path / "untied"))
