@@ -6,7 +6,6 @@ from __future__ import annotations
 
 import functools
 
-import torch
 import torch.nn.functional as _F
 
 from .._interop import call_unwrapped
