@@ -51,21 +51,26 @@ def hf_to_gguf(directory: str, path: str, ggml_type: gguf.GGMLType = gguf.GGMLTy
     ty = gguf.GGMLType(ggml_type)
     with HuggingFaceCheckpoint(directory) as ck:
         c = ck.config
+        # Qwen2 files keep the half-split rotation (the "neox" RoPE of GGUF readers) and carry q / k / v biases; Llama and
+        # Mistral files are written under the "llama" architecture with re-ordered q / k rows
+        a = "qwen2" if str(c.get("model_type", "")).lower() == "qwen2" else "llama"
         try:
             n_layer, n_head = int(c["num_hidden_layers"]), int(c["num_attention_heads"])
             n_kv = int(c.get("num_key_value_heads") or n_head)
-            md = {"general.architecture": "llama", "general.name": name or os.path.basename(os.path.normpath(directory)),
-                  "llama.block_count": n_layer, "llama.embedding_length": int(c["hidden_size"]),
-                  "llama.feed_forward_length": int(c["intermediate_size"]), "llama.attention.head_count": n_head,
-                  "llama.attention.head_count_kv": n_kv, "llama.rope.freq_base": float(c.get("rope_theta", 10000.0)),
-                  "llama.attention.layer_norm_rms_epsilon": float(c.get("rms_norm_eps", 1e-5)),
-                  "llama.context_length": int(c.get("max_position_embeddings", 2048)), "llama.vocab_size": int(c["vocab_size"])}
+            md = {"general.architecture": a, "general.name": name or os.path.basename(os.path.normpath(directory)),
+                  f"{a}.block_count": n_layer, f"{a}.embedding_length": int(c["hidden_size"]),
+                  f"{a}.feed_forward_length": int(c["intermediate_size"]), f"{a}.attention.head_count": n_head,
+                  f"{a}.attention.head_count_kv": n_kv, f"{a}.rope.freq_base": float(c.get("rope_theta", 10000.0)),
+                  f"{a}.attention.layer_norm_rms_epsilon": float(c.get("rms_norm_eps", 1e-5)),
+                  f"{a}.context_length": int(c.get("max_position_embeddings", 2048)), f"{a}.vocab_size": int(c["vocab_size"])}
         except KeyError as e:
             raise ValueError(f"{directory}: config.json lacks {e.args[0]!r}") from None
-        if c.get("rope_scaling"):
-            raise ValueError(f"{directory}: rope_scaling {c['rope_scaling']} has no counterpart in the written file")
-        if any(k.endswith(".bias") for k in ck.keys()):
-            raise ValueError(f"{directory}: projections with biases are not a Llama-style decoder")
+        if c.get("rope_scaling") or c.get("use_sliding_window"):
+            raise ValueError(f"{directory}: rope scaling / sliding-window attention have no counterpart in the written file")
+        qkv_bias = {"self_attn.q_proj.bias": "attn_q.bias", "self_attn.k_proj.bias": "attn_k.bias", "self_attn.v_proj.bias": "attn_v.bias"}
+        other = [k for k in ck.keys() if k.endswith(".bias") and k.split(".", 3)[-1] not in qkv_bias]
+        if other:
+            raise ValueError(f"{directory}: biases outside the q / k / v projections ({other[:3]}) are not a decoder this format path writes")
         emb_ty = gguf.GGMLType.F16 if ty in (gguf.GGMLType.Q8_0, gguf.GGMLType.Q4_0, gguf.GGMLType.F16) else gguf.GGMLType.F32
         tensors: Dict[str, Tuple[torch.Tensor, gguf.GGMLType]] = {
             "token_embd.weight": (ck.get("model.embed_tokens.weight").float(), emb_ty),
@@ -75,11 +80,18 @@ def hf_to_gguf(directory: str, path: str, ggml_type: gguf.GGMLType = gguf.GGMLTy
         for i in range(n_layer):
             for src, dst in _LAYER.items():
                 w = ck.get(f"model.layers.{i}.{src}.weight").float()
-                if dst == "attn_q":
+                if a == "llama" and dst == "attn_q":
                     w = interleave_rope_rows(w, n_head)
-                elif dst == "attn_k":
+                elif a == "llama" and dst == "attn_k":
                     w = interleave_rope_rows(w, n_kv)
                 tensors[f"blk.{i}.{dst}.weight"] = (w, gguf.GGMLType.F32 if dst.endswith("norm") else ty)
+            for src, dst in qkv_bias.items():
+                key = f"model.layers.{i}.{src}"
+                if key in ck:
+                    b = ck.get(key).float()
+                    if a == "llama":                       # a biased Llama: the bias follows its rows
+                        b = interleave_rope_rows(b.unsqueeze(1), n_head if dst == "attn_q.bias" else n_kv).squeeze(1) if dst != "attn_v.bias" else b
+                    tensors[f"blk.{i}.{dst}"] = (b, gguf.GGMLType.F32)
     spm_path = os.path.join(directory, "tokenizer.model")
     if os.path.exists(spm_path):
         md.update(sentencepiece_metadata(spm_path))

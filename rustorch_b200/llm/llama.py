@@ -82,7 +82,7 @@ class _DecodeGraph:
 
 
 class _Layer:
-    __slots__ = ("attn_norm", "wqkv", "wo", "ffn_norm", "w_gate_up", "w_down")
+    __slots__ = ("attn_norm", "wqkv", "wo", "ffn_norm", "w_gate_up", "w_down", "qkv_bias")
 
 
 class LlamaRuntime:
@@ -121,9 +121,14 @@ class LlamaRuntime:
             new.out_features = new.scales.shape[0]
         return new
 
-    def _assemble_layer(self, wq, wk, wv, wo, wg, wu, wd, attn_norm, ffn_norm) -> _Layer:
+    def _assemble_layer(self, wq, wk, wv, wo, wg, wu, wd, attn_norm, ffn_norm, qkv_bias=None) -> _Layer:
+        """``qkv_bias``: the three bias vectors of the q / k / v projections (Qwen2-style checkpoints), or None."""
         r, w = self.tp_rank, self.tp_world
         L = _Layer()
+        L.qkv_bias = None
+        if qkv_bias is not None:
+            parts = [b.float().chunk(w)[r] if w > 1 else b.float() for b in qkv_bias]      # rows are sharded like the weights
+            L.qkv_bias = torch.cat(parts).to(self.device, self.act_dtype)
         if w > 1:
             wq, wk, wv = wq.shard_rows(r, w), wk.shard_rows(r, w), wv.shard_rows(r, w)
             wg, wu = wg.shard_rows(r, w), wu.shard_rows(r, w)
@@ -145,12 +150,18 @@ class LlamaRuntime:
             need = ["token_embd.weight", "output_norm.weight"] + [f"blk.{i}.{t}.weight" for i in range(cfg.n_layer) for t in (
                 "attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down", "attn_norm", "ffn_norm")]
             absent = [n for n in need if n not in g.tensors]
-            extra = sorted({n.split(".", 2)[-1] for n in g.tensors if n.startswith("blk.") and n.endswith(".bias")}
+            qkv_b = ("attn_q.bias", "attn_k.bias", "attn_v.bias")
+            biased = all(f"blk.0.{b}" in g.tensors for b in qkv_b)
+            extra = sorted({n.split(".", 2)[-1] for n in g.tensors if n.startswith("blk.") and n.endswith(".bias")
+                            and not (biased and n.split(".", 2)[-1] in qkv_b)}
                            | {n.split(".", 2)[-1] for n in g.tensors if "_exps." in n or "ffn_gate_inp" in n})
             if absent or extra:
                 what = (f"missing {absent[:4]}{'...' if len(absent) > 4 else ''}" if absent else "") + \
                        (("; " if absent else "") + f"tensors this runtime does not execute: {extra[:6]}" if extra else "")
-                raise ValueError(f"{path}: architecture '{mc['architecture']}' is not a bias-free Llama-style decoder ({what})")
+                raise ValueError(f"{path}: architecture '{mc['architecture']}' is not a Llama-style decoder this runtime runs ({what})")
+            # Llama-architecture files rotate adjacent pairs (their q / k rows were re-ordered by the converter); the Qwen
+            # family and the other "neox" architectures rotate the two halves of a head
+            cfg.rope_interleaved = str(mc["architecture"]).lower() not in ("qwen", "qwen2", "phi3", "gemma", "stablelm", "falcon")
             rt = cls(cfg, device, tp_rank, tp_world, tp_group)
 
             def ql(name: str) -> QuantLinear:
@@ -165,7 +176,8 @@ class LlamaRuntime:
                 rt.layers.append(rt._assemble_layer(ql(p + "attn_q.weight"), ql(p + "attn_k.weight"), ql(p + "attn_v.weight"),
                                                     ql(p + "attn_output.weight"), ql(p + "ffn_gate.weight"), ql(p + "ffn_up.weight"),
                                                     ql(p + "ffn_down.weight"), g.load_tensor(p + "attn_norm.weight"),
-                                                    g.load_tensor(p + "ffn_norm.weight")))
+                                                    g.load_tensor(p + "ffn_norm.weight"),
+                                                    [g.load_tensor(p + b) for b in qkv_b] if biased else None))
             rt.tok_emb = g.load_tensor("token_embd.weight").to(rt.device, rt.act_dtype)
             rt.out_norm = g.load_tensor("output_norm.weight").to(rt.device, rt.act_dtype)
             head_name = "output.weight" if "output.weight" in g.tensors else "token_embd.weight"
@@ -201,17 +213,23 @@ class LlamaRuntime:
                      "mlp.down_proj", "input_layernorm", "post_attention_layernorm")
             need = ["model.embed_tokens.weight", "model.norm.weight"] + [lay(i, t) for i in range(cfg.n_layer) for t in parts]
             absent = [n for n in need if n not in ck]
-            extra = sorted({n.split(".", 3)[-1] for n in ck.keys() if n.startswith("model.layers.") and n.endswith(".bias")}
+            qkv_b = ("self_attn.q_proj.bias", "self_attn.k_proj.bias", "self_attn.v_proj.bias")
+            biased = all(f"model.layers.0.{b}" in ck for b in qkv_b)
+            extra = sorted({n.split(".", 3)[-1] for n in ck.keys() if n.startswith("model.layers.") and n.endswith(".bias")
+                            and not (biased and n.split(".", 3)[-1] in qkv_b)}
                            | {n.split(".", 3)[-1] for n in ck.keys() if ".experts." in n or "block_sparse_moe" in n})
+            if c.get("use_sliding_window"):
+                raise ValueError(f"{directory}: sliding-window attention is not implemented by this runtime")
             if absent or extra:
                 what = (f"missing {absent[:4]}{'...' if len(absent) > 4 else ''}" if absent else "") + \
                        (("; " if absent else "") + f"tensors this runtime does not execute: {extra[:6]}" if extra else "")
-                raise ValueError(f"{directory}: '{arch}' is not a bias-free Llama-style decoder ({what})")
+                raise ValueError(f"{directory}: '{arch}' is not a Llama-style decoder this runtime runs ({what})")
             rt = cls(cfg, device, tp_rank, tp_world, tp_group)
             ql = lambda name: QuantLinear.from_float(ck.get(name).float(), ggml_type, rt.device)      # noqa: E731
             for i in range(cfg.n_layer):
                 rt.layers.append(rt._assemble_layer(*(ql(lay(i, t)) for t in parts[:7]), ck.get(lay(i, parts[7])).float(),
-                                                    ck.get(lay(i, parts[8])).float()))
+                                                    ck.get(lay(i, parts[8])).float(),
+                                                    [ck.get(f"model.layers.{i}.{b}") for b in qkv_b] if biased else None))
             rt.tok_emb = ck.get("model.embed_tokens.weight").to(rt.device, rt.act_dtype)
             rt.out_norm = ck.get("model.norm.weight").to(rt.device, rt.act_dtype)
             rt.lm_head = ql("lm_head.weight" if "lm_head.weight" in ck else "model.embed_tokens.weight")
@@ -321,7 +339,8 @@ class LlamaRuntime:
         for li, L in enumerate(self.layers):
             rope_done = False
             if fuse:
-                if cfg.rope_interleaved and QuantLinear.ROPE_FUSED and L.wqkv.in_features % 64 == 0 and (H + 2 * Hkv) * D % 4 == 0:
+                if (cfg.rope_interleaved and QuantLinear.ROPE_FUSED and L.qkv_bias is None and L.wqkv.in_features % 64 == 0
+                        and (H + 2 * Hkv) * D % 4 == 0):
                     # rotary embedding and the cache append ride in the projection's epilogue
                     qkv = L.wqkv.fused(x, norm_w=L.attn_norm, eps=cfg.rms_eps,
                                        rope=dict(pos=pos32, seq=seq32, cache_k=cache.k[li], cache_v=cache.v[li], n_head=H,
@@ -333,6 +352,8 @@ class LlamaRuntime:
                 if h is None:
                     h = self._rmsnorm(x, L.attn_norm)
                 qkv = L.wqkv(h)                                            # [n, (H + 2 Hkv) D]
+            if L.qkv_bias is not None:
+                qkv = qkv + L.qkv_bias.to(qkv.dtype)
             q = qkv[:, : H * D].view(n, H, D)
             k = qkv[:, H * D: (H + Hkv) * D].view(n, Hkv, D)
             v = qkv[:, (H + Hkv) * D:].view(n, Hkv, D)

@@ -243,3 +243,36 @@ def test_hf_to_gguf_embeds_the_sentencepiece_tokenizer(tmp_path):
     for text in ("the quick brown fox", "lazy dog runs far away", "zebra!"):
         ids = tok.encode(text, add_bos=False)
         assert ids == sp.encode(text) and tok.decode(ids).strip() == text
+
+
+def test_qwen2_style_checkpoints_with_qkv_biases(tmp_path):
+    """q / k / v biases and the half-split rotation of the Qwen2 family: the runtime on the Hugging Face directory and on
+    the GGUF file written from it agrees with ``transformers``' Qwen2."""
+    tf = pytest.importorskip("transformers")
+    torch.manual_seed(0)
+    hc = tf.Qwen2Config(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                        max_position_embeddings=64, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=True, use_sliding_window=False)
+    ref = tf.Qwen2ForCausalLM(hc).eval()
+    with torch.no_grad():
+        for n, p in ref.named_parameters():
+            if n.endswith("bias"):
+                p.normal_(0, 0.2)
+    d = str(tmp_path / "qwen")
+    ref.save_pretrained(d, safe_serialization=True)
+    prompt = torch.randint(0, 96, (2, 9), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = ref(prompt).logits[:, -1]
+        nxt = want.argmax(-1)
+        want2 = ref(torch.cat([prompt, nxt[:, None]], 1)).logits[:, -1]
+    out = str(tmp_path / "qwen.gguf")
+    assert llm.hf_to_gguf(d, out, gguf.GGMLType.Q8_0)["tensors"] == 2 + 12 * 2          # tied head: no output.weight
+    for rt in (llm.LlamaRuntime.from_hf(d, device="cpu"), llm.LlamaRuntime.from_gguf(out, device="cpu")):
+        assert not rt.cfg.rope_interleaved and rt.layers[0].qkv_bias.shape == (4 * 16 + 2 * 2 * 16,)
+        cache = rt.new_cache(2, 16)
+        got = rt.prefill(prompt, cache)
+        assert float((want - got).abs().max()) < 0.03 * float(want.abs().max())
+        assert float((want2 - rt.decode_step(nxt, cache)).abs().max()) < 0.03 * float(want2.abs().max())
+    half = llm.LlamaRuntime.from_hf(d, device="cpu", tp_rank=1, tp_world=2)               # bias rows are sharded with the weight rows
+    assert half.layers[0].qkv_bias.shape == (2 * 16 + 2 * 16,)
+    full = llm.LlamaRuntime.from_hf(d, device="cpu").layers[0].qkv_bias
+    assert torch.equal(half.layers[0].qkv_bias, torch.cat([full[32:64], full[64 + 16:64 + 32], full[96 + 16:128]]))
