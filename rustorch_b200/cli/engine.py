@@ -82,7 +82,8 @@ class ModelLoader:
             import json as _json
             cfg_path = os.path.join(path, "config.json")
             hf = _json.load(open(cfg_path)) if os.path.exists(cfg_path) else {}
-            if str(hf.get("model_type", "")).lower() in ("llama", "mistral") or any("Llama" in a or "Mistral" in a for a in hf.get("architectures", [])):
+            if str(hf.get("model_type", "")).lower() in ("llama", "mistral", "qwen2") or any(
+                    k in a for a in hf.get("architectures", []) for k in ("Llama", "Mistral", "Qwen2ForCausalLM")):
                 rt = LlamaRuntime.from_hf(path, device)
                 tok = load_tokenizer(tokenizer_path or path, vocab_size=rt.cfg.vocab_size)
                 meta = ModelMetadata(os.path.basename(os.path.normpath(path)), "huggingface", rt.cfg.vocab_size, rt.cfg.n_embd, rt.cfg.n_layer,
