@@ -159,6 +159,11 @@ class LlamaRuntime:
                 what = (f"missing {absent[:4]}{'...' if len(absent) > 4 else ''}" if absent else "") + \
                        (("; " if absent else "") + f"tensors this runtime does not execute: {extra[:6]}" if extra else "")
                 raise ValueError(f"{path}: architecture '{mc['architecture']}' is not a Llama-style decoder this runtime runs ({what})")
+            scaling = g.metadata.get(f"{mc['architecture']}.rope.scaling.type")
+            if "rope_freqs.weight" in g.tensors or scaling not in (None, "none"):
+                # long-context variants rescale the rotation frequencies; the rotary kernels take one base only, and
+                # ignoring the factors would change the logits at every position
+                raise ValueError(f"{path}: RoPE frequency scaling ({scaling or 'rope_freqs.weight'}) is not implemented by this runtime")
             # Llama-architecture files rotate adjacent pairs (their q / k rows were re-ordered by the converter); the Qwen
             # family and the other "neox" architectures rotate the two halves of a head
             cfg.rope_interleaved = str(mc["architecture"]).lower() not in ("qwen", "qwen2", "phi3", "gemma", "stablelm", "falcon")

@@ -276,3 +276,19 @@ def test_qwen2_style_checkpoints_with_qkv_biases(tmp_path):
     assert half.layers[0].qkv_bias.shape == (2 * 16 + 2 * 16,)
     full = llm.LlamaRuntime.from_hf(d, device="cpu").layers[0].qkv_bias
     assert torch.equal(half.layers[0].qkv_bias, torch.cat([full[32:64], full[64 + 16:64 + 32], full[96 + 16:128]]))
+
+
+def test_from_gguf_refuses_rope_frequency_scaling(tmp_path):
+    p = str(tmp_path / "t.gguf")
+    _tiny_gguf(p)
+    with gguf.GGUFFile(p) as g:
+        md = dict(g.metadata)
+        tensors = {n: (g.load_tensor(n), gguf.GGMLType.F32) for n in g.tensors}
+    tensors["rope_freqs.weight"] = (torch.ones(8), gguf.GGMLType.F32)
+    gguf.write_gguf(p, md, tensors)
+    with pytest.raises(ValueError, match="frequency scaling"):
+        llm.LlamaRuntime.from_gguf(p, device="cpu")
+    del tensors["rope_freqs.weight"]
+    gguf.write_gguf(p, {**md, "llama.rope.scaling.type": "linear"}, tensors)
+    with pytest.raises(ValueError, match="linear"):
+        llm.LlamaRuntime.from_gguf(p, device="cpu")
