@@ -128,10 +128,14 @@ class HuggingFaceCheckpoint:
     def __init__(self, directory: str):
         self.directory = directory
         cp = os.path.join(directory, "config.json")
-        self.config: dict = json.load(open(cp)) if os.path.exists(cp) else {}
+        self.config: dict = {}
+        if os.path.exists(cp):
+            with open(cp) as f:
+                self.config = json.load(f)
         idx = os.path.join(directory, "model.safetensors.index.json")
         if os.path.exists(idx):
-            self.weight_map: Dict[str, str] = dict(json.load(open(idx))["weight_map"])
+            with open(idx) as f:
+                self.weight_map: Dict[str, str] = dict(json.load(f)["weight_map"])
         else:
             single = os.path.join(directory, "model.safetensors")
             if not os.path.exists(single):

@@ -72,11 +72,15 @@ def hf_to_gguf(directory: str, path: str, ggml_type: gguf.GGMLType = gguf.GGMLTy
         if other:
             raise ValueError(f"{directory}: biases outside the q / k / v projections ({other[:3]}) are not a decoder this format path writes")
         emb_ty = gguf.GGMLType.F16 if ty in (gguf.GGMLType.Q8_0, gguf.GGMLType.Q4_0, gguf.GGMLType.F16) else gguf.GGMLType.F32
-        tensors: Dict[str, Tuple[torch.Tensor, gguf.GGMLType]] = {
-            "token_embd.weight": (ck.get("model.embed_tokens.weight").float(), emb_ty),
-            "output_norm.weight": (ck.get("model.norm.weight").float(), gguf.GGMLType.F32)}
+
+        def enc(w: torch.Tensor, t: gguf.GGMLType):
+            """Encoded at once, so that the checkpoint is held in its written size, not in fp32."""
+            return gguf.RawTensor(tuple(w.shape), gguf.encode_tensor(w, t)), t
+        tensors: Dict[str, Tuple[object, gguf.GGMLType]] = {
+            "token_embd.weight": enc(ck.get("model.embed_tokens.weight").float(), emb_ty),
+            "output_norm.weight": enc(ck.get("model.norm.weight").float(), gguf.GGMLType.F32)}
         if "lm_head.weight" in ck:
-            tensors["output.weight"] = (ck.get("lm_head.weight").float(), ty)
+            tensors["output.weight"] = enc(ck.get("lm_head.weight").float(), ty)
         for i in range(n_layer):
             for src, dst in _LAYER.items():
                 w = ck.get(f"model.layers.{i}.{src}.weight").float()
@@ -84,14 +88,14 @@ def hf_to_gguf(directory: str, path: str, ggml_type: gguf.GGMLType = gguf.GGMLTy
                     w = interleave_rope_rows(w, n_head)
                 elif a == "llama" and dst == "attn_k":
                     w = interleave_rope_rows(w, n_kv)
-                tensors[f"blk.{i}.{dst}.weight"] = (w, gguf.GGMLType.F32 if dst.endswith("norm") else ty)
+                tensors[f"blk.{i}.{dst}.weight"] = enc(w, gguf.GGMLType.F32 if dst.endswith("norm") else ty)
             for src, dst in qkv_bias.items():
                 key = f"model.layers.{i}.{src}"
                 if key in ck:
                     b = ck.get(key).float()
                     if a == "llama":                       # a biased Llama: the bias follows its rows
                         b = interleave_rope_rows(b.unsqueeze(1), n_head if dst == "attn_q.bias" else n_kv).squeeze(1) if dst != "attn_v.bias" else b
-                    tensors[f"blk.{i}.{dst}"] = (b, gguf.GGMLType.F32)
+                    tensors[f"blk.{i}.{dst}"] = enc(b, gguf.GGMLType.F32)
     spm_path = os.path.join(directory, "tokenizer.model")
     if os.path.exists(spm_path):
         md.update(sentencepiece_metadata(spm_path))
