@@ -334,6 +334,18 @@ class Sequential(Model):
         self.compiled = False
         self._metrics: Dict[str, Callable] = {}
 
+    def to(self, *args, **kwargs):
+        """Also remembers the device for layers that do not exist yet and for the batches ``fit`` / ``evaluate`` feed in."""
+        dev = torch._C._nn._parse_to(*args, **kwargs)[0]
+        if dev is not None:
+            self.__dict__["_target_device"] = dev
+        return super().to(*args, **kwargs)
+
+    def _dev(self) -> torch.device:
+        for p in self.parameters():
+            return p.device
+        return self.__dict__.get("_target_device", torch.device("cpu"))
+
     def add(self, layer: Union[nn.Module, str]) -> "Sequential":
         """A module, or a layer description as the binding's builder writes them (src/python/training.rs:326-347):
         ``"Dense(64, activation=relu)"``, ``"Conv2D(32, 3, activation=relu)"``, ``"Dropout(0.5)"``, ``"Flatten"``, or an
@@ -434,7 +446,7 @@ class Sequential(Model):
             tot, n = 0.0, 0
             _rewind(train)
             for batch in train:
-                xb, yb = _raw(batch[0]), _raw(batch[1])
+                xb, yb = _raw(batch[0]).to(self._dev(), non_blocking=True), _raw(batch[1]).to(self._dev(), non_blocking=True)
                 self._ready(xb)
                 self._optimizer.zero_grad()
                 loss = self._loss(self(xb), yb)
@@ -461,7 +473,7 @@ class Sequential(Model):
         n = 0
         if _is_loader(x):
             _rewind(x)
-            batches = ((_raw(b[0]), _raw(b[1])) for b in x)
+            batches = ((_raw(b[0]).to(self._dev()), _raw(b[1]).to(self._dev())) for b in x)
         else:
             batches = self._loader(_raw(x), _raw(y), batch_size, False)
         for xb, yb in batches:
