@@ -416,6 +416,7 @@ class Sequential(Model):
             self.train()
             tot, n = 0.0, 0
             for xb, yb in self._loader(xt, yt, cfg.batch_size, cfg.shuffle, None if cfg.seed is None else cfg.seed + epoch):
+                xb, yb = xb.to(self._dev(), non_blocking=True), yb.to(self._dev(), non_blocking=True)
                 self._optimizer.zero_grad()
                 loss = self._loss(self(xb), yb)
                 loss.backward()
@@ -477,6 +478,7 @@ class Sequential(Model):
         else:
             batches = self._loader(_raw(x), _raw(y), batch_size, False)
         for xb, yb in batches:
+            xb, yb = xb.to(self._dev()), yb.to(self._dev())
             out = self(xb)
             tot["loss"] += float(self._loss(out, yb)) * len(xb)
             for m, fn in self._metrics.items():
@@ -489,7 +491,7 @@ class Sequential(Model):
         """Outputs for ``x`` in evaluation mode; a ``Tensor`` / ``Variable`` argument gives a result of its own kind."""
         self.eval()
         from .._interop import call_unwrapped
-        return call_unwrapped(lambda t: torch.cat([self(t[i:i + batch_size]) for i in range(0, len(t), batch_size)]), (x,), {})
+        return call_unwrapped(lambda t: torch.cat([self(t[i:i + batch_size].to(self._dev())) for i in range(0, len(t), batch_size)]), (x,), {})
 
     def summary(self) -> str:
         line = "_" * 65
