@@ -233,3 +233,14 @@ def test_save_hf_is_read_back_by_transformers(tmp_path):
     assert all(torch.equal(a, b) for a, b in zip(g.parameters(), GPT.from_hf(d2).parameters()))
     with pytest.raises(ValueError, match="ties the head"):
         GPT(GPTConfig(vocab_size=100, n_positions=32, n_embd=64, n_layer=1, n_head=4), seed=0).save_hf(str(tmp_path / "untied"))
+
+
+def test_metrics_against_sklearn():
+    sk = pytest.importorskip("sklearn.metrics")
+    g = torch.Generator().manual_seed(0)
+    y = torch.randint(0, 5, (400,), generator=g)
+    pred = torch.where(torch.rand(400, generator=g) < 0.7, y, torch.randint(0, 5, (400,), generator=g))
+    m = M.Metrics.from_predictions(pred, y, num_classes=5)
+    p, r, _f, _ = sk.precision_recall_fscore_support(y.numpy(), pred.numpy(), average="macro", zero_division=0)
+    assert m.accuracy == pytest.approx(sk.accuracy_score(y.numpy(), pred.numpy())) and m.precision == pytest.approx(p) and m.recall == pytest.approx(r)
+    assert m.f1_score == pytest.approx(2 * p * r / (p + r))           # harmonic mean of the macro averages (src/models/mod.rs keeps one f1 field)
