@@ -121,6 +121,22 @@ class SafetensorsFile:
         return False
 
 
+def hf_rope_settings(config: dict) -> Tuple[float, Optional[dict]]:
+    """``(rope_theta, rope_scaling or None)`` of a Hugging Face ``config.json``.  Older files carry ``rope_theta`` and
+    ``rope_scaling`` at the top level; newer ones one ``rope_parameters`` entry that holds the base, the type and the
+    scaling factors together."""
+    rp = config.get("rope_parameters")
+    if isinstance(rp, dict):
+        theta = float(rp.get("rope_theta", config.get("rope_theta", 10000.0)))
+        kind = str(rp.get("rope_type", rp.get("type", "default"))).lower()
+        scaling = None if kind in ("default", "none") else {k: v for k, v in rp.items() if k != "rope_theta"}
+        return theta, scaling
+    sc = config.get("rope_scaling") or None
+    if isinstance(sc, dict) and str(sc.get("rope_type", sc.get("type", "default"))).lower() in ("default", "none"):
+        sc = None
+    return float(config.get("rope_theta", 10000.0)), sc
+
+
 class HuggingFaceCheckpoint:
     """A Hugging Face model directory: ``config.json`` plus ``model.safetensors`` or the shards named by
     ``model.safetensors.index.json``; tensors are fetched one at a time from whichever shard holds them."""

@@ -13,7 +13,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from ..formats import gguf
-from ..formats.safetensors import HuggingFaceCheckpoint
+from ..formats.safetensors import HuggingFaceCheckpoint, hf_rope_settings
 
 _LAYER = {"self_attn.q_proj": "attn_q", "self_attn.k_proj": "attn_k", "self_attn.v_proj": "attn_v", "self_attn.o_proj": "attn_output",
           "mlp.gate_proj": "ffn_gate", "mlp.up_proj": "ffn_up", "mlp.down_proj": "ffn_down", "input_layernorm": "attn_norm",
@@ -54,18 +54,19 @@ def hf_to_gguf(directory: str, path: str, ggml_type: gguf.GGMLType = gguf.GGMLTy
         # Qwen2 files keep the half-split rotation (the "neox" RoPE of GGUF readers) and carry q / k / v biases; Llama and
         # Mistral files are written under the "llama" architecture with re-ordered q / k rows
         a = "qwen2" if str(c.get("model_type", "")).lower() == "qwen2" else "llama"
+        theta, scaling = hf_rope_settings(c)
         try:
             n_layer, n_head = int(c["num_hidden_layers"]), int(c["num_attention_heads"])
             n_kv = int(c.get("num_key_value_heads") or n_head)
             md = {"general.architecture": a, "general.name": name or os.path.basename(os.path.normpath(directory)),
                   f"{a}.block_count": n_layer, f"{a}.embedding_length": int(c["hidden_size"]),
                   f"{a}.feed_forward_length": int(c["intermediate_size"]), f"{a}.attention.head_count": n_head,
-                  f"{a}.attention.head_count_kv": n_kv, f"{a}.rope.freq_base": float(c.get("rope_theta", 10000.0)),
+                  f"{a}.attention.head_count_kv": n_kv, f"{a}.rope.freq_base": theta,
                   f"{a}.attention.layer_norm_rms_epsilon": float(c.get("rms_norm_eps", 1e-5)),
                   f"{a}.context_length": int(c.get("max_position_embeddings", 2048)), f"{a}.vocab_size": int(c["vocab_size"])}
         except KeyError as e:
             raise ValueError(f"{directory}: config.json lacks {e.args[0]!r}") from None
-        if c.get("rope_scaling") or c.get("use_sliding_window"):
+        if scaling or c.get("use_sliding_window"):
             raise ValueError(f"{directory}: rope scaling / sliding-window attention have no counterpart in the written file")
         qkv_bias = {"self_attn.q_proj.bias": "attn_q.bias", "self_attn.k_proj.bias": "attn_k.bias", "self_attn.v_proj.bias": "attn_v.bias"}
         other = [k for k in ck.keys() if k.endswith(".bias") and k.split(".", 3)[-1] not in qkv_bias]

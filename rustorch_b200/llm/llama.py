@@ -196,22 +196,23 @@ class LlamaRuntime:
         is quantised to ``ggml_type`` (Q8_0 or Q4_0) as it is read, one tensor at a time, so a bf16 checkpoint never
         sits in memory whole.  These checkpoints rotate the two halves of a head (``rotate_half``), not adjacent pairs
         as GGUF files do, hence ``rope_interleaved=False``."""
-        from ..formats.safetensors import HuggingFaceCheckpoint
+        from ..formats.safetensors import HuggingFaceCheckpoint, hf_rope_settings
         with HuggingFaceCheckpoint(directory) as ck:
             c = ck.config
+            theta, scaling = hf_rope_settings(c)
             arch = (c.get("architectures") or [c.get("model_type", "?")])[0]
             try:
                 n_head = int(c["num_attention_heads"])
                 cfg = LlamaConfig(vocab_size=int(c["vocab_size"]), n_layer=int(c["num_hidden_layers"]), n_embd=int(c["hidden_size"]),
                                   n_head=n_head, n_head_kv=int(c.get("num_key_value_heads") or n_head), n_ff=int(c["intermediate_size"]),
-                                  rope_theta=float(c.get("rope_theta", 10000.0)), rms_eps=float(c.get("rms_norm_eps", 1e-5)),
+                                  rope_theta=theta, rms_eps=float(c.get("rms_norm_eps", 1e-5)),
                                   context_length=int(c.get("max_position_embeddings", 2048)))
             except KeyError as e:
                 raise ValueError(f"{directory}: config.json lacks {e.args[0]!r}") from None
             if c.get("head_dim") not in (None, cfg.n_embd // cfg.n_head):
                 raise ValueError(f"{directory}: head_dim {c['head_dim']} differs from hidden_size / num_attention_heads")
-            if c.get("rope_scaling"):
-                raise ValueError(f"{directory}: rope_scaling {c['rope_scaling']} is not implemented by this runtime")
+            if scaling:
+                raise ValueError(f"{directory}: rope_scaling {scaling} is not implemented by this runtime")
             cfg.rope_interleaved = False
             lay = lambda i, t: f"model.layers.{i}.{t}.weight"      # noqa: E731
             parts = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj", "mlp.gate_proj", "mlp.up_proj",

@@ -35,6 +35,7 @@ class LlamaTrainConfig:
     rope_theta: float = 10000.0
     rms_eps: float = 1e-5
     init_std: float = 0.02
+    rope_scaling: Optional[dict] = None          # Hugging Face ``rope_scaling`` entry: linear or llama3 (see scale_rope_frequencies)
 
     @property
     def head_dim(self) -> int:
@@ -55,8 +56,33 @@ class LlamaTrainConfig:
         return LlamaTrainConfig(**base)
 
 
-def rope_tables(T: int, D: int, theta: float, device, dtype=torch.float32) -> Tuple[torch.Tensor, torch.Tensor]:
-    inv = theta ** (-torch.arange(0, D, 2, device=device, dtype=torch.float32) / D)
+def scale_rope_frequencies(inv: torch.Tensor, scaling: Optional[dict]) -> torch.Tensor:
+    """Long-context variants of the rotation frequencies.  ``{"rope_type": "linear", "factor": f}`` divides every
+    frequency by ``f``; ``"llama3"`` (Llama 3.1 onwards) divides only the low frequencies (wavelength above
+    ``original_max_position_embeddings / low_freq_factor``), leaves the high ones (wavelength below
+    ``original / high_freq_factor``) and blends in between."""
+    if not scaling:
+        return inv
+    kind = str(scaling.get("rope_type", scaling.get("type", "default"))).lower()
+    if kind in ("default", "none"):
+        return inv
+    factor = float(scaling["factor"])
+    if kind == "linear":
+        return inv / factor
+    if kind != "llama3":
+        raise ValueError(f"rope scaling {kind!r} is not implemented (linear and llama3 are)")
+    lo, hi = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+    old = float(scaling["original_max_position_embeddings"])
+    wavelen = 2 * math.pi / inv
+    scaled = torch.where(wavelen > old / lo, inv / factor, inv)
+    smooth = (old / wavelen - lo) / (hi - lo)
+    blended = (1 - smooth) * scaled / factor + smooth * scaled
+    medium = ~(wavelen < old / hi) & ~(wavelen > old / lo)
+    return torch.where(medium, blended, scaled)
+
+
+def rope_tables(T: int, D: int, theta: float, device, dtype=torch.float32, scaling: Optional[dict] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    inv = scale_rope_frequencies(theta ** (-torch.arange(0, D, 2, device=device, dtype=torch.float32) / D), scaling)
     ang = torch.arange(T, device=device, dtype=torch.float32)[:, None] * inv[None, :]
     return ang.cos().to(dtype), ang.sin().to(dtype)
 
@@ -249,16 +275,19 @@ class LlamaModel(nn.Module):
         """A single-rank model with the weights of a Hugging Face Llama checkpoint directory (``config.json`` +
         safetensors, sharded or not), e.g. to fine-tune it.  Same head layout (rotate-half RoPE) as those checkpoints, so
         the tensors are copied as they are: q | k | v stacked into ``wqkv``, gate | up into ``w_gate_up``."""
-        from ..formats.safetensors import HuggingFaceCheckpoint
+        from ..formats.safetensors import HuggingFaceCheckpoint, hf_rope_settings
         with HuggingFaceCheckpoint(directory) as ck:
             c = ck.config
-            if c.get("rope_scaling") or any(k.endswith(".bias") for k in ck.keys()):
-                raise ValueError(f"{directory}: rope scaling and projection biases are outside this model")
+            if any(k.endswith(".bias") for k in ck.keys()):
+                raise ValueError(f"{directory}: projection biases are outside this model")
+            theta, scaling = hf_rope_settings(c)
+            if scaling:
+                scale_rope_frequencies(torch.ones(1), scaling)               # refuses the kinds that are not implemented
             n_head = int(c["num_attention_heads"])
             cfg = LlamaTrainConfig(vocab_size=int(c["vocab_size"]), n_layer=int(c["num_hidden_layers"]), n_embd=int(c["hidden_size"]),
                                    n_head=n_head, n_head_kv=int(c.get("num_key_value_heads") or n_head), n_ff=int(c["intermediate_size"]),
-                                   max_seq_len=int(c.get("max_position_embeddings", 4096)), rope_theta=float(c.get("rope_theta", 10000.0)),
-                                   rms_eps=float(c.get("rms_norm_eps", 1e-5)))
+                                   max_seq_len=int(c.get("max_position_embeddings", 4096)), rope_theta=theta,
+                                   rms_eps=float(c.get("rms_norm_eps", 1e-5)), rope_scaling=scaling)
             model = cls(cfg, device=device, dtype=dtype)
             get = lambda n: ck.get(n).to(device=device, dtype=dtype or torch.float32)      # noqa: E731
             with torch.no_grad():
@@ -279,7 +308,7 @@ class LlamaModel(nn.Module):
         B, T = idx.shape
         c = self.cfg
         if self._rope is None or self._rope[0].shape[0] < T or self._rope[0].device != idx.device:
-            self._rope = rope_tables(max(T, c.max_seq_len), c.head_dim, c.rope_theta, idx.device)
+            self._rope = rope_tables(max(T, c.max_seq_len), c.head_dim, c.rope_theta, idx.device, scaling=c.rope_scaling)
         cos, sin = self._rope
         flat = idx.reshape(-1)
         lo, hi = 0, B * T
@@ -329,6 +358,8 @@ class LlamaModel(nn.Module):
             json.dump({"architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": c.vocab_size, "hidden_size": c.n_embd,
                        "intermediate_size": c.n_ff, "num_hidden_layers": c.n_layer, "num_attention_heads": H, "num_key_value_heads": Hkv,
                        "hidden_act": "silu", "max_position_embeddings": c.max_seq_len, "rms_norm_eps": c.rms_eps, "rope_theta": c.rope_theta,
+                       "rope_scaling": c.rope_scaling,
+                       "rope_parameters": {"rope_theta": c.rope_theta, **(c.rope_scaling or {"rope_type": "default"})},
                        "tie_word_embeddings": False, "attention_bias": False, "mlp_bias": False, "torch_dtype": name}, f, indent=2)
 
     def replicated_parameters(self):

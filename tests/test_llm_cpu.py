@@ -138,12 +138,13 @@ def test_from_hf_matches_transformers_llama(tmp_path):
     tf = pytest.importorskip("transformers")
     torch.manual_seed(0)
     hc = tf.LlamaConfig(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
-                        num_key_value_heads=2, max_position_embeddings=64, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False)
+                        num_key_value_heads=2, max_position_embeddings=64, rms_norm_eps=1e-5, rope_theta=50000.0, tie_word_embeddings=False)
     ref = tf.LlamaForCausalLM(hc).eval()
     d = str(tmp_path / "hf")
     ref.save_pretrained(d, safe_serialization=True)
     rt = llm.LlamaRuntime.from_hf(d, device="cpu")
     assert not rt.cfg.rope_interleaved and rt.cfg.n_head_kv == 2 and len(rt.layers) == 2
+    assert rt.cfg.rope_theta == 50000.0              # whichever layout this transformers version writes the base in
     prompt = torch.randint(0, 96, (2, 9), generator=torch.Generator().manual_seed(1))
     with torch.no_grad():
         want = ref(prompt).logits[:, -1]
@@ -182,9 +183,22 @@ def test_from_hf_matches_transformers_llama(tmp_path):
     save_safetensors(full, os.path.join(bad, "model.safetensors"))
     with pytest.raises(ValueError, match="q_proj.bias"):
         llm.LlamaRuntime.from_hf(bad, device="cpu")
-    json.dump({**cfg, "rope_scaling": {"type": "linear", "factor": 2.0}}, open(os.path.join(d, "config.json"), "w"))
+    json.dump({**cfg, "rope_scaling": {"type": "linear", "factor": 2.0}, "rope_parameters": None}, open(os.path.join(d, "config.json"), "w"))
     with pytest.raises(ValueError, match="rope_scaling"):
         llm.LlamaRuntime.from_hf(d, device="cpu")
+    json.dump({**cfg, "rope_parameters": {"rope_type": "llama3", "factor": 8.0, "rope_theta": 1e4}}, open(os.path.join(d, "config.json"), "w"))
+    with pytest.raises(ValueError, match="rope_scaling"):
+        llm.LlamaRuntime.from_hf(d, device="cpu")
+
+
+def test_hf_rope_settings_reads_both_config_layouts():
+    from rustorch_b200.formats.safetensors import hf_rope_settings
+    assert hf_rope_settings({}) == (10000.0, None)
+    assert hf_rope_settings({"rope_theta": 5e5, "rope_scaling": None}) == (5e5, None)
+    assert hf_rope_settings({"rope_theta": 5e5, "rope_scaling": {"type": "linear", "factor": 2.0}}) == (5e5, {"type": "linear", "factor": 2.0})
+    assert hf_rope_settings({"rope_parameters": {"rope_theta": 1e6, "rope_type": "default"}}) == (1e6, None)
+    th, sc = hf_rope_settings({"rope_theta": 1.0, "rope_parameters": {"rope_theta": 5e5, "rope_type": "llama3", "factor": 8.0}})
+    assert th == 5e5 and sc == {"rope_type": "llama3", "factor": 8.0}
 
 
 def test_hf_to_gguf_keeps_the_logits(tmp_path):
@@ -193,7 +207,7 @@ def test_hf_to_gguf_keeps_the_logits(tmp_path):
     tf = pytest.importorskip("transformers")
     torch.manual_seed(0)
     hc = tf.LlamaConfig(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
-                        num_key_value_heads=2, max_position_embeddings=64, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False)
+                        num_key_value_heads=2, max_position_embeddings=64, rms_norm_eps=1e-5, rope_theta=50000.0, tie_word_embeddings=False)
     ref = tf.LlamaForCausalLM(hc).eval()
     d = str(tmp_path / "hf")
     ref.save_pretrained(d, safe_serialization=True)
@@ -205,7 +219,7 @@ def test_hf_to_gguf_keeps_the_logits(tmp_path):
         info = llm.hf_to_gguf(d, out, ty)
         assert info["tensors"] == 3 + 9 * 2 and info["bytes"] == os.path.getsize(out)
         rt = llm.LlamaRuntime.from_gguf(out, device="cpu")
-        assert rt.cfg.rope_interleaved
+        assert rt.cfg.rope_interleaved and rt.cfg.rope_theta == 50000.0
         got = rt.prefill(prompt, rt.new_cache(2, 16))
         assert float((want - got).abs().max()) < tol * float(want.abs().max()), ty
     w = torch.arange(16.0).view(8, 2)                                # two heads of four rows: halves (0, 1 | 2, 3) -> pairs (0, 2, 1, 3)
@@ -267,7 +281,7 @@ def test_qwen2_style_checkpoints_with_qkv_biases(tmp_path):
     out = str(tmp_path / "qwen.gguf")
     assert llm.hf_to_gguf(d, out, gguf.GGMLType.Q8_0)["tensors"] == 2 + 12 * 2          # tied head: no output.weight
     for rt in (llm.LlamaRuntime.from_hf(d, device="cpu"), llm.LlamaRuntime.from_gguf(out, device="cpu")):
-        assert not rt.cfg.rope_interleaved and rt.layers[0].qkv_bias.shape == (4 * 16 + 2 * 2 * 16,)
+        assert not rt.cfg.rope_interleaved and rt.layers[0].qkv_bias.shape == (4 * 16 + 2 * 2 * 16,) and rt.cfg.rope_theta == 1e6
         cache = rt.new_cache(2, 16)
         got = rt.prefill(prompt, cache)
         assert float((want - got).abs().max()) < 0.03 * float(want.abs().max())

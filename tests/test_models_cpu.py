@@ -200,6 +200,37 @@ def test_bert_matches_transformers(tmp_path):
     assert m.masked_lm_logits(ids).shape == (2, 10, 120) and m.classify(ids).shape == (2, 2)
 
 
+def test_llama_from_hf_applies_rope_base_and_scaling(tmp_path):
+    """The RoPE base and the llama3 / linear frequency scaling of a Hugging Face config reach the training model: logits
+    agree with ``transformers`` at positions where the unscaled tables are measurably off, and ``save_hf`` keeps them."""
+    tf = pytest.importorskip("transformers")
+    from rustorch_b200.models.llama import LlamaModel, scale_rope_frequencies
+    idx = torch.randint(0, 96, (2, 100), generator=torch.Generator().manual_seed(3))
+    for rs in ({"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 32},
+               {"rope_type": "linear", "factor": 2.0}, None):
+        torch.manual_seed(0)
+        hc = tf.LlamaConfig(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                            num_key_value_heads=2, max_position_embeddings=128, rope_theta=50000.0, rope_scaling=rs, tie_word_embeddings=False)
+        ref = tf.LlamaForCausalLM(hc).eval()
+        d = str(tmp_path / f"hf_{rs['rope_type'] if rs else 'plain'}")
+        ref.save_pretrained(d, safe_serialization=True)
+        m = LlamaModel.from_hf(d).eval()
+        assert m.cfg.rope_theta == 50000.0 and (m.cfg.rope_scaling or {}).get("rope_type") == (rs or {}).get("rope_type")
+        with torch.no_grad():
+            want = ref(idx).logits.view(-1, 96)
+            assert float((want - m(idx)[0]).abs().max()) < 2e-5
+            if rs:
+                m.cfg.rope_scaling, m._rope = None, None
+                assert float((want - m(idx)[0]).abs().max()) > 1e-3      # the scaling is what made them agree
+                m.cfg.rope_scaling, m._rope = rs, None
+        out = str(tmp_path / f"out_{rs['rope_type'] if rs else 'plain'}")
+        m.save_hf(out)
+        with torch.no_grad():
+            assert torch.allclose(tf.LlamaForCausalLM.from_pretrained(out).eval()(idx).logits.view(-1, 96), want, atol=2e-5)
+    with pytest.raises(ValueError, match="yarn"):
+        scale_rope_frequencies(torch.ones(4), {"rope_type": "yarn", "factor": 2.0})
+
+
 def test_save_hf_is_read_back_by_transformers(tmp_path):
     """Fine-tuning loop closed: a model of this package written with ``save_hf`` loads in ``transformers`` and gives the
     same logits; ``from_hf`` of the written directory reproduces the parameters."""
