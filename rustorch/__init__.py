@@ -37,3 +37,4 @@ for _name, _mod in list(sys.modules.items()):          # submodules that are loa
     if _name.startswith(_REAL + "."):
         sys.modules.setdefault(_ALIAS + _name[len(_REAL):], _mod)
 sys.modules[__name__] = _impl
+sys.modules.setdefault("_rustorch_py", _impl)            # the extension module's own name in the reference's wheel

@@ -24,6 +24,8 @@ _LAZY = {
     "Tensor": "tensor", "tensor": "tensor", "zeros": "tensor", "ones": "tensor", "Variable": "autograd", "no_grad": "autograd",
     "enable_grad": "autograd", "grad": "autograd", "gradcheck": "autograd", "jacobian": "autograd", "hessian": "autograd",
     "Complex": "complex",
+    **{n: "callbacks" for n in ("CallbackRegistry", "Result", "init_callback_system", "call_python_from_rust", "progress_callback_example",
+                                "try_catch", "get_version", "hello_from_rust", "add_numbers", "sum_list")},
     # layers and losses
     **{n: "nn" for n in ("Module", "Parameter", "Sequential", "Linear", "Conv1d", "Conv2d", "Conv3d", "ConvTranspose2d", "MaxPool2d",
                          "AvgPool2d", "BatchNorm1d", "BatchNorm2d", "LayerNorm", "RMSNorm", "GroupNorm", "Dropout", "Flatten", "Embedding",

@@ -17,9 +17,9 @@ class RusTorchError(Exception):
 
     kind = "RusTorchError"
 
-    def __init__(self, message: str = "", **context: Any):
+    def __init__(self, message: str = "", error_code: Optional[int] = None, **context: Any):
         super().__init__(message)
-        self.message, self.context = message, context
+        self.message, self.error_code, self.context = message, error_code, context
 
     def __str__(self) -> str:
         ctx = ", ".join(f"{k}={v}" for k, v in self.context.items())

@@ -133,6 +133,25 @@ class Callback:
     def on_batch_end(self, state: TrainingState, batch: BatchState) -> None: ...
 
 
+class RegistryCallback(Callback):
+    """Bridges a ``CallbackRegistry`` of named host functions into the training loop: ``"progress"(epoch, epochs,
+    percent)`` after every epoch, ``"log"("info", text)`` with the epoch's losses, ``"completed"(epochs_run)`` at the end.
+    A ``"progress"`` function that returns ``False`` stops training.  Entries that are not registered are skipped."""
+
+    def __init__(self, registry, total_epochs: Optional[int] = None):
+        self.registry, self.total_epochs = registry, total_epochs
+
+    def on_epoch_end(self, state: TrainingState, epoch: EpochState) -> Optional[CallbackSignal]:
+        total = int(self.total_epochs or max(epoch.epoch + 1, 1))
+        val = "" if epoch.val_loss is None else f", val_loss {epoch.val_loss:.6f}"
+        self.registry.call_if_registered("log", "info", f"epoch {epoch.epoch + 1}/{total}: train_loss {epoch.train_loss:.6f}{val}")
+        go_on = self.registry.call_if_registered("progress", epoch.epoch + 1, total, 100.0 * (epoch.epoch + 1) / total)
+        return CallbackSignal.STOP if go_on is False else None
+
+    def on_train_end(self, state: TrainingState) -> None:
+        self.registry.call_if_registered("completed", len(state.history))
+
+
 class EarlyStopping(Callback):
     """``(monitor, patience, min_delta, mode_max)`` (callbacks.rs:89-109)."""
 
@@ -417,6 +436,8 @@ class Trainer:
     def __init__(self, config: Optional[TrainerConfig] = None, callbacks: Optional[List[Callback]] = None,
                  metric_fns: Optional[Dict[str, Callable]] = None):
         self.config = config or TrainerConfig()
+        if hasattr(callbacks, "call_if_registered"):                  # a CallbackRegistry in place of a list
+            callbacks = [RegistryCallback(callbacks)]
         self.callbacks: List[Callback] = list(callbacks or [])
         self.metrics = MetricsCollector(metric_fns)
         self.state = TrainingState()
@@ -510,6 +531,8 @@ class Trainer:
         for cb in self.callbacks:
             if isinstance(cb, ModelCheckpoint) and cb.model is None:
                 cb.bind(model, optimizer)
+            if isinstance(cb, RegistryCallback) and cb.total_epochs is None:
+                cb.total_epochs = int(cfg.epochs)
             cb.on_train_begin(st)
         for epoch in range(st.epoch, cfg.epochs):
             st.epoch = epoch

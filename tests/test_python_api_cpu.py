@@ -517,3 +517,57 @@ def test_described_layers_load_checkpoints_before_seeing_data(tmp_path):
         rt.ModelSerializer.load(plain, extra)                        # strict: the unknown name is reported
     rt.ModelSerializer.load(plain, extra, strict=False)
     assert float(plain.weight.abs().sum()) == 0.0
+
+
+def test_callback_registry_result_and_try_catch():
+    """The binding's host-callback utilities (python/tests/test_advanced.py:9-150, test_direct.py:16-30), reachable
+    through the extension module's own name too."""
+    import rustorch as rt
+    import _rustorch_py as ext
+    assert ext is rt
+    reg = rt.init_callback_system()
+    reg.register_callback("my_callback", lambda m: f"Python received: {m}")
+    reg.register_callback("progress", lambda s, t, p: f"Progress: {s}/{t} ({p:.1f}%)")
+    reg.register_callback("completed", lambda n: f"Completed {n} operations")
+    assert reg.list_callbacks() == ["completed", "my_callback", "progress"] and "progress" in reg and len(reg) == 3
+    assert rt.call_python_from_rust(reg, "my_callback", "hi") == "Python received: hi"
+    assert rt.progress_callback_example(reg, 4) == ["Progress: 1/4 (25.0%)", "Progress: 2/4 (50.0%)", "Progress: 3/4 (75.0%)",
+                                                    "Progress: 4/4 (100.0%)", "Completed 4 operations"]
+    with pytest.raises(rt.RusTorchError, match="no callback named 'nope'"):
+        reg.call("nope")
+    with pytest.raises(rt.RusTorchError):
+        reg.register_callback("x", 3)
+    assert reg.unregister_callback("completed") and not reg.unregister_callback("completed")
+    e = rt.RusTorchError("Test error", 1001)
+    assert e.message == "Test error" and e.error_code == 1001 and "Test error" in str(e)
+    ok, err = rt.Result.ok("v"), rt.Result.err("bad")
+    assert ok.is_ok and not ok.is_err and err.is_err and ok.unwrap() == "v" and err.unwrap_or("d") == "d" and ok.unwrap_or("d") == "v"
+    with pytest.raises(rt.RusTorchError, match="bad"):
+        err.unwrap()
+    with pytest.raises(KeyError):
+        rt.Result.err(KeyError("k")).unwrap()
+    assert ok.map(str.upper).unwrap() == "V" and err.map(str.upper) is err and err.unwrap_err() == "bad" and repr(ok) == "Ok('v')"
+    assert rt.try_catch(lambda: "Success!") == "Success!"
+    assert rt.try_catch(lambda: 1 / 0, lambda ex: f"handled {type(ex).__name__}") == "handled ZeroDivisionError"
+    with pytest.raises(ZeroDivisionError):
+        rt.try_catch(lambda: 1 / 0)
+    assert rt.get_version() == rt.__version__ and "RusTorch" in rt.hello_from_rust()
+    assert rt.add_numbers(1.5, 2.5) == 4.0 and rt.sum_list([1.0, 2.0, 3.0, 4.0, 5.0]) == 15.0
+
+
+def test_trainer_reports_through_a_callback_registry():
+    import rustorch as rt
+    from rustorch_b200.training import Trainer, TrainerConfig
+    torch.manual_seed(0)
+    seen, logs = [], []
+    reg = rt.init_callback_system()
+    reg.register_callback("progress", lambda s, t, p: seen.append((s, t, round(p))) or (s < 3))      # False at epoch 3: stop
+    reg.register_callback("log", lambda level, text: logs.append((level, text)))
+    reg.register_callback("completed", lambda n: seen.append(("done", n)))
+    model = torch.nn.Linear(4, 1)
+    data = [(torch.randn(8, 4), torch.randn(8, 1)) for _ in range(3)]
+    cfg = TrainerConfig()
+    cfg.epochs = 5
+    Trainer(cfg, callbacks=reg).train(model, data, torch.nn.MSELoss(), torch.optim.SGD(model.parameters(), lr=0.01))
+    assert seen == [(1, 5, 20), (2, 5, 40), (3, 5, 60), ("done", 3)]
+    assert len(logs) == 3 and logs[0][0] == "info" and logs[0][1].startswith("epoch 1/5: train_loss ")
