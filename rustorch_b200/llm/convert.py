@@ -66,8 +66,21 @@ def hf_to_gguf(directory: str, path: str, ggml_type: gguf.GGMLType = gguf.GGMLTy
                   f"{a}.context_length": int(c.get("max_position_embeddings", 2048)), f"{a}.vocab_size": int(c["vocab_size"])}
         except KeyError as e:
             raise ValueError(f"{directory}: config.json lacks {e.args[0]!r}") from None
-        if scaling or c.get("use_sliding_window"):
-            raise ValueError(f"{directory}: rope scaling / sliding-window attention have no counterpart in the written file")
+        if c.get("use_sliding_window"):
+            raise ValueError(f"{directory}: sliding-window attention has no counterpart in the written file")
+        rope_freqs = None
+        if scaling:
+            kind = str(scaling.get("rope_type", scaling.get("type", ""))).lower()
+            if kind == "linear":
+                md[f"{a}.rope.scaling.type"], md[f"{a}.rope.scaling.factor"] = "linear", float(scaling["factor"])
+            else:
+                # other kinds travel as per-frequency divisors: plain frequency / scaled frequency
+                from ..models.llama import scale_rope_frequencies
+                hd = int(c.get("head_dim") or int(c["hidden_size"]) // n_head)
+                inv = theta ** (-torch.arange(0, hd, 2, dtype=torch.float32) / hd)
+                rope_freqs = inv / scale_rope_frequencies(inv, scaling)
+                if "original_max_position_embeddings" in scaling:
+                    md[f"{a}.rope.scaling.original_context_length"] = int(scaling["original_max_position_embeddings"])
         qkv_bias = {"self_attn.q_proj.bias": "attn_q.bias", "self_attn.k_proj.bias": "attn_k.bias", "self_attn.v_proj.bias": "attn_v.bias"}
         other = [k for k in ck.keys() if k.endswith(".bias") and k.split(".", 3)[-1] not in qkv_bias]
         if other:
@@ -82,6 +95,8 @@ def hf_to_gguf(directory: str, path: str, ggml_type: gguf.GGMLType = gguf.GGMLTy
             "output_norm.weight": enc(ck.get("model.norm.weight").float(), gguf.GGMLType.F32)}
         if "lm_head.weight" in ck:
             tensors["output.weight"] = enc(ck.get("lm_head.weight").float(), ty)
+        if rope_freqs is not None:
+            tensors["rope_freqs.weight"] = enc(rope_freqs, gguf.GGMLType.F32)
         for i in range(n_layer):
             for src, dst in _LAYER.items():
                 w = ck.get(f"model.layers.{i}.{src}.weight").float()

@@ -38,6 +38,7 @@ class LlamaConfig:
     rms_eps: float = 1e-5
     context_length: int = 2048
     rope_interleaved: bool = True
+    rope_scaling: Optional[dict] = None          # Hugging Face ``rope_scaling`` entry (linear / llama3); None: plain RoPE
 
     @property
     def head_dim(self) -> int:
@@ -160,10 +161,16 @@ class LlamaRuntime:
                        (("; " if absent else "") + f"tensors this runtime does not execute: {extra[:6]}" if extra else "")
                 raise ValueError(f"{path}: architecture '{mc['architecture']}' is not a Llama-style decoder this runtime runs ({what})")
             scaling = g.metadata.get(f"{mc['architecture']}.rope.scaling.type")
-            if "rope_freqs.weight" in g.tensors or scaling not in (None, "none"):
-                # long-context variants rescale the rotation frequencies; the rotary kernels take one base only, and
+            if "rope_freqs.weight" in g.tensors:
+                # per-frequency divisors (how Llama 3.1 files carry their long-context scaling)
+                cfg.rope_scaling = {"rope_type": "factors", "factors": [float(v) for v in g.load_tensor("rope_freqs.weight").float().flatten()]}
+                if len(cfg.rope_scaling["factors"]) != cfg.head_dim // 2:
+                    raise ValueError(f"{path}: rope_freqs.weight has {len(cfg.rope_scaling['factors'])} entries for head size {cfg.head_dim}")
+            elif scaling == "linear":
+                cfg.rope_scaling = {"rope_type": "linear", "factor": float(g.metadata.get(f"{mc['architecture']}.rope.scaling.factor", 1.0))}
+            elif scaling not in (None, "none"):
                 # ignoring the factors would change the logits at every position
-                raise ValueError(f"{path}: RoPE frequency scaling ({scaling or 'rope_freqs.weight'}) is not implemented by this runtime")
+                raise ValueError(f"{path}: RoPE frequency scaling '{scaling}' is not implemented by this runtime (linear and rope_freqs.weight are)")
             # Llama-architecture files rotate adjacent pairs (their q / k rows were re-ordered by the converter); the Qwen
             # family and the other "neox" architectures rotate the two halves of a head
             cfg.rope_interleaved = str(mc["architecture"]).lower() not in ("qwen", "qwen2", "phi3", "gemma", "stablelm", "falcon")
@@ -212,7 +219,9 @@ class LlamaRuntime:
             if c.get("head_dim") not in (None, cfg.n_embd // cfg.n_head):
                 raise ValueError(f"{directory}: head_dim {c['head_dim']} differs from hidden_size / num_attention_heads")
             if scaling:
-                raise ValueError(f"{directory}: rope_scaling {scaling} is not implemented by this runtime")
+                from ..models.llama import scale_rope_frequencies
+                scale_rope_frequencies(torch.ones(1), scaling)         # refuses the kinds that are not implemented
+                cfg.rope_scaling = dict(scaling)
             cfg.rope_interleaved = False
             lay = lambda i, t: f"model.layers.{i}.{t}.weight"      # noqa: E731
             parts = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj", "mlp.gate_proj", "mlp.up_proj",
@@ -301,10 +310,21 @@ class LlamaRuntime:
         xf = x.float()
         return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.cfg.rms_eps) * w.float()).to(x.dtype)
 
+    def _inv_freq(self, D: int, device) -> torch.Tensor:
+        """Rotation frequencies of the ``D // 2`` pairs, with the checkpoint's frequency scaling applied."""
+        cached = getattr(self, "_inv_freq_cache", None)
+        if cached is None or cached.shape[0] != D // 2 or cached.device != torch.device(device):
+            cached = self.cfg.rope_theta ** (-torch.arange(D // 2, device=device, dtype=torch.float32) * 2.0 / D)
+            if self.cfg.rope_scaling:
+                from ..models.llama import scale_rope_frequencies
+                cached = scale_rope_frequencies(cached, self.cfg.rope_scaling)
+            self._inv_freq_cache = cached
+        return cached
+
     def _rope_reference(self, t: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
         D = t.shape[-1]
         half = D // 2
-        inv = self.cfg.rope_theta ** (-torch.arange(half, device=t.device, dtype=torch.float32) * 2.0 / D)
+        inv = self._inv_freq(D, t.device)
         ang = pos.float()[:, None, None] * inv
         cs, sn = ang.cos(), ang.sin()
         tf = t.float()
@@ -346,7 +366,7 @@ class LlamaRuntime:
             rope_done = False
             if fuse:
                 if (cfg.rope_interleaved and QuantLinear.ROPE_FUSED and L.qkv_bias is None and L.wqkv.in_features % 64 == 0
-                        and (H + 2 * Hkv) * D % 4 == 0):
+                        and (H + 2 * Hkv) * D % 4 == 0 and not cfg.rope_scaling):
                     # rotary embedding and the cache append ride in the projection's epilogue
                     qkv = L.wqkv.fused(x, norm_w=L.attn_norm, eps=cfg.rms_eps,
                                        rope=dict(pos=pos32, seq=seq32, cache_k=cache.k[li], cache_v=cache.v[li], n_head=H,
@@ -364,7 +384,13 @@ class LlamaRuntime:
             k = qkv[:, H * D: (H + Hkv) * D].view(n, Hkv, D)
             v = qkv[:, (H + Hkv) * D:].view(n, Hkv, D)
             if C is not None:
-                if not rope_done:
+                if cfg.rope_scaling:
+                    # scaled frequencies: the rotation kernels derive theta^(-2i/D) themselves, so these checkpoints
+                    # rotate with the frequency table in tensor ops and append to the cache by index
+                    q, k = self._rope_reference(q, pos), self._rope_reference(k, pos)
+                    cache.k[li][seq.long(), :, pos.long()] = k
+                    cache.v[li][seq.long(), :, pos.long()] = v
+                elif not rope_done:
                     C.rope_kv(q, k, v, cache.k[li], cache.v[li], pos32, seq32, cfg.rope_theta, cfg.rope_interleaved)
                 att = torch.empty((n, H, D), dtype=q.dtype, device=q.device)
                 if flash_bt is not None:

@@ -60,17 +60,23 @@ def scale_rope_frequencies(inv: torch.Tensor, scaling: Optional[dict]) -> torch.
     """Long-context variants of the rotation frequencies.  ``{"rope_type": "linear", "factor": f}`` divides every
     frequency by ``f``; ``"llama3"`` (Llama 3.1 onwards) divides only the low frequencies (wavelength above
     ``original_max_position_embeddings / low_freq_factor``), leaves the high ones (wavelength below
-    ``original / high_freq_factor``) and blends in between."""
+    ``original / high_freq_factor``) and blends in between; ``{"rope_type": "factors", "factors": [...]}`` divides
+    frequency ``i`` by ``factors[i]`` (the ``rope_freqs.weight`` tensor of GGUF files)."""
     if not scaling:
         return inv
     kind = str(scaling.get("rope_type", scaling.get("type", "default"))).lower()
     if kind in ("default", "none"):
         return inv
+    if kind == "factors":
+        div = torch.as_tensor(scaling["factors"], dtype=inv.dtype, device=inv.device)
+        if div.shape != inv.shape:
+            raise ValueError(f"rope frequency factors: {tuple(div.shape)} for {tuple(inv.shape)} frequencies")
+        return inv / div
     factor = float(scaling["factor"])
     if kind == "linear":
         return inv / factor
     if kind != "llama3":
-        raise ValueError(f"rope scaling {kind!r} is not implemented (linear and llama3 are)")
+        raise ValueError(f"rope scaling {kind!r} is not implemented (linear, llama3 and per-frequency factors are)")
     lo, hi = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
     old = float(scaling["original_max_position_embeddings"])
     wavelen = 2 * math.pi / inv

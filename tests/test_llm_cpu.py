@@ -183,12 +183,44 @@ def test_from_hf_matches_transformers_llama(tmp_path):
     save_safetensors(full, os.path.join(bad, "model.safetensors"))
     with pytest.raises(ValueError, match="q_proj.bias"):
         llm.LlamaRuntime.from_hf(bad, device="cpu")
-    json.dump({**cfg, "rope_scaling": {"type": "linear", "factor": 2.0}, "rope_parameters": None}, open(os.path.join(d, "config.json"), "w"))
-    with pytest.raises(ValueError, match="rope_scaling"):
+    json.dump({**cfg, "rope_scaling": {"type": "yarn", "factor": 2.0}, "rope_parameters": None}, open(os.path.join(d, "config.json"), "w"))
+    with pytest.raises(ValueError, match="yarn"):
         llm.LlamaRuntime.from_hf(d, device="cpu")
-    json.dump({**cfg, "rope_parameters": {"rope_type": "llama3", "factor": 8.0, "rope_theta": 1e4}}, open(os.path.join(d, "config.json"), "w"))
-    with pytest.raises(ValueError, match="rope_scaling"):
+    json.dump({**cfg, "rope_parameters": {"rope_type": "longrope", "factor": 8.0, "rope_theta": 1e4}}, open(os.path.join(d, "config.json"), "w"))
+    with pytest.raises(ValueError, match="longrope"):
         llm.LlamaRuntime.from_hf(d, device="cpu")
+
+
+def test_runtime_applies_rope_scaling_from_hf_and_gguf(tmp_path):
+    """Long-context checkpoints (llama3 and linear frequency scaling): the serving runtime on the Hugging Face directory
+    and on the GGUF file converted from it rotates with ``transformers``' frequencies and agrees on the logits."""
+    tf = pytest.importorskip("transformers")
+    prompt = torch.randint(0, 96, (1, 90), generator=torch.Generator().manual_seed(2))
+    for rs in ({"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 32},
+               {"rope_type": "linear", "factor": 4.0}):
+        torch.manual_seed(0)
+        hc = tf.LlamaConfig(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                            num_key_value_heads=2, max_position_embeddings=128, rope_theta=50000.0, rope_scaling=rs, tie_word_embeddings=False)
+        ref = tf.LlamaForCausalLM(hc).eval()
+        d = str(tmp_path / f"hf_{rs['rope_type']}")
+        ref.save_pretrained(d, safe_serialization=True)
+        out = str(tmp_path / f"{rs['rope_type']}.gguf")
+        info = llm.hf_to_gguf(d, out, gguf.GGMLType.Q8_0)
+        assert info["tensors"] == 3 + 9 * 2 + (rs["rope_type"] == "llama3")
+        with torch.no_grad():
+            want = ref(prompt).logits[:, -1]
+            nxt = want.argmax(-1)
+            want2 = ref(torch.cat([prompt, nxt[:, None]], 1)).logits[:, -1]
+        for rt in (llm.LlamaRuntime.from_hf(d, device="cpu"), llm.LlamaRuntime.from_gguf(out, device="cpu")):
+            assert rt.cfg.rope_scaling["rope_type"] in (rs["rope_type"], "factors")
+            cache = rt.new_cache(1, 96)
+            got = rt.prefill(prompt, cache)
+            err = float((want - got).abs().max()) / float(want.abs().max())
+            assert err < 0.03 and float((want2 - rt.decode_step(nxt, cache)).abs().max()) < 0.03 * float(want2.abs().max())
+            # at random initialisation attention is near uniform and Q8_0 rounding is as large as the effect of the
+            # scaling on the logits, so the frequencies themselves are compared with the library's
+            assert torch.allclose(rt._inv_freq(16, "cpu"), ref.model.rotary_emb.inv_freq.float(), rtol=1e-5, atol=0)
+            assert not torch.allclose(rt._inv_freq(16, "cpu"), 50000.0 ** (-torch.arange(8.0) / 8), rtol=1e-2)
 
 
 def test_hf_rope_settings_reads_both_config_layouts():
@@ -292,17 +324,19 @@ def test_qwen2_style_checkpoints_with_qkv_biases(tmp_path):
     assert torch.equal(half.layers[0].qkv_bias, torch.cat([full[32:64], full[64 + 16:64 + 32], full[96 + 16:128]]))
 
 
-def test_from_gguf_refuses_rope_frequency_scaling(tmp_path):
+def test_from_gguf_rope_frequency_scaling_kinds(tmp_path):
     p = str(tmp_path / "t.gguf")
     _tiny_gguf(p)
     with gguf.GGUFFile(p) as g:
         md = dict(g.metadata)
         tensors = {n: (g.load_tensor(n), gguf.GGMLType.F32) for n in g.tensors}
-    tensors["rope_freqs.weight"] = (torch.ones(8), gguf.GGMLType.F32)
+    tensors["rope_freqs.weight"] = (torch.ones(5), gguf.GGMLType.F32)
     gguf.write_gguf(p, md, tensors)
-    with pytest.raises(ValueError, match="frequency scaling"):
+    with pytest.raises(ValueError, match="rope_freqs.weight has 5 entries"):
         llm.LlamaRuntime.from_gguf(p, device="cpu")
     del tensors["rope_freqs.weight"]
-    gguf.write_gguf(p, {**md, "llama.rope.scaling.type": "linear"}, tensors)
-    with pytest.raises(ValueError, match="linear"):
+    gguf.write_gguf(p, {**md, "llama.rope.scaling.type": "yarn"}, tensors)
+    with pytest.raises(ValueError, match="yarn"):
         llm.LlamaRuntime.from_gguf(p, device="cpu")
+    gguf.write_gguf(p, {**md, "llama.rope.scaling.type": "linear", "llama.rope.scaling.factor": 2.0}, tensors)
+    assert llm.LlamaRuntime.from_gguf(p, device="cpu").cfg.rope_scaling == {"rope_type": "linear", "factor": 2.0}
