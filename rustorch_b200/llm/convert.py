@@ -112,8 +112,17 @@ def hf_to_gguf(directory: str, path: str, ggml_type: gguf.GGMLType = gguf.GGMLTy
                     if a == "llama":                       # a biased Llama: the bias follows its rows
                         b = interleave_rope_rows(b.unsqueeze(1), n_head if dst == "attn_q.bias" else n_kv).squeeze(1) if dst != "attn_v.bias" else b
                     tensors[f"blk.{i}.{dst}"] = enc(b, gguf.GGMLType.F32)
-    spm_path = os.path.join(directory, "tokenizer.model")
+    spm_path, json_path = os.path.join(directory, "tokenizer.model"), os.path.join(directory, "tokenizer.json")
+    tokenizer = None
     if os.path.exists(spm_path):
         md.update(sentencepiece_metadata(spm_path))
+        tokenizer = "llama"
+    elif os.path.exists(json_path):
+        from ..cli.tokenizer import BPETokenizer
+        try:
+            md.update(BPETokenizer.from_tokenizer_json(json_path).gguf_metadata())
+            tokenizer = "gpt2"
+        except ValueError:                                 # not byte-level BPE: the file is written without a tokenizer
+            pass
     gguf.write_gguf(path, md, tensors)
-    return {"tensors": len(tensors), "bytes": os.path.getsize(path), "tokenizer": os.path.exists(spm_path)}
+    return {"tensors": len(tensors), "bytes": os.path.getsize(path), "tokenizer": tokenizer is not None, "tokenizer_model": tokenizer}

@@ -272,3 +272,72 @@ def test_cli_runs_a_hugging_face_gpt2_directory(tmp_path):
     buf = []
     assert cli.main(["--model", d, "--backend", "cpu", "--max-tokens", "5", "--temperature", "0", "--prompt", "The quick brown"], out=buf.append) == 0
     assert "Assistant: " in "".join(buf) and "error" not in "".join(buf)
+
+
+def test_tokenizer_json_byte_level_bpe_matches_the_tokenizers_library(tmp_path):
+    """``tokenizer.json`` (the only tokenizer file of Llama 3 / Qwen2 directories): vocabulary, merges, the split pattern,
+    ``ignore_merges``, added tokens inside the text and the prepended start marker give the ids of the ``tokenizers``
+    library, for the GPT-2 layout and for the Split + ByteLevel layout."""
+    tk = pytest.importorskip("tokenizers")
+    import json
+    from tokenizers import Regex, decoders, models, pre_tokenizers, processors, trainers
+    from rustorch_b200.cli.tokenizer import BPETokenizer, load_tokenizer
+    corpus = ["The quick brown fox jumps over the lazy dog. " * 3, "Ünïcödé tëxt with 12345 numbers and 日本語 too!",
+              "don't you're they'll  spaces   and\nnewlines\n\n", "def f(x):\n    return x + 1  # code"] * 20
+    texts = ["Hello world, the fox don't jump 1234567!", "  leading spaces and\n\nnewlines ", "日本語 mixed Ünï",
+             "<|begin_of_text|>system<|eot_id|>hi there", ""]
+    for style in ("gpt2", "llama3"):
+        tok = tk.Tokenizer(models.BPE(ignore_merges=(style == "llama3")))
+        if style == "gpt2":
+            tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+        else:
+            pat = r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+"
+            tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(Regex(pat), behavior="isolated"),
+                                                         pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+        tok.decoder = decoders.ByteLevel()
+        tok.train_from_iterator(corpus, trainers.BpeTrainer(vocab_size=400, special_tokens=["<|begin_of_text|>", "<|eot_id|>"],
+                                                            initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
+        if style == "llama3":
+            tok.post_processor = processors.Sequence([processors.ByteLevel(trim_offsets=False), processors.TemplateProcessing(
+                single="<|begin_of_text|> $A", special_tokens=[("<|begin_of_text|>", tok.token_to_id("<|begin_of_text|>"))])])
+        d = tmp_path / style
+        d.mkdir()
+        tok.save(str(d / "tokenizer.json"))
+        json.dump({"eos_token": {"content": "<|eot_id|>"}}, open(d / "tokenizer_config.json", "w"))
+        mine = load_tokenizer(str(d))
+        assert isinstance(mine, BPETokenizer) and mine.vocab_size == tok.get_vocab_size() and mine.eos_id == tok.token_to_id("<|eot_id|>")
+        assert mine.bos_id == (tok.token_to_id("<|begin_of_text|>") if style == "llama3" else None)
+        for t in texts:
+            want = tok.encode(t).ids
+            got = mine.encode(t)
+            assert got == want, (style, t)
+            assert mine.decode(got) == tok.decode(want)
+        assert mine.decode(mine.encode("a<|eot_id|>b"), skip_special=False).endswith("a<|eot_id|>b")
+        assert mine.encode("hi", add_bos=False) == tok.encode("hi", add_special_tokens=False).ids
+        # the same tokenizer carried by a GGUF file (tokenizer.ggml.model = gpt2: tokens, merges, token types, pre name)
+        from rustorch_b200.formats import gguf
+        md = mine.gguf_metadata()
+        assert md["tokenizer.ggml.model"] == "gpt2" and md["tokenizer.ggml.pre"] == ("llama-bpe" if style == "llama3" else "gpt-2")
+        gp = str(tmp_path / f"{style}.gguf")
+        gguf.write_gguf(gp, {"general.architecture": "llama", **md}, {"w": (torch.zeros(4), gguf.GGMLType.F32)})
+        with gguf.GGUFFile(gp) as g:
+            carried = load_tokenizer(None, g)
+            g.metadata.pop("tokenizer.rustorch.pattern")          # a file from another writer: the pattern comes from the pre name
+            g.metadata.pop("tokenizer.rustorch.ignore_merges")
+            foreign = load_tokenizer(None, g)
+            g.metadata["tokenizer.ggml.pre"] = "some-new-model"
+            with pytest.raises(ValueError, match="some-new-model"):
+                load_tokenizer(None, g)
+        for t in texts:
+            assert carried.encode(t) == tok.encode(t).ids and carried.decode(carried.encode(t)) == tok.decode(tok.encode(t).ids)
+            if "'" not in t:                                       # the two spellings of the contraction rule differ on case only
+                assert foreign.encode(t) == tok.encode(t).ids, (style, t)
+        assert isinstance(carried, BPETokenizer) and carried.eos_id == mine.eos_id and carried.bos_id == mine.bos_id
+    sp = tmp_path / "unigram"
+    sp.mkdir()
+    json.dump({"model": {"type": "Unigram"}}, open(sp / "tokenizer.json", "w"))
+    with pytest.raises(ValueError, match="Unigram"):
+        load_tokenizer(str(sp))
+    json.dump({"model": {"type": "BPE", "vocab": {}, "merges": []}, "pre_tokenizer": {"type": "Metaspace"}}, open(sp / "tokenizer.json", "w"))
+    with pytest.raises(ValueError, match="not byte-level"):
+        load_tokenizer(str(sp))

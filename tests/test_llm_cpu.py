@@ -291,6 +291,45 @@ def test_hf_to_gguf_embeds_the_sentencepiece_tokenizer(tmp_path):
         assert ids == sp.encode(text) and tok.decode(ids).strip() == text
 
 
+def test_hf_to_gguf_embeds_a_byte_level_bpe_tokenizer(tmp_path):
+    """A directory whose only tokenizer file is ``tokenizer.json`` (Llama 3, Qwen2): the GGUF file carries it as a ``gpt2``
+    tokenizer, and the CLI's loader, given the file alone, tokenizes like the ``tokenizers`` library and generates."""
+    tf = pytest.importorskip("transformers")
+    tk = pytest.importorskip("tokenizers")
+    from tokenizers import Regex, decoders, models, pre_tokenizers, processors, trainers
+    from rustorch_b200.cli.engine import InferenceEngine, ModelLoader
+    from rustorch_b200.cli.session import GenerationConfig
+    d = str(tmp_path / "hf")
+    os.makedirs(d)
+    tok = tk.Tokenizer(models.BPE(ignore_merges=True))
+    pat = r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+"
+    tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(Regex(pat), behavior="isolated"),
+                                                 pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    tok.decoder = decoders.ByteLevel()
+    tok.train_from_iterator(["the quick brown fox jumps over the lazy dog 1234 times, doesn't it?\n"] * 50, trainers.BpeTrainer(
+        vocab_size=330, special_tokens=["<|begin_of_text|>", "<|eot_id|>"], initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
+    tok.post_processor = processors.TemplateProcessing(single="<|begin_of_text|> $A", special_tokens=[("<|begin_of_text|>", 0)])
+    tok.save(os.path.join(d, "tokenizer.json"))
+    import json
+    json.dump({"eos_token": "<|eot_id|>"}, open(os.path.join(d, "tokenizer_config.json"), "w"))
+    n = tok.get_vocab_size()
+    torch.manual_seed(0)
+    tf.LlamaForCausalLM(tf.LlamaConfig(vocab_size=n, hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4,
+                                       num_key_value_heads=2, max_position_embeddings=64)).save_pretrained(d, safe_serialization=True)
+    out = str(tmp_path / "m.gguf")
+    info = llm.hf_to_gguf(d, out, gguf.GGMLType.Q8_0)
+    assert info["tokenizer"] and info["tokenizer_model"] == "gpt2"
+    rt, carried, meta = ModelLoader.from_file(out, "cpu")
+    assert carried.vocab_size == n == meta.vocab_size and carried.bos_id == 0 and carried.eos_id == 1
+    for text in ("the quick brown fox", "doesn't it? 123456", "<|eot_id|>lazy dog\n"):
+        assert carried.encode(text) == tok.encode(text).ids
+    eng = InferenceEngine(rt, carried, GenerationConfig(max_tokens=5, temperature=0.0), "cpu", seed=0)
+    assert isinstance(eng.generate("the quick"), str) and eng.last_token_count <= 5
+    # the directory itself is served with the same tokenizer
+    rt2, tok2, _ = ModelLoader.from_file(d, "cpu")
+    assert tok2.encode("the quick brown fox") == tok.encode("the quick brown fox").ids
+
+
 def test_qwen2_style_checkpoints_with_qkv_biases(tmp_path):
     """q / k / v biases and the half-split rotation of the Qwen2 family: the runtime on the Hugging Face directory and on
     the GGUF file written from it agrees with ``transformers``' Qwen2."""
