@@ -36,6 +36,7 @@ class CliArgs:
     top_p: float = 0.9
     top_k: int = 40
     system_prompt: Optional[str] = None
+    chat_template: Optional[str] = None
     save_history: Optional[str] = None
     load_history: Optional[str] = None
     no_progress: bool = False
@@ -75,6 +76,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--no-progress", action="store_true")
     p.add_argument("--tokenizer", help="tokenizer file (sentencepiece .model); GGUF files carry their own")
     p.add_argument("--prompt", help="answer one prompt and exit")
+    p.add_argument("--chat-template", default=None, choices=["auto", "plain", "llama3", "chatml", "llama2"],
+                   help="chat layout of the prompt (auto: from the model's tokenizer)")
     sub = p.add_subparsers(dest="command")
     d = sub.add_parser("download", help="download a model: hf:<org>/<repo>[:file] or ollama:<name>[:tag]")
     d.add_argument("target")
@@ -92,7 +95,7 @@ def parse_args(argv: Optional[List[str]] = None, config=None) -> CliArgs:
     ns = build_parser().parse_args(argv)
     a = CliArgs(model=ns.model, backend=Backend(ns.backend), config=ns.config, log_level=ns.log_level, system_prompt=ns.system_prompt,
                 save_history=ns.save_history, load_history=ns.load_history, no_progress=ns.no_progress, tokenizer=ns.tokenizer,
-                prompt=ns.prompt, command=ns.command, target=getattr(ns, "target", None), output_dir=getattr(ns, "output_dir", None),
+                prompt=ns.prompt, chat_template=ns.chat_template, command=ns.command, target=getattr(ns, "target", None), output_dir=getattr(ns, "output_dir", None),
                 revision=getattr(ns, "revision", None), token=getattr(ns, "token", None), force=getattr(ns, "force", False))
     if config is None and ns.config:
         from .config import Config

@@ -29,6 +29,7 @@ class ModelMetadata:
     num_layers: int = 0
     num_heads: int = 0
     context_length: int = 0
+    chat_template: str = "plain"
 
 
 class _GPTAdapter:
@@ -62,7 +63,16 @@ class _GPTAdapter:
 class ModelLoader:
     @staticmethod
     def from_file(path: str, device: str = "cpu", tokenizer_path: Optional[str] = None):
-        """-> ``(runtime, tokenizer, ModelMetadata)``."""
+        """-> ``(runtime, tokenizer, ModelMetadata)``; ``ModelMetadata.chat_template`` names the chat layout that the
+        file's tokenizer points to."""
+        rt, tok, meta = ModelLoader._from_file(path, device, tokenizer_path)
+        if path != "dummy" and meta.chat_template == "plain":
+            from .session import detect_chat_template
+            meta.chat_template = detect_chat_template(tok)
+        return rt, tok, meta
+
+    @staticmethod
+    def _from_file(path: str, device: str = "cpu", tokenizer_path: Optional[str] = None):
         if path == "dummy":
             return None, ByteTokenizer(), ModelMetadata("dummy", "dummy", 258)
         if not os.path.exists(path):
@@ -73,8 +83,10 @@ class ModelLoader:
             with gguf_fmt.GGUFFile(path) as g:
                 tok = load_tokenizer(tokenizer_path, g)
                 mc = g.model_config()
+                from .session import detect_chat_template
+                template = detect_chat_template(tok, g.metadata)
             rt = LlamaRuntime.from_gguf(path, device)
-            meta = ModelMetadata(name, "gguf", rt.cfg.vocab_size, rt.cfg.n_embd, rt.cfg.n_layer, rt.cfg.n_head, rt.cfg.context_length)
+            meta = ModelMetadata(name, "gguf", rt.cfg.vocab_size, rt.cfg.n_embd, rt.cfg.n_layer, rt.cfg.n_head, rt.cfg.context_length, template)
             if isinstance(tok, ByteTokenizer):
                 tok = ByteTokenizer(rt.cfg.vocab_size)
             return rt, tok, meta
@@ -124,6 +136,12 @@ class InferenceEngine:
         self.device, self.seed = device, seed
         self.timer = InferenceTimer()
         self.last_token_count = 0
+        self.stop_ids: set = set()                    # ids besides the tokenizer's eos that end a reply
+
+    def set_stop_tokens(self, names) -> None:
+        """Ends replies at the named marker tokens too (those that the tokenizer knows)."""
+        added = getattr(self.tokenizer, "added", None) or {}
+        self.stop_ids = {added[n] for n in names if n in added}
 
     def is_loaded(self) -> bool:
         return self.runtime is not None
@@ -158,7 +176,7 @@ class InferenceEngine:
         for _ in range(budget):
             tok = int(sampler(logits.cpu() if logits.device.type != self.device else logits)[0])
             self.timer.token()
-            if tok == self.tokenizer.eos_id:
+            if tok == self.tokenizer.eos_id or tok in self.stop_ids:
                 break
             out.append(tok)
             text = self.tokenizer.decode(out)

@@ -10,7 +10,7 @@ from .commands import HELP_TEXT, Command, CommandKind
 from .config import Config
 from .download import DownloadOptions, ModelDownloadManager, ModelIdentifier, ModelSource
 from .engine import InferenceEngine, ModelLoader
-from .session import GenerationConfig, SessionManager
+from .session import TURN_END_TOKENS, GenerationConfig, SessionManager
 
 
 class Repl:
@@ -22,6 +22,12 @@ class Repl:
         self.running = True
         self.errors = 0                              # generations that failed in this session
         self.tokenizer_path: Optional[str] = None
+        self.template_choice = "auto"                # "auto": follow what each loaded model's tokenizer points to
+
+    def apply_chat_template(self, detected: str = "plain") -> None:
+        name = detected if self.template_choice in (None, "auto") else self.template_choice
+        self.session.set_chat_template(name)
+        self.engine.set_stop_tokens(TURN_END_TOKENS[name])
 
     # -- one line of input -> True while the loop should go on
     def handle_line(self, line: str) -> bool:
@@ -77,7 +83,8 @@ class Repl:
             rt, tok, meta = ModelLoader.from_file(cmd.arg, self.engine.device, self.tokenizer_path)
             self.engine.runtime, self.engine.tokenizer = rt, tok
             self.session.set_model_name(meta.name)
-            self.out(f"Loaded {meta.name} ({meta.format}, {meta.num_layers} layers, vocab {meta.vocab_size})\n")
+            self.apply_chat_template(meta.chat_template)
+            self.out(f"Loaded {meta.name} ({meta.format}, {meta.num_layers} layers, vocab {meta.vocab_size}, chat template {self.session.chat_template})\n")
         elif k is CommandKind.BACKEND:
             b = Backend(cmd.arg.lower())
             if not b.available():
@@ -147,11 +154,11 @@ def main(argv: Optional[List[str]] = None, read: Callable[[str], str] = input, o
     device = a.backend.device()
     gen = GenerationConfig(a.max_tokens, a.temperature, a.top_p, a.top_k)
     runtime = tokenizer = None
-    model_name = "dummy"
+    model_name, detected = "dummy", "plain"
     if a.model:
         try:
             runtime, tokenizer, meta = ModelLoader.from_file(a.model, device, a.tokenizer)
-            model_name = meta.name
+            model_name, detected = meta.name, meta.chat_template
         except (OSError, ValueError, KeyError) as e:
             out(f"error: cannot load model: {e}\n")
             return 1
@@ -165,6 +172,8 @@ def main(argv: Optional[List[str]] = None, read: Callable[[str], str] = input, o
     engine = InferenceEngine(runtime, tokenizer, gen, device)
     repl = Repl(session, engine, config, out, config.ui.stream, config.ui.show_metrics)
     repl.tokenizer_path = a.tokenizer
+    repl.template_choice = a.chat_template or "auto"
+    repl.apply_chat_template(detected)
     if a.prompt is not None:
         repl.handle_line(a.prompt)
         if a.save_history:

@@ -97,6 +97,26 @@ class SessionHistory:
         return (m for m in self._messages if m.is_assistant())
 
 
+CHAT_TEMPLATES = ("plain", "llama3", "chatml", "llama2")
+# tokens that end an assistant turn in the template's family (looked up in the tokenizer's added tokens)
+TURN_END_TOKENS = {"plain": (), "llama3": ("<|eot_id|>", "<|end_of_text|>"), "chatml": ("<|im_end|>", "<|endoftext|>"), "llama2": ("</s>",)}
+
+
+def detect_chat_template(tokenizer=None, metadata: Optional[dict] = None) -> str:
+    """Names the chat layout a model was tuned on from what it carries: the ``tokenizer.chat_template`` text of a GGUF
+    file or the marker tokens in the tokenizer's vocabulary.  ``plain`` (``User:`` / ``Assistant:`` lines, the reference's
+    only layout) when nothing tells."""
+    text = str((metadata or {}).get("tokenizer.chat_template", ""))
+    known = set(getattr(tokenizer, "added", None) or ())
+    if "<|start_header_id|>" in text or "<|start_header_id|>" in known:
+        return "llama3"
+    if "<|im_start|>" in text or "<|im_start|>" in known:
+        return "chatml"
+    if "[INST]" in text:
+        return "llama2"
+    return "plain"
+
+
 class SessionManager:
     def __init__(self, generation_config: Optional[GenerationConfig] = None, backend_name: str = "cpu", model_name: str = "none",
                  max_history: int = 1000):
@@ -107,6 +127,12 @@ class SessionManager:
         self._system: Optional[str] = None
         self._auto_save: Optional[str] = None
         self.tokens_generated = 0
+        self.chat_template = "plain"
+
+    def set_chat_template(self, name: str) -> None:
+        if name not in CHAT_TEMPLATES:
+            raise ValueError(f"chat template '{name}' is not one of {CHAT_TEMPLATES}")
+        self.chat_template = name
 
     def with_auto_save(self, path: str) -> "SessionManager":
         self._auto_save = path
@@ -179,10 +205,36 @@ class SessionManager:
     def describe_config(self) -> str:
         g = self._gen
         return (f"model: {self._model}\nbackend: {self._backend}\nmax_tokens: {g.max_tokens}\ntemperature: {g.temperature}\n"
-                f"top_p: {g.top_p}\ntop_k: {g.top_k}\nsystem prompt: {self._system or '(none)'}")
+                f"top_p: {g.top_p}\ntop_k: {g.top_k}\nchat template: {self.chat_template}\nsystem prompt: {self._system or '(none)'}")
+
+    def _turns(self):
+        """``(role, text)`` of the system prompt and the history, in order."""
+        out = [("system", self._system)] if self._system else []
+        for m in self.history.messages():
+            out.append(("system" if m.is_system() else "user" if m.is_user() else "assistant", m.content))
+        return out
 
     def build_prompt(self) -> str:
-        """Plain chat template: system prompt, then ``User:`` / ``Assistant:`` turns, ending with an open assistant turn."""
+        """The conversation as one prompt that ends with an open assistant turn.  ``plain``: system prompt, then ``User:`` /
+        ``Assistant:`` lines; ``llama3`` / ``chatml`` / ``llama2``: the marker layouts those model families were tuned on
+        (the start-of-text marker is the tokenizer's business, not part of the text)."""
+        if self.chat_template == "llama3":
+            return "".join(f"<|start_header_id|>{r}<|end_header_id|>\n\n{t}<|eot_id|>" for r, t in self._turns()) + \
+                "<|start_header_id|>assistant<|end_header_id|>\n\n"
+        if self.chat_template == "chatml":
+            return "".join(f"<|im_start|>{r}\n{t}<|im_end|>\n" for r, t in self._turns()) + "<|im_start|>assistant\n"
+        if self.chat_template == "llama2":
+            out, system = [], None
+            for r, t in self._turns():
+                if r == "system":
+                    system = t if system is None else system + "\n" + t
+                elif r == "user":
+                    body = f"<<SYS>>\n{system}\n<</SYS>>\n\n{t}" if system is not None else t
+                    system = None
+                    out.append(f"[INST] {body} [/INST]")
+                else:
+                    out.append(f" {t} </s><s>")
+            return "".join(out)
         parts = [self._system + "\n"] if self._system else []
         for m in self.history.messages():
             if m.is_system():

@@ -60,6 +60,8 @@ class GGUFTokenizer(Tokenizer):
             self.index.setdefault(t, i)
         self.bos_id, self.eos_id, self.unk_id, self.add_space_prefix = bos_id, eos_id, unk_id, add_space_prefix
         self.byte_ids = {b: self.index[f"<0x{b:02X}>"] for b in range(256) if f"<0x{b:02X}>" in self.index}
+        # control tokens (<s>, </s>, chat markers) written out in a prompt stand for their ids
+        self.added = {t: i for i, t in enumerate(self.tokens) if self.types[i] == 3 and len(t) > 2 and self.index.get(t) == i}
 
     @classmethod
     def from_gguf(cls, gguf_file) -> "GGUFTokenizer":
@@ -76,6 +78,19 @@ class GGUFTokenizer(Tokenizer):
         return len(self.tokens)
 
     def encode(self, text, add_bos=True):
+        hits = [t for t in self.added if t in text] if self.added else []
+        if hits:
+            import re
+            ids = [self.bos_id] if add_bos and self.bos_id is not None else []
+            for chunk in re.split("(" + "|".join(re.escape(t) for t in sorted(hits, key=len, reverse=True)) + ")", text):
+                if chunk in self.added:
+                    ids.append(self.added[chunk])
+                elif chunk:
+                    ids += self._encode_plain(chunk, False)
+            return ids
+        return self._encode_plain(text, add_bos)
+
+    def _encode_plain(self, text, add_bos):
         if self.add_space_prefix and text and not text.startswith(" "):
             text = " " + text
         pieces = list(text.replace(" ", self.SPACE))

@@ -341,3 +341,59 @@ def test_tokenizer_json_byte_level_bpe_matches_the_tokenizers_library(tmp_path):
     json.dump({"model": {"type": "BPE", "vocab": {}, "merges": []}, "pre_tokenizer": {"type": "Metaspace"}}, open(sp / "tokenizer.json", "w"))
     with pytest.raises(ValueError, match="not byte-level"):
         load_tokenizer(str(sp))
+
+
+def test_chat_templates_detection_and_turn_end_tokens():
+    """Prompt layouts of the model families, chosen from what the model's tokenizer carries; replies end at the family's
+    turn-end marker as well as at the tokenizer's eos."""
+    from rustorch_b200.cli.engine import InferenceEngine
+    from rustorch_b200.cli.session import TURN_END_TOKENS, GenerationConfig, SessionManager, detect_chat_template
+    from rustorch_b200.cli.tokenizer import BPETokenizer, GGUFTokenizer
+    s = SessionManager()
+    s.set_system_prompt("Be brief.")
+    s.add_user_message("Hi")
+    s.add_assistant_message("Hello!")
+    s.add_user_message("Bye")
+    assert s.build_prompt() == "Be brief.\nUser: Hi\nAssistant: Hello!\nUser: Bye\nAssistant:"
+    s.set_chat_template("llama3")
+    assert s.build_prompt() == ("<|start_header_id|>system<|end_header_id|>\n\nBe brief.<|eot_id|><|start_header_id|>user<|end_header_id|>\n\nHi<|eot_id|>"
+                                "<|start_header_id|>assistant<|end_header_id|>\n\nHello!<|eot_id|><|start_header_id|>user<|end_header_id|>\n\nBye<|eot_id|>"
+                                "<|start_header_id|>assistant<|end_header_id|>\n\n")
+    s.set_chat_template("chatml")
+    assert s.build_prompt() == ("<|im_start|>system\nBe brief.<|im_end|>\n<|im_start|>user\nHi<|im_end|>\n<|im_start|>assistant\nHello!<|im_end|>\n"
+                                "<|im_start|>user\nBye<|im_end|>\n<|im_start|>assistant\n")
+    s.set_chat_template("llama2")
+    assert s.build_prompt() == "[INST] <<SYS>>\nBe brief.\n<</SYS>>\n\nHi [/INST] Hello! </s><s>[INST] Bye [/INST]"
+    with pytest.raises(ValueError, match="not one of"):
+        s.set_chat_template("vicuna")
+    alphabet = {c: i for i, c in enumerate("abcdefgh ĠĊ")}
+    l3 = BPETokenizer(alphabet, [], None, None, {"<|start_header_id|>": 20, "<|end_header_id|>": 21, "<|eot_id|>": 22})
+    cm = BPETokenizer(alphabet, [], None, None, {"<|im_start|>": 20, "<|im_end|>": 21})
+    assert detect_chat_template(l3) == "llama3" and detect_chat_template(cm) == "chatml" and detect_chat_template(BPETokenizer(alphabet, [])) == "plain"
+    assert detect_chat_template(None, {"tokenizer.chat_template": "{% for m in messages %}[INST] {{ m }} [/INST]{% endfor %}"}) == "llama2"
+    assert detect_chat_template(None, {"tokenizer.chat_template": "...<|im_start|>..."}) == "chatml"
+    # control tokens written out in a prompt become their ids in the SentencePiece-style GGUF tokenizer too
+    gt = GGUFTokenizer(["<unk>", "<s>", "</s>", "▁a", "▁b", "a", "b", "▁"], [0, 0, 0, -1, -2, -3, -4, -5], [2, 3, 3, 1, 1, 1, 1, 1])
+    assert gt.encode("a </s><s>b", add_bos=True) == [1, 3, 7, 2, 1, 4] and gt.encode("a b", add_bos=False) == [3, 4]
+
+    class OneShot:                                   # a runtime that always proposes the same next token
+        class cfg:
+            vocab_size, context_length = 32, 64
+
+        def __init__(self, tok):
+            self.tok = tok
+
+        def new_cache(self, b, n):
+            return None
+
+        def prefill(self, prompts, cache):
+            out = torch.full((1, 32), -1e4)
+            out[0, self.tok] = 0.0
+            return out
+        decode_step = prefill
+    eng = InferenceEngine(OneShot(22), l3, GenerationConfig(max_tokens=6, temperature=0.0), "cpu")
+    eng.generate("ab")
+    assert eng.last_token_count == 6                 # nothing says that 22 ends a turn
+    eng.set_stop_tokens(TURN_END_TOKENS["llama3"])
+    eng.generate("ab")
+    assert eng.stop_ids == {22} and eng.last_token_count == 0
