@@ -137,6 +137,17 @@ def hf_rope_settings(config: dict) -> Tuple[float, Optional[dict]]:
     return float(config.get("rope_theta", 10000.0)), sc
 
 
+def hf_attention_window(config: dict) -> Optional[int]:
+    """Width of the sliding attention window that a Hugging Face config switches on, or None.  Mistral-style configs
+    switch it on by giving ``sliding_window`` a value; Qwen2-style ones carry a value but use it only with
+    ``use_sliding_window``."""
+    width = config.get("sliding_window")
+    if not width:
+        return None
+    default_on = str(config.get("model_type", "")).lower() not in ("qwen2", "qwen2_moe", "qwen3")
+    return int(width) if config.get("use_sliding_window", default_on) else None
+
+
 class HuggingFaceCheckpoint:
     """A Hugging Face model directory: ``config.json`` plus ``model.safetensors`` or the shards named by
     ``model.safetensors.index.json``; tensors are fetched one at a time from whichever shard holds them."""

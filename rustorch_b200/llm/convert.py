@@ -13,7 +13,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from ..formats import gguf
-from ..formats.safetensors import HuggingFaceCheckpoint, hf_rope_settings
+from ..formats.safetensors import HuggingFaceCheckpoint, hf_attention_window, hf_rope_settings
 
 _LAYER = {"self_attn.q_proj": "attn_q", "self_attn.k_proj": "attn_k", "self_attn.v_proj": "attn_v", "self_attn.o_proj": "attn_output",
           "mlp.gate_proj": "ffn_gate", "mlp.up_proj": "ffn_up", "mlp.down_proj": "ffn_down", "input_layernorm": "attn_norm",
@@ -66,8 +66,10 @@ def hf_to_gguf(directory: str, path: str, ggml_type: gguf.GGMLType = gguf.GGMLTy
                   f"{a}.context_length": int(c.get("max_position_embeddings", 2048)), f"{a}.vocab_size": int(c["vocab_size"])}
         except KeyError as e:
             raise ValueError(f"{directory}: config.json lacks {e.args[0]!r}") from None
-        if c.get("use_sliding_window"):
-            raise ValueError(f"{directory}: sliding-window attention has no counterpart in the written file")
+        window = hf_attention_window(c)
+        if window is not None:                             # readers of the file attend over the whole context: one window at most
+            md[f"{a}.context_length"] = min(int(md[f"{a}.context_length"]), window)
+            md[f"{a}.attention.sliding_window"] = window
         rope_freqs = None
         if scaling:
             kind = str(scaling.get("rope_type", scaling.get("type", ""))).lower()

@@ -160,6 +160,9 @@ class LlamaRuntime:
                 what = (f"missing {absent[:4]}{'...' if len(absent) > 4 else ''}" if absent else "") + \
                        (("; " if absent else "") + f"tensors this runtime does not execute: {extra[:6]}" if extra else "")
                 raise ValueError(f"{path}: architecture '{mc['architecture']}' is not a Llama-style decoder this runtime runs ({what})")
+            window = g.metadata.get(f"{mc['architecture']}.attention.sliding_window")
+            if window and 0 < int(window) < cfg.context_length:
+                cfg.context_length = int(window)                  # full attention equals windowed attention up to one window
             scaling = g.metadata.get(f"{mc['architecture']}.rope.scaling.type")
             if "rope_freqs.weight" in g.tensors:
                 # per-frequency divisors (how Llama 3.1 files carry their long-context scaling)
@@ -203,7 +206,7 @@ class LlamaRuntime:
         is quantised to ``ggml_type`` (Q8_0 or Q4_0) as it is read, one tensor at a time, so a bf16 checkpoint never
         sits in memory whole.  These checkpoints rotate the two halves of a head (``rotate_half``), not adjacent pairs
         as GGUF files do, hence ``rope_interleaved=False``."""
-        from ..formats.safetensors import HuggingFaceCheckpoint, hf_rope_settings
+        from ..formats.safetensors import HuggingFaceCheckpoint, hf_attention_window, hf_rope_settings
         with HuggingFaceCheckpoint(directory) as ck:
             c = ck.config
             theta, scaling = hf_rope_settings(c)
@@ -233,8 +236,11 @@ class LlamaRuntime:
             extra = sorted({n.split(".", 3)[-1] for n in ck.keys() if n.startswith("model.layers.") and n.endswith(".bias")
                             and not (biased and n.split(".", 3)[-1] in qkv_b)}
                            | {n.split(".", 3)[-1] for n in ck.keys() if ".experts." in n or "block_sparse_moe" in n})
-            if c.get("use_sliding_window"):
-                raise ValueError(f"{directory}: sliding-window attention is not implemented by this runtime")
+            window = hf_attention_window(c)
+            if window is not None and window < cfg.context_length:
+                # attention here always sees the whole cache; within one window's length that is what the model computes,
+                # so the context is limited to the window instead of attending further back than the model was trained to
+                cfg.context_length = window
             if absent or extra:
                 what = (f"missing {absent[:4]}{'...' if len(absent) > 4 else ''}" if absent else "") + \
                        (("; " if absent else "") + f"tensors this runtime does not execute: {extra[:6]}" if extra else "")

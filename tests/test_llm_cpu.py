@@ -379,3 +379,30 @@ def test_from_gguf_rope_frequency_scaling_kinds(tmp_path):
         llm.LlamaRuntime.from_gguf(p, device="cpu")
     gguf.write_gguf(p, {**md, "llama.rope.scaling.type": "linear", "llama.rope.scaling.factor": 2.0}, tensors)
     assert llm.LlamaRuntime.from_gguf(p, device="cpu").cfg.rope_scaling == {"rope_type": "linear", "factor": 2.0}
+
+
+def test_sliding_window_checkpoints_limit_the_context(tmp_path):
+    """A Mistral-style config switches a sliding attention window on by naming its width: the runtime (which attends over
+    its whole cache) takes the window as its context length, from the directory and from the converted GGUF file, and
+    agrees with ``transformers`` inside it.  Qwen2-style configs carry a width that is off unless ``use_sliding_window``."""
+    tf = pytest.importorskip("transformers")
+    from rustorch_b200.formats.safetensors import hf_attention_window
+    assert hf_attention_window({"model_type": "mistral", "sliding_window": 4096}) == 4096
+    assert hf_attention_window({"model_type": "mistral", "sliding_window": None}) is None
+    assert hf_attention_window({"model_type": "qwen2", "sliding_window": 4096}) is None
+    assert hf_attention_window({"model_type": "qwen2", "sliding_window": 4096, "use_sliding_window": True}) == 4096
+    torch.manual_seed(0)
+    hc = tf.MistralConfig(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                          max_position_embeddings=128, sliding_window=24, tie_word_embeddings=False)
+    ref = tf.MistralForCausalLM(hc).eval()
+    d = str(tmp_path / "mistral")
+    ref.save_pretrained(d, safe_serialization=True)
+    out = str(tmp_path / "mistral.gguf")
+    llm.hf_to_gguf(d, out, gguf.GGMLType.Q8_0)
+    prompt = torch.randint(0, 96, (1, 20), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = ref(prompt).logits[:, -1]
+    for rt in (llm.LlamaRuntime.from_hf(d, device="cpu"), llm.LlamaRuntime.from_gguf(out, device="cpu")):
+        assert rt.cfg.context_length == 24
+        got = rt.prefill(prompt, rt.new_cache(1, 24))
+        assert float((want - got).abs().max()) < 0.03 * float(want.abs().max())
