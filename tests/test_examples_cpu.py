@@ -63,3 +63,21 @@ def test_quickstart_notebook_cells_run(monkeypatch):
                 exec(compile(src, "<notebook cell>", "exec"), ns)
     text = out.getvalue()
     assert "dy/dx = [7.0, 9.0]" in text and "Total params" in text and "epochs" in text
+
+
+def test_names_imported_in_the_guides_exist():
+    """Every ``import`` line inside a Python block of the guides under ``docs/`` and of the README resolves."""
+    import glob
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lines = []
+    for path in glob.glob(os.path.join(root, "docs", "*.md")) + [os.path.join(root, "README.md")]:
+        text = open(path, encoding="utf-8").read()
+        for block in re.findall(r"```python\n(.*?)```", text, flags=re.S):
+            lines += [(path, ln.strip()) for ln in block.splitlines() if re.match(r"\s*(from\s+(rustorch|rustorch_b200)[\w.]*\s+import|import\s+(rustorch|rustorch_b200))", ln)]
+    assert len(lines) >= 6
+    for path, ln in lines:
+        try:
+            exec(ln, {})
+        except Exception as e:  # noqa: BLE001
+            raise AssertionError(f"{os.path.basename(path)}: `{ln}` fails: {e}") from None
