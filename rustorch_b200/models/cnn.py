@@ -90,6 +90,31 @@ class ResNet(nn.Module):
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         return self.fc(torch.flatten(self.avgpool(x), 1))
 
+    @classmethod
+    def from_torchvision(cls, source, **kw) -> "ResNet":
+        """A model with the weights of a ``torchvision`` ResNet-18 / 34 / 50: ``source`` is that model, its ``state_dict()``
+        or the path of a saved one (``.pth``).  Parameter and buffer names are torchvision's, so the tensors load as they
+        are (stride on the 3x3 convolution of the bottleneck, as in torchvision); depth and class count are read from the
+        tensors."""
+        sd = source.state_dict() if isinstance(source, nn.Module) else source
+        if isinstance(sd, (str, bytes)) or hasattr(sd, "__fspath__"):
+            sd = torch.load(sd, map_location="cpu", weights_only=True)
+        sd = sd.get("state_dict", sd) if isinstance(sd, dict) else sd
+        sd = {k[7:] if k.startswith("module.") else k: v for k, v in sd.items()}
+        try:
+            depth = [1 + max(int(k.split(".")[1]) for k in sd if k.startswith(f"layer{i}.")) for i in (1, 2, 3, 4)]
+            classes, width = sd["fc.weight"].shape
+            in_ch = sd["conv1.weight"].shape[1]
+        except (KeyError, ValueError):
+            raise ValueError("not a torchvision ResNet state dict (conv1 / layer1..4 / fc expected)") from None
+        bottleneck = any(k.endswith(".conv3.weight") for k in sd)
+        c1, c2 = sd["layer1.0.conv1.weight"].shape, sd["layer1.0.conv2.weight"].shape
+        if width != 512 * (4 if bottleneck else 1) or sd["conv1.weight"].shape[0] != 64 or c1[0] != 64 or c2[0] != c2[1]:
+            raise ValueError(f"stage-1 convolutions {tuple(c1)} / {tuple(c2)}, fc input width {width}: wide and grouped variants are outside this model")
+        model = cls(Bottleneck if bottleneck else BasicBlock, depth, int(classes), in_channels=int(in_ch), **kw)
+        model.load_state_dict(sd, strict=True)
+        return model
+
     @staticmethod
     def resnet18(num_classes: int = 1000, **kw) -> "ResNet":
         return ResNet(BasicBlock, [2, 2, 2, 2], num_classes, **kw)

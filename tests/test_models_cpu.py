@@ -275,3 +275,33 @@ def test_metrics_against_sklearn():
     p, r, _f, _ = sk.precision_recall_fscore_support(y.numpy(), pred.numpy(), average="macro", zero_division=0)
     assert m.accuracy == pytest.approx(sk.accuracy_score(y.numpy(), pred.numpy())) and m.precision == pytest.approx(p) and m.recall == pytest.approx(r)
     assert m.f1_score == pytest.approx(2 * p * r / (p + r))           # harmonic mean of the macro averages (src/models/mod.rs keeps one f1 field)
+
+
+def test_resnet_takes_torchvision_weights(tmp_path):
+    """``ResNet.from_torchvision``: same tensors, same logits as the torchvision model, in eval and in training mode
+    (batch statistics), for basic-block and bottleneck depths; from the module, the state dict or a saved file."""
+    tv = pytest.importorskip("torchvision")
+    from rustorch_b200.models.cnn import ResNet
+    x = torch.randn(2, 3, 64, 64, generator=torch.Generator().manual_seed(0))
+    for name in ("resnet18", "resnet50"):
+        torch.manual_seed(0)
+        ref = getattr(tv.models, name)(num_classes=10)
+        with torch.no_grad():
+            for m in ref.modules():
+                if isinstance(m, torch.nn.BatchNorm2d):
+                    m.running_mean.normal_(0, 0.1)
+                    m.running_var.uniform_(0.5, 1.5)
+                    m.weight.uniform_(0.5, 1.5)
+        mine = ResNet.from_torchvision(ref)
+        assert sum(p.numel() for p in mine.parameters()) == sum(p.numel() for p in ref.parameters())
+        with torch.no_grad():
+            assert torch.allclose(ref.eval()(x), mine.eval()(x), atol=1e-5)
+            assert torch.allclose(ref.train()(x), mine.train()(x), atol=1e-5)
+    path = str(tmp_path / "r18.pth")
+    ref18 = tv.models.resnet18(num_classes=7)
+    torch.save({"state_dict": {"module." + k: v for k, v in ref18.state_dict().items()}}, path)     # a DataParallel-style checkpoint
+    assert ResNet.from_torchvision(path).fc.out_features == 7
+    with pytest.raises(ValueError, match="wide and grouped"):
+        ResNet.from_torchvision(tv.models.wide_resnet50_2(num_classes=3).state_dict())
+    with pytest.raises(ValueError, match="not a torchvision ResNet"):
+        ResNet.from_torchvision({"a": torch.zeros(1)})
