@@ -131,10 +131,10 @@ def check_status_to_error(code: int, message: Optional[str] = None) -> Optional[
     if code == 0:
         return None
     if 101 <= code <= 105:
-        return KernelTimeout(message or "a bounded device-side wait ran out", code=code)
+        return KernelTimeout(message or "a bounded device-side wait ran out", code, code=code)
     if code == 201:
-        return IndexOutOfBounds(message or "index or alignment check failed in a kernel", code=code)
-    return KernelError(message or "kernel reported an error", code=code)
+        return IndexOutOfBounds(message or "index or alignment check failed in a kernel", code, code=code)
+    return KernelError(message or "kernel reported an error", code, code=code)
 
 
 __all__ = [n for n, v in list(globals().items()) if isinstance(v, type) and issubclass(v, RusTorchError)] + ["RusTorchResult", "check_status_to_error"]
