@@ -33,31 +33,37 @@ class ModelMetadata:
 
 
 class _GPTAdapter:
-    """Gives the training-time ``GPT`` module the prefill / decode interface (no KV cache: re-runs the window)."""
+    """Gives the training-time ``GPT`` module the prefill / decode interface.  Decode steps run against per-block key /
+    value tensors (``GPT.forward_cached``); when the learned positions run out, the window slides: the newest half of
+    the tokens is prefilled again at positions 0 ... and decoding goes on from there."""
 
     def __init__(self, model, device):
         self.model, self.device = model.to(device).eval(), torch.device(device)
         self.tokens: Optional[torch.Tensor] = None
+        self.kv = None
 
     def new_cache(self, batch: int, max_len: int):
-        self.tokens = None
+        self.tokens, self.kv = None, None
         return self
 
     @torch.no_grad()
     def prefill(self, prompts: torch.Tensor, cache) -> torch.Tensor:
-        self.tokens = prompts.to(self.device)
-        return self._last_logits()
+        ctx = self.model.cfg.n_positions
+        self.tokens = prompts.to(self.device)[:, -ctx:]
+        logits, self.kv = self.model.forward_cached(self.tokens)
+        return logits[:, -1].float()
 
     @torch.no_grad()
     def decode_step(self, tokens: torch.Tensor, cache) -> torch.Tensor:
-        self.tokens = torch.cat([self.tokens, tokens.view(-1, 1).to(self.device)], 1)
-        return self._last_logits()
-
-    def _last_logits(self) -> torch.Tensor:
+        new = tokens.view(-1, 1).to(self.device)
+        self.tokens = torch.cat([self.tokens, new], 1)
         ctx = self.model.cfg.n_positions
-        out = self.model.forward_reference(self.tokens[:, -ctx:]) if hasattr(self.model, "forward_reference") else self.model(self.tokens[:, -ctx:])
-        logits = out[0] if isinstance(out, tuple) else out
-        return logits[:, -1, : self.model.cfg.vocab_size].float()
+        if self.tokens.shape[1] > ctx:                   # positions are learned and absolute: re-base the window
+            self.tokens = self.tokens[:, -(ctx // 2):]
+            logits, self.kv = self.model.forward_cached(self.tokens)
+        else:
+            logits, self.kv = self.model.forward_cached(new, self.kv)
+        return logits[:, -1].float()
 
 
 class ModelLoader:

@@ -257,6 +257,38 @@ class GPT(nn.Module):
         return F.cross_entropy(logits.float().view(-1, c.vocab_size), targets.reshape(-1))
 
     @torch.no_grad()
+    def forward_cached(self, idx: torch.Tensor, cache: Optional[list] = None):
+        """Incremental inference: ``idx [B, t]`` are the tokens after the ones that ``cache`` already holds (``None`` to
+        start).  Returns ``(logits [B, t, vocab], cache)``; the cache is one ``(k, v)`` pair ``[B, H, T, D]`` per block,
+        so a decode step costs one row of attention per block instead of the whole window again."""
+        c = self.cfg
+        B, t = idx.shape
+        H, D = c.n_head, c.n_embd // c.n_head
+        eps = c.layer_norm_eps
+        past = 0 if not cache else cache[0][0].shape[2]
+        if past + t > c.n_positions:
+            raise ValueError(f"{past} cached + {t} new tokens exceed the {c.n_positions} learned positions")
+        x = self.wte[idx] + self.wpe[past: past + t]
+        out_cache = []
+        for li, b in enumerate(self.blocks):
+            h = F.layer_norm(x, (c.n_embd,), b.ln1_w, b.ln1_b, eps)
+            qkv = F.linear(h, b.w_qkv, b.b_qkv).view(B, t, 3, H, D)
+            q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+            if cache:
+                k, v = torch.cat([cache[li][0], k], 2), torch.cat([cache[li][1], v], 2)
+            out_cache.append((k, v))
+            if past == 0:
+                att = F.scaled_dot_product_attention(q, k, v, is_causal=t > 1)
+            else:                                        # new row i sees the cached tokens and new rows 0 .. i
+                mask = torch.ones(t, past + t, dtype=torch.bool, device=idx.device).tril(past)
+                att = F.scaled_dot_product_attention(q, k, v, attn_mask=mask)
+            x = x + F.linear(att.transpose(1, 2).reshape(B, t, c.n_embd), b.w_proj, b.b_proj)
+            h = F.layer_norm(x, (c.n_embd,), b.ln2_w, b.ln2_b, eps)
+            x = x + F.linear(F.gelu(F.linear(h, b.w_fc, b.b_fc), approximate="tanh"), b.w_fc2, b.b_fc2)
+        x = F.layer_norm(x, (c.n_embd,), self.lnf_w, self.lnf_b, eps)
+        return F.linear(x, self.lm_head)[..., :c.vocab_size], out_cache
+
+    @torch.no_grad()
     def generate(self, idx: torch.Tensor, max_new_tokens: int, temperature: float = 1.0,
                  top_k: Optional[int] = None) -> torch.Tensor:
         for _ in range(max_new_tokens):

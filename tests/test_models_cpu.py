@@ -305,3 +305,35 @@ def test_resnet_takes_torchvision_weights(tmp_path):
         ResNet.from_torchvision(tv.models.wide_resnet50_2(num_classes=3).state_dict())
     with pytest.raises(ValueError, match="not a torchvision ResNet"):
         ResNet.from_torchvision({"a": torch.zeros(1)})
+
+
+def test_gpt_forward_cached_equals_the_full_forward():
+    """Prefill + decode steps (one token, then three at once) against the key / value cache reproduce the logits of the
+    whole-sequence forward; the CLI adapter built on it slides its window when the learned positions run out."""
+    from rustorch_b200.cli.engine import _GPTAdapter
+    from rustorch_b200.models.gpt import GPT, GPTConfig
+    g = GPT(GPTConfig(vocab_size=100, n_positions=16, n_embd=64, n_layer=2, n_head=4, dropout=0.0, tie_weights=True), seed=0).eval()
+    with torch.no_grad():
+        for b in g.blocks:
+            b.b_qkv.normal_(0, 0.1)
+    ids = torch.randint(0, 100, (2, 12), generator=torch.Generator().manual_seed(0))
+    with torch.no_grad():
+        want = g.forward_reference(ids)
+        l0, kv = g.forward_cached(ids[:, :8])
+        l1, kv = g.forward_cached(ids[:, 8:9], kv)
+        l2, kv = g.forward_cached(ids[:, 9:12], kv)
+    assert torch.allclose(torch.cat([l0, l1, l2], 1), want, atol=1e-5) and kv[0][0].shape == (2, 4, 12, 16)
+    with pytest.raises(ValueError, match="learned positions"):
+        g.forward_cached(ids[:, :6], kv)
+    ad = _GPTAdapter(g, "cpu")
+    logits = ad.prefill(ids[:1], ad.new_cache(1, 64))
+    assert torch.allclose(logits, want[:1, -1], atol=1e-5)
+    seq = ids[:1]
+    for step in range(8):                                # crosses the 16 learned positions at the fifth step
+        nxt = logits.argmax(-1)
+        seq = torch.cat([seq, nxt[:, None]], 1)
+        logits = ad.decode_step(nxt, ad)
+        window = seq if seq.shape[1] <= 16 else ad.tokens
+        with torch.no_grad():
+            assert torch.allclose(logits, g.forward_reference(window)[:, -1], atol=1e-5), step
+    assert ad.tokens.shape[1] <= 16 and torch.equal(ad.tokens, seq[:, -ad.tokens.shape[1]:])
