@@ -19,13 +19,14 @@ class CommandKind(Enum):
     STATS = "stats"
     SYSTEM = "system"
     CONFIG = "config"
+    TEMPLATE = "template"                # an addition: the reference has one prompt layout
     UNKNOWN = "unknown"
 
 
 _ALIASES = {"exit": CommandKind.EXIT, "quit": CommandKind.EXIT, "q": CommandKind.EXIT, "help": CommandKind.HELP, "h": CommandKind.HELP,
             "?": CommandKind.HELP, "clear": CommandKind.CLEAR, "cls": CommandKind.CLEAR, "save": CommandKind.SAVE, "load": CommandKind.LOAD,
             "model": CommandKind.MODEL, "backend": CommandKind.BACKEND, "stats": CommandKind.STATS, "system": CommandKind.SYSTEM,
-            "config": CommandKind.CONFIG}
+            "config": CommandKind.CONFIG, "template": CommandKind.TEMPLATE}
 _NEEDS_ARG = {CommandKind.LOAD: "/load <path>", CommandKind.MODEL: "/model <path>", CommandKind.BACKEND: "/backend <name>",
               CommandKind.SYSTEM: "/system <prompt>"}
 
@@ -39,7 +40,8 @@ HELP_TEXT = """Commands:
   /backend <name>      switch backend (cpu, cuda)
   /stats               session and performance statistics
   /system <prompt>     set the system prompt
-  /config              show the current configuration"""
+  /config              show the current configuration
+  /template [name]     show or set the chat layout (auto, plain, llama3, chatml, llama2)"""
 
 
 @dataclass

@@ -23,9 +23,12 @@ class Repl:
         self.errors = 0                              # generations that failed in this session
         self.tokenizer_path: Optional[str] = None
         self.template_choice = "auto"                # "auto": follow what each loaded model's tokenizer points to
+        self.detected_template = "plain"             # what the loaded model's tokenizer points to
 
-    def apply_chat_template(self, detected: str = "plain") -> None:
-        name = detected if self.template_choice in (None, "auto") else self.template_choice
+    def apply_chat_template(self, detected: Optional[str] = None) -> None:
+        if detected is not None:
+            self.detected_template = detected
+        name = self.detected_template if self.template_choice in (None, "auto") else self.template_choice
         self.session.set_chat_template(name)
         self.engine.set_stop_tokens(TURN_END_TOKENS[name])
 
@@ -102,6 +105,14 @@ class Repl:
             self.out("System prompt set.\n")
         elif k is CommandKind.CONFIG:
             self.out(self.session.describe_config() + "\n")
+        elif k is CommandKind.TEMPLATE:
+            if cmd.arg:
+                choice = cmd.arg.lower()
+                if choice != "auto":
+                    self.session.set_chat_template(choice)          # refuses unknown names before anything changes
+                self.template_choice = choice
+                self.apply_chat_template()
+            self.out(f"chat template: {self.session.chat_template}" + (" (auto)" if self.template_choice in (None, "auto") else "") + "\n")
         else:
             self.out(f"Unknown command '/{cmd.arg}'. Type /help.\n")
 

@@ -397,3 +397,22 @@ def test_chat_templates_detection_and_turn_end_tokens():
     eng.set_stop_tokens(TURN_END_TOKENS["llama3"])
     eng.generate("ab")
     assert eng.stop_ids == {22} and eng.last_token_count == 0
+
+
+def test_template_command_switches_the_prompt_layout():
+    from rustorch_b200.cli.engine import InferenceEngine
+    from rustorch_b200.cli.repl import Repl
+    from rustorch_b200.cli.session import SessionManager
+    out = []
+    repl = Repl(SessionManager(), InferenceEngine(), out=out.append, stream=False)
+    repl.apply_chat_template("chatml")                       # what a loaded model pointed to
+    repl.handle_line("/template")
+    assert out[-1] == "chat template: chatml (auto)\n"
+    repl.handle_line("/template llama3")
+    assert out[-1] == "chat template: llama3\n" and repl.session.build_prompt().endswith("<|start_header_id|>assistant<|end_header_id|>\n\n")
+    repl.handle_line("/template vicuna")
+    assert out[-1].startswith("error:") and repl.session.chat_template == "llama3"
+    repl.handle_line("/template auto")
+    assert out[-1] == "chat template: chatml (auto)\n"
+    repl.handle_line("/help")
+    assert "/template" in out[-1]
