@@ -29,7 +29,7 @@ def test_example_runs(name):
                                   "batchnorm_demo", "adamw_scheduler_demo", "gradient_flow_demo", "neural_network_demo",
                                   "complete_training_demo", "rnn_sequence_demo", "data_loading_demo", "vision_pipeline_demo",
                                   "visualization_demo", "distributions_demo", "quantization_sparsity_demo", "model_hub_demo",
-                                  "validation_debug_demo", "llm_decode_demo", "finetune_export_serve_demo", "gpu_kernel_demo"])
+                                  "validation_debug_demo", "llm_decode_demo", "finetune_export_serve_demo", "chat_prompt_demo", "gpu_kernel_demo"])
 def test_example_runs_in_process(name, monkeypatch):
     """The single-process examples, run inside this interpreter (no second import of torch per program)."""
     if torch.cuda.is_available():
